@@ -1,0 +1,765 @@
+// bf16 GEMM for sm_100a: persistent, warp-specialised, TMA -> shared memory (128B swizzle)
+// -> tcgen05.mma (cta_group::1, M=128) -> TMEM accumulators (double buffered) -> epilogue.
+//
+//   C[M,N] = alpha * A . B + beta * C      (fp32 accumulate, C bf16 or fp32)
+//
+// Operand layouts (both given as row-major 2-D tensors):
+//   A K-major : A[M,K]      A MN-major: A[K,M]   (i.e. A^T is what is stored)
+//   B K-major : B[N,K]      B MN-major: B[K,N]
+// so that  x @ W^T (nn.Linear forward) = (A K-major, B K-major),
+//          dY @ W  (dgrad)             = (A K-major, B MN-major),
+//          dY^T @ X (wgrad)            = (A MN-major, B MN-major).
+//
+// Grouped (MoE) mode: rows of A / C are 128-row blocks that each belong to one expert
+// (`block_expert[blk]`, -1 = unused block); B is the stacked per-expert weight viewed as a
+// 2-D tensor with `b_rows_per_expert` rows per expert. No host synchronisation is needed:
+// the grid covers the static upper bound of blocks and unused blocks are skipped.
+//
+// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2..5 =
+// epilogue (one TMEM lane quarter each). All waits are bounded (see common.cuh).
+//
+// Replaces nn.Linear / cuBLAS and torch._grouped_mm in the reference
+// (src/prime_rl/trainer/models/layers/grouped_gemm.py:21-31, layers/moe.py:124-164).
+#include "common.cuh"
+#include "tma_host.cuh"
+#include <type_traits>
+
+namespace prb {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kGemmThreads = 192;
+
+struct GemmParams {
+  int M, N, K;
+  long long rows_total;  // rows of C (M, or num_experts * M when K-grouped)
+  void* C;
+  long long ldc;
+  int out_fp32;
+  float alpha, beta;
+  const int* block_expert;  // nullptr = dense
+  int b_rows_per_expert;
+  int* status;
+  const int* expert_offset;  // K-grouped mode
+  int num_experts;
+  // fused LM head (logprob / entropy) extras
+  int num_splits;
+  const int* labels;
+  const float* inv_temp;
+  float* part_m;
+  float* part_s;
+  float* part_t;
+  float* target_logit;
+  const float* grad_logprob;
+  const float* lse;
+};
+
+// Width in columns of one vocabulary split (the unit `end_item` indexes partials by).
+__device__ __forceinline__ int sched_split_width(const GemmParams& p, int bn) {
+  if (p.num_splits <= 0) return 1 << 30;
+  const int tiles_n = (p.N + bn - 1) / bn;
+  return ((tiles_n + p.num_splits - 1) / p.num_splits) * bn;
+}
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int A_BYTES = kBM * kBK * 2;
+  static constexpr int B_BYTES = BN * kBK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int ACC_COLS = 2 * BN;  // two accumulator buffers; 512 / 256 / 128 columns
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+// ---------------------------------------------------------------- tile schedulers
+// A scheduler enumerates the (m_blk, n_blk) tiles of one CTA; all three warp roles run the
+// same enumeration so that their pipelines stay in step.
+struct SchedDense {
+  int tile, num_tiles, tiles_m, tiles_n;
+  __device__ SchedDense(const GemmParams& p, int bn)
+      : tile(blockIdx.x - gridDim.x), tiles_m((p.M + kBM - 1) / kBM), tiles_n((p.N + bn - 1) / bn) {
+    num_tiles = tiles_m * tiles_n;
+  }
+  // Grouped raster: 8 consecutive M blocks share their B tiles in L2.
+  __device__ bool next(const GemmParams& p, int& m_blk, int& n_blk, int& brow, bool& last_of_item, int& kb0,
+                       int& nkb, long long& c_row0) {
+    kb0 = 0;
+    nkb = (p.K + kBK - 1) / kBK;
+    c_row0 = 0;
+    tile += gridDim.x;
+    if (tile >= num_tiles) return false;
+    constexpr int kGroup = 8;
+    const int per_group = kGroup * tiles_n;
+    const int g = tile / per_group;
+    const int first_m = g * kGroup;
+    const int gsize = min(tiles_m - first_m, kGroup);
+    const int r = tile - g * per_group;
+    m_blk = first_m + (r % gsize);
+    n_blk = r / gsize;
+    brow = 0;
+    last_of_item = true;
+    return true;
+  }
+};
+
+struct SchedGrouped : SchedDense {
+  __device__ SchedGrouped(const GemmParams& p, int bn) : SchedDense(p, bn) {}
+  __device__ bool next(const GemmParams& p, int& m_blk, int& n_blk, int& brow, bool& last_of_item, int& kb0,
+                       int& nkb, long long& c_row0) {
+    while (SchedDense::next(p, m_blk, n_blk, brow, last_of_item, kb0, nkb, c_row0)) {
+      const int e = p.block_expert[m_blk];
+      if (e >= 0) {
+        brow = e * p.b_rows_per_expert;
+        return true;
+      }
+    }
+    return false;
+  }
+};
+
+// Split order for the fused LM head: an item is (split, m_blk) and covers the N tiles
+// [split * per_split, (split + 1) * per_split); consecutive tiles of a CTA stay on one
+// M block so that per-row running statistics can live in registers. Items are numbered
+// split-major so that the CTAs in flight stream the same slice of the vocabulary.
+struct SchedSplit {
+  int item, j, tiles_m, tiles_n, per_split, num_items;
+  __device__ SchedSplit(const GemmParams& p, int bn)
+      : item(blockIdx.x - gridDim.x), j(0x7fffffff), tiles_m((p.M + kBM - 1) / kBM),
+        tiles_n((p.N + bn - 1) / bn) {
+    per_split = (tiles_n + p.num_splits - 1) / p.num_splits;
+    num_items = tiles_m * p.num_splits;
+  }
+  __device__ bool next(const GemmParams& p, int& m_blk, int& n_blk, int& brow, bool& last_of_item, int& kb0,
+                       int& nkb, long long& c_row0) {
+    kb0 = 0;
+    nkb = (p.K + kBK - 1) / kBK;
+    c_row0 = 0;
+    for (;;) {
+      if (j >= per_split) {
+        item += gridDim.x;
+        j = 0;
+        if (item >= num_items) return false;
+      }
+      const int split = item / tiles_m;
+      m_blk = item - split * tiles_m;
+      n_blk = split * per_split + j;
+      ++j;
+      if (n_blk < tiles_n) {
+        brow = 0;
+        last_of_item = (j >= per_split) || (n_blk + 1 >= tiles_n);
+        if (last_of_item) j = per_split;
+        return true;
+      }
+      j = per_split;  // rest of this split is empty
+    }
+  }
+};
+
+// K-grouped (per-expert weight gradient): tile = (expert, m_blk, n_blk); the reduction runs
+// over the expert's 128-aligned row range [expert_offset[e], expert_offset[e+1]) of the
+// MN-major operands and the result goes to rows [e*M, (e+1)*M) of the stacked output.
+// Experts without rows produce nkb = 0: producer and MMA skip the tile, the epilogue
+// writes zeros.
+struct SchedKGrouped {
+  int tile, num_tiles, tiles_m, tiles_n;
+  __device__ SchedKGrouped(const GemmParams& p, int bn)
+      : tile(blockIdx.x - gridDim.x), tiles_m((p.M + kBM - 1) / kBM), tiles_n((p.N + bn - 1) / bn) {
+    num_tiles = tiles_m * tiles_n * p.num_experts;
+  }
+  __device__ bool next(const GemmParams& p, int& m_blk, int& n_blk, int& brow, bool& last_of_item, int& kb0,
+                       int& nkb, long long& c_row0) {
+    tile += gridDim.x;
+    if (tile >= num_tiles) return false;
+    const int per_e = tiles_m * tiles_n;
+    const int e = tile / per_e;
+    const int r = tile - e * per_e;
+    m_blk = r % tiles_m;
+    n_blk = r / tiles_m;
+    brow = 0;
+    last_of_item = true;
+    const int r0 = p.expert_offset[e], r1 = p.expert_offset[e + 1];
+    kb0 = r0 / kBK;
+    nkb = (r1 - r0) / kBK;
+    c_row0 = static_cast<long long>(e) * p.M;
+    return true;
+  }
+};
+
+// ---------------------------------------------------------------- epilogues
+// An epilogue consumes 32-column chunks of one accumulator row per thread.
+struct EpiStore {
+  __device__ EpiStore(const GemmParams&) {}
+  __device__ void begin_item(const GemmParams&, long long) {}
+  __device__ void end_item(const GemmParams&, long long, int) {}
+  __device__ void chunk(const GemmParams& p, long long row, int col0, uint32_t (&v)[32]) {
+    if (row >= p.rows_total || col0 >= p.N) return;
+    const bool base_ok = (reinterpret_cast<uintptr_t>(p.C) & 15) == 0;
+    if (p.out_fp32) {
+      float* dst = reinterpret_cast<float*>(p.C) + row * p.ldc + col0;
+      if (col0 + 32 <= p.N && (p.ldc % 4 == 0) && base_ok) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float4 o;
+          o.x = p.alpha * __uint_as_float(v[4 * j + 0]);
+          o.y = p.alpha * __uint_as_float(v[4 * j + 1]);
+          o.z = p.alpha * __uint_as_float(v[4 * j + 2]);
+          o.w = p.alpha * __uint_as_float(v[4 * j + 3]);
+          if (p.beta != 0.f) {
+            const float4 old = *reinterpret_cast<const float4*>(dst + 4 * j);
+            o.x += p.beta * old.x; o.y += p.beta * old.y; o.z += p.beta * old.z; o.w += p.beta * old.w;
+          }
+          *reinterpret_cast<float4*>(dst + 4 * j) = o;
+        }
+      } else {
+        for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+          float o = p.alpha * __uint_as_float(v[j]);
+          if (p.beta != 0.f) o += p.beta * dst[j];
+          dst[j] = o;
+        }
+      }
+    } else {
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0;
+      if (col0 + 32 <= p.N && (p.ldc % 8 == 0) && base_ok) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float f[8];
+#pragma unroll
+          for (int t = 0; t < 8; ++t) f[t] = p.alpha * __uint_as_float(v[8 * j + t]);
+          if (p.beta != 0.f) {
+            const uint4 old = *reinterpret_cast<const uint4*>(dst + 8 * j);
+            const float2 o0 = unpack_bf16(old.x), o1 = unpack_bf16(old.y), o2 = unpack_bf16(old.z),
+                         o3 = unpack_bf16(old.w);
+            f[0] += p.beta * o0.x; f[1] += p.beta * o0.y; f[2] += p.beta * o1.x; f[3] += p.beta * o1.y;
+            f[4] += p.beta * o2.x; f[5] += p.beta * o2.y; f[6] += p.beta * o3.x; f[7] += p.beta * o3.y;
+          }
+          uint4 o;
+          o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
+          o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+          *reinterpret_cast<uint4*>(dst + 8 * j) = o;
+        }
+      } else {
+        for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+          float o = p.alpha * __uint_as_float(v[j]);
+          if (p.beta != 0.f) o += p.beta * __bfloat162float(dst[j]);
+          dst[j] = __float2bfloat16(o);
+        }
+      }
+    }
+  }
+};
+
+// Fused LM head, forward: per row running (max, sum exp, sum exp * z) over the vocabulary
+// slice of this item plus the target logit; z = logit * inv_temp[row].
+struct EpiLogprobStats {
+  float m, s, t, it;
+  int label;
+  __device__ EpiLogprobStats(const GemmParams&) : m(-INFINITY), s(0.f), t(0.f), it(1.f), label(-1) {}
+  __device__ void begin_item(const GemmParams& p, long long row) {
+    m = -INFINITY; s = 0.f; t = 0.f;
+    const bool ok = row < p.M;
+    it = (ok && p.inv_temp) ? p.inv_temp[row] : 1.f;
+    label = ok ? p.labels[row] : -1;
+  }
+  __device__ void chunk(const GemmParams& p, long long row, int col0, uint32_t (&v)[32]) {
+    if (col0 >= p.N) return;
+    float z[32];
+    float cm = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      z[j] = (col0 + j < p.N) ? __uint_as_float(v[j]) * it : -INFINITY;
+      cm = fmaxf(cm, z[j]);
+    }
+    if (label >= col0 && label < col0 + 32 && row < p.M) {
+      float zl = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) zl = (col0 + j == label) ? z[j] : zl;
+      p.target_logit[row] = zl;
+    }
+    const float mn = fmaxf(m, cm);
+    const float corr = __expf(m - mn);  // m = -inf on the first chunk -> 0
+    float ls = 0.f, lt = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float e = __expf(z[j] - mn);  // -inf -> 0
+      ls += e;
+      lt += (col0 + j < p.N) ? e * z[j] : 0.f;
+    }
+    s = s * corr + ls;
+    t = t * corr + lt;
+    m = mn;
+  }
+  __device__ void end_item(const GemmParams& p, long long row, int split) {
+    if (row >= p.M) return;
+    const long long o = static_cast<long long>(split) * p.M + row;
+    p.part_m[o] = m;
+    p.part_s[o] = s;
+    p.part_t[o] = t;
+  }
+};
+
+// Fused LM head, backward: dlogits = g[row] * inv_temp[row] * (onehot(label) - softmax(z)),
+// written as bf16 [M, N] (C). softmax is rebuilt from the saved log-sum-exp.
+struct EpiDLogits {
+  float it, g, lse;
+  int label;
+  __device__ EpiDLogits(const GemmParams&) : it(1.f), g(0.f), lse(0.f), label(-1) {}
+  __device__ void begin_item(const GemmParams& p, long long row) {
+    const bool ok = row < p.M;
+    it = (ok && p.inv_temp) ? p.inv_temp[row] : 1.f;
+    g = ok ? p.grad_logprob[row] : 0.f;
+    lse = ok ? p.lse[row] : 0.f;
+    label = ok ? p.labels[row] : -1;
+  }
+  __device__ void end_item(const GemmParams&, long long, int) {}
+  __device__ void chunk(const GemmParams& p, long long row, int col0, uint32_t (&v)[32]) {
+    if (row >= p.M || col0 >= p.N) return;
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + row * p.ldc + col0;
+    float d[32];
+    const float gs = g * it;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float z = __uint_as_float(v[j]) * it;
+      const float pr = __expf(z - lse);
+      d[j] = gs * (((col0 + j) == label ? 1.f : 0.f) - pr);
+    }
+    if (col0 + 32 <= p.N && (p.ldc % 8 == 0)) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 o;
+        o.x = pack_bf16(d[8 * j + 0], d[8 * j + 1]); o.y = pack_bf16(d[8 * j + 2], d[8 * j + 3]);
+        o.z = pack_bf16(d[8 * j + 4], d[8 * j + 5]); o.w = pack_bf16(d[8 * j + 6], d[8 * j + 7]);
+        *reinterpret_cast<uint4*>(dst + 8 * j) = o;
+      }
+    } else {
+      for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = __float2bfloat16(d[j]);
+    }
+  }
+};
+
+template <int BN, bool A_MN, bool B_MN, class Sched, class Epi>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 4);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::ACC_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  int m_blk = 0, n_blk = 0, brow = 0, kb0 = 0, nkb = 0;
+  long long c_row0 = 0;
+  bool last = true;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      Sched sched(p, BN);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      while (ok && sched.next(p, m_blk, n_blk, brow, last, kb0, nkb, c_row0)) {
+        for (int kb = kb0; kb < kb0 + nkb; ++kb) {
+          if (!mbar_wait(&empty[s], ph ^ 1, p.status, kTimeoutEmptyBarrier)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+          uint8_t* a_dst = smem + s * Cfg::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + Cfg::A_BYTES;
+          if (!A_MN) {
+            tma_load_2d(a_dst, &tmA, &full[s], kb * kBK, m_blk * kBM);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kBM / 64; ++j)
+              tma_load_2d(a_dst + j * 8192, &tmA, &full[s], m_blk * kBM + 64 * j, kb * kBK);
+          }
+          if (!B_MN) {
+            tma_load_2d(b_dst, &tmB, &full[s], kb * kBK, brow + n_blk * BN);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(b_dst + j * 8192, &tmB, &full[s], n_blk * BN + 64 * j, brow + kb * kBK);
+          }
+          if (++s == STAGES) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+      }
+      if (!ok) __nanosleep(200000);  // let copies that are still in flight land before exit
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(1, kBM, BN, A_MN, B_MN);
+      Sched sched(p, BN);
+      int s = 0, acc = 0;
+      uint32_t ph = 0, acc_ph = 0;
+      bool ok = true;
+      while (ok && sched.next(p, m_blk, n_blk, brow, last, kb0, nkb, c_row0)) {
+        if (nkb == 0) continue;
+        if (!mbar_wait(&tempty[acc], acc_ph ^ 1, p.status, kTimeoutTmemEmpty)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&full[s], ph, p.status, kTimeoutFullBarrier)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t adesc =
+                A_MN ? umma_smem_desc(a_addr + k * 2048, 8192, 1024) : umma_smem_desc(a_addr + k * 32, 0, 1024);
+            const uint64_t bdesc =
+                B_MN ? umma_smem_desc(b_addr + k * 2048, 8192, 1024) : umma_smem_desc(b_addr + k * 32, 0, 1024);
+            umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
+          }
+          umma_commit(&empty[s]);
+          if (++s == STAGES) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&tfull[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_ph ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // TMEM lanes [32q, 32q+32) are the ones this warp may read
+    Sched sched(p, BN);
+    Epi epi(p);
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    bool first = true;
+    while (sched.next(p, m_blk, n_blk, brow, last, kb0, nkb, c_row0)) {
+      const int row_in_m = m_blk * kBM + q * 32 + lane;
+      const long long row = (row_in_m < p.M) ? c_row0 + row_in_m : (1LL << 40);  // out of range -> masked
+      if (nkb == 0) {
+        // nothing to reduce: the tile is all zeros
+        uint32_t z[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) z[j] = 0u;
+        for (int c = 0; c < BN / 32; ++c) epi.chunk(p, row, n_blk * BN + c * 32, z);
+        continue;
+      }
+      if (first) epi.begin_item(p, row);
+      bool ok = mbar_wait(&tfull[acc], acc_ph, p.status, kTimeoutTmemFull);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
+        tmem_ld_wait();
+        epi.chunk(p, row, n_blk * BN + c * 32, v);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_ph ^= 1;
+      if (last) epi.end_item(p, row, (n_blk * BN) / (sched_split_width(p, BN)));
+      first = last;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::ACC_COLS);
+}
+
+template <int BN, bool A_MN, bool B_MN, bool GROUPED>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  using Sched = typename std::conditional<GROUPED, SchedGrouped, SchedDense>::type;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, Sched, EpiStore>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return -10;
+    configured = true;
+  }
+  const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  if (grid <= 0) return 0;
+  kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+template <bool A_MN, bool B_MN, bool GROUPED>
+static int dispatch_bn(int bn, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
+                       cudaStream_t stream) {
+  switch (bn) {
+    case 256: return launch_gemm<256, A_MN, B_MN, GROUPED>(tmA, tmB, p, stream);
+    case 128: return launch_gemm<128, A_MN, B_MN, GROUPED>(tmA, tmB, p, stream);
+    default: return launch_gemm<64, A_MN, B_MN, GROUPED>(tmA, tmB, p, stream);
+  }
+}
+
+}  // namespace prb
+
+// A, B, C are device pointers; lda/ldb/ldc are row pitches in elements of the stored 2-D
+// tensors described at the top of this file. `block_expert` (device, int32) switches on
+// grouped mode. `status` is a device int that receives a prb::StatusCode on a bounded-wait
+// failure (and is left untouched otherwise). Returns 0 when the launch was issued.
+PRB_API int prb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                          long long ldc, int a_mn, int b_mn, int out_fp32, float alpha, float beta,
+                          const int* block_expert, int num_experts, int b_rows_per_expert, int force_bn,
+                          int* status, void* stream_) {
+  using namespace prb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0) return -3;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+    return -4;  // TMA needs 16-byte aligned bases and row pitches
+  const bool grouped = block_expert != nullptr;
+  if (grouped && b_mn && (b_rows_per_expert % kBK)) return -5;
+  int bn = force_bn > 0 ? force_bn : (N > 128 ? 256 : (N > 64 ? 128 : 64));
+  // prefer 128-wide tiles when 256 would leave most SMs idle
+  if (force_bn <= 0 && bn == 256) {
+    const long long t256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
+    if (t256 < sm_count() && N % 256 != 0) bn = 128;
+  }
+  if (b_mn && bn < 64) bn = 64;
+
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!a_mn)
+    rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda, kBM, kBK,
+                      true);
+  else
+    rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda, kBK, 64,
+                      true);
+  if (rc) return rc;
+  const uint64_t E = grouped ? (uint64_t)num_experts : 1;
+  if (!b_mn)
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, grouped ? E * b_rows_per_expert : (uint64_t)N,
+                      (uint64_t)K, (uint64_t)ldb, bn, kBK, true);
+  else
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, grouped ? E * b_rows_per_expert : (uint64_t)K,
+                      (uint64_t)N, (uint64_t)ldb, kBK, 64, true);
+  if (rc) return rc;
+
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.rows_total = M;
+  p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32;
+  p.expert_offset = nullptr; p.num_experts = 0;
+  p.alpha = alpha; p.beta = beta;
+  p.block_expert = block_expert;
+  p.b_rows_per_expert = b_rows_per_expert;
+  p.status = status;
+  p.num_splits = 0;
+  p.labels = nullptr; p.inv_temp = nullptr; p.part_m = p.part_s = p.part_t = p.target_logit = nullptr;
+  p.grad_logprob = nullptr; p.lse = nullptr;
+
+#define PRB_DISPATCH(AMN, BMN)                                                              \
+  (grouped ? dispatch_bn<AMN, BMN, true>(bn, tmA, tmB, p, stream)                           \
+           : dispatch_bn<AMN, BMN, false>(bn, tmA, tmB, p, stream))
+  if (!a_mn && !b_mn) return PRB_DISPATCH(false, false);
+  if (!a_mn && b_mn) return PRB_DISPATCH(false, true);
+  if (a_mn && b_mn) return PRB_DISPATCH(true, true);
+  return PRB_DISPATCH(true, false);
+#undef PRB_DISPATCH
+}
+
+// ---------------------------------------------------------------- fused LM head
+// Replaces _SequenceChunkedLogProbEntropyFn (trainer/models/layers/lm_head.py:114-266 of the
+// reference): logits never reach global memory in the forward pass.
+namespace prb {
+
+// logprob = z_label - lse, entropy = lse - sum(p z), from the per-split partials.
+__global__ void __launch_bounds__(256)
+lmhead_combine_kernel(const float* __restrict__ part_m, const float* __restrict__ part_s,
+                      const float* __restrict__ part_t, const float* __restrict__ target, const int* __restrict__ labels,
+                      float* __restrict__ logprob, float* __restrict__ entropy, float* __restrict__ lse_out,
+                      long long T, int splits, int V) {
+  const long long r = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (r >= T) return;
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, part_m[static_cast<long long>(s) * T + r]);
+  float S = 0.f, Tt = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float c = __expf(part_m[static_cast<long long>(s) * T + r] - M);
+    S += part_s[static_cast<long long>(s) * T + r] * c;
+    Tt += part_t[static_cast<long long>(s) * T + r] * c;
+  }
+  const float lse = M + logf(S);
+  lse_out[r] = lse;
+  const int lb = labels[r];
+  logprob[r] = (lb >= 0 && lb < V) ? target[r] - lse : 0.f;
+  entropy[r] = lse - Tt / S;
+}
+
+static int lmhead_maps(CUtensorMap* tmA, CUtensorMap* tmB, const void* h, const void* W, int T, int V, int H,
+                       long long ldh, long long ldw) {
+  if ((ldh % 8) || (ldw % 8) || (reinterpret_cast<uintptr_t>(h) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
+    return -4;
+  int rc = make_tmap_2d(tmA, h, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)T, (uint64_t)H, (uint64_t)ldh, kBM,
+                        kBK, true);
+  if (rc) return rc;
+  return make_tmap_2d(tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)V, (uint64_t)H, (uint64_t)ldw, 256, kBK,
+                      true);
+}
+
+}  // namespace prb
+
+// Number of vocabulary splits the forward kernel will use for T rows and V columns; the
+// caller sizes part_m / part_s / part_t as fp32 [splits, T].
+PRB_API int prb_lmhead_num_splits(int T, int V) {
+  const int tiles_m = (T + 127) / 128;
+  const int tiles_n = (V + 255) / 256;
+  int s = (2 * prb::sm_count() + tiles_m - 1) / tiles_m;
+  if (s < 1) s = 1;
+  if (s > tiles_n) s = tiles_n;
+  // avoid empty trailing splits
+  const int per = (tiles_n + s - 1) / s;
+  s = (tiles_n + per - 1) / per;
+  return s;
+}
+
+// h: bf16 [T, H]; W: bf16 [V, H]; labels: int32 [T] (outside [0, V) = ignored, logprob 0);
+// inv_temp: fp32 [T] or null. Outputs fp32 [T]: logprob, entropy, lse. Scratch: part_*
+// fp32 [splits, T] and target fp32 [T] (zeroed here).
+PRB_API int prb_lmhead_fwd(const void* h, const void* W, const int* labels, const float* inv_temp, float* part_m,
+                           float* part_s, float* part_t, float* target, float* logprob, float* entropy, float* lse,
+                           int T, int V, int H, long long ldh, long long ldw, int splits, int* status,
+                           void* stream_) {
+  using namespace prb;
+  if (T <= 0) return 0;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  CUtensorMap tmA, tmB;
+  int rc = lmhead_maps(&tmA, &tmB, h, W, T, V, H, ldh, ldw);
+  if (rc) return rc;
+  GemmParams p = {};
+  p.M = T; p.N = V; p.K = H; p.rows_total = T;
+  p.alpha = 1.f; p.status = status;
+  p.num_splits = splits;
+  p.labels = labels; p.inv_temp = inv_temp;
+  p.part_m = part_m; p.part_s = part_s; p.part_t = part_t; p.target_logit = target;
+  cudaMemsetAsync(target, 0, sizeof(float) * T, stream);
+  using Cfg = GemmCfg<256>;
+  auto kern = gemm_bf16_kernel<256, false, false, SchedSplit, EpiLogprobStats>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
+      return -10;
+    configured = true;
+  }
+  const int items = ((T + 127) / 128) * splits;
+  const int grid = items < sm_count() ? items : sm_count();
+  kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  lmhead_combine_kernel<<<(T + 255) / 256, 256, 0, stream>>>(part_m, part_s, part_t, target, labels, logprob, entropy,
+                                                            lse, T, splits, V);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// dlogits (bf16 [T, V], pitch ldd) = grad_logprob[row] * inv_temp[row] * (onehot - softmax).
+PRB_API int prb_lmhead_bwd_dlogits(const void* h, const void* W, const int* labels, const float* inv_temp,
+                                   const float* grad_logprob, const float* lse, void* dlogits, int T, int V, int H,
+                                   long long ldh, long long ldw, long long ldd, int* status, void* stream_) {
+  using namespace prb;
+  if (T <= 0) return 0;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  CUtensorMap tmA, tmB;
+  int rc = lmhead_maps(&tmA, &tmB, h, W, T, V, H, ldh, ldw);
+  if (rc) return rc;
+  GemmParams p = {};
+  p.M = T; p.N = V; p.K = H; p.rows_total = T;
+  p.C = dlogits; p.ldc = ldd;
+  p.alpha = 1.f; p.status = status;
+  p.labels = labels; p.inv_temp = inv_temp; p.grad_logprob = grad_logprob; p.lse = lse;
+  using Cfg = GemmCfg<256>;
+  auto kern = gemm_bf16_kernel<256, false, false, SchedDense, EpiDLogits>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
+      return -10;
+    configured = true;
+  }
+  const int tiles = ((T + 127) / 128) * ((V + 255) / 256);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Per-expert weight gradient: C[e] (rows [e*M, (e+1)*M) of a [E*M, N] tensor) =
+// alpha * A_e^T . B_e + beta * C[e], where A is [rows, M] and B is [rows, N] (both
+// MN-major, bf16) and expert e owns rows [expert_offset[e], expert_offset[e+1]) — multiples
+// of 128. Rows of A / B past the last expert are never read.
+PRB_API int prb_gemm_bf16_kgrouped(const void* A, const void* B, void* C, int M, int N, long long total_rows,
+                                   long long lda, long long ldb, long long ldc, int out_fp32, float alpha,
+                                   float beta, const int* expert_offset, int num_experts, int* status,
+                                   void* stream_) {
+  using namespace prb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || num_experts <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+    return -4;
+  const int bn = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_rows, (uint64_t)M,
+                        (uint64_t)lda, kBK, 64, true);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_rows, (uint64_t)N, (uint64_t)ldb,
+                    kBK, 64, true);
+  if (rc) return rc;
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = 0; p.rows_total = static_cast<long long>(num_experts) * M;
+  p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32;
+  p.alpha = alpha; p.beta = beta;
+  p.status = status;
+  p.expert_offset = expert_offset; p.num_experts = num_experts;
+  const long long tiles = static_cast<long long>(num_experts) * ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
+  const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
+#define PRB_KG(BN_)                                                                                       \
+  {                                                                                                       \
+    auto kern = gemm_bf16_kernel<BN_, true, true, SchedKGrouped, EpiStore>;                               \
+    static bool configured = false;                                                                       \
+    if (!configured) {                                                                                    \
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                         \
+                               GemmCfg<BN_>::SMEM_BYTES) != cudaSuccess)                                  \
+        return -10;                                                                                       \
+      configured = true;                                                                                  \
+    }                                                                                                     \
+    kern<<<grid, kGemmThreads, GemmCfg<BN_>::SMEM_BYTES, stream>>>(tmA, tmB, p);                          \
+  }
+  if (bn == 256) PRB_KG(256) else if (bn == 128) PRB_KG(128) else PRB_KG(64)
+#undef PRB_KG
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}

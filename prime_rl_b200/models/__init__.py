@@ -1,0 +1,5 @@
+"""Model families, layers and checkpoint-layout conversions."""
+
+from .config import PRESETS, ModelArch, resolve_arch  # noqa: F401
+from .layers import SeqInfo  # noqa: F401
+from .model import CausalLM, apply_lora, build_model, freeze_router  # noqa: F401

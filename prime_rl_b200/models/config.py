@@ -1,0 +1,247 @@
+"""Architecture description shared by the trainer models and the rollout engine.
+
+One ``ModelArch`` covers the supported decoder families; ``from_hf_config`` reads a
+HuggingFace ``config.json`` dict (llama, qwen2, qwen3, qwen3_moe, glm4_moe, gpt_oss,
+minimax_m2, afmoe) and ``to_hf_config`` writes one back for exported checkpoints.
+The reference keeps one configuration class per family
+(src/prime_rl/trainer/models/*/configuration_*.py); here a family is a set of flags.
+"""
+
+from __future__ import annotations
+
+import json
+from pathlib import Path
+from typing import Any, Literal
+
+from pydantic import BaseModel, ConfigDict
+
+
+class ModelArch(BaseModel):
+    model_config = ConfigDict(extra="ignore")
+
+    model_type: str = "qwen3"
+    vocab_size: int = 151936
+    hidden_size: int = 1024
+    num_hidden_layers: int = 28
+    num_attention_heads: int = 16
+    num_key_value_heads: int = 8
+    head_dim: int = 128
+    intermediate_size: int = 3072
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1e6
+    partial_rotary_factor: float = 1.0
+    max_position_embeddings: int = 40960
+    tie_word_embeddings: bool = False
+    attention_bias: bool = False
+    qk_norm: bool = True                       # per-head RMSNorm on q and k (Qwen3 family)
+    hidden_act: Literal["silu", "swiglu_clamped", "relu2"] = "silu"
+    swiglu_limit: float = 7.0
+    swiglu_alpha: float = 1.702
+    # attention pattern
+    sliding_window: int | None = None
+    layer_types: list[str] | None = None       # per layer "full_attention" | "sliding_attention"
+    attention_sinks: bool = False              # learnable per-head sink logit (GPT-OSS)
+    # MoE
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    score_func: Literal["softmax", "sigmoid"] = "softmax"
+    routed_scaling_factor: float = 1.0
+    router_bias: bool = False                  # selection bias (e_score_correction_bias)
+    router_linear_bias: bool = False           # bias term of the gate projection (GPT-OSS)
+    expert_bias: bool = False                  # per-expert projection biases (GPT-OSS)
+    n_shared_experts: int = 0
+    first_k_dense_replace: int = 0             # first k layers use a dense MLP
+    mlp_only_layers: list[int] = []
+    decoder_sparse_step: int = 1
+    initializer_range: float = 0.02
+
+    # ------------------------------------------------------------------ derived
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    def layer_is_moe(self, idx: int) -> bool:
+        if not self.is_moe or idx in self.mlp_only_layers or idx < self.first_k_dense_replace:
+            return False
+        return (idx + 1) % self.decoder_sparse_step == 0
+
+    def layer_window(self, idx: int) -> int | None:
+        if self.sliding_window is None:
+            return None
+        if self.layer_types is None:
+            return self.sliding_window
+        return self.sliding_window if self.layer_types[idx] == "sliding_attention" else None
+
+    @property
+    def rotary_dim(self) -> int:
+        rd = int(self.head_dim * self.partial_rotary_factor)
+        return rd - rd % 2
+
+    @property
+    def q_dim(self) -> int:
+        return self.num_attention_heads * self.head_dim
+
+    @property
+    def kv_dim(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    def param_count(self, active_only: bool = False, matmul_only: bool = False) -> int:
+        """Parameter count; ``active_only`` counts top-k experts instead of all of them and
+        ``matmul_only`` leaves out embeddings and norms (the MFU formula's convention)."""
+        H = self.hidden_size
+        attn = H * (self.q_dim + 2 * self.kv_dim) + self.q_dim * H
+        dense_mlp = 3 * H * self.intermediate_size
+        expert = 3 * H * self.moe_intermediate_size
+        total = 0
+        for i in range(self.num_hidden_layers):
+            total += attn
+            if self.layer_is_moe(i):
+                n = self.num_experts_per_tok if active_only else self.num_experts
+                total += n * expert + H * self.num_experts + self.n_shared_experts * expert
+            else:
+                total += dense_mlp
+            if not matmul_only:
+                total += 2 * H + (2 * self.head_dim if self.qk_norm else 0)
+        total += self.vocab_size * H  # lm head
+        if not matmul_only:
+            total += H + (0 if self.tie_word_embeddings else self.vocab_size * H)
+        return total
+
+    # ------------------------------------------------------------------ HF interchange
+    @classmethod
+    def from_hf_config(cls, cfg: dict[str, Any]) -> "ModelArch":
+        mt = cfg.get("model_type", "llama")
+        heads = cfg["num_attention_heads"]
+        d: dict[str, Any] = dict(
+            model_type=mt,
+            vocab_size=cfg["vocab_size"],
+            hidden_size=cfg["hidden_size"],
+            num_hidden_layers=cfg["num_hidden_layers"],
+            num_attention_heads=heads,
+            num_key_value_heads=cfg.get("num_key_value_heads", heads),
+            head_dim=cfg.get("head_dim") or cfg["hidden_size"] // heads,
+            intermediate_size=cfg.get("intermediate_size", 0),
+            rms_norm_eps=cfg.get("rms_norm_eps", 1e-6),
+            rope_theta=cfg.get("rope_theta") or (cfg.get("rope_parameters") or {}).get("rope_theta", 1e4),
+            partial_rotary_factor=cfg.get("partial_rotary_factor", 1.0),
+            max_position_embeddings=cfg.get("max_position_embeddings", 32768),
+            tie_word_embeddings=cfg.get("tie_word_embeddings", False),
+            attention_bias=cfg.get("attention_bias", False),
+            sliding_window=cfg.get("sliding_window") if cfg.get("use_sliding_window", True) else None,
+            layer_types=cfg.get("layer_types"),
+            initializer_range=cfg.get("initializer_range", 0.02),
+        )
+        if mt in ("llama", "mistral"):
+            d.update(qk_norm=False)
+        elif mt == "qwen2":
+            d.update(qk_norm=False, attention_bias=True, sliding_window=None)
+        elif mt == "qwen3":
+            d.update(qk_norm=True, sliding_window=None)
+        elif mt == "qwen3_moe":
+            d.update(qk_norm=True, sliding_window=None, num_experts=cfg["num_experts"],
+                     num_experts_per_tok=cfg["num_experts_per_tok"],
+                     moe_intermediate_size=cfg["moe_intermediate_size"],
+                     norm_topk_prob=cfg.get("norm_topk_prob", True),
+                     mlp_only_layers=cfg.get("mlp_only_layers", []),
+                     decoder_sparse_step=cfg.get("decoder_sparse_step", 1))
+        elif mt == "glm4_moe":
+            d.update(qk_norm=cfg.get("use_qk_norm", False), num_experts=cfg["n_routed_experts"],
+                     num_experts_per_tok=cfg["num_experts_per_tok"],
+                     moe_intermediate_size=cfg["moe_intermediate_size"],
+                     norm_topk_prob=cfg.get("norm_topk_prob", True), score_func="sigmoid", router_bias=True,
+                     routed_scaling_factor=cfg.get("routed_scaling_factor", 1.0),
+                     n_shared_experts=cfg.get("n_shared_experts", 1),
+                     first_k_dense_replace=cfg.get("first_k_dense_replace", 0), sliding_window=None)
+        elif mt == "gpt_oss":
+            d.update(qk_norm=False, attention_bias=True, attention_sinks=True, hidden_act="swiglu_clamped",
+                     swiglu_limit=cfg.get("swiglu_limit", 7.0), num_experts=cfg["num_local_experts"],
+                     num_experts_per_tok=cfg.get("num_experts_per_tok", cfg.get("experts_per_token", 4)),
+                     moe_intermediate_size=cfg["intermediate_size"], norm_topk_prob=True,
+                     router_linear_bias=True, expert_bias=True)
+        elif mt == "minimax_m2":
+            d.update(qk_norm=True, num_experts=cfg["num_local_experts"],
+                     num_experts_per_tok=cfg["num_experts_per_tok"], moe_intermediate_size=cfg["intermediate_size"],
+                     score_func="sigmoid", router_bias=True, sliding_window=None)
+        elif mt == "afmoe":
+            d.update(qk_norm=True, num_experts=cfg["num_experts"], num_experts_per_tok=cfg["num_experts_per_tok"],
+                     moe_intermediate_size=cfg["moe_intermediate_size"], score_func="sigmoid", router_bias=True,
+                     n_shared_experts=cfg.get("num_shared_experts", 0),
+                     first_k_dense_replace=cfg.get("num_dense_layers", 0),
+                     routed_scaling_factor=cfg.get("route_scale", 1.0))
+        else:
+            raise ValueError(f"unsupported model_type '{mt}'")
+        return cls(**d)
+
+    @classmethod
+    def from_pretrained(cls, path: str | Path) -> "ModelArch":
+        return cls.from_hf_config(json.loads((Path(path) / "config.json").read_text()))
+
+    def to_hf_config(self) -> dict[str, Any]:
+        arch_names = {"llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
+                      "qwen3_moe": "Qwen3MoeForCausalLM", "glm4_moe": "Glm4MoeForCausalLM",
+                      "gpt_oss": "GptOssForCausalLM", "minimax_m2": "MiniMaxM2ForCausalLM",
+                      "afmoe": "AfmoeForCausalLM"}
+        cfg: dict[str, Any] = dict(
+            architectures=[arch_names.get(self.model_type, "LlamaForCausalLM")], model_type=self.model_type,
+            vocab_size=self.vocab_size, hidden_size=self.hidden_size, num_hidden_layers=self.num_hidden_layers,
+            num_attention_heads=self.num_attention_heads, num_key_value_heads=self.num_key_value_heads,
+            head_dim=self.head_dim, intermediate_size=self.intermediate_size, rms_norm_eps=self.rms_norm_eps,
+            rope_theta=self.rope_theta, max_position_embeddings=self.max_position_embeddings,
+            tie_word_embeddings=self.tie_word_embeddings, attention_bias=self.attention_bias,
+            hidden_act="silu", torch_dtype="bfloat16", initializer_range=self.initializer_range)
+        if self.is_moe:
+            if self.model_type == "glm4_moe":
+                cfg.update(n_routed_experts=self.num_experts, n_shared_experts=self.n_shared_experts,
+                           first_k_dense_replace=self.first_k_dense_replace,
+                           routed_scaling_factor=self.routed_scaling_factor, use_qk_norm=self.qk_norm)
+            elif self.model_type in ("gpt_oss", "minimax_m2"):
+                cfg.update(num_local_experts=self.num_experts)
+            else:
+                cfg.update(num_experts=self.num_experts, mlp_only_layers=self.mlp_only_layers,
+                           decoder_sparse_step=self.decoder_sparse_step)
+            cfg.update(num_experts_per_tok=self.num_experts_per_tok,
+                       moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob)
+        if self.sliding_window is not None:
+            cfg.update(sliding_window=self.sliding_window, layer_types=self.layer_types)
+        return cfg
+
+
+# Shapes named by the benchmarks and examples (random-init; no download needed).
+PRESETS: dict[str, dict[str, Any]] = {
+    "qwen3-0.6b": dict(model_type="qwen3", hidden_size=1024, num_hidden_layers=28, num_attention_heads=16,
+                       num_key_value_heads=8, head_dim=128, intermediate_size=3072, tie_word_embeddings=True),
+    "qwen3-4b": dict(model_type="qwen3", hidden_size=2560, num_hidden_layers=36, num_attention_heads=32,
+                     num_key_value_heads=8, head_dim=128, intermediate_size=9728, tie_word_embeddings=True),
+    "qwen3-8b": dict(model_type="qwen3", hidden_size=4096, num_hidden_layers=36, num_attention_heads=32,
+                     num_key_value_heads=8, head_dim=128, intermediate_size=12288),
+    "qwen3-30b-a3b": dict(model_type="qwen3_moe", hidden_size=2048, num_hidden_layers=48, num_attention_heads=32,
+                          num_key_value_heads=4, head_dim=128, intermediate_size=6144, num_experts=128,
+                          num_experts_per_tok=8, moe_intermediate_size=768, norm_topk_prob=True),
+    "tiny-qwen3-moe": dict(model_type="qwen3_moe", hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                           num_key_value_heads=2, head_dim=64, intermediate_size=512, num_experts=8,
+                           num_experts_per_tok=2, moe_intermediate_size=512, vocab_size=4096),
+    "tiny-qwen3": dict(model_type="qwen3", hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                       num_key_value_heads=2, head_dim=64, intermediate_size=512, vocab_size=4096),
+}
+
+
+def resolve_arch(name_or_path: str, overrides: dict[str, Any] | None = None) -> ModelArch:
+    """A preset name, a local HF directory, or inline overrides only."""
+    key = name_or_path.lower().split("/")[-1]
+    base: dict[str, Any] = {}
+    if Path(name_or_path).is_dir() and (Path(name_or_path) / "config.json").exists():
+        base = ModelArch.from_pretrained(name_or_path).model_dump()
+    else:
+        for preset, vals in PRESETS.items():
+            if key.startswith(preset) or preset == key:
+                base = dict(vals)
+                break
+        else:
+            if not overrides:
+                raise FileNotFoundError(
+                    f"'{name_or_path}' is neither a local HF directory nor a known preset {sorted(PRESETS)}; "
+                    "pass model.arch to describe the architecture inline")
+    base.update(overrides or {})
+    return ModelArch(**base)

@@ -1,0 +1,243 @@
+"""State-dict layouts and the invertible conversions between them.
+
+Three layouts exist:
+
+``native``  what the modules hold: fused ``self_attn.qkv_proj``, ``mlp.gate_up_proj``,
+            ``mlp.experts.gate_up_proj [E, 2I, H]``.
+``prime``   the checkpoint layout (DCP ``app.model.*``): per-projection names, experts stacked
+            ``mlp.experts.{gate,up,down}_proj [E, ., .]``, router at ``mlp.router.gate.weight``
+            (reference: trainer/models/qwen3_moe/modeling_qwen3_moe.py:43-224).
+``hf``      HuggingFace names: ``mlp.gate.weight`` and one tensor per expert
+            ``mlp.experts.{e}.{gate,up,down}_proj.weight``
+            (reference: trainer/models/qwen3_moe/converting_qwen3_moe.py:8-14).
+
+Conversions are built from small invertible ops (rename / split-concat / stack), in the
+spirit of the reference's ``conversion_ops.py`` but written against plain dicts.
+"""
+
+from __future__ import annotations
+
+import re
+from dataclasses import dataclass
+from typing import Callable
+
+import torch
+
+from .config import ModelArch
+
+StateDict = dict[str, torch.Tensor]
+
+
+# ---------------------------------------------------------------------- invertible ops
+@dataclass
+class Rename:
+    """Regex rename; ``inverse`` swaps pattern and replacement templates."""
+
+    pattern: str
+    repl: str
+    inv_pattern: str
+    inv_repl: str
+
+    def forward(self, sd: StateDict) -> StateDict:
+        return {re.sub(self.pattern, self.repl, k): v for k, v in sd.items()}
+
+    def inverse(self, sd: StateDict) -> StateDict:
+        return {re.sub(self.inv_pattern, self.inv_repl, k): v for k, v in sd.items()}
+
+
+@dataclass
+class SplitConcat:
+    """One fused tensor <-> several tensors concatenated on ``dim``; ``sizes(key_prefix)``
+    gives the member widths."""
+
+    fused_suffix: str
+    member_suffixes: list[str]
+    sizes: Callable[[torch.Tensor], list[int]]
+    dim: int = 0
+
+    def forward(self, sd: StateDict) -> StateDict:  # fused -> members
+        out: StateDict = {}
+        for k, v in sd.items():
+            if k.endswith(self.fused_suffix):
+                base = k[: -len(self.fused_suffix)]
+                for suf, part in zip(self.member_suffixes, torch.split(v, self.sizes(v), dim=self.dim)):
+                    out[base + suf] = part
+            else:
+                out[k] = v
+        return out
+
+    def inverse(self, sd: StateDict) -> StateDict:  # members -> fused
+        out: StateDict = {}
+        groups: dict[str, dict[str, torch.Tensor]] = {}
+        for k, v in sd.items():
+            for suf in self.member_suffixes:
+                if k.endswith(suf):
+                    groups.setdefault(k[: -len(suf)], {})[suf] = v
+                    break
+            else:
+                out[k] = v
+        for base, members in groups.items():
+            if len(members) != len(self.member_suffixes):
+                for suf, v in members.items():
+                    out[base + suf] = v
+                continue
+            out[base + self.fused_suffix] = torch.cat([members[s] for s in self.member_suffixes], dim=self.dim)
+        return out
+
+
+@dataclass
+class StackExperts:
+    """Stacked ``[E, ...]`` tensor <-> one tensor per expert."""
+
+    stacked_suffix: str      # e.g. "mlp.experts.gate_proj"
+    per_expert_fmt: str      # e.g. "mlp.experts.{e}.gate_proj.weight"
+
+    def forward(self, sd: StateDict) -> StateDict:  # stacked -> per expert
+        out: StateDict = {}
+        for k, v in sd.items():
+            if k.endswith(self.stacked_suffix):
+                base = k[: -len(self.stacked_suffix)]
+                for e in range(v.shape[0]):
+                    out[base + self.per_expert_fmt.format(e=e)] = v[e]
+            else:
+                out[k] = v
+        return out
+
+    def inverse(self, sd: StateDict) -> StateDict:
+        pat = re.compile("^(.*)" + re.escape(self.per_expert_fmt).replace(r"\{e\}", r"(\d+)") + "$")
+        out: StateDict = {}
+        groups: dict[str, dict[int, torch.Tensor]] = {}
+        for k, v in sd.items():
+            m = pat.match(k)
+            if m:
+                groups.setdefault(m.group(1), {})[int(m.group(2))] = v
+            else:
+                out[k] = v
+        for base, items in groups.items():
+            out[base + self.stacked_suffix] = torch.stack([items[e] for e in sorted(items)], dim=0)
+        return out
+
+
+class Chain:
+    def __init__(self, ops: list):
+        self.ops = ops
+
+    def forward(self, sd: StateDict) -> StateDict:
+        for op in self.ops:
+            sd = op.forward(sd)
+        return sd
+
+    def inverse(self, sd: StateDict) -> StateDict:
+        for op in reversed(self.ops):
+            sd = op.inverse(sd)
+        return sd
+
+
+# ---------------------------------------------------------------------- layout chains
+def native_to_prime_chain(arch: ModelArch) -> Chain:
+    q, kv = arch.q_dim, arch.kv_dim
+    ops: list = [
+        SplitConcat("self_attn.qkv_proj.weight", ["self_attn.q_proj.weight", "self_attn.k_proj.weight",
+                                                  "self_attn.v_proj.weight"], lambda v: [q, kv, kv]),
+        SplitConcat("self_attn.qkv_proj.bias", ["self_attn.q_proj.bias", "self_attn.k_proj.bias",
+                                                "self_attn.v_proj.bias"], lambda v: [q, kv, kv]),
+        SplitConcat("mlp.experts.gate_up_proj", ["mlp.experts.gate_proj", "mlp.experts.up_proj"],
+                    lambda v: [v.shape[1] // 2, v.shape[1] // 2], dim=1),
+        SplitConcat("shared_experts.gate_up_proj.weight", ["shared_experts.gate_proj.weight",
+                                                           "shared_experts.up_proj.weight"],
+                    lambda v: [v.shape[0] // 2, v.shape[0] // 2]),
+        SplitConcat("mlp.gate_up_proj.weight", ["mlp.gate_proj.weight", "mlp.up_proj.weight"],
+                    lambda v: [v.shape[0] // 2, v.shape[0] // 2]),
+    ]
+    return Chain(ops)
+
+
+def prime_to_hf_chain(arch: ModelArch) -> Chain:
+    ops: list = []
+    if arch.is_moe:
+        ops += [
+            Rename(r"mlp\.router\.gate\.(weight|bias)$", r"mlp.gate.\1", r"mlp\.gate\.(weight|bias)$",
+                   r"mlp.router.gate.\1"),
+            Rename(r"mlp\.router\.e_score_correction_bias$", r"mlp.gate.e_score_correction_bias",
+                   r"mlp\.gate\.e_score_correction_bias$", r"mlp.router.e_score_correction_bias"),
+            StackExperts("mlp.experts.gate_proj", "mlp.experts.{e}.gate_proj.weight"),
+            StackExperts("mlp.experts.up_proj", "mlp.experts.{e}.up_proj.weight"),
+            StackExperts("mlp.experts.down_proj", "mlp.experts.{e}.down_proj.weight"),
+        ]
+    return Chain(ops)
+
+
+def native_to_prime(sd: StateDict, arch: ModelArch) -> StateDict:
+    return native_to_prime_chain(arch).forward(sd)
+
+
+def prime_to_native(sd: StateDict, arch: ModelArch) -> StateDict:
+    return native_to_prime_chain(arch).inverse(sd)
+
+
+def prime_to_hf(sd: StateDict, arch: ModelArch) -> StateDict:
+    sd = prime_to_hf_chain(arch).forward(sd)
+    if arch.tie_word_embeddings:
+        sd.pop("lm_head.weight", None)
+    return sd
+
+
+def hf_to_prime(sd: StateDict, arch: ModelArch) -> StateDict:
+    return prime_to_hf_chain(arch).inverse(sd)
+
+
+def native_to_hf(sd: StateDict, arch: ModelArch) -> StateDict:
+    return prime_to_hf(native_to_prime(sd, arch), arch)
+
+
+def hf_to_native(sd: StateDict, arch: ModelArch) -> StateDict:
+    return prime_to_native(hf_to_prime(sd, arch), arch)
+
+
+def model_state(model, layout: str = "prime", include_lora: bool = False) -> StateDict:
+    """State dict of a CausalLM in the requested layout (views, no copies where possible)."""
+    sd = {k: v for k, v in model.state_dict().items() if include_lora or "lora_" not in k}
+    if layout == "native":
+        return sd
+    sd = native_to_prime(sd, model.arch)
+    return sd if layout == "prime" else prime_to_hf(sd, model.arch)
+
+
+@torch.no_grad()
+def load_model_state(model, sd: StateDict, layout: str = "prime", strict: bool = True) -> None:
+    arch = model.arch
+    if layout == "hf":
+        sd = hf_to_prime(sd, arch)
+    if layout in ("hf", "prime"):
+        sd = prime_to_native(sd, arch)
+    own = model.state_dict()
+    missing = [k for k in own if k not in sd and "lora_" not in k and not k.endswith("inv_freq")]
+    unexpected = [k for k in sd if k not in own]
+    if strict and (missing or unexpected):
+        raise KeyError(f"state dict mismatch: missing={missing[:5]} unexpected={unexpected[:5]}")
+    for k, v in sd.items():
+        if k in own:
+            own[k].copy_(v.to(own[k].dtype))
+
+
+# ---------------------------------------------------------------------- LoRA adapters (PEFT layout)
+def lora_to_peft(model) -> StateDict:
+    """Adapter tensors under PEFT names ``base_model.model.<module>.lora_{A,B}.weight``; fused
+    projections are split back into their members; experts keep a leading ``[E]`` dim."""
+    out: StateDict = {}
+    from .layers import LoRAAdapter
+
+    for name, mod in model.named_modules():
+        if not isinstance(mod, LoRAAdapter):
+            continue
+        owner = name.rsplit(".", 1)[0]                      # module that holds the adapter
+        parent = owner.rsplit(".", 1)[0] if "." in owner else ""
+        is_expert = name.endswith("lora_gate_up") or name.endswith("lora_down")
+        r = mod.rank
+        for s, member in enumerate(mod.names):
+            a = mod.lora_A[..., s * r:(s + 1) * r, :]
+            b = mod.lora_B[s]
+            target = f"{owner}.{member}" if is_expert else f"{parent}.{member}"
+            out[f"base_model.model.{target}.lora_A.weight"] = a.detach()
+            out[f"base_model.model.{target}.lora_B.weight"] = b.detach()
+    return out

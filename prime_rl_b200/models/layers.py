@@ -1,0 +1,304 @@
+"""Decoder building blocks. Activations are packed token-major (``[T, ...]``, one row per
+token of the packed micro-batch); document structure travels in ``SeqInfo``.
+
+Projections are stored fused (``qkv_proj``, ``gate_up_proj``) because that is how the
+kernels consume them; ``models/convert.py`` maps to and from the canonical per-projection
+names that checkpoints use (the reference does the same with state-dict hooks,
+src/prime_rl/trainer/models/fusions.py:47-67).
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from ..ops import activation as act_ops
+from ..ops import attention as attn_ops
+from ..ops import lora as lora_ops
+from ..ops import moe as moe_ops
+from .config import ModelArch
+
+
+@dataclass
+class SeqInfo:
+    """Document layout of one packed micro-batch."""
+
+    cu_seqlens: torch.Tensor      # int32 [num_docs + 1]
+    max_seqlen: int
+    position_ids: torch.Tensor    # int32 [T]
+    # optional per-layer expert ids captured by the rollout engine ([T, layers, k])
+    routed_experts: torch.Tensor | None = None
+    cp: object | None = None      # context-parallel state (parallel/cp.py)
+
+    @classmethod
+    def from_lengths(cls, lengths: list[int], device) -> "SeqInfo":
+        cu = torch.zeros(len(lengths) + 1, dtype=torch.int32)
+        cu[1:] = torch.tensor(lengths, dtype=torch.int32).cumsum(0)
+        pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lengths]) if lengths else torch.zeros(0, dtype=torch.int32)
+        return cls(cu.to(device), max(lengths) if lengths else 0, pos.to(device))
+
+
+def _init(t: torch.Tensor, std: float) -> torch.Tensor:
+    return nn.init.normal_(t, mean=0.0, std=std)
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, dim: int, eps: float, dtype=None, device=None):
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype, device=device))
+
+    def forward(self, x):
+        return ops.rms_norm(x, self.weight, self.eps)
+
+
+class LoRAAdapter(nn.Module):
+    """Rank-r adapter for a (possibly fused) projection: one (A, B) pair per segment.
+    ``lora_A`` is stored stacked ``[S*r, in]``; ``lora_B`` per segment ``[out_s, r]``
+    (``[E, ...]`` leading dim for experts)."""
+
+    def __init__(self, in_dim: int, seg_sizes: list[int], rank: int, alpha: float, names: list[str],
+                 num_experts: int | None = None, dtype=None, device=None):
+        super().__init__()
+        self.rank, self.scale, self.names, self.seg_sizes = rank, alpha / rank, names, seg_sizes
+        lead = () if num_experts is None else (num_experts,)
+        self.lora_A = nn.Parameter(torch.empty(*lead, len(seg_sizes) * rank, in_dim, dtype=dtype, device=device))
+        self.lora_B = nn.ParameterList(
+            [nn.Parameter(torch.zeros(*lead, s, rank, dtype=dtype, device=device)) for s in seg_sizes])
+        self.reset()
+
+    def reset(self, seed: int | None = None):
+        gen = None
+        if seed is not None:
+            gen = torch.Generator(device=self.lora_A.device).manual_seed(seed)
+        bound = 1.0 / math.sqrt(self.lora_A.shape[-1])
+        with torch.no_grad():
+            self.lora_A.uniform_(-bound, bound, generator=gen)
+            for b in self.lora_B:
+                b.zero_()
+
+
+class Linear(nn.Module):
+    """Bias-free (by default) projection ``[out, in]`` with an optional LoRA adapter."""
+
+    def __init__(self, in_dim: int, out_dim: int, bias: bool = False, std: float = 0.02, dtype=None, device=None):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(out_dim, in_dim, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(out_dim, dtype=dtype, device=device)) if bias else None
+        self.lora: LoRAAdapter | None = None
+        self.std = std
+
+    def reset_parameters(self):
+        _init(self.weight, self.std)
+        if self.bias is not None:
+            nn.init.zeros_(self.bias)
+
+    def forward(self, x):
+        if self.lora is not None:
+            y = lora_ops.lora_linear(x, self.weight, self.lora.lora_A, list(self.lora.lora_B), self.lora.scale)
+            return y if self.bias is None else y + self.bias
+        return ops.linear(x, self.weight, self.bias)
+
+
+class Attention(nn.Module):
+    def __init__(self, arch: ModelArch, layer_idx: int, attn_backend: str = "auto", dtype=None, device=None):
+        super().__init__()
+        self.arch, self.layer_idx, self.backend = arch, layer_idx, attn_backend
+        H, D = arch.hidden_size, arch.head_dim
+        self.nq, self.nkv, self.D = arch.num_attention_heads, arch.num_key_value_heads, D
+        std = arch.initializer_range
+        self.qkv_proj = Linear(H, arch.q_dim + 2 * arch.kv_dim, bias=arch.attention_bias, std=std, dtype=dtype,
+                               device=device)
+        self.o_proj = Linear(arch.q_dim, H, bias=arch.attention_bias and arch.model_type == "gpt_oss", std=std,
+                             dtype=dtype, device=device)
+        if arch.qk_norm:
+            self.q_norm = RMSNorm(D, arch.rms_norm_eps, dtype=dtype, device=device)
+            self.k_norm = RMSNorm(D, arch.rms_norm_eps, dtype=dtype, device=device)
+        else:
+            self.q_norm = self.k_norm = None
+        self.sinks = nn.Parameter(torch.zeros(self.nq, dtype=dtype, device=device)) if arch.attention_sinks else None
+        self.window = arch.layer_window(layer_idx)
+        self.register_buffer("inv_freq", ops.inv_freq(D, arch.rope_theta, device=device, rotary_dim=arch.rotary_dim),
+                             persistent=False)
+
+    def forward(self, x: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
+        T = x.shape[0]
+        qkv = self.qkv_proj(x)
+        q_dim, kv_dim = self.nq * self.D, self.nkv * self.D
+        q = qkv[:, :q_dim].view(T, self.nq, self.D)
+        k = qkv[:, q_dim:q_dim + kv_dim].view(T, self.nkv, self.D)
+        v = qkv[:, q_dim + kv_dim:].view(T, self.nkv, self.D)
+        qw = self.q_norm.weight if self.q_norm is not None else None
+        kw = self.k_norm.weight if self.k_norm is not None else None
+        q = ops.qknorm_rope(q, qw, seq.position_ids, self.inv_freq, self.arch.rms_norm_eps)
+        k = ops.qknorm_rope(k, kw, seq.position_ids, self.inv_freq, self.arch.rms_norm_eps)
+        if seq.cp is not None:
+            o = seq.cp.attention(q, k, v, seq, window=self.window, sinks=self.sinks, backend=self.backend)
+        else:
+            o = attn_ops.attention(q, k, v, seq.cu_seqlens, seq.max_seqlen, causal=True, window=self.window,
+                                   sinks=self.sinks, backend=self.backend)
+        return self.o_proj(o.reshape(T, q_dim))
+
+
+_ACT = {"silu": act_ops.SWIGLU, "swiglu_clamped": act_ops.SWIGLU_CLAMPED, "relu2": act_ops.RELU2}
+
+
+class DenseMLP(nn.Module):
+    def __init__(self, arch: ModelArch, intermediate: int | None = None, dtype=None, device=None):
+        super().__init__()
+        I = intermediate or arch.intermediate_size
+        self.act = _ACT[arch.hidden_act]
+        self.arch = arch
+        width = I if self.act == act_ops.RELU2 else 2 * I
+        self.gate_up_proj = Linear(arch.hidden_size, width, std=arch.initializer_range, dtype=dtype, device=device)
+        self.down_proj = Linear(I, arch.hidden_size, std=arch.initializer_range, dtype=dtype, device=device)
+
+    def forward(self, x):
+        gu = self.gate_up_proj(x)
+        return self.down_proj(ops.glu(gu, self.act, self.arch.swiglu_limit, self.arch.swiglu_alpha))
+
+
+class Router(nn.Module):
+    """Token-choice top-k router: gate projection (fp32 accumulate and output), softmax or
+    sigmoid scores, optional selection bias, optional replay of engine-chosen experts
+    (reference: TokenChoiceTopKRouter, src/prime_rl/trainer/models/layers/moe.py:182-322)."""
+
+    def __init__(self, arch: ModelArch, dtype=None, device=None):
+        super().__init__()
+        self.arch = arch
+        self.gate = Linear(arch.hidden_size, arch.num_experts, bias=arch.router_linear_bias,
+                           std=arch.initializer_range, dtype=dtype, device=device)
+        if arch.router_bias:
+            self.register_buffer("e_score_correction_bias", torch.zeros(arch.num_experts, dtype=torch.float32,
+                                                                        device=device))
+        else:
+            self.e_score_correction_bias = None
+        self.force_balanced = False
+
+    def forward(self, x: torch.Tensor, forced: torch.Tensor | None = None):
+        a = self.arch
+        if x.is_cuda and x.dtype == torch.bfloat16:
+            logits = _RouterLogits.apply(x, self.gate.weight)
+        else:
+            logits = (x.float() @ self.gate.weight.float().t())
+        if self.gate.bias is not None:
+            logits = logits + self.gate.bias.float()
+        if self.force_balanced and forced is None:
+            T = x.shape[0]
+            base = torch.arange(T, device=x.device)[:, None] * a.num_experts_per_tok
+            forced = ((base + torch.arange(a.num_experts_per_tok, device=x.device)[None, :]) % a.num_experts)
+        idx, w, counts = moe_ops.route_topk(logits, a.num_experts_per_tok, score_func=a.score_func,
+                                            norm_topk=a.norm_topk_prob, route_scale=a.routed_scaling_factor,
+                                            sel_bias=self.e_score_correction_bias, forced=forced)
+        return idx, w, counts, logits
+
+
+class _RouterLogits(torch.autograd.Function):
+    """bf16 operands, fp32 accumulate, fp32 logits (the reference's moe_router_dtype=float32)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        return ops.gemm(x, w, out_dtype=torch.float32)
+
+    @staticmethod
+    def backward(ctx, dlogits):
+        x, w = ctx.saved_tensors
+        dl = dlogits.to(torch.bfloat16)
+        dx = ops.gemm(dl, w, b_mn=True) if ctx.needs_input_grad[0] else None
+        dw = ops.gemm(dl, x, a_mn=True, b_mn=True) if ctx.needs_input_grad[1] else None
+        return dx, dw
+
+
+class GroupedExperts(nn.Module):
+    """Stacked expert weights ``gate_up_proj [E, 2I, H]`` and ``down_proj [E, H, I]``."""
+
+    def __init__(self, arch: ModelArch, num_local_experts: int | None = None, dtype=None, device=None):
+        super().__init__()
+        self.arch = arch
+        E = num_local_experts or arch.num_experts
+        I, H = arch.moe_intermediate_size, arch.hidden_size
+        self.act = _ACT[arch.hidden_act]
+        width = I if self.act == act_ops.RELU2 else 2 * I
+        self.gate_up_proj = nn.Parameter(torch.empty(E, width, H, dtype=dtype, device=device))
+        self.down_proj = nn.Parameter(torch.empty(E, H, I, dtype=dtype, device=device))
+        self.lora_gate_up: LoRAAdapter | None = None
+        self.lora_down: LoRAAdapter | None = None
+
+    def reset_parameters(self):
+        _init(self.gate_up_proj, self.arch.initializer_range)
+        _init(self.down_proj, self.arch.initializer_range)
+
+    def forward(self, xp: torch.Tensor, block_expert: torch.Tensor, expert_offset: torch.Tensor) -> torch.Tensor:
+        if self.lora_gate_up is not None:
+            l = self.lora_gate_up
+            gu = lora_ops.lora_grouped_linear(xp, self.gate_up_proj, l.lora_A, list(l.lora_B), l.scale, block_expert,
+                                              expert_offset)
+        else:
+            gu = ops.grouped_linear(xp, self.gate_up_proj, block_expert, expert_offset)
+        h = ops.glu(gu, self.act, self.arch.swiglu_limit, self.arch.swiglu_alpha)
+        if self.lora_down is not None:
+            l = self.lora_down
+            return lora_ops.lora_grouped_linear(h, self.down_proj, l.lora_A, list(l.lora_B), l.scale, block_expert,
+                                                expert_offset)
+        return ops.grouped_linear(h, self.down_proj, block_expert, expert_offset)
+
+
+class MoE(nn.Module):
+    """Router -> dispatch (local permute, or expert-parallel all-to-all) -> grouped experts
+    -> combine, plus optional shared experts."""
+
+    def __init__(self, arch: ModelArch, layer_idx: int, dtype=None, device=None):
+        super().__init__()
+        self.arch, self.layer_idx = arch, layer_idx
+        self.router = Router(arch, dtype=dtype, device=device)
+        self.experts = GroupedExperts(arch, dtype=dtype, device=device)
+        if arch.n_shared_experts > 0:
+            self.shared_experts = DenseMLP(arch, arch.moe_intermediate_size * arch.n_shared_experts, dtype=dtype,
+                                           device=device)
+        else:
+            self.shared_experts = None
+        self.dispatcher = None            # parallel/ep.py installs an expert-parallel dispatcher here
+        self.last_counts: torch.Tensor | None = None
+        self.last_router_stats: dict | None = None
+
+    def forward(self, x: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
+        T = x.shape[0]
+        forced = None
+        if seq.routed_experts is not None:
+            forced = seq.routed_experts[:, self.layer_idx, :].to(torch.int32)
+        idx, w, counts, logits = self.router(x, forced)
+        self.last_counts = counts
+        if self.dispatcher is not None:
+            y = self.dispatcher(self.experts, x, idx, w, counts)
+        else:
+            plan = moe_ops.build_plan(idx, counts, self.arch.num_experts)
+            xp = moe_ops.permute(x, plan)
+            yp = self.experts(xp, plan.block_expert, plan.expert_offset)
+            y = moe_ops.combine(yp, w, plan, T)
+        if self.shared_experts is not None:
+            y = y + self.shared_experts(x)
+        return y
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, arch: ModelArch, layer_idx: int, attn_backend: str = "auto", dtype=None, device=None):
+        super().__init__()
+        self.input_layernorm = RMSNorm(arch.hidden_size, arch.rms_norm_eps, dtype=dtype, device=device)
+        self.self_attn = Attention(arch, layer_idx, attn_backend, dtype=dtype, device=device)
+        self.post_attention_layernorm = RMSNorm(arch.hidden_size, arch.rms_norm_eps, dtype=dtype, device=device)
+        if arch.layer_is_moe(layer_idx):
+            self.mlp = MoE(arch, layer_idx, dtype=dtype, device=device)
+        else:
+            self.mlp = DenseMLP(arch, dtype=dtype, device=device)
+        self.is_moe = arch.layer_is_moe(layer_idx)
+
+    def forward(self, h: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
+        a = self.self_attn(self.input_layernorm(h), seq)
+        x, h = ops.add_rms_norm(a, h, self.post_attention_layernorm.weight, self.post_attention_layernorm.eps)
+        m = self.mlp(x, seq) if self.is_moe else self.mlp(x)
+        return h + m

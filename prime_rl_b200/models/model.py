@@ -1,0 +1,185 @@
+"""Causal LM over packed token streams, with the fused LM head, per-layer activation
+recomputation, LoRA injection and freezing helpers.
+
+The forward contract follows the reference's custom models (packed ``[1, T]`` ids with
+document boundaries; src/prime_rl/trainer/model.py:1040-1101): ``forward`` returns the
+final hidden states, ``logprobs_entropy`` the per-token label log-probabilities and
+entropies without materialising logits.
+"""
+
+from __future__ import annotations
+
+import re
+from typing import Iterable
+
+import torch
+import torch.nn as nn
+from torch.utils.checkpoint import checkpoint
+
+from .. import ops
+from .config import ModelArch
+from .layers import DecoderLayer, GroupedExperts, Linear, LoRAAdapter, MoE, RMSNorm, SeqInfo
+
+
+class DecoderStack(nn.Module):
+    def __init__(self, arch: ModelArch, attn_backend: str, dtype, device):
+        super().__init__()
+        self.embed_tokens = nn.Embedding(arch.vocab_size, arch.hidden_size, dtype=dtype, device=device)
+        self.layers = nn.ModuleList(
+            [DecoderLayer(arch, i, attn_backend, dtype=dtype, device=device) for i in range(arch.num_hidden_layers)])
+        self.norm = RMSNorm(arch.hidden_size, arch.rms_norm_eps, dtype=dtype, device=device)
+
+
+class CausalLM(nn.Module):
+    def __init__(self, arch: ModelArch, *, attn_backend: str = "auto", dtype=torch.bfloat16, device=None):
+        super().__init__()
+        self.arch = arch
+        self.model = DecoderStack(arch, attn_backend, dtype, device)
+        if arch.tie_word_embeddings:
+            self.lm_head = None
+        else:
+            self.lm_head = Linear(arch.hidden_size, arch.vocab_size, std=arch.initializer_range, dtype=dtype,
+                                  device=device)
+        self.ac_every: int | None = None       # recompute every n-th layer in backward (None = never)
+        self.layer_hooks = None                # parallel/fsdp.py installs gather/release hooks here
+
+    # ------------------------------------------------------------------ init
+    @torch.no_grad()
+    def init_weights(self, seed: int = 0):
+        """Seeded normal(0, initializer_range) for matrices, ones for norms."""
+        gen_dev = next(self.parameters()).device
+        gen = torch.Generator(device=gen_dev).manual_seed(seed)
+        std = self.arch.initializer_range
+        for name, p in self.named_parameters():
+            if "lora_" in name:
+                continue
+            if name.endswith("norm.weight") or name.endswith("layernorm.weight"):
+                p.fill_(1.0)
+            elif name.endswith(".bias") or name.endswith("sinks"):
+                p.zero_()
+            else:
+                p.normal_(0.0, std, generator=gen)
+        return self
+
+    @property
+    def output_weight(self) -> torch.Tensor:
+        return self.model.embed_tokens.weight if self.lm_head is None else self.lm_head.weight
+
+    # ------------------------------------------------------------------ forward
+    def _run_layer(self, layer: DecoderLayer, idx: int, h: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
+        if self.layer_hooks is not None:
+            return self.layer_hooks.run(layer, idx, h, seq)
+        return layer(h, seq)
+
+    def forward(self, input_ids: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
+        """input_ids: [T] (or [1, T]) packed ids -> final hidden states [T, H] (normed)."""
+        ids = input_ids.reshape(-1)
+        h = self.model.embed_tokens(ids)
+        for i, layer in enumerate(self.model.layers):
+            if self.ac_every is not None and self.training and i % self.ac_every == 0 and torch.is_grad_enabled():
+                h = checkpoint(self._run_layer, layer, i, h, seq, use_reentrant=False)
+            else:
+                h = self._run_layer(layer, i, h, seq)
+        return self.model.norm(h)
+
+    def logprobs_entropy(self, hidden: torch.Tensor, labels: torch.Tensor,
+                         inv_temperature: torch.Tensor | None = None):
+        """Per-token log-probability of ``labels`` and entropy, fp32 [T]."""
+        w = self.output_weight
+        if self.lm_head is not None and self.lm_head.lora is not None:
+            raise NotImplementedError("LoRA on lm_head is not supported with the fused head")
+        return ops.fused_logprob_entropy(hidden, w, labels.reshape(-1), inv_temperature)
+
+    def logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        return ops.linear(hidden, self.output_weight)
+
+    # ------------------------------------------------------------------ MoE helpers
+    def moe_layers(self) -> Iterable[MoE]:
+        for layer in self.model.layers:
+            if isinstance(layer.mlp, MoE):
+                yield layer.mlp
+
+    def load_balance_stats(self) -> dict[str, torch.Tensor]:
+        """max-violation of the per-expert token share, averaged over MoE layers (the
+        reference's ``max_vio`` metric)."""
+        vios = []
+        for m in self.moe_layers():
+            if m.last_counts is None:
+                continue
+            c = m.last_counts.float()
+            vios.append((c.max() - c.mean()) / c.mean().clamp_min(1.0))
+        if not vios:
+            return {}
+        return {"max_vio": torch.stack(vios).mean()}
+
+
+# ---------------------------------------------------------------------- LoRA / freezing
+def _matches(name: str, patterns: list[str]) -> bool:
+    parts = name.split(".")
+    for pat in patterns:
+        if pat in parts or re.search(pat, name):
+            return True
+    return False
+
+
+_FUSED_MEMBERS = {"qkv_proj": ["q_proj", "k_proj", "v_proj"], "gate_up_proj": ["gate_proj", "up_proj"]}
+
+
+def apply_lora(model: CausalLM, rank: int, alpha: float, target_modules: list[str],
+               modules_to_save: list[str] | None = None, seed: int = 0) -> list[str]:
+    """Freezes the base model and attaches adapters to every targeted projection. A fused
+    projection gets one adapter segment per member that is targeted; members that are not
+    targeted keep a zero-width contribution. Returns the names of adapted modules."""
+    arch = model.arch
+    for p in model.parameters():
+        p.requires_grad_(False)
+    adapted: list[str] = []
+    dtype = next(model.parameters()).dtype
+    device = next(model.parameters()).device
+    for name, mod in model.named_modules():
+        leaf = name.split(".")[-1]
+        if isinstance(mod, Linear) and leaf not in ("gate", "lm_head"):
+            members = _FUSED_MEMBERS.get(leaf, [leaf])
+            full = [name.rsplit(".", 1)[0] + "." + m if "." in name else m for m in members]
+            if not all(_matches(f, target_modules) for f in full):
+                if any(_matches(f, target_modules) for f in full):
+                    raise ValueError(f"{name}: LoRA must target all of {members} or none (fused projection)")
+                continue
+            if leaf == "qkv_proj":
+                segs = [arch.q_dim, arch.kv_dim, arch.kv_dim]
+            elif leaf == "gate_up_proj":
+                half = mod.weight.shape[0] // 2
+                segs = [half, half]
+            else:
+                segs = [mod.weight.shape[0]]
+            mod.lora = LoRAAdapter(mod.weight.shape[1], segs, rank, alpha, members, dtype=dtype, device=device)
+            adapted.append(name)
+        elif isinstance(mod, GroupedExperts) and _matches(name, target_modules):
+            E, width, H = mod.gate_up_proj.shape
+            segs = [width // 2, width // 2] if width == 2 * arch.moe_intermediate_size else [width]
+            mod.lora_gate_up = LoRAAdapter(H, segs, rank, alpha, ["gate_proj", "up_proj"][: len(segs)],
+                                           num_experts=E, dtype=dtype, device=device)
+            mod.lora_down = LoRAAdapter(mod.down_proj.shape[2], [H], rank, alpha, ["down_proj"], num_experts=E,
+                                        dtype=dtype, device=device)
+            adapted.append(name)
+    # deterministic adapter init, identical on every data-parallel replica
+    for i, (name, mod) in enumerate((n, m) for n, m in model.named_modules() if isinstance(m, LoRAAdapter)):
+        mod.reset(seed=seed * 100003 + i)
+    for name, p in model.named_parameters():
+        if "lora_" in name or (modules_to_save and _matches(name, modules_to_save)):
+            p.requires_grad_(True)
+    return adapted
+
+
+def freeze_router(model: CausalLM) -> None:
+    for m in model.moe_layers():
+        for p in m.router.parameters():
+            p.requires_grad_(False)
+
+
+def build_model(arch: ModelArch, *, device, dtype=torch.bfloat16, attn_backend: str = "auto", seed: int = 0,
+                init: bool = True) -> CausalLM:
+    model = CausalLM(arch, attn_backend=attn_backend, dtype=dtype, device=device)
+    if init:
+        model.init_weights(seed)
+    return model

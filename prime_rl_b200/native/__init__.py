@@ -1,0 +1,89 @@
+"""ctypes bindings for the in-tree native libraries.
+
+``cuda()`` returns the sm_100a kernel library, ``cpu()`` the C++ CPU optimizer library. Both
+raise a clear error when the shared object is missing instead of falling back silently: on
+a GPU machine the hand-written kernels are the only implementation of the CUDA path.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from functools import lru_cache
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+CUDA_LIB = HERE / "libprb200_cuda.so"
+CPU_LIB = HERE / "libprb200_cpu.so"
+
+P, I, L, F = c_void_p, c_int, c_longlong, c_float
+
+_CUDA_SIGNATURES = {
+    # name: argtypes (restype is always int)
+    "prb_gemm_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, F, F, P, I, I, I, P, P],
+    "prb_gemm_bf16_kgrouped": [P, P, P, I, I, L, L, L, L, I, F, F, P, I, P, P],
+    "prb_lmhead_num_splits": [I, I],
+    "prb_lmhead_fwd": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, L, L, I, P, P],
+    "prb_lmhead_bwd_dlogits": [P, P, P, P, P, P, P, I, I, I, L, L, L, P, P],
+    "prb_rmsnorm_fwd": [P, P, P, P, P, P, L, I, F, P],
+    "prb_rmsnorm_bwd_parts": [L],
+    "prb_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, L, I, P],
+    "prb_qknorm_rope": [P, P, P, P, P, P, P, P, L, I, I, L, L, F, I, P],
+    "prb_glu_fwd": [P, P, P, L, I, L, L, I, F, F, P],
+    "prb_glu_bwd": [P, P, P, P, P, L, I, L, L, L, I, F, F, P],
+    "prb_sumsq": [P, L, I, P, P],
+    "prb_clip_coef": [P, F, P, P, P],
+    "prb_adamw": [P, P, P, P, I, P, L, P, F, F, F, F, F, P, P],
+    "prb_rl_loss": [P, P, P, P, P, P, L, I, F, F, F, F, P, P],
+    "prb_router_topk": [P, P, P, P, P, P, P, L, I, I, I, I, F, P],
+    "prb_moe_plan": [P, P, P, P, P, P, P, P, L, I, I, I, I, P],
+    "prb_moe_gather_rows": [P, P, P, P, L, I, I, P, P],
+    "prb_moe_combine": [P, P, P, P, P, L, I, I, P],
+    "prb_moe_combine_bwd_w": [P, P, P, P, L, I, I, P],
+}
+
+
+class NativeLibraryMissing(RuntimeError):
+    pass
+
+
+def _load(path: Path, signatures: dict) -> ctypes.CDLL:
+    if not path.exists():
+        raise NativeLibraryMissing(
+            f"{path.name} is not built. Run `python -m prime_rl_b200.native.build` "
+            "(needs nvcc / g++); the CUDA path has no eager fallback."
+        )
+    lib = ctypes.CDLL(str(path))
+    for name, argtypes in signatures.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError:
+            continue  # optional symbol; looked up lazily by callers that need it
+        fn.argtypes = argtypes
+        fn.restype = c_int
+    return lib
+
+
+@lru_cache(maxsize=None)
+def cuda() -> ctypes.CDLL:
+    return _load(CUDA_LIB, _CUDA_SIGNATURES)
+
+
+@lru_cache(maxsize=None)
+def cpu() -> ctypes.CDLL:
+    from .cpu_signatures import CPU_SIGNATURES
+
+    return _load(CPU_LIB, CPU_SIGNATURES)
+
+
+def cuda_available() -> bool:
+    return CUDA_LIB.exists()
+
+
+def register(name: str, argtypes: list) -> None:
+    """Declare the signature of an additional exported symbol (used by optional kernels)."""
+    _CUDA_SIGNATURES[name] = argtypes
+    if cuda.cache_info().currsize:
+        fn = getattr(cuda(), name)
+        fn.argtypes = argtypes
+        fn.restype = c_int

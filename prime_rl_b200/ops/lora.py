@@ -1,0 +1,169 @@
+"""LoRA-adapted linear layers with the adapter GEMMs fused into the base projection's output.
+
+``lora_linear``          y = x W^T + scale * sum_s (x A_s^T) B_s^T written into the column
+                         segment of s (a fused qkv / gate_up projection has one adapter per
+                         original projection, as the reference's per-module LoRA has);
+``lora_grouped_linear``  the same per expert over the permuted 128-row-block row space
+                         (the reference's MultiLoRAGroupedExperts,
+                         src/prime_rl/trainer/models/layers/lora/).
+
+The base weight is frozen (no weight gradient is formed); every product runs on the
+tcgen05 GEMM: the rank-r operands ride on TMA's out-of-bounds zero fill, and the adapter
+output is accumulated in the epilogue (``beta = 1``) instead of a separate add.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .matmul import gemm, grouped_gemm_ref
+from . import _runtime as rt
+
+
+def _segments(seg_sizes):
+    out, c = [], 0
+    for s in seg_sizes:
+        out.append((c, c + s))
+        c += s
+    return out
+
+
+def lora_linear_ref(x, w, a_cat, b_list, scale):
+    """Differentiable PyTorch reference. a_cat: [S*r, in]; b_list[s]: [out_s, r]."""
+    r = b_list[0].shape[1]
+    y = x @ w.to(x.dtype).t()
+    t = x @ a_cat.to(x.dtype).t()
+    parts = [t[..., s * r:(s + 1) * r] @ b.to(x.dtype).t() for s, b in enumerate(b_list)]
+    return y + scale * torch.cat(parts, dim=-1)
+
+
+class _LoRALinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, a_cat, scale, *b_list):
+        r = b_list[0].shape[1]
+        y = gemm(x, w)
+        t = gemm(x, a_cat)
+        for s, (c0, c1) in enumerate(_segments([b.shape[0] for b in b_list])):
+            gemm(t[:, s * r:(s + 1) * r], b_list[s], out=y[:, c0:c1], alpha=scale, beta=1.0)
+        ctx.save_for_backward(x, w, a_cat, t, *b_list)
+        ctx.scale = scale
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, a_cat, t, *b_list = ctx.saved_tensors
+        scale = ctx.scale
+        r = b_list[0].shape[1]
+        S = len(b_list)
+        if not dy.is_contiguous():
+            dy = dy.contiguous()
+        T = dy.shape[0]
+        dt = torch.empty(T, S * r, dtype=dy.dtype, device=dy.device)
+        db = []
+        for s, (c0, c1) in enumerate(_segments([b.shape[0] for b in b_list])):
+            dys = dy[:, c0:c1]
+            gemm(dys, b_list[s], b_mn=True, out=dt[:, s * r:(s + 1) * r], alpha=scale)
+            db.append(gemm(dys, t[:, s * r:(s + 1) * r], a_mn=True, b_mn=True, out_dtype=torch.float32,
+                           alpha=scale).to(b_list[s].dtype))
+        da = gemm(dt, x, a_mn=True, b_mn=True, out_dtype=torch.float32).to(a_cat.dtype)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy, w, b_mn=True)
+            gemm(dt, a_cat, b_mn=True, out=dx, beta=1.0)
+        return (dx, None, da, None, *db)
+
+
+def lora_linear(x, w, a_cat, b_list, scale: float):
+    """x: [..., in]; w: [out, in] frozen; a_cat: [S*r, in]; b_list: S tensors [out_s, r]."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        y = _LoRALinear.apply(x2, w, a_cat, float(scale), *b_list)
+        return y.reshape(*shape[:-1], w.shape[0])
+    return lora_linear_ref(x, w, a_cat, list(b_list), scale)
+
+
+def kgrouped_gemm(a: torch.Tensor, b: torch.Tensor, expert_offset: torch.Tensor, num_experts: int, *,
+                  alpha: float = 1.0, out_dtype=torch.float32) -> torch.Tensor:
+    """out[e] = alpha * a_e^T @ b_e over expert e's rows; a: [P, M], b: [P, N] -> [E, M, N]."""
+    M, N = a.shape[1], b.shape[1]
+    if a.is_cuda and a.dtype == torch.bfloat16:
+        out = torch.empty(num_experts, M, N, dtype=out_dtype, device=a.device)
+        status = rt.status_tensor(a.device)
+        rc = rt.lib().prb_gemm_bf16_kgrouped(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, a.shape[0],
+                                             a.stride(0), b.stride(0), N, int(out_dtype == torch.float32),
+                                             float(alpha), 0.0, expert_offset.data_ptr(), num_experts,
+                                             status.data_ptr(), rt.stream_ptr(a.device))
+        rt.check(rc, "prb_gemm_bf16_kgrouped")
+        return out
+    offs = expert_offset.tolist()
+    out = torch.zeros(num_experts, M, N, dtype=out_dtype, device=a.device)
+    for e in range(num_experts):
+        r0, r1 = offs[e], offs[e + 1]
+        if r1 > r0:
+            out[e] = (alpha * (a[r0:r1].float().t() @ b[r0:r1].float())).to(out_dtype)
+    return out
+
+
+def lora_grouped_linear_ref(x, w, a_cat, b_list, scale, block_expert):
+    r = b_list[0].shape[2]
+    y = grouped_gemm_ref(x, w, block_expert, out_dtype=torch.float32)
+    t = grouped_gemm_ref(x, a_cat, block_expert, out_dtype=torch.float32)
+    parts = [grouped_gemm_ref(t[:, s * r:(s + 1) * r].contiguous(), b, block_expert, out_dtype=torch.float32)
+             for s, b in enumerate(b_list)]
+    return (y + scale * torch.cat(parts, dim=-1)).to(x.dtype)
+
+
+class _LoRAGroupedLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, a_cat, scale, block_expert, expert_offset, *b_list):
+        r = b_list[0].shape[2]
+        y = gemm(x, w, block_expert=block_expert)
+        t = gemm(x, a_cat, block_expert=block_expert)
+        for s, (c0, c1) in enumerate(_segments([b.shape[1] for b in b_list])):
+            gemm(t[:, s * r:(s + 1) * r], b_list[s], block_expert=block_expert, out=y[:, c0:c1], alpha=scale,
+                 beta=1.0)
+        ctx.save_for_backward(x, w, a_cat, t, block_expert, expert_offset, *b_list)
+        ctx.scale = scale
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, a_cat, t, block_expert, expert_offset, *b_list = ctx.saved_tensors
+        scale = ctx.scale
+        E = w.shape[0]
+        r = b_list[0].shape[2]
+        S = len(b_list)
+        if not dy.is_contiguous():
+            dy = dy.contiguous()
+        P = dy.shape[0]
+        dt = torch.empty(P, S * r, dtype=dy.dtype, device=dy.device)
+        db = []
+        for s, (c0, c1) in enumerate(_segments([b.shape[1] for b in b_list])):
+            dys = dy[:, c0:c1]
+            gemm(dys, b_list[s], b_mn=True, block_expert=block_expert, out=dt[:, s * r:(s + 1) * r], alpha=scale)
+            db.append(kgrouped_gemm(dys, t[:, s * r:(s + 1) * r], expert_offset, E, alpha=scale)
+                      .to(b_list[s].dtype))
+        da = kgrouped_gemm(dt, x, expert_offset, E).to(a_cat.dtype)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy, w, b_mn=True, block_expert=block_expert)
+            gemm(dt, a_cat, b_mn=True, block_expert=block_expert, out=dx, beta=1.0)
+        return (dx, None, da, None, None, None, *db)
+
+
+def lora_grouped_linear(x, w, a_cat, b_list, scale: float, block_expert, expert_offset):
+    """x: [P, in] permuted rows; w: [E, out, in] frozen; a_cat: [E, S*r, in]; b_list[s]: [E, out_s, r]."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        return _LoRAGroupedLinear.apply(x, w, a_cat, float(scale), block_expert, expert_offset, *b_list)
+    # CPU: differentiable composition
+    from .matmul import grouped_linear
+
+    r = b_list[0].shape[2]
+    y = grouped_linear(x, w, block_expert, expert_offset)
+    t = grouped_linear(x, a_cat, block_expert, expert_offset)
+    parts = [grouped_linear(t[:, s * r:(s + 1) * r].contiguous(), b, block_expert, expert_offset)
+             for s, b in enumerate(b_list)]
+    return y + scale * torch.cat(parts, dim=-1)

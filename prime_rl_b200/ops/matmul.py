@@ -1,0 +1,179 @@
+"""bf16 GEMM front end (tcgen05 kernel in ``csrc/gemm.cu``) and the autograd linear layers
+built on it.
+
+``gemm(a, b, a_mn=..., b_mn=...)`` follows the kernel's operand convention:
+
+* ``a`` is ``[M, K]`` (K-major) or, with ``a_mn``, the stored tensor is ``[K, M]``;
+* ``b`` is ``[N, K]`` (K-major, the ``nn.Linear`` weight layout) or, with ``b_mn``, ``[K, N]``.
+
+CPU tensors (and non-bf16 dtypes) run the PyTorch reference, which is also the oracle of
+the GPU tests.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _runtime as rt
+
+
+def gemm_ref(a, b, *, a_mn=False, b_mn=False, out_dtype=None, alpha=1.0, beta=0.0, out=None):
+    A = a.t() if a_mn else a
+    B = b if b_mn else b.t()
+    res = alpha * (A.float() @ B.float())
+    if beta != 0.0 and out is not None:
+        res = res + beta * out.float()
+    res = res.to(out_dtype or a.dtype)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    out: torch.Tensor | None = None,
+    out_dtype: torch.dtype | None = None,
+    alpha: float = 1.0,
+    beta: float = 0.0,
+    block_expert: torch.Tensor | None = None,
+    num_experts: int = 0,
+    b_rows_per_expert: int = 0,
+    n: int | None = None,
+    force_bn: int = 0,
+) -> torch.Tensor:
+    """C = alpha * A.B + beta * C. Grouped mode when ``block_expert`` is given: ``b`` is the
+    stacked expert weight ``[E, rows, cols]`` and ``n`` the output width."""
+    if not a.is_cuda or a.dtype != torch.bfloat16:
+        if block_expert is not None:
+            return grouped_gemm_ref(a, b, block_expert, b_mn=b_mn, out_dtype=out_dtype, n=n)
+        return gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=out_dtype, alpha=alpha, beta=beta, out=out)
+    assert a.dim() == 2 and a.stride(1) == 1 and b.stride(-1) == 1
+    M = a.shape[1] if a_mn else a.shape[0]
+    K = a.shape[0] if a_mn else a.shape[1]
+    grouped = block_expert is not None
+    if grouped:
+        assert b.dim() == 3 and b.is_contiguous()
+        num_experts = b.shape[0]
+        b_rows_per_expert = b.shape[1]
+        N = n if n is not None else (b.shape[2] if b_mn else b.shape[1])
+        kb = b.shape[1] if b_mn else b.shape[2]
+        ldb = b.shape[2]
+    else:
+        assert b.dim() == 2
+        N = b.shape[1] if b_mn else b.shape[0]
+        kb = b.shape[0] if b_mn else b.shape[1]
+        ldb = b.stride(0)
+    assert kb == K, f"reduction mismatch {kb} vs {K}"
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=a.device)
+        assert beta == 0.0
+    assert out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
+    status = rt.status_tensor(a.device)
+    rc = rt.lib().prb_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), ldb, out.stride(0),
+        int(a_mn), int(b_mn), int(out.dtype == torch.float32), float(alpha), float(beta),
+        rt.ptr(block_expert), int(num_experts), int(b_rows_per_expert), int(force_bn),
+        status.data_ptr(), rt.stream_ptr(a.device),
+    )
+    rt.check(rc, "prb_gemm_bf16")
+    return out
+
+
+def grouped_gemm_ref(a, w, block_expert, *, b_mn=False, out_dtype=None, n=None):
+    """Rows of ``a`` come in 128-row blocks owned by ``block_expert[blk]`` (-1 = unused)."""
+    E = w.shape[0]
+    N = n if n is not None else (w.shape[2] if b_mn else w.shape[1])
+    out = torch.zeros(a.shape[0], N, dtype=out_dtype or a.dtype, device=a.device)
+    be = block_expert.tolist()
+    for blk, e in enumerate(be):
+        if e < 0 or e >= E:
+            continue
+        rows = slice(blk * 128, min((blk + 1) * 128, a.shape[0]))
+        W = w[e].float() if b_mn else w[e].float().t()
+        out[rows] = (a[rows].float() @ W).to(out.dtype)
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    """y = x @ w^T with all three GEMMs on the tcgen05 kernel."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm(x2, w)
+        return y.reshape(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn=True).reshape(x.shape)
+        if ctx.needs_input_grad[1]:
+            x2 = x.reshape(-1, x.shape[-1])
+            dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype)
+        return dx, dw
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        if not x.is_contiguous():
+            x = x.contiguous()
+        y = _Linear.apply(x, w)
+    else:
+        y = torch.nn.functional.linear(x, w.to(x.dtype))
+    if bias is not None:
+        y = y + bias.to(y.dtype)
+    return y
+
+
+class _GroupedLinear(torch.autograd.Function):
+    """Per-expert y = x @ w[e]^T over 128-row blocks; x is the permuted, padded row space."""
+
+    @staticmethod
+    def forward(ctx, x, w, block_expert, expert_offset):
+        ctx.save_for_backward(x, w, block_expert, expert_offset)
+        return gemm(x, w, block_expert=block_expert)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, block_expert, expert_offset = ctx.saved_tensors
+        if not dy.is_contiguous():
+            dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy, w, b_mn=True, block_expert=block_expert)
+        if ctx.needs_input_grad[1]:
+            dw = grouped_wgrad(dy, x, expert_offset, w.shape[0])
+        return dx, dw, None, None
+
+
+def grouped_linear(x, w, block_expert, expert_offset):
+    return _GroupedLinear.apply(x, w, block_expert, expert_offset)
+
+
+def grouped_wgrad(dy: torch.Tensor, x: torch.Tensor, expert_offset: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """dW[e] = dY_e^T @ X_e over the (128-aligned) row range of each expert."""
+    E = num_experts
+    N, K = dy.shape[1], x.shape[1]
+    dw = torch.empty(E, N, K, dtype=x.dtype, device=x.device)
+    offs = expert_offset.tolist()
+    for e in range(E):
+        r0, r1 = offs[e], offs[e + 1]
+        if r1 <= r0:
+            dw[e].zero_()
+            continue
+        if x.is_cuda and x.dtype == torch.bfloat16:
+            gemm(dy[r0:r1], x[r0:r1], a_mn=True, b_mn=True, out=dw[e])
+        else:
+            dw[e] = (dy[r0:r1].float().t() @ x[r0:r1].float()).to(x.dtype)
+    return dw

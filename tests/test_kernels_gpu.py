@@ -1,0 +1,259 @@
+"""Numerics of the sm_100a kernels against fp32 PyTorch references of the same op."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from prime_rl_b200.ops import _runtime as rt  # noqa: E402
+from prime_rl_b200.ops import activation, lm_head, moe, norm, optim, rope
+from prime_rl_b200.ops import matmul as G  # noqa: E402
+
+DEV = "cuda"
+
+
+def _rand(*shape, scale=1.0):
+    return (torch.randn(*shape, device=DEV) * scale).to(torch.bfloat16)
+
+
+def _close(a, b, atol, rtol):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    assert bool((err <= tol).all()), f"max err {err.max().item():.4g} (tol {atol}+{rtol}*|ref|), shape {tuple(a.shape)}"
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 512), (1000, 520, 264), (77, 72, 40), (4096, 2048, 1024)])
+def test_gemm_layouts(M, N, K, a_mn, b_mn):
+    if a_mn and M % 8:
+        pytest.skip("MN-major A needs a 16-byte row pitch")
+    if b_mn and N % 8:
+        pytest.skip("MN-major B needs a 16-byte row pitch")
+    a = _rand(K, M) if a_mn else _rand(M, K)
+    b = _rand(K, N) if b_mn else _rand(N, K)
+    ref = G.gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    out = G.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    rt.check_status()
+    _close(out, ref, atol=1e-2 * K ** 0.5 / 8, rtol=1e-2)
+    out_bf = G.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    rt.check_status()
+    _close(out_bf, ref, atol=0.02 * K ** 0.5, rtol=2e-2)
+
+
+@pytest.mark.parametrize("bn", [64, 128, 256])
+def test_gemm_tile_widths_and_beta(bn):
+    M, N, K = 640, 768, 320
+    a, b = _rand(M, K), _rand(N, K)
+    c0 = torch.randn(M, N, device=DEV)
+    ref = 0.5 * (a.float() @ b.float().t()) + 2.0 * c0
+    out = c0.clone()
+    G.gemm(a, b, out=out, alpha=0.5, beta=2.0, force_bn=bn)
+    rt.check_status()
+    _close(out, ref, atol=0.05, rtol=1e-2)
+
+
+def test_gemm_grouped_fwd_and_dgrad():
+    E, N, K = 6, 384, 256
+    counts = torch.tensor([130, 0, 5, 256, 127, 1], dtype=torch.int32)
+    padded = (counts + 127) // 128 * 128
+    P = int(padded.sum()) + 256
+    block_expert = torch.full((P // 128,), -1, dtype=torch.int32)
+    blk = 0
+    for e in range(E):
+        for _ in range(int(padded[e]) // 128):
+            block_expert[blk] = e
+            blk += 1
+    x = _rand(P, K)
+    w = _rand(E, N, K, scale=0.1)
+    be = block_expert.to(DEV)
+    ref = G.grouped_gemm_ref(x, w, block_expert, out_dtype=torch.float32)
+    out = G.gemm(x, w, block_expert=be, out_dtype=torch.float32)
+    rt.check_status()
+    used = blk * 128
+    _close(out[:used], ref[:used], atol=0.03, rtol=1e-2)
+    dy = _rand(P, N)
+    ref_dx = G.grouped_gemm_ref(dy, w, block_expert, b_mn=True, out_dtype=torch.float32)
+    dx = G.gemm(dy, w, b_mn=True, block_expert=be, out_dtype=torch.float32)
+    rt.check_status()
+    _close(dx[:used], ref_dx[:used], atol=0.05, rtol=1e-2)
+
+
+def test_linear_autograd():
+    x = _rand(300, 512).requires_grad_()
+    w = _rand(384, 512, scale=0.05).requires_grad_()
+    y = G.linear(x, w)
+    dy = _rand(300, 384)
+    y.backward(dy)
+    rt.check_status()
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    yr = xr @ wr.t()
+    yr.backward(dy.float())
+    _close(y, yr, atol=0.05, rtol=2e-2)
+    _close(x.grad, xr.grad, atol=0.05, rtol=2e-2)
+    _close(w.grad, wr.grad, atol=0.3, rtol=2e-2)
+
+
+@pytest.mark.parametrize("T,V,H", [(256, 1024, 256), (300, 5000, 512), (1024, 32000, 1024)])
+def test_fused_lm_head(T, V, H):
+    h = _rand(T, H).requires_grad_()
+    w = _rand(V, H, scale=0.05).requires_grad_()
+    labels = torch.randint(0, V, (T,), device=DEV)
+    labels[::7] = -100
+    inv_temp = (0.5 + torch.rand(T, device=DEV))
+    lp, ent = lm_head.fused_logprob_entropy(h, w, labels, inv_temp)
+    rt.check_status()
+    g = torch.randn(T, device=DEV)
+    (lp * g).sum().backward()
+    rt.check_status()
+    hr = h.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    lpr, entr = lm_head.logprob_entropy_ref(hr, wr, labels, inv_temp)
+    (lpr * g).sum().backward()
+    _close(lp, lpr, atol=2e-2, rtol=1e-2)
+    _close(ent, entr, atol=2e-2, rtol=1e-2)
+    _close(h.grad, hr.grad, atol=2e-2, rtol=5e-2)
+    _close(w.grad, wr.grad, atol=2e-2, rtol=5e-2)
+
+
+@pytest.mark.parametrize("rows,cols", [(33, 256), (1000, 2048), (257, 4096), (64, 128), (50, 1024)])
+def test_rmsnorm(rows, cols):
+    x = _rand(rows, cols).requires_grad_()
+    w = (1 + 0.1 * torch.randn(cols, device=DEV)).to(torch.bfloat16).requires_grad_()
+    y = norm.rms_norm(x, w, 1e-6)
+    dy = _rand(rows, cols)
+    y.backward(dy)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = norm.rms_norm_ref(xr, wr, 1e-6)
+    yr.backward(dy.float())
+    _close(y, yr, atol=2e-2, rtol=1e-2)
+    _close(x.grad, xr.grad, atol=3e-2, rtol=2e-2)
+    _close(w.grad, wr.grad, atol=0.05 * rows ** 0.5, rtol=2e-2)
+
+
+def test_add_rmsnorm():
+    rows, cols = 300, 2048
+    x, r = _rand(rows, cols).requires_grad_(), _rand(rows, cols).requires_grad_()
+    w = (1 + 0.1 * torch.randn(cols, device=DEV)).to(torch.bfloat16).requires_grad_()
+    y, h = norm.add_rms_norm(x, r, w, 1e-6)
+    dy, dh = _rand(rows, cols), _rand(rows, cols)
+    (y * dy).sum().backward(retain_graph=True)
+    gx_y = x.grad.clone()
+    x.grad = None
+    r.grad = None
+    w.grad = None
+    torch.autograd.backward([y, h], [dy, dh])
+    xr, rr, wr = (t.detach().float().requires_grad_() for t in (x, r, w))
+    hr = (xr + rr)
+    yr = norm.rms_norm_ref(hr.to(torch.bfloat16).float(), wr, 1e-6)
+    torch.autograd.backward([yr, hr], [dy.float(), dh.float()])
+    _close(y, yr, atol=3e-2, rtol=2e-2)
+    _close(h, hr, atol=2e-2, rtol=1e-2)
+    _close(x.grad, xr.grad, atol=5e-2, rtol=2e-2)
+    _close(r.grad, xr.grad, atol=5e-2, rtol=2e-2)
+    assert gx_y is not None
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("with_norm", [True, False])
+def test_qknorm_rope(D, with_norm):
+    T, Hh = 200, 6
+    x = _rand(T, Hh, D).requires_grad_()
+    w = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16).requires_grad_() if with_norm else None
+    pos = torch.randint(0, 4096, (T,), device=DEV, dtype=torch.int32)
+    inv_f = rope.inv_freq(D, 1e6, device=DEV)
+    y = rope.qknorm_rope(x, w, pos, inv_f, 1e-6)
+    dy = _rand(T, Hh, D)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_() if with_norm else None
+    yr = rope.qknorm_rope_ref(xr, wr, pos, inv_f, 1e-6)
+    yr.backward(dy.float())
+    _close(y, yr, atol=3e-2, rtol=2e-2)
+    _close(x.grad, xr.grad, atol=5e-2, rtol=3e-2)
+    if with_norm:
+        _close(w.grad, wr.grad, atol=0.6, rtol=3e-2)
+
+
+@pytest.mark.parametrize("act", [activation.SWIGLU, activation.SWIGLU_CLAMPED, activation.RELU2])
+def test_glu(act):
+    rows, I = 123, 768
+    width = I if act == activation.RELU2 else 2 * I
+    gu = _rand(rows, width, scale=2.0).requires_grad_()
+    y = activation.glu(gu, act)
+    dy = _rand(rows, I)
+    y.backward(dy)
+    gur = gu.detach().float().requires_grad_()
+    if act == activation.RELU2:
+        yr = activation.glu_ref(gur, None, act)
+    else:
+        yr = activation.glu_ref(gur[:, :I], gur[:, I:], act)
+    yr.backward(dy.float())
+    _close(y, yr, atol=3e-2, rtol=2e-2)
+    _close(gu.grad, gur.grad, atol=5e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("grad_dtype", [torch.float32, torch.bfloat16])
+def test_adamw_flat(grad_dtype):
+    n = 100003
+    p = torch.randn(n, device=DEV)
+    m = torch.randn(n, device=DEV) * 0.01
+    v = torch.rand(n, device=DEV) * 0.01
+    g = torch.randn(n, device=DEV).to(grad_dtype)
+    pr, mr, vr = p.clone(), m.clone(), v.clone()
+    lowp = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    step, lr, b1, b2, eps, wd = 3, 1e-3, 0.9, 0.95, 1e-8, 0.1
+    ss = torch.zeros(1, device=DEV)
+    optim.sumsq(g, ss)
+    coef, gnorm = optim.clip_coef(ss, 1.0)
+    hyper = torch.tensor([lr, 1 - b1 ** step, (1 - b2 ** step) ** 0.5], device=DEV)
+    optim.adamw_flat(p, m, v, g, lowp, hyper, b1=b1, b2=b2, eps=eps, wd=wd, clip=coef)
+    ref_norm = g.float().norm()
+    _close(gnorm, ref_norm.reshape(1), atol=1e-2, rtol=1e-4)
+    scale = min(1.0, 1.0 / (ref_norm.item() + 1e-6))
+    optim.adamw_ref(pr, mr, vr, g, lr=lr, b1=b1, b2=b2, eps=eps, wd=wd, step=step, grad_scale=scale)
+    _close(p, pr, atol=1e-5, rtol=1e-4)
+    _close(m, mr, atol=1e-6, rtol=1e-4)
+    _close(v, vr, atol=1e-7, rtol=1e-4)
+    _close(lowp, pr, atol=1e-2, rtol=1e-2)
+
+
+def test_moe_route_permute_combine():
+    T, E, k, H = 1000, 16, 4, 256
+    logits = torch.randn(T, E, device=DEV)
+    idx, w, counts, scores = moe.router_topk_cuda(logits, k)
+    idx_r, w_r, counts_r = moe.route_topk(logits.cpu(), k)
+    assert torch.equal(idx.cpu().sort(-1).values, idx_r.sort(-1).values)
+    assert torch.equal(counts.cpu(), counts_r)
+    _close(w.cpu().sort(-1).values, w_r.sort(-1).values, atol=1e-5, rtol=1e-4)
+    _close(scores.cpu(), torch.softmax(logits.cpu(), -1), atol=1e-5, rtol=1e-4)
+
+    for det in (False, True):
+        plan = moe.build_plan(idx, counts, E, deterministic=det)
+        x = _rand(T, H).requires_grad_()
+        wt = w.clone().requires_grad_()
+        xp = moe.permute(x, plan)
+        total = int(plan.total_rows.item())
+        assert total == int(((counts + 127) // 128 * 128).sum())
+        # every pair lands on a row that belongs to its expert and holds its token
+        slot = plan.slot.long()
+        offs = plan.expert_offset.long()
+        assert bool(((slot >= offs[idx.long()]) & (slot < offs[idx.long() + 1])).all())
+        assert torch.equal(xp[slot[:, 0]], x.detach())
+        rs = plan.row_src[:total]
+        assert bool((xp[:total][rs < 0] == 0).all())
+        be = plan.block_expert.cpu()
+        for b in range(total // 128):
+            assert offs[be[b]] <= b * 128 < offs[be[b] + 1]
+        assert bool((be[total // 128:] == -1).all())
+        y = moe.combine(xp * 1.0, wt, plan, T)
+        dy = _rand(T, H)
+        y.backward(dy)
+        xr = x.detach().float().requires_grad_()
+        wr = w.detach().clone().requires_grad_()
+        yr = (xr[:, None, :] * wr[:, :, None]).sum(1)
+        yr.backward(dy.float())
+        _close(y, yr, atol=3e-2, rtol=2e-2)
+        _close(x.grad, xr.grad, atol=5e-2, rtol=3e-2)
+        _close(wt.grad, wr.grad, atol=0.3, rtol=3e-2)
