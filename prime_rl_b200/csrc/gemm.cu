@@ -549,7 +549,9 @@ PRB_API int prb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, i
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
     return -4;  // TMA needs 16-byte aligned bases and row pitches
   const bool grouped = block_expert != nullptr;
-  if (grouped && b_mn && (b_rows_per_expert % kBK)) return -5;
+  // Grouped MN-major B with a reduction length that is not a multiple of 64: the last K
+  // slab of expert e also covers the first rows of expert e+1, but the matching columns of
+  // A lie past K and are zero-filled by TMA, so they contribute nothing (B must be finite).
   int bn = force_bn > 0 ? force_bn : (N > 128 ? 256 : (N > 64 ? 128 : 64));
   // prefer 128-wide tiles when 256 would leave most SMs idle
   if (force_bn <= 0 && bn == 256) {

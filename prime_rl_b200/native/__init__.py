@@ -20,6 +20,8 @@ P, I, L, F = c_void_p, c_int, c_longlong, c_float
 
 _CUDA_SIGNATURES = {
     # name: argtypes (restype is always int)
+    "prb_bind_device": [I],
+    "prb_sm_count": [],
     "prb_gemm_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, F, F, P, I, I, I, P, P],
     "prb_gemm_bf16_kgrouped": [P, P, P, I, I, L, L, L, L, I, F, F, P, I, P, P],
     "prb_lmhead_num_splits": [I, I],

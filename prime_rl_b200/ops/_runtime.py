@@ -31,7 +31,13 @@ def lib() -> ctypes.CDLL:
 
 
 def stream_ptr(device: torch.device | None = None) -> int:
-    return torch.cuda.current_stream(device).cuda_stream
+    """Current stream handle of ``device``; also binds the device's context to the calling
+    thread inside the native library (autograd worker threads start without one)."""
+    idx = device.index if device is not None and device.index is not None else torch.cuda.current_device()
+    rc = lib().prb_bind_device(idx)
+    if rc != 0:
+        raise KernelError(f"cannot bind CUDA device {idx} (code {rc})")
+    return torch.cuda.current_stream(idx).cuda_stream
 
 
 def ptr(t: torch.Tensor | None) -> int | None:
@@ -61,6 +67,16 @@ def check_status(device: torch.device | None = None) -> None:
             raise KernelError(f"device {idx}: {STATUS_NAMES.get(code, code)}")
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Number of native kernel-launching calls issued so far by this process."""
+    return _launches
+
+
 def check(rc: int, what: str) -> None:
+    global _launches
+    _launches += 1
     if rc != 0:
         raise KernelError(f"{what} failed with code {rc}")

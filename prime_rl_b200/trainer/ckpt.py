@@ -1,0 +1,117 @@
+"""Trainer checkpoints in torch DCP format.
+
+Layout ``<run_dir>/checkpoints/step_N/trainer/`` holding the DCP shards of
+``{"app": {"model", "optimizer", "progress"}}`` with model tensors under their *prime*
+names (per-projection, experts stacked), which is what the reference writes
+(src/prime_rl/trainer/ckpt.py:48-213) — runtime fusions never reach a checkpoint.
+Optimizer state is keyed by the same names. ``dataloader/rank_R.pt`` is written per rank.
+Retention follows ``keep_last`` / ``keep_interval``; only the master rank deletes.
+"""
+
+from __future__ import annotations
+
+import shutil
+from dataclasses import asdict, dataclass
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+import torch.distributed.checkpoint as dcp
+
+from ..models import convert
+from ..utils.logger import get_logger
+from ..utils.pathing import get_ckpt_dir, get_step_path, latest_step, list_steps
+
+
+@dataclass
+class Progress:
+    step: int = 0
+    total_tokens: int = 0
+    total_samples: int = 0
+
+
+def _optimizer_state_prime(optimizer, arch) -> dict:
+    """Optimizer tensors under prime names (fused parameters split like the weights)."""
+    sd = optimizer.state_dict()
+    out = {"step": torch.tensor(sd["step"])}
+    for key, named in sd["state"].items():
+        out[key] = convert.native_to_prime(dict(named), arch)
+    return out
+
+
+class CheckpointManager:
+    def __init__(self, run_dir: Path, config, *, is_master: bool = True, rank: int = 0):
+        self.run_dir, self.config, self.is_master, self.rank = run_dir, config, is_master, rank
+        self.ckpt_dir = get_ckpt_dir(Path(config.output_dir) if config and config.output_dir else run_dir)
+        self.saved_steps: list[int] = list_steps(self.ckpt_dir)
+
+    def step_path(self, step: int) -> Path:
+        return get_step_path(self.ckpt_dir, step) / "trainer"
+
+    def latest(self) -> int | None:
+        return latest_step(self.ckpt_dir)
+
+    # ------------------------------------------------------------------ save
+    def save(self, step: int, model, optimizer, progress: Progress, dataloader=None) -> Path:
+        path = self.step_path(step)
+        if self.is_master:
+            path.mkdir(parents=True, exist_ok=True)
+        if dist.is_initialized():
+            dist.barrier()
+        app = {"model": convert.model_state(model, "prime", include_lora=True)}
+        if not (self.config and self.config.skip_optimizer) and optimizer is not None:
+            app["optimizer"] = _optimizer_state_prime(optimizer, model.arch)
+        if not (self.config and self.config.skip_progress):
+            app["progress"] = {k: torch.tensor(v) for k, v in asdict(progress).items()}
+        dcp.save({"app": app}, checkpoint_id=str(path))
+        if dataloader is not None and hasattr(dataloader, "state_dict") and \
+                not (self.config and self.config.skip_dataloader):
+            dl = path / "dataloader"
+            dl.mkdir(parents=True, exist_ok=True)
+            torch.save(dataloader.state_dict(), dl / f"rank_{self.rank}.pt")
+        if dist.is_initialized():
+            dist.barrier()
+        if step not in self.saved_steps:
+            self.saved_steps.append(step)
+        get_logger().info(f"saved checkpoint step {step} to {path}")
+        return path
+
+    # ------------------------------------------------------------------ load
+    def load(self, step: int, model, optimizer, progress: Progress, dataloader=None, path: Path | None = None) -> None:
+        path = path or self.step_path(step)
+        if not path.exists():
+            raise FileNotFoundError(f"checkpoint not found: {path}")
+        app = {"model": convert.model_state(model, "prime", include_lora=True)}
+        has_opt = optimizer is not None and not (self.config and self.config.skip_optimizer)
+        if has_opt:
+            app["optimizer"] = _optimizer_state_prime(optimizer, model.arch)
+        if not (self.config and self.config.skip_progress):
+            app["progress"] = {k: torch.tensor(v) for k, v in asdict(progress).items()}
+        dcp.load({"app": app}, checkpoint_id=str(path))
+        # the prime-layout tensors are views of the live parameters / optimizer buffers, so
+        # the load above already landed in place; scalars are copied back here
+        if has_opt:
+            optimizer.step_count = int(app["optimizer"]["step"])
+            optimizer.buf.sync_from_master()
+        if "progress" in app:
+            for k, v in app["progress"].items():
+                setattr(progress, k, int(v))
+        dl = path / "dataloader" / f"rank_{self.rank}.pt"
+        if dataloader is not None and dl.exists() and hasattr(dataloader, "load_state_dict"):
+            dataloader.load_state_dict(torch.load(dl))
+        get_logger().info(f"loaded checkpoint {path}")
+
+    # ------------------------------------------------------------------ retention
+    def maybe_clean(self) -> None:
+        if not self.is_master or self.config is None:
+            return
+        keep_last, keep_interval = self.config.keep_last, self.config.keep_interval
+        if keep_last is None:
+            return
+        steps = sorted(self.saved_steps)
+        doomed = steps[:-keep_last] if keep_last else []
+        for s in doomed:
+            if keep_interval and s % keep_interval == 0:
+                continue
+            shutil.rmtree(get_step_path(self.ckpt_dir, s), ignore_errors=True)
+            self.saved_steps.remove(s)

@@ -1,0 +1,289 @@
+"""RL trainer: receives packed micro-batches, runs forward / fused logprob head / per-token
+loss / backward / optimizer step, then offers the new weights to the inference engine.
+
+``RLTrainer`` is the programmatic API (``setup()`` once, ``step()`` per optimizer step);
+``train(config)`` is the loop the ``trainer`` entrypoint and ``torchrun -m
+prime_rl_b200.trainer.rl.train @ trainer.toml`` run. Structure follows the reference's
+``train()`` (src/prime_rl/trainer/rl/train.py:74-749).
+"""
+
+from __future__ import annotations
+
+import gc
+import math
+import time
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+from ... import monitors as monitors_mod
+from ...configs.trainer import TrainerConfig
+from ...models import SeqInfo, apply_lora, build_model, freeze_router, resolve_arch
+from ...parallel import get_parallel_dims, get_world, setup_distributed
+from ...utils.logger import get_logger, setup_logger
+from ..ckpt import CheckpointManager, Progress
+from ..data import DataLoader, FakeDataLoader, TensorMicroBatch
+from ..loss import compute_loss, setup_rl_loss_fn, shift_left, shift_right
+from ..optim import setup_optimizer
+from ..perf import PerfCounter
+
+
+class RLTrainer:
+    def __init__(self, config: TrainerConfig, device: torch.device | None = None):
+        self.config = config
+        self.world = get_world()
+        self.device = device if device is not None else setup_distributed(timeout_seconds=config.dist_timeout_seconds)
+        self.logger = get_logger()
+        self.progress = Progress()
+        self.run_dir = Path(config.output_dir)
+        self.step_metrics: dict = {}
+
+    # ------------------------------------------------------------------ setup
+    def setup(self) -> "RLTrainer":
+        cfg, mc = self.config, self.config.model
+        self.arch = resolve_arch(mc.name, mc.arch)
+        if mc.debug.num_layers is not None:
+            self.arch = self.arch.model_copy(update={"num_hidden_layers": mc.debug.num_layers})
+        self.dims = get_parallel_dims(mc, self.world.world_size, is_moe=self.arch.is_moe,
+                                      num_experts=self.arch.num_experts)
+        dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+        self.monitor = monitors_mod.setup(cfg.monitors, self.run_dir, "trainer", is_master=self.world.is_master,
+                                          run_config=cfg.model_dump(mode="json"))
+        t0 = time.perf_counter()
+        self.model = build_model(self.arch, device=self.device, dtype=dtype, attn_backend=mc.attn, seed=0)
+        self._maybe_load_pretrained()
+        if mc.debug.force_balanced_routing:
+            for m in self.model.moe_layers():
+                m.router.force_balanced = True
+        if mc.lora is not None:
+            adapted = apply_lora(self.model, mc.lora.rank, mc.lora.alpha, mc.lora.target_modules,
+                                 mc.lora.modules_to_save)
+            self.logger.info(f"LoRA r={mc.lora.rank} on {len(adapted)} modules")
+        if mc.freeze_moe_router:
+            freeze_router(self.model)
+        if mc.ac is not None:
+            self.model.ac_every = mc.ac.freq
+        self.model.train()
+        self._setup_parallel()
+        self.loss_fn = setup_rl_loss_fn(cfg.loss)
+        self.optimizer = setup_optimizer(cfg.optim, self.model, max_steps=cfg.max_steps,
+                                         scheduler_config=cfg.scheduler, dp_group=self.dp_cp_group)
+        self.ckpt = CheckpointManager(self.run_dir, cfg.ckpt, is_master=self.world.is_master, rank=self.world.rank) \
+            if cfg.ckpt is not None or cfg.resume is not None else None
+        self._setup_data()
+        self._maybe_resume()
+        self.weight_sender = None
+        if cfg.data.fake is None:
+            from ...transports.weights import setup_weight_sender
+
+            self.weight_sender = setup_weight_sender(cfg.weight_broadcast, self.run_dir, self.world, self.model,
+                                                     lora=mc.lora is not None)
+        dev_name = torch.cuda.get_device_name(self.device) if self.device.type == "cuda" else "cpu"
+        self.perf = PerfCounter(self.arch, mc.seq_len, self.world.world_size, dev_name, lora=mc.lora is not None)
+        n_train = sum(p.numel() for p in self.model.parameters() if p.requires_grad)
+        n_all = sum(p.numel() for p in self.model.parameters())
+        self.logger.info(f"model {self.arch.model_type}: {n_all / 1e9:.2f}B params ({n_train / 1e6:.1f}M trainable), "
+                         f"setup {time.perf_counter() - t0:.1f}s, dims {self.dims}")
+        return self
+
+    def _maybe_load_pretrained(self) -> None:
+        mc = self.config.model
+        p = Path(mc.name)
+        if mc.debug.random_init or not p.is_dir():
+            return
+        from ..weights import load_hf_checkpoint
+
+        load_hf_checkpoint(self.model, p)
+
+    def _setup_parallel(self) -> None:
+        dims = self.dims
+        self.dp_cp_group = dims.group("dp_cp") if dist.is_initialized() else None
+        coords = dims.coords(self.world.rank)
+        self.dp_rank, self.cp_rank = coords["dp"], coords["cp"]
+        self.cp_ctx = None
+        if dims.cp_enabled:
+            from ...parallel.cp import ContextParallel
+
+            self.cp_ctx = ContextParallel(dims.group("cp"), dims.cp, self.cp_rank, style=self.config.model.cp_style)
+        if dims.ep_enabled:
+            from ...parallel.ep import install_expert_parallel
+
+            install_expert_parallel(self.model, dims, self.config.model.moe)
+        if dims.dp_shard_cp > 1 and self.config.model.lora is None:
+            from ...parallel.fsdp import shard_model
+
+            self.sharded = shard_model(self.model, dims, self.config.model)
+        else:
+            self.sharded = None
+
+    def _setup_data(self) -> None:
+        cfg = self.config
+        if cfg.data.fake is not None:
+            self.dataloader = FakeDataLoader(cfg.data.fake.batch_size, cfg.model.seq_len, self.dims.dp, self.dp_rank,
+                                             generate_samples=cfg.data.fake.generate_samples,
+                                             vocab_size=min(self.arch.vocab_size, 120000))
+        else:
+            self.dataloader = DataLoader(self.run_dir, self.progress.step, self.dims.dp, self.dp_rank,
+                                         cfg.rollout_transport)
+
+    def _maybe_resume(self) -> None:
+        cfg = self.config
+        if cfg.resume is None or self.ckpt is None:
+            return
+        if cfg.resume.dir is not None:
+            step, path = cfg.resume.dir_step, cfg.resume.dir / "trainer"
+        else:
+            step = cfg.resume.step if cfg.resume.step is not None else self.ckpt.latest()
+            path = None
+        if step is None:
+            self.logger.warning("resume requested but no checkpoint found; starting fresh")
+            return
+        self.ckpt.load(step, self.model, self.optimizer, self.progress, self.dataloader, path=path)
+        self.progress.step = step + 1 if not (cfg.ckpt and cfg.ckpt.skip_progress) else self.progress.step
+
+    # ------------------------------------------------------------------ one micro-batch
+    def forward_backward(self, mb: TensorMicroBatch, scales: tuple[float, float, float]) -> dict:
+        dev = self.device
+        mb = mb.to(dev)
+        ids = mb.input_ids
+        labels = shift_left(ids)
+        inv_temp = 1.0 / mb.temperatures
+        seq = SeqInfo(None, max(mb.sequence_lengths), mb.position_ids.to(torch.int32))
+        cu = torch.zeros(len(mb.sequence_lengths) + 1, dtype=torch.int32)
+        cu[1:] = torch.tensor(mb.sequence_lengths, dtype=torch.int32).cumsum(0)
+        seq.cu_seqlens = cu.to(dev, non_blocking=True)
+        if self.config.enable_router_replay:
+            if mb.routed_experts is None:
+                raise ValueError("router replay is enabled but the batch carries no routed_experts "
+                                 "(enable return_routed_experts on the inference side)")
+            seq.routed_experts = mb.routed_experts
+        if self.cp_ctx is not None:
+            ids, labels, inv_temp, seq = self.cp_ctx.shard_inputs(ids, labels, inv_temp, seq)
+        hidden = self.model(ids, seq)
+        logprobs, entropy = self.model.logprobs_entropy(hidden, labels, inv_temp)
+        if self.cp_ctx is not None:
+            logprobs, entropy = self.cp_ctx.gather_outputs(logprobs, entropy)
+        V = self.arch.vocab_size
+        logprobs = shift_right(logprobs, math.log(1.0 / V))
+        entropy = shift_right(entropy, math.log(float(V)))
+        loss, lm = compute_loss(
+            trainer_logprobs=logprobs, inference_logprobs=mb.inference_logprobs, advantages=mb.advantages,
+            loss_mask=mb.loss_mask, rl_loss_fn=self.loss_fn, rl_scale=scales[0], ce_scale=scales[1],
+            ref_kl_scale=scales[2], ref_logprobs=mb.ref_logprobs, rl_weights=mb.rl_weights, ce_weights=mb.ce_weights,
+            ref_kl_weights=mb.ref_kl_weights, sequence_lengths=mb.sequence_lengths)
+        loss.backward()
+        mask = mb.loss_mask
+        out = {"loss": loss.detach(), "entropy": (entropy * mask).sum() / mask.sum().clamp_min(1)}
+        out.update({k: v.detach() for k, v in lm.items()})
+        return out
+
+    # ------------------------------------------------------------------ one optimizer step
+    def step(self, micro_batches: list[TensorMicroBatch] | None = None) -> dict:
+        t_start = time.perf_counter()
+        if micro_batches is None:
+            self.dataloader.wait_for_batch()
+            t_wait = time.perf_counter() - t_start
+            micro_batches = self.dataloader.get_batch()
+        else:
+            t_wait = 0.0
+        counts = [0, 0, 0]
+        for mb in micro_batches:
+            for i, c in enumerate(mb.loss_token_counts()):
+                counts[i] += c
+        if dist.is_initialized() and self.world.world_size > 1:
+            t = torch.tensor(counts, dtype=torch.int64, device=self.device)
+            dist.all_reduce(t, group=self.dp_cp_group)
+            if self.dims.cp > 1:
+                t = t // self.dims.cp  # context-parallel ranks of a replica hold the same rows
+            counts = t.tolist()
+        scales = tuple(float(max(c, 1)) for c in counts)
+        t_fb = time.perf_counter()
+        agg: dict[str, list] = {}
+        for mb in micro_batches:
+            for k, v in self.forward_backward(mb, scales).items():
+                agg.setdefault(k, []).append(v)
+        self.optimizer.reduce_gradients()
+        grad_norm = self.optimizer.step()
+        lr = self.optimizer.schedule.lr_at(self.optimizer.step_count - 1)
+        self.optimizer.zero_grad()
+        metrics = {k: torch.stack(v).sum() if k == "loss" else torch.stack(v).mean() for k, v in agg.items()}
+        metrics["optim/grad_norm"] = grad_norm.reshape(())
+        metrics.update({f"moe/{k}": v for k, v in self.model.load_balance_stats().items()})
+        # one device->host read for the whole step
+        keys = list(metrics)
+        vals = torch.stack([metrics[k].float().reshape(()) for k in keys]).cpu().tolist()
+        out = dict(zip(keys, vals))
+        tokens = sum(mb.num_tokens for mb in micro_batches) * self.dims.dp
+        self.progress.total_tokens += tokens
+        self.progress.total_samples += sum(len(mb.sequence_lengths) for mb in micro_batches) * self.dims.dp
+        self.perf.count_tokens(tokens)
+        now = time.perf_counter()
+        out.update({"optim/lr": lr, "time/step": now - t_start, "time/wait_for_batch": t_wait,
+                    "time/forward_backward": now - t_fb, "perf/tokens": tokens})
+        tps = tokens / max(now - t_fb, 1e-9)
+        out["perf/throughput"] = tps
+        out["perf/throughput_per_gpu"] = tps / self.world.world_size
+        out["perf/mfu"] = self.perf.mfu(tps)
+        if self.device.type == "cuda":
+            out["perf/peak_memory"] = torch.cuda.max_memory_allocated(self.device) / 2 ** 30
+        self.step_metrics = out
+        return out
+
+    # ------------------------------------------------------------------ loop
+    def run(self) -> None:
+        cfg = self.config
+        if self.weight_sender is not None and self.progress.step == 0 or \
+                (self.weight_sender is not None and cfg.resume is not None):
+            # startup policy so that the (stateless) inference engine is seeded
+            self.weight_sender.broadcast(self.model, max(self.progress.step - 1, 0))
+        while cfg.max_steps is None or self.progress.step < cfg.max_steps:
+            step = self.progress.step
+            m = self.step()
+            if self.weight_sender is not None:
+                t0 = time.perf_counter()
+                self.weight_sender.broadcast(self.model, step)
+                m["time/broadcast_weights"] = time.perf_counter() - t0
+            if self.ckpt is not None and cfg.ckpt is not None and cfg.ckpt.interval and \
+                    (step + 1) % cfg.ckpt.interval == 0:
+                t0 = time.perf_counter()
+                self.ckpt.save(step, self.model, self.optimizer, self.progress, self.dataloader)
+                self.ckpt.maybe_clean()
+                m["time/save_ckpt"] = time.perf_counter() - t0
+            self.monitor.log(m, step)
+            if self.world.is_master:
+                self.logger.info(f"step {step} | loss {m['loss']:.4f} | entropy {m.get('entropy', 0):.3f} | "
+                                 f"grad_norm {m['optim/grad_norm']:.3f} | {m['perf/throughput']:.0f} tok/s | "
+                                 f"mfu {m['perf/mfu']:.1f}% | {m['time/step']:.2f}s")
+            self.progress.step += 1
+            if cfg.gc is not None and self.progress.step % cfg.gc.interval == 0:
+                gc.collect()
+        if self.ckpt is not None and cfg.ckpt is not None and self.progress.step > 0:
+            last = self.progress.step - 1
+            if last not in self.ckpt.saved_steps:
+                self.ckpt.save(last, self.model, self.optimizer, self.progress, self.dataloader)
+        self.monitor.finalize()
+
+
+def train(config: TrainerConfig) -> RLTrainer:
+    setup_logger(config.log.level, tag=f"trainer:{get_world().rank}", json_logging=config.log.json_logging)
+    trainer = RLTrainer(config).setup()
+    trainer.run()
+    return trainer
+
+
+def main(argv: list[str] | None = None) -> None:
+    from ...configs.base import cli
+
+    config = cli(TrainerConfig, argv)
+    if config.dry_run:
+        print(config.to_json())
+        return
+    train(config)
+    from ...parallel.world import cleanup
+
+    cleanup()
+
+
+if __name__ == "__main__":
+    main()

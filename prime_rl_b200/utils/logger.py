@@ -1,0 +1,52 @@
+"""Process-wide logger (loguru) with an optional JSON sink and stdlib interception."""
+
+from __future__ import annotations
+
+import logging
+import sys
+from pathlib import Path
+
+from loguru import logger as _logger
+
+_configured = False
+
+
+class _Intercept(logging.Handler):
+    def emit(self, record: logging.LogRecord) -> None:
+        try:
+            level = _logger.level(record.levelname).name
+        except ValueError:
+            level = record.levelno
+        _logger.opt(depth=6, exception=record.exc_info).log(level, record.getMessage())
+
+
+def setup_logger(level: str = "info", *, log_file: Path | None = None, json_logging: bool = False,
+                 tag: str | None = None, intercept_stdlib: bool = False):
+    """(Re)configures the global logger: console sink, optional per-process log file."""
+    global _configured
+    _logger.remove()
+    prefix = f"[{tag}] " if tag else ""
+    fmt = "<dim>{time:HH:mm:ss}</dim> <level>{level: <7}</level> " + prefix + "{message}"
+    if json_logging:
+        _logger.add(sys.stdout, level=level.upper(), serialize=True)
+    else:
+        _logger.add(sys.stdout, level=level.upper(), format=fmt, colorize=False)
+    if log_file is not None:
+        log_file.parent.mkdir(parents=True, exist_ok=True)
+        _logger.add(str(log_file), level=level.upper(), format=fmt, serialize=json_logging)
+    if intercept_stdlib:
+        logging.basicConfig(handlers=[_Intercept()], level=0, force=True)
+    _configured = True
+    return _logger
+
+
+def get_logger():
+    if not _configured:
+        setup_logger()
+    return _logger
+
+
+def reset_logger() -> None:
+    global _configured
+    _logger.remove()
+    _configured = False

@@ -113,8 +113,9 @@ def test_fused_lm_head(T, V, H):
     (lpr * g).sum().backward()
     _close(lp, lpr, atol=2e-2, rtol=1e-2)
     _close(ent, entr, atol=2e-2, rtol=1e-2)
-    _close(h.grad, hr.grad, atol=2e-2, rtol=5e-2)
-    _close(w.grad, wr.grad, atol=2e-2, rtol=5e-2)
+    # dlogits are rounded to bf16 before the two gradient GEMMs
+    _close(h.grad, hr.grad, atol=8e-2, rtol=5e-2)
+    _close(w.grad, wr.grad, atol=8e-2, rtol=5e-2)
 
 
 @pytest.mark.parametrize("rows,cols", [(33, 256), (1000, 2048), (257, 4096), (64, 128), (50, 1024)])
@@ -257,3 +258,76 @@ def test_moe_route_permute_combine():
         _close(y, yr, atol=3e-2, rtol=2e-2)
         _close(x.grad, xr.grad, atol=5e-2, rtol=3e-2)
         _close(wt.grad, wr.grad, atol=0.3, rtol=3e-2)
+
+
+def _blocks(counts):
+    padded = (counts + 127) // 128 * 128
+    offs = torch.zeros(len(counts) + 1, dtype=torch.int32)
+    offs[1:] = padded.cumsum(0)
+    P = int(offs[-1]) + 128
+    be = torch.full((P // 128,), -1, dtype=torch.int32)
+    for e in range(len(counts)):
+        be[int(offs[e]) // 128:int(offs[e + 1]) // 128] = e
+    return offs, be, P
+
+
+def test_gemm_kgrouped():
+    from prime_rl_b200.ops import lora
+    counts = torch.tensor([130, 0, 5, 256], dtype=torch.int32)
+    offs, be, P = _blocks(counts)
+    a, b = _rand(P, 200), _rand(P, 320)
+    out = lora.kgrouped_gemm(a, b, offs.to(DEV), 4, alpha=0.5)
+    rt.check_status()
+    ref = lora.kgrouped_gemm(a.cpu(), b.cpu(), offs, 4, alpha=0.5)
+    _close(out.cpu(), ref, atol=0.3, rtol=2e-2)
+    assert bool((out[1] == 0).all())
+
+
+def test_lora_linear_and_grouped():
+    from prime_rl_b200.ops import lora
+    T, IN, r = 300, 256, 16
+    segs = [384, 128, 128]
+    x = _rand(T, IN).requires_grad_()
+    w = _rand(sum(segs), IN, scale=0.05)
+    a = _rand(len(segs) * r, IN, scale=0.1).requires_grad_()
+    bs = [_rand(s, r, scale=0.1).requires_grad_() for s in segs]
+    y = lora.lora_linear(x, w, a, bs, 2.0)
+    dy = _rand(T, sum(segs))
+    y.backward(dy)
+    rt.check_status()
+    xr, ar = x.detach().float().requires_grad_(), a.detach().float().requires_grad_()
+    bsr = [b.detach().float().requires_grad_() for b in bs]
+    yr = lora.lora_linear_ref(xr, w.float(), ar, bsr, 2.0)
+    yr.backward(dy.float())
+    _close(y, yr, atol=0.1, rtol=2e-2)
+    _close(x.grad, xr.grad, atol=0.1, rtol=3e-2)
+    _close(a.grad, ar.grad, atol=0.5, rtol=3e-2)
+    for b, br in zip(bs, bsr):
+        _close(b.grad, br.grad, atol=0.5, rtol=3e-2)
+
+    # grouped (experts)
+    E, H, I = 4, 256, 128
+    counts = torch.tensor([130, 0, 5, 256], dtype=torch.int32)
+    offs, be, P = _blocks(counts)
+    xp = _rand(P, H)
+    used = int(offs[-1])
+    xp[used:] = 0
+    xp.requires_grad_()
+    wg = _rand(E, 2 * I, H, scale=0.05)
+    ag = _rand(E, 2 * r, H, scale=0.1).requires_grad_()
+    bg = [_rand(E, I, r, scale=0.1).requires_grad_() for _ in range(2)]
+    yg = lora.lora_grouped_linear(xp, wg, ag, bg, 2.0, be.to(DEV), offs.to(DEV))
+    dyg = _rand(P, 2 * I)
+    dyg[used:] = 0
+    yg.backward(dyg)
+    rt.check_status()
+    xc = xp.detach().cpu().float().requires_grad_()
+    agc = ag.detach().cpu().float().requires_grad_()
+    bgc = [b.detach().cpu().float().requires_grad_() for b in bg]
+    ygc = lora.lora_grouped_linear(xc, wg.cpu().float(), agc, bgc, 2.0, be, offs)
+    ygc.backward(dyg.cpu().float())
+    _close(yg[:used].cpu(), ygc[:used], atol=0.1, rtol=3e-2)
+    _close(xp.grad[:used].cpu(), xc.grad[:used], atol=0.1, rtol=3e-2)
+    _close(ag.grad.cpu(), agc.grad, atol=0.5, rtol=3e-2)
+    for b, bc in zip(bg, bgc):
+        _close(b.grad.cpu(), bc.grad, atol=0.5, rtol=3e-2)
