@@ -23,7 +23,7 @@ import typing
 from pathlib import Path
 from typing import Any, TypeVar, Union, get_args, get_origin
 
-from pydantic import BaseModel, ConfigDict
+from pydantic import BaseModel, ConfigDict, model_validator
 
 T = TypeVar("T", bound="BaseConfig")
 
@@ -31,6 +31,14 @@ T = TypeVar("T", bound="BaseConfig")
 class BaseConfig(BaseModel):
     model_config = ConfigDict(extra="forbid", validate_assignment=False, validate_default=False,
                               arbitrary_types_allowed=True, populate_by_name=True)
+
+    @model_validator(mode="before")
+    @classmethod
+    def _default_union_tags(cls, data):
+        # {"optim": {"lr": 1e-5}} keeps the default optimizer's ``type``
+        if isinstance(data, dict):
+            return inject_union_defaults(cls, dict(data), recurse=False)
+        return data
 
     def to_json(self, **kw) -> str:
         """JSON dump that keeps nulls, so that a resolved config re-parses to itself."""
@@ -222,14 +230,14 @@ def parse_argv(model: type[T], argv: list[str]) -> dict:
 def _union_members(tp) -> list:
     out = []
     for a in _strip_optional(tp):
-        if get_origin(a) is not None:
+        if get_origin(a) in (Union, types.UnionType, typing.Annotated):
             out.extend(_union_members(a))
         else:
             out.append(a)
     return out
 
 
-def inject_union_defaults(model: type[BaseModel], data: Any) -> Any:
+def inject_union_defaults(model: type[BaseModel], data: Any, recurse: bool = True) -> Any:
     """A partially specified discriminated-union block (``--optim.lr 1e-5`` without
     ``optim.type``) keeps the ``type`` of the field's default value."""
     if not isinstance(data, dict):
@@ -240,7 +248,7 @@ def inject_union_defaults(model: type[BaseModel], data: Any) -> Any:
         members = [m for m in _union_members(fld.annotation) if isinstance(m, type) and issubclass(m, BaseModel)]
         if not members:
             continue
-        sub = data[name]
+        sub = data[name] = dict(data[name])
         target = None
         if len(members) == 1:
             target = members[0]
@@ -264,7 +272,7 @@ def inject_union_defaults(model: type[BaseModel], data: Any) -> Any:
                         break
             elif len(members) > 0 and not tagged:
                 target = members[0]
-        if target is not None:
+        if target is not None and recurse:
             inject_union_defaults(target, sub)
     return data
 

@@ -89,6 +89,10 @@ class ParallelDims:
             return [[r * inner + s * cp + c for s in range(ds)] for r in range(dr) for c in range(cp)]
         if name == "ep":
             return [list(range(s, s + ep)) for s in range(0, W, ep)] if ep > 1 else [[r] for r in range(W)]
+        if name == "ep_replicas":  # ranks that hold the same expert shard
+            if ep <= 1:
+                return [list(range(W))]
+            return [[i + j * ep for j in range(W // ep)] for i in range(ep)]
         if name == "dp_shard_mod_ep":
             if ep <= 1:
                 return self._rank_lists("dp_shard_cp")

@@ -92,7 +92,7 @@ class CheckpointManager:
         # the load above already landed in place; scalars are copied back here
         if has_opt:
             optimizer.step_count = int(app["optimizer"]["step"])
-            optimizer.buf.sync_from_master()
+            optimizer.sync_from_master()
         if "progress" in app:
             for k, v in app["progress"].items():
                 setattr(progress, k, int(v))

@@ -39,7 +39,7 @@ class FlatBuffers:
     """Owns the flat parameter / master / gradient storage of a set of parameters."""
 
     def __init__(self, named_params: list[tuple[str, torch.nn.Parameter]], master_dtype=torch.float32,
-                 align: int = 8):
+                 align: int = 8, pad_to: int = 1, full_master: bool = True):
         params = [(n, p) for n, p in named_params if p.requires_grad]
         if not params:
             raise ValueError("no trainable parameters")
@@ -52,6 +52,7 @@ class FlatBuffers:
                 raise ValueError(f"mixed parameter dtypes ({n}: {p.dtype} vs {self.dtype})")
             self.slots.append(ParamSlot(n, off, p.numel(), p.shape))
             off += (p.numel() + align - 1) // align * align
+        off = (off + pad_to - 1) // pad_to * pad_to
         self.numel = off
         self.params = [p for _, p in params]
         self.flat = torch.zeros(off, dtype=self.dtype, device=self.device)
@@ -59,7 +60,9 @@ class FlatBuffers:
             view = self.flat[s.offset:s.offset + s.numel].view(s.shape)
             view.copy_(p.data)
             p.data = view
-        if self.dtype == master_dtype:
+        if not full_master:
+            self.master = None          # the owner keeps a sharded master copy instead
+        elif self.dtype == master_dtype:
             self.master = self.flat
         else:
             self.master = self.flat.to(master_dtype)
@@ -68,7 +71,7 @@ class FlatBuffers:
 
     @property
     def has_lowp(self) -> bool:
-        return self.master is not self.flat
+        return self.master is not None and self.master is not self.flat
 
     def accumulate_grads(self) -> None:
         """grad_acc += p.grad (fp32) for every parameter, then drops p.grad."""
@@ -146,91 +149,217 @@ def newton_schulz(g: torch.Tensor, steps: int = 5) -> torch.Tensor:
     return x.to(g.dtype)
 
 
+def _backend(group) -> str:
+    return str(dist.get_backend(group)) if dist.is_initialized() else ""
+
+
+class _Group:
+    """One flat buffer set plus how its gradients are reduced.
+
+    ``reduce_group``  ranks that hold replicas of these parameters (gradients are summed);
+    ``norm_group``    ranks over which the parameters are *partitioned* (expert parallelism),
+                      whose squared gradient norms add up;
+    ``shard_group``   when given, optimizer state is partitioned ZeRO-style over it: the flat
+                      gradient is reduce-scattered, every rank updates its 1/N slice of the
+                      fp32 master / moments, and the compute-dtype parameters are all-gathered
+                      back. The bf16 parameters themselves stay replicated: with 180 GB per
+                      GPU there is nothing to gain from re-gathering them layer by layer.
+    """
+
+    def __init__(self, kind: str, named_params, reduce_group, norm_group, shard_group=None):
+        self.reduce_group, self.norm_group = reduce_group, norm_group
+        self.shard_n = dist.get_world_size(shard_group) if (shard_group is not None and dist.is_initialized()) else 1
+        self.shard_group = shard_group if self.shard_n > 1 else None
+        self.shard_rank = dist.get_rank(shard_group) if self.shard_group is not None else 0
+        sharded = self.shard_group is not None
+        self.buf = FlatBuffers(named_params, pad_to=8 * self.shard_n, full_master=not sharded)
+        n, dev = self.buf.numel // self.shard_n, self.buf.device
+        self.shard_len = n
+        lo = self.shard_rank * n
+        self.flat_shard = self.buf.flat[lo:lo + n]
+        if sharded:
+            self.master = self.flat_shard.float().clone()
+            self.grad_shard = torch.zeros(n, dtype=torch.float32, device=dev)
+        else:
+            self.master = self.buf.master
+            self.grad_shard = self.buf.grad
+        self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev) if kind in ("adamw", "sgd", "muon") else None
+        self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev) if kind in ("adamw", "muon") else None
+        self.buf.install_hooks()
+
+    @property
+    def sharded(self) -> bool:
+        return self.shard_group is not None
+
+    @property
+    def lowp_out(self):
+        """Compute-dtype destination of the update, or None when the master *is* the parameter."""
+        if self.sharded:
+            return self.flat_shard
+        return self.buf.flat if self.buf.has_lowp else None
+
+    def reduce(self) -> None:
+        if not dist.is_initialized():
+            return
+        if self.sharded:
+            if _backend(self.shard_group) == "gloo":
+                dist.all_reduce(self.buf.grad, group=self.shard_group)
+                lo = self.shard_rank * self.shard_len
+                self.grad_shard.copy_(self.buf.grad[lo:lo + self.shard_len])
+            else:
+                dist.reduce_scatter_tensor(self.grad_shard, self.buf.grad, op=dist.ReduceOp.SUM,
+                                           group=self.shard_group)
+            if self.reduce_group is not None and dist.get_world_size(self.reduce_group) > 1:
+                dist.all_reduce(self.grad_shard, group=self.reduce_group)
+        elif self.reduce_group is not None and dist.get_world_size(self.reduce_group) > 1:
+            dist.all_reduce(self.buf.grad, op=dist.ReduceOp.SUM, group=self.reduce_group)
+
+    def publish(self) -> None:
+        """After the update: make the new parameters visible in the replicated flat buffer."""
+        if self.sharded:
+            if _backend(self.shard_group) == "gloo":
+                parts = [torch.empty_like(self.flat_shard) for _ in range(self.shard_n)]
+                dist.all_gather(parts, self.flat_shard.contiguous(), group=self.shard_group)
+                self.buf.flat.copy_(torch.cat(parts))
+            else:
+                dist.all_gather_into_tensor(self.buf.flat, self.flat_shard, group=self.shard_group)
+        else:
+            self.buf.sync_from_master()
+
+    lowp_written_by_kernel = False
+
+    def gather_full(self, shard: torch.Tensor) -> torch.Tensor:
+        """Full-length copy of a sharded state tensor (checkpointing)."""
+        if not self.sharded:
+            return shard
+        parts = [torch.empty_like(shard) for _ in range(self.shard_n)]
+        dist.all_gather(parts, shard.contiguous(), group=self.shard_group)
+        return torch.cat(parts)
+
+    def scatter_full(self, full: torch.Tensor, shard: torch.Tensor) -> None:
+        lo = self.shard_rank * self.shard_len
+        shard.copy_(full[lo:lo + self.shard_len])
+
+
 class FlatOptimizer:
-    """SGD / AdamW / SignSGD / Muon over ``FlatBuffers``."""
+    """SGD / AdamW / SignSGD / Muon over one or more ``FlatBuffers`` groups (dense parameters
+    replicated over the data-parallel ranks, expert parameters sharded over the
+    expert-parallel ranks)."""
 
     def __init__(self, config, named_params, *, max_steps: int | None = None, scheduler_config=None,
-                 dp_group=None, grad_divide: float = 1.0):
+                 dp_group=None, expert_params=None, expert_reduce_group=None, expert_norm_group=None,
+                 shard_group=None, replicate_group=None, expert_shard_group=None):
         self.config = config
-        self.buf = FlatBuffers(named_params)
         self.kind = config.type
         self.step_count = 0
-        self.dp_group = dp_group
-        self.grad_divide = grad_divide
+        if self.kind == "muon":
+            shard_group = expert_shard_group = None  # Newton-Schulz needs whole matrices
+        self.groups = [_Group(self.kind, named_params, replicate_group if shard_group is not None else dp_group,
+                              None, shard_group)]
+        if expert_params and any(p.requires_grad for _, p in expert_params):
+            self.groups.append(_Group(self.kind, expert_params,
+                                      None if expert_shard_group is not None else expert_reduce_group,
+                                      expert_norm_group, expert_shard_group))
         self.schedule = LRSchedule(scheduler_config, max_steps, config.lr) if scheduler_config is not None \
             else LRSchedule(type("C", (), {"type": "constant"})(), max_steps, config.lr)
-        n, dev = self.buf.numel, self.buf.device
-        self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev) if self.kind in ("adamw", "sgd", "muon") else None
-        self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev) if self.kind in ("adamw", "muon") else None
+        dev = self.groups[0].buf.device
         self.hyper = torch.zeros(3, dtype=torch.float32, device=dev)
         self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
         self.last_grad_norm: torch.Tensor | None = None
-        self.buf.install_hooks()
 
     # ------------------------------------------------------------------ API
+    @property
+    def buf(self) -> FlatBuffers:
+        return self.groups[0].buf
+
     @property
     def lr(self) -> float:
         return self.schedule.lr_at(self.step_count)
 
     def zero_grad(self) -> None:
-        self.buf.zero_grad()
+        for g in self.groups:
+            g.buf.zero_grad()
 
     def reduce_gradients(self) -> None:
-        """Sum the flat gradient over the data-parallel group (one collective)."""
-        if self.dp_group is not None and dist.is_initialized() and dist.get_world_size(self.dp_group) > 1:
-            dist.all_reduce(self.buf.grad, op=dist.ReduceOp.SUM, group=self.dp_group)
+        """Sum each flat gradient over its replica group (one collective per group)."""
+        for g in self.groups:
+            g.reduce()
+
+    def _global_sumsq(self) -> torch.Tensor:
+        self._sumsq.zero_()
+        for g in self.groups:
+            part = torch.zeros_like(self._sumsq)
+            optim_ops.sumsq(g.grad_shard, part)
+            if dist.is_initialized():
+                if g.sharded:
+                    dist.all_reduce(part, group=g.shard_group)
+                if g.norm_group is not None and dist.get_world_size(g.norm_group) > 1:
+                    dist.all_reduce(part, group=g.norm_group)
+            self._sumsq += part
+        return self._sumsq
 
     def step(self) -> torch.Tensor:
         """Clips, updates and returns the (pre-clip) gradient norm as a device tensor."""
-        c, buf = self.config, self.buf
+        c = self.config
         lr = self.lr
         self.step_count += 1
         t = self.step_count
         max_norm = c.max_norm if c.max_norm is not None else 0.0
-        self._sumsq.zero_()
-        optim_ops.sumsq(buf.grad, self._sumsq)
-        coef, norm = optim_ops.clip_coef(self._sumsq, max_norm)
+        coef, norm = optim_ops.clip_coef(self._global_sumsq(), max_norm)
         self.last_grad_norm = norm
+        if self.kind == "adamw" and self.hyper.is_cuda:
+            b1, b2 = c.betas1, c.betas2
+            self.hyper.copy_(torch.tensor([lr, 1 - b1 ** t, math.sqrt(1 - b2 ** t)]), non_blocking=True)
+        for g in self.groups:
+            self._step_group(g, lr, coef, t)
+        return norm
+
+    def _step_group(self, g: _Group, lr: float, coef: torch.Tensor, t: int) -> None:
+        c, buf = self.config, g.buf
+        master, grad = g.master, g.grad_shard
+        g.lowp_written_by_kernel = False
         if self.kind == "adamw":
             b1, b2 = c.betas1, c.betas2
             if buf.device.type == "cuda":
-                self.hyper.copy_(torch.tensor([lr, 1 - b1 ** t, math.sqrt(1 - b2 ** t)]), non_blocking=True)
-                optim_ops.adamw_flat(buf.master, self.exp_avg, self.exp_avg_sq, buf.grad,
-                                     buf.flat if buf.has_lowp else None, self.hyper, b1=b1, b2=b2,
+                lowp = g.lowp_out
+                if lowp is not None and lowp.dtype != torch.bfloat16:
+                    lowp = None
+                optim_ops.adamw_flat(master, g.exp_avg, g.exp_avg_sq, grad, lowp, self.hyper, b1=b1, b2=b2,
                                      eps=getattr(c, "eps", 1e-8), wd=c.weight_decay, clip=coef)
+                g.lowp_written_by_kernel = lowp is not None
             else:
-                optim_ops.adamw_ref(buf.master, self.exp_avg, self.exp_avg_sq, buf.grad * coef, lr=lr, b1=b1, b2=b2,
+                optim_ops.adamw_ref(master, g.exp_avg, g.exp_avg_sq, grad * coef, lr=lr, b1=b1, b2=b2,
                                     eps=getattr(c, "eps", 1e-8), wd=c.weight_decay, step=t)
-                buf.sync_from_master()
         elif self.kind == "sgd":
-            g = buf.grad * coef
+            gr = grad * coef
             if c.weight_decay:
-                g = g + c.weight_decay * buf.master
-            self.exp_avg.mul_(c.momentum).add_(g)
-            upd = g + c.momentum * self.exp_avg if c.nesterov else self.exp_avg
-            buf.master.add_(upd, alpha=-lr)
-            buf.sync_from_master()
+                gr = gr + c.weight_decay * master
+            g.exp_avg.mul_(c.momentum).add_(gr)
+            upd = gr + c.momentum * g.exp_avg if c.nesterov else g.exp_avg
+            master.add_(upd, alpha=-lr)
         elif self.kind == "sign_sgd":
-            g = buf.grad * coef
-            buf.master.mul_(1 - lr * c.weight_decay).add_(torch.sign(g), alpha=-lr)
-            buf.sync_from_master()
+            gr = grad * coef
+            master.mul_(1 - lr * c.weight_decay).add_(torch.sign(gr), alpha=-lr)
         elif self.kind == "muon":
-            self._muon_step(lr, coef, t)
+            self._muon_step(g, lr, coef, t)
         else:
             raise ValueError(f"unknown optimizer {self.kind}")
-        return norm
+        if g.sharded and not g.lowp_written_by_kernel:
+            g.flat_shard.copy_(master)
+            g.lowp_written_by_kernel = True
+        g.publish()
 
-    def _muon_step(self, lr: float, coef: torch.Tensor, t: int) -> None:
+    def _muon_step(self, grp: _Group, lr: float, coef: torch.Tensor, t: int) -> None:
         """Muon on >= 2-D matrices that are not embeddings / heads; AdamW on the rest
         (the split the reference makes, trainer/optim/__init__.py:151-249)."""
-        c, buf = self.config, self.buf
+        c, buf = self.config, grp.buf
         g_all = buf.grad * coef
         b1, b2 = c.betas1, c.betas2
         for s in buf.slots:
             sl = slice(s.offset, s.offset + s.numel)
             g = g_all[sl].view(s.shape)
             p = buf.master[sl].view(s.shape)
-            m = self.exp_avg[sl].view(s.shape)
+            m = grp.exp_avg[sl].view(s.shape)
             is_matrix = len(s.shape) >= 2 and "embed" not in s.name and "lm_head" not in s.name
             if is_matrix:
                 m.mul_(c.mu).add_(g)
@@ -240,35 +369,57 @@ class FlatOptimizer:
                     (math.sqrt(max(1.0, rows / cols)) if c.adjust_lr == "spectral_norm" else 1.0)
                 p.mul_(1 - lr * c.weight_decay).add_(upd, alpha=-lr * scale)
             else:
-                v = self.exp_avg_sq[sl].view(s.shape)
+                v = grp.exp_avg_sq[sl].view(s.shape)
                 m.mul_(b1).add_(g, alpha=1 - b1)
                 v.mul_(b2).addcmul_(g, g, value=1 - b2)
                 denom = v.sqrt() / math.sqrt(1 - b2 ** t) + 1e-8
                 p.mul_(1 - lr * c.weight_decay).addcdiv_(m, denom, value=-lr / (1 - b1 ** t))
-        buf.sync_from_master()
 
     # ------------------------------------------------------------------ state
     def state_dict(self) -> dict:
         """Per-parameter (name-keyed) tensors, so that a checkpoint does not depend on the
         flat layout."""
         out: dict = {"step": self.step_count, "state": {}}
-        for key, flat in (("master", self.buf.master), ("exp_avg", self.exp_avg), ("exp_avg_sq", self.exp_avg_sq)):
-            if flat is not None:
-                out["state"][key] = self.buf.named_views(flat)
+        for g in self.groups:
+            for key, flat in (("master", g.master), ("exp_avg", g.exp_avg), ("exp_avg_sq", g.exp_avg_sq)):
+                if flat is not None:
+                    out["state"].setdefault(key, {}).update(g.buf.named_views(g.gather_full(flat)))
         return out
 
     def load_state_dict(self, sd: dict) -> None:
         self.step_count = int(sd.get("step", 0))
-        for key, flat in (("master", self.buf.master), ("exp_avg", self.exp_avg), ("exp_avg_sq", self.exp_avg_sq)):
-            if flat is None or key not in sd.get("state", {}):
-                continue
-            views = self.buf.named_views(flat)
-            for name, t in sd["state"][key].items():
-                if name in views:
-                    views[name].copy_(t)
-        self.buf.sync_from_master()
+        for g in self.groups:
+            for key, flat in (("master", g.master), ("exp_avg", g.exp_avg), ("exp_avg_sq", g.exp_avg_sq)):
+                if flat is None or key not in sd.get("state", {}):
+                    continue
+                full = g.gather_full(flat).clone() if g.sharded else flat
+                views = g.buf.named_views(full)
+                for name, t in sd["state"][key].items():
+                    if name in views:
+                        views[name].copy_(t)
+                if g.sharded:
+                    g.scatter_full(full, flat)
+        self.sync_from_master()
+
+    def sync_from_master(self) -> None:
+        """Re-derive the compute-dtype parameters from the fp32 master copy."""
+        for g in self.groups:
+            if g.sharded:
+                g.flat_shard.copy_(g.master)
+                g.lowp_written_by_kernel = True
+                g.publish()
+            else:
+                g.buf.sync_from_master()
 
 
-def setup_optimizer(config, model, *, max_steps=None, scheduler_config=None, dp_group=None) -> FlatOptimizer:
-    return FlatOptimizer(config, list(model.named_parameters()), max_steps=max_steps,
-                         scheduler_config=scheduler_config, dp_group=dp_group)
+def setup_optimizer(config, model, *, max_steps=None, scheduler_config=None, dp_group=None,
+                    expert_reduce_group=None, expert_norm_group=None, shard_group=None, replicate_group=None,
+                    expert_shard_group=None) -> FlatOptimizer:
+    """Parameters marked ``_is_expert_shard`` (set by the expert-parallel setup) form their own
+    group: they are reduced over the ranks that replicate the same expert shard."""
+    dense = [(n, p) for n, p in model.named_parameters() if not getattr(p, "_is_expert_shard", False)]
+    expert = [(n, p) for n, p in model.named_parameters() if getattr(p, "_is_expert_shard", False)]
+    return FlatOptimizer(config, dense, max_steps=max_steps, scheduler_config=scheduler_config, dp_group=dp_group,
+                         expert_params=expert, expert_reduce_group=expert_reduce_group,
+                         expert_norm_group=expert_norm_group, shard_group=shard_group,
+                         replicate_group=replicate_group, expert_shard_group=expert_shard_group)

@@ -67,8 +67,21 @@ class RLTrainer:
         self.model.train()
         self._setup_parallel()
         self.loss_fn = setup_rl_loss_fn(cfg.loss)
-        self.optimizer = setup_optimizer(cfg.optim, self.model, max_steps=cfg.max_steps,
-                                         scheduler_config=cfg.scheduler, dp_group=self.dp_cp_group)
+        d = self.dims
+        multi = dist.is_initialized() and self.world.world_size > 1
+        ep_on = d.ep_enabled and multi
+        # Optimizer state is partitioned over the sharding ranks for full fine-tuning; LoRA
+        # adapters are small and stay replicated.
+        zero = multi and d.dp_shard_cp > 1 and mc.lora is None and not mc.fsdp_cpu_offload
+        self.optimizer = setup_optimizer(
+            cfg.optim, self.model, max_steps=cfg.max_steps, scheduler_config=cfg.scheduler,
+            dp_group=self.dp_cp_group,
+            expert_reduce_group=d.group("ep_replicas") if ep_on else None,
+            expert_norm_group=d.group("ep") if ep_on else None,
+            shard_group=d.group("dp_shard_cp") if zero else None,
+            replicate_group=d.group("dp_replicate") if (zero and d.dp_replicate > 1) else None,
+            expert_shard_group=d.group("dp_shard_mod_ep")
+            if (zero and ep_on and d.dp_replicate == 1 and d.dp_shard_cp // d.ep > 1) else None)
         self.ckpt = CheckpointManager(self.run_dir, cfg.ckpt, is_master=self.world.is_master, rank=self.world.rank) \
             if cfg.ckpt is not None or cfg.resume is not None else None
         self._setup_data()
@@ -78,7 +91,7 @@ class RLTrainer:
             from ...transports.weights import setup_weight_sender
 
             self.weight_sender = setup_weight_sender(cfg.weight_broadcast, self.run_dir, self.world, self.model,
-                                                     lora=mc.lora is not None)
+                                                     lora=mc.lora is not None, lora_cfg=mc.lora)
         dev_name = torch.cuda.get_device_name(self.device) if self.device.type == "cuda" else "cpu"
         self.perf = PerfCounter(self.arch, mc.seq_len, self.world.world_size, dev_name, lora=mc.lora is not None)
         n_train = sum(p.numel() for p in self.model.parameters() if p.requires_grad)
@@ -110,12 +123,6 @@ class RLTrainer:
             from ...parallel.ep import install_expert_parallel
 
             install_expert_parallel(self.model, dims, self.config.model.moe)
-        if dims.dp_shard_cp > 1 and self.config.model.lora is None:
-            from ...parallel.fsdp import shard_model
-
-            self.sharded = shard_model(self.model, dims, self.config.model)
-        else:
-            self.sharded = None
 
     def _setup_data(self) -> None:
         cfg = self.config

@@ -1,0 +1,101 @@
+"""HuggingFace safetensors import / export.
+
+Export writes ``model-0000i-of-0000n.safetensors`` shards of at most ``max_shard_bytes`` plus
+``model.safetensors.index.json`` and ``config.json``; whole decoder layers stay in one shard
+(reference: src/prime_rl/utils/weights.py:45-252). LoRA runs export a PEFT adapter directory
+(``adapter_model.safetensors`` + ``adapter_config.json``) instead.
+"""
+
+from __future__ import annotations
+
+import json
+import re
+from pathlib import Path
+
+import torch
+from safetensors import safe_open
+from safetensors.torch import save_file
+
+from ..models import convert
+
+
+def _layer_key(name: str) -> str:
+    m = re.match(r"(model\.layers\.\d+)\.", name)
+    return m.group(1) if m else name.split(".")[0]
+
+
+def plan_shards(sizes: dict[str, int], max_shard_bytes: int) -> list[list[str]]:
+    """Greedy packing of tensors into shards that keeps each decoder layer together."""
+    groups: dict[str, list[str]] = {}
+    for n in sizes:
+        groups.setdefault(_layer_key(n), []).append(n)
+    shards: list[list[str]] = [[]]
+    cur = 0
+    for _, names in groups.items():
+        g = sum(sizes[n] for n in names)
+        if shards[-1] and cur + g > max_shard_bytes:
+            shards.append([])
+            cur = 0
+        shards[-1].extend(names)
+        cur += g
+    return [s for s in shards if s]
+
+
+@torch.no_grad()
+def save_hf_checkpoint(model, out_dir: Path, *, max_shard_bytes: int = 5 * 2 ** 30, dtype=torch.bfloat16,
+                       tokenizer_dir: Path | None = None) -> Path:
+    out_dir = Path(out_dir)
+    out_dir.mkdir(parents=True, exist_ok=True)
+    sd = convert.model_state(model, "hf")
+    sizes = {k: v.numel() * torch.empty((), dtype=dtype).element_size() for k, v in sd.items()}
+    shards = plan_shards(sizes, max_shard_bytes)
+    index = {"metadata": {"total_size": sum(sizes.values())}, "weight_map": {}}
+    for i, names in enumerate(shards):
+        fname = "model.safetensors" if len(shards) == 1 else f"model-{i + 1:05d}-of-{len(shards):05d}.safetensors"
+        save_file({n: sd[n].detach().to("cpu", dtype).contiguous() for n in names}, str(out_dir / fname),
+                  metadata={"format": "pt"})
+        for n in names:
+            index["weight_map"][n] = fname
+    (out_dir / "model.safetensors.index.json").write_text(json.dumps(index, indent=2))
+    (out_dir / "config.json").write_text(json.dumps(model.arch.to_hf_config(), indent=2))
+    if tokenizer_dir is not None:
+        import shutil
+
+        for f in Path(tokenizer_dir).glob("token*"):
+            shutil.copy(f, out_dir / f.name)
+    return out_dir
+
+
+@torch.no_grad()
+def save_lora_adapter(model, out_dir: Path, rank: int, alpha: float, target_modules: list[str]) -> Path:
+    out_dir = Path(out_dir)
+    out_dir.mkdir(parents=True, exist_ok=True)
+    sd = {k: v.detach().to("cpu").contiguous() for k, v in convert.lora_to_peft(model).items()}
+    save_file(sd, str(out_dir / "adapter_model.safetensors"), metadata={"format": "pt"})
+    (out_dir / "adapter_config.json").write_text(json.dumps({
+        "peft_type": "LORA", "r": rank, "lora_alpha": alpha, "target_modules": target_modules, "bias": "none",
+        "task_type": "CAUSAL_LM", "lora_dropout": 0.0}, indent=2))
+    return out_dir
+
+
+def read_hf_state(path: Path, device: str = "cpu") -> dict[str, torch.Tensor]:
+    path = Path(path)
+    files = sorted(path.glob("*.safetensors"))
+    if not files:
+        raise FileNotFoundError(f"no safetensors files in {path}")
+    out: dict[str, torch.Tensor] = {}
+    for f in files:
+        if f.name.startswith("adapter_"):
+            continue
+        with safe_open(str(f), framework="pt", device=device) as sf:
+            for k in sf.keys():
+                out[k] = sf.get_tensor(k)
+    return out
+
+
+@torch.no_grad()
+def load_hf_checkpoint(model, path: Path, strict: bool = True) -> None:
+    sd = read_hf_state(path)
+    if model.arch.tie_word_embeddings:
+        sd.pop("lm_head.weight", None)
+    convert.load_model_state(model, sd, "hf", strict=strict)

@@ -1,0 +1,112 @@
+import torch
+
+from prime_rl_b200.models import SeqInfo, apply_lora, build_model, convert, resolve_arch
+from prime_rl_b200.models.config import ModelArch
+from prime_rl_b200.ops import attention as A
+from prime_rl_b200.ops import lm_head, moe
+
+
+def _tiny(name="tiny-qwen3-moe", **over):
+    arch = resolve_arch(name, over or None)
+    return arch, build_model(arch, device="cpu", dtype=torch.float32)
+
+
+def test_packed_documents_do_not_interact():
+    arch, m = _tiny("tiny-qwen3")
+    ids = torch.randint(0, arch.vocab_size, (96,))
+    packed = m(ids, SeqInfo.from_lengths([40, 56], "cpu"))
+    a = m(ids[:40], SeqInfo.from_lengths([40], "cpu"))
+    b = m(ids[40:], SeqInfo.from_lengths([56], "cpu"))
+    assert torch.allclose(packed[:40], a, atol=1e-4) and torch.allclose(packed[40:], b, atol=1e-4)
+
+
+def test_fused_head_matches_full_logits():
+    arch, m = _tiny("tiny-qwen3")
+    T = 50
+    h = torch.randn(T, arch.hidden_size, requires_grad=True)
+    labels = torch.randint(0, arch.vocab_size, (T,))
+    it = 0.5 + torch.rand(T)
+    lp, ent = lm_head.logprob_entropy_ref(h, m.output_weight, labels, it, chunk=16)
+    z = (h @ m.output_weight.t()) * it[:, None]
+    want = torch.log_softmax(z, -1).gather(1, labels[:, None]).squeeze(1)
+    p = torch.softmax(z, -1)
+    assert torch.allclose(lp, want, atol=1e-5)
+    assert torch.allclose(ent, -(p * torch.log_softmax(z, -1)).sum(-1), atol=1e-4)
+
+
+def test_moe_matches_dense_loop():
+    arch, m = _tiny()
+    layer = m.model.layers[0].mlp
+    x = torch.randn(70, arch.hidden_size)
+    y = layer(x, SeqInfo.from_lengths([70], "cpu"))
+    idx, w, _, _ = layer.router(x)
+    I = arch.moe_intermediate_size
+    want = torch.zeros_like(x)
+    for t in range(70):
+        for j in range(arch.num_experts_per_tok):
+            e = int(idx[t, j])
+            gu = layer.experts.gate_up_proj[e] @ x[t]
+            hmid = torch.nn.functional.silu(gu[:I]) * gu[I:]
+            want[t] += w[t, j] * (layer.experts.down_proj[e] @ hmid)
+    assert torch.allclose(y, want, atol=1e-4)
+
+
+def test_plan_is_128_aligned_and_complete():
+    idx = torch.randint(0, 8, (300, 2), dtype=torch.int32)
+    counts = torch.bincount(idx.reshape(-1).long(), minlength=8).to(torch.int32)
+    plan = moe.build_plan(idx, counts, 8)
+    offs = plan.expert_offset.long()
+    assert (offs % 128 == 0).all()
+    slot = plan.slot.long()
+    assert ((slot >= offs[idx.long()]) & (slot < offs[idx.long() + 1])).all()
+    assert slot.unique().numel() == slot.numel()
+    assert (plan.row_src[slot.reshape(-1)].long() == torch.arange(600)).all()
+
+
+def test_layout_round_trips_and_hf_names():
+    arch, m = _tiny()
+    prime = convert.model_state(m, "prime")
+    assert "model.layers.0.self_attn.q_proj.weight" in prime
+    assert prime["model.layers.0.mlp.experts.gate_proj"].shape == (8, arch.moe_intermediate_size, arch.hidden_size)
+    assert "model.layers.0.mlp.router.gate.weight" in prime
+    hf = convert.model_state(m, "hf")
+    assert "model.layers.1.mlp.experts.7.down_proj.weight" in hf and "model.layers.0.mlp.gate.weight" in hf
+    back = convert.hf_to_native({k: v.clone() for k, v in hf.items()}, arch)
+    for k, v in m.state_dict().items():
+        if not k.endswith("inv_freq"):
+            assert torch.equal(back[k], v), k
+
+
+def test_lora_freezes_base_and_starts_as_identity():
+    arch, m = _tiny()
+    ids = torch.randint(0, arch.vocab_size, (64,))
+    seq = SeqInfo.from_lengths([64], "cpu")
+    before = m(ids, seq)
+    apply_lora(m, 4, 8.0, ["q_proj", "k_proj", "v_proj", "o_proj", "experts"])
+    after = m(ids, seq)
+    assert torch.allclose(before, after, atol=1e-6)  # B = 0 at init
+    trainable = [n for n, p in m.named_parameters() if p.requires_grad]
+    assert trainable and all("lora_" in n for n in trainable)
+    after.sum().backward()
+    assert all(p.grad is not None for n, p in m.named_parameters() if p.requires_grad)
+    peft = convert.lora_to_peft(m)
+    assert "base_model.model.model.layers.0.self_attn.q_proj.lora_A.weight" in peft
+    assert "base_model.model.model.layers.0.mlp.experts.gate_proj.lora_B.weight" in peft
+
+
+def test_attention_reference_window_and_sinks():
+    T, H, D = 24, 2, 16
+    q, k, v = torch.randn(T, H, D), torch.randn(T, H, D), torch.randn(T, H, D)
+    cu = torch.tensor([0, 10, 24], dtype=torch.int32)
+    full = A.attention_ref(q, k, v, cu)
+    win = A.attention_ref(q, k, v, cu, window=1)
+    assert torch.allclose(win, v, atol=1e-5)  # window of 1 attends to itself only
+    sink = A.attention_ref(q, k, v, cu, sinks=torch.full((H,), 50.0))
+    assert sink.abs().max() < 1e-3 * full.abs().max() + 1e-3  # a huge sink takes all the mass
+
+
+def test_hf_config_interchange():
+    arch = resolve_arch("qwen3-30b-a3b")
+    assert arch.param_count() > 30e9 and arch.param_count(active_only=True) < 3.5e9
+    again = ModelArch.from_hf_config(arch.to_hf_config())
+    assert again.num_experts == 128 and again.moe_intermediate_size == 768 and again.qk_norm
