@@ -306,9 +306,10 @@ struct EpiDLogits {
   __device__ void begin_item(const GemmParams& p, long long row) {
     const bool ok = row < p.M;
     it = (ok && p.inv_temp) ? p.inv_temp[row] : 1.f;
-    g = ok ? p.grad_logprob[row] : 0.f;
     lse = ok ? p.lse[row] : 0.f;
     label = ok ? p.labels[row] : -1;
+    // an ignored label makes the log-probability a constant 0: no gradient for that row
+    g = (ok && label >= 0 && label < p.N) ? p.grad_logprob[row] : 0.f;
   }
   __device__ void end_item(const GemmParams&, long long, int) {}
   __device__ void chunk(const GemmParams& p, long long row, int col0, uint32_t (&v)[32]) {

@@ -197,7 +197,8 @@ __global__ void __launch_bounds__(256)
 qknorm_rope_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gin,
                    const __nv_bfloat16* __restrict__ w, const int* __restrict__ pos,
                    const float* __restrict__ inv_freq, __nv_bfloat16* __restrict__ out, float* __restrict__ rstd_io,
-                   float* __restrict__ dw, long long T, int heads, long long ld_x, long long ld_out, float eps) {
+                   float* __restrict__ dw, long long T, int heads, long long ld_x, long long ld_out, long long ld_dx,
+                   float eps) {
   constexpr int EPL = D / 32;  // elements per lane, contiguous
   const int lane = threadIdx.x & 31;
   const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -260,7 +261,7 @@ qknorm_rope_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         const float other = __shfl_xor_sync(0xffffffffu, gv[i], 16);
         gn[i] = upper ? (gv[i] * cs[i] - other * sn[i]) : (gv[i] * cs[i] + other * sn[i]);
       }
-      __nv_bfloat16* dst = out + t * ld_x + static_cast<long long>(h) * D + e0;
+      __nv_bfloat16* dst = out + t * ld_dx + static_cast<long long>(h) * D + e0;
       if (w) {
         const float rstd = rstd_io[item];
         float dot = 0.f;
@@ -348,11 +349,12 @@ PRB_API int prb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const 
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
-// Forward: out = rope(norm(x)). Backward (bwd != 0): out (= dx, pitch ld_x) from gin
-// (= dy, pitch ld_out), x and the saved rstd; dw (fp32 [D], accumulated) may be null.
+// Forward: out = rope(norm(x)), out pitch ld_out. Backward (bwd != 0): out (= dx, pitch
+// ld_dx) from gin (= dy, pitch ld_out), x (pitch ld_x) and the saved rstd; dw (fp32 [D],
+// accumulated) may be null. Pitches are in elements per token.
 PRB_API int prb_qknorm_rope(const void* x, const void* gin, const void* w, const int* pos, const float* inv_freq,
                             void* out, float* rstd, float* dw, long long T, int heads, int D, long long ld_x,
-                            long long ld_out, float eps, int bwd, void* stream) {
+                            long long ld_out, long long ld_dx, float eps, int bwd, void* stream) {
   if (T == 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const long long items = T * heads;
@@ -360,7 +362,7 @@ PRB_API int prb_qknorm_rope(const void* x, const void* gin, const void* w, const
 #define LAUNCH(DD, B)                                                                                     \
   qknorm_rope_kernel<DD, B><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)gin,        \
                                                   (const __nv_bfloat16*)w, pos, inv_freq, (__nv_bfloat16*)out, \
-                                                  rstd, dw, T, heads, ld_x, ld_out, eps)
+                                                  rstd, dw, T, heads, ld_x, ld_out, ld_dx, eps)
   if (D == 128) { if (bwd) LAUNCH(128, true); else LAUNCH(128, false); }
   else if (D == 64) { if (bwd) LAUNCH(64, true); else LAUNCH(64, false); }
   else if (D == 256) { if (bwd) LAUNCH(256, true); else LAUNCH(256, false); }

@@ -1,0 +1,302 @@
+"""Rollout engine: continuous batching over the paged KV cache.
+
+One background thread runs the step loop (prefill of admitted requests, then one decode step
+for every running sequence); requests arrive from the HTTP server's event loop. Pausing
+freezes in-flight requests without aborting them (the reference pauses vLLM with
+``mode="keep", clear_cache=False``; src/prime_rl/inference/vllm/server.py:66-76); weight
+updates happen only while paused.
+"""
+
+from __future__ import annotations
+
+import asyncio
+import threading
+import time
+import uuid
+from dataclasses import dataclass, field
+
+import torch
+
+from ..utils.logger import get_logger
+from .kv_cache import KVCache, OutOfPages, SequenceKV
+from .runner import ModelRunner, StepInput
+from .sampler import SamplingParams, sample
+
+
+@dataclass
+class Request:
+    prompt: list[int]
+    params: SamplingParams
+    cache_salt: str = ""
+    request_id: str = field(default_factory=lambda: uuid.uuid4().hex)
+    # state
+    kv: SequenceKV = field(default_factory=SequenceKV)
+    output: list[int] = field(default_factory=list)
+    logprobs: list[float] = field(default_factory=list)
+    prompt_logprobs: list[float] | None = None
+    routed: list[torch.Tensor] = field(default_factory=list)
+    masks: list[torch.Tensor] = field(default_factory=list)
+    finish_reason: str | None = None
+    arrival: float = field(default_factory=time.monotonic)
+    future: asyncio.Future | None = None
+    loop: asyncio.AbstractEventLoop | None = None
+    generator: torch.Generator | None = None
+    prefilled: bool = False
+    preemptions: int = 0
+
+    @property
+    def all_tokens(self) -> list[int]:
+        return self.prompt + self.output
+
+
+class Engine:
+    def __init__(self, model, *, num_pages: int = 4096, page_size: int = 16, max_running: int = 256,
+                 max_prefill_tokens: int = 16384, eos_token_id: int | None = None, enable_prefix_cache: bool = True):
+        arch = model.arch
+        self.model = model.eval()
+        p = next(model.parameters())
+        self.device = p.device
+        self.cache = KVCache(arch.num_hidden_layers, num_pages, page_size, arch.num_key_value_heads, arch.head_dim,
+                             p.dtype, p.device)
+        self.runner = ModelRunner(model, self.cache)
+        self.max_running, self.max_prefill_tokens = max_running, max_prefill_tokens
+        self.eos, self.enable_prefix_cache = eos_token_id, enable_prefix_cache
+        self.waiting: list[Request] = []
+        self.running: list[Request] = []
+        self.lock = threading.Lock()
+        self.wake = threading.Condition(self.lock)
+        self.paused = False
+        self.idle_paused = threading.Event()
+        self.stop_flag = False
+        self.thread: threading.Thread | None = None
+        self.logger = get_logger()
+        self.policy_version = 0
+        self.stats = dict(prompt_tokens=0, generation_tokens=0, preemptions=0, prefix_hits=0, prefix_queries=0,
+                          requests=0, steps=0)
+        self.last_step_time = time.monotonic()
+
+    # ------------------------------------------------------------------ lifecycle
+    def start(self) -> "Engine":
+        if self.thread is None:
+            self.thread = threading.Thread(target=self._loop, name="engine-loop", daemon=True)
+            self.thread.start()
+        return self
+
+    def shutdown(self) -> None:
+        with self.wake:
+            self.stop_flag = True
+            self.wake.notify_all()
+        if self.thread is not None:
+            self.thread.join(timeout=10)
+
+    def pause(self, timeout: float = 60.0) -> None:
+        """Returns once the step loop is parked (no kernel of a step in flight)."""
+        with self.wake:
+            self.paused = True
+            self.idle_paused.clear()
+            self.wake.notify_all()
+        if self.thread is not None and not self.idle_paused.wait(timeout):
+            raise TimeoutError("engine did not pause in time")
+
+    def resume(self) -> None:
+        with self.wake:
+            self.paused = False
+            self.wake.notify_all()
+
+    def is_alive(self) -> bool:
+        return self.thread is not None and self.thread.is_alive()
+
+    # ------------------------------------------------------------------ requests
+    def submit(self, req: Request) -> Request:
+        if req.params.seed is not None:
+            req.generator = torch.Generator(device=self.device).manual_seed(req.params.seed)
+        with self.wake:
+            self.waiting.append(req)
+            self.stats["requests"] += 1
+            self.wake.notify_all()
+        return req
+
+    async def generate(self, prompt: list[int], params: SamplingParams, cache_salt: str = "") -> Request:
+        loop = asyncio.get_running_loop()
+        req = Request(prompt=list(prompt), params=params, cache_salt=cache_salt, loop=loop,
+                      future=loop.create_future())
+        self.submit(req)
+        return await req.future
+
+    def generate_sync(self, prompts: list[list[int]], params: SamplingParams, cache_salt: str = "") -> list[Request]:
+        """Blocking helper for tests and benchmarks (runs the loop inline if no thread is active)."""
+        reqs = [self.submit(Request(prompt=list(p), params=params, cache_salt=cache_salt)) for p in prompts]
+        if self.thread is None:
+            while any(r.finish_reason is None for r in reqs):
+                self.step()
+        else:
+            while any(r.finish_reason is None for r in reqs):
+                time.sleep(0.001)
+        return reqs
+
+    # ------------------------------------------------------------------ step loop
+    def _loop(self) -> None:
+        while True:
+            with self.wake:
+                while not self.stop_flag and (self.paused or (not self.waiting and not self.running)):
+                    if self.paused:
+                        self.idle_paused.set()
+                    self.wake.wait(timeout=0.5)
+                if self.stop_flag:
+                    return
+            try:
+                self.step()
+            except Exception as e:  # fail the in-flight requests, keep serving
+                self.logger.exception(f"engine step failed: {e}")
+                with self.lock:
+                    doomed, self.running = self.running, []
+                for r in doomed:
+                    self._finish(r, "error")
+
+    def _finish(self, r: Request, reason: str) -> None:
+        r.finish_reason = reason
+        self.cache.free(r.kv)
+        if r.future is not None and r.loop is not None:
+            r.loop.call_soon_threadsafe(lambda: r.future.done() or r.future.set_result(r))
+
+    def _admit(self) -> list[Request]:
+        """Moves waiting requests to running while pages and the prefill budget allow."""
+        admitted, budget = [], self.max_prefill_tokens
+        with self.lock:
+            while self.waiting and len(self.running) + len(admitted) < self.max_running:
+                r = self.waiting[0]
+                toks = r.all_tokens
+                need_pages = (len(toks) + self.cache.page_size) // self.cache.page_size + 1
+                if len(toks) > budget and admitted:
+                    break
+                if self.cache.blocks.num_free < need_pages and (self.running or admitted):
+                    break
+                self.waiting.pop(0)
+                admitted.append(r)
+                budget -= len(toks)
+        return admitted
+
+    def _preempt_one(self) -> bool:
+        """Out of pages: push the most recent running request back to the queue (its KV is
+        recomputed on re-admission)."""
+        with self.lock:
+            if len(self.running) <= 1:
+                return False
+            r = self.running.pop()
+            self.cache.free(r.kv)
+            r.prefilled = False
+            r.preemptions += 1
+            self.stats["preemptions"] += 1
+            self.waiting.insert(0, r)
+        return True
+
+    def step(self) -> None:
+        self.stats["steps"] += 1
+        self.last_step_time = time.monotonic()
+        new = self._admit()
+        if new:
+            self._prefill(new)
+        with self.lock:
+            batch = [r for r in self.running if r.prefilled and r.finish_reason is None]
+        if batch:
+            self._decode(batch)
+
+    # ------------------------------------------------------------------ prefill
+    def _prefill(self, reqs: list[Request]) -> None:
+        inputs = []
+        for r in reqs:
+            toks = r.all_tokens
+            self.stats["prefix_queries"] += len(toks)
+            if self.enable_prefix_cache and not r.params.prompt_logprobs:
+                pages = self.cache.blocks.lookup_prefix(r.cache_salt, toks[:-1])
+                r.kv.pages, r.kv.length = pages, len(pages) * self.cache.page_size
+                self.stats["prefix_hits"] += r.kv.length
+            inputs.append(StepInput(r.kv, toks[r.kv.length:], want_all_logits=r.params.prompt_logprobs))
+        try:
+            logits, offsets = self.runner.forward(inputs)
+        except OutOfPages:
+            for r in reqs:
+                self.cache.free(r.kv)
+            with self.lock:
+                self.waiting = reqs + self.waiting
+            if not self._preempt_one():
+                raise
+            return
+        self.stats["prompt_tokens"] += sum(len(i.tokens) for i in inputs)
+        rows = []
+        for r, inp, off in zip(reqs, inputs, offsets):
+            n = len(inp.tokens)
+            if r.params.prompt_logprobs:
+                lp = torch.log_softmax(logits[off:off + n - 1], -1)
+                tgt = torch.tensor(r.prompt[1:], device=lp.device)
+                r.prompt_logprobs = [0.0] + lp.gather(1, tgt[:n - 1, None]).squeeze(1).tolist()
+                rows.append(off + n - 1)
+            else:
+                rows.append(off)
+            if self.enable_prefix_cache:
+                self.cache.blocks.register_prefix(r.cache_salt, r.all_tokens, r.kv.pages)
+            r.prefilled = True
+        self._sample_and_append(reqs, logits[torch.tensor(rows, device=logits.device)], self.runner.last_routed,
+                                [sum(len(i.tokens) for i in inputs[:j + 1]) - 1 for j in range(len(inputs))])
+        with self.lock:
+            self.running.extend(r for r in reqs if r.finish_reason is None)
+
+    # ------------------------------------------------------------------ decode
+    def _decode(self, reqs: list[Request]) -> None:
+        inputs = [StepInput(r.kv, [r.output[-1]]) for r in reqs]
+        while True:
+            try:
+                logits, _ = self.runner.forward(inputs)
+                break
+            except OutOfPages:
+                if not self._preempt_one():
+                    raise
+                with self.lock:
+                    alive = set(id(r) for r in self.running)
+                keep = [(r, i) for r, i in zip(reqs, inputs) if id(r) in alive]
+                reqs, inputs = [k[0] for k in keep], [k[1] for k in keep]
+                if not reqs:
+                    return
+        self._sample_and_append(reqs, logits, self.runner.last_routed, list(range(len(reqs))))
+        with self.lock:
+            self.running = [r for r in self.running if r.finish_reason is None]
+
+    def _sample_and_append(self, reqs, logits, routed, routed_rows) -> None:
+        dev = logits.device
+        temp = torch.tensor([r.params.temperature for r in reqs], dtype=torch.float32, device=dev)
+        top_k = torch.tensor([r.params.top_k for r in reqs], dtype=torch.long, device=dev)
+        top_p = torch.tensor([r.params.top_p for r in reqs], dtype=torch.float32, device=dev)
+        want_mask = any(r.params.return_sampling_mask and r.params.truncated for r in reqs)
+        gen = reqs[0].generator if len(reqs) == 1 else None
+        tok, lp, masks = sample(logits, temp, top_k, top_p, generator=gen, want_mask=want_mask)
+        tok_l, lp_l = tok.tolist(), lp.tolist()
+        self.stats["generation_tokens"] += len(reqs)
+        for i, r in enumerate(reqs):
+            r.output.append(tok_l[i])
+            r.logprobs.append(lp_l[i])
+            if routed is not None and r.params.return_routed_experts:
+                r.routed.append(routed[routed_rows[i]].to("cpu", torch.int16))
+            if masks is not None and r.params.return_sampling_mask:
+                r.masks.append(masks[i].cpu())
+            n = len(r.output)
+            if n >= r.params.max_tokens:
+                self._finish(r, "length")
+            elif n >= r.params.min_tokens and (tok_l[i] == self.eos or tok_l[i] in r.params.stop_token_ids):
+                self._finish(r, "stop")
+
+    # ------------------------------------------------------------------ weights
+    def update_weights_from_dir(self, weight_dir: str) -> None:
+        """Must be called while paused. HF safetensors directory, or a PEFT adapter directory."""
+        from pathlib import Path
+
+        from ..trainer.weights import load_hf_checkpoint
+
+        assert self.paused or self.thread is None, "update_weights requires a paused engine"
+        load_hf_checkpoint(self.model, Path(weight_dir), strict=False)
+        self.cache.blocks.clear_prefix_cache()
+        self.policy_version += 1
+
+    def metrics(self) -> dict:
+        with self.lock:
+            return dict(self.stats, running=len(self.running), waiting=len(self.waiting),
+                        kv_usage=self.cache.blocks.usage, policy_version=self.policy_version)

@@ -1,0 +1,189 @@
+"""HTTP surface of the rollout engine (FastAPI).
+
+Routes (same paths and payloads as the reference's vLLM wrapper,
+src/prime_rl/inference/vllm/server.py:66-147 and serving_tokens.py:46-116):
+
+  POST /inference/v1/generate   token-in / token-out with logprobs, routed experts, sampling mask
+  POST /v1/chat/completions, /v1/completions   OpenAI-style (needs a tokenizer)
+  GET  /v1/models, /health, /liveness, /metrics
+  POST /pause, /resume, /update_weights, /init_broadcaster, /load_lora_adapter
+"""
+
+from __future__ import annotations
+
+import asyncio
+import base64
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+from fastapi import FastAPI, HTTPException, Request as HTTPRequest
+from fastapi.responses import JSONResponse, PlainTextResponse
+
+from .engine import Engine
+from .sampler import SamplingParams
+
+
+def _encode_routed(routed: list[torch.Tensor], start: int = 0) -> dict | None:
+    if not routed:
+        return None
+    arr = torch.stack(routed).numpy().astype(np.int16)        # [tokens, layers, topk]
+    return {"data": base64.b64encode(arr.tobytes()).decode(), "shape": list(arr.shape), "start": start,
+            "dtype": "int16"}
+
+
+def _encode_mask(masks: list[torch.Tensor]) -> dict | None:
+    if not masks:
+        return None
+    counts = np.array([m.numel() for m in masks], dtype=np.int32)
+    ids = np.concatenate([m.numpy().astype(np.int32) for m in masks]) if counts.sum() else np.zeros(0, np.int32)
+    return {"ids": base64.b64encode(ids.tobytes()).decode(), "counts": base64.b64encode(counts.tobytes()).decode()}
+
+
+def build_app(engine: Engine, model_name: str, tokenizer=None, liveness_timeout: float = 30.0,
+              weight_receiver=None) -> FastAPI:
+    app = FastAPI(title="prime-rl-b200 inference")
+    app.state.engine = engine
+
+    @app.get("/health")
+    async def health():
+        return {"status": "ok"}
+
+    @app.get("/liveness")
+    async def liveness():
+        # the step loop must have made progress (or be idle / paused) within the timeout
+        age = time.monotonic() - engine.last_step_time
+        busy = bool(engine.running or engine.waiting)
+        if not engine.is_alive() or (busy and not engine.paused and age > liveness_timeout):
+            return JSONResponse({"status": "engine_unresponsive"}, status_code=503)
+        return {"status": "ok"}
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": model_name, "object": "model", "owned_by": "prime-rl-b200"}]}
+
+    @app.get("/metrics")
+    async def metrics():
+        m = engine.metrics()
+        hit = m["prefix_hits"]
+        lines = [
+            f"vllm:num_requests_running {m['running']}", f"vllm:num_requests_waiting {m['waiting']}",
+            f"vllm:kv_cache_usage_perc {m['kv_usage']:.6f}", f"vllm:gpu_cache_usage_perc {m['kv_usage']:.6f}",
+            f"vllm:num_preemptions_total {m['preemptions']}", f"vllm:prompt_tokens_total {m['prompt_tokens']}",
+            f"vllm:generation_tokens_total {m['generation_tokens']}", f"vllm:prefix_cache_hits_total {hit}",
+            f"vllm:prefix_cache_queries_total {m['prefix_queries']}", f"vllm:request_success_total {m['requests']}",
+            f"prime_rl:policy_version {m['policy_version']}",
+        ]
+        return PlainTextResponse("\n".join(lines) + "\n")
+
+    @app.post("/inference/v1/generate")
+    async def generate(body: dict):
+        token_ids = body.get("token_ids")
+        if not token_ids:
+            raise HTTPException(400, "token_ids is required")
+        sp = dict(body.get("sampling_params") or {})
+        n = int(sp.pop("n", 1) or 1)
+        if engine.runner.capture_routed:
+            sp.setdefault("return_routed_experts", True)
+        params = SamplingParams.from_dict(sp)
+        if body.get("return_sampling_mask") or app.state.__dict__.get("return_sampling_mask"):
+            params.return_sampling_mask = True
+        salt = str(body.get("cache_salt", ""))
+        reqs = await asyncio.gather(*[engine.generate(token_ids, params, salt) for _ in range(n)])
+        choices = []
+        for i, r in enumerate(reqs):
+            choices.append({
+                "index": i, "token_ids": r.output, "logprobs": r.logprobs, "finish_reason": r.finish_reason,
+                "prompt_logprobs": r.prompt_logprobs, "routed_experts": _encode_routed(r.routed),
+                "sampling_mask": _encode_mask(r.masks)})
+        return {"id": reqs[0].request_id, "model": body.get("model", model_name), "choices": choices,
+                "usage": {"prompt_tokens": len(token_ids), "completion_tokens": sum(len(r.output) for r in reqs)},
+                "policy_version": engine.policy_version}
+
+    def _need_tokenizer():
+        if tokenizer is None:
+            raise HTTPException(501, "this server was started without a tokenizer; use /inference/v1/generate")
+
+    @app.post("/v1/completions")
+    async def completions(body: dict):
+        _need_tokenizer()
+        ids = tokenizer.encode(body["prompt"])
+        params = SamplingParams.from_dict({"max_tokens": body.get("max_tokens", 16),
+                                           "temperature": body.get("temperature", 1.0),
+                                           "top_p": body.get("top_p", 1.0)})
+        r = await engine.generate(ids, params, str(body.get("cache_salt", "")))
+        return {"id": r.request_id, "object": "text_completion", "model": model_name,
+                "choices": [{"index": 0, "text": tokenizer.decode(r.output), "finish_reason": r.finish_reason}]}
+
+    @app.post("/v1/chat/completions")
+    async def chat(body: dict):
+        _need_tokenizer()
+        ids = tokenizer.apply_chat_template(body["messages"], add_generation_prompt=True, tokenize=True)
+        params = SamplingParams.from_dict({"max_tokens": body.get("max_tokens", body.get("max_completion_tokens", 256)),
+                                           "temperature": body.get("temperature", 1.0),
+                                           "top_p": body.get("top_p", 1.0)})
+        r = await engine.generate(list(ids), params, str(body.get("cache_salt", "")))
+        return {"id": r.request_id, "object": "chat.completion", "model": model_name,
+                "choices": [{"index": 0, "finish_reason": r.finish_reason,
+                             "message": {"role": "assistant", "content": tokenizer.decode(r.output)}}],
+                "usage": {"prompt_tokens": len(ids), "completion_tokens": len(r.output)}}
+
+    @app.post("/pause")
+    async def pause():
+        await asyncio.to_thread(engine.pause)
+        return {"status": "paused"}
+
+    @app.post("/resume")
+    async def resume():
+        engine.resume()
+        return {"status": "running"}
+
+    @app.post("/update_weights")
+    async def update_weights(body: dict | None = None):
+        weight_dir = (body or {}).get("weight_dir")
+        was_paused = engine.paused
+        if not was_paused:
+            await asyncio.to_thread(engine.pause)
+        try:
+            if weight_dir is not None:
+                await asyncio.to_thread(engine.update_weights_from_dir, weight_dir)
+            elif weight_receiver is not None:
+                await asyncio.to_thread(weight_receiver.receive_into, engine)
+            else:
+                raise HTTPException(400, "weight_dir is null and no in-memory broadcaster was initialised")
+        finally:
+            if not was_paused:
+                engine.resume()
+        return {"status": "ok", "policy_version": engine.policy_version}
+
+    @app.post("/init_broadcaster")
+    async def init_broadcaster(body: dict):
+        nonlocal weight_receiver
+        from ..transports.weights.nccl import NCCLWeightReceiver
+
+        weight_receiver = NCCLWeightReceiver(host=body["host"], port=int(body["port"]),
+                                             rank=int(body.get("rank_offset", 0)) + 1,
+                                             world_size=int(body["inference_world_size"]) + 1,
+                                             timeout=int(body.get("timeout", 1200)))
+        await asyncio.to_thread(weight_receiver.connect)
+        return {"status": "ok"}
+
+    @app.post("/load_lora_adapter")
+    async def load_lora(body: dict):
+        from ..models.lora_io import load_peft_adapter
+
+        path = Path(body["lora_path"])
+        was_paused = engine.paused
+        if not was_paused:
+            await asyncio.to_thread(engine.pause)
+        try:
+            await asyncio.to_thread(load_peft_adapter, engine.model, path)
+            engine.cache.blocks.clear_prefix_cache()
+            engine.policy_version += 1
+        finally:
+            if not was_paused:
+                engine.resume()
+        return {"status": "ok", "lora_name": body.get("lora_name")}
+
+    return app

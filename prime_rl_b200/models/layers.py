@@ -129,13 +129,10 @@ class Attention(nn.Module):
         T = x.shape[0]
         qkv = self.qkv_proj(x)
         q_dim, kv_dim = self.nq * self.D, self.nkv * self.D
-        q = qkv[:, :q_dim].view(T, self.nq, self.D)
-        k = qkv[:, q_dim:q_dim + kv_dim].view(T, self.nkv, self.D)
-        v = qkv[:, q_dim + kv_dim:].view(T, self.nkv, self.D)
         qw = self.q_norm.weight if self.q_norm is not None else None
         kw = self.k_norm.weight if self.k_norm is not None else None
-        q = ops.qknorm_rope(q, qw, seq.position_ids, self.inv_freq, self.arch.rms_norm_eps)
-        k = ops.qknorm_rope(k, kw, seq.position_ids, self.inv_freq, self.arch.rms_norm_eps)
+        q, k, v = ops.qkv_norm_rope(qkv, qw, kw, seq.position_ids, self.inv_freq, self.arch.rms_norm_eps, self.nq,
+                                    self.nkv, self.D)
         if seq.cp is not None:
             o = seq.cp.attention(q, k, v, seq, window=self.window, sinks=self.sinks, backend=self.backend)
         else:
@@ -264,6 +261,7 @@ class MoE(nn.Module):
             self.shared_experts = None
         self.dispatcher = None            # parallel/ep.py installs an expert-parallel dispatcher here
         self.last_counts: torch.Tensor | None = None
+        self.last_topk: torch.Tensor | None = None     # [T, k] expert ids of the last forward (router replay capture)
         self.last_router_stats: dict | None = None
 
     def forward(self, x: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
@@ -273,6 +271,7 @@ class MoE(nn.Module):
             forced = seq.routed_experts[:, self.layer_idx, :].to(torch.int32)
         idx, w, counts, logits = self.router(x, forced)
         self.last_counts = counts
+        self.last_topk = idx
         if self.dispatcher is not None:
             y = self.dispatcher(self.experts, x, idx, w, counts)
         else:

@@ -30,7 +30,7 @@ _CUDA_SIGNATURES = {
     "prb_rmsnorm_fwd": [P, P, P, P, P, P, L, I, F, P],
     "prb_rmsnorm_bwd_parts": [L],
     "prb_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, L, I, P],
-    "prb_qknorm_rope": [P, P, P, P, P, P, P, P, L, I, I, L, L, F, I, P],
+    "prb_qknorm_rope": [P, P, P, P, P, P, P, P, L, I, I, L, L, L, F, I, P],
     "prb_glu_fwd": [P, P, P, L, I, L, L, I, F, F, P],
     "prb_glu_bwd": [P, P, P, P, P, L, I, L, L, L, I, F, F, P],
     "prb_sumsq": [P, L, I, P, P],

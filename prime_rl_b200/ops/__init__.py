@@ -5,4 +5,4 @@ from .activation import RELU2, SWIGLU, SWIGLU_CLAMPED, glu, glu_ref  # noqa: F40
 from .matmul import gemm, gemm_ref, grouped_gemm_ref, grouped_linear, linear  # noqa: F401
 from .lm_head import fused_logprob_entropy, logprob_entropy_ref  # noqa: F401
 from .norm import add_rms_norm, rms_norm, rms_norm_ref  # noqa: F401
-from .rope import inv_freq, qknorm_rope, qknorm_rope_ref  # noqa: F401
+from .rope import inv_freq, qknorm_rope, qknorm_rope_ref, qkv_norm_rope  # noqa: F401

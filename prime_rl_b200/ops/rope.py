@@ -40,7 +40,7 @@ class _QKNormRope(torch.autograd.Function):
         out = torch.empty(T, Hh, D, dtype=x.dtype, device=x.device)
         rstd = torch.empty(T * Hh, dtype=torch.float32, device=x.device) if w is not None else None
         rc = rt.lib().prb_qknorm_rope(x.data_ptr(), None, rt.ptr(w), pos.data_ptr(), inv_f.data_ptr(),
-                                      out.data_ptr(), rt.ptr(rstd), None, T, Hh, D, x.stride(0), out.stride(0),
+                                      out.data_ptr(), rt.ptr(rstd), None, T, Hh, D, x.stride(0), out.stride(0), 0,
                                       float(eps), 0, rt.stream_ptr(x.device))
         rt.check(rc, "prb_qknorm_rope")
         ctx.save_for_backward(x, w, pos, inv_f, rstd)
@@ -57,9 +57,8 @@ class _QKNormRope(torch.autograd.Function):
         dw = torch.zeros(D, dtype=torch.float32, device=x.device) if need_dw else None
         rc = rt.lib().prb_qknorm_rope(x.data_ptr(), dy.data_ptr(), rt.ptr(w), pos.data_ptr(), inv_f.data_ptr(),
                                       dx.data_ptr(), rt.ptr(rstd), rt.ptr(dw), T, Hh, D, x.stride(0), dy.stride(0),
-                                      float(ctx.eps), 1, rt.stream_ptr(x.device))
+                                      dx.stride(0), float(ctx.eps), 1, rt.stream_ptr(x.device))
         rt.check(rc, "prb_qknorm_rope(bwd)")
-        # dx is written with x's pitch
         return dx, (dw.to(w.dtype) if need_dw else None), None, None, None
 
 
@@ -74,3 +73,68 @@ def qknorm_rope(x: torch.Tensor, w: torch.Tensor | None, pos: torch.Tensor, inv_
             x = x.contiguous()
         return _QKNormRope.apply(x, w, pos.to(torch.int32), inv_f, eps)
     return qknorm_rope_ref(x, w, pos, inv_f, eps)
+
+
+class _QKVNormRope(torch.autograd.Function):
+    """Splits a packed qkv projection, applies per-head RMSNorm + RoPE to q and k, and in
+    backward writes dq / dk / dv straight into one ``[T, W]`` gradient (no slice-backward
+    zero fills and adds)."""
+
+    @staticmethod
+    def forward(ctx, qkv, qw, kw, pos, inv_f, eps, nq, nkv, D):
+        T, W = qkv.shape
+        qd, kd = nq * D, nkv * D
+        q = torch.empty(T, nq, D, dtype=qkv.dtype, device=qkv.device)
+        k = torch.empty(T, nkv, D, dtype=qkv.dtype, device=qkv.device)
+        has_norm = qw is not None
+        rq = torch.empty(T * nq, dtype=torch.float32, device=qkv.device) if has_norm else None
+        rk = torch.empty(T * nkv, dtype=torch.float32, device=qkv.device) if has_norm else None
+        es = qkv.element_size()
+        st = rt.stream_ptr(qkv.device)
+        rc = rt.lib().prb_qknorm_rope(qkv.data_ptr(), None, rt.ptr(qw), pos.data_ptr(), inv_f.data_ptr(),
+                                      q.data_ptr(), rt.ptr(rq), None, T, nq, D, W, qd, 0, float(eps), 0, st)
+        rt.check(rc, "prb_qknorm_rope(q)")
+        rc = rt.lib().prb_qknorm_rope(qkv.data_ptr() + qd * es, None, rt.ptr(kw), pos.data_ptr(), inv_f.data_ptr(),
+                                      k.data_ptr(), rt.ptr(rk), None, T, nkv, D, W, kd, 0, float(eps), 0, st)
+        rt.check(rc, "prb_qknorm_rope(k)")
+        v = qkv[:, qd + kd:].view(T, nkv, D)
+        ctx.save_for_backward(qkv, qw, kw, pos, inv_f, rq, rk)
+        ctx.cfg = (eps, nq, nkv, D)
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        qkv, qw, kw, pos, inv_f, rq, rk = ctx.saved_tensors
+        eps, nq, nkv, D = ctx.cfg
+        T, W = qkv.shape
+        qd, kd = nq * D, nkv * D
+        es = qkv.element_size()
+        dqkv = torch.empty_like(qkv)
+        dq, dk = dq.contiguous(), dk.contiguous()
+        need_w = qw is not None and (ctx.needs_input_grad[1] or ctx.needs_input_grad[2])
+        dqw = torch.zeros(D, dtype=torch.float32, device=qkv.device) if need_w else None
+        dkw = torch.zeros(D, dtype=torch.float32, device=qkv.device) if need_w else None
+        st = rt.stream_ptr(qkv.device)
+        rc = rt.lib().prb_qknorm_rope(qkv.data_ptr(), dq.data_ptr(), rt.ptr(qw), pos.data_ptr(), inv_f.data_ptr(),
+                                      dqkv.data_ptr(), rt.ptr(rq), rt.ptr(dqw), T, nq, D, W, qd, W, float(eps), 1, st)
+        rt.check(rc, "prb_qknorm_rope(dq)")
+        rc = rt.lib().prb_qknorm_rope(qkv.data_ptr() + qd * es, dk.data_ptr(), rt.ptr(kw), pos.data_ptr(),
+                                      inv_f.data_ptr(), dqkv.data_ptr() + qd * es, rt.ptr(rk), rt.ptr(dkw), T, nkv, D,
+                                      W, kd, W, float(eps), 1, st)
+        rt.check(rc, "prb_qknorm_rope(dk)")
+        dqkv[:, qd + kd:].copy_(dv.reshape(T, kd))
+        return (dqkv, dqw.to(qw.dtype) if need_w else None, dkw.to(kw.dtype) if need_w else None, None, None, None,
+                None, None, None)
+
+
+def qkv_norm_rope(qkv: torch.Tensor, qw, kw, pos, inv_f, eps: float, nq: int, nkv: int, D: int):
+    """qkv: [T, (nq + 2 nkv) * D] -> (q [T, nq, D], k [T, nkv, D], v [T, nkv, D])."""
+    T = qkv.shape[0]
+    qd, kd = nq * D, nkv * D
+    if (qkv.is_cuda and qkv.dtype == torch.bfloat16 and D in (64, 128, 256) and inv_f.numel() * 2 == D
+            and qkv.is_contiguous() and (qw is None or qw.dtype == torch.bfloat16)):
+        return _QKVNormRope.apply(qkv, qw, kw, pos.to(torch.int32), inv_f, eps, nq, nkv, D)
+    q = qkv[:, :qd].view(T, nq, D)
+    k = qkv[:, qd:qd + kd].view(T, nkv, D)
+    v = qkv[:, qd + kd:].view(T, nkv, D)
+    return qknorm_rope(q, qw, pos, inv_f, eps), qknorm_rope(k, kw, pos, inv_f, eps), v

@@ -1,0 +1,88 @@
+import torch
+
+from prime_rl_b200.engine.engine import Engine
+from prime_rl_b200.engine.sampler import SamplingParams, sample
+from prime_rl_b200.models import SeqInfo, build_model, resolve_arch
+
+
+def _engine(name="tiny-qwen3", **kw):
+    arch = resolve_arch(name)
+    model = build_model(arch, device="cpu", dtype=torch.float32)
+    return arch, model, Engine(model, num_pages=256, page_size=16, **kw)
+
+
+def _greedy_reference(model, prompt, n):
+    toks = list(prompt)
+    for _ in range(n):
+        ids = torch.tensor(toks)
+        h = model(ids, SeqInfo.from_lengths([len(toks)], "cpu"))
+        toks.append(int(model.logits(h[-1:]).argmax(-1)))
+    return toks[len(prompt):]
+
+
+def test_greedy_decode_matches_uncached_forward():
+    arch, model, eng = _engine()
+    prompts = [torch.randint(0, arch.vocab_size, (n,)).tolist() for n in (5, 23, 40)]
+    reqs = eng.generate_sync(prompts, SamplingParams(max_tokens=12, temperature=0.0))
+    for p, r in zip(prompts, reqs):
+        assert r.output == _greedy_reference(model, p, 12)
+        assert r.finish_reason == "length" and len(r.logprobs) == 12
+    assert eng.cache.blocks.num_free + len(eng.cache.blocks.prefix_cache) == 256
+
+
+def test_prefix_sharing_and_salt():
+    arch, model, eng = _engine()
+    prompt = torch.randint(0, arch.vocab_size, (50,)).tolist()
+    sp = SamplingParams(max_tokens=4, temperature=0.0)
+    a = eng.generate_sync([prompt], sp, cache_salt="1")[0]
+    hits0 = eng.stats["prefix_hits"]
+    b = eng.generate_sync([prompt] * 3, sp, cache_salt="1")
+    assert eng.stats["prefix_hits"] - hits0 == 3 * 48          # 3 full pages of 16 tokens each
+    assert all(r.output == a.output for r in b)
+    hits1 = eng.stats["prefix_hits"]
+    eng.generate_sync([prompt], sp, cache_salt="2")            # new policy version: no reuse
+    assert eng.stats["prefix_hits"] == hits1
+
+
+def test_moe_engine_returns_routed_experts_and_logprobs():
+    arch, model, eng = _engine("tiny-qwen3-moe")
+    eng.runner.capture_routed = True
+    prompt = torch.randint(0, arch.vocab_size, (20,)).tolist()
+    r = eng.generate_sync([prompt], SamplingParams(max_tokens=5, temperature=1.0, seed=3,
+                                                   return_routed_experts=True))[0]
+    assert len(r.routed) == 5 and r.routed[0].shape == (arch.num_hidden_layers, arch.num_experts_per_tok)
+    assert all(lp <= 0 for lp in r.logprobs)
+    # the reported logprob is the model's log-probability of the sampled token
+    ids = torch.tensor(prompt + r.output)
+    h = model(ids, SeqInfo.from_lengths([len(ids)], "cpu"))
+    lp = torch.log_softmax(model.logits(h).float(), -1)
+    for i, tok in enumerate(r.output):
+        assert abs(float(lp[len(prompt) - 1 + i, tok]) - r.logprobs[i]) < 1e-3
+
+
+def test_sampler_truncation_and_mask():
+    logits = torch.tensor([[5.0, 4.0, 1.0, 0.0, -1.0]] * 2)
+    tok, lp, masks = sample(logits, torch.tensor([1.0, 1.0]), torch.tensor([2, -1]), torch.tensor([1.0, 0.6]),
+                            want_mask=True)
+    assert set(masks[0].tolist()) == {0, 1} and int(tok[0]) in (0, 1)
+    assert masks[1].tolist() == [0]                 # top-p 0.6 keeps only the 0.72 head
+    assert abs(float(lp[1])) < 1e-6                 # renormalised over the kept set
+    g_tok, _, _ = sample(logits, torch.tensor([0.0, 0.0]), torch.tensor([-1, -1]), torch.tensor([1.0, 1.0]))
+    assert g_tok.tolist() == [0, 0]
+
+
+def test_pause_blocks_progress_and_resume_continues():
+    import time
+    arch, model, eng = _engine()
+    eng.start()
+    eng.pause()
+    req = eng.submit(__import__("prime_rl_b200.engine.engine", fromlist=["Request"]).Request(
+        prompt=[1, 2, 3], params=SamplingParams(max_tokens=3, temperature=0.0)))
+    time.sleep(0.2)
+    assert req.finish_reason is None and not req.output
+    eng.resume()
+    t0 = time.time()
+    while req.finish_reason is None and time.time() - t0 < 20:
+        time.sleep(0.01)
+    assert req.finish_reason == "length"
+    eng.shutdown()
