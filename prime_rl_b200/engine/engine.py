@@ -157,7 +157,10 @@ class Engine:
         r.finish_reason = reason
         self.cache.free(r.kv)
         if r.future is not None and r.loop is not None:
-            r.loop.call_soon_threadsafe(lambda: r.future.done() or r.future.set_result(r))
+            try:
+                r.loop.call_soon_threadsafe(lambda: r.future.done() or r.future.set_result(r))
+            except RuntimeError:
+                pass  # the client's event loop is gone (caller shut down mid-request)
 
     def _admit(self) -> list[Request]:
         """Moves waiting requests to running while pages and the prefill budget allow."""

@@ -33,6 +33,8 @@ class SeqInfo:
     # optional per-layer expert ids captured by the rollout engine ([T, layers, k])
     routed_experts: torch.Tensor | None = None
     cp: object | None = None      # context-parallel state (parallel/cp.py)
+    # attention outputs kept across activation recomputation, keyed by layer (ops/attention.py)
+    attn_cache: dict | None = None
 
     @classmethod
     def from_lengths(cls, lengths: list[int], device) -> "SeqInfo":
@@ -137,7 +139,8 @@ class Attention(nn.Module):
             o = seq.cp.attention(q, k, v, seq, window=self.window, sinks=self.sinks, backend=self.backend)
         else:
             o = attn_ops.attention(q, k, v, seq.cu_seqlens, seq.max_seqlen, causal=True, window=self.window,
-                                   sinks=self.sinks, backend=self.backend)
+                                   sinks=self.sinks, backend=self.backend, cache=seq.attn_cache,
+                                   cache_key=self.layer_idx)
         return self.o_proj(o.reshape(T, q_dim))
 
 

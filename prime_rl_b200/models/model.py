@@ -41,6 +41,7 @@ class CausalLM(nn.Module):
             self.lm_head = Linear(arch.hidden_size, arch.vocab_size, std=arch.initializer_range, dtype=dtype,
                                   device=device)
         self.ac_every: int | None = None       # recompute every n-th layer in backward (None = never)
+        self.cache_attention = True            # keep attention outputs across recomputation
         self.layer_hooks = None                # parallel/fsdp.py installs gather/release hooks here
 
     # ------------------------------------------------------------------ init
@@ -75,8 +76,12 @@ class CausalLM(nn.Module):
         """input_ids: [T] (or [1, T]) packed ids -> final hidden states [T, H] (normed)."""
         ids = input_ids.reshape(-1)
         h = self.model.embed_tokens(ids)
+        use_ac = self.ac_every is not None and self.training and torch.is_grad_enabled()
+        # recomputation re-runs everything but the attention kernel: its output (and lse) of the
+        # first pass is kept, 2 bytes x q_dim per token and layer
+        seq.attn_cache = {} if (use_ac and self.cache_attention) else None
         for i, layer in enumerate(self.model.layers):
-            if self.ac_every is not None and self.training and i % self.ac_every == 0 and torch.is_grad_enabled():
+            if use_ac and i % self.ac_every == 0:
                 h = checkpoint(self._run_layer, layer, i, h, seq, use_reentrant=False)
             else:
                 h = self._run_layer(layer, i, h, seq)

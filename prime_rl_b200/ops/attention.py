@@ -47,44 +47,78 @@ def attention_ref(q, k, v, cu_seqlens, *, causal=True, window=None, sinks=None, 
     return o.to(q.dtype)
 
 
-_flash = None
+def _fa2():
+    from flash_attn.flash_attn_interface import _flash_attn_varlen_backward, _flash_attn_varlen_forward
 
-
-def _flash_attn():
-    global _flash
-    if _flash is None:
-        from flash_attn import flash_attn_varlen_func
-
-        _flash = flash_attn_varlen_func
-    return _flash
+    return _flash_attn_varlen_forward, _flash_attn_varlen_backward
 
 
 def default_backend(device: torch.device) -> str:
     if device.type != "cuda":
         return "sdpa"
-    try:
-        from . import flash_native
+    from . import flash_native
 
-        if flash_native.available():
-            return "tcgen05"
-    except Exception:
-        pass
-    return "flash_attention_2"
+    return "tcgen05" if flash_native.available() else "flash_attention_2"
+
+
+class _FlashAttention(torch.autograd.Function):
+    """Forward: the tcgen05 kernel (or the flash-attn library for shapes it does not cover).
+    Backward: flash-attn library kernel on the saved (q, k, v, out, lse). ``cached`` carries
+    (out, lse) computed by an earlier no-grad pass of the same layer (activation
+    recomputation), in which case the forward launches nothing."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu, max_seqlen, scale, window, backend, cached, store):
+        ws = (-1, -1) if window is None else (window - 1, 0)
+        if cached is not None:
+            out, lse = cached
+        elif backend == "tcgen05":
+            from . import flash_native
+
+            out, lse = flash_native.flash_fwd(q, k, v, cu, scale=scale, window=window)
+        else:
+            fwd, _ = _fa2()
+            out, lse, _, _ = fwd(q, k, v, cu, cu, max_seqlen, max_seqlen, 0.0, scale, True, ws[0], ws[1], 0.0, None,
+                                 False, None)
+        if store is not None:
+            store.append((out, lse))
+        ctx.save_for_backward(q, k, v, out, lse, cu)
+        ctx.cfg = (max_seqlen, scale, ws)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse, cu = ctx.saved_tensors
+        max_seqlen, scale, ws = ctx.cfg
+        _, bwd = _fa2()
+        dq, dk, dv = torch.empty_like(q), torch.empty(k.shape, dtype=k.dtype, device=k.device), \
+            torch.empty(v.shape, dtype=v.dtype, device=v.device)
+        bwd(dout.contiguous(), q, k, v, out, lse, dq, dk, dv, cu, cu, max_seqlen, max_seqlen, 0.0, scale, True, ws[0],
+            ws[1], 0.0, None, False, None)
+        return dq, dk, dv, None, None, None, None, None, None, None
 
 
 def attention(q, k, v, cu_seqlens, max_seqlen: int, *, causal: bool = True, window: int | None = None,
-              sinks: torch.Tensor | None = None, scale: float | None = None, backend: str = "auto"):
-    if backend in ("auto", None):
+              sinks: torch.Tensor | None = None, scale: float | None = None, backend: str = "auto",
+              cache: dict | None = None, cache_key=None):
+    """``cache`` (a dict owned by the caller) lets an activation-recomputation pass reuse the
+    attention output of the first pass of the same layer: a call whose ``cache_key`` is absent
+    computes and stores ``(out, lse)``; the next call with that key consumes the entry and
+    launches no forward kernel."""
+    if backend in ("auto", None, "flash_attention_3", "flash_attention_4"):
         backend = default_backend(q.device)
-    if backend in ("flash_attention_3", "flash_attention_4"):
-        backend = default_backend(q.device)
-    if backend == "tcgen05" and sinks is None and q.shape[-1] == 128 and q.dtype == torch.bfloat16:
-        from . import flash_native
-
-        return flash_native.flash_attn_varlen(q, k, v, cu_seqlens, max_seqlen, causal=causal, window=window,
-                                              scale=scale)
-    if backend in ("tcgen05", "flash_attention_2") and q.is_cuda and sinks is None:
-        ws = (-1, -1) if window is None else (window - 1, 0)
-        return _flash_attn()(q, k, v, cu_seqlens, cu_seqlens, max_seqlen, max_seqlen, softmax_scale=scale,
-                             causal=causal, window_size=ws)
-    return attention_ref(q, k, v, cu_seqlens, causal=causal, window=window, sinks=sinks, scale=scale)
+    fast = q.is_cuda and sinks is None and causal and q.dtype == torch.bfloat16 and backend != "sdpa"
+    if not fast:
+        return attention_ref(q, k, v, cu_seqlens, causal=causal, window=window, sinks=sinks, scale=scale)
+    if backend == "tcgen05" and q.shape[-1] != 128:
+        backend = "flash_attention_2"
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    cached = store = None
+    if cache is not None:
+        cached = cache.pop(cache_key, None)
+        if cached is None:
+            store = []
+    out = _FlashAttention.apply(q, k, v, cu_seqlens, max_seqlen, scale, window, backend, cached, store)
+    if store:
+        cache[cache_key] = store.pop()
+    return out

@@ -1,0 +1,39 @@
+"""Front end of the hand-written flash-attention kernels (``csrc/flash_attn.cu``)."""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import native
+from . import _runtime as rt
+
+
+def available() -> bool:
+    try:
+        return hasattr(native.cuda(), "prb_flash_fwd")
+    except Exception:
+        return False
+
+
+def flash_fwd(q, k, v, cu_seqlens, *, scale: float | None = None, window: int | None = None):
+    """q: [T, Hq, 128] bf16 (contiguous heads), k/v: [T, Hkv, 128] bf16 (may be strided over
+    tokens). Returns (out [T, Hq, 128] bf16, lse [Hq, T] fp32, natural log)."""
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    assert D == 128 and q.dtype == torch.bfloat16
+    for t in (q, k, v):
+        assert t.stride(2) == 1 and t.stride(1) == D, "heads must be contiguous"
+    out = torch.empty(T, Hq, D, dtype=q.dtype, device=q.device)
+    lse = torch.empty(Hq, T, dtype=torch.float32, device=q.device)
+    num_docs = cu_seqlens.numel() - 1
+    max_pairs = (T + 255) // 256 + num_docs
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    status = rt.status_tensor(q.device)
+    rc = rt.lib().prb_flash_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                cu_seqlens.data_ptr(), num_docs, T, Hq, Hkv, D, q.stride(0), k.stride(0), v.stride(0),
+                                out.stride(0), float(scale), int(window or 0), max_pairs, status.data_ptr(),
+                                rt.stream_ptr(q.device))
+    rt.check(rc, "prb_flash_fwd")
+    return out, lse

@@ -240,10 +240,10 @@ class RLTrainer:
     # ------------------------------------------------------------------ loop
     def run(self) -> None:
         cfg = self.config
-        if self.weight_sender is not None and self.progress.step == 0 or \
-                (self.weight_sender is not None and cfg.resume is not None):
-            # startup policy so that the (stateless) inference engine is seeded
-            self.weight_sender.broadcast(self.model, max(self.progress.step - 1, 0))
+        if self.weight_sender is not None and self.progress.step > 0:
+            # resumed run: re-seed the (stateless) inference engines with the restored policy; a
+            # fresh run starts from weights both sides already share
+            self.weight_sender.broadcast(self.model, self.progress.step - 1)
         while cfg.max_steps is None or self.progress.step < cfg.max_steps:
             step = self.progress.step
             m = self.step()

@@ -362,3 +362,52 @@ def test_qkv_norm_rope_packed_projection():
     y = rope.qknorm_rope(qs, qw.detach(), pos, inv_f, 1e-6)
     y.backward(gq)
     assert qs.grad.shape == (T, nq, D)
+
+
+@pytest.mark.parametrize("lens,window", [([256], None), ([300, 77, 1000], None), ([5, 640, 129], None),
+                                         ([700, 300], 200), ([2048], None)])
+def test_flash_fwd_matches_reference(lens, window):
+    from prime_rl_b200.ops import attention as A, flash_native
+    T, Hq, Hkv, D = sum(lens), 8, 2, 128
+    q, k, v = _rand(T, Hq, D), _rand(T, Hkv, D), _rand(T, Hkv, D)
+    cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
+    cu[1:] = torch.tensor(lens).cumsum(0)
+    cu = cu.to(DEV)
+    out, lse = flash_native.flash_fwd(q, k, v, cu, window=window)
+    rt.check_status()
+    ref = A.attention_ref(q, k, v, cu, window=window)
+    _close(out, ref, atol=2e-2, rtol=2e-2)
+    # lse against an fp32 computation
+    scale = D ** -0.5
+    kk = k.float().repeat_interleave(Hq // Hkv, 1)
+    s = torch.einsum("thd,shd->hts", q.float(), kk) * scale
+    pos = torch.arange(T, device=DEV)
+    doc = torch.searchsorted(cu[1:].long().contiguous(), pos, right=True)
+    mask = (doc[:, None] == doc[None, :]) & (pos[None, :] <= pos[:, None])
+    if window is not None:
+        mask &= pos[:, None] - pos[None, :] < window
+    ref_lse = torch.logsumexp(s.masked_fill(~mask[None], float("-inf")), dim=-1)
+    _close(lse, ref_lse, atol=1e-2, rtol=1e-3)
+
+
+def test_flash_attention_autograd_and_cache():
+    from prime_rl_b200.ops import attention as A
+    lens = [300, 212]
+    T, Hq, Hkv, D = sum(lens), 4, 2, 128
+    q, k, v = (_rand(T, Hq, D).requires_grad_(), _rand(T, Hkv, D).requires_grad_(), _rand(T, Hkv, D).requires_grad_())
+    cu = torch.tensor([0, 300, 512], dtype=torch.int32, device=DEV)
+    cache = {}
+    with torch.no_grad():
+        o1 = A.attention(q, k, v, cu, 300, cache=cache, cache_key=0)
+    assert 0 in cache
+    launches = rt.launch_count()
+    o2 = A.attention(q, k, v, cu, 300, cache=cache, cache_key=0)
+    assert rt.launch_count() == launches and 0 not in cache    # reused, nothing launched
+    assert torch.equal(o1, o2)
+    do = _rand(T, Hq, D)
+    o2.backward(do)
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    A.attention_ref(qr, kr, vr, cu).backward(do.float())
+    _close(q.grad, qr.grad, atol=5e-2, rtol=5e-2)
+    _close(k.grad, kr.grad, atol=5e-2, rtol=5e-2)
+    _close(v.grad, vr.grad, atol=5e-2, rtol=5e-2)
