@@ -2,7 +2,7 @@
 
 ``libprb200_cuda.so``  every ``csrc/*.cu`` compiled for sm_100a (nvcc cross-compiles on a host
                        without a GPU) and linked against the (static) CUDA runtime only;
-``libprb200_cpu.so``   the C++ CPU optimizer (``csrc/cpu/*.cpp``) with OpenMP.
+``libprb200_cpu.so``   the C++ CPU optimizer (``csrc/cpu/*.cpp``), std::thread parallel.
 
 Both expose a plain C ABI and are loaded through ``ctypes`` (see ``native/__init__.py``), so
 there is no dependency on torch headers and a full rebuild takes well under a minute.
@@ -89,7 +89,7 @@ def build_cpu() -> Path:
     if CPU_LIB.exists() and CPU_LIB.stat().st_mtime > _newest(sources):
         return CPU_LIB
     cxx = os.environ.get("CXX", "g++")
-    cmd = [cxx, "-O3", "-std=c++17", "-fPIC", "-shared", "-fopenmp", "-fvisibility=hidden", "-o", str(CPU_LIB),
+    cmd = [cxx, "-O3", "-std=c++17", "-fPIC", "-shared", "-pthread", "-fvisibility=hidden", "-o", str(CPU_LIB),
            *map(str, sources)]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:

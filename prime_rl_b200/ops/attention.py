@@ -47,6 +47,11 @@ def attention_ref(q, k, v, cu_seqlens, *, causal=True, window=None, sinks=None, 
     return o.to(q.dtype)
 
 
+# Which kernel computes the attention backward when the forward ran on the tcgen05 kernel:
+# "tcgen05" (csrc/flash_attn_bwd.cu) or "flash_attention_2" (library).
+BWD_BACKEND = "tcgen05"
+
+
 def _fa2():
     from flash_attn.flash_attn_interface import _flash_attn_varlen_backward, _flash_attn_varlen_forward
 
@@ -83,13 +88,19 @@ class _FlashAttention(torch.autograd.Function):
         if store is not None:
             store.append((out, lse))
         ctx.save_for_backward(q, k, v, out, lse, cu)
-        ctx.cfg = (max_seqlen, scale, ws)
+        ctx.cfg = (max_seqlen, scale, ws, window, backend)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, out, lse, cu = ctx.saved_tensors
-        max_seqlen, scale, ws = ctx.cfg
+        max_seqlen, scale, ws, window, backend = ctx.cfg
+        if backend == "tcgen05" and BWD_BACKEND == "tcgen05":
+            from . import flash_native
+
+            if flash_native.bwd_available():
+                dq, dk, dv = flash_native.flash_bwd(dout, q, k, v, out, lse, cu, scale=scale, window=window)
+                return dq, dk, dv, None, None, None, None, None, None, None
         _, bwd = _fa2()
         dq, dk, dv = torch.empty_like(q), torch.empty(k.shape, dtype=k.dtype, device=k.device), \
             torch.empty(v.shape, dtype=v.dtype, device=v.device)

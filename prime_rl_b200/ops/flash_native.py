@@ -37,3 +37,38 @@ def flash_fwd(q, k, v, cu_seqlens, *, scale: float | None = None, window: int | 
                                 rt.stream_ptr(q.device))
     rt.check(rc, "prb_flash_fwd")
     return out, lse
+
+
+def bwd_available() -> bool:
+    try:
+        return hasattr(native.cuda(), "prb_flash_bwd")
+    except Exception:
+        return False
+
+
+def flash_bwd(dout, q, k, v, out, lse, cu_seqlens, *, scale: float | None = None, window: int | None = None,
+              dk_out: torch.Tensor | None = None, dv_out: torch.Tensor | None = None):
+    """Returns (dq [T, Hq, 128], dk, dv [T, Hkv, 128]) in bf16."""
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    assert D == 128 and q.dtype == torch.bfloat16
+    dout = dout.contiguous()
+    for t in (q, k, v, out, dout):
+        assert t.stride(2) == 1 and t.stride(1) == D, "heads must be contiguous"
+    dev = q.device
+    dq = torch.empty(T, Hq, D, dtype=q.dtype, device=dev)
+    dk = dk_out if dk_out is not None else torch.empty(T, Hkv, D, dtype=q.dtype, device=dev)
+    dv = dv_out if dv_out is not None else torch.empty(T, Hkv, D, dtype=q.dtype, device=dev)
+    delta = torch.empty(Hq, T, dtype=torch.float32, device=dev)
+    dq_acc = torch.empty(T, Hq, D, dtype=torch.float32, device=dev)
+    num_docs = cu_seqlens.numel() - 1
+    max_blocks = (T + 127) // 128 + num_docs
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    status = rt.status_tensor(dev)
+    rc = rt.lib().prb_flash_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(),
+                                lse.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+                                dv.data_ptr(), cu_seqlens.data_ptr(), num_docs, T, Hq, Hkv, D, q.stride(0),
+                                k.stride(0), v.stride(0), out.stride(0), dout.stride(0), dk.stride(0), dv.stride(0),
+                                float(scale), int(window or 0), max_blocks, status.data_ptr(), rt.stream_ptr(dev))
+    rt.check(rc, "prb_flash_bwd")
+    return dq, dk, dv

@@ -1,0 +1,174 @@
+"""SFT trainer: token-weighted cross-entropy over packed rows, normalised by the *global*
+number of loss tokens of the step (all-reduced), optional validation loop, checkpoints and
+weight broadcasts for online evals (reference: src/prime_rl/trainer/sft/train.py)."""
+
+from __future__ import annotations
+
+import time
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+from ... import monitors as monitors_mod
+from ...configs.sft import SFTConfig
+from ...models import SeqInfo, apply_lora, build_model, resolve_arch
+from ...parallel import get_parallel_dims, get_world, setup_distributed
+from ...utils.logger import get_logger, setup_logger
+from ..ckpt import CheckpointManager, Progress
+from ..loss import shift_left
+from ..optim import setup_optimizer
+from ..perf import PerfCounter
+from .data import setup_dataset
+
+
+class SFTTrainer:
+    def __init__(self, config: SFTConfig, device: torch.device | None = None):
+        self.config = config
+        self.world = get_world()
+        self.device = device if device is not None else setup_distributed(timeout_seconds=config.dist_timeout_seconds)
+        self.logger = get_logger()
+        self.progress = Progress()
+        self.run_dir = Path(config.output_dir) / (config.run.dir or config.run.name or "")
+
+    def setup(self) -> "SFTTrainer":
+        cfg, mc = self.config, self.config.model
+        self.arch = resolve_arch(mc.name, mc.arch)
+        if mc.debug.num_layers is not None:
+            self.arch = self.arch.model_copy(update={"num_hidden_layers": mc.debug.num_layers})
+        self.dims = get_parallel_dims(mc, self.world.world_size, is_moe=self.arch.is_moe,
+                                      num_experts=self.arch.num_experts)
+        dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+        self.model = build_model(self.arch, device=self.device, dtype=dtype, attn_backend=mc.attn)
+        p = Path(mc.name)
+        if p.is_dir() and not mc.debug.random_init:
+            from ..weights import load_hf_checkpoint
+
+            load_hf_checkpoint(self.model, p)
+        if mc.lora is not None:
+            apply_lora(self.model, mc.lora.rank, mc.lora.alpha, mc.lora.target_modules, mc.lora.modules_to_save)
+        if mc.ac is not None:
+            self.model.ac_every = mc.ac.freq
+        self.model.train()
+        multi = dist.is_initialized() and self.world.world_size > 1
+        self.dp_group = self.dims.group("dp_cp") if multi else None
+        zero = multi and mc.lora is None
+        self.optimizer = setup_optimizer(cfg.optim, self.model, max_steps=cfg.max_steps, scheduler_config=cfg.scheduler,
+                                         dp_group=self.dp_group,
+                                         shard_group=self.dims.group("dp_shard_cp") if zero else None)
+        self.monitor = monitors_mod.setup(cfg.monitors, self.run_dir, "trainer", is_master=self.world.is_master)
+        self.ckpt = CheckpointManager(self.run_dir, cfg.ckpt, is_master=self.world.is_master, rank=self.world.rank) \
+            if cfg.ckpt is not None or cfg.resume is not None else None
+        self.dataset = setup_dataset(cfg.data, self.arch.vocab_size, self.world.rank, self.world.world_size)
+        self.val_dataset = setup_dataset(cfg.val.data, self.arch.vocab_size, self.world.rank, self.world.world_size) \
+            if cfg.val is not None else None
+        if cfg.resume is not None and self.ckpt is not None:
+            step = cfg.resume.step if cfg.resume.step is not None else self.ckpt.latest()
+            if step is not None:
+                self.ckpt.load(step, self.model, self.optimizer, self.progress, self.dataset)
+                self.progress.step = step + 1
+        self.data_iter = iter(self.dataset)
+        self.micro_steps = max(1, cfg.data.batch_size // (cfg.data.micro_batch_size * self.world.world_size))
+        dev_name = torch.cuda.get_device_name(self.device) if self.device.type == "cuda" else "cpu"
+        self.perf = PerfCounter(self.arch, cfg.data.seq_len, self.world.world_size, dev_name, lora=mc.lora is not None)
+        return self
+
+    def _row_loss(self, row: dict) -> tuple[torch.Tensor, torch.Tensor]:
+        """Sum of the label NLL over loss tokens of one packed row, and the token count."""
+        ids = row["input_ids"].to(self.device)
+        mask = row["loss_mask"].to(self.device)
+        seq = SeqInfo.from_lengths(row["sequence_lengths"], self.device)
+        labels = shift_left(ids)
+        lmask = shift_left(mask.to(torch.float32)).bool()        # position t predicts token t + 1
+        # the last position of each document predicts the next document's first token: drop it
+        ends = torch.tensor(row["sequence_lengths"], device=self.device).cumsum(0) - 1
+        lmask[ends] = False
+        hidden = self.model(ids, seq)
+        lp, _ = self.model.logprobs_entropy(hidden, labels)
+        return -(lp * lmask).sum(), lmask.sum()
+
+    def step(self) -> dict:
+        t0 = time.perf_counter()
+        rows = [next(self.data_iter) for _ in range(self.micro_steps * self.config.data.micro_batch_size)]
+        # global number of loss tokens of this step (same masks as _row_loss, computed on the host)
+        exact = 0
+        for r in rows:
+            m = shift_left(r["loss_mask"].float()).bool()
+            ends = torch.tensor(r["sequence_lengths"]).cumsum(0) - 1
+            m[ends] = False
+            exact += int(m.sum())
+        count = torch.tensor([float(exact)], device=self.device)
+        if self.dp_group is not None:
+            dist.all_reduce(count, group=self.dp_group)
+        denom = count.clamp_min(1.0)
+        total = torch.zeros((), device=self.device)
+        for r in rows:
+            nll, _ = self._row_loss(r)
+            (nll / denom.squeeze()).backward()
+            total += nll.detach()
+        self.optimizer.reduce_gradients()
+        gnorm = self.optimizer.step()
+        self.optimizer.zero_grad()
+        if self.dp_group is not None:
+            dist.all_reduce(total, group=self.dp_group)
+        tokens = len(rows) * self.config.data.seq_len * self.world.world_size
+        self.progress.total_tokens += tokens
+        dt = time.perf_counter() - t0
+        tps = tokens / dt
+        return {"loss": float(total / denom.squeeze()), "optim/grad_norm": float(gnorm), "optim/lr": self.optimizer.lr,
+                "perf/throughput": tps, "perf/mfu": self.perf.mfu(tps), "time/step": dt, "loss_tokens": float(count)}
+
+    @torch.no_grad()
+    def validate(self, num_rows: int = 8) -> float:
+        self.model.eval()
+        it = iter(self.val_dataset)
+        nll, cnt = torch.zeros((), device=self.device), torch.zeros((), device=self.device)
+        for _ in range(num_rows):
+            a, b = self._row_loss(next(it))
+            nll += a
+            cnt += b
+        if self.dp_group is not None:
+            dist.all_reduce(nll, group=self.dp_group)
+            dist.all_reduce(cnt, group=self.dp_group)
+        self.model.train()
+        return float(nll / cnt.clamp_min(1))
+
+    def run(self) -> None:
+        cfg = self.config
+        while cfg.max_steps is None or self.progress.step < cfg.max_steps:
+            step = self.progress.step
+            if self.val_dataset is not None and ((step == 0 and cfg.val.eval_on_start) or
+                                                 (step > 0 and step % cfg.val.interval == 0)):
+                self.monitor.log({"val/loss": self.validate()}, step)
+            m = self.step()
+            self.monitor.log(m, step)
+            if self.world.is_master:
+                self.logger.info(f"step {step} | loss {m['loss']:.4f} | grad_norm {m['optim/grad_norm']:.3f} | "
+                                 f"{m['perf/throughput']:.0f} tok/s")
+            if self.ckpt is not None and cfg.ckpt is not None and cfg.ckpt.interval and \
+                    (step + 1) % cfg.ckpt.interval == 0:
+                self.ckpt.save(step, self.model, self.optimizer, self.progress, self.dataset)
+                self.ckpt.maybe_clean()
+            self.progress.step += 1
+        self.monitor.finalize()
+
+
+def train(config: SFTConfig) -> SFTTrainer:
+    setup_logger(config.log.level, tag=f"sft:{get_world().rank}", json_logging=config.log.json_logging)
+    t = SFTTrainer(config).setup()
+    t.run()
+    return t
+
+
+def main(argv: list[str] | None = None) -> None:
+    from ...configs.base import cli
+
+    config = cli(SFTConfig, argv)
+    if config.dry_run:
+        print(config.to_json())
+        return
+    train(config)
+
+
+if __name__ == "__main__":
+    main()

@@ -411,3 +411,23 @@ def test_flash_attention_autograd_and_cache():
     _close(q.grad, qr.grad, atol=5e-2, rtol=5e-2)
     _close(k.grad, kr.grad, atol=5e-2, rtol=5e-2)
     _close(v.grad, vr.grad, atol=5e-2, rtol=5e-2)
+
+
+@pytest.mark.parametrize("lens,window", [([128], None), ([256], None), ([300, 77, 1000], None), ([700, 300], 200)])
+def test_flash_bwd_matches_reference(lens, window):
+    from prime_rl_b200.ops import attention as A, flash_native
+    T, Hq, Hkv, D = sum(lens), 4, 2, 128
+    q, k, v = _rand(T, Hq, D), _rand(T, Hkv, D), _rand(T, Hkv, D)
+    cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
+    cu[1:] = torch.tensor(lens).cumsum(0)
+    cu = cu.to(DEV)
+    out, lse = flash_native.flash_fwd(q, k, v, cu, window=window)
+    do = _rand(T, Hq, D)
+    dq, dk, dv = flash_native.flash_bwd(do, q, k, v, out, lse, cu, window=window)
+    rt.check_status()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    A.attention_ref(qr, kr, vr, cu, window=window).backward(do.float())
+    for got, want, name in ((dq, qr.grad, "dq"), (dk, kr.grad, "dk"), (dv, vr.grad, "dv")):
+        rel = (got.float() - want).norm() / want.norm()
+        assert rel < 2e-2, f"{name}: relative error {rel:.4f}"
+        _close(got, want, atol=0.1, rtol=5e-2)
