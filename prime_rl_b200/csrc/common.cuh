@@ -27,15 +27,9 @@ enum StatusCode : int {
   kBadArgument = 6,
 };
 
-// Two seconds of GPU time; generous for any single stage, short enough that a stuck
-// kernel ends by itself.
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
-
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
+// About two seconds of SM clock (4e9 cycles at ~2 GHz); generous for any single stage, short
+// enough that a stuck kernel ends by itself.
+constexpr long long kWaitLimitCycles = 4000000000ll;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -83,15 +77,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Bounded wait on an mbarrier phase. Returns false (after recording `code` in *status)
-// when the limit runs out or when another thread already recorded a failure.
+// when the limit runs out or when another thread already recorded a failure. The clock and
+// the status word are only looked at every 1024 failed polls: the common case (the phase
+// completes within a few polls) costs nothing but the try_wait itself.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_timer_ns();
   uint32_t spins = 0;
+  long long t0 = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0xff) == 0) {
+    if ((++spins & 0x3ff) == 0) {
       if (*reinterpret_cast<volatile int*>(status) != 0) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitCycles) {
         atomicCAS(status, 0, code);
         return false;
       }

@@ -273,11 +273,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tmem_ld_wait();
       const int col0 = j * kFaBN;
       const bool need_mask = (col0 + kFaBN - 1 > q0[t]) || (p.window > 0 && q1[t] - 1 - col0 >= p.window);
+      // raw scores; masked entries become -inf. The running reference `m` (log2 domain) only
+      // moves when the block maximum exceeds it by more than 8: P then stays below 2^8, and
+      // most blocks need no rescale of O at all.
       float s[64];
       float mx = -INFINITY;
 #pragma unroll
       for (int c = 0; c < 64; ++c) {
-        float x = __uint_as_float(sv[c >> 5][c & 31]) * p.scale_log2;
+        float x = __uint_as_float(sv[c >> 5][c & 31]);
         if (need_mask) {
           const int col = col0 + c;
           const bool keep = (col <= row) && (p.window <= 0 || row - col < p.window);
@@ -286,21 +289,23 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         s[c] = x;
         mx = fmaxf(mx, x);
       }
-      const float m_new = fmaxf(m, mx);
-      // rows past the document end (and fully masked rows) keep m = -inf: use 0 as the
-      // reference point so that no NaN is produced; their output is never stored
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = ex2(m - m_use);   // m = -inf -> 0
+      const float m_blk = mx * p.scale_log2;          // scale > 0, so max commutes with it
+      float alpha = 1.f;
+      if (m_blk > m + 8.f) {                          // also true on the first unmasked block (m = -inf)
+        alpha = ex2(m - m_blk);                       // m = -inf -> 0
+        m = m_blk;
+      }
+      // rows without any valid key so far keep m = -inf: use 0 so that no NaN appears
+      const float neg_m = (m == -INFINITY) ? 0.f : -m;
       float sum = 0.f;
       uint32_t pk[32];
 #pragma unroll
       for (int c = 0; c < 64; c += 2) {
-        const float p0 = ex2(s[c] - m_use), p1 = ex2(s[c + 1] - m_use);
+        const float p0 = ex2(fmaf(s[c], p.scale_log2, neg_m)), p1 = ex2(fmaf(s[c + 1], p.scale_log2, neg_m));
         sum += p0 + p1;
         pk[c >> 1] = pack_bf16(p0, p1);
       }
       l = l * alpha + sum;
-      m = m_new;
       if (it > 0) {
         // O holds blocks < j: wait for the last PV, then rescale in place
         ok = mbar_wait(&o_ready[t], (it - 1) & 1, p.status, kTimeoutTmemFull);

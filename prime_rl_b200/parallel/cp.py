@@ -1,0 +1,184 @@
+"""Context parallelism: the packed token stream is cut into ``cp`` contiguous chunks, every
+non-attention layer runs on the local chunk, attention sees the whole (causal) context.
+
+``ring``     (the reference's default, utils/cp.py:40-70 + layers/ring_attn.py:218-368): K/V of
+             all chunks are all-gathered, local queries attend the keys up to the end of the
+             local chunk, dK/dV are reduce-scattered in backward.
+``ulysses``  (layers/ulysses_attn.py:53-152): all-to-all from sequence-sharded to head-sharded
+             q/k/v, full-sequence attention on ``heads / cp`` heads, all-to-all back; KV heads are
+             replicated when ``heads_kv < cp``.
+
+Both run on ``torch.distributed`` collectives (NCCL / gloo); per-token outputs (logprobs,
+entropy) are gathered back along the sequence for the loss.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import replace
+
+import torch
+import torch.distributed as dist
+
+from ..models.layers import SeqInfo
+from ..ops import attention as attn_ops
+
+
+class _AllGatherSeq(torch.autograd.Function):
+    """Concatenate the local chunks along dim 0. Backward: sum the incoming gradients over
+    ranks and keep the local slice (reduce-scatter)."""
+
+    @staticmethod
+    def forward(ctx, x, group, reduce_backward):
+        ctx.group, ctx.reduce = group, reduce_backward
+        n = dist.get_world_size(group)
+        parts = [torch.empty_like(x) for _ in range(n)]
+        dist.all_gather(parts, x.contiguous(), group=group)
+        ctx.rank, ctx.len = dist.get_rank(group), x.shape[0]
+        return torch.cat(parts, 0)
+
+    @staticmethod
+    def backward(ctx, dy):
+        if ctx.reduce:
+            dy = dy.contiguous()
+            dist.all_reduce(dy, group=ctx.group)
+        return dy[ctx.rank * ctx.len:(ctx.rank + 1) * ctx.len].contiguous(), None, None
+
+
+class _AllToAll(torch.autograd.Function):
+    """Equal-split all-to-all: input ``[cp, n, ...]`` (block i goes to rank i); backward is the
+    same exchange."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        x = x.contiguous()
+        out = torch.empty_like(x)
+        dist.all_to_all_single(out, x, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        dy = dy.contiguous()          # empty_like of a permuted gradient would keep its strides
+        dx = torch.empty_like(dy)
+        dist.all_to_all_single(dx, dy, group=ctx.group)
+        return dx, None
+
+
+def attention_offset_ref(q, k, v, q_pos, k_pos, q_doc, k_doc, *, window=None, sinks=None, scale=None):
+    """fp32 reference with explicit global positions / document ids for queries and keys."""
+    Hq, Hkv, D = q.shape[1], k.shape[1], q.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    kf = k.float().repeat_interleave(Hq // Hkv, dim=1)
+    vf = v.float().repeat_interleave(Hq // Hkv, dim=1)
+    s = torch.einsum("thd,shd->hts", q.float(), kf) * scale
+    mask = (q_doc[:, None] == k_doc[None, :]) & (k_pos[None, :] <= q_pos[:, None])
+    if window is not None:
+        mask &= q_pos[:, None] - k_pos[None, :] < window
+    s = s.masked_fill(~mask[None], float("-inf"))
+    if sinks is not None:
+        sk = sinks.float().view(Hq, 1, 1).expand(Hq, q.shape[0], 1)
+        p = torch.softmax(torch.cat([s, sk], -1), -1)[..., :-1]
+    else:
+        p = torch.softmax(s, -1)
+    return torch.einsum("hts,shd->thd", p, vf).to(q.dtype)
+
+
+class ContextParallel:
+    def __init__(self, group, cp: int, rank: int, style: str = "ring"):
+        self.group, self.cp, self.rank, self.style = group, cp, rank, style
+
+    # ------------------------------------------------------------------ sharding
+    def shard(self, t: torch.Tensor) -> torch.Tensor:
+        n = t.shape[0] // self.cp
+        return t[self.rank * n:(self.rank + 1) * n]
+
+    def shard_inputs(self, ids, labels, inv_temp, seq: SeqInfo):
+        T = ids.shape[0]
+        if T % self.cp:
+            raise ValueError(f"packed length {T} is not a multiple of cp={self.cp} (set pad_to_multiple_of)")
+        local = replace(seq, position_ids=self.shard(seq.position_ids), cp=self)
+        if seq.routed_experts is not None:
+            local.routed_experts = self.shard(seq.routed_experts)
+        local.full_cu_seqlens = seq.cu_seqlens
+        local.full_len = T
+        return self.shard(ids), self.shard(labels), self.shard(inv_temp), local
+
+    def gather_outputs(self, logprobs, entropy):
+        lp = _AllGatherSeq.apply(logprobs, self.group, False)
+        with torch.no_grad():
+            ent = _AllGatherSeq.apply(entropy, self.group, False)
+        return lp, ent
+
+    # ------------------------------------------------------------------ attention
+    def _doc_ids(self, cu, T, device):
+        pos = torch.arange(T, device=device)
+        return torch.searchsorted(cu[1:].to(torch.long).contiguous(), pos, right=True)
+
+    def attention(self, q, k, v, seq: SeqInfo, *, window=None, sinks=None, backend="auto"):
+        if self.style == "ulysses":
+            return self._ulysses(q, k, v, seq, window, sinks, backend)
+        return self._gather_kv(q, k, v, seq, window, sinks, backend)
+
+    def _gather_kv(self, q, k, v, seq, window, sinks, backend):
+        Tl, T = q.shape[0], seq.full_len
+        kg = _AllGatherSeq.apply(k, self.group, True)
+        vg = _AllGatherSeq.apply(v.contiguous(), self.group, True)
+        lo, hi = self.rank * Tl, (self.rank + 1) * Tl
+        cu = seq.full_cu_seqlens
+        if q.is_cuda and sinks is None and q.dtype == torch.bfloat16:
+            # per document that intersects the local chunk: queries = doc ∩ chunk, keys = doc start
+            # .. chunk end; flash-attn aligns the causal mask bottom-right, which is exactly this
+            cul = cu.tolist()
+            cq, ck, k0 = [0], [0], None
+            for a, b in zip(cul[:-1], cul[1:]):
+                if b <= lo or a >= hi:
+                    continue
+                if k0 is None:
+                    k0 = a
+                cq.append(cq[-1] + min(b, hi) - max(a, lo))
+                ck.append(ck[-1] + min(b, hi) - a)
+            from flash_attn import flash_attn_varlen_func
+
+            cq_t = torch.tensor(cq, dtype=torch.int32, device=q.device)
+            ck_t = torch.tensor(ck, dtype=torch.int32, device=q.device)
+            ws = (-1, -1) if window is None else (window - 1, 0)
+            return flash_attn_varlen_func(q, kg[k0:k0 + ck[-1]], vg[k0:k0 + ck[-1]], cq_t, ck_t,
+                                          max(b - a for a, b in zip(cq[:-1], cq[1:])),
+                                          max(b - a for a, b in zip(ck[:-1], ck[1:])), causal=True, window_size=ws)
+        doc = self._doc_ids(cu, T, q.device)
+        pos = torch.arange(T, device=q.device)
+        return attention_offset_ref(q, kg[:hi], vg[:hi], pos[lo:hi], pos[:hi], doc[lo:hi], doc[:hi], window=window,
+                                    sinks=sinks)
+
+    def _ulysses(self, q, k, v, seq, window, sinks, backend):
+        cp, Tl = self.cp, q.shape[0]
+        Hq, Hkv, D = q.shape[1], k.shape[1], q.shape[2]
+        if Hq % cp:
+            raise ValueError(f"ulysses needs num_attention_heads ({Hq}) divisible by cp ({cp})")
+        if Hkv < cp:
+            if cp % Hkv:
+                raise ValueError("ulysses needs cp | heads_kv or heads_kv | cp")
+            k = k.repeat_interleave(cp // Hkv, dim=1)
+            v = v.repeat_interleave(cp // Hkv, dim=1)
+            Hkv = cp
+        elif Hkv % cp:
+            raise ValueError("ulysses needs cp | heads_kv or heads_kv | cp")
+
+        def seq_to_head(x, H):      # [Tl, H, D] -> [T, H/cp, D]
+            x = x.reshape(Tl, cp, H // cp, D).permute(1, 0, 2, 3).contiguous()      # [cp, Tl, H/cp, D]
+            return _AllToAll.apply(x, self.group).reshape(cp * Tl, H // cp, D)
+
+        def head_to_seq(x, H):      # [T, H/cp, D] -> [Tl, H, D]
+            x = _AllToAll.apply(x.reshape(cp, Tl, H // cp, D).contiguous(), self.group)   # [cp(head blk), Tl, H/cp, D]
+            return x.permute(1, 0, 2, 3).reshape(Tl, H, D)
+
+        qf, kf, vf = seq_to_head(q, Hq), seq_to_head(k, Hkv), seq_to_head(v.contiguous(), Hkv)
+        local_sinks = None
+        if sinks is not None:
+            h0 = self.rank * (Hq // cp)
+            local_sinks = sinks[h0:h0 + Hq // cp]
+        cu = seq.full_cu_seqlens
+        max_len = int((cu[1:] - cu[:-1]).max())
+        o = attn_ops.attention(qf, kf, vf, cu, max_len, causal=True, window=window, sinks=local_sinks, backend=backend)
+        return head_to_seq(o, Hq)

@@ -36,8 +36,9 @@ if dist.is_initialized():
 
 
 def _run(tmp_path, port, world, cfg):
-    script = tmp_path / f"worker_{world}_{cfg['model'].get('ep', 1)}.py"
-    out = tmp_path / f"out_{world}_{cfg['model'].get('ep', 1)}"
+    tag = f"{world}_{cfg['model'].get('ep', 1)}_{cfg['model'].get('cp', 1)}_{cfg['model'].get('cp_style', 'ring')}"
+    script = tmp_path / f"worker_{tag}.py"
+    out = tmp_path / f"out_{tag}"
     out.mkdir()
     cfg = dict(cfg, output_dir=str(out))
     script.write_text(WORKER.format(root=str(ROOT), cfg=json.dumps(cfg), out=str(out)))
@@ -77,3 +78,22 @@ def test_dp2_and_ep2_match_single_process(tmp_path, free_port):
         assert a[0] == pytest.approx(b[0], rel=1e-4, abs=1e-6)
         assert a[1] == pytest.approx(b[1], rel=1e-4)
     assert single["steps"][0][1] > 0
+
+
+@pytest.mark.slow
+@pytest.mark.parametrize("style", ["ring", "ulysses"])
+def test_cp2_matches_single_process(tmp_path, free_port, style):
+    """Context-parallel ranks of one replica see the same rows, so CP=2 must reproduce CP=1."""
+    base = json.loads(json.dumps(BASE))
+    base["model"]["name"] = "tiny-qwen3"
+    single = _run(tmp_path, free_port, 1, base)[0]
+    cfg = json.loads(json.dumps(base))
+    cfg["model"].update(cp=2, cp_style=style)
+    cp2 = _run(tmp_path, free_port + 1, 2, cfg)
+    assert cp2[0]["wsum"] == pytest.approx(cp2[1]["wsum"], rel=1e-9)
+    assert cp2[0]["wabs"] == pytest.approx(single["wabs"], rel=1e-5)
+    assert cp2[0]["wsum"] == pytest.approx(single["wsum"], abs=1e-4)
+    for a, b in zip(single["steps"], cp2[0]["steps"]):
+        assert a[0] == pytest.approx(b[0], rel=1e-3, abs=1e-6)     # loss
+        assert a[1] == pytest.approx(b[1], rel=1e-3)               # grad norm
+        assert a[2] == pytest.approx(b[2], rel=1e-4)               # entropy

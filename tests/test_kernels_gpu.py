@@ -431,3 +431,23 @@ def test_flash_bwd_matches_reference(lens, window):
         rel = (got.float() - want).norm() / want.norm()
         assert rel < 2e-2, f"{name}: relative error {rel:.4f}"
         _close(got, want, atol=0.1, rtol=5e-2)
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(32, 4), (8, 8), (16, 4)])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_paged_decode(Hq, Hkv, splits):
+    from prime_rl_b200.ops import paged
+    B, D, ps, pages = 5, 128, 16, 64
+    kpool, vpool = _rand(pages, ps, Hkv, D), _rand(pages, ps, Hkv, D)
+    ctx = torch.tensor([1, 17, 250, 64, 300], dtype=torch.int32)
+    perm = torch.randperm(pages)
+    bt = torch.zeros(B, 20, dtype=torch.int32)
+    used = 0
+    for b in range(B):
+        n = (int(ctx[b]) + ps - 1) // ps
+        bt[b, :n] = perm[used:used + n] if used + n <= pages else perm[:n]
+        used = (used + n) % (pages - 20)
+    q = _rand(B, Hq, D)
+    out = paged.paged_decode_raw(q, kpool, vpool, bt.to(DEV), ctx.to(DEV), splits=splits)
+    ref = paged.paged_decode_ref(q, kpool, vpool, bt.to(DEV), ctx)
+    _close(out, ref, atol=2e-2, rtol=2e-2)
