@@ -98,6 +98,42 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   return true;
 }
 
+// Non-blocking probe of an mbarrier phase.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Same contract as mbar_wait, but polls with test_wait instead of the potentially suspending
+// try_wait: for waits on the critical path of a short software pipeline, where the wake-up
+// latency of a suspended thread would be a large part of the stage time.
+__device__ __forceinline__ bool mbar_wait_poll(uint64_t* bar, uint32_t parity, int* status, int code) {
+  uint32_t spins = 0;
+  long long t0 = 0;
+  while (!mbar_test_wait(bar, parity)) {
+    if ((++spins & 0x3ff) == 0) {
+      if (*reinterpret_cast<volatile int*>(status) != 0) return false;
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitCycles) {
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
 // ---------------------------------------------------------------- proxies / fences
 __device__ __forceinline__ void fence_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

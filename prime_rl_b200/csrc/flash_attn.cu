@@ -2,17 +2,22 @@
 // window, GQA, head_dim 128, bf16 in / bf16 out + fp32 log-sum-exp.
 //
 // One CTA owns 256 query rows of one head inside one document, as two 128-row tiles that
-// ping-pong: while one tile's softmax warps work on S, the tensor core runs the other
-// tile's MMAs. Per 64-key block and tile:
-//     S = Q K^T           tcgen05.mma  M128 x N64 x K128  (Q, K from shared memory, S in TMEM)
-//     softmax             4 warps, one thread per row, S read with tcgen05.ld, running max / sum
-//                         in registers, P written as bf16 into a 128B-swizzled shared tile,
-//                         O (TMEM) rescaled in place when the running max moved
-//     O += P V            tcgen05.mma  M128 x N128 x K64   (P from shared memory, V MN-major)
-// K and V tiles arrive by TMA (no multicast) through separate 3-stage rings.
+// run independently and share the K / V stream and the tensor core. Per 128-key block and tile:
+//     S = Q K^T           tcgen05.mma  M128 x N128 x K128 (Q, K from shared memory, S in TMEM);
+//                         N = 128 because an N = 64 product runs at half the tensor rate
+//     softmax             4 warps, one thread per row, in two 64-key halves: S read with
+//                         tcgen05.ld, running max / sum in registers, P written as bf16 into a
+//                         128B-swizzled shared tile, O (TMEM) rescaled in place only when the
+//                         running max moved by more than 2^8. The S buffer is handed back to
+//                         the tensor core as soon as its second half is in registers, so the
+//                         next Q K^T overlaps the exponentials of this block.
+//     O += P V            tcgen05.mma  M128 x N128 x K64 per half (P from shared memory, V MN-major)
+// K (128-key stages) and V (64-key stages) arrive by TMA (no multicast) through separate rings.
+// TMEM per tile (256 columns): S (128) | O (128).
 //
-// Warp roles: 0 = TMA producer, 1 = MMA issuer + TMEM owner, 2..5 = softmax of tile 0,
-// 6..9 = softmax of tile 1. All waits are bounded and report through the status word.
+// Warp roles: 0 = TMA producer, 1 / 2 = MMA issuer of tile 0 / 1 (one thread each; a single
+// issuer would serialise the two tiles' barrier round trips), 3..6 = softmax of tile 0,
+// 7..10 = softmax of tile 1. All waits are bounded and report through the status word.
 //
 // Replaces flash_attn_varlen_func in the reference (src/prime_rl/trainer/models/layers/attn.py:101-115).
 #include "common.cuh"
@@ -22,14 +27,17 @@ namespace prb {
 
 constexpr int kFaD = 128;        // head dim
 constexpr int kFaBM = 128;       // rows per tile
-constexpr int kFaBN = 64;        // keys per block
-constexpr int kFaStages = 3;
-constexpr int kFaThreads = 320;
+constexpr int kFaBN = 128;       // keys per Q K^T block
+constexpr int kFaHN = 64;        // keys per softmax / P V half
+constexpr int kFaKStages = 2;
+constexpr int kFaVStages = 3;
+constexpr int kFaThreads = 352;
 
 constexpr int kQBytes = kFaBM * kFaD * 2;          // 32 KB per tile (two 16 KB slabs of 64 columns)
-constexpr int kKVBytes = kFaBN * kFaD * 2;         // 16 KB per stage (two 8 KB halves)
-constexpr int kPBytes = kFaBM * kFaBN * 2;         // 16 KB per tile
-constexpr int kFaSmem = 2 * kQBytes + 2 * kFaStages * kKVBytes + 2 * kPBytes + 1024 + 512;
+constexpr int kKBytes = kFaBN * kFaD * 2;          // 32 KB per stage (two 16 KB slabs of 64 columns)
+constexpr int kVBytes = kFaHN * kFaD * 2;          // 16 KB per stage (two 8 KB slabs)
+constexpr int kPBytes = kFaBM * kFaHN * 2;         // 16 KB per tile
+constexpr int kFaSmem = 2 * kQBytes + kFaKStages * kKBytes + kFaVStages * kVBytes + 2 * kPBytes + 1024 + 512;
 
 struct FaParams {
   const int* cu_seqlens;  // [num_docs + 1]
@@ -46,7 +54,8 @@ struct FaParams {
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
-  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  // not volatile: a pure function, so the compiler may batch the MUFU ops of a row
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 
@@ -57,19 +66,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_s = smem;
   uint8_t* k_s = q_s + 2 * kQBytes;
-  uint8_t* v_s = k_s + kFaStages * kKVBytes;
-  uint8_t* p_s = v_s + kFaStages * kKVBytes;
+  uint8_t* v_s = k_s + kFaKStages * kKBytes;
+  uint8_t* p_s = v_s + kFaVStages * kVBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 2 * kPBytes);
   uint64_t* q_full = bars;                      // 1
-  uint64_t* k_full = q_full + 1;                // stages
-  uint64_t* k_empty = k_full + kFaStages;
-  uint64_t* v_full = k_empty + kFaStages;
-  uint64_t* v_empty = v_full + kFaStages;
-  uint64_t* s_full = v_empty + kFaStages;       // 2
-  uint64_t* p_ready = s_full + 2;               // 2
+  uint64_t* k_full = q_full + 1;                // K stages
+  uint64_t* k_empty = k_full + kFaKStages;      // count 2: both MMA threads release a stage
+  uint64_t* v_full = k_empty + kFaKStages;      // V stages
+  uint64_t* v_empty = v_full + kFaVStages;      // count 2
+  uint64_t* s_full = v_empty + kFaVStages;      // 2 (per tile)
+  uint64_t* s_free = s_full + 2;                // 2, count 4 (softmax warps)
+  uint64_t* p_ready = s_free + 2;               // 2, count 4
   uint64_t* o_ready = p_ready + 2;              // 2
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + 2);
-  int* s_work = reinterpret_cast<int*>(tmem_slot + 1);  // doc_start, doc_len, row0 (in doc)
+  int* s_work = reinterpret_cast<int*>(tmem_slot + 1);  // doc_start, doc_len, row0 (in doc), found
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -78,14 +88,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   // ------------------------------------------------------------ locate this CTA's work
   if (threadIdx.x == 0) {
-    int pair = gridDim.x - 1 - blockIdx.x;  // heavy (late) tiles first
-    int found = 0;
-    // pairs are numbered document by document; walk documents from the last one so that
-    // the numbering matches the reversed launch order
-    int acc = 0;
+    const int pair = gridDim.x - 1 - blockIdx.x;  // heavy (late) tiles first
+    int found = 0, acc = 0;
     for (int d = 0; d < p.num_docs; ++d) {
-      const int s0 = p.cu_seqlens[d], s1 = p.cu_seqlens[d + 1];
-      const int len = s1 - s0;
+      const int s0 = p.cu_seqlens[d], len = p.cu_seqlens[d + 1] - s0;
       const int np = (len + 2 * kFaBM - 1) / (2 * kFaBM);
       if (pair < acc + np) {
         s_work[0] = s0;
@@ -104,29 +110,24 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int doc_len = s_work[1];
   const int row0 = s_work[2];
 
-  // rows [q0_t, q1_t) of the document for each tile and the key blocks they need
-  int q0[2], q1[2], nblk[2], blk0[2];
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    q0[t] = row0 + t * kFaBM;
-    q1[t] = min(q0[t] + kFaBM, doc_len);
-    nblk[t] = (q1[t] > q0[t]) ? (q1[t] + kFaBN - 1) / kFaBN : 0;
-    blk0[t] = 0;
-    if (p.window > 0 && nblk[t] > 0) blk0[t] = max(0, q0[t] - p.window + 1) / kFaBN;
-  }
-  const int j_begin = min(blk0[0], nblk[1] > 0 ? blk0[1] : blk0[0]);
-  const int j_end = max(nblk[0], nblk[1]);
+  // rows [q0, q1) of the document for each tile and the 128-key blocks [blk0, nblk) they need
+  const int q0_0 = row0, q0_1 = row0 + kFaBM;
+  const int q1_0 = min(q0_0 + kFaBM, doc_len), q1_1 = min(q0_1 + kFaBM, doc_len);
+  const int nblk_0 = (q1_0 > q0_0) ? (q1_0 + kFaBN - 1) / kFaBN : 0;
+  const int nblk_1 = (q1_1 > q0_1) ? (q1_1 + kFaBN - 1) / kFaBN : 0;
+  const int blk0_0 = (p.window > 0 && nblk_0 > 0) ? max(0, q0_0 - p.window + 1) / kFaBN : 0;
+  const int blk0_1 = (p.window > 0 && nblk_1 > 0) ? max(0, q0_1 - p.window + 1) / kFaBN : 0;
+  // union of the two ranges: the K / V stream of this CTA (tile 0 always has rows)
+  const int j_begin = (nblk_1 > 0) ? min(blk0_0, blk0_1) : blk0_0;
+  const int j_end = max(nblk_0, nblk_1);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < kFaStages; ++i) {
-      mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], 1);
-      mbar_init(&v_full[i], 1);
-      mbar_init(&v_empty[i], 1);
-    }
+    for (int i = 0; i < kFaKStages; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 2); }
+    for (int i = 0; i < kFaVStages; ++i) { mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 2); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
+      mbar_init(&s_free[i], 4);
       mbar_init(&p_ready[i], 4);
       mbar_init(&o_ready[i], 1);
     }
@@ -153,192 +154,206 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int s = 0; s < 2; ++s)
           tma_load_2d(q_s + t * kQBytes + s * (kQBytes / 2), &tmQ, q_full, head * kFaD + s * 64,
-                      doc_start + q0[t]);
+                      doc_start + row0 + t * kFaBM);
       int ks = 0, vs = 0;
       uint32_t kph = 0, vph = 0;
       bool ok = true;
       for (int j = j_begin; j < j_end && ok; ++j) {
         const int krow = doc_start + j * kFaBN;
         if (!mbar_wait(&k_empty[ks], kph ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
-        mbar_expect_tx(&k_full[ks], kKVBytes);
-        tma_load_2d(k_s + ks * kKVBytes, &tmK, &k_full[ks], kv_head * kFaD, krow);
-        tma_load_2d(k_s + ks * kKVBytes + kKVBytes / 2, &tmK, &k_full[ks], kv_head * kFaD + 64, krow);
-        if (++ks == kFaStages) { ks = 0; kph ^= 1; }
-        if (!mbar_wait(&v_empty[vs], vph ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
-        mbar_expect_tx(&v_full[vs], kKVBytes);
-        tma_load_2d(v_s + vs * kKVBytes, &tmV, &v_full[vs], kv_head * kFaD, krow);
-        tma_load_2d(v_s + vs * kKVBytes + kKVBytes / 2, &tmV, &v_full[vs], kv_head * kFaD + 64, krow);
-        if (++vs == kFaStages) { vs = 0; vph ^= 1; }
+        mbar_expect_tx(&k_full[ks], kKBytes);
+        tma_load_2d(k_s + ks * kKBytes, &tmK, &k_full[ks], kv_head * kFaD, krow);
+        tma_load_2d(k_s + ks * kKBytes + kKBytes / 2, &tmK, &k_full[ks], kv_head * kFaD + 64, krow);
+        if (++ks == kFaKStages) { ks = 0; kph ^= 1; }
+        for (int h = 0; h < 2; ++h) {
+          if (!mbar_wait(&v_empty[vs], vph ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
+          mbar_expect_tx(&v_full[vs], kVBytes);
+          tma_load_2d(v_s + vs * kVBytes, &tmV, &v_full[vs], kv_head * kFaD, krow + h * kFaHN);
+          tma_load_2d(v_s + vs * kVBytes + kVBytes / 2, &tmV, &v_full[vs], kv_head * kFaD + 64, krow + h * kFaHN);
+          if (++vs == kFaVStages) { vs = 0; vph ^= 1; }
+        }
       }
       if (!ok) __nanosleep(200000);
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
+  } else if (warp <= 2) {
+    // ------------------------------------------------------------ MMA issuer of tile (warp - 1)
     if (lane == 0) {
+      const int t = warp - 1;
+      const int my_blk0 = t ? blk0_1 : blk0_0, my_nblk = t ? nblk_1 : nblk_0;
       constexpr uint32_t idesc_qk = umma_idesc(1, kFaBM, kFaBN, false, false);
       constexpr uint32_t idesc_pv = umma_idesc(1, kFaBM, kFaD, false, true);
-      const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), v_addr = smem_u32(v_s), p_addr = smem_u32(p_s);
+      const uint32_t q_addr = smem_u32(q_s) + t * kQBytes, k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
+      const uint32_t p_addr = smem_u32(p_s) + t * kPBytes;
+      const uint32_t s_tm = tmem_base + t * 256, o_tm = s_tm + 128;
       bool ok = mbar_wait(q_full, 0, p.status, kTimeoutFullBarrier);
       int ks = 0, vs = 0;
       uint32_t kph = 0, vph = 0;
-      uint32_t cnt[2] = {0, 0};  // blocks issued per tile (phase source)
+      uint32_t n_qk = 0, n_pv = 0;   // products issued so far (phase sources)
 
-      auto issue_qk = [&](int t, int stage) {
+      // K block j sits in stage ks: S = Q K^T if this tile needs the block, then release the stage.
+      // Every stage is released by both issuers, so a tile that skips a block still arrives
+      // (after the stage filled: an earlier arrival could land in the previous phase).
+      auto handle_k = [&](int j) {
+        if (!mbar_wait(&k_full[ks], kph, p.status, kTimeoutFullBarrier)) { ok = false; return; }
+        if (j >= my_blk0 && j < my_nblk) {
+          // the softmax warps hand S back once block n_qk - 1 is in their registers
+          if (n_qk > 0 && !mbar_wait(&s_free[t], (n_qk - 1) & 1, p.status, kTimeoutTmemEmpty)) { ok = false; return; }
+          tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint64_t a = umma_smem_desc(q_addr + t * kQBytes + (kk >> 2) * (kQBytes / 2) + (kk & 3) * 32, 0, 1024);
-          const uint64_t b = umma_smem_desc(k_addr + stage * kKVBytes + (kk >> 2) * (kKVBytes / 2) + (kk & 3) * 32, 0, 1024);
-          umma_f16(tmem_base + t * 256, a, b, idesc_qk, kk != 0);
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint64_t a = umma_smem_desc(q_addr + (kk >> 2) * (kQBytes / 2) + (kk & 3) * 32, 0, 1024);
+            const uint64_t b = umma_smem_desc(k_addr + ks * kKBytes + (kk >> 2) * (kKBytes / 2) + (kk & 3) * 32, 0, 1024);
+            umma_f16(s_tm, a, b, idesc_qk, kk != 0);
+          }
+          umma_commit(&s_full[t]);
+          umma_commit(&k_empty[ks]);
+          ++n_qk;
+        } else {
+          mbar_arrive(&k_empty[ks]);
         }
-        umma_commit(&s_full[t]);
+        if (++ks == kFaKStages) { ks = 0; kph ^= 1; }
+      };
+      // one 64-key half of V sits in stage vs: O += P V once the softmax warps published P
+      auto handle_v = [&](int j) {
+        if (!mbar_wait(&v_full[vs], vph, p.status, kTimeoutFullBarrier)) { ok = false; return; }
+        if (j >= my_blk0 && j < my_nblk) {
+          if (!mbar_wait(&p_ready[t], n_pv & 1, p.status, kTimeoutPeerFlag)) { ok = false; return; }
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t a = umma_smem_desc(p_addr + kk * 32, 0, 1024);
+            const uint64_t b = umma_smem_desc(v_addr + vs * kVBytes + kk * 2048, kVBytes / 2, 1024);
+            umma_f16(o_tm, a, b, idesc_pv, (n_pv | kk) != 0);
+          }
+          umma_commit(&o_ready[t]);
+          umma_commit(&v_empty[vs]);
+          ++n_pv;
+        } else {
+          mbar_arrive(&v_empty[vs]);
+        }
+        if (++vs == kFaVStages) { vs = 0; vph ^= 1; }
       };
 
-      // prologue: S for the first block of both tiles
-      if (ok && j_begin < j_end) {
-        ok = mbar_wait(&k_full[ks], kph, p.status, kTimeoutFullBarrier);
-        if (ok) {
-          tc_fence_after();
-          for (int t = 0; t < 2; ++t)
-            if (j_begin >= blk0[t] && j_begin < nblk[t]) issue_qk(t, ks);
-          umma_commit(&k_empty[ks]);
-          if (++ks == kFaStages) { ks = 0; kph ^= 1; }
-        }
-      }
+      if (ok && j_begin < j_end) handle_k(j_begin);
       for (int j = j_begin; j < j_end && ok; ++j) {
-        const bool has_next = (j + 1 < j_end);
-        bool k_next_ready = false;
-        if (!mbar_wait(&v_full[vs], vph, p.status, kTimeoutFullBarrier)) { ok = false; break; }
-        for (int t = 0; t < 2 && ok; ++t) {
-          const bool active = (j >= blk0[t] && j < nblk[t]);
-          if (active) {
-            // P_j of this tile is in shared memory and its O has been rescaled
-            if (!mbar_wait(&p_ready[t], cnt[t] & 1, p.status, kTimeoutPeerFlag)) { ok = false; break; }
-            tc_fence_after();
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-              const uint64_t a = umma_smem_desc(p_addr + t * kPBytes + kk * 32, 0, 1024);
-              const uint64_t b = umma_smem_desc(v_addr + vs * kKVBytes + kk * 2048, 8192, 1024);
-              umma_f16(tmem_base + t * 256 + 128, a, b, idesc_pv, (cnt[t] | kk) != 0);
-            }
-            umma_commit(&o_ready[t]);
-            ++cnt[t];
-          }
-          // S of this tile is free again (its softmax finished block j before arriving on
-          // p_ready, or the tile has not started yet): issue the next Q K^T right away
-          const bool next_active = has_next && (j + 1 >= blk0[t] && j + 1 < nblk[t]);
-          if (next_active) {
-            if (!k_next_ready) {
-              if (!mbar_wait(&k_full[ks], kph, p.status, kTimeoutFullBarrier)) { ok = false; break; }
-              tc_fence_after();
-              k_next_ready = true;
-            }
-            issue_qk(t, ks);
-          }
-        }
-        if (!ok) break;
-        umma_commit(&v_empty[vs]);
-        if (++vs == kFaStages) { vs = 0; vph ^= 1; }
-        if (has_next) {
-          if (!k_next_ready) {
-            // no tile needs block j+1 (cannot happen for j+1 < j_end, kept for symmetry)
-            if (!mbar_wait(&k_full[ks], kph, p.status, kTimeoutFullBarrier)) break;
-          }
-          umma_commit(&k_empty[ks]);
-          if (++ks == kFaStages) { ks = 0; kph ^= 1; }
-        }
+        handle_v(j);
+        // the next Q K^T goes in between the two halves: S is free again as soon as the softmax
+        // warps have loaded the second half, long before they publish its P
+        if (ok && j + 1 < j_end) handle_k(j + 1);
+        if (ok) handle_v(j);
       }
     }
   } else {
     // ------------------------------------------------------------ softmax warps
-    const int t = (warp - 2) >> 2;          // tile
-    const int qtr = warp & 3;               // TMEM lane quarter
+    const int t = (warp - 3) >> 2;          // tile
+    const int qtr = warp & 3;               // TMEM lane quarter this warp may access
     const int r = qtr * 32 + lane;          // row in tile
-    const int row = q0[t] + r;              // row in document
-    const bool row_ok = row < q1[t];
+    // scalars, not arrays indexed by t: a runtime index would put them in local memory
+    const int my_q0 = t ? q0_1 : q0_0, my_q1 = t ? q1_1 : q1_0;
+    const int my_blk0 = t ? blk0_1 : blk0_0, my_nblk = t ? nblk_1 : nblk_0;
+    const int row = my_q0 + r;              // row in document
+    const bool row_ok = row < my_q1;
     const uint32_t lane_off = static_cast<uint32_t>(qtr * 32) << 16;
     const uint32_t s_tm = tmem_base + t * 256 + lane_off;
     const uint32_t o_tm = s_tm + 128;
     uint8_t* p_row = p_s + t * kPBytes + r * 128;
     float m = -INFINITY, l = 0.f;
-    uint32_t it = 0;
+    uint32_t n = 0, it = 0;                 // blocks / halves done
     bool ok = true;
-    for (int j = blk0[t]; j < nblk[t]; ++j, ++it) {
-      ok = mbar_wait(&s_full[t], it & 1, p.status, kTimeoutTmemFull);
+    for (int j = my_blk0; j < my_nblk && ok; ++j, ++n) {
+      ok = mbar_wait(&s_full[t], n & 1, p.status, kTimeoutTmemFull);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      uint32_t sv[2][32];
-      tmem_ld_32x32(s_tm, sv[0]);
-      tmem_ld_32x32(s_tm + 32, sv[1]);
-      tmem_ld_wait();
-      const int col0 = j * kFaBN;
-      const bool need_mask = (col0 + kFaBN - 1 > q0[t]) || (p.window > 0 && q1[t] - 1 - col0 >= p.window);
-      // raw scores; masked entries become -inf. The running reference `m` (log2 domain) only
-      // moves when the block maximum exceeds it by more than 8: P then stays below 2^8, and
-      // most blocks need no rescale of O at all.
-      float s[64];
-      float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        float x = __uint_as_float(sv[c >> 5][c & 31]);
-        if (need_mask) {
-          const int col = col0 + c;
-          const bool keep = (col <= row) && (p.window <= 0 || row - col < p.window);
-          x = keep ? x : -INFINITY;
-        }
-        s[c] = x;
-        mx = fmaxf(mx, x);
-      }
-      const float m_blk = mx * p.scale_log2;          // scale > 0, so max commutes with it
-      float alpha = 1.f;
-      if (m_blk > m + 8.f) {                          // also true on the first unmasked block (m = -inf)
-        alpha = ex2(m - m_blk);                       // m = -inf -> 0
-        m = m_blk;
-      }
-      // rows without any valid key so far keep m = -inf: use 0 so that no NaN appears
-      const float neg_m = (m == -INFINITY) ? 0.f : -m;
-      float sum = 0.f;
-      uint32_t pk[32];
-#pragma unroll
-      for (int c = 0; c < 64; c += 2) {
-        const float p0 = ex2(fmaf(s[c], p.scale_log2, neg_m)), p1 = ex2(fmaf(s[c + 1], p.scale_log2, neg_m));
-        sum += p0 + p1;
-        pk[c >> 1] = pack_bf16(p0, p1);
-      }
-      l = l * alpha + sum;
-      if (it > 0) {
-        // O holds blocks < j: wait for the last PV, then rescale in place
-        ok = mbar_wait(&o_ready[t], (it - 1) & 1, p.status, kTimeoutTmemFull);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
-        const bool skip = __all_sync(0xffffffffu, alpha == 1.f);
-        if (!skip) {
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t ov[32];
-            tmem_ld_32x32(o_tm + c * 32, ov);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-            tmem_st_32x32(o_tm + c * 32, ov);
-          }
-          tmem_st_wait();
+      for (int h = 0; h < 2; ++h, ++it) {
+        uint32_t sv[2][32];
+        tmem_ld_32x32(s_tm + h * kFaHN, sv[0]);
+        tmem_ld_32x32(s_tm + h * kFaHN + 32, sv[1]);
+        tmem_ld_wait();
+        if (h == 1) {
+          // all of S is in registers: the tensor core may overwrite it with the next block
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s_free[t]);
         }
-      }
-      // P row: 8 chunks of 16 bytes, 128B swizzle (chunk ^ (row & 7))
+        const int col0 = j * kFaBN + h * kFaHN;
+        const bool need_mask = (col0 + kFaHN - 1 > my_q0) || (p.window > 0 && my_q1 - 1 - col0 >= p.window);
+        // raw scores; masked entries become -inf. The running reference `m` (log2 domain) only
+        // moves when the block maximum exceeds it by more than 8: P then stays below 2^8, and
+        // most blocks need no rescale of O at all.
+        float s[64];
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one
+        // two straight-line variants: a per-element `if (need_mask)` is compiled to 64 branches
+        if (need_mask) {
+          const int lim_hi = row - col0;                                   // keep c <= lim_hi
+          const int lim_lo = (p.window > 0) ? lim_hi - p.window : -1;      // keep c >  lim_lo
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const uint4 val = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-        *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = val;
+          for (int c = 0; c < 64; ++c) {
+            const float x = __uint_as_float(sv[c >> 5][c & 31]);
+            s[c] = ((c <= lim_hi) & (c > lim_lo)) ? x : -INFINITY;
+            mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 64; ++c) {
+            s[c] = __uint_as_float(sv[c >> 5][c & 31]);
+            mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+          }
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        const float m_blk = mx * p.scale_log2;          // scale > 0, so max commutes with it
+        float alpha = 1.f;
+        if (m_blk > m + 8.f) {                          // also true on the first unmasked block (m = -inf)
+          alpha = ex2(m - m_blk);                       // m = -inf -> 0
+          m = m_blk;
+        }
+        // rows without any valid key so far keep m = -inf: use 0 so that no NaN appears
+        const float neg_m = (m == -INFINITY) ? 0.f : -m;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t pk[32];
+#pragma unroll
+        for (int c = 0; c < 64; c += 2) {
+          const float p0 = ex2(fmaf(s[c], p.scale_log2, neg_m)), p1 = ex2(fmaf(s[c + 1], p.scale_log2, neg_m));
+          sum4[(c >> 1) & 3] += p0 + p1;
+          pk[c >> 1] = pack_bf16(p0, p1);
+        }
+        l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+        if (it > 0) {
+          // O holds the halves before this one and P is still being read by the last P V:
+          // wait for it, then rescale O in place if some row of this warp moved its reference
+          ok = mbar_wait(&o_ready[t], (it - 1) & 1, p.status, kTimeoutTmemFull);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          const bool skip = __all_sync(0xffffffffu, alpha == 1.f);
+          if (!skip) {
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              uint32_t ov[32];
+              tmem_ld_32x32(o_tm + c * 32, ov);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+              tmem_st_32x32(o_tm + c * 32, ov);
+            }
+            tmem_st_wait();
+          }
+        }
+        // P row: 8 chunks of 16 bytes, 128B swizzle (chunk ^ (row & 7))
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 val = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+          *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) = val;
+        }
+        fence_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_ready[t]);
       }
-      fence_async_smem();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&p_ready[t]);
     }
     // ---------------------------------------------------------- epilogue: O / l, LSE
-    if (ok && nblk[t] > blk0[t]) {
+    if (ok && it > 0) {
       ok = mbar_wait(&o_ready[t], (it - 1) & 1, p.status, kTimeoutTmemFull);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
@@ -372,6 +387,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   tc_fence_before();
   __syncthreads();
+  tc_fence_after();
   if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
@@ -398,7 +414,7 @@ PRB_API int prb_flash_fwd(const void* q, const void* k, const void* v, void* out
                     (uint64_t)ld_k, kFaBN, 64, true);
   if (rc) return rc;
   rc = make_tmap_2d(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_q, (uint64_t)heads_kv * kFaD,
-                    (uint64_t)ld_v, kFaBN, 64, true);
+                    (uint64_t)ld_v, kFaHN, 64, true);
   if (rc) return rc;
   FaParams p;
   p.cu_seqlens = cu_seqlens; p.num_docs = num_docs; p.total_q = total_q;

@@ -51,7 +51,7 @@ struct FaBwdParams {
 
 __device__ __forceinline__ float bw_ex2(float x) {
   float y;
-  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));  // pure: let the compiler batch them
   return y;
 }
 
@@ -279,15 +279,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (lane == 0) mbar_arrive(sdp_free);
         const int col0 = kv0 + h * 64 + 32 * w;           // key index in document
         uint32_t pp[16], dd[16];
+        // keep column c of this slab iff lim_lo < c <= lim_hi; branch-free so that the 32
+        // exponentials of a row are issued back to back
+        const int lim_hi = row_ok ? row - col0 : -1;
+        const int lim_lo = (p.window > 0) ? lim_hi - p.window : -1;
+        const float neg_lse2 = -lse2;
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
           float pv[2], dv[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int col = col0 + c + e;
-            const bool keep = row_ok && (col <= row) && (p.window <= 0 || row - col < p.window);
-            const float s = __uint_as_float(sv[c + e]);
-            const float pr = keep ? bw_ex2(fmaf(s, p.scale_log2, -lse2)) : 0.f;
+            const float ex = bw_ex2(fmaf(__uint_as_float(sv[c + e]), p.scale_log2, neg_lse2));
+            const float pr = ((c + e <= lim_hi) & (c + e > lim_lo)) ? ex : 0.f;
             pv[e] = pr;
             dv[e] = pr * (__uint_as_float(dpv[c + e]) - delta) * p.scale;
           }
