@@ -60,13 +60,12 @@ def flash_bwd(dout, q, k, v, out, lse, cu_seqlens, *, scale: float | None = None
     dk = dk_out if dk_out is not None else torch.empty(T, Hkv, D, dtype=q.dtype, device=dev)
     dv = dv_out if dv_out is not None else torch.empty(T, Hkv, D, dtype=q.dtype, device=dev)
     delta = torch.empty(Hq, T, dtype=torch.float32, device=dev)
-    dq_acc = torch.empty(T, Hq, D, dtype=torch.float32, device=dev)
     num_docs = cu_seqlens.numel() - 1
     max_blocks = (T + 127) // 128 + num_docs
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     status = rt.status_tensor(dev)
     rc = rt.lib().prb_flash_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(),
-                                lse.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+                                lse.data_ptr(), delta.data_ptr(), None, dq.data_ptr(), dk.data_ptr(),
                                 dv.data_ptr(), cu_seqlens.data_ptr(), num_docs, T, Hq, Hkv, D, q.stride(0),
                                 k.stride(0), v.stride(0), out.stride(0), dout.stride(0), dk.stride(0), dv.stride(0),
                                 float(scale), int(window or 0), max_blocks, status.data_ptr(), rt.stream_ptr(dev))
