@@ -261,7 +261,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     uint32_t n = 0, it = 0;                 // blocks / halves done
     bool ok = true;
     for (int j = my_blk0; j < my_nblk && ok; ++j, ++n) {
-      ok = mbar_wait(&s_full[t], n & 1, p.status, kTimeoutTmemFull);
+      ok = mbar_wait_poll(&s_full[t], n & 1, p.status, kTimeoutTmemFull);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -322,7 +322,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (it > 0) {
           // O holds the halves before this one and P is still being read by the last P V:
           // wait for it, then rescale O in place if some row of this warp moved its reference
-          ok = mbar_wait(&o_ready[t], (it - 1) & 1, p.status, kTimeoutTmemFull);
+          ok = mbar_wait_poll(&o_ready[t], (it - 1) & 1, p.status, kTimeoutTmemFull);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();

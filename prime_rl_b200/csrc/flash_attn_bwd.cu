@@ -14,7 +14,7 @@
 // Recomputing S / dP in both kernels costs two extra products per block but removes the fp32
 // dQ reductions through L2, which were the bottleneck of a single-kernel version.
 // TMEM: dkdv  S 0 | dP 128 | dV 256 | dK 384;   dq  S0 0 | S1 128 | dP 256 | dQ 384.
-// Shared memory (7 tiles of 32 KB): dkdv  K V Q0 Q1 dO P dS;   dq  Q dO K0 K1 V0 V1 dS.
+// Shared memory (7 tiles of 32 KB): dkdv  K V Q0 Q1 dO P dS;   dq  Q dO K0 K1 K2 V dS.
 //
 // Warps: 0 = TMA producer, 1 = front MMA issuer + TMEM owner, 2 = back MMA issuer,
 // 3..10 = softmax (two warps per TMEM lane quarter; the pair splits the 128 columns).
@@ -58,27 +58,34 @@ __device__ __forceinline__ float bw_ex2(float x) {
 // 128-byte swizzle, so the thread's 64 bf16 are exactly one swizzled row of slab w.
 
 // P = exp2(S c - lse2) for the thread's 64 columns; column c is kept iff lim_lo < c <= lim_hi.
+// Most blocks lie below the diagonal and inside the window: the warp then skips the compares.
 __device__ __forceinline__ void bw_load_p(uint32_t s_taddr, float (&pf)[64], int lim_hi, int lim_lo, float scale_log2,
                                           float neg_lse2) {
   uint32_t sv[2][32];
   tmem_ld_32x32(s_taddr, sv[0]);
   tmem_ld_32x32(s_taddr + 32, sv[1]);
+  const bool need_mask = __any_sync(0xffffffffu, (lim_hi < 63) | (lim_lo >= 0));
   tmem_ld_wait();
+  if (need_mask) {
 #pragma unroll
-  for (int c = 0; c < 64; ++c) {
-    const float ex = bw_ex2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), scale_log2, neg_lse2));
-    pf[c] = ((c <= lim_hi) & (c > lim_lo)) ? ex : 0.f;
+    for (int c = 0; c < 64; ++c) {
+      const float ex = bw_ex2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), scale_log2, neg_lse2));
+      pf[c] = ((c <= lim_hi) & (c > lim_lo)) ? ex : 0.f;
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < 64; ++c) pf[c] = bw_ex2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), scale_log2, neg_lse2));
   }
 }
 
-// dS = P (dP - delta) scale, in place.
-__device__ __forceinline__ void bw_load_ds(uint32_t dp_taddr, float (&pf)[64], float delta, float scale) {
+// dS = P (dP - delta), in place. The softmax scale is applied once, when dK / dQ leave TMEM.
+__device__ __forceinline__ void bw_load_ds(uint32_t dp_taddr, float (&pf)[64], float neg_delta) {
   uint32_t dv[2][32];
   tmem_ld_32x32(dp_taddr, dv[0]);
   tmem_ld_32x32(dp_taddr + 32, dv[1]);
   tmem_ld_wait();
 #pragma unroll
-  for (int c = 0; c < 64; ++c) pf[c] = pf[c] * (__uint_as_float(dv[c >> 5][c & 31]) - delta) * scale;
+  for (int c = 0; c < 64; ++c) pf[c] *= __uint_as_float(dv[c >> 5][c & 31]) + neg_delta;
 }
 
 __device__ __forceinline__ void bw_store_row(uint8_t* row_ptr, int r, const float (&pf)[64]) {
@@ -282,11 +289,11 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       const bool row_ok = row < doc_len;
       const long long stat_idx = static_cast<long long>(head) * p.total_q + doc_start + row;
       const float neg_lse2 = row_ok ? -p.lse[stat_idx] * 1.4426950408889634f : 0.f;
-      const float delta = row_ok ? p.delta[stat_idx] : 0.f;
+      const float neg_delta = row_ok ? -p.delta[stat_idx] : 0.f;
       const int lim_hi = row_ok ? row - col0 : -1;
       const int lim_lo = (p.window > 0) ? lim_hi - p.window : -1;
 
-      ok = mbar_wait(s_full, n & 1, p.status, kTimeoutTmemFull);
+      ok = mbar_wait_poll(s_full, n & 1, p.status, kTimeoutTmemFull);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -296,7 +303,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive(s_free);
       if (n > 0) {                                        // dV of block n - 1 still reads P
-        ok = mbar_wait(p_free, (n - 1) & 1, p.status, kTimeoutTmemFull);
+        ok = mbar_wait_poll(p_free, (n - 1) & 1, p.status, kTimeoutTmemFull);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
       }
@@ -305,16 +312,16 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready);
 
-      ok = mbar_wait(dp_full, n & 1, p.status, kTimeoutTmemFull);
+      ok = mbar_wait_poll(dp_full, n & 1, p.status, kTimeoutTmemFull);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      bw_load_ds(tmem_base + lane_off + kTmDP + 64 * w, pf, delta, p.scale);
+      bw_load_ds(tmem_base + lane_off + kTmDP + 64 * w, pf, neg_delta);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(dp_free);
       if (n > 0) {                                        // dK of block n - 1 still reads dS
-        ok = mbar_wait(ds_free, (n - 1) & 1, p.status, kTimeoutTmemFull);
+        ok = mbar_wait_poll(ds_free, (n - 1) & 1, p.status, kTimeoutTmemFull);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
       }
@@ -337,6 +344,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                              static_cast<long long>(doc_start + key) * (which ? p.ld_dk : p.ld_dv) +
                              static_cast<long long>(kv_head) * kBwD + 64 * w;
         const uint32_t tm = tmem_base + lane_off + (which ? kTmDK : kTmDV) + 64 * w;
+        const float mul = which ? p.scale : 1.f;
 #pragma unroll 1
         for (int c = 0; c < 2; ++c) {
           uint32_t gv[32];
@@ -346,10 +354,10 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               uint4 o;
-              o.x = pack_bf16(__uint_as_float(gv[8 * e + 0]), __uint_as_float(gv[8 * e + 1]));
-              o.y = pack_bf16(__uint_as_float(gv[8 * e + 2]), __uint_as_float(gv[8 * e + 3]));
-              o.z = pack_bf16(__uint_as_float(gv[8 * e + 4]), __uint_as_float(gv[8 * e + 5]));
-              o.w = pack_bf16(__uint_as_float(gv[8 * e + 6]), __uint_as_float(gv[8 * e + 7]));
+              o.x = pack_bf16(__uint_as_float(gv[8 * e + 0]) * mul, __uint_as_float(gv[8 * e + 1]) * mul);
+              o.y = pack_bf16(__uint_as_float(gv[8 * e + 2]) * mul, __uint_as_float(gv[8 * e + 3]) * mul);
+              o.z = pack_bf16(__uint_as_float(gv[8 * e + 4]) * mul, __uint_as_float(gv[8 * e + 5]) * mul);
+              o.w = pack_bf16(__uint_as_float(gv[8 * e + 6]) * mul, __uint_as_float(gv[8 * e + 7]) * mul);
               *reinterpret_cast<uint4*>(dst + 32 * c + 8 * e) = o;
             }
           }
@@ -373,16 +381,16 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_s = smem;
   uint8_t* do_s = q_s + kBwTile;
-  uint8_t* k_s = do_s + kBwTile;           // 2 stages
-  uint8_t* v_s = k_s + 2 * kBwTile;        // 2 stages
-  uint8_t* ds_s = v_s + 2 * kBwTile;
+  uint8_t* k_s = do_s + kBwTile;           // 3 stages: K of block n is held until dQ of block n is done
+  uint8_t* v_s = k_s + 3 * kBwTile;        // 1 stage: V is released right after dP
+  uint8_t* ds_s = v_s + kBwTile;
   uint64_t* bars = reinterpret_cast<uint64_t*>(ds_s + kBwTile);
   uint64_t* qdo_full = bars;
-  uint64_t* k_full = qdo_full + 1;         // [2]
-  uint64_t* k_empty = k_full + 2;          // [2], count 2: S (front) and dQ (back) both read K
-  uint64_t* v_full = k_empty + 2;          // [2]
-  uint64_t* v_empty = v_full + 2;          // [2]
-  uint64_t* s_full = v_empty + 2;          // [2]
+  uint64_t* k_full = qdo_full + 1;         // [3]
+  uint64_t* k_empty = k_full + 3;          // [3], count 2: S (front) and dQ (back) both read K
+  uint64_t* v_full = k_empty + 3;
+  uint64_t* v_empty = v_full + 1;
+  uint64_t* s_full = v_empty + 1;          // [2]
   uint64_t* s_free = s_full + 2;           // [2], count 8
   uint64_t* dp_full = s_free + 2;
   uint64_t* dp_free = dp_full + 1;         // count 8
@@ -419,11 +427,10 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 2);
-      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 8);
-    }
+    for (int i = 0; i < 3; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 2); }
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 8); }
     mbar_init(dp_full, 1);
     mbar_init(dp_free, 8);
     mbar_init(ds_ready, 8);
@@ -448,16 +455,17 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       bw_load_tile(q_s, &tmQ, qdo_full, head * kBwD, doc_start + q0);
       bw_load_tile(do_s, &tmDO, qdo_full, head * kBwD, doc_start + q0);
       bool ok = true;
+      int ks = 0;
+      uint32_t kph = 0;
       for (int n = 0; n < num_iters && ok; ++n) {
-        const int st = n & 1;
-        const uint32_t ph = ((n >> 1) & 1) ^ 1;
         const int krow = doc_start + (j_begin + n) * kBwB;
-        if (!mbar_wait(&k_empty[st], ph, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
-        mbar_expect_tx(&k_full[st], kBwTile);
-        bw_load_tile(k_s + st * kBwTile, &tmK, &k_full[st], kv_head * kBwD, krow);
-        if (!mbar_wait(&v_empty[st], ph, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
-        mbar_expect_tx(&v_full[st], kBwTile);
-        bw_load_tile(v_s + st * kBwTile, &tmV, &v_full[st], kv_head * kBwD, krow);
+        if (!mbar_wait(&k_empty[ks], kph ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
+        mbar_expect_tx(&k_full[ks], kBwTile);
+        bw_load_tile(k_s + ks * kBwTile, &tmK, &k_full[ks], kv_head * kBwD, krow);
+        if (++ks == 3) { ks = 0; kph ^= 1; }
+        if (!mbar_wait(v_empty, (n & 1) ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
+        mbar_expect_tx(v_full, kBwTile);
+        bw_load_tile(v_s, &tmV, v_full, kv_head * kBwD, krow);
       }
       if (!ok) __nanosleep(200000);
     }
@@ -466,22 +474,25 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (lane == 0) {
       const uint32_t k_a = smem_u32(k_s), v_a = smem_u32(v_s), q_a = smem_u32(q_s), do_a = smem_u32(do_s);
       bool ok = mbar_wait(qdo_full, 0, p.status, kTimeoutFullBarrier);
+      int ks = 0;
+      uint32_t kph = 0;
       for (int n = 0; n < num_iters && ok; ++n) {
-        const int st = n & 1;
+        const int st = n & 1;                 // S buffer
         const uint32_t ph = (n >> 1) & 1;
-        if (!mbar_wait(&k_full[st], ph, p.status, kTimeoutFullBarrier)) break;
+        if (!mbar_wait(&k_full[ks], kph, p.status, kTimeoutFullBarrier)) break;
         // S buffer st was last used by block n - 2
         if (n >= 2 && !mbar_wait(&s_free[st], ph ^ 1, p.status, kTimeoutTmemEmpty)) break;
         tc_fence_after();
-        bw_mma_block<false, false>(tmem_base + kTmS + st * 128, q_a, k_a + st * kBwTile, false);
+        bw_mma_block<false, false>(tmem_base + kTmS + st * 128, q_a, k_a + ks * kBwTile, false);
         umma_commit(&s_full[st]);
-        umma_commit(&k_empty[st]);
-        if (!mbar_wait(&v_full[st], ph, p.status, kTimeoutFullBarrier)) break;
+        umma_commit(&k_empty[ks]);
+        if (++ks == 3) { ks = 0; kph ^= 1; }
+        if (!mbar_wait(v_full, n & 1, p.status, kTimeoutFullBarrier)) break;
         if (n > 0 && !mbar_wait(dp_free, (n - 1) & 1, p.status, kTimeoutTmemEmpty)) break;
         tc_fence_after();
-        bw_mma_block<false, false>(tmem_base + kTmDP, do_a, v_a + st * kBwTile, false);
+        bw_mma_block<false, false>(tmem_base + kTmDP, do_a, v_a, false);
         umma_commit(dp_full);
-        umma_commit(&v_empty[st]);
+        umma_commit(v_empty);
       }
     }
   } else if (warp == 2) {
@@ -489,15 +500,16 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (lane == 0) {
       const uint32_t k_a = smem_u32(k_s), ds_a = smem_u32(ds_s);
       bool ok = true;
+      int ks = 0;
       for (int n = 0; n < num_iters && ok; ++n) {
-        const int st = n & 1;
-        // dS of block n is published only after S of block n was read, so K stage st is loaded
+        // dS of block n is published only after S of block n was read, so K stage ks is loaded
         if (!mbar_wait(ds_ready, n & 1, p.status, kTimeoutPeerFlag)) { ok = false; break; }
         tc_fence_after();
         // dQ[row][d] += sum_key dS[row][key] K[key][d]: K is read MN-major
-        bw_mma_block<false, true>(tmem_base + kTmDQ, ds_a, k_a + st * kBwTile, n > 0);
+        bw_mma_block<false, true>(tmem_base + kTmDQ, ds_a, k_a + ks * kBwTile, n > 0);
         umma_commit(ds_free);
-        umma_commit(&k_empty[st]);
+        umma_commit(&k_empty[ks]);
+        if (++ks == 3) ks = 0;
       }
       if (ok) umma_commit(final_done);
     }
@@ -512,14 +524,14 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const bool row_ok = row < doc_len;
     const long long stat_idx = static_cast<long long>(head) * p.total_q + doc_start + row;
     const float neg_lse2 = row_ok ? -p.lse[stat_idx] * 1.4426950408889634f : 0.f;
-    const float delta = row_ok ? p.delta[stat_idx] : 0.f;
+    const float neg_delta = row_ok ? -p.delta[stat_idx] : 0.f;
     bool ok = true;
     for (int n = 0; n < num_iters && ok; ++n) {
       const int st = n & 1;
       const int col0 = (j_begin + n) * kBwB + 64 * w;
       const int lim_hi = row_ok ? row - col0 : -1;
       const int lim_lo = (p.window > 0) ? lim_hi - p.window : -1;
-      ok = mbar_wait(&s_full[st], (n >> 1) & 1, p.status, kTimeoutTmemFull);
+      ok = mbar_wait_poll(&s_full[st], (n >> 1) & 1, p.status, kTimeoutTmemFull);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -529,16 +541,16 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free[st]);
 
-      ok = mbar_wait(dp_full, n & 1, p.status, kTimeoutTmemFull);
+      ok = mbar_wait_poll(dp_full, n & 1, p.status, kTimeoutTmemFull);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      bw_load_ds(tmem_base + lane_off + kTmDP + 64 * w, pf, delta, p.scale);
+      bw_load_ds(tmem_base + lane_off + kTmDP + 64 * w, pf, neg_delta);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(dp_free);
       if (n > 0) {                                        // dQ of block n - 1 still reads dS
-        ok = mbar_wait(ds_free, (n - 1) & 1, p.status, kTimeoutTmemFull);
+        ok = mbar_wait_poll(ds_free, (n - 1) & 1, p.status, kTimeoutTmemFull);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
       }
@@ -564,10 +576,10 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             uint4 o;
-            o.x = pack_bf16(__uint_as_float(gv[8 * e + 0]), __uint_as_float(gv[8 * e + 1]));
-            o.y = pack_bf16(__uint_as_float(gv[8 * e + 2]), __uint_as_float(gv[8 * e + 3]));
-            o.z = pack_bf16(__uint_as_float(gv[8 * e + 4]), __uint_as_float(gv[8 * e + 5]));
-            o.w = pack_bf16(__uint_as_float(gv[8 * e + 6]), __uint_as_float(gv[8 * e + 7]));
+            o.x = pack_bf16(__uint_as_float(gv[8 * e + 0]) * p.scale, __uint_as_float(gv[8 * e + 1]) * p.scale);
+            o.y = pack_bf16(__uint_as_float(gv[8 * e + 2]) * p.scale, __uint_as_float(gv[8 * e + 3]) * p.scale);
+            o.z = pack_bf16(__uint_as_float(gv[8 * e + 4]) * p.scale, __uint_as_float(gv[8 * e + 5]) * p.scale);
+            o.w = pack_bf16(__uint_as_float(gv[8 * e + 6]) * p.scale, __uint_as_float(gv[8 * e + 7]) * p.scale);
             *reinterpret_cast<uint4*>(dst + 32 * c + 8 * e) = o;
           }
         }
