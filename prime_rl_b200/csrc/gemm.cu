@@ -40,6 +40,12 @@ struct GemmParams {
   const int* block_expert;  // nullptr = dense
   int b_rows_per_expert;
   int* status;
+  // optional extra reduction segment (fused low-rank term): after the K blocks of (A, B) the
+  // same accumulator takes k2_blocks more blocks from a second operand pair (A2 [M, K2],
+  // B2 laid out like B with b2_rows_per_expert rows per expert); K2 need not be a multiple of
+  // 64, TMA zero-fills A2 past K2
+  int k2_blocks = 0;
+  int b2_rows_per_expert = 0;
   const int* expert_offset;  // K-grouped mode
   int num_experts;
   // fused LM head (logprob / entropy) extras
@@ -340,6 +346,7 @@ struct EpiDLogits {
 template <int BN, bool A_MN, bool B_MN, class Sched, class Epi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
                  const GemmParams p) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
@@ -366,6 +373,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (p.k2_blocks > 0) {
+      tma_prefetch_desc(&tmA2);
+      tma_prefetch_desc(&tmB2);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::ACC_COLS);
@@ -388,7 +399,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t ph = 0;
       bool ok = true;
       while (ok && sched.next(p, m_blk, n_blk, brow, last, kb0, nkb, c_row0)) {
-        for (int kb = kb0; kb < kb0 + nkb; ++kb) {
+        const int nk_total = nkb > 0 ? nkb + p.k2_blocks : 0;
+        for (int it = 0; it < nk_total; ++it) {
+          const bool ext = it >= nkb;                 // block of the extra (A2, B2) segment
+          const int kb = ext ? it - nkb : kb0 + it;
+          const CUtensorMap* ma = ext ? &tmA2 : &tmA;
+          const CUtensorMap* mb = ext ? &tmB2 : &tmB;
+          const int brow_k = (ext && p.b_rows_per_expert > 0) ? (brow / p.b_rows_per_expert) * p.b2_rows_per_expert
+                                                              : brow;
           if (!mbar_wait(&empty[s], ph ^ 1, p.status, kTimeoutEmptyBarrier)) {
             ok = false;
             break;
@@ -397,18 +415,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* a_dst = smem + s * Cfg::STAGE_BYTES;
           uint8_t* b_dst = a_dst + Cfg::A_BYTES;
           if (!A_MN) {
-            tma_load_2d(a_dst, &tmA, &full[s], kb * kBK, m_blk * kBM);
+            tma_load_2d(a_dst, ma, &full[s], kb * kBK, m_blk * kBM);
           } else {
 #pragma unroll
             for (int j = 0; j < kBM / 64; ++j)
-              tma_load_2d(a_dst + j * 8192, &tmA, &full[s], m_blk * kBM + 64 * j, kb * kBK);
+              tma_load_2d(a_dst + j * 8192, ma, &full[s], m_blk * kBM + 64 * j, kb * kBK);
           }
           if (!B_MN) {
-            tma_load_2d(b_dst, &tmB, &full[s], kb * kBK, brow + n_blk * BN);
+            tma_load_2d(b_dst, mb, &full[s], kb * kBK, brow_k + n_blk * BN);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(b_dst + j * 8192, &tmB, &full[s], n_blk * BN + 64 * j, brow + kb * kBK);
+              tma_load_2d(b_dst + j * 8192, mb, &full[s], n_blk * BN + 64 * j, brow_k + kb * kBK);
           }
           if (++s == STAGES) {
             s = 0;
@@ -431,7 +449,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!mbar_wait(&tempty[acc], acc_ph ^ 1, p.status, kTimeoutTmemEmpty)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < nkb; ++kb) {
+        const int nk_total = nkb + p.k2_blocks;
+        for (int kb = 0; kb < nk_total; ++kb) {
           if (!mbar_wait(&full[s], ph, p.status, kTimeoutFullBarrier)) {
             ok = false;
             break;
@@ -506,7 +525,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 template <int BN, bool A_MN, bool B_MN, bool GROUPED>
-static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, cudaStream_t stream) {
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmA2,
+                       const CUtensorMap& tmB2, const GemmParams& p, cudaStream_t stream) {
   using Cfg = GemmCfg<BN>;
   using Sched = typename std::conditional<GROUPED, SchedGrouped, SchedDense>::type;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, Sched, EpiStore>;
@@ -519,17 +539,17 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
   const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
   if (grid <= 0) return 0;
-  kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmA2, tmB2, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
 template <bool A_MN, bool B_MN, bool GROUPED>
-static int dispatch_bn(int bn, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
-                       cudaStream_t stream) {
+static int dispatch_bn(int bn, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmA2,
+                       const CUtensorMap& tmB2, const GemmParams& p, cudaStream_t stream) {
   switch (bn) {
-    case 256: return launch_gemm<256, A_MN, B_MN, GROUPED>(tmA, tmB, p, stream);
-    case 128: return launch_gemm<128, A_MN, B_MN, GROUPED>(tmA, tmB, p, stream);
-    default: return launch_gemm<64, A_MN, B_MN, GROUPED>(tmA, tmB, p, stream);
+    case 256: return launch_gemm<256, A_MN, B_MN, GROUPED>(tmA, tmB, tmA2, tmB2, p, stream);
+    case 128: return launch_gemm<128, A_MN, B_MN, GROUPED>(tmA, tmB, tmA2, tmB2, p, stream);
+    default: return launch_gemm<64, A_MN, B_MN, GROUPED>(tmA, tmB, tmA2, tmB2, p, stream);
   }
 }
 
@@ -539,10 +559,11 @@ static int dispatch_bn(int bn, const CUtensorMap& tmA, const CUtensorMap& tmB, c
 // tensors described at the top of this file. `block_expert` (device, int32) switches on
 // grouped mode. `status` is a device int that receives a prb::StatusCode on a bounded-wait
 // failure (and is left untouched otherwise). Returns 0 when the launch was issued.
-PRB_API int prb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                           long long ldc, int a_mn, int b_mn, int out_fp32, float alpha, float beta,
                           const int* block_expert, int num_experts, int b_rows_per_expert, int force_bn,
-                          int* status, void* stream_) {
+                          const void* A2, const void* B2, int K2, long long lda2, long long ldb2,
+                          int b2_rows_per_expert, int* status, void* stream_) {
   using namespace prb;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0) return 0;
@@ -578,10 +599,29 @@ PRB_API int prb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, i
     rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, grouped ? E * b_rows_per_expert : (uint64_t)K,
                       (uint64_t)N, (uint64_t)ldb, kBK, 64, true);
   if (rc) return rc;
+  CUtensorMap tmA2 = tmA, tmB2 = tmB;
+  if (A2 != nullptr && K2 > 0) {
+    // the extra segment shares the layout flags of the main operands; A2 is always [M, K2]
+    if (a_mn) return -6;
+    if ((lda2 % 8) || (ldb2 % 8) || (reinterpret_cast<uintptr_t>(A2) & 15) || (reinterpret_cast<uintptr_t>(B2) & 15))
+      return -4;
+    rc = make_tmap_2d(&tmA2, A2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K2, (uint64_t)lda2, kBM,
+                      kBK, true);
+    if (rc) return rc;
+    if (!b_mn)
+      rc = make_tmap_2d(&tmB2, B2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                        grouped ? E * b2_rows_per_expert : (uint64_t)N, (uint64_t)K2, (uint64_t)ldb2, bn, kBK, true);
+    else
+      rc = make_tmap_2d(&tmB2, B2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                        grouped ? E * b2_rows_per_expert : (uint64_t)K2, (uint64_t)N, (uint64_t)ldb2, kBK, 64, true);
+    if (rc) return rc;
+  }
 
   GemmParams p;
   p.M = M; p.N = N; p.K = K; p.rows_total = M;
   p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32;
+  p.k2_blocks = (A2 != nullptr && K2 > 0) ? (K2 + kBK - 1) / kBK : 0;
+  p.b2_rows_per_expert = b2_rows_per_expert;
   p.expert_offset = nullptr; p.num_experts = 0;
   p.alpha = alpha; p.beta = beta;
   p.block_expert = block_expert;
@@ -592,13 +632,35 @@ PRB_API int prb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, i
   p.grad_logprob = nullptr; p.lse = nullptr;
 
 #define PRB_DISPATCH(AMN, BMN)                                                              \
-  (grouped ? dispatch_bn<AMN, BMN, true>(bn, tmA, tmB, p, stream)                           \
-           : dispatch_bn<AMN, BMN, false>(bn, tmA, tmB, p, stream))
+  (grouped ? dispatch_bn<AMN, BMN, true>(bn, tmA, tmB, tmA2, tmB2, p, stream)                           \
+           : dispatch_bn<AMN, BMN, false>(bn, tmA, tmB, tmA2, tmB2, p, stream))
   if (!a_mn && !b_mn) return PRB_DISPATCH(false, false);
   if (!a_mn && b_mn) return PRB_DISPATCH(false, true);
   if (a_mn && b_mn) return PRB_DISPATCH(true, true);
   return PRB_DISPATCH(true, false);
 #undef PRB_DISPATCH
+}
+
+PRB_API int prb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                          long long ldc, int a_mn, int b_mn, int out_fp32, float alpha, float beta,
+                          const int* block_expert, int num_experts, int b_rows_per_expert, int force_bn,
+                          int* status, void* stream_) {
+  return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_fp32, alpha, beta, block_expert, num_experts,
+                        b_rows_per_expert, force_bn, nullptr, nullptr, 0, 0, 0, 0, status, stream_);
+}
+
+// C = alpha * (A B + A2 B2) + beta * C in one pass: the accumulator of every tile takes the
+// K blocks of (A, B) and then those of (A2, B2). Used for y = x W^T + (x A^T) B^T of a LoRA
+// linear (and its input gradient), where a separate rank-r product would re-read and re-write
+// all of C. A2: bf16 [M, K2] row-major; B2 is laid out like B (K-major [N, K2] rows, or
+// MN-major [K2, N]); grouped mode: b2_rows_per_expert rows of B2 per expert.
+PRB_API int prb_gemm_bf16_ext(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                              long long ldb, long long ldc, int a_mn, int b_mn, int out_fp32, float alpha,
+                              float beta, const int* block_expert, int num_experts, int b_rows_per_expert,
+                              int force_bn, const void* A2, const void* B2, int K2, long long lda2, long long ldb2,
+                              int b2_rows_per_expert, int* status, void* stream_) {
+  return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_fp32, alpha, beta, block_expert, num_experts,
+                        b_rows_per_expert, force_bn, A2, B2, K2, lda2, ldb2, b2_rows_per_expert, status, stream_);
 }
 
 // ---------------------------------------------------------------- fused LM head
@@ -686,7 +748,7 @@ PRB_API int prb_lmhead_fwd(const void* h, const void* W, const int* labels, cons
   }
   const int items = ((T + 127) / 128) * splits;
   const int grid = items < sm_count() ? items : sm_count();
-  kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmA, tmB, p);
   lmhead_combine_kernel<<<(T + 255) / 256, 256, 0, stream>>>(part_m, part_s, part_t, target, labels, logprob, entropy,
                                                             lse, T, splits, V);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
@@ -717,7 +779,7 @@ PRB_API int prb_lmhead_bwd_dlogits(const void* h, const void* W, const int* labe
   }
   const int tiles = ((T + 127) / 128) * ((V + 255) / 256);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+  kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmA, tmB, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -760,7 +822,7 @@ PRB_API int prb_gemm_bf16_kgrouped(const void* A, const void* B, void* C, int M,
         return -10;                                                                                       \
       configured = true;                                                                                  \
     }                                                                                                     \
-    kern<<<grid, kGemmThreads, GemmCfg<BN_>::SMEM_BYTES, stream>>>(tmA, tmB, p);                          \
+    kern<<<grid, kGemmThreads, GemmCfg<BN_>::SMEM_BYTES, stream>>>(tmA, tmB, tmA, tmB, p);                          \
   }
   if (bn == 256) PRB_KG(256) else if (bn == 128) PRB_KG(128) else PRB_KG(64)
 #undef PRB_KG

@@ -8,8 +8,10 @@
                          src/prime_rl/trainer/models/layers/lora/).
 
 The base weight is frozen (no weight gradient is formed); every product runs on the
-tcgen05 GEMM: the rank-r operands ride on TMA's out-of-bounds zero fill, and the adapter
-output is accumulated in the epilogue (``beta = 1``) instead of a separate add.
+tcgen05 GEMM. The adapter term is not a separate pass over the output: the S adapters' B
+matrices are laid out block-diagonally as one ``[out, S*r]`` operand and the base GEMM takes
+``(x A^T, B_blockdiag)`` as one extra reduction block into the same TMEM accumulator (TMA
+zero-fills the rank-r operands up to the 64-wide block), in forward and for the input gradient.
 """
 
 from __future__ import annotations
@@ -37,39 +39,48 @@ def lora_linear_ref(x, w, a_cat, b_list, scale):
     return y + scale * torch.cat(parts, dim=-1)
 
 
+def _block_diag(b_list, scale):
+    """[.., out_s, r] x S -> [.., sum(out_s), S*r] with B_s * scale in its own r columns."""
+    r = b_list[0].shape[-1]
+    S = len(b_list)
+    out = sum(b.shape[-2] for b in b_list)
+    bd = torch.zeros(*b_list[0].shape[:-2], out, S * r, dtype=b_list[0].dtype, device=b_list[0].device)
+    c = 0
+    for s, b in enumerate(b_list):
+        bd[..., c:c + b.shape[-2], s * r:(s + 1) * r] = b if scale == 1.0 else b * scale
+        c += b.shape[-2]
+    return bd
+
+
 class _LoRALinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, a_cat, scale, *b_list):
-        r = b_list[0].shape[1]
-        y = gemm(x, w)
         t = gemm(x, a_cat)
-        for s, (c0, c1) in enumerate(_segments([b.shape[0] for b in b_list])):
-            gemm(t[:, s * r:(s + 1) * r], b_list[s], out=y[:, c0:c1], alpha=scale, beta=1.0)
-        ctx.save_for_backward(x, w, a_cat, t, *b_list)
+        bd = _block_diag(b_list, scale)
+        y = gemm(x, w, ext=(t, bd))
+        ctx.save_for_backward(x, w, a_cat, t, bd)
         ctx.scale = scale
+        ctx.seg = [b.shape[0] for b in b_list]
+        ctx.b_dtype = b_list[0].dtype
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x, w, a_cat, t, *b_list = ctx.saved_tensors
+        x, w, a_cat, t, bd = ctx.saved_tensors
         scale = ctx.scale
-        r = b_list[0].shape[1]
-        S = len(b_list)
+        S = len(ctx.seg)
+        r = bd.shape[1] // S
         if not dy.is_contiguous():
             dy = dy.contiguous()
-        T = dy.shape[0]
-        dt = torch.empty(T, S * r, dtype=dy.dtype, device=dy.device)
+        dt = gemm(dy, bd, b_mn=True)                       # [T, S*r], scale is inside bd
         db = []
-        for s, (c0, c1) in enumerate(_segments([b.shape[0] for b in b_list])):
-            dys = dy[:, c0:c1]
-            gemm(dys, b_list[s], b_mn=True, out=dt[:, s * r:(s + 1) * r], alpha=scale)
-            db.append(gemm(dys, t[:, s * r:(s + 1) * r], a_mn=True, b_mn=True, out_dtype=torch.float32,
-                           alpha=scale).to(b_list[s].dtype))
+        for s, (c0, c1) in enumerate(_segments(ctx.seg)):
+            db.append(gemm(dy[:, c0:c1], t[:, s * r:(s + 1) * r], a_mn=True, b_mn=True, out_dtype=torch.float32,
+                           alpha=scale).to(ctx.b_dtype))
         da = gemm(dt, x, a_mn=True, b_mn=True, out_dtype=torch.float32).to(a_cat.dtype)
         dx = None
         if ctx.needs_input_grad[0]:
-            dx = gemm(dy, w, b_mn=True)
-            gemm(dt, a_cat, b_mn=True, out=dx, beta=1.0)
+            dx = gemm(dy, w, b_mn=True, ext=(dt, a_cat))
         return (dx, None, da, None, *db)
 
 
@@ -119,38 +130,33 @@ def lora_grouped_linear_ref(x, w, a_cat, b_list, scale, block_expert):
 class _LoRAGroupedLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, a_cat, scale, block_expert, expert_offset, *b_list):
-        r = b_list[0].shape[2]
-        y = gemm(x, w, block_expert=block_expert)
         t = gemm(x, a_cat, block_expert=block_expert)
-        for s, (c0, c1) in enumerate(_segments([b.shape[1] for b in b_list])):
-            gemm(t[:, s * r:(s + 1) * r], b_list[s], block_expert=block_expert, out=y[:, c0:c1], alpha=scale,
-                 beta=1.0)
-        ctx.save_for_backward(x, w, a_cat, t, block_expert, expert_offset, *b_list)
+        bd = _block_diag(b_list, scale)                    # [E, out, S*r]
+        y = gemm(x, w, block_expert=block_expert, ext=(t, bd))
+        ctx.save_for_backward(x, w, a_cat, t, block_expert, expert_offset, bd)
         ctx.scale = scale
+        ctx.seg = [b.shape[1] for b in b_list]
+        ctx.b_dtype = b_list[0].dtype
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x, w, a_cat, t, block_expert, expert_offset, *b_list = ctx.saved_tensors
+        x, w, a_cat, t, block_expert, expert_offset, bd = ctx.saved_tensors
         scale = ctx.scale
         E = w.shape[0]
-        r = b_list[0].shape[2]
-        S = len(b_list)
+        S = len(ctx.seg)
+        r = bd.shape[2] // S
         if not dy.is_contiguous():
             dy = dy.contiguous()
-        P = dy.shape[0]
-        dt = torch.empty(P, S * r, dtype=dy.dtype, device=dy.device)
+        dt = gemm(dy, bd, b_mn=True, block_expert=block_expert)     # [P, S*r], scale is inside bd
         db = []
-        for s, (c0, c1) in enumerate(_segments([b.shape[1] for b in b_list])):
-            dys = dy[:, c0:c1]
-            gemm(dys, b_list[s], b_mn=True, block_expert=block_expert, out=dt[:, s * r:(s + 1) * r], alpha=scale)
-            db.append(kgrouped_gemm(dys, t[:, s * r:(s + 1) * r], expert_offset, E, alpha=scale)
-                      .to(b_list[s].dtype))
+        for s, (c0, c1) in enumerate(_segments(ctx.seg)):
+            db.append(kgrouped_gemm(dy[:, c0:c1], t[:, s * r:(s + 1) * r], expert_offset, E, alpha=scale)
+                      .to(ctx.b_dtype))
         da = kgrouped_gemm(dt, x, expert_offset, E).to(a_cat.dtype)
         dx = None
         if ctx.needs_input_grad[0]:
-            dx = gemm(dy, w, b_mn=True, block_expert=block_expert)
-            gemm(dt, a_cat, b_mn=True, block_expert=block_expert, out=dx, beta=1.0)
+            dx = gemm(dy, w, b_mn=True, block_expert=block_expert, ext=(dt, a_cat))
         return (dx, None, da, None, None, None, *db)
 
 

@@ -45,12 +45,26 @@ def gemm(
     b_rows_per_expert: int = 0,
     n: int | None = None,
     force_bn: int = 0,
+    ext: tuple[torch.Tensor, torch.Tensor] | None = None,
 ) -> torch.Tensor:
     """C = alpha * A.B + beta * C. Grouped mode when ``block_expert`` is given: ``b`` is the
-    stacked expert weight ``[E, rows, cols]`` and ``n`` the output width."""
+    stacked expert weight ``[E, rows, cols]`` and ``n`` the output width. ``ext = (a2, b2)`` adds
+    ``a2.b2`` in the same pass (``a2``: [M, K2]; ``b2`` laid out like ``b`` with reduction K2)."""
     if not a.is_cuda or a.dtype != torch.bfloat16:
         if block_expert is not None:
-            return grouped_gemm_ref(a, b, block_expert, b_mn=b_mn, out_dtype=out_dtype, n=n)
+            res = grouped_gemm_ref(a, b, block_expert, b_mn=b_mn, out_dtype=torch.float32, n=n)
+            if ext is not None:
+                res = res + grouped_gemm_ref(ext[0], ext[1], block_expert, b_mn=b_mn, out_dtype=torch.float32, n=n)
+            return res.to(out_dtype or a.dtype)
+        if ext is not None:
+            res = gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32) + \
+                gemm_ref(ext[0], ext[1], b_mn=b_mn, out_dtype=torch.float32)
+            res = alpha * res + (beta * out.float() if (beta != 0.0 and out is not None) else 0.0)
+            res = res.to(out_dtype or a.dtype)
+            if out is not None:
+                out.copy_(res)
+                return out
+            return res
         return gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=out_dtype, alpha=alpha, beta=beta, out=out)
     assert a.dim() == 2 and a.stride(1) == 1 and b.stride(-1) == 1
     M = a.shape[1] if a_mn else a.shape[0]
@@ -74,6 +88,26 @@ def gemm(
         assert beta == 0.0
     assert out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
     status = rt.status_tensor(a.device)
+    if ext is not None:
+        a2, b2 = ext
+        assert not a_mn and a2.dim() == 2 and a2.shape[0] == M and a2.stride(1) == 1 and b2.stride(-1) == 1
+        K2 = a2.shape[1]
+        if grouped:
+            assert b2.dim() == 3 and b2.is_contiguous() and b2.shape[0] == num_experts
+            assert (b2.shape[1] if b_mn else b2.shape[2]) == K2
+            ldb2, b2_rows = b2.shape[2], b2.shape[1]
+        else:
+            assert b2.dim() == 2 and (b2.shape[0] if b_mn else b2.shape[1]) == K2
+            ldb2, b2_rows = b2.stride(0), 0
+        rc = rt.lib().prb_gemm_bf16_ext(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), ldb, out.stride(0),
+            int(a_mn), int(b_mn), int(out.dtype == torch.float32), float(alpha), float(beta),
+            rt.ptr(block_expert), int(num_experts), int(b_rows_per_expert), int(force_bn),
+            a2.data_ptr(), b2.data_ptr(), K2, a2.stride(0), ldb2, b2_rows,
+            status.data_ptr(), rt.stream_ptr(a.device),
+        )
+        rt.check(rc, "prb_gemm_bf16_ext")
+        return out
     rc = rt.lib().prb_gemm_bf16(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), ldb, out.stride(0),
         int(a_mn), int(b_mn), int(out.dtype == torch.float32), float(alpha), float(beta),

@@ -284,6 +284,40 @@ def test_gemm_kgrouped():
     assert bool((out[1] == 0).all())
 
 
+def test_gemm_extra_reduction_segment():
+    """C = A B^T + A2 B2^T in one pass (dense and grouped, K-major and MN-major B)."""
+    from prime_rl_b200.ops.matmul import gemm, grouped_gemm_ref
+    M, N, K, K2 = 300, 520, 200, 48
+    a, b, a2, b2 = _rand(M, K), _rand(N, K), _rand(M, K2), _rand(N, K2)
+    out = gemm(a, b, ext=(a2, b2))
+    rt.check_status()
+    ref = a.float() @ b.float().t() + a2.float() @ b2.float().t()
+    _close(out, ref, atol=0.3, rtol=2e-2)
+    # MN-major B (the input-gradient form): B [K, N], B2 [K2, N]
+    bt, b2t = _rand(K, N), _rand(K2, N)
+    out = gemm(a, bt, b_mn=True, ext=(a2, b2t))
+    rt.check_status()
+    _close(out, a.float() @ bt.float() + a2.float() @ b2t.float(), atol=0.3, rtol=2e-2)
+    # grouped
+    counts = torch.tensor([130, 0, 5, 256], dtype=torch.int32)
+    offs, be, P = _blocks(counts)
+    E = 4
+    x, t = _rand(P, K), _rand(P, K2)
+    w, w2 = _rand(E, N, K), _rand(E, N, K2)
+    out = gemm(x, w, block_expert=be.to(DEV), ext=(t, w2))
+    rt.check_status()
+    ref = grouped_gemm_ref(x.cpu(), w.cpu(), be, out_dtype=torch.float32) + \
+        grouped_gemm_ref(t.cpu(), w2.cpu(), be, out_dtype=torch.float32)
+    used = (be >= 0).repeat_interleave(128)
+    _close(out.cpu()[used], ref[used], atol=0.3, rtol=2e-2)
+    wt, w2t = _rand(E, K, N), _rand(E, K2, N)
+    out = gemm(x, wt, b_mn=True, block_expert=be.to(DEV), ext=(t, w2t))
+    rt.check_status()
+    ref = grouped_gemm_ref(x.cpu(), wt.cpu(), be, b_mn=True, out_dtype=torch.float32) + \
+        grouped_gemm_ref(t.cpu(), w2t.cpu(), be, b_mn=True, out_dtype=torch.float32)
+    _close(out.cpu()[used], ref[used], atol=0.3, rtol=2e-2)
+
+
 def test_lora_linear_and_grouped():
     from prime_rl_b200.ops import lora
     T, IN, r = 300, 256, 16
