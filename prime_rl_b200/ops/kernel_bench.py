@@ -1,0 +1,201 @@
+"""Micro-benchmarks of the native kernels against the measured roofline of the device.
+
+    python -m prime_rl_b200.ops.kernel_bench                      # all ops, default sizes
+    python -m prime_rl_b200.ops.kernel_bench --op flash_fwd --tokens 4096 --iters 1 --warmup 1
+
+Every number is the median of CUDA-event timings on the launching stream after warm-up, with
+a 256 MB buffer written between iterations so that nothing is served from L2. Fractions are
+relative to the peaks in ``MEASURED_PEAKS.json`` at the repository root when that file exists
+(a plain copy for bandwidth, a cuBLAS bf16 GEMM for FLOP/s), else to 6.65 TB/s / 1.59 PFLOP/s.
+The ``--iters 1 --warmup 1`` form is the small, short case meant to be run under a profiler.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+import torch
+
+from . import _runtime as rt
+
+
+def _peaks():
+    f = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if f.exists():
+        d = json.loads(f.read_text())
+        return d["hbm_gbs"], d["bf16_tflops"], "of measured"
+    return 6650.0, 1590.0, "of fallback"
+
+
+class Timer:
+    def __init__(self, iters, warmup, device):
+        self.iters, self.warmup = iters, warmup
+        self.flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
+
+    def __call__(self, fn):
+        for _ in range(self.warmup):
+            fn()
+        torch.cuda.synchronize()
+        rt.check_status()
+        ts = []
+        for _ in range(self.iters):
+            self.flush.zero_()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e))
+        rt.check_status()
+        return sorted(ts)[len(ts) // 2]
+
+
+def _report(name, ms, *, flops=None, bytes_=None, extra=""):
+    hbm, tf, tag = _peaks()
+    parts = [f"{name:44s} {ms:9.3f} ms"]
+    if flops is not None:
+        t = flops / ms / 1e9
+        parts.append(f"{t:8.0f} TFLOP/s ({t / tf:.2f} {tag})")
+    if bytes_ is not None:
+        g = bytes_ / ms / 1e6
+        parts.append(f"{g:8.0f} GB/s ({g / hbm:.2f} {tag})")
+    print("  ".join(parts) + (f"  {extra}" if extra else ""), flush=True)
+
+
+def bench_gemm(timer, args, dev):
+    from .matmul import gemm
+
+    shapes = [(8192, 8192, 8192), (16384, 4096, 2048), (16384, 5120, 2048), (16384, 2048, 4096)]
+    if args.tokens:
+        shapes = [(args.tokens, 4096, 2048)]
+    for M, N, K in shapes:
+        a = torch.randn(M, K, device=dev).bfloat16()
+        b = torch.randn(N, K, device=dev).bfloat16()
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        _report(f"gemm {M}x{N}x{K} (K-major B)", timer(lambda: gemm(a, b, out=out)), flops=2 * M * N * K)
+        if not args.tokens:
+            _report(f"  cuBLAS (torch.matmul) {M}x{N}x{K}", timer(lambda: torch.matmul(a, b.t(), out=out)),
+                    flops=2 * M * N * K)
+
+
+def bench_grouped(timer, args, dev):
+    from .matmul import gemm
+
+    T = args.tokens or 16384
+    E, topk, H, I = 128, 8, 2048, 768
+    rows = T * topk
+    per = rows // E
+    padded = (per + 127) // 128 * 128
+    P = padded * E
+    be = torch.arange(E, dtype=torch.int32, device=dev).repeat_interleave(padded // 128)
+    x = torch.randn(P, H, device=dev).bfloat16()
+    w1 = torch.randn(E, 2 * I, H, device=dev).bfloat16()
+    w2 = torch.randn(E, H, I, device=dev).bfloat16()
+    h = torch.randn(P, I, device=dev).bfloat16()
+    t = torch.randn(P, 32, device=dev).bfloat16()
+    b2 = torch.randn(E, 2 * I, 32, device=dev).bfloat16()
+    _report(f"grouped gate_up {P}x{2 * I}x{H} E={E}", timer(lambda: gemm(x, w1, block_expert=be)), flops=2 * P * 2 * I * H)
+    _report("  + fused rank-32 LoRA segment", timer(lambda: gemm(x, w1, block_expert=be, ext=(t, b2))),
+            flops=2 * P * 2 * I * (H + 32))
+    _report(f"grouped down {P}x{H}x{I} E={E}", timer(lambda: gemm(h, w2, block_expert=be)), flops=2 * P * H * I)
+    dy = torch.randn(P, 2 * I, device=dev).bfloat16()
+    _report("grouped input gradient of gate_up (MN-major B)", timer(lambda: gemm(dy, w1, b_mn=True, block_expert=be)),
+            flops=2 * P * 2 * I * H)
+
+
+def bench_lm_head(timer, args, dev):
+    from .lm_head import fused_logprob_entropy
+
+    T, V, H = args.tokens or 16384, 151936, 2048
+    h = torch.randn(T, H, device=dev).bfloat16().requires_grad_()
+    w = (torch.randn(V, H, device=dev) * 0.02).bfloat16()
+    labels = torch.randint(0, V, (T,), device=dev)
+    _report(f"lm head fwd (logprob+entropy) {T}x{V}x{H}",
+            timer(lambda: fused_logprob_entropy(h.detach(), w, labels, None)), flops=2 * T * V * H)
+
+    def fb():
+        lp, _ = fused_logprob_entropy(h, w, labels, None)
+        lp.sum().backward()
+
+    _report("lm head fwd + bwd (dlogits, dh)", timer(fb), flops=6 * T * V * H)
+
+
+def _attn_inputs(args, dev):
+    T = args.tokens or 16384
+    Hq, Hkv, D = 32, 4, 128
+    q = torch.randn(T, Hq, D, device=dev).bfloat16()
+    k = torch.randn(T, Hkv, D, device=dev).bfloat16()
+    v = torch.randn(T, Hkv, D, device=dev).bfloat16()
+    cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+    return T, Hq, D, q, k, v, cu
+
+
+def bench_flash_fwd(timer, args, dev):
+    from . import flash_native
+
+    T, Hq, D, q, k, v, cu = _attn_inputs(args, dev)
+    fl = 4 * T * T / 2 * Hq * D
+    _report(f"flash fwd causal T={T} Hq={Hq} Hkv=4 D=128", timer(lambda: flash_native.flash_fwd(q, k, v, cu)), flops=fl)
+
+
+def bench_flash_bwd(timer, args, dev):
+    from . import flash_native
+
+    T, Hq, D, q, k, v, cu = _attn_inputs(args, dev)
+    out, lse = flash_native.flash_fwd(q, k, v, cu)
+    do = torch.randn_like(out)
+    fl = 10 * T * T / 2 * Hq * D
+    _report(f"flash bwd causal T={T} (dK/dV kernel + dQ kernel)",
+            timer(lambda: flash_native.flash_bwd(do, q, k, v, out, lse, cu)), flops=fl,
+            extra="(FLOPs counted as 5 products per block; 7 are executed)")
+
+
+def bench_paged(timer, args, dev):
+    from .paged import paged_decode_raw
+
+    B, ctx, Hq, Hkv, D, page = 64, args.tokens or 4096, 32, 4, 128, 16
+    blocks = (ctx + page - 1) // page
+    pool = B * blocks
+    kpool = torch.randn(pool, page, Hkv, D, device=dev).bfloat16()
+    vpool = torch.randn(pool, page, Hkv, D, device=dev).bfloat16()
+    tables = torch.arange(pool, dtype=torch.int32, device=dev).view(B, blocks)
+    lens = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+    q = torch.randn(B, Hq, D, device=dev).bfloat16()
+    by = 2 * B * ctx * Hkv * D * 2
+    _report(f"paged decode B={B} ctx={ctx} GQA 32/4", timer(lambda: paged_decode_raw(q, kpool, vpool, tables, lens)), bytes_=by)
+
+
+def bench_norm(timer, args, dev):
+    from .norm import rms_norm
+
+    T, H = args.tokens or 16384, 2048
+    x = torch.randn(T, H, device=dev).bfloat16()
+    w = torch.ones(H, device=dev).bfloat16()
+    _report(f"rmsnorm fwd {T}x{H}", timer(lambda: rms_norm(x, w, 1e-6)), bytes_=2 * T * H * 2)
+
+
+OPS = {"gemm": bench_gemm, "grouped": bench_grouped, "lm_head": bench_lm_head, "flash_fwd": bench_flash_fwd,
+       "flash_bwd": bench_flash_bwd, "paged": bench_paged, "norm": bench_norm}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--op", default="all", choices=["all", *OPS])
+    ap.add_argument("--tokens", type=int, default=0, help="problem size override (rows / sequence length)")
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args(argv)
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    torch.manual_seed(0)
+    timer = Timer(args.iters, args.warmup, dev)
+    for name, fn in OPS.items():
+        if args.op in ("all", name):
+            fn(timer, args, dev)
+            torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()
