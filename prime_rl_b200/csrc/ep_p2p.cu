@@ -1,0 +1,356 @@
+// Expert-parallel token exchange over NVLink peer memory (one process per GPU, buffers mapped
+// into every rank with CUDA IPC). Rows go straight from the sender's activations into their
+// final position of the owner's expert-sorted, 128-row-aligned buffer (no staging copy, no
+// host read of split sizes), and come back through peer loads fused with the top-k weighted
+// sum. Synchronisation is by epoch flags in peer memory; every wait is bounded.
+//
+//   ep_hist_kernel     every rank stores its per-expert pair counts into all peers' tables
+//   ep_plan_kernel     waits for the tables, then derives (a) where this rank's rows of each
+//                      expert start inside the owner's buffer, (b) the local expert offsets /
+//                      block map for the grouped GEMM
+//   ep_push_kernel     one warp per (token, k) pair: 16-byte peer stores of the row (optionally
+//                      scaled: the gradient of the combine), then a data flag on every peer
+//   ep_recv_kernel     waits for all senders' data flags, zeroes the padding rows
+//   ep_signal_kernel   "my buffer is complete" flag on every peer
+//   ep_pull_kernel     waits for the owners' flags; out[t] = sum_k w[t,k] * peer_row(t,k) with
+//                      peer loads (also: gradient of the dispatch with w = 1); optional
+//                      dw[t,k] = <peer_row(t,k), g[t]>
+//
+// Takes the place of the all-to-all token dispatchers of the reference
+// (src/prime_rl/trainer/distributed/token_dispatcher.py:247-301 and its DeepEP variant,
+// deepep.py): those move rows with library collectives and permute them in separate kernels.
+// No TMA multicast and no library kernel ever touches peer memory here: plain ld / st only.
+#include "common.cuh"
+
+namespace prb {
+
+constexpr int kEpMaxRanks = 16;
+constexpr long long kEpWaitCycles = 4000000000LL;   // about 2 s
+
+struct EpPeers {
+  void* buf[kEpMaxRanks];     // a symmetric buffer on every rank (index = rank)
+};
+
+// flags: int32 [kinds][R] on every rank; slot [kind][src] is written by rank src only.
+__device__ __forceinline__ bool ep_wait_flag(const int* flag, int epoch, int* status) {
+  const volatile int* f = flag;
+  if (*f - epoch >= 0) return true;
+  const long long t0 = clock64();
+  unsigned spins = 0;
+  while (*f - epoch < 0) {
+    if ((++spins & 0xff) == 0) {
+      if (*reinterpret_cast<volatile int*>(status) != 0) return false;
+      if (clock64() - t0 > kEpWaitCycles) {
+        atomicCAS(status, 0, static_cast<int>(kTimeoutPeerFlag));
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// All threads of the CTA return the same verdict; thread i < R waits for source i.
+__device__ __forceinline__ bool ep_wait_all(const int* flags_kind, int R, int epoch, int* status) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < R && !ep_wait_flag(flags_kind + threadIdx.x, epoch, status)) s_ok = 0;
+  __syncthreads();
+  __threadfence_system();   // acquire side: order the payload reads after the flag reads
+  return s_ok != 0;
+}
+
+__global__ void __launch_bounds__(128)
+ep_hist_kernel(const int* __restrict__ counts, EpPeers hist, EpPeers flags, int rank, int R, int E, int kind,
+               int epoch) {
+  for (int d = 0; d < R; ++d) {
+    int* dst = reinterpret_cast<int*>(hist.buf[d]) + rank * E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) dst[e] = counts[e];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < R) {
+    volatile int* f = reinterpret_cast<int*>(flags.buf[threadIdx.x]) + kind * R + rank;
+    *f = epoch;
+  }
+}
+
+// hist: local table [R][E]. send_base[e]: first row of this rank's pairs of expert e inside the
+// owner's buffer. expert_offset [El + 1], block_expert [max_blocks], total_rows [1]: the local
+// receive layout. Sets kBadArgument in *status when the local layout exceeds cap_rows.
+__global__ void __launch_bounds__(128)
+ep_plan_kernel(const int* __restrict__ hist, const int* __restrict__ flags_kind, int rank, int R, int E, int epoch,
+               int cap_rows, int max_blocks, int* __restrict__ send_base, int* __restrict__ expert_offset,
+               int* __restrict__ block_expert, int* __restrict__ total_rows, int* status) {
+  __shared__ int s_off[1024 + 1];
+  if (!ep_wait_all(flags_kind, R, epoch, status)) return;
+  const int El = E / R;
+  // every thread owns some global experts: totals and the part in front of this rank
+  __shared__ int s_tot[1024], s_pre[1024];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int tot = 0, pre = 0;
+    for (int s = 0; s < R; ++s) {
+      const int c = hist[s * E + e];
+      tot += c;
+      if (s < rank) pre += c;
+    }
+    s_tot[e] = tot;
+    s_pre[e] = pre;
+  }
+  __syncthreads();
+  if (threadIdx.x < R) {   // thread d lays out destination d
+    const int d = threadIdx.x;
+    int off = 0;
+    for (int le = 0; le < El; ++le) {
+      const int e = d * El + le;
+      send_base[e] = off + s_pre[e];
+      if (d == rank) s_off[le] = off;
+      off += (s_tot[e] + 127) / 128 * 128;
+    }
+    if (d == rank) {
+      s_off[El] = off;
+      total_rows[0] = off;
+      if (off > cap_rows) atomicCAS(status, 0, static_cast<int>(kBadArgument));
+    }
+  }
+  __syncthreads();
+  for (int le = threadIdx.x; le <= El; le += blockDim.x) expert_offset[le] = s_off[le];
+  for (int b = threadIdx.x; b < max_blocks; b += blockDim.x) {
+    const int row = b * 128;
+    int ex = -1;
+    if (row < s_off[El]) {
+      int lo = 0, hi = El;   // last le with s_off[le] <= row
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (s_off[mid] <= row) lo = mid; else hi = mid;
+      }
+      ex = lo;
+    }
+    block_expert[b] = ex;
+  }
+}
+
+// One warp per pair. pos_out[p] = row inside the owner's buffer (kept for the way back).
+// When pos_in != nullptr the positions are given (second trip over the same routes).
+__global__ void __launch_bounds__(256)
+ep_push_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ topk_idx, const int* __restrict__ slot,
+               const int* __restrict__ local_off, const int* __restrict__ send_base, const int* __restrict__ pos_in,
+               const float* __restrict__ scale, EpPeers dst, EpPeers flags, int* __restrict__ pos_out,
+               unsigned* __restrict__ done_counter, int num_pairs, int k, int H, int El, int rank, int R, int kind,
+               int epoch, int cap_rows, int* status) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = blockDim.x >> 5;
+  for (int p = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); p < num_pairs; p += gridDim.x * warps_per_cta) {
+    const int e = topk_idx[p];
+    const int d = e / El;
+    const int pos = pos_in ? pos_in[p] : send_base[e] + slot[p] - local_off[e];
+    if (pos_out && lane == 0) pos_out[p] = pos;
+    if (pos < 0 || pos >= cap_rows) {   // never store outside the peer's buffer
+      if (lane == 0) atomicCAS(status, 0, static_cast<int>(kBadArgument));
+      continue;
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<long long>(p / k) * H);
+    uint4* out = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst.buf[d]) + static_cast<long long>(pos) * H);
+    if (scale == nullptr) {
+      for (int i = lane; i < H / 8; i += 32) out[i] = src[i];
+    } else {
+      const float s = scale[p];
+      for (int i = lane; i < H / 8; i += 32) {
+        uint4 v = src[i];
+        float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y), c = unpack_bf16(v.z), dd = unpack_bf16(v.w);
+        v.x = pack_bf16(a.x * s, a.y * s); v.y = pack_bf16(b.x * s, b.y * s);
+        v.z = pack_bf16(c.x * s, c.y * s); v.w = pack_bf16(dd.x * s, dd.y * s);
+        out[i] = v;
+      }
+    }
+  }
+  // completion: the last CTA to finish raises the data flag on every peer
+  __threadfence_system();
+  __syncthreads();
+  __shared__ unsigned s_last;
+  if (threadIdx.x == 0) s_last = (atomicAdd(done_counter, 1u) == gridDim.x - 1) ? 1u : 0u;
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    if (threadIdx.x < R) {
+      volatile int* f = reinterpret_cast<int*>(flags.buf[threadIdx.x]) + kind * R + rank;
+      *f = epoch;
+    }
+    if (threadIdx.x == 0) *done_counter = 0;   // ready for the next launch on this stream
+  }
+}
+
+// One CTA per local expert: wait for every sender, then zero the rows between the expert's
+// real rows and its 128-aligned end (they take part in reductions over the row range).
+__global__ void __launch_bounds__(256)
+ep_recv_kernel(__nv_bfloat16* __restrict__ buf, const int* __restrict__ hist, const int* __restrict__ expert_offset,
+               const int* __restrict__ flags_kind, int rank, int R, int E, int H, int epoch, int* status) {
+  if (!ep_wait_all(flags_kind, R, epoch, status)) return;
+  const int El = E / R;
+  const int le = blockIdx.x;
+  if (le >= El) return;
+  int tot = 0;
+  for (int s = 0; s < R; ++s) tot += hist[s * E + rank * El + le];
+  const long long r0 = expert_offset[le] + tot, r1 = expert_offset[le + 1];
+  uint4* p = reinterpret_cast<uint4*>(buf + r0 * H);
+  const long long n = (r1 - r0) * (H / 8);
+  for (long long i = threadIdx.x; i < n; i += blockDim.x) p[i] = make_uint4(0u, 0u, 0u, 0u);
+}
+
+__global__ void __launch_bounds__(32)
+ep_signal_kernel(EpPeers flags, int rank, int R, int kind, int epoch) {
+  __threadfence_system();
+  if (threadIdx.x < R) {
+    volatile int* f = reinterpret_cast<int*>(flags.buf[threadIdx.x]) + kind * R + rank;
+    *f = epoch;
+  }
+}
+
+// One CTA per token: out[t] = sum_j w[t, j] * row(owner(t, j), pos[t, j]); w == nullptr -> 1.
+// dw (optional): dw[t, j] = <row(t, j), g[t]>.
+__global__ void __launch_bounds__(256)
+ep_pull_kernel(EpPeers src, const int* __restrict__ topk_idx, const int* __restrict__ pos, const float* __restrict__ w,
+               const __nv_bfloat16* __restrict__ g, __nv_bfloat16* __restrict__ out, float* __restrict__ dw,
+               const int* __restrict__ flags_kind, int T, int k, int H, int El, int R, int epoch, int* status) {
+  if (!ep_wait_all(flags_kind, R, epoch, status)) return;
+  __shared__ float s_red[8];
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    // thread i handles 8 consecutive features (H <= 2048 per pass of 256 threads)
+    for (int c0 = 0; c0 < H; c0 += blockDim.x * 8) {
+      const int c = c0 + threadIdx.x * 8;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int j = 0; j < k; ++j) {
+        const int pr = t * k + j;
+        const int d = topk_idx[pr] / El;
+        const float wj = w ? w[pr] : 1.f;
+        if (c < H) {
+          const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(src.buf[d]) +
+                                                          static_cast<long long>(pos[pr]) * H + c);
+          const float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y), cc = unpack_bf16(v.z), dd = unpack_bf16(v.w);
+          acc[0] += wj * a.x; acc[1] += wj * a.y; acc[2] += wj * b.x; acc[3] += wj * b.y;
+          acc[4] += wj * cc.x; acc[5] += wj * cc.y; acc[6] += wj * dd.x; acc[7] += wj * dd.y;
+        }
+      }
+      if (out && c < H) {
+        uint4 o;
+        o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
+        o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
+        *reinterpret_cast<uint4*>(out + static_cast<long long>(t) * H + c) = o;
+      }
+    }
+    if (dw) {
+      for (int j = 0; j < k; ++j) {
+        const int pr = t * k + j;
+        const int d = topk_idx[pr] / El;
+        float part = 0.f;
+        for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+          const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(src.buf[d]) +
+                                                          static_cast<long long>(pos[pr]) * H + c);
+          const uint4 gv = *reinterpret_cast<const uint4*>(g + static_cast<long long>(t) * H + c);
+          const float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y), cc = unpack_bf16(v.z), dd = unpack_bf16(v.w);
+          const float2 ga = unpack_bf16(gv.x), gb = unpack_bf16(gv.y), gc = unpack_bf16(gv.z), gd = unpack_bf16(gv.w);
+          part += a.x * ga.x + a.y * ga.y + b.x * gb.x + b.y * gb.y + cc.x * gc.x + cc.y * gc.y + dd.x * gd.x +
+                  dd.y * gd.y;
+        }
+        part = warp_sum(part);
+        if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = part;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          float s = 0.f;
+          for (int i = 0; i < (blockDim.x >> 5); ++i) s += s_red[i];
+          dw[pr] = s;
+        }
+        __syncthreads();
+      }
+    }
+  }
+}
+
+}  // namespace prb
+
+// ---------------------------------------------------------------- symmetric memory (CUDA IPC)
+PRB_API int prb_symm_alloc(long long bytes, void** out) {
+  return cudaMalloc(out, static_cast<size_t>(bytes)) == cudaSuccess ? 0 : -1;
+}
+PRB_API int prb_symm_free(void* p) { return cudaFree(p) == cudaSuccess ? 0 : -1; }
+PRB_API int prb_symm_memset(void* p, int v, long long bytes, void* stream) {
+  return cudaMemsetAsync(p, v, static_cast<size_t>(bytes), reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess ? 0 : -1;
+}
+// handle: 64 bytes
+PRB_API int prb_symm_export(void* p, void* handle) {
+  return cudaIpcGetMemHandle(reinterpret_cast<cudaIpcMemHandle_t*>(handle), p) == cudaSuccess ? 0 : -1;
+}
+PRB_API int prb_symm_import(const void* handle, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  return cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess ? 0 : -1;
+}
+PRB_API int prb_symm_unmap(void* p) { return cudaIpcCloseMemHandle(p) == cudaSuccess ? 0 : -1; }
+
+// ---------------------------------------------------------------- launches
+// `peers` arrays hold R device pointers (own pointer at index rank).
+static prb::EpPeers ep_peers(void* const* p, int R) {
+  prb::EpPeers o;
+  for (int i = 0; i < prb::kEpMaxRanks; ++i) o.buf[i] = i < R ? p[i] : nullptr;
+  return o;
+}
+
+PRB_API int prb_ep_hist(const int* counts, void* const* hist_peers, void* const* flag_peers, int rank, int R, int E,
+                        int kind, int epoch, void* stream) {
+  if (R > prb::kEpMaxRanks || E > 1024 || E % R) return -2;
+  prb::ep_hist_kernel<<<1, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(counts, ep_peers(hist_peers, R),
+                                                                           ep_peers(flag_peers, R), rank, R, E, kind, epoch);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+PRB_API int prb_ep_plan(const int* hist, const int* flags, int rank, int R, int E, int kind, int epoch, int cap_rows,
+                        int max_blocks, int* send_base, int* expert_offset, int* block_expert, int* total_rows,
+                        int* status, void* stream) {
+  if (R > prb::kEpMaxRanks || E > 1024 || E % R) return -2;
+  prb::ep_plan_kernel<<<1, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      hist, flags + kind * R, rank, R, E, epoch, cap_rows, max_blocks, send_base, expert_offset, block_expert, total_rows,
+      status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+PRB_API int prb_ep_push(const void* x, const int* topk_idx, const int* slot, const int* local_off,
+                        const int* send_base, const int* pos_in, const float* scale, void* const* dst_peers,
+                        void* const* flag_peers, int* pos_out, unsigned* done_counter, int num_pairs, int k, int H,
+                        int E, int rank, int R, int kind, int epoch, int cap_rows, int* status, void* stream) {
+  if (R > prb::kEpMaxRanks || (H % 8) || E % R) return -2;
+  if (num_pairs <= 0) {
+    prb::ep_signal_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(ep_peers(flag_peers, R), rank, R, kind, epoch);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  }
+  int grid = (num_pairs + 7) / 8;
+  if (grid > 148 * 8) grid = 148 * 8;
+  prb::ep_push_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), topk_idx, slot, local_off, send_base, pos_in, scale,
+      ep_peers(dst_peers, R), ep_peers(flag_peers, R), pos_out, done_counter, num_pairs, k, H, E / R, rank, R, kind, epoch,
+      cap_rows, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+PRB_API int prb_ep_recv(void* buf, const int* hist, const int* expert_offset, const int* flags, int rank, int R, int E,
+                        int H, int kind, int epoch, int* status, void* stream) {
+  prb::ep_recv_kernel<<<E / R, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<__nv_bfloat16*>(buf), hist, expert_offset, flags + kind * R, rank, R, E, H, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+PRB_API int prb_ep_signal(void* const* flag_peers, int rank, int R, int kind, int epoch, void* stream) {
+  prb::ep_signal_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(ep_peers(flag_peers, R), rank, R, kind, epoch);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+PRB_API int prb_ep_pull(void* const* src_peers, const int* topk_idx, const int* pos, const float* w, const void* g,
+                        void* out, float* dw, const int* flags, int T, int k, int H, int E, int R, int kind, int epoch,
+                        int* status, void* stream) {
+  if (R > prb::kEpMaxRanks || (H % 8) || E % R) return -2;
+  if (T <= 0) return 0;
+  int grid = T < 148 * 8 ? T : 148 * 8;
+  prb::ep_pull_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      ep_peers(src_peers, R), topk_idx, pos, w, reinterpret_cast<const __nv_bfloat16*>(g),
+      reinterpret_cast<__nv_bfloat16*>(out), dw, flags + kind * R, T, k, H, E / R, R, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}

@@ -25,6 +25,14 @@ _CUDA_SIGNATURES = {
     "prb_gemm_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, F, F, P, I, I, I, P, P],
     "prb_gemm_bf16_kgrouped": [P, P, P, I, I, L, L, L, L, I, F, F, P, I, P, P],
     "prb_flash_fwd": [P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, F, I, I, P, P],
+    "prb_symm_alloc": [L, P], "prb_symm_free": [P], "prb_symm_memset": [P, I, L, P],
+    "prb_symm_export": [P, P], "prb_symm_import": [P, P], "prb_symm_unmap": [P],
+    "prb_ep_hist": [P, P, P, I, I, I, I, I, P],
+    "prb_ep_plan": [P, P, I, I, I, I, I, I, I, P, P, P, P, P, P],
+    "prb_ep_push": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
+    "prb_ep_recv": [P, P, P, P, I, I, I, I, I, I, P, P],
+    "prb_ep_signal": [P, I, I, I, I, P],
+    "prb_ep_pull": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
     "prb_gemm_bf16_ext": [P, P, P, I, I, I, L, L, L, I, I, I, F, F, P, I, I, I, P, P, I, L, L, I, P, P],
     "prb_flash_bwd": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, L, L, L, F, I, I, P, P],
     "prb_paged_decode": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P],

@@ -1,0 +1,21 @@
+"""Peer-memory expert-parallel dispatcher against the all-to-all baseline on two GPUs
+(child processes, one per GPU; NVLS off, plain peer loads / stores only)."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_p2p_dispatcher_matches_all_to_all():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", EP_SELFTEST_TIMING="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", "29533", "-m", "prime_rl_b200.parallel.ep_selftest"]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and "EP_SELFTEST_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
