@@ -206,6 +206,13 @@ ep_signal_kernel(EpPeers flags, int rank, int R, int kind, int epoch) {
   }
 }
 
+// Waits until every rank's flag of one kind has reached `epoch` (a stream-ordered barrier
+// between kernels that touch peer memory).
+__global__ void __launch_bounds__(32)
+ep_wait_kernel(const int* __restrict__ flags_kind, int R, int epoch, int* status) {
+  ep_wait_all(flags_kind, R, epoch, status);
+}
+
 // One CTA per token: out[t] = sum_j w[t, j] * row(owner(t, j), pos[t, j]); w == nullptr -> 1.
 // dw (optional): dw[t, j] = <row(t, j), g[t]>.
 __global__ void __launch_bounds__(256)
@@ -340,6 +347,11 @@ PRB_API int prb_ep_recv(void* buf, const int* hist, const int* expert_offset, co
 
 PRB_API int prb_ep_signal(void* const* flag_peers, int rank, int R, int kind, int epoch, void* stream) {
   prb::ep_signal_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(ep_peers(flag_peers, R), rank, R, kind, epoch);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+PRB_API int prb_ep_wait(const int* flags, int R, int kind, int epoch, int* status, void* stream) {
+  prb::ep_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(flags + kind * R, R, epoch, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

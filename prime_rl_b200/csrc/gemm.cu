@@ -46,6 +46,9 @@ struct GemmParams {
   // 64, TMA zero-fills A2 past K2
   int k2_blocks = 0;
   int b2_rows_per_expert = 0;
+  // reduce-scatter epilogue: row r of C is added into peer_c[r / rows_per_rank] (fp32, pitch ldc)
+  float* peer_c[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  int rows_per_rank = 0;
   const int* expert_offset;  // K-grouped mode
   int num_experts;
   // fused LM head (logprob / entropy) extras
@@ -250,6 +253,33 @@ struct EpiStore {
           dst[j] = __float2bfloat16(o);
         }
       }
+    }
+  }
+};
+
+// GEMM -> reduce-scatter in one kernel: the fp32 tile leaves TMEM as vector reductions into the
+// row owner's shard (peer memory over NVLink, or this GPU's own shard), so the transfer of a
+// tile overlaps the tensor-core work of the next one and no partial result is materialised.
+// The shards must be zero (or hold the running sum) before any rank starts.
+struct EpiPeerReduce {
+  __device__ EpiPeerReduce(const GemmParams&) {}
+  __device__ void begin_item(const GemmParams&, long long) {}
+  __device__ void end_item(const GemmParams&, long long, int) {}
+  __device__ void chunk(const GemmParams& p, long long row, int col0, uint32_t (&v)[32]) {
+    if (row >= p.rows_total || col0 >= p.N) return;
+    const int owner = static_cast<int>(row / p.rows_per_rank);
+    float* dst = p.peer_c[owner] + (row - static_cast<long long>(owner) * p.rows_per_rank) * p.ldc + col0;
+    if (col0 + 32 <= p.N && (p.ldc % 4 == 0)) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * j),
+                     "f"(p.alpha * __uint_as_float(v[4 * j + 0])), "f"(p.alpha * __uint_as_float(v[4 * j + 1])),
+                     "f"(p.alpha * __uint_as_float(v[4 * j + 2])), "f"(p.alpha * __uint_as_float(v[4 * j + 3]))
+                     : "memory");
+    } else {
+      for (int j = 0; j < 32 && col0 + j < p.N; ++j)
+        asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(dst + j), "f"(p.alpha * __uint_as_float(v[j]))
+                     : "memory");
     }
   }
 };
@@ -661,6 +691,71 @@ PRB_API int prb_gemm_bf16_ext(const void* A, const void* B, void* C, int M, int 
                               int b2_rows_per_expert, int* status, void* stream_) {
   return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_fp32, alpha, beta, block_expert, num_experts,
                         b_rows_per_expert, force_bn, A2, B2, K2, lda2, ldb2, b2_rows_per_expert, status, stream_);
+}
+
+// C_shard[owner(row)] += alpha * (A B)[row] with fp32 reductions into the owners' shards
+// (peer_c: R device pointers, own shard at index rank; rows_per_rank rows of pitch ldc each).
+// Dense operands only; B K-major [N, K] or MN-major [K, N]; A K-major [M, K] or MN-major [K, M].
+PRB_API int prb_gemm_bf16_reduce_scatter(const void* A, const void* B, int M, int N, int K, long long lda,
+                                         long long ldb, int a_mn, int b_mn, float alpha, void* const* peer_c,
+                                         int num_ranks, int rows_per_rank, long long ldc, int* status,
+                                         void* stream_) {
+  using namespace prb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || num_ranks < 1 || num_ranks > 8 || rows_per_rank <= 0 ||
+      static_cast<long long>(rows_per_rank) * num_ranks < M)
+    return -3;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+    return -4;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!a_mn)
+    rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda, kBM, kBK,
+                      true);
+  else
+    rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda, kBK, 64,
+                      true);
+  if (rc) return rc;
+  if (!b_mn)
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 256, kBK,
+                      true);
+  else
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, kBK, 64,
+                      true);
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.rows_total = M;
+  p.C = nullptr; p.ldc = ldc; p.out_fp32 = 1;
+  p.expert_offset = nullptr; p.num_experts = 0;
+  p.alpha = alpha; p.beta = 0.f;
+  p.block_expert = nullptr; p.b_rows_per_expert = 0;
+  p.status = status;
+  p.num_splits = 0;
+  p.labels = nullptr; p.inv_temp = nullptr; p.part_m = p.part_s = p.part_t = p.target_logit = nullptr;
+  p.grad_logprob = nullptr; p.lse = nullptr;
+  for (int i = 0; i < num_ranks; ++i) p.peer_c[i] = reinterpret_cast<float*>(peer_c[i]);
+  p.rows_per_rank = rows_per_rank;
+  using Cfg = GemmCfg<256>;
+  const int tiles = ((M + kBM - 1) / kBM) * ((N + 255) / 256);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+#define PRB_RS_LAUNCH(AMN, BMN)                                                                              \
+  {                                                                                                          \
+    auto kern = gemm_bf16_kernel<256, AMN, BMN, SchedDense, EpiPeerReduce>;                                  \
+    static bool configured = false;                                                                          \
+    if (!configured) {                                                                                       \
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) \
+        return -10;                                                                                          \
+      configured = true;                                                                                     \
+    }                                                                                                        \
+    kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmA, tmB, p);                            \
+  }
+  if (!a_mn && !b_mn) PRB_RS_LAUNCH(false, false)
+  else if (!a_mn && b_mn) PRB_RS_LAUNCH(false, true)
+  else if (a_mn && b_mn) PRB_RS_LAUNCH(true, true)
+  else PRB_RS_LAUNCH(true, false)
+#undef PRB_RS_LAUNCH
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
 // ---------------------------------------------------------------- fused LM head
