@@ -36,6 +36,7 @@ class ModelRunner:
         self.fp32_lm_head = fp32_lm_head
         self.capture_routed = False
         self.last_routed: torch.Tensor | None = None   # [N, moe_layers, k] of the last step
+        self._decode_meta = None                        # (block tables, context lengths) of a pure decode step
 
     # ------------------------------------------------------------------ attention over pages
     def _attend(self, layer: int, q, k_new, v_new, batch: list[StepInput], starts: list[int], window, sinks):
@@ -46,11 +47,11 @@ class ModelRunner:
             cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
             cu[1:] = torch.tensor(lens, dtype=torch.int32).cumsum(0)
             return attn_ops.attention(q, k_new, v_new, cu.to(q.device), max(lens), causal=True, window=window)
-        if q.is_cuda and all(len(s.tokens) == 1 for s in batch) and sinks is None and window is None:
+        if self._decode_meta is not None and sinks is None and window is None:
             from ..ops import paged
 
-            if paged.available():
-                return paged.paged_decode(q, self.cache, layer, batch)
+            bt, ctx = self._decode_meta
+            return paged.paged_decode_raw(q.contiguous(), self.cache.k[layer], self.cache.v[layer], bt, ctx)
         outs = []
         scale = 1.0 / math.sqrt(q.shape[-1])
         rep = q.shape[1] // k_new.shape[1]
@@ -96,6 +97,17 @@ class ModelRunner:
         pos_t = torch.tensor(pos, dtype=torch.int32, device=dev)
         slots_t = torch.tensor(slots, dtype=torch.long, device=dev)
         seq = SeqInfo(None, 0, pos_t)
+        # a pure decode step on the GPU: one block table / length vector for all layers
+        self._decode_meta = None
+        if dev.type == "cuda" and all(len(s.tokens) == 1 for s in batch):
+            from ..ops import paged
+
+            if paged.available() and self.arch.head_dim == 128:
+                max_blocks = max(len(s.kv.pages) for s in batch)
+                bt = torch.tensor([s.kv.pages + [0] * (max_blocks - len(s.kv.pages)) for s in batch],
+                                  dtype=torch.int32)
+                ctx = torch.tensor([s.kv.length + 1 for s in batch], dtype=torch.int32)
+                self._decode_meta = (bt.to(dev, non_blocking=True), ctx.to(dev, non_blocking=True))
         h = model.model.embed_tokens(ids_t)
         N = h.shape[0]
         routed = []
@@ -128,10 +140,17 @@ class ModelRunner:
         rows, offsets = [], []
         for s, st in zip(batch, starts):
             n = len(s.tokens)
-            offsets.append(sum(r.numel() for r in rows))
-            rows.append(torch.arange(st, st + n, device=dev) if s.want_all_logits
-                        else torch.tensor([st + n - 1], device=dev))
-        sel = h[torch.cat(rows)]
+            offsets.append(len(rows))
+            if s.want_all_logits:
+                rows.extend(range(st, st + n))
+            else:
+                rows.append(st + n - 1)
+        sel = h[torch.tensor(rows, dtype=torch.long, device=dev)]
         w = model.output_weight
-        logits = sel.float() @ w.float().t() if self.fp32_lm_head else ops.linear(sel, w).float()
+        if sel.is_cuda and sel.dtype == torch.bfloat16:
+            # bf16 operands, fp32 accumulation and fp32 logits (no fp32 copy of the embedding matrix)
+            logits = ops.gemm(sel.contiguous(), w, out_dtype=torch.float32)
+        else:
+            logits = sel.float() @ w.float().t() if self.fp32_lm_head else ops.linear(sel, w).float()
+        self._decode_meta = None
         return logits, offsets

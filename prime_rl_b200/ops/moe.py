@@ -42,6 +42,19 @@ def route_topk(logits: torch.Tensor, k: int, *, score_func: str = "softmax", nor
                forced: torch.Tensor | None = None):
     """Returns (topk_idx [T,k] int32, topk_w [T,k] fp32 differentiable w.r.t. logits, counts [E])."""
     T, E = logits.shape
+    if logits.is_cuda and logits.dtype == torch.float32 and E <= 1024:
+        # selection, weights and histogram in one kernel (no host synchronisation, unlike
+        # bincount); when gradients are needed the weights are rebuilt differentiably from the
+        # kernel's choice
+        idx32, w_nd, counts, _ = router_topk_cuda(logits.detach().contiguous(), k, score_func=score_func,
+                                                  norm_topk=norm_topk, route_scale=route_scale, sel_bias=sel_bias,
+                                                  forced=None if forced is None else forced.to(torch.int32).contiguous())
+        if not (torch.is_grad_enabled() and logits.requires_grad):
+            return idx32, w_nd, counts
+        w = router_scores_ref(logits, score_func).gather(1, idx32.long())
+        if norm_topk:
+            w = w / (w.sum(-1, keepdim=True) + 1e-20)
+        return idx32, w * route_scale, counts
     scores = router_scores_ref(logits, score_func)
     if forced is not None:
         idx = forced.long()
