@@ -123,6 +123,10 @@ def load_environment(cfg) -> Environment:
         env = factory(**cfg.args)
         env.name = cfg.resolved_name
         return env
+    if cfg.id == "remote":
+        from .env_server import RemoteEnvironment
+
+        return RemoteEnvironment(name=cfg.name, **cfg.args)       # args: base_url = "http://host:port"
     if cfg.id not in REGISTRY:
         raise KeyError(f"unknown environment '{cfg.id}'; built-ins: {sorted(REGISTRY)}")
     return REGISTRY[cfg.id](name=cfg.resolved_name, **cfg.args)
