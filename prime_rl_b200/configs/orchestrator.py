@@ -178,6 +178,8 @@ class NIXLWeightBroadcastConfig(InMemoryWeightBroadcastConfig):
 
 class P2PWeightBroadcastConfig(InMemoryWeightBroadcastConfig):
     type: Literal["p2p"] = "p2p"
+    port: int = 0
+    quantize: Literal["fp8"] | None = None      # quantise 2-D weights to block-scaled fp8 in flight
     port: int = 29502
     quantize_in_weight_transfer: bool = True
 

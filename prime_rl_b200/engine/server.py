@@ -160,6 +160,13 @@ def build_app(engine: Engine, model_name: str, tokenizer=None, liveness_timeout:
     @app.post("/init_broadcaster")
     async def init_broadcaster(body: dict):
         nonlocal weight_receiver
+        if body.get("type") == "p2p":
+            # the trainer writes into this process's parameter storage over NVLink peer memory
+            from ..transports.weights.p2p import P2PWeightPort
+
+            weight_receiver = await asyncio.to_thread(P2PWeightPort, engine.model, Path(body["run_dir"]),
+                                                      int(body.get("rank_offset", 0)), body.get("quantize"))
+            return {"status": "ok"}
         from ..transports.weights.nccl import NCCLWeightReceiver
 
         weight_receiver = NCCLWeightReceiver(host=body["host"], port=int(body["port"]),

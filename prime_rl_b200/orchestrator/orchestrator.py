@@ -274,6 +274,14 @@ class Orchestrator:
         self.dispatcher = Dispatcher(self.sources, self.client, self.policy, self.controller, seed=c.seed,
                                      tasks_per_minute=c.tasks_per_minute)
         self.sink = TrainSink(c, self.policy)
+        wb = c.weight_broadcast
+        if wb.type == "p2p":
+            # every engine publishes the IPC handles of its parameter storage under the run directory
+            await self.admin.init_broadcaster(type="p2p", run_dir=str(self.run_dir),
+                                              quantize=getattr(wb, "quantize", None))
+        elif wb.type == "nccl":
+            await self.admin.init_broadcaster(type="nccl", host=wb.host, port=wb.port,
+                                              inference_world_size=wb.inference_world_size, timeout=wb.timeout)
         self.receiver = WeightReceiver(c.weight_broadcast, self.run_dir, self.admin)
         self.watcher = WeightWatcher(self.receiver, self.policy, self.dispatcher)
         self._maybe_resume()

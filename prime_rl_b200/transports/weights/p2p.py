@@ -1,0 +1,190 @@
+"""Peer-memory weight transport: the trainer writes new parameter values straight into the
+engine's parameter storage over NVLink (``csrc/weight_push.cu``), optionally quantising to
+block-scaled fp8 on the way.
+
+Engine side (``P2PWeightPort``): once, export every parameter's storage with CUDA IPC and write
+``<run_dir>/broadcasts/p2p_manifest_<replica>.json`` (name -> handle, byte offset, shape,
+dtype; for ``quantize = "fp8"`` also the handles of the e4m3 payload and fp32 scale buffers the
+port allocates). Parameters never move afterwards, so the manifest stays valid for the run.
+
+Trainer side (``P2PWeightSender``): after the usual marker-file handshake (the engine is paused
+once ``.receiver_ready`` exists) map the handles (cached), launch one push kernel per tensor,
+synchronise, and let the base class touch ``.finished``. With several engine replicas trainer
+rank r serves replicas r, r + world, ...; parameters are replicated on the trainer, so no
+gather is needed.
+
+Same role as the reference's NCCL / NIXL transports (src/prime_rl/transports/weights/nccl.py,
+nixl.py) for engines on the same NVSwitch box as the trainer.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import json
+import time
+from pathlib import Path
+
+import torch
+
+from ...ops import _runtime as rt
+from ...utils.logger import get_logger
+from ...utils.pathing import get_broadcast_dir
+from . import FINISHED, WeightSender
+
+_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16}
+
+
+def manifest_path(run_dir: Path, replica: int) -> Path:
+    return get_broadcast_dir(run_dir) / f"p2p_manifest_{replica}.json"
+
+
+def _export(t: torch.Tensor) -> dict:
+    handle = (ctypes.c_ubyte * 64)()
+    off = ctypes.c_longlong()
+    rc = rt.lib().prb_ipc_export_range(t.data_ptr(), handle, ctypes.byref(off))
+    if rc != 0:
+        raise RuntimeError(f"cannot export device memory over IPC (code {rc})")
+    return {"handle": bytes(handle).hex(), "offset": off.value}
+
+
+class P2PWeightPort:
+    """Engine side. ``quantize``: ``None`` (values land in the live bf16 parameters) or ``"fp8"``
+    (2-D weights land as e4m3 + 128 x 128 scales in buffers owned by the port, other tensors as
+    they are; ``dequantize_into_model`` refreshes the live parameters from them)."""
+
+    def __init__(self, model, run_dir: Path, replica: int = 0, quantize: str | None = None):
+        self.model, self.run_dir, self.replica, self.quantize = model, Path(run_dir), replica, quantize
+        self.params = dict(model.named_parameters())
+        dev = next(model.parameters()).device
+        rt.stream_ptr(dev)
+        self.fp8: dict[str, tuple[torch.Tensor, torch.Tensor]] = {}
+        entries = {}
+        for name, p in self.params.items():
+            assert p.is_contiguous(), name
+            e = {"shape": list(p.shape), "dtype": str(p.dtype).replace("torch.", ""), **_export(p.data)}
+            if quantize == "fp8" and p.dim() >= 2 and p.shape[-1] % 2 == 0 and p.dtype == torch.bfloat16:
+                K = p.shape[-1]
+                N = p.numel() // K
+                q = torch.empty(N, K, dtype=torch.uint8, device=dev)
+                s = torch.empty((N + 127) // 128, (K + 127) // 128, dtype=torch.float32, device=dev)
+                self.fp8[name] = (q, s)
+                e["fp8"] = {"q": _export(q), "scales": _export(s), "rows": N, "cols": K}
+            entries[name] = e
+        self.manifest = {"device": dev.index or 0, "quantize": quantize, "params": entries}
+        path = manifest_path(self.run_dir, replica)
+        path.parent.mkdir(parents=True, exist_ok=True)
+        tmp = path.with_suffix(".tmp")
+        tmp.write_text(json.dumps(self.manifest))
+        tmp.replace(path)
+
+    def wait_finished(self, step_dir: Path, timeout: float = 1200.0) -> None:
+        t0 = time.monotonic()
+        while not (Path(step_dir) / FINISHED).exists():
+            if time.monotonic() - t0 > timeout:
+                raise TimeoutError(f"weight push into {step_dir} did not finish after {timeout}s")
+            time.sleep(0.01)
+        torch.cuda.synchronize()
+
+    def dequantize_into_model(self) -> None:
+        """fp8 mode: live bf16 parameter = e4m3 payload x block scale."""
+        for name, (q, s) in self.fp8.items():
+            p = self.params[name]
+            N, K = q.shape
+            w = q.view(torch.float8_e4m3fn).float()
+            sc = s.repeat_interleave(128, 0)[:N].repeat_interleave(128, 1)[:, :K]
+            p.data.copy_((w * sc).view(p.shape))
+
+    def receive_into(self, engine, step_dir: Path | None = None) -> None:
+        """Called while the engine is paused; returns when the trainer's kernels are done."""
+        if step_dir is None:
+            steps = sorted((d for d in get_broadcast_dir(self.run_dir).glob("step_*")),
+                           key=lambda d: int(d.name[5:]))
+            step_dir = steps[-1]
+        self.wait_finished(step_dir)
+        if self.quantize == "fp8":
+            self.dequantize_into_model()
+        engine.cache.blocks.clear_prefix_cache()
+        engine.policy_version += 1
+
+
+class _Mapped:
+    """IPC mappings of one process, keyed by handle bytes (a block is mapped once)."""
+
+    def __init__(self):
+        self.base: dict[str, int] = {}
+
+    def ptr(self, entry: dict) -> int:
+        h = entry["handle"]
+        if h not in self.base:
+            buf = (ctypes.c_ubyte * 64).from_buffer_copy(bytes.fromhex(h))
+            out = ctypes.c_void_p()
+            if rt.lib().prb_symm_import(buf, ctypes.byref(out)) != 0:
+                raise RuntimeError("cudaIpcOpenMemHandle failed (engine and trainer GPUs need peer access)")
+            self.base[h] = out.value
+        return self.base[h] + entry["offset"]
+
+    def close(self):
+        for p in self.base.values():
+            rt.lib().prb_symm_unmap(p)
+        self.base = {}
+
+
+def push_state(named_tensors: dict[str, torch.Tensor], manifest: dict, mapped: _Mapped) -> int:
+    """Launches the push kernels on the current stream; returns the bytes written to the peer."""
+    lib = rt.lib()
+    total = 0
+    for name, e in manifest["params"].items():
+        t = named_tensors.get(name)
+        if t is None:
+            continue
+        t = t.detach()
+        if list(t.shape) != e["shape"]:
+            raise ValueError(f"{name}: trainer shape {list(t.shape)} != engine shape {e['shape']}")
+        dev = t.device
+        stream = rt.stream_ptr(dev)
+        if "fp8" in e and manifest.get("quantize") == "fp8" and t.dtype == torch.bfloat16:
+            f = e["fp8"]
+            t2 = t.reshape(f["rows"], f["cols"])
+            t2 = t2 if t2.is_contiguous() else t2.contiguous()
+            rt.check(lib.prb_weight_push_fp8(t2.data_ptr(), t2.stride(0), mapped.ptr(f["q"]), mapped.ptr(f["scales"]),
+                                             f["rows"], f["cols"], stream), "prb_weight_push_fp8")
+            total += f["rows"] * f["cols"] + 4 * ((f["rows"] + 127) // 128) * ((f["cols"] + 127) // 128)
+        else:
+            src = t.to(_DTYPES[e["dtype"]]) if str(t.dtype).replace("torch.", "") != e["dtype"] else t
+            src = src if src.is_contiguous() else src.contiguous()
+            nbytes = src.numel() * src.element_size()
+            rt.check(lib.prb_weight_push(src.data_ptr(), mapped.ptr(e), nbytes, stream), "prb_weight_push")
+            total += nbytes
+    return total
+
+
+class P2PWeightSender(WeightSender):
+    def __init__(self, config, run_dir: Path, world):
+        super().__init__(config, run_dir, world, require_ack=True)
+        self.run_dir = Path(run_dir)
+        self.mapped = _Mapped()
+        self.manifests: dict[int, dict] = {}
+        self.num_replicas = int(getattr(config, "inference_world_size", 1) or 1)
+
+    def _manifest(self, replica: int) -> dict:
+        if replica not in self.manifests:
+            path = manifest_path(self.run_dir, replica)
+            t0 = time.monotonic()
+            while not path.exists():
+                if time.monotonic() - t0 > self.config.timeout:
+                    raise TimeoutError(f"engine replica {replica} never published {path}")
+                time.sleep(0.05)
+            self.manifests[replica] = json.loads(path.read_text())
+        return self.manifests[replica]
+
+    def _broadcast(self, model, step: int, d: Path) -> None:
+        tensors = dict(model.named_parameters())
+        pushed = 0
+        t0 = time.monotonic()
+        for replica in range(self.world.rank, self.num_replicas, max(1, self.world.world_size)):
+            pushed += push_state(tensors, self._manifest(replica), self.mapped)
+        torch.cuda.synchronize()
+        if pushed:
+            dt = time.monotonic() - t0
+            get_logger().info(f"weight push step {step}: {pushed / 2**30:.2f} GiB in {dt * 1e3:.1f} ms "
+                              f"({pushed / dt / 1e9:.0f} GB/s)")

@@ -29,3 +29,13 @@ def test_gemm_reduce_scatter_over_peer_memory():
            "127.0.0.1", "--master-port", "29534", "-m", "prime_rl_b200.parallel.fused_collectives"]
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0 and "FUSED_RS_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
+
+
+def test_weight_push_over_peer_memory():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", P2P_SELFTEST_TIMING="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", "29535", "-m", "prime_rl_b200.transports.weights.p2p_selftest"]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and "P2P_WEIGHTS_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
