@@ -178,10 +178,13 @@ class NIXLWeightBroadcastConfig(InMemoryWeightBroadcastConfig):
 
 class P2PWeightBroadcastConfig(InMemoryWeightBroadcastConfig):
     type: Literal["p2p"] = "p2p"
-    port: int = 0
-    quantize: Literal["fp8"] | None = None      # quantise 2-D weights to block-scaled fp8 in flight
     port: int = 29502
-    quantize_in_weight_transfer: bool = True
+    quantize_in_weight_transfer: bool = False
+
+    @property
+    def quantize(self) -> str | None:
+        """"fp8": 2-D weights are quantised to block-scaled fp8 in flight."""
+        return "fp8" if self.quantize_in_weight_transfer else None
 
 
 WeightBroadcastConfig: TypeAlias = Annotated[
