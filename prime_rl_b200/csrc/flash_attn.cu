@@ -42,7 +42,8 @@ constexpr int kFaSmem = 2 * kQBytes + kFaKStages * kKBytes + kFaVStages * kVByte
 struct FaParams {
   const int* cu_seqlens;  // [num_docs + 1]
   int num_docs;
-  int total_q;            // T
+  int total_q;            // T (rows of K / V)
+  int q_off, q_rows;      // the query / output tensors hold global rows [q_off, q_off + q_rows) only
   int heads_q, heads_kv;
   __nv_bfloat16* out;     // [T, heads_q, D]
   long long ld_out;       // elements per token
@@ -109,16 +110,21 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int doc_start = s_work[0];
   const int doc_len = s_work[1];
   const int row0 = s_work[2];
+  // context parallelism: this rank holds only a slice of the query rows (keys are complete)
+  const int g0 = doc_start + row0;                       // first global row of this CTA
+  if (g0 + 2 * kFaBM <= p.q_off || g0 >= p.q_off + p.q_rows) return;
 
   // rows [q0, q1) of the document for each tile and the 128-key blocks [blk0, nblk) they need
   const int q0_0 = row0, q0_1 = row0 + kFaBM;
-  const int q1_0 = min(q0_0 + kFaBM, doc_len), q1_1 = min(q0_1 + kFaBM, doc_len);
+  const bool out_0 = (g0 + kFaBM <= p.q_off) || (g0 >= p.q_off + p.q_rows);               // tile 0 not held here
+  const bool out_1 = (g0 + 2 * kFaBM <= p.q_off) || (g0 + kFaBM >= p.q_off + p.q_rows);
+  const int q1_0 = out_0 ? q0_0 : min(q0_0 + kFaBM, doc_len), q1_1 = out_1 ? q0_1 : min(q0_1 + kFaBM, doc_len);
   const int nblk_0 = (q1_0 > q0_0) ? (q1_0 + kFaBN - 1) / kFaBN : 0;
   const int nblk_1 = (q1_1 > q0_1) ? (q1_1 + kFaBN - 1) / kFaBN : 0;
   const int blk0_0 = (p.window > 0 && nblk_0 > 0) ? max(0, q0_0 - p.window + 1) / kFaBN : 0;
   const int blk0_1 = (p.window > 0 && nblk_1 > 0) ? max(0, q0_1 - p.window + 1) / kFaBN : 0;
   // union of the two ranges: the K / V stream of this CTA (tile 0 always has rows)
-  const int j_begin = (nblk_1 > 0) ? min(blk0_0, blk0_1) : blk0_0;
+  const int j_begin = (nblk_1 > 0) ? (nblk_0 > 0 ? min(blk0_0, blk0_1) : blk0_1) : blk0_0;
   const int j_end = max(nblk_0, nblk_1);
 
   if (threadIdx.x == 0) {
@@ -154,7 +160,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int s = 0; s < 2; ++s)
           tma_load_2d(q_s + t * kQBytes + s * (kQBytes / 2), &tmQ, q_full, head * kFaD + s * 64,
-                      doc_start + row0 + t * kFaBM);
+                      g0 + t * kFaBM - p.q_off);   // rows outside the held slice are zero-filled
       int ks = 0, vs = 0;
       uint32_t kph = 0, vph = 0;
       bool ok = true;
@@ -252,7 +258,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int my_q0 = t ? q0_1 : q0_0, my_q1 = t ? q1_1 : q1_0;
     const int my_blk0 = t ? blk0_1 : blk0_0, my_nblk = t ? nblk_1 : nblk_0;
     const int row = my_q0 + r;              // row in document
-    const bool row_ok = row < my_q1;
+    const int grow = doc_start + row - p.q_off;          // row inside the held slice
+    const bool row_ok = row < my_q1 && grow >= 0 && grow < p.q_rows;
     const uint32_t lane_off = static_cast<uint32_t>(qtr * 32) << 16;
     const uint32_t s_tm = tmem_base + t * 256 + lane_off;
     const uint32_t o_tm = s_tm + 128;
@@ -359,7 +366,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (ok) {
         tc_fence_after();
         const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
-        __nv_bfloat16* dst = p.out + static_cast<long long>(doc_start + row) * p.ld_out +
+        __nv_bfloat16* dst = p.out + static_cast<long long>(grow) * p.ld_out +
                              static_cast<long long>(head) * kFaD;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -379,7 +386,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
         if (row_ok)
-          p.lse[static_cast<long long>(head) * p.total_q + doc_start + row] =
+          p.lse[static_cast<long long>(head) * p.q_rows + grow] =
               (m + log2f(l)) * 0.6931471805599453f;
       }
     }
@@ -397,17 +404,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 // ld_k / ld_v; views into a packed qkv projection are fine), out: bf16 [T, heads_q, 128],
 // lse: fp32 [heads_q, T] (natural log). max_pairs bounds the number of 256-row tile pairs:
 // sum over documents of ceil(len / 256).
-PRB_API int prb_flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_seqlens,
-                          int num_docs, int total_q, int heads_q, int heads_kv, int head_dim, long long ld_q,
-                          long long ld_k, long long ld_v, long long ld_out, float scale, int window, int max_pairs,
-                          int* status, void* stream_) {
+// Context-parallel form: q / out / lse hold only the global rows [q_off, q_off + q_rows) (lse is
+// [heads_q, q_rows]); k / v and cu_seqlens describe the complete sequence of total_q tokens.
+PRB_API int prb_flash_fwd_slice(const void* q, const void* k, const void* v, void* out, float* lse,
+                                const int* cu_seqlens, int num_docs, int total_q, int q_off, int q_rows, int heads_q,
+                                int heads_kv, int head_dim, long long ld_q, long long ld_k, long long ld_v,
+                                long long ld_out, float scale, int window, int max_pairs, int* status, void* stream_) {
   using namespace prb;
+  if (q_off < 0 || q_rows <= 0 || q_off + q_rows > total_q) return -3;
   if (head_dim != kFaD || heads_q % heads_kv) return -2;
   if (total_q <= 0 || num_docs <= 0) return 0;
   if ((ld_q % 8) || (ld_k % 8) || (ld_v % 8) || (ld_out % 8)) return -4;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   CUtensorMap tmQ, tmK, tmV;
-  int rc = make_tmap_2d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_q, (uint64_t)heads_q * kFaD,
+  int rc = make_tmap_2d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)q_rows, (uint64_t)heads_q * kFaD,
                         (uint64_t)ld_q, kFaBM, 64, true);
   if (rc) return rc;
   rc = make_tmap_2d(&tmK, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_q, (uint64_t)heads_kv * kFaD,
@@ -418,6 +428,7 @@ PRB_API int prb_flash_fwd(const void* q, const void* k, const void* v, void* out
   if (rc) return rc;
   FaParams p;
   p.cu_seqlens = cu_seqlens; p.num_docs = num_docs; p.total_q = total_q;
+  p.q_off = q_off; p.q_rows = q_rows;
   p.heads_q = heads_q; p.heads_kv = heads_kv;
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.ld_out = ld_out; p.lse = lse;
   p.scale_log2 = scale * 1.4426950408889634f;
@@ -431,4 +442,12 @@ PRB_API int prb_flash_fwd(const void* q, const void* k, const void* v, void* out
   dim3 grid(max_pairs, heads_q);
   flash_fwd_kernel<<<grid, kFaThreads, kFaSmem, stream>>>(tmQ, tmK, tmV, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+PRB_API int prb_flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_seqlens,
+                          int num_docs, int total_q, int heads_q, int heads_kv, int head_dim, long long ld_q,
+                          long long ld_k, long long ld_v, long long ld_out, float scale, int window, int max_pairs,
+                          int* status, void* stream_) {
+  return prb_flash_fwd_slice(q, k, v, out, lse, cu_seqlens, num_docs, total_q, 0, total_q, heads_q, heads_kv, head_dim,
+                             ld_q, ld_k, ld_v, ld_out, scale, window, max_pairs, status, stream_);
 }

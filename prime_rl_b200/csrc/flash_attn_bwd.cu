@@ -36,6 +36,7 @@ constexpr int kBwSmem = 7 * kBwTile + 1024 + 512;
 struct FaBwdParams {
   const int* cu_seqlens;
   int num_docs, total_q, heads_q, heads_kv;
+  int q_off, q_rows;       // q / dO / lse / delta / dq hold the global rows [q_off, q_off + q_rows) only
   const float* lse;        // [heads_q, T] natural log
   const float* delta;      // [heads_q, T] rowsum(dO * O)
   __nv_bfloat16* dq;       // [T, heads_q, D] contiguous
@@ -175,11 +176,26 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   __syncthreads();
   if (!s_work[3]) return;
   const int doc_start = s_work[0], doc_len = s_work[1], kv0 = s_work[2];
-  const int i_begin = kv0 / kBwB;
+  int i_begin = kv0 / kBwB;
   int i_end = (doc_len + kBwB - 1) / kBwB;
   if (p.window > 0) i_end = min(i_end, (kv0 + kBwB - 1 + p.window - 1) / kBwB + 1);
+  // context parallelism: only the query blocks that intersect the held row slice
+  if (p.q_off > doc_start) i_begin = max(i_begin, (p.q_off - doc_start) / kBwB);
+  i_end = min(i_end, (p.q_off + p.q_rows - doc_start + kBwB - 1) / kBwB);
   const int iters_per_head = i_end - i_begin;
-  const int num_iters = iters_per_head * group;   // >= 1: the diagonal block always exists
+  const int num_iters = iters_per_head * group;
+  if (iters_per_head <= 0) {
+    // no query of this rank sees these keys: their gradient contribution is zero
+    for (int idx = threadIdx.x; idx < kBwB * (kBwD / 8); idx += blockDim.x) {
+      const int key = kv0 + idx / (kBwD / 8), c = (idx % (kBwD / 8)) * 8;
+      if (key < doc_len) {
+        const long long tok = doc_start + key;
+        *reinterpret_cast<uint4*>(p.dk + tok * p.ld_dk + static_cast<long long>(kv_head) * kBwD + c) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(p.dv + tok * p.ld_dv + static_cast<long long>(kv_head) * kBwD + c) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    return;
+  }
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -221,10 +237,10 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const int head = kv_head * group + g;
         if (!mbar_wait(&q_empty[st], ((n >> 1) & 1) ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
         mbar_expect_tx(&q_full[st], kBwTile);
-        bw_load_tile(q_s + st * kBwTile, &tmQ, &q_full[st], head * kBwD, doc_start + i * kBwB);
+        bw_load_tile(q_s + st * kBwTile, &tmQ, &q_full[st], head * kBwD, doc_start + i * kBwB - p.q_off);
         if (!mbar_wait(do_empty, (n & 1) ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
         mbar_expect_tx(do_full, kBwTile);
-        bw_load_tile(do_s, &tmDO, do_full, head * kBwD, doc_start + i * kBwB);
+        bw_load_tile(do_s, &tmDO, do_full, head * kBwD, doc_start + i * kBwB - p.q_off);
       }
       if (!ok) __nanosleep(200000);
     }
@@ -286,8 +302,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       const int i = i_begin + (n - g * iters_per_head);
       const int head = kv_head * group + g;
       const int row = i * kBwB + r;                       // row in document
-      const bool row_ok = row < doc_len;
-      const long long stat_idx = static_cast<long long>(head) * p.total_q + doc_start + row;
+      const int grow = doc_start + row - p.q_off;         // row inside the held slice
+      const bool row_ok = row < doc_len && grow >= 0 && grow < p.q_rows;
+      const long long stat_idx = static_cast<long long>(head) * p.q_rows + grow;
       const float neg_lse2 = row_ok ? -p.lse[stat_idx] * 1.4426950408889634f : 0.f;
       const float neg_delta = row_ok ? -p.delta[stat_idx] : 0.f;
       const int lim_hi = row_ok ? row - col0 : -1;
@@ -422,6 +439,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __syncthreads();
   if (!s_work[3]) return;
   const int doc_start = s_work[0], doc_len = s_work[1], q0 = s_work[2];
+  if (doc_start + q0 + kBwB <= p.q_off || doc_start + q0 >= p.q_off + p.q_rows) return;   // rows not held here
   const int j_begin = (p.window > 0) ? max(0, q0 - p.window + 1) / kBwB : 0;
   const int num_iters = q0 / kBwB + 1 - j_begin;     // up to and including the diagonal block
 
@@ -452,8 +470,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       mbar_expect_tx(qdo_full, 2 * kBwTile);
-      bw_load_tile(q_s, &tmQ, qdo_full, head * kBwD, doc_start + q0);
-      bw_load_tile(do_s, &tmDO, qdo_full, head * kBwD, doc_start + q0);
+      bw_load_tile(q_s, &tmQ, qdo_full, head * kBwD, doc_start + q0 - p.q_off);
+      bw_load_tile(do_s, &tmDO, qdo_full, head * kBwD, doc_start + q0 - p.q_off);
       bool ok = true;
       int ks = 0;
       uint32_t kph = 0;
@@ -521,8 +539,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t lane_off = static_cast<uint32_t>(qtr * 32) << 16;
     uint8_t* ds_row = ds_s + w * (kBwTile / 2) + r * 128;
     const int row = q0 + r;
-    const bool row_ok = row < doc_len;
-    const long long stat_idx = static_cast<long long>(head) * p.total_q + doc_start + row;
+    const int grow = doc_start + row - p.q_off;           // row inside the held slice
+    const bool row_ok = row < doc_len && grow >= 0 && grow < p.q_rows;
+    const long long stat_idx = static_cast<long long>(head) * p.q_rows + grow;
     const float neg_lse2 = row_ok ? -p.lse[stat_idx] * 1.4426950408889634f : 0.f;
     const float neg_delta = row_ok ? -p.delta[stat_idx] : 0.f;
     bool ok = true;
@@ -566,7 +585,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     if (ok) {
       tc_fence_after();
-      __nv_bfloat16* dst = p.dq + (static_cast<long long>(doc_start + row) * p.heads_q + head) * kBwD + 64 * w;
+      __nv_bfloat16* dst = p.dq + (static_cast<long long>(grow) * p.heads_q + head) * kBwD + 64 * w;
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
         uint32_t gv[32];
@@ -614,24 +633,26 @@ flash_bwd_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16*
 // q, k, v as in prb_flash_fwd; o / d_o: bf16 [T, heads_q, 128] (pitches ld_o / ld_do); lse: fp32
 // [heads_q, T]. Scratch supplied by the caller: delta fp32 [heads_q, T]. Outputs dq (contiguous
 // [T, heads_q, 128]), dk, dv (pitches ld_dk / ld_dv). max_blocks = sum over documents of
-// ceil(len / 128). dq_acc is unused (kept in the signature for existing callers; may be null).
-PRB_API int prb_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
-                          const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv,
-                          const int* cu_seqlens, int num_docs, int total_q, int heads_q, int heads_kv, int head_dim,
-                          long long ld_q, long long ld_k, long long ld_v, long long ld_o, long long ld_do,
-                          long long ld_dk, long long ld_dv, float scale, int window, int max_blocks, int* status,
-                          void* stream_) {
+// ceil(len / 128).
+// Context-parallel form: q / o / d_o / lse / delta / dq hold only the global rows
+// [q_off, q_off + q_rows); k / v / dk / dv and cu_seqlens describe the complete sequence.
+PRB_API int prb_flash_bwd_slice(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                                const float* lse, float* delta, void* dq, void* dk, void* dv, const int* cu_seqlens,
+                                int num_docs, int total_q, int q_off, int q_rows, int heads_q, int heads_kv,
+                                int head_dim, long long ld_q, long long ld_k, long long ld_v, long long ld_o,
+                                long long ld_do, long long ld_dk, long long ld_dv, float scale, int window,
+                                int max_blocks, int* status, void* stream_) {
   using namespace prb;
-  (void)dq_acc;
+  if (q_off < 0 || q_rows <= 0 || q_off + q_rows > total_q) return -3;
   if (head_dim != kBwD || heads_q % heads_kv) return -2;
   if (total_q <= 0 || num_docs <= 0) return 0;
   if ((ld_q % 8) || (ld_k % 8) || (ld_v % 8) || (ld_do % 8) || (ld_dk % 8) || (ld_dv % 8)) return -4;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   CUtensorMap tmQ, tmK, tmV, tmDO;
-  int rc = make_tmap_2d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_q, (uint64_t)heads_q * kBwD,
+  int rc = make_tmap_2d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)q_rows, (uint64_t)heads_q * kBwD,
                         (uint64_t)ld_q, kBwB, 64, true);
   if (rc) return rc;
-  rc = make_tmap_2d(&tmDO, d_o, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_q, (uint64_t)heads_q * kBwD,
+  rc = make_tmap_2d(&tmDO, d_o, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)q_rows, (uint64_t)heads_q * kBwD,
                     (uint64_t)ld_do, kBwB, 64, true);
   if (rc) return rc;
   rc = make_tmap_2d(&tmK, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_q, (uint64_t)heads_kv * kBwD,
@@ -640,11 +661,12 @@ PRB_API int prb_flash_bwd(const void* q, const void* k, const void* v, const voi
   rc = make_tmap_2d(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_q, (uint64_t)heads_kv * kBwD,
                     (uint64_t)ld_v, kBwB, 64, true);
   if (rc) return rc;
-  const long long items = static_cast<long long>(total_q) * heads_q;
+  const long long items = static_cast<long long>(q_rows) * heads_q;
   flash_bwd_delta_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, stream>>>(
-      (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, total_q, heads_q, ld_o, ld_do);
+      (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, q_rows, heads_q, ld_o, ld_do);
   FaBwdParams p;
   p.cu_seqlens = cu_seqlens; p.num_docs = num_docs; p.total_q = total_q; p.heads_q = heads_q; p.heads_kv = heads_kv;
+  p.q_off = q_off; p.q_rows = q_rows;
   p.lse = lse; p.delta = delta;
   p.dq = reinterpret_cast<__nv_bfloat16*>(dq);
   p.dk = reinterpret_cast<__nv_bfloat16*>(dk); p.dv = reinterpret_cast<__nv_bfloat16*>(dv);
@@ -660,4 +682,17 @@ PRB_API int prb_flash_bwd(const void* q, const void* k, const void* v, const voi
   flash_bwd_dkdv_kernel<<<dim3(max_blocks, heads_kv), kBwThreads, kBwSmem, stream>>>(tmQ, tmK, tmV, tmDO, p);
   flash_bwd_dq_kernel<<<dim3(max_blocks, heads_q), kBwThreads, kBwSmem, stream>>>(tmQ, tmK, tmV, tmDO, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// dq_acc is unused (kept in the signature for existing callers; may be null).
+PRB_API int prb_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                          const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv,
+                          const int* cu_seqlens, int num_docs, int total_q, int heads_q, int heads_kv, int head_dim,
+                          long long ld_q, long long ld_k, long long ld_v, long long ld_o, long long ld_do,
+                          long long ld_dk, long long ld_dv, float scale, int window, int max_blocks, int* status,
+                          void* stream_) {
+  (void)dq_acc;
+  return prb_flash_bwd_slice(q, k, v, o, d_o, lse, delta, dq, dk, dv, cu_seqlens, num_docs, total_q, 0, total_q, heads_q,
+                             heads_kv, head_dim, ld_q, ld_k, ld_v, ld_o, ld_do, ld_dk, ld_dv, scale, window, max_blocks,
+                             status, stream_);
 }

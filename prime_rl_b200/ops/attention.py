@@ -73,14 +73,14 @@ class _FlashAttention(torch.autograd.Function):
     recomputation), in which case the forward launches nothing."""
 
     @staticmethod
-    def forward(ctx, q, k, v, cu, max_seqlen, scale, window, backend, cached, store):
+    def forward(ctx, q, k, v, cu, max_seqlen, scale, window, backend, cached, store, q_offset=None):
         ws = (-1, -1) if window is None else (window - 1, 0)
         if cached is not None:
             out, lse = cached
         elif backend == "tcgen05":
             from . import flash_native
 
-            out, lse = flash_native.flash_fwd(q, k, v, cu, scale=scale, window=window)
+            out, lse = flash_native.flash_fwd(q, k, v, cu, scale=scale, window=window, q_offset=q_offset)
         else:
             fwd, _ = _fa2()
             out, lse, _, _ = fwd(q, k, v, cu, cu, max_seqlen, max_seqlen, 0.0, scale, True, ws[0], ws[1], 0.0, None,
@@ -88,34 +88,37 @@ class _FlashAttention(torch.autograd.Function):
         if store is not None:
             store.append((out, lse))
         ctx.save_for_backward(q, k, v, out, lse, cu)
-        ctx.cfg = (max_seqlen, scale, ws, window, backend)
+        ctx.cfg = (max_seqlen, scale, ws, window, backend, q_offset)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, out, lse, cu = ctx.saved_tensors
-        max_seqlen, scale, ws, window, backend = ctx.cfg
+        max_seqlen, scale, ws, window, backend, q_offset = ctx.cfg
         if backend == "tcgen05" and BWD_BACKEND == "tcgen05":
             from . import flash_native
 
             if flash_native.bwd_available():
-                dq, dk, dv = flash_native.flash_bwd(dout, q, k, v, out, lse, cu, scale=scale, window=window)
-                return dq, dk, dv, None, None, None, None, None, None, None
+                dq, dk, dv = flash_native.flash_bwd(dout, q, k, v, out, lse, cu, scale=scale, window=window,
+                                                    q_offset=q_offset)
+                return dq, dk, dv, None, None, None, None, None, None, None, None
+        assert q_offset is None, "query slices need the tcgen05 kernels"
         _, bwd = _fa2()
         dq, dk, dv = torch.empty_like(q), torch.empty(k.shape, dtype=k.dtype, device=k.device), \
             torch.empty(v.shape, dtype=v.dtype, device=v.device)
         bwd(dout.contiguous(), q, k, v, out, lse, dq, dk, dv, cu, cu, max_seqlen, max_seqlen, 0.0, scale, True, ws[0],
             ws[1], 0.0, None, False, None)
-        return dq, dk, dv, None, None, None, None, None, None, None
+        return dq, dk, dv, None, None, None, None, None, None, None, None
 
 
 def attention(q, k, v, cu_seqlens, max_seqlen: int, *, causal: bool = True, window: int | None = None,
               sinks: torch.Tensor | None = None, scale: float | None = None, backend: str = "auto",
-              cache: dict | None = None, cache_key=None):
+              cache: dict | None = None, cache_key=None, q_offset: int | None = None):
     """``cache`` (a dict owned by the caller) lets an activation-recomputation pass reuse the
     attention output of the first pass of the same layer: a call whose ``cache_key`` is absent
     computes and stores ``(out, lse)``; the next call with that key consumes the entry and
-    launches no forward kernel."""
+    launches no forward kernel. ``q_offset`` (context parallelism): ``q`` holds only the global
+    rows ``[q_offset, q_offset + len(q))`` while k / v / cu_seqlens cover the whole sequence."""
     if backend in ("auto", None, "flash_attention_3", "flash_attention_4"):
         backend = default_backend(q.device)
     fast = q.is_cuda and sinks is None and causal and q.dtype == torch.bfloat16 and backend != "sdpa"
@@ -123,13 +126,15 @@ def attention(q, k, v, cu_seqlens, max_seqlen: int, *, causal: bool = True, wind
         return attention_ref(q, k, v, cu_seqlens, causal=causal, window=window, sinks=sinks, scale=scale)
     if backend == "tcgen05" and q.shape[-1] != 128:
         backend = "flash_attention_2"
+    if q_offset is not None and backend != "tcgen05":
+        raise NotImplementedError("query-slice attention needs head_dim 128 and the tcgen05 backend")
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     cached = store = None
     if cache is not None:
         cached = cache.pop(cache_key, None)
         if cached is None:
             store = []
-    out = _FlashAttention.apply(q, k, v, cu_seqlens, max_seqlen, scale, window, backend, cached, store)
+    out = _FlashAttention.apply(q, k, v, cu_seqlens, max_seqlen, scale, window, backend, cached, store, q_offset)
     if store:
         cache[cache_key] = store.pop()
     return out

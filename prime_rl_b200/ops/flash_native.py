@@ -17,25 +17,33 @@ def available() -> bool:
         return False
 
 
-def flash_fwd(q, k, v, cu_seqlens, *, scale: float | None = None, window: int | None = None):
+def flash_fwd(q, k, v, cu_seqlens, *, scale: float | None = None, window: int | None = None,
+              q_offset: int | None = None):
     """q: [T, Hq, 128] bf16 (contiguous heads), k/v: [T, Hkv, 128] bf16 (may be strided over
-    tokens). Returns (out [T, Hq, 128] bf16, lse [Hq, T] fp32, natural log)."""
-    T, Hq, D = q.shape
+    tokens). Returns (out [T, Hq, 128] bf16, lse [Hq, T] fp32, natural log).
+
+    Context-parallel form (``q_offset`` given): ``q`` holds only the global rows
+    ``[q_offset, q_offset + q.shape[0])`` while k / v / cu_seqlens describe the whole sequence;
+    out and lse are for the held rows."""
+    Tq, Hq, D = q.shape
+    T = k.shape[0]
     Hkv = k.shape[1]
     assert D == 128 and q.dtype == torch.bfloat16
     for t in (q, k, v):
         assert t.stride(2) == 1 and t.stride(1) == D, "heads must be contiguous"
-    out = torch.empty(T, Hq, D, dtype=q.dtype, device=q.device)
-    lse = torch.empty(Hq, T, dtype=torch.float32, device=q.device)
+    off = 0 if q_offset is None else int(q_offset)
+    assert q_offset is not None or Tq == T
+    out = torch.empty(Tq, Hq, D, dtype=q.dtype, device=q.device)
+    lse = torch.empty(Hq, Tq, dtype=torch.float32, device=q.device)
     num_docs = cu_seqlens.numel() - 1
     max_pairs = (T + 255) // 256 + num_docs
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     status = rt.status_tensor(q.device)
-    rc = rt.lib().prb_flash_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
-                                cu_seqlens.data_ptr(), num_docs, T, Hq, Hkv, D, q.stride(0), k.stride(0), v.stride(0),
-                                out.stride(0), float(scale), int(window or 0), max_pairs, status.data_ptr(),
-                                rt.stream_ptr(q.device))
-    rt.check(rc, "prb_flash_fwd")
+    rc = rt.lib().prb_flash_fwd_slice(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                      cu_seqlens.data_ptr(), num_docs, T, off, Tq, Hq, Hkv, D, q.stride(0),
+                                      k.stride(0), v.stride(0), out.stride(0), float(scale), int(window or 0),
+                                      max_pairs, status.data_ptr(), rt.stream_ptr(q.device))
+    rt.check(rc, "prb_flash_fwd_slice")
     return out, lse
 
 
@@ -47,27 +55,32 @@ def bwd_available() -> bool:
 
 
 def flash_bwd(dout, q, k, v, out, lse, cu_seqlens, *, scale: float | None = None, window: int | None = None,
-              dk_out: torch.Tensor | None = None, dv_out: torch.Tensor | None = None):
-    """Returns (dq [T, Hq, 128], dk, dv [T, Hkv, 128]) in bf16."""
-    T, Hq, D = q.shape
+              dk_out: torch.Tensor | None = None, dv_out: torch.Tensor | None = None, q_offset: int | None = None):
+    """Returns (dq [Tq, Hq, 128], dk, dv [T, Hkv, 128]) in bf16. With ``q_offset`` the query-side
+    tensors hold the global rows ``[q_offset, q_offset + Tq)`` only and dk / dv are this
+    rank's contributions for all T keys."""
+    Tq, Hq, D = q.shape
+    T = k.shape[0]
     Hkv = k.shape[1]
     assert D == 128 and q.dtype == torch.bfloat16
     dout = dout.contiguous()
     for t in (q, k, v, out, dout):
         assert t.stride(2) == 1 and t.stride(1) == D, "heads must be contiguous"
+    off = 0 if q_offset is None else int(q_offset)
     dev = q.device
-    dq = torch.empty(T, Hq, D, dtype=q.dtype, device=dev)
+    dq = torch.empty(Tq, Hq, D, dtype=q.dtype, device=dev)
     dk = dk_out if dk_out is not None else torch.empty(T, Hkv, D, dtype=q.dtype, device=dev)
     dv = dv_out if dv_out is not None else torch.empty(T, Hkv, D, dtype=q.dtype, device=dev)
-    delta = torch.empty(Hq, T, dtype=torch.float32, device=dev)
+    delta = torch.empty(Hq, Tq, dtype=torch.float32, device=dev)
     num_docs = cu_seqlens.numel() - 1
     max_blocks = (T + 127) // 128 + num_docs
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     status = rt.status_tensor(dev)
-    rc = rt.lib().prb_flash_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(),
-                                lse.data_ptr(), delta.data_ptr(), None, dq.data_ptr(), dk.data_ptr(),
-                                dv.data_ptr(), cu_seqlens.data_ptr(), num_docs, T, Hq, Hkv, D, q.stride(0),
-                                k.stride(0), v.stride(0), out.stride(0), dout.stride(0), dk.stride(0), dv.stride(0),
-                                float(scale), int(window or 0), max_blocks, status.data_ptr(), rt.stream_ptr(dev))
-    rt.check(rc, "prb_flash_bwd")
+    rc = rt.lib().prb_flash_bwd_slice(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(),
+                                      lse.data_ptr(), delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                      cu_seqlens.data_ptr(), num_docs, T, off, Tq, Hq, Hkv, D, q.stride(0),
+                                      k.stride(0), v.stride(0), out.stride(0), dout.stride(0), dk.stride(0),
+                                      dv.stride(0), float(scale), int(window or 0), max_blocks, status.data_ptr(),
+                                      rt.stream_ptr(dev))
+    rt.check(rc, "prb_flash_bwd_slice")
     return dq, dk, dv

@@ -8,8 +8,9 @@ non-attention layer runs on the local chunk, attention sees the whole (causal) c
              q/k/v, full-sequence attention on ``heads / cp`` heads, all-to-all back; KV heads are
              replicated when ``heads_kv < cp``.
 
-Both run on ``torch.distributed`` collectives (NCCL / gloo); per-token outputs (logprobs,
-entropy) are gathered back along the sequence for the loss.
+Both run on ``torch.distributed`` collectives (NCCL / gloo) for the exchange and on the tcgen05
+flash-attention kernels for the math (query-slice form for the all-gather path); per-token
+outputs (logprobs, entropy) are gathered back along the sequence for the loss.
 """
 
 from __future__ import annotations
@@ -126,26 +127,13 @@ class ContextParallel:
         vg = _AllGatherSeq.apply(v.contiguous(), self.group, True)
         lo, hi = self.rank * Tl, (self.rank + 1) * Tl
         cu = seq.full_cu_seqlens
-        if q.is_cuda and sinks is None and q.dtype == torch.bfloat16:
-            # per document that intersects the local chunk: queries = doc ∩ chunk, keys = doc start
-            # .. chunk end; flash-attn aligns the causal mask bottom-right, which is exactly this
-            cul = cu.tolist()
-            cq, ck, k0 = [0], [0], None
-            for a, b in zip(cul[:-1], cul[1:]):
-                if b <= lo or a >= hi:
-                    continue
-                if k0 is None:
-                    k0 = a
-                cq.append(cq[-1] + min(b, hi) - max(a, lo))
-                ck.append(ck[-1] + min(b, hi) - a)
-            from flash_attn import flash_attn_varlen_func
-
-            cq_t = torch.tensor(cq, dtype=torch.int32, device=q.device)
-            ck_t = torch.tensor(ck, dtype=torch.int32, device=q.device)
-            ws = (-1, -1) if window is None else (window - 1, 0)
-            return flash_attn_varlen_func(q, kg[k0:k0 + ck[-1]], vg[k0:k0 + ck[-1]], cq_t, ck_t,
-                                          max(b - a for a, b in zip(cq[:-1], cq[1:])),
-                                          max(b - a for a, b in zip(ck[:-1], ck[1:])), causal=True, window_size=ws)
+        if q.is_cuda and sinks is None and q.dtype == torch.bfloat16 and q.shape[-1] == 128:
+            # the tcgen05 kernels take a query slice directly: local rows [lo, hi) of the global
+            # sequence against all gathered keys (causality hides the keys past hi); the
+            # backward returns this rank's dK / dV for every key, which _AllGatherSeq reduces
+            max_len = int((cu[1:] - cu[:-1]).max())
+            return attn_ops.attention(q.contiguous(), kg, vg, cu.to(torch.int32), max_len, causal=True, window=window,
+                                      backend="tcgen05", q_offset=lo)
         doc = self._doc_ids(cu, T, q.device)
         pos = torch.arange(T, device=q.device)
         return attention_offset_ref(q, kg[:hi], vg[:hi], pos[lo:hi], pos[:hi], doc[lo:hi], doc[:hi], window=window,

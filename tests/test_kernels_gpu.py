@@ -467,6 +467,42 @@ def test_flash_bwd_matches_reference(lens, window):
         _close(got, want, atol=0.1, rtol=5e-2)
 
 
+@pytest.mark.parametrize("lens,window,cp", [([300, 77, 1000], None, 3), ([700, 300], 200, 2), ([1024], None, 4)])
+def test_flash_query_slices_sum_to_full_attention(lens, window, cp):
+    """Context-parallel form: each slice of the query rows against all keys reproduces its rows of
+    the full attention, and the per-slice dK / dV add up to the full gradients."""
+    from prime_rl_b200.ops import attention as A, flash_native
+    T, Hq, Hkv, D = sum(lens), 4, 2, 128
+    pad = (-T) % cp
+    lens = lens[:-1] + [lens[-1] + pad]
+    T += pad
+    q, k, v = _rand(T, Hq, D), _rand(T, Hkv, D), _rand(T, Hkv, D)
+    cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
+    cu[1:] = torch.tensor(lens).cumsum(0)
+    cu = cu.to(DEV)
+    do = _rand(T, Hq, D)
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = A.attention_ref(qr, kr, vr, cu, window=window)
+    ref.backward(do.float())
+    Tl = T // cp
+    dk_sum = torch.zeros(T, Hkv, D, device=DEV)
+    dv_sum = torch.zeros(T, Hkv, D, device=DEV)
+    for r in range(cp):
+        lo = r * Tl
+        ql, dol = q[lo:lo + Tl].contiguous(), do[lo:lo + Tl].contiguous()
+        out, lse = flash_native.flash_fwd(ql, k, v, cu, window=window, q_offset=lo)
+        dq, dk, dv = flash_native.flash_bwd(dol, ql, k, v, out, lse, cu, window=window, q_offset=lo)
+        rt.check_status()
+        _close(out, ref[lo:lo + Tl], atol=3e-2, rtol=3e-2)
+        rel = (dq.float() - qr.grad[lo:lo + Tl]).norm() / qr.grad[lo:lo + Tl].norm()
+        assert rel < 2e-2, f"dq slice {r}: relative error {rel:.4f}"
+        dk_sum += dk.float()
+        dv_sum += dv.float()
+    for got, want, name in ((dk_sum, kr.grad, "dk"), (dv_sum, vr.grad, "dv")):
+        rel = (got - want).norm() / want.norm()
+        assert rel < 2e-2, f"{name}: relative error {rel:.4f}"
+
+
 @pytest.mark.parametrize("Hq,Hkv", [(32, 4), (8, 8), (16, 4)])
 @pytest.mark.parametrize("splits", [1, 3])
 def test_paged_decode(Hq, Hkv, splits):
