@@ -149,6 +149,179 @@ paged_decode_kernel(const PagedParams p) {
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Tensor-core variant for 16-token pages and up to 8 query heads per KV head. With a GQA group
+// of 8 the op needs 8 FLOP per KV byte, more than the fp32 pipes deliver at HBM speed, so the
+// scores and the P V product run on mma.sync m16n8k16 (rows 8..15 of the M = 16 tile are zero).
+// One CTA = one (sequence, KV head, split), four warps; a warp owns whole pages: it copies the
+// page's K and V rows (16 x 256 B each) into its private, double-buffered, XOR-swizzled shared
+// memory with cp.async, reads operand fragments with ldmatrix (V transposed), keeps the online
+// softmax state of its pages in registers; the warps' partial results are merged at the end.
+constexpr int kPmPage = 16;
+constexpr int kPmWarpBytes = 2 * 2 * kPmPage * kPdD * 2;   // 2 buffers x (K, V) x 4 KB = 16 KB
+
+__device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void* gptr) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr), "l"(gptr) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int G>
+__global__ void __launch_bounds__(kPdWarps * 32)
+paged_decode_mma_kernel(const PagedParams p) {
+  extern __shared__ __align__(128) uint8_t pm_smem[];
+  const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, j = lane & 3;        // fragment row (query head of the group) / column pair
+  const int ctx = p.ctx_lens[b];
+  const int pages = (ctx + kPmPage - 1) / kPmPage;
+  const int per = (pages + p.splits - 1) / p.splits;
+  const int pg_begin = split * per, pg_end = min(pages, pg_begin + per);
+  const int* table = p.block_tables + static_cast<long long>(b) * p.max_blocks;
+  const long long row_stride = static_cast<long long>(p.Hkv) * kPdD;          // elements between keys of a page
+  const uint32_t sbase = smem_u32(pm_smem) + warp * kPmWarpBytes;
+  const float scale_log2 = p.scale * 1.4426950408889634f;
+
+  // Q fragments: row g of the A tile is query head g of this KV head's group (rows >= G are zero)
+  uint32_t qa[8][2];
+  {
+    const __nv_bfloat16* qrow = p.q + (static_cast<long long>(b) * p.Hq + kvh * G + (g < G ? g : 0)) * kPdD;
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      qa[kk][0] = (g < G) ? *reinterpret_cast<const uint32_t*>(qrow + 16 * kk + 2 * j) : 0u;
+      qa[kk][1] = (g < G) ? *reinterpret_cast<const uint32_t*>(qrow + 16 * kk + 8 + 2 * j) : 0u;
+    }
+  }
+  float o[16][4];
+#pragma unroll
+  for (int n = 0; n < 16; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m = -INFINITY, l = 0.f;                 // running max (log2 domain) / sum of row g
+
+  // copy one page (K and V rows of this KV head) into buffer `buf`: 512 chunks of 16 bytes
+  auto issue_page = [&](int pg, int buf) {
+    const long long base = static_cast<long long>(table[pg]) * kPmPage * row_stride + static_cast<long long>(kvh) * kPdD;
+    const uint32_t kdst = sbase + buf * (2 * kPmPage * kPdD * 2), vdst = kdst + kPmPage * kPdD * 2;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = lane + 32 * i;              // chunk id: key = c / 16, 16-byte chunk of the row = c % 16
+      const int key = c >> 4, ch = c & 15;
+      const long long off = base + key * row_stride + ch * 8;
+      const uint32_t sw = key * 256 + ((ch ^ (key & 7)) << 4);
+      cp_async16(kdst + sw, p.kpool + off);
+      cp_async16(vdst + sw, p.vpool + off);
+    }
+    cp_async_commit();
+  };
+
+  int pg = pg_begin + warp;
+  if (pg < pg_end) issue_page(pg, 0);
+  int buf = 0;
+  for (; pg < pg_end; pg += kPdWarps, buf ^= 1) {
+    const int nxt = pg + kPdWarps;
+    if (nxt < pg_end) { issue_page(nxt, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    __syncwarp();
+    const uint32_t ks = sbase + buf * (2 * kPmPage * kPdD * 2), vs = ks + kPmPage * kPdD * 2;
+    // ---- S = Q K^T for the 16 keys of the page (two n-tiles of 8 keys)
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+    {
+      const int key = 8 * (lane >> 4) + (lane & 7);          // matrices 0, 1 -> keys 0..7; 2, 3 -> keys 8..15
+      const int hi = (lane >> 3) & 1;                        // second 8 columns of the k-step
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(ks + key * 256 + (((2 * kk + hi) ^ (key & 7)) << 4), b0, b1, b2, b3);
+        mma_16816(s0, qa[kk][0], 0u, qa[kk][1], 0u, b0, b1);
+        mma_16816(s1, qa[kk][0], 0u, qa[kk][1], 0u, b2, b3);
+      }
+    }
+    // ---- online softmax of row g: this thread holds keys 2j, 2j+1 (s0) and 8+2j, 9+2j (s1)
+    const int k0 = pg * kPmPage + 2 * j;
+    float x0 = (k0 < ctx) ? s0[0] * scale_log2 : -INFINITY, x1 = (k0 + 1 < ctx) ? s0[1] * scale_log2 : -INFINITY;
+    float x2 = (k0 + 8 < ctx) ? s1[0] * scale_log2 : -INFINITY, x3 = (k0 + 9 < ctx) ? s1[1] * scale_log2 : -INFINITY;
+    float mx = fmaxf(fmaxf(x0, x1), fmaxf(x2, x3));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float mn = fmaxf(m, mx);                            // finite: key pg * 16 < ctx exists
+    const float alpha = exp2f(m - mn);
+    const float p0 = exp2f(x0 - mn), p1 = exp2f(x1 - mn), p2 = exp2f(x2 - mn), p3 = exp2f(x3 - mn);
+    float rs = p0 + p1 + p2 + p3;
+    rs += __shfl_xor_sync(0xffffffffu, rs, 1);
+    rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+    l = l * alpha + rs;
+    m = mn;
+    const uint32_t pa0 = pack_bf16(p0, p1), pa2 = pack_bf16(p2, p3);   // A fragment of P (rows 8..15 zero)
+    // ---- O = O * alpha + P V
+    {
+      const int key = 8 * ((lane >> 3) & 1) + (lane & 7);    // matrices 0, 2 -> keys 0..7; 1, 3 -> keys 8..15
+      const int sub = lane >> 4;                             // second d tile of the pair
+#pragma unroll
+      for (int pr = 0; pr < 8; ++pr) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(vs + key * 256 + (((2 * pr + sub) ^ (key & 7)) << 4), b0, b1, b2, b3);
+        o[2 * pr][0] *= alpha; o[2 * pr][1] *= alpha;
+        o[2 * pr + 1][0] *= alpha; o[2 * pr + 1][1] *= alpha;
+        mma_16816(o[2 * pr], pa0, 0u, pa2, 0u, b0, b1);
+        mma_16816(o[2 * pr + 1], pa0, 0u, pa2, 0u, b2, b3);
+      }
+    }
+    __syncwarp();
+  }
+
+  // ---- merge the four warps: row g < G, this thread holds d = 8 n + 2 j, 2 j + 1 of every n-tile
+  __syncthreads();                                            // all cp.async traffic is done, smem is reusable
+  float* s_m = reinterpret_cast<float*>(pm_smem);             // [warps][8]
+  float* s_l = s_m + kPdWarps * 8;
+  float* s_o = s_l + kPdWarps * 8;                            // [warps][8][128]
+  if (g < G) {
+    if (j == 0) { s_m[warp * 8 + g] = m; s_l[warp * 8 + g] = l; }
+#pragma unroll
+    for (int n = 0; n < 16; ++n)
+      *reinterpret_cast<float2*>(&s_o[(warp * 8 + g) * kPdD + 8 * n + 2 * j]) = make_float2(o[n][0], o[n][1]);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < G * kPdD; i += blockDim.x) {
+    const int gg = i / kPdD, d = i - gg * kPdD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kPdWarps; ++w) M = fmaxf(M, s_m[w * 8 + gg]);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < kPdWarps; ++w) {
+      const float a = (s_m[w * 8 + gg] == -INFINITY) ? 0.f : exp2f(s_m[w * 8 + gg] - M);
+      L += s_l[w * 8 + gg] * a;
+      O += s_o[(w * 8 + gg) * kPdD + d] * a;
+    }
+    const long long head = static_cast<long long>(b) * p.Hq + kvh * G + gg;
+    if (p.splits == 1) {
+      p.out[head * kPdD + d] = __float2bfloat16(L > 0.f ? O / L : 0.f);
+    } else {
+      p.o_part[(head * p.splits + split) * kPdD + d] = O;
+      if (d == 0) {
+        // the merge kernel works in the natural-log domain
+        p.ml_part[(head * p.splits + split) * 2] = (M == -INFINITY) ? -INFINITY : M * 0.6931471805599453f;
+        p.ml_part[(head * p.splits + split) * 2 + 1] = L;
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kPdD)
 paged_decode_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
                           __nv_bfloat16* __restrict__ out, int splits) {
@@ -186,6 +359,31 @@ PRB_API int prb_paged_decode(const void* q, const void* kpool, const void* vpool
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size; p.max_blocks = max_blocks; p.splits = splits;
   dim3 grid(B, Hkv, splits);
   const int G = Hq / Hkv;
+  if (page_size == kPmPage && G <= 8 && (G & (G - 1)) == 0) {
+    constexpr int smem = kPdWarps * kPmWarpBytes;     // 64 KB (also holds the 17 KB merge scratch)
+#define PRB_PM_LAUNCH(GG)                                                                                       \
+    {                                                                                                           \
+      static bool configured = false;                                                                           \
+      if (!configured) {                                                                                        \
+        if (cudaFuncSetAttribute(paged_decode_mma_kernel<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != \
+            cudaSuccess)                                                                                        \
+          return -10;                                                                                           \
+        configured = true;                                                                                      \
+      }                                                                                                         \
+      paged_decode_mma_kernel<GG><<<grid, kPdWarps * 32, smem, stream>>>(p);                                    \
+    }
+    switch (G) {
+      case 1: PRB_PM_LAUNCH(1) break;
+      case 2: PRB_PM_LAUNCH(2) break;
+      case 4: PRB_PM_LAUNCH(4) break;
+      default: PRB_PM_LAUNCH(8) break;
+    }
+#undef PRB_PM_LAUNCH
+    if (splits > 1)
+      paged_decode_merge_kernel<<<static_cast<unsigned>(B) * Hq, kPdD, 0, stream>>>(o_part, ml_part,
+                                                                                   (__nv_bfloat16*)out, splits);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  }
   switch (G) {
     case 1: paged_decode_kernel<1><<<grid, kPdWarps * 32, 0, stream>>>(p); break;
     case 2: paged_decode_kernel<2><<<grid, kPdWarps * 32, 0, stream>>>(p); break;

@@ -31,6 +31,7 @@ def main(argv=None):
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--layers", type=int, default=None, help="debug: truncate the model")
+    ap.add_argument("--no-graphs", action="store_true", help="launch the decode step kernel by kernel")
     args = ap.parse_args(argv)
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -38,12 +39,16 @@ def main(argv=None):
     if args.layers:
         arch = arch.model_copy(update={"num_hidden_layers": args.layers})
     model = build_model(arch, device=dev, dtype=torch.bfloat16, seed=0)
-    total = args.prompt + args.warmup + args.steps + 2
+    # requests admitted early keep decoding while the rest is prefilled: give every request enough
+    # budget to still be running in the timed region
+    prefill_steps = (args.batch * args.prompt + 16383) // 16384 + 1
+    budget = prefill_steps + args.warmup + args.steps + 4
+    total = args.prompt + budget + 2
     pages = args.batch * ((total + 15) // 16 + 1) + 64
     eng = Engine(model, num_pages=pages, page_size=16, max_running=args.batch, max_prefill_tokens=16384,
-                 enable_prefix_cache=False)
+                 enable_prefix_cache=False, use_cuda_graphs=not args.no_graphs, max_model_len=total + 16)
     g = torch.Generator().manual_seed(0)
-    params = SamplingParams(temperature=1.0, max_tokens=args.warmup + args.steps + 1)
+    params = SamplingParams(temperature=1.0, max_tokens=budget)
     for _ in range(args.batch):
         eng.submit(Request(prompt=torch.randint(0, arch.vocab_size, (args.prompt,), generator=g).tolist(), params=params))
     torch.cuda.synchronize()
@@ -66,10 +71,10 @@ def main(argv=None):
 
     rt.check_status()
     print(json.dumps({"metric": "rollout decode tokens/s", "model": args.model, "layers": arch.num_hidden_layers,
-                      "batch": args.batch, "prompt_len": args.prompt, "steps": args.steps,
+                      "batch": args.batch, "mean_running": toks / args.steps, "prompt_len": args.prompt, "steps": args.steps,
                       "decode_tokens_per_s": toks / dt, "ms_per_step": 1e3 * dt / args.steps,
                       "prefill_tokens_per_s": args.batch * args.prompt / t_prefill,
-                      "peak_memory_gib": torch.cuda.max_memory_allocated() / 2**30, "n_gpus": 1, "dtype": "bf16",
+                      "peak_memory_gib": torch.cuda.max_memory_allocated() / 2**30, "n_gpus": 1, "dtype": "bf16", "cuda_graphs": not args.no_graphs,
                       "data": "synthetic (uniform random token ids, random-init weights)"}), flush=True)
 
 

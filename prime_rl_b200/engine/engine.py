@@ -51,14 +51,15 @@ class Request:
 
 class Engine:
     def __init__(self, model, *, num_pages: int = 4096, page_size: int = 16, max_running: int = 256,
-                 max_prefill_tokens: int = 16384, eos_token_id: int | None = None, enable_prefix_cache: bool = True):
+                 max_prefill_tokens: int = 16384, eos_token_id: int | None = None, enable_prefix_cache: bool = True,
+                 use_cuda_graphs: bool = False, max_model_len: int = 8192):
         arch = model.arch
         self.model = model.eval()
         p = next(model.parameters())
         self.device = p.device
         self.cache = KVCache(arch.num_hidden_layers, num_pages, page_size, arch.num_key_value_heads, arch.head_dim,
                              p.dtype, p.device)
-        self.runner = ModelRunner(model, self.cache)
+        self.runner = ModelRunner(model, self.cache, use_cuda_graphs=use_cuda_graphs, max_model_len=max_model_len)
         self.max_running, self.max_prefill_tokens = max_running, max_prefill_tokens
         self.eos, self.enable_prefix_cache = eos_token_id, enable_prefix_cache
         self.waiting: list[Request] = []

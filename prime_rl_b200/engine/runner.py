@@ -30,28 +30,37 @@ class StepInput:
 
 
 class ModelRunner:
-    def __init__(self, model, cache: KVCache, fp32_lm_head: bool = True):
+    def __init__(self, model, cache: KVCache, fp32_lm_head: bool = True, use_cuda_graphs: bool = False,
+                 max_model_len: int = 8192):
         self.model, self.cache, self.arch = model, cache, model.arch
         self.device = next(model.parameters()).device
         self.fp32_lm_head = fp32_lm_head
         self.capture_routed = False
         self.last_routed: torch.Tensor | None = None   # [N, moe_layers, k] of the last step
         self._decode_meta = None                        # (block tables, context lengths) of a pure decode step
+        # CUDA graphs for decode steps: batch sizes are padded to a multiple of ``graph_bucket``;
+        # one page of the cache is reserved as the target of the padding rows
+        plain = all(l.self_attn.window is None and l.self_attn.sinks is None for l in model.model.layers)
+        self.use_cuda_graphs = use_cuda_graphs and self.device.type == "cuda" and plain
+        self.graph_bucket = 8
+        self.graph_max_blocks = max(1, (max_model_len + cache.page_size - 1) // cache.page_size)
+        self._graphs: dict[int, dict] = {}
+        self.scratch_page = cache.blocks.alloc() if self.use_cuda_graphs else 0
 
     # ------------------------------------------------------------------ attention over pages
     def _attend(self, layer: int, q, k_new, v_new, batch: list[StepInput], starts: list[int], window, sinks):
         """q: [N, Hq, D] for the concatenated new tokens. Context = cached prefix + new tokens."""
+        if self._decode_meta is not None and sinks is None and window is None:
+            from ..ops import paged
+
+            bt, ctx = self._decode_meta
+            return paged.paged_decode_raw(q.contiguous(), self.cache.k[layer], self.cache.v[layer], bt, ctx)
         fresh = all(s.kv.length == 0 for s in batch)
         if fresh and sinks is None:
             lens = [len(s.tokens) for s in batch]
             cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
             cu[1:] = torch.tensor(lens, dtype=torch.int32).cumsum(0)
             return attn_ops.attention(q, k_new, v_new, cu.to(q.device), max(lens), causal=True, window=window)
-        if self._decode_meta is not None and sinks is None and window is None:
-            from ..ops import paged
-
-            bt, ctx = self._decode_meta
-            return paged.paged_decode_raw(q.contiguous(), self.cache.k[layer], self.cache.v[layer], bt, ctx)
         outs = []
         scale = 1.0 / math.sqrt(q.shape[-1])
         rep = q.shape[1] // k_new.shape[1]
@@ -77,37 +86,13 @@ class ModelRunner:
             outs.append((p @ vs).transpose(0, 1).to(q.dtype))
         return torch.cat(outs, 0)
 
-    # ------------------------------------------------------------------ one forward over new tokens
-    @torch.no_grad()
-    def forward(self, batch: list[StepInput]) -> tuple[torch.Tensor, list[int]]:
-        """Runs the new tokens of every sequence, appends their K/V to the cache and returns
-        (fp32 logits rows, row offsets): one row per sequence (its last token) unless
-        ``want_all_logits`` asks for every position."""
-        dev, cache, model = self.device, self.cache, self.model
-        ids, pos, slots, starts = [], [], [], []
-        for s in batch:
-            n = len(s.tokens)
-            cache.make_writable_tail(s.kv)
-            cache.ensure_capacity(s.kv, s.kv.length + n)
-            starts.append(len(ids))
-            ids.extend(s.tokens)
-            pos.extend(range(s.kv.length, s.kv.length + n))
-            slots.extend(cache.slot_mapping(s.kv, s.kv.length, n))
-        ids_t = torch.tensor(ids, dtype=torch.long, device=dev)
-        pos_t = torch.tensor(pos, dtype=torch.int32, device=dev)
-        slots_t = torch.tensor(slots, dtype=torch.long, device=dev)
+    # ------------------------------------------------------------------ decoder over device tensors
+    def _core(self, ids_t, pos_t, slots_t, rows_t, batch, starts):
+        """ids / positions / cache slots of the N new tokens -> fp32 logits of ``rows_t``. Everything
+        here is device work with static shapes for a given N, so a pure decode step can be captured
+        in a CUDA graph (``batch`` / ``starts`` are only used by the non-paged attention paths)."""
+        model, cache = self.model, self.cache
         seq = SeqInfo(None, 0, pos_t)
-        # a pure decode step on the GPU: one block table / length vector for all layers
-        self._decode_meta = None
-        if dev.type == "cuda" and all(len(s.tokens) == 1 for s in batch):
-            from ..ops import paged
-
-            if paged.available() and self.arch.head_dim == 128:
-                max_blocks = max(len(s.kv.pages) for s in batch)
-                bt = torch.tensor([s.kv.pages + [0] * (max_blocks - len(s.kv.pages)) for s in batch],
-                                  dtype=torch.int32)
-                ctx = torch.tensor([s.kv.length + 1 for s in batch], dtype=torch.int32)
-                self._decode_meta = (bt.to(dev, non_blocking=True), ctx.to(dev, non_blocking=True))
         h = model.model.embed_tokens(ids_t)
         N = h.shape[0]
         routed = []
@@ -133,10 +118,108 @@ class ModelRunner:
             else:
                 m = layer.mlp(x2)
             h = h + m
-        for s in batch:
-            s.kv.length += len(s.tokens)
-        self.last_routed = torch.stack(routed, dim=1) if routed else None
+        routed_t = torch.stack(routed, dim=1) if routed else None
         h = model.model.norm(h)
+        sel = h[rows_t]
+        w = model.output_weight
+        if sel.is_cuda and sel.dtype == torch.bfloat16:
+            # bf16 operands, fp32 accumulation and fp32 logits (no fp32 copy of the embedding matrix)
+            logits = ops.gemm(sel.contiguous(), w, out_dtype=torch.float32)
+        else:
+            logits = sel.float() @ w.float().t() if self.fp32_lm_head else ops.linear(sel, w).float()
+        return logits, routed_t
+
+    # ------------------------------------------------------------------ CUDA-graph decode
+    def _graph_for(self, B: int):
+        """Captures one decode step for ``B`` sequences (padded batch size). Static inputs: token
+        ids, positions, cache slots, block tables, context lengths; static outputs: logits, routed
+        experts. Padding rows point at page 0 / slot 0 of a reserved scratch page."""
+        g = self._graphs.get(B)
+        if g is not None:
+            return g
+        dev, ps = self.device, self.cache.page_size
+        W = self.graph_max_blocks
+        st = {"ids": torch.zeros(B, dtype=torch.long, device=dev), "pos": torch.zeros(B, dtype=torch.int32, device=dev),
+              "slots": torch.full((B,), self.scratch_page * ps, dtype=torch.long, device=dev),
+              "bt": torch.full((B, W), self.scratch_page, dtype=torch.int32, device=dev),
+              "ctx": torch.ones(B, dtype=torch.int32, device=dev), "rows": torch.arange(B, device=dev)}
+        self._decode_meta = (st["bt"], st["ctx"])
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):                      # warm-up: first-use initialisation must not be captured
+                self._core(st["ids"], st["pos"], st["slots"], st["rows"], None, None)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits, routed = self._core(st["ids"], st["pos"], st["slots"], st["rows"], None, None)
+        st["logits"], st["routed"], st["graph"] = logits, routed, graph
+        self._graphs[B] = st
+        return st
+
+    def _decode_with_graph(self, batch):
+        dev, B = self.device, len(batch)
+        Bp = (B + self.graph_bucket - 1) // self.graph_bucket * self.graph_bucket
+        st = self._graph_for(Bp)
+        W, sp = self.graph_max_blocks, self.scratch_page
+        ids = [s.tokens[0] for s in batch] + [0] * (Bp - B)
+        pos = [s.kv.length for s in batch] + [0] * (Bp - B)
+        slots, bt = [], []
+        for s in batch:
+            slots.extend(self.cache.slot_mapping(s.kv, s.kv.length, 1))
+            bt.append(s.kv.pages + [sp] * (W - len(s.kv.pages)))
+        slots += [sp * self.cache.page_size] * (Bp - B)
+        bt += [[sp] * W] * (Bp - B)
+        ctx = [s.kv.length + 1 for s in batch] + [1] * (Bp - B)
+        st["ids"].copy_(torch.tensor(ids, dtype=torch.long), non_blocking=True)
+        st["pos"].copy_(torch.tensor(pos, dtype=torch.int32), non_blocking=True)
+        st["slots"].copy_(torch.tensor(slots, dtype=torch.long), non_blocking=True)
+        st["bt"].copy_(torch.tensor(bt, dtype=torch.int32), non_blocking=True)
+        st["ctx"].copy_(torch.tensor(ctx, dtype=torch.int32), non_blocking=True)
+        st["graph"].replay()
+        routed = st["routed"][:B].clone() if st["routed"] is not None else None
+        return st["logits"][:B].clone(), routed
+
+    # ------------------------------------------------------------------ one forward over new tokens
+    @torch.no_grad()
+    def forward(self, batch: list[StepInput]) -> tuple[torch.Tensor, list[int]]:
+        """Runs the new tokens of every sequence, appends their K/V to the cache and returns
+        (fp32 logits rows, row offsets): one row per sequence (its last token) unless
+        ``want_all_logits`` asks for every position."""
+        dev, cache = self.device, self.cache
+        for s in batch:
+            cache.make_writable_tail(s.kv)
+            cache.ensure_capacity(s.kv, s.kv.length + len(s.tokens))
+        decode = dev.type == "cuda" and self.arch.head_dim == 128 and all(len(s.tokens) == 1 for s in batch)
+        if decode:
+            from ..ops import paged
+
+            decode = paged.available()
+        if decode and self.use_cuda_graphs and \
+                max(len(s.kv.pages) for s in batch) <= self.graph_max_blocks:
+            logits, routed = self._decode_with_graph(batch)
+            for s in batch:
+                s.kv.length += 1
+            self.last_routed = routed
+            return logits, list(range(len(batch)))
+        ids, pos, slots, starts = [], [], [], []
+        for s in batch:
+            n = len(s.tokens)
+            starts.append(len(ids))
+            ids.extend(s.tokens)
+            pos.extend(range(s.kv.length, s.kv.length + n))
+            slots.extend(cache.slot_mapping(s.kv, s.kv.length, n))
+        ids_t = torch.tensor(ids, dtype=torch.long, device=dev)
+        pos_t = torch.tensor(pos, dtype=torch.int32, device=dev)
+        slots_t = torch.tensor(slots, dtype=torch.long, device=dev)
+        # a pure decode step on the GPU: one block table / length vector for all layers
+        self._decode_meta = None
+        if decode:
+            max_blocks = max(len(s.kv.pages) for s in batch)
+            bt = torch.tensor([s.kv.pages + [0] * (max_blocks - len(s.kv.pages)) for s in batch], dtype=torch.int32)
+            ctx = torch.tensor([s.kv.length + 1 for s in batch], dtype=torch.int32)
+            self._decode_meta = (bt.to(dev, non_blocking=True), ctx.to(dev, non_blocking=True))
         rows, offsets = [], []
         for s, st in zip(batch, starts):
             n = len(s.tokens)
@@ -145,12 +228,10 @@ class ModelRunner:
                 rows.extend(range(st, st + n))
             else:
                 rows.append(st + n - 1)
-        sel = h[torch.tensor(rows, dtype=torch.long, device=dev)]
-        w = model.output_weight
-        if sel.is_cuda and sel.dtype == torch.bfloat16:
-            # bf16 operands, fp32 accumulation and fp32 logits (no fp32 copy of the embedding matrix)
-            logits = ops.gemm(sel.contiguous(), w, out_dtype=torch.float32)
-        else:
-            logits = sel.float() @ w.float().t() if self.fp32_lm_head else ops.linear(sel, w).float()
+        rows_t = torch.tensor(rows, dtype=torch.long, device=dev)
+        logits, routed = self._core(ids_t, pos_t, slots_t, rows_t, batch, starts)
+        for s in batch:
+            s.kv.length += len(s.tokens)
+        self.last_routed = routed
         self._decode_meta = None
         return logits, offsets
