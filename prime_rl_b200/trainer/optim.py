@@ -248,7 +248,8 @@ class FlatOptimizer:
 
     def __init__(self, config, named_params, *, max_steps: int | None = None, scheduler_config=None,
                  dp_group=None, expert_params=None, expert_reduce_group=None, expert_norm_group=None,
-                 shard_group=None, replicate_group=None, expert_shard_group=None):
+                 shard_group=None, replicate_group=None, expert_shard_group=None, offload: str | None = None,
+                 offload_chunk: int = 16 * 1024 * 1024):
         self.config = config
         self.kind = config.type
         self.step_count = 0
@@ -266,6 +267,19 @@ class FlatOptimizer:
         self.hyper = torch.zeros(3, dtype=torch.float32, device=dev)
         self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
         self.last_grad_norm: torch.Tensor | None = None
+        # optimizer state in host memory: "state" parks it there between steps, "cpu" also runs the update there
+        self.offload = offload
+        self._state_offload, self._cpu_step = [], []
+        if offload == "state":
+            from .optim_offload import StateOffload
+
+            self._state_offload = [StateOffload(g) for g in self.groups]
+        elif offload == "cpu":
+            from .optim_offload import CPUStep
+
+            self._cpu_step = [CPUStep(g, self.kind, offload_chunk) for g in self.groups]
+        elif offload is not None:
+            raise ValueError(f"unknown optimizer offload mode {offload}")
 
     # ------------------------------------------------------------------ API
     @property
@@ -310,8 +324,20 @@ class FlatOptimizer:
         if self.kind == "adamw" and self.hyper.is_cuda:
             b1, b2 = c.betas1, c.betas2
             self.hyper.copy_(torch.tensor([lr, 1 - b1 ** t, math.sqrt(1 - b2 ** t)]), non_blocking=True)
+        if self._cpu_step:
+            scale = float(coef)                       # host value: the update runs on the CPU
+            for g, cs in zip(self.groups, self._cpu_step):
+                cs.step(lr=lr, grad_scale=scale, t=t, cfg=c)      # writes the new parameters to the device
+                g.lowp_written_by_kernel = True
+                if g.sharded:
+                    g.publish()
+            return norm
+        for so in self._state_offload:
+            so.load()
         for g in self.groups:
             self._step_group(g, lr, coef, t)
+        for so in self._state_offload:
+            so.store()
         return norm
 
     def _step_group(self, g: _Group, lr: float, coef: torch.Tensor, t: int) -> None:
@@ -414,7 +440,8 @@ class FlatOptimizer:
 
 def setup_optimizer(config, model, *, max_steps=None, scheduler_config=None, dp_group=None,
                     expert_reduce_group=None, expert_norm_group=None, shard_group=None, replicate_group=None,
-                    expert_shard_group=None) -> FlatOptimizer:
+                    expert_shard_group=None, offload: str | None = None,
+                    offload_chunk: int = 16 * 1024 * 1024) -> FlatOptimizer:
     """Parameters marked ``_is_expert_shard`` (set by the expert-parallel setup) form their own
     group: they are reduced over the ranks that replicate the same expert shard."""
     dense = [(n, p) for n, p in model.named_parameters() if not getattr(p, "_is_expert_shard", False)]
@@ -422,4 +449,5 @@ def setup_optimizer(config, model, *, max_steps=None, scheduler_config=None, dp_
     return FlatOptimizer(config, dense, max_steps=max_steps, scheduler_config=scheduler_config, dp_group=dp_group,
                          expert_params=expert, expert_reduce_group=expert_reduce_group,
                          expert_norm_group=expert_norm_group, shard_group=shard_group,
-                         replicate_group=replicate_group, expert_shard_group=expert_shard_group)
+                         replicate_group=replicate_group, expert_shard_group=expert_shard_group, offload=offload,
+                         offload_chunk=offload_chunk)

@@ -1,3 +1,4 @@
+import pytest
 import torch
 
 from prime_rl_b200.configs.trainer import (AdamWConfig, CheckpointConfig, CosineSchedulerConfig, LinearSchedulerConfig,
@@ -118,3 +119,31 @@ def test_trainer_resume_continues_identically(tmp_path):
 def pytest_approx(x):
     import pytest
     return pytest.approx(x, rel=1e-5, abs=1e-7)
+
+
+@pytest.mark.parametrize("mode", ["state", "cpu"])
+def test_optimizer_offload_matches_device_resident_step(mode):
+    """Optimizer state parked in host memory (and the C++ CPU update) give the same parameters
+    as the resident optimizer."""
+    import copy
+
+    from prime_rl_b200.configs.trainer import AdamWConfig
+    from prime_rl_b200.trainer.optim import FlatOptimizer
+
+    torch.manual_seed(0)
+    ref_model = torch.nn.Sequential(torch.nn.Linear(24, 40), torch.nn.Linear(40, 8))
+    off_model = copy.deepcopy(ref_model)
+    cfg = AdamWConfig(lr=1e-2, weight_decay=0.1, max_norm=0.5)
+    opt_ref = FlatOptimizer(cfg, list(ref_model.named_parameters()))
+    opt_off = FlatOptimizer(cfg, list(off_model.named_parameters()), offload=mode, offload_chunk=300)
+    for step in range(3):
+        x = torch.randn(16, 24)
+        for model, opt in ((ref_model, opt_ref), (off_model, opt_off)):
+            opt.zero_grad()
+            model(x).pow(2).mean().backward()
+            opt.reduce_gradients()
+            opt.step()
+    for a, b in zip(ref_model.parameters(), off_model.parameters()):
+        assert torch.allclose(a, b, rtol=2e-5, atol=2e-6)
+    sd = opt_off.state_dict()
+    assert set(sd["state"]) >= {"exp_avg", "exp_avg_sq"}
