@@ -51,6 +51,7 @@ class Source:
     ratio: float
     next_task: int = 0
     gates: list = field(default_factory=list)
+    sampler: object = None          # orchestrator/curriculum.py task sampler (None: round robin)
 
 
 class Dispatcher:
@@ -99,8 +100,12 @@ class Dispatcher:
 
     def _launch_group(self) -> None:
         src = self._pick()
-        task_id = src.next_task % max(1, getattr(src.env, "num_tasks", 1 << 30))
-        src.next_task += 1
+        if src.sampler is not None:
+            task_id = src.sampler.sample()
+            src.next_task = getattr(src.sampler, "next", src.next_task)
+        else:
+            task_id = src.next_task % max(1, getattr(src.env, "num_tasks", 1 << 30))
+            src.next_task += 1
         gid = uuid.uuid4().hex
         for _ in range(src.group_size):
             t = asyncio.create_task(self._episode(src, task_id, gid))
@@ -167,6 +172,8 @@ class TrainSink:
             self.stats["groups_dropped_stale"] += 1
             return
         await src.algo.score_group(group)
+        if src.sampler is not None:
+            src.sampler.update(group[0].task_id, sum(r.reward for r in group) / len(group))
         advs = [r.advantage or 0.0 for r in group]
         for gate in src.gates:
             if all(gate.reject_min <= a <= gate.reject_max for a in advs):
@@ -266,8 +273,12 @@ class Orchestrator:
         for s in c.train.source:
             algo = setup_algorithm(c.source_algo(s), self.client)
             gates = list((s.curriculum.gates.values()) if s.curriculum else [])
-            self.sources.append(Source(load_environment(s), algo, c.source_group_size(s), c.source_sampling(s),
-                                       s.ratio, gates=gates))
+            env = load_environment(s)
+            from .curriculum import build_sampler
+
+            sampler = build_sampler(s.curriculum, getattr(env, "num_tasks", 1 << 30)) if s.curriculum else None
+            self.sources.append(Source(env, algo, c.source_group_size(s), c.source_sampling(s), s.ratio, gates=gates,
+                                       sampler=sampler))
         self.sender = setup_batch_sender(self.run_dir, c.num_train_workers, c.rollout_transport)
         await self.admin.wait_for_ready()
         self.controller = ConcurrencyController(c.concurrency, c.group_size)
@@ -297,6 +308,7 @@ class Orchestrator:
         tmp = p.with_suffix(".tmp")
         state = {"step": step, "policy_version": self.policy.version,
                  "next_task": [s.next_task for s in self.sources],
+                 "sampler": [s.sampler.state_dict() if s.sampler is not None else None for s in self.sources],
                  "algo": [s.algo.state_dict() if hasattr(s.algo, "state_dict") else None for s in self.sources]}
         torch.save(state, tmp)
         tmp.replace(p)
@@ -310,6 +322,9 @@ class Orchestrator:
             return
         state = torch.load(self._ckpt_path(step), weights_only=False)
         self.step = state["step"] + 1
+        for s, sd in zip(self.sources, state.get("sampler", [])):
+            if s.sampler is not None and sd is not None:
+                s.sampler.load_state_dict(sd)
         for s, nt, a in zip(self.sources, state["next_task"], state["algo"]):
             s.next_task = nt
             if a is not None and hasattr(s.algo, "load_state_dict"):

@@ -169,7 +169,14 @@ class RLTrainer:
             seq.routed_experts = mb.routed_experts
         if self.cp_ctx is not None:
             ids, labels, inv_temp, seq = self.cp_ctx.shard_inputs(ids, labels, inv_temp, seq)
-        hidden = self.model(ids, seq)
+        offload = self.config.model.ac_offloading
+        if offload is not None and dev.type == "cuda":
+            from ...utils.act_offloading import OffloadActivations
+
+            with OffloadActivations(pin_memory=offload.pin_memory, max_inflight=offload.max_inflight_activations):
+                hidden = self.model(ids, seq)
+        else:
+            hidden = self.model(ids, seq)
         logprobs, entropy = self.model.logprobs_entropy(hidden, labels, inv_temp)
         if self.cp_ctx is not None:
             logprobs, entropy = self.cp_ctx.gather_outputs(logprobs, entropy)
@@ -242,6 +249,15 @@ class RLTrainer:
     # ------------------------------------------------------------------ loop
     def run(self) -> None:
         cfg = self.config
+        heartbeat = metrics_server = None
+        if self.world.is_master and cfg.heartbeat is not None:
+            from ...utils.heartbeat import Heartbeat
+
+            heartbeat = Heartbeat(cfg.heartbeat.url)
+        if self.world.is_master and cfg.metrics_server is not None:
+            from ...utils.metrics_server import MetricsServer
+
+            metrics_server = MetricsServer(cfg.metrics_server.port, cfg.metrics_server.host).start()
         if self.weight_sender is not None and self.progress.step > 0:
             # resumed run: re-seed the (stateless) inference engines with the restored policy; a
             # fresh run starts from weights both sides already share
@@ -260,6 +276,10 @@ class RLTrainer:
                 self.ckpt.maybe_clean()
                 m["time/save_ckpt"] = time.perf_counter() - t0
             self.monitor.log(m, step)
+            if metrics_server is not None:
+                metrics_server.update(m, step)
+            if heartbeat is not None:
+                heartbeat.beat()
             if self.world.is_master:
                 self.logger.info(f"step {step} | loss {m['loss']:.4f} | entropy {m.get('entropy', 0):.3f} | "
                                  f"grad_norm {m['optim/grad_norm']:.3f} | {m['perf/throughput']:.0f} tok/s | "
@@ -272,6 +292,8 @@ class RLTrainer:
             if last not in self.ckpt.saved_steps:
                 self.ckpt.save(last, self.model, self.optimizer, self.progress, self.dataloader)
         self.monitor.finalize()
+        if metrics_server is not None:
+            metrics_server.stop()
 
 
 def train(config: TrainerConfig) -> RLTrainer:
