@@ -109,7 +109,7 @@ class ModelRunner:
             k = ops.qknorm_rope(k, at.k_norm.weight if at.k_norm is not None else None, pos_t, at.inv_freq, eps)
             cache.write(li, k, v, slots_t)
             o = self._attend(li, q, k, v.contiguous(), batch, starts, at.window, at.sinks)
-            a = at.o_proj(o.reshape(N, qd))
+            a = at.finish(o, x)
             x2, h = ops.add_rms_norm(a, h, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.eps)
             if layer.is_moe:
                 m = layer.mlp(x2, seq)

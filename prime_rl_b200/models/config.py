@@ -41,6 +41,8 @@ class ModelArch(BaseModel):
     sliding_window: int | None = None
     layer_types: list[str] | None = None       # per layer "full_attention" | "sliding_attention"
     attention_sinks: bool = False              # learnable per-head sink logit (GPT-OSS)
+    attn_gate: Literal["none", "per_head", "per_element"] = "none"   # softplus output gate (Laguna)
+    heads_per_layer: list[int] | None = None   # query heads of every layer when they differ (Laguna)
     # MoE
     num_experts: int = 0
     num_experts_per_tok: int = 0
@@ -54,6 +56,8 @@ class ModelArch(BaseModel):
     n_shared_experts: int = 0
     first_k_dense_replace: int = 0             # first k layers use a dense MLP
     mlp_only_layers: list[int] = []
+    mlp_layer_types: list[str] | None = None   # per layer "dense" | "sparse" (overrides the rules below)
+    shared_expert_intermediate_size: int = 0   # width of the shared expert when it differs from moe_intermediate_size
     decoder_sparse_step: int = 1
     initializer_range: float = 0.02
 
@@ -63,6 +67,8 @@ class ModelArch(BaseModel):
         return self.num_experts > 0
 
     def layer_is_moe(self, idx: int) -> bool:
+        if self.is_moe and self.mlp_layer_types is not None:
+            return self.mlp_layer_types[idx] == "sparse"
         if not self.is_moe or idx in self.mlp_only_layers or idx < self.first_k_dense_replace:
             return False
         return (idx + 1) % self.decoder_sparse_step == 0
@@ -73,6 +79,13 @@ class ModelArch(BaseModel):
         if self.layer_types is None:
             return self.sliding_window
         return self.sliding_window if self.layer_types[idx] == "sliding_attention" else None
+
+    def layer_heads(self, idx: int) -> int:
+        return self.heads_per_layer[idx] if self.heads_per_layer is not None else self.num_attention_heads
+
+    @property
+    def shared_width(self) -> int:
+        return self.shared_expert_intermediate_size or self.moe_intermediate_size * self.n_shared_experts
 
     @property
     def rotary_dim(self) -> int:
@@ -170,6 +183,17 @@ class ModelArch(BaseModel):
                      n_shared_experts=cfg.get("num_shared_experts", 0),
                      first_k_dense_replace=cfg.get("num_dense_layers", 0),
                      routed_scaling_factor=cfg.get("route_scale", 1.0))
+        elif mt == "laguna":
+            gating = cfg.get("gating", True)
+            n = cfg["num_hidden_layers"]
+            d.update(qk_norm=True, num_experts=cfg.get("num_experts", cfg.get("num_local_experts", 0)),
+                     num_experts_per_tok=cfg["num_experts_per_tok"],
+                     moe_intermediate_size=cfg["moe_intermediate_size"], score_func="sigmoid", norm_topk_prob=True,
+                     router_bias=True, routed_scaling_factor=cfg.get("moe_routed_scaling_factor", 1.0),
+                     n_shared_experts=1, shared_expert_intermediate_size=cfg.get("shared_expert_intermediate_size", 0),
+                     mlp_layer_types=cfg.get("mlp_layer_types") or ["sparse"] * n,
+                     heads_per_layer=cfg.get("num_attention_heads_per_layer"),
+                     attn_gate="none" if not gating else ("per_head" if gating == "per-head" else "per_element"))
         else:
             raise ValueError(f"unsupported model_type '{mt}'")
         return cls(**d)
@@ -182,7 +206,7 @@ class ModelArch(BaseModel):
         arch_names = {"llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
                       "qwen3_moe": "Qwen3MoeForCausalLM", "glm4_moe": "Glm4MoeForCausalLM",
                       "gpt_oss": "GptOssForCausalLM", "minimax_m2": "MiniMaxM2ForCausalLM",
-                      "afmoe": "AfmoeForCausalLM"}
+                      "afmoe": "AfmoeForCausalLM", "laguna": "LagunaForCausalLM"}
         cfg: dict[str, Any] = dict(
             architectures=[arch_names.get(self.model_type, "LlamaForCausalLM")], model_type=self.model_type,
             vocab_size=self.vocab_size, hidden_size=self.hidden_size, num_hidden_layers=self.num_hidden_layers,
@@ -198,6 +222,13 @@ class ModelArch(BaseModel):
                            routed_scaling_factor=self.routed_scaling_factor, use_qk_norm=self.qk_norm)
             elif self.model_type in ("gpt_oss", "minimax_m2"):
                 cfg.update(num_local_experts=self.num_experts)
+            elif self.model_type == "laguna":
+                gating = {"none": False, "per_head": "per-head", "per_element": True}[self.attn_gate]
+                cfg.update(num_experts=self.num_experts, mlp_layer_types=self.mlp_layer_types, gating=gating,
+                           shared_expert_intermediate_size=self.shared_width,
+                           num_attention_heads_per_layer=self.heads_per_layer or
+                           [self.num_attention_heads] * self.num_hidden_layers,
+                           moe_routed_scaling_factor=self.routed_scaling_factor)
             else:
                 cfg.update(num_experts=self.num_experts, mlp_only_layers=self.mlp_only_layers,
                            decoder_sparse_step=self.decoder_sparse_step)
@@ -219,6 +250,13 @@ PRESETS: dict[str, dict[str, Any]] = {
     "qwen3-30b-a3b": dict(model_type="qwen3_moe", hidden_size=2048, num_hidden_layers=48, num_attention_heads=32,
                           num_key_value_heads=4, head_dim=128, intermediate_size=6144, num_experts=128,
                           num_experts_per_tok=8, moe_intermediate_size=768, norm_topk_prob=True),
+    "tiny-laguna": dict(model_type="laguna", hidden_size=128, num_hidden_layers=3, num_attention_heads=4,
+                        num_key_value_heads=2, head_dim=32, intermediate_size=256, vocab_size=512, qk_norm=True,
+                        num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, score_func="sigmoid",
+                        router_bias=True, n_shared_experts=1, shared_expert_intermediate_size=96,
+                        mlp_layer_types=["dense", "sparse", "sparse"], heads_per_layer=[4, 2, 4],
+                        sliding_window=16, layer_types=["sliding_attention", "full_attention", "sliding_attention"],
+                        attn_gate="per_head", max_position_embeddings=512),
     "tiny-qwen3-moe": dict(model_type="qwen3_moe", hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
                            num_key_value_heads=2, head_dim=64, intermediate_size=512, num_experts=8,
                            num_experts_per_tok=2, moe_intermediate_size=512, vocab_size=4096),

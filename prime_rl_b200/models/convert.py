@@ -135,12 +135,13 @@ class Chain:
 
 # ---------------------------------------------------------------------- layout chains
 def native_to_prime_chain(arch: ModelArch) -> Chain:
-    q, kv = arch.q_dim, arch.kv_dim
+    kv = arch.kv_dim
     ops: list = [
+        # the query width comes from the tensor: families with per-layer head counts differ by layer
         SplitConcat("self_attn.qkv_proj.weight", ["self_attn.q_proj.weight", "self_attn.k_proj.weight",
-                                                  "self_attn.v_proj.weight"], lambda v: [q, kv, kv]),
+                                                  "self_attn.v_proj.weight"], lambda v: [v.shape[0] - 2 * kv, kv, kv]),
         SplitConcat("self_attn.qkv_proj.bias", ["self_attn.q_proj.bias", "self_attn.k_proj.bias",
-                                                "self_attn.v_proj.bias"], lambda v: [q, kv, kv]),
+                                                "self_attn.v_proj.bias"], lambda v: [v.shape[0] - 2 * kv, kv, kv]),
         SplitConcat("mlp.experts.gate_up_proj", ["mlp.experts.gate_proj", "mlp.experts.up_proj"],
                     lambda v: [v.shape[1] // 2, v.shape[1] // 2], dim=1),
         SplitConcat("shared_experts.gate_up_proj.weight", ["shared_experts.gate_proj.weight",
@@ -154,6 +155,13 @@ def native_to_prime_chain(arch: ModelArch) -> Chain:
 
 def prime_to_hf_chain(arch: ModelArch) -> Chain:
     ops: list = []
+    if arch.model_type == "laguna":
+        # Laguna checkpoints name the shared expert in the singular and keep the selection bias under `experts`
+        ops += [
+            Rename(r"mlp\.shared_experts\.", r"mlp.shared_expert.", r"mlp\.shared_expert\.", r"mlp.shared_experts."),
+            Rename(r"mlp\.router\.e_score_correction_bias$", r"mlp.experts.e_score_correction_bias",
+                   r"mlp\.experts\.e_score_correction_bias$", r"mlp.router.e_score_correction_bias"),
+        ]
     if arch.is_moe:
         ops += [
             Rename(r"mlp\.router\.gate\.(weight|bias)$", r"mlp.gate.\1", r"mlp\.gate\.(weight|bias)$",

@@ -111,12 +111,19 @@ class Attention(nn.Module):
         super().__init__()
         self.arch, self.layer_idx, self.backend = arch, layer_idx, attn_backend
         H, D = arch.hidden_size, arch.head_dim
-        self.nq, self.nkv, self.D = arch.num_attention_heads, arch.num_key_value_heads, D
+        self.nq, self.nkv, self.D = arch.layer_heads(layer_idx), arch.num_key_value_heads, D
+        q_dim = self.nq * D
         std = arch.initializer_range
-        self.qkv_proj = Linear(H, arch.q_dim + 2 * arch.kv_dim, bias=arch.attention_bias, std=std, dtype=dtype,
+        self.qkv_proj = Linear(H, q_dim + 2 * arch.kv_dim, bias=arch.attention_bias, std=std, dtype=dtype,
                                device=device)
-        self.o_proj = Linear(arch.q_dim, H, bias=arch.attention_bias and arch.model_type == "gpt_oss", std=std,
+        self.o_proj = Linear(q_dim, H, bias=arch.attention_bias and arch.model_type == "gpt_oss", std=std,
                              dtype=dtype, device=device)
+        # softplus output gate computed from the layer input: one value per head or per channel
+        # (reference: LagunaFlashAttention, src/prime_rl/trainer/models/laguna/modeling_laguna.py:101-165)
+        self.g_proj = None
+        if arch.attn_gate != "none":
+            self.g_proj = Linear(H, self.nq if arch.attn_gate == "per_head" else q_dim, std=std, dtype=dtype,
+                                 device=device)
         if arch.qk_norm:
             self.q_norm = RMSNorm(D, arch.rms_norm_eps, dtype=dtype, device=device)
             self.k_norm = RMSNorm(D, arch.rms_norm_eps, dtype=dtype, device=device)
@@ -141,7 +148,15 @@ class Attention(nn.Module):
             o = attn_ops.attention(q, k, v, seq.cu_seqlens, seq.max_seqlen, causal=True, window=self.window,
                                    sinks=self.sinks, backend=self.backend, cache=seq.attn_cache,
                                    cache_key=self.layer_idx)
-        return self.o_proj(o.reshape(T, q_dim))
+        return self.finish(o, x)
+
+    def finish(self, o: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+        """Output gate (when the family has one) and output projection; ``x`` is the layer input."""
+        T = o.shape[0]
+        if self.g_proj is not None:
+            gate = torch.nn.functional.softplus(self.g_proj(x).float()).to(o.dtype)
+            o = o * (gate.unsqueeze(-1) if self.arch.attn_gate == "per_head" else gate.view(T, self.nq, self.D))
+        return self.o_proj(o.reshape(T, self.nq * self.D))
 
 
 _ACT = {"silu": act_ops.SWIGLU, "swiglu_clamped": act_ops.SWIGLU_CLAMPED, "relu2": act_ops.RELU2}
@@ -258,7 +273,7 @@ class MoE(nn.Module):
         self.router = Router(arch, dtype=dtype, device=device)
         self.experts = GroupedExperts(arch, dtype=dtype, device=device)
         if arch.n_shared_experts > 0:
-            self.shared_experts = DenseMLP(arch, arch.moe_intermediate_size * arch.n_shared_experts, dtype=dtype,
+            self.shared_experts = DenseMLP(arch, arch.shared_width, dtype=dtype,
                                            device=device)
         else:
             self.shared_experts = None

@@ -151,7 +151,7 @@ def apply_lora(model: CausalLM, rank: int, alpha: float, target_modules: list[st
                     raise ValueError(f"{name}: LoRA must target all of {members} or none (fused projection)")
                 continue
             if leaf == "qkv_proj":
-                segs = [arch.q_dim, arch.kv_dim, arch.kv_dim]
+                segs = [mod.weight.shape[0] - 2 * arch.kv_dim, arch.kv_dim, arch.kv_dim]
             elif leaf == "gate_up_proj":
                 half = mod.weight.shape[0] // 2
                 segs = [half, half]

@@ -110,3 +110,41 @@ def test_hf_config_interchange():
     assert arch.param_count() > 30e9 and arch.param_count(active_only=True) < 3.5e9
     again = ModelArch.from_hf_config(arch.to_hf_config())
     assert again.num_experts == 128 and again.moe_intermediate_size == 768 and again.qk_norm
+
+
+def test_laguna_family_gating_per_layer_heads_and_round_trip(tmp_path):
+    """Attention output gate, per-layer head counts, dense / sparse layer list, shared expert of
+    its own width; HF config and checkpoint names round-trip."""
+    import torch
+
+    from prime_rl_b200.models import ModelArch, build_model, convert, resolve_arch
+    from prime_rl_b200.models.layers import MoE, SeqInfo
+
+    arch = resolve_arch("tiny-laguna")
+    model = build_model(arch, device="cpu", dtype=torch.float32, seed=0)
+    layers = model.model.layers
+    assert [l.self_attn.nq for l in layers] == [4, 2, 4]
+    assert [isinstance(l.mlp, MoE) for l in layers] == [False, True, True]
+    assert layers[1].self_attn.g_proj.weight.shape == (2, arch.hidden_size)
+    assert layers[1].mlp.shared_experts.down_proj.weight.shape[1] == 96
+    assert [l.self_attn.window for l in layers] == [16, None, 16]
+    ids = torch.randint(0, arch.vocab_size, (40,))
+    seq = SeqInfo(torch.tensor([0, 25, 40], dtype=torch.int32), 25, torch.cat([torch.arange(25), torch.arange(15)]).int())
+    h = model(ids, seq)
+    assert h.shape == (40, arch.hidden_size) and torch.isfinite(h).all()
+    h.sum().backward()
+    assert layers[1].self_attn.g_proj.weight.grad.abs().sum() > 0
+    # config round trip
+    again = ModelArch.from_hf_config(arch.to_hf_config())
+    assert again.heads_per_layer == [4, 2, 4] and again.attn_gate == "per_head" and again.shared_width == 96
+    assert again.mlp_layer_types == ["dense", "sparse", "sparse"]
+    # names: singular shared expert and the bias under `experts`, and back
+    hf = convert.model_state(model, "hf")
+    assert "model.layers.1.mlp.shared_expert.gate_proj.weight" in hf
+    assert "model.layers.1.mlp.experts.e_score_correction_bias" in hf
+    assert "model.layers.1.self_attn.g_proj.weight" in hf
+    assert hf["model.layers.1.self_attn.q_proj.weight"].shape[0] == 2 * arch.head_dim
+    other = build_model(arch, device="cpu", dtype=torch.float32, seed=1)
+    convert.load_model_state(other, hf, "hf")
+    for (n, a), (_, b) in zip(model.state_dict().items(), other.state_dict().items()):
+        assert torch.equal(a, b), n
