@@ -31,6 +31,7 @@ def main(argv=None):
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--layers", type=int, default=None, help="debug: truncate the model")
+    ap.add_argument("--fp8", action="store_true", help="block-scaled fp8 weights (128x128 scales), 1x128 activation scales")
     ap.add_argument("--no-graphs", action="store_true", help="launch the decode step kernel by kernel")
     args = ap.parse_args(argv)
     dev = torch.device("cuda", 0)
@@ -46,7 +47,8 @@ def main(argv=None):
     total = args.prompt + budget + 2
     pages = args.batch * ((total + 15) // 16 + 1) + 64
     eng = Engine(model, num_pages=pages, page_size=16, max_running=args.batch, max_prefill_tokens=16384,
-                 enable_prefix_cache=False, use_cuda_graphs=not args.no_graphs, max_model_len=total + 16)
+                 enable_prefix_cache=False, use_cuda_graphs=not args.no_graphs, max_model_len=total + 16,
+                 weight_dtype="fp8" if args.fp8 else "bf16")
     g = torch.Generator().manual_seed(0)
     params = SamplingParams(temperature=1.0, max_tokens=budget)
     for _ in range(args.batch):
@@ -74,7 +76,7 @@ def main(argv=None):
                       "batch": args.batch, "mean_running": toks / args.steps, "prompt_len": args.prompt, "steps": args.steps,
                       "decode_tokens_per_s": toks / dt, "ms_per_step": 1e3 * dt / args.steps,
                       "prefill_tokens_per_s": args.batch * args.prompt / t_prefill,
-                      "peak_memory_gib": torch.cuda.max_memory_allocated() / 2**30, "n_gpus": 1, "dtype": "bf16", "cuda_graphs": not args.no_graphs,
+                      "peak_memory_gib": torch.cuda.max_memory_allocated() / 2**30, "n_gpus": 1, "dtype": "fp8 weights / bf16 KV" if args.fp8 else "bf16", "cuda_graphs": not args.no_graphs,
                       "data": "synthetic (uniform random token ids, random-init weights)"}), flush=True)
 
 

@@ -52,9 +52,14 @@ class Request:
 class Engine:
     def __init__(self, model, *, num_pages: int = 4096, page_size: int = 16, max_running: int = 256,
                  max_prefill_tokens: int = 16384, eos_token_id: int | None = None, enable_prefix_cache: bool = True,
-                 use_cuda_graphs: bool = False, max_model_len: int = 8192):
+                 use_cuda_graphs: bool = False, max_model_len: int = 8192, weight_dtype: str = "bf16"):
         arch = model.arch
         self.model = model.eval()
+        self.weight_dtype = weight_dtype
+        if weight_dtype == "fp8":
+            from ..models.model import quantize_fp8_
+
+            quantize_fp8_(self.model)
         p = next(model.parameters())
         self.device = p.device
         self.cache = KVCache(arch.num_hidden_layers, num_pages, page_size, arch.num_key_value_heads, arch.head_dim,
@@ -297,6 +302,10 @@ class Engine:
 
         assert self.paused or self.thread is None, "update_weights requires a paused engine"
         load_hf_checkpoint(self.model, Path(weight_dir), strict=False)
+        if self.weight_dtype == "fp8":
+            from ..models.model import quantize_fp8_
+
+            quantize_fp8_(self.model)
         self.cache.blocks.clear_prefix_cache()
         self.policy_version += 1
 

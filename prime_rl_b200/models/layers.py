@@ -93,13 +93,35 @@ class Linear(nn.Module):
         self.bias = nn.Parameter(torch.zeros(out_dim, dtype=dtype, device=device)) if bias else None
         self.lora: LoRAAdapter | None = None
         self.std = std
+        self.fp8: tuple[torch.Tensor, torch.Tensor] | None = None    # (e4m3 weight, 128 x 128 scales): inference only
 
     def reset_parameters(self):
         _init(self.weight, self.std)
         if self.bias is not None:
             nn.init.zeros_(self.bias)
 
+    def quantize_fp8_(self) -> bool:
+        """(Re)builds the block-scaled fp8 copy of the weight used by no-grad forwards."""
+        if self.lora is not None or self.weight.shape[1] % 16 or not self.weight.is_cuda:
+            return False
+        from .fp8 import quantize_to_fp8_blockwise
+
+        q, s = quantize_to_fp8_blockwise(self.weight.data)
+        if self.fp8 is None:
+            self.fp8 = (q.view(torch.uint8).contiguous(), s.contiguous())
+        else:                           # keep the buffers (a peer-memory weight push may write into them)
+            self.fp8[0].copy_(q.view(torch.uint8))
+            self.fp8[1].copy_(s)
+        return True
+
     def forward(self, x):
+        if self.fp8 is not None and not torch.is_grad_enabled() and x.dtype == torch.bfloat16:
+            from ..ops import fp8 as fp8_ops
+
+            x2 = x.reshape(-1, x.shape[-1])
+            xq, xs = fp8_ops.quantize_act(x2)
+            y = fp8_ops.fp8_gemm(xq, xs, self.fp8[0], self.fp8[1]).reshape(*x.shape[:-1], self.weight.shape[0])
+            return y if self.bias is None else y + self.bias
         if self.lora is not None:
             y = lora_ops.lora_linear(x, self.weight, self.lora.lora_A, list(self.lora.lora_B), self.lora.scale)
             return y if self.bias is None else y + self.bias
@@ -243,12 +265,38 @@ class GroupedExperts(nn.Module):
         self.down_proj = nn.Parameter(torch.empty(E, H, I, dtype=dtype, device=device))
         self.lora_gate_up: LoRAAdapter | None = None
         self.lora_down: LoRAAdapter | None = None
+        self.fp8: dict[str, tuple[torch.Tensor, torch.Tensor]] | None = None   # inference-only fp8 copies
 
     def reset_parameters(self):
         _init(self.gate_up_proj, self.arch.initializer_range)
         _init(self.down_proj, self.arch.initializer_range)
 
+    def quantize_fp8_(self) -> bool:
+        if self.lora_gate_up is not None or self.lora_down is not None or not self.gate_up_proj.is_cuda:
+            return False
+        from .fp8 import quantize_to_fp8_blockwise
+
+        new = {}
+        for name in ("gate_up_proj", "down_proj"):
+            q, s = quantize_to_fp8_blockwise(getattr(self, name).data)
+            new[name] = (q.view(torch.uint8).contiguous(), s.contiguous())
+        if self.fp8 is None:
+            self.fp8 = new
+        else:
+            for name, (q, s) in new.items():
+                self.fp8[name][0].copy_(q)
+                self.fp8[name][1].copy_(s)
+        return True
+
     def forward(self, xp: torch.Tensor, block_expert: torch.Tensor, expert_offset: torch.Tensor) -> torch.Tensor:
+        if self.fp8 is not None and not torch.is_grad_enabled() and xp.dtype == torch.bfloat16:
+            from ..ops import fp8 as fp8_ops
+
+            xq, xs = fp8_ops.quantize_act(xp)
+            gu = fp8_ops.fp8_gemm(xq, xs, *self.fp8["gate_up_proj"], block_expert=block_expert)
+            h = ops.glu(gu, self.act, self.arch.swiglu_limit, self.arch.swiglu_alpha)
+            hq, hs = fp8_ops.quantize_act(h)
+            return fp8_ops.fp8_gemm(hq, hs, *self.fp8["down_proj"], block_expert=block_expert)
         if self.lora_gate_up is not None:
             l = self.lora_gate_up
             gu = lora_ops.lora_grouped_linear(xp, self.gate_up_proj, l.lora_A, list(l.lora_B), l.scale, block_expert,

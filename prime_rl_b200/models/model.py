@@ -182,6 +182,19 @@ def freeze_router(model: CausalLM) -> None:
             p.requires_grad_(False)
 
 
+def quantize_fp8_(model, skip: tuple[str, ...] = ("lm_head", "embed_tokens", "router", "g_proj")) -> int:
+    """Gives every eligible projection of ``model`` (dense linears and grouped experts) a
+    block-scaled fp8 copy that no-grad forwards use instead of the bf16 weight (the rollout
+    engine's ``weight_dtype = "fp8"``); call again after the bf16 weights changed. Returns the
+    number of quantised modules."""
+    n = 0
+    for name, mod in model.named_modules():
+        if any(s in name for s in skip) or not hasattr(mod, "quantize_fp8_"):
+            continue
+        n += bool(mod.quantize_fp8_())
+    return n
+
+
 def build_model(arch: ModelArch, *, device, dtype=torch.bfloat16, attn_backend: str = "auto", seed: int = 0,
                 init: bool = True) -> CausalLM:
     model = CausalLM(arch, attn_backend=attn_backend, dtype=dtype, device=device)

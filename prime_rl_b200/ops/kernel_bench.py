@@ -105,6 +105,36 @@ def bench_grouped(timer, args, dev):
             flops=2 * P * 2 * I * H)
 
 
+def bench_fp8(timer, args, dev):
+    from ..models.fp8 import quantize_to_fp8_blockwise
+    from . import fp8
+
+    M, N, K = args.tokens or 16384, 4096, 2048
+    x = torch.randn(M, K, device=dev).bfloat16()
+    w = torch.randn(N, K, device=dev).bfloat16()
+    wq, ws = quantize_to_fp8_blockwise(w)
+    wq = wq.view(torch.uint8)
+    xq, xs = fp8.quantize_act(x)
+    _report(f"fp8 block-scaled gemm {M}x{N}x{K}", timer(lambda: fp8.fp8_gemm(xq, xs, wq, ws)), flops=2 * M * N * K)
+    _report(f"activation quantiser {M}x{K} (bf16 -> e4m3 + 1x128 scales)", timer(lambda: fp8.quantize_act(x)),
+            bytes_=M * K * 3)
+    # decode-shaped grouped experts: 256 tokens x top-8 over 128 experts (weight-bandwidth bound)
+    E, H, I = 128, 2048, 768
+    P = E * 128
+    be = torch.arange(E, dtype=torch.int32, device=dev)
+    xp = torch.randn(P, H, device=dev).bfloat16()
+    w1 = torch.randn(E, 2 * I, H, device=dev).bfloat16()
+    w1q, w1s = quantize_to_fp8_blockwise(w1)
+    w1q = w1q.view(torch.uint8)
+    xpq, xps = fp8.quantize_act(xp)
+    from .matmul import gemm
+
+    _report("decode grouped gate_up, bf16 weights (805 MB)", timer(lambda: gemm(xp, w1, block_expert=be)),
+            bytes_=w1.numel() * 2)
+    _report("decode grouped gate_up, fp8 weights (403 MB)",
+            timer(lambda: fp8.fp8_gemm(xpq, xps, w1q, w1s, block_expert=be)), bytes_=w1.numel())
+
+
 def bench_lm_head(timer, args, dev):
     from .lm_head import fused_logprob_entropy
 
@@ -176,7 +206,7 @@ def bench_norm(timer, args, dev):
     _report(f"rmsnorm fwd {T}x{H}", timer(lambda: rms_norm(x, w, 1e-6)), bytes_=2 * T * H * 2)
 
 
-OPS = {"gemm": bench_gemm, "grouped": bench_grouped, "lm_head": bench_lm_head, "flash_fwd": bench_flash_fwd,
+OPS = {"gemm": bench_gemm, "grouped": bench_grouped, "fp8": bench_fp8, "lm_head": bench_lm_head, "flash_fwd": bench_flash_fwd,
        "flash_bwd": bench_flash_bwd, "paged": bench_paged, "norm": bench_norm}
 
 

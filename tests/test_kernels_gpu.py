@@ -318,6 +318,40 @@ def test_gemm_extra_reduction_segment():
     _close(out.cpu()[used], ref[used], atol=0.3, rtol=2e-2)
 
 
+def test_fp8_block_scaled_gemm_dense_and_grouped():
+    """e4m3 operands with 1 x 128 / 128 x 128 scales against dequantise-then-multiply in fp32."""
+    from prime_rl_b200.models.fp8 import quantize_to_fp8_blockwise
+    from prime_rl_b200.ops import fp8
+    M, N, K = 300, 520, 400
+    x = _rand(M, K)
+    w = _rand(N, K)
+    xq, xs = fp8.quantize_act(x)
+    xq_r, xs_r = fp8.quantize_act(x.cpu())
+    assert torch.allclose(xs.cpu(), xs_r, rtol=1e-6)
+    assert (xq.cpu().view(torch.float8_e4m3fn).float() - xq_r.view(torch.float8_e4m3fn).float()).abs().max() <= 32
+    wq, ws = quantize_to_fp8_blockwise(w)
+    out = fp8.fp8_gemm(xq, xs, wq.view(torch.uint8), ws)
+    rt.check_status()
+    ref = fp8.fp8_gemm_ref(xq, xs, wq, ws)
+    _close(out, ref, atol=0.3, rtol=2e-2)
+    # the quantised product stays close to the bf16 one
+    full = x.float() @ w.float().t()
+    assert ((out.float() - full).norm() / full.norm()) < 0.08
+    # grouped
+    counts = torch.tensor([130, 0, 5, 256], dtype=torch.int32)
+    offs, be, P = _blocks(counts)
+    E = 4
+    xp = _rand(P, K)
+    wg = _rand(E, N, K)
+    xpq, xps = fp8.quantize_act(xp)
+    wgq, wgs = quantize_to_fp8_blockwise(wg)
+    out = fp8.fp8_gemm(xpq, xps, wgq.view(torch.uint8), wgs, block_expert=be.to(DEV))
+    rt.check_status()
+    ref = fp8.fp8_gemm_ref(xpq.cpu(), xps.cpu(), wgq.cpu(), wgs.cpu(), be)
+    used = (be >= 0).repeat_interleave(128)
+    _close(out.cpu()[used], ref[used], atol=0.3, rtol=2e-2)
+
+
 def test_lora_linear_and_grouped():
     from prime_rl_b200.ops import lora
     T, IN, r = 300, 256, 16
