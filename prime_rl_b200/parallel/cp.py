@@ -51,9 +51,11 @@ class _AllToAll(torch.autograd.Function):
     same exchange."""
 
     @staticmethod
-    def forward(ctx, x, group):
-        ctx.group = group
+    def forward(ctx, x, group, p2p=None):
+        ctx.group, ctx.p2p = group, p2p
         x = x.contiguous()
+        if p2p is not None:
+            return p2p(x)             # peer-memory exchange (parallel/p2p_a2a.py)
         out = torch.empty_like(x)
         dist.all_to_all_single(out, x, group=group)
         return out
@@ -61,9 +63,11 @@ class _AllToAll(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         dy = dy.contiguous()          # empty_like of a permuted gradient would keep its strides
+        if ctx.p2p is not None:
+            return ctx.p2p(dy), None, None
         dx = torch.empty_like(dy)
         dist.all_to_all_single(dx, dy, group=ctx.group)
-        return dx, None
+        return dx, None, None
 
 
 def attention_offset_ref(q, k, v, q_pos, k_pos, q_doc, k_doc, *, window=None, sinks=None, scale=None):
@@ -86,8 +90,19 @@ def attention_offset_ref(q, k, v, q_pos, k_pos, q_doc, k_doc, *, window=None, si
 
 
 class ContextParallel:
-    def __init__(self, group, cp: int, rank: int, style: str = "ring"):
+    def __init__(self, group, cp: int, rank: int, style: str = "ring", p2p_all_to_all: bool = False):
         self.group, self.cp, self.rank, self.style = group, cp, rank, style
+        # Ulysses exchanges over NVLink peer memory instead of NCCL (built on first use, sized by the first block)
+        self.use_p2p, self._p2p = p2p_all_to_all, None
+
+    def _exchange(self, x):
+        if self.use_p2p and x.is_cuda:
+            if self._p2p is None:
+                from .p2p_a2a import P2PAllToAll
+
+                self._p2p = P2PAllToAll(self.group, 4 * x[0].numel() * x.element_size(), x.device)
+            return _AllToAll.apply(x, self.group, self._p2p)
+        return _AllToAll.apply(x, self.group)
 
     # ------------------------------------------------------------------ sharding
     def shard(self, t: torch.Tensor) -> torch.Tensor:
@@ -155,10 +170,10 @@ class ContextParallel:
 
         def seq_to_head(x, H):      # [Tl, H, D] -> [T, H/cp, D]
             x = x.reshape(Tl, cp, H // cp, D).permute(1, 0, 2, 3).contiguous()      # [cp, Tl, H/cp, D]
-            return _AllToAll.apply(x, self.group).reshape(cp * Tl, H // cp, D)
+            return self._exchange(x).reshape(cp * Tl, H // cp, D)
 
         def head_to_seq(x, H):      # [T, H/cp, D] -> [Tl, H, D]
-            x = _AllToAll.apply(x.reshape(cp, Tl, H // cp, D).contiguous(), self.group)   # [cp(head blk), Tl, H/cp, D]
+            x = self._exchange(x.reshape(cp, Tl, H // cp, D).contiguous())   # [cp(head blk), Tl, H/cp, D]
             return x.permute(1, 0, 2, 3).reshape(Tl, H, D)
 
         qf, kf, vf = seq_to_head(q, Hq), seq_to_head(k, Hkv), seq_to_head(v.contiguous(), Hkv)

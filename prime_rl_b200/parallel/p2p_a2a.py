@@ -1,0 +1,120 @@
+"""Equal-split all-to-all over NVLink peer memory (the sequence <-> head exchange of Ulysses
+context parallelism): every rank stores block ``d`` of its input straight into rank ``d``'s
+receive buffer with a copy kernel (``csrc/weight_push.cu: weight_copy_kernel``, plain 16-byte
+peer stores), then raises an epoch flag there (``csrc/ep_p2p.cu``); the receiver waits for the
+flags of all senders (bounded) and reads its own memory. Two receive buffers alternate, and a
+sender reuses a buffer only after every peer has reported that it consumed the previous contents.
+
+Takes the place of ``dist.all_to_all_single`` in ``parallel/cp.py`` (the reference's Ulysses
+path, src/prime_rl/trainer/models/layers/ulysses_attn.py:53-152, uses NCCL).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _runtime as rt
+from .symm import SymmetricBuffer
+
+_K_DATA, _K_CONSUMED = 0, 1
+
+
+class P2PAllToAll:
+    def __init__(self, group, max_bytes_per_block: int, device: torch.device):
+        self.group, self.device = group, device
+        self.R, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.slot = (int(max_bytes_per_block) + 255) // 256 * 256
+        self.buf_bytes = self.R * self.slot
+        self.off_flags = 2 * self.buf_bytes
+        self.mem = SymmetricBuffer(group, self.off_flags + 256, device, zero=True)
+        self.flags = self.mem.local(torch.int32, self.off_flags, 2 * self.R)
+        self.p_flags = self.mem.offset_ptrs(self.off_flags)
+        self.local = [self.mem.local(torch.uint8, b * self.buf_bytes, self.buf_bytes) for b in range(2)]
+        self.epoch = 0
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        """x: [R, ...] contiguous (block d goes to rank d). Returns [R, ...] (block s came from rank s)."""
+        lib, dev, R = rt.lib(), self.device, self.R
+        assert x.shape[0] == R and x.is_contiguous()
+        nbytes = x[0].numel() * x.element_size()
+        if nbytes > self.slot:
+            raise ValueError(f"block of {nbytes} bytes exceeds the {self.slot}-byte slots of this exchange")
+        self.epoch += 1
+        ep, b = self.epoch, self.epoch & 1
+        st, stream = rt.status_tensor(dev).data_ptr(), rt.stream_ptr(dev)
+        if ep > 2:      # the buffer was last used at epoch ep - 2: wait until every peer has consumed that
+            rt.check(lib.prb_ep_wait(self.flags.data_ptr(), R, _K_CONSUMED, ep - 2, st, stream), "prb_ep_wait")
+        base = b * self.buf_bytes + self.rank * self.slot
+        for d in range(R):
+            rt.check(lib.prb_weight_push(x[d].data_ptr(), self.mem.ptrs[d] + base, nbytes, stream), "prb_weight_push")
+        rt.check(lib.prb_ep_signal(self.p_flags, self.rank, R, _K_DATA, ep, stream), "prb_ep_signal")
+        rt.check(lib.prb_ep_wait(self.flags.data_ptr(), R, _K_DATA, ep, st, stream), "prb_ep_wait")
+        out = torch.empty_like(x)
+        flat = out.view(R, -1).view(torch.uint8) if x.dtype != torch.uint8 else out.view(R, -1)
+        flat.copy_(self.local[b].view(R, self.slot)[:, :nbytes])
+        rt.check(lib.prb_ep_signal(self.p_flags, self.rank, R, _K_CONSUMED, ep, stream), "prb_ep_signal")
+        return out
+
+    def close(self):
+        self.mem.close()
+
+
+def _selftest() -> int:
+    """python -m torch.distributed.run --nproc-per-node N -m prime_rl_b200.parallel.p2p_a2a"""
+    import os
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    group = dist.group.WORLD
+    torch.manual_seed(rank)
+    ok = True
+    op = P2PAllToAll(group, 8192 * 8 * 128 * 2, dev)
+    for it in range(5):                       # more than two rounds: both buffers get reused
+        x = torch.randn(world, 300 + it, 4, 128, device=dev).bfloat16()
+        got = op(x)
+        ref = torch.empty_like(x)
+        dist.all_to_all_single(ref, x, group=group)
+        ok &= bool(torch.equal(got, ref))
+    torch.cuda.synchronize()
+    rt.check_status()
+    t = torch.tensor([1.0 if ok else 0.0], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    ok = bool(t.item() > 0)
+    if rank == 0:
+        print("P2P_A2A_OK" if ok else "P2P_A2A_FAIL", flush=True)
+    if ok and os.environ.get("P2P_SELFTEST_TIMING", "1") == "1":
+        x = torch.randn(world, 8192 // world, 32 // world * 1, 128, device=dev).bfloat16()   # Ulysses q block
+        x = torch.randn(world, 8192, 8, 128, device=dev).bfloat16()
+        ref = torch.empty_like(x)
+        for name, fn in (("NCCL all_to_all_single", lambda: dist.all_to_all_single(ref, x, group=group)),
+                         ("peer-memory all-to-all", lambda: op(x))):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(10):
+                fn()
+            e.record()
+            torch.cuda.synchronize()
+            ms = torch.tensor([s.elapsed_time(e) / 10], device=dev)
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            if rank == 0:
+                sent = x.numel() * 2 * (world - 1) / world
+                print(f"P2P_A2A_TIMING {name}: {float(ms):.3f} ms ({sent / float(ms) / 1e6:.0f} GB/s sent per rank, "
+                      f"{x.numel() * 2 / 2**20:.0f} MiB per rank, {world} ranks)", flush=True)
+    op.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0 if ok else 1
+
+
+if __name__ == "__main__":
+    import sys
+
+    sys.exit(_selftest())

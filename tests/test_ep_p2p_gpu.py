@@ -39,3 +39,34 @@ def test_weight_push_over_peer_memory():
            "127.0.0.1", "--master-port", "29535", "-m", "prime_rl_b200.transports.weights.p2p_selftest"]
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0 and "P2P_WEIGHTS_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
+
+
+def test_all_to_all_over_peer_memory():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", P2P_SELFTEST_TIMING="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", "29536", "-m", "prime_rl_b200.parallel.p2p_a2a"]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and "P2P_A2A_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
+
+
+def test_bounded_peer_wait_reports_timeout_instead_of_hanging():
+    """A wait on a flag that nothing sets runs out (about 2 s of GPU time), records
+    kTimeoutPeerFlag in the status word and returns; the context stays usable."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from prime_rl_b200.ops import _runtime as rt
+
+    dev = torch.device("cuda", 0)
+    flags = torch.zeros(8, dtype=torch.int32, device=dev)
+    st = rt.status_tensor(dev)
+    st.zero_()
+    rc = rt.lib().prb_ep_wait(flags.data_ptr(), 2, 0, 1, st.data_ptr(), rt.stream_ptr(dev))
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(st.item()) == 5            # kTimeoutPeerFlag
+    with pytest.raises(Exception):
+        rt.check_status()
+    st.zero_()
+    assert float((torch.ones(4, device=dev) * 2).sum()) == 8.0      # the device still answers
