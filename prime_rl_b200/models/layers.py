@@ -288,7 +288,9 @@ class GroupedExperts(nn.Module):
                 self.fp8[name][1].copy_(s)
         return True
 
-    def forward(self, xp: torch.Tensor, block_expert: torch.Tensor, expert_offset: torch.Tensor) -> torch.Tensor:
+    def forward(self, xp: torch.Tensor, block_expert: torch.Tensor, expert_offset: torch.Tensor,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+        """``out`` (optional, ``[P, H]`` bf16): memory the last projection writes into."""
         if self.fp8 is not None and not torch.is_grad_enabled() and xp.dtype == torch.bfloat16:
             from ..ops import fp8 as fp8_ops
 
@@ -296,7 +298,7 @@ class GroupedExperts(nn.Module):
             gu = fp8_ops.fp8_gemm(xq, xs, *self.fp8["gate_up_proj"], block_expert=block_expert)
             h = ops.glu(gu, self.act, self.arch.swiglu_limit, self.arch.swiglu_alpha)
             hq, hs = fp8_ops.quantize_act(h)
-            return fp8_ops.fp8_gemm(hq, hs, *self.fp8["down_proj"], block_expert=block_expert)
+            return fp8_ops.fp8_gemm(hq, hs, *self.fp8["down_proj"], block_expert=block_expert, out=out)
         if self.lora_gate_up is not None:
             l = self.lora_gate_up
             gu = lora_ops.lora_grouped_linear(xp, self.gate_up_proj, l.lora_A, list(l.lora_B), l.scale, block_expert,
@@ -307,8 +309,8 @@ class GroupedExperts(nn.Module):
         if self.lora_down is not None:
             l = self.lora_down
             return lora_ops.lora_grouped_linear(h, self.down_proj, l.lora_A, list(l.lora_B), l.scale, block_expert,
-                                                expert_offset)
-        return ops.grouped_linear(h, self.down_proj, block_expert, expert_offset)
+                                                expert_offset, out=out)
+        return ops.grouped_linear(h, self.down_proj, block_expert, expert_offset, out=out)
 
 
 class MoE(nn.Module):

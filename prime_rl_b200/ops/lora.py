@@ -129,10 +129,11 @@ def lora_grouped_linear_ref(x, w, a_cat, b_list, scale, block_expert):
 
 class _LoRAGroupedLinear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, a_cat, scale, block_expert, expert_offset, *b_list):
+    def forward(ctx, x, w, a_cat, scale, block_expert, expert_offset, out, *b_list):
         t = gemm(x, a_cat, block_expert=block_expert)
         bd = _block_diag(b_list, scale)                    # [E, out, S*r]
-        y = gemm(x, w, block_expert=block_expert, ext=(t, bd))
+        y = gemm(x, w, block_expert=block_expert, ext=(t, bd), out=out)
+        ctx.grad_out = getattr(x, "_grad_out_buf", None)   # see ops/matmul.py _GroupedLinear
         ctx.save_for_backward(x, w, a_cat, t, block_expert, expert_offset, bd)
         ctx.scale = scale
         ctx.seg = [b.shape[1] for b in b_list]
@@ -156,14 +157,15 @@ class _LoRAGroupedLinear(torch.autograd.Function):
         da = kgrouped_gemm(dt, x, expert_offset, E).to(a_cat.dtype)
         dx = None
         if ctx.needs_input_grad[0]:
-            dx = gemm(dy, w, b_mn=True, block_expert=block_expert, ext=(dt, a_cat))
-        return (dx, None, da, None, None, None, *db)
+            go = ctx.grad_out if (ctx.grad_out is not None and ctx.grad_out.shape == x.shape) else None
+            dx = gemm(dy, w, b_mn=True, block_expert=block_expert, ext=(dt, a_cat), out=go)
+        return (dx, None, da, None, None, None, None, *db)
 
 
-def lora_grouped_linear(x, w, a_cat, b_list, scale: float, block_expert, expert_offset):
+def lora_grouped_linear(x, w, a_cat, b_list, scale: float, block_expert, expert_offset, out=None):
     """x: [P, in] permuted rows; w: [E, out, in] frozen; a_cat: [E, S*r, in]; b_list[s]: [E, out_s, r]."""
     if x.is_cuda and x.dtype == torch.bfloat16:
-        return _LoRAGroupedLinear.apply(x, w, a_cat, float(scale), block_expert, expert_offset, *b_list)
+        return _LoRAGroupedLinear.apply(x, w, a_cat, float(scale), block_expert, expert_offset, out, *b_list)
     # CPU: differentiable composition
     from .matmul import grouped_linear
 

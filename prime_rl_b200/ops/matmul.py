@@ -174,9 +174,12 @@ class _GroupedLinear(torch.autograd.Function):
     """Per-expert y = x @ w[e]^T over 128-row blocks; x is the permuted, padded row space."""
 
     @staticmethod
-    def forward(ctx, x, w, block_expert, expert_offset):
+    def forward(ctx, x, w, block_expert, expert_offset, out=None):
         ctx.save_for_backward(x, w, block_expert, expert_offset)
-        return gemm(x, w, block_expert=block_expert)
+        # a caller that owns the memory of the input gradient (the peer-memory EP dispatcher)
+        # hangs it on the input tensor; the backward then writes straight into it
+        ctx.grad_out = getattr(x, "_grad_out_buf", None)
+        return gemm(x, w, block_expert=block_expert, out=out)
 
     @staticmethod
     def backward(ctx, dy):
@@ -185,20 +188,26 @@ class _GroupedLinear(torch.autograd.Function):
             dy = dy.contiguous()
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            dx = gemm(dy, w, b_mn=True, block_expert=block_expert)
+            go = ctx.grad_out if (ctx.grad_out is not None and ctx.grad_out.shape == x.shape) else None
+            dx = gemm(dy, w, b_mn=True, block_expert=block_expert, out=go)
         if ctx.needs_input_grad[1]:
             dw = grouped_wgrad(dy, x, expert_offset, w.shape[0])
-        return dx, dw, None, None
+        return dx, dw, None, None, None
 
 
-def grouped_linear(x, w, block_expert, expert_offset):
-    return _GroupedLinear.apply(x, w, block_expert, expert_offset)
+def grouped_linear(x, w, block_expert, expert_offset, out=None):
+    return _GroupedLinear.apply(x, w, block_expert, expert_offset, out)
 
 
 def grouped_wgrad(dy: torch.Tensor, x: torch.Tensor, expert_offset: torch.Tensor, num_experts: int) -> torch.Tensor:
     """dW[e] = dY_e^T @ X_e over the (128-aligned) row range of each expert."""
     E = num_experts
     N, K = dy.shape[1], x.shape[1]
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        # one k-grouped launch over the experts' row ranges, no host read of the offsets
+        from .lora import kgrouped_gemm
+
+        return kgrouped_gemm(dy, x, expert_offset, E, out_dtype=x.dtype)
     dw = torch.empty(E, N, K, dtype=x.dtype, device=x.device)
     offs = expert_offset.tolist()
     for e in range(E):

@@ -99,7 +99,8 @@ class _Dispatch(torch.autograd.Function):
                                  sh.flags.data_ptr(), sh.rank, sh.R, sh.E, sh.H, K_DATA_X, ep, _status(dev),
                                  rt.stream_ptr(dev)), "prb_ep_recv")
         ctx.route = route
-        return sh.xbuf.view(sh.cap, sh.H)        # a fresh tensor object over the shared buffer
+        xin = sh.xbuf.view(sh.cap, sh.H)         # a fresh tensor object over the shared buffer
+        return xin
 
     @staticmethod
     def backward(ctx, g):
@@ -196,5 +197,10 @@ class P2PDispatcher:
         route.hist = sh.hist.clone()                              # the table is reused by the next call
         route.pos = torch.empty(T, k, dtype=torch.int32, device=dev)
         xin = _Dispatch.apply(x, route)
-        yp = experts(xin, route.block_expert, route.expert_offset)
+        # the experts write their output and their input gradient straight into the symmetric buffers
+        xin._grad_out_buf = sh.dxbuf
+        try:
+            yp = experts(xin, route.block_expert, route.expert_offset, out=sh.ybuf.view(sh.cap, sh.H))
+        except TypeError:                       # an experts callable without the `out` argument
+            yp = experts(xin, route.block_expert, route.expert_offset)
         return _Combine.apply(yp, w, route)
