@@ -154,6 +154,7 @@ class P2PMoEDispatchConfig(BaseConfig):
 
     type: Literal["p2p"] = "p2p"
     num_sms: int = Field(32, ge=1)
+    capacity_factor: float = Field(2.0, gt=0)   # receive-buffer rows as a multiple of the rows a rank sends
 
 
 MoEDispatchConfig: TypeAlias = Annotated[

@@ -102,10 +102,12 @@ def install_expert_parallel(model, dims, moe_cfg=None) -> None:
                 for b in ad.lora_B:
                     b.data = b.data[ep_rank * El:(ep_rank + 1) * El].clone()
                     b._is_expert_shard = True
-        if kind == "p2p":
+        if kind in ("p2p", "deepep"):
             from .ep_p2p import P2PDispatcher
 
-            moe.dispatcher = P2PDispatcher(group, ep, E)
+            moe.dispatcher = P2PDispatcher(group, ep, E,
+                                           capacity_factor=getattr(getattr(moe_cfg, "dispatch", None),
+                                                                   "capacity_factor", 2.0))
         else:
             moe.dispatcher = TorchA2ADispatcher(group, ep, E)
         moe.ep_rank, moe.ep = ep_rank, ep

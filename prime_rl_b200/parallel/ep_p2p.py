@@ -163,12 +163,18 @@ class P2PDispatcher:
     receive as a multiple of the rows it sends (``T * k``); an overflow is reported through the
     kernel status word (``ops._runtime.check_status``)."""
 
-    def __init__(self, group, ep: int, num_experts: int, capacity_factor: float = 2.0):
+    def __init__(self, group, ep: int, num_experts: int, capacity_factor: float = 2.0, max_tokens: int | None = None):
         self.group, self.ep, self.E = group, ep, num_experts
         self.E_local = num_experts // ep
         self.capacity_factor = capacity_factor
+        # Tokens per rank and call the buffers are sized for. Every rank must derive the SAME
+        # capacity: the symmetric buffers have one layout, and peers compute addresses inside each
+        # other's allocation from it. When not given, the first call agrees on the maximum over the
+        # ranks (one host synchronisation, once).
+        self.max_tokens = max_tokens
 
-    def _cap(self, T: int, k: int) -> int:
+    def _cap(self, k: int) -> int:
+        T = self.max_tokens
         rows = int(T * k * self.capacity_factor) + self.E_local * 128
         return min(max(rows, 1024), self.ep * T * k + self.E_local * 128) // 128 * 128 + 128
 
@@ -176,7 +182,14 @@ class P2PDispatcher:
         T, k = idx.shape
         dev = x.device
         lib = rt.lib()
-        sh = _Shared.get(self.group, self.ep, self.E, x.shape[1], self._cap(T, k), dev)
+        if self.max_tokens is None:
+            t = torch.tensor([T], dtype=torch.int64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+            self.max_tokens = int(t.item())
+        if T > self.max_tokens:
+            raise ValueError(f"{T} tokens in one call, but the dispatcher's buffers are sized for {self.max_tokens} "
+                             "(pass max_tokens = tokens per rank and micro-batch)")
+        sh = _Shared.get(self.group, self.ep, self.E, x.shape[1], self._cap(k), dev)
         idx = idx.contiguous()
         counts = counts.to(torch.int32).contiguous()
         local = moe_ops.build_plan(idx, counts, self.E)          # rank of every pair inside its expert

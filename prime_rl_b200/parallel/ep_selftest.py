@@ -61,7 +61,7 @@ def main() -> int:
         return ex, x, idx.to(torch.int32).contiguous(), w.detach(), counts, dout
 
     # ---- numerics on a small, ragged case (some experts get no token)
-    ex, x, idx, w, counts, dout = setup(T=300 + 17 * rank, E=8 * world, H=256, I=128, k=2)
+    ex, x, idx, w, counts, dout = setup(T=300 + 117 * rank, E=8 * world, H=256, I=128, k=2)
     ref = _run(TorchA2ADispatcher(group, world, 8 * world), ex, x, idx, w, counts, dout)
     p2p = P2PDispatcher(group, world, 8 * world, capacity_factor=float(world))
     got = _run(p2p, ex, x, idx, w, counts, dout)
