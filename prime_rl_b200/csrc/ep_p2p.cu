@@ -213,6 +213,60 @@ ep_wait_kernel(const int* __restrict__ flags_kind, int R, int epoch, int* status
   ep_wait_all(flags_kind, R, epoch, status);
 }
 
+// Equal-split all-to-all, send side: blockIdx.y = destination rank; block d of `src` (bytes16
+// 16-byte units) goes to slot `rank` of rank d's receive buffer. The last CTA raises the data flag
+// on every peer.
+__global__ void __launch_bounds__(256)
+a2a_push_kernel(const uint4* __restrict__ src, EpPeers dst, EpPeers flags, long long bytes16, long long slot16,
+                long long buf_off16, unsigned* __restrict__ done_counter, int rank, int R, int kind, int epoch) {
+  const int d = blockIdx.y;
+  const uint4* s = src + static_cast<long long>(d) * bytes16;
+  uint4* o = reinterpret_cast<uint4*>(dst.buf[d]) + buf_off16 + static_cast<long long>(rank) * slot16;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < bytes16;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    o[i] = s[i];
+  __threadfence_system();
+  __syncthreads();
+  __shared__ unsigned s_last;
+  if (threadIdx.x == 0) s_last = (atomicAdd(done_counter, 1u) == gridDim.x * gridDim.y - 1) ? 1u : 0u;
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    if (threadIdx.x < R) {
+      volatile int* f = reinterpret_cast<int*>(flags.buf[threadIdx.x]) + kind * R + rank;
+      *f = epoch;
+    }
+    if (threadIdx.x == 0) *done_counter = 0;
+  }
+}
+
+// Receive side: wait for every sender's data flag, copy the R slots of this rank's own buffer into
+// the (contiguous) output, then tell every peer that the buffer has been consumed.
+__global__ void __launch_bounds__(256)
+a2a_recv_kernel(const uint4* __restrict__ local, uint4* __restrict__ out, EpPeers flags, const int* __restrict__ my_flags,
+                long long bytes16, long long slot16, unsigned* __restrict__ done_counter, int rank, int R, int kind_data,
+                int kind_consumed, int epoch, int* status) {
+  if (!ep_wait_all(my_flags + kind_data * R, R, epoch, status)) return;
+  const int sblk = blockIdx.y;
+  const uint4* s = local + static_cast<long long>(sblk) * slot16;
+  uint4* o = out + static_cast<long long>(sblk) * bytes16;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < bytes16;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    o[i] = s[i];
+  __syncthreads();
+  __shared__ unsigned s_last;
+  if (threadIdx.x == 0) s_last = (atomicAdd(done_counter, 1u) == gridDim.x * gridDim.y - 1) ? 1u : 0u;
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    if (threadIdx.x < R) {
+      volatile int* f = reinterpret_cast<int*>(flags.buf[threadIdx.x]) + kind_consumed * R + rank;
+      *f = epoch;
+    }
+    if (threadIdx.x == 0) *done_counter = 0;
+  }
+}
+
 // One CTA per token: out[t] = sum_j w[t, j] * row(owner(t, j), pos[t, j]); w == nullptr -> 1.
 // dw (optional): dw[t, j] = <row(t, j), g[t]>.
 __global__ void __launch_bounds__(256)
@@ -352,6 +406,31 @@ PRB_API int prb_ep_signal(void* const* flag_peers, int rank, int R, int kind, in
 
 PRB_API int prb_ep_wait(const int* flags, int R, int kind, int epoch, int* status, void* stream) {
   prb::ep_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(flags + kind * R, R, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// src: R blocks of `bytes` each (multiple of 16); every peer buffer: [2 buffers][R slots of slot_bytes].
+PRB_API int prb_a2a_push(const void* src, void* const* buf_peers, void* const* flag_peers, long long bytes,
+                         long long slot_bytes, long long buf_off_bytes, unsigned* done_counter, int rank, int R,
+                         int kind, int epoch, void* stream) {
+  if (R > prb::kEpMaxRanks || (bytes % 16) || (slot_bytes % 16) || (buf_off_bytes % 16)) return -2;
+  long long per = (bytes / 16 + 255) / 256;
+  int gx = static_cast<int>(per < 1 ? 1 : (per > 148 ? 148 : per));
+  prb::a2a_push_kernel<<<dim3(gx, R), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint4*>(src), ep_peers(buf_peers, R), ep_peers(flag_peers, R), bytes / 16, slot_bytes / 16,
+      buf_off_bytes / 16, done_counter, rank, R, kind, epoch);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+PRB_API int prb_a2a_recv(const void* local, void* out, void* const* flag_peers, const int* my_flags, long long bytes,
+                         long long slot_bytes, unsigned* done_counter, int rank, int R, int kind_data,
+                         int kind_consumed, int epoch, int* status, void* stream) {
+  if (R > prb::kEpMaxRanks || (bytes % 16) || (slot_bytes % 16)) return -2;
+  long long per = (bytes / 16 + 255) / 256;
+  int gx = static_cast<int>(per < 1 ? 1 : (per > 148 ? 148 : per));
+  prb::a2a_recv_kernel<<<dim3(gx, R), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint4*>(local), reinterpret_cast<uint4*>(out), ep_peers(flag_peers, R), my_flags, bytes / 16,
+      slot_bytes / 16, done_counter, rank, R, kind_data, kind_consumed, epoch, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
