@@ -10,6 +10,8 @@ Retention follows ``keep_last`` / ``keep_interval``; only the master rank delete
 
 from __future__ import annotations
 
+import json
+
 import shutil
 from dataclasses import asdict, dataclass
 from pathlib import Path
@@ -64,6 +66,14 @@ class CheckpointManager:
         if not (self.config and self.config.skip_progress):
             app["progress"] = {k: torch.tensor(v) for k, v in asdict(progress).items()}
         dcp.save({"app": app}, checkpoint_id=str(path))
+        if dist.is_initialized():
+            dist.barrier()
+        if self.is_master:
+            # sizes of the shard files: a truncated copy must fail loudly at load time
+            sizes = {f.name: f.stat().st_size for f in path.glob("*.distcp")}
+            tmp = path / "sizes.json.tmp"
+            tmp.write_text(json.dumps(sizes))
+            tmp.replace(path / "sizes.json")
         if dataloader is not None and hasattr(dataloader, "state_dict") and \
                 not (self.config and self.config.skip_dataloader):
             dl = path / "dataloader"
@@ -81,6 +91,13 @@ class CheckpointManager:
         path = path or self.step_path(step)
         if not path.exists():
             raise FileNotFoundError(f"checkpoint not found: {path}")
+        sizes_file = path / "sizes.json"
+        if sizes_file.exists():
+            for name, size in json.loads(sizes_file.read_text()).items():
+                f = path / name
+                if not f.exists() or f.stat().st_size != size:
+                    have = f.stat().st_size if f.exists() else "missing"
+                    raise RuntimeError(f"checkpoint shard {f} is damaged: {have} bytes, expected {size}")
         app = {"model": convert.model_state(model, "prime", include_lora=True)}
         has_opt = optimizer is not None and not (self.config and self.config.skip_optimizer)
         if has_opt:

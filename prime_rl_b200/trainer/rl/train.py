@@ -262,9 +262,24 @@ class RLTrainer:
             # resumed run: re-seed the (stateless) inference engines with the restored policy; a
             # fresh run starts from weights both sides already share
             self.weight_sender.broadcast(self.model, self.progress.step - 1)
+        profiler = None
+        if cfg.trace_path is not None:
+            # torch.profiler trace (CPU + CUDA activities) of the whole run, one file per rank
+            # (reference: trainer/rl/train.py:243-247, 724-730; meant for runs of a few steps)
+            from torch.profiler import ProfilerActivity, profile
+
+            acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if self.device.type == "cuda" else [])
+            profiler = profile(activities=acts, record_shapes=True)
+            profiler.__enter__()
+        if cfg.memory_profiler_path is not None and self.device.type == "cuda":
+            torch.cuda.memory._record_memory_history(max_entries=100000)
         while cfg.max_steps is None or self.progress.step < cfg.max_steps:
             step = self.progress.step
             m = self.step()
+            if cfg.memory_profiler_path is not None and self.device.type == "cuda":
+                out = Path(cfg.memory_profiler_path)
+                out.mkdir(parents=True, exist_ok=True)
+                torch.cuda.memory._dump_snapshot(str(out / f"rank_{self.world.rank}_step_{step}.pickle"))
             if self.weight_sender is not None:
                 t0 = time.perf_counter()
                 self.weight_sender.broadcast(self.model, step)
@@ -291,6 +306,11 @@ class RLTrainer:
             last = self.progress.step - 1
             if last not in self.ckpt.saved_steps:
                 self.ckpt.save(last, self.model, self.optimizer, self.progress, self.dataloader)
+        if profiler is not None:
+            profiler.__exit__(None, None, None)
+            out = Path(cfg.trace_path)
+            out.mkdir(parents=True, exist_ok=True)
+            profiler.export_chrome_trace(str(out / f"trace_{self.world.rank}.json.gz"))
         self.monitor.finalize()
         if metrics_server is not None:
             metrics_server.stop()
