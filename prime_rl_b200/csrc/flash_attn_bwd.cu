@@ -319,8 +319,11 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_free);
-      if (n > 0) {                                        // dV of block n - 1 still reads P
-        ok = mbar_wait_poll(p_free, (n - 1) & 1, p.status, kTimeoutTmemFull);
+      if (n > 0) {
+        // P and dS of block n - 1 are still being read by dV / dK. Both products come from one
+        // issuing thread and complete in order, so the later one (dK -> ds_free) covers both
+        // buffers; by now it is almost always done, and the dS store below needs no wait of its own
+        ok = mbar_wait_poll(ds_free, (n - 1) & 1, p.status, kTimeoutTmemFull);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
       }
@@ -337,11 +340,6 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(dp_free);
-      if (n > 0) {                                        // dK of block n - 1 still reads dS
-        ok = mbar_wait_poll(ds_free, (n - 1) & 1, p.status, kTimeoutTmemFull);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-      }
       bw_store_row(ds_row, r, pf);
       fence_async_smem();
       __syncwarp();
