@@ -1,0 +1,74 @@
+"""Rollout engine on a GPU: paged tensor-core attention, CUDA-graph replay and fp8 weights against
+the plain paths of the same engine."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ARCH = dict(model_type="qwen3_moe", hidden_size=256, num_hidden_layers=2, num_attention_heads=8,
+            num_key_value_heads=2, head_dim=128, intermediate_size=512, num_experts=8, num_experts_per_tok=2,
+            moe_intermediate_size=256, vocab_size=2048)
+
+
+def _setup(**kw):
+    from prime_rl_b200.engine.engine import Engine
+    from prime_rl_b200.models import ModelArch, build_model
+
+    dev = torch.device("cuda", 0)
+    arch = ModelArch(**ARCH)
+    model = build_model(arch, device=dev, dtype=torch.bfloat16, seed=0)
+    return arch, model, Engine(model, num_pages=512, page_size=16, enable_prefix_cache=False, max_model_len=256, **kw)
+
+
+def _greedy(eng, prompts, n=12):
+    from prime_rl_b200.engine.sampler import SamplingParams
+
+    return eng.generate_sync(prompts, SamplingParams(max_tokens=n, temperature=0.0))
+
+
+def test_cuda_graph_decode_matches_eager_decode():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from prime_rl_b200.ops import _runtime as rt
+
+    arch, model, plain = _setup()
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, arch.vocab_size, (n,), generator=g).tolist() for n in (5, 33, 64, 17, 90)]
+    ref = _greedy(plain, prompts)
+    from prime_rl_b200.engine.engine import Engine
+
+    graphed = Engine(model, num_pages=512, page_size=16, enable_prefix_cache=False, max_model_len=256,
+                     use_cuda_graphs=True)
+    got = _greedy(graphed, prompts)
+    rt.check_status()
+    assert graphed.runner._graphs, "no decode graph was captured"
+    same = sum(a.output == b.output for a, b in zip(ref, got))
+    assert same >= len(prompts) - 1          # bf16 ties may flip one greedy token
+    for a, b in zip(ref, got):
+        n = min(len(a.logprobs), len(b.logprobs), 4)
+        assert all(abs(x - y) < 5e-2 for x, y in zip(a.logprobs[:n], b.logprobs[:n]))
+
+
+def test_fp8_weight_mode_stays_close_to_bf16():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from prime_rl_b200.engine.runner import StepInput
+    from prime_rl_b200.ops import _runtime as rt
+
+    arch, model, eng = _setup()
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, arch.vocab_size, (48,), generator=g).tolist()
+    from prime_rl_b200.engine.kv_cache import SequenceKV
+
+    ref, _ = eng.runner.forward([StepInput(SequenceKV(), prompt, want_all_logits=True)])
+    from prime_rl_b200.models.model import quantize_fp8_
+
+    assert quantize_fp8_(model) >= 4
+    out, _ = eng.runner.forward([StepInput(SequenceKV(), prompt, want_all_logits=True)])
+    rt.check_status()
+    assert torch.isfinite(out).all()
+    rel = (out - ref).norm() / ref.norm()
+    assert rel < 0.15, f"fp8 logits deviate by {rel:.3f}"
+    agree = (out.argmax(-1) == ref.argmax(-1)).float().mean()
+    assert agree > 0.7
