@@ -155,6 +155,7 @@ class P2PMoEDispatchConfig(BaseConfig):
     type: Literal["p2p"] = "p2p"
     num_sms: int = Field(32, ge=1)
     capacity_factor: float = Field(2.0, gt=0)   # receive-buffer rows as a multiple of the rows a rank sends
+    payload: Literal["bf16", "fp8"] = "bf16"    # fp8: e4m3 + 1x128 fp32 scales on the forward dispatch
 
 
 MoEDispatchConfig: TypeAlias = Annotated[

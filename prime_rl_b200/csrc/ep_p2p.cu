@@ -11,6 +11,9 @@
 //   ep_push_kernel     one warp per (token, k) pair: 16-byte peer stores of the row (optionally
 //                      scaled: the gradient of the combine), then a data flag on every peer
 //   ep_recv_kernel     waits for all senders' data flags, zeroes the padding rows
+//   ep_push_fp8_kernel / ep_recv_fp8_kernel   the same trip with an e4m3 payload: the sender
+//                      quantises each 128-column group of a row (scale = amax / 448, fp32) on
+//                      the way out, the owner expands its rows back to bf16 after the flags
 //   ep_signal_kernel   "my buffer is complete" flag on every peer
 //   ep_pull_kernel     waits for the owners' flags; out[t] = sum_k w[t,k] * peer_row(t,k) with
 //                      peer loads (also: gradient of the dispatch with w = 1); optional
@@ -20,6 +23,8 @@
 // (src/prime_rl/trainer/distributed/token_dispatcher.py:247-301 and its DeepEP variant,
 // deepep.py): those move rows with library collectives and permute them in separate kernels.
 // No TMA multicast and no library kernel ever touches peer memory here: plain ld / st only.
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 
 namespace prb {
@@ -195,6 +200,92 @@ ep_recv_kernel(__nv_bfloat16* __restrict__ buf, const int* __restrict__ hist, co
   uint4* p = reinterpret_cast<uint4*>(buf + r0 * H);
   const long long n = (r1 - r0) * (H / 8);
   for (long long i = threadIdx.x; i < n; i += blockDim.x) p[i] = make_uint4(0u, 0u, 0u, 0u);
+}
+
+// fp8 payload: one warp per pair, one 128-column group per iteration (lane = 4 columns). The
+// quantised row goes to qdst [cap_rows, H] (bytes) and its scales to sdst [cap_rows, H / 128].
+__global__ void __launch_bounds__(256)
+ep_push_fp8_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ topk_idx, const int* __restrict__ slot,
+                   const int* __restrict__ local_off, const int* __restrict__ send_base, const int* __restrict__ pos_in,
+                   const float* __restrict__ scale, EpPeers qdst, EpPeers sdst, EpPeers flags, int* __restrict__ pos_out,
+                   unsigned* __restrict__ done_counter, int num_pairs, int k, int H, int El, int rank, int R, int kind,
+                   int epoch, int cap_rows, int* status) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = blockDim.x >> 5;
+  const int groups = H / 128;
+  for (int p = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); p < num_pairs; p += gridDim.x * warps_per_cta) {
+    const int e = topk_idx[p];
+    const int d = e / El;
+    const int pos = pos_in ? pos_in[p] : send_base[e] + slot[p] - local_off[e];
+    if (pos_out && lane == 0) pos_out[p] = pos;
+    if (pos < 0 || pos >= cap_rows) {
+      if (lane == 0) atomicCAS(status, 0, static_cast<int>(kBadArgument));
+      continue;
+    }
+    const float s = scale ? scale[p] : 1.f;
+    const uint2* src = reinterpret_cast<const uint2*>(x + static_cast<long long>(p / k) * H);
+    uint32_t* qout = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(qdst.buf[d]) + static_cast<long long>(pos) * H);
+    float* sout = reinterpret_cast<float*>(sdst.buf[d]) + static_cast<long long>(pos) * groups;
+    for (int g = 0; g < groups; ++g) {
+      const uint2 u = src[g * 32 + lane];
+      const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y);
+      const float v0 = a.x * s, v1 = a.y * s, v2 = b.x * s, v3 = b.y * s;
+      float amax = fmaxf(fmaxf(fabsf(v0), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)));
+      amax = warp_max(amax);
+      const float sc = fmaxf(amax, 1e-12f) / 448.f, inv = 1.f / sc;
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v0 * inv, v1 * inv), __NV_SATFINITE, __NV_E4M3);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v2 * inv, v3 * inv), __NV_SATFINITE, __NV_E4M3);
+      qout[g * 32 + lane] = lo | (hi << 16);
+      if (lane == 0) sout[g] = sc;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ unsigned s_last;
+  if (threadIdx.x == 0) s_last = (atomicAdd(done_counter, 1u) == gridDim.x - 1) ? 1u : 0u;
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    if (threadIdx.x < R) {
+      volatile int* f = reinterpret_cast<int*>(flags.buf[threadIdx.x]) + kind * R + rank;
+      *f = epoch;
+    }
+    if (threadIdx.x == 0) *done_counter = 0;
+  }
+}
+
+// blockIdx.x = local expert, blockIdx.y strides over its rows: real rows are expanded from the
+// e4m3 staging buffer into the bf16 buffer the grouped GEMM reads, padding rows are zeroed.
+__global__ void __launch_bounds__(256)
+ep_recv_fp8_kernel(__nv_bfloat16* __restrict__ buf, const uint8_t* __restrict__ q, const float* __restrict__ scales,
+                   const int* __restrict__ hist, const int* __restrict__ expert_offset,
+                   const int* __restrict__ flags_kind, int rank, int R, int E, int H, int epoch, int* status) {
+  if (!ep_wait_all(flags_kind, R, epoch, status)) return;
+  const int El = E / R;
+  const int le = blockIdx.x;
+  if (le >= El) return;
+  int tot = 0;
+  for (int s = 0; s < R; ++s) tot += hist[s * E + rank * El + le];
+  const long long r0 = expert_offset[le], r_real = r0 + tot, r1 = expert_offset[le + 1];
+  const int groups = H / 128;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  for (long long r = r0 + blockIdx.y * warps + warp; r < r1; r += static_cast<long long>(gridDim.y) * warps) {
+    uint2* out = reinterpret_cast<uint2*>(buf + r * H);
+    if (r >= r_real) {
+      for (int i = lane; i < H / 4; i += 32) out[i] = make_uint2(0u, 0u);
+      continue;
+    }
+    const uint32_t* qr = reinterpret_cast<const uint32_t*>(q + r * H);
+    for (int g = 0; g < groups; ++g) {
+      const float sc = scales[r * groups + g];
+      const uint32_t w = qr[g * 32 + lane];
+      const __half2_raw h01 = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w & 0xffffu), __NV_E4M3);
+      const __half2_raw h23 = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w >> 16), __NV_E4M3);
+      const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&h01));
+      const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&h23));
+      out[g * 32 + lane] = make_uint2(pack_bf16(f01.x * sc, f01.y * sc), pack_bf16(f23.x * sc, f23.y * sc));
+    }
+  }
 }
 
 __global__ void __launch_bounds__(32)
@@ -396,6 +487,37 @@ PRB_API int prb_ep_recv(void* buf, const int* hist, const int* expert_offset, co
                         int H, int kind, int epoch, int* status, void* stream) {
   prb::ep_recv_kernel<<<E / R, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<__nv_bfloat16*>(buf), hist, expert_offset, flags + kind * R, rank, R, E, H, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// fp8 payload variants (H must be a multiple of 128).
+PRB_API int prb_ep_push_fp8(const void* x, const int* topk_idx, const int* slot, const int* local_off,
+                            const int* send_base, const int* pos_in, const float* scale, void* const* q_peers,
+                            void* const* s_peers, void* const* flag_peers, int* pos_out, unsigned* done_counter,
+                            int num_pairs, int k, int H, int E, int rank, int R, int kind, int epoch, int cap_rows,
+                            int* status, void* stream) {
+  if (R > prb::kEpMaxRanks || (H % 128) || E % R) return -2;
+  if (num_pairs <= 0) {
+    prb::ep_signal_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(ep_peers(flag_peers, R), rank, R, kind, epoch);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  }
+  int grid = (num_pairs + 7) / 8;
+  if (grid > 148 * 8) grid = 148 * 8;
+  prb::ep_push_fp8_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), topk_idx, slot, local_off, send_base, pos_in, scale,
+      ep_peers(q_peers, R), ep_peers(s_peers, R), ep_peers(flag_peers, R), pos_out, done_counter, num_pairs, k, H, E / R,
+      rank, R, kind, epoch, cap_rows, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+PRB_API int prb_ep_recv_fp8(void* buf, const void* q, const float* scales, const int* hist, const int* expert_offset,
+                            const int* flags, int rank, int R, int E, int H, int kind, int epoch, int* status,
+                            void* stream) {
+  if ((H % 128) || E % R) return -2;
+  dim3 grid(E / R, 32);
+  prb::ep_recv_fp8_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<__nv_bfloat16*>(buf), reinterpret_cast<const uint8_t*>(q), scales, hist, expert_offset,
+      flags + kind * R, rank, R, E, H, epoch, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -49,6 +49,17 @@ struct GemmParams {
   // reduce-scatter epilogue: row r of C is added into peer_c[r / rows_per_rank] (fp32, pitch ldc)
   float* peer_c[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   int rows_per_rank = 0;
+  // all-gather prologue: B [N, K] lives in a buffer that every rank holds in full but of which
+  // only the rows [r * ag_rows, (r + 1) * ag_rows) are valid on rank r. Gather warps copy the
+  // other ranks' rows (ag_src[r] = rank r's buffer base) into the local buffer in pieces and
+  // count finished pieces per N block in ag_ready; the producer loads a remote N block once
+  // its count reaches ag_target (counters only grow: target = call number * pieces per block).
+  const uint8_t* ag_src[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  uint8_t* ag_dst = nullptr;
+  unsigned* ag_ready = nullptr;
+  unsigned ag_target = 0;
+  int ag_rank = 0, ag_ranks = 1, ag_rows = 0;
+  long long ag_row_bytes = 0;
   const int* expert_offset;  // K-grouped mode
   int num_experts;
   // fused LM head (logprob / entropy) extras
@@ -84,6 +95,7 @@ struct GemmCfg {
 // A scheduler enumerates the (m_blk, n_blk) tiles of one CTA; all three warp roles run the
 // same enumeration so that their pipelines stay in step.
 struct SchedDense {
+  static constexpr int kGatherWarps = 0;
   int tile, num_tiles, tiles_m, tiles_n;
   __device__ SchedDense(const GemmParams& p, int bn)
       : tile(blockIdx.x - gridDim.x), tiles_m((p.M + kBM - 1) / kBM), tiles_n((p.N + bn - 1) / bn) {
@@ -131,6 +143,7 @@ struct SchedGrouped : SchedDense {
 // M block so that per-row running statistics can live in registers. Items are numbered
 // split-major so that the CTAs in flight stream the same slice of the vocabulary.
 struct SchedSplit {
+  static constexpr int kGatherWarps = 0;
   int item, j, tiles_m, tiles_n, per_split, num_items;
   __device__ SchedSplit(const GemmParams& p, int bn)
       : item(blockIdx.x - gridDim.x), j(0x7fffffff), tiles_m((p.M + kBM - 1) / kBM),
@@ -170,6 +183,7 @@ struct SchedSplit {
 // Experts without rows produce nkb = 0: producer and MMA skip the tile, the epilogue
 // writes zeros.
 struct SchedKGrouped {
+  static constexpr int kGatherWarps = 0;
   int tile, num_tiles, tiles_m, tiles_n;
   __device__ SchedKGrouped(const GemmParams& p, int bn)
       : tile(blockIdx.x - gridDim.x), tiles_m((p.M + kBM - 1) / kBM), tiles_n((p.N + bn - 1) / bn) {
@@ -193,6 +207,90 @@ struct SchedKGrouped {
     return true;
   }
 };
+
+// All-gather order: N-major (all M blocks of one N block are consecutive, so the CTAs in flight
+// share one B tile) and rotated so that the N blocks of this rank's own rows come first, then
+// those of rank+1, rank+2, ...; the gather warps fetch remote rows in the same order.
+constexpr int kAgPieceBytes = 16384;
+struct SchedAllGather {
+  static constexpr int kGatherWarps = 2;
+  int tile, num_tiles, tiles_m, tiles_n, first_n;
+  __device__ SchedAllGather(const GemmParams& p, int bn)
+      : tile(blockIdx.x - gridDim.x), tiles_m((p.M + kBM - 1) / kBM), tiles_n((p.N + bn - 1) / bn) {
+    num_tiles = tiles_m * tiles_n;
+    first_n = p.ag_rank * (p.ag_rows / bn);
+  }
+  __device__ bool next(const GemmParams& p, int& m_blk, int& n_blk, int& brow, bool& last_of_item, int& kb0,
+                       int& nkb, long long& c_row0) {
+    kb0 = 0;
+    nkb = (p.K + kBK - 1) / kBK;
+    c_row0 = 0;
+    tile += gridDim.x;
+    if (tile >= num_tiles) return false;
+    const int n_idx = tile / tiles_m;
+    m_blk = tile - n_idx * tiles_m;
+    n_blk = n_idx + first_n;
+    if (n_blk >= tiles_n) n_blk -= tiles_n;
+    brow = 0;
+    last_of_item = true;
+    return true;
+  }
+};
+
+// Gather warps of one CTA: pieces of kAgPieceBytes, numbered in schedule order over the remote
+// N blocks, are dealt round-robin to the CTAs. `bn` rows of `ag_row_bytes` make one N block.
+__device__ void ag_gather(const GemmParams& p, int bn, int tid, int nthreads) {
+  const int blocks_per_rank = p.ag_rows / bn;
+  const int tiles_n = p.ag_ranks * blocks_per_rank;
+  const long long block_bytes = static_cast<long long>(bn) * p.ag_row_bytes;
+  const int ppb = static_cast<int>((block_bytes + kAgPieceBytes - 1) / kAgPieceBytes);
+  const long long remote_pieces = static_cast<long long>(tiles_n - blocks_per_rank) * ppb;
+  for (long long g = blockIdx.x; g < remote_pieces; g += gridDim.x) {
+    const int n_idx = blocks_per_rank + static_cast<int>(g / ppb);
+    const int piece = static_cast<int>(g % ppb);
+    int n_blk = n_idx + p.ag_rank * blocks_per_rank;
+    if (n_blk >= tiles_n) n_blk -= tiles_n;
+    const int owner = n_blk / blocks_per_rank;
+    const long long off = static_cast<long long>(n_blk) * block_bytes + static_cast<long long>(piece) * kAgPieceBytes;
+    const long long len = min(static_cast<long long>(kAgPieceBytes), block_bytes - static_cast<long long>(piece) * kAgPieceBytes);
+    const int4* src = reinterpret_cast<const int4*>(p.ag_src[owner] + off);
+    int4* dst = reinterpret_cast<int4*>(p.ag_dst + off);
+    const int n16 = static_cast<int>(len >> 4);
+    for (int i = tid; i < n16; i += nthreads * 4) {
+      int4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i + u * nthreads < n16) v[u] = __ldcg(src + i + u * nthreads);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i + u * nthreads < n16) dst[i + u * nthreads] = v[u];
+    }
+    __threadfence();
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    if (tid == 0) atomicAdd(p.ag_ready + n_blk, 1u);
+  }
+}
+
+// Producer side: wait (bounded) until every piece of N block n_blk has landed.
+__device__ bool ag_wait_block(const GemmParams& p, int bn, int n_blk) {
+  const int blocks_per_rank = p.ag_rows / bn;
+  if (n_blk / blocks_per_rank == p.ag_rank) return true;
+  const long long block_bytes = static_cast<long long>(bn) * p.ag_row_bytes;
+  const unsigned ppb = static_cast<unsigned>((block_bytes + kAgPieceBytes - 1) / kAgPieceBytes);
+  const unsigned want = p.ag_target * ppb;
+  const unsigned* flag = p.ag_ready + n_blk;
+  for (long long spin = 0; spin < (1LL << 24); ++spin) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= want) {
+      asm volatile("fence.proxy.async;" ::: "memory");
+      return true;
+    }
+    __nanosleep(64);
+  }
+  if (p.status) atomicCAS(p.status, 0, kTimeoutPeerFlag);
+  return false;
+}
 
 // ---------------------------------------------------------------- epilogues
 // An epilogue consumes 32-column chunks of one accumulator row per thread.
@@ -374,7 +472,7 @@ struct EpiDLogits {
 };
 
 template <int BN, bool A_MN, bool B_MN, class Sched, class Epi>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreads + 32 * Sched::kGatherWarps, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
                  const GemmParams p) {
@@ -440,6 +538,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (!mbar_wait(&empty[s], ph ^ 1, p.status, kTimeoutEmptyBarrier)) {
             ok = false;
             break;
+          }
+          if constexpr (Sched::kGatherWarps > 0) {
+            if (it == 0 && !ag_wait_block(p, BN, n_blk)) {
+              ok = false;
+              break;
+            }
           }
           mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
           uint8_t* a_dst = smem + s * Cfg::STAGE_BYTES;
@@ -508,6 +612,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (acc == 0) acc_ph ^= 1;
       }
     }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------ gather warps (all-gather variant)
+    if constexpr (Sched::kGatherWarps > 0)
+      ag_gather(p, BN, threadIdx.x - kGemmThreads, 32 * Sched::kGatherWarps);
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;  // TMEM lanes [32q, 32q+32) are the ones this warp may read
@@ -755,6 +863,72 @@ PRB_API int prb_gemm_bf16_reduce_scatter(const void* A, const void* B, int M, in
   else if (a_mn && b_mn) PRB_RS_LAUNCH(true, true)
   else PRB_RS_LAUNCH(true, false)
 #undef PRB_RS_LAUNCH
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// C = alpha * A W^T where W [N, K] (K-major, dense pitch K) is row-sharded over the ranks: the
+// full-size buffer `w_local` holds this rank's rows [rank * rows_per_rank, ...) and receives the
+// other ranks' rows from `peer_w[r]` (the same buffer on rank r) while the tiles that need only
+// local rows are already running. `ready` holds one counter per 256-row N block (zero before the
+// first call, never reset); `call_index` counts calls from 1. The caller orders this launch after
+// every rank has published its rows and must not rewrite its rows until all ranks have finished.
+PRB_API int prb_gemm_bf16_allgather(const void* A, void* w_local, void* const* peer_w, void* C, int M, int N, int K,
+                                    long long lda, long long ldc, int a_mn, int out_fp32, float alpha, int rank,
+                                    int num_ranks, int rows_per_rank, unsigned* ready, unsigned call_index,
+                                    int* status, void* stream_) {
+  using namespace prb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || num_ranks < 1 || num_ranks > 8 || rank < 0 || rank >= num_ranks || rows_per_rank <= 0 ||
+      rows_per_rank % 256 != 0 || rows_per_rank * num_ranks != N || K % 8 != 0)
+    return -3;
+  if ((lda % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(w_local) & 15)) return -4;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!a_mn)
+    rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda, kBM, kBK,
+                      true);
+  else
+    rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda, kBK, 64,
+                      true);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmB, w_local, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)N, (uint64_t)K, (uint64_t)K, 256, kBK,
+                    true);
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.rows_total = M;
+  p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32;
+  p.expert_offset = nullptr; p.num_experts = 0;
+  p.alpha = alpha; p.beta = 0.f;
+  p.block_expert = nullptr; p.b_rows_per_expert = 0;
+  p.status = status;
+  p.num_splits = 0;
+  p.labels = nullptr; p.inv_temp = nullptr; p.part_m = p.part_s = p.part_t = p.target_logit = nullptr;
+  p.grad_logprob = nullptr; p.lse = nullptr;
+  for (int i = 0; i < num_ranks; ++i) p.ag_src[i] = reinterpret_cast<const uint8_t*>(peer_w[i]);
+  p.ag_dst = reinterpret_cast<uint8_t*>(w_local);
+  p.ag_ready = ready;
+  p.ag_target = call_index;
+  p.ag_rank = rank; p.ag_ranks = num_ranks; p.ag_rows = rows_per_rank;
+  p.ag_row_bytes = static_cast<long long>(K) * 2;
+  using Cfg = GemmCfg<256>;
+  const int tiles = ((M + kBM - 1) / kBM) * (N / 256);
+  // every CTA must be resident at once (producers wait on the gather warps of all CTAs)
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+#define PRB_AG_LAUNCH(AMN)                                                                                   \
+  {                                                                                                          \
+    auto kern = gemm_bf16_kernel<256, AMN, false, SchedAllGather, EpiStore>;                                 \
+    static bool configured = false;                                                                          \
+    if (!configured) {                                                                                       \
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) \
+        return -10;                                                                                          \
+      configured = true;                                                                                     \
+    }                                                                                                        \
+    kern<<<grid, kGemmThreads + 32 * SchedAllGather::kGatherWarps, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmA, tmB, p); \
+  }
+  if (!a_mn) PRB_AG_LAUNCH(false)
+  else PRB_AG_LAUNCH(true)
+#undef PRB_AG_LAUNCH
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

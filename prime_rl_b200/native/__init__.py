@@ -31,6 +31,8 @@ _CUDA_SIGNATURES = {
     "prb_ep_plan": [P, P, I, I, I, I, I, I, I, P, P, P, P, P, P],
     "prb_ep_push": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
     "prb_ep_recv": [P, P, P, P, I, I, I, I, I, I, P, P],
+    "prb_ep_push_fp8": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
+    "prb_ep_recv_fp8": [P, P, P, P, P, P, I, I, I, I, I, I, P, P],
     "prb_ipc_export_range": [P, P, P], "prb_weight_push": [P, P, L, P],
     "prb_weight_push_fp8": [P, L, P, P, I, I, P],
     "prb_gemm_fp8": [P, P, P, P, P, I, I, I, L, P, I, P, P], "prb_act_quant_fp8": [P, L, P, P, I, I, P],
@@ -38,6 +40,7 @@ _CUDA_SIGNATURES = {
     "prb_a2a_recv": [P, P, P, P, L, L, P, I, I, I, I, I, P, P],
     "prb_ep_wait": [P, I, I, I, P, P],
     "prb_gemm_bf16_reduce_scatter": [P, P, I, I, I, L, L, I, I, F, P, I, I, L, P, P],
+    "prb_gemm_bf16_allgather": [P, P, P, P, I, I, I, L, L, I, I, F, I, I, I, P, I, P, P],
     "prb_ep_signal": [P, I, I, I, I, P],
     "prb_ep_pull": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
     "prb_gemm_bf16_ext": [P, P, P, I, I, I, L, L, L, I, I, I, F, F, P, I, I, I, P, P, I, L, L, I, P, P],

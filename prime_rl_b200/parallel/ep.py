@@ -105,9 +105,9 @@ def install_expert_parallel(model, dims, moe_cfg=None) -> None:
         if kind in ("p2p", "deepep"):
             from .ep_p2p import P2PDispatcher
 
-            moe.dispatcher = P2PDispatcher(group, ep, E,
-                                           capacity_factor=getattr(getattr(moe_cfg, "dispatch", None),
-                                                                   "capacity_factor", 2.0))
+            dcfg = getattr(moe_cfg, "dispatch", None)
+            moe.dispatcher = P2PDispatcher(group, ep, E, capacity_factor=getattr(dcfg, "capacity_factor", 2.0),
+                                           payload=getattr(dcfg, "payload", "bf16"))
         else:
             moe.dispatcher = TorchA2ADispatcher(group, ep, E)
         moe.ep_rank, moe.ep = ep_rank, ep

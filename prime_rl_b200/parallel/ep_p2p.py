@@ -16,6 +16,11 @@ every layer; that is safe because any two uses are separated by a complete flag 
 all ranks, and it requires per-layer activation recomputation for training (the tensors autograd
 keeps are views of these buffers).
 
+``payload="fp8"`` sends the forward dispatch as e4m3 with one fp32 scale per row and 128 columns
+(quantised by the sending warp on its way out, expanded to bf16 by the owner after the flags):
+half the NVLink bytes of the largest transfer. The combine and both backward trips stay bf16, as
+in the reference's quantised all-to-all (src/prime_rl/trainer/distributed/collectives.py:95-152).
+
 Same role as the reference's DeepEP path (src/prime_rl/trainer/distributed/deepep.py,
 token_dispatcher.py:303-420).
 """
@@ -37,7 +42,7 @@ class _Shared:
 
     _cache: dict = {}
 
-    def __init__(self, group, R: int, E: int, H: int, cap_rows: int, device):
+    def __init__(self, group, R: int, E: int, H: int, cap_rows: int, device, fp8: bool = False):
         self.group, self.R, self.E, self.H, self.cap = group, R, E, H, cap_rows
         self.rank = dist.get_rank(group)
         row_bytes = cap_rows * H * 2
@@ -46,6 +51,13 @@ class _Shared:
         self.off_flags = self.off_hist + R * E * 4
         total = self.off_flags + 5 * R * 4
         total = (total + 255) // 256 * 256
+        self.fp8 = fp8
+        if fp8:
+            if H % 128:
+                raise ValueError("the fp8 payload needs a hidden size that is a multiple of 128")
+            self.off_q = total
+            self.off_s = self.off_q + cap_rows * H
+            total = (self.off_s + cap_rows * (H // 128) * 4 + 255) // 256 * 256
         self.mem = SymmetricBuffer(group, total, device, zero=True)
         m = self.mem
         self.xbuf = m.local(torch.bfloat16, self.off_x, cap_rows * H).view(cap_rows, H)
@@ -57,6 +69,10 @@ class _Shared:
         self.p_x, self.p_y = m.offset_ptrs(self.off_x), m.offset_ptrs(self.off_y)
         self.p_g, self.p_dx = m.offset_ptrs(self.off_g), m.offset_ptrs(self.off_dx)
         self.p_hist, self.p_flags = m.offset_ptrs(self.off_hist), m.offset_ptrs(self.off_flags)
+        if fp8:
+            self.qbuf = m.local(torch.uint8, self.off_q, cap_rows * H).view(cap_rows, H)
+            self.sbuf = m.local(torch.float32, self.off_s, cap_rows * (H // 128)).view(cap_rows, H // 128)
+            self.p_q, self.p_s = m.offset_ptrs(self.off_q), m.offset_ptrs(self.off_s)
         self.epoch = [0] * 5
         self.done = torch.zeros(1, dtype=torch.int32, device=device)
         self.device = device
@@ -66,11 +82,11 @@ class _Shared:
         return self.epoch[kind]
 
     @classmethod
-    def get(cls, group, R, E, H, cap_rows, device):
-        key = (id(group), R, E, H, device.index)
+    def get(cls, group, R, E, H, cap_rows, device, fp8: bool = False):
+        key = (id(group), R, E, H, device.index, fp8)
         sh = cls._cache.get(key)
         if sh is None or sh.cap < cap_rows:
-            sh = cls(group, R, E, H, cap_rows, device)
+            sh = cls(group, R, E, H, cap_rows, device, fp8)
             cls._cache[key] = sh
         return sh
 
@@ -91,13 +107,25 @@ class _Dispatch(torch.autograd.Function):
         sh, lib, dev = route.sh, rt.lib(), x.device
         x = x.contiguous()
         ep = sh.next_epoch(K_DATA_X)
-        rt.check(lib.prb_ep_push(x.data_ptr(), route.idx.data_ptr(), route.slot.data_ptr(), route.local_off.data_ptr(),
-                                 route.send_base.data_ptr(), None, None, sh.p_x, sh.p_flags, route.pos.data_ptr(),
-                                 sh.done.data_ptr(), route.T * route.k, route.k, sh.H, sh.E, sh.rank, sh.R, K_DATA_X,
-                                 ep, sh.cap, _status(dev), rt.stream_ptr(dev)), "prb_ep_push")
-        rt.check(lib.prb_ep_recv(sh.xbuf.data_ptr(), route.hist.data_ptr(), route.expert_offset.data_ptr(),
-                                 sh.flags.data_ptr(), sh.rank, sh.R, sh.E, sh.H, K_DATA_X, ep, _status(dev),
-                                 rt.stream_ptr(dev)), "prb_ep_recv")
+        if sh.fp8:
+            rt.check(lib.prb_ep_push_fp8(x.data_ptr(), route.idx.data_ptr(), route.slot.data_ptr(),
+                                         route.local_off.data_ptr(), route.send_base.data_ptr(), None, None, sh.p_q,
+                                         sh.p_s, sh.p_flags, route.pos.data_ptr(), sh.done.data_ptr(),
+                                         route.T * route.k, route.k, sh.H, sh.E, sh.rank, sh.R, K_DATA_X, ep, sh.cap,
+                                         _status(dev), rt.stream_ptr(dev)), "prb_ep_push_fp8")
+            rt.check(lib.prb_ep_recv_fp8(sh.xbuf.data_ptr(), sh.qbuf.data_ptr(), sh.sbuf.data_ptr(),
+                                         route.hist.data_ptr(), route.expert_offset.data_ptr(), sh.flags.data_ptr(),
+                                         sh.rank, sh.R, sh.E, sh.H, K_DATA_X, ep, _status(dev), rt.stream_ptr(dev)),
+                     "prb_ep_recv_fp8")
+        else:
+            rt.check(lib.prb_ep_push(x.data_ptr(), route.idx.data_ptr(), route.slot.data_ptr(),
+                                     route.local_off.data_ptr(), route.send_base.data_ptr(), None, None, sh.p_x,
+                                     sh.p_flags, route.pos.data_ptr(), sh.done.data_ptr(), route.T * route.k, route.k,
+                                     sh.H, sh.E, sh.rank, sh.R, K_DATA_X, ep, sh.cap, _status(dev),
+                                     rt.stream_ptr(dev)), "prb_ep_push")
+            rt.check(lib.prb_ep_recv(sh.xbuf.data_ptr(), route.hist.data_ptr(), route.expert_offset.data_ptr(),
+                                     sh.flags.data_ptr(), sh.rank, sh.R, sh.E, sh.H, K_DATA_X, ep, _status(dev),
+                                     rt.stream_ptr(dev)), "prb_ep_recv")
         ctx.route = route
         xin = sh.xbuf.view(sh.cap, sh.H)         # a fresh tensor object over the shared buffer
         return xin
@@ -163,7 +191,11 @@ class P2PDispatcher:
     receive as a multiple of the rows it sends (``T * k``); an overflow is reported through the
     kernel status word (``ops._runtime.check_status``)."""
 
-    def __init__(self, group, ep: int, num_experts: int, capacity_factor: float = 2.0, max_tokens: int | None = None):
+    def __init__(self, group, ep: int, num_experts: int, capacity_factor: float = 2.0, max_tokens: int | None = None,
+                 payload: str = "bf16"):
+        if payload not in ("bf16", "fp8"):
+            raise ValueError("payload must be 'bf16' or 'fp8'")
+        self.payload = payload
         self.group, self.ep, self.E = group, ep, num_experts
         self.E_local = num_experts // ep
         self.capacity_factor = capacity_factor
@@ -189,7 +221,7 @@ class P2PDispatcher:
         if T > self.max_tokens:
             raise ValueError(f"{T} tokens in one call, but the dispatcher's buffers are sized for {self.max_tokens} "
                              "(pass max_tokens = tokens per rank and micro-batch)")
-        sh = _Shared.get(self.group, self.ep, self.E, x.shape[1], self._cap(k), dev)
+        sh = _Shared.get(self.group, self.ep, self.E, x.shape[1], self._cap(k), dev, self.payload == "fp8")
         idx = idx.contiguous()
         counts = counts.to(torch.int32).contiguous()
         local = moe_ops.build_plan(idx, counts, self.E)          # rank of every pair inside its expert

@@ -80,12 +80,27 @@ def main() -> int:
     if rank == 0:
         print(("EP_SELFTEST_OK" if ok else "EP_SELFTEST_FAIL"), "max deviation", float(t), "per item", errs, flush=True)
 
+    # ---- fp8 payload on the forward dispatch: relative deviation of outputs and gradients
+    q = P2PDispatcher(group, world, 8 * world, capacity_factor=float(world), payload="fp8")
+    gotq = _run(q, ex, x, idx, w, counts, dout)
+    torch.cuda.synchronize()
+    rt.check_status()
+    rel = [float((a.float() - b.float()).norm() / (a.float().norm() + 1e-9)) for a, b in zip(ref[:3], gotq[:3])]
+    tq = torch.tensor([max(rel)], device=dev)
+    dist.all_reduce(tq, op=dist.ReduceOp.MAX)
+    okq = float(tq) < 5e-2
+    ok = ok and okq
+    if rank == 0:
+        print(("EP_FP8_PAYLOAD_OK" if okq else "EP_FP8_PAYLOAD_FAIL"), "relative deviation (out, dx, dw)", rel, flush=True)
+
     # ---- timing at a realistic layer shape
     if ok and os.environ.get("EP_SELFTEST_TIMING", "1") == "1":
         T, E, H, I, k = 8192, 128, 2048, 768, 8
         ex, x, idx, w, counts, dout = setup(T, E, H, I, k)
         for name, disp in (("all_to_all (NCCL)", TorchA2ADispatcher(group, world, E)),
-                           ("peer memory", P2PDispatcher(group, world, E, capacity_factor=2.0))):
+                           ("peer memory", P2PDispatcher(group, world, E, capacity_factor=2.0)),
+                           ("peer memory, fp8 dispatch payload",
+                            P2PDispatcher(group, world, E, capacity_factor=2.0, payload="fp8"))):
             for _ in range(3):
                 _run(disp, ex, x, idx, w, counts, dout)
             torch.cuda.synchronize()

@@ -1,4 +1,5 @@
-"""GEMM fused with a reduce-scatter over NVLink peer memory.
+"""GEMMs fused with their collective over NVLink peer memory: GEMM -> reduce-scatter and
+all-gather -> GEMM.
 
 ``GemmReduceScatter`` computes ``C = alpha * A.B`` on every rank (each rank holds its own A / B,
 e.g. its micro-batch's activations and output gradients for a weight gradient, or its K-slice
@@ -8,12 +9,23 @@ so the NVLink traffic of one tile overlaps the tensor-core work of the next and 
 product never exists in memory. A stream-ordered flag exchange (``csrc/ep_p2p.cu``) brackets
 the kernel: shards are zeroed before anybody adds, and complete before anybody reads.
 
-Takes the place of "GEMM, then ``reduce_scatter_tensor``" (the reference's FSDP2 gradient
+``AllGatherGemm`` computes ``y = x W^T`` for a weight whose rows are sharded over the ranks
+(the layout FSDP keeps parameters in). Every rank holds a full-size buffer of which its own rows
+are valid; two extra warps per CTA of the GEMM kernel copy the other ranks' rows over NVLink
+into that buffer (``csrc/gemm.cu: SchedAllGather / ag_gather``) while the tensor cores already
+work on the N blocks of the local rows, and the TMA producer waits on a per-N-block arrival
+counter before it loads a remote block. After the call the buffer holds the whole weight, so the
+backward GEMMs can use it without a second gather. Takes the place of the reference's FSDP2
+parameter all-gather followed by the first GEMM of the unit (src/prime_rl/trainer/model.py:470-559).
+
+``GemmReduceScatter`` takes the place of "GEMM, then ``reduce_scatter_tensor``" (the reference's FSDP2 gradient
 reduce-scatter, src/prime_rl/trainer/parallel_dims.py / torch FSDP; vLLM's row-parallel
 all-reduce in the engine).
 """
 
 from __future__ import annotations
+
+import os
 
 import torch
 import torch.distributed as dist
@@ -71,6 +83,117 @@ class GemmReduceScatter:
 
     def close(self):
         self.mem.close()
+
+
+class AllGatherGemm:
+    """``y = x W^T`` with ``W [N, K]`` row-sharded over the group (``N / R`` rows per rank, a multiple
+    of 256; ``K`` a multiple of 8)."""
+
+    def __init__(self, group, N: int, K: int, device: torch.device):
+        self.group = group
+        self.R = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.R > 8:
+            raise ValueError("at most 8 ranks (one NVSwitch box)")
+        if N % (256 * self.R) or K % 8:
+            raise ValueError("N must be a multiple of 256 * ranks and K of 8")
+        self.N, self.K, self.rows = N, K, N // self.R
+        w_bytes = N * K * 2
+        self.off_ready = (w_bytes + 255) // 256 * 256
+        self.off_flags = self.off_ready + (N // 256 * 4 + 255) // 256 * 256
+        self.mem = SymmetricBuffer(group, self.off_flags + 256, device, zero=True)
+        self.weight = self.mem.local(torch.bfloat16, 0, N * K).view(N, K)
+        self.shard = self.weight[self.rank * self.rows:(self.rank + 1) * self.rows]    # the rows this rank owns
+        self.ready = self.mem.local(torch.int32, self.off_ready, N // 256)
+        self.flags = self.mem.local(torch.int32, self.off_flags, 2 * self.R)
+        self.p_flags = self.mem.offset_ptrs(self.off_flags)
+        self.calls = 0
+        self.device = device
+
+    def __call__(self, x: torch.Tensor, *, out: torch.Tensor | None = None, alpha: float = 1.0) -> torch.Tensor:
+        """``x [M, K]`` bf16 -> ``[M, N]`` bf16. The caller writes ``self.shard`` before the call."""
+        lib, dev = rt.lib(), self.device
+        M = x.shape[0]
+        assert x.dtype == torch.bfloat16 and x.shape[1] == self.K and x.stride(1) == 1
+        if out is None:
+            out = torch.empty(M, self.N, dtype=torch.bfloat16, device=dev)
+        self.calls += 1
+        ep, st, stream = self.calls, rt.status_tensor(dev).data_ptr(), rt.stream_ptr(dev)
+        # every rank's rows are written (stream order on the owner), then visible to the readers
+        rt.check(lib.prb_ep_signal(self.p_flags, self.rank, self.R, _K_ZEROED, ep, stream), "prb_ep_signal")
+        rt.check(lib.prb_ep_wait(self.flags.data_ptr(), self.R, _K_ZEROED, ep, st, stream), "prb_ep_wait")
+        rt.check(lib.prb_gemm_bf16_allgather(x.data_ptr(), self.weight.data_ptr(), self.mem.c_ptrs, out.data_ptr(),
+                                             M, self.N, self.K, x.stride(0), out.stride(0), 0,
+                                             int(out.dtype == torch.float32), float(alpha), self.rank, self.R,
+                                             self.rows, self.ready.data_ptr(), ep, st, stream),
+                 "prb_gemm_bf16_allgather")
+        # all readers are done with my rows before I may rewrite them
+        rt.check(lib.prb_ep_signal(self.p_flags, self.rank, self.R, _K_DONE, ep, stream), "prb_ep_signal")
+        rt.check(lib.prb_ep_wait(self.flags.data_ptr(), self.R, _K_DONE, ep, st, stream), "prb_ep_wait")
+        return out
+
+    def close(self):
+        self.mem.close()
+
+
+def _selftest_allgather(group, dev, rank, world) -> bool:
+    from ..ops.matmul import gemm
+
+    torch.manual_seed(11)
+    N, K, M = 256 * world * 2, 520, 1000
+    w_full = (torch.randn(N, K, device=dev) * 0.05).bfloat16()          # same on every rank (same seed)
+    x = torch.randn(M, K, device=dev).bfloat16()
+    op = AllGatherGemm(group, N, K, dev)
+    worst = 0.0
+    for it in range(2):                                                   # second call: counters keep growing
+        op.weight.fill_(float("nan"))
+        op.shard.copy_(w_full[rank * op.rows:(rank + 1) * op.rows] * (it + 1))
+        y = op(x)
+        ref = x.float() @ (w_full.float() * (it + 1)).t()
+        torch.cuda.synchronize()
+        rt.check_status()
+        worst = max(worst, float((y.float() - ref).abs().max() / ref.abs().max()))
+        if not torch.equal(op.weight, w_full * (it + 1)):
+            worst = float("inf")
+    t = torch.tensor([worst], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ok = float(t) < 2e-2
+    if rank == 0:
+        print(("FUSED_AG_OK" if ok else "FUSED_AG_FAIL"), "max relative deviation", float(t), flush=True)
+    op.close()
+    if ok and os.environ.get("FUSED_SELFTEST_TIMING", "1") == "1":
+        M, N, K = 16384, 4096, 2048
+        x = torch.randn(M, K, device=dev).bfloat16()
+        op = AllGatherGemm(group, N, K, dev)
+        op.shard.normal_(std=0.02)
+        gathered = torch.empty(N, K, dtype=torch.bfloat16, device=dev)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+
+        def base():
+            dist.all_gather_into_tensor(gathered, op.shard, group=group)
+            gemm(x, gathered, out=out)
+
+        for name, fn in (("NCCL all_gather + GEMM", base),
+                         ("fused (gather warps inside the GEMM)", lambda: op(x, out=out))):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(10):
+                fn()
+            e.record()
+            torch.cuda.synchronize()
+            rt.check_status()
+            ms = torch.tensor([s.elapsed_time(e) / 10], device=dev)
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            if rank == 0:
+                flops = 2 * M * N * K
+                print(f"FUSED_AG_TIMING {name}: {float(ms):.3f} ms ({flops / float(ms) / 1e9:.0f} TFLOP/s per GPU; "
+                      f"weight {N}x{K} bf16 over {world} ranks, max over ranks)", flush=True)
+        op.close()
+    return ok
 
 
 def _selftest() -> int:
@@ -142,6 +265,7 @@ def _selftest() -> int:
                 print(f"FUSED_RS_TIMING {name}: {float(ms):.3f} ms ({flops / float(ms) / 1e9:.0f} TFLOP/s per GPU; "
                       f"{Nout}x{Kin} fp32 over {world} ranks, max over ranks)", flush=True)
         op.close()
+    ok = _selftest_allgather(group, dev, rank, world) and ok
     dist.barrier()
     dist.destroy_process_group()
     return 0 if ok else 1

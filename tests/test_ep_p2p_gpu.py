@@ -18,7 +18,7 @@ def test_p2p_dispatcher_matches_all_to_all():
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
            "127.0.0.1", "--master-port", "29533", "-m", "prime_rl_b200.parallel.ep_selftest"]
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert out.returncode == 0 and "EP_SELFTEST_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
+    assert out.returncode == 0 and "EP_SELFTEST_OK" in out.stdout and "EP_FP8_PAYLOAD_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
 
 
 def test_gemm_reduce_scatter_over_peer_memory():
@@ -28,7 +28,7 @@ def test_gemm_reduce_scatter_over_peer_memory():
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
            "127.0.0.1", "--master-port", "29534", "-m", "prime_rl_b200.parallel.fused_collectives"]
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert out.returncode == 0 and "FUSED_RS_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
+    assert out.returncode == 0 and "FUSED_RS_OK" in out.stdout and "FUSED_AG_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
 
 
 def test_weight_push_over_peer_memory():

@@ -318,6 +318,44 @@ def test_gemm_extra_reduction_segment():
     _close(out.cpu()[used], ref[used], atol=0.3, rtol=2e-2)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("ranks,rank", [(1, 0), (2, 0), (2, 1), (4, 2)])
+def test_gemm_with_all_gather_prologue_single_device(ranks, rank):
+    """The all-gather GEMM with every "peer" buffer on this GPU: one kernel copies the other
+    ranks' weight rows into the local buffer and multiplies, so the arrival counters, the rotated
+    tile order and the async-proxy fence are exercised without a second GPU."""
+    import ctypes
+
+    torch.manual_seed(3)
+    dev = torch.device("cuda")
+    M, K, rows = 777, 328, 256
+    N = rows * ranks
+    x = torch.randn(M, K, device=dev).bfloat16()
+    w = (torch.randn(N, K, device=dev) * 0.1).bfloat16()
+    bufs = []
+    for r in range(ranks):                       # buffer of rank r: only its own rows are valid
+        b = torch.full((N, K), float("nan"), device=dev, dtype=torch.bfloat16)
+        b[r * rows:(r + 1) * rows] = w[r * rows:(r + 1) * rows]
+        bufs.append(b)
+    ptrs = (ctypes.c_void_p * ranks)(*[b.data_ptr() for b in bufs])
+    ready = torch.zeros(N // 256, dtype=torch.int32, device=dev)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    lib = rt.lib()
+    for call in (1, 2):
+        if call == 2:                            # counters keep growing across calls
+            bufs[rank].fill_(float("nan"))
+            bufs[rank][rank * rows:(rank + 1) * rows] = w[rank * rows:(rank + 1) * rows]
+        rt.check(lib.prb_gemm_bf16_allgather(x.data_ptr(), bufs[rank].data_ptr(), ptrs, out.data_ptr(), M, N, K,
+                                             x.stride(0), out.stride(0), 0, 0, 1.0, rank, ranks, rows,
+                                             ready.data_ptr(), call, rt.status_tensor(dev).data_ptr(),
+                                             rt.stream_ptr(dev)), "prb_gemm_bf16_allgather")
+        torch.cuda.synchronize()
+        rt.check_status()
+        assert torch.equal(bufs[rank], w)
+        ref = x.float() @ w.float().t()
+        assert float((out.float() - ref).abs().max() / ref.abs().max()) < 1e-2
+
+
 def test_fp8_block_scaled_gemm_dense_and_grouped():
     """e4m3 operands with 1 x 128 / 128 x 128 scales against dequantise-then-multiply in fp32."""
     from prime_rl_b200.models.fp8 import quantize_to_fp8_blockwise
