@@ -60,13 +60,59 @@ class ModelArch(BaseModel):
     shared_expert_intermediate_size: int = 0   # width of the shared expert when it differs from moe_intermediate_size
     decoder_sparse_step: int = 1
     initializer_range: float = 0.02
+    shared_expert_gate: bool = False           # sigmoid gate on the shared expert's output (Qwen3.5-MoE)
+    moe_latent_size: int = 0                   # experts work in a projected space of this width (Nemotron-H)
+    # layer kinds. block_types: every layer is ONE pre-normed mixer ("mamba" | "attention" | "mlp" | "moe",
+    # Nemotron-H); mixer_types: token mixer of a standard two-sublayer block ("attention" | "gated_attention" |
+    # "gated_delta_net" | "mla_dsa")
+    block_types: list[str] | None = None
+    mixer_types: list[str] | None = None
+    use_rope: bool = True
+    # Mamba-2
+    mamba_num_heads: int = 0
+    mamba_head_dim: int = 0
+    ssm_state_size: int = 0
+    ssm_n_groups: int = 1
+    conv_kernel: int = 4
+    ssm_chunk_size: int = 128
+    mamba_proj_bias: bool = False
+    use_conv_bias: bool = True
+    time_step_limit: tuple[float, float] = (0.0, float("inf"))
+    # gated delta-net
+    linear_num_value_heads: int = 0
+    linear_num_key_heads: int = 0
+    linear_key_head_dim: int = 0
+    linear_value_head_dim: int = 0
+    linear_conv_kernel_dim: int = 4
+    # multi-head latent attention + sparse indexer
+    kv_lora_rank: int = 0
+    q_lora_rank: int = 0
+    qk_rope_head_dim: int = 0
+    qk_nope_head_dim: int = 0
+    v_head_dim: int = 0
+    index_n_heads: int = 0
+    index_head_dim: int = 0
+    index_topk: int = 0
+    index_share_layers: list[int] = []        # layers without an indexer: they reuse the previous selection
 
     # ------------------------------------------------------------------ derived
     @property
     def is_moe(self) -> bool:
         return self.num_experts > 0
 
+    def block_type(self, idx: int) -> str:
+        return self.block_types[idx] if self.block_types is not None else "standard"
+
+    def mixer_type(self, idx: int) -> str:
+        return self.mixer_types[idx] if self.mixer_types is not None else "attention"
+
+    @property
+    def expert_hidden(self) -> int:
+        return self.moe_latent_size or self.hidden_size
+
     def layer_is_moe(self, idx: int) -> bool:
+        if self.block_types is not None:
+            return self.block_types[idx] == "moe"
         if self.is_moe and self.mlp_layer_types is not None:
             return self.mlp_layer_types[idx] == "sparse"
         if not self.is_moe or idx in self.mlp_only_layers or idx < self.first_k_dense_replace:
@@ -109,7 +155,32 @@ class ModelArch(BaseModel):
         expert = 3 * H * self.moe_intermediate_size
         total = 0
         for i in range(self.num_hidden_layers):
-            total += attn
+            bt, mt = self.block_type(i), self.mixer_type(i)
+            if bt == "mamba":
+                inner = self.mamba_num_heads * self.mamba_head_dim
+                conv = inner + 2 * self.ssm_n_groups * self.ssm_state_size
+                total += H * (inner + conv + self.mamba_num_heads) + inner * H
+                continue
+            if bt in ("mlp", "moe"):
+                pass
+            elif mt == "gated_delta_net":
+                kd, vd = self.linear_num_key_heads * self.linear_key_head_dim, self.linear_num_value_heads * self.linear_value_head_dim
+                total += H * (2 * kd + 2 * vd + 2 * self.linear_num_value_heads) + vd * H
+            elif mt == "mla_dsa":
+                qk = self.qk_nope_head_dim + self.qk_rope_head_dim
+                total += (H * self.q_lora_rank + self.q_lora_rank * self.num_attention_heads * qk
+                          + H * (self.kv_lora_rank + self.qk_rope_head_dim)
+                          + self.kv_lora_rank * self.num_attention_heads * (self.qk_nope_head_dim + self.v_head_dim)
+                          + self.num_attention_heads * self.v_head_dim * H)
+            elif mt == "gated_attention":
+                total += attn + H * self.q_dim
+            else:
+                total += attn
+            if bt == "attention":
+                continue
+            if bt == "mlp":
+                total += (2 if self.hidden_act == "relu2" else 3) * H * self.intermediate_size
+                continue
             if self.layer_is_moe(i):
                 n = self.num_experts_per_tok if active_only else self.num_experts
                 total += n * expert + H * self.num_experts + self.n_shared_experts * expert
@@ -126,6 +197,9 @@ class ModelArch(BaseModel):
     @classmethod
     def from_hf_config(cls, cfg: dict[str, Any]) -> "ModelArch":
         mt = cfg.get("model_type", "llama")
+        if mt in ("qwen3_5", "qwen3_5_moe") and "text_config" in cfg:      # multimodal wrapper: the text tower
+            cfg = {**cfg["text_config"], "model_type": mt}
+        mt = {"qwen3_5_text": "qwen3_5", "qwen3_5_moe_text": "qwen3_5_moe"}.get(mt, mt)
         heads = cfg["num_attention_heads"]
         d: dict[str, Any] = dict(
             model_type=mt,
@@ -194,6 +268,56 @@ class ModelArch(BaseModel):
                      mlp_layer_types=cfg.get("mlp_layer_types") or ["sparse"] * n,
                      heads_per_layer=cfg.get("num_attention_heads_per_layer"),
                      attn_gate="none" if not gating else ("per_head" if gating == "per-head" else "per_element"))
+        elif mt == "nemotron_h":
+            kinds = {"M": "mamba", "*": "attention", "-": "mlp", "E": "moe"}
+            blocks = cfg.get("layers_block_type") or [kinds[c] for c in cfg.get("hybrid_override_pattern", "ME*E")]
+            d.update(num_hidden_layers=len(blocks), block_types=blocks, qk_norm=False, use_rope=False,
+                     hidden_act=cfg.get("mlp_hidden_act", "relu2"), rms_norm_eps=cfg.get("layer_norm_epsilon", 1e-5),
+                     mamba_num_heads=cfg.get("mamba_num_heads", 128), mamba_head_dim=cfg.get("mamba_head_dim", 64),
+                     ssm_state_size=cfg.get("ssm_state_size", 128), ssm_n_groups=cfg.get("n_groups", 8),
+                     conv_kernel=cfg.get("conv_kernel", 4), ssm_chunk_size=cfg.get("chunk_size", 128),
+                     mamba_proj_bias=cfg.get("use_bias", False), use_conv_bias=cfg.get("use_conv_bias", True),
+                     time_step_limit=tuple(cfg.get("time_step_limit") or (0.0, float("inf"))), sliding_window=None)
+            if "moe" in blocks:
+                d.update(num_experts=cfg.get("n_routed_experts", 8), num_experts_per_tok=cfg.get("num_experts_per_tok", 2),
+                         moe_intermediate_size=cfg.get("moe_intermediate_size", 0), score_func="sigmoid",
+                         router_bias=True, norm_topk_prob=cfg.get("norm_topk_prob", True),
+                         routed_scaling_factor=cfg.get("routed_scaling_factor", 1.0), n_shared_experts=1,
+                         shared_expert_intermediate_size=cfg.get("moe_shared_expert_intermediate_size", 0),
+                         moe_latent_size=cfg.get("moe_latent_size") or 0)
+        elif mt in ("qwen3_5", "qwen3_5_moe"):
+            n = cfg["num_hidden_layers"]
+            every = cfg.get("full_attention_interval", 4)
+            kinds = cfg.get("layer_types") or ["full_attention" if (i + 1) % every == 0 else "linear_attention"
+                                               for i in range(n)]
+            rope = cfg.get("rope_parameters") or cfg.get("rope_scaling") or {}
+            d.update(qk_norm=True, sliding_window=None, layer_types=None,
+                     mixer_types=["gated_attention" if k == "full_attention" else "gated_delta_net" for k in kinds],
+                     partial_rotary_factor=rope.get("partial_rotary_factor", cfg.get("partial_rotary_factor", 0.25)),
+                     rope_theta=rope.get("rope_theta", cfg.get("rope_theta", 1e4)),
+                     linear_num_value_heads=cfg.get("linear_num_value_heads", 32),
+                     linear_num_key_heads=cfg.get("linear_num_key_heads", 16),
+                     linear_key_head_dim=cfg.get("linear_key_head_dim", 128),
+                     linear_value_head_dim=cfg.get("linear_value_head_dim", 128),
+                     linear_conv_kernel_dim=cfg.get("linear_conv_kernel_dim", 4))
+            if mt == "qwen3_5_moe":
+                d.update(num_experts=cfg["num_experts"], num_experts_per_tok=cfg["num_experts_per_tok"],
+                         moe_intermediate_size=cfg["moe_intermediate_size"], norm_topk_prob=True, n_shared_experts=1,
+                         shared_expert_intermediate_size=cfg.get("shared_expert_intermediate_size", 0),
+                         shared_expert_gate=True)
+        elif mt == "glm_moe_dsa":
+            n = cfg["num_hidden_layers"]
+            d.update(qk_norm=False, sliding_window=None, mixer_types=["mla_dsa"] * n,
+                     kv_lora_rank=cfg["kv_lora_rank"], q_lora_rank=cfg["q_lora_rank"],
+                     qk_rope_head_dim=cfg["qk_rope_head_dim"], qk_nope_head_dim=cfg["qk_nope_head_dim"],
+                     v_head_dim=cfg["v_head_dim"], index_n_heads=cfg.get("index_n_heads", 32),
+                     index_head_dim=cfg.get("index_head_dim", 128), index_topk=cfg.get("index_topk", 2048),
+                     index_share_layers=cfg.get("index_share_layers") or [],
+                     num_experts=cfg["n_routed_experts"], num_experts_per_tok=cfg["num_experts_per_tok"],
+                     moe_intermediate_size=cfg["moe_intermediate_size"], norm_topk_prob=cfg.get("norm_topk_prob", True),
+                     score_func="sigmoid", router_bias=True, routed_scaling_factor=cfg.get("routed_scaling_factor", 1.0),
+                     n_shared_experts=cfg.get("n_shared_experts", 1),
+                     first_k_dense_replace=cfg.get("first_k_dense_replace", 0))
         else:
             raise ValueError(f"unsupported model_type '{mt}'")
         return cls(**d)
@@ -206,7 +330,9 @@ class ModelArch(BaseModel):
         arch_names = {"llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
                       "qwen3_moe": "Qwen3MoeForCausalLM", "glm4_moe": "Glm4MoeForCausalLM",
                       "gpt_oss": "GptOssForCausalLM", "minimax_m2": "MiniMaxM2ForCausalLM",
-                      "afmoe": "AfmoeForCausalLM", "laguna": "LagunaForCausalLM"}
+                      "afmoe": "AfmoeForCausalLM", "laguna": "LagunaForCausalLM",
+                      "nemotron_h": "NemotronHForCausalLM", "qwen3_5": "Qwen3_5ForCausalLM",
+                      "qwen3_5_moe": "Qwen3_5MoeForCausalLM", "glm_moe_dsa": "GlmMoeDsaForCausalLM"}
         cfg: dict[str, Any] = dict(
             architectures=[arch_names.get(self.model_type, "LlamaForCausalLM")], model_type=self.model_type,
             vocab_size=self.vocab_size, hidden_size=self.hidden_size, num_hidden_layers=self.num_hidden_layers,
@@ -236,6 +362,31 @@ class ModelArch(BaseModel):
                        moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob)
         if self.sliding_window is not None:
             cfg.update(sliding_window=self.sliding_window, layer_types=self.layer_types)
+        if self.model_type == "nemotron_h":
+            cfg.update(layers_block_type=self.block_types, mlp_hidden_act=self.hidden_act,
+                       layer_norm_epsilon=self.rms_norm_eps, mamba_num_heads=self.mamba_num_heads,
+                       mamba_head_dim=self.mamba_head_dim, ssm_state_size=self.ssm_state_size,
+                       n_groups=self.ssm_n_groups, conv_kernel=self.conv_kernel, chunk_size=self.ssm_chunk_size,
+                       use_bias=self.mamba_proj_bias, use_conv_bias=self.use_conv_bias,
+                       n_routed_experts=self.num_experts, moe_latent_size=self.moe_latent_size or None,
+                       moe_shared_expert_intermediate_size=self.shared_width)
+        elif self.model_type in ("qwen3_5", "qwen3_5_moe"):
+            cfg.update(layer_types=["full_attention" if m == "gated_attention" else "linear_attention"
+                                    for m in (self.mixer_types or [])],
+                       partial_rotary_factor=self.partial_rotary_factor,
+                       linear_num_value_heads=self.linear_num_value_heads,
+                       linear_num_key_heads=self.linear_num_key_heads, linear_key_head_dim=self.linear_key_head_dim,
+                       linear_value_head_dim=self.linear_value_head_dim,
+                       linear_conv_kernel_dim=self.linear_conv_kernel_dim,
+                       shared_expert_intermediate_size=self.shared_width)
+        elif self.model_type == "glm_moe_dsa":
+            cfg.update(kv_lora_rank=self.kv_lora_rank, q_lora_rank=self.q_lora_rank,
+                       qk_rope_head_dim=self.qk_rope_head_dim, qk_nope_head_dim=self.qk_nope_head_dim,
+                       v_head_dim=self.v_head_dim, index_n_heads=self.index_n_heads,
+                       index_head_dim=self.index_head_dim, index_topk=self.index_topk,
+                       index_share_layers=self.index_share_layers, n_routed_experts=self.num_experts,
+                       n_shared_experts=self.n_shared_experts, first_k_dense_replace=self.first_k_dense_replace,
+                       routed_scaling_factor=self.routed_scaling_factor)
         return cfg
 
 
@@ -257,6 +408,28 @@ PRESETS: dict[str, dict[str, Any]] = {
                         mlp_layer_types=["dense", "sparse", "sparse"], heads_per_layer=[4, 2, 4],
                         sliding_window=16, layer_types=["sliding_attention", "full_attention", "sliding_attention"],
                         attn_gate="per_head", max_position_embeddings=512),
+    "tiny-nemotron-h": dict(model_type="nemotron_h", hidden_size=128, num_hidden_layers=4, num_attention_heads=4,
+                            num_key_value_heads=2, head_dim=32, intermediate_size=256, vocab_size=512, qk_norm=False,
+                            use_rope=False, hidden_act="relu2", block_types=["mamba", "moe", "attention", "mlp"],
+                            mamba_num_heads=8, mamba_head_dim=16, ssm_state_size=16, ssm_n_groups=2, ssm_chunk_size=16,
+                            num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, score_func="sigmoid",
+                            router_bias=True, n_shared_experts=1, shared_expert_intermediate_size=96,
+                            moe_latent_size=64, rms_norm_eps=1e-5, max_position_embeddings=512),
+    "tiny-qwen3.5-moe": dict(model_type="qwen3_5_moe", hidden_size=128, num_hidden_layers=4, num_attention_heads=4,
+                             num_key_value_heads=2, head_dim=32, intermediate_size=256, vocab_size=512, qk_norm=True,
+                             partial_rotary_factor=0.25, rope_theta=1e4,
+                             mixer_types=["gated_delta_net", "gated_delta_net", "gated_delta_net", "gated_attention"],
+                             linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=16,
+                             linear_value_head_dim=16, num_experts=4, num_experts_per_tok=2,
+                             moe_intermediate_size=64, n_shared_experts=1, shared_expert_intermediate_size=64,
+                             shared_expert_gate=True, max_position_embeddings=512),
+    "tiny-glm-moe-dsa": dict(model_type="glm_moe_dsa", hidden_size=128, num_hidden_layers=3, num_attention_heads=4,
+                             num_key_value_heads=4, head_dim=32, intermediate_size=256, vocab_size=512, qk_norm=False,
+                             mixer_types=["mla_dsa"] * 3, kv_lora_rank=32, q_lora_rank=48, qk_rope_head_dim=16,
+                             qk_nope_head_dim=16, v_head_dim=24, index_n_heads=2, index_head_dim=32, index_topk=8,
+                             index_share_layers=[2], num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
+                             score_func="sigmoid", router_bias=True, n_shared_experts=1, first_k_dense_replace=1,
+                             max_position_embeddings=512),
     "tiny-qwen3-moe": dict(model_type="qwen3_moe", hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
                            num_key_value_heads=2, head_dim=64, intermediate_size=512, num_experts=8,
                            num_experts_per_tok=2, moe_intermediate_size=512, vocab_size=4096),

@@ -118,6 +118,24 @@ class StackExperts:
         return out
 
 
+@dataclass
+class MapValue:
+    """Renames ``suffix`` -> ``new_suffix`` and maps the tensor (``fwd``) / back (``inv``)."""
+
+    suffix: str
+    new_suffix: str
+    fwd: Callable[[torch.Tensor], torch.Tensor]
+    inv: Callable[[torch.Tensor], torch.Tensor]
+
+    def forward(self, sd: StateDict) -> StateDict:
+        return {(k[: -len(self.suffix)] + self.new_suffix if k.endswith(self.suffix) else k):
+                (self.fwd(v) if k.endswith(self.suffix) else v) for k, v in sd.items()}
+
+    def inverse(self, sd: StateDict) -> StateDict:
+        return {(k[: -len(self.new_suffix)] + self.suffix if k.endswith(self.new_suffix) else k):
+                (self.inv(v) if k.endswith(self.new_suffix) else v) for k, v in sd.items()}
+
+
 class Chain:
     def __init__(self, ops: list):
         self.ops = ops
@@ -134,14 +152,38 @@ class Chain:
 
 
 # ---------------------------------------------------------------------- layout chains
+def _plain(a: str, b: str) -> Rename:
+    """Literal suffix rename a <-> b."""
+    return Rename(re.escape(a) + "$", b, re.escape(b) + "$", a)
+
+
 def native_to_prime_chain(arch: ModelArch) -> Chain:
     kv = arch.kv_dim
-    ops: list = [
-        # the query width comes from the tensor: families with per-layer head counts differ by layer
-        SplitConcat("self_attn.qkv_proj.weight", ["self_attn.q_proj.weight", "self_attn.k_proj.weight",
-                                                  "self_attn.v_proj.weight"], lambda v: [v.shape[0] - 2 * kv, kv, kv]),
-        SplitConcat("self_attn.qkv_proj.bias", ["self_attn.q_proj.bias", "self_attn.k_proj.bias",
-                                                "self_attn.v_proj.bias"], lambda v: [v.shape[0] - 2 * kv, kv, kv]),
+    ops: list = []
+    # depthwise convolutions are stored [C, K] here and [C, 1, K] in checkpoints; gated norms as modules
+    ops += [MapValue("conv1d_weight", "conv1d.weight", lambda v: v.unsqueeze(1), lambda v: v.squeeze(1)),
+            _plain("conv1d_bias", "conv1d.bias"),
+            Rename(r"(mamba|self_attn)\.norm_weight$", r"\1.norm.weight", r"(mamba|self_attn)\.norm\.weight$",
+                   r"\1.norm_weight")]
+    if arch.hidden_act == "relu2":
+        # non-gated MLPs: the "gate_up" tensor is just the up projection
+        ops += [_plain("mlp.experts.gate_up_proj", "mlp.experts.up_proj"),
+                _plain("shared_experts.gate_up_proj.weight", "shared_experts.up_proj.weight"),
+                _plain("mlp.gate_up_proj.weight", "mlp.up_proj.weight")]
+        return Chain(ops + [
+            SplitConcat("self_attn.qkv_proj.weight", ["self_attn.q_proj.weight", "self_attn.k_proj.weight",
+                                                      "self_attn.v_proj.weight"], lambda v: [v.shape[0] - 2 * kv, kv, kv]),
+            SplitConcat("self_attn.qkv_proj.bias", ["self_attn.q_proj.bias", "self_attn.k_proj.bias",
+                                                    "self_attn.v_proj.bias"], lambda v: [v.shape[0] - 2 * kv, kv, kv])])
+    if arch.model_type not in ("qwen3_5", "qwen3_5_moe"):      # their gated attention keeps q / k / v separate
+        ops += [
+            # the query width comes from the tensor: families with per-layer head counts differ by layer
+            SplitConcat("self_attn.qkv_proj.weight", ["self_attn.q_proj.weight", "self_attn.k_proj.weight",
+                                                      "self_attn.v_proj.weight"], lambda v: [v.shape[0] - 2 * kv, kv, kv]),
+            SplitConcat("self_attn.qkv_proj.bias", ["self_attn.q_proj.bias", "self_attn.k_proj.bias",
+                                                    "self_attn.v_proj.bias"], lambda v: [v.shape[0] - 2 * kv, kv, kv]),
+        ]
+    ops += [
         SplitConcat("mlp.experts.gate_up_proj", ["mlp.experts.gate_proj", "mlp.experts.up_proj"],
                     lambda v: [v.shape[1] // 2, v.shape[1] // 2], dim=1),
         SplitConcat("shared_experts.gate_up_proj.weight", ["shared_experts.gate_proj.weight",
@@ -153,8 +195,42 @@ def native_to_prime_chain(arch: ModelArch) -> Chain:
     return Chain(ops)
 
 
+def _family_chain(arch: ModelArch) -> list:
+    """Renames that depend on the kind of every layer (Nemotron-H, Qwen3.5)."""
+    ops: list = []
+    if arch.model_type == "nemotron_h":
+        for i, kind in enumerate(arch.block_types or []):
+            ours = {"mamba": "mamba", "attention": "self_attn", "mlp": "mlp", "moe": "mlp"}[kind]
+            ops.append(Rename(rf"^model\.layers\.{i}\.{ours}\.", f"model.layers.{i}.mixer.",
+                              rf"^model\.layers\.{i}\.mixer\.", f"model.layers.{i}.{ours}."))
+        ops += [Rename(r"^model\.embed_tokens\.weight$", "model.embeddings.weight",
+                       r"^model\.embeddings\.weight$", "model.embed_tokens.weight"),
+                Rename(r"^model\.norm\.weight$", "model.norm_f.weight", r"^model\.norm_f\.weight$", "model.norm.weight"),
+                Rename(r"^model\.", "backbone.", r"^backbone\.", "model.")]
+    elif arch.model_type in ("qwen3_5", "qwen3_5_moe"):
+        for i, kind in enumerate(arch.mixer_types or []):
+            if kind == "gated_delta_net":
+                ops.append(Rename(rf"^model\.layers\.{i}\.self_attn\.", f"model.layers.{i}.linear_attn.",
+                                  rf"^model\.layers\.{i}\.linear_attn\.", f"model.layers.{i}.self_attn."))
+        # zero-centred RMSNorm: checkpoints hold w - 1 (the gated norm inside linear_attn is a plain weight)
+        for suf in ("input_layernorm.weight", "post_attention_layernorm.weight", "q_norm.weight", "k_norm.weight",
+                    "model.norm.weight"):
+            ops.append(MapValue(suf, suf, lambda v: v - 1, lambda v: v + 1))
+    return ops
+
+
 def prime_to_hf_chain(arch: ModelArch) -> Chain:
     ops: list = []
+    if arch.model_type in ("qwen3_5_moe",):
+        ops += [Rename(r"mlp\.shared_experts\.", r"mlp.shared_expert.", r"mlp\.shared_expert\.", r"mlp.shared_experts.")]
+    if arch.model_type == "nemotron_h" and arch.is_moe:
+        ops += [Rename(r"mlp\.router\.gate\.(weight|bias)$", r"mlp.gate.\1", r"mlp\.gate\.(weight|bias)$",
+                       r"mlp.router.gate.\1"),
+                Rename(r"mlp\.router\.e_score_correction_bias$", r"mlp.gate.e_score_correction_bias",
+                       r"mlp\.gate\.e_score_correction_bias$", r"mlp.router.e_score_correction_bias"),
+                StackExperts("mlp.experts.up_proj", "mlp.experts.{e}.up_proj.weight"),
+                StackExperts("mlp.experts.down_proj", "mlp.experts.{e}.down_proj.weight")]
+        return Chain(ops + _family_chain(arch))
     if arch.model_type == "laguna":
         # Laguna checkpoints name the shared expert in the singular and keep the selection bias under `experts`
         ops += [
@@ -172,7 +248,7 @@ def prime_to_hf_chain(arch: ModelArch) -> Chain:
             StackExperts("mlp.experts.up_proj", "mlp.experts.{e}.up_proj.weight"),
             StackExperts("mlp.experts.down_proj", "mlp.experts.{e}.down_proj.weight"),
         ]
-    return Chain(ops)
+    return Chain(ops + _family_chain(arch))
 
 
 def native_to_prime(sd: StateDict, arch: ModelArch) -> StateDict:

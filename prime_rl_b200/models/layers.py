@@ -35,6 +35,8 @@ class SeqInfo:
     cp: object | None = None      # context-parallel state (parallel/cp.py)
     # attention outputs kept across activation recomputation, keyed by layer (ops/attention.py)
     attn_cache: dict | None = None
+    # values one layer leaves for later layers of the same forward (sparse-attention indices)
+    shared: dict | None = None
 
     @classmethod
     def from_lengths(cls, lengths: list[int], device) -> "SeqInfo":
@@ -153,8 +155,10 @@ class Attention(nn.Module):
             self.q_norm = self.k_norm = None
         self.sinks = nn.Parameter(torch.zeros(self.nq, dtype=dtype, device=device)) if arch.attention_sinks else None
         self.window = arch.layer_window(layer_idx)
-        self.register_buffer("inv_freq", ops.inv_freq(D, arch.rope_theta, device=device, rotary_dim=arch.rotary_dim),
-                             persistent=False)
+        inv_f = ops.inv_freq(D, arch.rope_theta, device=device, rotary_dim=arch.rotary_dim)
+        if not arch.use_rope:
+            inv_f = torch.zeros_like(inv_f)         # angle 0 everywhere: the rotation is the identity
+        self.register_buffer("inv_freq", inv_f, persistent=False)
 
     def forward(self, x: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
         T = x.shape[0]
@@ -258,7 +262,7 @@ class GroupedExperts(nn.Module):
         super().__init__()
         self.arch = arch
         E = num_local_experts or arch.num_experts
-        I, H = arch.moe_intermediate_size, arch.hidden_size
+        I, H = arch.moe_intermediate_size, arch.expert_hidden
         self.act = _ACT[arch.hidden_act]
         width = I if self.act == act_ops.RELU2 else 2 * I
         self.gate_up_proj = nn.Parameter(torch.empty(E, width, H, dtype=dtype, device=device))
@@ -327,6 +331,16 @@ class MoE(nn.Module):
                                            device=device)
         else:
             self.shared_experts = None
+        self.shared_expert_gate = None
+        if arch.shared_expert_gate and self.shared_experts is not None:
+            self.shared_expert_gate = Linear(arch.hidden_size, 1, std=arch.initializer_range, dtype=dtype, device=device)
+        # experts that work in a projected ("latent") space: project in before dispatch, out after combine
+        self.fc1_latent_proj = self.fc2_latent_proj = None
+        if arch.moe_latent_size:
+            self.fc1_latent_proj = Linear(arch.hidden_size, arch.moe_latent_size, std=arch.initializer_range,
+                                          dtype=dtype, device=device)
+            self.fc2_latent_proj = Linear(arch.moe_latent_size, arch.hidden_size, std=arch.initializer_range,
+                                          dtype=dtype, device=device)
         self.dispatcher = None            # parallel/ep.py installs an expert-parallel dispatcher here
         self.last_counts: torch.Tensor | None = None
         self.last_topk: torch.Tensor | None = None     # [T, k] expert ids of the last forward (router replay capture)
@@ -340,23 +354,81 @@ class MoE(nn.Module):
         idx, w, counts, logits = self.router(x, forced)
         self.last_counts = counts
         self.last_topk = idx
+        xe = x if self.fc1_latent_proj is None else self.fc1_latent_proj(x)
         if self.dispatcher is not None:
-            y = self.dispatcher(self.experts, x, idx, w, counts)
+            y = self.dispatcher(self.experts, xe, idx, w, counts)
         else:
             plan = moe_ops.build_plan(idx, counts, self.arch.num_experts)
-            xp = moe_ops.permute(x, plan)
+            xp = moe_ops.permute(xe, plan)
             yp = self.experts(xp, plan.block_expert, plan.expert_offset)
             y = moe_ops.combine(yp, w, plan, T)
+        if self.fc2_latent_proj is not None:
+            y = self.fc2_latent_proj(y)
         if self.shared_experts is not None:
-            y = y + self.shared_experts(x)
+            sh = self.shared_experts(x)
+            if self.shared_expert_gate is not None:
+                sh = sh * torch.sigmoid(self.shared_expert_gate(x).float()).to(sh.dtype)
+            y = y + sh
         return y
 
 
+def _token_mixer(arch: ModelArch, layer_idx: int, attn_backend: str, dtype, device) -> nn.Module:
+    kind = arch.mixer_type(layer_idx)
+    if kind == "attention":
+        return Attention(arch, layer_idx, attn_backend, dtype=dtype, device=device)
+    from . import mixers
+
+    if kind == "gated_attention":
+        return mixers.GatedAttention(arch, layer_idx, attn_backend, dtype=dtype, device=device)
+    if kind == "gated_delta_net":
+        return mixers.GatedDeltaNet(arch, layer_idx, dtype=dtype, device=device)
+    if kind == "mla_dsa":
+        return mixers.SparseMLAAttention(arch, layer_idx, dtype=dtype, device=device)
+    raise ValueError(f"unknown token mixer '{kind}'")
+
+
+class SingleMixerBlock(nn.Module):
+    """One pre-normed mixer per layer, ``h + mixer(norm(h))``: the Nemotron-H layout, where a
+    layer is a Mamba-2 mixer, an attention, a dense MLP or an MoE
+    (reference: NemotronHDecoderLayer, src/prime_rl/trainer/models/nemotron_h/modeling_nemotron_h.py:45-125)."""
+
+    def __init__(self, arch: ModelArch, layer_idx: int, attn_backend: str = "auto", dtype=None, device=None):
+        super().__init__()
+        self.kind = arch.block_type(layer_idx)
+        self.norm = RMSNorm(arch.hidden_size, arch.rms_norm_eps, dtype=dtype, device=device)
+        self.is_moe = self.kind == "moe"
+        if self.kind == "mamba":
+            from . import mixers
+
+            self.mamba = mixers.Mamba2Mixer(arch, layer_idx, dtype=dtype, device=device)
+        elif self.kind == "attention":
+            self.self_attn = Attention(arch, layer_idx, attn_backend, dtype=dtype, device=device)
+        elif self.kind == "moe":
+            self.mlp = MoE(arch, layer_idx, dtype=dtype, device=device)
+        elif self.kind == "mlp":
+            self.mlp = DenseMLP(arch, dtype=dtype, device=device)
+        else:
+            raise ValueError(f"unknown block type '{self.kind}'")
+
+    def forward(self, h: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
+        x = self.norm(h)
+        if self.kind == "mamba":
+            return h + self.mamba(x, seq)
+        if self.kind == "attention":
+            return h + self.self_attn(x, seq)
+        return h + (self.mlp(x, seq) if self.is_moe else self.mlp(x))
+
+
 class DecoderLayer(nn.Module):
+    def __new__(cls, arch: ModelArch, layer_idx: int, *args, **kwargs):
+        if cls is DecoderLayer and arch.block_types is not None:
+            return SingleMixerBlock(arch, layer_idx, *args, **kwargs)
+        return super().__new__(cls)
+
     def __init__(self, arch: ModelArch, layer_idx: int, attn_backend: str = "auto", dtype=None, device=None):
         super().__init__()
         self.input_layernorm = RMSNorm(arch.hidden_size, arch.rms_norm_eps, dtype=dtype, device=device)
-        self.self_attn = Attention(arch, layer_idx, attn_backend, dtype=dtype, device=device)
+        self.self_attn = _token_mixer(arch, layer_idx, attn_backend, dtype, device)
         self.post_attention_layernorm = RMSNorm(arch.hidden_size, arch.rms_norm_eps, dtype=dtype, device=device)
         if arch.layer_is_moe(layer_idx):
             self.mlp = MoE(arch, layer_idx, dtype=dtype, device=device)

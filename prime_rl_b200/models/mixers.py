@@ -1,0 +1,248 @@
+"""Token mixers beyond plain softmax attention: Mamba-2 (Nemotron-H), gated delta-net and
+gated softmax attention (Qwen3.5), multi-head-latent attention with the DSA sparse indexer
+(GLM-MoE-DSA). All of them work on packed ``[T, hidden]`` activations with ``SeqInfo``.
+
+Parameter names follow the reference's modules so that checkpoints map one to one:
+``NemotronHMamba2`` (src/prime_rl/trainer/models/nemotron_h/mamba.py:78-236),
+``Qwen3_5GatedDeltaNet`` (qwen3_5/gated_delta_net.py:19-110), ``Qwen3_5Attention``
+(qwen3_5/attention.py:10-84), ``GlmMoeDsaAttention`` + ``Indexer``
+(glm_moe_dsa/sparse_mla_attention.py:47-238).
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+from ..ops import attention as attn_ops
+from ..ops import delta_rule, sparse_mla, ssm
+from .config import ModelArch
+from .layers import Linear, RMSNorm, SeqInfo
+
+
+def doc_windows(seq: SeqInfo) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per token: index of its document's first token and its own index + 1 (the causal window
+    ``[ks, ke)`` of the sparse indexer)."""
+    T = seq.position_ids.shape[0]
+    me = torch.arange(T, device=seq.position_ids.device, dtype=torch.int32)
+    return (me - seq.position_ids.to(torch.int32)), me + 1
+
+
+class Mamba2Mixer(nn.Module):
+    def __init__(self, arch: ModelArch, layer_idx: int, dtype=None, device=None):
+        super().__init__()
+        self.arch = arch
+        self.nh, self.hd, self.ng, self.ns = arch.mamba_num_heads, arch.mamba_head_dim, arch.ssm_n_groups, arch.ssm_state_size
+        self.inner = self.nh * self.hd
+        self.conv_dim = self.inner + 2 * self.ng * self.ns
+        std = arch.initializer_range
+        self.in_proj = Linear(arch.hidden_size, self.inner + self.conv_dim + self.nh, bias=arch.mamba_proj_bias, std=std,
+                              dtype=dtype, device=device)
+        self.conv1d_weight = nn.Parameter(torch.empty(self.conv_dim, arch.conv_kernel, dtype=dtype, device=device))
+        self.conv1d_bias = nn.Parameter(torch.zeros(self.conv_dim, dtype=dtype, device=device)) if arch.use_conv_bias else None
+        self.dt_bias = nn.Parameter(torch.zeros(self.nh, dtype=torch.float32, device=device))
+        self.A_log = nn.Parameter(torch.zeros(self.nh, dtype=torch.float32, device=device))
+        self.D = nn.Parameter(torch.ones(self.nh, dtype=torch.float32, device=device))
+        self.norm_weight = nn.Parameter(torch.ones(self.inner, dtype=dtype, device=device))
+        self.out_proj = Linear(self.inner, arch.hidden_size, bias=arch.mamba_proj_bias, std=std, dtype=dtype, device=device)
+        self.reset_ssm_parameters()
+
+    @torch.no_grad()
+    def reset_ssm_parameters(self, seed: int = 0):
+        """A = -(1..heads); dt_bias = inverse softplus of log-uniform time steps in [1e-3, 1e-1]."""
+        gen = torch.Generator().manual_seed(seed)
+        self.A_log.copy_(torch.log(torch.arange(1, self.nh + 1, dtype=torch.float32)))
+        lo, hi = math.log(1e-3), math.log(1e-1)
+        ts = torch.exp(torch.rand(self.nh, generator=gen) * (hi - lo) + lo).clamp(min=1e-4)
+        self.dt_bias.copy_(ts + torch.log(-torch.expm1(-ts)))
+        self.D.fill_(1.0)
+        nn.init.uniform_(self.conv1d_weight, -0.5, 0.5)
+
+    def forward(self, x: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
+        T = x.shape[0]
+        gate, conv_in, dt = self.in_proj(x).split([self.inner, self.conv_dim, self.nh], dim=-1)
+        conv = ssm.causal_conv1d(conv_in, self.conv1d_weight, self.conv1d_bias, seq.position_ids, "silu")
+        hs, Bm, Cm = conv.split([self.inner, self.ng * self.ns, self.ng * self.ns], dim=-1)
+        dtp = F.softplus(dt.float() + self.dt_bias)
+        lo, hi = self.arch.time_step_limit
+        if lo > 0.0 or math.isfinite(hi):
+            dtp = dtp.clamp(lo, hi)
+        y = ssm.mamba2_scan(hs.reshape(T, self.nh, self.hd), dtp, -torch.exp(self.A_log.float()),
+                            Bm.reshape(T, self.ng, self.ns), Cm.reshape(T, self.ng, self.ns), self.D, seq.position_ids,
+                            chunk=self.arch.ssm_chunk_size)
+        y = ssm.gated_rms_norm(y.reshape(T, self.inner).to(x.dtype), gate, self.norm_weight, self.arch.rms_norm_eps,
+                               self.inner // self.ng, "silu", gate_first=True)
+        return self.out_proj(y)
+
+
+class GatedDeltaNet(nn.Module):
+    def __init__(self, arch: ModelArch, layer_idx: int, dtype=None, device=None):
+        super().__init__()
+        self.arch = arch
+        self.nv, self.nk = arch.linear_num_value_heads, arch.linear_num_key_heads
+        self.dk, self.dv = arch.linear_key_head_dim, arch.linear_value_head_dim
+        self.key_dim, self.value_dim = self.nk * self.dk, self.nv * self.dv
+        conv_dim = 2 * self.key_dim + self.value_dim
+        H, std = arch.hidden_size, arch.initializer_range
+        self.in_proj_qkv = Linear(H, conv_dim, std=std, dtype=dtype, device=device)
+        self.in_proj_z = Linear(H, self.value_dim, std=std, dtype=dtype, device=device)
+        self.in_proj_b = Linear(H, self.nv, std=std, dtype=dtype, device=device)
+        self.in_proj_a = Linear(H, self.nv, std=std, dtype=dtype, device=device)
+        self.conv1d_weight = nn.Parameter(torch.empty(conv_dim, arch.linear_conv_kernel_dim, dtype=dtype, device=device))
+        self.dt_bias = nn.Parameter(torch.ones(self.nv, dtype=torch.float32, device=device))
+        self.A_log = nn.Parameter(torch.zeros(self.nv, dtype=torch.float32, device=device))
+        self.norm_weight = nn.Parameter(torch.ones(self.dv, dtype=dtype, device=device))
+        self.out_proj = Linear(self.value_dim, H, std=std, dtype=dtype, device=device)
+        self.reset_ssm_parameters()
+
+    @torch.no_grad()
+    def reset_ssm_parameters(self, seed: int = 0):
+        gen = torch.Generator().manual_seed(seed)
+        self.A_log.copy_(torch.log(torch.rand(self.nv, generator=gen) * 16 + 1e-3))
+        self.dt_bias.fill_(1.0)
+        nn.init.uniform_(self.conv1d_weight, -0.5, 0.5)
+
+    def forward(self, x: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
+        T = x.shape[0]
+        qkv = ssm.causal_conv1d(self.in_proj_qkv(x), self.conv1d_weight, None, seq.position_ids, "silu")
+        z = self.in_proj_z(x).reshape(T, self.nv, self.dv)
+        beta = torch.sigmoid(self.in_proj_b(x).float())
+        g = -torch.exp(self.A_log.float()) * F.softplus(self.in_proj_a(x).float() + self.dt_bias)
+        q, k, v = qkv.split([self.key_dim, self.key_dim, self.value_dim], dim=-1)
+        q, k = q.reshape(T, self.nk, self.dk), k.reshape(T, self.nk, self.dk)
+        rep = self.nv // self.nk
+        if rep > 1:
+            q, k = q.repeat_interleave(rep, dim=1), k.repeat_interleave(rep, dim=1)
+        o = delta_rule.gated_delta_rule(q, k, v.reshape(T, self.nv, self.dv), g, beta, seq.position_ids)
+        o = ssm.gated_rms_norm(o.to(x.dtype), z, self.norm_weight, self.arch.rms_norm_eps, self.dv, "silu",
+                               gate_first=False)
+        return self.out_proj(o.reshape(T, self.value_dim))
+
+
+class GatedAttention(nn.Module):
+    """Softmax attention whose query projection also emits a sigmoid output gate (per head:
+    ``[q | gate]``), with q/k RMSNorm and partial rotary embedding."""
+
+    def __init__(self, arch: ModelArch, layer_idx: int, attn_backend: str = "auto", dtype=None, device=None):
+        super().__init__()
+        self.arch, self.layer_idx, self.backend = arch, layer_idx, attn_backend
+        H, D, std = arch.hidden_size, arch.head_dim, arch.initializer_range
+        self.nq, self.nkv, self.D = arch.num_attention_heads, arch.num_key_value_heads, D
+        self.q_proj = Linear(H, self.nq * D * 2, bias=arch.attention_bias, std=std, dtype=dtype, device=device)
+        self.k_proj = Linear(H, self.nkv * D, bias=arch.attention_bias, std=std, dtype=dtype, device=device)
+        self.v_proj = Linear(H, self.nkv * D, bias=arch.attention_bias, std=std, dtype=dtype, device=device)
+        self.o_proj = Linear(self.nq * D, H, bias=arch.attention_bias, std=std, dtype=dtype, device=device)
+        self.q_norm = RMSNorm(D, arch.rms_norm_eps, dtype=dtype, device=device)
+        self.k_norm = RMSNorm(D, arch.rms_norm_eps, dtype=dtype, device=device)
+        self.register_buffer("inv_freq", ops.inv_freq(D, arch.rope_theta, device=device, rotary_dim=arch.rotary_dim),
+                             persistent=False)
+
+    def forward(self, x: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
+        T = x.shape[0]
+        qg = self.q_proj(x).view(T, self.nq, 2 * self.D)
+        q, gate = qg[..., : self.D], qg[..., self.D:]
+        k = self.k_proj(x).view(T, self.nkv, self.D)
+        v = self.v_proj(x).view(T, self.nkv, self.D)
+        q = ops.qknorm_rope(q, self.q_norm.weight, seq.position_ids, self.inv_freq, self.arch.rms_norm_eps)
+        k = ops.qknorm_rope(k, self.k_norm.weight, seq.position_ids, self.inv_freq, self.arch.rms_norm_eps)
+        o = attn_ops.attention(q, k, v, seq.cu_seqlens, seq.max_seqlen, causal=True, backend=self.backend,
+                               cache=seq.attn_cache, cache_key=self.layer_idx)
+        o = o * torch.sigmoid(gate.float()).to(o.dtype)
+        return self.o_proj(o.reshape(T, self.nq * self.D))
+
+
+def _deinterleave(x: torch.Tensor) -> torch.Tensor:
+    """(x0, x1, x2, x3, ...) -> (x0, x2, ..., x1, x3, ...): pairs stored interleaved become the
+    two halves that the rotary kernel rotates."""
+    d = x.shape[-1]
+    return x.reshape(*x.shape[:-1], d // 2, 2).transpose(-1, -2).reshape(*x.shape[:-1], d)
+
+
+class DSAIndexer(nn.Module):
+    def __init__(self, arch: ModelArch, dtype=None, device=None):
+        super().__init__()
+        self.nh, self.hd, self.rope = arch.index_n_heads, arch.index_head_dim, arch.qk_rope_head_dim
+        std = arch.initializer_range
+        self.wq_b = Linear(arch.q_lora_rank, self.nh * self.hd, std=std, dtype=dtype, device=device)
+        self.wk = Linear(arch.hidden_size, self.hd, bias=arch.attention_bias, std=std, dtype=dtype, device=device)
+        self.k_norm = nn.LayerNorm(self.hd, eps=1e-6, dtype=dtype, device=device)
+        self.weights_proj = Linear(arch.hidden_size, self.nh, std=std, dtype=dtype, device=device)
+        for p in self.parameters():         # the selection carries no gradient (as in the reference)
+            p.requires_grad_(False)
+
+    @torch.no_grad()
+    def forward(self, x, q_latent, seq: SeqInfo, inv_freq, topk: int) -> torch.Tensor:
+        T = x.shape[0]
+        q = self.wq_b(q_latent).view(T, self.nh, self.hd)
+        k = self.k_norm(self.wk(x)).view(T, 1, self.hd)
+        w = self.weights_proj(x)
+
+        def rope_head(t):
+            pe = ops.qknorm_rope(_deinterleave(t[..., : self.rope]).contiguous(), None, seq.position_ids, inv_freq)
+            return torch.cat([pe, t[..., self.rope:]], dim=-1)
+
+        ks, ke = doc_windows(seq)
+        return sparse_mla.dsa_indexer_topk(rope_head(q), rope_head(k)[:, 0], w, ks, ke, topk)
+
+
+class SparseMLAAttention(nn.Module):
+    """Multi-head latent attention in absorbed form over the top-k keys the indexer selects.
+    ``share_indices``: the layer reuses the selection of the closest earlier layer that has an
+    indexer (kept on ``seq`` for the duration of one forward)."""
+
+    def __init__(self, arch: ModelArch, layer_idx: int, dtype=None, device=None):
+        super().__init__()
+        self.arch, self.layer_idx = arch, layer_idx
+        a, std = arch, arch.initializer_range
+        self.nh = a.num_attention_heads
+        self.qk_head_dim = a.qk_nope_head_dim + a.qk_rope_head_dim
+        self.q_a_proj = Linear(a.hidden_size, a.q_lora_rank, bias=a.attention_bias, std=std, dtype=dtype, device=device)
+        self.q_a_layernorm = RMSNorm(a.q_lora_rank, a.rms_norm_eps, dtype=dtype, device=device)
+        self.q_b_proj = Linear(a.q_lora_rank, self.nh * self.qk_head_dim, std=std, dtype=dtype, device=device)
+        self.kv_a_proj_with_mqa = Linear(a.hidden_size, a.kv_lora_rank + a.qk_rope_head_dim, bias=a.attention_bias,
+                                         std=std, dtype=dtype, device=device)
+        self.kv_a_layernorm = RMSNorm(a.kv_lora_rank, a.rms_norm_eps, dtype=dtype, device=device)
+        self.kv_b_proj = Linear(a.kv_lora_rank, self.nh * (a.qk_nope_head_dim + a.v_head_dim), std=std, dtype=dtype,
+                                device=device)
+        self.o_proj = Linear(self.nh * a.v_head_dim, a.hidden_size, bias=a.attention_bias, std=std, dtype=dtype,
+                             device=device)
+        self.skip_topk = bool(a.index_share_layers and layer_idx in a.index_share_layers)
+        self.indexer = None if self.skip_topk else DSAIndexer(a, dtype=dtype, device=device)
+        # the layer whose selection this one uses (itself, or the closest earlier layer with an indexer)
+        self.index_source = layer_idx
+        while self.index_source in (a.index_share_layers or []):
+            self.index_source -= 1
+        self.scaling = self.qk_head_dim ** -0.5
+        self.register_buffer("inv_freq", ops.inv_freq(a.qk_rope_head_dim, a.rope_theta, device=device), persistent=False)
+
+    def forward(self, x: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
+        a, T = self.arch, x.shape[0]
+        q_latent = self.q_a_layernorm(self.q_a_proj(x))
+        ckv, k_rope = self.kv_a_proj_with_mqa(x).split([a.kv_lora_rank, a.qk_rope_head_dim], dim=-1)
+        ckv = self.kv_a_layernorm(ckv.contiguous())
+        if self.indexer is not None:
+            indices = self.indexer(x, q_latent, seq, self.inv_freq, a.index_topk)
+            if seq.shared is None:
+                seq.shared = {}
+            seq.shared[("dsa", self.layer_idx)] = indices
+        else:
+            indices = (seq.shared or {}).get(("dsa", self.index_source))
+            if indices is None:
+                raise RuntimeError("a layer that shares sparse indices ran before the layer that computes them")
+        q = self.q_b_proj(q_latent).view(T, self.nh, self.qk_head_dim)
+        q_nope, q_rope = q[..., : a.qk_nope_head_dim], q[..., a.qk_nope_head_dim:]
+        q_rope = ops.qknorm_rope(_deinterleave(q_rope).contiguous(), None, seq.position_ids, self.inv_freq)
+        k_rope = ops.qknorm_rope(_deinterleave(k_rope).reshape(T, 1, -1).contiguous(), None, seq.position_ids,
+                                 self.inv_freq)[:, 0]
+        w = self.kv_b_proj.weight.view(self.nh, a.qk_nope_head_dim + a.v_head_dim, a.kv_lora_rank)
+        w_k, w_v = w[:, : a.qk_nope_head_dim], w[:, a.qk_nope_head_dim:]
+        q_abs = torch.einsum("thd,hdk->thk", q_nope, w_k)          # absorb the key up-projection into q
+        sq = torch.cat([q_abs, q_rope], dim=-1)
+        skv = torch.cat([ckv, k_rope], dim=-1)
+        o = sparse_mla.sparse_mla_attention(sq, skv, indices, self.scaling, a.kv_lora_rank)
+        o = torch.einsum("thk,hdk->thd", o, w_v)                    # value up-projection per head
+        return self.o_proj(o.reshape(T, self.nh * a.v_head_dim))

@@ -51,15 +51,19 @@ class CausalLM(nn.Module):
         gen_dev = next(self.parameters()).device
         gen = torch.Generator(device=gen_dev).manual_seed(seed)
         std = self.arch.initializer_range
+        ssm_names = ("A_log", "dt_bias", ".D", "conv1d_weight", "conv1d_bias")
         for name, p in self.named_parameters():
-            if "lora_" in name:
+            if "lora_" in name or name.endswith(ssm_names):
                 continue
-            if name.endswith("norm.weight") or name.endswith("layernorm.weight"):
+            if name.endswith(("norm.weight", "layernorm.weight", "norm_weight")):
                 p.fill_(1.0)
             elif name.endswith(".bias") or name.endswith("sinks"):
                 p.zero_()
             else:
                 p.normal_(0.0, std, generator=gen)
+        for i, m in enumerate(self.modules()):
+            if hasattr(m, "reset_ssm_parameters"):
+                m.reset_ssm_parameters(seed=seed * 7919 + i)
         return self
 
     @property
@@ -101,7 +105,7 @@ class CausalLM(nn.Module):
     # ------------------------------------------------------------------ MoE helpers
     def moe_layers(self) -> Iterable[MoE]:
         for layer in self.model.layers:
-            if isinstance(layer.mlp, MoE):
+            if isinstance(getattr(layer, "mlp", None), MoE):
                 yield layer.mlp
 
     def load_balance_stats(self) -> dict[str, torch.Tensor]:

@@ -1,0 +1,140 @@
+"""Sequence mixers with a recurrent state over packed token streams: the depthwise causal
+convolution and the Mamba-2 selective state-space scan (SSD).
+
+Documents of a packed micro-batch must not see each other. Both ops take the per-token
+position inside its document (``position_ids``): the convolution masks taps that would reach
+before a document's first token, and the scan gives a document's first token a decay of
+``exp(RESET)`` (numerically zero), which clears the carried state exactly where the recurrence
+``S_t = a_t S_{t-1} + dt_t x_t B_t^T`` would otherwise leak it.
+
+The scan is the chunked SSD algorithm: inside a chunk of Q tokens the output is a masked,
+decay-weighted ``(C B^T) x`` product (tensor-core shaped), between chunks a small state
+``[heads, head_dim, state]`` is carried. ``mamba2_scan_ref`` is the token-by-token recurrence
+used by the tests.
+
+The reference calls ``fla.modules.conv.causal_conv1d`` and
+``mamba_ssm.ops.triton.ssd_combined.mamba_chunk_scan_combined`` for these
+(src/prime_rl/trainer/models/nemotron_h/mamba.py:81-83, :201-236).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+RESET = -80.0      # log-decay given to the first token of a document: exp(-80) ~ 1.8e-35
+
+
+def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, position_ids: torch.Tensor,
+                  activation: str | None = "silu") -> torch.Tensor:
+    """Depthwise causal convolution over tokens. ``x [T, C]``, ``weight [C, K]`` (tap K-1 multiplies
+    the current token), ``position_ids [T]`` position of every token in its document."""
+    T, C = x.shape
+    K = weight.shape[1]
+    xf = x.float()
+    y = xf * weight[:, K - 1].float()
+    for s in range(1, K):
+        if s >= T:
+            break
+        shifted = F.pad(xf[:-s], (0, 0, s, 0))
+        ok = (position_ids >= s).unsqueeze(1)
+        y = y + torch.where(ok, shifted, torch.zeros((), dtype=xf.dtype, device=x.device)) * weight[:, K - 1 - s].float()
+    if bias is not None:
+        y = y + bias.float()
+    if activation in ("silu", "swish"):
+        y = F.silu(y)
+    elif activation is not None:
+        raise ValueError(f"unsupported activation '{activation}'")
+    return y.to(x.dtype)
+
+
+def _pad_tokens(t: torch.Tensor, n: int) -> torch.Tensor:
+    if n == 0:
+        return t
+    return F.pad(t, (0, 0) * (t.dim() - 1) + (0, n))
+
+
+def mamba2_scan(x: torch.Tensor, dt: torch.Tensor, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor,
+                D: torch.Tensor | None, position_ids: torch.Tensor, chunk: int = 128) -> torch.Tensor:
+    """Chunked SSD. ``x [T, H, P]``, ``dt [T, H]`` (after softplus / clamping), ``A [H]`` (negative),
+    ``B, C [T, G, N]`` with ``H % G == 0``, ``D [H]`` skip weight. Returns ``[T, H, P]`` in fp32."""
+    T, H, P = x.shape
+    G, N = B.shape[1], B.shape[2]
+    rep = H // G
+    Q = chunk
+    pad = (-T) % Q
+    xf, dtf = _pad_tokens(x.float(), pad), _pad_tokens(dt.float(), pad)
+    Bf, Cf = _pad_tokens(B.float(), pad), _pad_tokens(C.float(), pad)
+    pos = F.pad(position_ids, (0, pad), value=1)
+    a = dtf * A.float()                                              # [Tp, H] log-decay per token
+    a = torch.where((pos == 0).unsqueeze(1), torch.full_like(a, RESET), a)
+    nc = (T + pad) // Q
+    xc = xf.view(nc, Q, H, P)
+    dtc = dtf.view(nc, Q, H)
+    ac = a.view(nc, Q, H)
+    Bc = Bf.view(nc, Q, G, N)
+    Cc = Cf.view(nc, Q, G, N)
+    cum = ac.cumsum(1)                                               # inclusive: decay from chunk start through token i
+    # ---- inside a chunk: y_i += sum_{j <= i} exp(cum_i - cum_j) dt_j (C_i . B_j) x_j
+    diff = cum.unsqueeze(2) - cum.unsqueeze(1)                       # [nc, Q(i), Q(j), H]
+    tri = torch.ones(Q, Q, dtype=torch.bool, device=x.device).tril()
+    L = torch.where(tri[None, :, :, None], diff, torch.full_like(diff, float("-inf"))).exp()
+    cb = torch.einsum("cign,cjgn->cijg", Cc, Bc)                     # [nc, Q, Q, G]
+    M = L * dtc.unsqueeze(1) * cb.repeat_interleave(rep, dim=3)      # [nc, Q, Q, H]
+    y = torch.einsum("cijh,cjhp->cihp", M, xc)
+    # ---- state every chunk hands on: sum_j exp(cum_end - cum_j) dt_j x_j B_j^T
+    to_end = (cum[:, -1:, :] - cum).exp() * dtc                      # [nc, Q, H]
+    Bh = Bc.repeat_interleave(rep, dim=2)                            # [nc, Q, H, N]
+    Ch = Cc.repeat_interleave(rep, dim=2)
+    S_chunk = torch.einsum("cjh,cjhp,cjhn->chpn", to_end, xc, Bh)
+    chunk_decay = cum[:, -1, :].exp()                                # [nc, H]
+    # ---- carry between chunks (a short sequential loop over nc small tensors)
+    carry = torch.zeros(H, P, N, dtype=torch.float32, device=x.device)
+    carries = []
+    for c in range(nc):
+        carries.append(carry)
+        carry = carry * chunk_decay[c][:, None, None] + S_chunk[c]
+    S_in = torch.stack(carries)                                      # state entering every chunk
+    y = y + torch.einsum("cih,cihn,chpn->cihp", cum.exp(), Ch, S_in)
+    y = y.reshape(nc * Q, H, P)[:T]
+    if D is not None:
+        y = y + x.float() * D.float()[None, :, None]
+    return y
+
+
+def mamba2_scan_ref(x, dt, A, B, C, D, position_ids) -> torch.Tensor:
+    """Token-by-token recurrence (fp32), for tests."""
+    T, H, P = x.shape
+    G, N = B.shape[1], B.shape[2]
+    rep = H // G
+    S = torch.zeros(H, P, N, dtype=torch.float32, device=x.device)
+    out = []
+    for t in range(T):
+        if int(position_ids[t]) == 0:
+            S = torch.zeros_like(S)
+        dA = (dt[t].float() * A.float()).exp()
+        Bt = B[t].float().repeat_interleave(rep, dim=0)
+        Ct = C[t].float().repeat_interleave(rep, dim=0)
+        S = S * dA[:, None, None] + dt[t].float()[:, None, None] * x[t].float()[:, :, None] * Bt[:, None, :]
+        y = torch.einsum("hpn,hn->hp", S, Ct)
+        if D is not None:
+            y = y + x[t].float() * D.float()[:, None]
+        out.append(y)
+    return torch.stack(out)
+
+
+def gated_rms_norm(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, group_size: int,
+                   gate_act: str = "silu", gate_first: bool = True) -> torch.Tensor:
+    """RMSNorm over groups of ``group_size`` channels combined with a gate. ``gate_first``:
+    ``norm(x * act(gate)) * w`` (Mamba-2); otherwise ``norm(x) * w * act(gate)`` (gated delta-net)."""
+    act = F.silu if gate_act in ("silu", "swish") else torch.sigmoid
+    xf = x.float()
+    if gate_first:
+        xf = xf * act(gate.float())
+    shp = xf.shape
+    g = xf.reshape(*shp[:-1], shp[-1] // group_size, group_size)
+    g = g * torch.rsqrt(g.square().mean(-1, keepdim=True) + eps)
+    y = g.reshape(shp) * weight.float()
+    if not gate_first:
+        y = y * act(gate.float())
+    return y.to(x.dtype)
