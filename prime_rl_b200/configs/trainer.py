@@ -409,6 +409,7 @@ class TrainerConfig(BaseConfig):
     matmul_precision: Literal["highest", "high", "medium"] = "high"
     max_steps: int | None = None
     enable_router_replay: bool = False
+    log_annotations: bool = False          # per-token trainer logprob / entropy of traced rollouts -> monitors
     memory_profiler_path: Path | None = None
     gc: GCConfig | None = GCConfig()
     trace_path: Path | None = None

@@ -60,6 +60,7 @@ class ModelArch(BaseModel):
     shared_expert_intermediate_size: int = 0   # width of the shared expert when it differs from moe_intermediate_size
     decoder_sparse_step: int = 1
     initializer_range: float = 0.02
+    final_logit_softcapping: float | None = None   # softcap * tanh(z / softcap) on the output logits (Gemma)
     shared_expert_gate: bool = False           # sigmoid gate on the shared expert's output (Qwen3.5-MoE)
     moe_latent_size: int = 0                   # experts work in a projected space of this width (Nemotron-H)
     # layer kinds. block_types: every layer is ONE pre-normed mixer ("mamba" | "attention" | "mlp" | "moe",

@@ -92,12 +92,23 @@ class CausalLM(nn.Module):
         return self.model.norm(h)
 
     def logprobs_entropy(self, hidden: torch.Tensor, labels: torch.Tensor,
-                         inv_temperature: torch.Tensor | None = None):
-        """Per-token log-probability of ``labels`` and entropy, fp32 [T]."""
+                         inv_temperature: torch.Tensor | None = None, sampling_mask: torch.Tensor | None = None):
+        """Per-token log-probability of ``labels`` and entropy, fp32 [T]. ``sampling_mask [T, K]``
+        (ids the engine sampled from, -1 padded) renormalises the log-probabilities over those ids."""
         w = self.output_weight
         if self.lm_head is not None and self.lm_head.lora is not None:
             raise NotImplementedError("LoRA on lm_head is not supported with the fused head")
-        return ops.fused_logprob_entropy(hidden, w, labels.reshape(-1), inv_temperature)
+        labels = labels.reshape(-1)
+        if self.arch.final_logit_softcapping:
+            lp, ent = ops.softcapped_logprob_entropy(hidden, w, labels, inv_temperature,
+                                                     self.arch.final_logit_softcapping)
+        else:
+            lp, ent = ops.fused_logprob_entropy(hidden, w, labels, inv_temperature)
+        if sampling_mask is not None:
+            if self.arch.final_logit_softcapping:
+                raise NotImplementedError("sampling-mask replay with a soft-capped head")
+            lp = ops.replay_sampling_mask(lp, hidden, w, labels, inv_temperature, sampling_mask)
+        return lp, ent
 
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
         return ops.linear(hidden, self.output_weight)

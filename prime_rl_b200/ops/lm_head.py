@@ -90,3 +90,70 @@ def fused_logprob_entropy(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor
         it = inv_temp.float().contiguous() if inv_temp is not None else None
         return _FusedLogprobEntropy.apply(h, w, lab, it)
     return logprob_entropy_ref(h, w, labels, inv_temp)
+
+
+def sampling_replay_rows(sampling_mask: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+    """Rows whose sampling mask can be replayed: not empty (-1 = padding) and containing the label
+    (a label outside its mask means misaligned data; such rows keep the full-vocabulary value)."""
+    return (sampling_mask >= 0).any(-1) & (sampling_mask == labels.unsqueeze(-1)).any(-1)
+
+
+def replay_sampling_mask(logprobs: torch.Tensor, h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor,
+                         inv_temp: torch.Tensor | None, sampling_mask: torch.Tensor,
+                         bytes_budget: int = 1 << 29) -> torch.Tensor:
+    """Renormalises ``logprobs [T]`` over the ids the rollout engine actually sampled from
+    (``sampling_mask [T, K]`` int, -1 padded; top-k / top-p / min-p truncation): replayable rows get
+    ``z[label] - logsumexp(z[mask ids])``, the rest keep their full-vocabulary value. Only the
+    ``K`` masked logits per row are recomputed (rows of ``w`` gathered in blocks of tokens), so the
+    fused head stays fused. Same contract as the reference's mask replay
+    (src/prime_rl/trainer/models/layers/lm_head.py:97-111, :167-198; trainer/rl/loss.py:66-84)."""
+    T, K = sampling_mask.shape
+    H = h.shape[1]
+    lab = labels.long()
+    replay = sampling_replay_rows(sampling_mask, lab)
+    ids = sampling_mask.clamp_min(0).long()
+    block = max(1, bytes_budget // max(1, K * H * w.element_size()))
+    outs = []
+    for t0 in range(0, T, block):
+        t1 = min(T, t0 + block)
+        hb = h[t0:t1]
+        z = torch.einsum("th,tkh->tk", hb.float(), w[ids[t0:t1]].float())
+        tgt = (hb.float() * w[lab[t0:t1].clamp(0, w.shape[0] - 1)].float()).sum(-1)
+        if inv_temp is not None:
+            it = inv_temp[t0:t1].float()
+            z, tgt = z * it[:, None], tgt * it
+        z = torch.where(sampling_mask[t0:t1] >= 0, z, torch.full_like(z, float("-inf")))
+        z = torch.where(replay[t0:t1, None], z, torch.zeros_like(z))     # keeps the unused branch finite
+        outs.append(tgt - torch.logsumexp(z, dim=-1))
+    return torch.where(replay, torch.cat(outs), logprobs)
+
+
+def softcapped_logprob_entropy(h, w, labels, inv_temp=None, softcap: float = 30.0, chunk: int = 2048):
+    """Head with ``softcap * tanh(z / softcap)`` applied to the logits before temperature scaling
+    (Gemma family; src/prime_rl/trainer/models/layers/lm_head_gemma.py). Token-chunked, with the
+    chunk's logits recomputed in backward by checkpointing, so at most ``chunk x V`` logits exist."""
+    from torch.utils.checkpoint import checkpoint
+
+    def piece(hc, lc, ic):
+        z = softcap * torch.tanh((hc.float() @ w.float().t()) / softcap)
+        if ic is not None:
+            z = z * ic.float()[:, None]
+        lse = torch.logsumexp(z, dim=-1)
+        lb = lc.long()
+        valid = (lb >= 0) & (lb < w.shape[0])
+        tgt = z.gather(1, lb.clamp(0, w.shape[0] - 1)[:, None]).squeeze(1)
+        lp = torch.where(valid, tgt - lse, torch.zeros_like(lse))
+        with torch.no_grad():
+            ent = lse - (torch.softmax(z, dim=-1) * z).sum(-1)
+        return lp, ent
+
+    lps, ents = [], []
+    for s in range(0, h.shape[0], chunk):
+        ic = inv_temp[s:s + chunk] if inv_temp is not None else None
+        if torch.is_grad_enabled() and (h.requires_grad or w.requires_grad):
+            lp, ent = checkpoint(piece, h[s:s + chunk], labels[s:s + chunk], ic, use_reentrant=False)
+        else:
+            lp, ent = piece(h[s:s + chunk], labels[s:s + chunk], ic)
+        lps.append(lp)
+        ents.append(ent.detach())
+    return torch.cat(lps), torch.cat(ents)

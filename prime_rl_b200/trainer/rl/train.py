@@ -50,6 +50,11 @@ class RLTrainer:
         dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
         self.monitor = monitors_mod.setup(cfg.monitors, self.run_dir, "trainer", is_master=self.world.is_master,
                                           run_config=cfg.model_dump(mode="json"))
+        self.annotations = None
+        if cfg.log_annotations:
+            from .annotations import AnnotationWriter
+
+            self.annotations = AnnotationWriter(self.monitor, self.world.rank, self.world.world_size)
         t0 = time.perf_counter()
         self.model = build_model(self.arch, device=self.device, dtype=dtype, attn_backend=mc.attn, seed=0)
         self._maybe_load_pretrained()
@@ -177,12 +182,20 @@ class RLTrainer:
                 hidden = self.model(ids, seq)
         else:
             hidden = self.model(ids, seq)
-        logprobs, entropy = self.model.logprobs_entropy(hidden, labels, inv_temp)
+        smask = None
+        if mb.sampling_mask is not None:
+            if self.cp_ctx is not None:
+                raise NotImplementedError("sampling-mask replay together with context parallelism")
+            sm = mb.sampling_mask                       # row t: the ids token t was drawn from
+            smask = torch.cat([sm[1:], torch.full_like(sm[:1], -1)], dim=0)     # aligned with the labels
+        logprobs, entropy = self.model.logprobs_entropy(hidden, labels, inv_temp, smask)
         if self.cp_ctx is not None:
             logprobs, entropy = self.cp_ctx.gather_outputs(logprobs, entropy)
         V = self.arch.vocab_size
         logprobs = shift_right(logprobs, math.log(1.0 / V))
         entropy = shift_right(entropy, math.log(float(V)))
+        if self.annotations is not None:
+            self.annotations.collect(mb, logprobs, entropy, self.progress.step)
         loss, lm = compute_loss(
             trainer_logprobs=logprobs, inference_logprobs=mb.inference_logprobs, advantages=mb.advantages,
             loss_mask=mb.loss_mask, rl_loss_fn=self.loss_fn, rl_scale=scales[0], ce_scale=scales[1],
@@ -219,6 +232,8 @@ class RLTrainer:
         for mb in micro_batches:
             for k, v in self.forward_backward(mb, scales).items():
                 agg.setdefault(k, []).append(v)
+        if self.annotations is not None:
+            self.annotations.flush()
         self.optimizer.reduce_gradients()
         grad_norm = self.optimizer.step()
         lr = self.optimizer.schedule.lr_at(self.optimizer.step_count - 1)

@@ -81,3 +81,80 @@ def test_sbatch_rendering_multi_node(tmp_path):
     assert "#SBATCH --nodes=4" in text and "--job-name=rl-test" in text and "--partition=b200" in text
     assert "--nnodes=2" in text and "prime_rl_b200.trainer.rl.train" in text
     assert "prime_rl_b200.entrypoints.inference" in text and "prime_rl_b200.entrypoints.orchestrator" in text
+
+
+def test_trainer_annotations_reach_the_file_monitor(tmp_path):
+    import json
+    from types import SimpleNamespace
+
+    import torch
+
+    from prime_rl_b200.monitors import FileMonitor, MultiMonitor
+    from prime_rl_b200.trainer.rl.annotations import AnnotationWriter
+
+    mon = MultiMonitor([FileMonitor(tmp_path, "trainer")])
+    w = AnnotationWriter(mon)
+    mb = SimpleNamespace(sequence_lengths=[3, 2, 4], trace_ids=["a", "", "b"], branch_indices=[0, -1, 2],
+                         loss_mask=torch.tensor([0, 1, 1, 0, 0, 0, 1, 1, 1], dtype=torch.bool))
+    w.collect(mb, torch.arange(9).float() * -0.5, torch.ones(9), step=7)
+    assert w.flush() == 2
+    files = list(tmp_path.rglob("annotations_trainer.jsonl"))
+    rows = [json.loads(l) for l in files[0].read_text().splitlines()]
+    assert [r["trace_id"] for r in rows] == ["a", "b"] and rows[1]["branch_index"] == 2 and rows[0]["step"] == 7
+    assert rows[1]["logprobs"] == [-2.5, -3.0, -3.5, -4.0] and rows[0]["loss_mask"] == [False, True, True]
+    assert w.flush() == 0
+
+
+def test_chat_session_keeps_history_and_handles_commands():
+    import httpx
+
+    from prime_rl_b200.engine.chat import ChatSession
+
+    seen = []
+
+    def handler(request: httpx.Request) -> httpx.Response:
+        import json as _json
+
+        if request.url.path == "/v1/models":
+            return httpx.Response(200, json={"data": [{"id": "m"}]})
+        body = _json.loads(request.content)
+        seen.append(body)
+        return httpx.Response(200, json={"choices": [{"message": {"role": "assistant",
+                                                                  "content": f"reply {len(body['messages'])}"}}]})
+
+    chat = ChatSession("http://x", system="be brief", transport=httpx.MockTransport(handler))
+    assert chat.say("hi") == "reply 2"
+    assert chat.say("again") == "reply 4"
+    assert seen[1]["messages"][0] == {"role": "system", "content": "be brief"} and seen[1]["model"] == "m"
+    assert chat.command("/temp 0.2") == "temperature 0.2" and chat.command("hello") is None
+    assert chat.command("/reset") == "conversation cleared" and chat.messages == []
+
+
+def test_benchmark_runner_config_and_result_table(tmp_path):
+    import importlib.util
+    import json
+
+    def load(name):
+        path = Path(__file__).resolve().parents[1] / "benchmarks" / f"{name}.py"
+        spec = importlib.util.spec_from_file_location(name, path)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        return mod
+
+    run, agg = load("run_single_benchmark"), load("aggregate_results")
+    cfg = run.build_config(run.parse_args(["--model-name", "qwen3-30b-a3b", "--lora-rank", "16", "--num-gpus", "8",
+                                           "--ac", "Offload", "--output", str(tmp_path / "r.json")]))
+    assert cfg["model"]["lora"] == {"rank": 16, "alpha": 32.0} and cfg["data"]["fake"]["batch_size"] == 16
+    assert cfg["model"]["ac_offloading"] == {"pin_memory": True}
+    from prime_rl_b200.configs.trainer import TrainerConfig
+
+    TrainerConfig.model_validate(cfg)
+    good = {"config": {"type": "rl", "model_name": "m", "num_gpus": 8, "success": True, "seq_len": 16384, "lora_rank": 16},
+            "metrics": {"throughput": {"mean": 9266.0}, "mfu": {"mean": 7.8}, "step_time": {"mean": 28.3},
+                        "peak_memory": {"gib": 100.0}}}
+    bad = {"config": {"success": False}, "metrics": {}}
+    (tmp_path / "a.json").write_text(json.dumps(good))
+    (tmp_path / "b.json").write_text(json.dumps(bad))
+    assert agg.main([str(tmp_path / "a.json"), str(tmp_path / "b.json"), "--output", str(tmp_path / "t.md")]) == 0
+    text = (tmp_path / "t.md").read_text()
+    assert "9266.00" in text and text.count("\n") == 3

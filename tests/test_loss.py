@@ -73,3 +73,55 @@ def test_empty_mask_still_backpropagates():
                            rl_scale=1.0)
     loss.backward()
     assert lp.grad is not None and float(loss) == 0.0 and math.isfinite(float(loss))
+
+
+def test_sampling_mask_replay_matches_masked_log_softmax():
+    import torch
+    from prime_rl_b200 import ops
+
+    torch.manual_seed(0)
+    T, H, V, K = 23, 16, 50, 6
+    h = torch.randn(T, H, requires_grad=True)
+    w = torch.randn(V, H) * 0.3
+    labels = torch.randint(0, V, (T,))
+    inv_t = torch.rand(T) + 0.5
+    mask = torch.full((T, K), -1, dtype=torch.int32)
+    for t in range(T):
+        if t % 5 == 0:
+            continue                                        # empty mask: full-vocabulary value
+        ids = torch.randperm(V)[: (t % K) + 1]
+        if t % 7 != 0:
+            ids[0] = labels[t]                              # t % 7 == 0: label not in mask -> full vocabulary
+        mask[t, : len(ids)] = ids.to(torch.int32)
+    full, _ = ops.logprob_entropy_ref(h, w, labels, inv_t)
+    got = ops.replay_sampling_mask(full, h, w, labels, inv_t, mask, bytes_budget=4 * K * H * 4)
+    z = (h @ w.t()) * inv_t[:, None]
+    for t in range(T):
+        ids = [int(i) for i in mask[t] if int(i) >= 0]
+        if ids and int(labels[t]) in ids:
+            want = z[t, labels[t]] - torch.logsumexp(z[t, ids], 0)
+        else:
+            want = full[t]
+        assert abs(float(got[t] - want)) < 1e-5, t
+    got.sum().backward()
+    assert torch.isfinite(h.grad).all()
+
+
+def test_softcapped_head_matches_direct_formula():
+    import torch
+    from prime_rl_b200 import ops
+
+    torch.manual_seed(1)
+    T, H, V = 19, 8, 40
+    h = torch.randn(T, H, requires_grad=True)
+    w = torch.randn(V, H)
+    labels = torch.randint(0, V, (T,))
+    lp, ent = ops.softcapped_logprob_entropy(h, w, labels, None, softcap=5.0, chunk=7)
+    z = 5.0 * torch.tanh((h @ w.t()) / 5.0)
+    want = torch.log_softmax(z, -1).gather(1, labels[:, None]).squeeze(1)
+    assert torch.allclose(lp, want, atol=1e-5)
+    p = torch.softmax(z, -1)
+    assert torch.allclose(ent, -(p * torch.log(p)).sum(-1), atol=1e-4)
+    g1, = torch.autograd.grad(lp.sum(), h, retain_graph=True)
+    g2, = torch.autograd.grad(want.sum(), h)
+    assert torch.allclose(g1, g2, atol=1e-5)
