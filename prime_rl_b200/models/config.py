@@ -34,7 +34,7 @@ class ModelArch(BaseModel):
     tie_word_embeddings: bool = False
     attention_bias: bool = False
     qk_norm: bool = True                       # per-head RMSNorm on q and k (Qwen3 family)
-    hidden_act: Literal["silu", "swiglu_clamped", "relu2"] = "silu"
+    hidden_act: Literal["silu", "swiglu_clamped", "relu2", "silu_clamped"] = "silu"
     swiglu_limit: float = 7.0
     swiglu_alpha: float = 1.702
     # attention pattern
@@ -95,6 +95,16 @@ class ModelArch(BaseModel):
     index_head_dim: int = 0
     index_topk: int = 0
     index_share_layers: list[int] = []        # layers without an indexer: they reuse the previous selection
+    # DeepSeek-V4: hyper-connection streams, compressed attention, grouped output projection, hash-routed layers
+    hc_mult: int = 0
+    hc_sinkhorn_iters: int = 20
+    hc_eps: float = 1e-6
+    csa_compress_rate: int = 0                # "compressed_sparse_attention" layers
+    hca_compress_rate: int = 0                # "heavily_compressed_attention" layers
+    compress_rope_theta: float = 160000.0
+    o_groups: int = 1
+    o_lora_rank: int = 0
+    num_hash_layers: int = 0
 
     # ------------------------------------------------------------------ derived
     @property
@@ -306,6 +316,31 @@ class ModelArch(BaseModel):
                          moe_intermediate_size=cfg["moe_intermediate_size"], norm_topk_prob=True, n_shared_experts=1,
                          shared_expert_intermediate_size=cfg.get("shared_expert_intermediate_size", 0),
                          shared_expert_gate=True)
+        elif mt == "deepseek_v4":
+            n = cfg["num_hidden_layers"]
+            rates = cfg.get("compress_rates") or {}
+            kinds = cfg.get("layer_types")
+            if kinds is None:
+                inter = ["compressed_sparse_attention" if i % 2 == 0 else "heavily_compressed_attention"
+                         for i in range(max(n - 2, 0))]
+                kinds = (["heavily_compressed_attention"] * min(n, 2) + inter)[:n]
+            hd = cfg.get("head_dim", 512)
+            d.update(qk_norm=False, head_dim=hd, num_key_value_heads=1, layer_types=kinds,
+                     sliding_window=cfg.get("sliding_window", 128), hidden_act="silu_clamped",
+                     swiglu_limit=cfg.get("swiglu_limit", 10.0), q_lora_rank=cfg["q_lora_rank"],
+                     qk_rope_head_dim=cfg.get("qk_rope_head_dim") or int(hd * cfg.get("partial_rotary_factor", 0.125)),
+                     compress_rope_theta=cfg.get("compress_rope_theta", 160000.0),
+                     csa_compress_rate=rates.get("compressed_sparse_attention", 4),
+                     hca_compress_rate=rates.get("heavily_compressed_attention", 128),
+                     index_n_heads=cfg.get("index_n_heads", 64), index_head_dim=cfg.get("index_head_dim", 128),
+                     index_topk=cfg.get("index_topk", 512), o_groups=cfg.get("o_groups", 8),
+                     o_lora_rank=cfg.get("o_lora_rank", 1024), num_hash_layers=cfg.get("num_hash_layers", 3),
+                     hc_mult=cfg.get("hc_mult", 4), hc_sinkhorn_iters=cfg.get("hc_sinkhorn_iters", 20),
+                     hc_eps=cfg.get("hc_eps", 1e-6), num_experts=cfg["n_routed_experts"],
+                     num_experts_per_tok=cfg["num_experts_per_tok"], moe_intermediate_size=cfg["moe_intermediate_size"],
+                     norm_topk_prob=True, score_func="sigmoid", router_bias=True,
+                     routed_scaling_factor=cfg.get("routed_scaling_factor", 1.0),
+                     n_shared_experts=1 if cfg.get("n_shared_experts", 1) > 0 else 0)
         elif mt == "glm_moe_dsa":
             n = cfg["num_hidden_layers"]
             d.update(qk_norm=False, sliding_window=None, mixer_types=["mla_dsa"] * n,
@@ -333,7 +368,8 @@ class ModelArch(BaseModel):
                       "gpt_oss": "GptOssForCausalLM", "minimax_m2": "MiniMaxM2ForCausalLM",
                       "afmoe": "AfmoeForCausalLM", "laguna": "LagunaForCausalLM",
                       "nemotron_h": "NemotronHForCausalLM", "qwen3_5": "Qwen3_5ForCausalLM",
-                      "qwen3_5_moe": "Qwen3_5MoeForCausalLM", "glm_moe_dsa": "GlmMoeDsaForCausalLM"}
+                      "qwen3_5_moe": "Qwen3_5MoeForCausalLM", "glm_moe_dsa": "GlmMoeDsaForCausalLM",
+                      "deepseek_v4": "DeepseekV4ForCausalLM"}
         cfg: dict[str, Any] = dict(
             architectures=[arch_names.get(self.model_type, "LlamaForCausalLM")], model_type=self.model_type,
             vocab_size=self.vocab_size, hidden_size=self.hidden_size, num_hidden_layers=self.num_hidden_layers,
@@ -380,6 +416,17 @@ class ModelArch(BaseModel):
                        linear_value_head_dim=self.linear_value_head_dim,
                        linear_conv_kernel_dim=self.linear_conv_kernel_dim,
                        shared_expert_intermediate_size=self.shared_width)
+        elif self.model_type == "deepseek_v4":
+            cfg.update(layer_types=self.layer_types, sliding_window=self.sliding_window, swiglu_limit=self.swiglu_limit,
+                       q_lora_rank=self.q_lora_rank, qk_rope_head_dim=self.qk_rope_head_dim,
+                       compress_rope_theta=self.compress_rope_theta,
+                       compress_rates={"compressed_sparse_attention": self.csa_compress_rate,
+                                       "heavily_compressed_attention": self.hca_compress_rate},
+                       index_n_heads=self.index_n_heads, index_head_dim=self.index_head_dim, index_topk=self.index_topk,
+                       o_groups=self.o_groups, o_lora_rank=self.o_lora_rank, num_hash_layers=self.num_hash_layers,
+                       hc_mult=self.hc_mult, hc_sinkhorn_iters=self.hc_sinkhorn_iters, hc_eps=self.hc_eps,
+                       n_routed_experts=self.num_experts, n_shared_experts=self.n_shared_experts,
+                       routed_scaling_factor=self.routed_scaling_factor)
         elif self.model_type == "glm_moe_dsa":
             cfg.update(kv_lora_rank=self.kv_lora_rank, q_lora_rank=self.q_lora_rank,
                        qk_rope_head_dim=self.qk_rope_head_dim, qk_nope_head_dim=self.qk_nope_head_dim,
@@ -430,6 +477,16 @@ PRESETS: dict[str, dict[str, Any]] = {
                              qk_nope_head_dim=16, v_head_dim=24, index_n_heads=2, index_head_dim=32, index_topk=8,
                              index_share_layers=[2], num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
                              score_func="sigmoid", router_bias=True, n_shared_experts=1, first_k_dense_replace=1,
+                             max_position_embeddings=512),
+    "tiny-deepseek-v4": dict(model_type="deepseek_v4", hidden_size=64, num_hidden_layers=4, num_attention_heads=4,
+                             num_key_value_heads=1, head_dim=32, intermediate_size=128, vocab_size=256, qk_norm=False,
+                             layer_types=["sliding_attention", "heavily_compressed_attention",
+                                          "compressed_sparse_attention", "heavily_compressed_attention"],
+                             sliding_window=6, hidden_act="silu_clamped", swiglu_limit=10.0, q_lora_rank=24,
+                             qk_rope_head_dim=8, csa_compress_rate=2, hca_compress_rate=4, index_n_heads=2,
+                             index_head_dim=16, index_topk=4, o_groups=2, o_lora_rank=16, num_hash_layers=1,
+                             hc_mult=2, hc_sinkhorn_iters=4, num_experts=4, num_experts_per_tok=2,
+                             moe_intermediate_size=32, score_func="sigmoid", router_bias=True, n_shared_experts=1,
                              max_position_embeddings=512),
     "tiny-qwen3-moe": dict(model_type="qwen3_moe", hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
                            num_key_value_heads=2, head_dim=64, intermediate_size=512, num_experts=8,

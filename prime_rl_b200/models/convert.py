@@ -136,6 +136,20 @@ class MapValue:
                 (self.inv(v) if k.endswith(self.new_suffix) else v) for k, v in sd.items()}
 
 
+class ExactMap:
+    """Key-for-key rename given as ``{prime name: published name}``."""
+
+    def __init__(self, table: dict[str, str]):
+        self.fwd = dict(table)
+        self.inv = {v: k for k, v in table.items()}
+
+    def forward(self, sd: StateDict) -> StateDict:
+        return {self.fwd.get(k, k): v for k, v in sd.items()}
+
+    def inverse(self, sd: StateDict) -> StateDict:
+        return {self.inv.get(k, k): v for k, v in sd.items()}
+
+
 class Chain:
     def __init__(self, ops: list):
         self.ops = ops
@@ -219,7 +233,48 @@ def _family_chain(arch: ModelArch) -> list:
     return ops
 
 
+def _deepseek_v4_chain(arch: ModelArch) -> Chain:
+    """The published DeepSeek-V4 checkpoints use a compact naming without a ``model.`` prefix
+    (``layers.N.attn.wq_a``, ``ffn.experts.E.w1`` ...; reference:
+    src/prime_rl/trainer/models/deepseek_v4/converting_deepseek_v4.py:27-106)."""
+    table = {"model.embed_tokens.weight": "embed.weight", "model.norm.weight": "norm.weight",
+             "lm_head.weight": "head.weight", "model.hc_head.hc_fn": "hc_head_fn",
+             "model.hc_head.hc_base": "hc_head_base", "model.hc_head.hc_scale": "hc_head_scale"}
+    comp = {"kv_proj.weight": "wkv.weight", "gate_proj.weight": "wgate.weight", "kv_norm.weight": "norm.weight",
+            "position_bias": "ape"}
+    for i in range(arch.num_hidden_layers):
+        a = b = f"model.layers.{i}"          # the last op of the chain strips the `model.` prefix of the layers
+        table.update({f"{a}.input_layernorm.weight": f"{b}.attn_norm.weight",
+                      f"{a}.post_attention_layernorm.weight": f"{b}.ffn_norm.weight"})
+        for hc, short in (("attn_hc", "hc_attn"), ("ffn_hc", "hc_ffn")):
+            for leaf in ("fn", "base", "scale"):
+                table[f"{a}.{hc}.{leaf}"] = f"{b}.{short}_{leaf}"
+        for ours, theirs in (("q_a_proj.weight", "wq_a.weight"), ("q_a_norm.weight", "q_norm.weight"),
+                             ("q_b_proj.weight", "wq_b.weight"), ("kv_proj.weight", "wkv.weight"),
+                             ("kv_norm.weight", "kv_norm.weight"), ("o_a_proj.weight", "wo_a.weight"),
+                             ("o_b_proj.weight", "wo_b.weight"), ("sinks", "attn_sink")):
+            table[f"{a}.self_attn.{ours}"] = f"{b}.attn.{theirs}"
+        for ours, theirs in comp.items():
+            table[f"{a}.self_attn.compressor.{ours}"] = f"{b}.attn.compressor.{theirs}"
+            table[f"{a}.self_attn.indexer.compressor.{ours}"] = f"{b}.attn.indexer.compressor.{theirs}"
+        table[f"{a}.self_attn.indexer.q_b_proj.weight"] = f"{b}.attn.indexer.wq_b.weight"
+        table[f"{a}.self_attn.indexer.weights_proj.weight"] = f"{b}.attn.indexer.weights_proj.weight"
+        table.update({f"{a}.mlp.router.gate.weight": f"{b}.ffn.gate.weight",
+                      f"{a}.mlp.router.e_score_correction_bias": f"{b}.ffn.gate.bias",
+                      f"{a}.mlp.router.tid2eid": f"{b}.ffn.gate.tid2eid",
+                      f"{a}.mlp.shared_experts.gate_proj.weight": f"{b}.ffn.shared_experts.w1.weight",
+                      f"{a}.mlp.shared_experts.down_proj.weight": f"{b}.ffn.shared_experts.w2.weight",
+                      f"{a}.mlp.shared_experts.up_proj.weight": f"{b}.ffn.shared_experts.w3.weight"})
+    return Chain([StackExperts("mlp.experts.gate_proj", "ffn.experts.{e}.w1.weight"),
+                  StackExperts("mlp.experts.down_proj", "ffn.experts.{e}.w2.weight"),
+                  StackExperts("mlp.experts.up_proj", "ffn.experts.{e}.w3.weight"),
+                  ExactMap(table),
+                  Rename(r"^model\.layers\.", "layers.", r"^layers\.", "model.layers.")])
+
+
 def prime_to_hf_chain(arch: ModelArch) -> Chain:
+    if arch.model_type == "deepseek_v4":
+        return _deepseek_v4_chain(arch)
     ops: list = []
     if arch.model_type in ("qwen3_5_moe",):
         ops += [Rename(r"mlp\.shared_experts\.", r"mlp.shared_expert.", r"mlp\.shared_expert\.", r"mlp.shared_experts.")]

@@ -185,7 +185,8 @@ class Attention(nn.Module):
         return self.o_proj(o.reshape(T, self.nq * self.D))
 
 
-_ACT = {"silu": act_ops.SWIGLU, "swiglu_clamped": act_ops.SWIGLU_CLAMPED, "relu2": act_ops.RELU2}
+_ACT = {"silu": act_ops.SWIGLU, "swiglu_clamped": act_ops.SWIGLU_CLAMPED, "relu2": act_ops.RELU2,
+        "silu_clamped": act_ops.SILU_CLAMPED}
 
 
 class DenseMLP(nn.Module):

@@ -25,8 +25,14 @@ class DecoderStack(nn.Module):
     def __init__(self, arch: ModelArch, attn_backend: str, dtype, device):
         super().__init__()
         self.embed_tokens = nn.Embedding(arch.vocab_size, arch.hidden_size, dtype=dtype, device=device)
+        layer_cls = DecoderLayer
+        if arch.hc_mult:                      # DeepSeek-V4: layers work on [T, hc_mult, hidden] residual streams
+            from .deepseek_v4 import DSV4DecoderLayer, HyperHead
+
+            layer_cls = DSV4DecoderLayer
+            self.hc_head = HyperHead(arch, dtype=dtype, device=device)
         self.layers = nn.ModuleList(
-            [DecoderLayer(arch, i, attn_backend, dtype=dtype, device=device) for i in range(arch.num_hidden_layers)])
+            [layer_cls(arch, i, attn_backend, dtype=dtype, device=device) for i in range(arch.num_hidden_layers)])
         self.norm = RMSNorm(arch.hidden_size, arch.rms_norm_eps, dtype=dtype, device=device)
 
 
@@ -55,8 +61,10 @@ class CausalLM(nn.Module):
         for name, p in self.named_parameters():
             if "lora_" in name or name.endswith(ssm_names):
                 continue
-            if name.endswith(("norm.weight", "layernorm.weight", "norm_weight")):
+            if name.endswith(("norm.weight", "layernorm.weight", "norm_weight", "hc.scale", "hc_head.hc_scale")):
                 p.fill_(1.0)
+            elif name.endswith(("hc.base", "hc_head.hc_base", "position_bias")):
+                p.zero_()
             elif name.endswith(".bias") or name.endswith("sinks"):
                 p.zero_()
             else:
@@ -80,6 +88,9 @@ class CausalLM(nn.Module):
         """input_ids: [T] (or [1, T]) packed ids -> final hidden states [T, H] (normed)."""
         ids = input_ids.reshape(-1)
         h = self.model.embed_tokens(ids)
+        if self.arch.hc_mult:
+            h = h.unsqueeze(1).expand(-1, self.arch.hc_mult, -1).contiguous()
+            seq.shared = dict(seq.shared or {}, input_ids=ids)      # hash-routed layers look tokens up by id
         use_ac = self.ac_every is not None and self.training and torch.is_grad_enabled()
         # recomputation re-runs everything but the attention kernel: its output (and lse) of the
         # first pass is kept, 2 bytes x q_dim per token and layer
@@ -89,6 +100,8 @@ class CausalLM(nn.Module):
                 h = checkpoint(self._run_layer, layer, i, h, seq, use_reentrant=False)
             else:
                 h = self._run_layer(layer, i, h, seq)
+        if self.arch.hc_mult:
+            h = self.model.hc_head(h)
         return self.model.norm(h)
 
     def logprobs_entropy(self, hidden: torch.Tensor, labels: torch.Tensor,

@@ -41,6 +41,7 @@ _CUDA_SIGNATURES = {
     "prb_ep_wait": [P, I, I, I, P, P],
     "prb_gemm_bf16_reduce_scatter": [P, P, I, I, I, L, L, I, I, F, P, I, I, L, P, P],
     "prb_gemm_bf16_allgather": [P, P, P, P, I, I, I, L, L, I, I, F, I, I, I, P, I, P, P],
+    "prb_sparse_mla_fwd": [P, P, P, P, P, I, I, I, I, F, P, P],
     "prb_ep_signal": [P, I, I, I, I, P],
     "prb_ep_pull": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
     "prb_gemm_bf16_ext": [P, P, P, I, I, I, L, L, L, I, I, I, F, F, P, I, I, I, P, P, I, L, L, I, P, P],

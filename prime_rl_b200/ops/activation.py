@@ -7,7 +7,7 @@ import torch.nn.functional as F
 
 from . import _runtime as rt
 
-SWIGLU, SWIGLU_CLAMPED, RELU2 = 0, 1, 2
+SWIGLU, SWIGLU_CLAMPED, RELU2, SILU_CLAMPED = 0, 1, 2, 3    # SILU_CLAMPED: silu(min(g, L)) * clamp(u, -L, L) (DeepSeek-V4)
 
 
 def glu_ref(g, u, act=SWIGLU, limit=7.0, alpha=1.702):
@@ -18,6 +18,8 @@ def glu_ref(g, u, act=SWIGLU, limit=7.0, alpha=1.702):
         gc = gf.clamp(max=limit)
         uc = u.float().clamp(-limit, limit)
         y = gc * torch.sigmoid(alpha * gc) * (uc + 1.0)
+    elif act == SILU_CLAMPED:
+        y = F.silu(gf.clamp(max=limit)) * u.float().clamp(-limit, limit)
     else:
         y = F.relu(gf) ** 2
     return y.to(g.dtype)
@@ -60,7 +62,7 @@ def glu(gate_up: torch.Tensor, act: int = SWIGLU, limit: float = 7.0, alpha: flo
     """``gate_up`` holds ``[gate | up]`` along the last dim (just ``gate`` for ReLU^2)."""
     shape = gate_up.shape
     I = shape[-1] if act == RELU2 else shape[-1] // 2
-    if gate_up.is_cuda and gate_up.dtype == torch.bfloat16 and I % 8 == 0:
+    if act != SILU_CLAMPED and gate_up.is_cuda and gate_up.dtype == torch.bfloat16 and I % 8 == 0:
         gu2 = gate_up.reshape(-1, shape[-1])
         if not gu2.is_contiguous():
             gu2 = gu2.contiguous()

@@ -206,7 +206,33 @@ def bench_norm(timer, args, dev):
     _report(f"rmsnorm fwd {T}x{H}", timer(lambda: rms_norm(x, w, 1e-6)), bytes_=2 * T * H * 2)
 
 
-OPS = {"gemm": bench_gemm, "grouped": bench_grouped, "fp8": bench_fp8, "lm_head": bench_lm_head, "flash_fwd": bench_flash_fwd,
+def bench_sparse_mla(timer, args, dev):
+    from . import _runtime as rt
+
+    T, H, topk = args.tokens or 4096, 128, 2048
+    S = T
+    q = (torch.randn(T, H, 576, device=dev) * 0.3).bfloat16()
+    kv = (torch.randn(S, 576, device=dev) * 0.3).bfloat16()
+    # causal-style selection: query t picks from [0, t]; early queries have empty slots
+    idx = (torch.rand(T, topk, device=dev) * (torch.arange(T, device=dev)[:, None] + 1)).to(torch.int32)
+    idx[:, :] = torch.where(torch.arange(topk, device=dev)[None, :] <= torch.arange(T, device=dev)[:, None], idx,
+                            torch.full_like(idx, S))
+    out = torch.empty(T, H, 512, dtype=torch.bfloat16, device=dev)
+    lse = torch.empty(T, H, dtype=torch.float32, device=dev)
+    st = rt.status_tensor(dev)
+
+    def run():
+        rt.check(rt.lib().prb_sparse_mla_fwd(q.data_ptr(), kv.data_ptr(), idx.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                             T, H, S, topk, 576 ** -0.5, st.data_ptr(), rt.stream_ptr(dev)),
+                 "prb_sparse_mla_fwd")
+
+    fl = 2.0 * T * H * topk * (576 + 512)
+    _report(f"sparse MLA fwd T={T} H={H} top-{topk} (576 + 512 channels)", timer(run), flops=fl,
+            extra="(algorithmic FLOPs; the two output halves each repeat Q K^T)")
+    rt.check_status()
+
+
+OPS = {"gemm": bench_gemm, "sparse_mla": bench_sparse_mla, "grouped": bench_grouped, "fp8": bench_fp8, "lm_head": bench_lm_head, "flash_fwd": bench_flash_fwd,
        "flash_bwd": bench_flash_bwd, "paged": bench_paged, "norm": bench_norm}
 
 

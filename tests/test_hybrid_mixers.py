@@ -152,7 +152,7 @@ def test_hf_state_dict_names_and_round_trip(name, expect):
     assert all(torch.equal(a[k], b[k]) for k in a)
 
 
-@pytest.mark.parametrize("name", ["tiny-nemotron-h", "tiny-qwen3.5-moe", "tiny-glm-moe-dsa"])
+@pytest.mark.parametrize("name", ["tiny-nemotron-h", "tiny-qwen3.5-moe", "tiny-glm-moe-dsa", "tiny-deepseek-v4"])
 def test_rl_trainer_steps_on_new_families(name, tmp_path):
     """Two RL optimizer steps on synthetic batches through the public trainer; the loss is finite
     and the weights move."""
@@ -188,3 +188,108 @@ def test_new_families_bf16_on_gpu_match_fp32_cpu(name):
     lp, _ = gpu.logprobs_entropy(h, ids.cuda())
     lp.sum().backward()
     assert all(torch.isfinite(p.grad).all() for p in gpu.parameters() if p.grad is not None)
+
+
+# ---------------------------------------------------------------------- DeepSeek-V4
+def test_slot_attention_with_sinks_matches_dense_softmax():
+    torch.manual_seed(7)
+    T, H, D, N, slots = 9, 3, 8, 20, 6
+    q = torch.randn(T, H, D, requires_grad=True)
+    kv = torch.randn(N, D, requires_grad=True)
+    idx = torch.randint(-1, N, (T, slots))
+    idx[2] = -1                                                    # nothing to read: only the sink
+    sinks = torch.randn(H)
+    got = sparse_mla.slot_attention(q, kv, idx, 0.4, sinks, rows_budget=4 * slots)
+    for t in range(T):
+        sel = [int(i) for i in idx[t] if int(i) >= 0]
+        for h in range(H):
+            logits = torch.cat([(kv[sel] @ q[t, h]) * 0.4, sinks[h:h + 1]]) if sel else sinks[h:h + 1]
+            p = torch.softmax(logits, 0)
+            want = (p[:-1, None] * kv[sel]).sum(0) if sel else torch.zeros(D)
+            assert torch.allclose(got[t, h], want, atol=1e-5), (t, h)
+    got.sum().backward()
+    assert torch.isfinite(q.grad).all() and torch.isfinite(kv.grad).all()
+
+
+def test_dsv4_compressor_matches_entry_by_entry_pooling():
+    from prime_rl_b200.models import deepseek_v4 as v4
+
+    torch.manual_seed(8)
+    arch = resolve_arch("tiny-deepseek-v4")
+    lengths = [9, 5, 3]
+    cu = torch.tensor([0, 9, 14, 17], dtype=torch.int32)
+    x = torch.randn(17, arch.hidden_size)
+    for series, rate in ((1, 4), (2, 2)):
+        comp = v4.Compressor(arch, 16, rate, series, dtype=torch.float32)
+        for p in (comp.kv_proj.weight, comp.gate_proj.weight, comp.position_bias):
+            torch.nn.init.normal_(p, std=0.5)
+        layout = v4.CompressionLayout(cu, rate)
+        assert layout.n == sum(n // rate for n in lengths)
+        got = comp.compress(x, layout)
+        kv, gate = comp.kv_proj(x), comp.gate_proj(x)
+        e, t0 = 0, 0
+        for n in lengths:
+            for le in range(n // rate):
+                toks = list(range(t0 + le * rate, t0 + (le + 1) * rate))
+                vals = [kv[t, -16:] for t in toks]
+                logit = [gate[t, -16:] + comp.position_bias[s, -16:] for s, t in enumerate(toks)]
+                if series == 2 and le > 0:                       # first series comes from the previous entry's tokens
+                    prev = [t - rate for t in toks]
+                    vals = [kv[t, :16] for t in prev] + vals
+                    logit = [gate[t, :16] + comp.position_bias[s, :16] for s, t in enumerate(prev)] + logit
+                w = torch.softmax(torch.stack(logit), 0)
+                pooled = comp.kv_norm((w * torch.stack(vals)).sum(0))
+                want = v4.rope_interleaved(pooled.view(1, 1, -1), torch.tensor([le * rate]), comp.inv_freq)[0, 0]
+                assert torch.allclose(got[e], want, atol=1e-5), (series, e)
+                e += 1
+            t0 += n
+
+
+def test_dsv4_hyper_connection_mixing_is_nearly_doubly_stochastic():
+    from prime_rl_b200.models import deepseek_v4 as v4
+
+    torch.manual_seed(9)
+    arch = resolve_arch("tiny-deepseek-v4", {"hc_mult": 4, "hc_sinkhorn_iters": 20})
+    hc = v4.HyperConnection(arch)
+    torch.nn.init.normal_(hc.fn, std=0.3)
+    streams = torch.randn(11, 4, arch.hidden_size)
+    post, comb, collapsed = hc(streams)
+    assert comb.shape == (11, 4, 4) and collapsed.shape == (11, arch.hidden_size)
+    # the last Sinkhorn step normalises columns exactly; rows are close after 20 rounds
+    assert float((comb.sum(-2) - 1).abs().max()) < 1e-4 and float((comb.sum(-1) - 1).abs().max()) < 0.1
+    assert float(post.min()) >= 0 and float(post.max()) <= 2
+    merged = v4.HyperConnection.merge(streams, torch.ones(11, arch.hidden_size), post, comb)
+    want = post.unsqueeze(-1) + torch.einsum("tij,tih->tjh", comb, streams)
+    assert torch.allclose(merged, want, atol=1e-5)
+
+
+def test_dsv4_model_end_to_end():
+    torch.manual_seed(10)
+    arch = resolve_arch("tiny-deepseek-v4", {"index_topk": 64})                 # no ties in the entry selection
+    model = build_model(arch, device="cpu", dtype=torch.float32, seed=5)
+    with torch.no_grad():                                                       # a frozen token -> experts table
+        for layer in model.model.layers:
+            if getattr(layer.mlp, "is_hash", False):
+                first = torch.arange(arch.vocab_size) % arch.num_experts
+                layer.mlp.router.tid2eid.copy_(torch.stack([first, (first + 1) % arch.num_experts], 1))
+    ids = torch.randint(0, arch.vocab_size, (37,))
+    packed = model(ids, SeqInfo.from_lengths([14, 23], "cpu"))
+    alone = model(ids[14:], SeqInfo.from_lengths([23], "cpu"))
+    assert torch.allclose(packed[14:], alone, atol=2e-4, rtol=1e-3)
+    hash_layer = model.model.layers[0].mlp
+    assert torch.equal(hash_layer.last_topk[:, 0].long(), ids[14:] % arch.num_experts)      # the last forward
+    lp, _ = model.logprobs_entropy(packed, ids)
+    lp.sum().backward()
+    missing = [n for n, p in model.named_parameters() if p.requires_grad and p.grad is None]
+    assert not missing, missing
+    from prime_rl_b200.models import convert
+
+    hf = convert.model_state(model, "hf")
+    for key in ("embed.weight", "head.weight", "hc_head_fn", "layers.0.ffn.gate.tid2eid", "layers.1.hc_attn_fn",
+                "layers.2.attn.indexer.compressor.ape", "layers.1.attn.compressor.wgate.weight",
+                "layers.3.ffn.experts.2.w3.weight", "layers.0.attn.attn_sink", "layers.2.ffn.gate.bias"):
+        assert key in hf, key
+    other = build_model(arch, device="cpu", dtype=torch.float32, seed=6)
+    convert.load_model_state(other, {k: v.clone() for k, v in hf.items()}, "hf")
+    assert all(torch.equal(a, b) for a, b in zip(model.state_dict().values(), other.state_dict().values()))
+    assert ModelArch.from_hf_config(arch.to_hf_config()) == arch

@@ -593,3 +593,34 @@ def test_paged_decode(Hq, Hkv, splits):
     out = paged.paged_decode_raw(q, kpool, vpool, bt.to(DEV), ctx.to(DEV), splits=splits)
     ref = paged.paged_decode_ref(q, kpool, vpool, bt.to(DEV), ctx)
     _close(out, ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("H,topk", [(128, 128), (64, 192), (16, 64)])
+def test_sparse_mla_forward_kernel_and_recomputed_backward(H, topk):
+    from prime_rl_b200.ops import sparse_mla
+
+    torch.manual_seed(11)
+    dev = torch.device("cuda")
+    T, S = 150, 700
+    q = (torch.randn(T, H, 576, device=dev) * 0.5).bfloat16().requires_grad_()
+    kv = (torch.randn(S, 576, device=dev) * 0.5).bfloat16().requires_grad_()
+    idx = torch.stack([torch.randperm(S, device=dev)[:topk] for _ in range(T)]).to(torch.int32)
+    idx[:, topk // 2:][torch.rand(T, topk - topk // 2, device=dev) < 0.4] = S      # empty slots
+    idx[3] = S                                                                      # a query without any slot
+    idx[7, : topk - 1] = S                                                          # exactly one slot, in the last block
+    scale = 576 ** -0.5
+    out = sparse_mla.sparse_mla_attention(q, kv, idx, scale, 512)
+    torch.cuda.synchronize()
+    rt.check_status()
+    qf, kvf = q.detach().float().requires_grad_(), kv.detach().float().requires_grad_()
+    ref = sparse_mla.sparse_mla_attention_ref(qf, kvf, idx, scale, 512)
+    assert out.shape == (T, H, 512) and float(out[3].abs().max()) == 0.0
+    err = float((out.float() - ref).abs().max())
+    assert err < 2e-2, err
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    ref.backward(dout.float())
+    for a, b in ((q.grad, qf.grad), (kv.grad, kvf.grad)):
+        rel = float((a.float() - b).norm() / b.norm())
+        assert rel < 3e-2, rel
