@@ -39,7 +39,7 @@ constexpr int kMlaBN = 64;          // selected rows per block
 constexpr int kMlaKB = kMlaD / 64;  // 9 k-blocks of 64 channels
 constexpr int kMlaQBytes = 128 * kMlaD * 2;        // 147456
 constexpr int kMlaKvBytes = kMlaBN * kMlaD * 2;    // 73728
-constexpr int kMlaSmem = kMlaQBytes + kMlaKvBytes + 1024 /*align*/ + 256 /*barriers, mask*/;
+constexpr int kMlaSmem = kMlaQBytes + kMlaKvBytes + 1024 /*align*/ + 512 /*barriers, mask, indices*/;
 constexpr int kMlaThreads = 288;    // warp 0 MMA + Q load, warps 1-4 softmax, warps 5-8 gather
 constexpr uint32_t kMlaColS = 0, kMlaColP = 64, kMlaColO = 128;
 
@@ -84,12 +84,15 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaParams p
   uint64_t* o_done = bars + 5;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
   uint32_t* valid_mask = tmem_slot + 1;   // two words: bit r = row r of the current block is a real slot
+  int* blk_idx = reinterpret_cast<int*>(smem + kMlaQBytes + kMlaKvBytes + 256);   // the block's 64 row indices
+  int* fail_flag = blk_idx + kMlaBN;      // set when a gather thread's wait ran out
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int half = blockIdx.x, t = blockIdx.y;
   const int nblocks = p.topk / kMlaBN;
 
   if (threadIdx.x == 0) {
+    *fail_flag = 0;
     mbar_init(q_full, 1);
     mbar_init(kv_full, 128);
     mbar_init(kv_empty, 1);
@@ -235,25 +238,27 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaParams p
     const uint32_t kv_addr = smem_u32(kv_s);
     const int* my_idx = p.idx + static_cast<long long>(t) * p.topk;
     bool ok = true;
+    int next_id = (g < kMlaBN) ? my_idx[g] : 0;    // threads 0..63 carry one row index of the coming block
     for (int j = 0; j < nblocks; ++j) {
-      if (j > 0) {
-        ok = mbar_wait(kv_empty, (j - 1) & 1, p.status, kTimeoutEmptyBarrier);
-        if (!ok) break;
+      if (j > 0 && !mbar_wait(kv_empty, (j - 1) & 1, p.status, kTimeoutEmptyBarrier)) atomicExch(fail_flag, 1);
+      if (g < kMlaBN) {
+        const bool live = next_id >= 0 && next_id < p.S;
+        blk_idx[g] = live ? next_id : -1;
+        const uint32_t bits = __ballot_sync(0xffffffffu, live);
+        if ((g & 31) == 0) valid_mask[g >> 5] = bits;
+        if (j + 1 < nblocks) next_id = my_idx[(j + 1) * kMlaBN + g];     // in flight while this block is copied
       }
-      if (g < 2) {
-        uint32_t bits = 0;
-        for (int r = 0; r < 32; ++r) {
-          const int id = my_idx[j * kMlaBN + g * 32 + r];
-          bits |= (id >= 0 && id < p.S) ? (1u << r) : 0u;
-        }
-        valid_mask[g] = bits;
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (*reinterpret_cast<volatile int*>(fail_flag) != 0) {   // the same verdict for all 128 threads
+        ok = false;
+        break;
       }
 #pragma unroll 4
       for (int pass = 0; pass < kMlaBN * kMlaKB / 16; ++pass) {   // 36 passes x 16 segments = 64 rows x 9 k-blocks
         const int seg = pass * 16 + seg0;
         const int r = seg / kMlaKB, c = seg - r * kMlaKB;
-        const int id = my_idx[j * kMlaBN + r];
-        const bool live = id >= 0 && id < p.S;
+        const int id = blk_idx[r];
+        const bool live = id >= 0;
         const __nv_bfloat16* src = p.kv + static_cast<long long>(live ? id : 0) * kMlaD + c * 64 + unit * 8;
         const uint32_t dst = kv_addr + c * 8192 + r * 128 + ((unit ^ (r & 7)) << 4);
         cp_async_16(dst, src, live ? 16u : 0u);

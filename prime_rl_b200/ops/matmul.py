@@ -83,6 +83,11 @@ def gemm(
         kb = b.shape[0] if b_mn else b.shape[1]
         ldb = b.stride(0)
     assert kb == K, f"reduction mismatch {kb} vs {K}"
+    if not grouped and ext is None and (a.stride(0) % 8 or ldb % 8 or a.data_ptr() % 16 or b.data_ptr() % 16):
+        # TMA needs 16-byte aligned bases and row pitches; odd little operands (a 4-expert router, a
+        # per-head gate) are not worth a copy into padded buffers
+        return gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=out_dtype or (out.dtype if out is not None else None),
+                        alpha=alpha, beta=beta, out=out)
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=a.device)
         assert beta == 0.0

@@ -173,10 +173,10 @@ def test_rl_trainer_steps_on_new_families(name, tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("name", ["tiny-nemotron-h", "tiny-qwen3.5-moe", "tiny-glm-moe-dsa"])
+@pytest.mark.parametrize("name", ["tiny-nemotron-h", "tiny-qwen3.5-moe", "tiny-glm-moe-dsa", "tiny-deepseek-v4"])
 def test_new_families_bf16_on_gpu_match_fp32_cpu(name):
     torch.manual_seed(6)
-    arch = resolve_arch(name, {"index_topk": 64} if "dsa" in name else None)
+    arch = resolve_arch(name, {"index_topk": 64} if ("dsa" in name or "deepseek" in name) else None)
     ref = build_model(arch, device="cpu", dtype=torch.float32, seed=3)
     gpu = build_model(arch, device="cuda", dtype=torch.bfloat16, seed=3)
     gpu.load_state_dict({k: v.to("cuda") for k, v in ref.state_dict().items()}, strict=False)
