@@ -1,7 +1,11 @@
-"""Run dashboard: a small FastAPI app that lists registered run directories and serves their
-``metrics.jsonl`` rows (trainer, orchestrator, evals) as JSON plus a single-page plot
-(reference: the ``dashboard`` console script, src/prime_rl/entrypoints/dashboard.py; plain web
-UI, no graphics API involved).
+"""Run dashboard: a read-only FastAPI app over registered run directories. Per run it serves
+the ``metrics.jsonl`` rows (trainer, orchestrator, evals) with a plot, the resolved configs, the
+tail of every log file, and a trace browser: the episodes the orchestrator shipped (reward,
+advantage, turns) with a token view that colours every sampled token by the engine's
+log-probability, the trainer's log-probability, their difference, or the trainer's entropy
+(joined from the trainer's annotation stream by trace id)
+(reference: src/prime_rl/dashboard/server.py and the ``dashboard`` console script; plain web UI,
+no graphics API involved).
 
 Registry: ``~/.cache/prime-rl-b200/dashboard/dirs.json`` (launchers add their output
 directory; the list is re-read on every request, so new runs appear without a restart).
@@ -64,6 +68,92 @@ def read_metrics(run_dir: Path, limit: int = 20000) -> list[dict]:
     return rows[-limit:]
 
 
+def _monitor_dir(run_dir: Path) -> Path:
+    from ..utils.pathing import get_monitor_dir
+
+    return get_monitor_dir(Path(run_dir))
+
+
+def read_trace_index(run_dir: Path) -> list[dict]:
+    """One summary row per episode (no token arrays), newest last."""
+    out = []
+    mdir = _monitor_dir(run_dir)
+    for f in sorted(mdir.glob("traces_*_*.jsonl")):
+        try:
+            with open(f) as fh:
+                for line_no, line in enumerate(fh):
+                    try:
+                        t = json.loads(line)
+                    except ValueError:
+                        continue
+                    out.append({"trace_id": t.get("trace_id"), "step": t.get("step"), "env": t.get("env"),
+                                "reward": t.get("reward"), "advantage": t.get("advantage"),
+                                "turns": len(t.get("turns", [])), "error": t.get("error"),
+                                "tokens": sum(len(u.get("completion_ids", [])) for u in t.get("turns", [])),
+                                "file": f.name, "line": line_no})
+        except OSError:
+            continue
+    return out
+
+
+def read_trace(run_dir: Path, trace_id: str) -> dict | None:
+    """The full episode plus the trainer's annotations for it (``annotations``: one record per
+    branch with per-token ``logprobs`` / ``entropy`` / ``loss_mask``)."""
+    mdir = _monitor_dir(run_dir)
+    found = None
+    for f in sorted(mdir.glob("traces_*_*.jsonl")):
+        with open(f) as fh:
+            for line in fh:
+                if trace_id in line:
+                    try:
+                        t = json.loads(line)
+                    except ValueError:
+                        continue
+                    if t.get("trace_id") == trace_id:
+                        found = t
+                        break
+        if found:
+            break
+    if found is None:
+        return None
+    ann = []
+    for f in sorted(mdir.glob("annotations_*.jsonl")):
+        with open(f) as fh:
+            for line in fh:
+                if trace_id in line:
+                    try:
+                        a = json.loads(line)
+                    except ValueError:
+                        continue
+                    if a.get("trace_id") == trace_id:
+                        ann.append(a)
+    found["annotations"] = ann
+    return found
+
+
+def read_configs(run_dir: Path) -> dict[str, str]:
+    out = {}
+    for f in sorted(Path(run_dir).rglob("*.toml"))[:32]:
+        try:
+            out[str(f.relative_to(run_dir))] = f.read_text()[:200_000]
+        except OSError:
+            pass
+    return out
+
+
+def read_log_tails(run_dir: Path, lines: int = 200) -> dict[str, str]:
+    out = {}
+    for f in sorted(Path(run_dir).rglob("*.log"))[:64]:
+        try:
+            with open(f, "rb") as fh:
+                fh.seek(0, 2)
+                fh.seek(max(0, fh.tell() - 64 * 1024))
+                out[str(f.relative_to(run_dir))] = "\n".join(fh.read().decode(errors="replace").splitlines()[-lines:])
+        except OSError:
+            pass
+    return out
+
+
 _PAGE = """<!doctype html><html><head><meta charset="utf-8"><title>prime-rl-b200 runs</title>
 <style>body{font-family:sans-serif;margin:1.5em}canvas{border:1px solid #ccc;margin:.4em}select{margin:.3em}</style></head>
 <body><h2>Runs</h2><select id="run"></select><select id="key"></select><br><canvas id="c" width="900" height="360"></canvas>
@@ -80,6 +170,34 @@ function draw(){const k=document.getElementById('key').value;const pts=rows.filt
  g.beginPath();pts.forEach((p,i)=>{const x=20+(c.width-40)*(p.step-x0)/((x1-x0)||1),y=c.height-20-(c.height-40)*(p[k]-y0)/((y1-y0)||1);
  i?g.lineTo(x,y):g.moveTo(x,y);});g.stroke();g.fillText(`${k}: ${y0.toPrecision(4)} .. ${y1.toPrecision(4)}  steps ${x0}..${x1}`,24,14);}
 runs();setInterval(load,10000);
+</script>
+<h2>Traces</h2><button onclick="traces()">refresh</button>
+<select id="overlay"><option value="engine">engine logprob</option><option value="trainer">trainer logprob</option>
+<option value="diff">trainer - engine</option><option value="entropy">trainer entropy</option></select>
+<div style="display:flex;gap:1em"><div id="tl" style="max-height:420px;overflow:auto;min-width:420px;font:12px monospace"></div>
+<div id="tv" style="flex:1;font:12px monospace;line-height:1.9"></div></div>
+<h2>Configs and logs</h2><button onclick="files()">load</button><pre id="files" style="max-height:400px;overflow:auto;background:#f6f6f6"></pre>
+<script>
+let cur=null;
+async function traces(){const i=document.getElementById('run').value;const r=await (await fetch(`api/runs/${i}/traces`)).json();
+ document.getElementById('tl').innerHTML=r.slice(-500).reverse().map(t=>`<div style="cursor:pointer" onclick="show('${t.trace_id}')">`+
+ `step ${t.step} ${t.env} r=${(t.reward??0).toFixed(3)} a=${t.advantage==null?'-':t.advantage.toFixed(3)} ${t.tokens} tok${t.error?' ERR':''}</div>`).join('');}
+function colour(v,lo,hi){if(v==null)return'#eee';const x=Math.max(0,Math.min(1,(v-lo)/(hi-lo)));return `hsl(${120*x},70%,80%)`;}
+async function show(id){const i=document.getElementById('run').value;cur=await (await fetch(`api/runs/${i}/traces/${id}`)).json();render();}
+document.getElementById('overlay').onchange=render;
+function render(){if(!cur)return;const mode=document.getElementById('overlay').value;const ann=(cur.annotations||[])[0];
+ let html=`<b>${cur.env}</b> reward ${cur.reward} advantage ${cur.advantage} policy v${cur.policy_version}<br>`;
+ cur.turns.forEach((t,ti)=>{const off=t.prompt_ids.length;html+=`<div><i>turn ${ti}: ${off} prompt tokens, finish ${t.finish_reason}</i><br>`;
+  t.completion_ids.forEach((id,k)=>{const e=t.completion_logprobs[k];const tr=ann&&ti===cur.turns.length-1?ann.logprobs[off+k]:null;
+   const en=ann&&ti===cur.turns.length-1?ann.entropy[off+k]:null;
+   const v=mode==='engine'?e:mode==='trainer'?tr:mode==='diff'?(tr==null?null:tr-e):en;
+   const c=mode==='diff'?colour(v==null?null:-Math.abs(v),-1,0):mode==='entropy'?colour(v==null?null:-v,-3,0):colour(v,-5,0);
+   html+=`<span title="id ${id} engine ${e} trainer ${tr} entropy ${en}" style="background:${c};padding:1px 3px;margin:1px">${id}</span>`;});
+  html+='</div>';});document.getElementById('tv').innerHTML=html;}
+async function files(){const i=document.getElementById('run').value;const c=await (await fetch(`api/runs/${i}/configs`)).json();
+ const l=await (await fetch(`api/runs/${i}/logs`)).json();
+ document.getElementById('files').textContent=Object.entries(c).map(([k,v])=>`### ${k}\n${v}`).join('\n\n')+'\n\n'+
+  Object.entries(l).map(([k,v])=>`### ${k}\n${v}`).join('\n\n');}
 </script></body></html>"""
 
 
@@ -111,6 +229,40 @@ def build_app(extra_dirs: list[str] | None = None):
         if not 0 <= i < len(d):
             raise HTTPException(404, "unknown run")
         return read_metrics(Path(d[i]))
+
+    def run_dir(i: int) -> Path:
+        d = dirs()
+        if not 0 <= i < len(d):
+            raise HTTPException(404, "unknown run")
+        return Path(d[i])
+
+    @app.get("/api/runs/{i}/traces")
+    def traces(i: int):
+        return read_trace_index(run_dir(i))
+
+    @app.get("/api/runs/{i}/traces/{trace_id}")
+    def trace(i: int, trace_id: str):
+        t = read_trace(run_dir(i), trace_id)
+        if t is None:
+            raise HTTPException(404, "unknown trace")
+        return t
+
+    @app.get("/api/runs/{i}/configs")
+    def configs(i: int):
+        return read_configs(run_dir(i))
+
+    @app.get("/api/runs/{i}/logs")
+    def logs(i: int):
+        return read_log_tails(run_dir(i))
+
+    @app.post("/api/view")
+    def add_view(body: dict):
+        """Registers a run directory with the running dashboard (what launchers call)."""
+        path = Path(str(body.get("path", "")))
+        if not path.is_dir():
+            raise HTTPException(400, "path is not a directory")
+        register_output_dir(path)
+        return {"runs": dirs()}
 
     @app.get("/health")
     def health():

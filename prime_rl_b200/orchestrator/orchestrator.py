@@ -345,6 +345,8 @@ class Orchestrator:
                                        pad_to_multiple_of=c.pad_to_multiple_of)
         await asyncio.to_thread(self.sender.send, self.step, grid)
         rollouts = [r for r, _ in batch]
+        for r in rollouts:                       # one trace record per episode, joined to the trainer's
+            self.monitor.log_trace(trace_record(r, self.step))     # annotations by (trace_id, branch_index)
         lag = [self.policy.version - r.policy_version for r in rollouts]
         m = {
             "reward": sum(r.reward for r in rollouts) / len(rollouts),
@@ -422,6 +424,17 @@ class Orchestrator:
             await self.client.close()
             await self.admin.close()
             self.monitor.finalize()
+
+
+def trace_record(r, step: int) -> dict:
+    """What the file monitor keeps of one episode: identity, outcome, and per turn the sampled
+    tokens with the engine's log-probabilities (the dashboard's token view reads these)."""
+    return {"trace_id": r.trace_id, "step": step, "env": r.env_name, "task_id": r.task_id, "group_id": r.group_id,
+            "agent": r.agent, "reward": r.reward, "advantage": r.advantage, "policy_version": r.policy_version,
+            "error": r.error, "metrics": r.metrics,
+            "turns": [{"prompt_ids": list(t.prompt_ids), "completion_ids": list(t.completion_ids),
+                       "completion_logprobs": [round(float(x), 6) for x in t.completion_logprobs],
+                       "temperature": t.temperature, "finish_reason": t.finish_reason} for t in r.turns]}
 
 
 async def run_orchestrator(config: OrchestratorConfig, **kw) -> Orchestrator:

@@ -158,3 +158,39 @@ def test_benchmark_runner_config_and_result_table(tmp_path):
     assert agg.main([str(tmp_path / "a.json"), str(tmp_path / "b.json"), "--output", str(tmp_path / "t.md")]) == 0
     text = (tmp_path / "t.md").read_text()
     assert "9266.00" in text and text.count("\n") == 3
+
+
+def test_dashboard_trace_browser_joins_traces_and_annotations(tmp_path, monkeypatch):
+    from fastapi.testclient import TestClient
+
+    from prime_rl_b200.dashboard import server as dash
+    from prime_rl_b200.monitors import FileMonitor
+    from prime_rl_b200.orchestrator.orchestrator import trace_record
+    from prime_rl_b200.orchestrator.types import Rollout, Turn
+
+    monkeypatch.setattr(dash, "STATE_DIR", tmp_path / "state")
+    monkeypatch.setattr(dash, "DIRS_FILE", tmp_path / "state" / "dirs.json")
+    run = tmp_path / "run"
+    run.mkdir()
+    (run / "rl.toml").write_text("max_steps = 3\n")
+    (run / "trainer.log").write_text("line one\nline two\n")
+    orch, trainer = FileMonitor(run, "orchestrator"), FileMonitor(run, "trainer")
+    r = Rollout("reverse-text", 3, "g", [Turn([1, 2, 3], [7, 8], [-0.5, -1.25], finish_reason="stop")], reward=0.75,
+                advantage=0.25)
+    orch.log_trace(trace_record(r, step=4))
+    orch.finalize()
+    trainer.log_annotations([{"trace_id": r.trace_id, "branch_index": 0, "step": 4,
+                              "logprobs": [0, 0, 0, -0.4, -1.5], "entropy": [0, 0, 0, 0.9, 1.1],
+                              "loss_mask": [False] * 3 + [True] * 2}], "trainer")
+    client = TestClient(dash.build_app([str(run)]))
+    rows = client.get("/api/runs/0/traces").json()
+    assert len(rows) == 1 and rows[0]["trace_id"] == r.trace_id and rows[0]["tokens"] == 2 and rows[0]["step"] == 4
+    full = client.get(f"/api/runs/0/traces/{r.trace_id}").json()
+    assert full["turns"][0]["completion_ids"] == [7, 8] and full["annotations"][0]["logprobs"][3] == -0.4
+    assert client.get("/api/runs/0/traces/nope").status_code == 404
+    assert "rl.toml" in client.get("/api/runs/0/configs").json()
+    assert "line two" in client.get("/api/runs/0/logs").json()["trainer.log"]
+    other = tmp_path / "run2"
+    other.mkdir()
+    assert str(other.resolve()) in client.post("/api/view", json={"path": str(other)}).json()["runs"]
+    assert "Traces" in client.get("/").text
