@@ -31,7 +31,7 @@ import torch.nn.functional as F
 from ..ops import moe as moe_ops
 from ..ops import sparse_mla
 from .config import ModelArch
-from .layers import DenseMLP, GroupedExperts, Linear, MoE, RMSNorm, SeqInfo
+from .layers import DenseMLP, Linear, MoE, RMSNorm, SeqInfo
 
 IGNORE_SLOT = -1
 
@@ -305,8 +305,8 @@ class DSV4Router(nn.Module):
             idx = (scores + self.e_score_correction_bias).topk(a.num_experts_per_tok, dim=1).indices
         w = scores.gather(1, idx)
         w = w / (w.sum(-1, keepdim=True) + 1e-20) * a.routed_scaling_factor
-        counts = torch.bincount(idx.reshape(-1), minlength=a.num_experts)
-        return idx.to(torch.int32), w, counts, scores
+        counts = torch.bincount(idx.reshape(-1), minlength=a.num_experts).to(torch.int32)   # the plan kernel reads int32
+        return idx.to(torch.int32).contiguous(), w, counts, scores
 
 
 class DSV4MoE(MoE):

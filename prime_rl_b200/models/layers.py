@@ -37,6 +37,9 @@ class SeqInfo:
     attn_cache: dict | None = None
     # values one layer leaves for later layers of the same forward (sparse-attention indices)
     shared: dict | None = None
+    # rotary angles [T, rotary_dim / 2] when positions have several axes (multimodal MRoPE); attention
+    # layers that support it use these instead of position_ids * inv_freq
+    mrope_angles: torch.Tensor | None = None
 
     @classmethod
     def from_lengths(cls, lengths: list[int], device) -> "SeqInfo":

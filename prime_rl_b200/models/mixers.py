@@ -123,6 +123,18 @@ class GatedDeltaNet(nn.Module):
         return self.out_proj(o.reshape(T, self.value_dim))
 
 
+def norm_rope_with_angles(x: torch.Tensor, w: torch.Tensor | None, ang: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMSNorm over the head dim, then the half-split rotation of the first ``2 * ang.shape[1]``
+    channels by the given angles ``[T, rd / 2]`` (positions with several axes)."""
+    xf = x.float()
+    if w is not None:
+        xf = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(x.dtype).float()
+    rd = ang.shape[1] * 2
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    x1, x2, rest = xf[..., : rd // 2], xf[..., rd // 2: rd], xf[..., rd:]
+    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin, rest], dim=-1).to(x.dtype)
+
+
 class GatedAttention(nn.Module):
     """Softmax attention whose query projection also emits a sigmoid output gate (per head:
     ``[q | gate]``), with q/k RMSNorm and partial rotary embedding."""
@@ -147,8 +159,12 @@ class GatedAttention(nn.Module):
         q, gate = qg[..., : self.D], qg[..., self.D:]
         k = self.k_proj(x).view(T, self.nkv, self.D)
         v = self.v_proj(x).view(T, self.nkv, self.D)
-        q = ops.qknorm_rope(q, self.q_norm.weight, seq.position_ids, self.inv_freq, self.arch.rms_norm_eps)
-        k = ops.qknorm_rope(k, self.k_norm.weight, seq.position_ids, self.inv_freq, self.arch.rms_norm_eps)
+        if seq.mrope_angles is not None:
+            q = norm_rope_with_angles(q, self.q_norm.weight, seq.mrope_angles, self.arch.rms_norm_eps)
+            k = norm_rope_with_angles(k, self.k_norm.weight, seq.mrope_angles, self.arch.rms_norm_eps)
+        else:
+            q = ops.qknorm_rope(q, self.q_norm.weight, seq.position_ids, self.inv_freq, self.arch.rms_norm_eps)
+            k = ops.qknorm_rope(k, self.k_norm.weight, seq.position_ids, self.inv_freq, self.arch.rms_norm_eps)
         o = attn_ops.attention(q, k, v, seq.cu_seqlens, seq.max_seqlen, causal=True, backend=self.backend,
                                cache=seq.attn_cache, cache_key=self.layer_idx)
         o = o * torch.sigmoid(gate.float()).to(o.dtype)

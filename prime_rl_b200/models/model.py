@@ -84,10 +84,11 @@ class CausalLM(nn.Module):
             return self.layer_hooks.run(layer, idx, h, seq)
         return layer(h, seq)
 
-    def forward(self, input_ids: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
-        """input_ids: [T] (or [1, T]) packed ids -> final hidden states [T, H] (normed)."""
+    def forward(self, input_ids: torch.Tensor, seq: SeqInfo, inputs_embeds: torch.Tensor | None = None) -> torch.Tensor:
+        """input_ids: [T] (or [1, T]) packed ids -> final hidden states [T, H] (normed).
+        ``inputs_embeds [T, H]`` replaces the embedding lookup (multimodal: image features merged in)."""
         ids = input_ids.reshape(-1)
-        h = self.model.embed_tokens(ids)
+        h = self.model.embed_tokens(ids) if inputs_embeds is None else inputs_embeds
         if self.arch.hc_mult:
             h = h.unsqueeze(1).expand(-1, self.arch.hc_mult, -1).contiguous()
             seq.shared = dict(seq.shared or {}, input_ids=ids)      # hash-routed layers look tokens up by id

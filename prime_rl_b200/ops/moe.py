@@ -76,6 +76,8 @@ def build_plan(topk_idx: torch.Tensor, counts: torch.Tensor, num_experts: int, d
     P = max_padded_rows(T * k, E)
     dev = topk_idx.device
     if topk_idx.is_cuda:
+        if topk_idx.dtype != torch.int32 or counts.dtype != torch.int32 or not topk_idx.is_contiguous():
+            raise TypeError("build_plan on a GPU takes contiguous int32 expert ids and int32 counts")
         expert_offset = torch.empty(E + 1, dtype=torch.int32, device=dev)
         block_expert = torch.empty(P // 128, dtype=torch.int32, device=dev)
         cursor = torch.empty(E, dtype=torch.int32, device=dev)

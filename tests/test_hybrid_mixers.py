@@ -183,6 +183,9 @@ def test_new_families_bf16_on_gpu_match_fp32_cpu(name):
     ids = torch.randint(0, arch.vocab_size, (48,))
     h_ref = ref(ids, SeqInfo.from_lengths([20, 28], "cpu"))
     h = gpu(ids.cuda(), SeqInfo.from_lengths([20, 28], "cuda"))
+    assert torch.isfinite(h_ref).all(), "the fp32 CPU model produced non-finite values"
+    bad = (~torch.isfinite(h.float()).all(-1)).nonzero().flatten().tolist()
+    assert not bad, f"non-finite rows on the GPU: {bad[:8]} of {h.shape[0]}"
     rel = float((h.float().cpu() - h_ref).norm() / h_ref.norm())
     assert rel < 0.08, rel
     lp, _ = gpu.logprobs_entropy(h, ids.cuda())
@@ -293,3 +296,58 @@ def test_dsv4_model_end_to_end():
     convert.load_model_state(other, {k: v.clone() for k, v in hf.items()}, "hf")
     assert all(torch.equal(a, b) for a, b in zip(model.state_dict().values(), other.state_dict().values()))
     assert ModelArch.from_hf_config(arch.to_hf_config()) == arch
+
+
+# ---------------------------------------------------------------------- multimodal (Qwen3.5 vision tower, MRoPE)
+def test_mrope_positions_and_axis_interleaving():
+    from prime_rl_b200.models import vision
+
+    # doc 0: 2 text, one 1x4x6 image merged 2x2 -> 2x3 = 6 tokens, 2 text; doc 1: 3 text
+    types = torch.tensor([0, 0, 1, 1, 1, 1, 1, 1, 0, 0, 0, 0, 0])
+    pos = vision.mrope_position_ids(types, [10, 3], [[1, 4, 6]], merge=2)
+    assert pos[:, :2].tolist() == [[0, 1]] * 3
+    assert pos[0, 2:8].tolist() == [2] * 6
+    assert pos[1, 2:8].tolist() == [2, 2, 2, 3, 3, 3] and pos[2, 2:8].tolist() == [2, 3, 4, 2, 3, 4]
+    assert pos[:, 8:10].tolist() == [[5, 6]] * 3                       # continues after max(rows, cols) = 3
+    assert pos[:, 10:].tolist() == [[0, 1, 2]] * 3                     # positions restart with the next document
+    axis = vision.mrope_axis_of_frequency(16, (6, 5, 5))
+    assert axis.tolist() == [0, 1, 2, 0, 1, 2, 0, 1, 2, 0, 1, 2, 0, 1, 2, 0]
+    text_only = vision.mrope_position_ids(torch.zeros(5, dtype=torch.long), [5], None, 2)
+    ang = vision.mrope_angles(text_only, torch.tensor([1.0, 0.5, 0.25, 0.125]), (2, 1, 1))
+    assert torch.allclose(ang, torch.arange(5.0)[:, None] * torch.tensor([1.0, 0.5, 0.25, 0.125]))
+
+
+def test_vision_tower_and_multimodal_forward():
+    from prime_rl_b200.models import vision
+
+    torch.manual_seed(12)
+    vc = vision.VisionConfig(depth=2, hidden_size=32, intermediate_size=64, num_heads=4, patch_size=4,
+                             temporal_patch_size=2, out_hidden_size=128, num_position_embeddings=64)
+    arch = resolve_arch("tiny-qwen3.5-moe")
+    lm = build_model(arch, device="cpu", dtype=torch.float32, seed=3)
+    image_token = arch.vocab_size - 1
+    mm = vision.MultimodalLM(lm, vc, image_token, mrope_section=(2, 1, 1), dtype=torch.float32)
+    grid = torch.tensor([[1, 4, 6], [1, 2, 2]])
+    n_patches = 4 * 6 + 2 * 2
+    pixels = torch.randn(n_patches, 3 * 2 * 4 * 4)
+    feats = mm.visual(pixels, grid)
+    assert feats.shape == (n_patches // 4, 128)
+    # the patch projection is the 3-D convolution applied to each patch
+    conv = mm.visual.patch_embed["proj"]
+    direct = conv(pixels.view(n_patches, 3, 2, 4, 4)).view(n_patches, -1)
+    again = torch.nn.functional.linear(pixels, conv.weight.reshape(32, -1), conv.bias)
+    assert torch.allclose(direct, again, atol=1e-5)
+    ids = torch.randint(0, arch.vocab_size - 1, (20,))
+    ids[3:9] = image_token                     # 6 merged tokens of the first image
+    ids[15:16] = image_token                   # 1 merged token of the second image (second document)
+    seq = SeqInfo.from_lengths([12, 8], "cpu")
+    h = mm(ids, seq, pixels, grid)
+    assert h.shape == (20, arch.hidden_size) and torch.isfinite(h).all()
+    lp, _ = mm.logprobs_entropy(h, ids)
+    lp.sum().backward()
+    assert mm.visual.patch_embed["proj"].weight.grad is not None and mm.visual.merger["linear_fc2"].weight.grad is not None
+    # a text-only batch through the wrapper equals the plain language model (all three axes agree)
+    tids = torch.randint(0, arch.vocab_size - 1, (14,))
+    a = mm(tids, SeqInfo.from_lengths([14], "cpu"))
+    b = lm(tids, SeqInfo.from_lengths([14], "cpu"))
+    assert torch.allclose(a, b, atol=1e-5)
