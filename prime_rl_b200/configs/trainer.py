@@ -184,6 +184,8 @@ class ModelConfig(BaseModelConfig):
     moe: MoERuntimeConfig = MoERuntimeConfig()
     cp: int = 1
     cp_style: Literal["ring", "ulysses"] = "ring"
+    # "p2p": the ring style's forward K / V exchange runs inside the attention kernel over NVLink peer memory
+    cp_kv_exchange: Literal["nccl", "p2p"] = "nccl"
     impl: Literal["hf", "custom", "auto"] = "auto"
     optimization_dtype: Literal["bfloat16", "float32"] = "float32"
     reduce_dtype: Literal["bfloat16", "float32"] = "float32"

@@ -51,7 +51,81 @@ struct FaParams {
   float scale_log2;       // softmax scale * log2(e)
   int window;             // <= 0: none; else a query attends keys with q - k < window
   int* status;
+  // context-parallel gather (flash_fwd_kernel<true> only): K and V of the whole sequence live in one
+  // buffer per rank ([K rows | V rows at v_off]) of which rank r has written the rows of its own
+  // chunk [r * chunk_rows, (r + 1) * chunk_rows). One extra warp per CTA pulls the chunks of the
+  // lower ranks from their owners (`peer[r]` = rank r's buffer) into the local buffer in 16 KB pieces
+  // that CTAs claim from a shared counter; `ready[c]` counts the finished pieces of chunk c.
+  const uint8_t* peer[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  uint8_t* kv_local = nullptr;
+  unsigned* claim = nullptr;
+  unsigned* ready = nullptr;
+  int cp_rank = 0;
+  int chunk_rows = 0;
+  long long row_bytes = 0, v_off = 0;
 };
+
+constexpr int kFaPiece = 16384;
+
+// Pieces of the chunks 0 .. cp_rank-1 (K region first, then V region of every chunk), claimed
+// dynamically: a CTA that is not resident yet owes nothing, so waiting CTAs cannot starve the copy.
+__device__ void fa_gather_warp(const FaParams& p, int lane) {
+  const long long chunk_bytes = static_cast<long long>(p.chunk_rows) * p.row_bytes;
+  const unsigned ppk = static_cast<unsigned>((chunk_bytes + kFaPiece - 1) / kFaPiece);
+  const unsigned total = static_cast<unsigned>(p.cp_rank) * 2u * ppk;
+  for (;;) {
+    unsigned id = 0;
+    if (lane == 0) id = atomicAdd(p.claim, 1u);
+    id = __shfl_sync(0xffffffffu, id, 0);
+    if (id >= total) break;
+    const unsigned chunk = id / (2u * ppk), w = id % (2u * ppk);
+    const unsigned piece = w % ppk;
+    const long long off = (w >= ppk ? p.v_off : 0) + static_cast<long long>(chunk) * chunk_bytes +
+                          static_cast<long long>(piece) * kFaPiece;
+    const long long len = min(static_cast<long long>(kFaPiece), chunk_bytes - static_cast<long long>(piece) * kFaPiece);
+    const int4* src = reinterpret_cast<const int4*>(p.peer[chunk] + off);
+    int4* dst = reinterpret_cast<int4*>(p.kv_local + off);
+    const int n16 = static_cast<int>(len >> 4);
+    for (int i = lane; i < n16; i += 32 * 8) {
+      int4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (i + u * 32 < n16) v[u] = __ldcg(src + i + u * 32);
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (i + u * 32 < n16) dst[i + u * 32] = v[u];
+    }
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) atomicAdd(p.ready + chunk, 1u);
+  }
+}
+
+// Producer side: rows [row0, row1] are about to be loaded by TMA; wait (bounded) for the chunks of
+// lower ranks they touch. `done` caches the chunks already seen complete.
+__device__ bool fa_wait_rows(const FaParams& p, int row0, int row1, unsigned& done) {
+  const long long chunk_bytes = static_cast<long long>(p.chunk_rows) * p.row_bytes;
+  const unsigned want = 2u * static_cast<unsigned>((chunk_bytes + kFaPiece - 1) / kFaPiece);
+  const int c1 = min(row1 / p.chunk_rows, p.cp_rank - 1);
+  for (int c = row0 / p.chunk_rows; c <= c1; ++c) {
+    if ((done >> c) & 1u) continue;
+    const unsigned* flag = p.ready + c;
+    bool ok = false;
+    for (long long spin = 0; spin < (1LL << 24); ++spin) {
+      unsigned v;
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+      if (v >= want) { ok = true; break; }
+      __nanosleep(64);
+    }
+    if (!ok) {
+      atomicCAS(p.status, 0, static_cast<int>(kTimeoutPeerFlag));
+      return false;
+    }
+    asm volatile("fence.proxy.async;" ::: "memory");
+    done |= 1u << c;
+  }
+  return true;
+}
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -60,7 +134,8 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(kFaThreads, 1)
+template <bool GATHER>
+__global__ void __launch_bounds__(kFaThreads + (GATHER ? 32 : 0), 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const FaParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -164,8 +239,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       int ks = 0, vs = 0;
       uint32_t kph = 0, vph = 0;
       bool ok = true;
+      unsigned chunks_done = 0;
       for (int j = j_begin; j < j_end && ok; ++j) {
         const int krow = doc_start + j * kFaBN;
+        if constexpr (GATHER) {
+          if (!fa_wait_rows(p, krow, krow + kFaBN - 1, chunks_done)) { ok = false; break; }
+        }
         if (!mbar_wait(&k_empty[ks], kph ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
         mbar_expect_tx(&k_full[ks], kKBytes);
         tma_load_2d(k_s + ks * kKBytes, &tmK, &k_full[ks], kv_head * kFaD, krow);
@@ -249,6 +328,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (ok) handle_v(j);
       }
     }
+  } else if (GATHER && warp == kFaThreads / 32) {
+    // ------------------------------------------------------------ gather warp (context parallelism)
+    fa_gather_warp(p, lane);
   } else {
     // ------------------------------------------------------------ softmax warps
     const int t = (warp - 3) >> 2;          // tile
@@ -435,12 +517,66 @@ PRB_API int prb_flash_fwd_slice(const void* q, const void* k, const void* v, voi
   p.window = window; p.status = status;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFaSmem) != cudaSuccess)
+    if (cudaFuncSetAttribute(flash_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFaSmem) != cudaSuccess)
       return -10;
     configured = true;
   }
   dim3 grid(max_pairs, heads_q);
-  flash_fwd_kernel<<<grid, kFaThreads, kFaSmem, stream>>>(tmQ, tmK, tmV, p);
+  flash_fwd_kernel<false><<<grid, kFaThreads, kFaSmem, stream>>>(tmQ, tmK, tmV, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Context-parallel forward with the K / V exchange inside the kernel. `kv_local` is this rank's
+// buffer [K: total_q rows | V: total_q rows at v_off_bytes], rows of heads_kv * 128 bf16; this rank
+// has written the rows [cp_rank * chunk_rows, (cp_rank + 1) * chunk_rows) of both halves, every peer
+// its own chunk of its own buffer (`peer_kv[r]`). `counters`: cp_size + 1 unsigned ints (piece claim
+// counter, then one arrival counter per chunk); they are zeroed here, stream-ordered. The caller
+// orders the launch after all ranks have written their chunk and keeps the chunk unchanged until
+// all ranks have finished. Queries: the local rows (global rows [cp_rank * chunk_rows, ...)).
+PRB_API int prb_flash_fwd_gather(const void* q, void* kv_local, void* const* peer_kv, long long v_off_bytes, void* out,
+                                 float* lse, const int* cu_seqlens, int num_docs, int total_q, int heads_q, int heads_kv,
+                                 long long ld_q, long long ld_out, float scale, int window, int max_pairs, int cp_rank,
+                                 int cp_size, int chunk_rows, unsigned* counters, int* status, void* stream_) {
+  using namespace prb;
+  if (cp_size < 1 || cp_size > 8 || cp_rank < 0 || cp_rank >= cp_size || chunk_rows <= 0 ||
+      static_cast<long long>(chunk_rows) * cp_size != total_q || heads_q % heads_kv)
+    return -3;
+  if ((ld_q % 8) || (ld_out % 8) || (v_off_bytes % 16) || (reinterpret_cast<uintptr_t>(kv_local) & 15)) return -4;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  const long long ldkv = static_cast<long long>(heads_kv) * kFaD;
+  const int q_off = cp_rank * chunk_rows, q_rows = chunk_rows;
+  const uint8_t* kbase = reinterpret_cast<const uint8_t*>(kv_local);
+  CUtensorMap tmQ, tmK, tmV;
+  int rc = make_tmap_2d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)q_rows, (uint64_t)heads_q * kFaD,
+                        (uint64_t)ld_q, kFaBM, 64, true);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmK, kbase, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_q, (uint64_t)ldkv, (uint64_t)ldkv,
+                    kFaBN, 64, true);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmV, kbase + v_off_bytes, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_q, (uint64_t)ldkv,
+                    (uint64_t)ldkv, kFaHN, 64, true);
+  if (rc) return rc;
+  FaParams p;
+  p.cu_seqlens = cu_seqlens; p.num_docs = num_docs; p.total_q = total_q;
+  p.q_off = q_off; p.q_rows = q_rows;
+  p.heads_q = heads_q; p.heads_kv = heads_kv;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out); p.ld_out = ld_out; p.lse = lse;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = window; p.status = status;
+  for (int r = 0; r < cp_size; ++r) p.peer[r] = reinterpret_cast<const uint8_t*>(peer_kv[r]);
+  p.kv_local = reinterpret_cast<uint8_t*>(kv_local);
+  p.claim = counters; p.ready = counters + 1;
+  p.cp_rank = cp_rank; p.chunk_rows = chunk_rows;
+  p.row_bytes = ldkv * 2; p.v_off = v_off_bytes;
+  if (cudaMemsetAsync(counters, 0, sizeof(unsigned) * (cp_size + 1), stream) != cudaSuccess) return -12;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(flash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFaSmem) != cudaSuccess)
+      return -10;
+    configured = true;
+  }
+  dim3 grid(max_pairs, heads_q);
+  flash_fwd_kernel<true><<<grid, kFaThreads + 32, kFaSmem, stream>>>(tmQ, tmK, tmV, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

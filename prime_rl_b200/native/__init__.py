@@ -41,6 +41,7 @@ _CUDA_SIGNATURES = {
     "prb_ep_wait": [P, I, I, I, P, P],
     "prb_gemm_bf16_reduce_scatter": [P, P, I, I, I, L, L, I, I, F, P, I, I, L, P, P],
     "prb_gemm_bf16_allgather": [P, P, P, P, I, I, I, L, L, I, I, F, I, I, I, P, I, P, P],
+    "prb_flash_fwd_gather": [P, P, P, L, P, P, P, I, I, I, I, L, L, F, I, I, I, I, I, P, P, P],
     "prb_sparse_mla_fwd": [P, P, P, P, P, I, I, I, I, F, P, P],
     "prb_ep_signal": [P, I, I, I, I, P],
     "prb_ep_pull": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],

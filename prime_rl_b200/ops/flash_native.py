@@ -47,6 +47,33 @@ def flash_fwd(q, k, v, cu_seqlens, *, scale: float | None = None, window: int | 
     return out, lse
 
 
+def flash_fwd_gather(q, k_full, v_full, peer_ptrs, cu_seqlens, cp_rank: int, cp_size: int, counters, *,
+                     scale: float | None = None, window: int | None = None):
+    """Context-parallel forward with the K / V exchange inside the kernel. ``k_full`` / ``v_full``
+    ``[T, Hkv, 128]`` are the two halves of ONE buffer per rank (``v_full`` directly after ``k_full``
+    or at any 16-byte aligned distance) in which this rank has written the rows of its own chunk;
+    ``peer_ptrs`` is a ctypes array with the address of that buffer (its ``k_full``) on every rank.
+    ``q [T / cp, Hq, 128]`` are the local rows. After the call the chunks of all lower ranks are
+    present in the local buffer as well. Returns (out, lse) for the local rows."""
+    Tq, Hq, D = q.shape
+    T, Hkv = k_full.shape[0], k_full.shape[1]
+    assert D == 128 and q.dtype == torch.bfloat16 and T == Tq * cp_size
+    assert k_full.is_contiguous() and v_full.is_contiguous() and q.stride(2) == 1 and q.stride(1) == D
+    v_off = v_full.data_ptr() - k_full.data_ptr()
+    out = torch.empty(Tq, Hq, D, dtype=q.dtype, device=q.device)
+    lse = torch.empty(Hq, Tq, dtype=torch.float32, device=q.device)
+    num_docs = cu_seqlens.numel() - 1
+    max_pairs = (T + 255) // 256 + num_docs
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    status = rt.status_tensor(q.device)
+    rc = rt.lib().prb_flash_fwd_gather(q.data_ptr(), k_full.data_ptr(), peer_ptrs, v_off, out.data_ptr(), lse.data_ptr(),
+                                       cu_seqlens.data_ptr(), num_docs, T, Hq, Hkv, q.stride(0), out.stride(0),
+                                       float(scale), int(window or 0), max_pairs, cp_rank, cp_size, Tq,
+                                       counters.data_ptr(), status.data_ptr(), rt.stream_ptr(q.device))
+    rt.check(rc, "prb_flash_fwd_gather")
+    return out, lse
+
+
 def bwd_available() -> bool:
     try:
         return hasattr(native.cuda(), "prb_flash_bwd")

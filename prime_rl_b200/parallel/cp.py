@@ -11,6 +11,13 @@ non-attention layer runs on the local chunk, attention sees the whole (causal) c
 Both run on ``torch.distributed`` collectives (NCCL / gloo) for the exchange and on the tcgen05
 flash-attention kernels for the math (query-slice form for the all-gather path); per-token
 outputs (logprobs, entropy) are gathered back along the sequence for the loss.
+
+``ContextParallel(fused_kv_gather=True)`` moves the forward K / V exchange of the ``ring`` style into
+the attention kernel: K and V live in a symmetric buffer, every rank writes its own chunk, and one
+extra warp per CTA of the flash-attention forward pulls the chunks of the lower ranks over NVLink
+with plain peer loads while the tensor cores already run (``csrc/flash_attn.cu:
+flash_fwd_kernel<true>``); causality means a rank never needs the chunks above its own. The
+backward uses the gathered copy and reduces dK / dV with the library collective as before.
 """
 
 from __future__ import annotations
@@ -89,11 +96,81 @@ def attention_offset_ref(q, k, v, q_pos, k_pos, q_doc, k_doc, *, window=None, si
     return torch.einsum("hts,shd->thd", p, vf).to(q.dtype)
 
 
+_K_WRITTEN, _K_READ = 0, 1
+
+
+class _FusedGatherAttention(torch.autograd.Function):
+    """Forward: local chunk into the symmetric buffer, flag exchange, flash forward with the gather
+    warp. Backward: the tcgen05 backward on the saved gathered K / V; dK / dV summed over ranks."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cp: "ContextParallel", cu, window):
+        from ..ops import _runtime as rt
+        from ..ops import flash_native
+
+        Tl, Hkv, D = k.shape
+        st = cp._kv_state(Tl, Hkv, D, q.device)
+        lib, dev, R, rank = rt.lib(), q.device, cp.cp, cp.rank
+        st["k"][rank * Tl:(rank + 1) * Tl].copy_(k)
+        st["v"][rank * Tl:(rank + 1) * Tl].copy_(v)
+        st["epoch"] += 1
+        ep, stat, stream = st["epoch"], rt.status_tensor(dev).data_ptr(), rt.stream_ptr(dev)
+        rt.check(lib.prb_ep_signal(st["p_flags"], rank, R, _K_WRITTEN, ep, stream), "prb_ep_signal")
+        rt.check(lib.prb_ep_wait(st["flags"].data_ptr(), R, _K_WRITTEN, ep, stat, stream), "prb_ep_wait")
+        out, lse = flash_native.flash_fwd_gather(q.contiguous(), st["k"], st["v"], st["mem"].c_ptrs, cu, rank, R,
+                                                 st["counters"], window=window)
+        # every rank is done reading my chunk before the next layer overwrites it
+        rt.check(lib.prb_ep_signal(st["p_flags"], rank, R, _K_READ, ep, stream), "prb_ep_signal")
+        rt.check(lib.prb_ep_wait(st["flags"].data_ptr(), R, _K_READ, ep, stat, stream), "prb_ep_wait")
+        hi = (rank + 1) * Tl
+        kg, vg = torch.zeros_like(st["k"]), torch.zeros_like(st["v"])      # keys above the local chunk are never read
+        kg[:hi].copy_(st["k"][:hi])
+        vg[:hi].copy_(st["v"][:hi])
+        ctx.save_for_backward(q, kg, vg, out, lse, cu)
+        ctx.cfg = (cp, window, Tl)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from ..ops import flash_native
+
+        q, kg, vg, out, lse, cu = ctx.saved_tensors
+        cp, window, Tl = ctx.cfg
+        dq, dk, dv = flash_native.flash_bwd(dout, q, kg, vg, out, lse, cu, window=window, q_offset=cp.rank * Tl)
+        dist.all_reduce(dk, group=cp.group)
+        dist.all_reduce(dv, group=cp.group)
+        lo = cp.rank * Tl
+        return dq, dk[lo:lo + Tl].contiguous(), dv[lo:lo + Tl].contiguous(), None, None, None
+
+
 class ContextParallel:
-    def __init__(self, group, cp: int, rank: int, style: str = "ring", p2p_all_to_all: bool = False):
+    def __init__(self, group, cp: int, rank: int, style: str = "ring", p2p_all_to_all: bool = False,
+                 fused_kv_gather: bool = False):
         self.group, self.cp, self.rank, self.style = group, cp, rank, style
+        self.fused_kv_gather, self._kv = fused_kv_gather, None
         # Ulysses exchanges over NVLink peer memory instead of NCCL (built on first use, sized by the first block)
         self.use_p2p, self._p2p = p2p_all_to_all, None
+
+    def _kv_state(self, Tl: int, Hkv: int, D: int, device) -> dict:
+        """Symmetric K / V buffer of the fused-gather path: [K: T rows | V: T rows | counters | flags]."""
+        key = (Tl, Hkv, D)
+        if self._kv is None or self._kv["key"] != key:
+            from .symm import SymmetricBuffer
+
+            if self._kv is not None:
+                self._kv["mem"].close()
+            T = Tl * self.cp
+            half = T * Hkv * D * 2
+            off_cnt = 2 * half
+            off_flags = off_cnt + 256
+            mem = SymmetricBuffer(self.group, off_flags + 256, device, zero=True)
+            self._kv = {"key": key, "mem": mem, "epoch": 0,
+                        "k": mem.local(torch.bfloat16, 0, T * Hkv * D).view(T, Hkv, D),
+                        "v": mem.local(torch.bfloat16, half, T * Hkv * D).view(T, Hkv, D),
+                        "counters": mem.local(torch.int32, off_cnt, self.cp + 1),
+                        "flags": mem.local(torch.int32, off_flags, 2 * self.cp),
+                        "p_flags": mem.offset_ptrs(off_flags)}
+        return self._kv
 
     def _exchange(self, x):
         if self.use_p2p and x.is_cuda:
@@ -138,6 +215,10 @@ class ContextParallel:
 
     def _gather_kv(self, q, k, v, seq, window, sinks, backend):
         Tl, T = q.shape[0], seq.full_len
+        if (self.fused_kv_gather and q.is_cuda and sinks is None and q.dtype == torch.bfloat16 and q.shape[-1] == 128
+                and self.cp <= 8):
+            return _FusedGatherAttention.apply(q, k.contiguous(), v.contiguous(), self,
+                                               seq.full_cu_seqlens.to(torch.int32), window)
         kg = _AllGatherSeq.apply(k, self.group, True)
         vg = _AllGatherSeq.apply(v.contiguous(), self.group, True)
         lo, hi = self.rank * Tl, (self.rank + 1) * Tl

@@ -80,3 +80,13 @@ def test_trainer_step_with_peer_memory_expert_parallelism():
            "127.0.0.1", "--master-port", "29537", "-m", "prime_rl_b200.parallel.ep_trainer_selftest"]
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0 and "EP_TRAINER_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
+
+
+def test_context_parallel_attention_with_in_kernel_kv_gather():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", CP_SELFTEST_TIMING="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", "29538", "-m", "prime_rl_b200.parallel.cp_selftest"]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and "CP_FUSED_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]

@@ -624,3 +624,41 @@ def test_sparse_mla_forward_kernel_and_recomputed_backward(H, topk):
     for a, b in ((q.grad, qf.grad), (kv.grad, kvf.grad)):
         rel = float((a.float() - b).norm() / b.norm())
         assert rel < 3e-2, rel
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("cp,rank", [(2, 1), (4, 2), (2, 0)])
+def test_flash_forward_with_in_kernel_kv_gather_single_device(cp, rank):
+    """The context-parallel forward whose gather warp pulls the lower ranks' K / V chunks itself,
+    with every "peer" buffer on this GPU (one kernel, no cross-launch waits): the result equals
+    the query-slice kernel on complete K / V, and the local buffer ends up holding the chunks."""
+    import ctypes
+
+    from prime_rl_b200.ops import flash_native
+
+    torch.manual_seed(21)
+    dev = torch.device("cuda")
+    Tl, Hq, Hkv, D = 640, 8, 2, 128
+    T = Tl * cp
+    lens = [T // 2 - 100, T // 2 + 100]
+    cu = torch.tensor([0, lens[0], T], dtype=torch.int32, device=dev)
+    q = torch.randn(Tl, Hq, D, device=dev).bfloat16()
+    k = torch.randn(T, Hkv, D, device=dev).bfloat16()
+    v = torch.randn(T, Hkv, D, device=dev).bfloat16()
+    bufs = []
+    for r in range(cp):                       # rank r's buffer: [K | V], only its own chunk is valid
+        b = torch.zeros(2, T, Hkv, D, device=dev, dtype=torch.bfloat16)
+        b[0, r * Tl:(r + 1) * Tl] = k[r * Tl:(r + 1) * Tl]
+        b[1, r * Tl:(r + 1) * Tl] = v[r * Tl:(r + 1) * Tl]
+        bufs.append(b)
+    ptrs = (ctypes.c_void_p * cp)(*[b.data_ptr() for b in bufs])
+    counters = torch.zeros(cp + 1, dtype=torch.int32, device=dev)
+    mine = bufs[rank]
+    out, lse = flash_native.flash_fwd_gather(q, mine[0], mine[1], ptrs, cu, rank, cp, counters)
+    torch.cuda.synchronize()
+    rt.check_status()
+    ref_out, ref_lse = flash_native.flash_fwd(q, k, v, cu, q_offset=rank * Tl)
+    assert torch.equal(mine[0, : (rank + 1) * Tl], k[: (rank + 1) * Tl])
+    assert torch.equal(mine[1, : (rank + 1) * Tl], v[: (rank + 1) * Tl])
+    assert float((out.float() - ref_out.float()).abs().max()) < 1e-6
+    assert float((lse - ref_lse).abs().max()) < 1e-6
