@@ -186,6 +186,9 @@ class ModelConfig(BaseModelConfig):
     cp_style: Literal["ring", "ulysses"] = "ring"
     # "p2p": the ring style's forward K / V exchange runs inside the attention kernel over NVLink peer memory
     cp_kv_exchange: Literal["nccl", "p2p"] = "nccl"
+    # "p2p": the sharded optimizer's gradient reduce-scatter (with cast / scale) and parameter all-gather run as
+    # peer-memory kernels over NVLink instead of NCCL collectives (one NVSwitch box, at most 8 ranks per shard group)
+    optim_collectives: Literal["nccl", "p2p"] = "nccl"
     impl: Literal["hf", "custom", "auto"] = "auto"
     optimization_dtype: Literal["bfloat16", "float32"] = "float32"
     reduce_dtype: Literal["bfloat16", "float32"] = "float32"

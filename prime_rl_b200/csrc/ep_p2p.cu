@@ -288,6 +288,36 @@ ep_recv_fp8_kernel(__nv_bfloat16* __restrict__ buf, const uint8_t* __restrict__ 
   }
 }
 
+// Reduce-scatter of a flat fp32 gradient buffer that every rank holds in symmetric memory: this
+// rank sums elements [off, off + n) of all R buffers with peer loads, scales the sum and writes its
+// fp32 shard (the cast / scale of the bucket happens in the same pass). n and off are multiples of 4.
+__global__ void __launch_bounds__(256)
+rs_pull_kernel(EpPeers grads, long long off, long long n4, float scale, float4* __restrict__ out, int R) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < R; ++r) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.buf[r]) + off) + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    out[i] = make_float4(acc.x * scale, acc.y * scale, acc.z * scale, acc.w * scale);
+  }
+}
+
+// All-gather by stores: this rank's updated slice (n16 16-byte units at unit offset off16 of the
+// flat parameter buffer) is written into the same place of every other rank's buffer; blockIdx.y
+// walks over the peers.
+__global__ void __launch_bounds__(256)
+ag_push_kernel(const uint4* __restrict__ src, EpPeers dst, long long off16, long long n16, int rank, int R) {
+  int d = blockIdx.y;
+  if (d >= rank) ++d;                      // R - 1 destinations: everybody but me
+  if (d >= R) return;
+  uint4* o = reinterpret_cast<uint4*>(dst.buf[d]) + off16;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    o[i] = src[i];
+}
+
 __global__ void __launch_bounds__(32)
 ep_signal_kernel(EpPeers flags, int rank, int R, int kind, int epoch) {
   __threadfence_system();
@@ -518,6 +548,31 @@ PRB_API int prb_ep_recv_fp8(void* buf, const void* q, const float* scales, const
   prb::ep_recv_fp8_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<__nv_bfloat16*>(buf), reinterpret_cast<const uint8_t*>(q), scales, hist, expert_offset,
       flags + kind * R, rank, R, E, H, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// out[i] = scale * sum_r peer_grads[r][off + i], i in [0, n); fp32; off and n multiples of 4.
+PRB_API int prb_rs_pull(void* const* peer_grads, long long off, long long n, float scale, float* out, int R,
+                        void* stream) {
+  if (R > prb::kEpMaxRanks || (off % 4) || (n % 4) || (reinterpret_cast<uintptr_t>(out) & 15)) return -2;
+  if (n <= 0) return 0;
+  long long blocks = (n / 4 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  prb::rs_pull_kernel<<<static_cast<unsigned>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      ep_peers(peer_grads, R), off, n / 4, scale, reinterpret_cast<float4*>(out), R);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Writes `bytes` bytes at `src` (this rank's slice, inside its own buffer at byte offset off_bytes) to
+// the same offset of every other rank's buffer.
+PRB_API int prb_ag_push(const void* src, void* const* peer_bufs, long long off_bytes, long long bytes, int rank, int R,
+                        void* stream) {
+  if (R > prb::kEpMaxRanks || (off_bytes % 16) || (bytes % 16) || (reinterpret_cast<uintptr_t>(src) & 15)) return -2;
+  if (bytes <= 0 || R < 2) return 0;
+  long long blocks = (bytes / 16 + 255) / 256;
+  if (blocks > 148 * 2) blocks = 148 * 2;
+  prb::ag_push_kernel<<<dim3(static_cast<unsigned>(blocks), R - 1), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint4*>(src), ep_peers(peer_bufs, R), off_bytes / 16, bytes / 16, rank, R);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -43,6 +43,8 @@ _CUDA_SIGNATURES = {
     "prb_gemm_bf16_allgather": [P, P, P, P, I, I, I, L, L, I, I, F, I, I, I, P, I, P, P],
     "prb_flash_fwd_gather": [P, P, P, L, P, P, P, I, I, I, I, L, L, F, I, I, I, I, I, P, P, P],
     "prb_sparse_mla_fwd": [P, P, P, P, P, I, I, I, I, F, P, P],
+    "prb_rs_pull": [P, L, L, F, P, I, P],
+    "prb_ag_push": [P, P, L, L, I, I, P],
     "prb_ep_signal": [P, I, I, I, I, P],
     "prb_ep_pull": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
     "prb_gemm_bf16_ext": [P, P, P, I, I, I, L, L, L, I, I, I, F, F, P, I, I, I, P, P, I, L, L, I, P, P],

@@ -39,7 +39,9 @@ class FlatBuffers:
     """Owns the flat parameter / master / gradient storage of a set of parameters."""
 
     def __init__(self, named_params: list[tuple[str, torch.nn.Parameter]], master_dtype=torch.float32,
-                 align: int = 8, pad_to: int = 1, full_master: bool = True):
+                 align: int = 8, pad_to: int = 1, full_master: bool = True, alloc=None):
+        """``alloc(numel, dtype) -> (flat, grad)`` supplies the two flat tensors (zero-filled) when they
+        have to live in special memory (the peer-memory collectives keep them in a symmetric buffer)."""
         params = [(n, p) for n, p in named_params if p.requires_grad]
         if not params:
             raise ValueError("no trainable parameters")
@@ -55,7 +57,11 @@ class FlatBuffers:
         off = (off + pad_to - 1) // pad_to * pad_to
         self.numel = off
         self.params = [p for _, p in params]
-        self.flat = torch.zeros(off, dtype=self.dtype, device=self.device)
+        given_grad = None
+        if alloc is not None:
+            self.flat, given_grad = alloc(off, self.dtype)
+        else:
+            self.flat = torch.zeros(off, dtype=self.dtype, device=self.device)
         for s, p in zip(self.slots, self.params):
             view = self.flat[s.offset:s.offset + s.numel].view(s.shape)
             view.copy_(p.data)
@@ -66,7 +72,7 @@ class FlatBuffers:
             self.master = self.flat
         else:
             self.master = self.flat.to(master_dtype)
-        self.grad = torch.zeros(off, dtype=torch.float32, device=self.device)
+        self.grad = given_grad if given_grad is not None else torch.zeros(off, dtype=torch.float32, device=self.device)
         self._grad_views = [self.grad[s.offset:s.offset + s.numel].view(s.shape) for s in self.slots]
 
     @property
@@ -166,13 +172,23 @@ class _Group:
                       GPU there is nothing to gain from re-gathering them layer by layer.
     """
 
-    def __init__(self, kind: str, named_params, reduce_group, norm_group, shard_group=None):
+    def __init__(self, kind: str, named_params, reduce_group, norm_group, shard_group=None, p2p: bool = False):
         self.reduce_group, self.norm_group = reduce_group, norm_group
+        self.p2p = None
         self.shard_n = dist.get_world_size(shard_group) if (shard_group is not None and dist.is_initialized()) else 1
         self.shard_group = shard_group if self.shard_n > 1 else None
         self.shard_rank = dist.get_rank(shard_group) if self.shard_group is not None else 0
         sharded = self.shard_group is not None
-        self.buf = FlatBuffers(named_params, pad_to=8 * self.shard_n, full_master=not sharded)
+        alloc = None
+        if p2p and sharded and self.shard_n <= 8 and any(p.is_cuda for _, p in named_params):
+            # flat parameters and gradients in symmetric memory: the two collectives become peer loads / stores
+            def alloc(numel, dtype, self=self, named_params=named_params):
+                from ..parallel.p2p_zero import P2PShardCollectives
+
+                dev = next(p for _, p in named_params if p.requires_grad).device
+                self.p2p = P2PShardCollectives(self.shard_group, numel, dtype, dev)
+                return self.p2p.flat, self.p2p.grad
+        self.buf = FlatBuffers(named_params, pad_to=8 * self.shard_n, full_master=not sharded, alloc=alloc)
         n, dev = self.buf.numel // self.shard_n, self.buf.device
         self.shard_len = n
         lo = self.shard_rank * n
@@ -202,7 +218,9 @@ class _Group:
         if not dist.is_initialized():
             return
         if self.sharded:
-            if _backend(self.shard_group) == "gloo":
+            if self.p2p is not None:
+                self.p2p.reduce_scatter(self.grad_shard, self.shard_rank * self.shard_len)
+            elif _backend(self.shard_group) == "gloo":
                 dist.all_reduce(self.buf.grad, group=self.shard_group)
                 lo = self.shard_rank * self.shard_len
                 self.grad_shard.copy_(self.buf.grad[lo:lo + self.shard_len])
@@ -217,7 +235,9 @@ class _Group:
     def publish(self) -> None:
         """After the update: make the new parameters visible in the replicated flat buffer."""
         if self.sharded:
-            if _backend(self.shard_group) == "gloo":
+            if self.p2p is not None:
+                self.p2p.all_gather(self.shard_rank * self.shard_len, self.shard_len)
+            elif _backend(self.shard_group) == "gloo":
                 parts = [torch.empty_like(self.flat_shard) for _ in range(self.shard_n)]
                 dist.all_gather(parts, self.flat_shard.contiguous(), group=self.shard_group)
                 self.buf.flat.copy_(torch.cat(parts))
@@ -249,18 +269,18 @@ class FlatOptimizer:
     def __init__(self, config, named_params, *, max_steps: int | None = None, scheduler_config=None,
                  dp_group=None, expert_params=None, expert_reduce_group=None, expert_norm_group=None,
                  shard_group=None, replicate_group=None, expert_shard_group=None, offload: str | None = None,
-                 offload_chunk: int = 16 * 1024 * 1024):
+                 offload_chunk: int = 16 * 1024 * 1024, p2p_collectives: bool = False):
         self.config = config
         self.kind = config.type
         self.step_count = 0
         if self.kind == "muon":
             shard_group = expert_shard_group = None  # Newton-Schulz needs whole matrices
         self.groups = [_Group(self.kind, named_params, replicate_group if shard_group is not None else dp_group,
-                              None, shard_group)]
+                              None, shard_group, p2p=p2p_collectives)]
         if expert_params and any(p.requires_grad for _, p in expert_params):
             self.groups.append(_Group(self.kind, expert_params,
                                       None if expert_shard_group is not None else expert_reduce_group,
-                                      expert_norm_group, expert_shard_group))
+                                      expert_norm_group, expert_shard_group, p2p=p2p_collectives))
         self.schedule = LRSchedule(scheduler_config, max_steps, config.lr) if scheduler_config is not None \
             else LRSchedule(type("C", (), {"type": "constant"})(), max_steps, config.lr)
         dev = self.groups[0].buf.device
@@ -441,7 +461,7 @@ class FlatOptimizer:
 def setup_optimizer(config, model, *, max_steps=None, scheduler_config=None, dp_group=None,
                     expert_reduce_group=None, expert_norm_group=None, shard_group=None, replicate_group=None,
                     expert_shard_group=None, offload: str | None = None,
-                    offload_chunk: int = 16 * 1024 * 1024) -> FlatOptimizer:
+                    offload_chunk: int = 16 * 1024 * 1024, p2p_collectives: bool = False) -> FlatOptimizer:
     """Parameters marked ``_is_expert_shard`` (set by the expert-parallel setup) form their own
     group: they are reduced over the ranks that replicate the same expert shard."""
     dense = [(n, p) for n, p in model.named_parameters() if not getattr(p, "_is_expert_shard", False)]
@@ -450,4 +470,4 @@ def setup_optimizer(config, model, *, max_steps=None, scheduler_config=None, dp_
                          expert_params=expert, expert_reduce_group=expert_reduce_group,
                          expert_norm_group=expert_norm_group, shard_group=shard_group,
                          replicate_group=replicate_group, expert_shard_group=expert_shard_group, offload=offload,
-                         offload_chunk=offload_chunk)
+                         offload_chunk=offload_chunk, p2p_collectives=p2p_collectives)

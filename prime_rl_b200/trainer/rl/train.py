@@ -88,7 +88,8 @@ class RLTrainer:
             expert_shard_group=d.group("dp_shard_mod_ep")
             if (zero and ep_on and d.dp_replicate == 1 and d.dp_shard_cp // d.ep > 1) else None,
             offload="cpu" if mc.full_offload else ("state" if mc.optim_cpu_offload else None),
-            offload_chunk=mc.full_offload.chunk_elements if mc.full_offload else 16 * 1024 * 1024)
+            offload_chunk=mc.full_offload.chunk_elements if mc.full_offload else 16 * 1024 * 1024,
+            p2p_collectives=mc.optim_collectives == "p2p" and self.device.type == "cuda")
         self.ckpt = CheckpointManager(self.run_dir, cfg.ckpt, is_master=self.world.is_master, rank=self.world.rank) \
             if cfg.ckpt is not None or cfg.resume is not None else None
         self._setup_data()
