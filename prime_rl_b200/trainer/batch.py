@@ -41,6 +41,12 @@ def prepare_sample(s: TrainingSample, seq_len: int) -> dict:
              ref_logprobs=_cut(s.ref_logprobs, n), rl_weights=_cut(s.rl_weights, n), ce_weights=_cut(s.ce_weights, n),
              ref_kl_weights=_cut(s.ref_kl_weights, n), routed_experts=s.routed_experts,
              sampling_mask=s.sampling_mask, trace_id=s.trace_id, branch_index=s.branch_index, length=n)
+    d["mm_kwargs"], d["mm_token_type_ids"] = s.mm_kwargs, _cut(s.mm_token_type_ids, n)
+    if s.mm_kwargs is not None and n < k and s.mm_token_type_ids is not None and any(s.mm_token_type_ids[n:]):
+        # the image features of a sample are one tensor for all its images: a cut through (or before) image
+        # placeholder tokens would leave features without tokens
+        raise ValueError(f"multimodal sample of {k} tokens has image tokens past seq_len={seq_len}; raise seq_len "
+                         "or filter such samples")
     return d
 
 
@@ -159,6 +165,22 @@ def _pack_row(rows: list[dict], pad_to: int) -> MicroBatch:
                 idbufs.append(np.frombuffer(sm.ids, np.int32)[: int(c.sum())])
         mb.sampling_mask = SamplingMask(ids=(np.concatenate(idbufs) if idbufs else np.zeros(0, np.int32)).tobytes(),
                                         counts=np.concatenate(counts).tobytes())
+    if any(r.get("mm_kwargs") is not None for r in rows):
+        from ..transports.batch.types import EncodedTensor
+
+        # image tensors of the row's samples, concatenated along dim 0 in token order
+        keys = sorted({k for r in rows if r.get("mm_kwargs") for k in r["mm_kwargs"]})
+        merged = {}
+        for key in keys:
+            parts = [r["mm_kwargs"][key] for r in rows if r.get("mm_kwargs") and key in r["mm_kwargs"]]
+            arrs = [np.frombuffer(e.data, dtype=np.dtype(e.dtype)).reshape(e.shape) for e in parts]
+            full = np.concatenate(arrs, 0)
+            merged[key] = EncodedTensor(dtype=str(full.dtype), shape=list(full.shape), data=full.tobytes())
+        mb.mm_kwargs = merged
+        types: list[int] = []
+        for r in rows:
+            types.extend(r.get("mm_token_type_ids") or [0] * r["length"])
+        mb.mm_token_type_ids = types
     total = len(ids)
     if pad_to > 1 and total % pad_to:
         _pad(mb, pad_to - total % pad_to)
@@ -176,6 +198,8 @@ def _pad(mb: MicroBatch, n: int) -> None:
             v.extend([fill] * n)
     if mb.trace_ids is not None:
         mb.trace_ids.append(""); mb.branch_indices.append(-1)
+    if mb.mm_token_type_ids is not None:
+        mb.mm_token_type_ids.extend([0] * n)
 
 
 def dummy_micro_batch(like: MicroBatch, length: int | None = None) -> MicroBatch:

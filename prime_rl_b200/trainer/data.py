@@ -43,6 +43,8 @@ class TensorMicroBatch:
     trace_ids: list[str] | None = None
     branch_indices: list[int] | None = None
     lora_num_tokens: torch.Tensor | None = None
+    mm_kwargs: dict | None = None                  # image tensors of the row: pixel_values, image_grid_thw
+    mm_token_type_ids: torch.Tensor | None = None  # int32 [T]: 0 text, 1 image placeholder
 
     TENSOR_FIELDS = ("input_ids", "position_ids", "advantages", "inference_logprobs", "loss_mask", "temperatures",
                      "ref_logprobs", "routed_experts", "sampling_mask", "rl_weights", "ce_weights",
@@ -64,7 +66,10 @@ class TensorMicroBatch:
               for f in self.TENSOR_FIELDS}
         return TensorMicroBatch(sequence_lengths=self.sequence_lengths, env_names=self.env_names,
                                 trace_ids=self.trace_ids, branch_indices=self.branch_indices,
-                                lora_num_tokens=self.lora_num_tokens, **kw)
+                                lora_num_tokens=self.lora_num_tokens,
+                                mm_kwargs={k: v.to(device, non_blocking=non_blocking) for k, v in self.mm_kwargs.items()}
+                                if self.mm_kwargs else None,
+                                mm_token_type_ids=self.mm_token_type_ids, **kw)
 
     def h2d_bytes(self) -> int:
         return sum(getattr(self, f).numel() * getattr(self, f).element_size()

@@ -58,6 +58,17 @@ class RLTrainer:
         t0 = time.perf_counter()
         self.model = build_model(self.arch, device=self.device, dtype=dtype, attn_backend=mc.attn, seed=0)
         self._maybe_load_pretrained()
+        self.mm = None
+        if mc.vlm is not None:
+            from ...models.vision import MultimodalLM, VisionConfig
+
+            if not mc.vlm.freeze_vision_encoder:
+                raise NotImplementedError("training the vision tower (set model.vlm.freeze_vision_encoder = true)")
+            vc = VisionConfig(**{"out_hidden_size": self.arch.hidden_size, **mc.vlm.vision})
+            self.mm = MultimodalLM(self.model, vc, mc.vlm.image_token_id, tuple(mc.vlm.mrope_section), dtype=dtype,
+                                   device=self.device)
+            for p in self.mm.visual.parameters():
+                p.requires_grad_(False)
         if mc.debug.force_balanced_routing:
             for m in self.model.moe_layers():
                 m.router.force_balanced = True
@@ -181,9 +192,9 @@ class RLTrainer:
             from ...utils.act_offloading import OffloadActivations
 
             with OffloadActivations(pin_memory=offload.pin_memory, max_inflight=offload.max_inflight_activations):
-                hidden = self.model(ids, seq)
+                hidden = self._forward(ids, seq, mb)
         else:
-            hidden = self.model(ids, seq)
+            hidden = self._forward(ids, seq, mb)
         smask = None
         if mb.sampling_mask is not None:
             if self.cp_ctx is not None:
@@ -208,6 +219,17 @@ class RLTrainer:
         out = {"loss": loss.detach(), "entropy": (entropy * mask).sum() / mask.sum().clamp_min(1)}
         out.update({k: v.detach() for k, v in lm.items()})
         return out
+
+    def _forward(self, ids, seq, mb):
+        """Decoder forward; multimodal rows go through the vision tower first."""
+        if self.mm is None:
+            if mb.mm_kwargs:
+                raise ValueError("the batch carries image tensors but the trainer has no model.vlm section")
+            return self.model(ids, seq)
+        if self.cp_ctx is not None:
+            raise NotImplementedError("multimodal batches together with context parallelism")
+        mm = mb.mm_kwargs or {}
+        return self.mm(ids, seq, mm.get("pixel_values"), mm.get("image_grid_thw"))
 
     # ------------------------------------------------------------------ one optimizer step
     def step(self, micro_batches: list[TensorMicroBatch] | None = None) -> dict:

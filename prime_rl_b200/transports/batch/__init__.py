@@ -15,7 +15,8 @@ import torch
 
 from ...utils.pathing import get_batch_dir, get_step_path
 from .types import (MicroBatch, RoutedExperts, SamplingMask, TrainingSample, decode_micro_batches,  # noqa: F401
-                    decode_routed_experts, decode_sampling_mask, encode_micro_batches)
+                    decode_routed_experts, decode_sampling_mask, decode_tensor, encode_micro_batches,
+                    encode_tensor)
 
 
 def micro_batch_to_tensors(mb: MicroBatch):
@@ -33,6 +34,8 @@ def micro_batch_to_tensors(mb: MicroBatch):
         sampling_mask=decode_sampling_mask(mb.sampling_mask, T) if mb.sampling_mask is not None else None,
         rl_weights=f32(mb.rl_weights), ce_weights=f32(mb.ce_weights), ref_kl_weights=f32(mb.ref_kl_weights),
         trace_ids=mb.trace_ids, branch_indices=mb.branch_indices,
+        mm_kwargs={k: decode_tensor(e) for k, e in mb.mm_kwargs.items()} if mb.mm_kwargs else None,
+        mm_token_type_ids=torch.tensor(mb.mm_token_type_ids, dtype=torch.int32) if mb.mm_token_type_ids else None,
         lora_num_tokens=torch.tensor([T], dtype=torch.int32))
 
 

@@ -85,6 +85,23 @@ def decode_micro_batches(buf: bytes) -> list[MicroBatch]:
     return _decoder.decode(buf)
 
 
+def encode_tensor(t: torch.Tensor) -> EncodedTensor:
+    """Any CPU tensor -> wire form (bf16 travels as its raw 16-bit words)."""
+    t = t.detach().cpu().contiguous()
+    if t.dtype == torch.bfloat16:
+        return EncodedTensor(dtype="bfloat16", shape=list(t.shape), data=t.view(torch.int16).numpy().tobytes())
+    arr = t.numpy()
+    return EncodedTensor(dtype=str(arr.dtype), shape=list(arr.shape), data=arr.tobytes())
+
+
+def decode_tensor(e: EncodedTensor) -> torch.Tensor:
+    if e.dtype == "bfloat16":
+        arr = np.frombuffer(e.data, dtype=np.int16).reshape(e.shape)
+        return torch.from_numpy(arr.copy()).view(torch.bfloat16)
+    arr = np.frombuffer(e.data, dtype=np.dtype(e.dtype)).reshape(e.shape)
+    return torch.from_numpy(arr.copy())
+
+
 def encode_routed_experts(arr: np.ndarray) -> RoutedExperts:
     return RoutedExperts(data=arr.tobytes(), shape=list(arr.shape), dtype=str(arr.dtype))
 

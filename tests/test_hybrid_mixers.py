@@ -351,3 +351,55 @@ def test_vision_tower_and_multimodal_forward():
     a = mm(tids, SeqInfo.from_lengths([14], "cpu"))
     b = lm(tids, SeqInfo.from_lengths([14], "cpu"))
     assert torch.allclose(a, b, atol=1e-5)
+
+
+def test_multimodal_samples_travel_from_packing_to_the_trainer(tmp_path):
+    """Two samples with images are packed into micro-batches, encoded to the wire format, decoded
+    and trained on by the RL trainer with a (frozen) vision tower."""
+    from prime_rl_b200.configs.trainer import TrainerConfig
+    from prime_rl_b200.trainer.batch import prepare_batch
+    from prime_rl_b200.trainer.rl.train import RLTrainer
+    from prime_rl_b200.transports.batch import micro_batch_to_tensors
+    from prime_rl_b200.transports.batch.types import (TrainingSample, decode_micro_batches, encode_micro_batches,
+                                                      encode_tensor)
+    from prime_rl_b200.utils.logger import setup_logger
+
+    setup_logger("warning")
+    torch.manual_seed(13)
+    arch = resolve_arch("tiny-qwen3.5-moe")
+    image_token = arch.vocab_size - 1
+    vision = dict(depth=1, hidden_size=32, intermediate_size=64, num_heads=4, patch_size=4, temporal_patch_size=2,
+                  num_position_embeddings=64)
+
+    def sample(n_text, grid):
+        t, h, w = grid
+        n_img = t * (h // 2) * (w // 2)
+        ids = [5] * 3 + [image_token] * n_img + list(range(10, 10 + n_text))
+        k = len(ids)
+        types = [0] * 3 + [1] * n_img + [0] * n_text
+        mm = {"pixel_values": encode_tensor(torch.randn(t * h * w, 3 * 2 * 4 * 4)),
+              "image_grid_thw": encode_tensor(torch.tensor([grid]))}
+        return TrainingSample(token_ids=ids, mask=[False] * (3 + n_img) + [True] * n_text, logprobs=[-1.0] * k,
+                              temperatures=[1.0] * k, env_name="vqa", advantages=[0.5] * k, mm_kwargs=mm,
+                              mm_token_type_ids=types)
+
+    grid = prepare_batch([sample(6, (1, 4, 4)), sample(9, (1, 2, 4))], seq_len=64, num_train_workers=1)
+    wire = decode_micro_batches(encode_micro_batches(grid[0]))
+    mbs = [micro_batch_to_tensors(m) for m in wire]
+    total_patches = sum(int(m.mm_kwargs["pixel_values"].shape[0]) for m in mbs if m.mm_kwargs)
+    assert total_patches == 16 + 8
+    for m in mbs:
+        if m.mm_kwargs:
+            n_img_tokens = int((m.mm_token_type_ids == 1).sum())
+            g = m.mm_kwargs["image_grid_thw"]
+            assert n_img_tokens == int((g[:, 0] * (g[:, 1] // 2) * (g[:, 2] // 2)).sum())
+    cfg = TrainerConfig.model_validate({
+        "model": {"name": "tiny-qwen3.5-moe", "seq_len": 64, "ac": None, "impl": "custom", "debug": {"random_init": True},
+                  "vlm": {"vision": vision, "image_token_id": image_token, "mrope_section": [2, 1, 1]}},
+        "optim": {"lr": 1e-3}, "max_steps": 1, "output_dir": str(tmp_path / "run"),
+        "data": {"fake": {"batch_size": 1}}})
+    tr = RLTrainer(cfg, device=torch.device("cpu")).setup()
+    m = tr.step(mbs)
+    assert m["loss"] == m["loss"] and m["optim/grad_norm"] > 0
+    with pytest.raises(ValueError):
+        prepare_batch([sample(6, (1, 4, 4))], seq_len=5, num_train_workers=1)
