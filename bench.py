@@ -26,6 +26,7 @@ import os
 import statistics
 import subprocess
 import sys
+import tempfile
 import threading
 import time
 from pathlib import Path
@@ -136,7 +137,7 @@ def main():
     cfg = TrainerConfig.model_validate({
         "model": mcfg, "data": {"fake": {"batch_size": args.micro_batches * n}},
         "optim": {"type": "adamw", "lr": 1e-5, "weight_decay": 0.01, "max_norm": 1.0},
-        "max_steps": None, "output_dir": str(ROOT / "gpurun_out" / "bench_run"), "monitors": {"file": None},
+        "max_steps": None, "output_dir": str(Path(tempfile.gettempdir()) / "prime_rl_b200_bench_run"), "monitors": {"file": None},
         "weight_broadcast": {"type": "filesystem"}})
     trainer = RLTrainer(cfg).setup()
     dev = trainer.device
