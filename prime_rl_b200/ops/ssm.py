@@ -25,10 +25,52 @@ import torch.nn.functional as F
 RESET = -80.0      # log-decay given to the first token of a document: exp(-80) ~ 1.8e-35
 
 
+class _CausalConv1d(torch.autograd.Function):
+    """``csrc/conv1d.cu``: bf16, 8 channels per thread, document boundaries from ``position_ids``."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, pos, silu):
+        from . import _runtime as rt
+
+        T, C = x.shape
+        y = torch.empty_like(x)
+        rt.check(rt.lib().prb_conv1d_fwd(x.data_ptr(), weight.data_ptr(), rt.ptr(bias), pos.data_ptr(), y.data_ptr(), T, C,
+                                         weight.shape[1], int(silu), rt.stream_ptr(x.device)), "prb_conv1d_fwd")
+        ctx.save_for_backward(x, weight, bias, pos)
+        ctx.silu = silu
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import _runtime as rt
+
+        x, weight, bias, pos = ctx.saved_tensors
+        T, C = x.shape
+        dy = dy.contiguous()
+        dx = torch.empty_like(x)
+        dw = torch.zeros(C, weight.shape[1], dtype=torch.float32, device=x.device)
+        db = torch.zeros(C, dtype=torch.float32, device=x.device) if bias is not None else None
+        rt.check(rt.lib().prb_conv1d_bwd(x.data_ptr(), weight.data_ptr(), rt.ptr(bias), pos.data_ptr(), dy.data_ptr(),
+                                         dx.data_ptr(), dw.data_ptr(), rt.ptr(db), T, C, weight.shape[1], int(ctx.silu),
+                                         rt.stream_ptr(x.device)), "prb_conv1d_bwd")
+        return dx, dw.to(weight.dtype), (db.to(bias.dtype) if db is not None else None), None, None
+
+
 def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, position_ids: torch.Tensor,
                   activation: str | None = "silu") -> torch.Tensor:
     """Depthwise causal convolution over tokens. ``x [T, C]``, ``weight [C, K]`` (tap K-1 multiplies
     the current token), ``position_ids [T]`` position of every token in its document."""
+    if (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+            and weight.shape[1] <= 4 and activation in ("silu", "swish", None)
+            and (bias is None or bias.dtype == torch.bfloat16)):
+        return _CausalConv1d.apply(x.contiguous(), weight.contiguous(), bias, position_ids.to(torch.int32).contiguous(),
+                                   activation is not None)
+    return causal_conv1d_ref(x, weight, bias, position_ids, activation)
+
+
+def causal_conv1d_ref(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, position_ids: torch.Tensor,
+                      activation: str | None = "silu") -> torch.Tensor:
+    """PyTorch definition of ``causal_conv1d`` (CPU path and oracle of the kernel)."""
     T, C = x.shape
     K = weight.shape[1]
     xf = x.float()

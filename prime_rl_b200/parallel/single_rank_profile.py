@@ -4,6 +4,10 @@ GPU's own buffer), so that a single-GPU profiler capture can look at them:
     python -m prime_rl_b200.parallel.single_rank_profile --op ep      # dispatch / combine kernels
     python -m prime_rl_b200.parallel.single_rank_profile --op rs      # GEMM with the reduce-scatter epilogue
     python -m prime_rl_b200.parallel.single_rank_profile --op push    # weight copy / fp8 quantising push
+    python -m prime_rl_b200.parallel.single_rank_profile --op ep8     # EP dispatch with the fp8 payload
+    python -m prime_rl_b200.parallel.single_rank_profile --op ag      # GEMM with the all-gather prologue (2 emulated ranks)
+    python -m prime_rl_b200.parallel.single_rank_profile --op cp      # flash forward with the K/V gather warp (2 emulated ranks)
+    python -m prime_rl_b200.parallel.single_rank_profile --op zero    # optimizer reduce-scatter pull / all-gather push
 
 The traffic that would cross NVLink stays in local HBM here; instruction mix, occupancy and
 local-memory behaviour are what such a capture shows.
@@ -20,7 +24,7 @@ import torch.distributed as dist
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--op", required=True, choices=["ep", "rs", "push"])
+    ap.add_argument("--op", required=True, choices=["ep", "ep8", "rs", "push", "ag", "cp", "zero"])
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=2)
     args = ap.parse_args(argv)
@@ -33,7 +37,48 @@ def main(argv=None):
     torch.manual_seed(0)
     from ..ops import _runtime as rt
 
-    if args.op == "ep":
+    if args.op == "ag":
+        import ctypes
+
+        M, N, K, rows = args.tokens, 4096, 2048, 2048             # "rank 0" of 2: half of the weight rows are remote
+        x = torch.randn(M, K, device=dev).bfloat16()
+        mine = torch.randn(N, K, device=dev).bfloat16()
+        other = torch.randn(N, K, device=dev).bfloat16()
+        ptrs = (ctypes.c_void_p * 2)(mine.data_ptr(), other.data_ptr())
+        ready = torch.zeros(N // 256, dtype=torch.int32, device=dev)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        for it in range(args.iters):
+            rt.check(rt.lib().prb_gemm_bf16_allgather(x.data_ptr(), mine.data_ptr(), ptrs, out.data_ptr(), M, N, K, K, N, 0,
+                                                      0, 1.0, 0, 2, rows, ready.data_ptr(), it + 1,
+                                                      rt.status_tensor(dev).data_ptr(), rt.stream_ptr(dev)),
+                     "prb_gemm_bf16_allgather")
+    elif args.op == "cp":
+        import ctypes
+
+        from ..ops import flash_native
+
+        Tl, Hq, Hkv = args.tokens, 32, 4                          # "rank 1" of 2: chunk 0 is pulled from the other buffer
+        T = 2 * Tl
+        cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        q = torch.randn(Tl, Hq, 128, device=dev).bfloat16()
+        bufs = [torch.randn(2, T, Hkv, 128, device=dev).bfloat16() for _ in range(2)]
+        ptrs = (ctypes.c_void_p * 2)(*[b.data_ptr() for b in bufs])
+        counters = torch.zeros(3, dtype=torch.int32, device=dev)
+        for _ in range(args.iters):
+            flash_native.flash_fwd_gather(q, bufs[1][0], bufs[1][1], ptrs, cu, 1, 2, counters)
+    elif args.op == "zero":
+        import ctypes
+
+        n = args.tokens * 16384                                   # 256 MiB of fp32 gradients at the default size
+        grads = [torch.randn(n, device=dev) for _ in range(2)]
+        flats = [torch.empty(n, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        pg = (ctypes.c_void_p * 2)(*[g.data_ptr() for g in grads])
+        pf = (ctypes.c_void_p * 2)(*[f.data_ptr() for f in flats])
+        shard = torch.empty(n // 2, dtype=torch.float32, device=dev)
+        for _ in range(args.iters):
+            rt.check(rt.lib().prb_rs_pull(pg, 0, n // 2, 0.5, shard.data_ptr(), 2, rt.stream_ptr(dev)), "prb_rs_pull")
+            rt.check(rt.lib().prb_ag_push(flats[0].data_ptr(), pf, 0, n, 0, 2, rt.stream_ptr(dev)), "prb_ag_push")
+    elif args.op in ("ep", "ep8"):
         from ..models.layers import GroupedExperts
         from ..ops import moe as moe_ops
         from .ep_p2p import P2PDispatcher
@@ -44,7 +89,7 @@ def main(argv=None):
         with torch.no_grad():
             ex.gate_up_proj.normal_(0, 0.05)
             ex.down_proj.normal_(0, 0.05)
-        disp = P2PDispatcher(group, 1, E, capacity_factor=1.0, max_tokens=T)
+        disp = P2PDispatcher(group, 1, E, capacity_factor=1.0, max_tokens=T, payload="fp8" if args.op == "ep8" else "bf16")
         for _ in range(args.iters):
             x = torch.randn(T, H, device=dev).bfloat16().requires_grad_()
             idx, w, counts = moe_ops.route_topk(torch.randn(T, E, device=dev), k)

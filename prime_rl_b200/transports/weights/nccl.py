@@ -32,6 +32,9 @@ def _new_group(host: str, port: int, rank: int, world_size: int, timeout: int, d
     if backend == "gloo":
         pg = dist.ProcessGroupGloo(prefix, rank, world_size, datetime.timedelta(seconds=timeout))
     else:
+        from ...utils.nccl import configure_nccl_transports
+
+        configure_nccl_transports()          # PCIe-only hosts: NCCL must not try CUDA IPC between the GPUs
         opts = dist.ProcessGroupNCCL.Options()
         pg = dist.ProcessGroupNCCL(prefix, rank, world_size, opts)
     return pg, store

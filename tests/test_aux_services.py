@@ -194,3 +194,30 @@ def test_dashboard_trace_browser_joins_traces_and_annotations(tmp_path, monkeypa
     other.mkdir()
     assert str(other.resolve()) in client.post("/api/view", json={"path": str(other)}).json()["runs"]
     assert "Traces" in client.get("/").text
+
+
+def test_nccl_transport_probe_with_a_fake_nvml():
+    from prime_rl_b200.utils import nccl
+
+    class FakeNVML:
+        def __init__(self, links):
+            self.links, self.shutdowns = links, 0
+
+        def nvmlInit(self): pass
+        def nvmlShutdown(self): self.shutdowns += 1
+        def nvmlDeviceGetCount(self): return len(self.links)
+        def nvmlDeviceGetHandleByIndex(self, i): return i
+
+        def nvmlDeviceGetNvLinkState(self, h, link):
+            if link >= len(self.links[h]):
+                raise RuntimeError("not supported")
+            return self.links[h][link]
+
+    with_links, without = FakeNVML([[0, 1], [0, 0]]), FakeNVML([[0, 0], []])
+    assert nccl.nvlink_present(with_links) is True and nccl.nvlink_present(without) is False
+    env = {}
+    assert nccl.configure_nccl_transports(with_links, env) is False and env == {}
+    assert nccl.configure_nccl_transports(without, env) is True
+    assert env == {"NCCL_P2P_DISABLE": "1", "NCCL_SHM_DISABLE": "1"} and without.shutdowns == 2
+    env = {"NCCL_P2P_DISABLE": "0", "NCCL_SHM_DISABLE": "0"}
+    assert nccl.configure_nccl_transports(without, env) is False and env["NCCL_P2P_DISABLE"] == "0"

@@ -662,3 +662,30 @@ def test_flash_forward_with_in_kernel_kv_gather_single_device(cp, rank):
     assert torch.equal(mine[1, : (rank + 1) * Tl], v[: (rank + 1) * Tl])
     assert float((out.float() - ref_out.float()).abs().max()) < 1e-6
     assert float((lse - ref_lse).abs().max()) < 1e-6
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("C,K,act,with_bias", [(264, 4, "silu", True), (64, 4, "silu", False), (40, 3, None, True)])
+def test_causal_conv1d_kernel_forward_and_backward(C, K, act, with_bias):
+    from prime_rl_b200.ops import ssm
+
+    torch.manual_seed(31)
+    dev = torch.device("cuda")
+    lengths = [70, 1, 3, 129, 40]
+    T = sum(lengths)
+    pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lengths]).to(dev)
+    x = torch.randn(T, C, device=dev).bfloat16().requires_grad_()
+    w = (torch.randn(C, K, device=dev) * 0.5).bfloat16().requires_grad_()
+    b = torch.randn(C, device=dev).bfloat16().requires_grad_() if with_bias else None
+    y = ssm.causal_conv1d(x, w, b, pos, act)
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    bf = b.detach().float().requires_grad_() if with_bias else None
+    ref = ssm.causal_conv1d_ref(xf, wf, bf, pos, act)
+    assert float((y.float() - ref).abs().max()) < 3e-2
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    ref.backward(dy.float())
+    assert float((x.grad.float() - xf.grad).abs().max()) < 5e-2
+    assert float((w.grad.float() - wf.grad).abs().max() / wf.grad.abs().max()) < 2e-2
+    if with_bias:
+        assert float((b.grad.float() - bf.grad).abs().max() / bf.grad.abs().max()) < 2e-2
