@@ -43,6 +43,8 @@ _CUDA_SIGNATURES = {
     "prb_gemm_bf16_allgather": [P, P, P, P, I, I, I, L, L, I, I, F, I, I, I, P, I, P, P],
     "prb_flash_fwd_gather": [P, P, P, L, P, P, P, I, I, I, I, L, L, F, I, I, I, I, I, P, P, P],
     "prb_sparse_mla_fwd": [P, P, P, P, P, I, I, I, I, F, P, P],
+    "prb_gated_norm_fwd": [P, P, P, P, L, I, I, I, F, I, P],
+    "prb_gated_norm_bwd": [P, P, P, P, P, P, P, L, I, I, I, F, I, P],
     "prb_conv1d_fwd": [P, P, P, P, P, L, I, I, I, P],
     "prb_conv1d_bwd": [P, P, P, P, P, P, P, P, L, I, I, I, P],
     "prb_rs_pull": [P, L, L, F, P, I, P],

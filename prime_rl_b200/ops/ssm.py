@@ -165,10 +165,57 @@ def mamba2_scan_ref(x, dt, A, B, C, D, position_ids) -> torch.Tensor:
     return torch.stack(out)
 
 
+class _GatedNorm(torch.autograd.Function):
+    """``csrc/gated_norm.cu``: one warp per (row, group); dw summed in registers per warp."""
+
+    @staticmethod
+    def forward(ctx, x, gate, weight, eps, group, gate_first):
+        from . import _runtime as rt
+
+        rows, cols = x.shape
+        y = torch.empty_like(x)
+        rt.check(rt.lib().prb_gated_norm_fwd(x.data_ptr(), gate.data_ptr(), weight.data_ptr(), y.data_ptr(), rows, cols,
+                                             group, weight.numel(), float(eps), int(gate_first), rt.stream_ptr(x.device)),
+                 "prb_gated_norm_fwd")
+        ctx.save_for_backward(x, gate, weight)
+        ctx.cfg = (eps, group, gate_first)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import _runtime as rt
+
+        x, gate, weight = ctx.saved_tensors
+        eps, group, gate_first = ctx.cfg
+        rows, cols = x.shape
+        dy = dy.contiguous()
+        dx, dg = torch.empty_like(x), torch.empty_like(gate)
+        dw = torch.zeros(weight.numel(), dtype=torch.float32, device=x.device)
+        rt.check(rt.lib().prb_gated_norm_bwd(x.data_ptr(), gate.data_ptr(), weight.data_ptr(), dy.data_ptr(), dx.data_ptr(),
+                                             dg.data_ptr(), dw.data_ptr(), rows, cols, group, weight.numel(), float(eps),
+                                             int(gate_first), rt.stream_ptr(x.device)), "prb_gated_norm_bwd")
+        return dx, dg, dw.to(weight.dtype), None, None, None
+
+
 def gated_rms_norm(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, group_size: int,
                    gate_act: str = "silu", gate_first: bool = True) -> torch.Tensor:
     """RMSNorm over groups of ``group_size`` channels combined with a gate. ``gate_first``:
-    ``norm(x * act(gate)) * w`` (Mamba-2); otherwise ``norm(x) * w * act(gate)`` (gated delta-net)."""
+    ``norm(x * act(gate)) * w`` (Mamba-2); otherwise ``norm(x) * w * act(gate)`` (gated delta-net).
+    ``weight`` has one entry per channel of the last dim, or ``group_size`` entries shared by all groups."""
+    cols = x.shape[-1]
+    if (x.is_cuda and x.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and gate_act in ("silu", "swish") and group_size % 8 == 0 and group_size <= 1024
+            and weight.numel() in (cols, group_size) and weight.numel() % 8 == 0):
+        shp = x.shape
+        y = _GatedNorm.apply(x.reshape(-1, cols).contiguous(), gate.reshape(-1, cols).contiguous(), weight.contiguous(),
+                             eps, group_size, gate_first)
+        return y.reshape(shp)
+    return gated_rms_norm_ref(x, gate, weight, eps, group_size, gate_act, gate_first)
+
+
+def gated_rms_norm_ref(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, group_size: int,
+                       gate_act: str = "silu", gate_first: bool = True) -> torch.Tensor:
+    """PyTorch definition of ``gated_rms_norm`` (CPU path and oracle of the kernel)."""
     act = F.silu if gate_act in ("silu", "swish") else torch.sigmoid
     xf = x.float()
     if gate_first:

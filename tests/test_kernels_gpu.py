@@ -689,3 +689,25 @@ def test_causal_conv1d_kernel_forward_and_backward(C, K, act, with_bias):
     assert float((w.grad.float() - wf.grad).abs().max() / wf.grad.abs().max()) < 2e-2
     if with_bias:
         assert float((b.grad.float() - bf.grad).abs().max() / bf.grad.abs().max()) < 2e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,cols,group,shared_w,gate_first", [(77, 1024, 128, False, True), (200, 2048, 1024, False, True),
+                                                               (333, 128, 128, True, False), (50, 64, 64, True, False)])
+def test_gated_group_rmsnorm_kernel(rows, cols, group, shared_w, gate_first):
+    from prime_rl_b200.ops import ssm
+
+    torch.manual_seed(41)
+    dev = torch.device("cuda")
+    x = torch.randn(rows, cols, device=dev).bfloat16().requires_grad_()
+    g = torch.randn(rows, cols, device=dev).bfloat16().requires_grad_()
+    w = (1 + 0.2 * torch.randn(group if shared_w else cols, device=dev)).bfloat16().requires_grad_()
+    y = ssm.gated_rms_norm(x, g, w, 1e-5, group, "silu", gate_first)
+    xf, gf, wf = (t.detach().float().requires_grad_() for t in (x, g, w))
+    ref = ssm.gated_rms_norm_ref(xf, gf, wf, 1e-5, group, "silu", gate_first)
+    assert float((y.float() - ref).abs().max()) < 4e-2
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    ref.backward(dy.float())
+    for a, b in ((x.grad, xf.grad), (g.grad, gf.grad), (w.grad, wf.grad)):
+        assert float((a.float() - b).abs().max() / b.abs().max()) < 2e-2
