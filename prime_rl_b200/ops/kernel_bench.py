@@ -232,7 +232,26 @@ def bench_sparse_mla(timer, args, dev):
     rt.check_status()
 
 
-OPS = {"gemm": bench_gemm, "sparse_mla": bench_sparse_mla, "grouped": bench_grouped, "fp8": bench_fp8, "lm_head": bench_lm_head, "flash_fwd": bench_flash_fwd,
+def bench_mixers(timer, args, dev):
+    """Memory-bound helpers of the recurrent mixers (Nemotron-H 8B shapes)."""
+    from . import ssm
+
+    T, inner, ng, ns = args.tokens or 16384, 8192, 8, 128
+    C = inner + 2 * ng * ns
+    x = torch.randn(T, C, device=dev).bfloat16()
+    w = torch.randn(C, 4, device=dev).bfloat16()
+    b = torch.randn(C, device=dev).bfloat16()
+    pos = (torch.arange(T, device=dev) % 4096).to(torch.int32)
+    _report(f"causal conv1d fwd {T}x{C} k=4 + silu", timer(lambda: ssm.causal_conv1d(x, w, b, pos, "silu")),
+            bytes_=2 * T * C * 2)
+    h = torch.randn(T, inner, device=dev).bfloat16()
+    g = torch.randn(T, inner, device=dev).bfloat16()
+    nw = torch.ones(inner, device=dev).bfloat16()
+    _report(f"gated group rmsnorm fwd {T}x{inner} groups of {inner // ng}",
+            timer(lambda: ssm.gated_rms_norm(h, g, nw, 1e-5, inner // ng, "silu", True)), bytes_=3 * T * inner * 2)
+
+
+OPS = {"gemm": bench_gemm, "sparse_mla": bench_sparse_mla, "mixers": bench_mixers, "grouped": bench_grouped, "fp8": bench_fp8, "lm_head": bench_lm_head, "flash_fwd": bench_flash_fwd,
        "flash_bwd": bench_flash_bwd, "paged": bench_paged, "norm": bench_norm}
 
 
