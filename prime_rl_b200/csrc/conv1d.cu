@@ -1,7 +1,7 @@
 // Depthwise causal convolution over the tokens of a packed stream (Mamba-2 and gated delta-net
 // mixers): y[t, c] = act(bias[c] + sum_s w[c, K-1-s] * x[t-s, c]) where tap s only counts when token
 // t-s belongs to the same document (pos[t] >= s). x, y bf16 [T, C]; w bf16 [C, K] (K <= 4);
-// pos int32 [T]. One thread handles 8 channels of one token (16-byte loads); memory-bound.
+// pos int32 [T]. A thread handles 8 channels (16-byte loads) of several tokens with the taps in registers; memory-bound.
 //
 // Backward recomputes the pre-activation, then
 //   dx[t, c]     = sum_s w[c, K-1-s] * dpre[t+s, c]     (token t+s in the same document: pos[t+s] >= s)
@@ -53,23 +53,33 @@ __device__ __forceinline__ void conv_load_w(const __nv_bfloat16* w, const __nv_b
   }
 }
 
+// grid: (channel groups of 32 vectors, token blocks of kConvFwdTok); block: 32 x 8 threads (x = channel
+// vector, y = token lane). A thread keeps the taps of its 8 channels in registers and walks
+// kConvFwdTok / 8 tokens, so the weights are read once per 8 tokens instead of once per token.
+constexpr int kConvFwdTok = 64;
+
 __global__ void __launch_bounds__(256)
 conv1d_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                   const __nv_bfloat16* __restrict__ bias, const int* __restrict__ pos, __nv_bfloat16* __restrict__ y,
                   long long T, int C, int K, int silu) {
-  const int cv = C / 8;
-  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= T * cv) return;
-  const long long t = i / cv;
-  const int c0 = static_cast<int>(i - t * cv) * 8;
-  float wr[kConvMaxK][8], br[8], pre[8];
+  const int cvec = blockIdx.x * 32 + threadIdx.x;
+  if (cvec >= C / 8) return;
+  const int c0 = cvec * 8;
+  float wr[kConvMaxK][8], br[8];
   conv_load_w(w, bias, c0, K, wr, br);
-  conv_pre(x, wr, br, pos, t, c0, C, K, pre);
-  if (silu) {
+  const long long t_blk = static_cast<long long>(blockIdx.y) * kConvFwdTok;
+#pragma unroll 2
+  for (int it = 0; it < kConvFwdTok / 8; ++it) {
+    const long long t = t_blk + it * 8 + threadIdx.y;
+    if (t >= T) break;
+    float pre[8];
+    conv_pre(x, wr, br, pos, t, c0, C, K, pre);
+    if (silu) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) pre[j] = pre[j] / (1.f + __expf(-pre[j]));
+      for (int j = 0; j < 8; ++j) pre[j] = pre[j] / (1.f + __expf(-pre[j]));
+    }
+    conv_store8(y + t * C + c0, pre);
   }
-  conv_store8(y + t * C + c0, pre);
 }
 
 // grid: (C / 8 / 32 channel groups of 32 vectors, token blocks of kConvTok); block: 32 x 8 threads
@@ -155,8 +165,8 @@ PRB_API int prb_conv1d_fwd(const void* x, const void* w, const void* bias, const
                            int K, int silu, void* stream) {
   if (T <= 0) return 0;
   if (C % 8 || K < 1 || K > prb::kConvMaxK) return -3;
-  const long long n = T * (C / 8);
-  prb::conv1d_fwd_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  dim3 grid((C / 8 + 31) / 32, static_cast<unsigned>((T + prb::kConvFwdTok - 1) / prb::kConvFwdTok));
+  prb::conv1d_fwd_kernel<<<grid, dim3(32, 8), 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<const __nv_bfloat16*>(w),
       reinterpret_cast<const __nv_bfloat16*>(bias), pos, reinterpret_cast<__nv_bfloat16*>(y), T, C, K, silu);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;

@@ -24,9 +24,9 @@
 // which is why the output channels are split over two CTAs (each repeats Q K^T). Q (147 KB) and
 // one KV tile (74 KB) fill the shared memory of the SM, so there is no second tile: the stages of a
 // block run one after another (measured per block of 64 rows at 1.9 GHz: gather 1.4 k cycles,
-// Q K^T 2.4 k, softmax 1.4 k, P V 0.5 k), except that the five k-blocks of the tile that only Q K^T
-// reads are refilled for the next block while softmax and P V of the current one still run. Every
-// wait is bounded and reports through the status word.
+// Q K^T 2.4 k, softmax 1.4 k, P V 0.5 k). Refilling the five k-blocks that only Q K^T reads while
+// softmax and P V still run was tried and measured slower (6.13 ms against 5.91 ms at T = 4096).
+// Every wait is bounded and reports through the status word.
 //
 // Takes the place of the reference's TileLang kernel
 // (src/prime_rl/trainer/models/kernels/sparse_mla_fwd.py:23-186).
@@ -263,14 +263,10 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaParams p
     const uint8_t* kv_bytes = reinterpret_cast<const uint8_t*>(p.kv);
     int next_id = (g < kMlaBN) ? my_idx[g] : 0;    // threads 0..63 carry one row index of the coming block
     uint32_t dst[kPasses];
-    // k-blocks outside this CTA's value half are only read by Q K^T: they can be refilled as soon as
-    // S of the previous block is complete, while the softmax and P V of that block still run
-    uint32_t early = 0;
 #pragma unroll
     for (int pass = 0; pass < kPasses; ++pass) {
       const int seg = pass * kSegs + seg0, r = seg / kMlaKB, c = seg - r * kMlaKB;
       dst[pass] = kv_addr + c * 8192 + r * 128 + ((unit ^ (r & 7)) << 4);
-      if (c < half * 4 || c >= half * 4 + 4) early |= 1u << pass;
     }
     for (int j = 0; j < nblocks; ++j) {
       // everything that does not touch the KV tile happens before the wait for its release
@@ -290,20 +286,13 @@ sparse_mla_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const MlaParams p
         const int id = bidx[r];
         src[pass] = id >= 0 ? static_cast<uint32_t>(id) * (kMlaD / 8) + c * 8 + unit : 0xffffffffu;
       }
-      if (j > 0 && !mbar_wait_poll(s_full, (j - 1) & 1, p.status, kTimeoutTmemFull)) atomicExch(fail_flag, 1);
-#pragma unroll
-      for (int pass = 0; pass < kPasses; ++pass)
-        if ((early >> pass) & 1u)
-          cp_async_16(dst[pass], kv_bytes + (src[pass] != 0xffffffffu ? static_cast<size_t>(src[pass]) << 4 : 0),
-                      src[pass] != 0xffffffffu ? 16u : 0u);
       if (j > 0 && !mbar_wait_poll(kv_empty, (j - 1) & 1, p.status, kTimeoutEmptyBarrier)) atomicExch(fail_flag, 1);
       asm volatile("bar.sync 2, 192;" ::: "memory");
       if (*reinterpret_cast<volatile int*>(fail_flag) != 0) break;   // the same verdict for all gather threads
 #pragma unroll
       for (int pass = 0; pass < kPasses; ++pass)
-        if (!((early >> pass) & 1u))
-          cp_async_16(dst[pass], kv_bytes + (src[pass] != 0xffffffffu ? static_cast<size_t>(src[pass]) << 4 : 0),
-                      src[pass] != 0xffffffffu ? 16u : 0u);
+        cp_async_16(dst[pass], kv_bytes + (src[pass] != 0xffffffffu ? static_cast<size_t>(src[pass]) << 4 : 0),
+                    src[pass] != 0xffffffffu ? 16u : 0u);
       asm volatile("cp.async.commit_group;" ::: "memory");
       asm volatile("cp.async.wait_group 0;" ::: "memory");
       fence_async_smem();                           // generic-proxy writes -> visible to the tensor core
