@@ -65,12 +65,75 @@ def serve(config: InferenceConfig) -> None:
     uvicorn.run(app, host=config.server.host or "0.0.0.0", port=config.server.port, log_level="warning")
 
 
+def serve_replicas(config: InferenceConfig, argv: list[str]) -> int:
+    """Data-parallel serving on one node: ``data_parallel_size`` engine processes, one GPU each, on
+    the ports after ``server.port``, and the request router (``engine/router.py``) on ``server.port``
+    in this process. The children get the same command line plus their own port and a replica
+    count of one; the first child that dies takes the service down."""
+    import os
+    import subprocess
+    import sys
+    import time
+
+    import httpx
+    import uvicorn
+
+    from ..engine.router import Router, build_app
+    from ..utils.process import Supervisor
+
+    n, port = config.vllm.data_parallel_size, config.server.port
+    visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+    gpus = [g for g in visible.split(",") if g] if visible else [str(i) for i in range(n)]
+    if len(gpus) < n:
+        raise ValueError(f"data_parallel_size={n} but only {len(gpus)} GPUs are visible")
+    sup = Supervisor()
+    urls = []
+    for i in range(n):
+        env = dict(os.environ, CUDA_VISIBLE_DEVICES=gpus[i])
+        cmd = [sys.executable, "-m", "prime_rl_b200.entrypoints.inference", *argv, "--vllm.data-parallel-size", "1",
+               "--server.port", str(port + 1 + i), "--server.host", "127.0.0.1"]
+        sup.add(f"replica{i}", subprocess.Popen(cmd, env=env))
+        urls.append(f"http://127.0.0.1:{port + 1 + i}")
+    deadline = time.time() + 1800
+    for u in urls:                                  # the router answers /health only once every replica does
+        while True:
+            try:
+                if httpx.get(u + "/health", timeout=5).status_code == 200:
+                    break
+            except httpx.HTTPError:
+                pass
+            if not sup.errors.empty() or time.time() > deadline:
+                sup.shutdown()
+                raise RuntimeError("an engine replica did not come up")
+            time.sleep(1.0)
+    server = uvicorn.Server(uvicorn.Config(build_app(Router(urls)), host=config.server.host or "0.0.0.0", port=port,
+                                           log_level="warning"))
+    import threading
+
+    def watch():
+        sup.errors.get()                            # blocks until a replica exits with an error
+        server.should_exit = True
+
+    threading.Thread(target=watch, daemon=True).start()
+    try:
+        server.run()
+    finally:
+        sup.shutdown()
+    return 0
+
+
 def main(argv: list[str] | None = None) -> None:
-    config = cli(InferenceConfig, argv)
+    import sys
+
+    args = list(sys.argv[1:] if argv is None else argv)
+    config = cli(InferenceConfig, args)
     if config.dry_run:
         print(config.to_json())
         return
     setup_logger(config.log.level, tag="inference", json_logging=config.log.json_logging)
+    if config.vllm.data_parallel_size > 1:
+        serve_replicas(config, args)
+        return
     serve(config)
 
 

@@ -1,7 +1,7 @@
 """Multi-GPU check of the sharded optimizer with peer-memory collectives against the NCCL ones:
 two full-parameter RL trainer steps on a tiny dense model with ``model.optim_collectives = "p2p"``
 and ``"nccl"``, same seeds; losses, gradient norms and the updated parameters must agree. Then the
-two kernels are timed on a 2 Gi-element... (1 GiB fp32) gradient buffer against
+two kernels are timed on 1 GiB of fp32 gradients / 512 MiB of bf16 parameters against
 ``reduce_scatter_tensor`` / ``all_gather_into_tensor``.
 
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m prime_rl_b200.parallel.p2p_zero_selftest

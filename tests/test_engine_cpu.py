@@ -1,3 +1,5 @@
+import json
+
 import torch
 
 from prime_rl_b200.engine.engine import Engine
@@ -86,3 +88,56 @@ def test_pause_blocks_progress_and_resume_continues():
         time.sleep(0.01)
     assert req.finish_reason == "length"
     eng.shutdown()
+
+
+def test_router_places_sessions_and_fans_out_admin_calls():
+    """Two CPU engines behind the router: a session always meets the same replica, free requests
+    spread, admin calls reach both, metrics are summed."""
+    import asyncio
+
+    import httpx
+
+    from prime_rl_b200.engine.engine import Engine
+    from prime_rl_b200.engine.router import HashRing, Router, build_app as build_router, merge_metrics
+    from prime_rl_b200.engine.server import build_app
+    from prime_rl_b200.models import build_model, resolve_arch
+
+    arch = resolve_arch("tiny-qwen3")
+    engines = [Engine(build_model(arch, device="cpu", dtype=torch.float32, seed=3), num_pages=128).start() for _ in range(2)]
+    apps = [build_app(e, "tiny-qwen3") for e in engines]
+    router = Router(["http://r0", "http://r1"], transports=[httpx.ASGITransport(app=a) for a in apps])
+    app = build_router(router)
+
+    async def go():
+        async with httpx.AsyncClient(transport=httpx.ASGITransport(app=app), base_url="http://router") as c:
+            assert (await c.get("/health")).json()["replicas"] == 2
+            body = {"token_ids": [1, 2, 3, 4], "sampling_params": {"max_tokens": 3, "temperature": 0.0}}
+            outs = [await c.post("/inference/v1/generate", json=dict(body, cache_salt="conversation-7")) for _ in range(4)]
+            assert all(o.status_code == 200 for o in outs)
+            served_after_session = list(router.served)
+            assert sorted(served_after_session) == [0, 4]                     # one replica took the whole session
+            outs = await asyncio.gather(*[c.post("/inference/v1/generate", json=body) for _ in range(6)])
+            assert all(o.status_code == 200 for o in outs)
+            assert min(router.served) >= 2                                    # the free requests were spread
+            texts = {json.dumps(o.json().get("choices", o.json())[0] if "choices" in o.json() else o.json(), sort_keys=True)
+                     for o in outs}
+            assert len(texts) >= 1
+            r = await c.post("/pause")
+            assert r.status_code == 200 and r.json()["replicas"] == 2
+            assert all(e.paused for e in engines)
+            assert (await c.post("/resume")).status_code == 200 and not any(e.paused for e in engines)
+            m = (await c.get("/metrics")).text
+            assert "vllm:num_requests_running" in m or "num_requests" in m
+            st = (await c.get("/router/state")).json()
+            assert st["inflight"] == [0, 0] and sum(st["served"]) == 10
+
+    try:
+        asyncio.run(go())
+    finally:
+        for e in engines:
+            e.shutdown()
+    ring = HashRing([0, 1, 2])
+    assert {ring.node(f"k{i}") for i in range(200)} == {0, 1, 2}
+    moved = sum(HashRing([0, 1]).node(f"k{i}") != ring.node(f"k{i}") for i in range(200) if ring.node(f"k{i}") != 2)
+    assert moved == 0                                                         # only the removed node's keys move
+    assert merge_metrics(["# HELP a x\na 1\nb{l=\"1\"} 2\n", "# HELP a x\na 3\n"]) == "# HELP a x\na 4.0\nb{l=\"1\"} 2.0\n"
