@@ -448,6 +448,113 @@ ep_pull_kernel(EpPeers src, const int* __restrict__ topk_idx, const int* __restr
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Tensor-parallel decode: all-reduce + residual add + RMSNorm in one kernel.
+//
+// Every rank has written its partial sums (bf16 [rows, cols]) into its own symmetric buffer with the
+// GEMM that precedes this kernel on the stream. The kernel then
+//   1. tells every peer "my partial of call e is complete" (CTA 0: release store into the peer's
+//      flag slot [rank]) and waits, with a bound, until all peers have said the same,
+//   2. reads the R partials of its rows with plain peer loads (always in rank order, so that all
+//      ranks get bit-identical sums), adds the residual stream and writes the new residual,
+//   3. normalises the row (RMSNorm with the weight of the NEXT norm layer) and writes that too.
+// The call number e lives in device memory (state[0], advanced by the last CTA), so a CUDA graph can
+// replay the launch with unchanged arguments. The caller alternates between two partial buffers:
+// a rank only reaches the barrier of call e + 1 after its reads of call e have finished, so a
+// buffer is never overwritten (by the GEMM of call e + 2) while a peer still reads it.
+//
+// Same role as the custom all-reduce + fused add-RMSNorm passes of the serving engine the reference
+// drives (vLLM tensor parallelism, packages/prime-rl-configs/src/prime_rl/configs/inference.py:88-97).
+constexpr int kArThreads = 256;
+constexpr int kArMaxVec = 4;            // 16-byte vectors per thread: cols <= 4 * 256 * 8 = 8192
+
+__global__ void __launch_bounds__(kArThreads)
+ar_add_rmsnorm_kernel(EpPeers partial, EpPeers flags, int* __restrict__ state, const __nv_bfloat16* __restrict__ residual,
+                      const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out_h,
+                      __nv_bfloat16* __restrict__ out_x, int rows, int cols, float eps, int rank, int R, int* status) {
+  const int e = *reinterpret_cast<volatile int*>(state) + 1;
+  if (blockIdx.x == 0) {
+    __threadfence_system();
+    if (threadIdx.x < R) {
+      volatile int* f = reinterpret_cast<int*>(flags.buf[threadIdx.x]) + rank;
+      *f = e;
+    }
+  }
+  const bool ok = ep_wait_all(reinterpret_cast<const int*>(flags.buf[rank]), R, e, status);
+  __shared__ float s_part[kArThreads / 32];
+  const int nvec = cols / 8;
+  if (ok) {
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+      const long long base = static_cast<long long>(row) * cols;
+      float acc[kArMaxVec][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < kArMaxVec; ++i) {
+        const int v = threadIdx.x + i * kArThreads;
+        if (v >= nvec) break;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+        for (int r = 0; r < R; ++r) {
+          const uint4 u = __ldcv(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(partial.buf[r]) + base) + v);
+          const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+          acc[i][0] += a.x; acc[i][1] += a.y; acc[i][2] += b.x; acc[i][3] += b.y;
+          acc[i][4] += c.x; acc[i][5] += c.y; acc[i][6] += d.x; acc[i][7] += d.y;
+        }
+        if (residual != nullptr) {
+          const uint4 u = *(reinterpret_cast<const uint4*>(residual + base) + v);
+          const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+          acc[i][0] += a.x; acc[i][1] += a.y; acc[i][2] += b.x; acc[i][3] += b.y;
+          acc[i][4] += c.x; acc[i][5] += c.y; acc[i][6] += d.x; acc[i][7] += d.y;
+        }
+        // the residual stream is stored in bf16: normalise what the next layer will read
+        uint4 o;
+        o.x = pack_bf16(acc[i][0], acc[i][1]); o.y = pack_bf16(acc[i][2], acc[i][3]);
+        o.z = pack_bf16(acc[i][4], acc[i][5]); o.w = pack_bf16(acc[i][6], acc[i][7]);
+        *(reinterpret_cast<uint4*>(out_h + base) + v) = o;
+        const float2 a = unpack_bf16(o.x), b = unpack_bf16(o.y), c = unpack_bf16(o.z), d = unpack_bf16(o.w);
+        acc[i][0] = a.x; acc[i][1] = a.y; acc[i][2] = b.x; acc[i][3] = b.y;
+        acc[i][4] = c.x; acc[i][5] = c.y; acc[i][6] = d.x; acc[i][7] = d.y;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss = fmaf(acc[i][j], acc[i][j], ss);
+      }
+      if (out_x != nullptr) {
+        ss = warp_sum(ss);
+        if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int k = 0; k < kArThreads / 32; ++k) tot += s_part[k];
+        __syncthreads();
+        const float rstd = rsqrtf(tot / static_cast<float>(cols) + eps);
+#pragma unroll
+        for (int i = 0; i < kArMaxVec; ++i) {
+          const int v = threadIdx.x + i * kArThreads;
+          if (v >= nvec) break;
+          const uint4 wu = *(reinterpret_cast<const uint4*>(w) + v);
+          const float2 a = unpack_bf16(wu.x), b = unpack_bf16(wu.y), c = unpack_bf16(wu.z), d = unpack_bf16(wu.w);
+          uint4 o;
+          o.x = pack_bf16(acc[i][0] * rstd * a.x, acc[i][1] * rstd * a.y);
+          o.y = pack_bf16(acc[i][2] * rstd * b.x, acc[i][3] * rstd * b.y);
+          o.z = pack_bf16(acc[i][4] * rstd * c.x, acc[i][5] * rstd * c.y);
+          o.w = pack_bf16(acc[i][6] * rstd * d.x, acc[i][7] * rstd * d.y);
+          *(reinterpret_cast<uint4*>(out_x + base) + v) = o;
+        }
+      }
+    }
+  }
+  // the last CTA to finish advances the call number for the next launch
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(state + 1, 1);
+    if (prev == static_cast<int>(gridDim.x) - 1) {
+      state[1] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile int*>(state) = e;
+    }
+  }
+}
+
 }  // namespace prb
 
 // ---------------------------------------------------------------- symmetric memory (CUDA IPC)
@@ -620,5 +727,22 @@ PRB_API int prb_ep_pull(void* const* src_peers, const int* topk_idx, const int* 
   prb::ep_pull_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       ep_peers(src_peers, R), topk_idx, pos, w, reinterpret_cast<const __nv_bfloat16*>(g),
       reinterpret_cast<__nv_bfloat16*>(out), dw, flags + kind * R, T, k, H, E / R, R, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// partial_peers: every rank's partial buffer for THIS call (bf16 [rows, cols]); flag_peers: int32 [R] on every
+// rank; state: int32 [2] local (call number, CTA counter), zero before the first call. residual / w / out_x may
+// be null (no residual add / no norm output). out_h gets the reduced (+ residual) rows.
+PRB_API int prb_ar_add_rmsnorm(void* const* partial_peers, void* const* flag_peers, int* state, const void* residual,
+                               const void* w, void* out_h, void* out_x, int rows, int cols, float eps, int rank, int R,
+                               int* status, void* stream) {
+  if (R > prb::kEpMaxRanks || R < 1 || cols % 8 || cols > prb::kArMaxVec * prb::kArThreads * 8) return -2;
+  if (out_x != nullptr && w == nullptr) return -2;
+  if (rows <= 0) return 0;
+  const int grid = rows < 148 * 4 ? rows : 148 * 4;
+  prb::ar_add_rmsnorm_kernel<<<grid, prb::kArThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      ep_peers(partial_peers, R), ep_peers(flag_peers, R), state, reinterpret_cast<const __nv_bfloat16*>(residual),
+      reinterpret_cast<const __nv_bfloat16*>(w), reinterpret_cast<__nv_bfloat16*>(out_h),
+      reinterpret_cast<__nv_bfloat16*>(out_x), rows, cols, eps, rank, R, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

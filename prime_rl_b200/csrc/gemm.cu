@@ -713,8 +713,12 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
   // slab of expert e also covers the first rows of expert e+1, but the matching columns of
   // A lie past K and are zero-filled by TMA, so they contribute nothing (B must be finite).
   int bn = force_bn > 0 ? force_bn : (N > 128 ? 256 : (N > 64 ? 128 : 64));
-  // prefer 128-wide tiles when 256 would leave most SMs idle
-  if (force_bn <= 0 && bn == 256) {
+  // narrower tiles while the wide ones would leave SMs idle (decode-sized M): a 128 x 64 tile keeps the
+  // tensor pipe half as busy per CTA, but an idle SM does nothing at all
+  if (force_bn <= 0 && !grouped) {
+    const long long tiles_m = (M + 127) / 128;
+    while (bn > 64 && tiles_m * ((N + bn - 1) / bn) < sm_count()) bn /= 2;
+  } else if (force_bn <= 0 && bn == 256) {
     const long long t256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
     if (t256 < sm_count() && N % 256 != 0) bn = 128;
   }

@@ -52,19 +52,32 @@ class Request:
 class Engine:
     def __init__(self, model, *, num_pages: int = 4096, page_size: int = 16, max_running: int = 256,
                  max_prefill_tokens: int = 16384, eos_token_id: int | None = None, enable_prefix_cache: bool = True,
-                 use_cuda_graphs: bool = False, max_model_len: int = 8192, weight_dtype: str = "bf16"):
+                 use_cuda_graphs: bool = False, max_model_len: int = 8192, weight_dtype: str = "bf16", tp=None):
         arch = model.arch
         self.model = model.eval()
         self.weight_dtype = weight_dtype
+        # tensor parallelism (engine/tp.py): this process holds one shard and steps in lockstep with its peers
+        self.tp = tp
+        self.tp_size = tp.size if tp is not None else 1
+        self._inbox: list[Request] = []
+        self._commands: list[tuple] = []
+        if tp is not None and tp.size > 1:
+            from .tp import shard_model_
+
+            if getattr(model, "tp_size", 1) != tp.size:
+                shard_model_(self.model, tp.rank, tp.size)
+            if tp.max_tokens < max(max_prefill_tokens, max_model_len):
+                raise ValueError("the tensor-parallel buffers are smaller than the largest step the engine may run")
         if weight_dtype == "fp8":
             from ..models.model import quantize_fp8_
 
             quantize_fp8_(self.model)
         p = next(model.parameters())
         self.device = p.device
-        self.cache = KVCache(arch.num_hidden_layers, num_pages, page_size, arch.num_key_value_heads, arch.head_dim,
-                             p.dtype, p.device)
-        self.runner = ModelRunner(model, self.cache, use_cuda_graphs=use_cuda_graphs, max_model_len=max_model_len)
+        self.cache = KVCache(arch.num_hidden_layers, num_pages, page_size, arch.num_key_value_heads // self.tp_size,
+                             arch.head_dim, p.dtype, p.device)
+        self.runner = ModelRunner(model, self.cache, use_cuda_graphs=use_cuda_graphs, max_model_len=max_model_len,
+                                  tp=tp if self.tp_size > 1 else None)
         self.max_running, self.max_prefill_tokens = max_running, max_prefill_tokens
         self.eos, self.enable_prefix_cache = eos_token_id, enable_prefix_cache
         self.waiting: list[Request] = []
@@ -94,6 +107,10 @@ class Engine:
             self.wake.notify_all()
         if self.thread is not None:
             self.thread.join(timeout=10)
+        if self.tp_size > 1 and self.tp.rank == 0:          # release the other ranks from their follow() loops
+            with self.lock:
+                self._commands.append(("stop",))
+            self._tp_sync()
 
     def pause(self, timeout: float = 60.0) -> None:
         """Returns once the step loop is parked (no kernel of a step in flight)."""
@@ -117,10 +134,45 @@ class Engine:
         if req.params.seed is not None:
             req.generator = torch.Generator(device=self.device).manual_seed(req.params.seed)
         with self.wake:
-            self.waiting.append(req)
+            # with tensor parallelism a request enters the queue when rank 0 announces it to all ranks
+            (self._inbox if self.tp_size > 1 else self.waiting).append(req)
             self.stats["requests"] += 1
             self.wake.notify_all()
         return req
+
+    # ------------------------------------------------------------------ tensor-parallel lockstep
+    def _tp_sync(self) -> bool:
+        """Rank 0 announces the requests and admin commands that arrived since the last step; every rank
+        queues / runs them in the same order. Returns False once a stop command came through."""
+        tp = self.tp
+        msg = None
+        if tp.rank == 0:
+            with self.lock:
+                new, self._inbox = self._inbox, []
+                cmds, self._commands = self._commands, []
+            msg = {"new": [(r.prompt, r.params, r.cache_salt) for r in new], "cmds": cmds}
+        msg = tp.broadcast_control(msg)
+        if tp.rank != 0:
+            new = [Request(prompt=list(p), params=params, cache_salt=salt) for p, params, salt in msg["new"]]
+            for r in new:
+                if r.params.seed is not None:
+                    r.generator = torch.Generator(device=self.device).manual_seed(r.params.seed)
+        with self.lock:
+            self.waiting.extend(new)
+        alive = True
+        for cmd in msg["cmds"]:
+            if cmd[0] == "update_weights":
+                self._update_weights_local(cmd[1])
+            elif cmd[0] == "stop":
+                alive = False
+        return alive
+
+    def follow(self) -> None:
+        """Step loop of the ranks other than 0: wait for rank 0's announcement, then take the same step."""
+        assert self.tp is not None and self.tp.rank != 0
+        while self._tp_sync():
+            if self.waiting or self.running:
+                self._step_local()
 
     async def generate(self, prompt: list[int], params: SamplingParams, cache_salt: str = "") -> Request:
         loop = asyncio.get_running_loop()
@@ -144,7 +196,8 @@ class Engine:
     def _loop(self) -> None:
         while True:
             with self.wake:
-                while not self.stop_flag and (self.paused or (not self.waiting and not self.running)):
+                while not self.stop_flag and (self.paused or not (self.waiting or self.running or self._inbox
+                                                                  or self._commands)):
                     if self.paused:
                         self.idle_paused.set()
                     self.wake.wait(timeout=0.5)
@@ -200,6 +253,14 @@ class Engine:
         return True
 
     def step(self) -> None:
+        if self.tp_size > 1:
+            if not self._tp_sync():
+                return
+            if not (self.waiting or self.running):
+                return
+        self._step_local()
+
+    def _step_local(self) -> None:
         self.stats["steps"] += 1
         self.last_step_time = time.monotonic()
         new = self._admit()
@@ -277,7 +338,10 @@ class Engine:
         top_p = torch.tensor([r.params.top_p for r in reqs], dtype=torch.float32, device=dev)
         want_mask = any(r.params.return_sampling_mask and r.params.truncated for r in reqs)
         gen = reqs[0].generator if len(reqs) == 1 else None
-        tok, lp, masks = sample(logits, temp, top_k, top_p, generator=gen, want_mask=want_mask)
+        tok, lp, masks = sample(logits, temp, top_k, top_p, generator=gen, want_mask=want_mask,
+                                truncated=any(r.params.truncated for r in reqs))
+        if self.tp_size > 1:                       # every rank appends rank 0's draw
+            tok, lp = self.tp.broadcast_sample(tok, lp)
         tok_l, lp_l = tok.tolist(), lp.tolist()
         self.stats["generation_tokens"] += len(reqs)
         for i, r in enumerate(reqs):
@@ -301,6 +365,20 @@ class Engine:
         from ..trainer.weights import load_hf_checkpoint
 
         assert self.paused or self.thread is None, "update_weights requires a paused engine"
+        if self.tp_size > 1:
+            # the step loop is parked, so this thread owns the control channel: all ranks load their shards
+            assert self.tp.rank == 0, "weight updates enter through rank 0"
+            with self.lock:
+                self._commands.append(("update_weights", str(weight_dir)))
+            self._tp_sync()
+            return
+        self._update_weights_local(weight_dir)
+
+    def _update_weights_local(self, weight_dir: str) -> None:
+        from pathlib import Path
+
+        from ..trainer.weights import load_hf_checkpoint
+
         load_hf_checkpoint(self.model, Path(weight_dir), strict=False)
         if self.weight_dtype == "fp8":
             from ..models.model import quantize_fp8_

@@ -31,8 +31,9 @@ class StepInput:
 
 class ModelRunner:
     def __init__(self, model, cache: KVCache, fp32_lm_head: bool = True, use_cuda_graphs: bool = False,
-                 max_model_len: int = 8192):
+                 max_model_len: int = 8192, tp=None):
         self.model, self.cache, self.arch = model, cache, model.arch
+        self.tp = tp                                    # engine/tp.py TPContext: sharded weights, fused reduces
         self.device = next(model.parameters()).device
         self.fp32_lm_head = fp32_lm_head
         self.capture_routed = False
@@ -91,35 +92,45 @@ class ModelRunner:
         """ids / positions / cache slots of the N new tokens -> fp32 logits of ``rows_t``. Everything
         here is device work with static shapes for a given N, so a pure decode step can be captured
         in a CUDA graph (``batch`` / ``starts`` are only used by the non-paged attention paths)."""
-        model, cache = self.model, self.cache
+        model, cache, tp = self.model, self.cache, self.tp
         seq = SeqInfo(None, 0, pos_t)
         h = model.model.embed_tokens(ids_t)
         N = h.shape[0]
         routed = []
-        for li, layer in enumerate(model.model.layers):
+        layers = model.model.layers
+        if tp is not None:
+            assert tp.calls % 2 == 0, "every forward makes an even number of tensor-parallel reduces"
+        x = None
+        for li, layer in enumerate(layers):
             at = layer.self_attn
-            x = layer.input_layernorm(h)
+            if tp is None or li == 0:                   # with TP the previous layer's reduce already normalised
+                x = layer.input_layernorm(h)
             qkv = at.qkv_proj(x)
-            qd, kd = at.nq * at.D, at.nkv * at.D
-            q = qkv[:, :qd].view(N, at.nq, at.D)
-            k = qkv[:, qd:qd + kd].view(N, at.nkv, at.D)
-            v = qkv[:, qd + kd:].view(N, at.nkv, at.D)
             eps = self.arch.rms_norm_eps
-            q = ops.qknorm_rope(q, at.q_norm.weight if at.q_norm is not None else None, pos_t, at.inv_freq, eps)
-            k = ops.qknorm_rope(k, at.k_norm.weight if at.k_norm is not None else None, pos_t, at.inv_freq, eps)
+            # one kernel: split, q / k RMSNorm, rotary, contiguous q, k, v
+            q, k, v = ops.qkv_norm_rope(qkv, at.q_norm.weight if at.q_norm is not None else None,
+                                        at.k_norm.weight if at.k_norm is not None else None, pos_t, at.inv_freq, eps,
+                                        at.nq, at.nkv, at.D)
             cache.write(li, k, v, slots_t)
             o = self._attend(li, q, k, v.contiguous(), batch, starts, at.window, at.sinks)
             a = at.finish(o, x)
-            x2, h = ops.add_rms_norm(a, h, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.eps)
+            if tp is None:
+                x2, h = ops.add_rms_norm(a, h, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.eps)
+            else:                                       # sum over ranks + residual + norm in one kernel
+                x2, h = tp.reduce(a, h, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.eps)
             if layer.is_moe:
                 m = layer.mlp(x2, seq)
                 if self.capture_routed and isinstance(layer.mlp, MoE) and layer.mlp.last_topk is not None:
                     routed.append(layer.mlp.last_topk)
             else:
                 m = layer.mlp(x2)
-            h = h + m
+            if tp is None:
+                h = h + m
+            else:
+                nxt = layers[li + 1].input_layernorm if li + 1 < len(layers) else model.model.norm
+                x, h = tp.reduce(m, h, nxt.weight, nxt.eps)
         routed_t = torch.stack(routed, dim=1) if routed else None
-        h = model.model.norm(h)
+        h = model.model.norm(h) if tp is None else x
         sel = h[rows_t]
         w = model.output_weight
         if sel.is_cuda and sel.dtype == torch.bfloat16:

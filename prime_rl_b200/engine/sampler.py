@@ -42,15 +42,48 @@ class SamplingParams:
         return self.top_p < 1.0 or self.top_k > 0
 
 
-def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
-           generator: torch.Generator | None = None, want_mask: bool = False):
-    """logits fp32 [B, V]; temperature/top_p fp32 [B]; top_k int [B] (<= 0 = off).
-    Returns (tokens [B], logprobs [B], mask_ids list[Tensor] | None). Temperature 0 = greedy."""
+def _draw_seed(generator: torch.Generator | None) -> int:
+    """63-bit seed for the counter-based generator of the sampling kernel, drawn on the host: from the
+    request's generator when it has one (so that a seeded request replays), else from the global CPU one."""
+    if generator is not None and generator.device.type != "cpu":
+        # advance the device generator's host-side state without launching anything
+        offset = generator.get_offset()
+        generator.set_offset(offset + 4)
+        return (generator.initial_seed() ^ ((offset + 1) * 0x9E3779B97F4A7C15)) & ((1 << 63) - 1)
+    return int(torch.empty((), dtype=torch.int64).random_(generator=generator)) & ((1 << 63) - 1)
+
+
+def sample_untruncated(logits: torch.Tensor, temperature: torch.Tensor, generator: torch.Generator | None = None):
+    """Temperature-only sampling in ONE kernel pass over fp32 logits [B, V] (Gumbel-max with a counter-based
+    generator, online log-softmax for the sampled token's log-probability). Returns (tokens int64, logprobs)."""
+    from ..ops import _runtime as rt
+
     B, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        logits = logits.float().contiguous()
+    tok = torch.empty(B, dtype=torch.int32, device=logits.device)
+    lp = torch.empty(B, dtype=torch.float32, device=logits.device)
+    rt.check(rt.lib().prb_sample_gumbel(logits.data_ptr(), temperature.data_ptr(), logits.stride(0), _draw_seed(generator),
+                                        tok.data_ptr(), lp.data_ptr(), B, V, rt.stream_ptr(logits.device)),
+             "prb_sample_gumbel")
+    return tok.long(), lp
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           generator: torch.Generator | None = None, want_mask: bool = False, truncated: bool | None = None):
+    """logits fp32 [B, V]; temperature/top_p fp32 [B]; top_k int [B] (<= 0 = off).
+    Returns (tokens [B], logprobs [B], mask_ids list[Tensor] | None). Temperature 0 = greedy.
+    ``truncated`` says whether any row uses top-k / top-p when the caller knows it on the host
+    (saves a device round trip); None = look at the tensors."""
+    B, V = logits.shape
+    if truncated is None:
+        truncated = bool(((top_k > 0) | (top_p < 1.0)).any())
+    if not truncated and logits.is_cuda:
+        tok, lp = sample_untruncated(logits, temperature.float().contiguous(), generator)
+        return tok, lp, None
     greedy = temperature <= 0
     t = torch.where(greedy, torch.ones_like(temperature), temperature)
     z = logits.float() / t[:, None]
-    truncated = bool(((top_k > 0) | (top_p < 1.0)).any())
     mask_ids = None
     if truncated:
         srt, idx = torch.sort(z, dim=-1, descending=True)

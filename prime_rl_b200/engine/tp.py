@@ -1,0 +1,315 @@
+"""Tensor parallelism for the rollout engine: one process per GPU, all ranks run the same
+scheduler in lockstep over the same request stream, the decoder's weights are split.
+
+What is split (``shard_tensor``):
+  attention   heads: rank r owns q heads [r nq/R, (r+1) nq/R) and their kv heads; ``o_proj`` by columns
+  dense MLP   the intermediate width: gate / up rows and ``down_proj`` columns
+  experts     the intermediate width of EVERY expert (all ranks route all tokens to all experts and
+              read 1/R of each expert's weights: decode is bound by that read)
+Embedding, router, norms and the LM head are replicated. Each decoder layer therefore ends in two
+sums over ranks (after ``o_proj`` and after the MLP); ``TPContext.reduce`` does each of them in ONE kernel
+over peer memory together with the residual add and the next RMSNorm (csrc/ep_p2p.cu,
+``ar_add_rmsnorm_kernel``), with a device-side call counter so that CUDA graphs can replay it.
+
+The reference gets tensor parallelism from the serving engine it drives (``tensor_parallel_size`` in
+packages/prime-rl-configs/src/prime_rl/configs/inference.py:88-97, NCCL / custom all-reduce plus
+separate add-norm kernels inside vLLM).
+
+Control plane: rank 0 owns the HTTP server; before every step it broadcasts the requests that
+arrived (and admin commands) to the other ranks over a gloo group, so every rank admits, preempts
+and finishes the same requests in the same order. Rank 0 samples; the tokens are broadcast.
+"""
+
+from __future__ import annotations
+
+import re
+
+import torch
+import torch.distributed as dist
+
+_LAYER = re.compile(r"(?:^|\.)layers\.(\d+)\.")
+
+
+def _rows(t: torch.Tensor, sections: list[int], rank: int, size: int) -> torch.Tensor:
+    """Slice ``rank`` of every section along dim -2 (matrices) or -1 (vectors), sections stacked."""
+    dim = t.dim() - 2 if t.dim() >= 2 else 0
+    out, start = [], 0
+    for n in sections:
+        if n % size:
+            raise ValueError(f"a section of {n} rows cannot be split over {size} ranks")
+        per = n // size
+        out.append(t.narrow(dim, start + rank * per, per))
+        start += n
+    assert start == t.shape[dim], (start, tuple(t.shape))
+    return torch.cat(out, dim) if len(out) > 1 else out[0]
+
+
+def _cols(t: torch.Tensor, rank: int, size: int) -> torch.Tensor:
+    n = t.shape[-1]
+    if n % size:
+        raise ValueError(f"{n} columns cannot be split over {size} ranks")
+    return t.narrow(-1, rank * (n // size), n // size)
+
+
+def shard_tensor(name: str, t: torch.Tensor, arch, rank: int, size: int) -> torch.Tensor:
+    """The part of native-layout tensor ``name`` that TP rank ``rank`` of ``size`` keeps (a view or a
+    new tensor; replicated tensors are returned as they are)."""
+    if size == 1:
+        return t
+    m = _LAYER.search(name)
+    if m is None:
+        return t
+    li = int(m.group(1))
+    D = arch.head_dim
+    nq, nkv = arch.layer_heads(li), arch.num_key_value_heads
+    single = arch.hidden_act == "relu2"                       # no up half
+    if ".self_attn." in name:
+        if "qkv_proj." in name:
+            return _rows(t, [nq * D, nkv * D, nkv * D], rank, size)
+        if name.endswith("o_proj.weight"):
+            return _cols(t, rank, size)
+        if name.endswith("o_proj.bias"):
+            return t if rank == 0 else torch.zeros_like(t)
+        if "g_proj." in name:
+            return _rows(t, [t.shape[0]], rank, size)
+        if name.endswith(".sinks"):
+            return _rows(t, [nq], rank, size)
+        return t
+    if name.endswith("experts.gate_up_proj"):
+        I = t.shape[-2] if single else t.shape[-2] // 2
+        return _rows(t, [I] if single else [I, I], rank, size)
+    if name.endswith("experts.down_proj"):
+        return _cols(t, rank, size)
+    if "gate_up_proj." in name:                               # dense MLP and shared experts
+        I = t.shape[0] if single else t.shape[0] // 2
+        return _rows(t, [I] if single else [I, I], rank, size)
+    if name.endswith("down_proj.weight"):
+        return _cols(t, rank, size)
+    if name.endswith("down_proj.bias"):
+        return t if rank == 0 else torch.zeros_like(t)
+    return t
+
+
+def shard_model_(model, rank: int, size: int) -> None:
+    """Replaces the parameters of ``model`` by this rank's shards (in place) and leaves a
+    ``model.tp_shard(name, tensor)`` hook that later weight loads go through."""
+    from ..models.layers import Attention, DecoderLayer
+
+    arch = model.arch
+    if size == 1:
+        return
+    if arch.num_key_value_heads % size or any(arch.layer_heads(i) % size for i in range(arch.num_hidden_layers)):
+        raise ValueError(f"{arch.num_key_value_heads} kv heads cannot be split over {size} ranks")
+    for layer in model.model.layers:
+        if not isinstance(layer, DecoderLayer) or not isinstance(layer.self_attn, Attention):
+            raise NotImplementedError("engine tensor parallelism covers the attention + MLP/MoE decoder families")
+    with torch.no_grad():
+        for name, p in list(model.named_parameters()):
+            if "lora_" in name:
+                raise NotImplementedError("merge or drop LoRA adapters before sharding the engine's model")
+            new = shard_tensor(name, p.data, arch, rank, size)
+            if new is not p.data:
+                p.data = new.contiguous()
+    for layer in model.model.layers:
+        at = layer.self_attn
+        at.nq, at.nkv = at.nq // size, at.nkv // size
+    model.tp_shard = lambda name, t: shard_tensor(name, t, arch, rank, size)
+    model.tp_size, model.tp_rank = size, rank
+
+
+class TPContext:
+    """Symmetric partial-sum buffers + flags of one TP group and the fused reduce kernel."""
+
+    def __init__(self, group, device: torch.device, hidden: int, max_tokens: int, control_group=None):
+        from ..ops import _runtime as rt
+        from ..parallel.symm import SymmetricBuffer
+
+        self.group, self.device, self.hidden = group, device, hidden
+        self.control = control_group
+        self.rank, self.size = dist.get_rank(group), dist.get_world_size(group)
+        self.max_tokens = max_tokens
+        self.buf_bytes = (max_tokens * hidden * 2 + 255) // 256 * 256
+        self.symm = SymmetricBuffer(group, 2 * self.buf_bytes + 256, device)
+        self.buf_ptrs = [self.symm.offset_ptrs(0), self.symm.offset_ptrs(self.buf_bytes)]
+        self.flag_ptrs = self.symm.offset_ptrs(2 * self.buf_bytes)
+        self.bufs = [self.symm.local(torch.bfloat16, 0, max_tokens * hidden).view(max_tokens, hidden),
+                     self.symm.local(torch.bfloat16, self.buf_bytes, max_tokens * hidden).view(max_tokens, hidden)]
+        self.state = torch.zeros(2, dtype=torch.int32, device=device)
+        self.calls = 0
+        self._rt = rt
+
+    def reduce(self, partial: torch.Tensor, residual: torch.Tensor | None, weight: torch.Tensor | None, eps: float):
+        """``partial`` [rows, hidden] bf16 of this rank -> (rmsnorm(sum + residual) * weight, sum + residual);
+        the first is None without ``weight``."""
+        rt = self._rt
+        rows = partial.shape[0]
+        if rows > self.max_tokens:
+            raise ValueError(f"{rows} rows exceed the {self.max_tokens} the tensor-parallel buffers were sized for")
+        b = self.calls & 1
+        self.calls += 1
+        self.bufs[b][:rows].copy_(partial)
+        out_h = torch.empty(rows, self.hidden, dtype=torch.bfloat16, device=self.device)
+        out_x = torch.empty_like(out_h) if weight is not None else None
+        rt.check(rt.lib().prb_ar_add_rmsnorm(self.buf_ptrs[b], self.flag_ptrs, self.state.data_ptr(),
+                                             residual.data_ptr() if residual is not None else None,
+                                             weight.data_ptr() if weight is not None else None, out_h.data_ptr(),
+                                             out_x.data_ptr() if out_x is not None else None, rows, self.hidden,
+                                             float(eps), self.rank, self.size, rt.status_tensor(self.device).data_ptr(),
+                                             rt.stream_ptr(self.device)), "prb_ar_add_rmsnorm")
+        return out_x, out_h
+
+    def broadcast_sample(self, tok: torch.Tensor, lp: torch.Tensor):
+        packed = torch.stack([tok.double(), lp.double()])
+        dist.broadcast(packed, src=dist.get_global_rank(self.group, 0), group=self.group)
+        return packed[0].long(), packed[1].float()
+
+    def broadcast_control(self, msg):
+        """Rank 0 passes ``msg`` (picklable); the others pass None and get rank 0's message."""
+        box = [msg]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(self.group, 0), group=self.control or self.group)
+        return box[0]
+
+    def close(self):
+        self.symm.close()
+
+
+def init_tp(max_tokens: int, hidden: int):
+    """Process-group setup for a launch with one process per GPU (``torchrun`` environment): NCCL group
+    for the data plane, gloo group for the control messages. Returns a ``TPContext``."""
+    import datetime
+    import os
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+    control = dist.new_group(backend="gloo", timeout=datetime.timedelta(days=2))
+    return TPContext(dist.group.WORLD, dev, hidden, max_tokens, control_group=control)
+
+
+class CollectiveTPContext:
+    """Same interface as ``TPContext`` on plain collectives and PyTorch arithmetic: what the CPU (gloo)
+    tests of the sharding and of the lockstep control plane run on."""
+
+    def __init__(self, group, device: torch.device, hidden: int, max_tokens: int, control_group=None):
+        self.group, self.device, self.hidden, self.max_tokens = group, device, hidden, max_tokens
+        self.control = control_group
+        self.rank, self.size = dist.get_rank(group), dist.get_world_size(group)
+        self.calls = 0
+
+    def reduce(self, partial, residual, weight, eps):
+        from ..ops.norm import rms_norm_ref
+
+        self.calls += 1
+        total = partial.clone()
+        dist.all_reduce(total, group=self.group)
+        h = total if residual is None else total + residual
+        return (rms_norm_ref(h, weight, eps) if weight is not None else None), h
+
+    broadcast_sample = TPContext.broadcast_sample
+    broadcast_control = TPContext.broadcast_control
+
+    def close(self):
+        pass
+
+
+def selftest(argv=None) -> None:
+    """``torchrun --nproc-per-node R -m prime_rl_b200.engine.tp``: the same prompts through an unsharded
+    engine and through the tensor-parallel one must give the same greedy tokens (and close
+    log-probabilities); on GPUs the decode step of both is timed."""
+    import argparse
+    import os
+    import time
+
+    from ..models import ModelArch, build_model, resolve_arch
+    from .engine import Engine
+    from .sampler import SamplingParams
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt", type=int, default=48)
+    ap.add_argument("--tokens", type=int, default=12)
+    ap.add_argument("--cuda-graphs", action="store_true")
+    ap.add_argument("--weight-dtype", default="bf16")
+    ap.add_argument("--skip-reference", action="store_true", help="no unsharded engine (model too large for the check)")
+    args = ap.parse_args(argv)
+    cuda = torch.cuda.is_available()
+    if args.model:
+        arch = resolve_arch(args.model)
+    else:
+        arch = ModelArch(model_type="qwen3_moe", hidden_size=256, num_hidden_layers=3, num_attention_heads=8,
+                         num_key_value_heads=4, head_dim=128 if cuda else 32, intermediate_size=512, num_experts=8,
+                         num_experts_per_tok=2, moe_intermediate_size=256, vocab_size=2048)
+    max_len = args.prompt + args.tokens + 16
+    if cuda:
+        tp = init_tp(max(max_len, args.batch * args.prompt), arch.hidden_size)
+        dev, dtype = tp.device, torch.bfloat16
+    else:
+        import datetime
+
+        dist.init_process_group("gloo", timeout=datetime.timedelta(minutes=10))
+        dev, dtype = torch.device("cpu"), torch.float32
+        tp = CollectiveTPContext(dist.group.WORLD, dev, arch.hidden_size, 1 << 20)
+    rank = tp.rank
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, arch.vocab_size, (args.prompt - (i % 3),), generator=g).tolist() for i in range(args.batch)]
+    params = SamplingParams(max_tokens=args.tokens, temperature=0.0)
+    kw = dict(num_pages=max(64, args.batch * (max_len // 16 + 2)), page_size=16, enable_prefix_cache=False,
+              max_model_len=max_len, max_prefill_tokens=max(max_len, args.batch * args.prompt), max_running=args.batch,
+              use_cuda_graphs=args.cuda_graphs, weight_dtype=args.weight_dtype)
+
+    def timed(engine, run):
+        if cuda:
+            torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = run()
+        if cuda:
+            torch.cuda.synchronize()
+        return out, (time.perf_counter() - t0) * 1e3 / max(1, engine.stats["steps"])
+
+    ref = None
+    if not args.skip_reference and rank == 0:
+        full = Engine(build_model(arch, device=dev, dtype=dtype, seed=0), **kw)
+        full.generate_sync(prompts[:1], params)                     # warm-up
+        full.stats["steps"] = 0
+        ref, ref_ms = timed(full, lambda: full.generate_sync(prompts, params))
+        ref = [(r.output, r.logprobs) for r in ref]
+        del full
+    dist.barrier()
+    eng = Engine(build_model(arch, device=dev, dtype=dtype, seed=0), tp=tp, **kw)
+    if rank == 0:
+        eng.generate_sync(prompts[:1], params)
+        eng.stats["steps"] = 0
+        out, ms = timed(eng, lambda: eng.generate_sync(prompts, params))
+        eng.shutdown()
+    else:
+        eng.follow()
+    if cuda:
+        from ..ops import _runtime as rt
+
+        torch.cuda.synchronize()
+        rt.check_status()
+    ok = True
+    if rank == 0:
+        if ref is not None:
+            same = sum(r.output == o for r, (o, _) in zip(out, ref))
+            worst = max((abs(a - b) for r, (_, lp) in zip(out, ref) for a, b in zip(r.logprobs[:1], lp[:1])), default=0.0)
+            # bf16 sums in another order can flip a near-tie of the arg-max: most sequences must agree fully,
+            # and the first token's log-probability (same context on both sides) must agree closely
+            ok = same >= (len(out) if not cuda else (3 * len(out)) // 4) and worst < (1e-4 if not cuda else 0.08)
+            print(f"TP_SELFTEST ranks={tp.size} identical_sequences={same}/{len(out)} first_logprob_diff={worst:.2e} "
+                  f"ms_per_step tp={ms:.2f} single={ref_ms:.2f}", flush=True)
+        else:
+            print(f"TP_SELFTEST ranks={tp.size} ms_per_step tp={ms:.2f} tokens={sum(len(r.output) for r in out)}", flush=True)
+        print("TP_SELFTEST_OK" if ok else "TP_SELFTEST_FAIL", flush=True)
+    dist.barrier()
+    tp.close()
+    dist.destroy_process_group()
+    if not ok:
+        raise SystemExit(1)
+
+
+if __name__ == "__main__":
+    selftest()

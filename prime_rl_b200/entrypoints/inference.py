@@ -12,7 +12,8 @@ from ..configs.inference import InferenceConfig
 from ..utils.logger import setup_logger
 
 
-def build_engine(config: InferenceConfig):
+def build_engine(config: InferenceConfig, tp=None):
+    """``tp``: the ``engine/tp.py`` context of a tensor-parallel launch (this process holds one shard)."""
     from ..engine.engine import Engine
     from ..models import build_model, resolve_arch
     from ..trainer.weights import load_hf_checkpoint
@@ -20,9 +21,15 @@ def build_engine(config: InferenceConfig):
     ec = config.vllm
     arch = resolve_arch(ec.model, ec.arch)
     device = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
+    if tp is not None:
+        device = tp.device
     dtype = {"auto": torch.bfloat16 if device.type == "cuda" else torch.float32, "bfloat16": torch.bfloat16,
              "float16": torch.float16, "float32": torch.float32}[ec.dtype]
     model = build_model(arch, device=device, dtype=dtype, seed=ec.seed)
+    if tp is not None and tp.size > 1:
+        from ..engine.tp import shard_model_
+
+        shard_model_(model, tp.rank, tp.size)       # before the checkpoint load: every rank reads only its slices
     if Path(ec.model).is_dir() and not ec.random_init:
         load_hf_checkpoint(model, Path(ec.model), strict=False)
     for p in model.parameters():
@@ -32,12 +39,13 @@ def build_engine(config: InferenceConfig):
     elif device.type == "cuda":
         free, total = torch.cuda.mem_get_info(device)
         per_page = 2 * arch.num_hidden_layers * ec.page_size * arch.kv_dim * torch.empty((), dtype=dtype).element_size()
+        per_page //= tp.size if tp is not None else 1
         pages = max(64, int((free - (1.0 - ec.gpu_memory_utilization) * total) // per_page))
     else:
         pages = 2048
     engine = Engine(model, num_pages=pages, page_size=ec.page_size, max_running=ec.max_num_seqs,
                     max_prefill_tokens=ec.max_num_batched_tokens,
-                    enable_prefix_cache=ec.enable_prefix_caching is not False)
+                    enable_prefix_cache=ec.enable_prefix_caching is not False, tp=tp)
     engine.runner.capture_routed = ec.enable_return_routed_experts and arch.is_moe
     return engine
 
@@ -58,11 +66,48 @@ def serve(config: InferenceConfig) -> None:
 
     from ..engine.server import build_app
 
-    engine = build_engine(config).start()
+    _serve_engine(build_engine(config).start(), config)
+
+
+def _serve_engine(engine, config: InferenceConfig) -> None:
+    import uvicorn
+
+    from ..engine.server import build_app
+
     app = build_app(engine, config.vllm.model, tokenizer=load_tokenizer(config.vllm.model),
                     liveness_timeout=config.server.liveness_timeout_seconds)
     app.state.return_sampling_mask = config.enable_return_sampling_mask
     uvicorn.run(app, host=config.server.host or "0.0.0.0", port=config.server.port, log_level="warning")
+
+
+def serve_tensor_parallel(config: InferenceConfig, argv: list[str]) -> int:
+    """``tensor_parallel_size`` processes, one GPU each. Outside a ``torchrun`` environment this
+    relaunches the same command line under it; inside, rank 0 serves HTTP and drives the step loop,
+    the other ranks follow its announcements (``Engine.follow``)."""
+    import os
+    import subprocess
+    import sys
+
+    n = config.vllm.tensor_parallel_size
+    if "LOCAL_RANK" not in os.environ:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+               "127.0.0.1", "--master-port", str(config.vllm.data_parallel_rpc_port), "-m",
+               "prime_rl_b200.entrypoints.inference", *argv]
+        return subprocess.call(cmd)
+    from ..engine.tp import init_tp
+    from ..models import resolve_arch
+
+    arch = resolve_arch(config.vllm.model, config.vllm.arch)
+    if int(os.environ.get("WORLD_SIZE", "1")) != n:
+        raise ValueError(f"tensor_parallel_size={n} but the launch has {os.environ.get('WORLD_SIZE')} processes")
+    tp = init_tp(max(config.vllm.max_num_batched_tokens, 8192), arch.hidden_size)
+    engine = build_engine(config, tp=tp)
+    if tp.rank == 0:
+        _serve_engine(engine.start(), config)
+        engine.shutdown()
+    else:
+        engine.follow()
+    return 0
 
 
 def serve_replicas(config: InferenceConfig, argv: list[str]) -> int:
@@ -133,6 +178,9 @@ def main(argv: list[str] | None = None) -> None:
     setup_logger(config.log.level, tag="inference", json_logging=config.log.json_logging)
     if config.vllm.data_parallel_size > 1:
         serve_replicas(config, args)
+        return
+    if config.vllm.tensor_parallel_size > 1:
+        serve_tensor_parallel(config, args)
         return
     serve(config)
 

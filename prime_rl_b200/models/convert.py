@@ -354,9 +354,10 @@ def load_model_state(model, sd: StateDict, layout: str = "prime", strict: bool =
     unexpected = [k for k in sd if k not in own]
     if strict and (missing or unexpected):
         raise KeyError(f"state dict mismatch: missing={missing[:5]} unexpected={unexpected[:5]}")
+    shard = getattr(model, "tp_shard", None)      # engine tensor parallelism: this process keeps one slice
     for k, v in sd.items():
         if k in own:
-            own[k].copy_(v.to(own[k].dtype))
+            own[k].copy_((v if shard is None else shard(k, v)).to(own[k].dtype))
 
 
 # ---------------------------------------------------------------------- LoRA adapters (PEFT layout)

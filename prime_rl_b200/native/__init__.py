@@ -46,8 +46,10 @@ _CUDA_SIGNATURES = {
     "prb_gated_norm_fwd": [P, P, P, P, L, I, I, I, F, I, P],
     "prb_gated_norm_bwd": [P, P, P, P, P, P, P, L, I, I, I, F, I, P],
     "prb_conv1d_fwd": [P, P, P, P, P, L, I, I, I, P],
+    "prb_sample_gumbel": [P, P, L, L, P, P, I, I, P],
     "prb_conv1d_bwd": [P, P, P, P, P, P, P, P, L, I, I, I, P],
     "prb_rs_pull": [P, L, L, F, P, I, P],
+    "prb_ar_add_rmsnorm": [P, P, P, P, P, P, P, I, I, F, I, I, P, P],
     "prb_ag_push": [P, P, L, L, I, I, P],
     "prb_ep_signal": [P, I, I, I, I, P],
     "prb_ep_pull": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],

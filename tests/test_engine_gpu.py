@@ -72,3 +72,41 @@ def test_fp8_weight_mode_stays_close_to_bf16():
     assert rel < 0.15, f"fp8 logits deviate by {rel:.3f}"
     agree = (out.argmax(-1) == ref.argmax(-1)).float().mean()
     assert agree > 0.7
+
+
+def test_sampling_kernel_matches_softmax_statistics_and_logprobs():
+    """The one-pass Gumbel-max sampler: greedy rows take the arg-max, sampled rows follow softmax(z / T)
+    (checked by frequencies over many draws of a small vocabulary), and the returned log-probability is
+    log softmax(z / T) at the drawn token. A seeded generator replays the same tokens."""
+    from prime_rl_b200.engine.sampler import sample
+
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    V, B = 37, 4096
+    row = torch.randn(V, device=dev) * 2.0
+    logits = row[None, :].repeat(B, 1).contiguous()
+    temp = torch.full((B,), 0.7, device=dev)
+    temp[:16] = 0.0
+    off = torch.zeros(B, dtype=torch.long, device=dev)
+    ones = torch.ones(B, device=dev)
+    g = torch.Generator(device=dev).manual_seed(11)
+    tok, lp, masks = sample(logits, temp, off, ones, generator=g, truncated=False)
+    assert masks is None and tok.dtype == torch.long
+    assert (tok[:16] == row.argmax()).all()
+    ref = torch.log_softmax(row / 0.7, -1)
+    torch.testing.assert_close(lp[16:], ref[tok[16:]], atol=2e-4, rtol=0)
+    torch.testing.assert_close(lp[:16], torch.log_softmax(row, -1)[tok[:16]], atol=2e-4, rtol=0)
+    freq = torch.bincount(tok[16:], minlength=V).float() / (B - 16)
+    # standard error of a frequency p over n draws is sqrt(p (1 - p) / n) <= 0.008 here
+    assert (freq - ref.exp()).abs().max() < 0.035
+    g2 = torch.Generator(device=dev).manual_seed(11)
+    tok2, _, _ = sample(logits, temp, off, ones, generator=g2, truncated=False)
+    assert torch.equal(tok, tok2)
+    tok3, _, _ = sample(logits, temp, off, ones, generator=g2, truncated=False)
+    assert not torch.equal(tok, tok3)
+    # a large vocabulary with a ragged length and a row pitch wider than V
+    wide = torch.randn(8, 151936 + 64, device=dev)
+    view = wide[:, :151931]
+    t8 = torch.full((8,), 1.3, device=dev)
+    tok, lp, _ = sample(view, t8, off[:8], ones[:8], truncated=False)
+    torch.testing.assert_close(lp, torch.log_softmax(view / 1.3, -1).gather(1, tok[:, None]).squeeze(1), atol=5e-4, rtol=0)

@@ -100,3 +100,14 @@ def test_sharded_optimizer_with_peer_memory_collectives():
            "127.0.0.1", "--master-port", "29539", "-m", "prime_rl_b200.parallel.p2p_zero_selftest"]
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0 and "P2P_ZERO_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
+
+
+def test_tensor_parallel_engine_with_fused_reduce_kernel():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    for extra in ([], ["--cuda-graphs"]):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+               "127.0.0.1", "--master-port", "29539", "-m", "prime_rl_b200.engine.tp", *extra]
+        out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+        assert out.returncode == 0 and "TP_SELFTEST_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]

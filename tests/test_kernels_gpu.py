@@ -711,3 +711,43 @@ def test_gated_group_rmsnorm_kernel(rows, cols, group, shared_w, gate_first):
     ref.backward(dy.float())
     for a, b in ((x.grad, xf.grad), (g.grad, gf.grad), (w.grad, wf.grad)):
         assert float((a.float() - b).abs().max() / b.abs().max()) < 2e-2
+
+
+def test_allreduce_add_rmsnorm_kernel_with_emulated_peers():
+    """The tensor-parallel reduce kernel on one GPU: the "peers" are local buffers and the peer's flag
+    slot is set beforehand, so the single launch waits on nothing. Two consecutive calls check the
+    device-side call counter."""
+    import ctypes
+
+    from prime_rl_b200.ops import _runtime as rt
+
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    rows, cols, R = 300, 2048, 2
+    parts = [torch.randn(rows, cols, device=dev).bfloat16() for _ in range(R)]
+    res = torch.randn(rows, cols, device=dev).bfloat16()
+    w = (1 + 0.1 * torch.randn(cols, device=dev)).bfloat16()
+    flags = [torch.zeros(R, dtype=torch.int32, device=dev) for _ in range(R)]
+    flags[0][1] = 1 << 30                                     # "rank 1 has arrived", for every call to come
+    pp = (ctypes.c_void_p * R)(*[p.data_ptr() for p in parts])
+    fp = (ctypes.c_void_p * R)(*[f.data_ptr() for f in flags])
+    state = torch.zeros(2, dtype=torch.int32, device=dev)
+    out_h, out_x = torch.empty_like(res), torch.empty_like(res)
+    for call in (1, 2):
+        rt.check(rt.lib().prb_ar_add_rmsnorm(pp, fp, state.data_ptr(), res.data_ptr(), w.data_ptr(), out_h.data_ptr(),
+                                             out_x.data_ptr(), rows, cols, 1e-6, 0, R, rt.status_tensor(dev).data_ptr(),
+                                             rt.stream_ptr(dev)), "prb_ar_add_rmsnorm")
+        torch.cuda.synchronize()
+        rt.check_status()
+        assert state.tolist() == [call, 0]
+        assert flags[0][0].item() == call and flags[1][0].item() == call     # announced to itself and to the peer
+    h = parts[0].float() + parts[1].float() + res.float()
+    torch.testing.assert_close(out_h.float(), h, atol=0.04, rtol=0.01)
+    hb = out_h.float()
+    ref = hb * torch.rsqrt(hb.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
+    torch.testing.assert_close(out_x.float(), ref, atol=0.03, rtol=0.01)
+    # no residual, no norm output
+    rt.check(rt.lib().prb_ar_add_rmsnorm(pp, fp, state.data_ptr(), None, None, out_h.data_ptr(), None, rows, cols, 1e-6, 0,
+                                         R, rt.status_tensor(dev).data_ptr(), rt.stream_ptr(dev)), "prb_ar_add_rmsnorm")
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out_h.float(), parts[0].float() + parts[1].float(), atol=0.04, rtol=0.01)
