@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import time
 
 import torch
@@ -34,11 +35,20 @@ def main(argv=None):
     ap.add_argument("--fp8", action="store_true", help="block-scaled fp8 weights (128x128 scales), 1x128 activation scales")
     ap.add_argument("--no-graphs", action="store_true", help="launch the decode step kernel by kernel")
     args = ap.parse_args(argv)
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
     arch = resolve_arch(args.model)
     if args.layers:
         arch = arch.model_copy(update={"num_hidden_layers": args.layers})
+    # under torchrun with N processes: one tensor-parallel engine over N GPUs (rank 0 drives and reports)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    tp = None
+    if world > 1:
+        from .tp import init_tp
+
+        tp = init_tp(16384 + args.prompt, arch.hidden_size)
+        dev = tp.device
+    else:
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
     model = build_model(arch, device=dev, dtype=torch.bfloat16, seed=0)
     # requests admitted early keep decoding while the rest is prefilled: give every request enough
     # budget to still be running in the timed region
@@ -48,14 +58,18 @@ def main(argv=None):
     pages = args.batch * ((total + 15) // 16 + 1) + 64
     eng = Engine(model, num_pages=pages, page_size=16, max_running=args.batch, max_prefill_tokens=16384,
                  enable_prefix_cache=False, use_cuda_graphs=not args.no_graphs, max_model_len=total + 16,
-                 weight_dtype="fp8" if args.fp8 else "bf16")
+                 weight_dtype="fp8" if args.fp8 else "bf16", tp=tp)
+    if tp is not None and tp.rank != 0:
+        eng.follow()
+        tp.close()
+        return
     g = torch.Generator().manual_seed(0)
     params = SamplingParams(temperature=1.0, max_tokens=budget)
     for _ in range(args.batch):
         eng.submit(Request(prompt=torch.randint(0, arch.vocab_size, (args.prompt,), generator=g).tolist(), params=params))
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    while eng.waiting:
+    while eng.waiting or eng._inbox:
         eng.step()
     torch.cuda.synchronize()
     t_prefill = time.perf_counter() - t0
@@ -76,8 +90,12 @@ def main(argv=None):
                       "batch": args.batch, "mean_running": toks / args.steps, "prompt_len": args.prompt, "steps": args.steps,
                       "decode_tokens_per_s": toks / dt, "ms_per_step": 1e3 * dt / args.steps,
                       "prefill_tokens_per_s": args.batch * args.prompt / t_prefill,
-                      "peak_memory_gib": torch.cuda.max_memory_allocated() / 2**30, "n_gpus": 1, "dtype": "fp8 weights / bf16 KV" if args.fp8 else "bf16", "cuda_graphs": not args.no_graphs,
+                      "peak_memory_gib": torch.cuda.max_memory_allocated() / 2**30, "n_gpus": world,
+                      "parallelism": f"tp{world}" if world > 1 else "single", "dtype": "fp8 weights / bf16 KV" if args.fp8 else "bf16", "cuda_graphs": not args.no_graphs,
                       "data": "synthetic (uniform random token ids, random-init weights)"}), flush=True)
+    if tp is not None:
+        eng.shutdown()
+        tp.close()
 
 
 if __name__ == "__main__":

@@ -61,6 +61,7 @@ class Engine:
         self.tp_size = tp.size if tp is not None else 1
         self._inbox: list[Request] = []
         self._commands: list[tuple] = []
+        self.mark = None
         if tp is not None and tp.size > 1:
             from .tp import shard_model_
 
@@ -163,6 +164,8 @@ class Engine:
         for cmd in msg["cmds"]:
             if cmd[0] == "update_weights":
                 self._update_weights_local(cmd[1])
+            elif cmd[0] == "mark":                  # a label every rank sees at the same step (benchmarks)
+                self.mark = cmd[1]
             elif cmd[0] == "stop":
                 alive = False
         return alive

@@ -251,7 +251,25 @@ def bench_mixers(timer, args, dev):
             timer(lambda: ssm.gated_rms_norm(h, g, nw, 1e-5, inner // ng, "silu", True)), bytes_=3 * T * inner * 2)
 
 
-OPS = {"gemm": bench_gemm, "sparse_mla": bench_sparse_mla, "mixers": bench_mixers, "grouped": bench_grouped, "fp8": bench_fp8, "lm_head": bench_lm_head, "flash_fwd": bench_flash_fwd,
+def bench_sample(timer, args, dev):
+    """Decode-step sampling over fp32 logits: the one-pass Gumbel-max kernel against the PyTorch sequence it
+    replaced (scale, log-softmax, exp, multinomial, gather)."""
+    from ..engine.sampler import sample_untruncated
+
+    B, V = args.tokens or 256, 151936
+    logits = torch.randn(B, V, device=dev)
+    temp = torch.ones(B, device=dev)
+
+    def torch_path():
+        logp = torch.log_softmax(logits / temp[:, None], dim=-1)
+        tok = torch.multinomial(logp.exp(), 1).squeeze(1)
+        return tok, logp.gather(1, tok[:, None])
+
+    _report(f"sampling kernel {B}x{V} fp32", timer(lambda: sample_untruncated(logits, temp)), bytes_=B * V * 4)
+    _report(f"sampling, PyTorch ops {B}x{V} fp32", timer(torch_path), bytes_=B * V * 4)
+
+
+OPS = {"sample": bench_sample, "gemm": bench_gemm, "sparse_mla": bench_sparse_mla, "mixers": bench_mixers, "grouped": bench_grouped, "fp8": bench_fp8, "lm_head": bench_lm_head, "flash_fwd": bench_flash_fwd,
        "flash_bwd": bench_flash_bwd, "paged": bench_paged, "norm": bench_norm}
 
 

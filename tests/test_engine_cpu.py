@@ -204,3 +204,59 @@ def test_tensor_parallel_engine_in_lockstep_matches_the_single_engine():
                        timeout=600, cwd=str(root))
     assert r.returncode == 0 and "TP_SELFTEST_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
     assert "identical_sequences=5/5" in r.stdout
+
+
+def test_tensor_parallel_http_server_serves_the_same_tokens(tmp_path):
+    """The inference entry point with ``tensor_parallel_size = 2`` (two CPU processes under torchrun):
+    rank 0 answers HTTP, the other rank follows; greedy tokens equal those of a local unsharded engine."""
+    import os
+    import signal
+    import subprocess
+    import sys
+    import time
+    from pathlib import Path
+
+    import httpx
+
+    from prime_rl_b200.engine.engine import Engine as LocalEngine
+
+    root = Path(__file__).resolve().parents[1]
+    port = 18431
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=str(root))
+    log = open(tmp_path / "server.log", "w")
+    proc = subprocess.Popen([sys.executable, "-m", "prime_rl_b200.entrypoints.inference", "@",
+                             str(root / "examples" / "inference.toml"), "--vllm.tensor-parallel-size", "2",
+                             "--server.port", str(port), "--server.host", "127.0.0.1", "--vllm.num-pages", "256",
+                             "--vllm.data-parallel-rpc-port", "29641"], env=env, cwd=str(root), stdout=log,
+                            stderr=subprocess.STDOUT, start_new_session=True)
+    try:
+        base = f"http://127.0.0.1:{port}"
+        deadline = time.time() + 240
+        while True:
+            try:
+                if httpx.get(base + "/health", timeout=2).status_code == 200:
+                    break
+            except httpx.HTTPError:
+                pass
+            assert proc.poll() is None and time.time() < deadline, (tmp_path / "server.log").read_text()[-3000:]
+            time.sleep(1.0)
+        prompt = [5, 17, 99, 3, 42, 8, 250, 77]
+        body = {"token_ids": prompt, "sampling_params": {"max_tokens": 6, "temperature": 0.0}}
+        r = httpx.post(base + "/inference/v1/generate", json=body, timeout=120)
+        assert r.status_code == 200, r.text
+        served = r.json()["choices"][0]["token_ids"]
+        arch = resolve_arch("tiny-qwen3-moe")
+        local = LocalEngine(build_model(arch, device=torch.device("cpu"), dtype=torch.float32, seed=0), num_pages=64)
+        want = local.generate_sync([prompt], SamplingParams(max_tokens=6, temperature=0.0))[0].output
+        assert served == want
+        assert httpx.post(base + "/pause", timeout=60).status_code == 200
+        assert httpx.post(base + "/resume", timeout=60).status_code == 200
+        r = httpx.post(base + "/inference/v1/generate", json=body, timeout=120)
+        assert r.json()["choices"][0]["token_ids"] == want
+    finally:
+        os.killpg(proc.pid, signal.SIGTERM)            # the process group this test started, nothing else
+        try:
+            proc.wait(timeout=30)
+        except subprocess.TimeoutExpired:
+            os.killpg(proc.pid, signal.SIGKILL)
+        log.close()
