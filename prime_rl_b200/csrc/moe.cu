@@ -278,7 +278,8 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ p, const int* __restrict__ 
       sl[j] = slot[t * k + j];
       ww[j] = w ? w[t * k + j] : 1.f;
     }
-    for (int v = lane; v < nvec; v += 32) {
+    // blockIdx.y splits the columns when there are few tokens (decode), so that the gather is spread over the SMs
+    for (int v = blockIdx.y * 32 + lane; v < nvec; v += 32 * gridDim.y) {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       if (residual) {
         const uint4 a = reinterpret_cast<const uint4*>(residual + t * cols)[v];
@@ -384,8 +385,15 @@ PRB_API int prb_moe_combine(const void* p, const int* slot, const float* w, cons
   if (cols % 8 || k > kMaxTopK) return -1;
   if (T == 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  moe_combine_kernel<<<row_grid(T), 256, 0, s>>>((const __nv_bfloat16*)p, slot, w, (const __nv_bfloat16*)residual,
-                                                 (__nv_bfloat16*)y, T, cols, k);
+  // few tokens: one warp per (token, 256-column slice) instead of one warp per token
+  int col_split = 1;
+  if (T <= 148 * 8 * 2) {
+    col_split = (cols / 8 + 31) / 32;
+    if (col_split > 16) col_split = 16;
+  }
+  moe_combine_kernel<<<dim3(row_grid(T), col_split), 256, 0, s>>>((const __nv_bfloat16*)p, slot, w,
+                                                                  (const __nv_bfloat16*)residual, (__nv_bfloat16*)y, T,
+                                                                  cols, k);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -100,10 +100,11 @@ class ModelRunner:
         layers = model.model.layers
         if tp is not None:
             assert tp.calls % 2 == 0, "every forward makes an even number of tensor-parallel reduces"
+        add_norm = ops.add_rms_norm if tp is None else tp.reduce
         x = None
         for li, layer in enumerate(layers):
             at = layer.self_attn
-            if tp is None or li == 0:                   # with TP the previous layer's reduce already normalised
+            if li == 0:                                 # later layers get their input norm from add_norm below
                 x = layer.input_layernorm(h)
             qkv = at.qkv_proj(x)
             eps = self.arch.rms_norm_eps
@@ -114,23 +115,18 @@ class ModelRunner:
             cache.write(li, k, v, slots_t)
             o = self._attend(li, q, k, v.contiguous(), batch, starts, at.window, at.sinks)
             a = at.finish(o, x)
-            if tp is None:
-                x2, h = ops.add_rms_norm(a, h, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.eps)
-            else:                                       # sum over ranks + residual + norm in one kernel
-                x2, h = tp.reduce(a, h, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.eps)
+            # residual add + norm in one kernel; with TP the same kernel also sums the ranks' partial outputs
+            x2, h = add_norm(a, h, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.eps)
             if layer.is_moe:
                 m = layer.mlp(x2, seq)
                 if self.capture_routed and isinstance(layer.mlp, MoE) and layer.mlp.last_topk is not None:
                     routed.append(layer.mlp.last_topk)
             else:
                 m = layer.mlp(x2)
-            if tp is None:
-                h = h + m
-            else:
-                nxt = layers[li + 1].input_layernorm if li + 1 < len(layers) else model.model.norm
-                x, h = tp.reduce(m, h, nxt.weight, nxt.eps)
+            nxt = layers[li + 1].input_layernorm if li + 1 < len(layers) else model.model.norm
+            x, h = add_norm(m, h, nxt.weight, nxt.eps)      # the next layer's input norm (or the final norm)
         routed_t = torch.stack(routed, dim=1) if routed else None
-        h = model.model.norm(h) if tp is None else x
+        h = x
         sel = h[rows_t]
         w = model.output_weight
         if sel.is_cuda and sel.dtype == torch.bfloat16:

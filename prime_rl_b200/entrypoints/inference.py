@@ -129,14 +129,16 @@ def serve_replicas(config: InferenceConfig, argv: list[str]) -> int:
     n, port = config.vllm.data_parallel_size, config.server.port
     visible = os.environ.get("CUDA_VISIBLE_DEVICES")
     gpus = [g for g in visible.split(",") if g] if visible else [str(i) for i in range(n)]
-    if len(gpus) < n:
-        raise ValueError(f"data_parallel_size={n} but only {len(gpus)} GPUs are visible")
+    tp = config.vllm.tensor_parallel_size                # every replica may itself span several GPUs
+    if len(gpus) < n * tp:
+        raise ValueError(f"data_parallel_size={n} x tensor_parallel_size={tp} but only {len(gpus)} GPUs are visible")
     sup = Supervisor()
     urls = []
     for i in range(n):
-        env = dict(os.environ, CUDA_VISIBLE_DEVICES=gpus[i])
+        env = dict(os.environ, CUDA_VISIBLE_DEVICES=",".join(gpus[i * tp:(i + 1) * tp]))
         cmd = [sys.executable, "-m", "prime_rl_b200.entrypoints.inference", *argv, "--vllm.data-parallel-size", "1",
-               "--server.port", str(port + 1 + i), "--server.host", "127.0.0.1"]
+               "--server.port", str(port + 1 + i), "--server.host", "127.0.0.1", "--vllm.data-parallel-rpc-port",
+               str(config.vllm.data_parallel_rpc_port + i)]
         sup.add(f"replica{i}", subprocess.Popen(cmd, env=env))
         urls.append(f"http://127.0.0.1:{port + 1 + i}")
     deadline = time.time() + 1800
