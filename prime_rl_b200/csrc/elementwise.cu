@@ -19,12 +19,13 @@ template <int ACT>
 __global__ void __launch_bounds__(256)
 glu_fwd_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
                __nv_bfloat16* __restrict__ y, long long rows, int cols, long long ld_in, long long ld_out,
-               float limit, float alpha_act) {
+               float limit, float alpha_act, const int* __restrict__ row_valid) {
   const int vec_per_row = cols >> 3;
   const long long total = rows * vec_per_row;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long r = i / vec_per_row;
+    if (row_valid != nullptr && row_valid[r] < 0) continue;      // padding row: neither read nor written
     const int c = static_cast<int>(i - r * vec_per_row) * 8;
     const uint4 gv = *reinterpret_cast<const uint4*>(g + r * ld_in + c);
     uint4 uv = make_uint4(0, 0, 0, 0);
@@ -267,17 +268,30 @@ static inline unsigned ew_grid(long long work_items, int per_thread = 1) {
 }
 
 // g, u: bf16 [rows, cols] windows with row pitch ld_in; y: bf16 pitch ld_out; cols % 8 == 0.
-PRB_API int prb_glu_fwd(const void* g, const void* u, void* y, long long rows, int cols, long long ld_in,
-                        long long ld_out, int act, float limit, float alpha_act, void* stream) {
+static int glu_fwd_launch(const void* g, const void* u, void* y, long long rows, int cols, long long ld_in,
+                          long long ld_out, int act, float limit, float alpha_act, const int* row_valid, void* stream) {
   if (cols % 8 || ld_in % 8 || ld_out % 8) return -1;
   if (rows == 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const unsigned grid = ew_grid(rows * (cols / 8));
-#define L(A) glu_fwd_kernel<A><<<grid, 256, 0, s>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)u, \
-                                                     (__nv_bfloat16*)y, rows, cols, ld_in, ld_out, limit, alpha_act)
+#define L(A) glu_fwd_kernel<A><<<grid, 256, 0, s>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)u,          \
+                                                     (__nv_bfloat16*)y, rows, cols, ld_in, ld_out, limit, alpha_act, \
+                                                     row_valid)
   if (act == kSwiGLU) L(kSwiGLU); else if (act == kSwiGLUClamped) L(kSwiGLUClamped); else L(kReLU2);
 #undef L
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+PRB_API int prb_glu_fwd(const void* g, const void* u, void* y, long long rows, int cols, long long ld_in,
+                        long long ld_out, int act, float limit, float alpha_act, void* stream) {
+  return glu_fwd_launch(g, u, y, rows, cols, ld_in, ld_out, act, limit, alpha_act, nullptr, stream);
+}
+
+// Rows r with row_valid[r] < 0 (padding rows of a grouped inference pass) are skipped.
+PRB_API int prb_glu_fwd_rowmask(const void* g, const void* u, void* y, long long rows, int cols, long long ld_in,
+                                long long ld_out, int act, float limit, float alpha_act, const int* row_valid,
+                                void* stream) {
+  return glu_fwd_launch(g, u, y, rows, cols, ld_in, ld_out, act, limit, alpha_act, row_valid, stream);
 }
 
 PRB_API int prb_glu_bwd(const void* dy, const void* g, const void* u, void* dg, void* du, long long rows, int cols,

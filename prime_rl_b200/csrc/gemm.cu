@@ -46,6 +46,8 @@ struct GemmParams {
   // 64, TMA zero-fills A2 past K2
   int k2_blocks = 0;
   int b2_rows_per_expert = 0;
+  // optional: rows r of C with row_valid[r] < 0 are not stored (padding rows of a grouped inference GEMM)
+  const int* row_valid = nullptr;
   // reduce-scatter epilogue: row r of C is added into peer_c[r / rows_per_rank] (fp32, pitch ldc)
   float* peer_c[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   int rows_per_rank = 0;
@@ -626,7 +628,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     bool first = true;
     while (sched.next(p, m_blk, n_blk, brow, last, kb0, nkb, c_row0)) {
       const int row_in_m = m_blk * kBM + q * 32 + lane;
-      const long long row = (row_in_m < p.M) ? c_row0 + row_in_m : (1LL << 40);  // out of range -> masked
+      long long row = (row_in_m < p.M) ? c_row0 + row_in_m : (1LL << 40);  // out of range -> masked
+      if (p.row_valid != nullptr && row < p.rows_total && p.row_valid[row] < 0) row = 1LL << 40;
       if (nkb == 0) {
         // nothing to reduce: the tile is all zeros
         uint32_t z[32];
@@ -701,7 +704,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
                           long long ldc, int a_mn, int b_mn, int out_fp32, float alpha, float beta,
                           const int* block_expert, int num_experts, int b_rows_per_expert, int force_bn,
                           const void* A2, const void* B2, int K2, long long lda2, long long ldb2,
-                          int b2_rows_per_expert, int* status, void* stream_) {
+                          int b2_rows_per_expert, int* status, void* stream_, const int* row_valid = nullptr) {
   using namespace prb;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0) return 0;
@@ -764,6 +767,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
   p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32;
   p.k2_blocks = (A2 != nullptr && K2 > 0) ? (K2 + kBK - 1) / kBK : 0;
   p.b2_rows_per_expert = b2_rows_per_expert;
+  p.row_valid = row_valid;
   p.expert_offset = nullptr; p.num_experts = 0;
   p.alpha = alpha; p.beta = beta;
   p.block_expert = block_expert;
@@ -789,6 +793,16 @@ PRB_API int prb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, i
                           int* status, void* stream_) {
   return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_fp32, alpha, beta, block_expert, num_experts,
                         b_rows_per_expert, force_bn, nullptr, nullptr, 0, 0, 0, 0, status, stream_);
+}
+
+// Same as prb_gemm_bf16, but rows r of C with row_valid[r] < 0 are computed and not stored: the padding rows that
+// round every expert of a grouped inference GEMM up to 128 (their inputs may hold anything).
+PRB_API int prb_gemm_bf16_rowmask(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                  long long ldb, long long ldc, int a_mn, int b_mn, int out_fp32, float alpha,
+                                  float beta, const int* block_expert, int num_experts, int b_rows_per_expert,
+                                  int force_bn, const int* row_valid, int* status, void* stream_) {
+  return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_fp32, alpha, beta, block_expert, num_experts,
+                        b_rows_per_expert, force_bn, nullptr, nullptr, 0, 0, 0, 0, status, stream_, row_valid);
 }
 
 // C = alpha * (A B + A2 B2) + beta * C in one pass: the accumulator of every tile takes the

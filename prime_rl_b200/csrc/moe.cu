@@ -234,7 +234,7 @@ moe_scatter_sorted_kernel(const int* __restrict__ topk_idx, const int* __restric
 __global__ void __launch_bounds__(256)
 moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ row_src,
                        const float* __restrict__ w, __nv_bfloat16* __restrict__ out, long long max_rows, int cols,
-                       int k, const int* __restrict__ total_rows) {
+                       int k, const int* __restrict__ total_rows, int zero_pad) {
   const int lane = threadIdx.x & 31;
   const int nvec = cols >> 3;
   const int total = total_rows[0];
@@ -244,7 +244,8 @@ moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restric
     const int src = row_src[pos];
     uint4* dst = reinterpret_cast<uint4*>(out + pos * cols);
     if (src < 0) {
-      for (int v = lane; v < nvec; v += 32) dst[v] = make_uint4(0, 0, 0, 0);
+      if (zero_pad)
+        for (int v = lane; v < nvec; v += 32) dst[v] = make_uint4(0, 0, 0, 0);
     } else {
       const uint4* s = reinterpret_cast<const uint4*>(x + static_cast<long long>(src / k) * cols);
       if (w) {
@@ -376,7 +377,18 @@ PRB_API int prb_moe_gather_rows(const void* x, const int* row_src, const float* 
   if (cols % 8) return -1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   moe_gather_rows_kernel<<<row_grid(max_rows), 256, 0, s>>>((const __nv_bfloat16*)x, row_src, w,
-                                                            (__nv_bfloat16*)out, max_rows, cols, k, total_rows);
+                                                            (__nv_bfloat16*)out, max_rows, cols, k, total_rows, 1);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Inference variant: padding rows of `out` are left as they are (the grouped GEMMs that follow are told, with the
+// same row_src, not to store those rows).
+PRB_API int prb_moe_gather_rows_nopad(const void* x, const int* row_src, const float* w, void* out, long long max_rows,
+                                      int cols, int k, const int* total_rows, void* stream) {
+  if (cols % 8) return -1;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  moe_gather_rows_kernel<<<row_grid(max_rows), 256, 0, s>>>((const __nv_bfloat16*)x, row_src, w,
+                                                            (__nv_bfloat16*)out, max_rows, cols, k, total_rows, 0);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -296,9 +296,21 @@ class GroupedExperts(nn.Module):
                 self.fp8[name][1].copy_(s)
         return True
 
+    def supports_row_mask(self, x: torch.Tensor) -> bool:
+        """No-grad bf16 forward on the GPU without adapters or fp8 copies: the padding rows that round every
+        expert up to 128 need not be written, read by the activation or stored by the GEMMs."""
+        return (not torch.is_grad_enabled() and x.is_cuda and x.dtype == torch.bfloat16 and self.fp8 is None
+                and self.lora_gate_up is None and self.lora_down is None and self.act != act_ops.SILU_CLAMPED
+                and self.gate_up_proj.dtype == torch.bfloat16)
+
     def forward(self, xp: torch.Tensor, block_expert: torch.Tensor, expert_offset: torch.Tensor,
-                out: torch.Tensor | None = None) -> torch.Tensor:
-        """``out`` (optional, ``[P, H]`` bf16): memory the last projection writes into."""
+                out: torch.Tensor | None = None, row_valid: torch.Tensor | None = None) -> torch.Tensor:
+        """``out`` (optional, ``[P, H]`` bf16): memory the last projection writes into. ``row_valid``
+        (int32 per permuted row, < 0 = padding; only where ``supports_row_mask``): those rows are skipped."""
+        if row_valid is not None:
+            gu = ops.gemm(xp, self.gate_up_proj, block_expert=block_expert, row_valid=row_valid)
+            h = act_ops.glu_rowmask(gu, row_valid, self.act, self.arch.swiglu_limit, self.arch.swiglu_alpha)
+            return ops.gemm(h, self.down_proj, block_expert=block_expert, out=out, row_valid=row_valid)
         if self.fp8 is not None and not torch.is_grad_enabled() and xp.dtype == torch.bfloat16:
             from ..ops import fp8 as fp8_ops
 
@@ -363,8 +375,13 @@ class MoE(nn.Module):
             y = self.dispatcher(self.experts, xe, idx, w, counts)
         else:
             plan = moe_ops.build_plan(idx, counts, self.arch.num_experts)
-            xp = moe_ops.permute(xe, plan)
-            yp = self.experts(xp, plan.block_expert, plan.expert_offset)
+            if self.experts.supports_row_mask(xe) and xe.shape[1] % 8 == 0:
+                # inference: nothing touches the rows that only pad every expert to a multiple of 128
+                xp = moe_ops.permute_nopad(xe, plan)
+                yp = self.experts(xp, plan.block_expert, plan.expert_offset, row_valid=plan.row_src)
+            else:
+                xp = moe_ops.permute(xe, plan)
+                yp = self.experts(xp, plan.block_expert, plan.expert_offset)
             y = moe_ops.combine(yp, w, plan, T)
         if self.fc2_latent_proj is not None:
             y = self.fc2_latent_proj(y)

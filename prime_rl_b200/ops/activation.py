@@ -58,6 +58,23 @@ class _GLU(torch.autograd.Function):
         return dgu, None, None, None
 
 
+def glu_rowmask(gate_up: torch.Tensor, row_valid: torch.Tensor, act: int = SWIGLU, limit: float = 7.0,
+                alpha: float = 1.702) -> torch.Tensor:
+    """Inference-only ``glu`` over the padded row space of grouped experts: rows with ``row_valid < 0``
+    (int32 per row) are neither read nor written, their outputs stay uninitialised."""
+    rows = gate_up.shape[0]
+    I = gate_up.shape[1] if act == RELU2 else gate_up.shape[1] // 2
+    assert gate_up.is_cuda and gate_up.dtype == torch.bfloat16 and gate_up.is_contiguous() and I % 8 == 0
+    assert act != SILU_CLAMPED and row_valid.dtype == torch.int32 and row_valid.numel() >= rows
+    y = torch.empty(rows, I, dtype=gate_up.dtype, device=gate_up.device)
+    g_ptr = gate_up.data_ptr()
+    rc = rt.lib().prb_glu_fwd_rowmask(g_ptr, g_ptr + I * gate_up.element_size(), y.data_ptr(), rows, I, gate_up.stride(0),
+                                      y.stride(0), act, float(limit), float(alpha), row_valid.data_ptr(),
+                                      rt.stream_ptr(gate_up.device))
+    rt.check(rc, "prb_glu_fwd_rowmask")
+    return y
+
+
 def glu(gate_up: torch.Tensor, act: int = SWIGLU, limit: float = 7.0, alpha: float = 1.702) -> torch.Tensor:
     """``gate_up`` holds ``[gate | up]`` along the last dim (just ``gate`` for ReLU^2)."""
     shape = gate_up.shape

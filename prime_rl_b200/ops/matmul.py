@@ -46,6 +46,7 @@ def gemm(
     n: int | None = None,
     force_bn: int = 0,
     ext: tuple[torch.Tensor, torch.Tensor] | None = None,
+    row_valid: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """C = alpha * A.B + beta * C. Grouped mode when ``block_expert`` is given: ``b`` is the
     stacked expert weight ``[E, rows, cols]`` and ``n`` the output width. ``ext = (a2, b2)`` adds
@@ -112,6 +113,17 @@ def gemm(
             status.data_ptr(), rt.stream_ptr(a.device),
         )
         rt.check(rc, "prb_gemm_bf16_ext")
+        return out
+    if row_valid is not None:
+        # inference-only: rows with row_valid < 0 (int32 per row of C) are not stored
+        assert row_valid.dtype == torch.int32 and row_valid.numel() >= M and not a_mn
+        rc = rt.lib().prb_gemm_bf16_rowmask(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), ldb, out.stride(0),
+            int(a_mn), int(b_mn), int(out.dtype == torch.float32), float(alpha), float(beta),
+            rt.ptr(block_expert), int(num_experts), int(b_rows_per_expert), int(force_bn),
+            row_valid.data_ptr(), status.data_ptr(), rt.stream_ptr(a.device),
+        )
+        rt.check(rc, "prb_gemm_bf16_rowmask")
         return out
     rc = rt.lib().prb_gemm_bf16(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), ldb, out.stride(0),

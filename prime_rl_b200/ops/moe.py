@@ -154,12 +154,13 @@ class _Combine(torch.autograd.Function):
         return dp, dw, None, None
 
 
-def _gather_rows(x, plan: RoutingPlan, w):
+def _gather_rows(x, plan: RoutingPlan, w, zero_pad: bool = True):
     P, H = plan.max_rows, x.shape[1]
     if x.is_cuda and x.dtype == torch.bfloat16 and H % 8 == 0:
         out = torch.empty(P, H, dtype=x.dtype, device=x.device)
-        rc = rt.lib().prb_moe_gather_rows(x.data_ptr(), plan.row_src.data_ptr(), rt.ptr(w), out.data_ptr(), P, H,
-                                          plan.k, plan.total_rows.data_ptr(), rt.stream_ptr(x.device))
+        fn = rt.lib().prb_moe_gather_rows if zero_pad else rt.lib().prb_moe_gather_rows_nopad
+        rc = fn(x.data_ptr(), plan.row_src.data_ptr(), rt.ptr(w), out.data_ptr(), P, H,
+                plan.k, plan.total_rows.data_ptr(), rt.stream_ptr(x.device))
         rt.check(rc, "prb_moe_gather_rows")
         return out
     src = plan.row_src.long()
@@ -192,6 +193,12 @@ def _combine(p, plan: RoutingPlan, w, residual, T):
 
 def permute(x: torch.Tensor, plan: RoutingPlan) -> torch.Tensor:
     return _Permute.apply(x, plan)
+
+
+def permute_nopad(x: torch.Tensor, plan: RoutingPlan) -> torch.Tensor:
+    """Inference-only ``permute``: the padding rows (``plan.row_src < 0``) are left uninitialised; the grouped
+    GEMMs / GLU that follow must be given ``row_valid=plan.row_src`` so that they skip those rows."""
+    return _gather_rows(x, plan, None, zero_pad=False)
 
 
 def combine(p: torch.Tensor, w: torch.Tensor, plan: RoutingPlan, num_tokens: int) -> torch.Tensor:

@@ -751,3 +751,32 @@ def test_allreduce_add_rmsnorm_kernel_with_emulated_peers():
                                          R, rt.status_tensor(dev).data_ptr(), rt.stream_ptr(dev)), "prb_ar_add_rmsnorm")
     torch.cuda.synchronize()
     torch.testing.assert_close(out_h.float(), parts[0].float() + parts[1].float(), atol=0.04, rtol=0.01)
+
+
+def test_moe_inference_path_skips_padding_rows_and_matches_the_training_path():
+    """Under no_grad the MoE layer leaves the rows that pad every expert to 128 untouched (no zero fill, no
+    GLU, no GEMM stores); the tokens' outputs must be bit-identical to the regular path."""
+    from prime_rl_b200.models import ModelArch, SeqInfo
+    from prime_rl_b200.models.layers import MoE
+
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    arch = ModelArch(model_type="qwen3_moe", hidden_size=512, num_hidden_layers=1, num_attention_heads=4,
+                     num_key_value_heads=2, head_dim=128, intermediate_size=512, num_experts=16, num_experts_per_tok=4,
+                     moe_intermediate_size=256, vocab_size=256)
+    moe = MoE(arch, 0, dtype=torch.bfloat16, device=dev)
+    with torch.no_grad():
+        for p in moe.parameters():
+            p.normal_(0, 0.05)
+    x = torch.randn(37, 512, device=dev).bfloat16()
+    seq = SeqInfo(None, 0, torch.arange(37, dtype=torch.int32, device=dev))
+    # poison the allocator's free blocks so that untouched padding rows hold NaNs
+    junk = torch.full((64 * 128, 512), float("nan"), device=dev, dtype=torch.bfloat16)
+    del junk
+    with torch.no_grad():
+        assert moe.experts.supports_row_mask(x)
+        y_inf = moe(x, seq)
+        moe.experts.supports_row_mask = lambda _x: False          # same arithmetic through the zero-padded path
+        y_ref = moe(x, seq)
+    assert torch.isfinite(y_inf.float()).all()
+    assert torch.equal(y_inf, y_ref)
