@@ -288,6 +288,83 @@ qknorm_rope_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
 }
 
+
+// Inference: the packed projection qkv [T, (nq + 2 nkv) * D] -> q [T, nq, D] (norm + rotary) and, in the same
+// launch, K (norm + rotary) and V written into the paged cache at slot[t] (cache rows of nkv * D elements) and,
+// when k_out / v_out are given, also as contiguous [T, nkv, D] tensors. One warp per (token, head); the
+// arithmetic is the one of qknorm_rope_kernel, so the engine and the trainer see the same values.
+template <int D>
+__global__ void __launch_bounds__(256)
+qkv_rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ qw,
+                      const __nv_bfloat16* __restrict__ kw, const int* __restrict__ pos,
+                      const float* __restrict__ inv_freq, const long long* __restrict__ slot,
+                      __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out,
+                      __nv_bfloat16* __restrict__ v_out, __nv_bfloat16* __restrict__ k_cache,
+                      __nv_bfloat16* __restrict__ v_cache, long long T, int nq, int nkv, float eps) {
+  constexpr int EPL = D / 32;
+  const int lane = threadIdx.x & 31;
+  const int heads = nq + 2 * nkv;
+  const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= T * heads) return;
+  const long long t = item / heads;
+  const int h = static_cast<int>(item - t * heads);
+  const int e0 = lane * EPL;
+  float xv[EPL];
+  {
+    const __nv_bfloat16* src = qkv + t * (static_cast<long long>(heads) * D) + static_cast<long long>(h) * D + e0;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) xv[i] = __bfloat162float(src[i]);
+  }
+  const bool is_q = h < nq, is_v = h >= nq + nkv;
+  const int hk = is_q ? h : (is_v ? h - nq - nkv : h - nq);      // head index inside its own tensor
+  __nv_bfloat16 res[EPL];
+  if (is_v) {
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) res[i] = __float2bfloat16(xv[i]);
+  } else {
+    const __nv_bfloat16* w = is_q ? qw : kw;
+    const float p = static_cast<float>(pos[t]);
+    float cs[EPL], sn[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      const int fi = (e0 + i) % (D / 2);
+      sincosf(p * inv_freq[fi], &sn[i], &cs[i]);
+    }
+    const bool upper = e0 >= D / 2;
+    if (w) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) ss += xv[i] * xv[i];
+      ss = warp_sum(ss);
+      const float rstd = rsqrtf(ss / D + eps);
+#pragma unroll
+      for (int i = 0; i < EPL; ++i)
+        xv[i] = __bfloat162float(__float2bfloat16(xv[i] * rstd * __bfloat162float(w[e0 + i])));
+    }
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      const float other = __shfl_xor_sync(0xffffffffu, xv[i], 16);
+      const float r = upper ? (xv[i] * cs[i] + other * sn[i]) : (xv[i] * cs[i] - other * sn[i]);
+      res[i] = __float2bfloat16(r);
+    }
+  }
+  if (is_q) {
+    __nv_bfloat16* dst = q_out + (t * nq + hk) * D + e0;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) dst[i] = res[i];
+    return;
+  }
+  __nv_bfloat16* lin = is_v ? v_out : k_out;
+  if (lin != nullptr) {
+    __nv_bfloat16* dst = lin + (t * nkv + hk) * D + e0;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) dst[i] = res[i];
+  }
+  __nv_bfloat16* dst = (is_v ? v_cache : k_cache) + (slot[t] * nkv + hk) * D + e0;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) dst[i] = res[i];
+}
+
 }  // namespace prb
 
 using namespace prb;
@@ -366,6 +443,28 @@ PRB_API int prb_qknorm_rope(const void* x, const void* gin, const void* w, const
   if (D == 128) { if (bwd) LAUNCH(128, true); else LAUNCH(128, false); }
   else if (D == 64) { if (bwd) LAUNCH(64, true); else LAUNCH(64, false); }
   else if (D == 256) { if (bwd) LAUNCH(256, true); else LAUNCH(256, false); }
+  else return -2;
+#undef LAUNCH
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// qkv bf16 [T, (nq + 2 nkv) * D] contiguous; qw / kw bf16 [D] or null (no QK norm); pos int32 [T]; slot int64 [T]
+// (row of the flattened cache [pages * page_size, nkv, D]); k_out / v_out may be null.
+PRB_API int prb_qkv_rope_cache(const void* qkv, const void* qw, const void* kw, const int* pos, const float* inv_freq,
+                               const long long* slot, void* q_out, void* k_out, void* v_out, void* k_cache,
+                               void* v_cache, long long T, int nq, int nkv, int D, float eps, void* stream) {
+  if (T == 0) return 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const long long items = T * (nq + 2 * nkv);
+  const unsigned grid = static_cast<unsigned>((items + 7) / 8);
+#define LAUNCH(DD)                                                                                                  \
+  prb::qkv_rope_cache_kernel<DD><<<grid, 256, 0, s>>>(                                                               \
+      (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, pos, inv_freq, slot,           \
+      (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out, (__nv_bfloat16*)k_cache,                 \
+      (__nv_bfloat16*)v_cache, T, nq, nkv, eps)
+  if (D == 128) LAUNCH(128);
+  else if (D == 64) LAUNCH(64);
+  else if (D == 256) LAUNCH(256);
   else return -2;
 #undef LAUNCH
   return cudaGetLastError() == cudaSuccess ? 0 : -11;

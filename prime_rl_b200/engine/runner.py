@@ -108,12 +108,14 @@ class ModelRunner:
                 x = layer.input_layernorm(h)
             qkv = at.qkv_proj(x)
             eps = self.arch.rms_norm_eps
-            # one kernel: split, q / k RMSNorm, rotary, contiguous q, k, v
-            q, k, v = ops.qkv_norm_rope(qkv, at.q_norm.weight if at.q_norm is not None else None,
-                                        at.k_norm.weight if at.k_norm is not None else None, pos_t, at.inv_freq, eps,
-                                        at.nq, at.nkv, at.D)
-            cache.write(li, k, v, slots_t)
-            o = self._attend(li, q, k, v.contiguous(), batch, starts, at.window, at.sinks)
+            # one kernel: split, q / k RMSNorm, rotary, K / V into their cache slots; a paged decode step reads
+            # K / V from the cache only, so it asks for no contiguous copies
+            paged = self._decode_meta is not None and at.sinks is None and at.window is None
+            q, k, v = ops.qkv_rope_to_cache(qkv, at.q_norm.weight if at.q_norm is not None else None,
+                                            at.k_norm.weight if at.k_norm is not None else None, pos_t, at.inv_freq,
+                                            eps, at.nq, at.nkv, at.D, cache.k[li], cache.v[li], slots_t,
+                                            want_kv=not paged)
+            o = self._attend(li, q, k, v, batch, starts, at.window, at.sinks)
             a = at.finish(o, x)
             # residual add + norm in one kernel; with TP the same kernel also sums the ranks' partial outputs
             x2, h = add_norm(a, h, layer.post_attention_layernorm.weight, layer.post_attention_layernorm.eps)

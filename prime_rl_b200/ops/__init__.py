@@ -6,4 +6,4 @@ from .matmul import gemm, gemm_ref, grouped_gemm_ref, grouped_linear, linear  # 
 from .lm_head import (fused_logprob_entropy, logprob_entropy_ref, replay_sampling_mask,  # noqa: F401
                       softcapped_logprob_entropy)
 from .norm import add_rms_norm, rms_norm, rms_norm_ref  # noqa: F401
-from .rope import inv_freq, qknorm_rope, qknorm_rope_ref, qkv_norm_rope  # noqa: F401
+from .rope import inv_freq, qknorm_rope, qknorm_rope_ref, qkv_norm_rope, qkv_rope_to_cache  # noqa: F401

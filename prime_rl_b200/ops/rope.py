@@ -138,3 +138,32 @@ def qkv_norm_rope(qkv: torch.Tensor, qw, kw, pos, inv_f, eps: float, nq: int, nk
     k = qkv[:, qd:qd + kd].view(T, nkv, D)
     v = qkv[:, qd + kd:].view(T, nkv, D)
     return qknorm_rope(q, qw, pos, inv_f, eps), qknorm_rope(k, kw, pos, inv_f, eps), v
+
+
+def qkv_rope_to_cache(qkv: torch.Tensor, qw, kw, pos, inv_f, eps: float, nq: int, nkv: int, D: int,
+                      k_cache: torch.Tensor, v_cache: torch.Tensor, slots: torch.Tensor, want_kv: bool = True):
+    """Inference-only: ``qkv_norm_rope`` plus the write of K / V into the paged cache
+    (``k_cache`` / ``v_cache``: [pages, page_size, nkv, D]; ``slots``: int64 [T] rows of the flattened cache)
+    in ONE launch. Returns (q, k, v); k and v are None unless ``want_kv`` (a decode step reads them
+    from the cache only). Falls back to the separate ops where the kernel does not apply."""
+    T = qkv.shape[0]
+    fused = (qkv.is_cuda and qkv.dtype == torch.bfloat16 and D in (64, 128, 256) and inv_f.numel() * 2 == D
+             and qkv.is_contiguous() and (qw is None or qw.dtype == torch.bfloat16) and k_cache.dtype == torch.bfloat16
+             and k_cache.is_contiguous() and v_cache.is_contiguous() and slots.dtype == torch.int64
+             and not torch.is_grad_enabled())
+    if not fused:
+        q, k, v = qkv_norm_rope(qkv, qw, kw, pos, inv_f, eps, nq, nkv, D)
+        kf, vf = k_cache.view(-1, nkv, D), v_cache.view(-1, nkv, D)
+        kf.index_copy_(0, slots, k.to(kf.dtype))
+        vf.index_copy_(0, slots, v.to(vf.dtype))
+        return q, k, v
+    pos32 = pos.to(torch.int32)
+    q = torch.empty(T, nq, D, dtype=qkv.dtype, device=qkv.device)
+    k = torch.empty(T, nkv, D, dtype=qkv.dtype, device=qkv.device) if want_kv else None
+    v = torch.empty_like(k) if want_kv else None
+    rc = rt.lib().prb_qkv_rope_cache(qkv.data_ptr(), rt.ptr(qw), rt.ptr(kw), pos32.data_ptr(),
+                                     inv_f.data_ptr(), slots.data_ptr(), q.data_ptr(), rt.ptr(k), rt.ptr(v),
+                                     k_cache.data_ptr(), v_cache.data_ptr(), T, nq, nkv, D, float(eps),
+                                     rt.stream_ptr(qkv.device))
+    rt.check(rc, "prb_qkv_rope_cache")
+    return q, k, v

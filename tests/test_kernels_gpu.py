@@ -780,3 +780,35 @@ def test_moe_inference_path_skips_padding_rows_and_matches_the_training_path():
         y_ref = moe(x, seq)
     assert torch.isfinite(y_inf.float()).all()
     assert torch.equal(y_inf, y_ref)
+
+
+def test_qkv_rope_to_cache_matches_separate_ops():
+    """Fused split + QK-norm + rotary + paged-cache write against qkv_norm_rope followed by index_copy_
+    (bit-equal), with and without the contiguous K / V outputs and without QK-norm."""
+    from prime_rl_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    T, nq, nkv, D, pages, ps = 77, 8, 2, 128, 12, 16
+    qkv = torch.randn(T, (nq + 2 * nkv) * D, device=dev).bfloat16()
+    qw = (1 + 0.1 * torch.randn(D, device=dev)).bfloat16()
+    kw = (1 + 0.1 * torch.randn(D, device=dev)).bfloat16()
+    pos = torch.randint(0, 4000, (T,), device=dev, dtype=torch.int32)
+    inv_f = ops.inv_freq(D, 1e6, device=dev)
+    slots = torch.randperm(pages * ps, device=dev)[:T]
+    for norm in (True, False):
+        a, b = (qw, kw) if norm else (None, None)
+        with torch.no_grad():
+            q0, k0, v0 = ops.qkv_norm_rope(qkv, a, b, pos, inv_f, 1e-6, nq, nkv, D)
+            kc0 = torch.zeros(pages, ps, nkv, D, device=dev, dtype=torch.bfloat16)
+            vc0 = torch.zeros_like(kc0)
+            kc0.view(-1, nkv, D).index_copy_(0, slots, k0)
+            vc0.view(-1, nkv, D).index_copy_(0, slots, v0)
+            for want in (True, False):
+                kc, vc = torch.zeros_like(kc0), torch.zeros_like(vc0)
+                q, k, v = ops.qkv_rope_to_cache(qkv, a, b, pos, inv_f, 1e-6, nq, nkv, D, kc, vc, slots, want_kv=want)
+                assert torch.equal(q, q0) and torch.equal(kc, kc0) and torch.equal(vc, vc0)
+                if want:
+                    assert torch.equal(k, k0) and torch.equal(v, v0)
+                else:
+                    assert k is None and v is None
