@@ -467,8 +467,16 @@ ep_pull_kernel(EpPeers src, const int* __restrict__ topk_idx, const int* __restr
 // Same role as the custom all-reduce + fused add-RMSNorm passes of the serving engine the reference
 // drives (vLLM tensor parallelism, packages/prime-rl-configs/src/prime_rl/configs/inference.py:88-97).
 constexpr int kArThreads = 256;
-constexpr int kArMaxVec = 4;            // 16-byte vectors per thread: cols <= 4 * 256 * 8 = 8192
 
+__device__ __forceinline__ void ar_accumulate(float (&acc)[8], const uint4& u) {
+  const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+  acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+  acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+}
+
+// MAXVEC: 16-byte vectors per thread (cols <= MAXVEC * 256 * 8): 1 covers hidden sizes up to 2048 with few
+// registers (more CTAs per SM to hide the peer-load latency), 4 up to 8192.
+template <int MAXVEC>
 __global__ void __launch_bounds__(kArThreads)
 ar_add_rmsnorm_kernel(EpPeers partial, EpPeers flags, int* __restrict__ state, const __nv_bfloat16* __restrict__ residual,
                       const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out_h,
@@ -487,26 +495,29 @@ ar_add_rmsnorm_kernel(EpPeers partial, EpPeers flags, int* __restrict__ state, c
   if (ok) {
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
       const long long base = static_cast<long long>(row) * cols;
-      float acc[kArMaxVec][8];
+      float acc[MAXVEC][8];
       float ss = 0.f;
 #pragma unroll
-      for (int i = 0; i < kArMaxVec; ++i) {
+      for (int i = 0; i < MAXVEC; ++i) {
         const int v = threadIdx.x + i * kArThreads;
         if (v >= nvec) break;
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
-        for (int r = 0; r < R; ++r) {
-          const uint4 u = __ldcv(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(partial.buf[r]) + base) + v);
-          const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
-          acc[i][0] += a.x; acc[i][1] += a.y; acc[i][2] += b.x; acc[i][3] += b.y;
-          acc[i][4] += c.x; acc[i][5] += c.y; acc[i][6] += d.x; acc[i][7] += d.y;
+        // all loads of a group of four ranks are issued before the first add; the adds keep the rank order,
+        // so every rank computes bit-identical sums
+        uint4 rv = make_uint4(0u, 0u, 0u, 0u);
+        if (residual != nullptr) rv = *(reinterpret_cast<const uint4*>(residual + base) + v);
+        for (int r0 = 0; r0 < R; r0 += 4) {
+          uint4 pv[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (r0 + j < R)
+              pv[j] = __ldcv(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(partial.buf[r0 + j]) + base) + v);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (r0 + j < R) ar_accumulate(acc[i], pv[j]);
         }
-        if (residual != nullptr) {
-          const uint4 u = *(reinterpret_cast<const uint4*>(residual + base) + v);
-          const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
-          acc[i][0] += a.x; acc[i][1] += a.y; acc[i][2] += b.x; acc[i][3] += b.y;
-          acc[i][4] += c.x; acc[i][5] += c.y; acc[i][6] += d.x; acc[i][7] += d.y;
-        }
+        if (residual != nullptr) ar_accumulate(acc[i], rv);
         // the residual stream is stored in bf16: normalise what the next layer will read
         uint4 o;
         o.x = pack_bf16(acc[i][0], acc[i][1]); o.y = pack_bf16(acc[i][2], acc[i][3]);
@@ -528,7 +539,7 @@ ar_add_rmsnorm_kernel(EpPeers partial, EpPeers flags, int* __restrict__ state, c
         __syncthreads();
         const float rstd = rsqrtf(tot / static_cast<float>(cols) + eps);
 #pragma unroll
-        for (int i = 0; i < kArMaxVec; ++i) {
+        for (int i = 0; i < MAXVEC; ++i) {
           const int v = threadIdx.x + i * kArThreads;
           if (v >= nvec) break;
           const uint4 wu = *(reinterpret_cast<const uint4*>(w) + v);
@@ -736,13 +747,18 @@ PRB_API int prb_ep_pull(void* const* src_peers, const int* topk_idx, const int* 
 PRB_API int prb_ar_add_rmsnorm(void* const* partial_peers, void* const* flag_peers, int* state, const void* residual,
                                const void* w, void* out_h, void* out_x, int rows, int cols, float eps, int rank, int R,
                                int* status, void* stream) {
-  if (R > prb::kEpMaxRanks || R < 1 || cols % 8 || cols > prb::kArMaxVec * prb::kArThreads * 8) return -2;
+  if (R > prb::kEpMaxRanks || R < 1 || cols % 8 || cols > 4 * prb::kArThreads * 8) return -2;
   if (out_x != nullptr && w == nullptr) return -2;
   if (rows <= 0) return 0;
-  const int grid = rows < 148 * 4 ? rows : 148 * 4;
-  prb::ar_add_rmsnorm_kernel<<<grid, prb::kArThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      ep_peers(partial_peers, R), ep_peers(flag_peers, R), state, reinterpret_cast<const __nv_bfloat16*>(residual),
-      reinterpret_cast<const __nv_bfloat16*>(w), reinterpret_cast<__nv_bfloat16*>(out_h),
-      reinterpret_cast<__nv_bfloat16*>(out_x), rows, cols, eps, rank, R, status);
+  const bool narrow = cols <= prb::kArThreads * 8;
+  const int cap = 148 * (narrow ? 6 : 3);
+  const int grid = rows < cap ? rows : cap;
+#define PRB_AR_LAUNCH(MV)                                                                                            \
+  prb::ar_add_rmsnorm_kernel<MV><<<grid, prb::kArThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(              \
+      ep_peers(partial_peers, R), ep_peers(flag_peers, R), state, reinterpret_cast<const __nv_bfloat16*>(residual),  \
+      reinterpret_cast<const __nv_bfloat16*>(w), reinterpret_cast<__nv_bfloat16*>(out_h),                            \
+      reinterpret_cast<__nv_bfloat16*>(out_x), rows, cols, eps, rank, R, status)
+  if (narrow) PRB_AR_LAUNCH(1); else PRB_AR_LAUNCH(4);
+#undef PRB_AR_LAUNCH
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

@@ -8,6 +8,7 @@ GPU's own buffer), so that a single-GPU profiler capture can look at them:
     python -m prime_rl_b200.parallel.single_rank_profile --op ag      # GEMM with the all-gather prologue (2 emulated ranks)
     python -m prime_rl_b200.parallel.single_rank_profile --op cp      # flash forward with the K/V gather warp (2 emulated ranks)
     python -m prime_rl_b200.parallel.single_rank_profile --op zero    # optimizer reduce-scatter pull / all-gather push
+    python -m prime_rl_b200.parallel.single_rank_profile --op tp      # engine all-reduce + residual + RMSNorm (2 emulated ranks)
 
 The traffic that would cross NVLink stays in local HBM here; instruction mix, occupancy and
 local-memory behaviour are what such a capture shows.
@@ -24,7 +25,7 @@ import torch.distributed as dist
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--op", required=True, choices=["ep", "ep8", "rs", "push", "ag", "cp", "zero"])
+    ap.add_argument("--op", required=True, choices=["ep", "ep8", "rs", "push", "ag", "cp", "zero", "tp"])
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=2)
     args = ap.parse_args(argv)
@@ -66,6 +67,23 @@ def main(argv=None):
         counters = torch.zeros(3, dtype=torch.int32, device=dev)
         for _ in range(args.iters):
             flash_native.flash_fwd_gather(q, bufs[1][0], bufs[1][1], ptrs, cu, 1, 2, counters)
+    elif args.op == "tp":
+        import ctypes
+
+        rows, cols = args.tokens, 2048                            # "rank 0" of 2; the peer's flag slot is set beforehand
+        parts = [torch.randn(rows, cols, device=dev).bfloat16() for _ in range(2)]
+        res = torch.randn(rows, cols, device=dev).bfloat16()
+        w = torch.ones(cols, dtype=torch.bfloat16, device=dev)
+        flags = [torch.zeros(2, dtype=torch.int32, device=dev) for _ in range(2)]
+        flags[0][1] = 1 << 30
+        pp = (ctypes.c_void_p * 2)(*[p.data_ptr() for p in parts])
+        fp = (ctypes.c_void_p * 2)(*[f.data_ptr() for f in flags])
+        state = torch.zeros(2, dtype=torch.int32, device=dev)
+        out_h, out_x = torch.empty_like(res), torch.empty_like(res)
+        for _ in range(args.iters):
+            rt.check(rt.lib().prb_ar_add_rmsnorm(pp, fp, state.data_ptr(), res.data_ptr(), w.data_ptr(), out_h.data_ptr(),
+                                                 out_x.data_ptr(), rows, cols, 1e-6, 0, 2, rt.status_tensor(dev).data_ptr(),
+                                                 rt.stream_ptr(dev)), "prb_ar_add_rmsnorm")
     elif args.op == "zero":
         import ctypes
 
