@@ -273,6 +273,11 @@ class Engine:
             batch = [r for r in self.running if r.prefilled and r.finish_reason is None]
         if batch:
             self._decode(batch)
+        if self.tp_size > 1 and self.device.type == "cuda":
+            # a reduce whose bounded wait ran out (a peer that left) wrote nothing: fail the step, not the tokens
+            from ..ops import _runtime as rt
+
+            rt.check_status(self.device)
 
     # ------------------------------------------------------------------ prefill
     def _prefill(self, reqs: list[Request]) -> None:

@@ -812,3 +812,33 @@ def test_qkv_rope_to_cache_matches_separate_ops():
                     assert torch.equal(k, k0) and torch.equal(v, v0)
                 else:
                     assert k is None and v is None
+
+
+def test_allreduce_kernel_wait_runs_out_when_the_peer_never_arrives():
+    """The peer's flag slot stays 0: the bounded wait of the tensor-parallel reduce gives up (about 2 s of GPU
+    time), records kTimeoutPeerFlag, writes nothing, still advances its call counter and returns; the device
+    keeps answering. This is what a rank sees when its peer has left between two steps."""
+    import ctypes
+
+    from prime_rl_b200.ops import _runtime as rt
+
+    dev = torch.device("cuda", 0)
+    rows, cols, R = 4, 256, 2
+    parts = [torch.ones(rows, cols, device=dev).bfloat16() for _ in range(R)]
+    flags = [torch.zeros(R, dtype=torch.int32, device=dev) for _ in range(R)]
+    pp = (ctypes.c_void_p * R)(*[p.data_ptr() for p in parts])
+    fp = (ctypes.c_void_p * R)(*[f.data_ptr() for f in flags])
+    state = torch.zeros(2, dtype=torch.int32, device=dev)
+    out_h = torch.full((rows, cols), 7.0, device=dev).bfloat16()
+    st = rt.status_tensor(dev)
+    st.zero_()
+    rc = rt.lib().prb_ar_add_rmsnorm(pp, fp, state.data_ptr(), None, None, out_h.data_ptr(), None, rows, cols, 1e-6, 0, R,
+                                     st.data_ptr(), rt.stream_ptr(dev))
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(st.item()) == 5            # kTimeoutPeerFlag
+    with pytest.raises(Exception):
+        rt.check_status()
+    st.zero_()
+    assert float(out_h.float().min()) == 7.0 and state.tolist() == [1, 0]
+    assert float((torch.ones(4, device=dev) * 2).sum()) == 8.0      # the device still answers
