@@ -17,6 +17,11 @@ import torch
 from . import _runtime as rt
 
 
+# Inference-only dispatch of small plain GEMMs (no groups, no fused epilogue, M <= SMALL_M_ROWS) to cuBLAS.
+SMALL_M_LIBRARY = True
+SMALL_M_ROWS = 512
+
+
 def gemm_ref(a, b, *, a_mn=False, b_mn=False, out_dtype=None, alpha=1.0, beta=0.0, out=None):
     A = a.t() if a_mn else a
     B = b if b_mn else b.t()
@@ -89,6 +94,16 @@ def gemm(
         # per-head gate) are not worth a copy into padded buffers
         return gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=out_dtype or (out.dtype if out is not None else None),
                         alpha=alpha, beta=beta, out=out)
+    if (SMALL_M_LIBRARY and M <= SMALL_M_ROWS and not grouped and ext is None and row_valid is None and not a_mn
+            and not b_mn and alpha == 1.0 and beta == 0.0 and not torch.is_grad_enabled()):
+        # decode-sized plain projections in inference: the library GEMM has the lower fixed cost there
+        # (13 us against 27 us for 256 x 5120 x 2048); everything with gradients, large M, groups or fused
+        # epilogues stays on the tcgen05 kernel
+        want = out_dtype or (out.dtype if out is not None else torch.bfloat16)
+        if want == torch.bfloat16:
+            return torch.matmul(a, b.t(), out=out) if out is not None else torch.matmul(a, b.t())
+        if want == torch.float32 and out is None:
+            return torch.mm(a, b.t(), out_dtype=torch.float32)
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=a.device)
         assert beta == 0.0
