@@ -49,6 +49,8 @@ def parse_args():
     ap.add_argument("--mode", default="lora", choices=["lora", "full"])
     ap.add_argument("--layers", type=int, default=None, help="debug: truncate the model (result is not a bench value)")
     ap.add_argument("--attn", default="auto")
+    ap.add_argument("--no-rollout-decode", action="store_true",
+                    help="skip the second measurement (rollout decode tokens/s of the engine, one replica per GPU)")
     return ap.parse_args()
 
 
@@ -191,6 +193,39 @@ def main():
     dev_ms, e2e_s = t.tolist()
     value = tokens_per_step * args.steps / (dev_ms / 1e3)
     e2e = tokens_per_step * args.steps / e2e_s
+    loss_value, mfu, peak_gib = m.get("loss"), trainer.perf.mfu(value), torch.cuda.max_memory_allocated(dev) / 2 ** 30
+
+    # ------------------------------------------------------------ second number of the headline: rollout decode
+    # One engine replica per GPU (data-parallel serving), 256 requests of 1024 prompt tokens each, 16 timed
+    # decode steps through Engine.step; aggregate tokens/s = sum over replicas, step time = slowest replica.
+    rollout = None
+    if not args.no_rollout_decode:
+        import gc
+        import math
+
+        local, err = [float("nan"), float("nan")], None
+        try:
+            from prime_rl_b200.engine.bench_decode import run_decode
+
+            del trainer, mbs
+            gc.collect()
+            torch.cuda.empty_cache()
+            r = run_decode(args.model, batch=256, prompt=1024, steps=16, warmup=4, layers=args.layers, dev=dev)
+            local = [r["decode_tokens_per_s"], r["ms_per_step"]]
+        except Exception as e:  # the trainer number stands on its own
+            err = f"{type(e).__name__}: {e}"[:300]
+        t = torch.tensor(local, dtype=torch.float64, device=dev)
+        if n > 1:                                   # every rank takes part, whatever happened to its own replica
+            tot = t.clone()
+            dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            t[0] = tot[0]
+        if math.isnan(float(t[0])) or math.isnan(float(t[1])):
+            rollout = {"error": err or "an engine replica on another rank failed"}
+        else:
+            rollout = {"metric": "rollout decode tokens/s", "value": float(t[0]), "unit": "tokens/s",
+                       "ms_per_step": float(t[1]), "batch_per_gpu": 256, "prompt_len": 1024, "steps": 16,
+                       "parallelism": f"dp{n} (one engine replica per GPU)", "cuda_graphs": True, "dtype": "bf16"}
     if world.rank == 0:
         print(json.dumps({
             "metric": "RL trainer tokens/s, Qwen3-30B-A3B shape", "value": value, "unit": "tokens/s", "n_gpus": n,
@@ -207,8 +242,8 @@ def main():
                        "vs_baseline_note": "reference 9266 tok/s on 8 GPUs, scaled by n_gpus/8"},
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": launches, "loss": m.get("loss"), "mfu_percent": trainer.perf.mfu(value),
-            "peak_memory_gib": torch.cuda.max_memory_allocated(dev) / 2 ** 30,
+            "gpu_launches": launches, "loss": loss_value, "mfu_percent": mfu,
+            "peak_memory_gib": peak_gib, "rollout_decode": rollout,
         }))
     if n > 1:
         dist.barrier()

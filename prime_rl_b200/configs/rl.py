@@ -229,6 +229,11 @@ class RLConfig(BaseConfig):
                 if d.num_infer_gpus % tp:
                     raise ValueError("num_infer_gpus must be a multiple of inference tensor_parallel_size")
                 i.vllm.data_parallel_size = max(1, d.num_infer_gpus // tp)
+                if tp > 1 and getattr(t.weight_broadcast, "type", "filesystem") != "filesystem":
+                    # only rank 0 of a tensor-parallel engine answers the admin routes; every rank loads its
+                    # slices from the checkpoint directory
+                    raise ValueError("tensor-parallel inference engines take weight updates through "
+                                     "weight_broadcast.type = 'filesystem'")
                 if hasattr(t.weight_broadcast, "inference_world_size"):
                     t.weight_broadcast.inference_world_size = d.num_infer_gpus
                     if hasattr(o.weight_broadcast, "inference_world_size"):

@@ -19,13 +19,12 @@ template <int ACT>
 __global__ void __launch_bounds__(256)
 glu_fwd_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
                __nv_bfloat16* __restrict__ y, long long rows, int cols, long long ld_in, long long ld_out,
-               float limit, float alpha_act, const int* __restrict__ row_valid) {
+               float limit, float alpha_act) {
   const int vec_per_row = cols >> 3;
   const long long total = rows * vec_per_row;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const long long r = i / vec_per_row;
-    if (row_valid != nullptr && row_valid[r] < 0) continue;      // padding row: neither read nor written
     const int c = static_cast<int>(i - r * vec_per_row) * 8;
     const uint4 gv = *reinterpret_cast<const uint4*>(g + r * ld_in + c);
     uint4 uv = make_uint4(0, 0, 0, 0);
@@ -56,6 +55,51 @@ glu_fwd_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restr
       ow[k] = pack_bf16(o0, o1);
     }
     *reinterpret_cast<uint4*>(y + r * ld_out + c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  }
+}
+
+// Row-masked variant for the padded row space of grouped experts in inference: one warp per row, the
+// validity of a row is looked up once, padding rows (row_valid < 0) cost one load.
+template <int ACT>
+__global__ void __launch_bounds__(256)
+glu_fwd_rows_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ u,
+                    __nv_bfloat16* __restrict__ y, long long rows, int cols, long long ld_in, long long ld_out,
+                    float limit, float alpha_act, const int* __restrict__ row_valid) {
+  const int lane = threadIdx.x & 31;
+  const int vec_per_row = cols >> 3;
+  for (long long r = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5); r < rows;
+       r += static_cast<long long>(gridDim.x) * 8) {
+    if (row_valid[r] < 0) continue;
+    for (int vi = lane; vi < vec_per_row; vi += 32) {
+      const int c = vi * 8;
+      const uint4 gv = *reinterpret_cast<const uint4*>(g + r * ld_in + c);
+      uint4 uv = make_uint4(0, 0, 0, 0);
+      if (ACT != kReLU2) uv = *reinterpret_cast<const uint4*>(u + r * ld_in + c);
+      const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+      const uint32_t uw[4] = {uv.x, uv.y, uv.z, uv.w};
+      uint32_t ow[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float2 gg = unpack_bf16(gw[k]);
+        float2 uu = unpack_bf16(uw[k]);
+        float o0, o1;
+        if (ACT == kSwiGLU) {
+          o0 = gg.x * sigmoidf_(gg.x) * uu.x;
+          o1 = gg.y * sigmoidf_(gg.y) * uu.y;
+        } else if (ACT == kSwiGLUClamped) {
+          const float g0 = fminf(gg.x, limit), g1 = fminf(gg.y, limit);
+          const float u0 = fminf(fmaxf(uu.x, -limit), limit), u1 = fminf(fmaxf(uu.y, -limit), limit);
+          o0 = g0 * sigmoidf_(alpha_act * g0) * (u0 + 1.f);
+          o1 = g1 * sigmoidf_(alpha_act * g1) * (u1 + 1.f);
+        } else {
+          const float r0 = fmaxf(gg.x, 0.f), r1 = fmaxf(gg.y, 0.f);
+          o0 = r0 * r0;
+          o1 = r1 * r1;
+        }
+        ow[k] = pack_bf16(o0, o1);
+      }
+      *reinterpret_cast<uint4*>(y + r * ld_out + c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
   }
 }
 
@@ -273,10 +317,19 @@ static int glu_fwd_launch(const void* g, const void* u, void* y, long long rows,
   if (cols % 8 || ld_in % 8 || ld_out % 8) return -1;
   if (rows == 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (row_valid != nullptr) {
+    long long blocks = (rows + 7) / 8;
+    if (blocks > 148LL * 64) blocks = 148LL * 64;
+#define LR(A) glu_fwd_rows_kernel<A><<<static_cast<unsigned>(blocks), 256, 0, s>>>(                                 \
+      (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (__nv_bfloat16*)y, rows, cols, ld_in, ld_out, limit, alpha_act, \
+      row_valid)
+    if (act == kSwiGLU) LR(kSwiGLU); else if (act == kSwiGLUClamped) LR(kSwiGLUClamped); else LR(kReLU2);
+#undef LR
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  }
   const unsigned grid = ew_grid(rows * (cols / 8));
-#define L(A) glu_fwd_kernel<A><<<grid, 256, 0, s>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)u,          \
-                                                     (__nv_bfloat16*)y, rows, cols, ld_in, ld_out, limit, alpha_act, \
-                                                     row_valid)
+#define L(A) glu_fwd_kernel<A><<<grid, 256, 0, s>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)u, \
+                                                     (__nv_bfloat16*)y, rows, cols, ld_in, ld_out, limit, alpha_act)
   if (act == kSwiGLU) L(kSwiGLU); else if (act == kSwiGLUClamped) L(kSwiGLUClamped); else L(kReLU2);
 #undef L
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
