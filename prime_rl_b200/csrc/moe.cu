@@ -23,9 +23,123 @@ namespace prb {
 constexpr int kMaxExperts = 512;
 constexpr int kMaxTopK = 16;
 
-// One warp per token. logits fp32 [T, E]. score_func: 0 softmax, 1 sigmoid.
-// sel_bias (nullable, fp32 [E]) is added for selection only. When `forced` (nullable, int32
-// [T, k]) is given those experts are used instead of the top-k (router replay).
+// Scores, top-k and weights of token t by one warp; the chosen experts are counted in s_hist (shared memory).
+// logits fp32 [T, E]. score_func: 0 softmax, 1 sigmoid. sel_bias (nullable, fp32 [E]) is added for
+// selection only. When `forced` (nullable, int32 [T, k]) is given those experts are used instead of
+// the top-k (router replay).
+__device__ __forceinline__ void router_token(const float* __restrict__ logits, const float* __restrict__ sel_bias,
+                                             const int* __restrict__ forced, int* __restrict__ topk_idx,
+                                             float* __restrict__ topk_w, float* __restrict__ scores_out, int* s_hist,
+                                             long long t, int lane, int E, int k, int score_func, int norm_topk,
+                                             float route_scale) {
+  constexpr int MAXPL = kMaxExperts / 32;
+  float sc[MAXPL];
+  const int pl = (E + 31) / 32;
+  const float* row = logits + t * E;
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < MAXPL; ++i) {
+    const int e = lane + i * 32;
+    sc[i] = (i < pl && e < E) ? row[e] : -INFINITY;
+    mx = fmaxf(mx, sc[i]);
+  }
+  if (score_func == 0) {
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXPL; ++i) {
+      const int e = lane + i * 32;
+      sc[i] = (i < pl && e < E) ? __expf(sc[i] - mx) : 0.f;
+      sum += sc[i];
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+#pragma unroll
+    for (int i = 0; i < MAXPL; ++i) sc[i] *= inv;
+  } else {
+#pragma unroll
+    for (int i = 0; i < MAXPL; ++i) {
+      const int e = lane + i * 32;
+      sc[i] = (i < pl && e < E) ? 1.f / (1.f + __expf(-sc[i])) : 0.f;
+    }
+  }
+  if (scores_out) {
+#pragma unroll
+    for (int i = 0; i < MAXPL; ++i) {
+      const int e = lane + i * 32;
+      if (i < pl && e < E) scores_out[t * E + e] = sc[i];
+    }
+  }
+  float sel[MAXPL];
+#pragma unroll
+  for (int i = 0; i < MAXPL; ++i) {
+    const int e = lane + i * 32;
+    sel[i] = (i < pl && e < E) ? sc[i] + (sel_bias ? sel_bias[e] : 0.f) : -INFINITY;
+  }
+  float wsum = 0.f;
+  float my_w = 0.f;
+  int my_e = 0;
+  for (int j = 0; j < k; ++j) {
+    int be;
+    float bw;
+    if (forced) {
+      be = forced[t * k + j];
+      // fetch the score of expert `be` from the lane that holds it
+      float cand = 0.f;
+#pragma unroll
+      for (int i = 0; i < MAXPL; ++i)
+        if (lane + i * 32 == be) cand = sc[i];
+      bw = __shfl_sync(0xffffffffu, cand, be & 31);
+    } else {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < MAXPL; ++i) {
+        const int e = lane + i * 32;
+        if (sel[i] > bv) {
+          bv = sel[i];
+          bi = e;
+        }
+      }
+      // warp arg-max; ties resolve to the lowest expert index (matches torch.topk order
+      // closely enough for replay, which is exact by construction)
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) {
+          bv = ov;
+          bi = oi;
+        }
+      }
+      be = bi;
+      float cand = 0.f;
+#pragma unroll
+      for (int i = 0; i < MAXPL; ++i) {
+        if (lane + i * 32 == be) {
+          cand = sc[i];
+          sel[i] = -INFINITY;
+        }
+      }
+      bw = __shfl_sync(0xffffffffu, cand, be & 31);
+    }
+    wsum += bw;
+    if (lane == j) {
+      my_w = bw;
+      my_e = be;
+    }
+  }
+  if (lane < k) {
+    float w = my_w;
+    if (norm_topk) w = w / (wsum + 1e-20f);
+    w *= route_scale;
+    topk_idx[t * k + lane] = my_e;
+    topk_w[t * k + lane] = w;
+    atomicAdd(&s_hist[my_e], 1);
+  }
+}
+
+// One warp per token.
 __global__ void __launch_bounds__(256)
 router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ sel_bias,
                    const int* __restrict__ forced, int* __restrict__ topk_idx, float* __restrict__ topk_w,
@@ -36,113 +150,9 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ s
   __syncthreads();
   const int lane = threadIdx.x & 31;
   const long long t = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (t < T) {
-    constexpr int MAXPL = kMaxExperts / 32;
-    float sc[MAXPL];
-    const int pl = (E + 31) / 32;
-    const float* row = logits + t * E;
-    float mx = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < MAXPL; ++i) {
-      const int e = lane + i * 32;
-      sc[i] = (i < pl && e < E) ? row[e] : -INFINITY;
-      mx = fmaxf(mx, sc[i]);
-    }
-    if (score_func == 0) {
-      mx = warp_max(mx);
-      float sum = 0.f;
-#pragma unroll
-      for (int i = 0; i < MAXPL; ++i) {
-        const int e = lane + i * 32;
-        sc[i] = (i < pl && e < E) ? __expf(sc[i] - mx) : 0.f;
-        sum += sc[i];
-      }
-      sum = warp_sum(sum);
-      const float inv = 1.f / sum;
-#pragma unroll
-      for (int i = 0; i < MAXPL; ++i) sc[i] *= inv;
-    } else {
-#pragma unroll
-      for (int i = 0; i < MAXPL; ++i) {
-        const int e = lane + i * 32;
-        sc[i] = (i < pl && e < E) ? 1.f / (1.f + __expf(-sc[i])) : 0.f;
-      }
-    }
-    if (scores_out) {
-#pragma unroll
-      for (int i = 0; i < MAXPL; ++i) {
-        const int e = lane + i * 32;
-        if (i < pl && e < E) scores_out[t * E + e] = sc[i];
-      }
-    }
-    float sel[MAXPL];
-#pragma unroll
-    for (int i = 0; i < MAXPL; ++i) {
-      const int e = lane + i * 32;
-      sel[i] = (i < pl && e < E) ? sc[i] + (sel_bias ? sel_bias[e] : 0.f) : -INFINITY;
-    }
-    float wsum = 0.f;
-    float my_w = 0.f;
-    int my_e = 0;
-    for (int j = 0; j < k; ++j) {
-      int be;
-      float bw;
-      if (forced) {
-        be = forced[t * k + j];
-        // fetch the score of expert `be` from the lane that holds it
-        float cand = 0.f;
-#pragma unroll
-        for (int i = 0; i < MAXPL; ++i)
-          if (lane + i * 32 == be) cand = sc[i];
-        bw = __shfl_sync(0xffffffffu, cand, be & 31);
-      } else {
-        float bv = -INFINITY;
-        int bi = 0x7fffffff;
-#pragma unroll
-        for (int i = 0; i < MAXPL; ++i) {
-          const int e = lane + i * 32;
-          if (sel[i] > bv) {
-            bv = sel[i];
-            bi = e;
-          }
-        }
-        // warp arg-max; ties resolve to the lowest expert index (matches torch.topk order
-        // closely enough for replay, which is exact by construction)
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-          const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-          const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-          if (ov > bv || (ov == bv && oi < bi)) {
-            bv = ov;
-            bi = oi;
-          }
-        }
-        be = bi;
-        float cand = 0.f;
-#pragma unroll
-        for (int i = 0; i < MAXPL; ++i) {
-          if (lane + i * 32 == be) {
-            cand = sc[i];
-            sel[i] = -INFINITY;
-          }
-        }
-        bw = __shfl_sync(0xffffffffu, cand, be & 31);
-      }
-      wsum += bw;
-      if (lane == j) {
-        my_w = bw;
-        my_e = be;
-      }
-    }
-    if (lane < k) {
-      float w = my_w;
-      if (norm_topk) w = w / (wsum + 1e-20f);
-      w *= route_scale;
-      topk_idx[t * k + lane] = my_e;
-      topk_w[t * k + lane] = w;
-      atomicAdd(&s_hist[my_e], 1);
-    }
-  }
+  if (t < T)
+    router_token(logits, sel_bias, forced, topk_idx, topk_w, scores_out, s_hist, t, lane, E, k, score_func, norm_topk,
+                 route_scale);
   __syncthreads();
   for (int i = threadIdx.x; i < E; i += blockDim.x)
     if (s_hist[i]) atomicAdd(&counts[i], s_hist[i]);
@@ -226,6 +236,69 @@ moe_scatter_sorted_kernel(const int* __restrict__ topk_idx, const int* __restric
     __syncthreads();
     if (threadIdx.x == 0) s_base += total;
     __syncthreads();
+  }
+}
+
+// Decode-sized batches (T * k pairs that one CTA walks in a few rounds): router scores + top-k + histogram +
+// padded expert offsets + block -> expert table + row_src fill + scatter in ONE launch of one CTA, instead of a
+// fill, the router kernel, a memset, the plan kernel and the scatter kernel. counts need not be zeroed.
+__global__ void __launch_bounds__(1024)
+moe_route_plan_small_kernel(const float* __restrict__ logits, const float* __restrict__ sel_bias,
+                            const int* __restrict__ forced, int* __restrict__ topk_idx, float* __restrict__ topk_w,
+                            float* __restrict__ scores_out, int* __restrict__ counts, int* __restrict__ expert_offset,
+                            int* __restrict__ block_expert, int* __restrict__ total_rows, int* __restrict__ slot,
+                            int* __restrict__ row_src, long long T, int E, int k, int max_blocks, int score_func,
+                            int norm_topk, float route_scale) {
+  __shared__ int s_hist[kMaxExperts];
+  __shared__ int s_off[kMaxExperts + 1];
+  __shared__ int s_cur[kMaxExperts];
+  for (int i = threadIdx.x; i < E; i += blockDim.x) {
+    s_hist[i] = 0;
+    s_cur[i] = 0;
+  }
+  // padding marker for the whole row space (valid rows are overwritten by the scatter below)
+  for (int i = threadIdx.x; i < max_blocks * 128; i += blockDim.x) row_src[i] = -1;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  for (long long t = threadIdx.x >> 5; t < T; t += blockDim.x >> 5)
+    router_token(logits, sel_bias, forced, topk_idx, topk_w, scores_out, s_hist, t, lane, E, k, score_func, norm_topk,
+                 route_scale);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < E; ++e) {
+      s_off[e] = acc;
+      acc += (s_hist[e] + 127) / 128 * 128;
+    }
+    s_off[E] = acc;
+    total_rows[0] = acc;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+    expert_offset[e] = s_off[e];
+    if (e < E) counts[e] = s_hist[e];
+  }
+  for (int b = threadIdx.x; b < max_blocks; b += blockDim.x) {
+    const int row = b * 128;
+    int ex = -1;
+    if (row < s_off[E]) {
+      int lo = 0, hi = E;  // largest e with s_off[e] <= row
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (s_off[mid] <= row) lo = mid; else hi = mid;
+      }
+      ex = lo;
+      while (ex + 1 < E && s_off[ex + 1] <= row) ++ex;   // skip experts without rows that share the offset
+    }
+    block_expert[b] = ex;
+  }
+  // the expert ids were written to global memory by this CTA before the barriers above
+  const long long n = T * k;
+  for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = topk_idx[i];
+    const int pos = s_off[e] + atomicAdd(&s_cur[e], 1);
+    slot[i] = pos;
+    row_src[pos] = static_cast<int>(i);
   }
 }
 
@@ -416,5 +489,20 @@ PRB_API int prb_moe_combine_bwd_w(const void* dy, const void* p, const int* slot
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   moe_combine_bwd_w_kernel<<<row_grid(T * k), 256, 0, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)p, slot,
                                                            dw, T * k, cols, k);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// One launch for router + plan when T * k <= 8192 (decode steps). Outputs as prb_router_topk + prb_moe_plan;
+// counts / row_src need no initialisation.
+PRB_API int prb_moe_route_plan_small(const float* logits, const float* sel_bias, const int* forced, int* topk_idx,
+                                     float* topk_w, float* scores_out, int* counts, int* expert_offset,
+                                     int* block_expert, int* total_rows, int* slot, int* row_src, long long T, int E,
+                                     int k, int max_blocks, int score_func, int norm_topk, float route_scale,
+                                     void* stream) {
+  if (E > kMaxExperts || k > kMaxTopK || k > 32 || T * k > 8192) return -1;
+  if (T == 0) return 0;
+  moe_route_plan_small_kernel<<<1, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      logits, sel_bias, forced, topk_idx, topk_w, scores_out, counts, expert_offset, block_expert, total_rows, slot,
+      row_src, T, E, k, max_blocks, score_func, norm_topk, route_scale);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

@@ -223,6 +223,8 @@ class Router(nn.Module):
         else:
             self.e_score_correction_bias = None
         self.force_balanced = False
+        self.want_plan = False            # set by the owning MoE layer when it runs its experts locally
+        self.last_plan = None             # the experts' row plan, when the last forward built it with the selection
 
     def forward(self, x: torch.Tensor, forced: torch.Tensor | None = None):
         a = self.arch
@@ -236,6 +238,15 @@ class Router(nn.Module):
             T = x.shape[0]
             base = torch.arange(T, device=x.device)[:, None] * a.num_experts_per_tok
             forced = ((base + torch.arange(a.num_experts_per_tok, device=x.device)[None, :]) % a.num_experts)
+        self.last_plan = None
+        if self.want_plan:
+            # decode-sized inference batches: selection, histogram and the row plan of the experts in one launch
+            fused = moe_ops.route_and_plan_small(logits, a.num_experts_per_tok, score_func=a.score_func,
+                                                 norm_topk=a.norm_topk_prob, route_scale=a.routed_scaling_factor,
+                                                 sel_bias=self.e_score_correction_bias, forced=forced)
+            if fused is not None:
+                idx, w, counts, self.last_plan = fused
+                return idx, w, counts, logits
         idx, w, counts = moe_ops.route_topk(logits, a.num_experts_per_tok, score_func=a.score_func,
                                             norm_topk=a.norm_topk_prob, route_scale=a.routed_scaling_factor,
                                             sel_bias=self.e_score_correction_bias, forced=forced)
@@ -367,6 +378,7 @@ class MoE(nn.Module):
         forced = None
         if seq.routed_experts is not None:
             forced = seq.routed_experts[:, self.layer_idx, :].to(torch.int32)
+        self.router.want_plan = self.dispatcher is None
         idx, w, counts, logits = self.router(x, forced)
         self.last_counts = counts
         self.last_topk = idx
@@ -374,7 +386,9 @@ class MoE(nn.Module):
         if self.dispatcher is not None:
             y = self.dispatcher(self.experts, xe, idx, w, counts)
         else:
-            plan = moe_ops.build_plan(idx, counts, self.arch.num_experts)
+            plan = self.router.last_plan
+            if plan is None:
+                plan = moe_ops.build_plan(idx, counts, self.arch.num_experts)
             if self.experts.supports_row_mask(xe) and xe.shape[1] % 8 == 0:
                 # inference: nothing touches the rows that only pad every expert to a multiple of 128
                 xp = moe_ops.permute_nopad(xe, plan)

@@ -75,6 +75,7 @@ _CUDA_SIGNATURES = {
     "prb_moe_plan": [P, P, P, P, P, P, P, P, L, I, I, I, I, P],
     "prb_moe_gather_rows": [P, P, P, P, L, I, I, P, P],
     "prb_qkv_rope_cache": [P, P, P, P, P, P, P, P, P, P, P, L, I, I, I, F, P],
+    "prb_moe_route_plan_small": [P, P, P, P, P, P, P, P, P, P, P, P, L, I, I, I, I, I, F, P],
     "prb_moe_gather_rows_nopad": [P, P, P, P, L, I, I, P, P],
     "prb_glu_fwd_rowmask": [P, P, P, L, I, L, L, I, F, F, P, P],
     "prb_gemm_bf16_rowmask": [P, P, P, I, I, I, L, L, L, I, I, I, F, F, P, I, I, I, P, P, P],

@@ -842,3 +842,37 @@ def test_allreduce_kernel_wait_runs_out_when_the_peer_never_arrives():
     st.zero_()
     assert float(out_h.float().min()) == 7.0 and state.tolist() == [1, 0]
     assert float((torch.ones(4, device=dev) * 2).sum()) == 8.0      # the device still answers
+
+
+def test_route_and_plan_small_matches_the_separate_kernels():
+    """One-launch router + plan for decode batches against router_topk + build_plan: same experts, weights,
+    histogram, offsets and block table; slots form a valid placement (row_src inverts slot, rows stay inside
+    their expert's range, everything else is padding)."""
+    from prime_rl_b200.ops import moe as moe_ops
+
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    moe_ops.SMALL_ROUTE_TOKENS, keep = 1024, moe_ops.SMALL_ROUTE_TOKENS     # exercise several tokens per warp too
+    for T, E, k, func, bias in ((256, 128, 8, "softmax", False), (37, 64, 6, "sigmoid", True), (1, 16, 2, "softmax", False)):
+        logits = torch.randn(T, E, device=dev)
+        sel_bias = torch.randn(E, device=dev) * 0.1 if bias else None
+        with torch.no_grad():
+            fused = moe_ops.route_and_plan_small(logits, k, score_func=func, norm_topk=True, route_scale=1.5, sel_bias=sel_bias)
+            assert fused is not None
+            idx, w, counts, plan = fused
+            idx0, w0, counts0 = moe_ops.route_topk(logits, k, score_func=func, norm_topk=True, route_scale=1.5, sel_bias=sel_bias)
+            plan0 = moe_ops.build_plan(idx0, counts0, E)
+        assert torch.equal(idx, idx0) and torch.equal(w, w0) and torch.equal(counts, counts0)
+        assert torch.equal(plan.expert_offset, plan0.expert_offset) and torch.equal(plan.block_expert, plan0.block_expert)
+        assert torch.equal(plan.total_rows, plan0.total_rows) and plan.max_rows == plan0.max_rows
+        slot, row_src = plan.slot.reshape(-1).long(), plan.row_src
+        assert torch.equal(row_src[slot], torch.arange(T * k, device=dev, dtype=torch.int32))
+        assert int((row_src >= 0).sum()) == T * k
+        off = plan.expert_offset.long()
+        e = idx.reshape(-1).long()
+        assert bool(((slot >= off[e]) & (slot < off[e] + counts.long()[e])).all())
+    moe_ops.SMALL_ROUTE_TOKENS = keep
+    with torch.enable_grad():
+        assert moe_ops.route_and_plan_small(torch.randn(4, 16, device=dev), 2) is None
+    with torch.no_grad():
+        assert moe_ops.route_and_plan_small(torch.randn(keep + 1, 16, device=dev), 2) is None
