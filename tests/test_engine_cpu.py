@@ -253,6 +253,16 @@ def test_tensor_parallel_http_server_serves_the_same_tokens(tmp_path):
         assert httpx.post(base + "/resume", timeout=60).status_code == 200
         r = httpx.post(base + "/inference/v1/generate", json=body, timeout=120)
         assert r.json()["choices"][0]["token_ids"] == want
+        # a weight update from a checkpoint directory: every rank loads its own slices of the new weights
+        from prime_rl_b200.trainer.weights import save_hf_checkpoint
+
+        other = build_model(arch, device=torch.device("cpu"), dtype=torch.float32, seed=7)
+        save_hf_checkpoint(other, tmp_path / "step_1", dtype=torch.float32)
+        r = httpx.post(base + "/update_weights", json={"weight_dir": str(tmp_path / "step_1")}, timeout=120)
+        assert r.status_code == 200 and r.json()["policy_version"] == 1, r.text
+        want2 = LocalEngine(other, num_pages=64).generate_sync([prompt], SamplingParams(max_tokens=6, temperature=0.0))[0].output
+        r = httpx.post(base + "/inference/v1/generate", json=body, timeout=120)
+        assert r.json()["choices"][0]["token_ids"] == want2 and want2 != want
     finally:
         os.killpg(proc.pid, signal.SIGTERM)            # the process group this test started, nothing else
         try:
