@@ -293,6 +293,35 @@ qknorm_rope_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 // launch, K (norm + rotary) and V written into the paged cache at slot[t] (cache rows of nkv * D elements) and,
 // when k_out / v_out are given, also as contiguous [T, nkv, D] tensors. One warp per (token, head); the
 // arithmetic is the one of qknorm_rope_kernel, so the engine and the trainer see the same values.
+// EPL contiguous bf16 values of one lane as one 4 / 8 / 16-byte access (the addresses are multiples of EPL * 2 bytes:
+// rows of D elements, lane offsets of EPL elements, 16-byte aligned bases).
+template <int EPL>
+__device__ __forceinline__ void rope_load(const __nv_bfloat16* src, float (&x)[EPL]) {
+  if constexpr (EPL == 4) {
+    const uint2 u = *reinterpret_cast<const uint2*>(src);
+    const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y);
+    x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+  } else if constexpr (EPL == 2) {
+    const float2 a = unpack_bf16(*reinterpret_cast<const uint32_t*>(src));
+    x[0] = a.x; x[1] = a.y;
+  } else {
+    const uint4 u = *reinterpret_cast<const uint4*>(src);
+    const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+    x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y; x[4] = c.x; x[5] = c.y; x[6] = d.x; x[7] = d.y;
+  }
+}
+
+template <int EPL>
+__device__ __forceinline__ void rope_store(__nv_bfloat16* dst, const __nv_bfloat16 (&r)[EPL]) {
+  if constexpr (EPL == 4) {
+    *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(r);
+  } else if constexpr (EPL == 2) {
+    *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(r);
+  } else {
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(r);
+  }
+}
+
 template <int D>
 __global__ void __launch_bounds__(256)
 qkv_rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ qw,
@@ -302,33 +331,42 @@ qkv_rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16
                       __nv_bfloat16* __restrict__ v_out, __nv_bfloat16* __restrict__ k_cache,
                       __nv_bfloat16* __restrict__ v_cache, long long T, int nq, int nkv, float eps) {
   constexpr int EPL = D / 32;
+  constexpr int kTok = 9;                    // the 8 consecutive (token, head) items of a CTA touch at most 9 tokens
+  __shared__ float s_cs[kTok][D / 2], s_sn[kTok][D / 2];
   const int lane = threadIdx.x & 31;
   const int heads = nq + 2 * nkv;
-  const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long item0 = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5);
+  const long long t0 = item0 / heads;
+  // the sine / cosine table of the CTA's tokens, computed once instead of once per head
+  for (int i = threadIdx.x; i < kTok * (D / 2); i += blockDim.x) {
+    const int which = i / (D / 2), fi = i - which * (D / 2);
+    const long long tt = t0 + which;
+    if (tt < T && tt * heads < item0 + (blockDim.x >> 5))
+      sincosf(static_cast<float>(pos[tt]) * inv_freq[fi], &s_sn[which][fi], &s_cs[which][fi]);
+  }
+  __syncthreads();
+  const long long item = item0 + (threadIdx.x >> 5);
   if (item >= T * heads) return;
   const long long t = item / heads;
   const int h = static_cast<int>(item - t * heads);
+  const int tw = static_cast<int>(t - t0);
   const int e0 = lane * EPL;
   float xv[EPL];
-  {
-    const __nv_bfloat16* src = qkv + t * (static_cast<long long>(heads) * D) + static_cast<long long>(h) * D + e0;
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) xv[i] = __bfloat162float(src[i]);
-  }
+  rope_load<EPL>(qkv + t * (static_cast<long long>(heads) * D) + static_cast<long long>(h) * D + e0, xv);
   const bool is_q = h < nq, is_v = h >= nq + nkv;
   const int hk = is_q ? h : (is_v ? h - nq - nkv : h - nq);      // head index inside its own tensor
-  __nv_bfloat16 res[EPL];
+  __align__(16) __nv_bfloat16 res[EPL];
   if (is_v) {
 #pragma unroll
     for (int i = 0; i < EPL; ++i) res[i] = __float2bfloat16(xv[i]);
   } else {
     const __nv_bfloat16* w = is_q ? qw : kw;
-    const float p = static_cast<float>(pos[t]);
     float cs[EPL], sn[EPL];
 #pragma unroll
     for (int i = 0; i < EPL; ++i) {
       const int fi = (e0 + i) % (D / 2);
-      sincosf(p * inv_freq[fi], &sn[i], &cs[i]);
+      cs[i] = s_cs[tw][fi];
+      sn[i] = s_sn[tw][fi];
     }
     const bool upper = e0 >= D / 2;
     if (w) {
@@ -349,20 +387,12 @@ qkv_rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16
     }
   }
   if (is_q) {
-    __nv_bfloat16* dst = q_out + (t * nq + hk) * D + e0;
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) dst[i] = res[i];
+    rope_store<EPL>(q_out + (t * nq + hk) * D + e0, res);
     return;
   }
   __nv_bfloat16* lin = is_v ? v_out : k_out;
-  if (lin != nullptr) {
-    __nv_bfloat16* dst = lin + (t * nkv + hk) * D + e0;
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) dst[i] = res[i];
-  }
-  __nv_bfloat16* dst = (is_v ? v_cache : k_cache) + (slot[t] * nkv + hk) * D + e0;
-#pragma unroll
-  for (int i = 0; i < EPL; ++i) dst[i] = res[i];
+  if (lin != nullptr) rope_store<EPL>(lin + (t * nkv + hk) * D + e0, res);
+  rope_store<EPL>((is_v ? v_cache : k_cache) + (slot[t] * nkv + hk) * D + e0, res);
 }
 
 }  // namespace prb
