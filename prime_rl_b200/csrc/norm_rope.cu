@@ -322,6 +322,8 @@ __device__ __forceinline__ void rope_store(__nv_bfloat16* dst, const __nv_bfloat
   }
 }
 
+constexpr int kRopeHeadsPerWarp = 4;   // rows a warp has in flight at once (one 256-byte row alone cannot cover DRAM latency)
+
 template <int D>
 __global__ void __launch_bounds__(256)
 qkv_rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ qw,
@@ -331,68 +333,80 @@ qkv_rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16
                       __nv_bfloat16* __restrict__ v_out, __nv_bfloat16* __restrict__ k_cache,
                       __nv_bfloat16* __restrict__ v_cache, long long T, int nq, int nkv, float eps) {
   constexpr int EPL = D / 32;
-  constexpr int kTok = 9;                    // the 8 consecutive (token, head) items of a CTA touch at most 9 tokens
+  constexpr int HPW = kRopeHeadsPerWarp;
+  constexpr int kTok = 9;                    // the 8 consecutive (token, head group) items of a CTA touch at most 9 tokens
   __shared__ float s_cs[kTok][D / 2], s_sn[kTok][D / 2];
   const int lane = threadIdx.x & 31;
   const int heads = nq + 2 * nkv;
+  const int groups = (heads + HPW - 1) / HPW;          // items per token
   const long long item0 = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5);
-  const long long t0 = item0 / heads;
+  const long long t0 = item0 / groups;
   // the sine / cosine table of the CTA's tokens, computed once instead of once per head
   for (int i = threadIdx.x; i < kTok * (D / 2); i += blockDim.x) {
     const int which = i / (D / 2), fi = i - which * (D / 2);
     const long long tt = t0 + which;
-    if (tt < T && tt * heads < item0 + (blockDim.x >> 5))
+    if (tt < T && tt * groups < item0 + (blockDim.x >> 5))
       sincosf(static_cast<float>(pos[tt]) * inv_freq[fi], &s_sn[which][fi], &s_cs[which][fi]);
   }
   __syncthreads();
   const long long item = item0 + (threadIdx.x >> 5);
-  if (item >= T * heads) return;
-  const long long t = item / heads;
-  const int h = static_cast<int>(item - t * heads);
+  if (item >= T * groups) return;
+  const long long t = item / groups;
+  const int h0 = static_cast<int>(item - t * groups) * HPW;
   const int tw = static_cast<int>(t - t0);
   const int e0 = lane * EPL;
-  float xv[EPL];
-  rope_load<EPL>(qkv + t * (static_cast<long long>(heads) * D) + static_cast<long long>(h) * D + e0, xv);
-  const bool is_q = h < nq, is_v = h >= nq + nkv;
-  const int hk = is_q ? h : (is_v ? h - nq - nkv : h - nq);      // head index inside its own tensor
-  __align__(16) __nv_bfloat16 res[EPL];
-  if (is_v) {
+  const bool upper = e0 >= D / 2;
+  float cs[EPL], sn[EPL];
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) res[i] = __float2bfloat16(xv[i]);
-  } else {
-    const __nv_bfloat16* w = is_q ? qw : kw;
-    float cs[EPL], sn[EPL];
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) {
-      const int fi = (e0 + i) % (D / 2);
-      cs[i] = s_cs[tw][fi];
-      sn[i] = s_sn[tw][fi];
-    }
-    const bool upper = e0 >= D / 2;
-    if (w) {
-      float ss = 0.f;
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) ss += xv[i] * xv[i];
-      ss = warp_sum(ss);
-      const float rstd = rsqrtf(ss / D + eps);
-#pragma unroll
-      for (int i = 0; i < EPL; ++i)
-        xv[i] = __bfloat162float(__float2bfloat16(xv[i] * rstd * __bfloat162float(w[e0 + i])));
-    }
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) {
-      const float other = __shfl_xor_sync(0xffffffffu, xv[i], 16);
-      const float r = upper ? (xv[i] * cs[i] + other * sn[i]) : (xv[i] * cs[i] - other * sn[i]);
-      res[i] = __float2bfloat16(r);
-    }
+  for (int i = 0; i < EPL; ++i) {
+    const int fi = (e0 + i) % (D / 2);
+    cs[i] = s_cs[tw][fi];
+    sn[i] = s_sn[tw][fi];
   }
-  if (is_q) {
-    rope_store<EPL>(q_out + (t * nq + hk) * D + e0, res);
-    return;
+  // all rows of the group are requested before the first one is used
+  float xv[HPW][EPL];
+  const __nv_bfloat16* row = qkv + t * (static_cast<long long>(heads) * D) + e0;
+#pragma unroll
+  for (int j = 0; j < HPW; ++j)
+    if (h0 + j < heads) rope_load<EPL>(row + static_cast<long long>(h0 + j) * D, xv[j]);
+  const long long cache_row = slot[t] * nkv;
+#pragma unroll
+  for (int j = 0; j < HPW; ++j) {
+    const int h = h0 + j;
+    if (h >= heads) break;
+    const bool is_q = h < nq, is_v = h >= nq + nkv;
+    const int hk = is_q ? h : (is_v ? h - nq - nkv : h - nq);      // head index inside its own tensor
+    __align__(16) __nv_bfloat16 res[EPL];
+    if (is_v) {
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) res[i] = __float2bfloat16(xv[j][i]);
+    } else {
+      const __nv_bfloat16* w = is_q ? qw : kw;
+      if (w) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) ss += xv[j][i] * xv[j][i];
+        ss = warp_sum(ss);
+        const float rstd = rsqrtf(ss / D + eps);
+#pragma unroll
+        for (int i = 0; i < EPL; ++i)
+          xv[j][i] = __bfloat162float(__float2bfloat16(xv[j][i] * rstd * __bfloat162float(w[e0 + i])));
+      }
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        const float other = __shfl_xor_sync(0xffffffffu, xv[j][i], 16);
+        const float r = upper ? (xv[j][i] * cs[i] + other * sn[i]) : (xv[j][i] * cs[i] - other * sn[i]);
+        res[i] = __float2bfloat16(r);
+      }
+    }
+    if (is_q) {
+      rope_store<EPL>(q_out + (t * nq + hk) * D + e0, res);
+      continue;
+    }
+    __nv_bfloat16* lin = is_v ? v_out : k_out;
+    if (lin != nullptr) rope_store<EPL>(lin + (t * nkv + hk) * D + e0, res);
+    rope_store<EPL>((is_v ? v_cache : k_cache) + (cache_row + hk) * D + e0, res);
   }
-  __nv_bfloat16* lin = is_v ? v_out : k_out;
-  if (lin != nullptr) rope_store<EPL>(lin + (t * nkv + hk) * D + e0, res);
-  rope_store<EPL>((is_v ? v_cache : k_cache) + (slot[t] * nkv + hk) * D + e0, res);
 }
 
 }  // namespace prb
@@ -485,7 +499,7 @@ PRB_API int prb_qkv_rope_cache(const void* qkv, const void* qw, const void* kw, 
                                void* v_cache, long long T, int nq, int nkv, int D, float eps, void* stream) {
   if (T == 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const long long items = T * (nq + 2 * nkv);
+  const long long items = T * ((nq + 2 * nkv + prb::kRopeHeadsPerWarp - 1) / prb::kRopeHeadsPerWarp);
   const unsigned grid = static_cast<unsigned>((items + 7) / 8);
 #define LAUNCH(DD)                                                                                                  \
   prb::qkv_rope_cache_kernel<DD><<<grid, 256, 0, s>>>(                                                               \
