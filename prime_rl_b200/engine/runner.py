@@ -39,6 +39,7 @@ class ModelRunner:
         self.capture_routed = False
         self.last_routed: torch.Tensor | None = None   # [N, moe_layers, k] of the last step
         self._decode_meta = None                        # (block tables, context lengths) of a pure decode step
+        self._cu_batch, self._cu = None, []             # per-sequence cu_seqlens of the current prefix-hit prefill
         # CUDA graphs for decode steps: batch sizes are padded to a multiple of ``graph_bucket``;
         # one page of the cache is reserved as the target of the padding rows
         plain = all(l.self_attn.window is None and l.self_attn.sinks is None for l in model.model.layers)
@@ -65,10 +66,22 @@ class ModelRunner:
         outs = []
         scale = 1.0 / math.sqrt(q.shape[-1])
         rep = q.shape[1] // k_new.shape[1]
-        for s, st in zip(batch, starts):
+        # prefill on top of a cached prefix (prefix-cache hit, chunked prompt): the tensor-core kernel takes the new
+        # tokens as a query slice [prefix, ctx) of the sequence whose K / V are gathered from the pages
+        sliced = (q.is_cuda and sinks is None and q.dtype == torch.bfloat16 and q.shape[-1] == 128
+                  and attn_ops.default_backend(q.device) == "tcgen05")
+        if sliced and self._cu_batch is not batch:
+            self._cu_batch = batch
+            self._cu = [torch.tensor([0, s.kv.length + len(s.tokens)], dtype=torch.int32).to(q.device, non_blocking=True)
+                        for s in batch]
+        for bi, (s, st) in enumerate(zip(batch, starts)):
             n = len(s.tokens)
             ctx = s.kv.length + n
             k, v = self.cache.gather(layer, s.kv, ctx)          # includes the tokens just written
+            if sliced:
+                outs.append(attn_ops.attention(q[st:st + n].contiguous(), k.contiguous(), v.contiguous(), self._cu[bi], ctx,
+                                               causal=True, window=window, q_offset=s.kv.length))
+                continue
             qs = q[st:st + n].float().transpose(0, 1)            # [Hq, n, D]
             ks = k.float().repeat_interleave(rep, dim=1).permute(1, 2, 0)   # [Hq, D, ctx]
             vs = v.float().repeat_interleave(rep, dim=1).transpose(0, 1)    # [Hq, ctx, D]

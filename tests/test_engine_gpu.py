@@ -110,3 +110,27 @@ def test_sampling_kernel_matches_softmax_statistics_and_logprobs():
     t8 = torch.full((8,), 1.3, device=dev)
     tok, lp, _ = sample(view, t8, off[:8], ones[:8], truncated=False)
     torch.testing.assert_close(lp, torch.log_softmax(view / 1.3, -1).gather(1, tok[:, None]).squeeze(1), atol=5e-4, rtol=0)
+
+
+def test_prefill_on_a_cached_prefix_uses_the_query_slice_kernel_and_matches_a_fresh_prefill():
+    """A prompt whose first pages are already cached is prefilled as a query slice [prefix, ctx) against K / V
+    gathered from the pages (tensor-core kernel); tokens and log-probabilities must be those of an engine
+    that has no prefix cache and prefills the whole prompt."""
+    from prime_rl_b200.engine.engine import Engine
+    from prime_rl_b200.ops import _runtime as rt
+
+    arch, model, plain = _setup()
+    g = torch.Generator().manual_seed(3)
+    base = torch.randint(0, arch.vocab_size, (80,), generator=g).tolist()
+    tails = [torch.randint(0, arch.vocab_size, (n,), generator=g).tolist() for n in (7, 21, 40)]
+    prompts = [base + t for t in tails]
+    ref = _greedy(plain, prompts, n=6)
+    cached = Engine(model, num_pages=512, page_size=16, enable_prefix_cache=True, max_model_len=256)
+    _greedy(cached, [base + [1, 2, 3]], n=2)                    # fills the cache with the pages of `base`
+    got = _greedy(cached, prompts, n=6)
+    rt.check_status()
+    assert cached.stats["prefix_hits"] >= 3 * 64               # 80 tokens = 5 pages, at least 4 of them shared
+    same = sum(a.output == b.output for a, b in zip(ref, got))
+    assert same >= len(prompts) - 1                             # bf16 ties may flip one greedy token
+    for a, b in zip(ref, got):
+        assert abs(a.logprobs[0] - b.logprobs[0]) < 5e-2
