@@ -466,7 +466,6 @@ ep_pull_kernel(EpPeers src, const int* __restrict__ topk_idx, const int* __restr
 //
 // Same role as the custom all-reduce + fused add-RMSNorm passes of the serving engine the reference
 // drives (vLLM tensor parallelism, packages/prime-rl-configs/src/prime_rl/configs/inference.py:88-97).
-constexpr int kArThreads = 256;
 
 __device__ __forceinline__ void ar_accumulate(float (&acc)[8], const uint4& u) {
   const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
@@ -474,9 +473,10 @@ __device__ __forceinline__ void ar_accumulate(float (&acc)[8], const uint4& u) {
   acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
 }
 
-// MAXVEC: 16-byte vectors per thread (cols <= MAXVEC * 256 * 8): 1 covers hidden sizes up to 2048 with few
-// registers (more CTAs per SM to hide the peer-load latency), 4 up to 8192.
-template <int MAXVEC>
+// MAXVEC 16-byte vectors per thread, kArThreads threads per row (cols <= MAXVEC * kArThreads * 8). Hidden sizes up to
+// 2048 run with 128 threads x 2 vectors: small CTAs, so that many rows are in flight per SM to hide the peer-load
+// latency; wider rows use 256 threads x 4.
+template <int MAXVEC, int kArThreads>
 __global__ void __launch_bounds__(kArThreads)
 ar_add_rmsnorm_kernel(EpPeers partial, EpPeers flags, int* __restrict__ state, const __nv_bfloat16* __restrict__ residual,
                       const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out_h,
@@ -747,18 +747,18 @@ PRB_API int prb_ep_pull(void* const* src_peers, const int* topk_idx, const int* 
 PRB_API int prb_ar_add_rmsnorm(void* const* partial_peers, void* const* flag_peers, int* state, const void* residual,
                                const void* w, void* out_h, void* out_x, int rows, int cols, float eps, int rank, int R,
                                int* status, void* stream) {
-  if (R > prb::kEpMaxRanks || R < 1 || cols % 8 || cols > 4 * prb::kArThreads * 8) return -2;
+  if (R > prb::kEpMaxRanks || R < 1 || cols % 8 || cols > 4 * 256 * 8) return -2;
   if (out_x != nullptr && w == nullptr) return -2;
   if (rows <= 0) return 0;
-  const bool narrow = cols <= prb::kArThreads * 8;
-  const int cap = 148 * (narrow ? 6 : 3);
+  const bool narrow = cols <= 2 * 128 * 8;
+  const int cap = 148 * (narrow ? 12 : 3);
   const int grid = rows < cap ? rows : cap;
-#define PRB_AR_LAUNCH(MV)                                                                                            \
-  prb::ar_add_rmsnorm_kernel<MV><<<grid, prb::kArThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(              \
+#define PRB_AR_LAUNCH(MV, TH)                                                                                        \
+  prb::ar_add_rmsnorm_kernel<MV, TH><<<grid, TH, 0, reinterpret_cast<cudaStream_t>(stream)>>>(                       \
       ep_peers(partial_peers, R), ep_peers(flag_peers, R), state, reinterpret_cast<const __nv_bfloat16*>(residual),  \
       reinterpret_cast<const __nv_bfloat16*>(w), reinterpret_cast<__nv_bfloat16*>(out_h),                            \
       reinterpret_cast<__nv_bfloat16*>(out_x), rows, cols, eps, rank, R, status)
-  if (narrow) PRB_AR_LAUNCH(1); else PRB_AR_LAUNCH(4);
+  if (narrow) PRB_AR_LAUNCH(2, 128); else PRB_AR_LAUNCH(4, 256);
 #undef PRB_AR_LAUNCH
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
