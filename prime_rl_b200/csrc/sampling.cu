@@ -19,6 +19,17 @@ __device__ __forceinline__ unsigned long long splitmix64(unsigned long long x) {
   return x ^ (x >> 31);
 }
 
+// 32-bit finaliser (three multiplies) over the element index mixed with a per-row seed: enough for 24 random bits
+// per element, and a third of the instructions of the 64-bit hash above.
+__device__ __forceinline__ unsigned mix32(unsigned x) {
+  x ^= x >> 16;
+  x *= 0x7feb352du;
+  x ^= x >> 15;
+  x *= 0x846ca68bu;
+  x ^= x >> 16;
+  return x;
+}
+
 struct SampleState {
   float m, s;        // running max and sum of exp(z - m)
   float key, z;      // best perturbed score and the unperturbed z of that token
@@ -46,19 +57,13 @@ sample_gumbel_kernel(const float* __restrict__ logits, const float* __restrict__
   const float* z_row = logits + static_cast<long long>(row) * ld;
   const unsigned long long base = splitmix64(seed ^ (0x51ed270b0f3a9d1bull * (row + 1)));
   SampleState st{-INFINITY, 0.f, -INFINITY, 0.f, -1};
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float z = z_row[i] * inv_t;
-    if (z > st.m) {
-      st.s = st.s * __expf(st.m - z) + 1.f;      // exp(-inf) = 0 on the first element
-      st.m = z;
-    } else {
-      st.s += __expf(z - st.m);
-    }
+  const unsigned row_key = static_cast<unsigned>(base) ^ static_cast<unsigned>(base >> 32);
+  auto take = [&](float z, int i) {
     float key = z;
     if (!greedy) {
       // 24 random bits -> u in (0, 1), g = -log(-log(u))
-      const unsigned long long h = splitmix64(base + static_cast<unsigned long long>(i));
-      const float u = (static_cast<float>(h >> 40) + 0.5f) * (1.f / 16777216.f);
+      const unsigned h = mix32(static_cast<unsigned>(i) * 0x9e3779b1u ^ row_key);
+      const float u = (static_cast<float>(h >> 8) + 0.5f) * (1.f / 16777216.f);
       key = z - __logf(-__logf(u));
     }
     if (key > st.key) {
@@ -66,6 +71,32 @@ sample_gumbel_kernel(const float* __restrict__ logits, const float* __restrict__
       st.z = z;
       st.idx = i;
     }
+  };
+  // rows whose start is 16-byte aligned are read four elements at a time; the log-sum-exp is updated once per group
+  const bool vec = (reinterpret_cast<uintptr_t>(z_row) & 15) == 0;
+  const int v4 = vec ? V / 4 : 0;
+  for (int g4 = threadIdx.x; g4 < v4; g4 += blockDim.x) {
+    const float4 q = reinterpret_cast<const float4*>(z_row)[g4];
+    const float z0 = q.x * inv_t, z1 = q.y * inv_t, z2 = q.z * inv_t, z3 = q.w * inv_t;
+    const float gm = fmaxf(fmaxf(z0, z1), fmaxf(z2, z3));
+    if (gm > st.m) {
+      st.s *= __expf(st.m - gm);                  // exp(-inf) = 0 on the first group
+      st.m = gm;
+    }
+    if (gm > -INFINITY)                            // a group of -inf logits adds nothing (and -inf - -inf is NaN)
+      st.s += __expf(z0 - st.m) + __expf(z1 - st.m) + __expf(z2 - st.m) + __expf(z3 - st.m);
+    const int i = g4 * 4;
+    take(z0, i); take(z1, i + 1); take(z2, i + 2); take(z3, i + 3);
+  }
+  for (int i = v4 * 4 + threadIdx.x; i < V; i += blockDim.x) {
+    const float z = z_row[i] * inv_t;
+    if (z > st.m) {
+      st.s = st.s * __expf(st.m - z) + 1.f;
+      st.m = z;
+    } else if (z > -INFINITY) {
+      st.s += __expf(z - st.m);
+    }
+    take(z, i);
   }
   // warp, then block reduction
 #pragma unroll
