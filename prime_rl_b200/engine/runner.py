@@ -181,24 +181,42 @@ class ModelRunner:
         return st
 
     def _decode_with_graph(self, batch):
-        dev, B = self.device, len(batch)
+        """Fills the graph's static inputs and replays it. The host side is on the critical path of a decode
+        step (the next step cannot start before the sampled tokens were read), so the inputs are assembled in
+        one pinned int32 staging array with numpy and cross to the device in ONE copy."""
+        import numpy as np
+
+        B = len(batch)
         Bp = (B + self.graph_bucket - 1) // self.graph_bucket * self.graph_bucket
         st = self._graph_for(Bp)
-        W, sp = self.graph_max_blocks, self.scratch_page
-        ids = [s.tokens[0] for s in batch] + [0] * (Bp - B)
-        pos = [s.kv.length for s in batch] + [0] * (Bp - B)
-        slots, bt = [], []
-        for s in batch:
-            slots.extend(self.cache.slot_mapping(s.kv, s.kv.length, 1))
-            bt.append(s.kv.pages + [sp] * (W - len(s.kv.pages)))
-        slots += [sp * self.cache.page_size] * (Bp - B)
-        bt += [[sp] * W] * (Bp - B)
-        ctx = [s.kv.length + 1 for s in batch] + [1] * (Bp - B)
-        st["ids"].copy_(torch.tensor(ids, dtype=torch.long), non_blocking=True)
-        st["pos"].copy_(torch.tensor(pos, dtype=torch.int32), non_blocking=True)
-        st["slots"].copy_(torch.tensor(slots, dtype=torch.long), non_blocking=True)
-        st["bt"].copy_(torch.tensor(bt, dtype=torch.int32), non_blocking=True)
-        st["ctx"].copy_(torch.tensor(ctx, dtype=torch.int32), non_blocking=True)
+        W, sp, ps = self.graph_max_blocks, self.scratch_page, self.cache.page_size
+        stage = st.get("stage")
+        if stage is None:
+            # [ids | pos | slots | ctx | block table]: int32 [Bp, 4 + W], pinned; a device twin receives the copy
+            stage = st["stage"] = torch.empty(Bp, 4 + W, dtype=torch.int32).pin_memory()
+            st["stage_np"] = stage.numpy()
+            st["stage_dev"] = torch.empty(Bp, 4 + W, dtype=torch.int32, device=self.device)
+        arr = st["stage_np"]
+        arr[:, 0] = 0
+        arr[:, 1] = 0
+        arr[:, 2] = sp * ps
+        arr[:, 3] = 1
+        arr[:, 4:] = sp
+        for i, s in enumerate(batch):
+            n, pages = s.kv.length, s.kv.pages
+            row = arr[i]
+            row[0] = s.tokens[0]
+            row[1] = n
+            row[2] = pages[n // ps] * ps + n % ps
+            row[3] = n + 1
+            row[4:4 + len(pages)] = pages
+        dev = st["stage_dev"]
+        dev.copy_(stage, non_blocking=True)
+        st["ids"].copy_(dev[:, 0])
+        st["pos"].copy_(dev[:, 1])
+        st["slots"].copy_(dev[:, 2])
+        st["ctx"].copy_(dev[:, 3])
+        st["bt"].copy_(dev[:, 4:])
         st["graph"].replay()
         routed = st["routed"][:B].clone() if st["routed"] is not None else None
         return st["logits"][:B].clone(), routed
