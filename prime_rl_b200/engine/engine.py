@@ -62,6 +62,7 @@ class Engine:
         self._inbox: list[Request] = []
         self._commands: list[tuple] = []
         self.mark = None
+        self._sampling_cache = None
         if tp is not None and tp.size > 1:
             from .tp import shard_model_
 
@@ -341,16 +342,22 @@ class Engine:
 
     def _sample_and_append(self, reqs, logits, routed, routed_rows) -> None:
         dev = logits.device
-        temp = torch.tensor([r.params.temperature for r in reqs], dtype=torch.float32, device=dev)
-        top_k = torch.tensor([r.params.top_k for r in reqs], dtype=torch.long, device=dev)
-        top_p = torch.tensor([r.params.top_p for r in reqs], dtype=torch.float32, device=dev)
+        # the sampling parameters of an unchanged set of requests stay on the device from step to step
+        c = self._sampling_cache           # holds the request objects themselves, so an identity match cannot be stale
+        if c is None or len(c[0]) != len(reqs) or any(a is not b for a, b in zip(c[0], reqs)):
+            self._sampling_cache = (list(reqs),
+                                    torch.tensor([r.params.temperature for r in reqs], dtype=torch.float32, device=dev),
+                                    torch.tensor([r.params.top_k for r in reqs], dtype=torch.long, device=dev),
+                                    torch.tensor([r.params.top_p for r in reqs], dtype=torch.float32, device=dev))
+        _, temp, top_k, top_p = self._sampling_cache
         want_mask = any(r.params.return_sampling_mask and r.params.truncated for r in reqs)
         gen = reqs[0].generator if len(reqs) == 1 else None
         tok, lp, masks = sample(logits, temp, top_k, top_p, generator=gen, want_mask=want_mask,
                                 truncated=any(r.params.truncated for r in reqs))
         if self.tp_size > 1:                       # every rank appends rank 0's draw
             tok, lp = self.tp.broadcast_sample(tok, lp)
-        tok_l, lp_l = tok.tolist(), lp.tolist()
+        both = torch.stack([tok.double(), lp.double()]).tolist()       # one device-to-host read per step
+        tok_l, lp_l = [int(t) for t in both[0]], both[1]
         self.stats["generation_tokens"] += len(reqs)
         for i, r in enumerate(reqs):
             r.output.append(tok_l[i])
