@@ -270,3 +270,29 @@ def test_tensor_parallel_http_server_serves_the_same_tokens(tmp_path):
         except subprocess.TimeoutExpired:
             os.killpg(proc.pid, signal.SIGKILL)
         log.close()
+
+
+def test_rope_to_cache_fallback_writes_the_same_cache_rows():
+    """Without the fused kernel (CPU), ``qkv_rope_to_cache`` is ``qkv_norm_rope`` plus index writes into the pages."""
+    from prime_rl_b200 import ops
+
+    torch.manual_seed(0)
+    T, nq, nkv, D, pages, ps = 9, 4, 2, 16, 3, 4
+    qkv = torch.randn(T, (nq + 2 * nkv) * D)
+    qw, kw = torch.rand(D) + 0.5, torch.rand(D) + 0.5
+    pos = torch.arange(T, dtype=torch.int32)
+    inv_f = ops.inv_freq(D, 1e4)
+    slots = torch.randperm(pages * ps)[:T]
+    kc, vc = torch.zeros(pages, ps, nkv, D), torch.zeros(pages, ps, nkv, D)
+    q, k, v = ops.qkv_rope_to_cache(qkv, qw, kw, pos, inv_f, 1e-6, nq, nkv, D, kc, vc, slots)
+    q0, k0, v0 = ops.qkv_norm_rope(qkv, qw, kw, pos, inv_f, 1e-6, nq, nkv, D)
+    assert torch.equal(q, q0) and torch.equal(k, k0) and torch.equal(v, v0)
+    assert torch.equal(kc.view(-1, nkv, D)[slots], k0) and torch.equal(vc.view(-1, nkv, D)[slots], v0)
+    assert int((kc.view(-1, nkv * D).abs().sum(-1) > 0).sum()) == T
+
+
+def test_small_route_plan_is_gpu_only():
+    from prime_rl_b200.ops import moe as moe_ops
+
+    with torch.no_grad():
+        assert moe_ops.route_and_plan_small(torch.randn(4, 8), 2) is None
