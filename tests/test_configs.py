@@ -52,3 +52,19 @@ def test_resolved_json_round_trip():
     c = cli(TrainerConfig, ["--model.lora.rank", "8", "--max-steps", "3"])
     again = TrainerConfig.model_validate(json.loads(c.to_json()))
     assert again == c
+
+
+def test_tensor_parallel_inference_in_the_rl_config(tmp_path):
+    """num_infer_gpus splits into replicas x tensor-parallel ranks; sharded engines only take filesystem updates."""
+    import pytest
+
+    from prime_rl_b200.configs.rl import RLConfig
+
+    base = {"deployment": {"type": "single_node", "num_infer_gpus": 4, "num_train_gpus": 2},
+            "inference": {"vllm": {"tensor_parallel_size": 2}}, "output_dir": str(tmp_path)}
+    cfg = RLConfig.model_validate(base)
+    assert cfg.inference.vllm.data_parallel_size == 2 and cfg.inference.vllm.tensor_parallel_size == 2
+    with pytest.raises(ValueError):
+        RLConfig.model_validate(dict(base, deployment=dict(base["deployment"], num_infer_gpus=3)))
+    with pytest.raises(ValueError):
+        RLConfig.model_validate(dict(base, trainer={"weight_broadcast": {"type": "nccl"}}))
