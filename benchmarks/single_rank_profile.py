@@ -1,14 +1,14 @@
 """Runs the peer-memory kernels with a process group of ONE rank (every "peer" pointer is this
 GPU's own buffer), so that a single-GPU profiler capture can look at them:
 
-    python -m prime_rl_b200.parallel.single_rank_profile --op ep      # dispatch / combine kernels
-    python -m prime_rl_b200.parallel.single_rank_profile --op rs      # GEMM with the reduce-scatter epilogue
-    python -m prime_rl_b200.parallel.single_rank_profile --op push    # weight copy / fp8 quantising push
-    python -m prime_rl_b200.parallel.single_rank_profile --op ep8     # EP dispatch with the fp8 payload
-    python -m prime_rl_b200.parallel.single_rank_profile --op ag      # GEMM with the all-gather prologue (2 emulated ranks)
-    python -m prime_rl_b200.parallel.single_rank_profile --op cp      # flash forward with the K/V gather warp (2 emulated ranks)
-    python -m prime_rl_b200.parallel.single_rank_profile --op zero    # optimizer reduce-scatter pull / all-gather push
-    python -m prime_rl_b200.parallel.single_rank_profile --op tp      # engine all-reduce + residual + RMSNorm (2 emulated ranks)
+    python -m benchmarks.single_rank_profile --op ep      # dispatch / combine kernels
+    python -m benchmarks.single_rank_profile --op rs      # GEMM with the reduce-scatter epilogue
+    python -m benchmarks.single_rank_profile --op push    # weight copy / fp8 quantising push
+    python -m benchmarks.single_rank_profile --op ep8     # EP dispatch with the fp8 payload
+    python -m benchmarks.single_rank_profile --op ag      # GEMM with the all-gather prologue (2 emulated ranks)
+    python -m benchmarks.single_rank_profile --op cp      # flash forward with the K/V gather warp (2 emulated ranks)
+    python -m benchmarks.single_rank_profile --op zero    # optimizer reduce-scatter pull / all-gather push
+    python -m benchmarks.single_rank_profile --op tp      # engine all-reduce + residual + RMSNorm (2 emulated ranks)
 
 The traffic that would cross NVLink stays in local HBM here; instruction mix, occupancy and
 local-memory behaviour are what such a capture shows.
@@ -36,7 +36,7 @@ def main(argv=None):
     dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
     group = dist.group.WORLD
     torch.manual_seed(0)
-    from ..ops import _runtime as rt
+    from prime_rl_b200.ops import _runtime as rt
 
     if args.op == "ag":
         import ctypes
@@ -56,7 +56,7 @@ def main(argv=None):
     elif args.op == "cp":
         import ctypes
 
-        from ..ops import flash_native
+        from prime_rl_b200.ops import flash_native
 
         Tl, Hq, Hkv = args.tokens, 32, 4                          # "rank 1" of 2: chunk 0 is pulled from the other buffer
         T = 2 * Tl
@@ -97,10 +97,14 @@ def main(argv=None):
             rt.check(rt.lib().prb_rs_pull(pg, 0, n // 2, 0.5, shard.data_ptr(), 2, rt.stream_ptr(dev)), "prb_rs_pull")
             rt.check(rt.lib().prb_ag_push(flats[0].data_ptr(), pf, 0, n, 0, 2, rt.stream_ptr(dev)), "prb_ag_push")
     elif args.op in ("ep", "ep8"):
-        from ..models.layers import GroupedExperts
-        from ..ops import moe as moe_ops
-        from .ep_p2p import P2PDispatcher
-        from .ep_selftest import _arch
+        from prime_rl_b200.models.layers import GroupedExperts
+        from prime_rl_b200.ops import moe as moe_ops
+        from prime_rl_b200.parallel.ep_p2p import P2PDispatcher
+        from prime_rl_b200.models.config import PRESETS, ModelArch
+
+        def _arch(E, H, I, k):
+            return ModelArch(**{**PRESETS["tiny-qwen3-moe"], "num_experts": E, "hidden_size": H,
+                                "moe_intermediate_size": I, "num_experts_per_tok": k})
 
         T, E, H, I, k = args.tokens, 128, 2048, 768, 8
         ex = GroupedExperts(_arch(E, H, I, k), num_local_experts=E, dtype=torch.bfloat16, device=dev)
@@ -115,7 +119,7 @@ def main(argv=None):
             y = disp(ex, x, idx.to(torch.int32).contiguous(), w, counts)
             y.backward(torch.randn_like(y))
     elif args.op == "rs":
-        from .fused_collectives import GemmReduceScatter
+        from prime_rl_b200.parallel.fused_collectives import GemmReduceScatter
 
         T, N, K = args.tokens, 4096, 2048
         op = GemmReduceScatter(group, N, K, dev)
@@ -123,7 +127,7 @@ def main(argv=None):
         for _ in range(args.iters):
             op(dy, x, a_mn=True, b_mn=True)
     else:
-        from ..models.fp8 import quantize_to_fp8_blockwise
+        from prime_rl_b200.models.fp8 import quantize_to_fp8_blockwise
 
         w = torch.randn(args.tokens * 16, 2048, device=dev).bfloat16()       # 256 MB at the default size
         dst = torch.empty_like(w)

@@ -14,7 +14,23 @@
 
 #define PRB_API extern "C" __attribute__((visibility("default")))
 
+#include <atomic>
+
 namespace prb {
+
+// One-time set-up per (call site, device): kernel attributes such as the dynamic shared
+// memory limit belong to the device that was current when they were set, so a process that
+// drives several GPUs has to set them once on each. Safe to race: setting twice is harmless.
+struct DeviceOnce {
+  std::atomic<unsigned long long> done{0};
+  static unsigned long long bit() {
+    int d = 0;
+    cudaGetDevice(&d);
+    return 1ull << (d & 63);
+  }
+  bool pending() const { return !(done.load(std::memory_order_acquire) & bit()); }
+  void mark() { done.fetch_or(bit(), std::memory_order_release); }
+};
 
 // ---------------------------------------------------------------- status word codes
 enum StatusCode : int {

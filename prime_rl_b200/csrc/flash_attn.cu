@@ -515,11 +515,11 @@ PRB_API int prb_flash_fwd_slice(const void* q, const void* k, const void* v, voi
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.ld_out = ld_out; p.lse = lse;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.window = window; p.status = status;
-  static bool configured = false;
-  if (!configured) {
+  static prb::DeviceOnce configured;
+  if (configured.pending()) {
     if (cudaFuncSetAttribute(flash_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFaSmem) != cudaSuccess)
       return -10;
-    configured = true;
+    configured.mark();
   }
   dim3 grid(max_pairs, heads_q);
   flash_fwd_kernel<false><<<grid, kFaThreads, kFaSmem, stream>>>(tmQ, tmK, tmV, p);
@@ -569,11 +569,11 @@ PRB_API int prb_flash_fwd_gather(const void* q, void* kv_local, void* const* pee
   p.cp_rank = cp_rank; p.chunk_rows = chunk_rows;
   p.row_bytes = ldkv * 2; p.v_off = v_off_bytes;
   if (cudaMemsetAsync(counters, 0, sizeof(unsigned) * (cp_size + 1), stream) != cudaSuccess) return -12;
-  static bool configured = false;
-  if (!configured) {
+  static prb::DeviceOnce configured;
+  if (configured.pending()) {
     if (cudaFuncSetAttribute(flash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFaSmem) != cudaSuccess)
       return -10;
-    configured = true;
+    configured.mark();
   }
   dim3 grid(max_pairs, heads_q);
   flash_fwd_kernel<true><<<grid, kFaThreads + 32, kFaSmem, stream>>>(tmQ, tmK, tmV, p);

@@ -670,12 +670,12 @@ PRB_API int prb_flash_bwd_slice(const void* q, const void* k, const void* v, con
   p.dk = reinterpret_cast<__nv_bfloat16*>(dk); p.dv = reinterpret_cast<__nv_bfloat16*>(dv);
   p.ld_dk = ld_dk; p.ld_dv = ld_dv;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f; p.window = window; p.status = status;
-  static bool configured = false;
-  if (!configured) {
+  static prb::DeviceOnce configured;
+  if (configured.pending()) {
     if (cudaFuncSetAttribute(flash_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwSmem) != cudaSuccess ||
         cudaFuncSetAttribute(flash_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwSmem) != cudaSuccess)
       return -10;
-    configured = true;
+    configured.mark();
   }
   flash_bwd_dkdv_kernel<<<dim3(max_blocks, heads_kv), kBwThreads, kBwSmem, stream>>>(tmQ, tmK, tmV, tmDO, p);
   flash_bwd_dq_kernel<<<dim3(max_blocks, heads_q), kBwThreads, kBwSmem, stream>>>(tmQ, tmK, tmV, tmDO, p);

@@ -671,11 +671,11 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   using Cfg = GemmCfg<BN>;
   using Sched = typename std::conditional<GROUPED, SchedGrouped, SchedDense>::type;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, Sched, EpiStore>;
-  static bool configured = false;
-  if (!configured) {
+  static prb::DeviceOnce configured;
+  if (configured.pending()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return -10;
-    configured = true;
+    configured.mark();
   }
   const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
@@ -868,11 +868,11 @@ PRB_API int prb_gemm_bf16_reduce_scatter(const void* A, const void* B, int M, in
 #define PRB_RS_LAUNCH(AMN, BMN)                                                                              \
   {                                                                                                          \
     auto kern = gemm_bf16_kernel<256, AMN, BMN, SchedDense, EpiPeerReduce>;                                  \
-    static bool configured = false;                                                                          \
-    if (!configured) {                                                                                       \
+    static prb::DeviceOnce configured;                                                                          \
+    if (configured.pending()) {                                                                                       \
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) \
         return -10;                                                                                          \
-      configured = true;                                                                                     \
+      configured.mark();                                                                                     \
     }                                                                                                        \
     kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmA, tmB, p);                            \
   }
@@ -936,11 +936,11 @@ PRB_API int prb_gemm_bf16_allgather(const void* A, void* w_local, void* const* p
 #define PRB_AG_LAUNCH(AMN)                                                                                   \
   {                                                                                                          \
     auto kern = gemm_bf16_kernel<256, AMN, false, SchedAllGather, EpiStore>;                                 \
-    static bool configured = false;                                                                          \
-    if (!configured) {                                                                                       \
+    static prb::DeviceOnce configured;                                                                          \
+    if (configured.pending()) {                                                                                       \
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess) \
         return -10;                                                                                          \
-      configured = true;                                                                                     \
+      configured.mark();                                                                                     \
     }                                                                                                        \
     kern<<<grid, kGemmThreads + 32 * SchedAllGather::kGatherWarps, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmA, tmB, p); \
   }
@@ -1015,6 +1015,14 @@ PRB_API int prb_lmhead_fwd(const void* h, const void* W, const int* labels, cons
   using namespace prb;
   if (T <= 0) return 0;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (splits < 1) return -12;
+  {
+    // a slice without vocabulary tiles writes no partial row, and the merge reads every row:
+    // use only as many slices as own at least one tile (the scratch layout is indexed by slice)
+    const int tiles_n = (V + 255) / 256;
+    const int per = (tiles_n + splits - 1) / splits;
+    splits = (tiles_n + per - 1) / per;
+  }
   CUtensorMap tmA, tmB;
   int rc = lmhead_maps(&tmA, &tmB, h, W, T, V, H, ldh, ldw);
   if (rc) return rc;
@@ -1027,11 +1035,11 @@ PRB_API int prb_lmhead_fwd(const void* h, const void* W, const int* labels, cons
   cudaMemsetAsync(target, 0, sizeof(float) * T, stream);
   using Cfg = GemmCfg<256>;
   auto kern = gemm_bf16_kernel<256, false, false, SchedSplit, EpiLogprobStats>;
-  static bool configured = false;
-  if (!configured) {
+  static prb::DeviceOnce configured;
+  if (configured.pending()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
       return -10;
-    configured = true;
+    configured.mark();
   }
   const int items = ((T + 127) / 128) * splits;
   const int grid = items < sm_count() ? items : sm_count();
@@ -1058,11 +1066,11 @@ PRB_API int prb_lmhead_bwd_dlogits(const void* h, const void* W, const int* labe
   p.labels = labels; p.inv_temp = inv_temp; p.grad_logprob = grad_logprob; p.lse = lse;
   using Cfg = GemmCfg<256>;
   auto kern = gemm_bf16_kernel<256, false, false, SchedDense, EpiDLogits>;
-  static bool configured = false;
-  if (!configured) {
+  static prb::DeviceOnce configured;
+  if (configured.pending()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
       return -10;
-    configured = true;
+    configured.mark();
   }
   const int tiles = ((T + 127) / 128) * ((V + 255) / 256);
   const int grid = tiles < sm_count() ? tiles : sm_count();
@@ -1102,12 +1110,12 @@ PRB_API int prb_gemm_bf16_kgrouped(const void* A, const void* B, void* C, int M,
 #define PRB_KG(BN_)                                                                                       \
   {                                                                                                       \
     auto kern = gemm_bf16_kernel<BN_, true, true, SchedKGrouped, EpiStore>;                               \
-    static bool configured = false;                                                                       \
-    if (!configured) {                                                                                    \
+    static prb::DeviceOnce configured;                                                                       \
+    if (configured.pending()) {                                                                                    \
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                         \
                                GemmCfg<BN_>::SMEM_BYTES) != cudaSuccess)                                  \
         return -10;                                                                                       \
-      configured = true;                                                                                  \
+      configured.mark();                                                                                  \
     }                                                                                                     \
     kern<<<grid, kGemmThreads, GemmCfg<BN_>::SMEM_BYTES, stream>>>(tmA, tmB, tmA, tmB, p);                          \
   }

@@ -250,11 +250,11 @@ PRB_API int prb_gemm_fp8(const void* Aq, const float* sa, const void* Bq, const 
   p.M = M; p.N = N; p.K = K; p.sa = sa; p.sb = sb;
   p.C = reinterpret_cast<__nv_bfloat16*>(C); p.ldc = ldc;
   p.block_expert = block_expert; p.b_rows_per_expert = grouped ? N : 0; p.status = status;
-  static bool configured = false;
-  if (!configured) {
+  static prb::DeviceOnce configured;
+  if (configured.pending()) {
     if (cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kF8Smem) != cudaSuccess)
       return -10;
-    configured = true;
+    configured.mark();
   }
   const int tiles = ((M + kF8BM - 1) / kF8BM) * ((N + kF8BN - 1) / kF8BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();

@@ -363,12 +363,12 @@ PRB_API int prb_paged_decode(const void* q, const void* kpool, const void* vpool
     constexpr int smem = kPdWarps * kPmWarpBytes;     // 64 KB (also holds the 17 KB merge scratch)
 #define PRB_PM_LAUNCH(GG)                                                                                       \
     {                                                                                                           \
-      static bool configured = false;                                                                           \
-      if (!configured) {                                                                                        \
+      static prb::DeviceOnce configured;                                                                           \
+      if (configured.pending()) {                                                                                        \
         if (cudaFuncSetAttribute(paged_decode_mma_kernel<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != \
             cudaSuccess)                                                                                        \
           return -10;                                                                                           \
-        configured = true;                                                                                      \
+        configured.mark();                                                                                      \
       }                                                                                                         \
       paged_decode_mma_kernel<GG><<<grid, kPdWarps * 32, smem, stream>>>(p);                                    \
     }

@@ -322,11 +322,11 @@ PRB_API int prb_sparse_mla_fwd(const void* q, const void* kv, const int* idx, vo
   int rc = make_tmap_2d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)T * H, (uint64_t)kMlaD, (uint64_t)kMlaD,
                         128, 64, true);
   if (rc) return rc;
-  static bool configured = false;
-  if (!configured) {
+  static prb::DeviceOnce configured;
+  if (configured.pending()) {
     if (cudaFuncSetAttribute(sparse_mla_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem) != cudaSuccess)
       return -10;
-    configured = true;
+    configured.mark();
   }
   MlaParams p;
   p.kv = reinterpret_cast<const __nv_bfloat16*>(kv);

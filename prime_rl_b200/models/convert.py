@@ -91,6 +91,7 @@ class StackExperts:
 
     stacked_suffix: str      # e.g. "mlp.experts.gate_proj"
     per_expert_fmt: str      # e.g. "mlp.experts.{e}.gate_proj.weight"
+    first: int = 0           # global index of the first stacked expert (expert-parallel ranks hold a range)
 
     def forward(self, sd: StateDict) -> StateDict:  # stacked -> per expert
         out: StateDict = {}
@@ -98,7 +99,7 @@ class StackExperts:
             if k.endswith(self.stacked_suffix):
                 base = k[: -len(self.stacked_suffix)]
                 for e in range(v.shape[0]):
-                    out[base + self.per_expert_fmt.format(e=e)] = v[e]
+                    out[base + self.per_expert_fmt.format(e=self.first + e)] = v[e]
             else:
                 out[k] = v
         return out
@@ -233,7 +234,7 @@ def _family_chain(arch: ModelArch) -> list:
     return ops
 
 
-def _deepseek_v4_chain(arch: ModelArch) -> Chain:
+def _deepseek_v4_chain(arch: ModelArch, first_expert: int = 0) -> Chain:
     """The published DeepSeek-V4 checkpoints use a compact naming without a ``model.`` prefix
     (``layers.N.attn.wq_a``, ``ffn.experts.E.w1`` ...; reference:
     src/prime_rl/trainer/models/deepseek_v4/converting_deepseek_v4.py:27-106)."""
@@ -265,16 +266,18 @@ def _deepseek_v4_chain(arch: ModelArch) -> Chain:
                       f"{a}.mlp.shared_experts.gate_proj.weight": f"{b}.ffn.shared_experts.w1.weight",
                       f"{a}.mlp.shared_experts.down_proj.weight": f"{b}.ffn.shared_experts.w2.weight",
                       f"{a}.mlp.shared_experts.up_proj.weight": f"{b}.ffn.shared_experts.w3.weight"})
-    return Chain([StackExperts("mlp.experts.gate_proj", "ffn.experts.{e}.w1.weight"),
-                  StackExperts("mlp.experts.down_proj", "ffn.experts.{e}.w2.weight"),
-                  StackExperts("mlp.experts.up_proj", "ffn.experts.{e}.w3.weight"),
+    return Chain([StackExperts("mlp.experts.gate_proj", "ffn.experts.{e}.w1.weight", first_expert),
+                  StackExperts("mlp.experts.down_proj", "ffn.experts.{e}.w2.weight", first_expert),
+                  StackExperts("mlp.experts.up_proj", "ffn.experts.{e}.w3.weight", first_expert),
                   ExactMap(table),
                   Rename(r"^model\.layers\.", "layers.", r"^layers\.", "model.layers.")])
 
 
-def prime_to_hf_chain(arch: ModelArch) -> Chain:
+def prime_to_hf_chain(arch: ModelArch, first_expert: int = 0) -> Chain:
+    """``first_expert``: global index of the first expert in the stacked tensors (an expert-parallel
+    rank exports its own range under global numbers)."""
     if arch.model_type == "deepseek_v4":
-        return _deepseek_v4_chain(arch)
+        return _deepseek_v4_chain(arch, first_expert)
     ops: list = []
     if arch.model_type in ("qwen3_5_moe",):
         ops += [Rename(r"mlp\.shared_experts\.", r"mlp.shared_expert.", r"mlp\.shared_expert\.", r"mlp.shared_experts.")]
@@ -283,8 +286,8 @@ def prime_to_hf_chain(arch: ModelArch) -> Chain:
                        r"mlp.router.gate.\1"),
                 Rename(r"mlp\.router\.e_score_correction_bias$", r"mlp.gate.e_score_correction_bias",
                        r"mlp\.gate\.e_score_correction_bias$", r"mlp.router.e_score_correction_bias"),
-                StackExperts("mlp.experts.up_proj", "mlp.experts.{e}.up_proj.weight"),
-                StackExperts("mlp.experts.down_proj", "mlp.experts.{e}.down_proj.weight")]
+                StackExperts("mlp.experts.up_proj", "mlp.experts.{e}.up_proj.weight", first_expert),
+                StackExperts("mlp.experts.down_proj", "mlp.experts.{e}.down_proj.weight", first_expert)]
         return Chain(ops + _family_chain(arch))
     if arch.model_type == "laguna":
         # Laguna checkpoints name the shared expert in the singular and keep the selection bias under `experts`
@@ -299,9 +302,9 @@ def prime_to_hf_chain(arch: ModelArch) -> Chain:
                    r"mlp.router.gate.\1"),
             Rename(r"mlp\.router\.e_score_correction_bias$", r"mlp.gate.e_score_correction_bias",
                    r"mlp\.gate\.e_score_correction_bias$", r"mlp.router.e_score_correction_bias"),
-            StackExperts("mlp.experts.gate_proj", "mlp.experts.{e}.gate_proj.weight"),
-            StackExperts("mlp.experts.up_proj", "mlp.experts.{e}.up_proj.weight"),
-            StackExperts("mlp.experts.down_proj", "mlp.experts.{e}.down_proj.weight"),
+            StackExperts("mlp.experts.gate_proj", "mlp.experts.{e}.gate_proj.weight", first_expert),
+            StackExperts("mlp.experts.up_proj", "mlp.experts.{e}.up_proj.weight", first_expert),
+            StackExperts("mlp.experts.down_proj", "mlp.experts.{e}.down_proj.weight", first_expert),
         ]
     return Chain(ops + _family_chain(arch))
 
@@ -314,8 +317,8 @@ def prime_to_native(sd: StateDict, arch: ModelArch) -> StateDict:
     return native_to_prime_chain(arch).inverse(sd)
 
 
-def prime_to_hf(sd: StateDict, arch: ModelArch) -> StateDict:
-    sd = prime_to_hf_chain(arch).forward(sd)
+def prime_to_hf(sd: StateDict, arch: ModelArch, first_expert: int = 0) -> StateDict:
+    sd = prime_to_hf_chain(arch, first_expert).forward(sd)
     if arch.tie_word_embeddings:
         sd.pop("lm_head.weight", None)
     return sd
@@ -333,13 +336,47 @@ def hf_to_native(sd: StateDict, arch: ModelArch) -> StateDict:
     return prime_to_native(hf_to_prime(sd, arch), arch)
 
 
-def model_state(model, layout: str = "prime", include_lora: bool = False) -> StateDict:
-    """State dict of a CausalLM in the requested layout (views, no copies where possible)."""
+def is_expert_sharded_key(key: str) -> bool:
+    """Tensors that expert parallelism slices on their leading (expert) dimension, in the native and
+    prime layouts: the stacked expert projections and the adapters attached to them."""
+    return ".mlp.experts." in key and not key.endswith("e_score_correction_bias")
+
+
+def expert_parallel_info(model):
+    """``None`` or the record ``install_expert_parallel`` leaves on the model: ``ep``, ``ep_rank``,
+    ``group`` (the ep process group), ``num_experts``, ``local_experts``, ``writer`` (this rank's ep
+    group is the one that exports weights when several groups replicate the experts)."""
+    info = getattr(model, "ep_info", None)
+    return info if info is not None and info["ep"] > 1 else None
+
+
+def model_state(model, layout: str = "prime", include_lora: bool = False, gather_experts: bool = False) -> StateDict:
+    """State dict of a CausalLM in the requested layout (views, no copies where possible).
+
+    With expert parallelism every rank holds ``[E / ep, ...]`` slices: ``layout="hf"`` then numbers
+    this rank's experts globally; ``gather_experts=True`` (a collective over the ep group, every
+    rank of it must call) returns the full stacks instead."""
     sd = {k: v for k, v in model.state_dict().items() if include_lora or "lora_" not in k}
+    info = expert_parallel_info(model)
+    first = 0
+    if info is not None:
+        if gather_experts:
+            sd = {k: (gather_expert_shards(v, info) if is_expert_sharded_key(k) else v) for k, v in sd.items()}
+        else:
+            first = info["ep_rank"] * info["local_experts"]
     if layout == "native":
         return sd
     sd = native_to_prime(sd, model.arch)
-    return sd if layout == "prime" else prime_to_hf(sd, model.arch)
+    return sd if layout == "prime" else prime_to_hf(sd, model.arch, first)
+
+
+def gather_expert_shards(local: torch.Tensor, info) -> torch.Tensor:
+    """All-gather of one expert-sharded tensor over the ep group -> ``[E, ...]`` on every rank."""
+    import torch.distributed as dist
+
+    parts = [torch.empty_like(local) for _ in range(info["ep"])]
+    dist.all_gather(parts, local.detach().contiguous(), group=info["group"])
+    return torch.cat(parts, dim=0)
 
 
 @torch.no_grad()
@@ -355,8 +392,12 @@ def load_model_state(model, sd: StateDict, layout: str = "prime", strict: bool =
     if strict and (missing or unexpected):
         raise KeyError(f"state dict mismatch: missing={missing[:5]} unexpected={unexpected[:5]}")
     shard = getattr(model, "tp_shard", None)      # engine tensor parallelism: this process keeps one slice
+    info = expert_parallel_info(model)
     for k, v in sd.items():
         if k in own:
+            if info is not None and is_expert_sharded_key(k) and v.shape[0] == info["num_experts"] != own[k].shape[0]:
+                lo = info["ep_rank"] * info["local_experts"]      # a full stack: keep this rank's expert range
+                v = v[lo:lo + info["local_experts"]]
             own[k].copy_((v if shard is None else shard(k, v)).to(own[k].dtype))
 
 

@@ -363,19 +363,32 @@ class Orchestrator:
         m.update({f"watcher/{k}": v for k, v in self.watcher.stats.items()})
         return m
 
-    async def _metrics_loop(self) -> None:
+    async def _metrics_loop(self, max_consecutive_failures: int = 30) -> None:
+        """Polls the engines' metrics once a second and feeds the concurrency controller. A scrape
+        that fails is logged and retried; after ``max_consecutive_failures`` in a row the task raises,
+        which ends the run (the controller would otherwise be silently blind to KV pressure)."""
+        failures = 0
         while True:
             await asyncio.sleep(1.0)
             try:
                 ms = await self.admin.metrics()
-                usage = max((m.get("vllm:kv_cache_usage_perc", 0.0) for m in ms), default=0.0)
-                waiting = sum(m.get("vllm:num_requests_waiting", 0.0) for m in ms)
-                pre = sum(m.get("vllm:num_preemptions_total", 0.0) for m in ms)
-                d = self.controller.update(usage, waiting, pre, len(self.dispatcher.inflight))
-                if d.cancel:
-                    self.dispatcher.cancel_newest(d.cancel)
-            except Exception:
-                pass
+            except asyncio.CancelledError:
+                raise
+            except Exception as e:
+                failures += 1
+                self.logger.warning(f"inference metrics scrape failed ({failures}/{max_consecutive_failures}): "
+                                    f"{type(e).__name__}: {e}")
+                if failures >= max_consecutive_failures:
+                    raise RuntimeError("inference metrics endpoint unreachable: concurrency control cannot work "
+                                       "(set collect_inference_metrics = false to run without it)") from e
+                continue
+            failures = 0
+            usage = max((m.get("vllm:kv_cache_usage_perc", 0.0) for m in ms), default=0.0)
+            waiting = sum(m.get("vllm:num_requests_waiting", 0.0) for m in ms)
+            pre = sum(m.get("vllm:num_preemptions_total", 0.0) for m in ms)
+            d = self.controller.update(usage, waiting, pre, len(self.dispatcher.inflight))
+            if d.cancel:
+                self.dispatcher.cancel_newest(d.cancel)
 
     async def run(self) -> None:
         c = self.config

@@ -85,6 +85,7 @@ def install_expert_parallel(model, dims, moe_cfg=None) -> None:
     ep_rank = dims.coords(rank)["ep"]
     group = dims.group("ep")
     kind = getattr(getattr(moe_cfg, "dispatch", None), "type", "torch")
+    model.ep_info = None
     for moe in model.moe_layers():
         E = moe.arch.num_experts
         if E % ep:
@@ -111,3 +112,9 @@ def install_expert_parallel(model, dims, moe_cfg=None) -> None:
         else:
             moe.dispatcher = TorchA2ADispatcher(group, ep, E)
         moe.ep_rank, moe.ep = ep_rank, ep
+        if model.ep_info is None:
+            # what checkpoints and weight transports need to know about the slicing; when several ep
+            # groups replicate the experts, the group of global rank 0 is the one that exports them
+            model.ep_info = {"ep": ep, "ep_rank": ep_rank, "group": group, "num_experts": E, "local_experts": El,
+                             "writer": rank < ep, "replicas": dims.world_size // ep,
+                             "replica": rank // ep, "rank_lists": dims._rank_lists("ep")}

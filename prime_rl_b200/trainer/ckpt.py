@@ -32,13 +32,51 @@ class Progress:
     total_samples: int = 0
 
 
-def _optimizer_state_prime(optimizer, arch) -> dict:
-    """Optimizer tensors under prime names (fused parameters split like the weights)."""
-    sd = optimizer.state_dict()
+def _optimizer_state_prime(sd: dict, arch) -> dict:
+    """``FlatOptimizer.state_dict()`` tensors under prime names (fused parameters split like the weights)."""
     out = {"step": torch.tensor(sd["step"])}
     for key, named in sd["state"].items():
         out[key] = convert.native_to_prime(dict(named), arch)
     return out
+
+
+def _ep_mesh(info, device_type: str):
+    """Device mesh ``(replica, ep)`` (or just ``(ep,)``) over which expert-sharded tensors are
+    described to DCP. Creating it is a collective over all ranks; it is cached on the record."""
+    if "mesh" not in info:
+        from torch.distributed.device_mesh import DeviceMesh
+
+        lists = info["rank_lists"]
+        if len(lists) == 1:
+            info["mesh"] = DeviceMesh.from_group(info["group"], device_type, mesh=torch.tensor(lists[0]),
+                                                 mesh_dim_names=("ep",))
+        else:
+            info["mesh"] = DeviceMesh(device_type, torch.tensor(lists), mesh_dim_names=("ep_replica", "ep"))
+    return info["mesh"]
+
+
+def _describe_expert_shards(tree: dict, model) -> dict:
+    """Expert-parallel ranks keep ``[E / ep, ...]`` slices under the same names. DCP treats equal names
+    of plain tensors as replicas and would keep one rank's slice, so the slices are presented as
+    DTensors sharded on dim 0 over the ep group (replicated over the groups that hold the same
+    slice): the checkpoint then holds the full ``[E, ...]`` stacks and can be read back with another
+    ep degree. The wrappers share storage with the live tensors, so a load still lands in place."""
+    info = convert.expert_parallel_info(model)
+    if info is None:
+        return tree
+    from torch.distributed.tensor import DTensor, Replicate, Shard
+
+    def wrap(prefix: str, node):
+        if isinstance(node, dict):
+            return {k: wrap(f"{prefix}.{k}", v) for k, v in node.items()}
+        if isinstance(node, torch.Tensor) and convert.is_expert_sharded_key(prefix) and node.dim() >= 1 \
+                and node.shape[0] == info["local_experts"]:
+            mesh = _ep_mesh(info, node.device.type)
+            placements = [Shard(0)] if mesh.ndim == 1 else [Replicate(), Shard(0)]
+            return DTensor.from_local(node.detach(), mesh, placements, run_check=False)
+        return node
+
+    return wrap("", tree)
 
 
 class CheckpointManager:
@@ -62,7 +100,8 @@ class CheckpointManager:
             dist.barrier()
         app = {"model": convert.model_state(model, "prime", include_lora=True)}
         if not (self.config and self.config.skip_optimizer) and optimizer is not None:
-            app["optimizer"] = _optimizer_state_prime(optimizer, model.arch)
+            app["optimizer"] = _optimizer_state_prime(optimizer.state_dict(), model.arch)
+        app = _describe_expert_shards(app, model)
         if not (self.config and self.config.skip_progress):
             app["progress"] = {k: torch.tensor(v) for k, v in asdict(progress).items()}
         dcp.save({"app": app}, checkpoint_id=str(path))
@@ -100,16 +139,21 @@ class CheckpointManager:
                     raise RuntimeError(f"checkpoint shard {f} is damaged: {have} bytes, expected {size}")
         app = {"model": convert.model_state(model, "prime", include_lora=True)}
         has_opt = optimizer is not None and not (self.config and self.config.skip_optimizer)
+        opt_sd = None
         if has_opt:
-            app["optimizer"] = _optimizer_state_prime(optimizer, model.arch)
+            opt_sd = optimizer.state_dict()
+            app["optimizer"] = _optimizer_state_prime(opt_sd, model.arch)
+        app = _describe_expert_shards(app, model)
         if not (self.config and self.config.skip_progress):
             app["progress"] = {k: torch.tensor(v) for k, v in asdict(progress).items()}
         dcp.load({"app": app}, checkpoint_id=str(path))
-        # the prime-layout tensors are views of the live parameters / optimizer buffers, so
-        # the load above already landed in place; scalars are copied back here
+        # The prime-layout model tensors are views of the live parameters, so the load landed in place.
+        # Optimizer tensors are views of ``opt_sd``: the live buffers where the state is not partitioned,
+        # gathered full-length copies where it is (ZeRO). ``load_state_dict`` copies them back into the
+        # owner's slice, refreshes the fp32 master and re-derives the compute-dtype parameters from it.
         if has_opt:
-            optimizer.step_count = int(app["optimizer"]["step"])
-            optimizer.sync_from_master()
+            opt_sd["step"] = int(app["optimizer"]["step"])
+            optimizer.load_state_dict(opt_sd)
         if "progress" in app:
             for k, v in app["progress"].items():
                 setattr(progress, k, int(v))

@@ -41,35 +41,81 @@ def plan_shards(sizes: dict[str, int], max_shard_bytes: int) -> list[list[str]]:
     return [s for s in shards if s]
 
 
+def _is_expert_hf_key(name: str) -> bool:
+    return re.search(r"\.experts\.\d+\.", name) is not None
+
+
 @torch.no_grad()
 def save_hf_checkpoint(model, out_dir: Path, *, max_shard_bytes: int = 5 * 2 ** 30, dtype=torch.bfloat16,
                        tokenizer_dir: Path | None = None) -> Path:
+    """Replicated model: call on one rank. Expert-parallel model: a collective, every rank calls it;
+    the ranks of the exporting ep group each write the experts they own (numbered globally) into files
+    of their own, the first of them also writes everything else and the merged index."""
     out_dir = Path(out_dir)
+    info = convert.expert_parallel_info(model)
+    if info is not None:
+        return _save_hf_expert_parallel(model, out_dir, info, max_shard_bytes, dtype, tokenizer_dir)
     out_dir.mkdir(parents=True, exist_ok=True)
     sd = convert.model_state(model, "hf")
+    index = _write_shards(sd, out_dir, "model", max_shard_bytes, dtype)
+    (out_dir / "model.safetensors.index.json").write_text(json.dumps(index, indent=2))
+    _write_config(model, out_dir, tokenizer_dir)
+    return out_dir
+
+
+def _write_shards(sd: dict, out_dir: Path, stem: str, max_shard_bytes: int, dtype) -> dict:
     sizes = {k: v.numel() * torch.empty((), dtype=dtype).element_size() for k, v in sd.items()}
     shards = plan_shards(sizes, max_shard_bytes)
     index = {"metadata": {"total_size": sum(sizes.values())}, "weight_map": {}}
     for i, names in enumerate(shards):
-        fname = "model.safetensors" if len(shards) == 1 else f"model-{i + 1:05d}-of-{len(shards):05d}.safetensors"
+        fname = f"{stem}.safetensors" if len(shards) == 1 else f"{stem}-{i + 1:05d}-of-{len(shards):05d}.safetensors"
         save_file({n: sd[n].detach().to("cpu", dtype).contiguous() for n in names}, str(out_dir / fname),
                   metadata={"format": "pt"})
         for n in names:
             index["weight_map"][n] = fname
-    (out_dir / "model.safetensors.index.json").write_text(json.dumps(index, indent=2))
+    return index
+
+
+def _save_hf_expert_parallel(model, out_dir: Path, info, max_shard_bytes, dtype, tokenizer_dir) -> Path:
+    import torch.distributed as dist
+
+    leader = info["writer"] and info["ep_rank"] == 0
+    if leader:
+        out_dir.mkdir(parents=True, exist_ok=True)
+    dist.barrier()
+    index = None
+    if info["writer"]:
+        sd = convert.model_state(model, "hf")               # this rank's experts under their global numbers
+        mine = {k: v for k, v in sd.items() if _is_expert_hf_key(k) or leader}
+        index = _write_shards(mine, out_dir, f"model-ep{info['ep_rank']:02d}", max_shard_bytes, dtype)
+        parts = [None] * info["ep"]
+        dist.all_gather_object(parts, index, group=info["group"])
+        if leader:
+            merged = {"metadata": {"total_size": sum(p["metadata"]["total_size"] for p in parts)}, "weight_map": {}}
+            for p in parts:
+                merged["weight_map"].update(p["weight_map"])
+            (out_dir / "model.safetensors.index.json").write_text(json.dumps(merged, indent=2))
+            _write_config(model, out_dir, tokenizer_dir)
+    dist.barrier()
+    return out_dir
+
+
+def _write_config(model, out_dir: Path, tokenizer_dir: Path | None) -> None:
     (out_dir / "config.json").write_text(json.dumps(model.arch.to_hf_config(), indent=2))
     if tokenizer_dir is not None:
         import shutil
 
         for f in Path(tokenizer_dir).glob("token*"):
             shutil.copy(f, out_dir / f.name)
-    return out_dir
 
 
 @torch.no_grad()
 def save_lora_adapter(model, out_dir: Path, rank: int, alpha: float, target_modules: list[str]) -> Path:
     out_dir = Path(out_dir)
     out_dir.mkdir(parents=True, exist_ok=True)
+    if convert.expert_parallel_info(model) is not None:
+        raise NotImplementedError("LoRA adapter export of an expert-parallel model: gather the adapters first "
+                                  "(convert.model_state(..., gather_experts=True)) or train the adapters with ep = 1")
     sd = {k: v.detach().to("cpu").contiguous() for k, v in convert.lora_to_peft(model).items()}
     save_file(sd, str(out_dir / "adapter_model.safetensors"), metadata={"format": "pt"})
     (out_dir / "adapter_config.json").write_text(json.dumps({

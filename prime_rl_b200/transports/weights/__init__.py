@@ -79,8 +79,13 @@ class FileSystemWeightSender(WeightSender):
     def _broadcast(self, model, step, d):
         from ...trainer.weights import save_hf_checkpoint, save_lora_adapter
 
+        from ...models.convert import expert_parallel_info
+
+        if expert_parallel_info(model) is not None and self.lora_cfg is None:
+            save_hf_checkpoint(model, d)        # collective: every ep rank writes the experts it owns
+            return
         if not self.world.is_master:
-            return  # replicated weights: one writer is enough; sharded models gather in save_hf_checkpoint
+            return  # replicated weights: one writer is enough
         if self.lora_cfg is not None:
             save_lora_adapter(model, d, self.lora_cfg.rank, self.lora_cfg.alpha, self.lora_cfg.target_modules)
         else:

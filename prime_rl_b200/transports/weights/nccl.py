@@ -67,15 +67,28 @@ class NCCLWeightSender(WeightSender):
                                              self.config.inference_world_size + 1, self.config.timeout, device)
 
     def _broadcast(self, model, step, d):
-        if not self.world.is_master:
-            return
+        info = convert.expert_parallel_info(model)
+        if info is not None:
+            # Experts are sliced over the ep group: the ranks of the master's group gather them one decoder
+            # layer at a time (a collective among them), the master then broadcasts the full layer.
+            if not info["writer"]:
+                return
+            per_layer = _gathered_layers(model, info)
+        else:
+            if not self.world.is_master:
+                return
+            sd = convert.model_state(model, "hf")
+            per_layer = ({n: sd[n] for n in names} for names in layer_groups(list(sd)))
+            info = None
         device = next(model.parameters()).device
-        self._connect(device)
-        sd = convert.model_state(model, "hf")
-        groups = layer_groups(list(sd))
-        header = torch.tensor([len(groups)], dtype=torch.int64, device=device)
-        _broadcast(self.pg, header)
-        for names in groups:
+        if self.world.is_master:
+            self._connect(device)
+            n_groups = len(layer_groups(list(convert.model_state(model, "native"))))
+            _broadcast(self.pg, torch.tensor([n_groups], dtype=torch.int64, device=device))
+        for sd in per_layer:
+            if not self.world.is_master:
+                continue
+            names = list(sd)
             meta = [(n, tuple(sd[n].shape), str(sd[n].dtype).replace("torch.", "")) for n in names]
             blob = torch.frombuffer(bytearray(pickle.dumps(meta)), dtype=torch.uint8).to(device)
             size = torch.tensor([blob.numel()], dtype=torch.int64, device=device)
@@ -86,6 +99,16 @@ class NCCLWeightSender(WeightSender):
                 by_dtype.setdefault(dt, []).append(sd[n].detach().reshape(-1))
             for dt in sorted(by_dtype):
                 _broadcast(self.pg, torch.cat(by_dtype[dt]))
+
+
+def _gathered_layers(model, info):
+    """Yields the HF-layout tensors of one decoder layer at a time (then of everything else) with the
+    expert stacks all-gathered over the ep group, so that at most one layer's experts are held twice."""
+    native = {k: v for k, v in model.state_dict().items() if "lora_" not in k}
+    for names in layer_groups(list(native)):
+        part = {n: (convert.gather_expert_shards(native[n], info) if convert.is_expert_sharded_key(n) else native[n])
+                for n in names}
+        yield convert.native_to_hf(part, model.arch)
 
 
 class NCCLWeightReceiver:

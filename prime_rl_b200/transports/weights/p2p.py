@@ -10,8 +10,8 @@ port allocates). Parameters never move afterwards, so the manifest stays valid f
 Trainer side (``P2PWeightSender``): after the usual marker-file handshake (the engine is paused
 once ``.receiver_ready`` exists) map the handles (cached), launch one push kernel per tensor,
 synchronise, and let the base class touch ``.finished``. With several engine replicas trainer
-rank r serves replicas r, r + world, ...; parameters are replicated on the trainer, so no
-gather is needed.
+rank r serves replicas r, r + world, ...; replicated parameters need no gather, and an
+expert-parallel trainer has every rank write its own expert range at its offset of the engine's stack.
 
 Same role as the reference's NCCL / NIXL transports (src/prime_rl/transports/weights/nccl.py,
 nixl.py) for engines on the same NVSwitch box as the trainer.
@@ -129,8 +129,12 @@ class _Mapped:
         self.base = {}
 
 
-def push_state(named_tensors: dict[str, torch.Tensor], manifest: dict, mapped: _Mapped) -> int:
-    """Launches the push kernels on the current stream; returns the bytes written to the peer."""
+def push_state(named_tensors: dict[str, torch.Tensor], manifest: dict, mapped: _Mapped,
+               first_expert: dict[str, int] | None = None) -> int:
+    """Launches the push kernels on the current stream; returns the bytes written to the peer.
+
+    ``first_expert``: for an expert-parallel trainer, name -> index of the first expert of this
+    rank's ``[E / ep, ...]`` slice; the slice lands at that offset of the engine's full stack."""
     lib = rt.lib()
     total = 0
     for name, e in manifest["params"].items():
@@ -138,22 +142,36 @@ def push_state(named_tensors: dict[str, torch.Tensor], manifest: dict, mapped: _
         if t is None:
             continue
         t = t.detach()
-        if list(t.shape) != e["shape"]:
-            raise ValueError(f"{name}: trainer shape {list(t.shape)} != engine shape {e['shape']}")
+        lo = (first_expert or {}).get(name)
+        if lo is None:
+            if list(t.shape) != e["shape"]:
+                raise ValueError(f"{name}: trainer shape {list(t.shape)} != engine shape {e['shape']}")
+        else:
+            if list(t.shape[1:]) != e["shape"][1:] or lo + t.shape[0] > e["shape"][0]:
+                raise ValueError(f"{name}: expert slice {list(t.shape)} at {lo} does not fit engine shape {e['shape']}")
         dev = t.device
         stream = rt.stream_ptr(dev)
         if "fp8" in e and manifest.get("quantize") == "fp8" and t.dtype == torch.bfloat16:
             f = e["fp8"]
-            t2 = t.reshape(f["rows"], f["cols"])
+            rows, row0 = f["rows"], 0
+            if lo is not None:
+                per = f["rows"] // e["shape"][0]              # rows of the 2-D view per expert
+                rows, row0 = t.shape[0] * per, lo * per
+                if row0 % 128 or (rows % 128 and row0 + rows != f["rows"]):
+                    raise ValueError(f"{name}: expert slice is not aligned to the 128-row scale blocks")
+            t2 = t.reshape(rows, f["cols"])
             t2 = t2 if t2.is_contiguous() else t2.contiguous()
-            rt.check(lib.prb_weight_push_fp8(t2.data_ptr(), t2.stride(0), mapped.ptr(f["q"]), mapped.ptr(f["scales"]),
-                                             f["rows"], f["cols"], stream), "prb_weight_push_fp8")
-            total += f["rows"] * f["cols"] + 4 * ((f["rows"] + 127) // 128) * ((f["cols"] + 127) // 128)
+            scale_cols = (f["cols"] + 127) // 128
+            rt.check(lib.prb_weight_push_fp8(t2.data_ptr(), t2.stride(0), mapped.ptr(f["q"]) + row0 * f["cols"],
+                                             mapped.ptr(f["scales"]) + 4 * (row0 // 128) * scale_cols,
+                                             rows, f["cols"], stream), "prb_weight_push_fp8")
+            total += rows * f["cols"] + 4 * ((rows + 127) // 128) * scale_cols
         else:
             src = t.to(_DTYPES[e["dtype"]]) if str(t.dtype).replace("torch.", "") != e["dtype"] else t
             src = src if src.is_contiguous() else src.contiguous()
             nbytes = src.numel() * src.element_size()
-            rt.check(lib.prb_weight_push(src.data_ptr(), mapped.ptr(e), nbytes, stream), "prb_weight_push")
+            off = 0 if lo is None else lo * (nbytes // t.shape[0])
+            rt.check(lib.prb_weight_push(src.data_ptr(), mapped.ptr(e) + off, nbytes, stream), "prb_weight_push")
             total += nbytes
     return total
 
@@ -178,11 +196,27 @@ class P2PWeightSender(WeightSender):
         return self.manifests[replica]
 
     def _broadcast(self, model, step: int, d: Path) -> None:
+        from ...models.convert import expert_parallel_info, is_expert_sharded_key
+
         tensors = dict(model.named_parameters())
         pushed = 0
         t0 = time.monotonic()
-        for replica in range(self.world.rank, self.num_replicas, max(1, self.world.world_size)):
-            pushed += push_state(tensors, self._manifest(replica), self.mapped)
+        info = expert_parallel_info(model)
+        if info is not None:
+            # every rank of the exporting ep group writes the experts it owns into every replica; the
+            # replicated tensors of replica i come from the group's rank i % ep
+            if info["writer"]:
+                lo = info["ep_rank"] * info["local_experts"]
+                sliced = {n: t for n, t in tensors.items() if is_expert_sharded_key(n)}
+                dense = {n: t for n, t in tensors.items() if n not in sliced}
+                for replica in range(self.num_replicas):
+                    man = self._manifest(replica)
+                    pushed += push_state(sliced, man, self.mapped, first_expert={n: lo for n in sliced})
+                    if replica % info["ep"] == info["ep_rank"]:
+                        pushed += push_state(dense, man, self.mapped)
+        else:
+            for replica in range(self.world.rank, self.num_replicas, max(1, self.world.world_size)):
+                pushed += push_state(tensors, self._manifest(replica), self.mapped)
         torch.cuda.synchronize()
         if pushed:
             dt = time.monotonic() - t0

@@ -2,7 +2,7 @@
 flash-attention kernel, against the all-gather (NCCL) path: outputs and gradients of q, k, v on
 a packed two-document stream, then timings of forward + backward at a long sequence.
 
-    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m prime_rl_b200.parallel.cp_selftest
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m tests.distributed.cp_attention
 """
 
 from __future__ import annotations
@@ -14,8 +14,8 @@ from types import SimpleNamespace
 import torch
 import torch.distributed as dist
 
-from ..ops import _runtime as rt
-from .cp import ContextParallel
+from prime_rl_b200.ops import _runtime as rt
+from prime_rl_b200.parallel.cp import ContextParallel
 
 
 def _run(cp, q, k, v, seq, dout):

@@ -2,7 +2,7 @@
 the all-to-all baseline. Launch with one process per GPU:
 
     NCCL_NVLS_ENABLE=0 python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 \
-        --master-addr 127.0.0.1 --master-port 29533 -m prime_rl_b200.parallel.ep_selftest
+        --master-addr 127.0.0.1 --master-port 29533 -m tests.distributed.ep_dispatch
 
 Rank 0 prints ``EP_SELFTEST_OK`` with the largest deviations, then the device-timed
 forward + backward of both dispatchers (max over ranks) at a Qwen3-30B-A3B-like layer shape.
@@ -16,12 +16,12 @@ import sys
 import torch
 import torch.distributed as dist
 
-from ..models.config import ModelArch, PRESETS
-from ..models.layers import GroupedExperts
-from ..ops import _runtime as rt
-from ..ops import moe as moe_ops
-from .ep import TorchA2ADispatcher
-from .ep_p2p import P2PDispatcher
+from prime_rl_b200.models.config import ModelArch, PRESETS
+from prime_rl_b200.models.layers import GroupedExperts
+from prime_rl_b200.ops import _runtime as rt
+from prime_rl_b200.ops import moe as moe_ops
+from prime_rl_b200.parallel.ep import TorchA2ADispatcher
+from prime_rl_b200.parallel.ep_p2p import P2PDispatcher
 
 
 def _arch(E, H, I, k) -> ModelArch:

@@ -3,7 +3,7 @@ small MoE model with experts sharded over 2 ranks, once with the all-to-all disp
 with the peer-memory dispatcher; losses and gradient norms must agree.
 
     NCCL_NVLS_ENABLE=0 python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 \
-        --master-addr 127.0.0.1 --master-port 29537 -m prime_rl_b200.parallel.ep_trainer_selftest
+        --master-addr 127.0.0.1 --master-port 29537 -m tests.distributed.ep_trainer
 """
 
 from __future__ import annotations
@@ -17,8 +17,8 @@ import torch.distributed as dist
 
 
 def _step(dispatch: str, out_dir: str):
-    from ..configs.trainer import TrainerConfig
-    from ..trainer.rl.train import RLTrainer
+    from prime_rl_b200.configs.trainer import TrainerConfig
+    from prime_rl_b200.trainer.rl.train import RLTrainer
 
     cfg = TrainerConfig.model_validate({
         "model": {"name": "qwen3-30b-a3b", "seq_len": 1024, "ep": 2,
@@ -35,7 +35,7 @@ def _step(dispatch: str, out_dir: str):
 
 
 def main() -> int:
-    from ..ops import _runtime as rt
+    from prime_rl_b200.ops import _runtime as rt
 
     out = tempfile.mkdtemp()
     a = _step("torch", out)

@@ -2,7 +2,7 @@
 plays the engine, rank 0 the trainer):
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
-        --master-port 29535 -m prime_rl_b200.transports.weights.p2p_selftest
+        --master-port 29535 -m tests.distributed.weight_push
 
 Checks that bf16 pushes are bit exact and that fp8 pushes match a PyTorch block quantiser, then
 times a push of a Qwen3-30B-A3B-sized set of expert weights against an NCCL broadcast.
@@ -18,8 +18,8 @@ from pathlib import Path
 import torch
 import torch.distributed as dist
 
-from ...ops import _runtime as rt
-from .p2p import P2PWeightPort, _Mapped, manifest_path, push_state
+from prime_rl_b200.ops import _runtime as rt
+from prime_rl_b200.transports.weights.p2p import P2PWeightPort, _Mapped, manifest_path, push_state
 
 
 class _Toy(torch.nn.Module):

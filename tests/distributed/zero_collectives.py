@@ -4,7 +4,7 @@ and ``"nccl"``, same seeds; losses, gradient norms and the updated parameters mu
 two kernels are timed on 1 GiB of fp32 gradients / 512 MiB of bf16 parameters against
 ``reduce_scatter_tensor`` / ``all_gather_into_tensor``.
 
-    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m prime_rl_b200.parallel.p2p_zero_selftest
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 -m tests.distributed.zero_collectives
 """
 
 from __future__ import annotations
@@ -16,12 +16,12 @@ import tempfile
 import torch
 import torch.distributed as dist
 
-from ..ops import _runtime as rt
+from prime_rl_b200.ops import _runtime as rt
 
 
 def _trainer_run(kind: str, tmp: str):
-    from ..configs.trainer import TrainerConfig
-    from ..trainer.rl.train import RLTrainer
+    from prime_rl_b200.configs.trainer import TrainerConfig
+    from prime_rl_b200.trainer.rl.train import RLTrainer
 
     cfg = TrainerConfig.model_validate({
         "model": {"name": "tiny-qwen3", "seq_len": 256, "ac": None, "optim_collectives": kind,
@@ -44,7 +44,7 @@ def main() -> int:
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    from ..utils.logger import setup_logger
+    from prime_rl_b200.utils.logger import setup_logger
 
     setup_logger("warning")
     with tempfile.TemporaryDirectory() as tmp:
@@ -62,7 +62,7 @@ def main() -> int:
         print(("P2P_ZERO_OK" if ok else "P2P_ZERO_FAIL"), "deviation of (loss, grad norm, parameters), p2p used:",
               t.tolist(), flush=True)
     if ok and os.environ.get("P2P_ZERO_TIMING", "1") == "1":
-        from .p2p_zero import P2PShardCollectives
+        from prime_rl_b200.parallel.p2p_zero import P2PShardCollectives
 
         group = dist.group.WORLD
         n = 256 * 1024 * 1024                       # 1 GiB of fp32 gradients, 512 MiB of bf16 parameters

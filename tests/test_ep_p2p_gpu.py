@@ -5,8 +5,12 @@ import os
 import subprocess
 import sys
 
+from pathlib import Path
+
 import pytest
 import torch
+
+ROOT = str(Path(__file__).resolve().parents[1])      # the children are run as `-m tests.distributed.<name>`
 
 pytestmark = pytest.mark.gpu
 
@@ -16,8 +20,8 @@ def test_p2p_dispatcher_matches_all_to_all():
         pytest.skip("needs two GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", EP_SELFTEST_TIMING="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", "29533", "-m", "prime_rl_b200.parallel.ep_selftest"]
-    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+           "127.0.0.1", "--master-port", "29533", "-m", "tests.distributed.ep_dispatch"]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
     assert out.returncode == 0 and "EP_SELFTEST_OK" in out.stdout and "EP_FP8_PAYLOAD_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
 
 
@@ -26,8 +30,8 @@ def test_gemm_reduce_scatter_over_peer_memory():
         pytest.skip("needs two GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", FUSED_SELFTEST_TIMING="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", "29534", "-m", "prime_rl_b200.parallel.fused_collectives"]
-    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+           "127.0.0.1", "--master-port", "29534", "-m", "tests.distributed.fused_collectives"]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
     assert out.returncode == 0 and "FUSED_RS_OK" in out.stdout and "FUSED_AG_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
 
 
@@ -36,8 +40,8 @@ def test_weight_push_over_peer_memory():
         pytest.skip("needs two GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", P2P_SELFTEST_TIMING="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", "29535", "-m", "prime_rl_b200.transports.weights.p2p_selftest"]
-    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+           "127.0.0.1", "--master-port", "29535", "-m", "tests.distributed.weight_push"]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
     assert out.returncode == 0 and "P2P_WEIGHTS_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
 
 
@@ -46,8 +50,8 @@ def test_all_to_all_over_peer_memory():
         pytest.skip("needs two GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", P2P_SELFTEST_TIMING="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", "29536", "-m", "prime_rl_b200.parallel.p2p_a2a"]
-    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+           "127.0.0.1", "--master-port", "29536", "-m", "tests.distributed.p2p_a2a"]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
     assert out.returncode == 0 and "P2P_A2A_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
 
 
@@ -77,8 +81,8 @@ def test_trainer_step_with_peer_memory_expert_parallelism():
         pytest.skip("needs two GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", "29537", "-m", "prime_rl_b200.parallel.ep_trainer_selftest"]
-    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+           "127.0.0.1", "--master-port", "29537", "-m", "tests.distributed.ep_trainer"]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
     assert out.returncode == 0 and "EP_TRAINER_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
 
 
@@ -87,8 +91,8 @@ def test_context_parallel_attention_with_in_kernel_kv_gather():
         pytest.skip("needs two GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", CP_SELFTEST_TIMING="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", "29538", "-m", "prime_rl_b200.parallel.cp_selftest"]
-    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+           "127.0.0.1", "--master-port", "29538", "-m", "tests.distributed.cp_attention"]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
     assert out.returncode == 0 and "CP_FUSED_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
 
 
@@ -97,8 +101,8 @@ def test_sharded_optimizer_with_peer_memory_collectives():
         pytest.skip("needs two GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", P2P_ZERO_TIMING="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", "29539", "-m", "prime_rl_b200.parallel.p2p_zero_selftest"]
-    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+           "127.0.0.1", "--master-port", "29539", "-m", "tests.distributed.zero_collectives"]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
     assert out.returncode == 0 and "P2P_ZERO_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
 
 
@@ -108,6 +112,6 @@ def test_tensor_parallel_engine_with_fused_reduce_kernel():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     for extra in ([], ["--cuda-graphs"]):
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-               "127.0.0.1", "--master-port", "29539", "-m", "prime_rl_b200.engine.tp", *extra]
-        out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+               "127.0.0.1", "--master-port", "29540" if extra else "29541", "-m", "tests.distributed.tp_engine", *extra]
+        out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
         assert out.returncode == 0 and "TP_SELFTEST_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]

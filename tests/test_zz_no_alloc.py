@@ -85,6 +85,39 @@ def test_noalloc_lm_head_matches_regular_entry_point_twice():
         assert bool(((got[2] - lse).abs() <= 2e-2 + 1e-2 * lse.abs()).all())
 
 
+def test_noalloc_decode_shapes_after_a_call_that_dirtied_the_scratch():
+    """Few rows and a large vocabulary ask for more vocabulary slices than the built-in scratch has;
+    the entry point then re-spreads the tiles so that every slice it merges was written by this call.
+    Runs after a larger call so that the shared array holds foreign values."""
+    lib = _load()
+    dev = torch.device("cuda", 0)
+    assert lib.prb_bind_device(0) == 0
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    g = torch.Generator(device=dev).manual_seed(2)
+    H, V = 256, 151936
+    w = (torch.randn(V, H, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    for T in (2048, 256, 128, 512):         # the first call fills all 64 slices for 2048 rows
+        h = (torch.randn(T, H, device=dev, generator=g) * 3.0).to(torch.bfloat16)
+        labels = torch.randint(0, V, (T,), device=dev, generator=g).to(torch.int32)
+        inv_temp = 0.5 + torch.rand(T, device=dev, generator=g)
+        got = _noalloc(lib, h, w, labels, inv_temp, status, stream)
+        ref = _regular(lib, h, w, labels, inv_temp, status, stream)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        z = (h.float() @ w.float().t()) * inv_temp[:, None]
+        lse = torch.logsumexp(z, -1)
+        lp = z.gather(1, labels.long()[:, None])[:, 0] - lse
+        p = torch.softmax(z, -1)
+        ent = lse - (p * z).sum(-1)
+        for a, b, name in zip(got, (lp, ent, lse), ("logprob", "entropy", "lse")):
+            err = (a - b).abs()
+            assert bool((err <= 3e-2 + 1e-2 * b.abs()).all()), f"T={T} {name} vs fp32: max err {err.max().item():.4g}"
+        for a, b, name in zip(got, ref, ("logprob", "entropy", "lse")):
+            err = (a - b).abs()
+            assert bool((err <= 2e-2 + 1e-2 * b.abs()).all()), f"T={T} {name} vs regular: max err {err.max().item():.4g}"
+
+
 def test_noalloc_rejects_oversized_input():
     lib = _load()
     dev = torch.device("cuda", 0)
