@@ -1,27 +1,46 @@
-"""Headline benchmark: RL trainer tokens/s on the Qwen3-30B-A3B shape.
+"""Headline benchmark: RL trainer tokens/s and rollout decode tokens/s on the Qwen3-30B-A3B shape.
 
     python bench.py --gpus N --steps K --warmup W            (N = 1)
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port P bench.py --gpus N --steps K --warmup W
 
-Config (the reference's own published 8xB200 row for this model): RL step, LoRA rank 16 on
-attention projections and experts, full activation recomputation, packed sequences of
-16384 tokens, 2 micro-batches per GPU and step, bf16, synthetic token ids, random-init
-weights. Weak scaling: per-GPU work is fixed, the frozen base weights are replicated
-(61 GB of the 180 GB) and only the adapter gradients are all-reduced.
+Trainer (``value``). Two configurations; ``--mode auto`` (the default) picks by what fits:
+
+  full   the headline one: full fine-tuning, expert parallelism over all N GPUs (every rank owns
+         128 / N experts; tokens travel through the peer-memory dispatcher), optimizer state of the
+         dense parameters partitioned over the ranks with its reduce-scatter / all-gather as
+         peer-memory kernels, full activation recomputation, packed rows of 8192 tokens, 64 rows per
+         optimizer step for the whole job (64 / N micro-batches per GPU: the total work is fixed,
+         strong scaling). Needs fp32 master + moments + gradients of 30.5 B parameters spread over
+         the GPUs: N >= 4.
+  lora   the reference's published 8xB200 row for this model: LoRA rank 16 on attention
+         projections and experts, 16384-token rows, 2 micro-batches per GPU and step (weak
+         scaling), frozen base replicated, adapter gradients all-reduced. Used where ``full``
+         does not fit (the line then says ``"config_3": "does not fit"``), and always reported
+         under ``lora_dp`` next to a ``full`` result so that both numbers stay comparable over time.
 
 Two passes of K steps each are timed after W warm-up steps:
   * ``value``  device time (CUDA events, max over ranks) with the step's inputs already on
     the device;
   * ``e2e``    wall clock through ``RLTrainer.step()`` fed by the data loader: pinned host
     batches -> device every step, loss / metrics read back every step.
+
+Rollout (``rollout_decode``): the engine with block-scaled fp8 weights (128 x 128 weight blocks,
+1 x 128 activation scales) and a bf16 paged KV cache of 16-token pages, tensor-parallel over up
+to 4 GPUs (the shape has 4 KV heads) with data-parallel groups beyond that, 256 concurrent
+requests per group = 32 prompts of 1024 tokens x 8 samples that share the prompt's pages through
+the prefix cache, temperature 1.0. Decode steps are timed at the contexts a 4096-token generation
+passes through (1024, 3072, 5120 tokens), then one full weight push bf16 -> fp8 in flight.
+
 Rank 0 prints one JSON line.
 """
 
 from __future__ import annotations
 
 import argparse
+import gc
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -34,7 +53,9 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-BASELINE_TPS_8GPU = 9266.4  # reference, 8xB200, Qwen3-30B-A3B RL LoRA r16, seq 16384 (benchmarks/results/BENCHMARKS.md:60)
+# reference, 8xB200, Qwen3-30B-A3B RL LoRA r16, seq 16384 (benchmarks/results/BENCHMARKS.md:60): its only
+# successful 8xB200 run of this model (the full fine-tuning runs of the same table failed on B200)
+BASELINE_TPS_8GPU = 9266.4
 
 
 def parse_args():
@@ -44,13 +65,18 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--model", default="qwen3-30b-a3b")
-    ap.add_argument("--seq-len", type=int, default=16384)
-    ap.add_argument("--micro-batches", type=int, default=2, help="micro-batches per GPU and step")
-    ap.add_argument("--mode", default="lora", choices=["lora", "full"])
+    ap.add_argument("--mode", default="auto", choices=["auto", "lora", "full"])
+    ap.add_argument("--seq-len", type=int, default=None, help="tokens per packed row (default: 8192 full, 16384 lora)")
+    ap.add_argument("--rows", type=int, default=64, help="full mode: rows per optimizer step over the whole job")
+    ap.add_argument("--micro-batches", type=int, default=2, help="lora mode: micro-batches per GPU and step")
+    ap.add_argument("--dispatch", default="p2p", choices=["p2p", "torch"], help="full mode: expert-parallel dispatcher")
+    ap.add_argument("--optim-collectives", default="p2p", choices=["p2p", "nccl"])
     ap.add_argument("--layers", type=int, default=None, help="debug: truncate the model (result is not a bench value)")
     ap.add_argument("--attn", default="auto")
-    ap.add_argument("--no-rollout-decode", action="store_true",
-                    help="skip the second measurement (rollout decode tokens/s of the engine, one replica per GPU)")
+    ap.add_argument("--no-rollout-decode", action="store_true", help="skip the rollout measurement")
+    ap.add_argument("--no-secondary", action="store_true", help="full mode: skip the LoRA / data-parallel comparison run")
+    ap.add_argument("--rollout-contexts", default="1024,3072,5120")
+    ap.add_argument("--rollout-steps", type=int, default=16)
     return ap.parse_args()
 
 
@@ -113,54 +139,70 @@ def reference_arm(args):
     print(json.dumps({"impl": "reference", "unavailable": reason}))
 
 
-def main():
-    args = parse_args()
-    if args.impl == "reference":
-        if int(os.environ.get("RANK", 0)) == 0:
-            reference_arm(args)
-        return
+def full_fit(arch, n: int, total_bytes: int) -> tuple[bool, float]:
+    """Does full fine-tuning with experts and optimizer state spread over ``n`` GPUs fit in one GPU's
+    memory? Per parameter: 2 B bf16 value + 4 B flat fp32 gradient on every holder, 12 B master + moments
+    (+ 4 B reduced gradient slice for the partitioned dense part) on its owner."""
+    from prime_rl_b200.trainer.perf import count_params
 
+    dense, expert = count_params(arch)
+    per_gpu = 6 * (dense + expert / n) + 12 * (dense + expert) / n + 4 * dense / n
+    need = per_gpu + 14e9            # activations, logits gradient chunk, dispatch buffers, allocator slack
+    return need <= 0.93 * total_bytes, need / 1e9
+
+
+def trainer_pass(args, mode: str, world, steps: int, warmup: int, want_e2e: bool = True) -> dict:
+    """Builds the trainer for ``mode``, times it and tears it down again. Collective: every rank calls."""
     import torch
     import torch.distributed as dist
 
     from prime_rl_b200.configs.trainer import TrainerConfig
     from prime_rl_b200.ops import _runtime as rt
-    from prime_rl_b200.parallel import get_world
     from prime_rl_b200.trainer.rl.train import RLTrainer
-    from prime_rl_b200.utils.logger import setup_logger
 
-    world = get_world()
     n = world.world_size
-    setup_logger("warning" if world.rank else "info", tag=f"bench:{world.rank}")
-    mcfg = {"name": args.model, "seq_len": args.seq_len, "attn": args.attn, "ac": {"mode": "full", "freq": 1},
-            "ep": 1, "debug": {"random_init": True, "num_layers": args.layers}}
-    if args.mode == "lora":
-        mcfg["lora"] = {"rank": 16, "alpha": 32.0}
+    if mode == "full":
+        seq_len = args.seq_len or 8192
+        per_gpu = max(1, args.rows // n)
+        global_rows = per_gpu * n
+        mcfg = {"name": args.model, "seq_len": seq_len, "attn": args.attn, "ac": {"mode": "full", "freq": 1},
+                "ep": n if n > 1 else 1, "optim_collectives": args.optim_collectives,
+                "moe": {"dispatch": {"type": args.dispatch} if args.dispatch == "torch" else
+                        {"type": "p2p", "capacity_factor": float(min(n, 4))}},
+                "debug": {"random_init": True, "num_layers": args.layers}}
+        scaling = "strong"
+        par = (f"ep{n} (128/{n} experts per GPU, peer-memory dispatch) x zero{n} (dense optimizer state partitioned, "
+               f"{args.optim_collectives} reduce-scatter / all-gather)") if n > 1 else "single GPU"
+    else:
+        seq_len = args.seq_len or 16384
+        per_gpu = args.micro_batches
+        global_rows = per_gpu * n
+        mcfg = {"name": args.model, "seq_len": seq_len, "attn": args.attn, "ac": {"mode": "full", "freq": 1},
+                "ep": 1, "lora": {"rank": 16, "alpha": 32.0}, "debug": {"random_init": True, "num_layers": args.layers}}
+        scaling = "weak"
+        par = f"dp{n} (frozen base replicated, adapter grads all-reduced)"
     cfg = TrainerConfig.model_validate({
-        "model": mcfg, "data": {"fake": {"batch_size": args.micro_batches * n}},
+        "model": mcfg, "data": {"fake": {"batch_size": global_rows}},
         "optim": {"type": "adamw", "lr": 1e-5, "weight_decay": 0.01, "max_norm": 1.0},
-        "max_steps": None, "output_dir": str(Path(tempfile.gettempdir()) / "prime_rl_b200_bench_run"), "monitors": {"file": None},
-        "weight_broadcast": {"type": "filesystem"}})
+        "max_steps": None, "output_dir": str(Path(tempfile.gettempdir()) / f"prime_rl_b200_bench_{mode}"),
+        "monitors": {"file": None}, "weight_broadcast": {"type": "filesystem"}})
     trainer = RLTrainer(cfg).setup()
     dev = trainer.device
-    tokens_per_step = args.micro_batches * args.seq_len * n
+    tokens_per_step = global_rows * seq_len
 
     def sync():
         if n > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ------------------------------------------------------------ warm-up (shared by both passes)
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         trainer.step()
     rt.check_status()
     sync()
-
     sampler = ClockSampler(dev.index or 0)
     sampler.start()
-
-    # ------------------------------------------------------------ pass A: device time, inputs pre-staged
-    staged = [[mb.to(dev) for mb in trainer.dataloader.get_batch()] for _ in range(args.steps)]
+    # ---- pass A: device time, inputs pre-staged on the device
+    staged = [[mb.to(dev) for mb in trainer.dataloader.get_batch()] for _ in range(steps)]
     sync()
     launches0 = rt.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -172,79 +214,115 @@ def main():
     dev_ms = ev0.elapsed_time(ev1)
     launches = rt.launch_count() - launches0
     del staged
-
-    # ------------------------------------------------------------ pass B: end to end through the public API
+    # ---- pass B: end to end through the public API
     h2d = d2h = 0
-    sync()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        mbs = trainer.dataloader.get_batch()           # pinned host memory
-        h2d = sum(mb.h2d_bytes() for mb in mbs)
-        m = trainer.step(mbs)                          # H2D copies + one D2H read of the step's metrics
-        d2h = 4 * len([k for k in m if not k.startswith(("time/", "perf/", "optim/lr"))])
-    sync()
-    e2e_s = time.perf_counter() - t0
+    e2e_s = float("nan")
+    if want_e2e:
+        sync()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            mbs = trainer.dataloader.get_batch()           # pinned host memory
+            h2d = sum(mb.h2d_bytes() for mb in mbs)
+            m = trainer.step(mbs)                          # H2D copies + one D2H read of the step's metrics
+            d2h = 4 * len([k for k in m if not k.startswith(("time/", "perf/", "optim/lr"))])
+        sync()
+        e2e_s = time.perf_counter() - t0
     clocks = sampler.stop()
     rt.check_status()
-
     t = torch.tensor([dev_ms, e2e_s], dtype=torch.float64, device=dev)
     if n > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dev_ms, e2e_s = t.tolist()
-    value = tokens_per_step * args.steps / (dev_ms / 1e3)
-    e2e = tokens_per_step * args.steps / e2e_s
-    loss_value, mfu, peak_gib = m.get("loss"), trainer.perf.mfu(value), torch.cuda.max_memory_allocated(dev) / 2 ** 30
+    value = tokens_per_step * steps / (dev_ms / 1e3)
+    out = {"mode": mode, "value": value, "ms_per_step": dev_ms / steps, "tokens_per_step": tokens_per_step,
+           "seq_len": seq_len, "global_rows": global_rows, "rows_per_gpu": per_gpu, "scaling": scaling,
+           "parallelism": par, "clocks": clocks, "gpu_launches": launches, "loss": m.get("loss"),
+           "mfu_percent": trainer.perf.mfu(value), "peak_memory_gib": torch.cuda.max_memory_allocated(dev) / 2 ** 30,
+           "e2e": None if not want_e2e else {"value": tokens_per_step * steps / e2e_s, "unit": "tokens/s",
+                                            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}}
+    # ---- tear down: the next phase needs the memory (symmetric buffers are outside torch's allocator)
+    trainer.close()
+    del trainer, mbs, m
+    gc.collect()
+    torch.cuda.empty_cache()
+    torch.cuda.reset_peak_memory_stats(dev)
+    sync()
+    return out
 
-    # ------------------------------------------------------------ second number of the headline: rollout decode
-    # One engine replica per GPU (data-parallel serving), 256 requests of 1024 prompt tokens each, 16 timed
-    # decode steps through Engine.step; aggregate tokens/s = sum over replicas, step time = slowest replica.
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", 0)) == 0:
+            reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from prime_rl_b200.models import resolve_arch
+    from prime_rl_b200.parallel import get_world, setup_distributed
+    from prime_rl_b200.utils.logger import setup_logger
+
+    world = get_world()
+    n = world.world_size
+    setup_logger("warning" if world.rank else "info", tag=f"bench:{world.rank}")
+    dev = setup_distributed()
+    arch = resolve_arch(args.model)
+    if args.layers:
+        arch = arch.model_copy(update={"num_hidden_layers": args.layers})
+    fits, need_gb = full_fit(arch, n, torch.cuda.get_device_properties(dev).total_memory)
+    mode = args.mode
+    if mode == "auto":
+        mode = "full" if (fits and (n > 1 or not arch.is_moe)) else "lora"
+    primary = trainer_pass(args, mode, world, args.steps, args.warmup)
+    secondary = None
+    if mode == "full" and not args.no_secondary:
+        try:
+            s = trainer_pass(args, "lora", world, min(args.steps, 3), 3, want_e2e=False)
+            secondary = {k: s[k] for k in ("value", "ms_per_step", "seq_len", "global_rows", "scaling", "parallelism",
+                                           "mfu_percent", "peak_memory_gib")}
+            secondary["metric"] = "RL trainer tokens/s, LoRA r16, data parallel (the reference's published B200 row)"
+            secondary["vs_baseline"] = s["value"] / (BASELINE_TPS_8GPU * n / 8)
+        except Exception as e:      # the headline number stands on its own
+            secondary = {"error": f"{type(e).__name__}: {e}"[:300]}
+
     rollout = None
     if not args.no_rollout_decode:
-        import gc
-        import math
-
-        local, err = [float("nan"), float("nan")], None
         try:
-            from prime_rl_b200.engine.bench_decode import run_decode
+            from prime_rl_b200.engine.bench_decode import run_rollout_bench
 
-            del trainer, mbs
-            gc.collect()
-            torch.cuda.empty_cache()
-            r = run_decode(args.model, batch=256, prompt=1024, steps=16, warmup=4, layers=args.layers, dev=dev)
-            local = [r["decode_tokens_per_s"], r["ms_per_step"]]
-        except Exception as e:  # the trainer number stands on its own
+            rollout = run_rollout_bench(args.model, contexts=[int(c) for c in args.rollout_contexts.split(",")],
+                                        steps=args.rollout_steps, layers=args.layers, dev=dev)
+        except Exception as e:
             err = f"{type(e).__name__}: {e}"[:300]
-        t = torch.tensor(local, dtype=torch.float64, device=dev)
-        if n > 1:                                   # every rank takes part, whatever happened to its own replica
-            tot = t.clone()
-            dist.all_reduce(tot, op=dist.ReduceOp.SUM)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            t[0] = tot[0]
-        if math.isnan(float(t[0])) or math.isnan(float(t[1])):
-            rollout = {"error": err or "an engine replica on another rank failed"}
-        else:
-            rollout = {"metric": "rollout decode tokens/s", "value": float(t[0]), "unit": "tokens/s",
-                       "ms_per_step": float(t[1]), "batch_per_gpu": 256, "prompt_len": 1024, "steps": 16,
-                       "parallelism": f"dp{n} (one engine replica per GPU)", "cuda_graphs": True, "dtype": "bf16"}
+            rollout = {"error": err}
     if world.rank == 0:
-        print(json.dumps({
-            "metric": "RL trainer tokens/s, Qwen3-30B-A3B shape", "value": value, "unit": "tokens/s", "n_gpus": n,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": value / (BASELINE_TPS_8GPU * n / 8),
+        p = primary
+        line = {
+            "metric": "RL trainer tokens/s, Qwen3-30B-A3B shape", "value": p["value"], "unit": "tokens/s", "n_gpus": n,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": p["ms_per_step"],
+            "higher_is_better": True, "scaling": p["scaling"],
+            "vs_baseline": p["value"] / (BASELINE_TPS_8GPU * n / 8),
             "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init weights)",
             "config": {"model": args.model if args.layers is None else f"{args.model}[{args.layers} layers: debug]",
-                       "mode": f"rl-{args.mode}" + ("-r16" if args.mode == "lora" else ""),
-                       "global_batch": args.micro_batches * n, "seq_len": args.seq_len,
-                       "parallelism": f"dp{n}" + (" (frozen base replicated, adapter grads all-reduced)"
-                                                   if args.mode == "lora" else ""),
-                       "activation_checkpointing": "full", "loss": "ipo", "optimizer": "adamw",
-                       "l2": "inputs and weights (61 GB) exceed L2; no flush between steps",
-                       "vs_baseline_note": "reference 9266 tok/s on 8 GPUs, scaled by n_gpus/8"},
-            "clocks": clocks,
-            "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": launches, "loss": loss_value, "mfu_percent": mfu,
-            "peak_memory_gib": peak_gib, "rollout_decode": rollout,
-        }))
+                       "mode": "rl-full" if p["mode"] == "full" else "rl-lora-r16",
+                       "global_batch": p["global_rows"], "seq_len": p["seq_len"], "rows_per_gpu": p["rows_per_gpu"],
+                       "parallelism": p["parallelism"], "activation_checkpointing": "full", "loss": "ipo",
+                       "optimizer": "adamw",
+                       "l2": "inputs, activations and weights exceed L2 many times over; no flush between steps",
+                       "vs_baseline_note": "reference 9266 tok/s (LoRA r16, seq 16384, 8 GPUs; its full fine-tuning runs "
+                                           "failed on B200), scaled by n_gpus/8"},
+            "clocks": p["clocks"], "e2e": p["e2e"], "gpu_launches": p["gpu_launches"], "loss": p["loss"],
+            "mfu_percent": p["mfu_percent"], "peak_memory_gib": p["peak_memory_gib"],
+            "rollout_decode": rollout,
+        }
+        if p["mode"] == "full":
+            line["lora_dp"] = secondary
+        else:
+            line["config_3"] = ("does not fit" if not fits else "not selected") + \
+                f": full fine-tuning of this shape needs about {need_gb:.0f} GB per GPU at N = {n}"
+        print(json.dumps(line))
     if n > 1:
         dist.barrier()
         dist.destroy_process_group()

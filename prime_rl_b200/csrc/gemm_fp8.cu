@@ -36,6 +36,7 @@ struct Fp8Params {
   long long ldc;
   const int* block_expert;  // nullptr = dense
   int b_rows_per_expert;    // N rows of B per expert
+  const int* row_valid;     // optional [M]: rows with a negative entry are padding and are not stored
   int* status;
 };
 
@@ -143,8 +144,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     bool ok = true;
     while (ok && sched.next(p, m_blk, n_blk, expert)) {
       const int row = m_blk * kF8BM + q * 32 + lane;
-      const bool row_ok = row < p.M;
-      const float* sa_row = p.sa + static_cast<long long>(row_ok ? row : 0) * KB;
+      const bool row_ok = row < p.M && (p.row_valid == nullptr || p.row_valid[row] >= 0);
+      const float* sa_row = p.sa + static_cast<long long>(row < p.M ? row : 0) * KB;
       const float* sb_row = p.sb + (static_cast<long long>(expert) * n_tiles_scale + n_blk) * KB;
       float acc[kF8BN];
 #pragma unroll
@@ -156,13 +157,19 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
+        // two TMEM loads in flight per wait: the load latency is paid twice per K block, not four times
 #pragma unroll
-        for (int c = 0; c < kF8BN / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(tmem_base + buf * kF8BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
+        for (int c = 0; c < kF8BN / 64; ++c) {
+          uint32_t v0[32], v1[32];
+          const uint32_t taddr = tmem_base + buf * kF8BN + c * 64 + (static_cast<uint32_t>(q * 32) << 16);
+          tmem_ld_32x32(taddr, v0);
+          tmem_ld_32x32(taddr + 32, v1);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(__uint_as_float(v[j]), sc, acc[c * 32 + j]);
+          for (int j = 0; j < 32; ++j) {
+            acc[c * 64 + j] = fmaf(__uint_as_float(v0[j]), sc, acc[c * 64 + j]);
+            acc[c * 64 + 32 + j] = fmaf(__uint_as_float(v1[j]), sc, acc[c * 64 + 32 + j]);
+          }
         }
         tc_fence_before();
         __syncwarp();
@@ -196,11 +203,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 // amax / 448 per row and 128-wide block). One warp per (row, block): lane = 4 elements.
 __global__ void __launch_bounds__(256)
 act_quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ q,
-                     float* __restrict__ scales, int M, int K) {
+                     float* __restrict__ scales, int M, int K, const int* __restrict__ row_valid) {
   const int KB = (K + 127) / 128;
   const long long item = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   if (item >= static_cast<long long>(M) * KB) return;
   const int row = static_cast<int>(item / KB), kb = static_cast<int>(item - static_cast<long long>(row) * KB);
+  if (row_valid != nullptr && row_valid[row] < 0) return;      // padding row: neither read nor written
   const int lane = threadIdx.x & 31;
   const int c = kb * 128 + lane * 4;
   float v[4] = {0.f, 0.f, 0.f, 0.f};
@@ -231,8 +239,10 @@ act_quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t
 
 // Aq e4m3 [M, K] (pitch K), sa fp32 [M, ceil(K/128)]; Bq e4m3 [E * N, K] (E = 1 when dense),
 // sb fp32 [E, ceil(N/128), ceil(K/128)]; C bf16 [M, N] (pitch ldc). K must be a multiple of 16.
+// row_valid (optional, [M] int32): rows with a negative entry are not stored (padding rows of a grouped call).
 PRB_API int prb_gemm_fp8(const void* Aq, const float* sa, const void* Bq, const float* sb, void* C, int M, int N, int K,
-                         long long ldc, const int* block_expert, int num_experts, int* status, void* stream_) {
+                         long long ldc, const int* block_expert, int num_experts, const int* row_valid, int* status,
+                         void* stream_) {
   using namespace prb;
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K % 16) || (reinterpret_cast<uintptr_t>(Aq) & 15) || (reinterpret_cast<uintptr_t>(Bq) & 15)) return -4;
@@ -249,7 +259,7 @@ PRB_API int prb_gemm_fp8(const void* Aq, const float* sa, const void* Bq, const 
   Fp8Params p;
   p.M = M; p.N = N; p.K = K; p.sa = sa; p.sb = sb;
   p.C = reinterpret_cast<__nv_bfloat16*>(C); p.ldc = ldc;
-  p.block_expert = block_expert; p.b_rows_per_expert = grouped ? N : 0; p.status = status;
+  p.block_expert = block_expert; p.b_rows_per_expert = grouped ? N : 0; p.row_valid = row_valid; p.status = status;
   static prb::DeviceOnce configured;
   if (configured.pending()) {
     if (cudaFuncSetAttribute(gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kF8Smem) != cudaSuccess)
@@ -262,10 +272,12 @@ PRB_API int prb_gemm_fp8(const void* Aq, const float* sa, const void* Bq, const 
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
-PRB_API int prb_act_quant_fp8(const void* x, long long ldx, void* q, float* scales, int M, int K, void* stream) {
+// row_valid (optional, [M] int32): rows with a negative entry are skipped.
+PRB_API int prb_act_quant_fp8(const void* x, long long ldx, void* q, float* scales, int M, int K, const int* row_valid,
+                              void* stream) {
   if (M <= 0 || K <= 0) return 0;
   const long long items = static_cast<long long>(M) * ((K + 127) / 128);
   prb::act_quant_fp8_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const __nv_bfloat16*>(x), ldx, reinterpret_cast<uint8_t*>(q), scales, M, K);
+      reinterpret_cast<const __nv_bfloat16*>(x), ldx, reinterpret_cast<uint8_t*>(q), scales, M, K, row_valid);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

@@ -52,7 +52,8 @@ class Request:
 class Engine:
     def __init__(self, model, *, num_pages: int = 4096, page_size: int = 16, max_running: int = 256,
                  max_prefill_tokens: int = 16384, eos_token_id: int | None = None, enable_prefix_cache: bool = True,
-                 use_cuda_graphs: bool = False, max_model_len: int = 8192, weight_dtype: str = "bf16", tp=None):
+                 use_cuda_graphs: bool = False, max_model_len: int = 8192, weight_dtype: str = "bf16", tp=None,
+                 keep_bf16_weights: bool = True):
         arch = model.arch
         self.model = model.eval()
         self.weight_dtype = weight_dtype
@@ -70,11 +71,14 @@ class Engine:
                 shard_model_(self.model, tp.rank, tp.size)
             if tp.max_tokens < max(max_prefill_tokens, max_model_len):
                 raise ValueError("the tensor-parallel buffers are smaller than the largest step the engine may run")
+        # fp8 serving: with ``keep_bf16_weights=False`` the bf16 storage of every quantised projection is
+        # released (weight updates are then quantised tensor by tensor as they arrive)
+        self.drop_bf16 = weight_dtype == "fp8" and not keep_bf16_weights
         if weight_dtype == "fp8":
             from ..models.model import quantize_fp8_
 
-            quantize_fp8_(self.model)
-        p = next(model.parameters())
+            quantize_fp8_(self.model, drop_bf16=self.drop_bf16)
+        p = next(p for p in model.parameters() if p.numel() > 0)
         self.device = p.device
         self.cache = KVCache(arch.num_hidden_layers, num_pages, page_size, arch.num_key_value_heads // self.tp_size,
                              arch.head_dim, p.dtype, p.device)
@@ -398,7 +402,7 @@ class Engine:
         if self.weight_dtype == "fp8":
             from ..models.model import quantize_fp8_
 
-            quantize_fp8_(self.model)
+            quantize_fp8_(self.model, drop_bf16=self.drop_bf16)
         self.cache.blocks.clear_prefix_cache()
         self.policy_version += 1
 

@@ -398,7 +398,18 @@ def load_model_state(model, sd: StateDict, layout: str = "prime", strict: bool =
             if info is not None and is_expert_sharded_key(k) and v.shape[0] == info["num_experts"] != own[k].shape[0]:
                 lo = info["ep_rank"] * info["local_experts"]      # a full stack: keep this rank's expert range
                 v = v[lo:lo + info["local_experts"]]
-            own[k].copy_((v if shard is None else shard(k, v)).to(own[k].dtype))
+            v = v if shard is None else shard(k, v)
+            if own[k].numel() == 0 and v.numel() > 0:
+                # a serving model that released the bf16 storage of its fp8 projections: quantise the new
+                # values straight into the fp8 copy
+                owner_name, leaf = k.rsplit(".", 1)
+                owner = model.get_submodule(owner_name)
+                src = v.to(own[k].device)
+                ok = owner.quantize_fp8_(drop_bf16=True, source={leaf: src} if hasattr(owner, "gate_up_proj") else src)
+                if not ok:
+                    raise RuntimeError(f"{k}: the bf16 storage was released but the module cannot be re-quantised")
+                continue
+            own[k].copy_(v.to(own[k].dtype))
 
 
 # ---------------------------------------------------------------------- LoRA adapters (PEFT layout)

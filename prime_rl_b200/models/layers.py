@@ -105,18 +105,25 @@ class Linear(nn.Module):
         if self.bias is not None:
             nn.init.zeros_(self.bias)
 
-    def quantize_fp8_(self) -> bool:
-        """(Re)builds the block-scaled fp8 copy of the weight used by no-grad forwards."""
-        if self.lora is not None or self.weight.shape[1] % 16 or not self.weight.is_cuda:
+    def quantize_fp8_(self, drop_bf16: bool = False, source: torch.Tensor | None = None) -> bool:
+        """(Re)builds the block-scaled fp8 copy of the weight used by no-grad forwards. ``source``: new
+        bf16 values to quantise instead of ``self.weight`` (a weight update of a module whose bf16 copy
+        was dropped). ``drop_bf16``: afterwards release the bf16 storage; the module then serves from
+        the fp8 copy only (serving engines: the freed memory goes to the KV cache)."""
+        w = source if source is not None else self.weight.data
+        if self.lora is not None or w.numel() == 0 or w.shape[1] % 16 or not w.is_cuda:
             return False
         from .fp8 import quantize_to_fp8_blockwise
 
-        q, s = quantize_to_fp8_blockwise(self.weight.data)
+        q, s = quantize_to_fp8_blockwise(w.to(torch.bfloat16))
         if self.fp8 is None:
             self.fp8 = (q.view(torch.uint8).contiguous(), s.contiguous())
         else:                           # keep the buffers (a peer-memory weight push may write into them)
             self.fp8[0].copy_(q.view(torch.uint8))
             self.fp8[1].copy_(s)
+        if drop_bf16:
+            self.fp8_shape = tuple(w.shape)
+            self.weight.data = torch.empty(0, dtype=self.weight.dtype, device=self.weight.device)
         return True
 
     def forward(self, x):
@@ -125,7 +132,7 @@ class Linear(nn.Module):
 
             x2 = x.reshape(-1, x.shape[-1])
             xq, xs = fp8_ops.quantize_act(x2)
-            y = fp8_ops.fp8_gemm(xq, xs, self.fp8[0], self.fp8[1]).reshape(*x.shape[:-1], self.weight.shape[0])
+            y = fp8_ops.fp8_gemm(xq, xs, self.fp8[0], self.fp8[1]).reshape(*x.shape[:-1], self.fp8[0].shape[0])
             return y if self.bias is None else y + self.bias
         if self.lora is not None:
             y = lora_ops.lora_linear(x, self.weight, self.lora.lora_A, list(self.lora.lora_B), self.lora.scale)
@@ -290,22 +297,55 @@ class GroupedExperts(nn.Module):
         _init(self.gate_up_proj, self.arch.initializer_range)
         _init(self.down_proj, self.arch.initializer_range)
 
-    def quantize_fp8_(self) -> bool:
-        if self.lora_gate_up is not None or self.lora_down is not None or not self.gate_up_proj.is_cuda:
+    def quantize_fp8_(self, drop_bf16: bool = False, source: dict[str, torch.Tensor] | None = None) -> bool:
+        """Block-scaled fp8 copies of both expert stacks (see ``Linear.quantize_fp8_``); ``source`` maps
+        ``gate_up_proj`` / ``down_proj`` to new bf16 values."""
+        if self.lora_gate_up is not None or self.lora_down is not None:
             return False
         from .fp8 import quantize_to_fp8_blockwise
 
-        new = {}
+        done = False
         for name in ("gate_up_proj", "down_proj"):
-            q, s = quantize_to_fp8_blockwise(getattr(self, name).data)
-            new[name] = (q.view(torch.uint8).contiguous(), s.contiguous())
-        if self.fp8 is None:
-            self.fp8 = new
-        else:
-            for name, (q, s) in new.items():
-                self.fp8[name][0].copy_(q)
+            p = getattr(self, name)
+            w = source.get(name) if source is not None else p.data
+            if w is None or w.numel() == 0 or not w.is_cuda:
+                continue
+            if self.fp8 is None:
+                self.fp8 = {}
+            # expert by expert: the fp32 staging of the quantiser never exceeds one expert
+            q, s = quantize_to_fp8_blockwise(w.to(torch.bfloat16))
+            if name not in self.fp8:
+                self.fp8[name] = (q.view(torch.uint8).contiguous(), s.contiguous())
+            else:
+                self.fp8[name][0].copy_(q.view(torch.uint8))
                 self.fp8[name][1].copy_(s)
-        return True
+            if drop_bf16:
+                p.data = torch.empty(0, dtype=p.dtype, device=p.device)
+            done = True
+        return done
+
+    def supports_fp8_row_mask(self, x: torch.Tensor) -> bool:
+        """No-grad forward from the fp8 copies on the GPU: the token rows are quantised once, gathered as
+        fp8 into the expert-sorted order, and the padding rows are skipped by every kernel."""
+        return (not torch.is_grad_enabled() and x.is_cuda and x.dtype == torch.bfloat16 and self.fp8 is not None
+                and self.act != act_ops.SILU_CLAMPED and x.shape[1] % 512 == 0)
+
+    def forward_fp8_masked(self, x: torch.Tensor, plan) -> torch.Tensor:
+        """``x`` [T, H] bf16 (unpermuted) -> expert outputs [P, H] in the plan's row order; rows with
+        ``plan.row_src < 0`` are left unwritten."""
+        from ..ops import fp8 as fp8_ops
+        from ..ops import moe as moe_ops
+
+        T, H = x.shape
+        xq, xs = fp8_ops.quantize_act(x)                              # T rows, not T * k
+        # the fp8 payload and its scales travel through the row gather as opaque 16-bit words
+        xpq = moe_ops.permute_nopad(xq.view(torch.bfloat16), plan).view(torch.uint8)
+        xps = moe_ops.permute_nopad(xs.view(torch.bfloat16), plan).view(torch.float32)
+        valid = plan.row_src
+        gu = fp8_ops.fp8_gemm(xpq, xps, *self.fp8["gate_up_proj"], block_expert=plan.block_expert, row_valid=valid)
+        h = act_ops.glu_rowmask(gu, valid, self.act, self.arch.swiglu_limit, self.arch.swiglu_alpha)
+        hq, hs = fp8_ops.quantize_act(h, row_valid=valid)
+        return fp8_ops.fp8_gemm(hq, hs, *self.fp8["down_proj"], block_expert=plan.block_expert, row_valid=valid)
 
     def supports_row_mask(self, x: torch.Tensor) -> bool:
         """No-grad bf16 forward on the GPU without adapters or fp8 copies: the padding rows that round every
@@ -389,7 +429,9 @@ class MoE(nn.Module):
             plan = self.router.last_plan
             if plan is None:
                 plan = moe_ops.build_plan(idx, counts, self.arch.num_experts)
-            if self.experts.supports_row_mask(xe) and xe.shape[1] % 8 == 0:
+            if self.experts.supports_fp8_row_mask(xe):
+                yp = self.experts.forward_fp8_masked(xe, plan)
+            elif self.experts.supports_row_mask(xe) and xe.shape[1] % 8 == 0:
                 # inference: nothing touches the rows that only pad every expert to a multiple of 128
                 xp = moe_ops.permute_nopad(xe, plan)
                 yp = self.experts(xp, plan.block_expert, plan.expert_offset, row_valid=plan.row_src)

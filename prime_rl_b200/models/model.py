@@ -211,16 +211,18 @@ def freeze_router(model: CausalLM) -> None:
             p.requires_grad_(False)
 
 
-def quantize_fp8_(model, skip: tuple[str, ...] = ("lm_head", "embed_tokens", "router", "g_proj")) -> int:
+def quantize_fp8_(model, skip: tuple[str, ...] = ("lm_head", "embed_tokens", "router", "g_proj"),
+                  drop_bf16: bool = False) -> int:
     """Gives every eligible projection of ``model`` (dense linears and grouped experts) a
     block-scaled fp8 copy that no-grad forwards use instead of the bf16 weight (the rollout
-    engine's ``weight_dtype = "fp8"``); call again after the bf16 weights changed. Returns the
-    number of quantised modules."""
+    engine's ``weight_dtype = "fp8"``); call again after the bf16 weights changed. With
+    ``drop_bf16`` the bf16 storage of the quantised projections is released. Returns the number of
+    quantised modules."""
     n = 0
     for name, mod in model.named_modules():
         if any(s in name for s in skip) or not hasattr(mod, "quantize_fp8_"):
             continue
-        n += bool(mod.quantize_fp8_())
+        n += bool(mod.quantize_fp8_(drop_bf16=drop_bf16))
     return n
 
 

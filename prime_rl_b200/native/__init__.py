@@ -35,7 +35,7 @@ _CUDA_SIGNATURES = {
     "prb_ep_recv_fp8": [P, P, P, P, P, P, I, I, I, I, I, I, P, P],
     "prb_ipc_export_range": [P, P, P], "prb_weight_push": [P, P, L, P],
     "prb_weight_push_fp8": [P, L, P, P, I, I, P],
-    "prb_gemm_fp8": [P, P, P, P, P, I, I, I, L, P, I, P, P], "prb_act_quant_fp8": [P, L, P, P, I, I, P],
+    "prb_gemm_fp8": [P, P, P, P, P, I, I, I, L, P, I, P, P, P], "prb_act_quant_fp8": [P, L, P, P, I, I, P, P],
     "prb_a2a_push": [P, P, P, L, L, L, P, I, I, I, I, P],
     "prb_a2a_recv": [P, P, P, P, L, L, P, I, I, I, I, I, P, P],
     "prb_ep_wait": [P, I, I, I, P, P],

@@ -9,8 +9,9 @@ import torch
 from . import _runtime as rt
 
 
-def quantize_act(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
-    """x bf16 [M, K] -> (e4m3 as uint8 [M, K], fp32 scales [M, ceil(K/128)])."""
+def quantize_act(x: torch.Tensor, row_valid: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """x bf16 [M, K] -> (e4m3 as uint8 [M, K], fp32 scales [M, ceil(K/128)]). ``row_valid`` (int32 [M]):
+    rows with a negative entry are padding; on a GPU they are neither read nor written."""
     M, K = x.shape
     KB = (K + 127) // 128
     if x.is_cuda and x.dtype == torch.bfloat16:
@@ -18,10 +19,10 @@ def quantize_act(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
         q = torch.empty(M, K, dtype=torch.uint8, device=x.device)
         s = torch.empty(M, KB, dtype=torch.float32, device=x.device)
         rt.check(rt.lib().prb_act_quant_fp8(x.data_ptr(), x.stride(0), q.data_ptr(), s.data_ptr(), M, K,
-                                            rt.stream_ptr(x.device)), "prb_act_quant_fp8")
+                                            rt.ptr(row_valid), rt.stream_ptr(x.device)), "prb_act_quant_fp8")
         return q, s
     pad = torch.zeros(M, KB * 128, dtype=torch.float32, device=x.device)
-    pad[:, :K] = x.float()
+    pad[:, :K] = x.float() if row_valid is None else torch.where((row_valid >= 0)[:, None], x.float(), 0.0)
     blocks = pad.view(M, KB, 128)
     s = blocks.abs().amax(-1).clamp_min(1e-12) / 448.0
     q = (blocks / s[..., None]).view(M, KB * 128)[:, :K].to(torch.float8_e4m3fn)
@@ -47,13 +48,19 @@ def fp8_gemm_ref(aq, sa, bq, sb, block_expert=None) -> torch.Tensor:
     return out
 
 
-def fp8_gemm(aq, sa, bq, sb, *, block_expert: torch.Tensor | None = None, out: torch.Tensor | None = None
-             ) -> torch.Tensor:
+def fp8_gemm(aq, sa, bq, sb, *, block_expert: torch.Tensor | None = None, out: torch.Tensor | None = None,
+             row_valid: torch.Tensor | None = None) -> torch.Tensor:
     """C bf16 [M, N] = dequant(aq, sa) @ dequant(bq, sb)^T. Grouped when ``block_expert`` is given
-    (``bq`` [E, N, K], ``sb`` [E, ceil(N/128), ceil(K/128)], rows in 128-row expert blocks)."""
+    (``bq`` [E, N, K], ``sb`` [E, ceil(N/128), ceil(K/128)], rows in 128-row expert blocks).
+    ``row_valid`` (int32 [M]): rows with a negative entry are padding whose inputs may be uninitialised
+    and whose outputs are not stored."""
     M, K = aq.shape
     N = bq.shape[-2]
     if not aq.is_cuda:
+        if row_valid is not None:           # padding rows may hold anything: keep them out of the arithmetic
+            aq, sa = aq.clone(), sa.clone()
+            aq[row_valid < 0] = 0
+            sa[row_valid < 0] = 0
         return fp8_gemm_ref(aq, sa, bq, sb, block_expert).to(torch.bfloat16)
     assert aq.is_contiguous() and bq.is_contiguous() and sa.is_contiguous() and sb.is_contiguous()
     assert bq.shape[-1] == K and K % 16 == 0
@@ -62,6 +69,7 @@ def fp8_gemm(aq, sa, bq, sb, *, block_expert: torch.Tensor | None = None, out: t
         out = torch.empty(M, N, dtype=torch.bfloat16, device=aq.device)
     status = rt.status_tensor(aq.device)
     rt.check(rt.lib().prb_gemm_fp8(aq.data_ptr(), sa.data_ptr(), bq.data_ptr(), sb.data_ptr(), out.data_ptr(), M, N, K,
-                                   out.stride(0), rt.ptr(block_expert), E, status.data_ptr(), rt.stream_ptr(aq.device)),
+                                   out.stride(0), rt.ptr(block_expert), E, rt.ptr(row_valid), status.data_ptr(),
+                                   rt.stream_ptr(aq.device)),
              "prb_gemm_fp8")
     return out

@@ -91,6 +91,13 @@ class _Shared:
         return sh
 
 
+def release_shared() -> None:
+    """Frees the symmetric buffers of every dispatcher of this process (collective over their groups)."""
+    for sh in list(_Shared._cache.values()):
+        sh.mem.close()
+    _Shared._cache.clear()
+
+
 class _Route:
     """Per-call routing state shared by the two autograd functions."""
     __slots__ = ("sh", "idx", "slot", "local_off", "send_base", "pos", "hist", "expert_offset", "block_expert",

@@ -33,6 +33,15 @@ def flops_per_token(arch: ModelArch, seq_len: int, *, lora: bool = False, causal
     return float(mm + attn)
 
 
+def count_params(arch: ModelArch) -> tuple[int, int]:
+    """(parameters outside the routed experts, parameters of the routed experts): what expert parallelism
+    replicates and what it spreads over the ranks."""
+    H = arch.hidden_size
+    moe_layers = sum(1 for i in range(arch.num_hidden_layers) if arch.is_moe and arch.layer_is_moe(i))
+    expert = moe_layers * arch.num_experts * 3 * H * arch.moe_intermediate_size if arch.is_moe else 0
+    return arch.param_count() - expert, expert
+
+
 class PerfCounter:
     def __init__(self, arch: ModelArch, seq_len: int, world_size: int, device_name: str = "B200", lora: bool = False,
                  window: int = 10):

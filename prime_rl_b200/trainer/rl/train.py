@@ -119,6 +119,21 @@ class RLTrainer:
                          f"setup {time.perf_counter() - t0:.1f}s, dims {self.dims}")
         return self
 
+    def close(self) -> None:
+        """Releases what lives outside the tensor allocator (symmetric peer-memory buffers of the optimizer
+        collectives, of the expert-parallel dispatcher and of context parallelism). Collective: every rank
+        calls it. The trainer cannot step afterwards."""
+        for g in getattr(self.optimizer, "groups", []):
+            if g.p2p is not None:
+                g.p2p.close()
+                g.p2p = None
+        if self.dims.ep_enabled:
+            from ...parallel import ep_p2p
+
+            ep_p2p.release_shared()
+        if self.cp_ctx is not None and hasattr(self.cp_ctx, "close"):
+            self.cp_ctx.close()
+
     def _maybe_load_pretrained(self) -> None:
         mc = self.config.model
         p = Path(mc.name)

@@ -52,30 +52,56 @@ class P2PWeightPort:
     (2-D weights land as e4m3 + 128 x 128 scales in buffers owned by the port, other tensors as
     they are; ``dequantize_into_model`` refreshes the live parameters from them)."""
 
-    def __init__(self, model, run_dir: Path, replica: int = 0, quantize: str | None = None):
-        self.model, self.run_dir, self.replica, self.quantize = model, Path(run_dir), replica, quantize
+    def __init__(self, model, run_dir: Path | None, replica: int = 0, quantize: str | None = None):
+        """``run_dir=None``: build the manifest only (``self.manifest``), write no file — for callers that
+        hand it to the sender through another channel."""
+        self.model, self.replica, self.quantize = model, replica, quantize
+        self.run_dir = Path(run_dir) if run_dir is not None else None
         self.params = dict(model.named_parameters())
         dev = next(model.parameters()).device
         rt.stream_ptr(dev)
+        # An engine that serves from fp8 copies owns (payload, scales) buffers per projection: the push lands
+        # in those, nothing is copied or re-quantised on this side afterwards.
+        self.live_fp8: dict[str, tuple[torch.Tensor, torch.Tensor]] = {}
+        if quantize == "fp8":
+            for mname, mod in model.named_modules():
+                f8 = getattr(mod, "fp8", None)
+                if isinstance(f8, tuple):
+                    self.live_fp8[f"{mname}.weight"] = f8
+                elif isinstance(f8, dict):
+                    for leaf, pair in f8.items():
+                        self.live_fp8[f"{mname}.{leaf}"] = pair
         self.fp8: dict[str, tuple[torch.Tensor, torch.Tensor]] = {}
         entries = {}
         for name, p in self.params.items():
+            live = self.live_fp8.get(name)
+            if live is not None:
+                q, s_ = live
+                K = q.shape[-1]
+                N = q.numel() // K
+                shape = list(p.shape) if p.numel() else list(q.shape)
+                entries[name] = {"shape": shape, "dtype": "bfloat16",
+                                 "fp8": {"q": _export(q), "scales": _export(s_), "rows": N, "cols": K}}
+                continue
+            if p.numel() == 0:
+                continue
             assert p.is_contiguous(), name
             e = {"shape": list(p.shape), "dtype": str(p.dtype).replace("torch.", ""), **_export(p.data)}
             if quantize == "fp8" and p.dim() >= 2 and p.shape[-1] % 2 == 0 and p.dtype == torch.bfloat16:
                 K = p.shape[-1]
                 N = p.numel() // K
                 q = torch.empty(N, K, dtype=torch.uint8, device=dev)
-                s = torch.empty((N + 127) // 128, (K + 127) // 128, dtype=torch.float32, device=dev)
-                self.fp8[name] = (q, s)
-                e["fp8"] = {"q": _export(q), "scales": _export(s), "rows": N, "cols": K}
+                s_ = torch.empty((N + 127) // 128, (K + 127) // 128, dtype=torch.float32, device=dev)
+                self.fp8[name] = (q, s_)
+                e["fp8"] = {"q": _export(q), "scales": _export(s_), "rows": N, "cols": K}
             entries[name] = e
         self.manifest = {"device": dev.index or 0, "quantize": quantize, "params": entries}
-        path = manifest_path(self.run_dir, replica)
-        path.parent.mkdir(parents=True, exist_ok=True)
-        tmp = path.with_suffix(".tmp")
-        tmp.write_text(json.dumps(self.manifest))
-        tmp.replace(path)
+        if self.run_dir is not None:
+            path = manifest_path(self.run_dir, replica)
+            path.parent.mkdir(parents=True, exist_ok=True)
+            tmp = path.with_suffix(".tmp")
+            tmp.write_text(json.dumps(self.manifest))
+            tmp.replace(path)
 
     def wait_finished(self, step_dir: Path, timeout: float = 1200.0) -> None:
         t0 = time.monotonic()
@@ -86,9 +112,14 @@ class P2PWeightPort:
         torch.cuda.synchronize()
 
     def dequantize_into_model(self) -> None:
-        """fp8 mode: live bf16 parameter = e4m3 payload x block scale."""
-        for name, (q, s) in self.fp8.items():
+        """fp8 mode: live bf16 parameter = e4m3 payload x block scale (projections that serve straight
+        from the pushed fp8 buffers need nothing; a bf16 copy they still keep is refreshed too)."""
+        both = dict(self.fp8)
+        both.update({n: pair for n, pair in self.live_fp8.items() if self.params[n].numel() > 0})
+        for name, (q, s) in both.items():
             p = self.params[name]
+            q = q.reshape(-1, q.shape[-1])
+            s = s.reshape(-1, s.shape[-1])
             N, K = q.shape
             w = q.view(torch.float8_e4m3fn).float()
             sc = s.repeat_interleave(128, 0)[:N].repeat_interleave(128, 1)[:, :K]

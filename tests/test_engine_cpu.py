@@ -199,7 +199,7 @@ def test_tensor_parallel_engine_in_lockstep_matches_the_single_engine():
     root = Path(__file__).resolve().parents[1]
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=str(root))
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-                        "--master-addr", "127.0.0.1", "--master-port", "29617", "-m", "prime_rl_b200.engine.tp",
+                        "--master-addr", "127.0.0.1", "--master-port", "29617", "-m", "tests.distributed.tp_engine",
                         "--batch", "5", "--prompt", "24", "--tokens", "8"], env=env, capture_output=True, text=True,
                        timeout=600, cwd=str(root))
     assert r.returncode == 0 and "TP_SELFTEST_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]

@@ -134,3 +134,39 @@ def test_prefill_on_a_cached_prefix_uses_the_query_slice_kernel_and_matches_a_fr
     assert same >= len(prompts) - 1                             # bf16 ties may flip one greedy token
     for a, b in zip(ref, got):
         assert abs(a.logprobs[0] - b.logprobs[0]) < 5e-2
+
+
+def test_fp8_engine_without_bf16_copies_serves_and_takes_weight_updates(tmp_path):
+    """``keep_bf16_weights=False`` releases the bf16 storage of every quantised projection. The engine must
+    give the same greedy tokens as the fp8 engine that keeps them, and a weight update from a checkpoint
+    directory must be quantised straight into the fp8 copies."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from prime_rl_b200.engine.engine import Engine
+    from prime_rl_b200.models import ModelArch, build_model
+    from prime_rl_b200.ops import _runtime as rt
+    from prime_rl_b200.trainer.weights import save_hf_checkpoint
+
+    dev = torch.device("cuda", 0)
+    arch = ModelArch(**ARCH)
+    kw = dict(num_pages=512, page_size=16, enable_prefix_cache=False, max_model_len=256, weight_dtype="fp8")
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, arch.vocab_size, (n,), generator=g).tolist() for n in (9, 40, 64)]
+    keep = Engine(build_model(arch, device=dev, dtype=torch.bfloat16, seed=0), **kw)
+    lean = Engine(build_model(arch, device=dev, dtype=torch.bfloat16, seed=0), keep_bf16_weights=False, **kw)
+    layer = lean.model.model.layers[0]
+    assert layer.mlp.experts.gate_up_proj.numel() == 0 and layer.self_attn.qkv_proj.weight.numel() == 0
+    a, b = _greedy(keep, prompts), _greedy(lean, prompts)
+    assert [r.output for r in a] == [r.output for r in b]
+    # new weights arrive as an HF directory
+    other = build_model(arch, device=dev, dtype=torch.bfloat16, seed=7)
+    save_hf_checkpoint(other, tmp_path / "w")
+    lean.update_weights_from_dir(str(tmp_path / "w"))
+    keep.update_weights_from_dir(str(tmp_path / "w"))
+    assert layer.mlp.experts.gate_up_proj.numel() == 0
+    a, b = _greedy(keep, prompts), _greedy(lean, prompts)
+    rt.check_status()
+    assert [r.output for r in a] == [r.output for r in b]
+    fresh = Engine(other, **kw)
+    c = _greedy(fresh, prompts)
+    assert sum(x.output == y.output for x, y in zip(b, c)) >= 2

@@ -782,6 +782,48 @@ def test_moe_inference_path_skips_padding_rows_and_matches_the_training_path():
     assert torch.equal(y_inf, y_ref)
 
 
+def test_fp8_experts_skip_padding_rows_and_match_the_padded_fp8_path():
+    """fp8 expert weights at inference: token rows are quantised once and gathered as fp8, every kernel skips the
+    rows that pad an expert to 128. Must agree with the zero-padded fp8 path (same quantised operands) and stay
+    close to the bf16 result; padding rows poisoned with NaNs must not leak."""
+    from prime_rl_b200.models import ModelArch, SeqInfo
+    from prime_rl_b200.models.layers import MoE
+    from prime_rl_b200.ops import fp8
+
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    arch = ModelArch(model_type="qwen3_moe", hidden_size=512, num_hidden_layers=1, num_attention_heads=4,
+                     num_key_value_heads=2, head_dim=128, intermediate_size=512, num_experts=16, num_experts_per_tok=4,
+                     moe_intermediate_size=256, vocab_size=256)
+    moe = MoE(arch, 0, dtype=torch.bfloat16, device=dev)
+    with torch.no_grad():
+        for p in moe.parameters():
+            p.normal_(0, 0.05)
+    x = torch.randn(53, 512, device=dev).bfloat16()
+    seq = SeqInfo(None, 0, torch.arange(53, dtype=torch.int32, device=dev))
+    with torch.no_grad():
+        y_bf16 = moe(x, seq)
+        assert moe.experts.quantize_fp8_()
+        junk = torch.full((64 * 128, 512), float("nan"), device=dev, dtype=torch.bfloat16)
+        del junk
+        assert moe.experts.supports_fp8_row_mask(x)
+        y_masked = moe(x, seq)
+        moe.experts.supports_fp8_row_mask = lambda _x: False      # zero-padded rows through the same fp8 GEMMs
+        moe.experts.supports_row_mask = lambda _x: False
+        y_padded = moe(x, seq)
+    rt.check_status()
+    assert torch.isfinite(y_masked.float()).all()
+    _close(y_masked, y_padded, atol=2e-2, rtol=2e-2)
+    assert ((y_masked.float() - y_bf16.float()).norm() / y_bf16.float().norm()) < 0.1
+    # the masked quantiser leaves padding rows alone and agrees with the full one on the others
+    h = torch.randn(256, 384, device=dev).bfloat16()
+    valid = torch.full((256,), -1, dtype=torch.int32, device=dev)
+    valid[::3] = 1
+    q_all, s_all = fp8.quantize_act(h)
+    q_m, s_m = fp8.quantize_act(h, row_valid=valid)
+    assert torch.equal(q_m[::3], q_all[::3]) and torch.equal(s_m[::3], s_all[::3])
+
+
 def test_qkv_rope_to_cache_matches_separate_ops():
     """Fused split + QK-norm + rotary + paged-cache write against qkv_norm_rope followed by index_copy_
     (bit-equal), with and without the contiguous K / V outputs and without QK-norm."""
