@@ -182,12 +182,18 @@ def run_rollout_bench(model: str = "qwen3-30b-a3b", contexts=(1024, 3072, 5120),
             torch.cuda.synchronize()
             wall = time.perf_counter() - t0
             toks = eng.stats["generation_tokens"] - n0
+            if running < batch:
+                raise RuntimeError(f"only {running} of {batch} requests were running at context {C}: the KV pool is too "
+                                   "small for the benchmark (requests were preempted)")
             points.append({"context": C, "ms_per_step": e0.elapsed_time(e1) / steps, "wall_ms_per_step": 1e3 * wall / steps,
                            "tokens": toks, "running": running, "prefix_shared_tokens": shared_tokens,
                            "kv_usage": eng.cache.blocks.usage})
             while eng.running or eng.waiting:           # let the requests run out before the next context
                 eng.step()
             del first, rest
+            eng.clear_prefix_cache()                    # the next context needs the pages these prompts still hold
+            if tp is not None:
+                eng.step()                              # carries the command to the other ranks
         from ..ops import _runtime as rt
 
         rt.check_status()

@@ -171,6 +171,8 @@ class Engine:
                 self._update_weights_local(cmd[1])
             elif cmd[0] == "mark":                  # a label every rank sees at the same step (benchmarks)
                 self.mark = cmd[1]
+            elif cmd[0] == "clear_prefix_cache":
+                self.cache.blocks.clear_prefix_cache()
             elif cmd[0] == "stop":
                 alive = False
         return alive
@@ -239,7 +241,7 @@ class Engine:
                 need_pages = (len(toks) + self.cache.page_size) // self.cache.page_size + 1
                 if len(toks) > budget and admitted:
                     break
-                if self.cache.blocks.num_free < need_pages and (self.running or admitted):
+                if self.cache.blocks.num_available < need_pages and (self.running or admitted):
                     break
                 self.waiting.pop(0)
                 admitted.append(r)
@@ -405,6 +407,16 @@ class Engine:
             quantize_fp8_(self.model, drop_bf16=self.drop_bf16)
         self.cache.blocks.clear_prefix_cache()
         self.policy_version += 1
+
+    def clear_prefix_cache(self) -> None:
+        """Drops every cached prefix (their pages return to the free list once no running request uses them).
+        With tensor parallelism the command travels with the next step announcement so that every rank drops
+        the same pages at the same step."""
+        if self.tp_size > 1:
+            with self.lock:
+                self._commands.append(("clear_prefix_cache",))
+        else:
+            self.cache.blocks.clear_prefix_cache()
 
     def metrics(self) -> dict:
         with self.lock:

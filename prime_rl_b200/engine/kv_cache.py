@@ -27,14 +27,20 @@ class BlockManager:
         self.refcount = [0] * num_pages
         self.prefix_cache: dict[tuple, int] = {}     # (salt, tokens-so-far hash) -> page id
         self.page_key: dict[int, tuple] = {}
+        self.evictable = 0                            # cached pages that no sequence holds any more
 
     @property
     def num_free(self) -> int:
         return len(self.free)
 
     @property
+    def num_available(self) -> int:
+        """Pages an allocation can get: the free list plus cached prefix pages nobody is using."""
+        return len(self.free) + self.evictable
+
+    @property
     def usage(self) -> float:
-        return 1.0 - len(self.free) / max(1, self.num_pages)
+        return 1.0 - self.num_available / max(1, self.num_pages)
 
     def alloc(self) -> int:
         if not self.free:
@@ -52,11 +58,14 @@ class BlockManager:
                 del self.prefix_cache[key]
                 self.page_key.pop(p, None)
                 self.refcount[p] = 0
+                self.evictable -= 1
                 self.free.append(p)
                 if len(self.free) >= 8:
                     break
 
     def incref(self, p: int) -> None:
+        if self.refcount[p] == 1 and p in self.page_key:
+            self.evictable -= 1                      # a sequence picks a cached page up again
         self.refcount[p] += 1
 
     def release(self, pages: list[int]) -> None:
@@ -67,6 +76,8 @@ class BlockManager:
                 if key is not None:
                     self.prefix_cache.pop(key, None)
                 self.free.append(p)
+            elif self.refcount[p] == 1 and p in self.page_key:
+                self.evictable += 1                  # only the cache holds it now
 
     # prefix cache -----------------------------------------------------------------
     def lookup_prefix(self, salt: str, tokens: list[int]) -> list[int]:
@@ -91,8 +102,8 @@ class BlockManager:
             key = (salt, h)
             if key not in self.prefix_cache and n < len(pages) and pages[n] not in self.page_key:
                 self.prefix_cache[key] = pages[n]
+                self.refcount[pages[n]] += 1      # the cache holds one reference
                 self.page_key[pages[n]] = key
-                self.incref(pages[n])      # the cache holds one reference
 
     def clear_prefix_cache(self) -> None:
         for key, p in list(self.prefix_cache.items()):
@@ -101,6 +112,7 @@ class BlockManager:
                 self.free.append(p)
         self.prefix_cache.clear()
         self.page_key.clear()
+        self.evictable = 0
 
 
 @dataclass

@@ -211,6 +211,12 @@ class ModelArch(BaseModel):
         if mt in ("qwen3_5", "qwen3_5_moe") and "text_config" in cfg:      # multimodal wrapper: the text tower
             cfg = {**cfg["text_config"], "model_type": mt}
         mt = {"qwen3_5_text": "qwen3_5", "qwen3_5_moe_text": "qwen3_5_moe"}.get(mt, mt)
+        # transformers >= 5 writes some fields under other names (``num_local_experts`` for ``num_experts``,
+        # ``rope_parameters`` for ``rope_theta`` / ``rope_scaling``): accept both spellings
+        cfg = dict(cfg)
+        for ours, theirs in (("num_experts", "num_local_experts"), ("num_local_experts", "num_experts")):
+            if ours not in cfg and theirs in cfg:
+                cfg[ours] = cfg[theirs]
         heads = cfg["num_attention_heads"]
         d: dict[str, Any] = dict(
             model_type=mt,
@@ -223,7 +229,8 @@ class ModelArch(BaseModel):
             intermediate_size=cfg.get("intermediate_size", 0),
             rms_norm_eps=cfg.get("rms_norm_eps", 1e-6),
             rope_theta=cfg.get("rope_theta") or (cfg.get("rope_parameters") or {}).get("rope_theta", 1e4),
-            partial_rotary_factor=cfg.get("partial_rotary_factor", 1.0),
+            partial_rotary_factor=cfg.get("partial_rotary_factor") or
+            (cfg.get("rope_parameters") or {}).get("partial_rotary_factor", 1.0),
             max_position_embeddings=cfg.get("max_position_embeddings", 32768),
             tie_word_embeddings=cfg.get("tie_word_embeddings", False),
             attention_bias=cfg.get("attention_bias", False),

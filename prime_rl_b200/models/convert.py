@@ -120,6 +120,56 @@ class StackExperts:
 
 
 @dataclass
+class GptOssExperts:
+    """GPT-OSS checkpoints keep every layer's experts fused and input-major: ``gate_up_proj [E, H, 2I]`` with
+    gate and up columns interleaved (gate = even columns), ``down_proj [E, I, H]``, and biases alike; the prime
+    layout has ``gate_proj / up_proj [E, I, H]``, ``down_proj [E, H, I]`` and separate bias tensors
+    (reference: src/prime_rl/trainer/models/gpt_oss/converting_gpt_oss.py:8-44)."""
+
+    def forward(self, sd: StateDict) -> StateDict:       # prime -> hf
+        out: StateDict = {}
+        for k, v in sd.items():
+            if k.endswith("mlp.experts.gate_proj"):
+                base = k[:-len("gate_proj")]
+                up = sd[base + "up_proj"]
+                fused = v.new_empty(v.shape[0], v.shape[2], 2 * v.shape[1])
+                fused[..., ::2] = v.transpose(-2, -1)
+                fused[..., 1::2] = up.transpose(-2, -1)
+                out[base + "gate_up_proj"] = fused
+            elif k.endswith("mlp.experts.gate_proj_bias"):
+                base = k[:-len("gate_proj_bias")]
+                up = sd[base + "up_proj_bias"]
+                fused = v.new_empty(v.shape[0], 2 * v.shape[1])
+                fused[..., ::2] = v
+                fused[..., 1::2] = up
+                out[base + "gate_up_proj_bias"] = fused
+            elif k.endswith(("mlp.experts.up_proj", "mlp.experts.up_proj_bias")):
+                continue
+            elif k.endswith("mlp.experts.down_proj"):
+                out[k] = v.transpose(-2, -1).contiguous()
+            else:
+                out[k] = v
+        return out
+
+    def inverse(self, sd: StateDict) -> StateDict:       # hf -> prime
+        out: StateDict = {}
+        for k, v in sd.items():
+            if k.endswith("mlp.experts.gate_up_proj"):
+                base = k[:-len("gate_up_proj")]
+                out[base + "gate_proj"] = v[..., ::2].transpose(-2, -1).contiguous()
+                out[base + "up_proj"] = v[..., 1::2].transpose(-2, -1).contiguous()
+            elif k.endswith("mlp.experts.gate_up_proj_bias"):
+                base = k[:-len("gate_up_proj_bias")]
+                out[base + "gate_proj_bias"] = v[..., ::2].contiguous()
+                out[base + "up_proj_bias"] = v[..., 1::2].contiguous()
+            elif k.endswith("mlp.experts.down_proj"):
+                out[k] = v.transpose(-2, -1).contiguous()
+            else:
+                out[k] = v
+        return out
+
+
+@dataclass
 class MapValue:
     """Renames ``suffix`` -> ``new_suffix`` and maps the tensor (``fwd``) / back (``inv``)."""
 
@@ -200,6 +250,8 @@ def native_to_prime_chain(arch: ModelArch) -> Chain:
         ]
     ops += [
         SplitConcat("mlp.experts.gate_up_proj", ["mlp.experts.gate_proj", "mlp.experts.up_proj"],
+                    lambda v: [v.shape[1] // 2, v.shape[1] // 2], dim=1),
+        SplitConcat("mlp.experts.gate_up_proj_bias", ["mlp.experts.gate_proj_bias", "mlp.experts.up_proj_bias"],
                     lambda v: [v.shape[1] // 2, v.shape[1] // 2], dim=1),
         SplitConcat("shared_experts.gate_up_proj.weight", ["shared_experts.gate_proj.weight",
                                                            "shared_experts.up_proj.weight"],
@@ -289,6 +341,9 @@ def prime_to_hf_chain(arch: ModelArch, first_expert: int = 0) -> Chain:
                 StackExperts("mlp.experts.up_proj", "mlp.experts.{e}.up_proj.weight", first_expert),
                 StackExperts("mlp.experts.down_proj", "mlp.experts.{e}.down_proj.weight", first_expert)]
         return Chain(ops + _family_chain(arch))
+    if arch.model_type == "gpt_oss":
+        return Chain([Rename(r"mlp\.router\.gate\.(weight|bias)$", r"mlp.router.\1", r"mlp\.router\.(weight|bias)$",
+                             r"mlp.router.gate.\1"), GptOssExperts()])
     if arch.model_type == "laguna":
         # Laguna checkpoints name the shared expert in the singular and keep the selection bias under `experts`
         ops += [
@@ -382,6 +437,8 @@ def gather_expert_shards(local: torch.Tensor, info) -> torch.Tensor:
 @torch.no_grad()
 def load_model_state(model, sd: StateDict, layout: str = "prime", strict: bool = True) -> None:
     arch = model.arch
+    if arch.tie_word_embeddings and layout in ("hf", "prime") and "lm_head.weight" in sd:
+        sd = {k: v for k, v in sd.items() if k != "lm_head.weight"}      # the tied head is the embedding
     if layout == "hf":
         sd = hf_to_prime(sd, arch)
     if layout in ("hf", "prime"):

@@ -289,6 +289,9 @@ class GroupedExperts(nn.Module):
         width = I if self.act == act_ops.RELU2 else 2 * I
         self.gate_up_proj = nn.Parameter(torch.empty(E, width, H, dtype=dtype, device=device))
         self.down_proj = nn.Parameter(torch.empty(E, H, I, dtype=dtype, device=device))
+        # per-expert projection biases (GPT-OSS): [gate | up] in the row order of gate_up_proj
+        self.gate_up_proj_bias = nn.Parameter(torch.zeros(E, width, dtype=dtype, device=device)) if arch.expert_bias else None
+        self.down_proj_bias = nn.Parameter(torch.zeros(E, H, dtype=dtype, device=device)) if arch.expert_bias else None
         self.lora_gate_up: LoRAAdapter | None = None
         self.lora_down: LoRAAdapter | None = None
         self.fp8: dict[str, tuple[torch.Tensor, torch.Tensor]] | None = None   # inference-only fp8 copies
@@ -324,10 +327,19 @@ class GroupedExperts(nn.Module):
             done = True
         return done
 
+    def _biased(self, y: torch.Tensor, bias: torch.Tensor | None, block_expert: torch.Tensor) -> torch.Tensor:
+        """Adds every row's expert bias (rows come in 128-row blocks owned by ``block_expert``; unused blocks
+        borrow expert 0, nothing reads them)."""
+        if bias is None:
+            return y
+        row_expert = block_expert.clamp_min(0).long().repeat_interleave(128)[:y.shape[0]]
+        return y + bias[row_expert].to(y.dtype)
+
     def supports_fp8_row_mask(self, x: torch.Tensor) -> bool:
         """No-grad forward from the fp8 copies on the GPU: the token rows are quantised once, gathered as
         fp8 into the expert-sorted order, and the padding rows are skipped by every kernel."""
         return (not torch.is_grad_enabled() and x.is_cuda and x.dtype == torch.bfloat16 and self.fp8 is not None
+                and self.gate_up_proj_bias is None
                 and self.act != act_ops.SILU_CLAMPED and x.shape[1] % 512 == 0)
 
     def forward_fp8_masked(self, x: torch.Tensor, plan) -> torch.Tensor:
@@ -351,6 +363,7 @@ class GroupedExperts(nn.Module):
         """No-grad bf16 forward on the GPU without adapters or fp8 copies: the padding rows that round every
         expert up to 128 need not be written, read by the activation or stored by the GEMMs."""
         return (not torch.is_grad_enabled() and x.is_cuda and x.dtype == torch.bfloat16 and self.fp8 is None
+                and self.gate_up_proj_bias is None
                 and self.lora_gate_up is None and self.lora_down is None and self.act != act_ops.SILU_CLAMPED
                 and self.gate_up_proj.dtype == torch.bfloat16)
 
@@ -367,8 +380,12 @@ class GroupedExperts(nn.Module):
 
             xq, xs = fp8_ops.quantize_act(xp)
             gu = fp8_ops.fp8_gemm(xq, xs, *self.fp8["gate_up_proj"], block_expert=block_expert)
+            gu = self._biased(gu, self.gate_up_proj_bias, block_expert)
             h = ops.glu(gu, self.act, self.arch.swiglu_limit, self.arch.swiglu_alpha)
             hq, hs = fp8_ops.quantize_act(h)
+            if self.down_proj_bias is not None:
+                return self._biased(fp8_ops.fp8_gemm(hq, hs, *self.fp8["down_proj"], block_expert=block_expert),
+                                    self.down_proj_bias, block_expert)
             return fp8_ops.fp8_gemm(hq, hs, *self.fp8["down_proj"], block_expert=block_expert, out=out)
         if self.lora_gate_up is not None:
             l = self.lora_gate_up
@@ -376,12 +393,17 @@ class GroupedExperts(nn.Module):
                                               expert_offset)
         else:
             gu = ops.grouped_linear(xp, self.gate_up_proj, block_expert, expert_offset)
+        gu = self._biased(gu, self.gate_up_proj_bias, block_expert)
         h = ops.glu(gu, self.act, self.arch.swiglu_limit, self.arch.swiglu_alpha)
+        if self.down_proj_bias is not None:
+            out = None                # the bias add makes a new tensor anyway
         if self.lora_down is not None:
             l = self.lora_down
-            return lora_ops.lora_grouped_linear(h, self.down_proj, l.lora_A, list(l.lora_B), l.scale, block_expert,
-                                                expert_offset, out=out)
-        return ops.grouped_linear(h, self.down_proj, block_expert, expert_offset, out=out)
+            y = lora_ops.lora_grouped_linear(h, self.down_proj, l.lora_A, list(l.lora_B), l.scale, block_expert,
+                                             expert_offset, out=out)
+        else:
+            y = ops.grouped_linear(h, self.down_proj, block_expert, expert_offset, out=out)
+        return self._biased(y, self.down_proj_bias, block_expert)
 
 
 class MoE(nn.Module):

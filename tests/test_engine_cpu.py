@@ -296,3 +296,30 @@ def test_small_route_plan_is_gpu_only():
 
     with torch.no_grad():
         assert moe_ops.route_and_plan_small(torch.randn(4, 8), 2) is None
+
+
+def test_cached_prefix_pages_count_as_available_and_are_evicted_on_demand():
+    """Pages that only the prefix cache still holds must not block admission: they are counted as available
+    and reclaimed when the free list runs dry."""
+    from prime_rl_b200.engine.kv_cache import BlockManager, OutOfPages
+
+    bm = BlockManager(num_pages=8, page_size=4)
+    toks = list(range(16))
+    pages = [bm.alloc() for _ in range(4)]
+    bm.register_prefix("s", toks, pages)
+    assert bm.num_available == 4 and bm.evictable == 0          # the sequence still holds its pages
+    bm.release(pages)
+    assert bm.num_free == 4 and bm.evictable == 4 and bm.num_available == 8 and bm.usage == 0.0
+    hit = bm.lookup_prefix("s", toks[:8])                       # a new sequence takes two cached pages
+    assert hit == pages[:2] and bm.evictable == 2 and bm.num_available == 6
+    got = [bm.alloc() for _ in range(6)]                        # 4 free + 2 reclaimed from the cache
+    assert len(set(got)) == 6 and not set(got) & set(hit)
+    assert bm.num_available == 0
+    import pytest
+
+    with pytest.raises(OutOfPages):
+        bm.alloc()
+    bm.release(hit)
+    assert bm.evictable == 2                                    # back to cache-only
+    bm.clear_prefix_cache()
+    assert bm.evictable == 0 and bm.num_free == 2
