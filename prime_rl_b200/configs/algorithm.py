@@ -19,7 +19,8 @@ class FrozenModelConfig(ClientConfig):
 
 
 class SamplingConfig(BaseConfig):
-    source: str = "policy"
+    # "policy": the live, weight-updated policy; or an inline frozen model served elsewhere
+    source: Literal["policy"] | FrozenModelConfig = "policy"
 
 
 class LinearLengthPenaltyConfig(BaseConfig):

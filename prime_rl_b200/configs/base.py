@@ -35,9 +35,15 @@ class BaseConfig(BaseModel):
     @model_validator(mode="before")
     @classmethod
     def _default_union_tags(cls, data):
-        # {"optim": {"lr": 1e-5}} keeps the default optimizer's ``type``
+        # {"optim": {"lr": 1e-5}} keeps the default optimizer's ``type``; the string "None" (how TOML files
+        # and flags spell null, TOML having no null) clears any field that may be None
         if isinstance(data, dict):
-            return inject_union_defaults(cls, dict(data), recurse=False)
+            data = inject_union_defaults(cls, dict(data), recurse=False)
+            for k, v in list(data.items()):
+                if v == "None" and isinstance(v, str):
+                    fld = cls.model_fields.get(k)
+                    if fld is not None and type(None) in _flatten_union(fld.annotation):
+                        data[k] = None
         return data
 
     def to_json(self, **kw) -> str:
@@ -49,6 +55,18 @@ class BaseConfig(BaseModel):
         tmp = path.with_suffix(path.suffix + ".tmp")
         tmp.write_text(self.to_json())
         tmp.replace(path)
+
+
+def _flatten_union(tp) -> list:
+    origin = get_origin(tp)
+    if origin is typing.Annotated:
+        return _flatten_union(get_args(tp)[0])
+    if origin in (Union, types.UnionType):
+        out = []
+        for a in get_args(tp):
+            out.extend(_flatten_union(a))
+        return out
+    return [tp]
 
 
 def deep_merge(base: dict, other: dict) -> dict:

@@ -7,7 +7,7 @@ from __future__ import annotations
 from pathlib import Path
 from typing import Annotated, Any, Literal, TypeAlias
 
-from pydantic import Field
+from pydantic import Field, model_validator
 
 from .base import BaseConfig
 from .shared import EnvVars, LogConfig, SlurmConfig, default_output_dir
@@ -20,6 +20,34 @@ class ServerConfig(BaseConfig):
 
 
 class EngineConfig(BaseConfig):
+    """Engine arguments under the names the reference's ``[inference.vllm]`` block uses
+    (packages/prime-rl-configs/src/prime_rl/configs/inference.py:42-210). The typed fields are the ones
+    this engine reads; any other key is accepted and kept (``extra``), as the reference passes unknown keys
+    through to its serving engine: kebab-case keys become snake_case and string values from the command
+    line are JSON-parsed where they parse."""
+
+    model_config = {**BaseConfig.model_config, "extra": "allow"}
+
+    @model_validator(mode="before")
+    @classmethod
+    def _normalise_extras(cls, data):
+        if not isinstance(data, dict):
+            return data
+        import json
+
+        out = {}
+        for key, value in data.items():
+            if key in cls.model_fields:
+                out[key] = value
+                continue
+            if isinstance(value, str):
+                try:
+                    value = json.loads(value)
+                except ValueError:
+                    pass
+            out[key.replace("-", "_")] = value
+        return out
+
     model: str = "Qwen/Qwen3-0.6B"
     dtype: Literal["auto", "float16", "bfloat16", "float32"] = "auto"
     max_model_len: int | None = None
@@ -43,6 +71,7 @@ class EngineConfig(BaseConfig):
     max_lora_rank: int | None = None
     lora_target_modules: list[str] | None = None
     enable_expert_parallel: bool = False
+    all2all_backend: str = "allgather_reducescatter"
     enable_eplb: bool = False
     enable_dbo: bool = False
     enable_return_routed_experts: bool = False
@@ -146,6 +175,8 @@ class InferenceConfig(BaseConfig):
     kv_cache_offload: KVCacheOffloadConfig | None = None
     use_pd_kv_transfer: bool = False
     enable_return_sampling_mask: bool = False
+    enable_fp32_lm_head: bool = True              # the LM head of this engine always accumulates in fp32
+    enable_fp32_router_logits: bool = True        # router logits are fp32 here as well
     deployment: InferenceDeploymentConfig = SingleNodeInferenceDeploymentConfig()
     slurm: SlurmConfig | None = None
     output_dir: Path = Field(default_factory=default_output_dir)

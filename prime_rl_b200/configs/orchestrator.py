@@ -63,12 +63,52 @@ class EvalSamplingConfig(BaseConfig):
     extra_body: dict[str, Any] = {}
 
 
+class EnvServeConfig(BaseConfig):
+    """Where the environment of a source is served. ``address`` set: an externally managed env server;
+    unset: the launcher spawns one at ``tcp://127.0.0.1:<env_server_base_port + index>``."""
+
+    model_config = {**BaseConfig.model_config, "extra": "allow"}
+    address: str | None = None
+    num_workers: int | None = None
+
+
+class RendererConfig(BaseConfig):
+    """Chat renderer selection. ``name = "auto"`` picks by model name; other names and their options are
+    passed through to the renderer registry untouched (the reference takes this block from the external
+    ``renderers`` package: packages/prime-rl-configs/src/prime_rl/configs/orchestrator.py:507)."""
+
+    model_config = {**BaseConfig.model_config, "extra": "allow"}
+    name: str = "auto"
+
+
 class EnvConfig(BaseConfig):
+    """One environment. Two spellings are accepted:
+
+    * this framework's own: ``id`` from the built-in registry (``orchestrator/envs.py``) or an
+      ``import_path`` to a factory, with free-form ``args``;
+    * the reference's ``env.*`` tree (``env.taskset.id``, ``env.agent.harness.id``, ...), which belongs to the
+      external ``verifiers`` package there and is kept as an opaque mapping here; ``env.taskset.id`` (or
+      ``env.id``) names the environment and ``env.taskset.args`` / ``env.args`` feed its factory."""
+
     id: str = "reverse-text"
     import_path: str | None = None
     args: dict[str, Any] = {}
+    env: dict[str, Any] = {}
+    serve: EnvServeConfig = EnvServeConfig()
     name: str | None = None
     ratio: float = Field(1.0, gt=0)
+
+    @model_validator(mode="after")
+    def _from_env_tree(self):
+        tree = self.env or {}
+        taskset = tree.get("taskset") if isinstance(tree.get("taskset"), dict) else {}
+        ident = taskset.get("id") or tree.get("id")
+        if ident and "id" not in self.model_fields_set:
+            self.id = str(ident)
+        extra = taskset.get("args") or tree.get("args")
+        if isinstance(extra, dict) and "args" not in self.model_fields_set:
+            self.args = dict(extra)
+        return self
 
     @property
     def resolved_name(self) -> str:
@@ -212,6 +252,7 @@ class OrchestratorConfig(BaseConfig):
     model: ModelConfig = ModelConfig()
     train: TrainConfig = TrainConfig()
     tokenizer: TokenizerConfig = TokenizerConfig()
+    renderer: RendererConfig = RendererConfig()
     eval: EvalConfig | None = None
     log: LogConfig = LogConfig()
     env_vars: EnvVars = {}

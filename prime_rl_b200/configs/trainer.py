@@ -6,7 +6,7 @@ import warnings
 from pathlib import Path
 from typing import Annotated, Any, Literal, TypeAlias
 
-from pydantic import Field, model_validator
+from pydantic import BeforeValidator, Field, model_validator
 
 from .base import BaseConfig
 from .monitors import MonitorsConfig
@@ -40,7 +40,17 @@ class OptimizerInBackwardOffloadConfig(BaseConfig):
     numa_bind: bool = True
 
 
-OptimizerInBackwardOffload: TypeAlias = OptimizerInBackwardOffloadConfig | None
+def _normalize_full_offload(value):
+    """``full_offload = true`` enables the block with its defaults, ``false`` disables it."""
+    if value is True:
+        return {}
+    if value is False:
+        return None
+    return value
+
+
+OptimizerInBackwardOffload: TypeAlias = Annotated[OptimizerInBackwardOffloadConfig | None,
+                                                  BeforeValidator(_normalize_full_offload)]
 
 
 class CompileConfig(BaseConfig):

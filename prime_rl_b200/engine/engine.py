@@ -96,6 +96,7 @@ class Engine:
         self.thread: threading.Thread | None = None
         self.logger = get_logger()
         self.policy_version = 0
+        self.weight_receiver = None          # in-memory weight transport endpoint (NCCL receiver or peer-memory port)
         self.stats = dict(prompt_tokens=0, generation_tokens=0, preemptions=0, prefix_hits=0, prefix_queries=0,
                           requests=0, steps=0)
         self.last_step_time = time.monotonic()
@@ -173,6 +174,10 @@ class Engine:
                 self.mark = cmd[1]
             elif cmd[0] == "clear_prefix_cache":
                 self.cache.blocks.clear_prefix_cache()
+            elif cmd[0] == "init_broadcaster":
+                self._init_broadcaster_local(cmd[1])
+            elif cmd[0] == "receive_weights":
+                self.weight_receiver.receive_into(self)
             elif cmd[0] == "stop":
                 alive = False
         return alive
@@ -407,6 +412,50 @@ class Engine:
             quantize_fp8_(self.model, drop_bf16=self.drop_bf16)
         self.cache.blocks.clear_prefix_cache()
         self.policy_version += 1
+
+    # ------------------------------------------------------------------ in-memory weight updates
+    def init_broadcaster(self, spec: dict) -> None:
+        """Joins the trainer's in-memory weight transport. ``spec`` is the body of ``/init_broadcaster``:
+        ``type`` ("nccl" | "p2p"), ``rank_offset`` (index of this engine among all engine GPUs) and the
+        transport's own fields. With tensor parallelism every rank of the engine joins: rank r takes
+        transport slot ``rank_offset + r`` and, on every update, keeps its own slices of what arrives."""
+        if self.tp_size > 1:
+            assert self.tp.rank == 0, "admin commands enter through rank 0"
+            with self.lock:
+                self._commands.append(("init_broadcaster", dict(spec)))
+            self._tp_sync()
+            return
+        self._init_broadcaster_local(spec)
+
+    def _init_broadcaster_local(self, spec: dict) -> None:
+        from pathlib import Path
+
+        slot = int(spec.get("rank_offset", 0)) + (self.tp.rank if self.tp_size > 1 else 0)
+        if spec.get("type") == "p2p":
+            from ..transports.weights.p2p import P2PWeightPort
+
+            tp = (self.tp.rank, self.tp_size) if self.tp_size > 1 else None
+            self.weight_receiver = P2PWeightPort(self.model, Path(spec["run_dir"]), slot, spec.get("quantize"), tp=tp)
+            return
+        from ..transports.weights.nccl import NCCLWeightReceiver
+
+        self.weight_receiver = NCCLWeightReceiver(host=spec["host"], port=int(spec["port"]), rank=slot + 1,
+                                                  world_size=int(spec["inference_world_size"]) + 1,
+                                                  timeout=int(spec.get("timeout", 1200)))
+        self.weight_receiver.connect(self.device if self.device.type == "cuda" else None)
+
+    def receive_weights(self) -> None:
+        """Takes part in one in-memory weight update (engine paused). Tensor-parallel engines: all ranks."""
+        if self.weight_receiver is None:
+            raise RuntimeError("no in-memory broadcaster was initialised")
+        assert self.paused or self.thread is None, "weight updates require a paused engine"
+        if self.tp_size > 1:
+            assert self.tp.rank == 0
+            with self.lock:
+                self._commands.append(("receive_weights",))
+            self._tp_sync()
+            return
+        self.weight_receiver.receive_into(self)
 
     def clear_prefix_cache(self) -> None:
         """Drops every cached prefix (their pages return to the free list once no running request uses them).

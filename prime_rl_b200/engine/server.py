@@ -45,6 +45,8 @@ def build_app(engine: Engine, model_name: str, tokenizer=None, liveness_timeout:
               weight_receiver=None) -> FastAPI:
     app = FastAPI(title="prime-rl-b200 inference")
     app.state.engine = engine
+    if weight_receiver is not None:
+        engine.weight_receiver = weight_receiver
 
     @app.get("/health")
     async def health():
@@ -148,8 +150,8 @@ def build_app(engine: Engine, model_name: str, tokenizer=None, liveness_timeout:
         try:
             if weight_dir is not None:
                 await asyncio.to_thread(engine.update_weights_from_dir, weight_dir)
-            elif weight_receiver is not None:
-                await asyncio.to_thread(weight_receiver.receive_into, engine)
+            elif engine.weight_receiver is not None:
+                await asyncio.to_thread(engine.receive_weights)
             else:
                 raise HTTPException(400, "weight_dir is null and no in-memory broadcaster was initialised")
         finally:
@@ -159,21 +161,9 @@ def build_app(engine: Engine, model_name: str, tokenizer=None, liveness_timeout:
 
     @app.post("/init_broadcaster")
     async def init_broadcaster(body: dict):
-        nonlocal weight_receiver
-        if body.get("type") == "p2p":
-            # the trainer writes into this process's parameter storage over NVLink peer memory
-            from ..transports.weights.p2p import P2PWeightPort
-
-            weight_receiver = await asyncio.to_thread(P2PWeightPort, engine.model, Path(body["run_dir"]),
-                                                      int(body.get("rank_offset", 0)), body.get("quantize"))
-            return {"status": "ok"}
-        from ..transports.weights.nccl import NCCLWeightReceiver
-
-        weight_receiver = NCCLWeightReceiver(host=body["host"], port=int(body["port"]),
-                                             rank=int(body.get("rank_offset", 0)) + 1,
-                                             world_size=int(body["inference_world_size"]) + 1,
-                                             timeout=int(body.get("timeout", 1200)))
-        await asyncio.to_thread(weight_receiver.connect)
+        # NCCL: the engine's GPUs join the trainer's broadcast group; p2p: they publish where their parameter
+        # storage can be written over NVLink peer memory. A tensor-parallel engine joins with every rank.
+        await asyncio.to_thread(engine.init_broadcaster, body)
         return {"status": "ok"}
 
     @app.post("/load_lora_adapter")

@@ -1,7 +1,9 @@
-"""Online evals: for every weight step a trainer publishes (``<watch_dir>/broadcasts/step_N``
-with its ``.finished`` marker) load the step into the inference server, run each eval source's
-examples ``group_size`` times, and append one row per (step, env) with mean reward and
-pass@k to ``<output_dir>/evals.jsonl`` and the monitors
+"""Evals process. Standalone (no ``[online]`` block): every eval source runs once against the weights the
+server serves. Online: for every weight step a trainer publishes (``<broadcasts_dir>/step_N`` with its
+``.finished`` marker) load the step into the inference server, run each eval source's examples
+``group_size`` times, and append one row per (step, env) with mean reward and pass@k to
+``<output_dir>/evals.jsonl`` and the monitors. A newer eligible broadcast cancels a running epoch when
+``eval.cancel_on_new_checkpoint`` is set
 (reference: src/prime_rl/evals/evals.py:1-605, evals/ckpt.py).
 """
 
@@ -22,8 +24,11 @@ FINISHED = ".finished"      # written by the trainer when a step's weights are c
 
 
 def published_steps(watch_dir: Path) -> list[int]:
-    """Steps whose weights are complete (marker file present), ascending."""
-    root = Path(watch_dir) / "broadcasts"
+    """Steps whose weights are complete (marker file present), ascending. ``watch_dir`` is a run directory
+    (its ``broadcasts`` folder is read) or the broadcasts folder itself."""
+    root = Path(watch_dir)
+    if (root / "broadcasts").exists() or root.name != "broadcasts":
+        root = root / "broadcasts"
     out = []
     if root.exists():
         for d in root.iterdir():
@@ -49,9 +54,11 @@ def _sampling(cfg, source):
                            max_completion_tokens=s.max_completion_tokens, extra_body=s.extra_body)
 
 
-async def evaluate_once(config, client, step: int, sem: asyncio.Semaphore) -> list[dict]:
+async def evaluate_once(config, client, step: int, sem: asyncio.Semaphore, skip=()) -> list[dict]:
     rows = []
     for source in config.eval.source:
+        if source.resolved_name in skip:
+            continue
         env = load_environment(source)
         sampling = _sampling(config.eval, source)
         n = source.num_examples if source.num_examples > 0 else (config.eval.num_examples if config.eval.num_examples > 0 else 64)
@@ -85,40 +92,70 @@ async def run_evals(config) -> list[dict]:
     out_dir = Path(config.output_dir)
     out_dir.mkdir(parents=True, exist_ok=True)
     monitor = setup_monitors(config.monitors, out_dir, producer="evals")
-    client = InferenceClient(config.client, config.model.name)
-    admin = AdminPlane(config.client)
-    sem = asyncio.Semaphore(config.max_concurrent)
+    ev = config.eval
+    client = InferenceClient(ev.client, config.model)
+    admin = AdminPlane(ev.client)
+    band = ev.concurrency
+    sem = asyncio.Semaphore(band.initial_inflight or band.max_inflight or 256)
+    online = config.online
     done: set[int] = set()
     all_rows: list[dict] = []
     results = out_dir / "evals.jsonl"
+    progress = out_dir / "evals_progress.json"
+    if config.resume is not None and progress.exists():            # standalone resume: skip finished sources
+        done_envs = set(json.loads(progress.read_text()).get("envs", []))
+    else:
+        done_envs = set()
 
-    async def run_step(step: int):
-        if config.update_weights and config.watch_dir is not None:
+    async def run_step(step: int, load: bool):
+        if load:
             await admin.pause()
             try:
-                await admin.update_weights(str(Path(config.watch_dir) / "broadcasts" / f"step_{step}"))
+                await admin.update_weights(str(Path(online.broadcasts_dir) / f"step_{step}"))
             finally:
                 await admin.resume()
-        rows = await evaluate_once(config, client, step, sem)
+        rows = await evaluate_once(config, client, step, sem, skip=done_envs)
         with open(results, "a") as f:
             for r in rows:
                 f.write(json.dumps(r) + "\n")
                 monitor.log({f"eval/{r['env']}/{k}": v for k, v in r.items() if isinstance(v, (int, float))}, step=step)
                 log.info(f"step {step} {r['env']}: reward {r['reward/mean']:.4f}")
+                if config.ckpt is not None:
+                    done_envs.add(r["env"])
+                    progress.write_text(json.dumps({"envs": sorted(done_envs)}))
         all_rows.extend(rows)
 
+    def eligible() -> list[int]:
+        first = (online.resume_step or -1)
+        steps = [s for s in published_steps(online.broadcasts_dir) if s not in done and s > first
+                 and s % ev.interval == 0]
+        if ev.skip_first_step:
+            steps = [s for s in steps if s != 0]
+        return steps
+
     try:
-        if config.watch_dir is None:
-            await run_step(0)
+        if online is None:
+            await run_step(0, load=False)
             return all_rows
+        if ev.retrigger_on_resume and online.resume_step is not None and online.resume_step % ev.interval == 0:
+            await run_step(online.resume_step, load=True)
         while True:
-            steps = [s for s in published_steps(config.watch_dir) if s not in done and s % config.eval.interval == 0]
-            for s in steps:
-                await run_step(s)
+            for s in eligible():
+                task = asyncio.create_task(run_step(s, load=True))
+                while not task.done():
+                    await asyncio.sleep(min(online.poll_interval, 0.5))
+                    if ev.cancel_on_new_checkpoint and any(n > s for n in eligible()):
+                        task.cancel()              # newer weights are waiting: this epoch is stale
+                        log.info(f"eval epoch of step {s} cancelled: a newer broadcast is ready")
+                        break
+                try:
+                    await task
+                except asyncio.CancelledError:
+                    pass
                 done.add(s)
-            if config.max_steps is not None and done and max(done) >= config.max_steps:
+            if online.max_steps is not None and done and max(done) >= online.max_steps:
                 return all_rows
-            await asyncio.sleep(config.poll_interval)
+            await asyncio.sleep(online.poll_interval)
     finally:
         await client.close()
         monitor.finalize()

@@ -52,10 +52,13 @@ class P2PWeightPort:
     (2-D weights land as e4m3 + 128 x 128 scales in buffers owned by the port, other tensors as
     they are; ``dequantize_into_model`` refreshes the live parameters from them)."""
 
-    def __init__(self, model, run_dir: Path | None, replica: int = 0, quantize: str | None = None):
+    def __init__(self, model, run_dir: Path | None, replica: int = 0, quantize: str | None = None,
+                 tp: tuple[int, int] | None = None):
         """``run_dir=None``: build the manifest only (``self.manifest``), write no file — for callers that
-        hand it to the sender through another channel."""
+        hand it to the sender through another channel. ``tp = (rank, size)``: this process holds one
+        tensor-parallel shard of the engine; the manifest says so and the sender slices what it pushes."""
         self.model, self.replica, self.quantize = model, replica, quantize
+        self.tp = tp
         self.run_dir = Path(run_dir) if run_dir is not None else None
         self.params = dict(model.named_parameters())
         dev = next(model.parameters()).device
@@ -95,7 +98,8 @@ class P2PWeightPort:
                 self.fp8[name] = (q, s_)
                 e["fp8"] = {"q": _export(q), "scales": _export(s_), "rows": N, "cols": K}
             entries[name] = e
-        self.manifest = {"device": dev.index or 0, "quantize": quantize, "params": entries}
+        self.manifest = {"device": dev.index or 0, "quantize": quantize, "params": entries,
+                         "tp": list(tp) if tp is not None else None}
         if self.run_dir is not None:
             path = manifest_path(self.run_dir, replica)
             path.parent.mkdir(parents=True, exist_ok=True)
@@ -247,7 +251,15 @@ class P2PWeightSender(WeightSender):
                         pushed += push_state(dense, man, self.mapped)
         else:
             for replica in range(self.world.rank, self.num_replicas, max(1, self.world.world_size)):
-                pushed += push_state(tensors, self._manifest(replica), self.mapped)
+                man = self._manifest(replica)
+                src = tensors
+                if man.get("tp"):
+                    # the target process holds one tensor-parallel shard: send it its slices
+                    from ...engine.tp import shard_tensor
+
+                    r, size = man["tp"]
+                    src = {n: shard_tensor(n, t.detach(), model.arch, r, size) for n, t in tensors.items()}
+                pushed += push_state(src, man, self.mapped)
         torch.cuda.synchronize()
         if pushed:
             dt = time.monotonic() - t0
