@@ -7,16 +7,24 @@ batch ``step`` is shipped only once the engines run policy version >= ``step - 1
 TARGET_LAG``; rollouts generated more than ``max_off_policy_steps`` versions ago are dropped.
 
 Parts:
-  Dispatcher     keeps up to the controller's limit of episodes in flight, one group per task
-  TrainSink      groups -> advantages -> samples -> pending batch (stale / zero-advantage pruning)
+  Dispatcher     keeps up to the controller's limit of episodes in flight, one group per task; train and
+                 eval work share it (PREFER_TRAIN / PREFER_EVAL), admissions are rate-limited per burst
+                 window, scheduling stops while a weight update is pending and train groups that could
+                 never ship inside ``max_off_policy_steps`` are cancelled before the engines pause
+  TrainSink      groups -> advantages -> samples -> pending batch (stale / zero-advantage pruning); aborts
+                 after 10 batch-equivalents of finalized rollouts that admitted nothing
+  EvalSink       (eval_sink.py) eval episodes -> per (env, step) epochs -> eval metrics
   WeightWatcher  polls ``broadcasts/`` for offered versions and runs the receiver handshake
-  Orchestrator   main loop, metrics, checkpoints
+  Orchestrator   main loop, eval triggering, engine metrics, event-loop lag, checkpoints
 """
 
 from __future__ import annotations
 
 import asyncio
+import enum
+import os
 import random
+import threading
 import time
 import uuid
 from collections import defaultdict
@@ -36,10 +44,36 @@ from .algo import setup_algorithm
 from .clients import AdminPlane, InferenceClient
 from .concurrency import ConcurrencyController
 from .envs import load_environment
+from .eval_sink import EvalSink, EvalWork
+from .inference_metrics import InferenceMetrics
 from .types import Policy, Rollout
 
 TARGET_LAG = 1
 MAX_EMPTY_BATCHES = 10
+MAX_ZERO_OUTPUT_BATCH_EQUIVALENTS = 10      # finalized rollouts worth this many batches without any admitted payload
+TEARDOWN_TIMEOUT_S = 300.0                  # a shutdown that hangs longer than this ends the process
+
+
+def min_fresh_version(step: int, max_off_policy_steps: int) -> int:
+    """Oldest dispatch version whose episodes can still train in batch ``step`` (which trains on policy
+    ``step - 1``); anything older would ship beyond ``max_off_policy_steps``."""
+    return (step - 1) - max_off_policy_steps
+
+
+class DispatcherMode(enum.Enum):
+    PREFER_TRAIN = "train"
+    PREFER_EVAL = "eval"
+
+
+@dataclass
+class GroupMeta:
+    kind: str                       # "train" | "eval"
+    env_name: str
+    policy_version_at_start: int
+    live: bool                      # sampled from the live policy (frozen-sourced groups never go stale)
+    size: int
+    eval_step: int = -1
+    tasks: list = field(default_factory=list)
 
 
 @dataclass
@@ -55,21 +89,62 @@ class Source:
 
 
 class Dispatcher:
-    """Fills the in-flight budget with group episodes; finished rollouts go to ``out_q``."""
+    """Fills the in-flight budget with group episodes; finished rollouts go to ``out_q`` as ``Rollout``
+    objects, lost ones as ``("cancel" | "fail", group_id, kind, env_name, eval_step, detail)`` tuples.
+
+    Scheduling rules (reference: src/prime_rl/orchestrator/dispatcher.py:276-283 burst budget, :363-401
+    pending weight update, :407-440 modes):
+      * at most ``max(min_burst, max_inflight // 10)`` group admissions per ``admission_window_s``;
+      * ``PREFER_EVAL`` while eval work is queued (evals ignore the train dispatch gate), back to
+        ``PREFER_TRAIN`` once the eval queue drained;
+      * nothing is scheduled between ``on_version_pending`` and ``on_new_version``.
+    """
 
     def __init__(self, sources: list[Source], client: InferenceClient, policy: Policy,
-                 controller: ConcurrencyController, seed: int = 0, tasks_per_minute: int | None = None):
+                 controller: ConcurrencyController, seed: int = 0, tasks_per_minute: int | None = None,
+                 max_off_policy_steps: int = 8, min_burst: int = 4, admission_window_s: float = 1.0):
         self.sources, self.client, self.policy, self.controller = sources, client, policy, controller
         self.out_q: asyncio.Queue = asyncio.Queue()
         self.inflight: dict[asyncio.Task, str] = {}
+        self.groups: dict[str, GroupMeta] = {}
         self.rng = random.Random(seed)
         self.paused = asyncio.Event()
         self.paused.set()
+        self.dispatch_allowed = asyncio.Event()          # the orchestrator's gate on *train* scheduling
+        self.dispatch_allowed.set()
+        self.scheduling_lock = asyncio.Lock()
         self.stopped = False
-        self.min_fresh_version = 0
+        self.mode = DispatcherMode.PREFER_TRAIN
+        self.eval_queue: list[EvalWork] = []
+        self.policy_update_pending = False
+        self.max_off_policy_steps = max_off_policy_steps
+        self.progress_step = 0                           # batch the orchestrator is collecting (set by its loop)
         self.tasks_per_minute = tasks_per_minute
+        self.min_burst, self.admission_window_s = min_burst, admission_window_s
+        self._window_start, self._admissions = time.monotonic(), 0
         self._last_launch = 0.0
         self.stats = defaultdict(int)
+
+    # ------------------------------------------------------------------ admission
+    def admission_budget(self) -> int:
+        """Group admissions still allowed in the current burst window."""
+        now = time.monotonic()
+        if now - self._window_start >= self.admission_window_s:
+            self._window_start, self._admissions = now, 0
+        cap = max(self.min_burst, (self.controller.max or self.controller.limit) // 10)
+        return cap - self._admissions
+
+    def switch_mode(self, mode: DispatcherMode, reason: str = "") -> None:
+        if mode != self.mode:
+            self.mode = mode
+            self.stats[f"mode_switches_to_{mode.value}"] += 1
+            get_logger().info(f"dispatcher prefers {mode.value} work now ({reason})")
+
+    def request_eval(self, work: list[EvalWork]) -> None:
+        """Queues eval examples and gives them priority over train scheduling until they are dispatched."""
+        self.eval_queue.extend(work)
+        if self.eval_queue:
+            self.switch_mode(DispatcherMode.PREFER_EVAL, "an eval was triggered")
 
     def _pick(self) -> Source:
         total = sum(s.ratio for s in self.sources)
@@ -80,25 +155,47 @@ class Dispatcher:
                 return s
         return self.sources[-1]
 
-    async def _episode(self, src: Source, task_id: int, group_id: str) -> None:
+    async def _episode(self, src: Source, task_id: int, group_id: str, kind: str, eval_step: int) -> None:
         version = self.policy.version
         try:
             r: Rollout = await src.env.rollout(self.client, task_id, src.sampling, version, group_id)
-            await src.algo.finalize_episode(r)
-            r.info["_source"] = src
+            if kind == "train":
+                await src.algo.finalize_episode(r)
+            r.info["_source"], r.info["_kind"], r.info["_eval_step"] = src, kind, eval_step
             await self.out_q.put(r)
             self.stats["episodes_ok"] += 1
         except asyncio.CancelledError:
             self.stats["episodes_cancelled"] += 1
-            await self.out_q.put(("cancel", group_id))
+            await self.out_q.put(("cancel", group_id, kind, src.env.name, eval_step, ""))
             raise
         except Exception as e:
             self.stats["episodes_failed"] += 1
-            await self.out_q.put(("fail", group_id, repr(e)))
+            await self.out_q.put(("fail", group_id, kind, src.env.name, eval_step, repr(e)))
         finally:
             self.controller.on_episode_done()
 
-    def _launch_group(self) -> None:
+    def _launch(self, src: Source, task_id: int, kind: str, eval_step: int = -1) -> None:
+        gid = uuid.uuid4().hex
+        live = getattr(getattr(src.algo, "config", None), "sampling", None) is None or \
+            getattr(src.algo.config.sampling, "source", "policy") == "policy"
+        meta = GroupMeta(kind, getattr(src.env, "name", "env"), self.policy.version, live, src.group_size, eval_step)
+        self.groups[gid] = meta
+        for _ in range(src.group_size):
+            t = asyncio.create_task(self._episode(src, task_id, gid, kind, eval_step))
+            self.inflight[t] = gid
+            meta.tasks.append(t)
+            t.add_done_callback(self._on_task_done)
+        self._admissions += 1
+        self.stats[f"{kind}_groups_launched"] += 1
+        self.stats["groups_launched"] += 1
+
+    def _on_task_done(self, t: asyncio.Task) -> None:
+        gid = self.inflight.pop(t, None)
+        meta = self.groups.get(gid)
+        if meta is not None and all(x.done() for x in meta.tasks):
+            self.groups.pop(gid, None)
+
+    def _launch_train_group(self) -> None:
         src = self._pick()
         if src.sampler is not None:
             task_id = src.sampler.sample()
@@ -106,28 +203,79 @@ class Dispatcher:
         else:
             task_id = src.next_task % max(1, getattr(src.env, "num_tasks", 1 << 30))
             src.next_task += 1
-        gid = uuid.uuid4().hex
-        for _ in range(src.group_size):
-            t = asyncio.create_task(self._episode(src, task_id, gid))
-            self.inflight[t] = gid
-            t.add_done_callback(lambda t: self.inflight.pop(t, None))
-        self.stats["groups_launched"] += 1
+        self._launch(src, task_id, "train")
+
+    async def fill_inflight(self) -> bool:
+        """Schedules at most one group; returns whether it did."""
+        if self.policy_update_pending or self.admission_budget() <= 0:
+            return False
+        async with self.scheduling_lock:
+            if self.policy_update_pending:
+                return False
+            room = self.controller.limit - len(self.inflight)
+            if self.mode == DispatcherMode.PREFER_EVAL:
+                if not self.eval_queue:
+                    self.switch_mode(DispatcherMode.PREFER_TRAIN, "the eval queue drained")
+                    return False
+                work = self.eval_queue[0]
+                if room < work.source.group_size:
+                    return False
+                self.eval_queue.pop(0)
+                self._launch(work.source, work.task_id, "eval", work.step)
+                return True
+            if not self.dispatch_allowed.is_set() or not self.sources:
+                return False
+            if room < min(s.group_size for s in self.sources):
+                return False
+            if self.tasks_per_minute:
+                wait = 60.0 / self.tasks_per_minute - (time.monotonic() - self._last_launch)
+                if wait > 0:
+                    await asyncio.sleep(wait)
+            self._launch_train_group()
+            self._last_launch = time.monotonic()
+            return True
 
     async def run(self) -> None:
         while not self.stopped:
             await self.paused.wait()
-            room = self.controller.limit - len(self.inflight)
-            gs = min(s.group_size for s in self.sources)
-            if room >= gs:
-                if self.tasks_per_minute:
-                    wait = 60.0 / self.tasks_per_minute - (time.monotonic() - self._last_launch)
-                    if wait > 0:
-                        await asyncio.sleep(wait)
-                self._launch_group()
-                self._last_launch = time.monotonic()
+            if await self.fill_inflight():
                 await asyncio.sleep(0)
             else:
                 await asyncio.sleep(0.005)
+
+    # ------------------------------------------------------------------ weight updates
+    async def drop_group(self, gid: str, reason: str) -> int:
+        meta = self.groups.get(gid)
+        if meta is None:
+            return 0
+        n = 0
+        for t in meta.tasks:
+            if not t.done():
+                t.cancel()
+                n += 1
+        self.stats[f"groups_dropped_{reason}"] += 1
+        return n
+
+    async def on_version_pending(self, step: int) -> int:
+        """A weight update is about to be applied: stop scheduling, and cancel live-policy train groups that
+        started before ``min_fresh_version`` of the batch being collected (they could only ship beyond
+        ``max_off_policy_steps``). Runs before the engines are paused, so the aborts are processed while the
+        engines still step. Returns the number of cancelled episodes."""
+        self.policy_update_pending = True
+        async with self.scheduling_lock:        # a scheduling pass that began before the flag finishes first
+            pass
+        oldest = min_fresh_version(self.progress_step, self.max_off_policy_steps)
+        cancelled = 0
+        for gid, meta in list(self.groups.items()):
+            if meta.kind == "train" and meta.live and meta.policy_version_at_start < oldest:
+                cancelled += await self.drop_group(gid, "stale")
+        if cancelled:
+            get_logger().warning(f"cancelled {cancelled} train episodes past max_off_policy_steps="
+                                 f"{self.max_off_policy_steps}; consider raising it")
+        return cancelled
+
+    async def on_new_version(self, step: int) -> None:
+        self.policy_update_pending = False
 
     def cancel_newest(self, n: int) -> None:
         for t in list(self.inflight)[-n:]:
@@ -150,11 +298,37 @@ class TrainSink:
         self.dead_groups: set[str] = set()
         self.pending: list[tuple[Rollout, list]] = []     # (rollout, samples)
         self.stats = defaultdict(float)
-        self.zero_output_batches = 0
+        self.zero_output_units = 0            # finalized rollouts (or tokens) since the last admitted payload
+        self._reported_windows = 0
 
     def cancel(self, group_id: str) -> None:
-        self.groups.pop(group_id, None)
+        lost = self.groups.pop(group_id, None)
+        if group_id not in self.dead_groups:
+            self._record_zero_output(lost or [], owed=1)
         self.dead_groups.add(group_id)
+
+    def _record_zero_output(self, group: list, owed: int) -> None:
+        """A group ended without contributing anything trainable. After MAX_ZERO_OUTPUT_BATCH_EQUIVALENTS
+        batches' worth of such rollouts in a row the run is aborted: the curriculum gates, the task difficulty
+        or staleness drops are eating everything (reference: src/prime_rl/orchestrator/train_sink.py:334-363)."""
+        c = self.config
+        if c.batch_size is not None:
+            self.zero_output_units += len(group) or owed
+            target = c.batch_size
+        else:
+            self.zero_output_units += sum(r.num_total_tokens for r in group) or c.seq_len * owed
+            target = c.token_batch_size
+        windows = self.zero_output_units // max(1, target)
+        if windows > self._reported_windows:
+            self._reported_windows = windows
+            get_logger().warning(f"no admitted train payload after {self.zero_output_units} finalized units "
+                                 f"({windows}/{MAX_ZERO_OUTPUT_BATCH_EQUIVALENTS} batch equivalents)")
+            if windows >= MAX_ZERO_OUTPUT_BATCH_EQUIVALENTS:
+                raise RuntimeError(f"{windows} consecutive zero-output batch equivalents: check the curriculum "
+                                   "admission policy, task difficulty and staleness drops")
+
+    def _admitted(self) -> None:
+        self.zero_output_units, self._reported_windows = 0, 0
 
     async def add(self, r: Rollout) -> None:
         if r.group_id in self.dead_groups:
@@ -170,6 +344,7 @@ class TrainSink:
         oldest = min(r.policy_version for r in group)
         if self.policy.version - oldest > self.config.max_off_policy_steps:
             self.stats["groups_dropped_stale"] += 1
+            self._record_zero_output(group, owed=len(group))
             return
         await src.algo.score_group(group)
         if src.sampler is not None:
@@ -178,8 +353,10 @@ class TrainSink:
         for gate in src.gates:
             if all(gate.reject_min <= a <= gate.reject_max for a in advs):
                 self.stats["groups_rejected_by_gate"] += 1
+                self._record_zero_output(group, owed=len(group))
                 return
         self.stats["groups_scored"] += 1
+        before = len(self.pending)
         for r in group:
             self.stats["reward_sum"] += r.reward
             self.stats["reward_n"] += 1
@@ -188,6 +365,10 @@ class TrainSink:
                 self.stats["rollouts_pruned_zero_adv"] += 1
                 continue     # contributes no gradient
             self.pending.append((r, src.algo.to_samples(r)))
+        if len(self.pending) > before:
+            self._admitted()
+        # a group whose rollouts all tied (zero advantage) was scored fine and only carries no signal: that case
+        # is bounded by the empty-batch counter of the main loop, not by the zero-output budget
 
     def sweep_stale(self) -> None:
         keep = []
@@ -237,7 +418,13 @@ class WeightWatcher:
         if step is None:
             return False
         t0 = time.monotonic()
-        await self.receiver.receive(step)
+        # stale work is cut while the engines still step (their aborts need a running engine), and no new
+        # rollout may start until the new weights are live
+        self.stats["episodes_cancelled_stale"] += await self.dispatcher.on_version_pending(step)
+        try:
+            await self.receiver.receive(step)
+        finally:
+            await self.dispatcher.on_new_version(step)
         self.last_step = step
         self.policy.version = step + 1
         self.stats["updates"] += 1
@@ -283,8 +470,26 @@ class Orchestrator:
         await self.admin.wait_for_ready()
         self.controller = ConcurrencyController(c.concurrency, c.group_size)
         self.dispatcher = Dispatcher(self.sources, self.client, self.policy, self.controller, seed=c.seed,
-                                     tasks_per_minute=c.tasks_per_minute)
+                                     tasks_per_minute=c.tasks_per_minute, max_off_policy_steps=c.max_off_policy_steps)
         self.sink = TrainSink(c, self.policy)
+        # online evals: version-pinned measurements that share the dispatcher with training rollouts
+        self.eval_sources: list[tuple[object, Source]] = []
+        self.eval_sink = EvalSink()
+        self._evaluated_versions: set[int] = set()
+        if c.eval is not None:
+            for es in c.eval.source:
+                sampling = es.sampling if (es.sampling.temperature is not None or es.sampling.max_completion_tokens
+                                           or es.sampling.top_p is not None) else c.eval.sampling
+                from types import SimpleNamespace
+
+                sp = SimpleNamespace(temperature=sampling.temperature if sampling.temperature is not None else 0.0,
+                                     top_p=sampling.top_p if sampling.top_p is not None else 1.0, top_k=sampling.top_k,
+                                     max_completion_tokens=sampling.max_completion_tokens,
+                                     extra_body=sampling.extra_body)
+                src = Source(load_environment(es), None, max(es.group_size, c.eval.group_size), sp, 1.0)
+                self.eval_sources.append((es, src))
+        self.inference_metrics = InferenceMetrics(c.inference_metrics_roles)
+        self.loop_lag = {"max": 0.0, "sum": 0.0, "n": 0}
         wb = c.weight_broadcast
         if wb.type == "p2p":
             # every engine publishes the IPC handles of its parameter storage under the run directory
@@ -383,6 +588,7 @@ class Orchestrator:
                                        "(set collect_inference_metrics = false to run without it)") from e
                 continue
             failures = 0
+            self.inference_metrics.ingest(ms)
             usage = max((m.get("vllm:kv_cache_usage_perc", 0.0) for m in ms), default=0.0)
             waiting = sum(m.get("vllm:num_requests_waiting", 0.0) for m in ms)
             pre = sum(m.get("vllm:num_preemptions_total", 0.0) for m in ms)
@@ -390,9 +596,68 @@ class Orchestrator:
             if d.cancel:
                 self.dispatcher.cancel_newest(d.cancel)
 
+    async def _lag_loop(self, interval: float = 0.25) -> None:
+        """Event-loop lag: how late a short sleep wakes up. Long tails mean a coroutine is hogging the loop
+        (tokenisation, packing or scoring that should run in a thread) and every request deadline slips
+        with it (reference: src/prime_rl/orchestrator/orchestrator.py:394-412)."""
+        while True:
+            t0 = time.monotonic()
+            await asyncio.sleep(interval)
+            lag = max(0.0, time.monotonic() - t0 - interval)
+            ll = self.loop_lag
+            ll["max"], ll["sum"], ll["n"] = max(ll["max"], lag), ll["sum"] + lag, ll["n"] + 1
+            if lag > 1.0:
+                self.logger.warning(f"event loop was blocked for {lag:.2f}s")
+
+    def _maybe_trigger_eval(self) -> None:
+        """Queues one eval epoch per source when the live policy reached a version that is due."""
+        ev = self.config.eval
+        if ev is None or not self.eval_sources:
+            return
+        v = self.policy.version
+        if v in self._evaluated_versions:
+            return
+        self._evaluated_versions.add(v)
+        if v == 0 and ev.skip_first_step:
+            return
+        work = []
+        for es, src in self.eval_sources:
+            interval = es.interval if "interval" in es.model_fields_set else ev.interval
+            if v % interval:
+                continue
+            n = es.num_examples if es.num_examples > 0 else ev.num_examples
+            n = min(n if n > 0 else 64, getattr(src.env, "num_tasks", 1 << 30))
+            self.eval_sink.expect(src.env.name, v, n, src.group_size)
+            work.extend(EvalWork(src, t, v) for t in range(n))
+        if work:
+            for row in self.eval_sink.abandon(v):           # an older epoch still collecting is superseded
+                self._log_eval(row)
+            self.dispatcher.request_eval(work)
+
+    def _log_eval(self, row: dict) -> None:
+        env, step = row["env"], row["step"]
+        self.monitor.log({f"eval/{env}/{k}": v for k, v in row.items() if isinstance(v, (int, float)) and k != "step"},
+                         step)
+        self.logger.info(f"eval {env} @ policy v{step}: reward {row['reward/mean']:.4f} over {row['rollouts']} rollouts"
+                         f" ({row['failed']} failed, {row['cancelled']} cancelled)")
+        self.eval_rows.append(row)
+
+    def _handle_lost(self, item: tuple) -> None:
+        what, gid, kind, env_name, eval_step, detail = item
+        if kind == "eval":
+            row = self.eval_sink.fail(env_name, eval_step) if what == "fail" else self.eval_sink.cancel(env_name, eval_step)
+            if row is not None:
+                self._log_eval(row)
+        else:
+            self.sink.cancel(gid)
+        if what == "fail":
+            self.logger.warning(f"{kind} episode failed: {detail}")
+
     async def run(self) -> None:
         c = self.config
-        tasks = [asyncio.create_task(self.dispatcher.run()), asyncio.create_task(self.watcher.run())]
+        self.eval_rows: list[dict] = []
+        tasks = [asyncio.create_task(self.dispatcher.run()), asyncio.create_task(self.watcher.run()),
+                 asyncio.create_task(self._lag_loop())]
         if c.collect_inference_metrics:
             tasks.append(asyncio.create_task(self._metrics_loop()))
         empty = 0
@@ -401,14 +666,19 @@ class Orchestrator:
                 for t in tasks:
                     if t.done() and t.exception() is not None:
                         raise t.exception()
+                self.dispatcher.progress_step = self.step
+                self._maybe_trigger_eval()
                 try:
                     item = await asyncio.wait_for(self.dispatcher.out_q.get(), timeout=1.0)
                 except asyncio.TimeoutError:
                     continue
                 if isinstance(item, tuple):
-                    self.sink.cancel(item[1])
-                    if item[0] == "fail":
-                        self.logger.warning(f"episode failed: {item[2]}")
+                    self._handle_lost(item)
+                    continue
+                if item.info.get("_kind") == "eval":
+                    row = self.eval_sink.add(item, item.info["_eval_step"])
+                    if row is not None:
+                        self._log_eval(row)
                     continue
                 await self.sink.add(item)
                 batch = self.sink.maybe_batch()
@@ -421,6 +691,10 @@ class Orchestrator:
                     continue
                 empty = 0
                 m = await self._ship(batch)
+                m.update(self.inference_metrics.snapshot())
+                ll = self.loop_lag
+                m.update({"event_loop_lag/max": ll["max"], "event_loop_lag/mean": ll["sum"] / max(1, ll["n"])})
+                ll.update(max=0.0, sum=0.0, n=0)
                 self.monitor.log(m, self.step)
                 self.logger.info(f"step {self.step} | reward {m['reward']:.3f} | rollouts {m['batch/rollouts']} | "
                                  f"policy v{self.policy.version} | lag {m['off_policy/mean']:.2f}")
@@ -428,15 +702,23 @@ class Orchestrator:
                     self.save_ckpt(self.step)
                 self.step += 1
         finally:
-            self.watcher.stopped = True
-            await self.dispatcher.stop()
-            for t in tasks:
-                t.cancel()
-            await asyncio.gather(*tasks, return_exceptions=True)
-            self.sender.close()
-            await self.client.close()
-            await self.admin.close()
-            self.monitor.finalize()
+            # a teardown that hangs (an engine that never answers the aborts, a stuck transport) must not keep
+            # the launcher waiting forever: after TEARDOWN_TIMEOUT_S the process ends itself
+            watchdog = threading.Timer(TEARDOWN_TIMEOUT_S, lambda: os._exit(1))
+            watchdog.daemon = True
+            watchdog.start()
+            try:
+                self.watcher.stopped = True
+                await self.dispatcher.stop()
+                for t in tasks:
+                    t.cancel()
+                await asyncio.gather(*tasks, return_exceptions=True)
+                self.sender.close()
+                await self.client.close()
+                await self.admin.close()
+                self.monitor.finalize()
+            finally:
+                watchdog.cancel()
 
 
 def trace_record(r, step: int) -> dict:
