@@ -147,9 +147,9 @@ def run_rollout_bench(model: str = "qwen3-30b-a3b", contexts=(1024, 3072, 5120),
                  weight_dtype="fp8" if fp8 else "bf16", tp=tp, keep_bf16_weights=not fp8)
     leader = tp is None or tp.rank == 0
     points = []
-    if not leader:
-        eng.follow()
-    else:
+    failure = None
+
+    def drive():
         g = torch.Generator().manual_seed(1234 + rank)
         for C in contexts:
             params = SamplingParams(temperature=1.0, max_tokens=decode_budget(C))
@@ -197,19 +197,31 @@ def run_rollout_bench(model: str = "qwen3-30b-a3b", contexts=(1024, 3072, 5120),
         from ..ops import _runtime as rt
 
         rt.check_status()
-        if tp is not None:
-            eng.shutdown()
+
+    if not leader:
+        eng.follow()
+    else:
+        try:
+            drive()
+        except Exception as e:      # the other ranks of the group wait in follow(): release them whatever happened
+            failure = f"{type(e).__name__}: {e}"[:300]
+        finally:
+            if tp is not None:
+                eng.shutdown()
     # ---------------------------------------------------------------- one weight update, quantised in flight
     push = _timed_weight_push(eng, dev, world, rank) if fp8 else None
     # ---------------------------------------------------------------- merge over the groups
     mem = torch.cuda.max_memory_allocated(dev) / 2 ** 30
-    local = {"points": points, "push": push, "mem": mem, "leader": leader}
+    local = {"points": points, "push": push, "mem": mem, "leader": leader, "failure": failure}
     gathered = [local]
     if world > 1:
         gathered = [None] * world
         dist.all_gather_object(gathered, local)
     if tp is not None:
         tp.close()
+    failures = [x["failure"] for x in gathered if x.get("failure")]
+    if failures:
+        raise RuntimeError(f"rollout benchmark failed on {len(failures)} engine group(s): {failures[0]}")
     if rank != 0:
         return None
     leaders = [x for x in gathered if x["leader"]]

@@ -27,6 +27,7 @@ from ..data import DataLoader, FakeDataLoader, TensorMicroBatch
 from ..loss import compute_loss, setup_rl_loss_fn, shift_left, shift_right
 from ..optim import setup_optimizer
 from ..perf import PerfCounter
+from ..stats import TensorStats
 
 
 class RLTrainer:
@@ -113,6 +114,8 @@ class RLTrainer:
                                                      lora=mc.lora is not None, lora_cfg=mc.lora)
         dev_name = torch.cuda.get_device_name(self.device) if self.device.type == "cuda" else "cpu"
         self.perf = PerfCounter(self.arch, mc.seq_len, self.world.world_size, dev_name, lora=mc.lora is not None)
+        # distribution statistics over the loss tokens of all ranks (mean / median / std / min / max)
+        self.token_stats = TensorStats(self.dp_cp_group)
         n_train = sum(p.numel() for p in self.model.parameters() if p.requires_grad)
         n_all = sum(p.numel() for p in self.model.parameters())
         self.logger.info(f"model {self.arch.model_type}: {n_all / 1e9:.2f}B params ({n_train / 1e6:.1f}M trainable), "
@@ -231,6 +234,13 @@ class RLTrainer:
             ref_kl_weights=mb.ref_kl_weights, sequence_lengths=mb.sequence_lengths)
         loss.backward()
         mask = mb.loss_mask
+        with torch.no_grad():
+            # context-parallel ranks of one replica hold the same rows after the gather: only the first contributes
+            own = mask if self.cp_rank == 0 else torch.zeros_like(mask)
+            log_ratio = logprobs.detach() - mb.inference_logprobs
+            self.token_stats.add("entropy", entropy, own)
+            self.token_stats.add("mismatch_kl", torch.exp(log_ratio) - log_ratio - 1, own)
+            self.token_stats.add("log_importance_ratio", log_ratio, own)
         out = {"loss": loss.detach(), "entropy": (entropy * mask).sum() / mask.sum().clamp_min(1)}
         out.update({k: v.detach() for k, v in lm.items()})
         return out
@@ -279,6 +289,7 @@ class RLTrainer:
         self.optimizer.zero_grad()
         metrics = {k: torch.stack(v).sum() if k == "loss" else torch.stack(v).mean() for k, v in agg.items()}
         metrics["optim/grad_norm"] = grad_norm.reshape(())
+        metrics.update({f"tokens/{k}": v for k, v in self.token_stats.compute().items()})
         metrics.update({f"moe/{k}": v for k, v in self.model.load_balance_stats().items()})
         # one device->host read for the whole step
         keys = list(metrics)

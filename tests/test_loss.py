@@ -1,5 +1,7 @@
 import math
 
+import pytest
+
 import torch
 
 from prime_rl_b200.configs.trainer import IcePopLossConfig, IPOLossConfig
@@ -125,3 +127,26 @@ def test_softcapped_head_matches_direct_formula():
     g1, = torch.autograd.grad(lp.sum(), h, retain_graph=True)
     g2, = torch.autograd.grad(want.sum(), h)
     assert torch.allclose(g1, g2, atol=1e-5)
+
+
+def test_token_statistics_match_torch_on_the_concatenated_values():
+    """mean / median / std / min / max from sufficient statistics and histogram bisection equal the direct
+    computation on all values (single process; the multi-rank reduction is covered by the gloo tests)."""
+    from prime_rl_b200.trainer.stats import TensorStats
+
+    g = torch.Generator().manual_seed(3)
+    for n in (1, 2, 7, 4097, 20000):
+        x = torch.randn(n, generator=g) * 5 - 2
+        x[::3] = x[0]                                      # ties
+        st = TensorStats()
+        st.add("x", x[: n // 2])
+        st.add("x", x[n // 2:], mask=torch.ones(n - n // 2, dtype=torch.bool))
+        st.add("none", torch.empty(0))
+        out = st.compute()
+        assert out["x/median"].item() == x.median().item()
+        assert out["x/min"].item() == x.min().item() and out["x/max"].item() == x.max().item()
+        assert out["x/mean"].item() == pytest.approx(x.mean().item(), rel=1e-5, abs=1e-6)
+        if n > 1:
+            assert out["x/std"].item() == pytest.approx(x.std().item(), rel=1e-4)
+        assert out["none/mean"].item() != out["none/mean"].item()      # NaN for an empty key
+    assert st.values == {}
