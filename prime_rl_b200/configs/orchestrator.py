@@ -278,6 +278,11 @@ class OrchestratorConfig(BaseConfig):
     max_off_policy_steps: int = Field(8, ge=0)
     heartbeat: HeartbeatConfig | None = None
     enable_return_routed_experts: bool = False
+    # The built-in token-level environments run inside the orchestrator process. With this switch (or a
+    # source's ``serve.spawn = true``) the ``rl`` launcher starts one env-server process per train / eval source
+    # at ``http://127.0.0.1:<env_server_base_port + index>`` and the orchestrator talks to it over HTTP, which
+    # is how heavy or sandboxed environments are kept off the orchestrator's event loop.
+    spawn_env_servers: bool = False
     seed: int = 0
     dry_run: bool = False
 
@@ -294,6 +299,25 @@ class OrchestratorConfig(BaseConfig):
         if self.train.sampling.truncated and self.train.sampling.top_k and self.train.sampling.top_k > TRAIN_TOP_K_BOUND:
             raise ValueError(f"top_k must be <= {TRAIN_TOP_K_BOUND}")
         return self
+
+    @property
+    def env_addresses(self) -> dict[tuple[str, str], str]:
+        """(kind, source name) -> address of the source's env server: its explicit ``serve.address`` (an
+        externally managed server) or the port derived from ``env_server_base_port`` and the source's index,
+        train sources first (reference: configs/orchestrator.py ``env_addresses``)."""
+        out: dict[tuple[str, str], str] = {}
+        sources = [("train", s) for s in self.train.source] + [("eval", s) for s in (self.eval.source if self.eval else [])]
+        for index, (kind, s) in enumerate(sources):
+            out[(kind, s.resolved_name)] = s.serve.address or f"http://127.0.0.1:{self.env_server_base_port + index}"
+        return out
+
+    def spawned_sources(self) -> list[tuple[str, object, str]]:
+        """(kind, source, address) of every source the launcher has to start an env server for."""
+        addrs = self.env_addresses
+        sources = [("train", s) for s in self.train.source] + [("eval", s) for s in (self.eval.source if self.eval else [])]
+        return [(kind, s, addrs[(kind, s.resolved_name)]) for kind, s in sources
+                if s.serve.address is None and (self.spawn_env_servers or getattr(s.serve, "spawn", False))
+                and s.id != "remote"]
 
     def source_group_size(self, src: TrainSourceConfig) -> int:
         return src.group_size or self.group_size

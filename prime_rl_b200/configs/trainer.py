@@ -199,6 +199,11 @@ class ModelConfig(BaseModelConfig):
     # "p2p": the sharded optimizer's gradient reduce-scatter (with cast / scale) and parameter all-gather run as
     # peer-memory kernels over NVLink instead of NCCL collectives (one NVSwitch box, at most 8 ranks per shard group)
     optim_collectives: Literal["nccl", "p2p"] = "nccl"
+    # 2: bf16 parameters replicated, optimizer state (fp32 master, moments) and the gradient reduction partitioned
+    # over the sharding ranks: one reduce-scatter and one all-gather per step. 3: parameters partitioned too (FSDP):
+    # each decoder layer is all-gathered right before it runs (prefetched one layer ahead), re-gathered for its
+    # recomputation in the backward pass, and its gradients are reduce-scattered as soon as they are complete.
+    zero_stage: Literal[2, 3] = 2
     impl: Literal["hf", "custom", "auto"] = "auto"
     optimization_dtype: Literal["bfloat16", "float32"] = "float32"
     reduce_dtype: Literal["bfloat16", "float32"] = "float32"

@@ -33,6 +33,46 @@ def write_subconfigs(config: RLConfig, cfg_dir: Path) -> dict[str, Path]:
     return paths
 
 
+def prepare_env_servers(config: RLConfig, cfg_dir: Path) -> list[tuple[str, Path, str]]:
+    """One ``envs/<kind>-<name>.json`` (an ``EnvServerConfig``) per source that gets a server of its own; the
+    orchestrator's source is re-pointed at the server's address. Returns (label, config file, address)."""
+    from urllib.parse import urlparse
+
+    out = []
+    env_dir = cfg_dir / "envs"
+    for kind, src, addr in config.orchestrator.spawned_sources():
+        env_dir.mkdir(parents=True, exist_ok=True)
+        u = urlparse(addr)
+        spec = {"env": {"id": src.id, "import_path": src.import_path, "args": src.args, "name": src.resolved_name},
+                "serve": {"host": u.hostname or "127.0.0.1", "port": u.port or 80},
+                "log": {"level": config.log.level} if config.log.level else {}}
+        path = env_dir / f"{kind}-{src.resolved_name}.json"
+        import json
+
+        path.write_text(json.dumps(spec, indent=2))
+        src.name = src.resolved_name
+        src.id, src.import_path, src.args = "remote", None, {"base_url": addr}
+        out.append((f"env-{kind}-{src.name}", path, addr))
+    return out
+
+
+def wait_for_http(url: str, timeout: float = 120.0) -> None:
+    import time
+    import urllib.request
+
+    t0 = time.monotonic()
+    while True:
+        try:
+            with urllib.request.urlopen(url, timeout=2.0) as r:
+                if r.status == 200:
+                    return
+        except OSError:
+            pass
+        if time.monotonic() - t0 > timeout:
+            raise TimeoutError(f"{url} did not answer within {timeout}s")
+        time.sleep(0.2)
+
+
 def gpu_split(config: RLConfig) -> tuple[list[int], list[int]]:
     d = config.deployment
     visible = os.environ.get("CUDA_VISIBLE_DEVICES")
@@ -48,6 +88,7 @@ def rl_local(config: RLConfig) -> int:
         shutil.rmtree(run_dir)
     run_dir.mkdir(parents=True, exist_ok=True)
     attempt, cfg_dir, log_dir = prepare_attempt_dirs(run_dir)
+    env_servers = prepare_env_servers(config, cfg_dir)          # before the orchestrator's config is written
     paths = write_subconfigs(config, cfg_dir)
     log.info(f"run dir {run_dir} (attempt {attempt})")
     if config.dry_run:
@@ -67,6 +108,12 @@ def rl_local(config: RLConfig) -> int:
             env = dict(base_env, **config.inference.env_vars, CUDA_VISIBLE_DEVICES=",".join(map(str, infer_gpus)))
             sup.add("inference", popen([py, "-m", "prime_rl_b200.entrypoints.inference", "@", str(paths["inference"])],
                                        env, log_dir / "inference.log"))
+        for label, path, addr in env_servers:
+            env = dict(base_env, **config.orchestrator.env_vars, CUDA_VISIBLE_DEVICES="")
+            sup.add(label, popen([py, "-m", "prime_rl_b200.entrypoints.env_server", "@", str(path)], env,
+                                 log_dir / f"{label}.log"))
+        for label, _, addr in env_servers:
+            wait_for_http(addr.rstrip("/") + "/health")
         env = dict(base_env, **config.orchestrator.env_vars, CUDA_VISIBLE_DEVICES="")
         sup.add("orchestrator", popen([py, "-m", "prime_rl_b200.entrypoints.orchestrator", "@",
                                        str(paths["orchestrator"])], env, log_dir / "orchestrator.log"))

@@ -74,6 +74,16 @@ class CausalLM(nn.Module):
                 m.reset_ssm_parameters(seed=seed * 7919 + i)
         return self
 
+    def full_parameters(self, writeback: bool = False):
+        """Context in which every parameter is whole. A no-op for replicated parameters; with parameter
+        sharding (``parallel/fsdp.py``) all units are gathered for the duration (a collective: every rank
+        enters), and with ``writeback`` values assigned inside are re-sharded on exit (checkpoint load)."""
+        import contextlib
+
+        if self.layer_hooks is not None and hasattr(self.layer_hooks, "full_parameters"):
+            return self.layer_hooks.full_parameters(writeback=writeback)
+        return contextlib.nullcontext()
+
     @property
     def output_weight(self) -> torch.Tensor:
         return self.model.embed_tokens.weight if self.lm_head is None else self.lm_head.weight
@@ -88,6 +98,8 @@ class CausalLM(nn.Module):
         """input_ids: [T] (or [1, T]) packed ids -> final hidden states [T, H] (normed).
         ``inputs_embeds [T, H]`` replaces the embedding lookup (multimodal: image features merged in)."""
         ids = input_ids.reshape(-1)
+        if self.layer_hooks is not None:
+            self.layer_hooks.before_forward()
         h = self.model.embed_tokens(ids) if inputs_embeds is None else inputs_embeds
         if self.arch.hc_mult:
             h = h.unsqueeze(1).expand(-1, self.arch.hc_mult, -1).contiguous()

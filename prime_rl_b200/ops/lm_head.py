@@ -14,7 +14,7 @@ from __future__ import annotations
 import torch
 
 from . import _runtime as rt
-from .matmul import gemm
+from .matmul import gemm, grad_accumulator
 
 
 def logprob_entropy_ref(h, w, labels, inv_temp=None, chunk: int = 4096):
@@ -52,6 +52,7 @@ class _FusedLogprobEntropy(torch.autograd.Function):
                                      h.stride(0), w.stride(0), splits, status.data_ptr(), rt.stream_ptr(dev))
         rt.check(rc, "prb_lmhead_fwd")
         ctx.save_for_backward(h, w, labels, inv_temp, out[2])
+        ctx.grad_acc = grad_accumulator(w) if w.requires_grad else None
         ctx.mark_non_differentiable(out[1])
         return out[0], out[1]
 
@@ -76,7 +77,10 @@ class _FusedLogprobEntropy(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dh = gemm(dl, w, b_mn=True)
         if ctx.needs_input_grad[1]:
-            dw = gemm(dl, h, a_mn=True, b_mn=True)
+            if ctx.grad_acc is not None and H % 4 == 0:
+                gemm(dl, h, a_mn=True, b_mn=True, out=ctx.grad_acc, beta=1.0)      # added in place, no bf16 dW
+            else:
+                dw = gemm(dl, h, a_mn=True, b_mn=True)
         return dh, dw, None, None
 
 

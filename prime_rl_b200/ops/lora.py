@@ -97,15 +97,20 @@ def lora_linear(x, w, a_cat, b_list, scale: float):
 
 
 def kgrouped_gemm(a: torch.Tensor, b: torch.Tensor, expert_offset: torch.Tensor, num_experts: int, *,
-                  alpha: float = 1.0, out_dtype=torch.float32) -> torch.Tensor:
-    """out[e] = alpha * a_e^T @ b_e over expert e's rows; a: [P, M], b: [P, N] -> [E, M, N]."""
+                  alpha: float = 1.0, out_dtype=torch.float32, out: torch.Tensor | None = None,
+                  beta: float = 0.0) -> torch.Tensor:
+    """out[e] = alpha * a_e^T @ b_e (+ beta * out[e]) over expert e's rows; a: [P, M], b: [P, N] -> [E, M, N].
+    ``out`` (contiguous, bf16 or fp32) lets a weight gradient accumulate where it is kept."""
     M, N = a.shape[1], b.shape[1]
     if a.is_cuda and a.dtype == torch.bfloat16:
-        out = torch.empty(num_experts, M, N, dtype=out_dtype, device=a.device)
+        if out is None:
+            assert beta == 0.0
+            out = torch.empty(num_experts, M, N, dtype=out_dtype, device=a.device)
+        assert out.is_contiguous() and out.shape == (num_experts, M, N)
         status = rt.status_tensor(a.device)
         rc = rt.lib().prb_gemm_bf16_kgrouped(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, a.shape[0],
-                                             a.stride(0), b.stride(0), N, int(out_dtype == torch.float32),
-                                             float(alpha), 0.0, expert_offset.data_ptr(), num_experts,
+                                             a.stride(0), b.stride(0), N, int(out.dtype == torch.float32),
+                                             float(alpha), float(beta), expert_offset.data_ptr(), num_experts,
                                              status.data_ptr(), rt.stream_ptr(a.device))
         rt.check(rc, "prb_gemm_bf16_kgrouped")
         return out

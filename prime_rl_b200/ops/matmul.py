@@ -165,12 +165,25 @@ def grouped_gemm_ref(a, w, block_expert, *, b_mn=False, out_dtype=None, n=None):
     return out
 
 
+def grad_accumulator(w: torch.Tensor):
+    """fp32 tensor of ``w``'s shape into which weight gradients are to be accumulated directly (set on the
+    parameter by the flat-buffer optimizer), or None: the weight-gradient GEMM then adds its product to it in
+    its epilogue (``beta = 1``, fp32 output) instead of materialising a bf16 gradient that is added in a
+    second pass (which reads and writes 12 bytes per parameter and micro-batch)."""
+    acc = getattr(w, "_grad_acc", None)
+    if acc is None or not acc.is_cuda or acc.dtype != torch.float32 or not acc.is_contiguous() or \
+            acc.shape != w.shape or acc.data_ptr() % 16:
+        return None
+    return acc
+
+
 class _Linear(torch.autograd.Function):
     """y = x @ w^T with all three GEMMs on the tcgen05 kernel."""
 
     @staticmethod
     def forward(ctx, x, w):
         ctx.save_for_backward(x, w)
+        ctx.grad_acc = grad_accumulator(w) if w.requires_grad else None
         x2 = x.reshape(-1, x.shape[-1])
         y = gemm(x2, w)
         return y.reshape(*x.shape[:-1], w.shape[0])
@@ -186,7 +199,10 @@ class _Linear(torch.autograd.Function):
             dx = gemm(dy2, w, b_mn=True).reshape(x.shape)
         if ctx.needs_input_grad[1]:
             x2 = x.reshape(-1, x.shape[-1])
-            dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype)
+            if ctx.grad_acc is not None and w.shape[1] % 4 == 0:
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=ctx.grad_acc, beta=1.0)     # dw stays None: already added
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype)
         return dx, dw
 
 
@@ -208,6 +224,7 @@ class _GroupedLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, block_expert, expert_offset, out=None):
         ctx.save_for_backward(x, w, block_expert, expert_offset)
+        ctx.grad_acc = grad_accumulator(w) if w.requires_grad else None
         # a caller that owns the memory of the input gradient (the peer-memory EP dispatcher)
         # hangs it on the input tensor; the backward then writes straight into it
         ctx.grad_out = getattr(x, "_grad_out_buf", None)
@@ -223,7 +240,10 @@ class _GroupedLinear(torch.autograd.Function):
             go = ctx.grad_out if (ctx.grad_out is not None and ctx.grad_out.shape == x.shape) else None
             dx = gemm(dy, w, b_mn=True, block_expert=block_expert, out=go)
         if ctx.needs_input_grad[1]:
-            dw = grouped_wgrad(dy, x, expert_offset, w.shape[0])
+            if ctx.grad_acc is not None and w.shape[2] % 4 == 0:
+                grouped_wgrad(dy, x, expert_offset, w.shape[0], out=ctx.grad_acc, beta=1.0)
+            else:
+                dw = grouped_wgrad(dy, x, expert_offset, w.shape[0])
         return dx, dw, None, None, None
 
 
@@ -231,15 +251,18 @@ def grouped_linear(x, w, block_expert, expert_offset, out=None):
     return _GroupedLinear.apply(x, w, block_expert, expert_offset, out)
 
 
-def grouped_wgrad(dy: torch.Tensor, x: torch.Tensor, expert_offset: torch.Tensor, num_experts: int) -> torch.Tensor:
-    """dW[e] = dY_e^T @ X_e over the (128-aligned) row range of each expert."""
+def grouped_wgrad(dy: torch.Tensor, x: torch.Tensor, expert_offset: torch.Tensor, num_experts: int,
+                  out: torch.Tensor | None = None, beta: float = 0.0) -> torch.Tensor:
+    """dW[e] = dY_e^T @ X_e over the (128-aligned) row range of each expert; with ``out`` / ``beta`` the
+    product is added to an existing (fp32) accumulator."""
     E = num_experts
     N, K = dy.shape[1], x.shape[1]
     if x.is_cuda and x.dtype == torch.bfloat16:
         # one k-grouped launch over the experts' row ranges, no host read of the offsets
         from .lora import kgrouped_gemm
 
-        return kgrouped_gemm(dy, x, expert_offset, E, out_dtype=x.dtype)
+        return kgrouped_gemm(dy, x, expert_offset, E, out_dtype=x.dtype, out=out, beta=beta)
+    assert out is None, "accumulating weight gradients in place is the GPU path"
     dw = torch.empty(E, N, K, dtype=x.dtype, device=x.device)
     offs = expert_offset.tolist()
     for e in range(E):

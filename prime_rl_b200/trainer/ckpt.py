@@ -98,13 +98,14 @@ class CheckpointManager:
             path.mkdir(parents=True, exist_ok=True)
         if dist.is_initialized():
             dist.barrier()
-        app = {"model": convert.model_state(model, "prime", include_lora=True)}
-        if not (self.config and self.config.skip_optimizer) and optimizer is not None:
-            app["optimizer"] = _optimizer_state_prime(optimizer.state_dict(), model.arch)
-        app = _describe_expert_shards(app, model)
-        if not (self.config and self.config.skip_progress):
-            app["progress"] = {k: torch.tensor(v) for k, v in asdict(progress).items()}
-        dcp.save({"app": app}, checkpoint_id=str(path))
+        with model.full_parameters():          # sharded parameters are whole while the checkpoint is written
+            app = {"model": convert.model_state(model, "prime", include_lora=True)}
+            if not (self.config and self.config.skip_optimizer) and optimizer is not None:
+                app["optimizer"] = _optimizer_state_prime(optimizer.state_dict(), model.arch)
+            app = _describe_expert_shards(app, model)
+            if not (self.config and self.config.skip_progress):
+                app["progress"] = {k: torch.tensor(v) for k, v in asdict(progress).items()}
+            dcp.save({"app": app}, checkpoint_id=str(path))
         if dist.is_initialized():
             dist.barrier()
         if self.is_master:
@@ -137,16 +138,17 @@ class CheckpointManager:
                 if not f.exists() or f.stat().st_size != size:
                     have = f.stat().st_size if f.exists() else "missing"
                     raise RuntimeError(f"checkpoint shard {f} is damaged: {have} bytes, expected {size}")
-        app = {"model": convert.model_state(model, "prime", include_lora=True)}
         has_opt = optimizer is not None and not (self.config and self.config.skip_optimizer)
         opt_sd = None
-        if has_opt:
-            opt_sd = optimizer.state_dict()
-            app["optimizer"] = _optimizer_state_prime(opt_sd, model.arch)
-        app = _describe_expert_shards(app, model)
-        if not (self.config and self.config.skip_progress):
-            app["progress"] = {k: torch.tensor(v) for k, v in asdict(progress).items()}
-        dcp.load({"app": app}, checkpoint_id=str(path))
+        with model.full_parameters(writeback=True):      # sharded parameters: load whole, keep the own slices
+            app = {"model": convert.model_state(model, "prime", include_lora=True)}
+            if has_opt:
+                opt_sd = optimizer.state_dict()
+                app["optimizer"] = _optimizer_state_prime(opt_sd, model.arch)
+            app = _describe_expert_shards(app, model)
+            if not (self.config and self.config.skip_progress):
+                app["progress"] = {k: torch.tensor(v) for k, v in asdict(progress).items()}
+            dcp.load({"app": app}, checkpoint_id=str(path))
         # The prime-layout model tensors are views of the live parameters, so the load landed in place.
         # Optimizer tensors are views of ``opt_sd``: the live buffers where the state is not partitioned,
         # gathered full-length copies where it is (ZeRO). ``load_state_dict`` copies them back into the

@@ -94,6 +94,10 @@ class FlatBuffers:
                 gv.add_(param.grad)
                 param.grad = None
             p.register_post_accumulate_grad_hook(hook)
+            if p.is_cuda and p.dim() >= 2:
+                # the weight-gradient GEMMs of ops/matmul.py add straight into this view (no bf16 gradient, no
+                # second pass); gradients that still arrive through autograd take the hook above
+                p._grad_acc = gv
 
     def zero_grad(self) -> None:
         self.grad.zero_()
@@ -261,6 +265,48 @@ class _Group:
         shard.copy_(full[lo:lo + self.shard_len])
 
 
+class _FSDPGroup:
+    """Optimizer group over parameters that are sharded by ``parallel/fsdp.py``: the rank's persistent slice of
+    every unit is the compute-dtype destination of the update, the reduce-scatter already happened unit by unit
+    during the backward pass, and nothing is all-gathered after the step (the next forward pulls fresh slices).
+    Presents the attributes ``FlatOptimizer`` uses of ``_Group``."""
+
+    p2p = None
+    lowp_written_by_kernel = False
+
+    def __init__(self, kind: str, sharded, runtime, reduce_group=None):
+        self.buf, self.runtime = sharded, runtime
+        self.shard_group, self.shard_n, self.shard_rank = sharded.group, sharded.N, sharded.rank
+        self.reduce_group, self.norm_group = reduce_group, None
+        n, dev = sharded.shard_numel, sharded.device
+        self.shard_len = n
+        self.flat_shard = sharded.flat_shard
+        self.master = sharded.flat_shard.float().clone()
+        self.grad_shard = sharded.grad_shard
+        self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev) if kind in ("adamw", "sgd") else None
+        self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev) if kind == "adamw" else None
+
+    sharded = True
+
+    @property
+    def lowp_out(self):
+        return self.flat_shard
+
+    def reduce(self) -> None:
+        self.runtime.finish_backward()
+        if self.reduce_group is not None and dist.get_world_size(self.reduce_group) > 1:
+            dist.all_reduce(self.grad_shard, group=self.reduce_group)       # HSDP: sum over the replicas
+
+    def publish(self) -> None:
+        self.runtime.after_optimizer_step()
+
+    def gather_full(self, shard: torch.Tensor) -> torch.Tensor:
+        return self.buf.gather_full(shard)
+
+    def scatter_full(self, full: torch.Tensor, shard: torch.Tensor) -> None:
+        self.buf.scatter_full(full, shard)
+
+
 class FlatOptimizer:
     """SGD / AdamW / SignSGD / Muon over one or more ``FlatBuffers`` groups (dense parameters
     replicated over the data-parallel ranks, expert parameters sharded over the
@@ -269,14 +315,21 @@ class FlatOptimizer:
     def __init__(self, config, named_params, *, max_steps: int | None = None, scheduler_config=None,
                  dp_group=None, expert_params=None, expert_reduce_group=None, expert_norm_group=None,
                  shard_group=None, replicate_group=None, expert_shard_group=None, offload: str | None = None,
-                 offload_chunk: int = 16 * 1024 * 1024, p2p_collectives: bool = False):
+                 offload_chunk: int = 16 * 1024 * 1024, p2p_collectives: bool = False, fsdp=None):
+        """``fsdp``: ``(ShardedParameters, FSDPRuntime)`` when the dense parameters are sharded (ZeRO-3); the
+        dense group then works on the persistent slices and ``named_params`` is ignored."""
         self.config = config
         self.kind = config.type
         self.step_count = 0
         if self.kind == "muon":
+            if fsdp is not None:
+                raise ValueError("Muon needs whole matrices: use model.zero_stage = 2 with it")
             shard_group = expert_shard_group = None  # Newton-Schulz needs whole matrices
-        self.groups = [_Group(self.kind, named_params, replicate_group if shard_group is not None else dp_group,
-                              None, shard_group, p2p=p2p_collectives)]
+        if fsdp is not None:
+            self.groups = [_FSDPGroup(self.kind, fsdp[0], fsdp[1], reduce_group=replicate_group)]
+        else:
+            self.groups = [_Group(self.kind, named_params, replicate_group if shard_group is not None else dp_group,
+                                  None, shard_group, p2p=p2p_collectives)]
         if expert_params and any(p.requires_grad for _, p in expert_params):
             self.groups.append(_Group(self.kind, expert_params,
                                       None if expert_shard_group is not None else expert_reduce_group,
@@ -303,7 +356,7 @@ class FlatOptimizer:
 
     # ------------------------------------------------------------------ API
     @property
-    def buf(self) -> FlatBuffers:
+    def buf(self):
         return self.groups[0].buf
 
     @property
@@ -461,7 +514,7 @@ class FlatOptimizer:
 def setup_optimizer(config, model, *, max_steps=None, scheduler_config=None, dp_group=None,
                     expert_reduce_group=None, expert_norm_group=None, shard_group=None, replicate_group=None,
                     expert_shard_group=None, offload: str | None = None,
-                    offload_chunk: int = 16 * 1024 * 1024, p2p_collectives: bool = False) -> FlatOptimizer:
+                    offload_chunk: int = 16 * 1024 * 1024, p2p_collectives: bool = False, fsdp=None) -> FlatOptimizer:
     """Parameters marked ``_is_expert_shard`` (set by the expert-parallel setup) form their own
     group: they are reduced over the ranks that replicate the same expert shard."""
     dense = [(n, p) for n, p in model.named_parameters() if not getattr(p, "_is_expert_shard", False)]
@@ -470,4 +523,4 @@ def setup_optimizer(config, model, *, max_steps=None, scheduler_config=None, dp_
                          expert_params=expert, expert_reduce_group=expert_reduce_group,
                          expert_norm_group=expert_norm_group, shard_group=shard_group,
                          replicate_group=replicate_group, expert_shard_group=expert_shard_group, offload=offload,
-                         offload_chunk=offload_chunk, p2p_collectives=p2p_collectives)
+                         offload_chunk=offload_chunk, p2p_collectives=p2p_collectives, fsdp=fsdp)

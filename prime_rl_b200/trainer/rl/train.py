@@ -90,6 +90,11 @@ class RLTrainer:
         # Optimizer state is partitioned over the sharding ranks for full fine-tuning; LoRA
         # adapters are small and stay replicated.
         zero = multi and d.dp_shard_cp > 1 and mc.lora is None and not mc.fsdp_cpu_offload
+        fsdp = None
+        if zero and mc.zero_stage == 3:
+            from ...parallel.fsdp import install_fsdp
+
+            fsdp = install_fsdp(self.model, d.group("dp_shard_cp"), prefetch=mc.reshard_after_forward)
         self.optimizer = setup_optimizer(
             cfg.optim, self.model, max_steps=cfg.max_steps, scheduler_config=cfg.scheduler,
             dp_group=self.dp_cp_group,
@@ -101,7 +106,7 @@ class RLTrainer:
             if (zero and ep_on and d.dp_replicate == 1 and d.dp_shard_cp // d.ep > 1) else None,
             offload="cpu" if mc.full_offload else ("state" if mc.optim_cpu_offload else None),
             offload_chunk=mc.full_offload.chunk_elements if mc.full_offload else 16 * 1024 * 1024,
-            p2p_collectives=mc.optim_collectives == "p2p" and self.device.type == "cuda")
+            p2p_collectives=mc.optim_collectives == "p2p" and self.device.type == "cuda", fsdp=fsdp)
         self.ckpt = CheckpointManager(self.run_dir, cfg.ckpt, is_master=self.world.is_master, rank=self.world.rank) \
             if cfg.ckpt is not None or cfg.resume is not None else None
         self._setup_data()

@@ -25,6 +25,12 @@ import torch.distributed as dist
 from ...utils.logger import get_logger
 from ...utils.pathing import get_broadcast_dir, get_step_path, list_steps
 
+def _null():
+    import contextlib
+
+    return contextlib.nullcontext()
+
+
 SENDER_READY, RECEIVER_READY, STARTED, FINISHED = ".sender_ready", ".receiver_ready", ".started", ".finished"
 
 
@@ -55,7 +61,8 @@ class WeightSender:
             (d / STARTED).touch()
         if dist.is_initialized():
             dist.barrier()
-        self._broadcast(model, step, d)
+        with model.full_parameters() if hasattr(model, "full_parameters") else _null():
+            self._broadcast(model, step, d)       # sharded parameters are whole for the duration
         if dist.is_initialized():
             dist.barrier()
         if self.world.is_master:

@@ -221,3 +221,27 @@ def test_nccl_transport_probe_with_a_fake_nvml():
     assert env == {"NCCL_P2P_DISABLE": "1", "NCCL_SHM_DISABLE": "1"} and without.shutdowns == 2
     env = {"NCCL_P2P_DISABLE": "0", "NCCL_SHM_DISABLE": "0"}
     assert nccl.configure_nccl_transports(without, env) is False and env["NCCL_P2P_DISABLE"] == "0"
+
+
+def test_rl_launcher_prepares_one_env_server_per_source(tmp_path):
+    """With ``spawn_env_servers`` every train / eval source gets an env-server config at its derived address and
+    the orchestrator's source is re-pointed at it; explicit ``serve.address`` sources stay externally managed."""
+    import json
+
+    from prime_rl_b200.configs.evals import EnvServerConfig
+    from prime_rl_b200.configs.rl import RLConfig
+    from prime_rl_b200.entrypoints.rl import prepare_env_servers
+
+    cfg = RLConfig.model_validate({"output_dir": str(tmp_path), "orchestrator": {
+        "spawn_env_servers": True, "env_server_base_port": 6100,
+        "train": {"source": [{"id": "reverse-text"}, {"id": "copy", "name": "cp", "serve": {"address": "http://envs:9"}}]},
+        "eval": {"source": [{"env": {"taskset": {"id": "copy"}}, "name": "held-out"}]}}})
+    o = cfg.orchestrator
+    assert o.env_addresses == {("train", "reverse-text"): "http://127.0.0.1:6100", ("train", "cp"): "http://envs:9",
+                               ("eval", "held-out"): "http://127.0.0.1:6102"}
+    servers = prepare_env_servers(cfg, tmp_path)
+    assert [s[0] for s in servers] == ["env-train-reverse-text", "env-eval-held-out"]
+    assert o.train.source[0].id == "remote" and o.train.source[0].args == {"base_url": "http://127.0.0.1:6100"}
+    assert o.train.source[1].id == "copy"                                    # externally managed: left alone
+    spec = EnvServerConfig.model_validate(json.loads((tmp_path / "envs" / "eval-held-out.json").read_text()))
+    assert spec.env.id == "copy" and spec.serve.port == 6102 and spec.env.resolved_name == "held-out"

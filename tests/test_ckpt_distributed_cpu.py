@@ -109,8 +109,13 @@ def _run(tmp_path, port, mode, cfg):
 
 
 @pytest.mark.slow
-def test_resume_with_partitioned_optimizer_state_continues_identically(tmp_path, free_port):
-    runs = _run(tmp_path, free_port, "zero_resume", BASE)
+@pytest.mark.parametrize("zero_stage", [2, 3])
+def test_resume_with_partitioned_optimizer_state_continues_identically(tmp_path, free_port, zero_stage):
+    """Stage 2: optimizer state partitioned; stage 3: parameters partitioned as well (the checkpoint is written
+    from, and read into, temporarily whole parameters)."""
+    cfg = json.loads(json.dumps(BASE))
+    cfg["model"]["zero_stage"] = zero_stage
+    runs = _run(tmp_path, free_port, "zero_resume", cfg)
     for r in runs:
         assert r["sharded"], "the test must run with the optimizer state partitioned over the ranks"
         assert r["step_count"] == 3

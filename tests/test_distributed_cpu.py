@@ -26,8 +26,11 @@ out = []
 for _ in range(2):
     m = tr.step()
     out.append([m["loss"], m["optim/grad_norm"], m["entropy"]])
-w = tr.model.model.layers[0].self_attn.qkv_proj.weight.detach().double()
-res = dict(rank=tr.world.rank, steps=out, wsum=float(w.sum()), wabs=float(w.abs().sum()))
+with tr.model.full_parameters():
+    w = tr.model.model.layers[0].self_attn.qkv_proj.weight.detach().double().clone()
+    e = tr.model.model.embed_tokens.weight.detach().double().clone()
+res = dict(rank=tr.world.rank, steps=out, wsum=float(w.sum()), wabs=float(w.abs().sum()), esum=float(e.abs().sum()),
+           fsdp=getattr(tr.model.layer_hooks, "stats", None))
 open(os.path.join({out!r}, f"rank{{tr.world.rank}}.json"), "w").write(json.dumps(res))
 import torch.distributed as dist
 if dist.is_initialized():
@@ -36,7 +39,8 @@ if dist.is_initialized():
 
 
 def _run(tmp_path, port, world, cfg):
-    tag = f"{world}_{cfg['model'].get('ep', 1)}_{cfg['model'].get('cp', 1)}_{cfg['model'].get('cp_style', 'ring')}"
+    tag = (f"{world}_{cfg['model'].get('ep', 1)}_{cfg['model'].get('cp', 1)}_{cfg['model'].get('cp_style', 'ring')}"
+           f"_z{cfg['model'].get('zero_stage', 2)}_{'ac' if cfg['model'].get('ac') else 'noac'}")
     script = tmp_path / f"worker_{tag}.py"
     out = tmp_path / f"out_{tag}"
     out.mkdir()
@@ -97,3 +101,27 @@ def test_cp2_matches_single_process(tmp_path, free_port, style):
         assert a[0] == pytest.approx(b[0], rel=1e-3, abs=1e-6)     # loss
         assert a[1] == pytest.approx(b[1], rel=1e-3)               # grad norm
         assert a[2] == pytest.approx(b[2], rel=1e-4)               # entropy
+
+
+@pytest.mark.slow
+@pytest.mark.parametrize("ac", [{"mode": "full", "freq": 1}, None])
+def test_parameter_sharding_matches_the_replicated_parameters_run(tmp_path, free_port, ac):
+    """ZeRO-3 (every rank keeps half of each layer, layers are gathered as they run, gradients reduce-scattered
+    per layer) must give the losses, gradient norms and weights of ZeRO-2 (parameters replicated), with and
+    without activation recomputation, and for a dense as well as an MoE + expert-parallel model."""
+    for name, ep in (("tiny-qwen3", 1), ("tiny-qwen3-moe", 2)):
+        base = json.loads(json.dumps(BASE))
+        base["model"].update(name=name, ep=ep, ac=ac)
+        z2 = _run(tmp_path, free_port, 2, base)
+        cfg = json.loads(json.dumps(base))
+        cfg["model"]["zero_stage"] = 3
+        z3 = _run(tmp_path, free_port + 1, 2, cfg)
+        assert z3[0]["fsdp"] is not None and z3[0]["fsdp"]["gathers"] > 0 and z3[0]["fsdp"]["reduce_scatters"] > 0
+        assert z2[0]["fsdp"] is None
+        for r in range(2):
+            for a, b in zip(z2[r]["steps"], z3[r]["steps"]):
+                assert a[0] == pytest.approx(b[0], rel=1e-5, abs=1e-7)       # loss
+                assert a[1] == pytest.approx(b[1], rel=1e-4)                  # gradient norm
+            assert z2[r]["wsum"] == pytest.approx(z3[r]["wsum"], rel=1e-6, abs=1e-6)
+            assert z2[r]["wabs"] == pytest.approx(z3[r]["wabs"], rel=1e-6)
+            assert z2[r]["esum"] == pytest.approx(z3[r]["esum"], rel=1e-6)

@@ -170,3 +170,44 @@ def test_fp8_engine_without_bf16_copies_serves_and_takes_weight_updates(tmp_path
     fresh = Engine(other, **kw)
     c = _greedy(fresh, prompts)
     assert sum(x.output == y.output for x, y in zip(b, c)) >= 2
+
+
+@pytest.mark.parametrize("weight_dtype,bound", [("bf16", 0.015), ("fp8", 0.015)])
+def test_trainer_rescoring_of_engine_rollouts_stays_under_the_mismatch_kl_bar(weight_dtype, bound):
+    """The acceptance bar for a model family: sample 256 tokens per prompt with the engine (temperature 1),
+    re-score the same tokens with the trainer's forward and fused head, and require the mismatch KL
+    ``r - log r - 1`` (``r`` = trainer probability / engine probability of the sampled token) to stay under
+    0.015 on average (reference: docs/development.md:140, tests/integration/test_reverse_text.py:116-117)."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from prime_rl_b200.engine.engine import Engine
+    from prime_rl_b200.engine.sampler import SamplingParams
+    from prime_rl_b200.models import ModelArch, SeqInfo, build_model
+    from prime_rl_b200.ops import _runtime as rt
+
+    dev = torch.device("cuda", 0)
+    arch = ModelArch(**{**ARCH, "num_hidden_layers": 4, "hidden_size": 512, "moe_intermediate_size": 256})
+    engine_model = build_model(arch, device=dev, dtype=torch.bfloat16, seed=0)
+    trainer_model = build_model(arch, device=dev, dtype=torch.bfloat16, seed=0).eval()
+    eng = Engine(engine_model, num_pages=1024, page_size=16, enable_prefix_cache=False, max_model_len=512,
+                 weight_dtype=weight_dtype, use_cuda_graphs=True)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, arch.vocab_size, (n,), generator=g).tolist() for n in (16, 33, 48, 64, 20, 57, 40, 25)]
+    reqs = eng.generate_sync(prompts, SamplingParams(max_tokens=256, temperature=1.0))
+    rt.check_status()
+    kls = []
+    with torch.no_grad():
+        for r in reqs:
+            ids = torch.tensor(r.prompt + r.output, device=dev)
+            n_p, n_o = len(r.prompt), len(r.output)
+            assert n_o == 256 and len(r.logprobs) == n_o
+            hidden = trainer_model(ids, SeqInfo.from_lengths([ids.numel()], dev))
+            labels = torch.cat([ids[1:], ids[:1]]).to(torch.int32)
+            lp, _ = trainer_model.logprobs_entropy(hidden, labels, None)
+            mine = lp[n_p - 1:n_p - 1 + n_o].float()          # position t scores token t + 1
+            theirs = torch.tensor(r.logprobs, device=dev)
+            log_ratio = mine - theirs
+            kls.append((torch.exp(log_ratio) - log_ratio - 1).mean().item())
+    rt.check_status()
+    mean_kl = sum(kls) / len(kls)
+    assert mean_kl < bound, f"mismatch KL {mean_kl:.5f} per sequence {['%.4f' % k for k in kls]}"

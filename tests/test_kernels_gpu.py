@@ -918,3 +918,41 @@ def test_route_and_plan_small_matches_the_separate_kernels():
         assert moe_ops.route_and_plan_small(torch.randn(4, 16, device=dev), 2) is None
     with torch.no_grad():
         assert moe_ops.route_and_plan_small(torch.randn(keep + 1, 16, device=dev), 2) is None
+
+
+def test_weight_gradients_accumulate_straight_into_the_fp32_buffer():
+    """With a gradient accumulator attached to the weight, the dense and the grouped weight-gradient GEMMs add
+    into it (fp32, beta = 1) and hand autograd no gradient; two backward passes must equal the sum of the two
+    ordinary bf16 gradients."""
+    from prime_rl_b200.ops import matmul as mm
+
+    torch.manual_seed(0)
+    x = _rand(300, 256).requires_grad_()
+    w = torch.nn.Parameter(_rand(384, 256, scale=0.05))
+    dy = _rand(300, 384)
+    mm.linear(x, w).backward(dy)
+    ref = w.grad.float().clone()
+    w.grad = None
+    w._grad_acc = torch.zeros(384, 256, dtype=torch.float32, device=DEV)
+    for _ in range(2):
+        mm.linear(x, w).backward(dy)
+    rt.check_status()
+    assert w.grad is None
+    _close(w._grad_acc, 2 * ref, atol=0.05, rtol=2e-2)
+    # grouped: experts with and without rows
+    counts = torch.tensor([130, 0, 5, 256], dtype=torch.int32)
+    offs, be, P = _blocks(counts)
+    xg = _rand(P, 128)
+    valid = (be >= 0).repeat_interleave(128).to(DEV)
+    xg = (xg * valid[:, None]).requires_grad_()
+    wg = torch.nn.Parameter(_rand(4, 192, 128, scale=0.05))
+    dyg = _rand(P, 192) * valid[:, None]
+    mm.grouped_linear(xg, wg, be.to(DEV), offs.to(DEV)).backward(dyg)
+    refg = wg.grad.float().clone()
+    wg.grad = None
+    wg._grad_acc = torch.full((4, 192, 128), 1.0, dtype=torch.float32, device=DEV)
+    mm.grouped_linear(xg, wg, be.to(DEV), offs.to(DEV)).backward(dyg)
+    rt.check_status()
+    assert wg.grad is None
+    _close(wg._grad_acc, refg + 1.0, atol=0.05, rtol=2e-2)
+    assert torch.equal(wg._grad_acc[1], torch.ones(192, 128, device=DEV))      # an expert without rows adds nothing
