@@ -35,6 +35,8 @@ class SeqInfo:
     cp: object | None = None      # context-parallel state (parallel/cp.py)
     # attention outputs kept across activation recomputation, keyed by layer (ops/attention.py)
     attn_cache: dict | None = None
+    # outputs of GEMM-class operators kept across recomputation in "selective" mode (ops/stash.py)
+    op_stash: object | None = None
     # values one layer leaves for later layers of the same forward (sparse-attention indices)
     shared: dict | None = None
     # rotary angles [T, rotary_dim / 2] when positions have several axes (multimodal MRoPE); attention

@@ -48,6 +48,8 @@ class CausalLM(nn.Module):
                                   device=device)
         self.ac_every: int | None = None       # recompute every n-th layer in backward (None = never)
         self.cache_attention = True            # keep attention outputs across recomputation
+        # "selective" recomputation: operator classes whose outputs are kept as well (ops/stash.py); None = full
+        self.ac_keep: set[str] | None = None
         self.layer_hooks = None                # parallel/fsdp.py installs gather/release hooks here
 
     # ------------------------------------------------------------------ init
@@ -90,6 +92,13 @@ class CausalLM(nn.Module):
 
     # ------------------------------------------------------------------ forward
     def _run_layer(self, layer: DecoderLayer, idx: int, h: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
+        st = getattr(seq, "op_stash", None)
+        if st is not None:                       # selective recomputation: GEMM outputs survive the re-run
+            with st.layer(idx):
+                return self._run_layer_inner(layer, idx, h, seq)
+        return self._run_layer_inner(layer, idx, h, seq)
+
+    def _run_layer_inner(self, layer: DecoderLayer, idx: int, h: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
         if self.layer_hooks is not None:
             return self.layer_hooks.run(layer, idx, h, seq)
         return layer(h, seq)
@@ -107,7 +116,13 @@ class CausalLM(nn.Module):
         use_ac = self.ac_every is not None and self.training and torch.is_grad_enabled()
         # recomputation re-runs everything but the attention kernel: its output (and lse) of the
         # first pass is kept, 2 bytes x q_dim per token and layer
-        seq.attn_cache = {} if (use_ac and self.cache_attention) else None
+        keep_attn = self.cache_attention and (self.ac_keep is None or "attention" in self.ac_keep)
+        seq.attn_cache = {} if (use_ac and keep_attn) else None
+        seq.op_stash = None
+        if use_ac and self.ac_keep:
+            from ..ops.stash import OpStash
+
+            seq.op_stash = OpStash(self.ac_keep - {"attention"})
         for i, layer in enumerate(self.model.layers):
             if use_ac and i % self.ac_every == 0:
                 h = checkpoint(self._run_layer, layer, i, h, seq, use_reentrant=False)

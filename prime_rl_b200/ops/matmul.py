@@ -15,6 +15,7 @@ from __future__ import annotations
 import torch
 
 from . import _runtime as rt
+from . import stash
 
 
 # Inference-only dispatch of small plain GEMMs (no groups, no fused epilogue, M <= SMALL_M_ROWS) to cuBLAS.
@@ -185,7 +186,7 @@ class _Linear(torch.autograd.Function):
         ctx.save_for_backward(x, w)
         ctx.grad_acc = grad_accumulator(w) if w.requires_grad else None
         x2 = x.reshape(-1, x.shape[-1])
-        y = gemm(x2, w)
+        y = stash.run("mm", lambda: gemm(x2, w))          # selective recomputation keeps this product
         return y.reshape(*x.shape[:-1], w.shape[0])
 
     @staticmethod
@@ -207,7 +208,8 @@ class _Linear(torch.autograd.Function):
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
-    if x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+    if (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16) or \
+            (stash.active() and x.dtype == w.dtype):          # the stash lives in the autograd function
         if not x.is_contiguous():
             x = x.contiguous()
         y = _Linear.apply(x, w)
@@ -228,7 +230,9 @@ class _GroupedLinear(torch.autograd.Function):
         # a caller that owns the memory of the input gradient (the peer-memory EP dispatcher)
         # hangs it on the input tensor; the backward then writes straight into it
         ctx.grad_out = getattr(x, "_grad_out_buf", None)
-        return gemm(x, w, block_expert=block_expert, out=out)
+        if out is not None:          # the caller's buffer is shared between layers: its contents cannot be kept
+            return gemm(x, w, block_expert=block_expert, out=out)
+        return stash.run("grouped_mm", lambda: gemm(x, w, block_expert=block_expert))
 
     @staticmethod
     def backward(ctx, dy):

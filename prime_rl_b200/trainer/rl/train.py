@@ -81,6 +81,10 @@ class RLTrainer:
             freeze_router(self.model)
         if mc.ac is not None:
             self.model.ac_every = mc.ac.freq
+            if mc.ac.mode == "selective":
+                from ...ops.stash import kinds_from_targets
+
+                self.model.ac_keep = kinds_from_targets(mc.ac.targets)
         self.model.train()
         self._setup_parallel()
         self.loss_fn = setup_rl_loss_fn(cfg.loss)

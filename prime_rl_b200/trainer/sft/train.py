@@ -49,13 +49,50 @@ class SFTTrainer:
             apply_lora(self.model, mc.lora.rank, mc.lora.alpha, mc.lora.target_modules, mc.lora.modules_to_save)
         if mc.ac is not None:
             self.model.ac_every = mc.ac.freq
+            if mc.ac.mode == "selective":
+                from ...ops.stash import kinds_from_targets
+
+                self.model.ac_keep = kinds_from_targets(mc.ac.targets)
         self.model.train()
         multi = dist.is_initialized() and self.world.world_size > 1
-        self.dp_group = self.dims.group("dp_cp") if multi else None
-        zero = multi and mc.lora is None
-        self.optimizer = setup_optimizer(cfg.optim, self.model, max_steps=cfg.max_steps, scheduler_config=cfg.scheduler,
-                                         dp_group=self.dp_group,
-                                         shard_group=self.dims.group("dp_shard_cp") if zero else None)
+        d = self.dims
+        if d.cp_enabled:
+            raise NotImplementedError("context parallelism in the SFT trainer (use the RL trainer's CE loss path: "
+                                      "orchestrator.algo.type = 'sft')")
+        self.dp_group = d.group("dp_cp") if multi else None
+        ep_on = d.ep_enabled and multi
+        if ep_on:
+            from ...parallel.ep import install_expert_parallel
+
+            install_expert_parallel(self.model, d, mc.moe)
+        # same sharding choices as the RL trainer: optimizer state partitioned (stage 2) or parameters too (stage 3)
+        zero = multi and d.dp_shard_cp > 1 and mc.lora is None
+        fsdp = None
+        if zero and mc.zero_stage == 3:
+            from ...parallel.fsdp import install_fsdp
+
+            fsdp = install_fsdp(self.model, d.group("dp_shard_cp"), prefetch=mc.reshard_after_forward)
+        self.optimizer = setup_optimizer(
+            cfg.optim, self.model, max_steps=cfg.max_steps, scheduler_config=cfg.scheduler, dp_group=self.dp_group,
+            expert_reduce_group=d.group("ep_replicas") if ep_on else None,
+            expert_norm_group=d.group("ep") if ep_on else None,
+            shard_group=d.group("dp_shard_cp") if zero else None,
+            replicate_group=d.group("dp_replicate") if (zero and d.dp_replicate > 1) else None,
+            expert_shard_group=d.group("dp_shard_mod_ep")
+            if (zero and ep_on and d.dp_replicate == 1 and d.dp_shard_cp // d.ep > 1) else None,
+            offload="cpu" if mc.full_offload else ("state" if mc.optim_cpu_offload else None),
+            offload_chunk=mc.full_offload.chunk_elements if mc.full_offload else 16 * 1024 * 1024,
+            p2p_collectives=mc.optim_collectives == "p2p" and self.device.type == "cuda", fsdp=fsdp)
+        # online evals: an evals process (or the launcher's inference server) follows the weights written here
+        self.weight_sender = None
+        if cfg.eval is not None or cfg.weight_broadcast is not None:
+            from ...configs.trainer import FileSystemWeightBroadcastConfig
+            from ...transports.weights import setup_weight_sender
+
+            wb = cfg.weight_broadcast or FileSystemWeightBroadcastConfig()
+            self.weight_sender = setup_weight_sender(wb, self.run_dir, self.world, self.model,
+                                                     lora=mc.lora is not None, lora_cfg=mc.lora)
+            self.broadcast_interval = cfg.eval.interval if cfg.eval is not None else 1
         self.monitor = monitors_mod.setup(cfg.monitors, self.run_dir, "trainer", is_master=self.world.is_master)
         self.ckpt = CheckpointManager(self.run_dir, cfg.ckpt, is_master=self.world.is_master, rank=self.world.rank) \
             if cfg.ckpt is not None or cfg.resume is not None else None
@@ -145,6 +182,10 @@ class SFTTrainer:
             if self.world.is_master:
                 self.logger.info(f"step {step} | loss {m['loss']:.4f} | grad_norm {m['optim/grad_norm']:.3f} | "
                                  f"{m['perf/throughput']:.0f} tok/s")
+            if self.weight_sender is not None and (step + 1) % self.broadcast_interval == 0:
+                t0 = time.perf_counter()
+                self.weight_sender.broadcast(self.model, step)
+                self.monitor.log({"time/broadcast_weights": time.perf_counter() - t0}, step)
             if self.ckpt is not None and cfg.ckpt is not None and cfg.ckpt.interval and \
                     (step + 1) % cfg.ckpt.interval == 0:
                 self.ckpt.save(step, self.model, self.optimizer, self.progress, self.dataset)

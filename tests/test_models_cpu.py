@@ -148,3 +148,32 @@ def test_laguna_family_gating_per_layer_heads_and_round_trip(tmp_path):
     convert.load_model_state(other, hf, "hf")
     for (n, a), (_, b) in zip(model.state_dict().items(), other.state_dict().items()):
         assert torch.equal(a, b), n
+
+
+def test_selective_recomputation_keeps_gemm_outputs_and_matches_full_recomputation():
+    """``ac.mode = "selective"``: the re-run of a checkpointed layer replays the kept GEMM outputs instead of
+    recomputing them; losses and gradients equal full recomputation and no recomputation at all."""
+    from prime_rl_b200.ops import stash
+
+    def grads(keep, ac_every):
+        arch, m = _tiny("tiny-qwen3-moe")
+        m.train()
+        m.ac_every, m.ac_keep = ac_every, keep
+        ids = torch.randint(0, arch.vocab_size, (64,), generator=torch.Generator().manual_seed(0))
+        seq = SeqInfo.from_lengths([64], "cpu")
+        h = m(ids, seq)
+        (h.float() ** 2).mean().backward()
+        return {n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None}, seq
+
+    plain, _ = grads(None, None)
+    full, seq_full = grads(None, 1)
+    sel, seq_sel = grads({"mm", "grouped_mm"}, 1)
+    assert seq_full.op_stash is None and seq_sel.op_stash is not None
+    st = seq_sel.op_stash.stats
+    assert st["recorded"] > 0 and st["replayed"] == st["recorded"] and not seq_sel.op_stash.store
+    for n in plain:
+        assert torch.allclose(plain[n], full[n], atol=1e-6), n
+        assert torch.allclose(plain[n], sel[n], atol=1e-6), n
+    assert stash.kinds_from_targets(None) == {"mm", "grouped_mm", "attention"}
+    assert stash.kinds_from_targets(["aten::mm", "flash_attn"]) == {"mm", "attention"}
+    assert stash.kinds_from_targets([]) == set()
