@@ -10,11 +10,13 @@
 // One K block (128 e4m3 = one 128-byte swizzled row per tile row) is four tcgen05.mma
 // kind::f8f6f4 instructions (K = 32 each) into a TMEM accumulator that is NOT carried across
 // K blocks: the epilogue warps read each block's partial sum from TMEM and add it, times the
-// block's scale product, to fp32 accumulators in registers (two TMEM buffers, so block kb + 1 is
+// block's scale product, to fp32 accumulators in registers (four TMEM buffers, so the next blocks are
 // on the tensor core while block kb is being promoted). BN = 128 = one weight scale block, so
 // the scale of a tile and K block is one scalar per row.
 //
-// Warp roles: 0 = TMA producer, 1 = MMA issuer + TMEM owner, 2..5 = promotion / epilogue.
+// Warp roles: 0 = TMA producer, 1 = MMA issuer + TMEM owner, 2..9 = promotion / epilogue: warp w reads TMEM
+// lanes 32 (w % 4) .. + 31 (the quarter a warp may address) and columns 64 ((w - 2) / 4) .. + 63, so the
+// promotion of one K block is spread over eight warps and costs each of them two tcgen05.ld and 64 FMAs.
 // Grouped mode as in gemm.cu: 128-row blocks owned by block_expert[blk] (-1 = unused).
 #include "common.cuh"
 #include "tma_host.cuh"
@@ -24,7 +26,9 @@ namespace prb {
 
 constexpr int kF8BM = 128, kF8BN = 128, kF8BK = 128;      // BK in elements = bytes
 constexpr int kF8Stages = 6;
-constexpr int kF8Threads = 192;
+constexpr int kF8AccBufs = 4;                  // TMEM accumulators in flight (4 x 128 columns = all of TMEM)
+constexpr int kF8EpiWarps = 8;                 // two warps per TMEM lane quarter, 64 accumulator columns each
+constexpr int kF8Threads = 64 + 32 * kF8EpiWarps;
 constexpr int kF8StageBytes = (kF8BM + kF8BN) * kF8BK;    // 32 KB
 constexpr int kF8Smem = kF8Stages * kF8StageBytes + 1024 + 256;
 
@@ -72,20 +76,20 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + kF8Stages * kF8StageBytes);
   uint64_t* empty = full + kF8Stages;
-  uint64_t* tfull = empty + kF8Stages;     // [2] partial sum of a K block is in TMEM buffer b
-  uint64_t* tempty = tfull + 2;            // [2] count 4: the epilogue warps have read buffer b
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* tfull = empty + kF8Stages;     // [4] partial sum of a K block is in TMEM buffer b
+  uint64_t* tempty = tfull + kF8AccBufs;   // [4] count 8: the epilogue warps have read buffer b
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + kF8AccBufs);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int KB = (p.K + kF8BK - 1) / kF8BK;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kF8Stages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4); }
+    for (int i = 0; i < kF8AccBufs; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], kF8EpiWarps); }
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
   }
-  if (warp == 1) { tmem_alloc(tmem_slot, 256); tmem_relinquish(); }
+  if (warp == 1) { tmem_alloc(tmem_slot, kF8AccBufs * kF8BN); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -117,12 +121,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       constexpr uint32_t idesc = umma_idesc(0, kF8BM, kF8BN, false, false);
       Fp8Tile sched(p);
       int s = 0;
-      uint32_t ph = 0, u = 0;               // u: K blocks issued so far (TMEM buffer = u & 1)
+      uint32_t ph = 0, u = 0;               // u: K blocks issued so far (TMEM buffer = u % kF8AccBufs)
       bool ok = true;
       while (ok && sched.next(p, m_blk, n_blk, expert)) {
         for (int kb = 0; kb < KB; ++kb, ++u) {
-          const uint32_t buf = u & 1;
-          if (!mbar_wait(&tempty[buf], ((u >> 1) & 1) ^ 1, p.status, kTimeoutTmemEmpty)) { ok = false; break; }
+          const uint32_t buf = u % kF8AccBufs;
+          if (!mbar_wait(&tempty[buf], ((u / kF8AccBufs) & 1) ^ 1, p.status, kTimeoutTmemEmpty)) { ok = false; break; }
           if (!mbar_wait(&full[s], ph, p.status, kTimeoutFullBarrier)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + s * kF8StageBytes), b_addr = a_addr + kF8BM * kF8BK;
@@ -137,7 +141,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
     }
   } else {
-    const int q = warp & 3;
+    const int q = warp & 3;                    // TMEM lane quarter of this warp
+    const int half = (warp - 2) >> 2;          // which 64 of the tile's 128 columns
+    constexpr int kCols = kF8BN / 2;
     Fp8Tile sched(p);
     uint32_t u = 0;
     const int n_tiles_scale = (p.N + kF8BN - 1) / kF8BN;
@@ -147,41 +153,39 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const bool row_ok = row < p.M && (p.row_valid == nullptr || p.row_valid[row] >= 0);
       const float* sa_row = p.sa + static_cast<long long>(row < p.M ? row : 0) * KB;
       const float* sb_row = p.sb + (static_cast<long long>(expert) * n_tiles_scale + n_blk) * KB;
-      float acc[kF8BN];
+      float acc[kCols];
 #pragma unroll
-      for (int c = 0; c < kF8BN; ++c) acc[c] = 0.f;
+      for (int c = 0; c < kCols; ++c) acc[c] = 0.f;
       for (int kb = 0; kb < KB; ++kb, ++u) {
-        const uint32_t buf = u & 1;
+        const uint32_t buf = u % kF8AccBufs;
         const float sc = sa_row[kb] * sb_row[kb];
-        ok = mbar_wait(&tfull[buf], (u >> 1) & 1, p.status, kTimeoutTmemFull);
+        ok = mbar_wait(&tfull[buf], (u / kF8AccBufs) & 1, p.status, kTimeoutTmemFull);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        // two TMEM loads in flight per wait: the load latency is paid twice per K block, not four times
-#pragma unroll
-        for (int c = 0; c < kF8BN / 64; ++c) {
-          uint32_t v0[32], v1[32];
-          const uint32_t taddr = tmem_base + buf * kF8BN + c * 64 + (static_cast<uint32_t>(q * 32) << 16);
-          tmem_ld_32x32(taddr, v0);
-          tmem_ld_32x32(taddr + 32, v1);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            acc[c * 64 + j] = fmaf(__uint_as_float(v0[j]), sc, acc[c * 64 + j]);
-            acc[c * 64 + 32 + j] = fmaf(__uint_as_float(v1[j]), sc, acc[c * 64 + 32 + j]);
-          }
-        }
+        // both TMEM loads of this warp's 64 columns are in flight before the single wait
+        uint32_t v0[32], v1[32];
+        const uint32_t taddr = tmem_base + buf * kF8BN + half * kCols + (static_cast<uint32_t>(q * 32) << 16);
+        tmem_ld_32x32(taddr, v0);
+        tmem_ld_32x32(taddr + 32, v1);
+        tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tempty[buf]);
+        if (lane == 0) mbar_arrive(&tempty[buf]);       // the values are in registers: the buffer may be reused
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          acc[j] = fmaf(__uint_as_float(v0[j]), sc, acc[j]);
+          acc[32 + j] = fmaf(__uint_as_float(v1[j]), sc, acc[32 + j]);
+        }
       }
       if (!ok) break;
       if (row_ok) {
-        __nv_bfloat16* dst = p.C + static_cast<long long>(row) * p.ldc + n_blk * kF8BN;
+        const int col_base = n_blk * kF8BN + half * kCols;
+        __nv_bfloat16* dst = p.C + static_cast<long long>(row) * p.ldc + col_base;
         const bool vec = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
 #pragma unroll
-        for (int c = 0; c < kF8BN; c += 8) {
-          const int col = n_blk * kF8BN + c;
+        for (int c = 0; c < kCols; c += 8) {
+          const int col = col_base + c;
           if (vec && col + 8 <= p.N) {
             uint4 o;
             o.x = pack_bf16(acc[c], acc[c + 1]); o.y = pack_bf16(acc[c + 2], acc[c + 3]);
@@ -196,7 +200,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, 256);
+  if (warp == 1) tmem_dealloc(tmem_base, kF8AccBufs * kF8BN);
 }
 
 // Activation quantiser: x bf16 [M, K] -> e4m3 [M, K] + fp32 scales [M, ceil(K / 128)] (scale =

@@ -30,6 +30,14 @@ struct PagedParams {
   float* ml_part;               // [B, Hq, S, 2]
   float scale;
   int B, Hq, Hkv, page_size, max_blocks, splits;
+  // Shared-prefix decode (optional, tensor-core kernels only). Sequences whose leading pages are the same
+  // physical pages (samples of one prompt) form groups of up to 8: the group kernel reads those pages once
+  // for all members and leaves a partial result per member in split slots [splits, splits + prefix_splits);
+  // the per-sequence kernel then starts at page page_begin[b]. The merge kernel folds both.
+  const int* page_begin;        // [B] first page the per-sequence kernel reads (nullptr = 0 everywhere)
+  const int* group_seqs;        // [groups, 8] member sequence indices, -1 = unused slot
+  const int* group_pages;       // [groups] number of leading pages the members share (0 = no group in this slot)
+  int prefix_splits, total_splits;
 };
 
 template <int G>
@@ -192,11 +200,13 @@ paged_decode_mma_kernel(const PagedParams p) {
   const int g = lane >> 2, j = lane & 3;        // fragment row (query head of the group) / column pair
   const int ctx = p.ctx_lens[b];
   const int pages = (ctx + kPmPage - 1) / kPmPage;
-  const int per = (pages + p.splits - 1) / p.splits;
-  const int pg_begin = split * per, pg_end = min(pages, pg_begin + per);
+  const int first = p.page_begin ? min(p.page_begin[b], pages) : 0;            // pages before it: the group kernel
+  const int per = (pages - first + p.splits - 1) / p.splits;
+  const int pg_begin = first + split * per, pg_end = min(pages, pg_begin + per);
   const int* table = p.block_tables + static_cast<long long>(b) * p.max_blocks;
   const long long row_stride = static_cast<long long>(p.Hkv) * kPdD;          // elements between keys of a page
   const uint32_t sbase = smem_u32(pm_smem) + warp * kPmWarpBytes;
+  const int S = p.total_splits > 0 ? p.total_splits : p.splits;               // slots per head in the partial arrays
   const float scale_log2 = p.scale * 1.4426950408889634f;
 
   // Q fragments: row g of the A tile is query head g of this KV head's group (rows >= G are zero)
@@ -309,14 +319,158 @@ paged_decode_mma_kernel(const PagedParams p) {
       O += s_o[(w * 8 + gg) * kPdD + d] * a;
     }
     const long long head = static_cast<long long>(b) * p.Hq + kvh * G + gg;
-    if (p.splits == 1) {
+    if (S == 1) {
       p.out[head * kPdD + d] = __float2bfloat16(L > 0.f ? O / L : 0.f);
     } else {
-      p.o_part[(head * p.splits + split) * kPdD + d] = O;
+      p.o_part[(head * S + split) * kPdD + d] = O;
       if (d == 0) {
         // the merge kernel works in the natural-log domain
-        p.ml_part[(head * p.splits + split) * 2] = (M == -INFINITY) ? -INFINITY : M * 0.6931471805599453f;
-        p.ml_part[(head * p.splits + split) * 2 + 1] = L;
+        p.ml_part[(head * S + split) * 2] = (M == -INFINITY) ? -INFINITY : M * 0.6931471805599453f;
+        p.ml_part[(head * S + split) * 2 + 1] = L;
+      }
+    }
+  }
+}
+
+// Shared-prefix pass: one CTA = (group, KV head, slice of the shared pages). The four warps own the four
+// 16-row query tiles of the group (rows 0..7: the G heads of member 2w, rows 8..15: member 2w + 1), so the full
+// M = 16 of the mma tile is used; K and V pages are copied into shared memory ONCE per CTA (four pages per
+// stage, double buffered) and read by all four warps. Every key of a shared page is valid for every member
+// (shared pages are full), so no masking. Results are per-member partials in slots [splits, splits + prefix_splits).
+constexpr int kPxPages = 4;                                         // pages per stage
+constexpr int kPxPageBytes = 2 * kPmPage * kPdD * 2;                // K and V rows of one page: 8 KB
+constexpr int kPxStageBytes = kPxPages * kPxPageBytes;              // 32 KB
+
+template <int G>
+__global__ void __launch_bounds__(kPdWarps * 32)
+paged_prefix_mma_kernel(const PagedParams p) {
+  extern __shared__ __align__(128) uint8_t pm_smem[];
+  const int grp = blockIdx.x, kvh = blockIdx.y, ps = blockIdx.z;
+  const int shared_pages = p.group_pages[grp];
+  if (shared_pages <= 0) return;                              // uniform for the CTA: no barrier was reached yet
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, j = lane & 3;
+  const int* members = p.group_seqs + grp * 8;
+  const int leader = members[0];
+  const int seq_a = members[2 * warp], seq_b = members[2 * warp + 1];
+  const int per = (shared_pages + p.prefix_splits - 1) / p.prefix_splits;
+  const int pg_begin = ps * per, pg_end = min(shared_pages, pg_begin + per);
+  const int* table = p.block_tables + static_cast<long long>(leader) * p.max_blocks;
+  const long long row_stride = static_cast<long long>(p.Hkv) * kPdD;
+  const uint32_t sbase = smem_u32(pm_smem);
+  const float scale_log2 = p.scale * 1.4426950408889634f;
+
+  // Q fragments of both members (rows g and g + 8 of the A tile); absent members and heads >= G give zero rows
+  uint32_t qa[8][2], qb[8][2];
+  {
+    const bool va = seq_a >= 0 && g < G, vb = seq_b >= 0 && g < G;
+    const __nv_bfloat16* ra = p.q + (static_cast<long long>(va ? seq_a : 0) * p.Hq + kvh * G + (g < G ? g : 0)) * kPdD;
+    const __nv_bfloat16* rb = p.q + (static_cast<long long>(vb ? seq_b : 0) * p.Hq + kvh * G + (g < G ? g : 0)) * kPdD;
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      qa[kk][0] = va ? *reinterpret_cast<const uint32_t*>(ra + 16 * kk + 2 * j) : 0u;
+      qa[kk][1] = va ? *reinterpret_cast<const uint32_t*>(ra + 16 * kk + 8 + 2 * j) : 0u;
+      qb[kk][0] = vb ? *reinterpret_cast<const uint32_t*>(rb + 16 * kk + 2 * j) : 0u;
+      qb[kk][1] = vb ? *reinterpret_cast<const uint32_t*>(rb + 16 * kk + 8 + 2 * j) : 0u;
+    }
+  }
+  float o[16][4];
+#pragma unroll
+  for (int n = 0; n < 16; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m_a = -INFINITY, l_a = 0.f, m_b = -INFINITY, l_b = 0.f;
+
+  // the CTA copies up to kPxPages pages into stage `buf`: 2 x 256 16-byte chunks per page over 128 threads
+  auto issue_stage = [&](int pg0, int buf) {
+    const int n_pages = min(kPxPages, pg_end - pg0);
+    for (int c = threadIdx.x; c < n_pages * 256; c += kPdWarps * 32) {
+      const int page = c >> 8, r = c & 255;                   // r: key = r / 16, 16-byte chunk of the row = r % 16
+      const int key = r >> 4, ch = r & 15;
+      const long long off = static_cast<long long>(table[pg0 + page]) * kPmPage * row_stride +
+                            static_cast<long long>(kvh) * kPdD + key * row_stride + ch * 8;
+      const uint32_t kdst = sbase + buf * kPxStageBytes + page * kPxPageBytes;
+      const uint32_t sw = key * 256 + ((ch ^ (key & 7)) << 4);
+      cp_async16(kdst + sw, p.kpool + off);
+      cp_async16(kdst + kPmPage * kPdD * 2 + sw, p.vpool + off);
+    }
+    cp_async_commit();
+  };
+
+  int buf = 0;
+  if (pg_begin < pg_end) issue_stage(pg_begin, 0);
+  for (int pg0 = pg_begin; pg0 < pg_end; pg0 += kPxPages, buf ^= 1) {
+    const int nxt = pg0 + kPxPages;
+    if (nxt < pg_end) { issue_stage(nxt, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    __syncthreads();                                          // every thread's copies of this stage have landed
+    const int n_pages = min(kPxPages, pg_end - pg0);
+    for (int page = 0; page < n_pages; ++page) {
+      const uint32_t ks = sbase + buf * kPxStageBytes + page * kPxPageBytes, vs = ks + kPmPage * kPdD * 2;
+      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+      {
+        const int key = 8 * (lane >> 4) + (lane & 7);
+        const int hi = (lane >> 3) & 1;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4(ks + key * 256 + (((2 * kk + hi) ^ (key & 7)) << 4), b0, b1, b2, b3);
+          mma_16816(s0, qa[kk][0], qb[kk][0], qa[kk][1], qb[kk][1], b0, b1);
+          mma_16816(s1, qa[kk][0], qb[kk][0], qa[kk][1], qb[kk][1], b2, b3);
+        }
+      }
+      // rows g (member a): s0[0..1] = keys 2j, 2j+1 and s1[0..1] = keys 8+2j, 9+2j; rows g + 8 (member b): [2..3]
+      const float xa0 = s0[0] * scale_log2, xa1 = s0[1] * scale_log2, xa2 = s1[0] * scale_log2, xa3 = s1[1] * scale_log2;
+      const float xb0 = s0[2] * scale_log2, xb1 = s0[3] * scale_log2, xb2 = s1[2] * scale_log2, xb3 = s1[3] * scale_log2;
+      float mxa = fmaxf(fmaxf(xa0, xa1), fmaxf(xa2, xa3)), mxb = fmaxf(fmaxf(xb0, xb1), fmaxf(xb2, xb3));
+      mxa = fmaxf(mxa, __shfl_xor_sync(0xffffffffu, mxa, 1));
+      mxa = fmaxf(mxa, __shfl_xor_sync(0xffffffffu, mxa, 2));
+      mxb = fmaxf(mxb, __shfl_xor_sync(0xffffffffu, mxb, 1));
+      mxb = fmaxf(mxb, __shfl_xor_sync(0xffffffffu, mxb, 2));
+      const float na = fmaxf(m_a, mxa), nb = fmaxf(m_b, mxb);
+      const float alpha_a = exp2f(m_a - na), alpha_b = exp2f(m_b - nb);
+      const float pa0 = exp2f(xa0 - na), pa1 = exp2f(xa1 - na), pa2 = exp2f(xa2 - na), pa3 = exp2f(xa3 - na);
+      const float pb0 = exp2f(xb0 - nb), pb1 = exp2f(xb1 - nb), pb2 = exp2f(xb2 - nb), pb3 = exp2f(xb3 - nb);
+      float rsa = pa0 + pa1 + pa2 + pa3, rsb = pb0 + pb1 + pb2 + pb3;
+      rsa += __shfl_xor_sync(0xffffffffu, rsa, 1);
+      rsa += __shfl_xor_sync(0xffffffffu, rsa, 2);
+      rsb += __shfl_xor_sync(0xffffffffu, rsb, 1);
+      rsb += __shfl_xor_sync(0xffffffffu, rsb, 2);
+      l_a = l_a * alpha_a + rsa; m_a = na;
+      l_b = l_b * alpha_b + rsb; m_b = nb;
+      // A fragment of P: a0 = (row g, keys 2j..), a1 = (row g + 8, keys 2j..), a2 / a3 the same for keys 8 + 2j..
+      const uint32_t fa0 = pack_bf16(pa0, pa1), fa1 = pack_bf16(pb0, pb1), fa2 = pack_bf16(pa2, pa3),
+                     fa3 = pack_bf16(pb2, pb3);
+      {
+        const int key = 8 * ((lane >> 3) & 1) + (lane & 7);
+        const int sub = lane >> 4;
+#pragma unroll
+        for (int pr = 0; pr < 8; ++pr) {
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4_trans(vs + key * 256 + (((2 * pr + sub) ^ (key & 7)) << 4), b0, b1, b2, b3);
+          o[2 * pr][0] *= alpha_a; o[2 * pr][1] *= alpha_a; o[2 * pr][2] *= alpha_b; o[2 * pr][3] *= alpha_b;
+          o[2 * pr + 1][0] *= alpha_a; o[2 * pr + 1][1] *= alpha_a;
+          o[2 * pr + 1][2] *= alpha_b; o[2 * pr + 1][3] *= alpha_b;
+          mma_16816(o[2 * pr], fa0, fa1, fa2, fa3, b0, b1);
+          mma_16816(o[2 * pr + 1], fa0, fa1, fa2, fa3, b2, b3);
+        }
+      }
+    }
+    __syncthreads();                                          // the stage may be overwritten by the next copy
+  }
+  // each warp owns its rows: the partials of member a (rows g) and member b (rows g + 8) go out directly
+  if (g < G) {
+    const int S = p.total_splits, slot = p.splits + ps;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int seq = half ? seq_b : seq_a;
+      if (seq < 0) continue;
+      const float mm = half ? m_b : m_a, ll = half ? l_b : l_a;
+      const long long head = static_cast<long long>(seq) * p.Hq + kvh * G + g;
+#pragma unroll
+      for (int n = 0; n < 16; ++n)
+        *reinterpret_cast<float2*>(&p.o_part[(head * S + slot) * kPdD + 8 * n + 2 * j]) =
+            make_float2(o[n][2 * half], o[n][2 * half + 1]);
+      if (j == 0) {
+        p.ml_part[(head * S + slot) * 2] = (mm == -INFINITY) ? -INFINITY : mm * 0.6931471805599453f;
+        p.ml_part[(head * S + slot) * 2 + 1] = ll;
       }
     }
   }
@@ -324,13 +478,18 @@ paged_decode_mma_kernel(const PagedParams p) {
 
 __global__ void __launch_bounds__(kPdD)
 paged_decode_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
-                          __nv_bfloat16* __restrict__ out, int splits) {
+                          __nv_bfloat16* __restrict__ out, int splits, int own_splits, int heads_per_seq,
+                          const int* __restrict__ page_begin) {
+  // `splits` slots per head; slots >= own_splits belong to the shared-prefix pass and only count for sequences
+  // that are in a group (page_begin > 0): the others never wrote them
   const long long head = blockIdx.x;
   const int d = threadIdx.x;
+  int used = splits;
+  if (own_splits < splits && (page_begin == nullptr || page_begin[head / heads_per_seq] <= 0)) used = own_splits;
   float M = -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, ml_part[(head * splits + s) * 2]);
+  for (int s = 0; s < used; ++s) M = fmaxf(M, ml_part[(head * splits + s) * 2]);
   float L = 0.f, O = 0.f;
-  for (int s = 0; s < splits; ++s) {
+  for (int s = 0; s < used; ++s) {
     const float ms = ml_part[(head * splits + s) * 2];
     const float a = (ms == -INFINITY) ? 0.f : __expf(ms - M);
     L += ml_part[(head * splits + s) * 2 + 1] * a;
@@ -344,6 +503,58 @@ paged_decode_merge_kernel(const float* __restrict__ o_part, const float* __restr
 // q: bf16 [B, Hq, 128]; kpool / vpool: bf16 [pages, page_size, Hkv, 128]; block_tables: int32
 // [B, max_blocks]; ctx_lens: int32 [B]; out: bf16 [B, Hq, 128]. For splits > 1 the caller gives
 // o_part fp32 [B, Hq, splits, 128] and ml_part fp32 [B, Hq, splits, 2].
+// Shared-prefix form: group_seqs int32 [num_groups, 8] (-1 = unused), group_pages int32 [num_groups] (0 = slot
+// unused), page_begin int32 [B]; prefix_splits >= 1 slices of the shared pages; o_part / ml_part then hold
+// splits + prefix_splits slots per head. Needs 16-token pages and a GQA group of at most 8.
+PRB_API int prb_paged_decode_prefix(const void* q, const void* kpool, const void* vpool, const int* block_tables,
+                                    const int* ctx_lens, void* out, float* o_part, float* ml_part, int B, int Hq,
+                                    int Hkv, int head_dim, int page_size, int max_blocks, int splits, float scale,
+                                    const int* page_begin, const int* group_seqs, const int* group_pages,
+                                    int num_groups, int prefix_splits, void* stream_) {
+  using namespace prb;
+  if (head_dim != kPdD || Hq % Hkv) return -2;
+  if (B <= 0) return 0;
+  const int G = Hq / Hkv;
+  if (page_size != kPmPage || G > 8 || (G & (G - 1)) != 0) return -5;
+  if (splits < 1 || prefix_splits < 1 || num_groups < 1 || o_part == nullptr || ml_part == nullptr ||
+      page_begin == nullptr || group_seqs == nullptr || group_pages == nullptr)
+    return -3;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  PagedParams p;
+  p.q = (const __nv_bfloat16*)q; p.kpool = (const __nv_bfloat16*)kpool; p.vpool = (const __nv_bfloat16*)vpool;
+  p.block_tables = block_tables; p.ctx_lens = ctx_lens; p.out = (__nv_bfloat16*)out;
+  p.o_part = o_part; p.ml_part = ml_part; p.scale = scale;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.page_size = page_size; p.max_blocks = max_blocks; p.splits = splits;
+  p.page_begin = page_begin; p.group_seqs = group_seqs; p.group_pages = group_pages;
+  p.prefix_splits = prefix_splits; p.total_splits = splits + prefix_splits;
+  constexpr int smem = kPdWarps * kPmWarpBytes;       // 64 KB: four per-warp page buffers, or two shared 32 KB stages
+  static_assert(2 * kPxStageBytes <= smem, "the shared-prefix stages must fit the same allocation");
+#define PRB_PX_LAUNCH(GG)                                                                                       \
+  {                                                                                                             \
+    static prb::DeviceOnce configured;                                                                          \
+    if (configured.pending()) {                                                                                 \
+      if (cudaFuncSetAttribute(paged_decode_mma_kernel<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != \
+              cudaSuccess ||                                                                                    \
+          cudaFuncSetAttribute(paged_prefix_mma_kernel<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != \
+              cudaSuccess)                                                                                      \
+        return -10;                                                                                             \
+      configured.mark();                                                                                        \
+    }                                                                                                           \
+    paged_prefix_mma_kernel<GG><<<dim3(num_groups, Hkv, prefix_splits), kPdWarps * 32, smem, stream>>>(p);      \
+    paged_decode_mma_kernel<GG><<<dim3(B, Hkv, splits), kPdWarps * 32, smem, stream>>>(p);                      \
+  }
+  switch (G) {
+    case 1: PRB_PX_LAUNCH(1) break;
+    case 2: PRB_PX_LAUNCH(2) break;
+    case 4: PRB_PX_LAUNCH(4) break;
+    default: PRB_PX_LAUNCH(8) break;
+  }
+#undef PRB_PX_LAUNCH
+  paged_decode_merge_kernel<<<static_cast<unsigned>(B) * Hq, kPdD, 0, stream>>>(o_part, ml_part, (__nv_bfloat16*)out,
+                                                                               p.total_splits, splits, Hq, page_begin);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
 PRB_API int prb_paged_decode(const void* q, const void* kpool, const void* vpool, const int* block_tables,
                              const int* ctx_lens, void* out, float* o_part, float* ml_part, int B, int Hq, int Hkv,
                              int head_dim, int page_size, int max_blocks, int splits, float scale, void* stream_) {
@@ -353,6 +564,7 @@ PRB_API int prb_paged_decode(const void* q, const void* kpool, const void* vpool
   if (splits < 1 || (splits > 1 && (o_part == nullptr || ml_part == nullptr))) return -3;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   PagedParams p;
+  p.page_begin = nullptr; p.group_seqs = nullptr; p.group_pages = nullptr; p.prefix_splits = 0; p.total_splits = 0;
   p.q = (const __nv_bfloat16*)q; p.kpool = (const __nv_bfloat16*)kpool; p.vpool = (const __nv_bfloat16*)vpool;
   p.block_tables = block_tables; p.ctx_lens = ctx_lens; p.out = (__nv_bfloat16*)out;
   p.o_part = o_part; p.ml_part = ml_part; p.scale = scale;
@@ -380,8 +592,8 @@ PRB_API int prb_paged_decode(const void* q, const void* kpool, const void* vpool
     }
 #undef PRB_PM_LAUNCH
     if (splits > 1)
-      paged_decode_merge_kernel<<<static_cast<unsigned>(B) * Hq, kPdD, 0, stream>>>(o_part, ml_part,
-                                                                                   (__nv_bfloat16*)out, splits);
+      paged_decode_merge_kernel<<<static_cast<unsigned>(B) * Hq, kPdD, 0, stream>>>(
+          o_part, ml_part, (__nv_bfloat16*)out, splits, splits, Hq, nullptr);
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
   }
   switch (G) {
@@ -392,7 +604,7 @@ PRB_API int prb_paged_decode(const void* q, const void* kpool, const void* vpool
     default: return -4;
   }
   if (splits > 1)
-    paged_decode_merge_kernel<<<static_cast<unsigned>(B) * Hq, kPdD, 0, stream>>>(o_part, ml_part,
-                                                                                 (__nv_bfloat16*)out, splits);
+    paged_decode_merge_kernel<<<static_cast<unsigned>(B) * Hq, kPdD, 0, stream>>>(
+        o_part, ml_part, (__nv_bfloat16*)out, splits, splits, Hq, nullptr);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

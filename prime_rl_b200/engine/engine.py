@@ -83,7 +83,7 @@ class Engine:
         self.cache = KVCache(arch.num_hidden_layers, num_pages, page_size, arch.num_key_value_heads // self.tp_size,
                              arch.head_dim, p.dtype, p.device)
         self.runner = ModelRunner(model, self.cache, use_cuda_graphs=use_cuda_graphs, max_model_len=max_model_len,
-                                  tp=tp if self.tp_size > 1 else None)
+                                  tp=tp if self.tp_size > 1 else None, shared_prefix_decode=enable_prefix_cache)
         self.max_running, self.max_prefill_tokens = max_running, max_prefill_tokens
         self.eos, self.enable_prefix_cache = eos_token_id, enable_prefix_cache
         self.waiting: list[Request] = []

@@ -31,14 +31,20 @@ class StepInput:
 
 class ModelRunner:
     def __init__(self, model, cache: KVCache, fp32_lm_head: bool = True, use_cuda_graphs: bool = False,
-                 max_model_len: int = 8192, tp=None):
+                 max_model_len: int = 8192, tp=None, shared_prefix_decode: bool = False):
         self.model, self.cache, self.arch = model, cache, model.arch
         self.tp = tp                                    # engine/tp.py TPContext: sharded weights, fused reduces
         self.device = next(model.parameters()).device
         self.fp32_lm_head = fp32_lm_head
         self.capture_routed = False
         self.last_routed: torch.Tensor | None = None   # [N, moe_layers, k] of the last step
-        self._decode_meta = None                        # (block tables, context lengths) of a pure decode step
+        self._decode_meta = None                        # (block tables, context lengths, prefix groups) of a decode step
+        # samples of one prompt share its pages through the prefix cache: the decode kernels then read those
+        # pages once per group of up to 8 sequences instead of once per sequence (csrc/paged_attn.cu)
+        self.shared_prefix_decode = shared_prefix_decode and self.device.type == "cuda" and cache.page_size == 16
+        self.prefix_splits = 2
+        self._group_key = None                          # identity of the batch the current grouping was made for
+        self.prefix_stats = {"regroupings": 0, "grouped_sequences": 0, "shared_pages": 0}
         self._cu_batch, self._cu = None, []             # per-sequence cu_seqlens of the current prefix-hit prefill
         # CUDA graphs for decode steps: batch sizes are padded to a multiple of ``graph_bucket``;
         # one page of the cache is reserved as the target of the padding rows
@@ -55,8 +61,9 @@ class ModelRunner:
         if self._decode_meta is not None and sinks is None and window is None:
             from ..ops import paged
 
-            bt, ctx = self._decode_meta
-            return paged.paged_decode_raw(q.contiguous(), self.cache.k[layer], self.cache.v[layer], bt, ctx)
+            bt, ctx, prefix = self._decode_meta
+            return paged.paged_decode_raw(q.contiguous(), self.cache.k[layer], self.cache.v[layer], bt, ctx,
+                                          prefix=prefix)
         fresh = all(s.kv.length == 0 for s in batch)
         if fresh and sinks is None:
             lens = [len(s.tokens) for s in batch]
@@ -165,7 +172,8 @@ class ModelRunner:
               "slots": torch.full((B,), self.scratch_page * ps, dtype=torch.long, device=dev),
               "bt": torch.full((B, W), self.scratch_page, dtype=torch.int32, device=dev),
               "ctx": torch.ones(B, dtype=torch.int32, device=dev), "rows": torch.arange(B, device=dev)}
-        self._decode_meta = (st["bt"], st["ctx"])
+        st["prefix"] = self._prefix_tensors(B) if self.shared_prefix_decode else None
+        self._decode_meta = (st["bt"], st["ctx"], st["prefix"])
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
@@ -179,6 +187,47 @@ class ModelRunner:
         st["logits"], st["routed"], st["graph"] = logits, routed, graph
         self._graphs[B] = st
         return st
+
+    # ------------------------------------------------------------------ shared-prefix groups
+    def _prefix_tensors(self, B: int):
+        """Static device tensors of the group description for a batch of (at most) ``B`` sequences:
+        ``page_begin [B]``, ``group_seqs [B / 2, 8]``, ``group_pages [B / 2]`` (all zero / -1 = no groups)."""
+        dev = self.device
+        n_groups = max(1, B // 2)
+        return (torch.zeros(B, dtype=torch.int32, device=dev),
+                torch.full((n_groups, 8), -1, dtype=torch.int32, device=dev),
+                torch.zeros(n_groups, dtype=torch.int32, device=dev), self.prefix_splits)
+
+    def _update_groups(self, batch, prefix) -> None:
+        """Recomputes the grouping when the set of running sequences changed (shared pages are full pages, so a
+        grouping stays valid while its members run) and copies it to the device."""
+        import numpy as np
+
+        key = (id(prefix[0]),) + tuple(id(s.kv) for s in batch)
+        if key == self._group_key:
+            return
+        self._group_key = key
+        from ..ops.paged import group_shared_prefixes
+
+        page_begin_t, group_seqs_t, group_pages_t, _ = prefix
+        groups, page_begin = group_shared_prefixes([s.kv.pages for s in batch], [s.kv.length for s in batch],
+                                                   self.cache.page_size)
+        B, n_slots = page_begin_t.shape[0], group_pages_t.shape[0]
+        groups = groups[:n_slots]
+        pb = np.zeros(B, dtype=np.int32)
+        gs = np.full((n_slots, 8), -1, dtype=np.int32)
+        gp = np.zeros(n_slots, dtype=np.int32)
+        for gi, (members, shared) in enumerate(groups):
+            gs[gi, :len(members)] = members
+            gp[gi] = shared
+            for i in members:
+                pb[i] = shared
+        page_begin_t.copy_(torch.from_numpy(pb), non_blocking=False)
+        group_seqs_t.copy_(torch.from_numpy(gs), non_blocking=False)
+        group_pages_t.copy_(torch.from_numpy(gp), non_blocking=False)
+        self.prefix_stats["regroupings"] += 1
+        self.prefix_stats["grouped_sequences"] = int((pb > 0).sum())
+        self.prefix_stats["shared_pages"] = int(gp.sum())
 
     def _decode_with_graph(self, batch):
         """Fills the graph's static inputs and replays it. The host side is on the critical path of a decode
@@ -217,6 +266,8 @@ class ModelRunner:
         st["slots"].copy_(dev[:, 2])
         st["ctx"].copy_(dev[:, 3])
         st["bt"].copy_(dev[:, 4:])
+        if st["prefix"] is not None:
+            self._update_groups(batch, st["prefix"])
         st["graph"].replay()
         routed = st["routed"][:B].clone() if st["routed"] is not None else None
         return st["logits"][:B].clone(), routed
@@ -259,7 +310,14 @@ class ModelRunner:
             max_blocks = max(len(s.kv.pages) for s in batch)
             bt = torch.tensor([s.kv.pages + [0] * (max_blocks - len(s.kv.pages)) for s in batch], dtype=torch.int32)
             ctx = torch.tensor([s.kv.length + 1 for s in batch], dtype=torch.int32)
-            self._decode_meta = (bt.to(dev, non_blocking=True), ctx.to(dev, non_blocking=True))
+            prefix = None
+            if self.shared_prefix_decode and len(batch) > 1:
+                if getattr(self, "_eager_prefix", None) is None or self._eager_prefix[0].shape[0] < len(batch):
+                    self._eager_prefix = self._prefix_tensors(max(len(batch), 8))
+                    self._group_key = None
+                self._update_groups(batch, self._eager_prefix)
+                prefix = self._eager_prefix
+            self._decode_meta = (bt.to(dev, non_blocking=True), ctx.to(dev, non_blocking=True), prefix)
         rows, offsets = [], []
         for s, st in zip(batch, starts):
             n = len(s.tokens)

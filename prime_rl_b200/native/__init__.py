@@ -58,6 +58,7 @@ _CUDA_SIGNATURES = {
     "prb_flash_bwd_slice": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, L, L, L, L, L, L, L, F, I, I, P, P],
     "prb_flash_bwd": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, L, L, L, F, I, I, P, P],
     "prb_paged_decode": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P],
+    "prb_paged_decode_prefix": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P, P, P, I, I, P],
     "prb_lmhead_num_splits": [I, I],
     "prb_lmhead_fwd": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, L, L, I, P, P],
     "prb_lmhead_bwd_dlogits": [P, P, P, P, P, P, P, I, I, I, L, L, L, P, P],

@@ -1,5 +1,11 @@
-"""Context parallelism: the packed token stream is cut into ``cp`` contiguous chunks, every
-non-attention layer runs on the local chunk, attention sees the whole (causal) context.
+"""Context parallelism: the packed token stream is cut into chunks, every non-attention layer runs on the
+local chunks, attention sees the whole (causal) context.
+
+Token layout. ``contiguous``: rank r holds tokens ``[r T / cp, (r + 1) T / cp)``; with a causal mask rank r then
+attends to r + 1 chunks of keys, so the last rank does ``2 cp / (cp + 1)`` times the average work and every
+step waits for it. ``zigzag`` (default of the ``ring`` style): the stream is cut into ``2 cp`` chunks and rank
+r holds chunks r and ``2 cp - 1 - r``; its two query slices together attend ``2 cp + 1`` chunk-units of keys
+on every rank, so the attention kernels finish at the same time everywhere.
 
 ``ring``     (the reference's default, utils/cp.py:40-70 + layers/ring_attn.py:218-368): K/V of
              all chunks are all-gathered, local queries attend the keys up to the end of the
@@ -145,9 +151,13 @@ class _FusedGatherAttention(torch.autograd.Function):
 
 class ContextParallel:
     def __init__(self, group, cp: int, rank: int, style: str = "ring", p2p_all_to_all: bool = False,
-                 fused_kv_gather: bool = False):
+                 fused_kv_gather: bool = False, layout: str | None = None):
         self.group, self.cp, self.rank, self.style = group, cp, rank, style
         self.fused_kv_gather, self._kv = fused_kv_gather, None
+        # the in-kernel K / V gather and the Ulysses exchange address contiguous chunks
+        self.layout = layout or ("zigzag" if style == "ring" and not fused_kv_gather else "contiguous")
+        if self.layout == "zigzag" and (style != "ring" or fused_kv_gather):
+            raise ValueError("the zigzag token layout goes with cp_style = 'ring' and the all-gather K / V exchange")
         # Ulysses exchanges over NVLink peer memory instead of NCCL (built on first use, sized by the first block)
         self.use_p2p, self._p2p = p2p_all_to_all, None
 
@@ -183,13 +193,31 @@ class ContextParallel:
 
     # ------------------------------------------------------------------ sharding
     def shard(self, t: torch.Tensor) -> torch.Tensor:
+        if self.layout == "zigzag":
+            c = t.shape[0] // (2 * self.cp)
+            a, b = self.rank, 2 * self.cp - 1 - self.rank
+            return torch.cat([t[a * c:(a + 1) * c], t[b * c:(b + 1) * c]], 0)
         n = t.shape[0] // self.cp
         return t[self.rank * n:(self.rank + 1) * n]
 
+    def _to_global_order(self, gathered: torch.Tensor) -> torch.Tensor:
+        """Rank-major concatenation of the local rows (what an all-gather returns) -> global token order."""
+        if self.layout != "zigzag":
+            return gathered
+        cp = self.cp
+        c = gathered.shape[0] // (2 * cp)
+        v = gathered.view(cp, 2, c, *gathered.shape[1:])
+        # global chunk j sits on rank j (first half) for j < cp, on rank 2 cp - 1 - j (second half) otherwise
+        ranks = torch.tensor([j if j < cp else 2 * cp - 1 - j for j in range(2 * cp)], device=gathered.device)
+        halves = torch.tensor([0 if j < cp else 1 for j in range(2 * cp)], device=gathered.device)
+        return v[ranks, halves].reshape(gathered.shape)
+
     def shard_inputs(self, ids, labels, inv_temp, seq: SeqInfo):
         T = ids.shape[0]
-        if T % self.cp:
-            raise ValueError(f"packed length {T} is not a multiple of cp={self.cp} (set pad_to_multiple_of)")
+        unit = 2 * self.cp if self.layout == "zigzag" else self.cp
+        if T % unit:
+            raise ValueError(f"packed length {T} is not a multiple of {unit} (cp = {self.cp}, {self.layout} layout; "
+                             "set pad_to_multiple_of)")
         local = replace(seq, position_ids=self.shard(seq.position_ids), cp=self)
         if seq.routed_experts is not None:
             local.routed_experts = self.shard(seq.routed_experts)
@@ -198,9 +226,9 @@ class ContextParallel:
         return self.shard(ids), self.shard(labels), self.shard(inv_temp), local
 
     def gather_outputs(self, logprobs, entropy):
-        lp = _AllGatherSeq.apply(logprobs, self.group, False)
+        lp = self._to_global_order(_AllGatherSeq.apply(logprobs, self.group, False))
         with torch.no_grad():
-            ent = _AllGatherSeq.apply(entropy, self.group, False)
+            ent = self._to_global_order(_AllGatherSeq.apply(entropy, self.group, False))
         return lp, ent
 
     # ------------------------------------------------------------------ attention
@@ -219,10 +247,28 @@ class ContextParallel:
                 and self.cp <= 8):
             return _FusedGatherAttention.apply(q, k.contiguous(), v.contiguous(), self,
                                                seq.full_cu_seqlens.to(torch.int32), window)
-        kg = _AllGatherSeq.apply(k, self.group, True)
-        vg = _AllGatherSeq.apply(v.contiguous(), self.group, True)
-        lo, hi = self.rank * Tl, (self.rank + 1) * Tl
+        kg = self._to_global_order(_AllGatherSeq.apply(k, self.group, True))
+        vg = self._to_global_order(_AllGatherSeq.apply(v.contiguous(), self.group, True))
         cu = seq.full_cu_seqlens
+        if self.layout == "zigzag":
+            # two query slices per rank: chunk r against keys [0, (r + 1) c) and chunk 2 cp - 1 - r against keys
+            # [0, (2 cp - r) c): 2 cp + 1 chunk-units of keys on every rank
+            c = Tl // 2
+            outs = []
+            for half, chunk in ((0, self.rank), (1, 2 * self.cp - 1 - self.rank)):
+                qs, lo = q[half * c:(half + 1) * c], chunk * c
+                if q.is_cuda and sinks is None and q.dtype == torch.bfloat16 and q.shape[-1] == 128:
+                    max_len = int((cu[1:] - cu[:-1]).max())
+                    outs.append(attn_ops.attention(qs.contiguous(), kg, vg, cu.to(torch.int32), max_len, causal=True,
+                                                   window=window, backend="tcgen05", q_offset=lo))
+                else:
+                    doc = self._doc_ids(cu, T, q.device)
+                    pos = torch.arange(T, device=q.device)
+                    hi = lo + c
+                    outs.append(attention_offset_ref(qs, kg[:hi], vg[:hi], pos[lo:hi], pos[:hi], doc[lo:hi], doc[:hi],
+                                                     window=window, sinks=sinks))
+            return torch.cat(outs, 0)
+        lo, hi = self.rank * Tl, (self.rank + 1) * Tl
         if q.is_cuda and sinks is None and q.dtype == torch.bfloat16 and q.shape[-1] == 128:
             # the tcgen05 kernels take a query slice directly: local rows [lo, hi) of the global
             # sequence against all gathered keys (causality hides the keys past hi); the

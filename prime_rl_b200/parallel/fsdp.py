@@ -277,7 +277,8 @@ class FSDPRuntime:
                 g = param.grad
                 param.grad = None
                 buf = fixed_buffer() if fixed_buffer is not None else self._grad_buffer(u)
-                buf[s.offset:s.offset + s.numel].view(s.shape).add_(g)
+                if g is not None:
+                    buf[s.offset:s.offset + s.numel].view(s.shape).add_(g)
                 if fixed_buffer is None:
                     u.pending -= 1
                     if u.pending == 0:

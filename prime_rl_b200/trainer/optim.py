@@ -91,6 +91,8 @@ class FlatBuffers:
         that low-precision per-parameter gradients never pile up across micro-batches."""
         for p, gv in zip(self.params, self._grad_views):
             def hook(param, gv=gv):
+                if param.grad is None:          # the weight-gradient GEMM already added its product to ``gv``
+                    return
                 gv.add_(param.grad)
                 param.grad = None
             p.register_post_accumulate_grad_hook(hook)

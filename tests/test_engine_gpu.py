@@ -211,3 +211,32 @@ def test_trainer_rescoring_of_engine_rollouts_stays_under_the_mismatch_kl_bar(we
     rt.check_status()
     mean_kl = sum(kls) / len(kls)
     assert mean_kl < bound, f"mismatch KL {mean_kl:.5f} per sequence {['%.4f' % k for k in kls]}"
+
+
+def test_samples_of_one_prompt_decode_through_the_shared_prefix_kernel():
+    """With the prefix cache on, the samples of a prompt share its pages; the runner groups them and the decode
+    step reads the shared pages once per group. Tokens and log-probabilities must be those of an engine without
+    prefix sharing (greedy decoding), with and without CUDA graphs."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from prime_rl_b200.engine.engine import Engine
+    from prime_rl_b200.ops import _runtime as rt
+
+    arch, model, plain = _setup()
+    g = torch.Generator().manual_seed(9)
+    base = [torch.randint(0, arch.vocab_size, (n,), generator=g).tolist() for n in (96, 80)]
+    tails = [torch.randint(0, arch.vocab_size, (n,), generator=g).tolist() for n in (3, 9, 17, 5, 11, 2)]
+    prompts = [base[i % 2] + t for i, t in enumerate(tails)]
+    ref = _greedy(plain, prompts, n=20)
+    for graphs in (False, True):
+        eng = Engine(model, num_pages=512, page_size=16, enable_prefix_cache=True, max_model_len=256,
+                     use_cuda_graphs=graphs)
+        _greedy(eng, [b + [1, 2] for b in base], n=2)           # fill the cache with the two prompts' pages
+        got = _greedy(eng, prompts, n=20)
+        rt.check_status()
+        st = eng.runner.prefix_stats
+        assert st["regroupings"] >= 1 and st["grouped_sequences"] == 6 and st["shared_pages"] >= 4 + 5
+        same = sum(a.output == b.output for a, b in zip(ref, got))
+        assert same >= len(prompts) - 1
+        for a, b in zip(ref, got):
+            assert abs(a.logprobs[0] - b.logprobs[0]) < 5e-2

@@ -956,3 +956,62 @@ def test_weight_gradients_accumulate_straight_into_the_fp32_buffer():
     assert wg.grad is None
     _close(wg._grad_acc, refg + 1.0, atol=0.05, rtol=2e-2)
     assert torch.equal(wg._grad_acc[1], torch.ones(192, 128, device=DEV))      # an expert without rows adds nothing
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(32, 4), (8, 2), (8, 8)])
+def test_paged_decode_with_shared_prefix_groups_matches_the_reference(Hq, Hkv):
+    """Sequences whose leading pages are the same physical pages are attended in two passes (shared pages once per
+    group of up to 8 sequences, own pages per sequence) and merged: must equal the plain per-sequence result.
+    Covers full groups, a group of 3, a sequence in no group, and a shared run that is not a multiple of the
+    kernel's four-page stage."""
+    from prime_rl_b200.ops import paged
+
+    torch.manual_seed(0)
+    D, ps, n_pages = 128, 16, 400
+    kpool = _rand(n_pages, ps, Hkv, D)
+    vpool = _rand(n_pages, ps, Hkv, D)
+    free = list(range(n_pages))
+    import random
+
+    random.Random(0).shuffle(free)
+    page_lists, lengths = [], []
+
+    def family(n_members, shared_pages, own_tokens):
+        shared = [free.pop() for _ in range(shared_pages)]
+        for i in range(n_members):
+            n_own = own_tokens[i]
+            own = [free.pop() for _ in range((n_own + ps - 1) // ps)]
+            page_lists.append(shared + own)
+            lengths.append(shared_pages * ps + n_own)
+
+    family(8, 9, [1, 5, 16, 17, 33, 2, 40, 9])        # 9 shared pages: 2 full stages + 1 page
+    family(3, 4, [3, 20, 1])
+    family(1, 6, [7])                                   # alone: no group
+    family(8, 5, [12] * 8)
+    B = len(page_lists)
+    W = max(len(p) for p in page_lists)
+    bt = torch.zeros(B, W, dtype=torch.int32)
+    for i, p in enumerate(page_lists):
+        bt[i, :len(p)] = torch.tensor(p, dtype=torch.int32)
+    ctx = torch.tensor(lengths, dtype=torch.int32)
+    q = _rand(B, Hq, D)
+    ref = paged.paged_decode_ref(q.cpu(), kpool.cpu(), vpool.cpu(), bt, ctx)
+    # kv.length of the runner is the length before the new token: the last key of a sequence is its own
+    groups, page_begin = paged.group_shared_prefixes(page_lists, [n - 1 for n in lengths], ps, min_pages=4)
+    assert sorted(len(m) for m, _ in groups) == [3, 8, 8] and page_begin[11] == 0
+    n_slots = B // 2
+    gs = torch.full((n_slots, 8), -1, dtype=torch.int32)
+    gp = torch.zeros(n_slots, dtype=torch.int32)
+    for gi, (members, shared) in enumerate(groups):
+        gs[gi, :len(members)] = torch.tensor(members, dtype=torch.int32)
+        gp[gi] = shared
+    pb = torch.tensor(page_begin, dtype=torch.int32)
+    for splits, psplits in ((1, 1), (2, 2), (3, 4)):
+        out = paged.paged_decode_raw(q, kpool, vpool, bt.to(DEV), ctx.to(DEV), splits=splits,
+                                     prefix=(pb.to(DEV), gs.to(DEV), gp.to(DEV), psplits))
+        _close(out, ref, atol=2e-2, rtol=2e-2)
+    # no groups at all: the prefix slots must be ignored
+    out = paged.paged_decode_raw(q, kpool, vpool, bt.to(DEV), ctx.to(DEV), splits=2,
+                                 prefix=(torch.zeros_like(pb).to(DEV), torch.full_like(gs, -1).to(DEV),
+                                         torch.zeros_like(gp).to(DEV), 2))
+    _close(out, ref, atol=2e-2, rtol=2e-2)

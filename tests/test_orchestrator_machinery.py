@@ -94,16 +94,18 @@ def test_pending_weight_update_stops_scheduling_and_cuts_hopeless_groups():
 def test_admissions_are_capped_per_burst_window():
     async def go():
         env = SlowEnv()
-        d, _, _ = _dispatcher(env, group_size=1, limit=1000, min_burst=5, admission_window_s=0.2)
-        runner = asyncio.create_task(d.run())
-        await asyncio.sleep(0.1)
-        first = d.stats["groups_launched"]
-        assert first == max(5, 1000 // 10)                    # one window's cap, not the whole budget of 1000
-        await asyncio.sleep(0.25)
-        assert d.stats["groups_launched"] == 2 * first
+        d, _, _ = _dispatcher(env, group_size=1, limit=1000, min_burst=5, admission_window_s=3600.0)
+        for _ in range(400):                                  # far more scheduling passes than the cap allows
+            await d.fill_inflight()
+        cap = max(5, 1000 // 10)
+        assert d.stats["groups_launched"] == cap              # one window's cap, not the whole budget of 1000
+        assert d.admission_budget() == 0
+        d._window_start -= 7200.0                             # the window has passed
+        for _ in range(400):
+            await d.fill_inflight()
+        assert d.stats["groups_launched"] == 2 * cap
         env.release.set()
         await d.stop()
-        runner.cancel()
 
     asyncio.run(go())
 
