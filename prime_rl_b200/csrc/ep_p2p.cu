@@ -14,6 +14,11 @@
 //   ep_push_fp8_kernel / ep_recv_fp8_kernel   the same trip with an e4m3 payload: the sender
 //                      quantises each 128-column group of a row (scale = amax / 448, fp32) on
 //                      the way out, the owner expands its rows back to bf16 after the flags
+//   ep_prepare_kernel / ep_push_blocks_kernel   the dispatch without a global wait: rows are pushed in the
+//                      order of the owner's buffer (whole 128-row runs of one expert at a time, starting with
+//                      the next rank's experts), every run ends with a release-add of its row count onto
+//                      the arrival counter of the owner's 128-row block, and the owner's grouped GEMM waits
+//                      per block (csrc/gemm.cu: blk_wait) instead of for everybody
 //   ep_signal_kernel   "my buffer is complete" flag on every peer
 //   ep_pull_kernel     waits for the owners' flags; out[t] = sum_k w[t,k] * peer_row(t,k) with
 //                      peer loads (also: gradient of the dispatch with w = 1); optional
@@ -200,6 +205,88 @@ ep_recv_kernel(__nv_bfloat16* __restrict__ buf, const int* __restrict__ hist, co
   uint4* p = reinterpret_cast<uint4*>(buf + r0 * H);
   const long long n = (r1 - r0) * (H / 8);
   for (long long i = threadIdx.x; i < n; i += blockDim.x) p[i] = make_uint4(0u, 0u, 0u, 0u);
+}
+
+
+// Owner side of the per-block dispatch: one CTA per local expert. (a) rows each of its 128-row blocks will
+// receive (block_rows, what the GEMM producer compares the arrival counter with), (b) zeroes the padding rows
+// behind the expert's last real row (nobody pushes there), (c) zeroes the arrival counters of the OTHER parity
+// for the call after this one: no peer can be pushing for that call yet, because pushes start after the
+// histogram exchange in which this rank takes part only after this kernel.
+__global__ void __launch_bounds__(256)
+ep_prepare_kernel(__nv_bfloat16* __restrict__ buf, const int* __restrict__ hist, const int* __restrict__ expert_offset,
+                  int* __restrict__ block_rows, unsigned* __restrict__ zero_cnt, int max_blocks, int rank, int R, int E,
+                  int H) {
+  const int El = E / R;
+  const int le = blockIdx.x;
+  for (int b = blockIdx.x * blockDim.x + threadIdx.x; b < max_blocks; b += gridDim.x * blockDim.x) zero_cnt[b] = 0u;
+  int tot = 0;
+  for (int s = 0; s < R; ++s) tot += hist[s * E + rank * El + le];
+  const int r0 = expert_offset[le], r1 = expert_offset[le + 1];
+  for (int b = r0 / 128 + threadIdx.x; b < r1 / 128; b += blockDim.x)
+    block_rows[b] = max(0, min(128, tot - (b * 128 - r0)));
+  if (le == El - 1)
+    for (int b = r1 / 128 + threadIdx.x; b < max_blocks; b += blockDim.x) block_rows[b] = 0;
+  uint4* p = reinterpret_cast<uint4*>(buf + static_cast<long long>(r0 + tot) * H);
+  const long long n = static_cast<long long>(r1 - r0 - tot) * (H / 8);
+  for (long long i = threadIdx.x; i < n; i += blockDim.x) p[i] = make_uint4(0u, 0u, 0u, 0u);
+}
+
+// Sender side: CTA i takes the local 128-row block (i + first) % blocks of the expert-sorted pair order
+// (row_src / block_expert / local_off: the local routing plan), `first` = the first block of the next rank's
+// experts, so that at any moment the ranks write to different owners. The block's real rows are consecutive
+// rows of the owner's buffer; after the stores: system fence, CTA barrier, then one release-add per touched
+// owner block.
+__global__ void __launch_bounds__(256)
+ep_push_blocks_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ row_src,
+                      const int* __restrict__ local_block_expert, const int* __restrict__ local_off,
+                      const int* __restrict__ local_total, const int* __restrict__ counts,
+                      const int* __restrict__ send_base, EpPeers dst, EpPeers cnt, long long cnt_off,
+                      int* __restrict__ pos_out, int k, int H, int El, int rank, int R, int cap_rows, int* status) {
+  const int nblk = local_total[0] / 128;
+  if (nblk <= 0) return;
+  const int first = local_off[((rank + 1) % R) * El] / 128 % nblk;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = blockIdx.x; i < nblk; i += gridDim.x) {
+    int b = i + first;
+    if (b >= nblk) b -= nblk;
+    const int e = local_block_expert[b];
+    if (e < 0) continue;
+    const int d = e / El;
+    const int r0 = b * 128;
+    const int n = min(128, counts[e] - (r0 - local_off[e]));
+    const int pos0 = send_base[e] + (r0 - local_off[e]);
+    if (n <= 0) continue;
+    if (pos0 < 0 || pos0 + n > cap_rows) {   // never store outside the peer's buffer
+      if (threadIdx.x == 0) atomicCAS(status, 0, static_cast<int>(kBadArgument));
+      continue;
+    }
+    __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(dst.buf[d]) + static_cast<long long>(pos0) * H;
+    for (int j = warp; j < n; j += 8) {
+      const int p = row_src[r0 + j];
+      if (lane == 0) pos_out[p] = pos0 + j;
+      const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<long long>(p / k) * H);
+      uint4* out = reinterpret_cast<uint4*>(base + static_cast<long long>(j) * H);
+      for (int c = lane; c < H / 8; c += 128) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (c + 32 * u < H / 8) v[u] = src[c + 32 * u];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (c + 32 * u < H / 8) out[c + 32 * u] = v[u];
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned* c = reinterpret_cast<unsigned*>(reinterpret_cast<uint8_t*>(cnt.buf[d]) + cnt_off) + pos0 / 128;
+      const unsigned head = static_cast<unsigned>(min(n, 128 - (pos0 & 127)));
+      asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(c), "r"(head) : "memory");
+      if (static_cast<unsigned>(n) > head)
+        asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(c + 1), "r"(static_cast<unsigned>(n) - head) : "memory");
+    }
+  }
 }
 
 // fp8 payload: one warp per pair, one 128-column group per iteration (lane = 4 columns). The
@@ -628,6 +715,31 @@ PRB_API int prb_ep_push(const void* x, const int* topk_idx, const int* slot, con
       reinterpret_cast<const __nv_bfloat16*>(x), topk_idx, slot, local_off, send_base, pos_in, scale,
       ep_peers(dst_peers, R), ep_peers(flag_peers, R), pos_out, done_counter, num_pairs, k, H, E / R, rank, R, kind, epoch,
       cap_rows, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Per-block dispatch (see ep_prepare_kernel / ep_push_blocks_kernel). cnt_peers: the arrival counters inside the
+// symmetric buffers; cnt_off: byte offset of the parity in use. The push may run on a stream of its own.
+PRB_API int prb_ep_prepare(void* buf, const int* hist, const int* expert_offset, int* block_rows, void* zero_cnt,
+                           int max_blocks, int rank, int R, int E, int H, void* stream) {
+  if (R > prb::kEpMaxRanks || (H % 8) || E % R) return -2;
+  prb::ep_prepare_kernel<<<E / R, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<__nv_bfloat16*>(buf), hist, expert_offset, block_rows, reinterpret_cast<unsigned*>(zero_cnt),
+      max_blocks, rank, R, E, H);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+PRB_API int prb_ep_push_blocks(const void* x, const int* row_src, const int* local_block_expert, const int* local_off,
+                               const int* local_total, const int* counts, const int* send_base,
+                               void* const* dst_peers, void* const* cnt_peers, long long cnt_off, int* pos_out,
+                               int max_local_blocks, int k, int H, int E, int rank, int R, int cap_rows, int* status,
+                               void* stream) {
+  if (R > prb::kEpMaxRanks || (H % 8) || E % R || (cnt_off % 4)) return -2;
+  if (max_local_blocks <= 0) return 0;
+  const int grid = max_local_blocks < 148 * 4 ? max_local_blocks : 148 * 4;
+  prb::ep_push_blocks_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), row_src, local_block_expert, local_off, local_total, counts, send_base,
+      ep_peers(dst_peers, R), ep_peers(cnt_peers, R), cnt_off, pos_out, k, H, E / R, rank, R, cap_rows, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

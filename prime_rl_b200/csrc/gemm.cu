@@ -62,6 +62,14 @@ struct GemmParams {
   unsigned ag_target = 0;
   int ag_rank = 0, ag_ranks = 1, ag_rows = 0;
   long long ag_row_bytes = 0;
+  // grouped mode fed by a peer-memory dispatch: rows of M block b are complete once blk_arrive[b] (bumped by the
+  // senders with release-adds at system scope) has reached blk_rows[b]; the producer waits per block (bounded)
+  const unsigned* blk_arrive = nullptr;
+  const int* blk_rows = nullptr;
+  // split-K (decode-sized dense GEMMs): the K blocks of one output tile are dealt to sk_splits CTAs, split ks
+  // stores its fp32 partial tile to rows [ks * M, (ks + 1) * M) of a workspace (C points there) and a second
+  // kernel adds the partials in split order
+  int sk_splits = 1;
   const int* expert_offset;  // K-grouped mode
   int num_experts;
   // fused LM head (logprob / entropy) extras
@@ -137,6 +145,34 @@ struct SchedGrouped : SchedDense {
       }
     }
     return false;
+  }
+};
+
+// Split-K: tile = (m_blk, n_blk, k split); split ks writes to rows ks * M .. of the workspace (c_row0). Every
+// split owns at least one K block (the host sees to it).
+struct SchedSplitK {
+  static constexpr int kGatherWarps = 0;
+  int tile, num_tiles, tiles_m, tiles_n, nkb_total, per;
+  __device__ SchedSplitK(const GemmParams& p, int bn)
+      : tile(blockIdx.x - gridDim.x), tiles_m((p.M + kBM - 1) / kBM), tiles_n((p.N + bn - 1) / bn),
+        nkb_total((p.K + kBK - 1) / kBK) {
+    per = (nkb_total + p.sk_splits - 1) / p.sk_splits;
+    num_tiles = tiles_m * tiles_n * p.sk_splits;
+  }
+  __device__ bool next(const GemmParams& p, int& m_blk, int& n_blk, int& brow, bool& last_of_item, int& kb0,
+                       int& nkb, long long& c_row0) {
+    tile += gridDim.x;
+    if (tile >= num_tiles) return false;
+    const int mn = tile / p.sk_splits;
+    const int ks = tile - mn * p.sk_splits;
+    m_blk = mn % tiles_m;
+    n_blk = mn / tiles_m;
+    kb0 = ks * per;
+    nkb = min(per, nkb_total - kb0);
+    c_row0 = static_cast<long long>(ks) * p.M;
+    brow = 0;
+    last_of_item = true;
+    return true;
   }
 };
 
@@ -287,6 +323,29 @@ __device__ bool ag_wait_block(const GemmParams& p, int bn, int n_blk) {
     if (v >= want) {
       asm volatile("fence.proxy.async;" ::: "memory");
       return true;
+    }
+    __nanosleep(64);
+  }
+  if (p.status) atomicCAS(p.status, 0, kTimeoutPeerFlag);
+  return false;
+}
+
+// Producer side of a GEMM whose A rows are being written by other GPUs: wait (bounded) until every row of M block
+// m_blk has landed, then order the async-proxy reads (TMA) after the generic-proxy writes.
+__device__ bool blk_wait(const GemmParams& p, int m_blk) {
+  const unsigned want = static_cast<unsigned>(p.blk_rows[m_blk]);
+  const unsigned* flag = p.blk_arrive + m_blk;
+  const long long t0 = clock64();
+  for (unsigned spin = 0;; ++spin) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= want) {
+      asm volatile("fence.proxy.async;" ::: "memory");
+      return true;
+    }
+    if ((spin & 0xff) == 0xff) {
+      if (p.status && *reinterpret_cast<volatile int*>(p.status) != 0) return false;
+      if (clock64() - t0 > 4000000000LL) break;   // about 2 s
     }
     __nanosleep(64);
   }
@@ -547,6 +606,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               break;
             }
           }
+          if constexpr (std::is_same<Sched, SchedGrouped>::value) {
+            if (it == 0 && p.blk_arrive != nullptr && !blk_wait(p, m_blk)) {
+              ok = false;
+              break;
+            }
+          }
           mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
           uint8_t* a_dst = smem + s * Cfg::STAGE_BYTES;
           uint8_t* b_dst = a_dst + Cfg::A_BYTES;
@@ -684,6 +749,95 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
+template <int BN, bool B_MN>
+static int launch_gemm_splitk(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
+                              cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  auto kern = gemm_bf16_kernel<BN, false, B_MN, SchedSplitK, EpiStore>;
+  static prb::DeviceOnce configured;
+  if (configured.pending()) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return -10;
+    configured.mark();
+  }
+  const int items = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN) * p.sk_splits;
+  const int grid = items < sm_count() ? items : sm_count();
+  kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Adds the split-K partials in split order and applies the GEMM's alpha / beta / output type:
+// C[m, n] = alpha * sum_s ws[s][m][n] + beta * C[m, n]. One float4 of a workspace row per thread and step.
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ ws, int splits, int M, int N, void* __restrict__ C, long long ldc,
+                     int out_fp32, float alpha, float beta) {
+  const int n4 = N / 4;
+  const long long total = static_cast<long long>(M) * n4;
+  const long long plane = static_cast<long long>(M) * N;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = i / n4;
+    const int col = static_cast<int>(i - row * n4) * 4;
+    const float* src = ws + row * N + col;
+    float4 acc = __ldcg(reinterpret_cast<const float4*>(src));
+    for (int s2 = 1; s2 < splits; ++s2) {
+      const float4 t = __ldcg(reinterpret_cast<const float4*>(src + s2 * plane));
+      acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+    }
+    float o[4] = {alpha * acc.x, alpha * acc.y, alpha * acc.z, alpha * acc.w};
+    if (out_fp32) {
+      float* dst = reinterpret_cast<float*>(C) + row * ldc + col;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) dst[j] = (beta != 0.f) ? o[j] + beta * dst[j] : o[j];
+    } else {
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(C) + row * ldc + col;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        dst[j] = __float2bfloat16((beta != 0.f) ? o[j] + beta * __bfloat162float(dst[j]) : o[j]);
+    }
+  }
+}
+
+// Tile width and K split for a dense GEMM with few output tiles. Every CTA streams its operand slabs through
+// its own SM's L2 port (about 80 GB/s), so: time = fixed + waves x slab bytes of one work item / that rate, plus,
+// when split, the second kernel that adds the partials. Returns splits (1 = no split) and sets bn. N % 4 == 0
+// is needed for a split (the partials are read as float4).
+struct SplitKWorkspace {
+  float* ws;
+  long long ws_bytes;
+  int force_splits;
+};
+static int choose_splitk(int M, int N, int K, int force_bn, const SplitKWorkspace& w, int& bn_out) {
+  const int sms = sm_count();
+  const int nkb = (K + kBK - 1) / kBK;
+  const long long tiles_m = (M + kBM - 1) / kBM;
+  double best = 1e30;
+  int best_bn = bn_out, best_s = 1;
+  const int bns[3] = {256, 128, 64};
+  for (int bi = 0; bi < 3; ++bi) {
+    const int bn = bns[bi];
+    if (force_bn > 0 && bn != force_bn) continue;
+    if (bn > 64 && bn / 2 >= N) continue;               // a tile twice as wide as the output
+    const long long tiles = tiles_m * ((N + bn - 1) / bn);
+    for (int s = 1; s <= 8; ++s) {
+      if (w.force_splits > 0 && s != w.force_splits) continue;
+      const int per = (nkb + s - 1) / s;
+      if (s > 1 && (per < 2 || (nkb + per - 1) / per != s)) continue;     // no empty split
+      if (s > 1 && ((N % 4) || static_cast<long long>(s) * M * N * 4 > w.ws_bytes)) continue;
+      const long long waves = (tiles * s + sms - 1) / sms;
+      double t = 3.0 + waves * per * (kBM + bn) * kBK * 2.0 / 80e3;
+      if (s > 1) t += 6.0 + (s + 1.0) * M * N * 4.0 / 3e6;                // second launch + its traffic at 3 TB/s
+      if (t < best) {
+        best = t;
+        best_bn = bn;
+        best_s = s;
+      }
+    }
+  }
+  bn_out = best_bn;
+  return best_s;
+}
+
 template <bool A_MN, bool B_MN, bool GROUPED>
 static int dispatch_bn(int bn, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmA2,
                        const CUtensorMap& tmB2, const GemmParams& p, cudaStream_t stream) {
@@ -704,7 +858,9 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
                           long long ldc, int a_mn, int b_mn, int out_fp32, float alpha, float beta,
                           const int* block_expert, int num_experts, int b_rows_per_expert, int force_bn,
                           const void* A2, const void* B2, int K2, long long lda2, long long ldb2,
-                          int b2_rows_per_expert, int* status, void* stream_, const int* row_valid = nullptr) {
+                          int b2_rows_per_expert, int* status, void* stream_, const int* row_valid = nullptr,
+                          const prb::SplitKWorkspace* sk = nullptr, const unsigned* blk_arrive = nullptr,
+                          const int* blk_rows = nullptr) {
   using namespace prb;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0) return 0;
@@ -726,6 +882,10 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
     if (t256 < sm_count() && N % 256 != 0) bn = 128;
   }
   if (b_mn && bn < 64) bn = 64;
+  int splits = 1;
+  if (sk != nullptr && !grouped && !a_mn && A2 == nullptr && row_valid == nullptr &&
+      (long long)((M + 127) / 128) * ((N + 255) / 256) * 2 <= sm_count())
+    splits = choose_splitk(M, N, K, force_bn, *sk, bn);
 
   CUtensorMap tmA, tmB;
   int rc;
@@ -768,6 +928,8 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
   p.k2_blocks = (A2 != nullptr && K2 > 0) ? (K2 + kBK - 1) / kBK : 0;
   p.b2_rows_per_expert = b2_rows_per_expert;
   p.row_valid = row_valid;
+  p.blk_arrive = grouped ? blk_arrive : nullptr;
+  p.blk_rows = blk_rows;
   p.expert_offset = nullptr; p.num_experts = 0;
   p.alpha = alpha; p.beta = beta;
   p.block_expert = block_expert;
@@ -776,6 +938,25 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
   p.num_splits = 0;
   p.labels = nullptr; p.inv_temp = nullptr; p.part_m = p.part_s = p.part_t = p.target_logit = nullptr;
   p.grad_logprob = nullptr; p.lse = nullptr;
+  if (splits > 1) {
+    // the GEMM proper writes fp32 partials (alpha = 1, beta = 0) to the workspace, split ks to rows ks * M ..
+    p.sk_splits = splits;
+    p.C = sk->ws; p.ldc = N; p.out_fp32 = 1; p.alpha = 1.f; p.beta = 0.f;
+    p.rows_total = static_cast<long long>(splits) * M;
+    int rc2;
+    switch (bn) {
+      case 256: rc2 = b_mn ? launch_gemm_splitk<256, true>(tmA, tmB, p, stream) : launch_gemm_splitk<256, false>(tmA, tmB, p, stream); break;
+      case 128: rc2 = b_mn ? launch_gemm_splitk<128, true>(tmA, tmB, p, stream) : launch_gemm_splitk<128, false>(tmA, tmB, p, stream); break;
+      default: rc2 = b_mn ? launch_gemm_splitk<64, true>(tmA, tmB, p, stream) : launch_gemm_splitk<64, false>(tmA, tmB, p, stream); break;
+    }
+    if (rc2) return rc2;
+    const long long items = static_cast<long long>(M) * (N / 4);
+    long long blocks = (items + 255) / 256;
+    if (blocks > 4LL * sm_count()) blocks = 4LL * sm_count();
+    splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(sk->ws, splits, M, N, C, ldc, out_fp32,
+                                                                           alpha, beta);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  }
 
 #define PRB_DISPATCH(AMN, BMN)                                                              \
   (grouped ? dispatch_bn<AMN, BMN, true>(bn, tmA, tmB, tmA2, tmB2, p, stream)                           \
@@ -793,6 +974,30 @@ PRB_API int prb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, i
                           int* status, void* stream_) {
   return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_fp32, alpha, beta, block_expert, num_experts,
                         b_rows_per_expert, force_bn, nullptr, nullptr, 0, 0, 0, 0, status, stream_);
+}
+
+// Grouped GEMM whose A rows arrive from other GPUs while it runs: M block b is loaded once blk_arrive[b] >=
+// blk_rows[b] (uint32 / int32 per 128-row block; see csrc/ep_p2p.cu: ep_push_blocks_kernel).
+PRB_API int prb_gemm_bf16_grouped_arrive(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                         long long ldb, long long ldc, int b_mn, int out_fp32,
+                                         const int* block_expert, int num_experts, int b_rows_per_expert,
+                                         const void* blk_arrive, const int* blk_rows, int* status, void* stream_) {
+  if (block_expert == nullptr || blk_arrive == nullptr || blk_rows == nullptr) return -2;
+  return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, 0, b_mn, out_fp32, 1.f, 0.f, block_expert, num_experts,
+                        b_rows_per_expert, 0, nullptr, nullptr, 0, 0, 0, 0, status, stream_, nullptr, nullptr,
+                        reinterpret_cast<const unsigned*>(blk_arrive), blk_rows);
+}
+
+// Dense GEMM with few rows (decode): may split the reduction over several CTAs per output tile, whose fp32
+// partials a second kernel adds in split order (the result does not depend on timing). `ws` (ws_bytes, 16-byte
+// aligned) is scratch that calls on one stream may share; force_splits > 0 pins the split count (1 = one kernel).
+PRB_API int prb_gemm_bf16_splitk(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                 long long ldb, long long ldc, int b_mn, int out_fp32, float alpha, float beta,
+                                 void* ws, long long ws_bytes, int force_bn, int force_splits, int* status,
+                                 void* stream_) {
+  prb::SplitKWorkspace w{reinterpret_cast<float*>(ws), ws_bytes, force_splits};
+  return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, 0, b_mn, out_fp32, alpha, beta, nullptr, 0, 0, force_bn,
+                        nullptr, nullptr, 0, 0, 0, 0, status, stream_, nullptr, &w);
 }
 
 // Same as prb_gemm_bf16, but rows r of C with row_valid[r] < 0 are computed and not stored: the padding rows that

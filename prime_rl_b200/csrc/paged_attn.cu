@@ -402,6 +402,76 @@ paged_prefix_mma_kernel(const PagedParams p) {
     if (nxt < pg_end) { issue_stage(nxt, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
     __syncthreads();                                          // every thread's copies of this stage have landed
     const int n_pages = min(kPxPages, pg_end - pg0);
+    if (n_pages == kPxPages) {
+      // a full stage: one softmax step over its 64 keys (8 independent score tiles, one rescale of the output)
+      static_assert(kPxPages == 4, "the full-stage path is written for four pages of 16 keys");
+      float s[8][4];
+#pragma unroll
+      for (int t = 0; t < 8; ++t) s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
+      {
+        const int key = 8 * (lane >> 4) + (lane & 7);
+        const int hi = (lane >> 3) & 1;
+#pragma unroll
+        for (int page = 0; page < 4; ++page) {
+          const uint32_t ks = sbase + buf * kPxStageBytes + page * kPxPageBytes;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4(ks + key * 256 + (((2 * kk + hi) ^ (key & 7)) << 4), b0, b1, b2, b3);
+            mma_16816(s[2 * page], qa[kk][0], qb[kk][0], qa[kk][1], qb[kk][1], b0, b1);
+            mma_16816(s[2 * page + 1], qa[kk][0], qb[kk][0], qa[kk][1], qb[kk][1], b2, b3);
+          }
+        }
+      }
+      float mxa = -INFINITY, mxb = -INFINITY;
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        mxa = fmaxf(mxa, fmaxf(s[t][0], s[t][1]));
+        mxb = fmaxf(mxb, fmaxf(s[t][2], s[t][3]));
+      }
+      mxa = fmaxf(mxa, __shfl_xor_sync(0xffffffffu, mxa, 1));
+      mxa = fmaxf(mxa, __shfl_xor_sync(0xffffffffu, mxa, 2));
+      mxb = fmaxf(mxb, __shfl_xor_sync(0xffffffffu, mxb, 1));
+      mxb = fmaxf(mxb, __shfl_xor_sync(0xffffffffu, mxb, 2));
+      const float na = fmaxf(m_a, mxa * scale_log2), nb = fmaxf(m_b, mxb * scale_log2);
+      const float alpha_a = exp2f(m_a - na), alpha_b = exp2f(m_b - nb);
+      float rsa = 0.f, rsb = 0.f;
+      uint32_t pa[8], pb[8];
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        const float a0 = exp2f(s[t][0] * scale_log2 - na), a1 = exp2f(s[t][1] * scale_log2 - na);
+        const float b0 = exp2f(s[t][2] * scale_log2 - nb), b1 = exp2f(s[t][3] * scale_log2 - nb);
+        rsa += a0 + a1;
+        rsb += b0 + b1;
+        pa[t] = pack_bf16(a0, a1);
+        pb[t] = pack_bf16(b0, b1);
+      }
+      rsa += __shfl_xor_sync(0xffffffffu, rsa, 1);
+      rsa += __shfl_xor_sync(0xffffffffu, rsa, 2);
+      rsb += __shfl_xor_sync(0xffffffffu, rsb, 1);
+      rsb += __shfl_xor_sync(0xffffffffu, rsb, 2);
+      l_a = l_a * alpha_a + rsa; m_a = na;
+      l_b = l_b * alpha_b + rsb; m_b = nb;
+#pragma unroll
+      for (int n = 0; n < 16; ++n) {
+        o[n][0] *= alpha_a; o[n][1] *= alpha_a; o[n][2] *= alpha_b; o[n][3] *= alpha_b;
+      }
+      {
+        const int key = 8 * ((lane >> 3) & 1) + (lane & 7);
+        const int sub = lane >> 4;
+#pragma unroll
+        for (int page = 0; page < 4; ++page) {
+          const uint32_t vs = sbase + buf * kPxStageBytes + page * kPxPageBytes + kPmPage * kPdD * 2;
+#pragma unroll
+          for (int pr = 0; pr < 8; ++pr) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(vs + key * 256 + (((2 * pr + sub) ^ (key & 7)) << 4), b0, b1, b2, b3);
+            mma_16816(o[2 * pr], pa[2 * page], pb[2 * page], pa[2 * page + 1], pb[2 * page + 1], b0, b1);
+            mma_16816(o[2 * pr + 1], pa[2 * page], pb[2 * page], pa[2 * page + 1], pb[2 * page + 1], b2, b3);
+          }
+        }
+      }
+    } else
     for (int page = 0; page < n_pages; ++page) {
       const uint32_t ks = sbase + buf * kPxStageBytes + page * kPxPageBytes, vs = ks + kPmPage * kPdD * 2;
       float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};

@@ -182,3 +182,24 @@ def build_app(router: Router):
         return {"replicas": router.urls, "inflight": router.inflight, "served": router.served}
 
     return app
+
+
+def main(argv: list[str] | None = None) -> None:
+    """``python -m prime_rl_b200.engine.router --port 8000 --backends http://a:9000,http://b:9000``: the router as a
+    process of its own (multi-node serving: one router in front of the per-node servers)."""
+    import argparse
+
+    import uvicorn
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--host", default="0.0.0.0")
+    ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--backends", required=True, help="comma-separated base URLs of the engine servers")
+    ap.add_argument("--timeout", type=float, default=3600.0)
+    args = ap.parse_args(argv)
+    urls = [u for u in (x.strip() for x in args.backends.split(",")) if u]
+    uvicorn.run(build_app(Router(urls, timeout=args.timeout)), host=args.host, port=args.port, log_level="warning")
+
+
+if __name__ == "__main__":
+    main()

@@ -356,9 +356,18 @@ class GroupedExperts(nn.Module):
         xpq = moe_ops.permute_nopad(xq.view(torch.bfloat16), plan).view(torch.uint8)
         xps = moe_ops.permute_nopad(xs.view(torch.bfloat16), plan).view(torch.float32)
         valid = plan.row_src
-        gu = fp8_ops.fp8_gemm(xpq, xps, *self.fp8["gate_up_proj"], block_expert=plan.block_expert, row_valid=valid)
+        E = self.fp8["gate_up_proj"][0].shape[0]
+        few = T * plan.k < 64 * E and H <= 4096 and self.fp8["down_proj"][0].shape[-1] <= 4096
+        if few:
+            # decode: a handful of rows per expert, the 128-row blocks are mostly padding
+            rows = fp8_ops.count_block_rows(valid)
+            gu = fp8_ops.fp8_gemm_few_rows(xpq, xps, *self.fp8["gate_up_proj"], plan.block_expert, rows)
+        else:
+            gu = fp8_ops.fp8_gemm(xpq, xps, *self.fp8["gate_up_proj"], block_expert=plan.block_expert, row_valid=valid)
         h = act_ops.glu_rowmask(gu, valid, self.act, self.arch.swiglu_limit, self.arch.swiglu_alpha)
         hq, hs = fp8_ops.quantize_act(h, row_valid=valid)
+        if few:
+            return fp8_ops.fp8_gemm_few_rows(hq, hs, *self.fp8["down_proj"], plan.block_expert, rows)
         return fp8_ops.fp8_gemm(hq, hs, *self.fp8["down_proj"], block_expert=plan.block_expert, row_valid=valid)
 
     def supports_row_mask(self, x: torch.Tensor) -> bool:
@@ -369,10 +378,21 @@ class GroupedExperts(nn.Module):
                 and self.lora_gate_up is None and self.lora_down is None and self.act != act_ops.SILU_CLAMPED
                 and self.gate_up_proj.dtype == torch.bfloat16)
 
+    def supports_block_ready(self, x: torch.Tensor) -> bool:
+        """The first projection is the plain bf16 grouped GEMM, whose loader can wait per 128-row block for rows
+        that other GPUs are still writing (``forward(block_ready=...)``)."""
+        return (x.is_cuda and x.dtype == torch.bfloat16 and self.lora_gate_up is None
+                and self.gate_up_proj.dtype == torch.bfloat16
+                and not (self.fp8 is not None and not torch.is_grad_enabled()))
+
     def forward(self, xp: torch.Tensor, block_expert: torch.Tensor, expert_offset: torch.Tensor,
-                out: torch.Tensor | None = None, row_valid: torch.Tensor | None = None) -> torch.Tensor:
+                out: torch.Tensor | None = None, row_valid: torch.Tensor | None = None,
+                block_ready: tuple[torch.Tensor, torch.Tensor] | None = None) -> torch.Tensor:
         """``out`` (optional, ``[P, H]`` bf16): memory the last projection writes into. ``row_valid``
-        (int32 per permuted row, < 0 = padding; only where ``supports_row_mask``): those rows are skipped."""
+        (int32 per permuted row, < 0 = padding; only where ``supports_row_mask``): those rows are skipped.
+        ``block_ready = (arrived, expected)`` (only where ``supports_block_ready``): per 128-row block of ``xp``,
+        a counter that its writers raise and the row count at which the block is complete."""
+        assert block_ready is None or (row_valid is None and self.supports_block_ready(xp))
         if row_valid is not None:
             gu = ops.gemm(xp, self.gate_up_proj, block_expert=block_expert, row_valid=row_valid)
             h = act_ops.glu_rowmask(gu, row_valid, self.act, self.arch.swiglu_limit, self.arch.swiglu_alpha)
@@ -394,7 +414,7 @@ class GroupedExperts(nn.Module):
             gu = lora_ops.lora_grouped_linear(xp, self.gate_up_proj, l.lora_A, list(l.lora_B), l.scale, block_expert,
                                               expert_offset)
         else:
-            gu = ops.grouped_linear(xp, self.gate_up_proj, block_expert, expert_offset)
+            gu = ops.grouped_linear(xp, self.gate_up_proj, block_expert, expert_offset, block_ready=block_ready)
         gu = self._biased(gu, self.gate_up_proj_bias, block_expert)
         h = ops.glu(gu, self.act, self.arch.swiglu_limit, self.arch.swiglu_alpha)
         if self.down_proj_bias is not None:

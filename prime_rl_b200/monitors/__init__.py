@@ -125,4 +125,8 @@ def setup(config, run_dir: Path, producer: str, *, is_master: bool = True, run_c
                 mons.append(WandbMonitor(config.wandb, run_dir, producer, run_config))
             except Exception as e:
                 get_logger().warning(f"wandb monitor disabled: {e}")
+        if getattr(config, "prime", None) is not None:
+            from .prime import PrimeMonitor
+
+            mons.append(PrimeMonitor(config.prime, producer, run_config))     # a configured tracker must work: raises
     return MultiMonitor(mons, enabled=is_master)

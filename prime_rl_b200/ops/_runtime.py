@@ -40,6 +40,17 @@ def stream_ptr(device: torch.device | None = None) -> int:
     return torch.cuda.current_stream(idx).cuda_stream
 
 
+_sms: dict[int, int] = {}
+
+
+def sm_count(device: torch.device | None = None) -> int:
+    idx = device.index if device is not None and device.index is not None else torch.cuda.current_device()
+    n = _sms.get(idx)
+    if n is None:
+        n = _sms[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return n
+
+
 def ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 

@@ -18,9 +18,19 @@ from . import _runtime as rt
 from . import stash
 
 
-# Inference-only dispatch of small plain GEMMs (no groups, no fused epilogue, M <= SMALL_M_ROWS) to cuBLAS.
-SMALL_M_LIBRARY = True
-SMALL_M_ROWS = 512
+# Dense GEMMs whose 128 x 256 output tiles cover at most half of the SMs (decode-sized projections) may split
+# their reduction over several CTAs per tile (a second kernel adds the fp32 partials); the scratch for the
+# partials is kept per device and stream.
+SPLITK_WS_BYTES = 32 << 20
+_splitk_ws: dict = {}
+
+
+def _splitk_scratch(device: torch.device) -> torch.Tensor:
+    key = (device.index, rt.stream_ptr(device))
+    got = _splitk_ws.get(key)
+    if got is None:
+        got = _splitk_ws[key] = torch.empty(SPLITK_WS_BYTES, dtype=torch.uint8, device=device)
+    return got
 
 
 def gemm_ref(a, b, *, a_mn=False, b_mn=False, out_dtype=None, alpha=1.0, beta=0.0, out=None):
@@ -53,8 +63,11 @@ def gemm(
     force_bn: int = 0,
     ext: tuple[torch.Tensor, torch.Tensor] | None = None,
     row_valid: torch.Tensor | None = None,
+    splitk: int = 0,
+    block_ready: tuple[torch.Tensor, torch.Tensor] | None = None,
 ) -> torch.Tensor:
-    """C = alpha * A.B + beta * C. Grouped mode when ``block_expert`` is given: ``b`` is the
+    """C = alpha * A.B + beta * C. ``splitk``: pin the number of reduction splits of a small dense GEMM (0 = the
+    kernel's cost model decides, 1 = none). Grouped mode when ``block_expert`` is given: ``b`` is the
     stacked expert weight ``[E, rows, cols]`` and ``n`` the output width. ``ext = (a2, b2)`` adds
     ``a2.b2`` in the same pass (``a2``: [M, K2]; ``b2`` laid out like ``b`` with reduction K2)."""
     if not a.is_cuda or a.dtype != torch.bfloat16:
@@ -95,16 +108,6 @@ def gemm(
         # per-head gate) are not worth a copy into padded buffers
         return gemm_ref(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=out_dtype or (out.dtype if out is not None else None),
                         alpha=alpha, beta=beta, out=out)
-    if (SMALL_M_LIBRARY and M <= SMALL_M_ROWS and not grouped and ext is None and row_valid is None and not a_mn
-            and not b_mn and alpha == 1.0 and beta == 0.0 and not torch.is_grad_enabled()):
-        # decode-sized plain projections in inference: the library GEMM has the lower fixed cost there
-        # (13 us against 27 us for 256 x 5120 x 2048); everything with gradients, large M, groups or fused
-        # epilogues stays on the tcgen05 kernel
-        want = out_dtype or (out.dtype if out is not None else torch.bfloat16)
-        if want == torch.bfloat16:
-            return torch.matmul(a, b.t(), out=out) if out is not None else torch.matmul(a, b.t())
-        if want == torch.float32 and out is None:
-            return torch.mm(a, b.t(), out_dtype=torch.float32)
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=a.device)
         assert beta == 0.0
@@ -130,6 +133,19 @@ def gemm(
         )
         rt.check(rc, "prb_gemm_bf16_ext")
         return out
+    if block_ready is not None:
+        # grouped GEMM over rows that other GPUs are still writing: the loader waits per 128-row block until
+        # arrived[b] >= expected[b]
+        arrived, expected = block_ready
+        assert grouped and not a_mn and ext is None and row_valid is None and alpha == 1.0 and beta == 0.0
+        assert arrived.dtype == torch.int32 and expected.dtype == torch.int32 and arrived.numel() * 128 >= M
+        rc = rt.lib().prb_gemm_bf16_grouped_arrive(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), ldb, out.stride(0), int(b_mn),
+            int(out.dtype == torch.float32), block_expert.data_ptr(), int(num_experts), int(b_rows_per_expert),
+            arrived.data_ptr(), expected.data_ptr(), status.data_ptr(), rt.stream_ptr(a.device),
+        )
+        rt.check(rc, "prb_gemm_bf16_grouped_arrive")
+        return out
     if row_valid is not None:
         # inference-only: rows with row_valid < 0 (int32 per row of C) are not stored
         assert row_valid.dtype == torch.int32 and row_valid.numel() >= M and not a_mn
@@ -140,6 +156,16 @@ def gemm(
             row_valid.data_ptr(), status.data_ptr(), rt.stream_ptr(a.device),
         )
         rt.check(rc, "prb_gemm_bf16_rowmask")
+        return out
+    if not grouped and not a_mn and K >= 512 and -(-M // 128) * -(-N // 256) * 2 <= rt.sm_count(a.device):
+        # too few output tiles for the SMs: let the kernel split the reduction (it decides by its cost model)
+        ws = _splitk_scratch(a.device)
+        rc = rt.lib().prb_gemm_bf16_splitk(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), ldb, out.stride(0), int(b_mn),
+            int(out.dtype == torch.float32), float(alpha), float(beta), ws.data_ptr(), ws.numel(),
+            int(force_bn), int(splitk), status.data_ptr(), rt.stream_ptr(a.device),
+        )
+        rt.check(rc, "prb_gemm_bf16_splitk")
         return out
     rc = rt.lib().prb_gemm_bf16(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), ldb, out.stride(0),
@@ -224,14 +250,16 @@ class _GroupedLinear(torch.autograd.Function):
     """Per-expert y = x @ w[e]^T over 128-row blocks; x is the permuted, padded row space."""
 
     @staticmethod
-    def forward(ctx, x, w, block_expert, expert_offset, out=None):
+    def forward(ctx, x, w, block_expert, expert_offset, out=None, block_ready=None):
         ctx.save_for_backward(x, w, block_expert, expert_offset)
         ctx.grad_acc = grad_accumulator(w) if w.requires_grad else None
         # a caller that owns the memory of the input gradient (the peer-memory EP dispatcher)
         # hangs it on the input tensor; the backward then writes straight into it
         ctx.grad_out = getattr(x, "_grad_out_buf", None)
         if out is not None:          # the caller's buffer is shared between layers: its contents cannot be kept
-            return gemm(x, w, block_expert=block_expert, out=out)
+            return gemm(x, w, block_expert=block_expert, out=out, block_ready=block_ready)
+        if block_ready is not None:  # must run: it is the wait for rows that peers are still writing
+            return gemm(x, w, block_expert=block_expert, block_ready=block_ready)
         return stash.run("grouped_mm", lambda: gemm(x, w, block_expert=block_expert))
 
     @staticmethod
@@ -248,11 +276,11 @@ class _GroupedLinear(torch.autograd.Function):
                 grouped_wgrad(dy, x, expert_offset, w.shape[0], out=ctx.grad_acc, beta=1.0)
             else:
                 dw = grouped_wgrad(dy, x, expert_offset, w.shape[0])
-        return dx, dw, None, None, None
+        return dx, dw, None, None, None, None
 
 
-def grouped_linear(x, w, block_expert, expert_offset, out=None):
-    return _GroupedLinear.apply(x, w, block_expert, expert_offset, out)
+def grouped_linear(x, w, block_expert, expert_offset, out=None, block_ready=None):
+    return _GroupedLinear.apply(x, w, block_expert, expert_offset, out, block_ready)
 
 
 def grouped_wgrad(dy: torch.Tensor, x: torch.Tensor, expert_offset: torch.Tensor, num_experts: int,

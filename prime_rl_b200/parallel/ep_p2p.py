@@ -32,6 +32,7 @@ import torch.distributed as dist
 
 from ..ops import _runtime as rt
 from ..ops import moe as moe_ops
+from ..ops import stash
 from .symm import SymmetricBuffer
 
 K_HIST, K_DATA_X, K_OUT_Y, K_DATA_G, K_OUT_DX = range(5)
@@ -49,7 +50,10 @@ class _Shared:
         self.off_x, self.off_y, self.off_g, self.off_dx = 0, row_bytes, 2 * row_bytes, 3 * row_bytes
         self.off_hist = 4 * row_bytes
         self.off_flags = self.off_hist + R * E * 4
-        total = self.off_flags + 5 * R * 4
+        # arrival counters of the per-block dispatch: [parity][128-row block of xbuf]
+        self.max_blocks = cap_rows // 128
+        self.off_cnt = (self.off_flags + 5 * R * 4 + 15) // 16 * 16
+        total = self.off_cnt + 2 * self.max_blocks * 4
         total = (total + 255) // 256 * 256
         self.fp8 = fp8
         if fp8:
@@ -69,6 +73,10 @@ class _Shared:
         self.p_x, self.p_y = m.offset_ptrs(self.off_x), m.offset_ptrs(self.off_y)
         self.p_g, self.p_dx = m.offset_ptrs(self.off_g), m.offset_ptrs(self.off_dx)
         self.p_hist, self.p_flags = m.offset_ptrs(self.off_hist), m.offset_ptrs(self.off_flags)
+        self.cnt = m.local(torch.int32, self.off_cnt, 2 * self.max_blocks).view(2, self.max_blocks)
+        self.p_cnt = m.offset_ptrs(self.off_cnt)
+        self.blk_epoch = 0
+        self.side = torch.cuda.Stream(device=device)
         if fp8:
             self.qbuf = m.local(torch.uint8, self.off_q, cap_rows * H).view(cap_rows, H)
             self.sbuf = m.local(torch.float32, self.off_s, cap_rows * (H // 128)).view(cap_rows, H // 128)
@@ -101,7 +109,7 @@ def release_shared() -> None:
 class _Route:
     """Per-call routing state shared by the two autograd functions."""
     __slots__ = ("sh", "idx", "slot", "local_off", "send_base", "pos", "hist", "expert_offset", "block_expert",
-                 "T", "k", "ep_y")
+                 "T", "k", "ep_y", "local", "counts", "block_rows", "push_done")
 
 
 def _status(dev):
@@ -110,9 +118,35 @@ def _status(dev):
 
 class _Dispatch(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, route: _Route):
+    def forward(ctx, x, route: _Route, per_block: bool = False):
         sh, lib, dev = route.sh, rt.lib(), x.device
         x = x.contiguous()
+        ctx.route = route
+        if per_block:
+            # no global wait: the owner prepares its buffer, the rows leave on a side stream in the order of the
+            # owners' buffers, and the grouped GEMM that follows waits per 128-row block on the arrival counters
+            sh.blk_epoch += 1
+            par = sh.blk_epoch & 1
+            local = route.local
+            route.block_rows = torch.empty(sh.max_blocks, dtype=torch.int32, device=dev)
+            rt.check(lib.prb_ep_prepare(sh.xbuf.data_ptr(), route.hist.data_ptr(), route.expert_offset.data_ptr(),
+                                        route.block_rows.data_ptr(), sh.cnt[1 - par].data_ptr(), sh.max_blocks,
+                                        sh.rank, sh.R, sh.E, sh.H, rt.stream_ptr(dev)), "prb_ep_prepare")
+            main = torch.cuda.current_stream(dev)
+            sh.side.wait_stream(main)
+            with torch.cuda.stream(sh.side):
+                rt.check(lib.prb_ep_push_blocks(x.data_ptr(), local.row_src.data_ptr(), local.block_expert.data_ptr(),
+                                                local.expert_offset.data_ptr(), local.total_rows.data_ptr(),
+                                                route.counts.data_ptr(), route.send_base.data_ptr(), sh.p_x, sh.p_cnt,
+                                                par * sh.max_blocks * 4, route.pos.data_ptr(),
+                                                local.block_expert.numel(), route.k, sh.H, sh.E, sh.rank, sh.R, sh.cap,
+                                                _status(dev), rt.stream_ptr(dev)), "prb_ep_push_blocks")
+                route.push_done = torch.cuda.Event()
+                route.push_done.record(sh.side)
+            x.record_stream(sh.side)
+            xin = sh.xbuf.view(sh.cap, sh.H)
+            xin._blk_ready = (sh.cnt[par], route.block_rows)
+            return xin
         ep = sh.next_epoch(K_DATA_X)
         if sh.fp8:
             rt.check(lib.prb_ep_push_fp8(x.data_ptr(), route.idx.data_ptr(), route.slot.data_ptr(),
@@ -133,7 +167,6 @@ class _Dispatch(torch.autograd.Function):
             rt.check(lib.prb_ep_recv(sh.xbuf.data_ptr(), route.hist.data_ptr(), route.expert_offset.data_ptr(),
                                      sh.flags.data_ptr(), sh.rank, sh.R, sh.E, sh.H, K_DATA_X, ep, _status(dev),
                                      rt.stream_ptr(dev)), "prb_ep_recv")
-        ctx.route = route
         xin = sh.xbuf.view(sh.cap, sh.H)         # a fresh tensor object over the shared buffer
         return xin
 
@@ -149,13 +182,15 @@ class _Dispatch(torch.autograd.Function):
         rt.check(lib.prb_ep_pull(sh.p_dx, route.idx.data_ptr(), route.pos.data_ptr(), None, None, dx.data_ptr(), None,
                                  sh.flags.data_ptr(), route.T, route.k, sh.H, sh.E, sh.R, K_OUT_DX, ep, _status(dev),
                                  rt.stream_ptr(dev)), "prb_ep_pull")
-        return dx, None
+        return dx, None, None
 
 
 class _Combine(torch.autograd.Function):
     @staticmethod
     def forward(ctx, yp, w, route: _Route):
         sh, lib, dev = route.sh, rt.lib(), yp.device
+        if route.push_done is not None:          # the pull reads the positions the side-stream push wrote
+            torch.cuda.current_stream(dev).wait_event(route.push_done)
         if yp.data_ptr() != sh.ybuf.data_ptr():
             sh.ybuf[:yp.shape[0]].copy_(yp)
         ep = sh.next_epoch(K_OUT_Y)
@@ -199,10 +234,13 @@ class P2PDispatcher:
     kernel status word (``ops._runtime.check_status``)."""
 
     def __init__(self, group, ep: int, num_experts: int, capacity_factor: float = 2.0, max_tokens: int | None = None,
-                 payload: str = "bf16"):
+                 payload: str = "bf16", per_block: bool = True):
         if payload not in ("bf16", "fp8"):
             raise ValueError("payload must be 'bf16' or 'fp8'")
         self.payload = payload
+        # per_block: the forward dispatch overlaps the first expert GEMM (rows pushed on a side stream, the GEMM's
+        # loader waits per 128-row block); used where the experts run their plain bf16 grouped GEMM
+        self.per_block = per_block
         self.group, self.ep, self.E = group, ep, num_experts
         self.E_local = num_experts // ep
         self.capacity_factor = capacity_factor
@@ -234,6 +272,7 @@ class P2PDispatcher:
         local = moe_ops.build_plan(idx, counts, self.E)          # rank of every pair inside its expert
         route = _Route()
         route.sh, route.idx, route.slot, route.local_off, route.T, route.k = sh, idx, local.slot, local.expert_offset, T, k
+        route.local, route.counts, route.push_done, route.block_rows = local, counts, None, None
         ep = sh.next_epoch(K_HIST)
         rt.check(lib.prb_ep_hist(counts.data_ptr(), sh.p_hist, sh.p_flags, sh.rank, sh.R, sh.E, K_HIST, ep,
                                  rt.stream_ptr(dev)), "prb_ep_hist")
@@ -248,11 +287,18 @@ class P2PDispatcher:
                  "prb_ep_plan")
         route.hist = sh.hist.clone()                              # the table is reused by the next call
         route.pos = torch.empty(T, k, dtype=torch.int32, device=dev)
-        xin = _Dispatch.apply(x, route)
+        supports = getattr(experts, "supports_block_ready", None)
+        per_block = (self.per_block and self.payload == "bf16" and supports is not None and supports(x)
+                     and not stash.active())
+        xin = _Dispatch.apply(x, route, per_block)
         # the experts write their output and their input gradient straight into the symmetric buffers
         xin._grad_out_buf = sh.dxbuf
-        try:
-            yp = experts(xin, route.block_expert, route.expert_offset, out=sh.ybuf.view(sh.cap, sh.H))
-        except TypeError:                       # an experts callable without the `out` argument
-            yp = experts(xin, route.block_expert, route.expert_offset)
+        if per_block:
+            yp = experts(xin, route.block_expert, route.expert_offset, out=sh.ybuf.view(sh.cap, sh.H),
+                         block_ready=xin._blk_ready)
+        else:
+            try:
+                yp = experts(xin, route.block_expert, route.expert_offset, out=sh.ybuf.view(sh.cap, sh.H))
+            except TypeError:                       # an experts callable without the `out` argument
+                yp = experts(xin, route.block_expert, route.expert_offset)
         return _Combine.apply(yp, w, route)

@@ -1,11 +1,20 @@
 """sbatch script rendering for the ``rl`` / ``sft`` / ``inference`` launchers.
 
-The reference ships Jinja templates (src/prime_rl/templates/{single_node_rl,multi_node_rl,
-single_node_sft,multi_node_sft,inference}.sbatch.j2); the scripts here have the same structure
-(one job, ``srun`` per role, trainer under ``torch.distributed.run`` with the first train node as
-rendezvous host, inference replicas on their own nodes, orchestrator on the first train node or
-the first inference node) but are plain Python string assembly, so the launcher has no template
-dependency. A user template (``slurm.template_path``) is filled with ``str.format_map``.
+Scripts are Jinja templates under ``prime_rl_b200/templates`` (own text; same roles and the same template
+variable names as the reference's src/prime_rl/templates/{single_node_rl,multi_node_rl,single_node_sft,
+multi_node_sft,inference}.sbatch.j2, so a user template written for those variables, given as
+``slurm.template_path``, renders here too). Structure of a multi-node RL job:
+
+* one ``srun`` task per node, ``--kill-on-bad-exit=1``; the node's role follows from ``SLURM_PROCID``: the first
+  ``num_infer_nodes`` tasks serve inference (every node its own data-parallel replicas, one router on the first
+  node in front of all of them), the rest run one ``torch.distributed.run`` agent each;
+* the orchestrator and the environment servers run beside trainer rank 0, or on the last inference node with
+  ``deployment.orchestrator_on_inference``;
+* the trainer and the orchestrator leave marker files when they end cleanly; every node stays up until all
+  markers exist, so inference keeps serving while either still runs, and a component that fails ends the job
+  after ``slurm.cleanup_grace_period`` seconds (time for a checkpoint in flight elsewhere);
+* pids of everything a node starts are recorded under the run directory, and the next job ends exactly those
+  leftovers before it starts (nothing is matched by process name).
 """
 
 from __future__ import annotations
@@ -13,99 +22,119 @@ from __future__ import annotations
 import shlex
 from pathlib import Path
 
-
-def _header(slurm, nodes: int, gpus_per_node: int, log_dir: Path) -> list[str]:
-    lines = ["#!/bin/bash", f"#SBATCH --job-name={slurm.job_name}", f"#SBATCH --nodes={nodes}",
-             f"#SBATCH --gres=gpu:{gpus_per_node}", "#SBATCH --ntasks-per-node=1", "#SBATCH --exclusive",
-             f"#SBATCH --partition={slurm.partition}", f"#SBATCH --output={log_dir}/slurm-%j.out",
-             f"#SBATCH --error={log_dir}/slurm-%j.err"]
-    for key in ("nodelist", "exclude", "account", "time"):
-        val = getattr(slurm, key, None)
-        if val:
-            lines.append(f"#SBATCH --{key}={val}")
-    lines += ["", "set -euo pipefail", f"cd {shlex.quote(str(Path(slurm.project_dir).resolve()))}",
-              'NODES=($(scontrol show hostnames "$SLURM_JOB_NODELIST"))', 'HEAD=${NODES[0]}',
-              'export MASTER_ADDR=$HEAD', 'export MASTER_PORT=${MASTER_PORT:-29400}', 'export PYTHONUNBUFFERED=1']
-    if slurm.pre_run_command:
-        lines.append(slurm.pre_run_command)
-    return lines
+TEMPLATE_DIR = Path(__file__).resolve().parents[1] / "templates"
 
 
-def _cleanup(grace: int) -> list[str]:
-    return ["", "cleanup() {", "  trap - TERM INT EXIT", "  kill $(jobs -p) 2>/dev/null || true",
-            f"  sleep {min(grace, 30)}", "}", "trap cleanup TERM INT EXIT"]
+def _environment(extra_dir: Path | None = None):
+    import jinja2
+
+    search = [str(TEMPLATE_DIR)] + ([str(extra_dir)] if extra_dir else [])
+    env = jinja2.Environment(loader=jinja2.FileSystemLoader(search), undefined=jinja2.StrictUndefined,
+                             keep_trailing_newline=True, trim_blocks=False, lstrip_blocks=False)
+    env.filters["shq"] = lambda v: shlex.quote(str(v))
+    return env
 
 
-def _env_exports(env_vars: dict) -> list[str]:
-    return [f"export {k}={shlex.quote(str(v))}" for k, v in (env_vars or {}).items()]
+def _render(name: str, slurm, variables: dict) -> str:
+    """Renders the stock template ``name`` or, when ``slurm.template_path`` is set, the user's file (which may
+    ``{% include %}`` the stock pieces)."""
+    user = getattr(slurm, "template_path", None)
+    if user:
+        user = Path(user)
+        env = _environment(user.parent)
+        return env.from_string(user.read_text()).render(**variables)
+    return _environment().get_template(name).render(**variables)
 
 
-def render_rl_sbatch(config, paths: dict) -> str:
-    """``paths``: sub-config files written by the launcher (keys trainer / orchestrator / inference)."""
-    slurm = config.slurm
-    dep = config.deployment
-    log_dir = Path(config.run_dir) / "logs"
-    if getattr(dep, "type", "single_node") == "multi_node":
-        gpn = dep.gpus_per_node
-        n_train = dep.num_train_nodes
-        n_infer = dep.num_infer_nodes if dep.num_infer_nodes is not None else 0
-        nodes = n_train + n_infer
-    else:
-        gpn, n_train, n_infer, nodes = 8, 1, 0, 1
+def _common(slurm, run_dir: Path, total_nodes: int, gpus_per_node: int, env_vars: dict | None,
+            ranks_filter=(0,)) -> dict:
     if slurm is None:
         from ..configs.shared import SlurmConfig
 
         slurm = SlurmConfig()
-    if slurm.template_path:
-        return Path(slurm.template_path).read_text().format_map(
-            dict(slurm.template_vars, nodes=nodes, gpus_per_node=gpn, num_train_nodes=n_train,
-                 num_infer_nodes=n_infer, trainer_config=paths["trainer"], orchestrator_config=paths["orchestrator"],
-                 inference_config=paths.get("inference", ""), log_dir=log_dir))
-    L = _header(slurm, nodes, gpn, log_dir) + _env_exports(config.env_vars) + _cleanup(slurm.cleanup_grace_period)
-    L += ["", f"mkdir -p {log_dir}"]
-    if nodes == 1:
-        # everything on one node: the local launcher splits the GPUs itself
-        L += ["", f"srun --nodes=1 --ntasks=1 python -m prime_rl_b200.entrypoints.rl @ {paths.get('rl', paths['trainer'])} "
-                  f"--slurm None > {log_dir}/rl.log 2>&1"]
-        return "\n".join(L) + "\n"
-    L += ["", f"TRAIN_NODES=(\"${{NODES[@]:0:{n_train}}}\")", f"INFER_NODES=(\"${{NODES[@]:{n_train}:{n_infer}}}\")",
-          'TRAIN_HEAD=${TRAIN_NODES[0]}', 'export MASTER_ADDR=$TRAIN_HEAD']
-    if "inference" in paths and n_infer > 0:
-        per = max(1, n_infer // max(1, dep.num_infer_replicas))
-        L += ["", "# inference replicas", f"REPLICA_NODES={per}", "for ((r = 0; r < ${#INFER_NODES[@]}; r += REPLICA_NODES)); do",
-              "  node=${INFER_NODES[$r]}",
-              f"  srun --nodes=1 --ntasks=1 -w $node python -m prime_rl_b200.entrypoints.inference @ {paths['inference']} "
-              f"> {log_dir}/inference_$node.log 2>&1 &", "done",
-              'INFER_URLS=$(printf "http://%s:8000/v1," "${INFER_NODES[@]}")', 'export PRL_INFERENCE_URLS=${INFER_URLS%,}']
-    orch_node = "${INFER_NODES[0]}" if (dep.orchestrator_on_inference and n_infer > 0) else "$TRAIN_HEAD"
-    L += ["", "# orchestrator (CPU only)",
-          f"srun --nodes=1 --ntasks=1 --overlap -w {orch_node} env CUDA_VISIBLE_DEVICES= python -m "
-          f"prime_rl_b200.entrypoints.orchestrator @ {paths['orchestrator']} > {log_dir}/orchestrator.log 2>&1 &",
-          "", "# trainer: one torch.distributed.run agent per train node",
-          f"srun --nodes={n_train} --ntasks={n_train} -w $(IFS=,; echo \"${{TRAIN_NODES[*]}}\") bash -c '"
-          f"python -m torch.distributed.run --nnodes={n_train} --nproc-per-node={gpn} --node-rank=$SLURM_NODEID "
-          f"--master-addr=$MASTER_ADDR --master-port=$MASTER_PORT -m prime_rl_b200.trainer.rl.train @ {paths['trainer']}' "
-          f"> {log_dir}/trainer.log 2>&1 &", "", "wait -n", "exit $?"]
-    return "\n".join(L) + "\n"
+    run_dir = Path(run_dir)
+    launcher_dir = run_dir / "launcher"
+    return {
+        "job_name": slurm.job_name, "partition": slurm.partition, "project_dir": str(Path(slurm.project_dir).resolve()),
+        "account": slurm.account, "time": slurm.time, "nodelist": slurm.nodelist, "exclude": slurm.exclude,
+        "slurm_opts": {k: getattr(slurm, k, None) for k in ("account", "time", "nodelist", "exclude")},
+        "pre_run_command": slurm.pre_run_command, "cleanup_grace_period": int(slurm.cleanup_grace_period),
+        "shared_fs": slurm.shared_fs, "total_nodes": total_nodes, "gpus_per_node": gpus_per_node,
+        "output_dir": str(run_dir), "log_dir": str(run_dir / "logs"), "launcher_dir": str(launcher_dir),
+        "launcher_log_dir": str(launcher_dir / "logs"), "env_vars": dict(env_vars or {}),
+        "ranks_filter": ",".join(str(r) for r in ranks_filter),
+    }
+
+
+def _inference_vars(inference, gpus_per_node: int) -> dict:
+    """Placement of the inference servers: replicas per node, ports, prefill / decode split."""
+    out = {"is_disaggregated": False, "num_prefill_nodes": 0, "num_decode_nodes": 0, "prefill_port": 8100,
+           "decode_port": 8200, "prefill_env_vars": {}, "decode_env_vars": {}, "inference_tp": 1,
+           "dp_per_node": gpus_per_node, "router_port": 8000, "backend_port": 8001, "nodes_per_infer_replica": 1,
+           "inference_data_parallel_rpc_port": 13345}
+    if inference is None:
+        return out
+    tp = max(1, inference.vllm.tensor_parallel_size)
+    out.update(inference_tp=tp, dp_per_node=max(1, gpus_per_node // tp), router_port=inference.server.port,
+               backend_port=inference.server.port + 1000,
+               inference_data_parallel_rpc_port=inference.vllm.data_parallel_rpc_port)
+    dep = getattr(inference, "deployment", None)
+    kind = getattr(dep, "type", "single_node")
+    if kind == "multi_node":
+        out["nodes_per_infer_replica"] = dep.num_nodes
+    elif kind == "disaggregated":
+        out.update(is_disaggregated=True,
+                   num_prefill_nodes=dep.prefill_nodes_per_replica * dep.num_prefill_replicas,
+                   num_decode_nodes=dep.decode_nodes_per_replica * dep.num_decode_replicas,
+                   prefill_port=dep.prefill_port, decode_port=dep.decode_port,
+                   prefill_env_vars=dict(dep.prefill_env_vars), decode_env_vars=dict(dep.decode_env_vars),
+                   nodes_per_infer_replica=dep.prefill_nodes_per_replica + dep.decode_nodes_per_replica)
+    return out
+
+
+def render_rl_sbatch(config, paths: dict) -> str:
+    """``paths``: sub-config files written by the launcher (keys rl / trainer / orchestrator / inference); the
+    templates address them through their common directory."""
+    dep = config.deployment
+    multi = getattr(dep, "type", "single_node") == "multi_node"
+    gpn = dep.gpus_per_node
+    n_train = dep.num_train_nodes if multi else 1
+    n_infer = (dep.num_infer_nodes or 0) if multi else 0
+    if config.inference is None:
+        n_infer = 0
+    config_dir = Path(paths["trainer"]).parent
+    v = _common(config.slurm, config.run_dir, n_train + n_infer if multi else 1, gpn, config.env_vars,
+                getattr(config.trainer.log, "ranks_filter", [0]))
+    v.update(_inference_vars(config.inference, gpn))
+    wb, rt_ = config.trainer.weight_broadcast, getattr(config.trainer, "rollout_transport", None)
+    sources = list(config.orchestrator.spawned_sources()) if hasattr(config.orchestrator, "spawned_sources") else []
+    v.update(
+        config_dir=str(config_dir), config_path=str(paths.get("rl", paths["trainer"])),
+        num_train_nodes=n_train, num_infer_nodes=n_infer,
+        num_infer_replicas=getattr(dep, "num_infer_replicas", 1),
+        orchestrator_on_inference=bool(getattr(dep, "orchestrator_on_inference", False)),
+        trainer_env_vars=dict(config.trainer.env_vars), orchestrator_env_vars=dict(config.orchestrator.env_vars),
+        inference_env_vars=dict(config.inference.env_vars) if config.inference is not None else {},
+        use_nccl_broadcast=getattr(wb, "type", None) == "nccl", use_nixl_broadcast=getattr(wb, "type", None) == "nixl",
+        use_zmq_transport=getattr(rt_, "type", None) == "zmq",
+        train_env_names=[f"{kind}-{src.resolved_name}" for kind, src, _ in sources if kind == "train"],
+        eval_env_names=[f"{kind}-{src.resolved_name}" for kind, src, _ in sources if kind != "train"],
+    )
+    return _render("multi_node_rl.sbatch.j2" if multi else "single_node_rl.sbatch.j2", config.slurm, v)
 
 
 def render_sft_sbatch(config, trainer_config: Path, nodes: int = 1, gpus_per_node: int = 8) -> str:
-    slurm = config.slurm
-    log_dir = Path(config.run_dir) / "logs"
-    L = _header(slurm, nodes, gpus_per_node, log_dir) + _env_exports(getattr(config, "env_vars", {})) + \
-        _cleanup(slurm.cleanup_grace_period)
-    L += ["", f"mkdir -p {log_dir}",
-          f"srun --nodes={nodes} --ntasks={nodes} bash -c 'python -m torch.distributed.run --nnodes={nodes} "
-          f"--nproc-per-node={gpus_per_node} --node-rank=$SLURM_NODEID --master-addr=$MASTER_ADDR "
-          f"--master-port=$MASTER_PORT -m prime_rl_b200.trainer.sft.train @ {trainer_config}' > {log_dir}/sft.log 2>&1"]
-    return "\n".join(L) + "\n"
+    v = _common(config.slurm, config.run_dir, nodes, gpus_per_node, getattr(config, "env_vars", {}),
+                getattr(getattr(config, "log", None), "ranks_filter", [0]))
+    v.update(config_path=str(trainer_config), config_dir=str(Path(trainer_config).parent), num_nodes=nodes)
+    return _render("multi_node_sft.sbatch.j2" if nodes > 1 else "single_node_sft.sbatch.j2", config.slurm, v)
 
 
 def render_inference_sbatch(config, inference_config: Path, nodes: int = 1, gpus_per_node: int = 8) -> str:
-    slurm = config.slurm
-    log_dir = Path(getattr(config, "run_dir", Path("outputs"))) / "logs"
-    L = _header(slurm, nodes, gpus_per_node, log_dir) + _cleanup(slurm.cleanup_grace_period)
-    L += ["", f"mkdir -p {log_dir}", "for node in \"${NODES[@]}\"; do",
-          f"  srun --nodes=1 --ntasks=1 -w $node python -m prime_rl_b200.entrypoints.inference @ {inference_config} "
-          f"> {log_dir}/inference_$node.log 2>&1 &", "done", "wait"]
-    return "\n".join(L) + "\n"
+    run_dir = getattr(config, "run_dir", None) or getattr(config, "output_dir", None) or Path("outputs")
+    v = _common(config.slurm, run_dir, nodes, gpus_per_node, getattr(config, "env_vars", {}))
+    v.update(_inference_vars(config, gpus_per_node))
+    if nodes == 1:
+        v["backend_port"] = v["router_port"]          # a single node serves on the public port itself
+    v.update(config_path=str(inference_config), config_dir=str(Path(inference_config).parent), num_nodes=nodes)
+    return _render("inference.sbatch.j2", config.slurm, v)

@@ -66,12 +66,19 @@ def main() -> int:
     p2p = P2PDispatcher(group, world, 8 * world, capacity_factor=float(world))
     got = _run(p2p, ex, x, idx, w, counts, dout)
     got2 = _run(p2p, ex, x, idx, w, counts, dout)          # buffers and epochs are reused
+    # the same with one global wait instead of the per-block arrival counters, then per-block again: the two
+    # kinds of call may alternate on one set of buffers
+    glob = P2PDispatcher(group, world, 8 * world, capacity_factor=float(world), per_block=False)
+    got3 = _run(glob, ex, x, idx, w, counts, dout)
+    got4 = _run(p2p, ex, x, idx, w, counts, dout)
     torch.cuda.synchronize()
     rt.check_status()
     errs = []
-    for a, b, c in zip(ref[:3], got[:3], got2[:3]):
+    for a, b, c, d, e in zip(ref[:3], got[:3], got2[:3], got3[:3], got4[:3]):
         errs.append(float((a.float() - b.float()).abs().max()))
         errs.append(float((a.float() - c.float()).abs().max()))
+        errs.append(float((a.float() - d.float()).abs().max()))
+        errs.append(float((a.float() - e.float()).abs().max()))
     for a, b in zip(ref[3], got[3]):
         errs.append(float((a.float() - b.float()).abs().max() / (a.float().abs().max() + 1e-6)))
     t = torch.tensor([max(errs)], device=dev)
@@ -98,7 +105,9 @@ def main() -> int:
         T, E, H, I, k = 8192, 128, 2048, 768, 8
         ex, x, idx, w, counts, dout = setup(T, E, H, I, k)
         for name, disp in (("all_to_all (NCCL)", TorchA2ADispatcher(group, world, E)),
-                           ("peer memory", P2PDispatcher(group, world, E, capacity_factor=2.0)),
+                           ("peer memory, per-block arrival", P2PDispatcher(group, world, E, capacity_factor=2.0)),
+                           ("peer memory, one global wait",
+                            P2PDispatcher(group, world, E, capacity_factor=2.0, per_block=False)),
                            ("peer memory, fp8 dispatch payload",
                             P2PDispatcher(group, world, E, capacity_factor=2.0, payload="fp8"))):
             for _ in range(3):

@@ -68,19 +68,88 @@ def test_evals_step_discovery_and_pass_at_k(tmp_path):
     assert pass_at_k([[0.0, 1.0], [0.0, 0.0], [1.0, 1.0]]) == pytest.approx(2 / 3)
 
 
+def _bash_syntax_ok(text: str, tmp_path, name: str) -> None:
+    import subprocess
+
+    p = tmp_path / name
+    p.write_text(text)
+    r = subprocess.run(["bash", "-n", str(p)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+
+
 def test_sbatch_rendering_multi_node(tmp_path):
     from prime_rl_b200.configs.rl import RLConfig
     from prime_rl_b200.utils.slurm import render_rl_sbatch
 
     cfg = RLConfig.model_validate({"deployment": {"type": "multi_node", "num_train_nodes": 2, "num_infer_nodes": 2},
-                                   "slurm": {"job_name": "rl-test", "partition": "b200"},
+                                   "slurm": {"job_name": "rl-test", "partition": "b200", "account": "acct",
+                                             "cleanup_grace_period": 120, "pre_run_command": "module load cuda"},
+                                   "env_vars": {"NCCL_DEBUG": "WARN", "ODD": "a b"},
                                    "inference": {}, "output_dir": str(tmp_path)})
     paths = {"trainer": tmp_path / "trainer.json", "orchestrator": tmp_path / "orchestrator.json",
              "inference": tmp_path / "inference.json"}
     text = render_rl_sbatch(cfg, paths)
+    _bash_syntax_ok(text, tmp_path, "rl.sbatch")
     assert "#SBATCH --nodes=4" in text and "--job-name=rl-test" in text and "--partition=b200" in text
-    assert "--nnodes=2" in text and "prime_rl_b200.trainer.rl.train" in text
+    assert "#SBATCH --account=acct" in text and "#SBATCH --time" not in text
+    assert "NUM_TRAIN_NODES=2" in text and "NUM_INFER_NODES=2" in text and "prime_rl_b200.trainer.rl.train" in text
     assert "prime_rl_b200.entrypoints.inference" in text and "prime_rl_b200.entrypoints.orchestrator" in text
+    assert "prime_rl_b200.engine.router" in text and "--kill-on-bad-exit=1" in text
+    assert "export ODD='a b'" in text and "module load cuda" in text and "holding for 120s" in text
+    assert "ORCH_PROCID=$NUM_INFER_NODES" in text           # beside trainer rank 0 by default
+    assert "pkill" not in text and "killall" not in text    # leftovers are ended by recorded pid only
+    cfg2 = RLConfig.model_validate({"deployment": {"type": "multi_node", "num_train_nodes": 1, "num_infer_nodes": 2,
+                                                   "orchestrator_on_inference": True},
+                                    "inference": {}, "output_dir": str(tmp_path)})
+    text2 = render_rl_sbatch(cfg2, paths)
+    _bash_syntax_ok(text2, tmp_path, "rl2.sbatch")
+    assert "ORCH_PROCID=$((NUM_INFER_NODES - 1))" in text2
+
+
+def test_sbatch_rendering_other_launchers_and_user_templates(tmp_path):
+    from types import SimpleNamespace
+
+    from prime_rl_b200.configs.inference import InferenceConfig
+    from prime_rl_b200.configs.rl import RLConfig
+    from prime_rl_b200.configs.shared import SlurmConfig
+    from prime_rl_b200.utils.slurm import render_inference_sbatch, render_rl_sbatch, render_sft_sbatch
+
+    view = SimpleNamespace(slurm=SlurmConfig(job_name="sft"), run_dir=tmp_path, env_vars={})
+    one = render_sft_sbatch(view, tmp_path / "sft.json", nodes=1, gpus_per_node=4)
+    many = render_sft_sbatch(view, tmp_path / "sft.json", nodes=3, gpus_per_node=8)
+    _bash_syntax_ok(one, tmp_path, "sft1.sbatch")
+    _bash_syntax_ok(many, tmp_path, "sft3.sbatch")
+    assert "--nproc-per-node=4" in one and "#SBATCH --nodes=1" in one and "--master-addr=127.0.0.1" in one
+    assert "#SBATCH --nodes=3" in many and "--node-rank=$SLURM_PROCID" in many and "NUM_NODES=3" in many
+
+    inf = InferenceConfig.model_validate({"deployment": {"type": "disaggregated", "prefill_nodes_per_replica": 1,
+                                                         "decode_nodes_per_replica": 2,
+                                                         "prefill_env_vars": {"ROLE_HINT": "p"}},
+                                          "vllm": {"tensor_parallel_size": 2}, "slurm": {"job_name": "inf"}})
+    inf_view = SimpleNamespace(slurm=inf.slurm, run_dir=tmp_path, env_vars={}, vllm=inf.vllm, server=inf.server,
+                               deployment=inf.deployment)
+    text = render_inference_sbatch(inf_view, tmp_path / "inference.json", nodes=3, gpus_per_node=8)
+    _bash_syntax_ok(text, tmp_path, "inf.sbatch")
+    assert "PRL_INFERENCE_ROLE=prefill" in text and "--vllm.tensor-parallel-size 2" in text
+    assert "--vllm.data-parallel-size 4" in text and "prime_rl_b200.engine.router" in text
+
+    # single-node RL under SLURM hands over to the local launcher
+    cfg = RLConfig.model_validate({"slurm": {"job_name": "one"}, "inference": {}, "output_dir": str(tmp_path)})
+    single = render_rl_sbatch(cfg, {"rl": tmp_path / "rl.json", "trainer": tmp_path / "trainer.json",
+                                    "orchestrator": tmp_path / "orchestrator.json"})
+    _bash_syntax_ok(single, tmp_path, "one.sbatch")
+    assert "prime_rl_b200.entrypoints.rl @" in single and "--slurm None" in single
+
+    # a user template sees the same variables and may include the stock pieces
+    user = tmp_path / "mine.j2"
+    user.write_text('{% include "_header.sbatch.j2" %}\necho train={{ num_train_nodes }} infer={{ num_infer_nodes }} '
+                    'tp={{ inference_tp }} cfg={{ config_dir }}\n')
+    cfg3 = RLConfig.model_validate({"deployment": {"type": "multi_node", "num_train_nodes": 2, "num_infer_nodes": 1},
+                                    "slurm": {"template_path": str(user)}, "inference": {},
+                                    "output_dir": str(tmp_path)})
+    mine = render_rl_sbatch(cfg3, {"trainer": tmp_path / "c" / "trainer.json",
+                                   "orchestrator": tmp_path / "c" / "orchestrator.json"})
+    assert "echo train=2 infer=1 tp=1" in mine and f"cfg={tmp_path / 'c'}" in mine and "#SBATCH --nodes=3" in mine
 
 
 def test_trainer_annotations_reach_the_file_monitor(tmp_path):
@@ -245,3 +314,72 @@ def test_rl_launcher_prepares_one_env_server_per_source(tmp_path):
     assert o.train.source[1].id == "copy"                                    # externally managed: left alone
     spec = EnvServerConfig.model_validate(json.loads((tmp_path / "envs" / "eval-held-out.json").read_text()))
     assert spec.env.id == "copy" and spec.serve.port == 6102 and spec.env.resolved_name == "held-out"
+
+
+def test_platform_monitor_uploads_through_a_background_queue(monkeypatch):
+    """Registration, per-step metric rows, sampled traces every 10th step as one file, the terminal status, retry
+    of a failed request, attach through $RUN_ID and the disabled mode; the HTTP side is an in-process fake."""
+    import httpx
+
+    from prime_rl_b200.configs.monitors import PrimeMonitorConfig
+    from prime_rl_b200.monitors.prime import PrimeMonitor, encode_samples, resolve_base_url, sanitize
+
+    calls, fail_once = [], {"left": 1}
+
+    def handler(request: httpx.Request) -> httpx.Response:
+        path = request.url.path
+        if path.endswith("/metrics") and fail_once["left"]:
+            fail_once["left"] -= 1
+            return httpx.Response(503)
+        calls.append((path, dict(request.url.params), request.content))
+        if path == "/runs":
+            return httpx.Response(200, json={"id": "run-7", "url": "https://tracker/run-7"})
+        return httpx.Response(200, json={})
+
+    monkeypatch.delenv("RUN_ID", raising=False)
+    monkeypatch.delenv("PRIME_RUNS_MODE", raising=False)
+    client = httpx.Client(transport=httpx.MockTransport(handler), base_url="https://tracker")
+    mon = PrimeMonitor(PrimeMonitorConfig(run_name="exp"), "orchestrator",
+                       {"model": {"name": "tiny"}, "batch_size": 8, "train": {"source": [{"id": "reverse"}]}},
+                       client=client, finish_timeout=20.0)
+    assert mon.run_id == "run-7" and not mon.attached
+    mon.log({"reward": 0.5, "bad": float("nan"), "n": 3}, step=10)
+    for i in range(3):
+        mon.log_trace({"step": 10, "trace_id": f"t{i}", "turns": [[1, 2], [3]], "reward": 1.0})
+    mon.log_trace({"step": 11, "trace_id": "x", "reward": 0.0})       # off the cadence: not shipped
+    mon.log({"reward": 0.75}, step=11)
+    mon.finalize()
+    paths = [c[0] for c in calls]
+    assert paths[0] == "/runs" and json.loads(calls[0][2])["model"] == "tiny"
+    rows = [json.loads(c[2]) for c in calls if c[0].endswith("/metrics")]
+    assert [r["step"] for r in rows] == [10, 11] and rows[0]["metrics"] == {"reward": 0.5, "n": 3}   # 503 was retried
+    samples = [c for c in calls if c[0].endswith("/samples")]
+    assert len(samples) == 1 and samples[0][1] == {"step": "10", "count": "3"}
+    import pyarrow.parquet as pq
+    import io
+
+    table = pq.read_table(io.BytesIO(samples[0][2]))
+    assert table.num_rows == 3 and json.loads(table.column("turns")[0].as_py()) == [[1, 2], [3]]
+    assert paths[-1].endswith("/status") and json.loads(calls[-1][2])["status"] == "completed"
+
+    # attach: no registration, and a crash is left to the launcher
+    calls.clear()
+    monkeypatch.setenv("RUN_ID", "managed-1")
+    att = PrimeMonitor(PrimeMonitorConfig(), "orchestrator", {}, client=client, finish_timeout=20.0)
+    assert att.attached and att.run_id == "managed-1"
+    att.finalize("crashed")
+    assert not any(c[0].endswith("/status") or c[0] == "/runs" for c in calls)
+    monkeypatch.delenv("RUN_ID")
+
+    monkeypatch.setenv("PRIME_RUNS_MODE", "disabled")
+    off = PrimeMonitor(PrimeMonitorConfig(), "trainer", {})
+    off.log({"a": 1}, 0)
+    off.finalize()
+    monkeypatch.delenv("PRIME_RUNS_MODE")
+    with pytest.raises(RuntimeError, match="PRIME_API_KEY"):
+        monkeypatch.delenv("PRIME_API_KEY", raising=False)
+        PrimeMonitor(PrimeMonitorConfig(), "trainer", {})
+    monkeypatch.setenv("PRIME_API_BASE", "https://api.example/api/v1/rft/")
+    assert resolve_base_url("https://unused") == "https://api.example/api/v1"
+    assert sanitize({"a": float("inf"), "b": True, "c": [1]}) == ({"b": 1}, ["a", "c"])
+    assert encode_samples([{"a": 1}])[1] in ("application/vnd.apache.parquet", "application/x-ndjson")

@@ -53,6 +53,30 @@ def test_gemm_tile_widths_and_beta(bn):
     _close(out, ref, atol=0.05, rtol=1e-2)
 
 
+@pytest.mark.parametrize("splits", [0, 1, 2, 3, 4, 8])
+@pytest.mark.parametrize("M,N,K,b_mn", [(256, 5120, 2048, False), (77, 520, 1096, False), (512, 2048, 4096, True),
+                                        (32, 128, 768, False)])
+def test_gemm_split_k_for_decode_sized_outputs(M, N, K, b_mn, splits):
+    """Few output tiles: the reduction is dealt to several CTAs per tile whose fp32 partials the last arrival adds
+    in split order. Every split count (0 = the kernel's own choice) must give the unsplit result; twice in a row,
+    because the arrival counters must be back at zero after a launch."""
+    a = _rand(M, K)
+    b = _rand(K, N) if b_mn else _rand(N, K)
+    ref = G.gemm_ref(a, b, b_mn=b_mn, out_dtype=torch.float32)
+    for _ in range(2):
+        out = G.gemm(a, b, b_mn=b_mn, out_dtype=torch.float32, splitk=splits)
+        rt.check_status()
+        _close(out, ref, atol=1e-2 * K ** 0.5 / 8, rtol=1e-2)
+    c0 = torch.randn(M, N, device=DEV).to(torch.bfloat16)
+    out = c0.clone()
+    G.gemm(a, b, b_mn=b_mn, out=out, alpha=0.5, beta=1.0, splitk=splits)
+    rt.check_status()
+    _close(out, 0.5 * ref + c0.float(), atol=0.02 * K ** 0.5, rtol=2e-2)
+    again = c0.clone()
+    G.gemm(a, b, b_mn=b_mn, out=again, alpha=0.5, beta=1.0, splitk=splits)
+    assert torch.equal(out, again)                      # partials are added in a fixed order
+
+
 def test_gemm_grouped_fwd_and_dgrad():
     E, N, K = 6, 384, 256
     counts = torch.tensor([130, 0, 5, 256, 127, 1], dtype=torch.int32)
@@ -824,6 +848,49 @@ def test_fp8_experts_skip_padding_rows_and_match_the_padded_fp8_path():
     assert torch.equal(q_m[::3], q_all[::3]) and torch.equal(s_m[::3], s_all[::3])
 
 
+@pytest.mark.parametrize("N,K", [(384, 512), (200, 768), (1536, 2048)])
+def test_fp8_grouped_gemm_for_few_rows_per_expert(N, K):
+    """Decode-shaped grouped fp8 GEMM with the operands swapped (weight rows on the 128-row side, the block's real
+    rows on the other): every count of leading real rows, poisoned padding rows, empty and unused blocks."""
+    from prime_rl_b200.ops import fp8
+
+    torch.manual_seed(1)
+    E = 5
+    rows = [1, 31, 32, 33, 64, 100, 128, 0, 17, 128, 5]
+    experts = [0, 1, 2, 3, 4, 0, 1, -1, 2, 2, 4]
+    M = 128 * len(rows)
+    x = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(E, N, K, device=DEV) * 0.05).bfloat16()
+    aq, sa = fp8.quantize_act(x)
+    bq = torch.empty(E, N, K, dtype=torch.uint8, device=DEV)
+    sb = torch.empty(E, (N + 127) // 128, (K + 127) // 128, device=DEV)
+    for e in range(E):                                   # 128 x 128 block scales
+        we = w[e].float()
+        pad = torch.zeros((N + 127) // 128 * 128, (K + 127) // 128 * 128, device=DEV)
+        pad[:N, :K] = we
+        blocks = pad.view(pad.shape[0] // 128, 128, pad.shape[1] // 128, 128)
+        sc = blocks.abs().amax((1, 3)).clamp_min(1e-12) / 448.0
+        sb[e] = sc
+        q = (blocks / sc[:, None, :, None]).reshape(pad.shape)[:N, :K].to(torch.float8_e4m3fn)
+        bq[e] = q.view(torch.uint8)
+    block_expert = torch.tensor(experts, dtype=torch.int32, device=DEV)
+    block_rows = torch.tensor(rows, dtype=torch.int32, device=DEV)
+    valid = torch.full((M,), -1, dtype=torch.int32, device=DEV)
+    for b, n in enumerate(rows):
+        valid[b * 128:b * 128 + n] = 1
+    assert torch.equal(fp8.count_block_rows(valid), block_rows)
+    ref = fp8.fp8_gemm_ref(aq, sa, bq, sb, block_expert)
+    aq2, sa2 = aq.clone(), sa.clone()
+    aq2[valid < 0] = 0x7f                                # e4m3 NaN
+    sa2[valid < 0] = float("nan")
+    out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    fp8.fp8_gemm_few_rows(aq2, sa2, bq, sb, block_expert, block_rows, out=out)
+    rt.check_status()
+    keep = (valid >= 0) & (block_expert.repeat_interleave(128) >= 0)
+    _close(out[keep], ref[keep], atol=2e-2 * K ** 0.5 / 8, rtol=2e-2)
+    assert bool((out[~keep] == 7.0).all())               # padding rows are left alone
+
+
 def test_qkv_rope_to_cache_matches_separate_ops():
     """Fused split + QK-norm + rotary + paged-cache write against qkv_norm_rope followed by index_copy_
     (bit-equal), with and without the contiguous K / V outputs and without QK-norm."""
@@ -995,7 +1062,7 @@ def test_paged_decode_with_shared_prefix_groups_matches_the_reference(Hq, Hkv):
         bt[i, :len(p)] = torch.tensor(p, dtype=torch.int32)
     ctx = torch.tensor(lengths, dtype=torch.int32)
     q = _rand(B, Hq, D)
-    ref = paged.paged_decode_ref(q.cpu(), kpool.cpu(), vpool.cpu(), bt, ctx)
+    ref = paged.paged_decode_ref(q.cpu(), kpool.cpu(), vpool.cpu(), bt, ctx).to(DEV)
     # kv.length of the runner is the length before the new token: the last key of a sequence is its own
     groups, page_begin = paged.group_shared_prefixes(page_lists, [n - 1 for n in lengths], ps, min_pages=4)
     assert sorted(len(m) for m, _ in groups) == [3, 8, 8] and page_begin[11] == 0
