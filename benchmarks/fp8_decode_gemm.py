@@ -1,5 +1,5 @@
-"""Times the two grouped block-scaled fp8 GEMMs of one MoE layer at decode size (a handful of rows per expert):
-the 128 x 128-tile kernel with padding rows masked, and the swapped-operand kernel for few rows per expert.
+"""Times the two grouped block-scaled fp8 GEMMs of one MoE layer at decode size (a handful of rows per expert,
+padding rows masked).
 
     python benchmarks/fp8_decode_gemm.py [--tokens 256] [--experts 128] [--topk 8] [--hidden 2048] [--inter 768]
 
@@ -37,7 +37,6 @@ def main() -> None:
     plan = moe.build_plan(idx.to(torch.int32).contiguous(), counts.to(torch.int32), E)
     P = plan.max_rows
     valid = plan.row_src
-    rows = fp8.count_block_rows(valid)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
     def quant_w(n, kk):
@@ -67,12 +66,11 @@ def main() -> None:
         xq, xs = fp8.quantize_act(x)
         out = torch.empty(P, n, dtype=torch.bfloat16, device=dev)
         t_tile = timed(lambda: fp8.fp8_gemm(xq, xs, wq, ws, block_expert=plan.block_expert, out=out, row_valid=valid))
-        t_swap = timed(lambda: fp8.fp8_gemm_few_rows(xq, xs, wq, ws, plan.block_expert, rows, out=out))
         wbytes = E * n * kk
         floor = wbytes / (args.hbm_gbs * 1e3)
-        print(f"{name}: {T} tokens x top-{k} over {E} experts, N={n} K={kk}: 128x128 tiles {t_tile:.1f} us, "
-              f"swapped operands {t_swap:.1f} us; weights {wbytes / 1e6:.0f} MB = {floor:.1f} us at "
-              f"{args.hbm_gbs:.0f} GB/s -> {floor / t_tile:.2f} / {floor / t_swap:.2f} of the copy rate", flush=True)
+        print(f"{name}: {T} tokens x top-{k} over {E} experts, N={n} K={kk}: {t_tile:.1f} us; weights "
+              f"{wbytes / 1e6:.0f} MB = {floor:.1f} us at {args.hbm_gbs:.0f} GB/s -> {floor / t_tile:.2f} of the "
+              f"copy rate", flush=True)
     rt.check_status()
 
 

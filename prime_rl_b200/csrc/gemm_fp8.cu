@@ -209,201 +209,6 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 }
 
 
-// ---------------------------------------------------------------------------------------------------------
-// Grouped GEMM for few rows per expert (decode): the operands trade places. The 128 rows of a weight tile are the
-// M side of the instruction, the expert's tokens (rounded up to 32, at most 128) its N side, so a tile moves
-// 16 KB of weights and 4-16 KB of activations per K block instead of 16 + 16 KB per 128 x 128 output tile of
-// which most rows are padding; every weight byte crosses the L2 -> SM path once. The accumulator is
-// [weight row (TMEM lane)] x [token (column)]: the weight scale of a K block is one scalar for the whole tile, the
-// activation scales (one per token and K block) are staged in shared memory once per tile, and a thread writes
-// its weight row's value for every token (32 lanes = 64 contiguous bytes of one output row).
-constexpr int kSwStages = 6;
-constexpr int kSwMaxKB = 32;                                   // K <= 4096
-constexpr int kSwScaleBytes = 128 * kSwMaxKB * 4;              // staged activation scales of one tile
-constexpr int kSwSmem = kSwStages * kF8StageBytes + kSwScaleBytes + 1024 + 256;
-
-struct Fp8SwapParams {
-  int M, N, K;
-  const float* sa;          // [M, KB]
-  const float* sb;          // [E, ceil(N/128), KB]
-  __nv_bfloat16* C;
-  long long ldc;
-  const int* block_expert;  // [ceil(M/128)]
-  const int* block_rows;    // [ceil(M/128)] real rows at the start of each 128-row block
-  int* status;
-};
-
-struct Fp8SwapTile {
-  int tile, num_tiles, tiles_m, tiles_n;
-  __device__ Fp8SwapTile(const Fp8SwapParams& p)
-      : tile(blockIdx.x - gridDim.x), tiles_m((p.M + 127) / 128), tiles_n((p.N + 127) / 128) {
-    num_tiles = tiles_m * tiles_n;
-  }
-  // weight-tile major inside one token block: the CTAs in flight stream different weight tiles of few experts
-  __device__ bool next(const Fp8SwapParams& p, int& m_blk, int& n_blk, int& expert, int& nt) {
-    for (;;) {
-      tile += gridDim.x;
-      if (tile >= num_tiles) return false;
-      m_blk = tile / tiles_n;
-      n_blk = tile - m_blk * tiles_n;
-      expert = p.block_expert[m_blk];
-      if (expert < 0) continue;
-      const int rows = min(p.block_rows[m_blk], min(128, p.M - m_blk * 128));
-      if (rows <= 0) continue;
-      nt = (rows + 31) / 32 * 32;
-      return true;
-    }
-  }
-};
-
-__global__ void __launch_bounds__(kF8Threads, 1)
-gemm_fp8_swap_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
-                     const Fp8SwapParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float* sx_s = reinterpret_cast<float*>(smem + kSwStages * kF8StageBytes);
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kSwStages * kF8StageBytes + kSwScaleBytes);
-  uint64_t* empty = full + kSwStages;
-  uint64_t* tfull = empty + kSwStages;
-  uint64_t* tempty = tfull + kF8AccBufs;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + kF8AccBufs);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int KB = (p.K + kF8BK - 1) / kF8BK;
-
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < kSwStages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-    for (int i = 0; i < kF8AccBufs; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], kF8EpiWarps); }
-    mbar_fence_init();
-    tma_prefetch_desc(&tmW);
-    tma_prefetch_desc(&tmX);
-  }
-  if (warp == 1) { tmem_alloc(tmem_slot, kF8AccBufs * 128); tmem_relinquish(); }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
-  int m_blk = 0, n_blk = 0, expert = 0, nt = 32;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      Fp8SwapTile sched(p);
-      int s = 0;
-      uint32_t ph = 0;
-      bool ok = true;
-      while (ok && sched.next(p, m_blk, n_blk, expert, nt)) {
-        const int wrow = expert * p.N + n_blk * 128;
-        for (int kb = 0; kb < KB; ++kb) {
-          if (!mbar_wait(&empty[s], ph ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
-          mbar_expect_tx(&full[s], 128 * kF8BK + nt * kF8BK);
-          uint8_t* w_dst = smem + s * kF8StageBytes;
-          tma_load_2d(w_dst, &tmW, &full[s], kb * kF8BK, wrow);
-          for (int j = 0; j < nt / 32; ++j)
-            tma_load_2d(w_dst + 128 * kF8BK + j * 32 * kF8BK, &tmX, &full[s], kb * kF8BK, m_blk * 128 + 32 * j);
-          if (++s == kSwStages) { s = 0; ph ^= 1; }
-        }
-      }
-      if (!ok) __nanosleep(200000);
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      Fp8SwapTile sched(p);
-      int s = 0;
-      uint32_t ph = 0, u = 0;
-      bool ok = true;
-      while (ok && sched.next(p, m_blk, n_blk, expert, nt)) {
-        const uint32_t idesc = umma_idesc(0, 128, nt, false, false);
-        for (int kb = 0; kb < KB; ++kb, ++u) {
-          const uint32_t buf = u % kF8AccBufs;
-          if (!mbar_wait_poll(&tempty[buf], ((u / kF8AccBufs) & 1) ^ 1, p.status, kTimeoutTmemEmpty)) { ok = false; break; }
-          if (!mbar_wait_poll(&full[s], ph, p.status, kTimeoutFullBarrier)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t w_addr = smem_u32(smem + s * kF8StageBytes), x_addr = w_addr + 128 * kF8BK;
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_f8(tmem_base + buf * 128, umma_smem_desc(w_addr + k * 32, 0, 1024),
-                    umma_smem_desc(x_addr + k * 32, 0, 1024), idesc, k != 0);
-          umma_commit(&empty[s]);
-          umma_commit(&tfull[buf]);
-          if (++s == kSwStages) { s = 0; ph ^= 1; }
-        }
-      }
-    }
-  } else {
-    const int q = warp & 3;                    // TMEM lane quarter: weight rows 32 q .. 32 q + 31 of the tile
-    const int half = (warp - 2) >> 2;          // tokens 64 half .. 64 half + 63 of the block
-    const int etid = threadIdx.x - 64;         // 0 .. 255 among the epilogue threads
-    Fp8SwapTile sched(p);
-    uint32_t u = 0;
-    const int n_tiles_scale = (p.N + 127) / 128;
-    bool ok = true;
-    while (ok && sched.next(p, m_blk, n_blk, expert, nt)) {
-      // stage the activation scales of the block's tokens: sx_s[t * KB + kb]
-      asm volatile("bar.sync 1, 256;" ::: "memory");      // everybody is done with the previous tile's scales
-      {
-        const int rows_here = min(nt, p.M - m_blk * 128);
-        const float* src = p.sa + static_cast<long long>(m_blk) * 128 * KB;
-        for (int i = etid; i < rows_here * KB; i += 256) sx_s[i] = src[i];
-      }
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      const int wr = n_blk * 128 + q * 32 + lane;          // weight row = output column
-      const float* sb_row = p.sb + (static_cast<long long>(expert) * n_tiles_scale + n_blk) * KB;
-      const int c0 = half * 64;
-      const int cols = max(0, min(64, nt - c0));           // 0, 32 or 64 token columns for this warp
-      float acc[64];
-#pragma unroll
-      for (int c = 0; c < 64; ++c) acc[c] = 0.f;
-      float sw_next = sb_row[0];
-      for (int kb = 0; kb < KB; ++kb, ++u) {
-        const uint32_t buf = u % kF8AccBufs;
-        const float sw = sw_next;                     // fetched one K block ahead (see gemm_fp8_kernel)
-        if (kb + 1 < KB) sw_next = sb_row[kb + 1];
-        ok = mbar_wait_poll(&tfull[buf], (u / kF8AccBufs) & 1, p.status, kTimeoutTmemFull);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
-        uint32_t v0[32], v1[32];
-        const uint32_t taddr = tmem_base + buf * 128 + c0 + (static_cast<uint32_t>(q * 32) << 16);
-        if (cols > 0) tmem_ld_32x32(taddr, v0);
-        if (cols > 32) tmem_ld_32x32(taddr + 32, v1);
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tempty[buf]);
-        if (cols > 0) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            acc[j] = fmaf(__uint_as_float(v0[j]), sw * sx_s[(c0 + j) * KB + kb], acc[j]);
-        }
-        if (cols > 32) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            acc[32 + j] = fmaf(__uint_as_float(v1[j]), sw * sx_s[(c0 + 32 + j) * KB + kb], acc[32 + j]);
-        }
-      }
-      if (!ok) break;
-      if (wr < p.N) {
-        const int rows = min(p.block_rows[m_blk], min(128, p.M - m_blk * 128));
-        __nv_bfloat16* dst = p.C + static_cast<long long>(m_blk * 128 + c0) * p.ldc + wr;
-#pragma unroll
-        for (int j = 0; j < 64; ++j)
-          if (c0 + j < rows) dst[static_cast<long long>(j) * p.ldc] = __float2bfloat16(acc[j]);
-      }
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, kF8AccBufs * 128);
-}
-
-// block_rows[b] = number of rows r in [128 b, 128 b + 128) with row_valid[r] >= 0 (they come first in a block)
-__global__ void __launch_bounds__(128)
-count_block_rows_kernel(const int* __restrict__ row_valid, int M, int* __restrict__ block_rows) {
-  const int r = blockIdx.x * 128 + threadIdx.x;
-  const int ok = (r < M && row_valid[r] >= 0) ? 1 : 0;
-  const int n = __syncthreads_count(ok);
-  if (threadIdx.x == 0) block_rows[blockIdx.x] = n;
-}
-
 // Activation quantiser: x bf16 [M, K] -> e4m3 [M, K] + fp32 scales [M, ceil(K / 128)] (scale =
 // amax / 448 per row and 128-wide block). One warp per (row, block): lane = 4 elements.
 __global__ void __launch_bounds__(256)
@@ -474,47 +279,6 @@ PRB_API int prb_gemm_fp8(const void* Aq, const float* sa, const void* Bq, const 
   const int tiles = ((M + kF8BM - 1) / kF8BM) * ((N + kF8BN - 1) / kF8BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
   gemm_fp8_kernel<<<grid, kF8Threads, kF8Smem, stream>>>(tmA, tmB, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
-}
-
-// Grouped C = dequant(Aq) dequant(Bq_e)^T for blocks with few real rows (see gemm_fp8_swap_kernel): block_rows[b]
-// real rows lead each 128-row block b of Aq / C, the rest of the block is neither needed nor stored.
-// K <= 4096 and a multiple of 16.
-PRB_API int prb_gemm_fp8_swap(const void* Aq, const float* sa, const void* Bq, const float* sb, void* C, int M, int N,
-                              int K, long long ldc, const int* block_expert, int num_experts, const int* block_rows,
-                              int* status, void* stream_) {
-  using namespace prb;
-  if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || (K % 16) || K > kSwMaxKB * 128 || block_expert == nullptr || block_rows == nullptr ||
-      (reinterpret_cast<uintptr_t>(Aq) & 15) || (reinterpret_cast<uintptr_t>(Bq) & 15))
-    return -4;
-  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  CUtensorMap tmW, tmX;
-  int rc = make_tmap_2d(&tmW, Bq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)num_experts * (uint64_t)N, (uint64_t)K,
-                        (uint64_t)K, 128, kF8BK, true);
-  if (rc) return rc;
-  rc = make_tmap_2d(&tmX, Aq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)M, (uint64_t)K, (uint64_t)K, 32, kF8BK, true);
-  if (rc) return rc;
-  Fp8SwapParams p;
-  p.M = M; p.N = N; p.K = K; p.sa = sa; p.sb = sb;
-  p.C = reinterpret_cast<__nv_bfloat16*>(C); p.ldc = ldc;
-  p.block_expert = block_expert; p.block_rows = block_rows; p.status = status;
-  static prb::DeviceOnce configured;
-  if (configured.pending()) {
-    if (cudaFuncSetAttribute(gemm_fp8_swap_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSwSmem) != cudaSuccess)
-      return -10;
-    configured.mark();
-  }
-  const int tiles = ((M + 127) / 128) * ((N + 127) / 128);
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  gemm_fp8_swap_kernel<<<grid, kF8Threads, kSwSmem, stream>>>(tmW, tmX, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
-}
-
-PRB_API int prb_count_block_rows(const int* row_valid, int M, int* block_rows, void* stream) {
-  if (M <= 0) return 0;
-  prb::count_block_rows_kernel<<<(M + 127) / 128, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(row_valid, M,
-                                                                                                  block_rows);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

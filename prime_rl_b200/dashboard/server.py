@@ -176,6 +176,29 @@ runs();setInterval(load,10000);
 <option value="diff">trainer - engine</option><option value="entropy">trainer entropy</option></select>
 <div style="display:flex;gap:1em"><div id="tl" style="max-height:420px;overflow:auto;min-width:420px;font:12px monospace"></div>
 <div id="tv" style="flex:1;font:12px monospace;line-height:1.9"></div></div>
+<h2>Episodes</h2>
+step <input id="fstep" size="5"> env <input id="fenv" size="10"> reward &ge; <input id="fmin" size="4"> &le; <input id="fmax" size="4">
+sort <select id="fsort"><option>step</option><option>reward</option><option>advantage</option><option>tokens</option><option>lag</option></select>
+<button onclick="eps(0)">search</button> <button onclick="eps(epOff-50)">&lt;</button> <button onclick="eps(epOff+50)">&gt;</button>
+<span id="epinfo"></span><br><canvas id="hist" width="420" height="120"></canvas><canvas id="ser" width="460" height="120"></canvas>
+<table id="eptab" style="font:12px monospace;border-collapse:collapse"></table>
+<script>
+let epOff=0;
+function qs(){const p=new URLSearchParams();const v=(id)=>document.getElementById(id).value.trim();
+ if(v('fstep'))p.set('step',v('fstep'));if(v('fenv'))p.set('env',v('fenv'));if(v('fmin'))p.set('min_reward',v('fmin'));
+ if(v('fmax'))p.set('max_reward',v('fmax'));return p;}
+function bars(id,vals,label){const c=document.getElementById(id),g=c.getContext('2d');g.clearRect(0,0,c.width,c.height);
+ if(!vals.length)return;const m=Math.max(...vals)||1,w=(c.width-10)/vals.length;vals.forEach((v,i)=>g.fillRect(5+i*w,c.height-14-(c.height-28)*v/m,Math.max(1,w-1),(c.height-28)*v/m));
+ g.fillText(label,6,10);}
+async function eps(off){epOff=Math.max(0,off);const i=document.getElementById('run').value;const p=qs();p.set('offset',epOff);p.set('limit',50);
+ p.set('sort',document.getElementById('fsort').value);const r=await (await fetch(`api/runs/${i}/episodes?`+p)).json();
+ document.getElementById('epinfo').textContent=`${r.total} episodes, showing ${r.offset}..${r.offset+r.rows.length}; steps ${r.steps[0]}..${r.steps[1]}; envs ${r.envs.join(', ')}`;
+ document.getElementById('eptab').innerHTML='<tr><th>step</th><th>env</th><th>task</th><th>reward</th><th>adv</th><th>tok</th><th>lag</th><th>finish</th><th></th></tr>'+
+  r.rows.map(t=>`<tr style="cursor:pointer" onclick="show('${t.trace_id}')"><td>${t.step}</td><td>${t.env}</td><td>${t.task_id}</td><td>${t.reward==null?'-':t.reward.toFixed(3)}</td>`+
+  `<td>${t.advantage==null?'-':t.advantage.toFixed(3)}</td><td>${t.tokens}</td><td>${t.lag??'-'}</td><td>${t.finish_reason??''}</td><td>${t.error?'ERR':''}</td></tr>`).join('');
+ const h=await (await fetch(`api/runs/${i}/episodes/histogram?`+qs())).json();bars('hist',h.counts||[],`reward histogram, n=${h.n}`);
+ const s=await (await fetch(`api/runs/${i}/episodes/series?field=reward`)).json();bars('ser',s.map(x=>x.mean),'mean reward per step');}
+</script>
 <h2>Configs and logs</h2><button onclick="files()">load</button><pre id="files" style="max-height:400px;overflow:auto;background:#f6f6f6"></pre>
 <script>
 let cur=null;
@@ -254,6 +277,109 @@ def build_app(extra_dirs: list[str] | None = None):
     @app.get("/api/runs/{i}/logs")
     def logs(i: int):
         return read_log_tails(run_dir(i))
+
+    # ------------------------------------------------------------------ episode browser
+    indexes: dict[str, "EpisodeIndex"] = {}
+
+    def index_of(i: int):
+        from .episodes import EpisodeIndex
+
+        d = run_dir(i)
+        idx = indexes.get(str(d))
+        if idx is None:
+            idx = indexes[str(d)] = EpisodeIndex(_monitor_dir(d))
+        return idx.refresh()
+
+    def selected(i, step, min_step, max_step, env, task_id, group_id, min_reward, max_reward, errors, q):
+        return index_of(i).select(step=step, min_step=min_step, max_step=max_step, env=env, task_id=task_id,
+                                  group_id=group_id, min_reward=min_reward, max_reward=max_reward, errors=errors, text=q)
+
+    @app.get("/api/runs/{i}/episodes")
+    def episodes(i: int, step: int | None = None, min_step: int | None = None, max_step: int | None = None,
+                 env: str | None = None, task_id: str | None = None, group_id: str | None = None,
+                 min_reward: float | None = None, max_reward: float | None = None, errors: bool | None = None,
+                 q: str | None = None, sort: str = "step", descending: bool = True, offset: int = 0, limit: int = 100):
+        rows = selected(i, step, min_step, max_step, env, task_id, group_id, min_reward, max_reward, errors, q)
+        return index_of(i).page(rows, sort=sort, descending=descending, offset=offset, limit=limit)
+
+    @app.get("/api/runs/{i}/episodes/histogram")
+    def episodes_histogram(i: int, field: str = "reward", bins: int = 20, step: int | None = None,
+                           min_step: int | None = None, max_step: int | None = None, env: str | None = None):
+        from .episodes import EpisodeIndex
+
+        return EpisodeIndex.histogram(selected(i, step, min_step, max_step, env, None, None, None, None, None, None),
+                                      field, bins)
+
+    @app.get("/api/runs/{i}/episodes/series")
+    def episodes_series(i: int, field: str = "reward", env: str | None = None):
+        from .episodes import EpisodeIndex
+
+        return EpisodeIndex.series(selected(i, None, None, None, env, None, None, None, None, None, None), field)
+
+    @app.get("/api/runs/{i}/rollouts")
+    def rollouts(i: int, step: int | None = None, env: str | None = None, task_id: str | None = None,
+                 offset: int = 0, limit: int = 50):
+        from .episodes import EpisodeIndex
+
+        groups = EpisodeIndex.rollouts(selected(i, step, None, None, env, task_id, None, None, None, None, None))
+        return {"total": len(groups), "groups": groups[offset:offset + max(0, min(limit, 500))]}
+
+    @app.get("/api/runs/{i}/episodes/{trace_id}/timeline")
+    def episode_timeline(i: int, trace_id: str):
+        from .episodes import timeline
+
+        t = read_trace(run_dir(i), trace_id)
+        if t is None:
+            raise HTTPException(404, "unknown trace")
+        return {"trace_id": trace_id, "reward": t.get("reward"), "advantage": t.get("advantage"), "turns": timeline(t)}
+
+    @app.get("/api/runs/{i}/series")
+    def metric_series(i: int, key: str, points: int = 2000, producer: str | None = None):
+        from .episodes import downsample
+
+        return downsample(read_metrics(run_dir(i), limit=10 ** 9), key, points, producer)
+
+    @app.get("/api/runs/{i}/logfiles")
+    def logfiles(i: int):
+        d = run_dir(i)
+        out = []
+        for f in sorted(d.rglob("*.log"))[:256]:
+            try:
+                out.append({"name": str(f.relative_to(d)), "size": f.stat().st_size, "mtime": f.stat().st_mtime})
+            except OSError:
+                pass
+        return out
+
+    @app.get("/api/runs/{i}/log")
+    def log(i: int, name: str, offset: int | None = None, lines: int = 400):
+        from .episodes import read_log
+
+        try:
+            return read_log(run_dir(i), name, offset, lines)
+        except PermissionError as e:
+            raise HTTPException(403, str(e))
+        except OSError:
+            raise HTTPException(404, "unknown log file")
+
+    @app.get("/api/view/events")
+    async def view_events(once: bool = False):
+        """Server-sent events: the list of run directories, again whenever a launcher registers a new one."""
+        import asyncio
+
+        from fastapi.responses import StreamingResponse
+
+        async def gen():
+            last = None
+            while True:
+                cur = dirs()
+                if cur != last:
+                    last = cur
+                    yield f"event: runs\ndata: {json.dumps(cur)}\n\n"
+                    if once:
+                        return
+                await asyncio.sleep(2.0)
+
+        return StreamingResponse(gen(), media_type="text/event-stream")
 
     @app.post("/api/view")
     def add_view(body: dict):

@@ -356,18 +356,9 @@ class GroupedExperts(nn.Module):
         xpq = moe_ops.permute_nopad(xq.view(torch.bfloat16), plan).view(torch.uint8)
         xps = moe_ops.permute_nopad(xs.view(torch.bfloat16), plan).view(torch.float32)
         valid = plan.row_src
-        E = self.fp8["gate_up_proj"][0].shape[0]
-        few = T * plan.k < 64 * E and H <= 4096 and self.fp8["down_proj"][0].shape[-1] <= 4096
-        if few:
-            # decode: a handful of rows per expert, the 128-row blocks are mostly padding
-            rows = fp8_ops.count_block_rows(valid)
-            gu = fp8_ops.fp8_gemm_few_rows(xpq, xps, *self.fp8["gate_up_proj"], plan.block_expert, rows)
-        else:
-            gu = fp8_ops.fp8_gemm(xpq, xps, *self.fp8["gate_up_proj"], block_expert=plan.block_expert, row_valid=valid)
+        gu = fp8_ops.fp8_gemm(xpq, xps, *self.fp8["gate_up_proj"], block_expert=plan.block_expert, row_valid=valid)
         h = act_ops.glu_rowmask(gu, valid, self.act, self.arch.swiglu_limit, self.arch.swiglu_alpha)
         hq, hs = fp8_ops.quantize_act(h, row_valid=valid)
-        if few:
-            return fp8_ops.fp8_gemm_few_rows(hq, hs, *self.fp8["down_proj"], plan.block_expert, rows)
         return fp8_ops.fp8_gemm(hq, hs, *self.fp8["down_proj"], block_expert=plan.block_expert, row_valid=valid)
 
     def supports_row_mask(self, x: torch.Tensor) -> bool:

@@ -83,8 +83,6 @@ _CUDA_SIGNATURES = {
     "prb_gemm_bf16_grouped_arrive": [P, P, P, I, I, I, L, L, L, I, I, P, I, I, P, P, P, P],
     "prb_ep_prepare": [P, P, P, P, P, I, I, I, I, I, P],
     "prb_ep_push_blocks": [P, P, P, P, P, P, P, P, P, L, P, I, I, I, I, I, I, I, P, P],
-    "prb_gemm_fp8_swap": [P, P, P, P, P, I, I, I, L, P, I, P, P, P],
-    "prb_count_block_rows": [P, I, P, P],
     "prb_gemm_bf16_splitk": [P, P, P, I, I, I, L, L, L, I, I, F, F, P, L, I, I, P, P],
     "prb_moe_combine": [P, P, P, P, P, L, I, I, P],
     "prb_moe_combine_bwd_w": [P, P, P, P, L, I, I, P],

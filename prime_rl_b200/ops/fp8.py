@@ -48,45 +48,6 @@ def fp8_gemm_ref(aq, sa, bq, sb, block_expert=None) -> torch.Tensor:
     return out
 
 
-def count_block_rows(row_valid: torch.Tensor) -> torch.Tensor:
-    """Real rows (``row_valid >= 0``, they come first) of every 128-row block: int32 [ceil(M / 128)]."""
-    M = row_valid.numel()
-    nb = (M + 127) // 128
-    if not row_valid.is_cuda:
-        pad = torch.full((nb * 128,), -1, dtype=row_valid.dtype)
-        pad[:M] = row_valid
-        return (pad.view(nb, 128) >= 0).sum(1).to(torch.int32)
-    out = torch.empty(nb, dtype=torch.int32, device=row_valid.device)
-    rt.check(rt.lib().prb_count_block_rows(row_valid.data_ptr(), M, out.data_ptr(), rt.stream_ptr(row_valid.device)),
-             "prb_count_block_rows")
-    return out
-
-
-def fp8_gemm_few_rows(aq, sa, bq, sb, block_expert: torch.Tensor, block_rows: torch.Tensor,
-                      out: torch.Tensor | None = None) -> torch.Tensor:
-    """Grouped ``fp8_gemm`` for blocks that are mostly padding (decode: a handful of tokens per expert): the
-    weight tile is the 128-row side of the tensor-core instruction and the block's ``block_rows[b]`` leading rows
-    (rounded up to 32) the other, so the padding costs neither operand traffic nor stores. Rows past
-    ``block_rows[b]`` of a block are left unwritten."""
-    M, K = aq.shape
-    E, N = bq.shape[0], bq.shape[1]
-    if not aq.is_cuda:
-        valid = (torch.arange(M) % 128) < block_rows.repeat_interleave(128)[:M]
-        aq, sa = aq.clone(), sa.clone()
-        aq[~valid] = 0
-        sa[~valid] = 0
-        return fp8_gemm_ref(aq, sa, bq, sb, block_expert).to(torch.bfloat16)
-    assert aq.is_contiguous() and bq.is_contiguous() and sa.is_contiguous() and sb.is_contiguous()
-    assert bq.shape[-1] == K and K % 16 == 0 and K <= 4096
-    if out is None:
-        out = torch.empty(M, N, dtype=torch.bfloat16, device=aq.device)
-    status = rt.status_tensor(aq.device)
-    rt.check(rt.lib().prb_gemm_fp8_swap(aq.data_ptr(), sa.data_ptr(), bq.data_ptr(), sb.data_ptr(), out.data_ptr(), M, N,
-                                        K, out.stride(0), block_expert.data_ptr(), E, block_rows.data_ptr(),
-                                        status.data_ptr(), rt.stream_ptr(aq.device)), "prb_gemm_fp8_swap")
-    return out
-
-
 def fp8_gemm(aq, sa, bq, sb, *, block_expert: torch.Tensor | None = None, out: torch.Tensor | None = None,
              row_valid: torch.Tensor | None = None) -> torch.Tensor:
     """C bf16 [M, N] = dequant(aq, sa) @ dequant(bq, sb)^T. Grouped when ``block_expert`` is given

@@ -265,6 +265,78 @@ def test_dashboard_trace_browser_joins_traces_and_annotations(tmp_path, monkeypa
     assert "Traces" in client.get("/").text
 
 
+def test_dashboard_episode_browser_queries(tmp_path, monkeypatch):
+    """Filtered / sorted pages, histogram, per-step series, rollout groups, per-episode timeline with the
+    trainer's annotations, metric down-sampling, paged log reads and the run-list event stream."""
+    from fastapi.testclient import TestClient
+
+    from prime_rl_b200.dashboard import server as dash
+    from prime_rl_b200.monitors import FileMonitor
+    from prime_rl_b200.orchestrator.orchestrator import trace_record
+    from prime_rl_b200.orchestrator.types import Rollout, Turn
+
+    monkeypatch.setattr(dash, "STATE_DIR", tmp_path / "state")
+    monkeypatch.setattr(dash, "DIRS_FILE", tmp_path / "state" / "dirs.json")
+    run = tmp_path / "run"
+    run.mkdir()
+    (run / "logs").mkdir()
+    (run / "logs" / "trainer.log").write_text("".join(f"line {i}\n" for i in range(1000)))
+    orch, trainer = FileMonitor(run, "orchestrator", chunk_size=4), FileMonitor(run, "trainer")
+    made = []
+    for step in (1, 2, 3):
+        for task in range(2):
+            for sample in range(3):
+                rew = float((task + sample + step) % 2)
+                r = Rollout("rev" if task == 0 else "math", task, f"g{step}-{task}",
+                            [Turn([1, 2], [5, 6, 7][:1 + sample], [-0.5] * (1 + sample), finish_reason="stop")],
+                            reward=rew, advantage=rew - 0.5, policy_version=step - 1)
+                orch.log_trace(trace_record(r, step=step))
+                made.append(r)
+        trainer.log({"loss": 1.0 / step}, step)
+    orch.finalize()
+    last = made[-1]
+    trainer.log_annotations([{"trace_id": last.trace_id, "branch_index": 0, "step": 3,
+                              "logprobs": [0, 0, -0.4, -0.6, -0.5], "entropy": [0, 0, 1.0, 1.0, 1.0],
+                              "loss_mask": [False, False, True, True, True]}], "trainer")
+    trainer.finalize()
+    client = TestClient(dash.build_app([str(run)]))
+    page = client.get("/api/runs/0/episodes", params={"limit": 5, "sort": "reward"}).json()
+    assert page["total"] == 18 and len(page["rows"]) == 5 and page["rows"][0]["reward"] == 1.0
+    assert page["envs"] == ["math", "rev"] and page["steps"] == [1, 3]
+    only = client.get("/api/runs/0/episodes", params={"step": 2, "env": "rev", "min_reward": 0.5}).json()
+    assert only["total"] == sum(1 for r in made if r.env_name == "rev" and r.reward >= 0.5 and r.policy_version == 1)
+    assert all(r["step"] == 2 and r["env"] == "rev" and r["reward"] >= 0.5 for r in only["rows"])
+    assert client.get("/api/runs/0/episodes", params={"offset": 15, "limit": 10}).json()["rows"].__len__() == 3
+    h = client.get("/api/runs/0/episodes/histogram", params={"bins": 2}).json()
+    assert h["n"] == 18 and sum(h["counts"]) == 18 and len(h["counts"]) == 2
+    ser = client.get("/api/runs/0/episodes/series").json()
+    assert [p["step"] for p in ser] == [1, 2, 3] and all(p["count"] == 6 for p in ser)
+    groups = client.get("/api/runs/0/rollouts", params={"step": 3}).json()
+    assert groups["total"] == 2 and all(g["size"] == 3 for g in groups["groups"])
+    assert {g["group_id"] for g in groups["groups"]} == {"g3-0", "g3-1"} and groups["groups"][0]["reward_spread"] == 1.0
+    tl = client.get(f"/api/runs/0/episodes/{last.trace_id}/timeline").json()
+    turn = tl["turns"][0]
+    assert turn["completion_tokens"] == 3 and turn["loss_tokens"] == 3
+    assert turn["trainer_logprob_sum"] == pytest.approx(-1.5) and turn["mean_abs_gap"] == pytest.approx(0.2 / 3)
+    assert turn["mismatch_kl"] > 0
+    pts = client.get("/api/runs/0/series", params={"key": "loss", "points": 2}).json()
+    assert len(pts) == 2 and pts[0]["count"] == 2
+    files = client.get("/api/runs/0/logfiles").json()
+    assert files[0]["name"] == "logs/trainer.log"
+    tail = client.get("/api/runs/0/log", params={"name": "logs/trainer.log", "lines": 3}).json()
+    assert tail["text"].split("\n")[-2:] == ["line 999", ""] and tail["end"] == tail["size"]
+    head = client.get("/api/runs/0/log", params={"name": "logs/trainer.log", "offset": 0, "lines": 2}).json()
+    assert head["text"] == "line 0\nline 1"
+    assert client.get("/api/runs/0/log", params={"name": "../secret.log"}).status_code in (403, 404)
+    ev = client.get("/api/view/events", params={"once": True}).text
+    assert ev.startswith("event: runs") and str(run) in ev
+    # the index only reads what is new
+    orch2 = FileMonitor(run, "orchestrator2", chunk_size=1)
+    orch2.log_trace(trace_record(made[0], step=9))
+    orch2.finalize()
+    assert client.get("/api/runs/0/episodes").json()["total"] == 19
+
+
 def test_nccl_transport_probe_with_a_fake_nvml():
     from prime_rl_b200.utils import nccl
 

@@ -848,49 +848,6 @@ def test_fp8_experts_skip_padding_rows_and_match_the_padded_fp8_path():
     assert torch.equal(q_m[::3], q_all[::3]) and torch.equal(s_m[::3], s_all[::3])
 
 
-@pytest.mark.parametrize("N,K", [(384, 512), (200, 768), (1536, 2048)])
-def test_fp8_grouped_gemm_for_few_rows_per_expert(N, K):
-    """Decode-shaped grouped fp8 GEMM with the operands swapped (weight rows on the 128-row side, the block's real
-    rows on the other): every count of leading real rows, poisoned padding rows, empty and unused blocks."""
-    from prime_rl_b200.ops import fp8
-
-    torch.manual_seed(1)
-    E = 5
-    rows = [1, 31, 32, 33, 64, 100, 128, 0, 17, 128, 5]
-    experts = [0, 1, 2, 3, 4, 0, 1, -1, 2, 2, 4]
-    M = 128 * len(rows)
-    x = torch.randn(M, K, device=DEV).bfloat16()
-    w = (torch.randn(E, N, K, device=DEV) * 0.05).bfloat16()
-    aq, sa = fp8.quantize_act(x)
-    bq = torch.empty(E, N, K, dtype=torch.uint8, device=DEV)
-    sb = torch.empty(E, (N + 127) // 128, (K + 127) // 128, device=DEV)
-    for e in range(E):                                   # 128 x 128 block scales
-        we = w[e].float()
-        pad = torch.zeros((N + 127) // 128 * 128, (K + 127) // 128 * 128, device=DEV)
-        pad[:N, :K] = we
-        blocks = pad.view(pad.shape[0] // 128, 128, pad.shape[1] // 128, 128)
-        sc = blocks.abs().amax((1, 3)).clamp_min(1e-12) / 448.0
-        sb[e] = sc
-        q = (blocks / sc[:, None, :, None]).reshape(pad.shape)[:N, :K].to(torch.float8_e4m3fn)
-        bq[e] = q.view(torch.uint8)
-    block_expert = torch.tensor(experts, dtype=torch.int32, device=DEV)
-    block_rows = torch.tensor(rows, dtype=torch.int32, device=DEV)
-    valid = torch.full((M,), -1, dtype=torch.int32, device=DEV)
-    for b, n in enumerate(rows):
-        valid[b * 128:b * 128 + n] = 1
-    assert torch.equal(fp8.count_block_rows(valid), block_rows)
-    ref = fp8.fp8_gemm_ref(aq, sa, bq, sb, block_expert)
-    aq2, sa2 = aq.clone(), sa.clone()
-    aq2[valid < 0] = 0x7f                                # e4m3 NaN
-    sa2[valid < 0] = float("nan")
-    out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
-    fp8.fp8_gemm_few_rows(aq2, sa2, bq, sb, block_expert, block_rows, out=out)
-    rt.check_status()
-    keep = (valid >= 0) & (block_expert.repeat_interleave(128) >= 0)
-    _close(out[keep], ref[keep], atol=2e-2 * K ** 0.5 / 8, rtol=2e-2)
-    assert bool((out[~keep] == 7.0).all())               # padding rows are left alone
-
-
 def test_qkv_rope_to_cache_matches_separate_ops():
     """Fused split + QK-norm + rotary + paged-cache write against qkv_norm_rope followed by index_copy_
     (bit-equal), with and without the contiguous K / V outputs and without QK-norm."""
