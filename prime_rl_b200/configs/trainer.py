@@ -77,6 +77,7 @@ class LoRAConfig(BaseConfig):
     target_modules: list[str] = ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj",
                                  "experts", "fc1_latent_proj", "fc2_latent_proj"]
     modules_to_save: list[str] = []
+    num_adapters: int = Field(1, ge=1)      # > 1: independent adapters chosen per token by ``lora_num_tokens``
 
 
 class DebugModelConfig(BaseConfig):

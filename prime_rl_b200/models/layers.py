@@ -91,6 +91,31 @@ class LoRAAdapter(nn.Module):
                 b.zero_()
 
 
+class MultiLoRA(nn.ModuleList):
+    """Several adapters of one projection (one per concurrent run); which one a token uses follows from
+    ``set_lora_num_tokens`` (reference: src/prime_rl/trainer/models/layers/lora/base.py:14-60,
+    multi_linear.py:38)."""
+
+    def ops_args(self):
+        return [(a.lora_A, list(a.lora_B), a.scale) for a in self]
+
+
+_LORA_NUM_TOKENS: list[torch.Tensor | None] = [None]
+
+
+def set_lora_num_tokens(num_tokens: torch.Tensor | None) -> None:
+    """``num_tokens[i]`` consecutive tokens of the coming forward pass use adapter i (a micro-batch is sorted by
+    adapter). ``None``: every token uses adapter 0."""
+    _LORA_NUM_TOKENS[0] = num_tokens
+
+
+def get_lora_num_tokens(total: int, device) -> torch.Tensor:
+    t = _LORA_NUM_TOKENS[0]
+    if t is None:
+        return torch.tensor([total], dtype=torch.int32, device=device)
+    return t.to(device)
+
+
 class Linear(nn.Module):
     """Bias-free (by default) projection ``[out, in]`` with an optional LoRA adapter."""
 
@@ -135,6 +160,10 @@ class Linear(nn.Module):
             x2 = x.reshape(-1, x.shape[-1])
             xq, xs = fp8_ops.quantize_act(x2)
             y = fp8_ops.fp8_gemm(xq, xs, self.fp8[0], self.fp8[1]).reshape(*x.shape[:-1], self.fp8[0].shape[0])
+            return y if self.bias is None else y + self.bias
+        if isinstance(self.lora, MultiLoRA):
+            nt = get_lora_num_tokens(x.numel() // x.shape[-1], x.device)
+            y = lora_ops.multi_lora_linear(x, self.weight, self.lora.ops_args(), nt)
             return y if self.bias is None else y + self.bias
         if self.lora is not None:
             y = lora_ops.lora_linear(x, self.weight, self.lora.lora_A, list(self.lora.lora_B), self.lora.scale)
@@ -378,7 +407,8 @@ class GroupedExperts(nn.Module):
 
     def forward(self, xp: torch.Tensor, block_expert: torch.Tensor, expert_offset: torch.Tensor,
                 out: torch.Tensor | None = None, row_valid: torch.Tensor | None = None,
-                block_ready: tuple[torch.Tensor, torch.Tensor] | None = None) -> torch.Tensor:
+                block_ready: tuple[torch.Tensor, torch.Tensor] | None = None,
+                row_adapter: torch.Tensor | None = None) -> torch.Tensor:
         """``out`` (optional, ``[P, H]`` bf16): memory the last projection writes into. ``row_valid``
         (int32 per permuted row, < 0 = padding; only where ``supports_row_mask``): those rows are skipped.
         ``block_ready = (arrived, expected)`` (only where ``supports_block_ready``): per 128-row block of ``xp``,
@@ -400,7 +430,12 @@ class GroupedExperts(nn.Module):
                 return self._biased(fp8_ops.fp8_gemm(hq, hs, *self.fp8["down_proj"], block_expert=block_expert),
                                     self.down_proj_bias, block_expert)
             return fp8_ops.fp8_gemm(hq, hs, *self.fp8["down_proj"], block_expert=block_expert, out=out)
-        if self.lora_gate_up is not None:
+        if isinstance(self.lora_gate_up, MultiLoRA):
+            if row_adapter is None:
+                raise ValueError("several adapters on the experts need the adapter of every permuted row")
+            gu = lora_ops.multi_lora_grouped_linear(xp, self.gate_up_proj, self.lora_gate_up.ops_args(), row_adapter,
+                                                    block_expert, expert_offset)
+        elif self.lora_gate_up is not None:
             l = self.lora_gate_up
             gu = lora_ops.lora_grouped_linear(xp, self.gate_up_proj, l.lora_A, list(l.lora_B), l.scale, block_expert,
                                               expert_offset)
@@ -410,7 +445,10 @@ class GroupedExperts(nn.Module):
         h = ops.glu(gu, self.act, self.arch.swiglu_limit, self.arch.swiglu_alpha)
         if self.down_proj_bias is not None:
             out = None                # the bias add makes a new tensor anyway
-        if self.lora_down is not None:
+        if isinstance(self.lora_down, MultiLoRA):
+            y = lora_ops.multi_lora_grouped_linear(h, self.down_proj, self.lora_down.ops_args(), row_adapter,
+                                                   block_expert, expert_offset, out=out)
+        elif self.lora_down is not None:
             l = self.lora_down
             y = lora_ops.lora_grouped_linear(h, self.down_proj, l.lora_A, list(l.lora_B), l.scale, block_expert,
                                              expert_offset, out=out)
@@ -459,6 +497,9 @@ class MoE(nn.Module):
         self.last_topk = idx
         xe = x if self.fc1_latent_proj is None else self.fc1_latent_proj(x)
         if self.dispatcher is not None:
+            if isinstance(self.experts.lora_gate_up, MultiLoRA):
+                raise NotImplementedError("several adapters on expert-parallel experts: the adapter ids of the "
+                                          "dispatched rows are not exchanged")
             y = self.dispatcher(self.experts, xe, idx, w, counts)
         else:
             plan = self.router.last_plan
@@ -470,6 +511,13 @@ class MoE(nn.Module):
                 # inference: nothing touches the rows that only pad every expert to a multiple of 128
                 xp = moe_ops.permute_nopad(xe, plan)
                 yp = self.experts(xp, plan.block_expert, plan.expert_offset, row_valid=plan.row_src)
+            elif isinstance(self.experts.lora_gate_up, MultiLoRA):
+                # adapter of the token that every permuted row came from (-1: padding row)
+                tok_adapter = lora_ops.adapter_of_token(get_lora_num_tokens(T, x.device), T)
+                src = plan.row_src.long()
+                row_adapter = torch.where(src >= 0, tok_adapter[src.clamp(min=0) // plan.k], -1)
+                xp = moe_ops.permute(xe, plan)
+                yp = self.experts(xp, plan.block_expert, plan.expert_offset, row_adapter=row_adapter)
             else:
                 xp = moe_ops.permute(xe, plan)
                 yp = self.experts(xp, plan.block_expert, plan.expert_offset)

@@ -18,7 +18,7 @@ from torch.utils.checkpoint import checkpoint
 
 from .. import ops
 from .config import ModelArch
-from .layers import DecoderLayer, GroupedExperts, Linear, LoRAAdapter, MoE, RMSNorm, SeqInfo
+from .layers import DecoderLayer, GroupedExperts, Linear, LoRAAdapter, MoE, MultiLoRA, RMSNorm, SeqInfo
 
 
 class DecoderStack(nn.Module):
@@ -187,11 +187,17 @@ _FUSED_MEMBERS = {"qkv_proj": ["q_proj", "k_proj", "v_proj"], "gate_up_proj": ["
 
 
 def apply_lora(model: CausalLM, rank: int, alpha: float, target_modules: list[str],
-               modules_to_save: list[str] | None = None, seed: int = 0) -> list[str]:
+               modules_to_save: list[str] | None = None, seed: int = 0, num_adapters: int = 1) -> list[str]:
     """Freezes the base model and attaches adapters to every targeted projection. A fused
     projection gets one adapter segment per member that is targeted; members that are not
-    targeted keep a zero-width contribution. Returns the names of adapted modules."""
+    targeted keep a zero-width contribution. ``num_adapters > 1``: every projection gets that many independent
+    adapters (``layers.MultiLoRA``), chosen per token by ``layers.set_lora_num_tokens``. Returns the names of
+    adapted modules."""
     arch = model.arch
+
+    def many(make):
+        return make() if num_adapters == 1 else MultiLoRA([make() for _ in range(num_adapters)])
+
     for p in model.parameters():
         p.requires_grad_(False)
     adapted: list[str] = []
@@ -213,15 +219,16 @@ def apply_lora(model: CausalLM, rank: int, alpha: float, target_modules: list[st
                 segs = [half, half]
             else:
                 segs = [mod.weight.shape[0]]
-            mod.lora = LoRAAdapter(mod.weight.shape[1], segs, rank, alpha, members, dtype=dtype, device=device)
+            mod.lora = many(lambda: LoRAAdapter(mod.weight.shape[1], segs, rank, alpha, members, dtype=dtype,
+                                                device=device))
             adapted.append(name)
         elif isinstance(mod, GroupedExperts) and _matches(name, target_modules):
             E, width, H = mod.gate_up_proj.shape
             segs = [width // 2, width // 2] if width == 2 * arch.moe_intermediate_size else [width]
-            mod.lora_gate_up = LoRAAdapter(H, segs, rank, alpha, ["gate_proj", "up_proj"][: len(segs)],
-                                           num_experts=E, dtype=dtype, device=device)
-            mod.lora_down = LoRAAdapter(mod.down_proj.shape[2], [H], rank, alpha, ["down_proj"], num_experts=E,
-                                        dtype=dtype, device=device)
+            mod.lora_gate_up = many(lambda: LoRAAdapter(H, segs, rank, alpha, ["gate_proj", "up_proj"][: len(segs)],
+                                                        num_experts=E, dtype=dtype, device=device))
+            mod.lora_down = many(lambda: LoRAAdapter(mod.down_proj.shape[2], [H], rank, alpha, ["down_proj"],
+                                                     num_experts=E, dtype=dtype, device=device))
             adapted.append(name)
     # deterministic adapter init, identical on every data-parallel replica
     for i, (name, mod) in enumerate((n, m) for n, m in model.named_modules() if isinstance(m, LoRAAdapter)):

@@ -39,49 +39,57 @@ def lora_linear_ref(x, w, a_cat, b_list, scale):
     return y + scale * torch.cat(parts, dim=-1)
 
 
-def _block_diag(b_list, scale):
-    """[.., out_s, r] x S -> [.., sum(out_s), S*r] with B_s * scale in its own r columns."""
+def _block_diag(b_list, scale, rows=None):
+    """[.., out_s, r] x S -> [.., out, S*r] with B_s * scale in its own r columns. ``rows[s] = (c0, c1)`` places
+    block s at output rows c0..c1 (several adapters of one projection share rows); default: one after another."""
     r = b_list[0].shape[-1]
     S = len(b_list)
-    out = sum(b.shape[-2] for b in b_list)
+    if rows is None:
+        rows = _segments([b.shape[-2] for b in b_list])
+    out = max(c1 for _, c1 in rows)
     bd = torch.zeros(*b_list[0].shape[:-2], out, S * r, dtype=b_list[0].dtype, device=b_list[0].device)
-    c = 0
     for s, b in enumerate(b_list):
-        bd[..., c:c + b.shape[-2], s * r:(s + 1) * r] = b if scale == 1.0 else b * scale
-        c += b.shape[-2]
+        c0, c1 = rows[s]
+        bd[..., c0:c1, s * r:(s + 1) * r] = b if scale == 1.0 else b * scale
     return bd
 
 
 class _LoRALinear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, a_cat, scale, *b_list):
+    def forward(ctx, x, w, a_cat, scale, rank_mask, rows, *b_list):
+        """``rank_mask`` ([T, S*r] or None) multiplies x A^T: several adapters share one launch, every token keeps
+        only the rank columns of its own adapter (times that adapter's scale)."""
         t = gemm(x, a_cat)
-        bd = _block_diag(b_list, scale)
+        if rank_mask is not None:
+            t = t * rank_mask
+        bd = _block_diag(b_list, scale, rows)
         y = gemm(x, w, ext=(t, bd))
-        ctx.save_for_backward(x, w, a_cat, t, bd)
+        ctx.save_for_backward(x, w, a_cat, t, bd, rank_mask)
         ctx.scale = scale
-        ctx.seg = [b.shape[0] for b in b_list]
+        ctx.rows = rows if rows is not None else _segments([b.shape[0] for b in b_list])
         ctx.b_dtype = b_list[0].dtype
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x, w, a_cat, t, bd = ctx.saved_tensors
+        x, w, a_cat, t, bd, rank_mask = ctx.saved_tensors
         scale = ctx.scale
-        S = len(ctx.seg)
+        S = len(ctx.rows)
         r = bd.shape[1] // S
         if not dy.is_contiguous():
             dy = dy.contiguous()
         dt = gemm(dy, bd, b_mn=True)                       # [T, S*r], scale is inside bd
+        if rank_mask is not None:
+            dt = dt * rank_mask
         db = []
-        for s, (c0, c1) in enumerate(_segments(ctx.seg)):
+        for s, (c0, c1) in enumerate(ctx.rows):
             db.append(gemm(dy[:, c0:c1], t[:, s * r:(s + 1) * r], a_mn=True, b_mn=True, out_dtype=torch.float32,
                            alpha=scale).to(ctx.b_dtype))
         da = gemm(dt, x, a_mn=True, b_mn=True, out_dtype=torch.float32).to(a_cat.dtype)
         dx = None
         if ctx.needs_input_grad[0]:
             dx = gemm(dy, w, b_mn=True, ext=(dt, a_cat))
-        return (dx, None, da, None, *db)
+        return (dx, None, da, None, None, None, *db)
 
 
 def lora_linear(x, w, a_cat, b_list, scale: float):
@@ -91,9 +99,60 @@ def lora_linear(x, w, a_cat, b_list, scale: float):
         x2 = x.reshape(-1, shape[-1])
         if not x2.is_contiguous():
             x2 = x2.contiguous()
-        y = _LoRALinear.apply(x2, w, a_cat, float(scale), *b_list)
+        y = _LoRALinear.apply(x2, w, a_cat, float(scale), None, None, *b_list)
         return y.reshape(*shape[:-1], w.shape[0])
     return lora_linear_ref(x, w, a_cat, list(b_list), scale)
+
+
+def adapter_of_token(num_tokens: torch.Tensor, total: int) -> torch.Tensor:
+    """``num_tokens[i]`` consecutive tokens belong to adapter i -> adapter index per token ([total] int64); no
+    host read (tokens past the sum, if any, get the last adapter)."""
+    ends = num_tokens.to(torch.int64).cumsum(0)
+    pos = torch.arange(total, device=num_tokens.device)
+    return torch.searchsorted(ends, pos, right=True).clamp_(max=num_tokens.numel() - 1)
+
+
+def rank_mask_for(adapter_idx: torch.Tensor, scales, cols_per_adapter: int, dtype) -> torch.Tensor:
+    """[rows, n * cols_per_adapter]: scale_i in the columns of row's adapter i, zero elsewhere."""
+    n = len(scales)
+    sc = torch.as_tensor(scales, dtype=torch.float32, device=adapter_idx.device)
+    onehot = torch.nn.functional.one_hot(adapter_idx.clamp(min=0), n).to(torch.float32) * sc
+    onehot = onehot * (adapter_idx >= 0).unsqueeze(-1)
+    return onehot.repeat_interleave(cols_per_adapter, dim=1).to(dtype)
+
+
+def multi_lora_linear(x, w, adapters, num_tokens: torch.Tensor):
+    """Several adapters in one micro-batch (the reference's MultiLoRALinear,
+    src/prime_rl/trainer/models/layers/lora/multi_linear.py:38-164): ``num_tokens[i]`` consecutive tokens use
+    adapter i. ``adapters[i] = (a_cat_i [S*r, in], b_list_i (S tensors [out_s, r]), scale_i)``.
+
+    y[t] = x[t] W^T + scale_i * sum_s (x[t] A_{i,s}^T) B_{i,s}^T for the adapter i of token t. All adapters ride in
+    ONE extra reduction segment of the base GEMM: the A matrices are stacked along the rank, x A^T is masked so that
+    a token keeps only its adapter's columns, and the B matrices of all adapters sit side by side over the same
+    output rows."""
+    shape = x.shape
+    x2 = x.reshape(-1, shape[-1])
+    T = x2.shape[0]
+    n = len(adapters)
+    S = len(adapters[0][1])
+    r = adapters[0][1][0].shape[-1]
+    idx = adapter_of_token(num_tokens.to(x.device), T)
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
+        y = x2 @ w.to(x.dtype).t()
+        add = torch.zeros_like(y)
+        for i, (a_cat, b_list, scale) in enumerate(adapters):
+            t = x2 @ a_cat.to(x.dtype).t()
+            parts = [t[:, s * r:(s + 1) * r] @ b.to(x.dtype).t() for s, b in enumerate(b_list)]
+            add = add + (idx == i).unsqueeze(-1).to(x.dtype) * (scale * torch.cat(parts, dim=-1))
+        return (y + add).reshape(*shape[:-1], w.shape[0])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    a_all = torch.cat([a for a, _, _ in adapters], dim=0)                     # [n*S*r, in]
+    b_all = [b for _, bl, _ in adapters for b in bl]
+    seg = _segments([b.shape[0] for b in adapters[0][1]])
+    mask = rank_mask_for(idx, [sc for _, _, sc in adapters], S * r, x.dtype)
+    y = _LoRALinear.apply(x2, w, a_all, 1.0, mask, seg * n, *b_all)
+    return y.reshape(*shape[:-1], w.shape[0])
 
 
 def kgrouped_gemm(a: torch.Tensor, b: torch.Tensor, expert_offset: torch.Tensor, num_experts: int, *,
@@ -134,29 +193,33 @@ def lora_grouped_linear_ref(x, w, a_cat, b_list, scale, block_expert):
 
 class _LoRAGroupedLinear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, a_cat, scale, block_expert, expert_offset, out, *b_list):
+    def forward(ctx, x, w, a_cat, scale, block_expert, expert_offset, out, rank_mask, rows, *b_list):
         t = gemm(x, a_cat, block_expert=block_expert)
-        bd = _block_diag(b_list, scale)                    # [E, out, S*r]
+        if rank_mask is not None:                          # several adapters: see _LoRALinear
+            t = t * rank_mask
+        bd = _block_diag(b_list, scale, rows)              # [E, out, S*r]
         y = gemm(x, w, block_expert=block_expert, ext=(t, bd), out=out)
         ctx.grad_out = getattr(x, "_grad_out_buf", None)   # see ops/matmul.py _GroupedLinear
-        ctx.save_for_backward(x, w, a_cat, t, block_expert, expert_offset, bd)
+        ctx.save_for_backward(x, w, a_cat, t, block_expert, expert_offset, bd, rank_mask)
         ctx.scale = scale
-        ctx.seg = [b.shape[1] for b in b_list]
+        ctx.rows = rows if rows is not None else _segments([b.shape[1] for b in b_list])
         ctx.b_dtype = b_list[0].dtype
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x, w, a_cat, t, block_expert, expert_offset, bd = ctx.saved_tensors
+        x, w, a_cat, t, block_expert, expert_offset, bd, rank_mask = ctx.saved_tensors
         scale = ctx.scale
         E = w.shape[0]
-        S = len(ctx.seg)
+        S = len(ctx.rows)
         r = bd.shape[2] // S
         if not dy.is_contiguous():
             dy = dy.contiguous()
         dt = gemm(dy, bd, b_mn=True, block_expert=block_expert)     # [P, S*r], scale is inside bd
+        if rank_mask is not None:
+            dt = dt * rank_mask
         db = []
-        for s, (c0, c1) in enumerate(_segments(ctx.seg)):
+        for s, (c0, c1) in enumerate(ctx.rows):
             db.append(kgrouped_gemm(dy[:, c0:c1], t[:, s * r:(s + 1) * r], expert_offset, E, alpha=scale)
                       .to(ctx.b_dtype))
         da = kgrouped_gemm(dt, x, expert_offset, E).to(a_cat.dtype)
@@ -164,13 +227,38 @@ class _LoRAGroupedLinear(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             go = ctx.grad_out if (ctx.grad_out is not None and ctx.grad_out.shape == x.shape) else None
             dx = gemm(dy, w, b_mn=True, block_expert=block_expert, ext=(dt, a_cat), out=go)
-        return (dx, None, da, None, None, None, None, *db)
+        return (dx, None, da, None, None, None, None, None, None, *db)
+
+
+def multi_lora_grouped_linear(x, w, adapters, row_adapter: torch.Tensor, block_expert, expert_offset, out=None):
+    """Per-expert projection with several adapters in one micro-batch (the reference's multi-LoRA experts,
+    src/prime_rl/trainer/models/layers/lora/multi_moe.py). ``row_adapter`` [P] int64: adapter of the token each
+    permuted row came from (-1 for padding rows). ``adapters[i] = (a_cat_i [E, S*r, in], b_list_i, scale_i)``."""
+    n = len(adapters)
+    S = len(adapters[0][1])
+    r = adapters[0][1][0].shape[-1]
+    if not (x.is_cuda and x.dtype == torch.bfloat16):
+        from .matmul import grouped_linear
+
+        y = grouped_linear(x, w, block_expert, expert_offset)
+        for i, (a_cat, b_list, scale) in enumerate(adapters):
+            t = grouped_linear(x, a_cat, block_expert, expert_offset)
+            parts = [grouped_linear(t[:, s * r:(s + 1) * r].contiguous(), b, block_expert, expert_offset)
+                     for s, b in enumerate(b_list)]
+            y = y + (row_adapter == i).unsqueeze(-1).to(x.dtype) * (scale * torch.cat(parts, dim=-1))
+        return y
+    a_all = torch.cat([a for a, _, _ in adapters], dim=1)                     # [E, n*S*r, in]
+    b_all = [b for _, bl, _ in adapters for b in bl]
+    seg = _segments([b.shape[1] for b in adapters[0][1]])
+    mask = rank_mask_for(row_adapter, [sc for _, _, sc in adapters], S * r, x.dtype)
+    return _LoRAGroupedLinear.apply(x, w, a_all, 1.0, block_expert, expert_offset, out, mask, seg * n, *b_all)
 
 
 def lora_grouped_linear(x, w, a_cat, b_list, scale: float, block_expert, expert_offset, out=None):
     """x: [P, in] permuted rows; w: [E, out, in] frozen; a_cat: [E, S*r, in]; b_list[s]: [E, out_s, r]."""
     if x.is_cuda and x.dtype == torch.bfloat16:
-        return _LoRAGroupedLinear.apply(x, w, a_cat, float(scale), block_expert, expert_offset, out, *b_list)
+        return _LoRAGroupedLinear.apply(x, w, a_cat, float(scale), block_expert, expert_offset, out, None, None,
+                                        *b_list)
     # CPU: differentiable composition
     from .matmul import grouped_linear
 

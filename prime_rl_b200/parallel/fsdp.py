@@ -298,6 +298,15 @@ class FSDPRuntime:
             u.pending = len(u.params)
         return self.grad_pool[u.grad_buffer]
 
+    def _keep(self, u: Unit, mine: torch.Tensor) -> None:
+        """This rank's reduced slice of a unit joins the persistent accumulator on the device, or leaves for the
+        host accumulator when a sink is installed (``sp.grad_sink(offset, slice)``, the CPU-optimizer path)."""
+        sink = getattr(self.sp, "grad_sink", None)
+        if sink is not None:
+            sink(u.shard_offset, mine)
+        else:
+            self.sp.unit_shard(u, self.sp.grad_shard).add_(mine)
+
     def _reduce_unit(self, u: Unit) -> None:
         """Reduce-scatter of the unit's gradient buffer; this rank's slice joins the persistent accumulator."""
         if u.grad_buffer < 0:
@@ -306,7 +315,7 @@ class FSDPRuntime:
         n = u.numel // self.sp.N
         mine = torch.empty(n, dtype=torch.float32, device=self.sp.device)
         _reduce_scatter(mine, full, self.sp.group, self.sp.N)
-        self.sp.unit_shard(u, self.sp.grad_shard).add_(mine)
+        self._keep(u, mine)
         full.zero_()
         self.grad_pool_owner[u.grad_buffer] = None
         u.grad_buffer, u.pending = -1, 0
@@ -321,7 +330,7 @@ class FSDPRuntime:
             n = self.root.numel // self.sp.N
             mine = torch.empty(n, dtype=torch.float32, device=self.sp.device)
             _reduce_scatter(mine, self.root_grads, self.sp.group, self.sp.N)
-            self.sp.unit_shard(self.root, self.sp.grad_shard).add_(mine)
+            self._keep(self.root, mine)
             self.root_grads.zero_()
 
     def after_optimizer_step(self) -> None:

@@ -317,9 +317,13 @@ class FlatOptimizer:
     def __init__(self, config, named_params, *, max_steps: int | None = None, scheduler_config=None,
                  dp_group=None, expert_params=None, expert_reduce_group=None, expert_norm_group=None,
                  shard_group=None, replicate_group=None, expert_shard_group=None, offload: str | None = None,
-                 offload_chunk: int = 16 * 1024 * 1024, p2p_collectives: bool = False, fsdp=None):
+                 offload_chunk: int = 16 * 1024 * 1024, p2p_collectives: bool = False, fsdp=None,
+                 offload_gradients: bool = False, max_pinned_slots: int | None = None):
         """``fsdp``: ``(ShardedParameters, FSDPRuntime)`` when the dense parameters are sharded (ZeRO-3); the
-        dense group then works on the persistent slices and ``named_params`` is ignored."""
+        dense group then works on the persistent slices and ``named_params`` is ignored. ``offload_gradients``
+        (with ``offload = "cpu"`` and ``fsdp``): every layer's reduced gradient slice leaves for host memory as
+        soon as its reduce-scatter is done and is accumulated there, under the rest of the backward pass
+        (``optim_offload.GradientOffload``)."""
         self.config = config
         self.kind = config.type
         self.step_count = 0
@@ -344,7 +348,7 @@ class FlatOptimizer:
         self.last_grad_norm: torch.Tensor | None = None
         # optimizer state in host memory: "state" parks it there between steps, "cpu" also runs the update there
         self.offload = offload
-        self._state_offload, self._cpu_step = [], []
+        self._state_offload, self._cpu_step, self._grad_offload = [], [], []
         if offload == "state":
             from .optim_offload import StateOffload
 
@@ -353,6 +357,13 @@ class FlatOptimizer:
             from .optim_offload import CPUStep
 
             self._cpu_step = [CPUStep(g, self.kind, offload_chunk) for g in self.groups]
+            self._grad_offload = [None] * len(self.groups)
+            if offload_gradients and fsdp is not None:
+                from .optim_offload import GradientOffload
+
+                go = GradientOffload(self.groups[0].shard_len, dev, offload_chunk, max_pinned_slots)
+                self._grad_offload[0] = go
+                fsdp[0].grad_sink = go.submit_at
         elif offload is not None:
             raise ValueError(f"unknown optimizer offload mode {offload}")
 
@@ -376,9 +387,13 @@ class FlatOptimizer:
 
     def _global_sumsq(self) -> torch.Tensor:
         self._sumsq.zero_()
-        for g in self.groups:
+        for gi, g in enumerate(self.groups):
             part = torch.zeros_like(self._sumsq)
-            optim_ops.sumsq(g.grad_shard, part)
+            go = self._grad_offload[gi] if self._grad_offload else None
+            if go is not None:                        # the gradient lives in the host accumulator
+                part += float(go.wait().double().pow(2).sum())
+            else:
+                optim_ops.sumsq(g.grad_shard, part)
             if dist.is_initialized():
                 if g.sharded:
                     dist.all_reduce(part, group=g.shard_group)
@@ -401,8 +416,12 @@ class FlatOptimizer:
             self.hyper.copy_(torch.tensor([lr, 1 - b1 ** t, math.sqrt(1 - b2 ** t)]), non_blocking=True)
         if self._cpu_step:
             scale = float(coef)                       # host value: the update runs on the CPU
-            for g, cs in zip(self.groups, self._cpu_step):
-                cs.step(lr=lr, grad_scale=scale, t=t, cfg=c)      # writes the new parameters to the device
+            for gi, (g, cs) in enumerate(zip(self.groups, self._cpu_step)):
+                go = self._grad_offload[gi]
+                # writes the new parameters to the device
+                cs.step(lr=lr, grad_scale=scale, t=t, cfg=c, host_grad=go.wait() if go is not None else None)
+                if go is not None:
+                    go.reset()
                 g.lowp_written_by_kernel = True
                 if g.sharded:
                     g.publish()
@@ -516,7 +535,8 @@ class FlatOptimizer:
 def setup_optimizer(config, model, *, max_steps=None, scheduler_config=None, dp_group=None,
                     expert_reduce_group=None, expert_norm_group=None, shard_group=None, replicate_group=None,
                     expert_shard_group=None, offload: str | None = None,
-                    offload_chunk: int = 16 * 1024 * 1024, p2p_collectives: bool = False, fsdp=None) -> FlatOptimizer:
+                    offload_chunk: int = 16 * 1024 * 1024, p2p_collectives: bool = False, fsdp=None,
+                    offload_gradients: bool = False, max_pinned_slots: int | None = None) -> FlatOptimizer:
     """Parameters marked ``_is_expert_shard`` (set by the expert-parallel setup) form their own
     group: they are reduced over the ranks that replicate the same expert shard."""
     dense = [(n, p) for n, p in model.named_parameters() if not getattr(p, "_is_expert_shard", False)]
@@ -525,4 +545,5 @@ def setup_optimizer(config, model, *, max_steps=None, scheduler_config=None, dp_
                          expert_params=expert, expert_reduce_group=expert_reduce_group,
                          expert_norm_group=expert_norm_group, shard_group=shard_group,
                          replicate_group=replicate_group, expert_shard_group=expert_shard_group, offload=offload,
-                         offload_chunk=offload_chunk, p2p_collectives=p2p_collectives, fsdp=fsdp)
+                         offload_chunk=offload_chunk, p2p_collectives=p2p_collectives, fsdp=fsdp,
+                         offload_gradients=offload_gradients, max_pinned_slots=max_pinned_slots)

@@ -75,8 +75,9 @@ class RLTrainer:
                 m.router.force_balanced = True
         if mc.lora is not None:
             adapted = apply_lora(self.model, mc.lora.rank, mc.lora.alpha, mc.lora.target_modules,
-                                 mc.lora.modules_to_save)
-            self.logger.info(f"LoRA r={mc.lora.rank} on {len(adapted)} modules")
+                                 mc.lora.modules_to_save, num_adapters=mc.lora.num_adapters)
+            self.multi_lora = mc.lora.num_adapters > 1
+            self.logger.info(f"LoRA r={mc.lora.rank} x {mc.lora.num_adapters} on {len(adapted)} modules")
         if mc.freeze_moe_router:
             freeze_router(self.model)
         if mc.ac is not None:
@@ -110,7 +111,15 @@ class RLTrainer:
             if (zero and ep_on and d.dp_replicate == 1 and d.dp_shard_cp // d.ep > 1) else None,
             offload="cpu" if mc.full_offload else ("state" if mc.optim_cpu_offload else None),
             offload_chunk=mc.full_offload.chunk_elements if mc.full_offload else 16 * 1024 * 1024,
-            p2p_collectives=mc.optim_collectives == "p2p" and self.device.type == "cuda", fsdp=fsdp)
+            p2p_collectives=mc.optim_collectives == "p2p" and self.device.type == "cuda", fsdp=fsdp,
+            offload_gradients=bool(mc.full_offload) and fsdp is not None,
+            max_pinned_slots=mc.full_offload.max_pinned_slots if mc.full_offload else None)
+        if mc.full_offload and mc.full_offload.numa_bind and self.device.type == "cuda":
+            from ..optim_offload import bind_to_gpu_numa_node, pci_address
+
+            node = bind_to_gpu_numa_node(pci_address(self.device))      # host buffers next to the GPU's PCIe root
+            if node is not None:
+                self.logger.info(f"CPU optimizer threads bound to NUMA node {node}")
         self.ckpt = CheckpointManager(self.run_dir, cfg.ckpt, is_master=self.world.is_master, rank=self.world.rank) \
             if cfg.ckpt is not None or cfg.resume is not None else None
         self._setup_data()
@@ -256,6 +265,10 @@ class RLTrainer:
 
     def _forward(self, ids, seq, mb):
         """Decoder forward; multimodal rows go through the vision tower first."""
+        if getattr(self, "multi_lora", False):
+            from ...models.layers import set_lora_num_tokens
+
+            set_lora_num_tokens(mb.lora_num_tokens)          # which adapter the tokens of this micro-batch use
         if self.mm is None:
             if mb.mm_kwargs:
                 raise ValueError("the batch carries image tensors but the trainer has no model.vlm section")

@@ -82,7 +82,15 @@ class SFTTrainer:
             if (zero and ep_on and d.dp_replicate == 1 and d.dp_shard_cp // d.ep > 1) else None,
             offload="cpu" if mc.full_offload else ("state" if mc.optim_cpu_offload else None),
             offload_chunk=mc.full_offload.chunk_elements if mc.full_offload else 16 * 1024 * 1024,
-            p2p_collectives=mc.optim_collectives == "p2p" and self.device.type == "cuda", fsdp=fsdp)
+            p2p_collectives=mc.optim_collectives == "p2p" and self.device.type == "cuda", fsdp=fsdp,
+            offload_gradients=bool(mc.full_offload) and fsdp is not None,
+            max_pinned_slots=mc.full_offload.max_pinned_slots if mc.full_offload else None)
+        if mc.full_offload and mc.full_offload.numa_bind and self.device.type == "cuda":
+            from ..optim_offload import bind_to_gpu_numa_node, pci_address
+
+            node = bind_to_gpu_numa_node(pci_address(self.device))      # host buffers next to the GPU's PCIe root
+            if node is not None:
+                self.logger.info(f"CPU optimizer threads bound to NUMA node {node}")
         # online evals: an evals process (or the launcher's inference server) follows the weights written here
         self.weight_sender = None
         if cfg.eval is not None or cfg.weight_broadcast is not None:

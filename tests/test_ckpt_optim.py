@@ -147,3 +147,56 @@ def test_optimizer_offload_matches_device_resident_step(mode):
         assert torch.allclose(a, b, rtol=2e-5, atol=2e-6)
     sd = opt_off.state_dict()
     assert set(sd["state"]) >= {"exp_avg", "exp_avg_sq"}
+
+
+def test_gradient_offload_accumulates_pieces_on_the_host_with_bounded_slots():
+    """Pieces of a gradient shard submitted while 'the backward pass goes on' end up summed in the host
+    accumulator; more pieces than pinned slots only cause waiting, never loss; bf16 sources take the C++ path."""
+    import torch
+
+    from prime_rl_b200.trainer.optim_offload import GradientOffload
+
+    torch.manual_seed(0)
+    n = 10_000
+    go = GradientOffload(n, torch.device("cpu"), chunk_elements=1024, max_pinned_slots=2)
+    total = torch.zeros(n)
+    for _ in range(3):                                   # three micro-batches
+        g = torch.randn(n)
+        total += g
+        for lo in range(0, n, 2500):                     # four layers' slices each
+            piece = g[lo:lo + 2500].clone()
+            go.submit(piece, offset=lo)
+            assert float(piece.abs().sum()) == 0.0       # the device copy is cleared for the next micro-batch
+    acc = go.wait()
+    assert torch.allclose(acc, total, atol=1e-5) and go.stats["pieces"] == 3 * 4 * 3
+    go.reset()
+    assert float(go.wait().abs().sum()) == 0.0
+    go.close()
+    gb = GradientOffload(512, torch.device("cpu"), chunk_elements=512, src_dtype=torch.bfloat16)
+    src = torch.randn(512).bfloat16()
+    gb.submit_at(0, src.clone())
+    gb.submit_at(0, src.clone())
+    assert torch.allclose(gb.wait(), 2 * src.float(), atol=1e-6)
+    gb.close()
+
+
+def test_numa_binding_reads_the_gpu_node_from_sysfs(tmp_path):
+    import os
+
+    from prime_rl_b200.trainer.optim_offload import bind_to_gpu_numa_node, cpus_of_numa_node, numa_node_of_gpu
+
+    dev = tmp_path / "bus" / "pci" / "devices" / "0000:1b:00.0"
+    dev.mkdir(parents=True)
+    (dev / "numa_node").write_text("1\n")
+    node = tmp_path / "devices" / "system" / "node" / "node1"
+    node.mkdir(parents=True)
+    mine = sorted(os.sched_getaffinity(0))
+    (node / "cpulist").write_text(f"{mine[0]},{mine[-1]}-{mine[-1]},9999\n")
+    assert numa_node_of_gpu("00000000:1B:00.0", str(tmp_path)) == 1          # CUDA's 8-digit domain form
+    assert cpus_of_numa_node(1, str(tmp_path)) == {mine[0], mine[-1], 9999}
+    calls = []
+    assert bind_to_gpu_numa_node("0000:1b:00.0", str(tmp_path), setaffinity=lambda pid, c: calls.append((pid, c))) == 1
+    assert calls == [(0, {mine[0], mine[-1]})]                               # only cores this process may use
+    (dev / "numa_node").write_text("-1\n")
+    assert bind_to_gpu_numa_node("0000:1b:00.0", str(tmp_path), setaffinity=lambda *a: calls.append(a)) is None
+    assert len(calls) == 1 and numa_node_of_gpu("0000:ff:00.0", str(tmp_path)) is None

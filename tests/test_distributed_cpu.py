@@ -125,3 +125,25 @@ def test_parameter_sharding_matches_the_replicated_parameters_run(tmp_path, free
             assert z2[r]["wsum"] == pytest.approx(z3[r]["wsum"], rel=1e-6, abs=1e-6)
             assert z2[r]["wabs"] == pytest.approx(z3[r]["wabs"], rel=1e-6)
             assert z2[r]["esum"] == pytest.approx(z3[r]["esum"], rel=1e-6)
+
+
+@pytest.mark.slow
+def test_cpu_optimizer_with_gradients_accumulated_on_the_host_matches_the_device_path(tmp_path, free_port):
+    """ZeRO-3 with ``full_offload``: every layer's reduced gradient slice is handed to the host accumulator as its
+    reduce-scatter completes and the C++ AdamW reads it there; losses, gradient norms and weights must follow the
+    run that keeps gradients and optimizer on the device."""
+    base = json.loads(json.dumps(BASE))
+    base["model"].update(name="tiny-qwen3", ep=1, zero_stage=3)
+    base["optim"] = dict(base["optim"], weight_decay=0.01)
+    (tmp_path / "dev").mkdir()
+    (tmp_path / "host").mkdir()
+    dev = _run(tmp_path / "dev", free_port, 2, base)
+    cfg = json.loads(json.dumps(base))
+    cfg["model"]["full_offload"] = {"chunk_elements": 4096, "max_pinned_slots": 2, "numa_bind": False}
+    host = _run(tmp_path / "host", free_port + 1, 2, cfg)
+    for r in range(2):
+        for a, b in zip(dev[r]["steps"], host[r]["steps"]):
+            assert a[0] == pytest.approx(b[0], rel=1e-4, abs=1e-6)
+            assert a[1] == pytest.approx(b[1], rel=1e-3)
+        assert dev[r]["wabs"] == pytest.approx(host[r]["wabs"], rel=1e-5)
+        assert dev[r]["esum"] == pytest.approx(host[r]["esum"], rel=1e-5)

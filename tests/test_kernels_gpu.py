@@ -1039,3 +1039,72 @@ def test_paged_decode_with_shared_prefix_groups_matches_the_reference(Hq, Hkv):
                                  prefix=(torch.zeros_like(pb).to(DEV), torch.full_like(gs, -1).to(DEV),
                                          torch.zeros_like(gp).to(DEV), 2))
     _close(out, ref, atol=2e-2, rtol=2e-2)
+
+
+def test_multi_adapter_lora_linear_and_experts_match_the_reference_path():
+    """Several adapters in one launch (masked rank columns inside the base GEMM's extra reduction segment) against
+    the per-adapter PyTorch composition, forward and gradients, dense and grouped."""
+    from prime_rl_b200.ops import lora as L
+
+    torch.manual_seed(5)
+    T, IN, r, n = 300, 256, 16, 3
+    segs = [128, 64, 64]
+    x = _rand(T, IN)
+    w = _rand(sum(segs), IN, scale=0.05)
+    num_tokens = torch.tensor([100, 0, 200], dtype=torch.int32, device=DEV)
+
+    def adapters(lead=()):
+        out = []
+        for i in range(n):
+            a = (_rand(*lead, len(segs) * r, IN, scale=0.1)).requires_grad_()
+            bl = [(_rand(*lead, s, r, scale=0.1)).requires_grad_() for s in segs]
+            out.append((a, bl, 0.5 * (i + 1)))
+        return out
+
+    ad = adapters()
+    xg = x.clone().requires_grad_()
+    y = L.multi_lora_linear(xg, w, ad, num_tokens)
+    dy = _rand(*y.shape)
+    y.backward(dy)
+    rt.check_status()
+    ad_ref = [(a.detach().float().cpu().requires_grad_(), [b.detach().float().cpu().requires_grad_() for b in bl], sc)
+              for a, bl, sc in ad]
+    xr = x.float().cpu().requires_grad_()
+    yr = L.multi_lora_linear(xr, w.float().cpu(), ad_ref, num_tokens.cpu())
+    yr.backward(dy.float().cpu())
+    _close(y.cpu(), yr, atol=0.05, rtol=2e-2)
+    _close(xg.grad.cpu(), xr.grad, atol=0.05, rtol=3e-2)
+    for (a, bl, _), (ar, blr, _) in zip(ad, ad_ref):
+        _close(a.grad.cpu(), ar.grad, atol=0.1, rtol=5e-2)
+        for b, br in zip(bl, blr):
+            _close(b.grad.cpu(), br.grad, atol=0.1, rtol=5e-2)
+    assert float(ad[1][0].grad.abs().sum()) == 0.0              # adapter 1 has no tokens
+
+    # grouped: 3 experts, rows tagged with their adapter
+    counts = torch.tensor([130, 5, 256], dtype=torch.int32)
+    offs, be, P = _blocks(counts)
+    E = 3
+    xp = _rand(P, IN)
+    wg = _rand(E, sum(segs[:2]), IN, scale=0.05)
+    segs2 = segs[:2]
+    adg = []
+    for i in range(2):
+        a = _rand(E, len(segs2) * r, IN, scale=0.1).requires_grad_()
+        bl = [_rand(E, s, r, scale=0.1).requires_grad_() for s in segs2]
+        adg.append((a, bl, 1.0 + i))
+    row_adapter = torch.randint(0, 2, (P,), device=DEV)
+    row_adapter[::7] = -1
+    yg = L.multi_lora_grouped_linear(xp, wg, adg, row_adapter, be.to(DEV), offs.to(DEV))
+    dyg = _rand(*yg.shape)
+    yg.backward(dyg)
+    rt.check_status()
+    adg_ref = [(a.detach().float().cpu().requires_grad_(), [b.detach().float().cpu().requires_grad_() for b in bl], sc)
+               for a, bl, sc in adg]
+    ygr = L.multi_lora_grouped_linear(xp.float().cpu(), wg.float().cpu(), adg_ref, row_adapter.cpu(), be, offs)
+    ygr.backward(dyg.float().cpu())
+    used = (be >= 0).repeat_interleave(128)
+    _close(yg.cpu()[used], ygr[used], atol=0.05, rtol=2e-2)
+    for (a, bl, _), (ar, blr, _) in zip(adg, adg_ref):
+        _close(a.grad.cpu(), ar.grad, atol=0.15, rtol=5e-2)
+        for b, br in zip(bl, blr):
+            _close(b.grad.cpu(), br.grad, atol=0.15, rtol=5e-2)

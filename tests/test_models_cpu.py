@@ -177,3 +177,61 @@ def test_selective_recomputation_keeps_gemm_outputs_and_matches_full_recomputati
     assert stash.kinds_from_targets(None) == {"mm", "grouped_mm", "attention"}
     assert stash.kinds_from_targets(["aten::mm", "flash_attn"]) == {"mm", "attention"}
     assert stash.kinds_from_targets([]) == set()
+
+
+def test_several_lora_adapters_in_one_micro_batch():
+    """Tokens are sorted by adapter (``lora_num_tokens``); every token must get its own adapter's update on dense
+    projections and on the experts, gradients must stay with the adapter whose tokens produced them, and one
+    adapter must reproduce the single-adapter model."""
+    from prime_rl_b200.models import SeqInfo, apply_lora, build_model, resolve_arch
+    from prime_rl_b200.models.layers import LoRAAdapter, MultiLoRA, set_lora_num_tokens
+
+    torch.manual_seed(0)
+    arch = resolve_arch("tiny-qwen3-moe")
+    def fresh():
+        return build_model(arch, device=torch.device("cpu"), dtype=torch.float32, seed=1)
+
+    multi = fresh()
+    apply_lora(multi, 4, 8.0, ["q_proj", "k_proj", "v_proj", "o_proj", "experts"], num_adapters=2)
+    assert any(isinstance(m, MultiLoRA) for m in multi.modules())
+    with torch.no_grad():                                    # make the adapters differ and do something
+        for i, m in enumerate(mm for mm in multi.modules() if isinstance(mm, LoRAAdapter)):
+            for b in m.lora_B:
+                b.normal_(0, 0.05 * (1 + i % 2))
+    T = 24
+    ids = torch.randint(0, arch.vocab_size, (T,))
+    seq = SeqInfo.from_lengths([T], torch.device("cpu"))
+
+    def single_from(k):
+        m = fresh()
+        apply_lora(m, 4, 8.0, ["q_proj", "k_proj", "v_proj", "o_proj", "experts"])
+        src = {n: p for n, p in multi.named_parameters() if "lora_" in n}
+        with torch.no_grad():
+            for n, p in m.named_parameters():
+                if "lora_" in n:
+                    # layers.N.self_attn.qkv_proj.lora.lora_A  <-  ...qkv_proj.lora.<k>.lora_A
+                    head, tail = n.rsplit(".lora_", 1)
+                    p.copy_(src[f"{head}.{k}.lora_{tail}"])
+        return m
+
+    set_lora_num_tokens(torch.tensor([10, 14], dtype=torch.int32))
+    out = multi(ids, seq)
+    h = out[0] if isinstance(out, tuple) else out
+    set_lora_num_tokens(None)
+    ref0 = single_from(0)(ids[:10], SeqInfo.from_lengths([10], torch.device("cpu")))
+    ref0 = ref0[0] if isinstance(ref0, tuple) else ref0
+    # causal model: the first 10 tokens only see adapter-0 tokens, so they must match the single-adapter model
+    assert torch.allclose(h[:10], ref0, atol=2e-4, rtol=1e-3)
+    # all tokens on adapter 1 == the single-adapter model built from adapter 1
+    set_lora_num_tokens(torch.tensor([0, T], dtype=torch.int32))
+    h1 = multi(ids, seq)
+    h1 = h1[0] if isinstance(h1, tuple) else h1
+    ref1 = single_from(1)(ids, seq)
+    ref1 = ref1[0] if isinstance(ref1, tuple) else ref1
+    assert torch.allclose(h1, ref1, atol=2e-4, rtol=1e-3)
+    # gradients: with every token on adapter 1, adapter 0 gets exactly zero
+    h1.float().pow(2).mean().backward()
+    set_lora_num_tokens(None)
+    g0 = [p.grad for n, p in multi.named_parameters() if ".0.lora_" in n and p.grad is not None]
+    g1 = [p.grad for n, p in multi.named_parameters() if ".1.lora_" in n and p.grad is not None]
+    assert g1 and all(float(g.abs().sum()) == 0.0 for g in g0) and any(float(g.abs().sum()) > 0 for g in g1)
