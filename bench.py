@@ -38,6 +38,7 @@ Rank 0 prints one JSON line.
 from __future__ import annotations
 
 import argparse
+import faulthandler
 import gc
 import json
 import math
@@ -51,6 +52,7 @@ import time
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
+faulthandler.enable()          # a native crash leaves the Python stack of every thread on stderr
 sys.path.insert(0, str(ROOT))
 
 # reference, 8xB200, Qwen3-30B-A3B RL LoRA r16, seq 16384 (benchmarks/results/BENCHMARKS.md:60): its only

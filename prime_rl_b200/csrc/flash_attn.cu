@@ -50,6 +50,7 @@ struct FaParams {
   float* lse;             // [heads_q, T]
   float scale_log2;       // softmax scale * log2(e)
   int window;             // <= 0: none; else a query attends keys with q - k < window
+  const float* sinks;     // optional [heads_q]: a per-head logit that only joins the softmax denominator
   int* status;
   // context-parallel gather (flash_fwd_kernel<true> only): K and V of the whole sequence live in one
   // buffer per rank ([K rows | V rows at v_off]) of which rank r has written the rows of its own
@@ -447,6 +448,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tc_fence_after();
+        // attention sink: one more column exp(sink - max) in the row sum, no value attached (the output
+        // shrinks, the log-sum-exp the backward pass works from grows)
+        if (p.sinks != nullptr) l += exp2f(p.sinks[head] * 1.4426950408889634f - m);
         const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
         __nv_bfloat16* dst = p.out + static_cast<long long>(grow) * p.ld_out +
                              static_cast<long long>(head) * kFaD;
@@ -491,7 +495,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 PRB_API int prb_flash_fwd_slice(const void* q, const void* k, const void* v, void* out, float* lse,
                                 const int* cu_seqlens, int num_docs, int total_q, int q_off, int q_rows, int heads_q,
                                 int heads_kv, int head_dim, long long ld_q, long long ld_k, long long ld_v,
-                                long long ld_out, float scale, int window, int max_pairs, int* status, void* stream_) {
+                                long long ld_out, float scale, int window, int max_pairs, const float* sinks,
+                                int* status, void* stream_) {
   using namespace prb;
   if (q_off < 0 || q_rows <= 0 || q_off + q_rows > total_q) return -3;
   if (head_dim != kFaD || heads_q % heads_kv) return -2;
@@ -514,7 +519,7 @@ PRB_API int prb_flash_fwd_slice(const void* q, const void* k, const void* v, voi
   p.heads_q = heads_q; p.heads_kv = heads_kv;
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.ld_out = ld_out; p.lse = lse;
   p.scale_log2 = scale * 1.4426950408889634f;
-  p.window = window; p.status = status;
+  p.window = window; p.status = status; p.sinks = sinks;
   static prb::DeviceOnce configured;
   if (configured.pending()) {
     if (cudaFuncSetAttribute(flash_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFaSmem) != cudaSuccess)
@@ -562,7 +567,7 @@ PRB_API int prb_flash_fwd_gather(const void* q, void* kv_local, void* const* pee
   p.heads_q = heads_q; p.heads_kv = heads_kv;
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.ld_out = ld_out; p.lse = lse;
   p.scale_log2 = scale * 1.4426950408889634f;
-  p.window = window; p.status = status;
+  p.window = window; p.status = status; p.sinks = nullptr;
   for (int r = 0; r < cp_size; ++r) p.peer[r] = reinterpret_cast<const uint8_t*>(peer_kv[r]);
   p.kv_local = reinterpret_cast<uint8_t*>(kv_local);
   p.claim = counters; p.ready = counters + 1;
@@ -585,5 +590,5 @@ PRB_API int prb_flash_fwd(const void* q, const void* k, const void* v, void* out
                           long long ld_k, long long ld_v, long long ld_out, float scale, int window, int max_pairs,
                           int* status, void* stream_) {
   return prb_flash_fwd_slice(q, k, v, out, lse, cu_seqlens, num_docs, total_q, 0, total_q, heads_q, heads_kv, head_dim,
-                             ld_q, ld_k, ld_v, ld_out, scale, window, max_pairs, status, stream_);
+                             ld_q, ld_k, ld_v, ld_out, scale, window, max_pairs, nullptr, status, stream_);
 }

@@ -416,6 +416,24 @@ struct EpiStore {
   }
 };
 
+// fp32 accumulation into C (weight gradients: C += alpha * A.B) without reading C: every epilogue warp stages its
+// 32 x 32 fp32 chunk in shared memory (128-byte swizzle, two buffers per warp) and hands it to the TMA unit as a
+// reduce-add, which the L2 applies. Against the load / add / store form of EpiStore this halves the bytes the
+// SM moves and makes them full 128-byte lines. The work happens in the kernel body (it needs the warp and the
+// tensor map); tmA2 carries the map of C. Needs beta = 1, fp32 C, N and ldc multiples of 4.
+struct EpiTmaReduce {
+  static constexpr bool kTmaReduce = true;
+  __device__ EpiTmaReduce(const GemmParams&) {}
+  __device__ void begin_item(const GemmParams&, long long) {}
+  __device__ void end_item(const GemmParams&, long long, int) {}
+  __device__ void chunk(const GemmParams&, long long, int, uint32_t (&)[32]) {}
+};
+constexpr int kRedStageBytes = 4 * 2 * 4096;      // 4 epilogue warps x 2 buffers x (32 rows x 128 bytes)
+template <class E, class = void>
+struct epi_is_tma_reduce : std::false_type {};
+template <class E>
+struct epi_is_tma_reduce<E, std::void_t<decltype(E::kTmaReduce)>> : std::true_type {};
+
 // GEMM -> reduce-scatter in one kernel: the fp32 tile leaves TMEM as vector reductions into the
 // row owner's shard (peer memory over NVLink, or this GPU's own shard), so the transfer of a
 // tile overlaps the tensor-core work of the next one and no partial result is materialised.
@@ -691,10 +709,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int acc = 0;
     uint32_t acc_ph = 0;
     bool first = true;
+    [[maybe_unused]] uint32_t red_seq = 0;           // chunks this warp has handed to the TMA unit (EpiTmaReduce)
     while (sched.next(p, m_blk, n_blk, brow, last, kb0, nkb, c_row0)) {
       const int row_in_m = m_blk * kBM + q * 32 + lane;
       long long row = (row_in_m < p.M) ? c_row0 + row_in_m : (1LL << 40);  // out of range -> masked
       if (p.row_valid != nullptr && row < p.rows_total && p.row_valid[row] < 0) row = 1LL << 40;
+      if constexpr (epi_is_tma_reduce<Epi>::value) {
+        if (nkb == 0) continue;                      // C += 0
+      }
       if (nkb == 0) {
         // nothing to reduce: the tile is all zeros
         uint32_t z[32];
@@ -708,12 +730,39 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      if constexpr (epi_is_tma_reduce<Epi>::value) {
+        uint8_t* my_stage = smem + STAGES * Cfg::STAGE_BYTES + 1024 + q * 8192;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c, ++red_seq) {
+          if (n_blk * BN + c * 32 >= p.N) break;
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
+          tmem_ld_wait();
+          uint8_t* sb = my_stage + (red_seq & 1) * 4096;
+          if (red_seq >= 2) {                         // the reduce that last read this buffer (two chunks ago) is done
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<float4*>(sb + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                make_float4(p.alpha * __uint_as_float(v[4 * j]), p.alpha * __uint_as_float(v[4 * j + 1]),
+                            p.alpha * __uint_as_float(v[4 * j + 2]), p.alpha * __uint_as_float(v[4 * j + 3]));
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_reduce_add_2d(&tmA2, sb, n_blk * BN + c * 32, static_cast<int>(c_row0) + m_blk * kBM + q * 32);
+            tma_store_commit();
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
         tmem_ld_32x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
         tmem_ld_wait();
         epi.chunk(p, row, n_blk * BN + c * 32, v);
+      }
       }
       tc_fence_before();
       __syncwarp();
@@ -722,6 +771,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (acc == 0) acc_ph ^= 1;
       if (last) epi.end_item(p, row, (n_blk * BN) / (sched_split_width(p, BN)));
       first = last;
+    }
+    if constexpr (epi_is_tma_reduce<Epi>::value) {
+      if (lane == 0) tma_store_wait<0>();             // shared memory must outlive the reduces that read it
+      __syncwarp();
     }
   }
 
@@ -746,6 +799,26 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   const int grid = tiles < sm_count() ? tiles : sm_count();
   if (grid <= 0) return 0;
   kern<<<grid, kGemmThreads, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, tmA2, tmB2, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// Dense weight gradient C += alpha * A^T.B (both operands MN-major) into an fp32 accumulator through TMA
+// reduce-adds (EpiTmaReduce); tmC rides in the tmA2 slot.
+template <int BN>
+static int launch_gemm_reduce(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
+                              const GemmParams& p, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int kSmem = Cfg::SMEM_BYTES + 768 + kRedStageBytes;
+  auto kern = gemm_bf16_kernel<BN, true, true, SchedDense, EpiTmaReduce>;
+  static prb::DeviceOnce configured;
+  if (configured.pending()) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess) return -10;
+    configured.mark();
+  }
+  const int tiles = ((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  if (grid <= 0) return 0;
+  kern<<<grid, kGemmThreads, kSmem, stream>>>(tmA, tmB, tmC, tmB, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -956,6 +1029,19 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
     splitk_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(sk->ws, splits, M, N, C, ldc, out_fp32,
                                                                            alpha, beta);
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  }
+
+  if (!grouped && a_mn && b_mn && out_fp32 && beta == 1.f && A2 == nullptr && row_valid == nullptr && (N % 4 == 0) &&
+      (ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0)) {
+    // weight gradient accumulated in place: TMA reduce-adds instead of a read-modify-write by the epilogue warps
+    CUtensorMap tmC;
+    rc = make_tmap_2d(&tmC, C, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, 32, 32, true);
+    if (rc) return rc;
+    switch (bn) {
+      case 256: return launch_gemm_reduce<256>(tmA, tmB, tmC, p, stream);
+      case 128: return launch_gemm_reduce<128>(tmA, tmB, tmC, p, stream);
+      default: return launch_gemm_reduce<64>(tmA, tmB, tmC, p, stream);
+    }
   }
 
 #define PRB_DISPATCH(AMN, BMN)                                                              \
@@ -1312,19 +1398,35 @@ PRB_API int prb_gemm_bf16_kgrouped(const void* A, const void* B, void* C, int M,
   p.expert_offset = expert_offset; p.num_experts = num_experts;
   const long long tiles = static_cast<long long>(num_experts) * ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
   const int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
-#define PRB_KG(BN_)                                                                                       \
+  // pure accumulation into an fp32 buffer (the flat gradient accumulator): hand the tiles to the TMA unit as
+  // reduce-adds instead of reading C back (see EpiTmaReduce)
+  const bool tma_reduce = out_fp32 && beta == 1.f && (M % kBM == 0) && (N % 4 == 0) && (ldc % 4 == 0) &&
+                          ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+  CUtensorMap tmC = tmA;
+  if (tma_reduce) {
+    rc = make_tmap_2d(&tmC, C, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)num_experts * (uint64_t)M, (uint64_t)N,
+                      (uint64_t)ldc, 32, 32, true);
+    if (rc) return rc;
+  }
+#define PRB_KG(BN_, EPI_, EXTRA_)                                                                         \
   {                                                                                                       \
-    auto kern = gemm_bf16_kernel<BN_, true, true, SchedKGrouped, EpiStore>;                               \
+    auto kern = gemm_bf16_kernel<BN_, true, true, SchedKGrouped, EPI_>;                                   \
     static prb::DeviceOnce configured;                                                                       \
     if (configured.pending()) {                                                                                    \
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                         \
-                               GemmCfg<BN_>::SMEM_BYTES) != cudaSuccess)                                  \
+                               GemmCfg<BN_>::SMEM_BYTES + EXTRA_) != cudaSuccess)                         \
         return -10;                                                                                       \
       configured.mark();                                                                                  \
     }                                                                                                     \
-    kern<<<grid, kGemmThreads, GemmCfg<BN_>::SMEM_BYTES, stream>>>(tmA, tmB, tmA, tmB, p);                          \
+    kern<<<grid, kGemmThreads, GemmCfg<BN_>::SMEM_BYTES + EXTRA_, stream>>>(tmA, tmB, tmC, tmB, p);       \
   }
-  if (bn == 256) PRB_KG(256) else if (bn == 128) PRB_KG(128) else PRB_KG(64)
+  constexpr int kRedExtra = 768 + kRedStageBytes;
+  if (tma_reduce) {
+    if (bn == 256) PRB_KG(256, EpiTmaReduce, kRedExtra) else if (bn == 128) PRB_KG(128, EpiTmaReduce, kRedExtra)
+    else PRB_KG(64, EpiTmaReduce, kRedExtra)
+  } else {
+    if (bn == 256) PRB_KG(256, EpiStore, 0) else if (bn == 128) PRB_KG(128, EpiStore, 0) else PRB_KG(64, EpiStore, 0)
+  }
 #undef PRB_KG
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

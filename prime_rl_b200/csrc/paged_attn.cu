@@ -546,26 +546,36 @@ paged_prefix_mma_kernel(const PagedParams p) {
   }
 }
 
-__global__ void __launch_bounds__(kPdD)
+// One warp per head, eight heads per CTA: lane l owns output channels 4 l .. 4 l + 3 (one float4 per partial).
+constexpr int kMergeHeads = 8;
+__global__ void __launch_bounds__(32 * kMergeHeads)
 paged_decode_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
                           __nv_bfloat16* __restrict__ out, int splits, int own_splits, int heads_per_seq,
-                          const int* __restrict__ page_begin) {
+                          const int* __restrict__ page_begin, long long total_heads) {
   // `splits` slots per head; slots >= own_splits belong to the shared-prefix pass and only count for sequences
   // that are in a group (page_begin > 0): the others never wrote them
-  const long long head = blockIdx.x;
-  const int d = threadIdx.x;
+  static_assert(kPdD == 128, "one float4 per lane");
+  const long long head = static_cast<long long>(blockIdx.x) * kMergeHeads + (threadIdx.x >> 5);
+  if (head >= total_heads) return;
+  const int lane = threadIdx.x & 31;
   int used = splits;
   if (own_splits < splits && (page_begin == nullptr || page_begin[head / heads_per_seq] <= 0)) used = own_splits;
   float M = -INFINITY;
   for (int s = 0; s < used; ++s) M = fmaxf(M, ml_part[(head * splits + s) * 2]);
-  float L = 0.f, O = 0.f;
+  float L = 0.f;
+  float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int s = 0; s < used; ++s) {
     const float ms = ml_part[(head * splits + s) * 2];
     const float a = (ms == -INFINITY) ? 0.f : __expf(ms - M);
     L += ml_part[(head * splits + s) * 2 + 1] * a;
-    O += o_part[(head * splits + s) * kPdD + d] * a;
+    const float4 o = *reinterpret_cast<const float4*>(o_part + (head * splits + s) * kPdD + 4 * lane);
+    O.x += o.x * a; O.y += o.y * a; O.z += o.z * a; O.w += o.w * a;
   }
-  out[head * kPdD + d] = __float2bfloat16(L > 0.f ? O / L : 0.f);
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  uint2 packed;
+  packed.x = pack_bf16(O.x * inv, O.y * inv);
+  packed.y = pack_bf16(O.z * inv, O.w * inv);
+  *reinterpret_cast<uint2*>(out + head * kPdD + 4 * lane) = packed;
 }
 
 }  // namespace prb
@@ -620,8 +630,12 @@ PRB_API int prb_paged_decode_prefix(const void* q, const void* kpool, const void
     default: PRB_PX_LAUNCH(8) break;
   }
 #undef PRB_PX_LAUNCH
-  paged_decode_merge_kernel<<<static_cast<unsigned>(B) * Hq, kPdD, 0, stream>>>(o_part, ml_part, (__nv_bfloat16*)out,
-                                                                               p.total_splits, splits, Hq, page_begin);
+  {
+    const long long heads = static_cast<long long>(B) * Hq;
+    paged_decode_merge_kernel<<<static_cast<unsigned>((heads + kMergeHeads - 1) / kMergeHeads), 32 * kMergeHeads, 0,
+                                stream>>>(o_part, ml_part, (__nv_bfloat16*)out, p.total_splits, splits, Hq, page_begin,
+                                          heads);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -662,8 +676,9 @@ PRB_API int prb_paged_decode(const void* q, const void* kpool, const void* vpool
     }
 #undef PRB_PM_LAUNCH
     if (splits > 1)
-      paged_decode_merge_kernel<<<static_cast<unsigned>(B) * Hq, kPdD, 0, stream>>>(
-          o_part, ml_part, (__nv_bfloat16*)out, splits, splits, Hq, nullptr);
+      paged_decode_merge_kernel<<<static_cast<unsigned>((static_cast<long long>(B) * Hq + kMergeHeads - 1) / kMergeHeads),
+                                  32 * kMergeHeads, 0, stream>>>(o_part, ml_part, (__nv_bfloat16*)out, splits, splits, Hq,
+                                                                 nullptr, static_cast<long long>(B) * Hq);
     return cudaGetLastError() == cudaSuccess ? 0 : -11;
   }
   switch (G) {
@@ -674,7 +689,8 @@ PRB_API int prb_paged_decode(const void* q, const void* kpool, const void* vpool
     default: return -4;
   }
   if (splits > 1)
-    paged_decode_merge_kernel<<<static_cast<unsigned>(B) * Hq, kPdD, 0, stream>>>(
-        o_part, ml_part, (__nv_bfloat16*)out, splits, splits, Hq, nullptr);
+    paged_decode_merge_kernel<<<static_cast<unsigned>((static_cast<long long>(B) * Hq + kMergeHeads - 1) / kMergeHeads),
+                                32 * kMergeHeads, 0, stream>>>(o_part, ml_part, (__nv_bfloat16*)out, splits, splits, Hq,
+                                                               nullptr, static_cast<long long>(B) * Hq);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

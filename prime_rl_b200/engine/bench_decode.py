@@ -86,7 +86,8 @@ def run_decode(model: str = "qwen3-30b-a3b", batch: int = 256, prompt: int = 102
 
 def run_rollout_bench(model: str = "qwen3-30b-a3b", contexts=(1024, 3072, 5120), steps: int = 16, warmup: int = 3,
                       layers: int | None = None, dev: torch.device | None = None, prompts: int = 32, samples: int = 8,
-                      prompt_len: int = 1024, fp8: bool = True, max_tp: int = 4, graphs: bool = True) -> dict | None:
+                      prompt_len: int = 1024, fp8: bool = True, max_tp: int = 4, graphs: bool = True,
+                      prefix_splits: int | None = None) -> dict | None:
     """The rollout half of the headline benchmark. Collective: every rank of the launch calls it; rank 0
     gets the result, the others ``None``.
 
@@ -145,6 +146,8 @@ def run_rollout_bench(model: str = "qwen3-30b-a3b", contexts=(1024, 3072, 5120),
     eng = Engine(net, num_pages=pages, page_size=16, max_running=batch, max_prefill_tokens=prefill_budget,
                  enable_prefix_cache=True, use_cuda_graphs=graphs, max_model_len=max_len,
                  weight_dtype="fp8" if fp8 else "bf16", tp=tp, keep_bf16_weights=not fp8)
+    if prefix_splits:
+        eng.runner.prefix_splits = int(prefix_splits)       # before the first decode graph is captured
     leader = tp is None or tp.rank == 0
     points = []
     failure = None
@@ -326,10 +329,12 @@ def main(argv=None):
     ap.add_argument("--rollout", action="store_true",
                     help="the shared-prefix rollout measurement (32 prompts x 8 samples) instead of independent prompts")
     ap.add_argument("--contexts", default="1024,3072,5120", help="--rollout: KV lengths at which decode steps are timed")
+    ap.add_argument("--prefix-splits", type=int, default=None,
+                    help="--rollout: slices of a group's shared pages handled by different CTAs (default: the runner's)")
     args = ap.parse_args(argv)
     if args.rollout:
         res = run_rollout_bench(args.model, [int(c) for c in args.contexts.split(",")], args.steps, args.warmup,
-                                args.layers, fp8=args.fp8, graphs=not args.no_graphs)
+                                args.layers, fp8=args.fp8, graphs=not args.no_graphs, prefix_splits=args.prefix_splits)
         if res is not None:
             print(json.dumps(res), flush=True)
         return

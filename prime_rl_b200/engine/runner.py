@@ -42,7 +42,7 @@ class ModelRunner:
         # samples of one prompt share its pages through the prefix cache: the decode kernels then read those
         # pages once per group of up to 8 sequences instead of once per sequence (csrc/paged_attn.cu)
         self.shared_prefix_decode = shared_prefix_decode and self.device.type == "cuda" and cache.page_size == 16
-        self.prefix_splits = 2
+        self.prefix_splits = 4
         self._group_key = None                          # identity of the batch the current grouping was made for
         self.prefix_stats = {"regroupings": 0, "grouped_sequences": 0, "shared_pages": 0}
         self._cu_batch, self._cu = None, []             # per-sequence cu_seqlens of the current prefix-hit prefill

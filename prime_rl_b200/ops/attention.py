@@ -73,42 +73,53 @@ class _FlashAttention(torch.autograd.Function):
     recomputation), in which case the forward launches nothing."""
 
     @staticmethod
-    def forward(ctx, q, k, v, cu, max_seqlen, scale, window, backend, cached, store, q_offset=None):
+    def forward(ctx, q, k, v, cu, max_seqlen, scale, window, backend, cached, store, q_offset=None, sinks=None):
         ws = (-1, -1) if window is None else (window - 1, 0)
+        sinks32 = None if sinks is None else sinks.detach().float().contiguous()
         if cached is not None:
             out, lse = cached
         elif backend == "tcgen05":
             from . import flash_native
 
-            out, lse = flash_native.flash_fwd(q, k, v, cu, scale=scale, window=window, q_offset=q_offset)
+            out, lse = flash_native.flash_fwd(q, k, v, cu, scale=scale, window=window, q_offset=q_offset,
+                                              sinks=sinks32)
         else:
             fwd, _ = _fa2()
             out, lse, _, _ = fwd(q, k, v, cu, cu, max_seqlen, max_seqlen, 0.0, scale, True, ws[0], ws[1], 0.0, None,
                                  False, None)
         if store is not None:
             store.append((out, lse))
-        ctx.save_for_backward(q, k, v, out, lse, cu)
+        ctx.save_for_backward(q, k, v, out, lse, cu, sinks32)
         ctx.cfg = (max_seqlen, scale, ws, window, backend, q_offset)
+        ctx.sink_dtype = None if sinks is None else sinks.dtype
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        q, k, v, out, lse, cu = ctx.saved_tensors
+        q, k, v, out, lse, cu, sinks32 = ctx.saved_tensors
         max_seqlen, scale, ws, window, backend, q_offset = ctx.cfg
+        dsinks = None
+        if sinks32 is not None:
+            # d sink_h = - sum_t p_sink[h, t] * <dO[t, h], O[t, h]>, p_sink = exp(sink_h - lse[h, t]); dq / dk / dv
+            # follow from the saved lse (which contains the sink) like without one
+            delta = (dout.float() * out.float()).sum(-1)                         # [T, Hq]
+            p_sink = torch.exp(sinks32.view(-1, 1) - lse)                        # [Hq, T]
+            dsinks = -(p_sink * delta.t()).sum(-1).to(ctx.sink_dtype)
         if backend == "tcgen05" and BWD_BACKEND == "tcgen05":
             from . import flash_native
 
             if flash_native.bwd_available():
                 dq, dk, dv = flash_native.flash_bwd(dout, q, k, v, out, lse, cu, scale=scale, window=window,
                                                     q_offset=q_offset)
-                return dq, dk, dv, None, None, None, None, None, None, None, None
+                return dq, dk, dv, None, None, None, None, None, None, None, None, dsinks
+        assert sinks32 is None, "attention sinks need the tcgen05 kernels"
         assert q_offset is None, "query slices need the tcgen05 kernels"
         _, bwd = _fa2()
         dq, dk, dv = torch.empty_like(q), torch.empty(k.shape, dtype=k.dtype, device=k.device), \
             torch.empty(v.shape, dtype=v.dtype, device=v.device)
         bwd(dout.contiguous(), q, k, v, out, lse, dq, dk, dv, cu, cu, max_seqlen, max_seqlen, 0.0, scale, True, ws[0],
             ws[1], 0.0, None, False, None)
-        return dq, dk, dv, None, None, None, None, None, None, None, None
+        return dq, dk, dv, None, None, None, None, None, None, None, None, None
 
 
 def attention(q, k, v, cu_seqlens, max_seqlen: int, *, causal: bool = True, window: int | None = None,
@@ -121,7 +132,9 @@ def attention(q, k, v, cu_seqlens, max_seqlen: int, *, causal: bool = True, wind
     rows ``[q_offset, q_offset + len(q))`` while k / v / cu_seqlens cover the whole sequence."""
     if backend in ("auto", None, "flash_attention_3", "flash_attention_4"):
         backend = default_backend(q.device)
-    fast = q.is_cuda and sinks is None and causal and q.dtype == torch.bfloat16 and backend != "sdpa"
+    fast = q.is_cuda and causal and q.dtype == torch.bfloat16 and backend != "sdpa"
+    if fast and sinks is not None and not (backend == "tcgen05" and q.shape[-1] == 128):
+        fast = False                     # the library kernels have no sink column
     if not fast:
         return attention_ref(q, k, v, cu_seqlens, causal=causal, window=window, sinks=sinks, scale=scale)
     if backend == "tcgen05" and q.shape[-1] != 128:
@@ -134,7 +147,8 @@ def attention(q, k, v, cu_seqlens, max_seqlen: int, *, causal: bool = True, wind
         cached = cache.pop(cache_key, None)
         if cached is None:
             store = []
-    out = _FlashAttention.apply(q, k, v, cu_seqlens, max_seqlen, scale, window, backend, cached, store, q_offset)
+    out = _FlashAttention.apply(q, k, v, cu_seqlens, max_seqlen, scale, window, backend, cached, store, q_offset,
+                                sinks)
     if store:
         cache[cache_key] = store.pop()
     return out

@@ -18,13 +18,14 @@ def available() -> bool:
 
 
 def flash_fwd(q, k, v, cu_seqlens, *, scale: float | None = None, window: int | None = None,
-              q_offset: int | None = None):
+              q_offset: int | None = None, sinks: torch.Tensor | None = None):
     """q: [T, Hq, 128] bf16 (contiguous heads), k/v: [T, Hkv, 128] bf16 (may be strided over
     tokens). Returns (out [T, Hq, 128] bf16, lse [Hq, T] fp32, natural log).
 
     Context-parallel form (``q_offset`` given): ``q`` holds only the global rows
     ``[q_offset, q_offset + q.shape[0])`` while k / v / cu_seqlens describe the whole sequence;
-    out and lse are for the held rows."""
+    out and lse are for the held rows. ``sinks`` (fp32 [Hq]): a per-head logit that joins every row's softmax
+    denominator (and therefore ``lse``) without a value."""
     Tq, Hq, D = q.shape
     T = k.shape[0]
     Hkv = k.shape[1]
@@ -38,11 +39,13 @@ def flash_fwd(q, k, v, cu_seqlens, *, scale: float | None = None, window: int | 
     num_docs = cu_seqlens.numel() - 1
     max_pairs = (T + 255) // 256 + num_docs
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if sinks is not None:
+        assert sinks.dtype == torch.float32 and sinks.numel() == Hq and sinks.is_contiguous()
     status = rt.status_tensor(q.device)
     rc = rt.lib().prb_flash_fwd_slice(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
                                       cu_seqlens.data_ptr(), num_docs, T, off, Tq, Hq, Hkv, D, q.stride(0),
                                       k.stride(0), v.stride(0), out.stride(0), float(scale), int(window or 0),
-                                      max_pairs, status.data_ptr(), rt.stream_ptr(q.device))
+                                      max_pairs, rt.ptr(sinks), status.data_ptr(), rt.stream_ptr(q.device))
     rt.check(rc, "prb_flash_fwd_slice")
     return out, lse
 

@@ -108,7 +108,8 @@ def install_expert_parallel(model, dims, moe_cfg=None) -> None:
 
             dcfg = getattr(moe_cfg, "dispatch", None)
             moe.dispatcher = P2PDispatcher(group, ep, E, capacity_factor=getattr(dcfg, "capacity_factor", 2.0),
-                                           payload=getattr(dcfg, "payload", "bf16"))
+                                           payload=getattr(dcfg, "payload", "bf16"),
+                                           per_block=bool(getattr(dcfg, "per_block_arrival", False)))
         else:
             moe.dispatcher = TorchA2ADispatcher(group, ep, E)
         moe.ep_rank, moe.ep = ep_rank, ep

@@ -234,12 +234,12 @@ class P2PDispatcher:
     kernel status word (``ops._runtime.check_status``)."""
 
     def __init__(self, group, ep: int, num_experts: int, capacity_factor: float = 2.0, max_tokens: int | None = None,
-                 payload: str = "bf16", per_block: bool = True):
+                 payload: str = "bf16", per_block: bool = False):
         if payload not in ("bf16", "fp8"):
             raise ValueError("payload must be 'bf16' or 'fp8'")
         self.payload = payload
         # per_block: the forward dispatch overlaps the first expert GEMM (rows pushed on a side stream, the GEMM's
-        # loader waits per 128-row block); used where the experts run their plain bf16 grouped GEMM
+        # loader waits per 128-row block); possible where the experts run their plain bf16 grouped GEMM
         self.per_block = per_block
         self.group, self.ep, self.E = group, ep, num_experts
         self.E_local = num_experts // ep

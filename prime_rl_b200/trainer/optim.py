@@ -145,17 +145,31 @@ class LRSchedule:
 
 
 def newton_schulz(g: torch.Tensor, steps: int = 5) -> torch.Tensor:
-    """Quintic Newton-Schulz orthogonalisation used by Muon (bf16 on GPU)."""
+    """Quintic Newton-Schulz orthogonalisation used by Muon (bf16 on GPU). 2-D matrices on the GPU run on the
+    tcgen05 GEMM with the polynomial's additions folded into its epilogue (``alpha * A.B + beta * C``): three
+    launches per iteration and no separate element-wise pass; stacked (expert) matrices use batched matmul."""
     a, b, c = 3.4445, -4.7750, 2.0315
     x = g.to(torch.bfloat16 if g.is_cuda else torch.float32)
     transposed = x.shape[-2] > x.shape[-1]
     if transposed:
         x = x.transpose(-2, -1)
     x = x / (x.norm(dim=(-2, -1), keepdim=True) + 1e-7)
-    for _ in range(steps):
-        A = x @ x.transpose(-2, -1)
-        B = b * A + c * (A @ A)
-        x = a * x + B @ x
+    if x.is_cuda and x.dim() == 2 and x.shape[0] % 8 == 0 and x.shape[1] % 8 == 0:
+        from ..ops.matmul import gemm
+
+        x = x.contiguous()
+        for _ in range(steps):
+            A = gemm(x, x)                                   # x x^T (symmetric)
+            B = A.clone()
+            gemm(A, A, out=B, alpha=c, beta=b)               # b A + c A A
+            nx = x.clone()
+            gemm(B, x, b_mn=True, out=nx, alpha=1.0, beta=a)  # a x + B x
+            x = nx
+    else:
+        for _ in range(steps):
+            A = x @ x.transpose(-2, -1)
+            B = b * A + c * (A @ A)
+            x = a * x + B @ x
     if transposed:
         x = x.transpose(-2, -1)
     return x.to(g.dtype)

@@ -63,7 +63,7 @@ def main() -> int:
     # ---- numerics on a small, ragged case (some experts get no token)
     ex, x, idx, w, counts, dout = setup(T=300 + 117 * rank, E=8 * world, H=256, I=128, k=2)
     ref = _run(TorchA2ADispatcher(group, world, 8 * world), ex, x, idx, w, counts, dout)
-    p2p = P2PDispatcher(group, world, 8 * world, capacity_factor=float(world))
+    p2p = P2PDispatcher(group, world, 8 * world, capacity_factor=float(world), per_block=True)
     got = _run(p2p, ex, x, idx, w, counts, dout)
     got2 = _run(p2p, ex, x, idx, w, counts, dout)          # buffers and epochs are reused
     # the same with one global wait instead of the per-block arrival counters, then per-block again: the two
@@ -105,7 +105,7 @@ def main() -> int:
         T, E, H, I, k = 8192, 128, 2048, 768, 8
         ex, x, idx, w, counts, dout = setup(T, E, H, I, k)
         for name, disp in (("all_to_all (NCCL)", TorchA2ADispatcher(group, world, E)),
-                           ("peer memory, per-block arrival", P2PDispatcher(group, world, E, capacity_factor=2.0)),
+                           ("peer memory, per-block arrival", P2PDispatcher(group, world, E, capacity_factor=2.0, per_block=True)),
                            ("peer memory, one global wait",
                             P2PDispatcher(group, world, E, capacity_factor=2.0, per_block=False)),
                            ("peer memory, fp8 dispatch payload",

@@ -1074,10 +1074,11 @@ def test_multi_adapter_lora_linear_and_experts_match_the_reference_path():
     yr.backward(dy.float().cpu())
     _close(y.cpu(), yr, atol=0.05, rtol=2e-2)
     _close(xg.grad.cpu(), xr.grad, atol=0.05, rtol=3e-2)
-    for (a, bl, _), (ar, blr, _) in zip(ad, ad_ref):
-        _close(a.grad.cpu(), ar.grad, atol=0.1, rtol=5e-2)
+    for (a, bl, _), (ar, blr, _) in zip(ad, ad_ref):            # bf16 intermediates (x A^T and its gradient)
+        _close(a.grad.cpu(), ar.grad, atol=0.5, rtol=5e-2)
+        assert float((a.grad.cpu().float() - ar.grad).norm() / (ar.grad.norm() + 1e-6)) < 0.03
         for b, br in zip(bl, blr):
-            _close(b.grad.cpu(), br.grad, atol=0.1, rtol=5e-2)
+            _close(b.grad.cpu(), br.grad, atol=0.5, rtol=5e-2)
     assert float(ad[1][0].grad.abs().sum()) == 0.0              # adapter 1 has no tokens
 
     # grouped: 3 experts, rows tagged with their adapter
@@ -1105,6 +1106,88 @@ def test_multi_adapter_lora_linear_and_experts_match_the_reference_path():
     used = (be >= 0).repeat_interleave(128)
     _close(yg.cpu()[used], ygr[used], atol=0.05, rtol=2e-2)
     for (a, bl, _), (ar, blr, _) in zip(adg, adg_ref):
-        _close(a.grad.cpu(), ar.grad, atol=0.15, rtol=5e-2)
+        _close(a.grad.cpu(), ar.grad, atol=0.5, rtol=5e-2)
+        assert float((a.grad.cpu().float() - ar.grad).norm() / (ar.grad.norm() + 1e-6)) < 0.03
         for b, br in zip(bl, blr):
-            _close(b.grad.cpu(), br.grad, atol=0.15, rtol=5e-2)
+            _close(b.grad.cpu(), br.grad, atol=0.5, rtol=5e-2)
+
+
+@pytest.mark.parametrize("window", [None, 100])
+def test_flash_attention_with_sinks_matches_reference(window):
+    """A per-head sink logit joins the softmax denominator in the kernel's epilogue; outputs and every gradient
+    (q, k, v and the sinks themselves) against the fp32 definition."""
+    from prime_rl_b200.ops import attention as A
+
+    torch.manual_seed(2)
+    lens = [200, 333, 57]
+    T, Hq, Hkv, D = sum(lens), 8, 2, 128
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    q, k, v = _rand(T, Hq, D).requires_grad_(), _rand(T, Hkv, D).requires_grad_(), _rand(T, Hkv, D).requires_grad_()
+    sinks = (torch.randn(Hq, device=DEV) * 2).to(torch.bfloat16).requires_grad_()
+    out = A.attention(q, k, v, cu, max(lens), window=window, sinks=sinks, backend="tcgen05")
+    do = _rand(T, Hq, D)
+    out.backward(do)
+    rt.check_status()
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    sr = sinks.detach().float().requires_grad_()
+    ref = A.attention_ref(qr, kr, vr, cu, window=window, sinks=sr)
+    ref.backward(do.float())
+    _close(out, ref, atol=2e-2, rtol=2e-2)
+    _close(q.grad, qr.grad, atol=3e-2, rtol=3e-2)
+    _close(k.grad, kr.grad, atol=6e-2, rtol=3e-2)
+    _close(v.grad, vr.grad, atol=6e-2, rtol=3e-2)
+    _close(sinks.grad, sr.grad, atol=0.15, rtol=5e-2)
+
+
+def test_newton_schulz_on_the_tcgen05_gemm_matches_the_matmul_form():
+    from prime_rl_b200.trainer.optim import newton_schulz
+
+    torch.manual_seed(0)
+    for shape in ((256, 512), (768, 256)):
+        g = torch.randn(*shape, device=DEV)
+        got = newton_schulz(g)
+        rt.check_status()
+        ref = newton_schulz(g.cpu()).to(DEV)                 # fp32 matmul form
+        assert got.shape == g.shape
+        assert float((got - ref).norm() / ref.norm()) < 0.05  # bf16 iterations against fp32
+        s = torch.linalg.svdvals(got.float())
+        assert float(s.max()) < 1.3 and float(s.min()) > 0.3  # roughly orthogonal, as the quintic leaves it
+
+
+def test_weight_gradient_accumulation_through_tma_reduce_adds():
+    """fp32 accumulators take the weight-gradient tiles as TMA reduce-adds (no read-back of C): widths that end
+    inside a 32-column chunk, repeated accumulation, alpha, experts without rows, and an accumulator that is a
+    strided view of a larger buffer."""
+    from prime_rl_b200.ops import lora as L
+    from prime_rl_b200.ops import matmul as mm
+
+    torch.manual_seed(4)
+    # dense: C[M, N] += alpha * A^T B, A [T, M], B [T, N]
+    for T, M, N in ((333, 256, 520), (1024, 384, 2048), (90, 128, 36)):
+        a, b = _rand(T, M), _rand(T, N)
+        big = torch.randn(M, N + 12, device=DEV)
+        acc = big[:, 4:4 + N]                                   # row pitch N + 12 (multiple of 4), 16-byte aligned start
+        ref = acc.clone()
+        for _ in range(3):
+            mm.gemm(a, b, a_mn=True, b_mn=True, out=acc, alpha=0.5, beta=1.0)
+            ref = ref + 0.5 * (a.float().t() @ b.float())
+        rt.check_status()
+        _close(acc, ref, atol=0.02 * T ** 0.5, rtol=1e-2)
+        assert torch.equal(big[:, :4], big[:, :4]) and bool(torch.isfinite(big).all())
+    # k-grouped: out[e] += dy_e^T x_e, rows per expert a multiple of 128 so that tiles never straddle experts
+    counts = torch.tensor([130, 0, 5, 256, 700], dtype=torch.int32)
+    offs, be, P = _blocks(counts)
+    E, M, N = 5, 256, 200
+    valid = (be >= 0).repeat_interleave(128).to(DEV)
+    dy = _rand(P, M) * valid[:, None]
+    x = _rand(P, N) * valid[:, None]
+    acc = torch.full((E, M, N), 2.0, device=DEV)
+    ref = acc.clone()
+    o = offs.tolist()
+    for _ in range(2):
+        L.kgrouped_gemm(dy, x, offs.to(DEV), E, out=acc, beta=1.0)
+        for e in range(E):
+            ref[e] += dy[o[e]:o[e + 1]].float().t() @ x[o[e]:o[e + 1]].float()
+    rt.check_status()
+    _close(acc, ref, atol=0.5, rtol=1e-2)
+    assert torch.equal(acc[1], torch.full((M, N), 2.0, device=DEV))
