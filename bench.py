@@ -73,6 +73,10 @@ def parse_args():
     ap.add_argument("--micro-batches", type=int, default=2, help="lora mode: micro-batches per GPU and step")
     ap.add_argument("--dispatch", default="p2p", choices=["p2p", "torch"], help="full mode: expert-parallel dispatcher")
     ap.add_argument("--optim-collectives", default="p2p", choices=["p2p", "nccl"])
+    ap.add_argument("--zero-stage", type=int, default=None, choices=[2, 3],
+                    help="full mode: 3 = parameters sharded per layer (the default for dense models), 2 = replicated")
+    ap.add_argument("--cp", type=int, default=1, help="full mode: context-parallel ranks per replica (long rows)")
+    ap.add_argument("--cp-style", default="ring", choices=["ring", "ulysses"])
     ap.add_argument("--layers", type=int, default=None, help="debug: truncate the model (result is not a bench value)")
     ap.add_argument("--attn", default="auto")
     ap.add_argument("--no-rollout-decode", action="store_true", help="skip the rollout measurement")
@@ -164,17 +168,36 @@ def trainer_pass(args, mode: str, world, steps: int, warmup: int, want_e2e: bool
 
     n = world.world_size
     if mode == "full":
+        from prime_rl_b200.models import resolve_arch
+
+        moe = resolve_arch(args.model).is_moe
         seq_len = args.seq_len or 8192
-        per_gpu = max(1, args.rows // n)
-        global_rows = per_gpu * n
+        cp = max(1, args.cp)
+        replicas = max(1, n // cp)
+        per_gpu = max(1, args.rows // replicas)          # micro-batches per replica and step
+        global_rows = per_gpu * replicas
         mcfg = {"name": args.model, "seq_len": seq_len, "attn": args.attn, "ac": {"mode": "full", "freq": 1},
-                "ep": n if n > 1 else 1, "optim_collectives": args.optim_collectives,
-                "moe": {"dispatch": {"type": args.dispatch} if args.dispatch == "torch" else
-                        {"type": "p2p", "capacity_factor": float(min(n, 4))}},
+                "optim_collectives": args.optim_collectives,
                 "debug": {"random_init": True, "num_layers": args.layers}}
+        if cp > 1:
+            mcfg.update(cp=cp, cp_style=args.cp_style)
+        if moe:
+            mcfg.update(ep=n if n > 1 else 1,
+                        moe={"dispatch": {"type": args.dispatch} if args.dispatch == "torch" else
+                             {"type": "p2p", "capacity_factor": float(min(n, 4))}})
+            par = (f"ep{n} (128/{n} experts per GPU, peer-memory dispatch) x zero{n} (dense optimizer state "
+                   f"partitioned, {args.optim_collectives} reduce-scatter / all-gather)") if n > 1 else "single GPU"
+        else:
+            zs = args.zero_stage or (3 if n > 1 else 2)
+            mcfg.update(ep=1, zero_stage=zs)
+            if zs == 3:
+                mcfg["optim_collectives"] = "nccl"       # the per-layer collectives of the sharding runtime
+            par = (f"zero{zs} over {n} GPUs" + (" (parameters, gradients and optimizer state sharded per layer, "
+                                                 "next layer gathered ahead)" if zs == 3 else "")) if n > 1 \
+                else "single GPU"
+            if cp > 1:
+                par += f", cp{cp} ({args.cp_style}, zig-zag)"
         scaling = "strong"
-        par = (f"ep{n} (128/{n} experts per GPU, peer-memory dispatch) x zero{n} (dense optimizer state partitioned, "
-               f"{args.optim_collectives} reduce-scatter / all-gather)") if n > 1 else "single GPU"
     else:
         seq_len = args.seq_len or 16384
         per_gpu = args.micro_batches
@@ -301,11 +324,13 @@ def main():
             rollout = {"error": err}
     if world.rank == 0:
         p = primary
+        headline = args.model == "qwen3-30b-a3b"        # the published reference row is for this shape only
         line = {
-            "metric": "RL trainer tokens/s, Qwen3-30B-A3B shape", "value": p["value"], "unit": "tokens/s", "n_gpus": n,
+            "metric": "RL trainer tokens/s, Qwen3-30B-A3B shape" if headline else f"RL trainer tokens/s, {args.model} shape",
+            "value": p["value"], "unit": "tokens/s", "n_gpus": n,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": p["ms_per_step"],
             "higher_is_better": True, "scaling": p["scaling"],
-            "vs_baseline": p["value"] / (BASELINE_TPS_8GPU * n / 8),
+            "vs_baseline": p["value"] / (BASELINE_TPS_8GPU * n / 8) if headline else None,
             "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init weights)",
             "config": {"model": args.model if args.layers is None else f"{args.model}[{args.layers} layers: debug]",
                        "mode": "rl-full" if p["mode"] == "full" else "rl-lora-r16",

@@ -103,6 +103,18 @@ def bench_grouped(timer, args, dev):
     dy = torch.randn(P, 2 * I, device=dev).bfloat16()
     _report("grouped input gradient of gate_up (MN-major B)", timer(lambda: gemm(dy, w1, b_mn=True, block_expert=be)),
             flops=2 * P * 2 * I * H)
+    # weight gradients accumulated into the fp32 buffer (beta = 1): TMA reduce-adds from the epilogue
+    from .lora import kgrouped_gemm
+
+    offs = (torch.arange(E + 1, device=dev, dtype=torch.int32) * padded).contiguous()
+    acc1 = torch.zeros(E, 2 * I, H, device=dev)
+    acc2 = torch.zeros(E, H, I, device=dev)
+    dh = torch.randn(P, H, device=dev).bfloat16()
+    _report(f"k-grouped wgrad gate_up into fp32 ({per} rows / expert)",
+            timer(lambda: kgrouped_gemm(dy, x, offs, E, out=acc1, beta=1.0)), flops=2 * P * 2 * I * H,
+            bytes_=acc1.numel() * 4 + (dy.numel() + x.numel()) * 2)
+    _report("k-grouped wgrad down into fp32", timer(lambda: kgrouped_gemm(dh, h, offs, E, out=acc2, beta=1.0)),
+            flops=2 * P * H * I, bytes_=acc2.numel() * 4 + (dh.numel() + h.numel()) * 2)
 
 
 def bench_fp8(timer, args, dev):

@@ -173,8 +173,9 @@ class FSDPRuntime:
         self.pool_owner: list[Unit | None] = [None] * self.pool_size
         self._next_buffer = 0
         self.cuda = dev.type == "cuda"
-        self.prefetch = prefetch and self.cuda
-        self.comm_stream = torch.cuda.Stream(device=dev) if self.prefetch else None
+        # on the CPU the "prefetch" gathers run in place of the side stream: same buffer rotation, no overlap
+        self.prefetch = prefetch
+        self.comm_stream = torch.cuda.Stream(device=dev) if (self.prefetch and self.cuda) else None
         self.free_event: list = [None] * self.pool_size      # compute finished with the buffer's last occupant
         self.stats = {"gathers": 0, "reduce_scatters": 0, "prefetch_hits": 0}
         self._direction = 1
@@ -203,21 +204,26 @@ class FSDPRuntime:
         if self.root is not None:
             _all_gather(self.root_params, self.sp.unit_shard(self.root), self.sp.group, self.sp.N)
 
-    def _take_buffer(self, u: Unit) -> int:
+    def _take_buffer(self, u: Unit, keep: Unit | None = None) -> int:
+        """A pool buffer for ``u``, taken in rotation but never the one that holds ``keep`` (the unit that is about
+        to run while ``u`` is gathered ahead: when the direction of travel turns at the top of the backward pass the
+        rotation alone would hand out exactly that buffer)."""
         if self.keep_all:
             self.param_pool.append(torch.empty(u.numel, dtype=self.sp.dtype, device=self.sp.device))
             self.pool_owner.append(None)
             self.free_event.append(None)
             return len(self.param_pool) - 1
         b = self._next_buffer
+        if keep is not None and self.pool_owner[b] is keep:
+            b = (b + 1) % self.pool_size
         self._next_buffer = (b + 1) % self.pool_size
         old = self.pool_owner[b]
         if old is not None and old is not u:
             self._unbind(old)
         return b
 
-    def _gather(self, u: Unit, on_side_stream: bool) -> None:
-        b = self._take_buffer(u)
+    def _gather(self, u: Unit, on_side_stream: bool, keep: Unit | None = None) -> None:
+        b = self._take_buffer(u, keep)
         buf = self.param_pool[b][:u.numel]
         self.stats["gathers"] += 1
         if on_side_stream:
@@ -257,7 +263,9 @@ class FSDPRuntime:
         nxt = self.layer_units.get(idx + self._direction)
         if self.prefetch and not self.keep_all and nxt is not None and not (
                 nxt.buffer >= 0 and self.pool_owner[nxt.buffer] is nxt):
-            self._gather(nxt, on_side_stream=True)
+            self._gather(nxt, on_side_stream=self.comm_stream is not None, keep=u)
+        if u.params and u.params[0].numel() == 0:
+            raise RuntimeError(f"parameter-sharding runtime: layer {idx} is about to run without its parameters")
         return layer(h, seq)
 
     def before_forward(self) -> None:

@@ -235,3 +235,34 @@ def test_several_lora_adapters_in_one_micro_batch():
     g0 = [p.grad for n, p in multi.named_parameters() if ".0.lora_" in n and p.grad is not None]
     g1 = [p.grad for n, p in multi.named_parameters() if ".1.lora_" in n and p.grad is not None]
     assert g1 and all(float(g.abs().sum()) == 0.0 for g in g0) and any(float(g.abs().sum()) > 0 for g in g1)
+
+
+def test_parameter_sharding_runtime_keeps_the_running_layer_bound_when_the_backward_pass_turns():
+    """Two gather buffers, the next layer gathered ahead: at the top of the backward pass (the last layer of the
+    forward pass is recomputed first, nothing was gathered ahead of it) the rotation must not hand the buffer of
+    the layer that is about to run to the layer gathered ahead. Single process, sharding over one rank."""
+    from prime_rl_b200.models import SeqInfo, build_model, resolve_arch
+    from prime_rl_b200.parallel.fsdp import install_fsdp
+
+    arch = resolve_arch("tiny-qwen3").model_copy(update={"num_hidden_layers": 5})
+    ref = build_model(arch, device=torch.device("cpu"), dtype=torch.float32, seed=0)
+    m = build_model(arch, device=torch.device("cpu"), dtype=torch.float32, seed=0)
+    ref.ac_every = m.ac_every = 1
+    _, runtime = install_fsdp(m, None, pool=2, prefetch=True)
+    ref.train(), m.train()
+    ids = torch.randint(0, arch.vocab_size, (64,))
+    seq = SeqInfo.from_lengths([64], torch.device("cpu"))
+
+    def loss(model):
+        out = model(ids, seq)
+        h = out[0] if isinstance(out, tuple) else out
+        return h.float().pow(2).mean()
+
+    want = loss(ref)
+    want.backward()
+    runtime.before_forward()
+    got = loss(m)
+    got.backward()                               # raised "about to run without its parameters" before the fix
+    runtime.finish_backward()
+    assert torch.allclose(got, want, atol=1e-6)
+    assert runtime.stats["gathers"] == 8         # 5 on the way up, layers 2, 1, 0 again on the way down
