@@ -43,6 +43,7 @@ class Request:
     generator: torch.Generator | None = None
     prefilled: bool = False
     preemptions: int = 0
+    swapped: object = None          # kv_cache.HostKV while the request waits with its K / V in host memory
 
     @property
     def all_tokens(self) -> list[int]:
@@ -53,8 +54,13 @@ class Engine:
     def __init__(self, model, *, num_pages: int = 4096, page_size: int = 16, max_running: int = 256,
                  max_prefill_tokens: int = 16384, eos_token_id: int | None = None, enable_prefix_cache: bool = True,
                  use_cuda_graphs: bool = False, max_model_len: int = 8192, weight_dtype: str = "bf16", tp=None,
-                 keep_bf16_weights: bool = True):
+                 keep_bf16_weights: bool = True, kv_offload_bytes: int = 0):
+        """``kv_offload_bytes`` > 0: a request that is preempted for lack of pages keeps its K / V in (pinned) host
+        memory up to that many bytes in total and resumes without a second prefill (the reference configures this
+        as ``kv_cache_offload.cpu.num_bytes`` of its serving stack,
+        packages/prime-rl-configs/src/prime_rl/configs/inference.py:216-300)."""
         arch = model.arch
+        self.kv_offload_bytes, self.kv_offloaded = int(kv_offload_bytes), 0
         self.model = model.eval()
         self.weight_dtype = weight_dtype
         # tensor parallelism (engine/tp.py): this process holds one shard and steps in lockstep with its peers
@@ -230,6 +236,9 @@ class Engine:
     def _finish(self, r: Request, reason: str) -> None:
         r.finish_reason = reason
         self.cache.free(r.kv)
+        if r.swapped is not None:
+            self.kv_offloaded -= r.swapped.nbytes
+            r.swapped = None
         if r.future is not None and r.loop is not None:
             try:
                 r.loop.call_soon_threadsafe(lambda: r.future.done() or r.future.set_result(r))
@@ -242,6 +251,18 @@ class Engine:
         with self.lock:
             while self.waiting and len(self.running) + len(admitted) < self.max_running:
                 r = self.waiting[0]
+                if r.swapped is not None:
+                    # K / V waits in host memory: bring it back instead of prefilling again
+                    need = r.swapped.data.shape[2] + 1
+                    if self.cache.blocks.num_available < need and (self.running or admitted):
+                        break
+                    self.waiting.pop(0)
+                    self.cache.swap_in(r.kv, r.swapped)
+                    self.kv_offloaded -= r.swapped.nbytes
+                    r.swapped = None
+                    self.stats["kv_swap_ins"] = self.stats.get("kv_swap_ins", 0) + 1
+                    self.running.append(r)
+                    continue
                 toks = r.all_tokens
                 need_pages = (len(toks) + self.cache.page_size) // self.cache.page_size + 1
                 if len(toks) > budget and admitted:
@@ -260,8 +281,15 @@ class Engine:
             if len(self.running) <= 1:
                 return False
             r = self.running.pop()
-            self.cache.free(r.kv)
-            r.prefilled = False
+            nbytes = 2 * len(r.kv.pages) * self.cache.k[:, 0].numel() * self.cache.k.element_size()
+            if (self.kv_offload_bytes and r.prefilled and r.kv.pages
+                    and self.kv_offloaded + nbytes <= self.kv_offload_bytes):
+                r.swapped = self.cache.swap_out(r.kv)          # resumes where it stopped
+                self.kv_offloaded += nbytes
+                self.stats["kv_swap_outs"] = self.stats.get("kv_swap_outs", 0) + 1
+            else:
+                self.cache.free(r.kv)
+                r.prefilled = False
             r.preemptions += 1
             self.stats["preemptions"] += 1
             self.waiting.insert(0, r)

@@ -121,6 +121,18 @@ class SequenceKV:
     length: int = 0            # tokens whose K/V are in the cache
 
 
+@dataclass
+class HostKV:
+    """K / V of one preempted sequence in host memory: ``data`` [2, layers, pages, page_size, kv_heads, head_dim]."""
+    data: torch.Tensor
+    length: int
+    ready: object = None
+
+    @property
+    def nbytes(self) -> int:
+        return self.data.numel() * self.data.element_size()
+
+
 class KVCache:
     """Pools ``k[layer]``, ``v[layer]``: ``[num_pages, page_size, kv_heads, head_dim]``."""
 
@@ -155,6 +167,41 @@ class KVCache:
     def free(self, seq: SequenceKV) -> None:
         self.blocks.release(seq.pages)
         seq.pages, seq.length = [], 0
+
+    # host offload ---------------------------------------------------------------------
+    def swap_out(self, seq: SequenceKV, pin: bool = True) -> "HostKV":
+        """Copies the sequence's pages (all layers, K and V) to host memory and gives the pages back. The copy is
+        issued on the current stream into pinned memory; ``HostKV.ready`` fires when it has landed."""
+        n = len(seq.pages)
+        idx = torch.tensor(seq.pages, dtype=torch.long, device=self.k.device)
+        shape = (2, self.k.shape[0], n, *self.k.shape[2:])
+        host = torch.empty(shape, dtype=self.k.dtype, device="cpu")
+        if pin and self.k.is_cuda:
+            host = host.pin_memory()
+        host[0].copy_(self.k.index_select(1, idx), non_blocking=True)
+        host[1].copy_(self.v.index_select(1, idx), non_blocking=True)
+        ready = None
+        if self.k.is_cuda:
+            ready = torch.cuda.Event()
+            ready.record()
+        out = HostKV(host, seq.length, ready)
+        self.free(seq)
+        return out
+
+    def swap_in(self, seq: SequenceKV, host: "HostKV") -> None:
+        """Fresh pages for ``seq`` filled from ``host`` (raises ``OutOfPages`` before touching anything when
+        there are not enough)."""
+        n = host.data.shape[2]
+        if self.blocks.num_available < n:
+            raise OutOfPages()
+        pages = [self.blocks.alloc() for _ in range(n)]
+        idx = torch.tensor(pages, dtype=torch.long, device=self.k.device)
+        if host.ready is not None:
+            host.ready.synchronize()
+        dev = host.data.to(self.k.device, non_blocking=True)
+        self.k.index_copy_(1, idx, dev[0])
+        self.v.index_copy_(1, idx, dev[1])
+        seq.pages, seq.length = pages, host.length
 
     def slot_mapping(self, seq: SequenceKV, start: int, n: int) -> list[int]:
         """Flat slot (page * page_size + offset) of tokens [start, start + n)."""

@@ -45,9 +45,16 @@ def build_engine(config: InferenceConfig, tp=None):
         pages = 2048
     engine = Engine(model, num_pages=pages, page_size=ec.page_size, max_running=ec.max_num_seqs,
                     max_prefill_tokens=ec.max_num_batched_tokens,
-                    enable_prefix_cache=ec.enable_prefix_caching is not False, tp=tp)
+                    enable_prefix_cache=ec.enable_prefix_caching is not False, tp=tp,
+                    kv_offload_bytes=_kv_offload_bytes(config))
     engine.runner.capture_routed = ec.enable_return_routed_experts and arch.is_moe
     return engine
+
+
+def _kv_offload_bytes(config: InferenceConfig) -> int:
+    """Host-memory budget for the K / V of preempted requests (``kv_cache_offload.cpu.num_bytes``)."""
+    off = config.kv_cache_offload
+    return int(off.cpu.num_bytes) if off is not None and off.cpu is not None else 0
 
 
 def load_tokenizer(name: str):

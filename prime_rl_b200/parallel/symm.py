@@ -51,16 +51,26 @@ class SymmetricBuffer:
         dist.all_gather_object(handles, bytes(handle), group=group)
         self.ptrs: list[int] = []
         self._mapped: list[int] = []
-        for i, h in enumerate(handles):
-            if i == self.rank:
-                self.ptrs.append(self._own)
-                continue
-            buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
-            peer = ctypes.c_void_p()
-            if lib.prb_symm_import(buf, ctypes.byref(peer)) != 0:
-                raise RuntimeError(f"cudaIpcOpenMemHandle for rank {i} failed (no peer access between the GPUs?)")
-            self.ptrs.append(peer.value)
-            self._mapped.append(peer.value)
+        # Ranks map their peers one after the other: the first mapping of a peer GPU also switches on peer access
+        # inside the driver, and eight processes doing that at the same moment is the one thing at start-up that
+        # grows with the rank count.
+        failed = None
+        for turn in range(self.world):
+            if turn == self.rank:
+                for i, h in enumerate(handles):
+                    if i == self.rank:
+                        self.ptrs.append(self._own)
+                        continue
+                    buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                    peer = ctypes.c_void_p()
+                    if lib.prb_symm_import(buf, ctypes.byref(peer)) != 0:
+                        failed = i
+                        break
+                    self.ptrs.append(peer.value)
+                    self._mapped.append(peer.value)
+            dist.barrier(group=group)
+        if failed is not None:
+            raise RuntimeError(f"cudaIpcOpenMemHandle for rank {failed} failed (no peer access between the GPUs?)")
         self.c_ptrs = (ctypes.c_void_p * self.world)(*self.ptrs)     # host table handed to the launchers
         self._local = torch.as_tensor(_DevMem(self._own, self.nbytes), device=device)
         dist.barrier(group=group)        # nobody touches a peer before everybody has mapped it

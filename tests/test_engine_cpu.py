@@ -323,3 +323,34 @@ def test_cached_prefix_pages_count_as_available_and_are_evicted_on_demand():
     assert bm.evictable == 2                                    # back to cache-only
     bm.clear_prefix_cache()
     assert bm.evictable == 0 and bm.num_free == 2
+
+
+def test_preempted_requests_keep_their_kv_in_host_memory_and_resume_without_a_second_prefill():
+    """Too few pages for all requests at once: the engine preempts. With a host budget the victim's K / V is
+    swapped out and back in (same tokens as an engine with plenty of pages, no extra prompt tokens processed);
+    without one, or past the budget, it is recomputed."""
+    arch = resolve_arch("tiny-qwen3")
+    model = build_model(arch, device="cpu", dtype=torch.float32)
+    torch.manual_seed(0)
+    prompts = [torch.randint(0, arch.vocab_size, (40,)).tolist() for _ in range(6)]
+    sp = SamplingParams(max_tokens=40, temperature=0.0)
+    roomy = Engine(model, num_pages=256, page_size=16, enable_prefix_cache=False)
+    want = [r.output for r in roomy.generate_sync(prompts, sp)]
+    assert roomy.stats["preemptions"] == 0
+
+    tight = Engine(model, num_pages=24, page_size=16, enable_prefix_cache=False, kv_offload_bytes=1 << 30)
+    got = tight.generate_sync(prompts, sp)
+    assert [r.output for r in got] == want
+    assert tight.stats["preemptions"] > 0 and tight.stats["kv_swap_outs"] == tight.stats["kv_swap_ins"] > 0
+    assert tight.stats["prompt_tokens"] == roomy.stats["prompt_tokens"]        # nothing was prefilled twice
+    assert tight.kv_offloaded == 0 and tight.cache.blocks.num_free == 24
+
+    plain = Engine(model, num_pages=24, page_size=16, enable_prefix_cache=False)
+    again = plain.generate_sync(prompts, sp)
+    assert [r.output for r in again] == want and plain.stats["preemptions"] > 0
+    assert plain.stats.get("kv_swap_outs", 0) == 0
+    assert plain.stats["prompt_tokens"] > roomy.stats["prompt_tokens"]          # recomputed on re-admission
+
+    small = Engine(model, num_pages=24, page_size=16, enable_prefix_cache=False, kv_offload_bytes=1)
+    assert [r.output for r in small.generate_sync(prompts, sp)] == want          # budget too small: falls back
+    assert small.stats.get("kv_swap_outs", 0) == 0
