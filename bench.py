@@ -184,7 +184,7 @@ def trainer_pass(args, mode: str, world, steps: int, warmup: int, want_e2e: bool
         if moe:
             mcfg.update(ep=n if n > 1 else 1,
                         moe={"dispatch": {"type": args.dispatch} if args.dispatch == "torch" else
-                             {"type": "p2p", "capacity_factor": float(min(n, 4))}})
+                             {"type": "p2p"}})
             par = (f"ep{n} (128/{n} experts per GPU, peer-memory dispatch) x zero{n} (dense optimizer state "
                    f"partitioned, {args.optim_collectives} reduce-scatter / all-gather)") if n > 1 else "single GPU"
         else:

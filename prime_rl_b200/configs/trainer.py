@@ -165,7 +165,10 @@ class P2PMoEDispatchConfig(BaseConfig):
 
     type: Literal["p2p"] = "p2p"
     num_sms: int = Field(32, ge=1)
-    capacity_factor: float = Field(2.0, gt=0)   # receive-buffer rows as a multiple of the rows a rank sends
+    # receive-buffer rows as a multiple of the rows a rank sends. None = the worst case (every token of every rank
+    # routed to one rank: factor = ep), which cannot overflow however skewed the router is; a smaller factor saves
+    # 4 buffers x rows x hidden x 2 bytes of memory and reports an overflow through the kernel status word
+    capacity_factor: float | None = Field(None, gt=0)
     payload: Literal["bf16", "fp8"] = "bf16"    # fp8: e4m3 + 1x128 fp32 scales on the forward dispatch
     # forward dispatch without a global wait: rows leave on a side stream and the first expert GEMM's loader waits
     # per 128-row block. Measured a little slower than one wait at 2 and 8 GPUs (3.69 / 4.34 ms against 3.65 /

@@ -11,7 +11,7 @@
 //          dY^T @ X (wgrad)            = (A MN-major, B MN-major).
 //
 // Grouped (MoE) mode: rows of A / C are 128-row blocks that each belong to one expert
-// (`block_expert[blk]`, -1 = unused block); B is the stacked per-expert weight viewed as a
+// (`block_expert[blk]`, -1 = unused block; unused blocks come after all used ones); B is the stacked per-expert weight viewed as a
 // 2-D tensor with `b_rows_per_expert` rows per expert. No host synchronisation is needed:
 // the grid covers the static upper bound of blocks and unused blocks are skipped.
 //
@@ -107,6 +107,7 @@ struct GemmCfg {
 struct SchedDense {
   static constexpr int kGatherWarps = 0;
   int tile, num_tiles, tiles_m, tiles_n;
+  int group_first = 0;                 // first M block of the raster group of the current tile
   __device__ SchedDense(const GemmParams& p, int bn)
       : tile(blockIdx.x - gridDim.x), tiles_m((p.M + kBM - 1) / kBM), tiles_n((p.N + bn - 1) / bn) {
     num_tiles = tiles_m * tiles_n;
@@ -123,6 +124,7 @@ struct SchedDense {
     const int per_group = kGroup * tiles_n;
     const int g = tile / per_group;
     const int first_m = g * kGroup;
+    group_first = first_m;
     const int gsize = min(tiles_m - first_m, kGroup);
     const int r = tile - g * per_group;
     m_blk = first_m + (r % gsize);
@@ -143,6 +145,9 @@ struct SchedGrouped : SchedDense {
         brow = e * p.b_rows_per_expert;
         return true;
       }
+      // used blocks are a prefix of the row space (the grid covers a static upper bound): when the first block of
+      // a raster group is unused, so is everything after it
+      if (m_blk == group_first) return false;
     }
     return false;
   }
@@ -948,8 +953,12 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
   // narrower tiles while the wide ones would leave SMs idle (decode-sized M): a 128 x 64 tile keeps the
   // tensor pipe half as busy per CTA, but an idle SM does nothing at all
   if (force_bn <= 0 && !grouped) {
-    const long long tiles_m = (M + 127) / 128;
-    while (bn > 64 && tiles_m * ((N + bn - 1) / bn) < sm_count()) bn /= 2;
+    // the per-CTA traffic model of choose_splitk, one split only (a width that needs a second wave of CTAs is
+    // worse than a wider tile that leaves some SMs idle)
+    if ((long long)((M + 127) / 128) * ((N + 255) / 256) < sm_count()) {
+      const SplitKWorkspace none{nullptr, 0, 1};
+      choose_splitk(M, N, K, 0, none, bn);
+    }
   } else if (force_bn <= 0 && bn == 256) {
     const long long t256 = (long long)((M + 127) / 128) * ((N + 255) / 256);
     if (t256 < sm_count() && N % 256 != 0) bn = 128;

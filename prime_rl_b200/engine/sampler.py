@@ -69,6 +69,31 @@ def sample_untruncated(logits: torch.Tensor, temperature: torch.Tensor, generato
     return tok.long(), lp
 
 
+def sample_truncated(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+                     generator: torch.Generator | None = None, want_mask: bool = False):
+    """Top-k / top-p sampling on the GPU without a sort (``csrc/sampling.cu: sample_truncated_kernel``: radix
+    descent to the smallest kept logit, then Gumbel-max over the kept tokens). The kept ids come back unordered."""
+    B, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        logits = logits.float().contiguous()
+    dev = logits.device
+    tok = torch.empty(B, dtype=torch.int32, device=dev)
+    lp = torch.empty(B, dtype=torch.float32, device=dev)
+    ids = cnt = None
+    if want_mask:
+        ids = torch.empty(B, MAX_MASK, dtype=torch.int32, device=dev)
+        cnt = torch.zeros(B, dtype=torch.int32, device=dev)
+    rt.check(rt.lib().prb_sample_truncated(
+        logits.data_ptr(), temperature.float().contiguous().data_ptr(), top_k.to(torch.int32).contiguous().data_ptr(),
+        top_p.float().contiguous().data_ptr(), logits.stride(0), _draw_seed(generator), tok.data_ptr(), lp.data_ptr(),
+        rt.ptr(ids), rt.ptr(cnt), MAX_MASK, B, V, rt.stream_ptr(dev)), "prb_sample_truncated")
+    mask_ids = None
+    if want_mask:
+        counts = cnt.clamp(max=MAX_MASK).tolist()
+        mask_ids = [ids[b, :counts[b]] for b in range(B)]
+    return tok.long(), lp, mask_ids
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
            generator: torch.Generator | None = None, want_mask: bool = False, truncated: bool | None = None):
     """logits fp32 [B, V]; temperature/top_p fp32 [B]; top_k int [B] (<= 0 = off).
@@ -81,6 +106,8 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     if not truncated and logits.is_cuda:
         tok, lp = sample_untruncated(logits, temperature.float().contiguous(), generator)
         return tok, lp, None
+    if logits.is_cuda:
+        return sample_truncated(logits, temperature, top_k, top_p, generator, want_mask)
     greedy = temperature <= 0
     t = torch.where(greedy, torch.ones_like(temperature), temperature)
     z = logits.float() / t[:, None]

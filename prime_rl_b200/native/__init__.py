@@ -47,6 +47,7 @@ _CUDA_SIGNATURES = {
     "prb_gated_norm_bwd": [P, P, P, P, P, P, P, L, I, I, I, F, I, P],
     "prb_conv1d_fwd": [P, P, P, P, P, L, I, I, I, P],
     "prb_sample_gumbel": [P, P, L, L, P, P, I, I, P],
+    "prb_sample_truncated": [P, P, P, P, L, L, P, P, P, P, I, I, I, P],
     "prb_conv1d_bwd": [P, P, P, P, P, P, P, P, L, I, I, I, P],
     "prb_rs_pull": [P, L, L, F, P, I, P],
     "prb_ar_add_rmsnorm": [P, P, P, P, P, P, P, I, I, F, I, I, P, P],

@@ -107,7 +107,7 @@ def install_expert_parallel(model, dims, moe_cfg=None) -> None:
             from .ep_p2p import P2PDispatcher
 
             dcfg = getattr(moe_cfg, "dispatch", None)
-            moe.dispatcher = P2PDispatcher(group, ep, E, capacity_factor=getattr(dcfg, "capacity_factor", 2.0),
+            moe.dispatcher = P2PDispatcher(group, ep, E, capacity_factor=getattr(dcfg, "capacity_factor", None),
                                            payload=getattr(dcfg, "payload", "bf16"),
                                            per_block=bool(getattr(dcfg, "per_block_arrival", False)))
         else:

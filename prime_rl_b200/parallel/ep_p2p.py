@@ -233,7 +233,8 @@ class P2PDispatcher:
     receive as a multiple of the rows it sends (``T * k``); an overflow is reported through the
     kernel status word (``ops._runtime.check_status``)."""
 
-    def __init__(self, group, ep: int, num_experts: int, capacity_factor: float = 2.0, max_tokens: int | None = None,
+    def __init__(self, group, ep: int, num_experts: int, capacity_factor: float | None = None,
+                 max_tokens: int | None = None,
                  payload: str = "bf16", per_block: bool = False):
         if payload not in ("bf16", "fp8"):
             raise ValueError("payload must be 'bf16' or 'fp8'")
@@ -243,7 +244,9 @@ class P2PDispatcher:
         self.per_block = per_block
         self.group, self.ep, self.E = group, ep, num_experts
         self.E_local = num_experts // ep
-        self.capacity_factor = capacity_factor
+        # None: room for the worst case (all pairs of all ranks land on one rank), so a skewed router can never
+        # overflow the buffers; a smaller factor trades that guarantee for memory
+        self.capacity_factor = float(ep) if capacity_factor is None else capacity_factor
         # Tokens per rank and call the buffers are sized for. Every rank must derive the SAME
         # capacity: the symmetric buffers have one layout, and peers compute addresses inside each
         # other's allocation from it. When not given, the first call agrees on the maximum over the

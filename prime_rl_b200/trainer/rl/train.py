@@ -367,7 +367,10 @@ class RLTrainer:
                 out = Path(cfg.memory_profiler_path)
                 out.mkdir(parents=True, exist_ok=True)
                 torch.cuda.memory._dump_snapshot(str(out / f"rank_{self.world.rank}_step_{step}.pickle"))
-            if self.weight_sender is not None:
+            # the weights of the last step have no taker in an in-memory transport: the orchestrator stops after
+            # shipping the batch for it, and a sender that waits for an acknowledgement would wait out its timeout
+            last = cfg.max_steps is not None and step + 1 >= cfg.max_steps
+            if self.weight_sender is not None and not (last and getattr(self.weight_sender, "require_ack", False)):
                 t0 = time.perf_counter()
                 self.weight_sender.broadcast(self.model, step)
                 m["time/broadcast_weights"] = time.perf_counter() - t0

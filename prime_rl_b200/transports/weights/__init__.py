@@ -140,7 +140,9 @@ def setup_weight_sender(config, run_dir: Path, world, model, lora: bool = False,
     if config.type == "nccl":
         from .nccl import NCCLWeightSender
 
-        return NCCLWeightSender(config, run_dir, world)
+        sender = NCCLWeightSender(config, run_dir, world)
+        sender.connect_in_background(next(model.parameters()).device)     # the engines join before the first batch
+        return sender
     if config.type == "p2p":
         from .p2p import P2PWeightSender
 

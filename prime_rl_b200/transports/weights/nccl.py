@@ -60,9 +60,39 @@ class NCCLWeightSender(WeightSender):
     def __init__(self, config, run_dir: Path, world):
         super().__init__(config, run_dir, world, require_ack=True)
         self.pg = None
+        self._connecting = None
+        self._connect_error: BaseException | None = None
+
+    def connect_in_background(self, device) -> None:
+        """Starts the rendezvous with the engines right away (from the trainer's set-up). The engines join when the
+        orchestrator posts ``/init_broadcaster``, which it does before it produces the first batch: a trainer that
+        only connected at its first broadcast (after its first step) would wait for a batch that the orchestrator
+        cannot produce while its request to the engines is still waiting for the trainer."""
+        if not self.world.is_master or self.pg is not None or self._connecting is not None:
+            return
+        import threading
+
+        def run():
+            try:
+                if device.type == "cuda":
+                    torch.cuda.set_device(device)
+                self.pg, self.store = _new_group(self.config.host, self.config.port, 0,
+                                                 self.config.inference_world_size + 1, self.config.timeout, device)
+            except BaseException as e:       # surfaced by the first broadcast
+                self._connect_error = e
+
+        self._connecting = threading.Thread(target=run, name="weight-broadcast-connect", daemon=True)
+        self._connecting.start()
 
     def _connect(self, device):
-        if self.pg is None and self.world.is_master:
+        if not self.world.is_master:
+            return
+        if self._connecting is not None:
+            self._connecting.join()
+            self._connecting = None
+            if self._connect_error is not None:
+                raise RuntimeError("the weight-broadcast group could not be formed") from self._connect_error
+        if self.pg is None:
             self.pg, self.store = _new_group(self.config.host, self.config.port, 0,
                                              self.config.inference_world_size + 1, self.config.timeout, device)
 
@@ -77,8 +107,8 @@ class NCCLWeightSender(WeightSender):
         else:
             if not self.world.is_master:
                 return
-            sd = convert.model_state(model, "hf")
-            per_layer = ({n: sd[n] for n in names} for names in layer_groups(list(sd)))
+            full = convert.model_state(model, "hf")
+            per_layer = [{n: full[n] for n in names} for names in layer_groups(list(full))]
             info = None
         device = next(model.parameters()).device
         if self.world.is_master:

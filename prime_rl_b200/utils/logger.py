@@ -20,10 +20,24 @@ class _Intercept(logging.Handler):
         _logger.opt(depth=6, exception=record.exc_info).log(level, record.getMessage())
 
 
+def _arm_stack_dumps() -> None:
+    import faulthandler
+    import signal
+
+    try:
+        faulthandler.enable(file=sys.stderr, all_threads=True)
+        if hasattr(signal, "SIGUSR1"):
+            faulthandler.register(signal.SIGUSR1, file=sys.stderr, all_threads=True, chain=False)
+    except (ValueError, OSError, AttributeError):      # no usable stderr (embedded interpreters, closed streams)
+        pass
+
+
 def setup_logger(level: str = "info", *, log_file: Path | None = None, json_logging: bool = False,
                  tag: str | None = None, intercept_stdlib: bool = False):
-    """(Re)configures the global logger: console sink, optional per-process log file."""
+    """(Re)configures the global logger: console sink, optional per-process log file. Also arms the stack dumps:
+    a native crash prints the Python stacks, and ``kill -USR1 <pid>`` prints them from a process that seems stuck."""
     global _configured
+    _arm_stack_dumps()
     _logger.remove()
     prefix = f"[{tag}] " if tag else ""
     fmt = "<dim>{time:HH:mm:ss}</dim> <level>{level: <7}</level> " + prefix + "{message}"

@@ -240,3 +240,44 @@ def test_samples_of_one_prompt_decode_through_the_shared_prefix_kernel():
         assert same >= len(prompts) - 1
         for a, b in zip(ref, got):
             assert abs(a.logprobs[0] - b.logprobs[0]) < 5e-2
+
+
+def test_truncated_sampling_kernel_keeps_the_same_set_as_the_sorted_rule():
+    """Top-k / top-p without a sort: the kept set must be the prefix of the sorted order that the PyTorch rule
+    keeps, samples must fall inside it with the renormalised log-probability, and frequencies must follow it."""
+    from prime_rl_b200.engine import sampler as S
+
+    torch.manual_seed(0)
+    dev = torch.device("cuda", 0)
+    B, V = 6, 5000
+    logits = torch.randn(B, V, device=dev) * 3
+    temperature = torch.tensor([1.0, 0.7, 1.0, 1.3, 0.0, 1.0], device=dev)
+    top_k = torch.tensor([0, 50, 5, 0, 10, 1], device=dev)
+    top_p = torch.tensor([0.9, 1.0, 0.5, 0.3, 1.0, 1.0], device=dev)
+    # the kept set by the sorted rule
+    t = torch.where(temperature <= 0, torch.ones_like(temperature), temperature)
+    z = logits / t[:, None]
+    srt, idx = torch.sort(z, dim=-1, descending=True)
+    probs = torch.softmax(srt, -1)
+    keep = (probs.cumsum(-1) - probs) < top_p[:, None]
+    k = torch.where(top_k > 0, top_k, torch.full_like(top_k, V))
+    keep &= torch.arange(V, device=dev)[None] < k[:, None]
+    want = [set(idx[b][keep[b]].tolist()) for b in range(B)]
+    tok, lp, masks = S.sample(logits, temperature, top_k, top_p, want_mask=True)
+    for b in range(B):
+        got = set(masks[b].tolist())
+        assert got == want[b] or (len(want[b]) > S.MAX_MASK and got <= want[b]), (b, len(got), len(want[b]))
+        assert int(tok[b]) in want[b]
+        kept = torch.tensor(sorted(want[b]), device=dev)
+        ref_lp = z[b, tok[b]] - torch.logsumexp(z[b, kept], 0)
+        assert abs(float(lp[b]) - float(ref_lp)) < 1e-3
+    assert int(tok[4]) == int(logits[4].argmax()) and int(tok[5]) == int(logits[5].argmax())
+    # frequencies of row 2 (five kept tokens at most, top-p 0.5)
+    kept = sorted(want[2])
+    pr = torch.softmax(z[2, torch.tensor(kept, device=dev)], 0)
+    counts = torch.zeros(len(kept))
+    g = torch.Generator(device=dev).manual_seed(1)
+    for _ in range(2000):
+        tk, _, _ = S.sample(logits[2:3], temperature[2:3], top_k[2:3], top_p[2:3], generator=g)
+        counts[kept.index(int(tk[0]))] += 1
+    assert torch.allclose(counts / 2000, pr.cpu(), atol=0.04)
