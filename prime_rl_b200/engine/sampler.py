@@ -73,6 +73,8 @@ def sample_truncated(logits: torch.Tensor, temperature: torch.Tensor, top_k: tor
                      generator: torch.Generator | None = None, want_mask: bool = False):
     """Top-k / top-p sampling on the GPU without a sort (``csrc/sampling.cu: sample_truncated_kernel``: radix
     descent to the smallest kept logit, then Gumbel-max over the kept tokens). The kept ids come back unordered."""
+    from ..ops import _runtime as rt
+
     B, V = logits.shape
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         logits = logits.float().contiguous()
