@@ -202,8 +202,12 @@ class ModelConfig(BaseModelConfig):
     moe: MoERuntimeConfig = MoERuntimeConfig()
     cp: int = 1
     cp_style: Literal["ring", "ulysses"] = "ring"
-    # "p2p": the ring style's forward K / V exchange runs inside the attention kernel over NVLink peer memory
-    cp_kv_exchange: Literal["nccl", "p2p"] = "nccl"
+    # K / V exchange of the ring style. "nccl": all-gather, then one attention call per query slice. "p2p": the forward
+    # all-gather runs inside the attention kernel over NVLink peer memory. "ring": K / V blocks travel rank to rank,
+    # one partial attention per step merged through the log-sum-exp, dK / dV partials returned to the owners (K / V of
+    # the whole sequence never exist on one rank). "ring_p2p": the same ring with every block pulled straight from its
+    # owner's symmetric memory on a side stream and the dK / dV partials summed by peer loads (one NVSwitch box).
+    cp_kv_exchange: Literal["nccl", "p2p", "ring", "ring_p2p"] = "nccl"
     # "p2p": the sharded optimizer's gradient reduce-scatter (with cast / scale) and parameter all-gather run as
     # peer-memory kernels over NVLink instead of NCCL collectives (one NVSwitch box, at most 8 ranks per shard group)
     optim_collectives: Literal["nccl", "p2p"] = "nccl"

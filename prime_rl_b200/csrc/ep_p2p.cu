@@ -405,6 +405,35 @@ ag_push_kernel(const uint4* __restrict__ src, EpPeers dst, long long off16, long
     o[i] = src[i];
 }
 
+// Plain copy of 16-byte units from a peer's (or this rank's) memory into local memory with a bounded grid, so that
+// it can run on a side stream next to a compute kernel (the ring form of context parallelism pulls the K / V block
+// of the next step with it while the current block is in the tensor cores).
+__global__ void __launch_bounds__(256)
+peer_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long n16) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    dst[i] = __ldcg(src + i);
+}
+
+// Every rank holds R slots of n bf16 elements in symmetric memory (slot o = its contribution for owner o). The owner
+// sums slot `rank` of all R buffers in rank order (fp32) and writes bf16: a reduce-scatter by peer loads with a
+// fixed summation order. n is a multiple of 8.
+__global__ void __launch_bounds__(256)
+slot_pull_reduce_kernel(EpPeers bufs, long long slot_off16, long long n16, uint4* __restrict__ out, int R) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < R; ++r) {
+      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(bufs.buf[r]) + slot_off16 + i);
+      const float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y), c = unpack_bf16(v.z), d = unpack_bf16(v.w);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+      acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+    }
+    out[i] = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]),
+                        pack_bf16(acc[6], acc[7]));
+  }
+}
+
 __global__ void __launch_bounds__(32)
 ep_signal_kernel(EpPeers flags, int rank, int R, int kind, int epoch) {
   __threadfence_system();
@@ -803,6 +832,30 @@ PRB_API int prb_ag_push(const void* src, void* const* peer_bufs, long long off_b
   if (blocks > 148 * 2) blocks = 148 * 2;
   prb::ag_push_kernel<<<dim3(static_cast<unsigned>(blocks), R - 1), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const uint4*>(src), ep_peers(peer_bufs, R), off_bytes / 16, bytes / 16, rank, R);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// dst (local, 16-byte aligned) <- src (a peer's or local memory), bytes a multiple of 16; at most `max_ctas` CTAs.
+PRB_API int prb_peer_copy(const void* src, void* dst, long long bytes, int max_ctas, void* stream) {
+  if ((bytes % 16) || (reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15)) return -2;
+  if (bytes <= 0) return 0;
+  long long blocks = (bytes / 16 + 255) / 256;
+  if (max_ctas < 1) max_ctas = 1;
+  if (blocks > max_ctas) blocks = max_ctas;
+  prb::peer_copy_kernel<<<static_cast<unsigned>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint4*>(src), reinterpret_cast<uint4*>(dst), bytes / 16);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+// out[i] = sum_r bf16(peer_bufs[r] + slot_off_bytes)[i], i in [0, n): n bf16 elements, a multiple of 8.
+PRB_API int prb_slot_pull_reduce(void* const* peer_bufs, long long slot_off_bytes, long long n, void* out, int R,
+                                 void* stream) {
+  if (R > prb::kEpMaxRanks || (slot_off_bytes % 16) || (n % 8) || (reinterpret_cast<uintptr_t>(out) & 15)) return -2;
+  if (n <= 0) return 0;
+  long long blocks = (n / 8 + 255) / 256;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  prb::slot_pull_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      ep_peers(peer_bufs, R), slot_off_bytes / 16, n / 8, reinterpret_cast<uint4*>(out), R);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -44,6 +44,8 @@ struct FaParams {
   int num_docs;
   int total_q;            // T (rows of K / V)
   int q_off, q_rows;      // the query / output tensors hold global rows [q_off, q_off + q_rows) only
+  int k_off, k_rows;      // the K / V tensors hold global rows [k_off, k_off + k_rows) only; keys outside do not exist
+                          // for this call (ring step of context parallelism: the caller merges the partial results)
   int heads_q, heads_kv;
   __nv_bfloat16* out;     // [T, heads_q, D]
   long long ld_out;       // elements per token
@@ -195,10 +197,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const bool out_0 = (g0 + kFaBM <= p.q_off) || (g0 >= p.q_off + p.q_rows);               // tile 0 not held here
   const bool out_1 = (g0 + 2 * kFaBM <= p.q_off) || (g0 + kFaBM >= p.q_off + p.q_rows);
   const int q1_0 = out_0 ? q0_0 : min(q0_0 + kFaBM, doc_len), q1_1 = out_1 ? q0_1 : min(q0_1 + kFaBM, doc_len);
-  const int nblk_0 = (q1_0 > q0_0) ? (q1_0 + kFaBN - 1) / kFaBN : 0;
-  const int nblk_1 = (q1_1 > q0_1) ? (q1_1 + kFaBN - 1) / kFaBN : 0;
-  const int blk0_0 = (p.window > 0 && nblk_0 > 0) ? max(0, q0_0 - p.window + 1) / kFaBN : 0;
-  const int blk0_1 = (p.window > 0 && nblk_1 > 0) ? max(0, q0_1 - p.window + 1) / kFaBN : 0;
+  // keys held by this call, as columns of the document: [kcol_lo, kcol_hi)
+  const int kcol_lo = p.k_off - doc_start, kcol_hi = kcol_lo + p.k_rows;
+  int nblk_0 = (q1_0 > q0_0) ? (q1_0 + kFaBN - 1) / kFaBN : 0;
+  int nblk_1 = (q1_1 > q0_1) ? (q1_1 + kFaBN - 1) / kFaBN : 0;
+  int blk0_0 = (p.window > 0 && nblk_0 > 0) ? max(0, q0_0 - p.window + 1) / kFaBN : 0;
+  int blk0_1 = (p.window > 0 && nblk_1 > 0) ? max(0, q0_1 - p.window + 1) / kFaBN : 0;
+  if (kcol_lo > 0 || kcol_hi < doc_len) {
+    const int b_lo = max(kcol_lo, 0) / kFaBN, b_hi = (kcol_hi > 0) ? (kcol_hi + kFaBN - 1) / kFaBN : 0;
+    blk0_0 = max(blk0_0, b_lo); nblk_0 = min(nblk_0, b_hi);
+    blk0_1 = max(blk0_1, b_lo); nblk_1 = min(nblk_1, b_hi);
+    if (nblk_0 <= blk0_0) nblk_0 = blk0_0 = 0;      // no key of this call is visible to the tile
+    if (nblk_1 <= blk0_1) nblk_1 = blk0_1 = 0;
+  }
   // union of the two ranges: the K / V stream of this CTA (tile 0 always has rows)
   const int j_begin = (nblk_1 > 0) ? (nblk_0 > 0 ? min(blk0_0, blk0_1) : blk0_1) : blk0_0;
   const int j_end = max(nblk_0, nblk_1);
@@ -242,7 +253,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       bool ok = true;
       unsigned chunks_done = 0;
       for (int j = j_begin; j < j_end && ok; ++j) {
-        const int krow = doc_start + j * kFaBN;
+        const int krow = doc_start + j * kFaBN - p.k_off;     // may start before row 0: those rows read as zero
         if constexpr (GATHER) {
           if (!fa_wait_rows(p, krow, krow + kFaBN - 1, chunks_done)) { ok = false; break; }
         }
@@ -368,7 +379,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (lane == 0) mbar_arrive(&s_free[t]);
         }
         const int col0 = j * kFaBN + h * kFaHN;
-        const bool need_mask = (col0 + kFaHN - 1 > my_q0) || (p.window > 0 && my_q1 - 1 - col0 >= p.window);
+        const bool need_mask = (col0 + kFaHN - 1 > my_q0) || (p.window > 0 && my_q1 - 1 - col0 >= p.window) ||
+                               (col0 < kcol_lo) || (col0 + kFaHN > kcol_hi);
         // raw scores; masked entries become -inf. The running reference `m` (log2 domain) only
         // moves when the block maximum exceeds it by more than 8: P then stays below 2^8, and
         // most blocks need no rescale of O at all.
@@ -376,8 +388,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one
         // two straight-line variants: a per-element `if (need_mask)` is compiled to 64 branches
         if (need_mask) {
-          const int lim_hi = row - col0;                                   // keep c <= lim_hi
-          const int lim_lo = (p.window > 0) ? lim_hi - p.window : -1;      // keep c >  lim_lo
+          const int causal_hi = row - col0;
+          const int lim_hi = min(causal_hi, kcol_hi - 1 - col0);                                   // keep c <= lim_hi
+          const int lim_lo = max((p.window > 0) ? causal_hi - p.window : -1, kcol_lo - 1 - col0);  // keep c >  lim_lo
 #pragma unroll
           for (int c = 0; c < 64; ++c) {
             const float x = __uint_as_float(sv[c >> 5][c & 31]);
@@ -473,8 +486,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         if (row_ok)
           p.lse[static_cast<long long>(head) * p.q_rows + grow] =
-              (m + log2f(l)) * 0.6931471805599453f;
+              (l > 0.f) ? (m + log2f(l)) * 0.6931471805599453f : -INFINITY;
       }
+    } else if (ok && it == 0 && row_ok) {
+      // no key block of this call is visible to the tile: an empty partial result (weight zero in the merge)
+      __nv_bfloat16* dst = p.out + static_cast<long long>(grow) * p.ld_out + static_cast<long long>(head) * kFaD;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) *reinterpret_cast<uint4*>(dst + i * 8) = make_uint4(0, 0, 0, 0);
+      p.lse[static_cast<long long>(head) * p.q_rows + grow] = -INFINITY;
     }
   }
 
@@ -482,6 +501,36 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// Combines a partial attention result over one key range into the running result of the rows: one warp per
+// (token, head). acc / lse_acc: fp32 [T, H, 128] / [H, T]; part / lse_part: bf16 [T, H, 128] / fp32 [H, T].
+//   lse = log(exp(lse_acc) + exp(lse_part)), acc = acc exp(lse_acc - lse) + part exp(lse_part - lse)
+// A partial result with lse = -inf (no visible key) leaves the row unchanged.
+__global__ void __launch_bounds__(256)
+attn_merge_kernel(float* __restrict__ acc, float* __restrict__ lse_acc, const __nv_bfloat16* __restrict__ part,
+                  const float* __restrict__ lse_part, long long T, int heads) {
+  const int lane = threadIdx.x & 31;
+  const long long item = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (item >= T * heads) return;
+  const long long t = item / heads;
+  const int h = static_cast<int>(item - t * heads);
+  const long long si = static_cast<long long>(h) * T + t;
+  const float la = lse_acc[si], lp = lse_part[si];
+  if (lp == -INFINITY) return;
+  const float mx = fmaxf(la, lp);
+  const float wa = __expf(la - mx), wp = __expf(lp - mx);       // la = -inf -> 0
+  const float inv = 1.f / (wa + wp);
+  float4* a = reinterpret_cast<float4*>(acc + (t * heads + h) * kFaD) + lane;
+  const uint2 pv = *(reinterpret_cast<const uint2*>(part + (t * heads + h) * kFaD) + lane);
+  const float2 p0 = unpack_bf16(pv.x), p1 = unpack_bf16(pv.y);
+  float4 v = *a;
+  const float ca = wa * inv, cp = wp * inv;
+  v.x = v.x * ca + p0.x * cp; v.y = v.y * ca + p0.y * cp;
+  v.z = v.z * ca + p1.x * cp; v.w = v.w * ca + p1.y * cp;
+  *a = v;
+  __syncwarp();
+  if (lane == 0) lse_acc[si] = mx + __logf(wa + wp);
 }
 
 }  // namespace prb
@@ -492,13 +541,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 // sum over documents of ceil(len / 256).
 // Context-parallel form: q / out / lse hold only the global rows [q_off, q_off + q_rows) (lse is
 // [heads_q, q_rows]); k / v and cu_seqlens describe the complete sequence of total_q tokens.
-PRB_API int prb_flash_fwd_slice(const void* q, const void* k, const void* v, void* out, float* lse,
-                                const int* cu_seqlens, int num_docs, int total_q, int q_off, int q_rows, int heads_q,
-                                int heads_kv, int head_dim, long long ld_q, long long ld_k, long long ld_v,
-                                long long ld_out, float scale, int window, int max_pairs, const float* sinks,
-                                int* status, void* stream_) {
+//
+// Block form (`prb_flash_fwd_block`): in addition k / v hold only the global rows [k_off, k_off + k_rows); keys
+// outside that range do not take part, so out / lse are a partial result over those keys (rows that see none of
+// them get out = 0 and lse = -inf). Partial results over disjoint key ranges combine with
+// lse = logaddexp(lse_a, lse_b), out = out_a exp(lse_a - lse) + out_b exp(lse_b - lse). No sinks in this form.
+PRB_API int prb_flash_fwd_block(const void* q, const void* k, const void* v, void* out, float* lse,
+                                const int* cu_seqlens, int num_docs, int total_q, int q_off, int q_rows, int k_off,
+                                int k_rows, int heads_q, int heads_kv, int head_dim, long long ld_q, long long ld_k,
+                                long long ld_v, long long ld_out, float scale, int window, int max_pairs,
+                                const float* sinks, int* status, void* stream_) {
   using namespace prb;
   if (q_off < 0 || q_rows <= 0 || q_off + q_rows > total_q) return -3;
+  if (k_off < 0 || k_rows <= 0 || k_off + k_rows > total_q) return -3;
+  if (sinks != nullptr && (k_off != 0 || k_rows != total_q)) return -5;
   if (head_dim != kFaD || heads_q % heads_kv) return -2;
   if (total_q <= 0 || num_docs <= 0) return 0;
   if ((ld_q % 8) || (ld_k % 8) || (ld_v % 8) || (ld_out % 8)) return -4;
@@ -507,15 +563,16 @@ PRB_API int prb_flash_fwd_slice(const void* q, const void* k, const void* v, voi
   int rc = make_tmap_2d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)q_rows, (uint64_t)heads_q * kFaD,
                         (uint64_t)ld_q, kFaBM, 64, true);
   if (rc) return rc;
-  rc = make_tmap_2d(&tmK, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_q, (uint64_t)heads_kv * kFaD,
+  rc = make_tmap_2d(&tmK, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)k_rows, (uint64_t)heads_kv * kFaD,
                     (uint64_t)ld_k, kFaBN, 64, true);
   if (rc) return rc;
-  rc = make_tmap_2d(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_q, (uint64_t)heads_kv * kFaD,
+  rc = make_tmap_2d(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)k_rows, (uint64_t)heads_kv * kFaD,
                     (uint64_t)ld_v, kFaHN, 64, true);
   if (rc) return rc;
   FaParams p;
   p.cu_seqlens = cu_seqlens; p.num_docs = num_docs; p.total_q = total_q;
   p.q_off = q_off; p.q_rows = q_rows;
+  p.k_off = k_off; p.k_rows = k_rows;
   p.heads_q = heads_q; p.heads_kv = heads_kv;
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.ld_out = ld_out; p.lse = lse;
   p.scale_log2 = scale * 1.4426950408889634f;
@@ -564,6 +621,7 @@ PRB_API int prb_flash_fwd_gather(const void* q, void* kv_local, void* const* pee
   FaParams p;
   p.cu_seqlens = cu_seqlens; p.num_docs = num_docs; p.total_q = total_q;
   p.q_off = q_off; p.q_rows = q_rows;
+  p.k_off = 0; p.k_rows = total_q;
   p.heads_q = heads_q; p.heads_kv = heads_kv;
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.ld_out = ld_out; p.lse = lse;
   p.scale_log2 = scale * 1.4426950408889634f;
@@ -585,10 +643,31 @@ PRB_API int prb_flash_fwd_gather(const void* q, void* kv_local, void* const* pee
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
+PRB_API int prb_flash_fwd_slice(const void* q, const void* k, const void* v, void* out, float* lse,
+                                const int* cu_seqlens, int num_docs, int total_q, int q_off, int q_rows, int heads_q,
+                                int heads_kv, int head_dim, long long ld_q, long long ld_k, long long ld_v,
+                                long long ld_out, float scale, int window, int max_pairs, const float* sinks,
+                                int* status, void* stream_) {
+  return prb_flash_fwd_block(q, k, v, out, lse, cu_seqlens, num_docs, total_q, q_off, q_rows, 0, total_q, heads_q,
+                             heads_kv, head_dim, ld_q, ld_k, ld_v, ld_out, scale, window, max_pairs, sinks, status,
+                             stream_);
+}
+
 PRB_API int prb_flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int* cu_seqlens,
                           int num_docs, int total_q, int heads_q, int heads_kv, int head_dim, long long ld_q,
                           long long ld_k, long long ld_v, long long ld_out, float scale, int window, int max_pairs,
                           int* status, void* stream_) {
   return prb_flash_fwd_slice(q, k, v, out, lse, cu_seqlens, num_docs, total_q, 0, total_q, heads_q, heads_kv, head_dim,
                              ld_q, ld_k, ld_v, ld_out, scale, window, max_pairs, nullptr, status, stream_);
+}
+
+// acc fp32 [T, heads, 128] and lse_acc fp32 [heads, T] are updated in place with the partial result (part bf16
+// [T, heads, 128] contiguous, lse_part fp32 [heads, T]); start from acc = 0, lse_acc = -inf.
+PRB_API int prb_attn_merge(float* acc, float* lse_acc, const void* part, const float* lse_part, long long T, int heads,
+                           void* stream_) {
+  if (T <= 0 || heads <= 0) return 0;
+  const long long items = T * heads;
+  prb::attn_merge_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
+      acc, lse_acc, reinterpret_cast<const __nv_bfloat16*>(part), lse_part, T, heads);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

@@ -37,6 +37,8 @@ struct FaBwdParams {
   const int* cu_seqlens;
   int num_docs, total_q, heads_q, heads_kv;
   int q_off, q_rows;       // q / dO / lse / delta / dq hold the global rows [q_off, q_off + q_rows) only
+  int k_off, k_rows;       // k / v / dk / dv hold the global rows [k_off, k_off + k_rows) only (ring step); lse is the
+                           // log-sum-exp over ALL keys, so the products over this key range are the exact partial gradients
   const float* lse;        // [heads_q, T] natural log
   const float* delta;      // [heads_q, T] rowsum(dO * O)
   __nv_bfloat16* dq;       // [T, heads_q, D] contiguous
@@ -176,6 +178,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   __syncthreads();
   if (!s_work[3]) return;
   const int doc_start = s_work[0], doc_len = s_work[1], kv0 = s_work[2];
+  // keys held by this call, as columns of the document: [kcol_lo, kcol_hi)
+  const int kcol_lo = p.k_off - doc_start, kcol_hi = kcol_lo + p.k_rows;
+  if (kv0 + kBwB <= kcol_lo || kv0 >= kcol_hi) return;           // none of this block's keys is held: nothing to write
   int i_begin = kv0 / kBwB;
   int i_end = (doc_len + kBwB - 1) / kBwB;
   if (p.window > 0) i_end = min(i_end, (kv0 + kBwB - 1 + p.window - 1) / kBwB + 1);
@@ -188,8 +193,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     // no query of this rank sees these keys: their gradient contribution is zero
     for (int idx = threadIdx.x; idx < kBwB * (kBwD / 8); idx += blockDim.x) {
       const int key = kv0 + idx / (kBwD / 8), c = (idx % (kBwD / 8)) * 8;
-      if (key < doc_len) {
-        const long long tok = doc_start + key;
+      if (key < doc_len && key >= kcol_lo && key < kcol_hi) {
+        const long long tok = doc_start + key - p.k_off;
         *reinterpret_cast<uint4*>(p.dk + tok * p.ld_dk + static_cast<long long>(kv_head) * kBwD + c) = make_uint4(0, 0, 0, 0);
         *reinterpret_cast<uint4*>(p.dv + tok * p.ld_dv + static_cast<long long>(kv_head) * kBwD + c) = make_uint4(0, 0, 0, 0);
       }
@@ -227,8 +232,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       mbar_expect_tx(kv_full, 2 * kBwTile);
-      bw_load_tile(k_s, &tmK, kv_full, kv_head * kBwD, doc_start + kv0);
-      bw_load_tile(v_s, &tmV, kv_full, kv_head * kBwD, doc_start + kv0);
+      bw_load_tile(k_s, &tmK, kv_full, kv_head * kBwD, doc_start + kv0 - p.k_off);   // rows outside read as zero
+      bw_load_tile(v_s, &tmV, kv_full, kv_head * kBwD, doc_start + kv0 - p.k_off);
       bool ok = true;
       for (int n = 0; n < num_iters && ok; ++n) {
         const int st = n & 1;
@@ -307,8 +312,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       const long long stat_idx = static_cast<long long>(head) * p.q_rows + grow;
       const float neg_lse2 = row_ok ? -p.lse[stat_idx] * 1.4426950408889634f : 0.f;
       const float neg_delta = row_ok ? -p.delta[stat_idx] : 0.f;
-      const int lim_hi = row_ok ? row - col0 : -1;
-      const int lim_lo = (p.window > 0) ? lim_hi - p.window : -1;
+      const int causal_hi = row_ok ? row - col0 : -1;
+      const int lim_hi = min(causal_hi, kcol_hi - 1 - col0);
+      const int lim_lo = max((p.window > 0) ? causal_hi - p.window : -1, kcol_lo - 1 - col0);
 
       ok = mbar_wait_poll(s_full, n & 1, p.status, kTimeoutTmemFull);
       ok = __all_sync(0xffffffffu, ok);
@@ -356,7 +362,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         __nv_bfloat16* dst = (which ? p.dk : p.dv) +
-                             static_cast<long long>(doc_start + key) * (which ? p.ld_dk : p.ld_dv) +
+                             static_cast<long long>(doc_start + key - p.k_off) * (which ? p.ld_dk : p.ld_dv) +
                              static_cast<long long>(kv_head) * kBwD + 64 * w;
         const uint32_t tm = tmem_base + lane_off + (which ? kTmDK : kTmDV) + 64 * w;
         const float mul = which ? p.scale : 1.f;
@@ -365,7 +371,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           uint32_t gv[32];
           tmem_ld_32x32(tm + 32 * c, gv);
           tmem_ld_wait();
-          if (key < doc_len) {
+          if (key < doc_len && key >= kcol_lo && key < kcol_hi) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               uint4 o;
@@ -438,8 +444,22 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (!s_work[3]) return;
   const int doc_start = s_work[0], doc_len = s_work[1], q0 = s_work[2];
   if (doc_start + q0 + kBwB <= p.q_off || doc_start + q0 >= p.q_off + p.q_rows) return;   // rows not held here
-  const int j_begin = (p.window > 0) ? max(0, q0 - p.window + 1) / kBwB : 0;
-  const int num_iters = q0 / kBwB + 1 - j_begin;     // up to and including the diagonal block
+  const int kcol_lo = p.k_off - doc_start, kcol_hi = kcol_lo + p.k_rows;      // keys held by this call (document columns)
+  int j_begin = (p.window > 0) ? max(0, q0 - p.window + 1) / kBwB : 0;
+  int j_end = q0 / kBwB + 1;                          // up to and including the diagonal block
+  j_begin = max(j_begin, max(kcol_lo, 0) / kBwB);
+  j_end = min(j_end, (kcol_hi > 0) ? (kcol_hi + kBwB - 1) / kBwB : 0);
+  const int num_iters = j_end - j_begin;
+  if (num_iters <= 0) {
+    // no held key is visible to these rows: their partial dQ is zero
+    for (int idx = threadIdx.x; idx < kBwB * (kBwD / 8); idx += blockDim.x) {
+      const int row = q0 + idx / (kBwD / 8), c = (idx % (kBwD / 8)) * 8;
+      const int grow = doc_start + row - p.q_off;
+      if (row < doc_len && grow >= 0 && grow < p.q_rows)
+        *reinterpret_cast<uint4*>(p.dq + (static_cast<long long>(grow) * p.heads_q + head) * kBwD + c) = make_uint4(0, 0, 0, 0);
+    }
+    return;
+  }
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
@@ -474,7 +494,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       int ks = 0;
       uint32_t kph = 0;
       for (int n = 0; n < num_iters && ok; ++n) {
-        const int krow = doc_start + (j_begin + n) * kBwB;
+        const int krow = doc_start + (j_begin + n) * kBwB - p.k_off;        // rows outside read as zero
         if (!mbar_wait(&k_empty[ks], kph ^ 1, p.status, kTimeoutEmptyBarrier)) { ok = false; break; }
         mbar_expect_tx(&k_full[ks], kBwTile);
         bw_load_tile(k_s + ks * kBwTile, &tmK, &k_full[ks], kv_head * kBwD, krow);
@@ -546,8 +566,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     for (int n = 0; n < num_iters && ok; ++n) {
       const int st = n & 1;
       const int col0 = (j_begin + n) * kBwB + 64 * w;
-      const int lim_hi = row_ok ? row - col0 : -1;
-      const int lim_lo = (p.window > 0) ? lim_hi - p.window : -1;
+      const int causal_hi = row_ok ? row - col0 : -1;
+      const int lim_hi = min(causal_hi, kcol_hi - 1 - col0);
+      const int lim_lo = max((p.window > 0) ? causal_hi - p.window : -1, kcol_lo - 1 - col0);
       ok = mbar_wait_poll(&s_full[st], (n >> 1) & 1, p.status, kTimeoutTmemFull);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -634,14 +655,20 @@ flash_bwd_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16*
 // ceil(len / 128).
 // Context-parallel form: q / o / d_o / lse / delta / dq hold only the global rows
 // [q_off, q_off + q_rows); k / v / dk / dv and cu_seqlens describe the complete sequence.
-PRB_API int prb_flash_bwd_slice(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+//
+// Block form (`prb_flash_bwd_block`): in addition k / v / dk / dv hold only the global rows [k_off, k_off + k_rows).
+// With o and lse the FINAL output and log-sum-exp of the rows (over all keys of all blocks), dq is the rows' partial
+// gradient from these keys and dk / dv are these keys' partial gradients from these rows; the caller sums the
+// partials. Every row of dq and every row of dk / dv is written (zeros where nothing is visible).
+PRB_API int prb_flash_bwd_block(const void* q, const void* k, const void* v, const void* o, const void* d_o,
                                 const float* lse, float* delta, void* dq, void* dk, void* dv, const int* cu_seqlens,
-                                int num_docs, int total_q, int q_off, int q_rows, int heads_q, int heads_kv,
-                                int head_dim, long long ld_q, long long ld_k, long long ld_v, long long ld_o,
-                                long long ld_do, long long ld_dk, long long ld_dv, float scale, int window,
-                                int max_blocks, int* status, void* stream_) {
+                                int num_docs, int total_q, int q_off, int q_rows, int k_off, int k_rows, int heads_q,
+                                int heads_kv, int head_dim, long long ld_q, long long ld_k, long long ld_v,
+                                long long ld_o, long long ld_do, long long ld_dk, long long ld_dv, float scale,
+                                int window, int max_blocks, int* status, void* stream_) {
   using namespace prb;
   if (q_off < 0 || q_rows <= 0 || q_off + q_rows > total_q) return -3;
+  if (k_off < 0 || k_rows <= 0 || k_off + k_rows > total_q) return -3;
   if (head_dim != kBwD || heads_q % heads_kv) return -2;
   if (total_q <= 0 || num_docs <= 0) return 0;
   if ((ld_q % 8) || (ld_k % 8) || (ld_v % 8) || (ld_do % 8) || (ld_dk % 8) || (ld_dv % 8)) return -4;
@@ -653,10 +680,10 @@ PRB_API int prb_flash_bwd_slice(const void* q, const void* k, const void* v, con
   rc = make_tmap_2d(&tmDO, d_o, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)q_rows, (uint64_t)heads_q * kBwD,
                     (uint64_t)ld_do, kBwB, 64, true);
   if (rc) return rc;
-  rc = make_tmap_2d(&tmK, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_q, (uint64_t)heads_kv * kBwD,
+  rc = make_tmap_2d(&tmK, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)k_rows, (uint64_t)heads_kv * kBwD,
                     (uint64_t)ld_k, kBwB, 64, true);
   if (rc) return rc;
-  rc = make_tmap_2d(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)total_q, (uint64_t)heads_kv * kBwD,
+  rc = make_tmap_2d(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)k_rows, (uint64_t)heads_kv * kBwD,
                     (uint64_t)ld_v, kBwB, 64, true);
   if (rc) return rc;
   const long long items = static_cast<long long>(q_rows) * heads_q;
@@ -665,6 +692,7 @@ PRB_API int prb_flash_bwd_slice(const void* q, const void* k, const void* v, con
   FaBwdParams p;
   p.cu_seqlens = cu_seqlens; p.num_docs = num_docs; p.total_q = total_q; p.heads_q = heads_q; p.heads_kv = heads_kv;
   p.q_off = q_off; p.q_rows = q_rows;
+  p.k_off = k_off; p.k_rows = k_rows;
   p.lse = lse; p.delta = delta;
   p.dq = reinterpret_cast<__nv_bfloat16*>(dq);
   p.dk = reinterpret_cast<__nv_bfloat16*>(dk); p.dv = reinterpret_cast<__nv_bfloat16*>(dv);
@@ -680,6 +708,17 @@ PRB_API int prb_flash_bwd_slice(const void* q, const void* k, const void* v, con
   flash_bwd_dkdv_kernel<<<dim3(max_blocks, heads_kv), kBwThreads, kBwSmem, stream>>>(tmQ, tmK, tmV, tmDO, p);
   flash_bwd_dq_kernel<<<dim3(max_blocks, heads_q), kBwThreads, kBwSmem, stream>>>(tmQ, tmK, tmV, tmDO, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+PRB_API int prb_flash_bwd_slice(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                                const float* lse, float* delta, void* dq, void* dk, void* dv, const int* cu_seqlens,
+                                int num_docs, int total_q, int q_off, int q_rows, int heads_q, int heads_kv,
+                                int head_dim, long long ld_q, long long ld_k, long long ld_v, long long ld_o,
+                                long long ld_do, long long ld_dk, long long ld_dv, float scale, int window,
+                                int max_blocks, int* status, void* stream_) {
+  return prb_flash_bwd_block(q, k, v, o, d_o, lse, delta, dq, dk, dv, cu_seqlens, num_docs, total_q, q_off, q_rows, 0,
+                             total_q, heads_q, heads_kv, head_dim, ld_q, ld_k, ld_v, ld_o, ld_do, ld_dk, ld_dv, scale,
+                             window, max_blocks, status, stream_);
 }
 
 // dq_acc is unused (kept in the signature for existing callers; may be null).

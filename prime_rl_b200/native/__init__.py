@@ -56,6 +56,11 @@ _CUDA_SIGNATURES = {
     "prb_ep_pull": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
     "prb_gemm_bf16_ext": [P, P, P, I, I, I, L, L, L, I, I, I, F, F, P, I, I, I, P, P, I, L, L, I, P, P],
     "prb_flash_fwd_slice": [P, P, P, P, P, P, I, I, I, I, I, I, I, L, L, L, L, F, I, I, P, P, P],
+    "prb_attn_merge": [P, P, P, P, L, I, P],
+    "prb_peer_copy": [P, P, L, I, P],
+    "prb_slot_pull_reduce": [P, L, L, P, I, P],
+    "prb_flash_fwd_block": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, L, L, L, L, F, I, I, P, P, P],
+    "prb_flash_bwd_block": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, L, L, L, L, L, L, L, F, I, I, P, P],
     "prb_flash_bwd_slice": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, L, L, L, L, L, L, L, F, I, I, P, P],
     "prb_flash_bwd": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, L, L, L, L, L, L, L, F, I, I, P, P],
     "prb_paged_decode": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P],

@@ -50,6 +50,60 @@ def flash_fwd(q, k, v, cu_seqlens, *, scale: float | None = None, window: int | 
     return out, lse
 
 
+def flash_fwd_block(q, k, v, cu_seqlens, total: int, q_offset: int, k_offset: int, *, scale: float | None = None,
+                    window: int | None = None):
+    """Partial attention of the global rows ``[q_offset, q_offset + Tq)`` over the keys ``[k_offset, k_offset + Tk)``
+    of a packed sequence of ``total`` tokens (``cu_seqlens`` describes the whole sequence; causal and document masks
+    by global position). Returns (out [Tq, Hq, 128] bf16, lse [Hq, Tq] fp32): rows that see none of the keys come
+    back as out = 0, lse = -inf. One step of the ring form of context parallelism (``merge_partial`` combines)."""
+    Tq, Hq, D = q.shape
+    Tk, Hkv = k.shape[0], k.shape[1]
+    assert D == 128 and q.dtype == torch.bfloat16
+    for t in (q, k, v):
+        assert t.stride(2) == 1 and t.stride(1) == D, "heads must be contiguous"
+    out = torch.empty(Tq, Hq, D, dtype=q.dtype, device=q.device)
+    lse = torch.empty(Hq, Tq, dtype=torch.float32, device=q.device)
+    num_docs = cu_seqlens.numel() - 1
+    max_pairs = (total + 255) // 256 + num_docs
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    status = rt.status_tensor(q.device)
+    rc = rt.lib().prb_flash_fwd_block(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                      cu_seqlens.data_ptr(), num_docs, int(total), int(q_offset), Tq, int(k_offset), Tk,
+                                      Hq, Hkv, D, q.stride(0), k.stride(0), v.stride(0), out.stride(0), float(scale),
+                                      int(window or 0), max_pairs, None, status.data_ptr(), rt.stream_ptr(q.device))
+    rt.check(rc, "prb_flash_fwd_block")
+    return out, lse
+
+
+def flash_bwd_block(dout, q, k, v, out, lse, cu_seqlens, total: int, q_offset: int, k_offset: int, *,
+                    scale: float | None = None, window: int | None = None):
+    """Partial gradients of one (row slice, key range) block: ``out`` / ``lse`` are the rows' FINAL output and
+    log-sum-exp over all keys. Returns (dq [Tq, Hq, 128], dk, dv [Tk, Hkv, 128]) in bf16; the caller sums the blocks."""
+    Tq, Hq, D = q.shape
+    Tk, Hkv = k.shape[0], k.shape[1]
+    assert D == 128 and q.dtype == torch.bfloat16
+    dout = dout.contiguous()
+    for t in (q, k, v, out, dout):
+        assert t.stride(2) == 1 and t.stride(1) == D, "heads must be contiguous"
+    dev = q.device
+    dq = torch.empty(Tq, Hq, D, dtype=q.dtype, device=dev)
+    dk = torch.zeros(Tk, Hkv, D, dtype=q.dtype, device=dev)
+    dv = torch.zeros(Tk, Hkv, D, dtype=q.dtype, device=dev)
+    delta = torch.empty(Hq, Tq, dtype=torch.float32, device=dev)
+    num_docs = cu_seqlens.numel() - 1
+    max_blocks = (total + 127) // 128 + num_docs
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    status = rt.status_tensor(dev)
+    rc = rt.lib().prb_flash_bwd_block(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(),
+                                      lse.data_ptr(), delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                      cu_seqlens.data_ptr(), num_docs, int(total), int(q_offset), Tq, int(k_offset), Tk,
+                                      Hq, Hkv, D, q.stride(0), k.stride(0), v.stride(0), out.stride(0), dout.stride(0),
+                                      dk.stride(0), dv.stride(0), float(scale), int(window or 0), max_blocks,
+                                      status.data_ptr(), rt.stream_ptr(dev))
+    rt.check(rc, "prb_flash_bwd_block")
+    return dq, dk, dv
+
+
 def flash_fwd_gather(q, k_full, v_full, peer_ptrs, cu_seqlens, cp_rank: int, cp_size: int, counters, *,
                      scale: float | None = None, window: int | None = None):
     """Context-parallel forward with the K / V exchange inside the kernel. ``k_full`` / ``v_full``

@@ -83,6 +83,20 @@ class CopyEnv(ReverseTextEnv):
         return lcs_ratio(completion[: len(task["payload"])], task["payload"])
 
 
+class LowTokenEnv(ReverseTextEnv):
+    """Dense, quickly learnable reward for runs from random weights (where no pretrained model can be had): the
+    fraction of completion tokens whose id lies in the lowest eighth of the vocabulary. A random policy starts near
+    0.125 and a working trainer / weight-sync loop raises it within tens of steps."""
+
+    name = "low-token"
+
+    def score(self, task, completion):
+        if not completion:
+            return 0.0
+        cut = max(1, self.vocab_size // 8)
+        return sum(1 for t in completion if t < cut) / len(completion)
+
+
 class CountUpEnv(Environment):
     """Two-turn episode: after the first completion the environment appends an observation
     token; reward counts completions that start with the token following the observation."""
@@ -113,7 +127,7 @@ class CountUpEnv(Environment):
                        policy_version=policy_version, metrics={"reward": reward})
 
 
-REGISTRY = {"reverse-text": ReverseTextEnv, "copy": CopyEnv, "count-up": CountUpEnv}
+REGISTRY = {"reverse-text": ReverseTextEnv, "copy": CopyEnv, "count-up": CountUpEnv, "low-token": LowTokenEnv}
 
 
 def load_environment(cfg) -> Environment:

@@ -568,6 +568,23 @@ class Orchestrator:
         m.update({f"watcher/{k}": v for k, v in self.watcher.stats.items()})
         return m
 
+    async def _serve_remaining_weight_updates(self, timeout: float | None = None) -> None:
+        """The last batches ship up to ``TARGET_LAG + 1`` trainer steps ahead of the weights. A trainer whose sender
+        waits for the receiver's acknowledgement (the in-memory transports) still offers the weights of every step
+        but the last one, so the watcher keeps answering until version ``max_steps - 1`` is live; leaving earlier
+        would park the trainer in its acknowledgement wait until that times out."""
+        c = self.config
+        if c.max_steps is None or getattr(c.weight_broadcast, "type", "filesystem") == "filesystem":
+            return
+        timeout = timeout if timeout is not None else float(getattr(c.weight_broadcast, "timeout", 600.0))
+        deadline = time.monotonic() + timeout
+        while self.policy.version < c.max_steps - 1:
+            if time.monotonic() > deadline:
+                self.logger.warning(f"stopping at policy v{self.policy.version}: the trainer did not offer the weights "
+                                    f"of step {c.max_steps - 2} within {timeout:.0f}s")
+                return
+            await asyncio.sleep(0.05)
+
     async def _metrics_loop(self, max_consecutive_failures: int = 30) -> None:
         """Polls the engines' metrics once a second and feeds the concurrency controller. A scrape
         that fails is logged and retried; after ``max_consecutive_failures`` in a row the task raises,
@@ -701,6 +718,7 @@ class Orchestrator:
                 if c.ckpt is not None and c.ckpt.interval and (self.step + 1) % c.ckpt.interval == 0:
                     self.save_ckpt(self.step)
                 self.step += 1
+            await self._serve_remaining_weight_updates()
         finally:
             # a teardown that hangs (an engine that never answers the aborts, a stuck transport) must not keep
             # the launcher waiting forever: after TEARDOWN_TIMEOUT_S the process ends itself

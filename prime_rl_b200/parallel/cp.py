@@ -18,6 +18,9 @@ Both run on ``torch.distributed`` collectives (NCCL / gloo) for the exchange and
 flash-attention kernels for the math (query-slice form for the all-gather path); per-token
 outputs (logprobs, entropy) are gathered back along the sequence for the loss.
 
+``ContextParallel(kv_exchange="ring" | "ring_p2p")`` replaces the all-gather of the ``ring`` style by a ring of K / V
+blocks with one partial attention per step, merged through the log-sum-exp (``parallel/ring_attn.py``).
+
 ``ContextParallel(fused_kv_gather=True)`` moves the forward K / V exchange of the ``ring`` style into
 the attention kernel: K and V live in a symmetric buffer, every rank writes its own chunk, and one
 extra warp per CTA of the flash-attention forward pulls the chunks of the lower ranks over NVLink
@@ -151,9 +154,11 @@ class _FusedGatherAttention(torch.autograd.Function):
 
 class ContextParallel:
     def __init__(self, group, cp: int, rank: int, style: str = "ring", p2p_all_to_all: bool = False,
-                 fused_kv_gather: bool = False, layout: str | None = None):
+                 fused_kv_gather: bool = False, layout: str | None = None, kv_exchange: str = "nccl"):
         self.group, self.cp, self.rank, self.style = group, cp, rank, style
         self.fused_kv_gather, self._kv = fused_kv_gather, None
+        # "ring" / "ring_p2p": step-by-step K / V blocks with log-sum-exp merging (parallel/ring_attn.py)
+        self.kv_exchange, self._ring_state = kv_exchange, None
         # the in-kernel K / V gather and the Ulysses exchange address contiguous chunks
         self.layout = layout or ("zigzag" if style == "ring" and not fused_kv_gather else "contiguous")
         if self.layout == "zigzag" and (style != "ring" or fused_kv_gather):
@@ -241,8 +246,26 @@ class ContextParallel:
             return self._ulysses(q, k, v, seq, window, sinks, backend)
         return self._gather_kv(q, k, v, seq, window, sinks, backend)
 
+    def _ring(self, k):
+        """Exchange object of the ring form for K / V chunks shaped like ``k``."""
+        from .ring_attn import _RelayRing, _SymmRing
+
+        if self.kv_exchange == "ring_p2p" and k.is_cuda and k.dtype == torch.bfloat16:
+            key = tuple(k.shape)
+            if self._ring_state is None or self._ring_state[0] != key:
+                if self._ring_state is not None:
+                    self._ring_state[1].close()
+                self._ring_state = (key, _SymmRing(self, *key, k.device))
+            return self._ring_state[1]
+        return _RelayRing(self)
+
     def _gather_kv(self, q, k, v, seq, window, sinks, backend):
         Tl, T = q.shape[0], seq.full_len
+        if self.kv_exchange in ("ring", "ring_p2p") and sinks is None:
+            from .ring_attn import RingAttention
+
+            cu = seq.full_cu_seqlens.to(torch.int32) if q.is_cuda else seq.full_cu_seqlens
+            return RingAttention.apply(q, k.contiguous(), v.contiguous(), self, cu, T, window)
         if (self.fused_kv_gather and q.is_cuda and sinks is None and q.dtype == torch.bfloat16 and q.shape[-1] == 128
                 and self.cp <= 8):
             return _FusedGatherAttention.apply(q, k.contiguous(), v.contiguous(), self,

@@ -174,7 +174,8 @@ class RLTrainer:
             from ...parallel.cp import ContextParallel
 
             self.cp_ctx = ContextParallel(dims.group("cp"), dims.cp, self.cp_rank, style=self.config.model.cp_style,
-                                          fused_kv_gather=self.config.model.cp_kv_exchange == "p2p")
+                                          fused_kv_gather=self.config.model.cp_kv_exchange == "p2p",
+                                          kv_exchange=self.config.model.cp_kv_exchange)
         if dims.ep_enabled:
             from ...parallel.ep import install_expert_parallel
 

@@ -32,7 +32,7 @@ def main() -> int:
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     group = dist.group.WORLD
-    base = ContextParallel(group, world, rank, style="ring")
+    base = ContextParallel(group, world, rank, style="ring", layout="contiguous")      # the layout of the fused path
     fused = ContextParallel(group, world, rank, style="ring", fused_kv_gather=True)
 
     def setup(Tl, Hq, Hkv, lens):

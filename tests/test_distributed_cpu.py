@@ -85,14 +85,18 @@ def test_dp2_and_ep2_match_single_process(tmp_path, free_port):
 
 
 @pytest.mark.slow
-@pytest.mark.parametrize("style", ["ring", "ulysses"])
+@pytest.mark.parametrize("style", ["ring", "ulysses", "ring:ring"])
 def test_cp2_matches_single_process(tmp_path, free_port, style):
-    """Context-parallel ranks of one replica see the same rows, so CP=2 must reproduce CP=1."""
+    """Context-parallel ranks of one replica see the same rows, so CP=2 must reproduce CP=1 ("ring:ring": K / V blocks
+    passed rank to rank, partial attention per step merged through the log-sum-exp, dK / dV returned to the owners)."""
     base = json.loads(json.dumps(BASE))
     base["model"]["name"] = "tiny-qwen3"
     single = _run(tmp_path, free_port, 1, base)[0]
     cfg = json.loads(json.dumps(base))
+    style, _, exchange = style.partition(":")
     cfg["model"].update(cp=2, cp_style=style)
+    if exchange:
+        cfg["model"]["cp_kv_exchange"] = exchange
     cp2 = _run(tmp_path, free_port + 1, 2, cfg)
     assert cp2[0]["wsum"] == pytest.approx(cp2[1]["wsum"], rel=1e-9)
     assert cp2[0]["wabs"] == pytest.approx(single["wabs"], rel=1e-5)

@@ -96,6 +96,16 @@ def test_context_parallel_attention_with_in_kernel_kv_gather():
     assert out.returncode == 0 and "CP_FUSED_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
 
 
+def test_ring_attention_with_log_sum_exp_merging():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", CP_SELFTEST_TIMING="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", "29543", "-m", "tests.distributed.ring_attention"]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert out.returncode == 0 and "RING_ATTN_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
+
+
 def test_sharded_optimizer_with_peer_memory_collectives():
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

@@ -599,6 +599,69 @@ def test_flash_query_slices_sum_to_full_attention(lens, window, cp):
         assert rel < 2e-2, f"{name}: relative error {rel:.4f}"
 
 
+@pytest.mark.parametrize("lens,window,chunks", [([1024], None, 4), ([300, 77, 1000, 159], None, 4), ([700, 300, 200], 200, 6),
+                                                 ([2048], None, 8), ([130, 126], None, 2)])
+def test_flash_key_blocks_merge_to_full_attention(lens, window, chunks):
+    """Ring form of context parallelism on one device: every (query chunk, key chunk) block computed on its own
+    (chunk edges fall inside 128-row tiles and inside documents), partial results merged through the log-sum-exp
+    give the full attention; block gradients taken with the final output / log-sum-exp add up to the full ones."""
+    from prime_rl_b200.ops import attention as A, flash_native
+    from prime_rl_b200.parallel import ring_attn
+    T, Hq, Hkv, D = sum(lens), 4, 2, 128
+    assert T % chunks == 0
+    c = T // chunks
+    q, k, v = _rand(T, Hq, D), _rand(T, Hkv, D), _rand(T, Hkv, D)
+    cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
+    cu[1:] = torch.tensor(lens).cumsum(0)
+    cu = cu.to(DEV)
+    do = _rand(T, Hq, D)
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref = A.attention_ref(qr, kr, vr, cu, window=window)
+    ref.backward(do.float())
+
+    acc = torch.zeros(T, Hq, D, device=DEV)
+    lse = torch.empty(Hq, T, device=DEV)
+    for qi in range(chunks):
+        rows = slice(qi * c, (qi + 1) * c)
+        a = acc[rows]
+        l = torch.full((Hq, c), float("-inf"), device=DEV)
+        for ki in range(chunks):            # blocks above the diagonal come back empty and leave the rows unchanged
+            keys = slice(ki * c, (ki + 1) * c)
+            part, lp = flash_native.flash_fwd_block(q[rows], k[keys], v[keys], cu, T, qi * c, ki * c, window=window)
+            if ki > qi:
+                assert torch.isinf(lp).all() and float(part.float().abs().max()) == 0.0
+            else:
+                want, want_lse, _ = ring_attn.block_fwd_ref(q[rows], k[keys], v[keys], cu.long(), T, qi * c, ki * c, window)
+                seen = ~torch.isinf(want_lse)
+                assert torch.equal(seen, ~torch.isinf(lp))
+                _close(lp[seen], want_lse[seen], atol=2e-2, rtol=2e-2)
+                _close(part, want, atol=3e-2, rtol=3e-2)
+            ring_attn.merge_partial(a, l, part, lp)
+        lse[:, rows] = l
+    rt.check_status()
+    _close(acc, ref, atol=3e-2, rtol=3e-2)
+    full_out, full_lse = flash_native.flash_fwd(q, k, v, cu, window=window)
+    _close(lse, full_lse, atol=2e-2, rtol=2e-2)
+
+    out = acc.to(torch.bfloat16)
+    dq = torch.zeros(T, Hq, D, device=DEV)
+    dk = torch.zeros(T, Hkv, D, device=DEV)
+    dv = torch.zeros(T, Hkv, D, device=DEV)
+    for qi in range(chunks):
+        rows = slice(qi * c, (qi + 1) * c)
+        for ki in range(qi + 1):
+            keys = slice(ki * c, (ki + 1) * c)
+            a, b, e = flash_native.flash_bwd_block(do[rows], q[rows], k[keys], v[keys], out[rows],
+                                                   lse[:, rows].contiguous(), cu, T, qi * c, ki * c, window=window)
+            dq[rows] += a.float()
+            dk[keys] += b.float()
+            dv[keys] += e.float()
+    rt.check_status()
+    for got, want, name in ((dq, qr.grad, "dq"), (dk, kr.grad, "dk"), (dv, vr.grad, "dv")):
+        rel = (got - want).norm() / want.norm()
+        assert rel < 2e-2, f"{name}: relative error {rel:.4f}"
+
+
 @pytest.mark.parametrize("Hq,Hkv", [(32, 4), (8, 8), (16, 4)])
 @pytest.mark.parametrize("splits", [1, 3])
 def test_paged_decode(Hq, Hkv, splits):
