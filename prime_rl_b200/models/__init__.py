@@ -2,4 +2,5 @@
 
 from .config import PRESETS, ModelArch, resolve_arch  # noqa: F401
 from .layers import SeqInfo  # noqa: F401
-from .model import CausalLM, apply_lora, build_model, freeze_router  # noqa: F401
+from .model import (CausalLM, apply_fp8_training, apply_lora, build_model, freeze_router,  # noqa: F401
+                    setup_quantization)

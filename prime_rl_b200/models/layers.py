@@ -126,6 +126,7 @@ class Linear(nn.Module):
         self.lora: LoRAAdapter | None = None
         self.std = std
         self.fp8: tuple[torch.Tensor, torch.Tensor] | None = None    # (e4m3 weight, 128 x 128 scales): inference only
+        self.fp8_train = False      # forward product and input gradient in block-scaled fp8 (model.quantization)
 
     def reset_parameters(self):
         _init(self.weight, self.std)
@@ -168,6 +169,10 @@ class Linear(nn.Module):
         if self.lora is not None:
             y = lora_ops.lora_linear(x, self.weight, self.lora.lora_A, list(self.lora.lora_B), self.lora.scale)
             return y if self.bias is None else y + self.bias
+        if self.fp8_train and torch.is_grad_enabled() and x.dtype == self.weight.dtype:
+            from ..ops import fp8 as fp8_ops
+
+            return fp8_ops.fp8_linear(x, self.weight, self.bias)
         return ops.linear(x, self.weight, self.bias)
 
 
@@ -326,6 +331,7 @@ class GroupedExperts(nn.Module):
         self.lora_gate_up: LoRAAdapter | None = None
         self.lora_down: LoRAAdapter | None = None
         self.fp8: dict[str, tuple[torch.Tensor, torch.Tensor]] | None = None   # inference-only fp8 copies
+        self.fp8_train = False      # both projections' forward products and input gradients in block-scaled fp8
 
     def reset_parameters(self):
         _init(self.gate_up_proj, self.arch.initializer_range)
@@ -439,6 +445,10 @@ class GroupedExperts(nn.Module):
             l = self.lora_gate_up
             gu = lora_ops.lora_grouped_linear(xp, self.gate_up_proj, l.lora_A, list(l.lora_B), l.scale, block_expert,
                                               expert_offset)
+        elif self.fp8_train and torch.is_grad_enabled() and block_ready is None:
+            from ..ops import fp8 as fp8_ops
+
+            gu = fp8_ops.fp8_grouped_linear(xp, self.gate_up_proj, block_expert, expert_offset)
         else:
             gu = ops.grouped_linear(xp, self.gate_up_proj, block_expert, expert_offset, block_ready=block_ready)
         gu = self._biased(gu, self.gate_up_proj_bias, block_expert)
@@ -452,6 +462,10 @@ class GroupedExperts(nn.Module):
             l = self.lora_down
             y = lora_ops.lora_grouped_linear(h, self.down_proj, l.lora_A, list(l.lora_B), l.scale, block_expert,
                                              expert_offset, out=out)
+        elif self.fp8_train and torch.is_grad_enabled() and out is None:
+            from ..ops import fp8 as fp8_ops
+
+            y = fp8_ops.fp8_grouped_linear(h, self.down_proj, block_expert, expert_offset)
         else:
             y = ops.grouped_linear(h, self.down_proj, block_expert, expert_offset, out=out)
         return self._biased(y, self.down_proj_bias, block_expert)

@@ -186,6 +186,46 @@ def _matches(name: str, patterns: list[str]) -> bool:
 _FUSED_MEMBERS = {"qkv_proj": ["q_proj", "k_proj", "v_proj"], "gate_up_proj": ["gate_proj", "up_proj"]}
 
 
+def apply_fp8_training(model: CausalLM, ignore_patterns: list[str] | None = None, cache_weights: bool = True) -> list[str]:
+    """Switches the projections (and expert stacks) whose name matches none of ``ignore_patterns`` (regular
+    expressions, searched in the module name) to block-scaled fp8 for the forward product and the input gradient
+    (``ops/fp8.py``); modules with an adapter, or with a dimension that is not a multiple of 16, keep bf16.
+    Reference: src/prime_rl/trainer/models/layers/fp8_linear.py (module swap by name filter). Returns the names."""
+    import re
+
+    from ..ops import fp8 as fp8_ops
+
+    fp8_ops.CACHE_WEIGHTS = cache_weights
+    pats = [re.compile(p) for p in (ignore_patterns or [])]
+    done: list[str] = []
+    for name, mod in model.named_modules():
+        if any(p.search(name) for p in pats):
+            continue
+        if isinstance(mod, Linear) and mod.lora is None and mod.weight.shape[0] % 16 == 0 and mod.weight.shape[1] % 16 == 0:
+            mod.fp8_train = True
+            done.append(name)
+        elif isinstance(mod, GroupedExperts) and mod.lora_gate_up is None and mod.lora_down is None and \
+                all(d % 16 == 0 for d in (*mod.gate_up_proj.shape[1:], *mod.down_proj.shape[1:])):
+            mod.fp8_train = True
+            done.append(name)
+    return done
+
+
+def setup_quantization(model: CausalLM, mc, logger=None) -> list[str]:
+    """``model.quantization`` of the trainer config: fp8 = block-scaled e4m3 (1 x 128 activation groups, 128 x 128
+    weight blocks) for the forward products and input gradients of the projections outside ``ignore_patterns``. The
+    MXFP8 recipes (UE8M0 scales over groups of 32) are not built."""
+    q = mc.quantization
+    if q is None:
+        return []
+    if q.type != "fp8":
+        raise NotImplementedError(f"model.quantization.type = '{q.type}' is not built (block-scaled 'fp8' is)")
+    names = apply_fp8_training(model, q.ignore_patterns, cache_weights=getattr(mc, "zero_stage", 2) != 3)
+    if logger is not None:
+        logger.info(f"fp8 training: forward product and input gradient in block-scaled e4m3 on {len(names)} modules")
+    return names
+
+
 def apply_lora(model: CausalLM, rank: int, alpha: float, target_modules: list[str],
                modules_to_save: list[str] | None = None, seed: int = 0, num_adapters: int = 1) -> list[str]:
     """Freezes the base model and attaches adapters to every targeted projection. A fused

@@ -1,6 +1,12 @@
 """Block-scaled fp8 (e4m3) linear algebra: 1 x 128 activation scales, 128 x 128 weight scales
 (``csrc/gemm_fp8.cu``; weights are quantised with ``models/fp8.py`` or in flight by the weight
-push). Inference only: there is no backward."""
+push).
+
+Training (``fp8_linear`` / ``fp8_grouped_linear``; reference: src/prime_rl/trainer/models/layers/fp8_linear.py:18-81,
+layers/fp8_grouped_gemm.py:97-215): the forward product and the input gradient run on the fp8 kernel, with the
+activations (and the incoming gradient) quantised per token in 1 x 128 groups along the contraction and the weight
+(for the input gradient: its transpose) in 128 x 128 blocks; the weight gradient stays a bf16 product that adds into
+the fp32 gradient accumulator. The fp8 copies of a weight and of its transpose are made once per optimizer step."""
 
 from __future__ import annotations
 
@@ -73,3 +79,113 @@ def fp8_gemm(aq, sa, bq, sb, *, block_expert: torch.Tensor | None = None, out: t
                                    rt.stream_ptr(aq.device)),
              "prb_gemm_fp8")
     return out
+
+
+# ------------------------------------------------------------------------------------------ training
+_WEIGHT_EPOCH = 0
+_WEIGHT_CACHE: dict[int, tuple] = {}
+CACHE_WEIGHTS = True        # False: quantise at every use (parameter sharding: a whole-model fp8 copy would undo it)
+
+
+def bump_weight_epoch() -> None:
+    """Called after every optimizer step: the fp8 copies of the weights are stale."""
+    global _WEIGHT_EPOCH
+    _WEIGHT_EPOCH += 1
+    _WEIGHT_CACHE.clear()
+
+
+def _quantize_weight(w: torch.Tensor):
+    from ..models.fp8 import quantize_to_fp8_blockwise
+
+    q, s = quantize_to_fp8_blockwise(w.detach())
+    return q.view(torch.uint8).contiguous(), s.contiguous()
+
+
+def weight_fp8(w: torch.Tensor, transposed: bool):
+    """(e4m3 as uint8, 128 x 128 scales) of ``w`` ([N, K] or [E, N, K]) or of its transpose over the last two dims."""
+    key = (id(w), transposed)
+    hit = _WEIGHT_CACHE.get(key) if CACHE_WEIGHTS else None
+    if hit is not None and hit[0] == _WEIGHT_EPOCH and hit[1] == w.data_ptr():
+        return hit[2], hit[3]
+    src = w.detach().transpose(-1, -2).contiguous() if transposed else w.detach()
+    q, s = _quantize_weight(src.to(torch.bfloat16) if src.is_cuda else src)
+    if CACHE_WEIGHTS:
+        _WEIGHT_CACHE[key] = (_WEIGHT_EPOCH, w.data_ptr(), q, s)
+    return q, s
+
+
+class _FP8Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):
+        from .matmul import grad_accumulator
+
+        ctx.save_for_backward(x, w)
+        ctx.grad_acc = grad_accumulator(w) if w.requires_grad else None
+        x2 = x.reshape(-1, x.shape[-1])
+        xq, xs = quantize_act(x2)
+        wq, ws = weight_fp8(w, False)
+        return fp8_gemm(xq, xs, wq, ws).to(x.dtype).reshape(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .matmul import gemm
+
+        x, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            gq, gs = quantize_act(dy2)
+            wtq, wts = weight_fp8(w, True)
+            dx = fp8_gemm(gq, gs, wtq, wts).to(x.dtype).reshape(x.shape)
+        if ctx.needs_input_grad[1]:
+            x2 = x.reshape(-1, x.shape[-1])
+            if ctx.grad_acc is not None and w.shape[1] % 4 == 0:
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=ctx.grad_acc, beta=1.0)
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype)
+        return dx, dw
+
+
+def fp8_linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """y = x @ w^T with the forward product and the input gradient in block-scaled fp8."""
+    y = _FP8Linear.apply(x if x.is_contiguous() else x.contiguous(), w)
+    return y if bias is None else y + bias.to(y.dtype)
+
+
+class _FP8GroupedLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, block_expert, expert_offset):
+        from .matmul import grad_accumulator
+
+        ctx.save_for_backward(x, w, block_expert, expert_offset)
+        ctx.grad_acc = grad_accumulator(w) if w.requires_grad else None
+        xq, xs = quantize_act(x)
+        wq, ws = weight_fp8(w, False)
+        return fp8_gemm(xq, xs, wq, ws, block_expert=block_expert).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .matmul import grouped_wgrad
+
+        x, w, block_expert, expert_offset = ctx.saved_tensors
+        if not dy.is_contiguous():
+            dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            gq, gs = quantize_act(dy)
+            wtq, wts = weight_fp8(w, True)
+            dx = fp8_gemm(gq, gs, wtq, wts, block_expert=block_expert).to(x.dtype)
+        if ctx.needs_input_grad[1]:
+            if ctx.grad_acc is not None and w.shape[2] % 4 == 0:
+                grouped_wgrad(dy, x, expert_offset, w.shape[0], out=ctx.grad_acc, beta=1.0)
+            else:
+                dw = grouped_wgrad(dy, x, expert_offset, w.shape[0])
+        return dx, dw, None, None
+
+
+def fp8_grouped_linear(x, w, block_expert, expert_offset):
+    """Per-expert y = x @ w[e]^T over 128-row blocks (``ops.grouped_linear``) with the forward product and the input
+    gradient in block-scaled fp8."""
+    return _FP8GroupedLinear.apply(x, w, block_expert, expert_offset)

@@ -130,6 +130,23 @@ def bench_fp8(timer, args, dev):
     _report(f"fp8 block-scaled gemm {M}x{N}x{K}", timer(lambda: fp8.fp8_gemm(xq, xs, wq, ws)), flops=2 * M * N * K)
     _report(f"activation quantiser {M}x{K} (bf16 -> e4m3 + 1x128 scales)", timer(lambda: fp8.quantize_act(x)),
             bytes_=M * K * 3)
+    # training: forward + input gradient of one projection, bf16 products against the fp8 path (quantisers included;
+    # the fp8 copies of the weight and of its transpose are made once per optimizer step and are not timed)
+    from .matmul import linear
+
+    xg = x.clone().requires_grad_()
+    wg = w.clone().requires_grad_(False)
+    dy = torch.randn(M, N, device=dev).bfloat16()
+
+    def step(fn):
+        y = fn(xg, wg)
+        torch.autograd.grad(y, xg, dy)
+
+    fp8.bump_weight_epoch()
+    fp8.weight_fp8(wg, False), fp8.weight_fp8(wg, True)
+    _report(f"linear fwd + dgrad {M}x{N}x{K}, bf16", timer(lambda: step(linear)), flops=4 * M * N * K)
+    _report(f"linear fwd + dgrad {M}x{N}x{K}, fp8 (with activation / gradient quantisers)",
+            timer(lambda: step(fp8.fp8_linear)), flops=4 * M * N * K)
     # decode-shaped grouped experts: 256 tokens x top-8 over 128 experts (weight-bandwidth bound)
     E, H, I = 128, 2048, 768
     P = E * 128

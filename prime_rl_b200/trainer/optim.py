@@ -422,6 +422,9 @@ class FlatOptimizer:
         lr = self.lr
         self.step_count += 1
         t = self.step_count
+        from ..ops import fp8 as fp8_ops
+
+        fp8_ops.bump_weight_epoch()          # fp8 copies of the weights (fp8 training) are stale after this step
         max_norm = c.max_norm if c.max_norm is not None else 0.0
         coef, norm = optim_ops.clip_coef(self._global_sumsq(), max_norm)
         self.last_grad_norm = norm

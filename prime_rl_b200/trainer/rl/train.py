@@ -78,6 +78,9 @@ class RLTrainer:
                                  mc.lora.modules_to_save, num_adapters=mc.lora.num_adapters)
             self.multi_lora = mc.lora.num_adapters > 1
             self.logger.info(f"LoRA r={mc.lora.rank} x {mc.lora.num_adapters} on {len(adapted)} modules")
+        from ...models import setup_quantization
+
+        setup_quantization(self.model, mc, self.logger)
         if mc.freeze_moe_router:
             freeze_router(self.model)
         if mc.ac is not None:

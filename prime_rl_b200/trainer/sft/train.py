@@ -47,6 +47,9 @@ class SFTTrainer:
             load_hf_checkpoint(self.model, p)
         if mc.lora is not None:
             apply_lora(self.model, mc.lora.rank, mc.lora.alpha, mc.lora.target_modules, mc.lora.modules_to_save)
+        from ...models import setup_quantization
+
+        setup_quantization(self.model, mc, self.logger)
         if mc.ac is not None:
             self.model.ac_every = mc.ac.freq
             if mc.ac.mode == "selective":

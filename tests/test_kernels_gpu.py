@@ -1254,3 +1254,41 @@ def test_weight_gradient_accumulation_through_tma_reduce_adds():
     rt.check_status()
     _close(acc, ref, atol=0.5, rtol=1e-2)
     assert torch.equal(acc[1], torch.full((M, N), 2.0, device=DEV))
+
+
+@pytest.mark.gpu
+def test_fp8_training_linear_and_grouped_linear_on_the_fp8_kernel():
+    """Forward product and input gradient through the block-scaled fp8 kernel stay within e4m3 accuracy of the bf16
+    products; the weight gradient (bf16 product into the fp32 accumulator) is the exact one."""
+    from prime_rl_b200.ops import fp8 as F
+    from prime_rl_b200 import ops
+
+    torch.manual_seed(3)
+    F.bump_weight_epoch()
+    x = _rand(1000, 2048).requires_grad_()
+    w = (_rand(1536, 2048) * 0.05).requires_grad_()
+    dy = _rand(1000, 1536)
+    y = F.fp8_linear(x, w)
+    gx, gw = torch.autograd.grad(y, (x, w), dy)
+    ref = x.float() @ w.float().t()
+    rx, rw = torch.autograd.grad(ref, (x, w), dy.float())
+    rt.check_status()
+    for got, want, tol in ((y, ref, 0.06), (gx, rx, 0.06), (gw, rw, 0.01)):
+        rel = float((got.float() - want.float()).norm() / want.float().norm())
+        assert rel < tol, rel
+
+    E, N, K = 4, 768, 2048
+    block_expert = torch.tensor([0, 0, 1, 3, 3, 3, -1], dtype=torch.int32, device=DEV)
+    expert_offset = torch.tensor([0, 256, 384, 384, 768], dtype=torch.int32, device=DEV)
+    xp = _rand(7 * 128, K).requires_grad_()
+    we = (_rand(E, N, K) * 0.05).requires_grad_()
+    dyp = _rand(7 * 128, N)
+    dyp[768:] = 0
+    yp = F.fp8_grouped_linear(xp, we, block_expert, expert_offset)
+    gxp, gwe = torch.autograd.grad(yp, (xp, we), dyp)
+    yr = ops.grouped_linear(xp, we, block_expert, expert_offset)
+    rxp, rwe = torch.autograd.grad(yr, (xp, we), dyp)
+    rt.check_status()
+    for got, want, tol in ((yp[:768], yr[:768], 0.06), (gxp[:768], rxp[:768], 0.06), (gwe, rwe, 0.01)):
+        rel = float((got.float() - want.float()).norm() / want.float().norm())
+        assert rel < tol, rel
