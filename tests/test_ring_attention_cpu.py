@@ -75,3 +75,18 @@ def test_ring_pairs_are_balanced_in_the_zigzag_layout():
             assert per_step[0] == 3 and all(n == 2 for n in per_step[1:])
             counts.append(sum(per_step))
         assert len(set(counts)) == 1
+
+
+@pytest.mark.slow
+def test_ring_attention_on_four_cpu_ranks_matches_the_all_gather_path(free_port):
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=str(root))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "4", "--master-addr",
+           "127.0.0.1", "--master-port", str(free_port), "-m", "tests.distributed.ring_attention_cpu"]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=root)
+    assert out.returncode == 0 and "RING_CPU_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
