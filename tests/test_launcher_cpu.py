@@ -1,5 +1,6 @@
 """The ``rl`` launcher as real processes on CPU: inference server, orchestrator and trainer started by
-``entrypoints/rl.py``, weights broadcast in memory (gloo), three steps, clean exit with nothing left running."""
+``entrypoints/rl.py``, weights broadcast in memory (gloo), eight steps (the orchestrator ships its last batches ahead of the trainer and must
+keep answering the trainer's weight offers until the last one), clean exit with nothing left running."""
 
 import os
 import subprocess
@@ -15,12 +16,12 @@ ROOT = Path(__file__).resolve().parents[1]
 def test_rl_launcher_runs_three_processes_to_completion(tmp_path, free_port):
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=str(ROOT))
     cmd = [sys.executable, "-m", "prime_rl_b200.entrypoints.rl", "@", str(ROOT / "examples" / "rl.toml"),
-           "--output-dir", str(tmp_path), "--max-steps", "3", "--inference.server.port", str(free_port),
+           "--output-dir", str(tmp_path), "--max-steps", "8", "--inference.server.port", str(free_port),
            "--weight-broadcast.type", "nccl", "--weight-broadcast.port", str(free_port + 7)]
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     logs = {p.name: p.read_text() for p in tmp_path.rglob("*.log")}
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:] + "".join(f"\n== {k}\n{v[-1500:]}" for k, v in logs.items())
     assert "trainer and orchestrator finished" in r.stdout
     orch, trainer = logs["orchestrator.log"], logs["trainer.log"]
-    assert all(f"step {s} |" in orch for s in range(3)) and "policy v2" in orch     # the weights of step 1 arrived
-    assert all(f"step {s} |" in trainer for s in range(3))
+    assert all(f"step {s} |" in orch for s in range(8)) and "policy v6" in orch     # the weights of step 5 arrived
+    assert all(f"step {s} |" in trainer for s in range(8))
