@@ -197,10 +197,11 @@ moe_plan_kernel(const int* __restrict__ counts, int* __restrict__ expert_offset,
 
 __global__ void __launch_bounds__(256)
 moe_scatter_kernel(const int* __restrict__ topk_idx, const int* __restrict__ expert_offset, int* __restrict__ cursor,
-                   int* __restrict__ slot, int* __restrict__ row_src, long long n /* T*k */) {
+                   int* __restrict__ slot, int* __restrict__ row_src, long long n /* T*k */, int e_lo, int E) {
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= n) return;
-  const int e = topk_idx[i];
+  const int e = topk_idx[i] - e_lo;          // experts outside [e_lo, e_lo + E) live on another rank
+  if (e < 0 || e >= E) { slot[i] = -1; return; }
   const int pos = expert_offset[e] + atomicAdd(&cursor[e], 1);
   slot[i] = pos;
   row_src[pos] = static_cast<int>(i);
@@ -210,7 +211,7 @@ moe_scatter_kernel(const int* __restrict__ topk_idx, const int* __restrict__ exp
 // order, so that the position of a pair inside its expert does not depend on thread timing.
 __global__ void __launch_bounds__(256)
 moe_scatter_sorted_kernel(const int* __restrict__ topk_idx, const int* __restrict__ expert_offset,
-                          int* __restrict__ slot, int* __restrict__ row_src, long long n) {
+                          int* __restrict__ slot, int* __restrict__ row_src, long long n, int e_lo) {
   const int e = blockIdx.x;
   __shared__ int s_base;
   __shared__ int s_warp[8];
@@ -218,7 +219,7 @@ moe_scatter_sorted_kernel(const int* __restrict__ topk_idx, const int* __restric
   __syncthreads();
   for (long long i0 = 0; i0 < n; i0 += blockDim.x) {
     const long long i = i0 + threadIdx.x;
-    const bool hit = i < n && topk_idx[i] == e;
+    const bool hit = i < n && topk_idx[i] - e_lo == e;
     const unsigned ballot = __ballot_sync(0xffffffffu, hit);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) s_warp[warp] = __popc(ballot);
@@ -349,7 +350,7 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ p, const int* __restrict__ 
     int sl[kMaxTopK];
     float ww[kMaxTopK];
     for (int j = 0; j < k; ++j) {
-      sl[j] = slot[t * k + j];
+      sl[j] = slot[t * k + j];               // < 0: the pair's expert lives on another rank (its term comes from there)
       ww[j] = w ? w[t * k + j] : 1.f;
     }
     // blockIdx.y splits the columns when there are few tokens (decode), so that the gather is spread over the SMs
@@ -362,6 +363,7 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ p, const int* __restrict__ 
         acc[4] = f2.x; acc[5] = f2.y; acc[6] = f3.x; acc[7] = f3.y;
       }
       for (int j = 0; j < k; ++j) {
+        if (sl[j] < 0) continue;
         const uint4 a = reinterpret_cast<const uint4*>(p + static_cast<long long>(sl[j]) * cols)[v];
         float2 f0 = unpack_bf16(a.x), f1 = unpack_bf16(a.y), f2 = unpack_bf16(a.z), f3 = unpack_bf16(a.w);
         acc[0] += ww[j] * f0.x; acc[1] += ww[j] * f0.y; acc[2] += ww[j] * f1.x; acc[3] += ww[j] * f1.y;
@@ -427,22 +429,35 @@ PRB_API int prb_router_topk(const float* logits, const float* sel_bias, const in
 // Builds expert_offset[E+1], block_expert[max_blocks], slot[T*k], row_src[max_blocks*128]
 // from topk_idx and counts. row_src is filled with -1 first. `deterministic` selects the
 // order-preserving scatter.
-PRB_API int prb_moe_plan(const int* topk_idx, const int* counts, int* expert_offset, int* block_expert, int* cursor,
-                         int* total_rows, int* slot, int* row_src, long long T, int E, int k, int max_blocks,
-                         int deterministic, void* stream) {
-  if (E > kMaxExperts) return -1;
+//
+// Range form: this rank owns the E experts [e_lo, e_lo + E) of a larger set. `topk_idx` holds global ids, `counts`
+// points at the owned experts' counts; pairs of other experts get slot = -1 and no row (the combine skips them),
+// `block_expert` holds local ids (0 .. E-1).
+PRB_API int prb_moe_plan_range(const int* topk_idx, const int* counts, int* expert_offset, int* block_expert,
+                               int* cursor, int* total_rows, int* slot, int* row_src, long long T, int E, int k,
+                               int max_blocks, int deterministic, int e_lo, void* stream) {
+  if (E > kMaxExperts || E <= 0 || e_lo < 0) return -1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   cudaMemsetAsync(row_src, 0xff, sizeof(int) * static_cast<size_t>(max_blocks) * 128, s);
   moe_plan_kernel<<<1, 512, 0, s>>>(counts, expert_offset, block_expert, cursor, total_rows, E, max_blocks);
   const long long n = T * k;
   if (n > 0) {
-    if (deterministic)
-      moe_scatter_sorted_kernel<<<E, 256, 0, s>>>(topk_idx, expert_offset, slot, row_src, n);
-    else
+    if (deterministic) {
+      cudaMemsetAsync(slot, 0xff, sizeof(int) * static_cast<size_t>(n), s);       // pairs no CTA claims stay at -1
+      moe_scatter_sorted_kernel<<<E, 256, 0, s>>>(topk_idx, expert_offset, slot, row_src, n, e_lo);
+    } else {
       moe_scatter_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(topk_idx, expert_offset, cursor, slot,
-                                                                               row_src, n);
+                                                                               row_src, n, e_lo, E);
+    }
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+PRB_API int prb_moe_plan(const int* topk_idx, const int* counts, int* expert_offset, int* block_expert, int* cursor,
+                         int* total_rows, int* slot, int* row_src, long long T, int E, int k, int max_blocks,
+                         int deterministic, void* stream) {
+  return prb_moe_plan_range(topk_idx, counts, expert_offset, block_expert, cursor, total_rows, slot, row_src, T, E, k,
+                            max_blocks, deterministic, 0, stream);
 }
 
 PRB_API int prb_moe_gather_rows(const void* x, const int* row_src, const float* w, void* out, long long max_rows,
