@@ -388,6 +388,10 @@ moe_combine_bwd_w_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat
        i += static_cast<long long>(gridDim.x) * 8) {
     const long long t = i / k;
     const uint4* a = reinterpret_cast<const uint4*>(dy + t * cols);
+    if (slot[i] < 0) {                       // the pair's expert lives on another rank
+      if (lane == 0) dw[i] = 0.f;
+      continue;
+    }
     const uint4* b = reinterpret_cast<const uint4*>(p + static_cast<long long>(slot[i]) * cols);
     float acc = 0.f;
     for (int v = lane; v < nvec; v += 32) {

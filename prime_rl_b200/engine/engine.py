@@ -54,8 +54,9 @@ class Engine:
     def __init__(self, model, *, num_pages: int = 4096, page_size: int = 16, max_running: int = 256,
                  max_prefill_tokens: int = 16384, eos_token_id: int | None = None, enable_prefix_cache: bool = True,
                  use_cuda_graphs: bool = False, max_model_len: int = 8192, weight_dtype: str = "bf16", tp=None,
-                 keep_bf16_weights: bool = True, kv_offload_bytes: int = 0):
-        """``kv_offload_bytes`` > 0: a request that is preempted for lack of pages keeps its K / V in (pinned) host
+                 keep_bf16_weights: bool = True, kv_offload_bytes: int = 0, expert_parallel: bool = False):
+        """``expert_parallel`` (with ``tp``): the ranks split the experts by index instead of by width
+        (``engine/tp.py``). ``kv_offload_bytes`` > 0: a request that is preempted for lack of pages keeps its K / V in (pinned) host
         memory up to that many bytes in total and resumes without a second prefill (the reference configures this
         as ``kv_cache_offload.cpu.num_bytes`` of its serving stack,
         packages/prime-rl-configs/src/prime_rl/configs/inference.py:216-300)."""
@@ -74,7 +75,7 @@ class Engine:
             from .tp import shard_model_
 
             if getattr(model, "tp_size", 1) != tp.size:
-                shard_model_(self.model, tp.rank, tp.size)
+                shard_model_(self.model, tp.rank, tp.size, expert_parallel=expert_parallel)
             if tp.max_tokens < max(max_prefill_tokens, max_model_len):
                 raise ValueError("the tensor-parallel buffers are smaller than the largest step the engine may run")
         # fp8 serving: with ``keep_bf16_weights=False`` the bf16 storage of every quantised projection is
@@ -462,7 +463,8 @@ class Engine:
         if spec.get("type") == "p2p":
             from ..transports.weights.p2p import P2PWeightPort
 
-            tp = (self.tp.rank, self.tp_size) if self.tp_size > 1 else None
+            tp = (self.tp.rank, self.tp_size, bool(getattr(self.model, "tp_expert_parallel", False))) \
+                if self.tp_size > 1 else None
             self.weight_receiver = P2PWeightPort(self.model, Path(spec["run_dir"]), slot, spec.get("quantize"), tp=tp)
             return
         from ..transports.weights.nccl import NCCLWeightReceiver

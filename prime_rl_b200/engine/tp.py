@@ -5,7 +5,12 @@ What is split (``shard_tensor``):
   attention   heads: rank r owns q heads [r nq/R, (r+1) nq/R) and their kv heads; ``o_proj`` by columns
   dense MLP   the intermediate width: gate / up rows and ``down_proj`` columns
   experts     the intermediate width of EVERY expert (all ranks route all tokens to all experts and
-              read 1/R of each expert's weights: decode is bound by that read)
+              read 1/R of each expert's weights: decode is bound by that read); or, with
+              ``expert_parallel`` (``enable_expert_parallel`` of the inference config), whole experts:
+              rank r owns experts [r E/R, (r+1) E/R) at full width. The tokens are present on every
+              rank anyway (the layer input is the output of a reduction), so there is no dispatch: every
+              rank routes all tokens, runs the pairs whose expert it owns (``ops/moe.py: build_plan`` with
+              ``expert_range``) and the layer's reduction sums the partial outputs
 Embedding, router, norms and the LM head are replicated. Each decoder layer therefore ends in two
 sums over ranks (after ``o_proj`` and after the MLP); ``TPContext.reduce`` does each of them in ONE kernel
 over peer memory together with the residual add and the next RMSNorm (csrc/ep_p2p.cu,
@@ -51,11 +56,22 @@ def _cols(t: torch.Tensor, rank: int, size: int) -> torch.Tensor:
     return t.narrow(-1, rank * (n // size), n // size)
 
 
-def shard_tensor(name: str, t: torch.Tensor, arch, rank: int, size: int) -> torch.Tensor:
+def expert_slice(arch, rank: int, size: int) -> tuple[int, int]:
+    E = arch.num_experts
+    if E % size:
+        raise ValueError(f"{E} experts cannot be split over {size} ranks")
+    return rank * (E // size), (rank + 1) * (E // size)
+
+
+def shard_tensor(name: str, t: torch.Tensor, arch, rank: int, size: int, expert_parallel: bool = False
+                 ) -> torch.Tensor:
     """The part of native-layout tensor ``name`` that TP rank ``rank`` of ``size`` keeps (a view or a
     new tensor; replicated tensors are returned as they are)."""
     if size == 1:
         return t
+    if expert_parallel and ".experts." in name and t.dim() >= 1 and t.shape[0] == arch.num_experts:
+        lo, hi = expert_slice(arch, rank, size)
+        return t[lo:hi]                                           # weights and per-expert biases alike
     m = _LAYER.search(name)
     if m is None:
         return t
@@ -90,10 +106,10 @@ def shard_tensor(name: str, t: torch.Tensor, arch, rank: int, size: int) -> torc
     return t
 
 
-def shard_model_(model, rank: int, size: int) -> None:
+def shard_model_(model, rank: int, size: int, expert_parallel: bool = False) -> None:
     """Replaces the parameters of ``model`` by this rank's shards (in place) and leaves a
     ``model.tp_shard(name, tensor)`` hook that later weight loads go through."""
-    from ..models.layers import Attention, DecoderLayer
+    from ..models.layers import Attention, DecoderLayer, MoE
 
     arch = model.arch
     if size == 1:
@@ -107,14 +123,16 @@ def shard_model_(model, rank: int, size: int) -> None:
         for name, p in list(model.named_parameters()):
             if "lora_" in name:
                 raise NotImplementedError("merge or drop LoRA adapters before sharding the engine's model")
-            new = shard_tensor(name, p.data, arch, rank, size)
+            new = shard_tensor(name, p.data, arch, rank, size, expert_parallel)
             if new is not p.data:
                 p.data = new.contiguous()
     for layer in model.model.layers:
         at = layer.self_attn
         at.nq, at.nkv = at.nq // size, at.nkv // size
-    model.tp_shard = lambda name, t: shard_tensor(name, t, arch, rank, size)
-    model.tp_size, model.tp_rank = size, rank
+        if expert_parallel and isinstance(layer.mlp, MoE):
+            layer.mlp.expert_range = expert_slice(arch, rank, size)
+    model.tp_shard = lambda name, t: shard_tensor(name, t, arch, rank, size, expert_parallel)
+    model.tp_size, model.tp_rank, model.tp_expert_parallel = size, rank, expert_parallel
 
 
 class TPContext:

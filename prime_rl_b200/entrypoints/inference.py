@@ -29,7 +29,8 @@ def build_engine(config: InferenceConfig, tp=None):
     if tp is not None and tp.size > 1:
         from ..engine.tp import shard_model_
 
-        shard_model_(model, tp.rank, tp.size)       # before the checkpoint load: every rank reads only its slices
+        # before the checkpoint load: every rank reads only its slices
+        shard_model_(model, tp.rank, tp.size, expert_parallel=bool(ec.enable_expert_parallel) and arch.is_moe)
     if Path(ec.model).is_dir() and not ec.random_init:
         load_hf_checkpoint(model, Path(ec.model), strict=False)
     for p in model.parameters():
@@ -46,7 +47,8 @@ def build_engine(config: InferenceConfig, tp=None):
     engine = Engine(model, num_pages=pages, page_size=ec.page_size, max_running=ec.max_num_seqs,
                     max_prefill_tokens=ec.max_num_batched_tokens,
                     enable_prefix_cache=ec.enable_prefix_caching is not False, tp=tp,
-                    kv_offload_bytes=_kv_offload_bytes(config))
+                    kv_offload_bytes=_kv_offload_bytes(config),
+                    expert_parallel=bool(ec.enable_expert_parallel) and arch.is_moe)
     engine.runner.capture_routed = ec.enable_return_routed_experts and arch.is_moe
     return engine
 

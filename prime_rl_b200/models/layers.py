@@ -496,6 +496,9 @@ class MoE(nn.Module):
             self.fc2_latent_proj = Linear(arch.moe_latent_size, arch.hidden_size, std=arch.initializer_range,
                                           dtype=dtype, device=device)
         self.dispatcher = None            # parallel/ep.py installs an expert-parallel dispatcher here
+        # (lo, hi): this process holds only those experts while every token is present on every rank (the serving
+        # engine's expert parallelism, engine/tp.py); the output is then a partial sum that the caller reduces
+        self.expert_range: tuple[int, int] | None = None
         self.last_counts: torch.Tensor | None = None
         self.last_topk: torch.Tensor | None = None     # [T, k] expert ids of the last forward (router replay capture)
         self.last_router_stats: dict | None = None
@@ -505,7 +508,7 @@ class MoE(nn.Module):
         forced = None
         if seq.routed_experts is not None:
             forced = seq.routed_experts[:, self.layer_idx, :].to(torch.int32)
-        self.router.want_plan = self.dispatcher is None
+        self.router.want_plan = self.dispatcher is None and self.expert_range is None
         idx, w, counts, logits = self.router(x, forced)
         self.last_counts = counts
         self.last_topk = idx
@@ -518,7 +521,7 @@ class MoE(nn.Module):
         else:
             plan = self.router.last_plan
             if plan is None:
-                plan = moe_ops.build_plan(idx, counts, self.arch.num_experts)
+                plan = moe_ops.build_plan(idx, counts, self.arch.num_experts, expert_range=self.expert_range)
             if self.experts.supports_fp8_row_mask(xe):
                 yp = self.experts.forward_fp8_masked(xe, plan)
             elif self.experts.supports_row_mask(xe) and xe.shape[1] % 8 == 0:

@@ -105,10 +105,15 @@ def route_and_plan_small(logits: torch.Tensor, k: int, *, score_func: str = "sof
     return idx, w, counts, plan
 
 
-def build_plan(topk_idx: torch.Tensor, counts: torch.Tensor, num_experts: int, deterministic: bool = False
-               ) -> RoutingPlan:
+def build_plan(topk_idx: torch.Tensor, counts: torch.Tensor, num_experts: int, deterministic: bool = False,
+               expert_range: tuple[int, int] | None = None) -> RoutingPlan:
+    """``expert_range = (lo, hi)``: this rank owns only those experts of the ``num_experts`` (tokens replicated, experts
+    split: the serving engine's expert parallelism). The plan then covers ``hi - lo`` local experts; pairs of other
+    experts get ``slot = -1`` and no row, and ``combine`` leaves their term to the rank that owns them."""
     T, k = topk_idx.shape
     E = num_experts
+    if expert_range is not None:
+        return _build_plan_range(topk_idx, counts, expert_range, deterministic)
     P = max_padded_rows(T * k, E)
     dev = topk_idx.device
     if topk_idx.is_cuda:
@@ -145,6 +150,48 @@ def build_plan(topk_idx: torch.Tensor, counts: torch.Tensor, num_experts: int, d
     block_expert[blk_rows >= expert_offset[E]] = -1
     return RoutingPlan(topk_idx, slot.reshape(T, k).to(torch.int32), row_src, expert_offset.to(torch.int32),
                        block_expert, expert_offset[E:].to(torch.int32), counts, P, k, E)
+
+
+def _build_plan_range(topk_idx, counts, expert_range, deterministic) -> RoutingPlan:
+    lo, hi = expert_range
+    T, k = topk_idx.shape
+    E = hi - lo
+    P = max_padded_rows(T * k, E)
+    dev = topk_idx.device
+    local_counts = counts[lo:hi].contiguous()
+    if topk_idx.is_cuda:
+        expert_offset = torch.empty(E + 1, dtype=torch.int32, device=dev)
+        block_expert = torch.empty(P // 128, dtype=torch.int32, device=dev)
+        cursor = torch.empty(E, dtype=torch.int32, device=dev)
+        total = torch.empty(1, dtype=torch.int32, device=dev)
+        slot = torch.empty(T, k, dtype=torch.int32, device=dev)
+        row_src = torch.empty(P, dtype=torch.int32, device=dev)
+        rc = rt.lib().prb_moe_plan_range(topk_idx.data_ptr(), local_counts.data_ptr(), expert_offset.data_ptr(),
+                                         block_expert.data_ptr(), cursor.data_ptr(), total.data_ptr(), slot.data_ptr(),
+                                         row_src.data_ptr(), T, E, k, P // 128, int(deterministic), lo,
+                                         rt.stream_ptr(dev))
+        rt.check(rc, "prb_moe_plan_range")
+        return RoutingPlan(topk_idx, slot, row_src, expert_offset, block_expert, total, local_counts, P, k, E)
+    flat = topk_idx.reshape(-1).long() - lo
+    mine = (flat >= 0) & (flat < E)
+    pairs = torch.nonzero(mine).reshape(-1)                       # pair ids (t * k + j) of the owned experts
+    padded = (local_counts.long() + 127) // 128 * 128
+    expert_offset = torch.zeros(E + 1, dtype=torch.long)
+    expert_offset[1:] = padded.cumsum(0)
+    order = pairs[torch.argsort(flat[pairs], stable=True)]
+    sorted_e = flat[order]
+    starts = torch.zeros(E, dtype=torch.long)
+    starts[1:] = local_counts.long().cumsum(0)[:-1]
+    pos = expert_offset[sorted_e] + torch.arange(order.numel()) - starts[sorted_e]
+    slot = torch.full((flat.numel(),), -1, dtype=torch.long)
+    slot[order] = pos
+    row_src = torch.full((P,), -1, dtype=torch.int32)
+    row_src[pos] = order.to(torch.int32)
+    blk_rows = torch.arange(P // 128) * 128
+    block_expert = torch.searchsorted(expert_offset[1:].contiguous(), blk_rows, right=True).to(torch.int32)
+    block_expert[blk_rows >= expert_offset[E]] = -1
+    return RoutingPlan(topk_idx, slot.reshape(T, k).to(torch.int32), row_src, expert_offset.to(torch.int32),
+                       block_expert, expert_offset[E:].to(torch.int32), local_counts, P, k, E)
 
 
 class _Permute(torch.autograd.Function):
@@ -218,7 +265,8 @@ def _combine(p, plan: RoutingPlan, w, residual, T):
                                       T, H, plan.k, rt.stream_ptr(p.device))
         rt.check(rc, "prb_moe_combine")
         return y
-    rows = p[plan.slot.long()].float()  # [T, k, H]
+    sl = plan.slot.long()
+    rows = p[sl.clamp(min=0)].float() * (sl >= 0)[..., None]  # [T, k, H]; slot < 0: the pair belongs to another rank
     if w is not None:
         rows = rows * w.float()[:, :, None]
     y = rows.sum(1)

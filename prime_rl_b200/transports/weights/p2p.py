@@ -53,10 +53,10 @@ class P2PWeightPort:
     they are; ``dequantize_into_model`` refreshes the live parameters from them)."""
 
     def __init__(self, model, run_dir: Path | None, replica: int = 0, quantize: str | None = None,
-                 tp: tuple[int, int] | None = None):
+                 tp: tuple | None = None):
         """``run_dir=None``: build the manifest only (``self.manifest``), write no file — for callers that
-        hand it to the sender through another channel. ``tp = (rank, size)``: this process holds one
-        tensor-parallel shard of the engine; the manifest says so and the sender slices what it pushes."""
+        hand it to the sender through another channel. ``tp = (rank, size[, experts_by_index])``: this process
+        holds one tensor-parallel shard of the engine; the manifest says so and the sender slices what it pushes."""
         self.model, self.replica, self.quantize = model, replica, quantize
         self.tp = tp
         self.run_dir = Path(run_dir) if run_dir is not None else None
@@ -257,8 +257,9 @@ class P2PWeightSender(WeightSender):
                     # the target process holds one tensor-parallel shard: send it its slices
                     from ...engine.tp import shard_tensor
 
-                    r, size = man["tp"]
-                    src = {n: shard_tensor(n, t.detach(), model.arch, r, size) for n, t in tensors.items()}
+                    r, size, *rest = man["tp"]
+                    by_expert = bool(rest and rest[0])      # the engine splits its experts by index, not by width
+                    src = {n: shard_tensor(n, t.detach(), model.arch, r, size, by_expert) for n, t in tensors.items()}
                 pushed += push_state(src, man, self.mapped)
         torch.cuda.synchronize()
         if pushed:

@@ -73,6 +73,7 @@ def selftest(argv=None) -> None:
     ap.add_argument("--skip-reference", action="store_true", help="no unsharded engine (model too large for the check)")
     ap.add_argument("--bench-reduce", action="store_true", help="time the fused reduce against NCCL + norm first")
     ap.add_argument("--prefill-tokens", type=int, default=16384, help="token budget of one prefill step")
+    ap.add_argument("--expert-parallel", action="store_true", help="split the experts by index instead of by width")
     args = ap.parse_args(argv)
     cuda = torch.cuda.is_available()
     if args.model:
@@ -143,7 +144,12 @@ def selftest(argv=None) -> None:
         if cuda:
             torch.cuda.empty_cache()
     dist.barrier()
-    eng = Engine(build_model(arch, device=dev, dtype=dtype, seed=0), tp=tp, **kw)
+    eng = Engine(build_model(arch, device=dev, dtype=dtype, seed=0), tp=tp, expert_parallel=args.expert_parallel, **kw)
+    if args.expert_parallel and tp.size > 1:
+        moe = [l.mlp for l in eng.model.model.layers if getattr(l, "is_moe", False)]
+        assert moe and all(m.expert_range == (rank * arch.num_experts // tp.size, (rank + 1) * arch.num_experts // tp.size)
+                           and m.experts.gate_up_proj.shape[0] == arch.num_experts // tp.size
+                           and m.experts.gate_up_proj.shape[1] == 2 * arch.moe_intermediate_size for m in moe)
     acc = instrument(eng)
     if rank == 0:
         eng.generate_sync(prompts, params)                          # warm-up (graph capture for every batch size)

@@ -206,6 +206,47 @@ def test_tensor_parallel_engine_in_lockstep_matches_the_single_engine():
     assert "identical_sequences=5/5" in r.stdout
 
 
+def test_expert_parallel_engine_matches_the_single_engine(free_port):
+    """Two gloo ranks, experts split by index (``enable_expert_parallel``): every rank routes all tokens, runs the
+    pairs of the experts it owns, and the layer's reduction sums the partial outputs."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=str(root))
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", str(free_port), "-m",
+                        "tests.distributed.tp_engine", "--batch", "5", "--prompt", "24", "--tokens", "8",
+                        "--expert-parallel"], env=env, capture_output=True, text=True, timeout=600, cwd=str(root))
+    assert r.returncode == 0 and "TP_SELFTEST_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "identical_sequences=5/5" in r.stdout
+
+
+def test_range_plan_drops_the_pairs_of_other_ranks():
+    from prime_rl_b200.ops import moe as M
+
+    torch.manual_seed(0)
+    T, k, E, H = 37, 2, 8, 16
+    idx = torch.stack([torch.randperm(E)[:k] for _ in range(T)]).to(torch.int32)
+    counts = torch.bincount(idx.reshape(-1).long(), minlength=E).to(torch.int32)
+    w = torch.rand(T, k)
+    x = torch.randn(T, H)
+    full = M.build_plan(idx, counts, E)
+    y_full = M.combine(M.permute(x, full) * 2.0, w, full, T)       # every "expert" doubles its rows
+    parts = []
+    for lo, hi in ((0, 3), (3, 8)):
+        plan = M.build_plan(idx, counts, E, expert_range=(lo, hi))
+        assert plan.num_experts == hi - lo and int(plan.total_rows) == int(((counts[lo:hi] + 127) // 128 * 128).sum())
+        own = (idx >= lo) & (idx < hi)
+        assert torch.equal(plan.slot >= 0, own)
+        be = plan.block_expert[plan.block_expert >= 0]
+        assert be.numel() == 0 or (int(be.min()) >= 0 and int(be.max()) < hi - lo)
+        parts.append(M.combine(M.permute(x, plan) * 2.0, w, plan, T))
+    torch.testing.assert_close(parts[0] + parts[1], y_full)
+
+
 def test_tensor_parallel_http_server_serves_the_same_tokens(tmp_path):
     """The inference entry point with ``tensor_parallel_size = 2`` (two CPU processes under torchrun):
     rank 0 answers HTTP, the other rank follows; greedy tokens equal those of a local unsharded engine."""

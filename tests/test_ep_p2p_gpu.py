@@ -120,8 +120,8 @@ def test_tensor_parallel_engine_with_fused_reduce_kernel():
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    for extra in ([], ["--cuda-graphs"]):
+    for port, extra in ((29541, []), (29540, ["--cuda-graphs"]), (29544, ["--cuda-graphs", "--expert-parallel"])):
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-               "127.0.0.1", "--master-port", "29540" if extra else "29541", "-m", "tests.distributed.tp_engine", *extra]
+               "127.0.0.1", "--master-port", str(port), "-m", "tests.distributed.tp_engine", *extra]
         out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
         assert out.returncode == 0 and "TP_SELFTEST_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]

@@ -1292,3 +1292,32 @@ def test_fp8_training_linear_and_grouped_linear_on_the_fp8_kernel():
     for got, want, tol in ((yp[:768], yr[:768], 0.06), (gxp[:768], rxp[:768], 0.06), (gwe, rwe, 0.01)):
         rel = float((got.float() - want.float()).norm() / want.float().norm())
         assert rel < tol, rel
+
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("deterministic", [False, True])
+def test_moe_plan_over_an_expert_range_sums_to_the_full_plan(deterministic):
+    """Serving-side expert parallelism: plans over disjoint expert ranges (pairs of other experts get slot -1 and no
+    row) give partial outputs that add up to the output of the plan over all experts."""
+    T, k, E, H = 300, 4, 16, 256
+    torch.manual_seed(5)
+    idx = torch.stack([torch.randperm(E)[:k] for _ in range(T)]).to(torch.int32).to(DEV)
+    counts = torch.bincount(idx.reshape(-1).long(), minlength=E).to(torch.int32)
+    w = torch.rand(T, k, device=DEV)
+    x = _rand(T, H)
+    full = moe.build_plan(idx, counts, E, deterministic=deterministic)
+    y_full = moe.combine(moe.permute(x, full) * 2.0, w, full, T).float()
+    total = torch.zeros_like(y_full)
+    for lo, hi in ((0, 4), (4, 5), (5, 16)):
+        plan = moe.build_plan(idx, counts, E, deterministic=deterministic, expert_range=(lo, hi))
+        own = (idx >= lo) & (idx < hi)
+        assert torch.equal(plan.slot >= 0, own)
+        assert int(plan.total_rows) == int(((counts[lo:hi] + 127) // 128 * 128).sum())
+        src = plan.row_src[plan.row_src >= 0].long()
+        assert src.numel() == int(own.sum()) and bool(own.reshape(-1)[src].all())
+        be = plan.block_expert[plan.block_expert >= 0]
+        assert int(be.max()) < hi - lo
+        total += moe.combine(moe.permute(x, plan) * 2.0, w, plan, T).float()
+    rt.check_status()
+    _close(total, y_full, atol=3e-2, rtol=3e-2)
