@@ -89,8 +89,18 @@ class Engine:
         self.device = p.device
         self.cache = KVCache(arch.num_hidden_layers, num_pages, page_size, arch.num_key_value_heads // self.tp_size,
                              arch.head_dim, p.dtype, p.device)
-        self.runner = ModelRunner(model, self.cache, use_cuda_graphs=use_cuda_graphs, max_model_len=max_model_len,
-                                  tp=tp if self.tp_size > 1 else None, shared_prefix_decode=enable_prefix_cache)
+        from .hybrid import HybridRunner, needs_hybrid_runner
+
+        if needs_hybrid_runner(model):
+            # layers with a recurrent state (Mamba-2, gated delta-net): the state of a prefix cannot be shared through
+            # the page cache and is not part of a host-memory swap, so both are off for these families
+            if self.tp_size > 1:
+                raise NotImplementedError("tensor parallelism of the rollout engine covers the attention decoder families")
+            enable_prefix_cache, self.kv_offload_bytes = False, 0
+            self.runner = HybridRunner(model, self.cache, max_model_len=max_model_len)
+        else:
+            self.runner = ModelRunner(model, self.cache, use_cuda_graphs=use_cuda_graphs, max_model_len=max_model_len,
+                                      tp=tp if self.tp_size > 1 else None, shared_prefix_decode=enable_prefix_cache)
         self.max_running, self.max_prefill_tokens = max_running, max_prefill_tokens
         self.eos, self.enable_prefix_cache = eos_token_id, enable_prefix_cache
         self.waiting: list[Request] = []

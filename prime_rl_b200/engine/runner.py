@@ -48,7 +48,8 @@ class ModelRunner:
         self._cu_batch, self._cu = None, []             # per-sequence cu_seqlens of the current prefix-hit prefill
         # CUDA graphs for decode steps: batch sizes are padded to a multiple of ``graph_bucket``;
         # one page of the cache is reserved as the target of the padding rows
-        plain = all(l.self_attn.window is None and l.self_attn.sinks is None for l in model.model.layers)
+        plain = all(getattr(getattr(l, "self_attn", None), "window", None) is None
+                    and getattr(getattr(l, "self_attn", None), "sinks", None) is None for l in model.model.layers)
         self.use_cuda_graphs = use_cuda_graphs and self.device.type == "cuda" and plain
         self.graph_bucket = 8
         self.graph_max_blocks = max(1, (max_model_len + cache.page_size - 1) // cache.page_size)

@@ -42,6 +42,9 @@ class SeqInfo:
     # rotary angles [T, rotary_dim / 2] when positions have several axes (multimodal MRoPE); attention
     # layers that support it use these instead of position_ids * inv_freq
     mrope_angles: torch.Tensor | None = None
+    # rollout engine: an object that holds what precedes the new tokens (paged K / V, convolution tails, recurrent
+    # states) and answers ``attend / conv / mamba / delta`` for them (engine/hybrid.py)
+    engine: object | None = None
 
     @classmethod
     def from_lengths(cls, lengths: list[int], device) -> "SeqInfo":
@@ -214,7 +217,9 @@ class Attention(nn.Module):
         kw = self.k_norm.weight if self.k_norm is not None else None
         q, k, v = ops.qkv_norm_rope(qkv, qw, kw, seq.position_ids, self.inv_freq, self.arch.rms_norm_eps, self.nq,
                                     self.nkv, self.D)
-        if seq.cp is not None:
+        if seq.engine is not None:
+            o = seq.engine.attend(self.layer_idx, q, k, v, self.window, self.sinks)
+        elif seq.cp is not None:
             o = seq.cp.attention(q, k, v, seq, window=self.window, sinks=self.sinks, backend=self.backend)
         else:
             o = attn_ops.attention(q, k, v, seq.cu_seqlens, seq.max_seqlen, causal=True, window=self.window,

@@ -35,7 +35,7 @@ def doc_windows(seq: SeqInfo) -> tuple[torch.Tensor, torch.Tensor]:
 class Mamba2Mixer(nn.Module):
     def __init__(self, arch: ModelArch, layer_idx: int, dtype=None, device=None):
         super().__init__()
-        self.arch = arch
+        self.arch, self.layer_idx = arch, layer_idx
         self.nh, self.hd, self.ng, self.ns = arch.mamba_num_heads, arch.mamba_head_dim, arch.ssm_n_groups, arch.ssm_state_size
         self.inner = self.nh * self.hd
         self.conv_dim = self.inner + 2 * self.ng * self.ns
@@ -65,15 +65,24 @@ class Mamba2Mixer(nn.Module):
     def forward(self, x: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
         T = x.shape[0]
         gate, conv_in, dt = self.in_proj(x).split([self.inner, self.conv_dim, self.nh], dim=-1)
-        conv = ssm.causal_conv1d(conv_in, self.conv1d_weight, self.conv1d_bias, seq.position_ids, "silu")
+        eng = seq.engine                 # rollout engine: state of the sequences before these tokens (engine/hybrid.py)
+        if eng is not None:
+            conv = eng.conv(self.layer_idx, conv_in, self.conv1d_weight, self.conv1d_bias, "silu")
+        else:
+            conv = ssm.causal_conv1d(conv_in, self.conv1d_weight, self.conv1d_bias, seq.position_ids, "silu")
         hs, Bm, Cm = conv.split([self.inner, self.ng * self.ns, self.ng * self.ns], dim=-1)
         dtp = F.softplus(dt.float() + self.dt_bias)
         lo, hi = self.arch.time_step_limit
         if lo > 0.0 or math.isfinite(hi):
             dtp = dtp.clamp(lo, hi)
-        y = ssm.mamba2_scan(hs.reshape(T, self.nh, self.hd), dtp, -torch.exp(self.A_log.float()),
-                            Bm.reshape(T, self.ng, self.ns), Cm.reshape(T, self.ng, self.ns), self.D, seq.position_ids,
-                            chunk=self.arch.ssm_chunk_size)
+        if eng is not None:
+            y = eng.mamba(self.layer_idx, hs.reshape(T, self.nh, self.hd), dtp, -torch.exp(self.A_log.float()),
+                          Bm.reshape(T, self.ng, self.ns), Cm.reshape(T, self.ng, self.ns), self.D,
+                          self.arch.ssm_chunk_size)
+        else:
+            y = ssm.mamba2_scan(hs.reshape(T, self.nh, self.hd), dtp, -torch.exp(self.A_log.float()),
+                                Bm.reshape(T, self.ng, self.ns), Cm.reshape(T, self.ng, self.ns), self.D,
+                                seq.position_ids, chunk=self.arch.ssm_chunk_size)
         y = ssm.gated_rms_norm(y.reshape(T, self.inner).to(x.dtype), gate, self.norm_weight, self.arch.rms_norm_eps,
                                self.inner // self.ng, "silu", gate_first=True)
         return self.out_proj(y)
@@ -82,7 +91,7 @@ class Mamba2Mixer(nn.Module):
 class GatedDeltaNet(nn.Module):
     def __init__(self, arch: ModelArch, layer_idx: int, dtype=None, device=None):
         super().__init__()
-        self.arch = arch
+        self.arch, self.layer_idx = arch, layer_idx
         self.nv, self.nk = arch.linear_num_value_heads, arch.linear_num_key_heads
         self.dk, self.dv = arch.linear_key_head_dim, arch.linear_value_head_dim
         self.key_dim, self.value_dim = self.nk * self.dk, self.nv * self.dv
@@ -108,7 +117,11 @@ class GatedDeltaNet(nn.Module):
 
     def forward(self, x: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
         T = x.shape[0]
-        qkv = ssm.causal_conv1d(self.in_proj_qkv(x), self.conv1d_weight, None, seq.position_ids, "silu")
+        eng = seq.engine                 # rollout engine: state of the sequences before these tokens (engine/hybrid.py)
+        if eng is not None:
+            qkv = eng.conv(self.layer_idx, self.in_proj_qkv(x), self.conv1d_weight, None, "silu")
+        else:
+            qkv = ssm.causal_conv1d(self.in_proj_qkv(x), self.conv1d_weight, None, seq.position_ids, "silu")
         z = self.in_proj_z(x).reshape(T, self.nv, self.dv)
         beta = torch.sigmoid(self.in_proj_b(x).float())
         g = -torch.exp(self.A_log.float()) * F.softplus(self.in_proj_a(x).float() + self.dt_bias)
@@ -117,7 +130,10 @@ class GatedDeltaNet(nn.Module):
         rep = self.nv // self.nk
         if rep > 1:
             q, k = q.repeat_interleave(rep, dim=1), k.repeat_interleave(rep, dim=1)
-        o = delta_rule.gated_delta_rule(q, k, v.reshape(T, self.nv, self.dv), g, beta, seq.position_ids)
+        if eng is not None:
+            o = eng.delta(self.layer_idx, q, k, v.reshape(T, self.nv, self.dv), g, beta)
+        else:
+            o = delta_rule.gated_delta_rule(q, k, v.reshape(T, self.nv, self.dv), g, beta, seq.position_ids)
         o = ssm.gated_rms_norm(o.to(x.dtype), z, self.norm_weight, self.arch.rms_norm_eps, self.dv, "silu",
                                gate_first=False)
         return self.out_proj(o.reshape(T, self.value_dim))
@@ -165,8 +181,11 @@ class GatedAttention(nn.Module):
         else:
             q = ops.qknorm_rope(q, self.q_norm.weight, seq.position_ids, self.inv_freq, self.arch.rms_norm_eps)
             k = ops.qknorm_rope(k, self.k_norm.weight, seq.position_ids, self.inv_freq, self.arch.rms_norm_eps)
-        o = attn_ops.attention(q, k, v, seq.cu_seqlens, seq.max_seqlen, causal=True, backend=self.backend,
-                               cache=seq.attn_cache, cache_key=self.layer_idx)
+        if seq.engine is not None:
+            o = seq.engine.attend(self.layer_idx, q, k, v, None, None)
+        else:
+            o = attn_ops.attention(q, k, v, seq.cu_seqlens, seq.max_seqlen, causal=True, backend=self.backend,
+                                   cache=seq.attn_cache, cache_key=self.layer_idx)
         o = o * torch.sigmoid(gate.float()).to(o.dtype)
         return self.o_proj(o.reshape(T, self.nq * self.D))
 

@@ -31,9 +31,11 @@ def _l2norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
 
 
 def gated_delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
-                     position_ids: torch.Tensor, chunk: int = 64, l2norm: bool = True) -> torch.Tensor:
+                     position_ids: torch.Tensor, chunk: int = 64, l2norm: bool = True,
+                     initial_state: torch.Tensor | None = None, return_state: bool = False):
     """``q, k [T, H, dk]``, ``v [T, H, dv]``, ``g [T, H]`` (log-decay, <= 0), ``beta [T, H]``.
-    Returns ``[T, H, dv]`` in fp32."""
+    Returns ``[T, H, dv]`` in fp32. ``initial_state [H, dk, dv]`` / ``return_state``: the state before the first and
+    after the last token (serving: one sequence per call, continued across calls)."""
     T, H, dk = q.shape
     dv = v.shape[-1]
     qf, kf, vf = q.float(), k.float(), v.float()
@@ -74,14 +76,32 @@ def gated_delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch
     k_to_end = kc * (cum[..., -1:] - cum).exp().unsqueeze(-1)
     end_decay = cum[..., -1].exp()                                   # [H, nc]
     q_in = qc * cum.exp().unsqueeze(-1)
-    S = torch.zeros(H, dk, dv, dtype=torch.float32, device=q.device)
+    S = torch.zeros(H, dk, dv, dtype=torch.float32, device=q.device) if initial_state is None \
+        else initial_state.float()
     outs = []
     for c in range(nc):
         v_new = u[:, c] - w[:, c] @ S                                # what every token really writes
         outs.append(q_in[:, c] @ S + qk[:, c] @ v_new)
         S = S * end_decay[:, c, None, None] + k_to_end[:, c].transpose(-1, -2) @ v_new
     o = torch.stack(outs, dim=1)                                     # [H, nc, C, dv]
-    return o.movedim(0, 2).reshape(nc * C, H, dv)[:T]
+    o = o.movedim(0, 2).reshape(nc * C, H, dv)[:T]
+    # padding tokens have g = 0, beta = 0 and k = 0: they neither decay nor write, so S is the state after token T - 1
+    return (o, S) if return_state else o
+
+
+def gated_delta_rule_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
+                          state: torch.Tensor, l2norm: bool = True):
+    """One token for each of ``n`` sequences: ``q, k [n, H, dk]``, ``v [n, H, dv]``, ``g, beta [n, H]``,
+    ``state [n, H, dk, dv]`` (fp32). Returns (o ``[n, H, dv]`` fp32, new state)."""
+    dk = q.shape[-1]
+    qf, kf, vf = q.float(), k.float(), v.float()
+    if l2norm:
+        qf, kf = _l2norm(qf), _l2norm(kf)
+    qf = qf * dk ** -0.5
+    state = state * g.float().exp()[:, :, None, None]
+    pred = torch.einsum("bhk,bhkv->bhv", kf, state)
+    state = state + beta.float()[:, :, None, None] * kf[..., None] * (vf - pred)[:, :, None, :]
+    return torch.einsum("bhk,bhkv->bhv", qf, state), state
 
 
 def gated_delta_rule_ref(q, k, v, g, beta, position_ids, l2norm: bool = True) -> torch.Tensor:

@@ -97,9 +97,13 @@ def _pad_tokens(t: torch.Tensor, n: int) -> torch.Tensor:
 
 
 def mamba2_scan(x: torch.Tensor, dt: torch.Tensor, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor,
-                D: torch.Tensor | None, position_ids: torch.Tensor, chunk: int = 128) -> torch.Tensor:
+                D: torch.Tensor | None, position_ids: torch.Tensor, chunk: int = 128,
+                initial_state: torch.Tensor | None = None, return_state: bool = False):
     """Chunked SSD. ``x [T, H, P]``, ``dt [T, H]`` (after softplus / clamping), ``A [H]`` (negative),
-    ``B, C [T, G, N]`` with ``H % G == 0``, ``D [H]`` skip weight. Returns ``[T, H, P]`` in fp32."""
+    ``B, C [T, G, N]`` with ``H % G == 0``, ``D [H]`` skip weight. Returns ``[T, H, P]`` in fp32.
+    ``initial_state [H, P, N]``: the state before the first token (a sequence continued from an earlier call: its
+    positions then do not start at 0). ``return_state``: also return the state after the last token (serving:
+    one sequence per call)."""
     T, H, P = x.shape
     G, N = B.shape[1], B.shape[2]
     rep = H // G
@@ -131,7 +135,8 @@ def mamba2_scan(x: torch.Tensor, dt: torch.Tensor, A: torch.Tensor, B: torch.Ten
     S_chunk = torch.einsum("cjh,cjhp,cjhn->chpn", to_end, xc, Bh)
     chunk_decay = cum[:, -1, :].exp()                                # [nc, H]
     # ---- carry between chunks (a short sequential loop over nc small tensors)
-    carry = torch.zeros(H, P, N, dtype=torch.float32, device=x.device)
+    carry = torch.zeros(H, P, N, dtype=torch.float32, device=x.device) if initial_state is None \
+        else initial_state.float()
     carries = []
     for c in range(nc):
         carries.append(carry)
@@ -141,7 +146,48 @@ def mamba2_scan(x: torch.Tensor, dt: torch.Tensor, A: torch.Tensor, B: torch.Ten
     y = y.reshape(nc * Q, H, P)[:T]
     if D is not None:
         y = y + x.float() * D.float()[None, :, None]
-    return y
+    # padding tokens have dt = 0: no decay and no contribution, so the carry after the last chunk is the state
+    # after token T - 1
+    return (y, carry) if return_state else y
+
+
+def mamba2_step(x: torch.Tensor, dt: torch.Tensor, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor,
+                D: torch.Tensor | None, state: torch.Tensor):
+    """One token for each of ``n`` sequences: ``x [n, H, P]``, ``dt [n, H]``, ``B, C [n, G, N]``, ``state [n, H, P, N]``
+    (fp32). Returns (y ``[n, H, P]`` fp32, new state)."""
+    H, G = x.shape[1], B.shape[1]
+    rep = H // G
+    dA = (dt.float() * A.float()).exp()                                   # [n, H]
+    Bh = B.float().repeat_interleave(rep, dim=1)                          # [n, H, N]
+    Ch = C.float().repeat_interleave(rep, dim=1)
+    state = state * dA[:, :, None, None] + (dt.float()[:, :, None] * x.float())[..., None] * Bh[:, :, None, :]
+    y = torch.einsum("bhpn,bhn->bhp", state, Ch)
+    if D is not None:
+        y = y + x.float() * D.float()[None, :, None]
+    return y, state
+
+
+def conv1d_window(tail: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
+                  activation: str | None = "silu"):
+    """Causal convolution of the new tokens of ONE sequence whose last ``K - 1`` inputs are ``tail [K - 1, C]``
+    (zeros before the first token). Returns (y ``[n, C]``, new tail)."""
+    K = weight.shape[1]
+    full = torch.cat([tail.to(x.dtype), x], 0)
+    pos = torch.arange(K, K + full.shape[0], dtype=torch.int32, device=x.device)      # no tap is masked
+    y = causal_conv1d(full, weight, bias, pos, activation)[K - 1:]
+    return y, full[full.shape[0] - (K - 1):]
+
+
+def conv1d_step(tails: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None,
+                activation: str | None = "silu"):
+    """One token for each of ``n`` sequences: ``tails [n, K - 1, C]``, ``x [n, C]``. Returns (y ``[n, C]``, new tails)."""
+    win = torch.cat([tails.to(x.dtype), x[:, None, :]], 1)                # [n, K, C]
+    y = torch.einsum("nkc,ck->nc", win.float(), weight.float())
+    if bias is not None:
+        y = y + bias.float()
+    if activation in ("silu", "swish"):
+        y = F.silu(y)
+    return y.to(x.dtype), win[:, 1:]
 
 
 def mamba2_scan_ref(x, dt, A, B, C, D, position_ids) -> torch.Tensor:

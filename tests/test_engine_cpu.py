@@ -1,5 +1,6 @@
 import json
 
+import pytest
 import torch
 
 from prime_rl_b200.engine.engine import Engine
@@ -395,3 +396,35 @@ def test_preempted_requests_keep_their_kv_in_host_memory_and_resume_without_a_se
     small = Engine(model, num_pages=24, page_size=16, enable_prefix_cache=False, kv_offload_bytes=1)
     assert [r.output for r in small.generate_sync(prompts, sp)] == want          # budget too small: falls back
     assert small.stats.get("kv_swap_outs", 0) == 0
+
+
+@pytest.mark.parametrize("name", ["tiny-nemotron-h", "tiny-qwen3.5-moe"])
+def test_engine_serves_the_recurrent_state_families(name):
+    """Mamba-2 / gated delta-net layers next to attention: the engine keeps a convolution tail and a recurrent state per
+    sequence and layer, prefills in chunks from the stored state and decodes with one batched recurrence step. Greedy
+    tokens and their log-probabilities must be those of the model's own forward over the whole sequence."""
+    from prime_rl_b200.engine.engine import Engine
+    from prime_rl_b200.engine.hybrid import HybridRunner
+    from prime_rl_b200.engine.sampler import SamplingParams
+    from prime_rl_b200.models import SeqInfo, build_model, resolve_arch
+
+    arch = resolve_arch(name)
+    model = build_model(arch, device="cpu", dtype=torch.float32, seed=0).eval()
+    eng = Engine(model, num_pages=256, page_size=16, max_model_len=256, max_prefill_tokens=48)
+    assert isinstance(eng.runner, HybridRunner) and not eng.enable_prefix_cache
+    g = torch.Generator().manual_seed(1)
+    # 100 tokens: longer than one prefill step, so the scans continue from a stored state; the short prompts share steps
+    prompts = [torch.randint(0, arch.vocab_size, (n,), generator=g).tolist() for n in (20, 100, 7, 33)]
+    out = eng.generate_sync(prompts, SamplingParams(max_tokens=9, temperature=0.0))
+    for p, r in zip(prompts, out):
+        assert len(r.output) == 9
+        ids = torch.tensor(p + r.output)
+        with torch.no_grad():
+            h = model(ids, SeqInfo.from_lengths([len(ids)], torch.device("cpu")))
+            lp = torch.log_softmax(h.float() @ model.output_weight.float().t(), -1)
+        for i, tok in enumerate(r.output):
+            t = len(p) - 1 + i
+            assert int(lp[t].argmax()) == tok
+            assert abs(float(lp[t, tok]) - r.logprobs[i]) < 1e-3
+    # the states went away with the requests
+    assert all(not r.kv.pages for r in out)
