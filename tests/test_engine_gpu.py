@@ -281,3 +281,35 @@ def test_truncated_sampling_kernel_keeps_the_same_set_as_the_sorted_rule():
         tk, _, _ = S.sample(logits[2:3], temperature[2:3], top_k[2:3], top_p[2:3], generator=g)
         counts[kept.index(int(tk[0]))] += 1
     assert torch.allclose(counts / 2000, pr.cpu(), atol=0.04)
+
+
+@pytest.mark.parametrize("name", ["tiny-nemotron-h", "tiny-qwen3.5-moe"])
+def test_engine_serves_the_recurrent_state_families_on_the_gpu(name):
+    """bf16 on the GPU: the engine's incremental path (stored convolution tails and recurrent states, batched one-token
+    steps) against the model's own forward over the finished sequences."""
+    from prime_rl_b200.engine.engine import Engine
+    from prime_rl_b200.engine.hybrid import HybridRunner
+    from prime_rl_b200.engine.sampler import SamplingParams
+    from prime_rl_b200.models import SeqInfo, build_model, resolve_arch
+    from prime_rl_b200.ops import _runtime as rt
+
+    dev = torch.device("cuda", 0)
+    arch = resolve_arch(name)
+    model = build_model(arch, device=dev, dtype=torch.bfloat16, seed=0).eval()
+    eng = Engine(model, num_pages=256, page_size=16, max_model_len=256, max_prefill_tokens=48)
+    assert isinstance(eng.runner, HybridRunner)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, arch.vocab_size, (n,), generator=g).tolist() for n in (20, 100, 7, 33)]
+    out = eng.generate_sync(prompts, SamplingParams(max_tokens=8, temperature=1.0, seed=3))
+    torch.cuda.synchronize()
+    rt.check_status()
+    worst = 0.0
+    for p, r in zip(prompts, out):
+        assert len(r.output) == 8
+        ids = torch.tensor(p + r.output, device=dev)
+        with torch.no_grad():
+            h = model(ids, SeqInfo.from_lengths([len(ids)], dev))
+            lp = torch.log_softmax(h.float() @ model.output_weight.float().t(), -1)
+        for i, tok in enumerate(r.output):
+            worst = max(worst, abs(float(lp[len(p) - 1 + i, tok]) - r.logprobs[i]))
+    assert worst < 0.08, worst          # bf16 activations, sums in another order between the two paths
