@@ -328,6 +328,9 @@ class MuonConfig(BaseOptimizerConfig):
     betas2: float = 0.999
     ns_steps: int = 5
     adjust_lr: Literal["spectral_norm", "rms_norm"] | None = "rms_norm"
+    # every matrix is orthogonalised by ONE data-parallel rank (matrices dealt out by cost), the updates are summed
+    # over the ranks afterwards; False: every rank orthogonalises every matrix
+    distributed: bool = True
 
 
 class SignSGDConfig(BaseOptimizerConfig):

@@ -492,18 +492,43 @@ class FlatOptimizer:
         c, buf = self.config, grp.buf
         g_all = buf.grad * coef
         b1, b2 = c.betas1, c.betas2
+
+        def is_matrix(s):
+            return len(s.shape) >= 2 and "embed" not in s.name and "lm_head" not in s.name
+
+        # The gradients are identical on the ranks of the reduction group, so the orthogonalisations can be dealt
+        # out: every matrix has one owner (largest first onto the least loaded rank), which writes its scaled update
+        # into a buffer that is zero elsewhere; one sum over the ranks hands every update to everybody. The reference
+        # moves whole matrices to their owners with an all-to-all and gathers the updates
+        # (trainer/optim/__init__.py:151-249); with replicated gradients only the second half is needed.
+        group = grp.reduce_group
+        world = dist.get_world_size(group) if (dist.is_initialized() and group is not None) else 1
+        owner: dict[str, int] = {}
+        shared_upd = None
+        if getattr(c, "distributed", True) and world > 1:
+            rank = dist.get_rank(group)
+            load = [0.0] * world
+            mats = sorted((s for s in buf.slots if is_matrix(s)), key=lambda s: (-s.numel * min(s.shape[-2:]), s.name))
+            for s in mats:
+                r = min(range(world), key=lambda i: (load[i], i))
+                owner[s.name] = r
+                load[r] += s.numel * min(s.shape[-2:])
+            shared_upd = torch.zeros_like(buf.master)
         for s in buf.slots:
             sl = slice(s.offset, s.offset + s.numel)
             g = g_all[sl].view(s.shape)
             p = buf.master[sl].view(s.shape)
             m = grp.exp_avg[sl].view(s.shape)
-            is_matrix = len(s.shape) >= 2 and "embed" not in s.name and "lm_head" not in s.name
-            if is_matrix:
+            if is_matrix(s):
                 m.mul_(c.mu).add_(g)
-                upd = newton_schulz(g + c.mu * m, c.ns_steps).float()
                 rows, cols = s.shape[-2], s.shape[-1]
                 scale = 0.2 * math.sqrt(max(rows, cols)) if c.adjust_lr == "rms_norm" else \
                     (math.sqrt(max(1.0, rows / cols)) if c.adjust_lr == "spectral_norm" else 1.0)
+                if shared_upd is not None:
+                    if owner[s.name] == rank:
+                        shared_upd[sl].view(s.shape).copy_(newton_schulz(g + c.mu * m, c.ns_steps).float() * scale)
+                    continue
+                upd = newton_schulz(g + c.mu * m, c.ns_steps).float()
                 p.mul_(1 - lr * c.weight_decay).add_(upd, alpha=-lr * scale)
             else:
                 v = grp.exp_avg_sq[sl].view(s.shape)
@@ -511,6 +536,13 @@ class FlatOptimizer:
                 v.mul_(b2).addcmul_(g, g, value=1 - b2)
                 denom = v.sqrt() / math.sqrt(1 - b2 ** t) + 1e-8
                 p.mul_(1 - lr * c.weight_decay).addcdiv_(m, denom, value=-lr / (1 - b1 ** t))
+        if shared_upd is not None:
+            dist.all_reduce(shared_upd, group=group)
+            self.muon_owned = sum(1 for r in owner.values() if r == rank)
+            for s in buf.slots:
+                if s.name in owner:
+                    sl = slice(s.offset, s.offset + s.numel)
+                    buf.master[sl].mul_(1 - lr * c.weight_decay).add_(shared_upd[sl], alpha=-lr)
 
     # ------------------------------------------------------------------ state
     def state_dict(self) -> dict:

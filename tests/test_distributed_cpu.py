@@ -40,7 +40,8 @@ if dist.is_initialized():
 
 def _run(tmp_path, port, world, cfg):
     tag = (f"{world}_{cfg['model'].get('ep', 1)}_{cfg['model'].get('cp', 1)}_{cfg['model'].get('cp_style', 'ring')}"
-           f"_z{cfg['model'].get('zero_stage', 2)}_{'ac' if cfg['model'].get('ac') else 'noac'}")
+           f"_z{cfg['model'].get('zero_stage', 2)}_{'ac' if cfg['model'].get('ac') else 'noac'}"
+           f"_{cfg.get('optim', {}).get('type', 'adamw')}{int(bool(cfg.get('optim', {}).get('distributed', True)))}")
     script = tmp_path / f"worker_{tag}.py"
     out = tmp_path / f"out_{tag}"
     out.mkdir()
@@ -151,3 +152,23 @@ def test_cpu_optimizer_with_gradients_accumulated_on_the_host_matches_the_device
             assert a[1] == pytest.approx(b[1], rel=1e-3)
         assert dev[r]["wabs"] == pytest.approx(host[r]["wabs"], rel=1e-5)
         assert dev[r]["esum"] == pytest.approx(host[r]["esum"], rel=1e-5)
+
+
+@pytest.mark.slow
+def test_muon_with_the_orthogonalisations_dealt_out_matches_every_rank_doing_all(tmp_path, free_port):
+    """Two data-parallel ranks: with ``optim.distributed`` every matrix is orthogonalised by one rank and the updates are
+    summed; the weights and the losses must be those of the run where both ranks orthogonalise everything."""
+    runs = {}
+    for i, distributed in enumerate((False, True)):
+        cfg = json.loads(json.dumps(BASE))
+        cfg["model"]["name"] = "tiny-qwen3-moe"
+        cfg["optim"] = {"type": "muon", "lr": 1e-3, "max_norm": 1.0, "distributed": distributed}
+        runs[distributed] = _run(tmp_path, free_port + i, 2, cfg)
+    for r in range(2):
+        a, b = runs[False][r], runs[True][r]
+        assert a["wsum"] == pytest.approx(b["wsum"], rel=1e-6, abs=1e-7)
+        assert a["wabs"] == pytest.approx(b["wabs"], rel=1e-6)
+        assert a["esum"] == pytest.approx(b["esum"], rel=1e-6)
+        for x, y in zip(a["steps"], b["steps"]):
+            assert x[0] == pytest.approx(y[0], rel=1e-5, abs=1e-7)
+    assert runs[True][0]["wsum"] == pytest.approx(runs[True][1]["wsum"], rel=1e-9)
