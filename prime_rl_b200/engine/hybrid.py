@@ -12,8 +12,10 @@ it the three operations whose meaning depends on what came before the new tokens
                state and stores the state after its last token; a decode step runs one batched recurrence step for
                all sequences
 
-The state lives on the request's ``SequenceKV`` object, so it is dropped together with the pages when a request
-finishes or is preempted (a preempted request recomputes from its tokens). A recurrent state cannot be shared
+The states live in one pool per layer (``StatePool``: ``[slots, ...]``); a sequence owns one slot from its first step
+until its ``SequenceKV`` object dies (request finished, or preempted: a preempted request recomputes from its tokens).
+A decode step advances the slots of all running sequences in place with one launch per layer
+(``csrc/recurrent_step.cu``). A recurrent state cannot be shared
 through the page-level prefix cache, so engines of these families run without it.
 
 The reference serves these families through vLLM's hybrid KV-cache manager (one Mamba state slot per request next to
@@ -29,23 +31,62 @@ from ..ops import delta_rule, ssm
 from .runner import ModelRunner, StepInput
 
 
+class StatePool:
+    """Per (layer, kind) one tensor ``[capacity, ...]``; every live sequence owns one row index (its slot) in all of
+    them. Slots are handed out at a sequence's first step and return when its ``SequenceKV`` object dies."""
+
+    def __init__(self, device):
+        self.device, self.capacity = device, 0
+        self.tensors: dict[tuple, torch.Tensor] = {}
+        self.free: list[int] = []
+        self.next = 0
+
+    def slot(self, kv) -> int:
+        import weakref
+
+        sl = getattr(kv, "state_slot", None)
+        if sl is None:
+            sl = self.free.pop() if self.free else self.next
+            if sl == self.next:
+                self.next += 1
+            kv.state_slot = sl
+            weakref.finalize(kv, self.free.append, sl)
+        return sl
+
+    def get(self, key, shape, dtype) -> torch.Tensor:
+        t = self.tensors.get(key)
+        need = max(self.next, 1)
+        if t is None or t.shape[0] < need:
+            cap = max(8, 2 * need)
+            new = torch.zeros((cap, *shape), dtype=dtype, device=self.device)
+            if t is not None:
+                new[: t.shape[0]] = t
+            self.tensors[key] = t = new
+        return t
+
+    def clear(self, slot: int) -> None:
+        for t in self.tensors.values():
+            if slot < t.shape[0]:
+                t[slot].zero_()
+
+
 class RecurrentStep:
     def __init__(self, runner: "HybridRunner", batch: list[StepInput], starts: list[int], slots_t: torch.Tensor):
         self.runner, self.batch, self.starts, self.slots = runner, batch, starts, slots_t
+        self.pool = runner.pool
         self.lens = [len(s.tokens) for s in batch]
         self.decode = all(n == 1 and s.kv.length > 0 for n, s in zip(self.lens, batch))
-        for s in batch:
-            if s.kv.length == 0 or getattr(s.kv, "mixer_state", None) is None:
-                s.kv.mixer_state = {}               # a fresh (or restarted) sequence starts from nothing
+        self.state_slots = [self.pool.slot(s.kv) for s in batch]
+        for s, sl in zip(batch, self.state_slots):
+            if s.kv.length == 0:
+                self.pool.clear(sl)                 # a fresh (or restarted) sequence starts from nothing
+        self._slots_t = None
 
-    # ---------------------------------------------------------------- state bookkeeping
-    def _get(self, s: StepInput, key, shape, dtype, device):
-        st = s.kv.mixer_state
-        t = st.get(key)
-        if t is None:
-            t = torch.zeros(shape, dtype=dtype, device=device)
-            st[key] = t
-        return t
+    @property
+    def slots_t(self) -> torch.Tensor:
+        if self._slots_t is None:
+            self._slots_t = torch.tensor(self.state_slots, dtype=torch.int32, device=self.pool.device)
+        return self._slots_t
 
     # ---------------------------------------------------------------- attention
     def attend(self, layer: int, q, k, v, window, sinks):
@@ -58,57 +99,79 @@ class RecurrentStep:
     # ---------------------------------------------------------------- convolution
     def conv(self, layer: int, x, weight, bias, activation="silu"):
         K, C = weight.shape[1], x.shape[1]
-        key = (layer, "conv")
-        tails = [self._get(s, key, (K - 1, C), x.dtype, x.device) for s in self.batch]
+        tails = self.pool.get((layer, "conv"), (K - 1, C), x.dtype)
         if self.decode:
-            y, new = ssm.conv1d_step(torch.stack(tails), x, weight, bias, activation)
-            for s, t in zip(self.batch, new):
-                s.kv.mixer_state[key] = t
+            idx = self.slots_t.long()
+            y, new = ssm.conv1d_step(tails[idx], x, weight, bias, activation)
+            tails.index_copy_(0, idx, new)
             return y
         outs = []
-        for s, st, n, tail in zip(self.batch, self.starts, self.lens, tails):
-            y, new = ssm.conv1d_window(tail, x[st:st + n], weight, bias, activation)
-            s.kv.mixer_state[key] = new
+        for sl, st, n in zip(self.state_slots, self.starts, self.lens):
+            y, new = ssm.conv1d_window(tails[sl], x[st:st + n], weight, bias, activation)
+            tails[sl] = new
             outs.append(y)
         return torch.cat(outs, 0)
 
     # ---------------------------------------------------------------- Mamba-2
     def mamba(self, layer: int, x, dt, A, B, C, D, chunk: int):
         H, P, N = x.shape[1], x.shape[2], B.shape[2]
-        key = (layer, "ssm")
-        states = [self._get(s, key, (H, P, N), torch.float32, x.device) for s in self.batch]
+        states = self.pool.get((layer, "ssm"), (H, P, N), torch.float32)
         if self.decode:
-            y, new = ssm.mamba2_step(x, dt, A, B, C, D, torch.stack(states))
-            for s, t in zip(self.batch, new):
-                s.kv.mixer_state[key] = t
+            if x.is_cuda and N % 4 == 0:
+                from ..ops import _runtime as rt
+
+                n, G = x.shape[0], B.shape[1]
+                xf, dtf = x.float().contiguous(), dt.float().contiguous()
+                Bf, Cf = B.float().contiguous(), C.float().contiguous()
+                Af, Df = A.float().contiguous(), (D.float().contiguous() if D is not None else None)
+                y = torch.empty(n, H, P, dtype=torch.float32, device=x.device)
+                rt.check(rt.lib().prb_mamba2_step(states.data_ptr(), self.slots_t.data_ptr(), xf.data_ptr(), dtf.data_ptr(),
+                                                  Af.data_ptr(), Bf.data_ptr(), Cf.data_ptr(), rt.ptr(Df), y.data_ptr(), n,
+                                                  H, P, N, G, rt.stream_ptr(x.device)), "prb_mamba2_step")
+                return y
+            idx = self.slots_t.long()
+            y, new = ssm.mamba2_step(x, dt, A, B, C, D, states[idx])
+            states.index_copy_(0, idx, new)
             return y
         outs = []
-        for s, st, n, state in zip(self.batch, self.starts, self.lens, states):
+        for s, sl, st, n in zip(self.batch, self.state_slots, self.starts, self.lens):
             pos = torch.arange(s.kv.length, s.kv.length + n, dtype=torch.int32, device=x.device)
-            sl = slice(st, st + n)
-            y, new = ssm.mamba2_scan(x[sl], dt[sl], A, B[sl], C[sl], D, pos, chunk=chunk,
-                                     initial_state=state if s.kv.length else None, return_state=True)
-            s.kv.mixer_state[key] = new
+            r = slice(st, st + n)
+            y, new = ssm.mamba2_scan(x[r], dt[r], A, B[r], C[r], D, pos, chunk=chunk,
+                                     initial_state=states[sl] if s.kv.length else None, return_state=True)
+            states[sl] = new
             outs.append(y)
         return torch.cat(outs, 0)
 
     # ---------------------------------------------------------------- gated delta rule
     def delta(self, layer: int, q, k, v, g, beta):
         H, dk, dv = q.shape[1], q.shape[2], v.shape[2]
-        key = (layer, "delta")
-        states = [self._get(s, key, (H, dk, dv), torch.float32, q.device) for s in self.batch]
+        states = self.pool.get((layer, "delta"), (H, dk, dv), torch.float32)
         if self.decode:
-            o, new = delta_rule.gated_delta_rule_step(q, k, v, g, beta, torch.stack(states))
-            for s, t in zip(self.batch, new):
-                s.kv.mixer_state[key] = t
+            if q.is_cuda and dv <= 1024:
+                from ..ops import _runtime as rt
+
+                n = q.shape[0]
+                qf = (delta_rule._l2norm(q.float()) * dk ** -0.5).contiguous()
+                kf = delta_rule._l2norm(k.float()).contiguous()
+                vf, gf, bf = v.float().contiguous(), g.float().contiguous(), beta.float().contiguous()
+                o = torch.empty(n, H, dv, dtype=torch.float32, device=q.device)
+                rt.check(rt.lib().prb_delta_rule_step(states.data_ptr(), self.slots_t.data_ptr(), qf.data_ptr(),
+                                                      kf.data_ptr(), vf.data_ptr(), gf.data_ptr(), bf.data_ptr(),
+                                                      o.data_ptr(), n, H, dk, dv, rt.stream_ptr(q.device)),
+                         "prb_delta_rule_step")
+                return o
+            idx = self.slots_t.long()
+            o, new = delta_rule.gated_delta_rule_step(q, k, v, g, beta, states[idx])
+            states.index_copy_(0, idx, new)
             return o
         outs = []
-        for s, st, n, state in zip(self.batch, self.starts, self.lens, states):
+        for s, sl, st, n in zip(self.batch, self.state_slots, self.starts, self.lens):
             pos = torch.arange(s.kv.length, s.kv.length + n, dtype=torch.int32, device=q.device)
-            sl = slice(st, st + n)
-            o, new = delta_rule.gated_delta_rule(q[sl], k[sl], v[sl], g[sl], beta[sl], pos,
-                                                 initial_state=state if s.kv.length else None, return_state=True)
-            s.kv.mixer_state[key] = new
+            r = slice(st, st + n)
+            o, new = delta_rule.gated_delta_rule(q[r], k[r], v[r], g[r], beta[r], pos,
+                                                 initial_state=states[sl] if s.kv.length else None, return_state=True)
+            states[sl] = new
             outs.append(o)
         return torch.cat(outs, 0)
 
@@ -135,6 +198,7 @@ class HybridRunner(ModelRunner):
                                               f"(model type {model.arch.model_type})")
         if model.arch.hc_mult:
             raise NotImplementedError("the rollout engine does not serve hyper-connection models")
+        self.pool = StatePool(self.device)
 
     def _core(self, ids_t, pos_t, slots_t, rows_t, batch, starts):
         from .. import ops

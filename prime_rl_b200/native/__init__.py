@@ -80,6 +80,8 @@ _CUDA_SIGNATURES = {
     "prb_rl_loss": [P, P, P, P, P, P, L, I, F, F, F, F, P, P],
     "prb_router_topk": [P, P, P, P, P, P, P, L, I, I, I, I, F, P],
     "prb_moe_plan": [P, P, P, P, P, P, P, P, L, I, I, I, I, P],
+    "prb_mamba2_step": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
+    "prb_delta_rule_step": [P, P, P, P, P, P, P, P, I, I, I, I, P],
     "prb_moe_plan_range": [P, P, P, P, P, P, P, P, L, I, I, I, I, I, P],
     "prb_moe_gather_rows": [P, P, P, P, L, I, I, P, P],
     "prb_qkv_rope_cache": [P, P, P, P, P, P, P, P, P, P, P, L, I, I, I, F, P],

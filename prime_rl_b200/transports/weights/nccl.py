@@ -51,7 +51,7 @@ def layer_groups(names: list[str]) -> list[list[str]]:
     """One group per decoder layer plus one for everything else, in a stable order."""
     groups: dict[str, list[str]] = {}
     for n in names:
-        m = re.match(r"(model\.layers\.\d+)\.", n)
+        m = re.match(r"((?:model|backbone|language_model|model\.language_model)\.layers\.\d+)\.", n)
         groups.setdefault(m.group(1) if m else "_other", []).append(n)
     return list(groups.values())
 
@@ -104,16 +104,17 @@ class NCCLWeightSender(WeightSender):
             if not info["writer"]:
                 return
             per_layer = _gathered_layers(model, info)
+            n_groups = len(layer_groups([k for k in model.state_dict() if "lora_" not in k]))
         else:
             if not self.world.is_master:
                 return
             full = convert.model_state(model, "hf")
             per_layer = [{n: full[n] for n in names} for names in layer_groups(list(full))]
+            n_groups = len(per_layer)            # what the receiver is told to expect is what is sent
             info = None
         device = next(model.parameters()).device
         if self.world.is_master:
             self._connect(device)
-            n_groups = len(layer_groups(list(convert.model_state(model, "native"))))
             _broadcast(self.pg, torch.tensor([n_groups], dtype=torch.int64, device=device))
         for sd in per_layer:
             if not self.world.is_master:

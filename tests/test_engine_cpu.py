@@ -428,3 +428,17 @@ def test_engine_serves_the_recurrent_state_families(name):
             assert abs(float(lp[t, tok]) - r.logprobs[i]) < 1e-3
     # the states went away with the requests
     assert all(not r.kv.pages for r in out)
+
+
+@pytest.mark.parametrize("name", ["tiny-nemotron-h", "tiny-qwen3.5-moe", "tiny-qwen3-moe"])
+def test_weight_broadcast_groups_follow_the_checkpoint_naming_of_every_family(name):
+    """The in-memory weight broadcast announces a number of layer groups and then sends them; the groups are formed
+    from checkpoint-layout names, whose layer prefix differs between families (``model.layers``, ``backbone.layers``)."""
+    from prime_rl_b200.models import convert
+    from prime_rl_b200.transports.weights.nccl import layer_groups
+
+    arch = resolve_arch(name)
+    model = build_model(arch, device="cpu", dtype=torch.float32)
+    hf = layer_groups(list(convert.model_state(model, "hf")))
+    native = layer_groups(list(convert.model_state(model, "native")))
+    assert len(hf) == len(native) == arch.num_hidden_layers + 1

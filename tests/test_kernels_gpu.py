@@ -1321,3 +1321,42 @@ def test_moe_plan_over_an_expert_range_sums_to_the_full_plan(deterministic):
         total += moe.combine(moe.permute(x, plan) * 2.0, w, plan, T).float()
     rt.check_status()
     _close(total, y_full, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.gpu
+def test_recurrence_step_kernels_match_the_pytorch_steps():
+    """Decode-step kernels of the state-carrying mixers (in place on pooled states, sequences addressed by slot)."""
+    from prime_rl_b200.ops import delta_rule, ssm
+
+    torch.manual_seed(9)
+    lib = rt.lib()
+    n, H, P, N, G, cap = 5, 8, 64, 128, 2, 11
+    slots = torch.tensor([7, 0, 3, 10, 4], dtype=torch.int32, device=DEV)
+    pool = torch.randn(cap, H, P, N, device=DEV)
+    x, dt = torch.randn(n, H, P, device=DEV), torch.rand(n, H, device=DEV) * 0.1
+    A, D = -torch.rand(H, device=DEV), torch.randn(H, device=DEV)
+    B, C = torch.randn(n, G, N, device=DEV), torch.randn(n, G, N, device=DEV)
+    want_y, want_s = ssm.mamba2_step(x, dt, A, B, C, D, pool[slots.long()])
+    before = pool.clone()
+    y = torch.empty(n, H, P, device=DEV)
+    rt.check(lib.prb_mamba2_step(pool.data_ptr(), slots.data_ptr(), x.data_ptr(), dt.data_ptr(), A.data_ptr(),
+                                 B.data_ptr(), C.data_ptr(), D.data_ptr(), y.data_ptr(), n, H, P, N, G,
+                                 rt.stream_ptr(torch.device(DEV))), "prb_mamba2_step")
+    _close(y, want_y, atol=1e-3, rtol=1e-3)
+    _close(pool[slots.long()], want_s, atol=1e-4, rtol=1e-4)
+    untouched = [i for i in range(cap) if i not in slots.tolist()]
+    assert torch.equal(pool[untouched], before[untouched])
+
+    dk, dv = 128, 96
+    pool = torch.randn(cap, H, dk, dv, device=DEV) * 0.1
+    q, k, v = torch.randn(n, H, dk, device=DEV), torch.randn(n, H, dk, device=DEV), torch.randn(n, H, dv, device=DEV)
+    g, beta = -torch.rand(n, H, device=DEV), torch.rand(n, H, device=DEV)
+    want_o, want_s = delta_rule.gated_delta_rule_step(q, k, v, g, beta, pool[slots.long()])
+    qf = (delta_rule._l2norm(q) * dk ** -0.5).contiguous()
+    kf = delta_rule._l2norm(k).contiguous()
+    o = torch.empty(n, H, dv, device=DEV)
+    rt.check(lib.prb_delta_rule_step(pool.data_ptr(), slots.data_ptr(), qf.data_ptr(), kf.data_ptr(), v.data_ptr(),
+                                     g.data_ptr(), beta.data_ptr(), o.data_ptr(), n, H, dk, dv,
+                                     rt.stream_ptr(torch.device(DEV))), "prb_delta_rule_step")
+    _close(o, want_o, atol=1e-4, rtol=1e-3)
+    _close(pool[slots.long()], want_s, atol=1e-4, rtol=1e-3)

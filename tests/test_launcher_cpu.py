@@ -25,3 +25,22 @@ def test_rl_launcher_runs_three_processes_to_completion(tmp_path, free_port):
     orch, trainer = logs["orchestrator.log"], logs["trainer.log"]
     assert all(f"step {s} |" in orch for s in range(8)) and "policy v6" in orch     # the weights of step 5 arrived
     assert all(f"step {s} |" in trainer for s in range(8))
+
+
+@pytest.mark.slow
+def test_rl_launcher_with_a_recurrent_state_family(tmp_path, free_port):
+    """Nemotron-H (Mamba-2 + attention + MoE blocks) through the same three processes: the engine serves it with the
+    recurrent-state runner and takes the in-memory weight updates, whose layer groups follow the family's checkpoint
+    naming (``backbone.layers``)."""
+    toml = (ROOT / "examples" / "rl_low_token.toml").read_text().replace(
+        'id = "low-token"', 'id = "low-token"\nargs = { vocab_size = 512 }')
+    cfg = tmp_path / "rl.toml"
+    cfg.write_text(toml)
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=str(ROOT))
+    cmd = [sys.executable, "-m", "prime_rl_b200.entrypoints.rl", "@", str(cfg), "--output-dir", str(tmp_path / "out"),
+           "--max-steps", "4", "--model.name", "tiny-nemotron-h", "--inference.server.port", str(free_port),
+           "--weight-broadcast.type", "nccl", "--weight-broadcast.port", str(free_port + 7)]
+    r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    logs = {p.name: p.read_text() for p in tmp_path.rglob("*.log")}
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:] + "".join(f"\n== {k}\n{v[-1500:]}" for k, v in logs.items())
+    assert "policy v2" in logs["orchestrator.log"] and "step 3 |" in logs["trainer.log"]
