@@ -44,6 +44,10 @@ class Request:
     prefilled: bool = False
     preemptions: int = 0
     swapped: object = None          # kv_cache.HostKV while the request waits with its K / V in host memory
+    # prefill / decode disaggregation: a prefill-only request ends after its first sampled token with its K / V
+    # moved to host memory (``handoff``), ready to be imported by another engine (``Engine.submit_prefilled``)
+    prefill_only: bool = False
+    handoff: object = None
 
     @property
     def all_tokens(self) -> list[int]:
@@ -213,6 +217,42 @@ class Engine:
         self.submit(req)
         return await req.future
 
+    # ------------------------------------------------------------------ prefill / decode disaggregation
+    def _check_handoff_supported(self) -> None:
+        from .hybrid import HybridRunner
+
+        if isinstance(self.runner, HybridRunner) or self.tp_size > 1:
+            raise NotImplementedError("K / V hand-off between engines covers single-process engines of the attention "
+                                      "decoder families (a recurrent state or a sharded cache is not exported)")
+
+    async def prefill(self, prompt: list[int], params: SamplingParams, cache_salt: str = "") -> Request:
+        """Prefill role: runs the prompt, samples the first token and returns with ``handoff`` = the K / V of the
+        prompt in host memory (``finish_reason == "prefill_done"``; a request that ends at its first token
+        finishes normally and has nothing to hand off)."""
+        self._check_handoff_supported()
+        loop = asyncio.get_running_loop()
+        req = Request(prompt=list(prompt), params=params, cache_salt=cache_salt, loop=loop,
+                      future=loop.create_future(), prefill_only=True)
+        self.submit(req)
+        return await req.future
+
+    def submit_prefilled(self, prompt: list[int], output: list[int], logprobs: list[float], host_kv,
+                         params: SamplingParams, cache_salt: str = "", loop=None, future=None) -> Request:
+        """Decode role: a request whose prompt was run by another engine. ``host_kv`` (``kv_cache.HostKV``) holds the
+        K / V of the prompt; the request joins the queue like one that was swapped out and continues from
+        ``output[-1]`` without a prefill step."""
+        self._check_handoff_supported()
+        lay = self.cache.k.shape
+        if tuple(host_kv.data.shape[1:2]) != (lay[0],) or tuple(host_kv.data.shape[3:]) != tuple(lay[2:]):
+            raise ValueError(f"imported K / V {tuple(host_kv.data.shape)} does not fit this engine's cache layout "
+                             f"{tuple(lay)} (layers, page size, kv heads and head dim must match)")
+        req = Request(prompt=list(prompt), params=params, cache_salt=cache_salt, loop=loop, future=future)
+        req.output, req.logprobs = list(output), list(logprobs)
+        req.swapped, req.prefilled = host_kv, True
+        self.kv_offloaded += host_kv.nbytes
+        self.stats["kv_imports"] = self.stats.get("kv_imports", 0) + 1
+        return self.submit(req)
+
     def generate_sync(self, prompts: list[list[int]], params: SamplingParams, cache_salt: str = "") -> list[Request]:
         """Blocking helper for tests and benchmarks (runs the loop inline if no thread is active)."""
         reqs = [self.submit(Request(prompt=list(p), params=params, cache_salt=cache_salt)) for p in prompts]
@@ -246,6 +286,8 @@ class Engine:
 
     def _finish(self, r: Request, reason: str) -> None:
         r.finish_reason = reason
+        if reason == "prefill_done" and r.kv.pages:
+            r.handoff = self.cache.swap_out(r.kv, pin=False)       # the pages return to the pool
         self.cache.free(r.kv)
         if r.swapped is not None:
             self.kv_offloaded -= r.swapped.nbytes
@@ -417,7 +459,10 @@ class Engine:
             if masks is not None and r.params.return_sampling_mask:
                 r.masks.append(masks[i].cpu())
             n = len(r.output)
-            if n >= r.params.max_tokens:
+            if r.prefill_only and n >= 1 and n < r.params.max_tokens and not \
+                    (n >= r.params.min_tokens and (tok_l[i] == self.eos or tok_l[i] in r.params.stop_token_ids)):
+                self._finish(r, "prefill_done")
+            elif n >= r.params.max_tokens:
                 self._finish(r, "length")
             elif n >= r.params.min_tokens and (tok_l[i] == self.eos or tok_l[i] in r.params.stop_token_ids):
                 self._finish(r, "stop")

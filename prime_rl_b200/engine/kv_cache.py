@@ -132,6 +132,34 @@ class HostKV:
     def nbytes(self) -> int:
         return self.data.numel() * self.data.element_size()
 
+    def to_file(self, path) -> dict:
+        """Writes the K / V bytes to ``path`` (a file in shared memory when the peer engine runs on the same box) and
+        returns the description the importing side needs (``from_file``)."""
+        if self.ready is not None:
+            self.ready.synchronize()
+        self.data.contiguous().view(torch.uint8).numpy().tofile(str(path))
+        return {"path": str(path), "shape": list(self.data.shape), "dtype": str(self.data.dtype).replace("torch.", ""),
+                "length": int(self.length)}
+
+    @classmethod
+    def from_file(cls, meta: dict, delete: bool = True) -> "HostKV":
+        import os
+
+        dtype = getattr(torch, meta["dtype"])
+        shape = tuple(int(x) for x in meta["shape"])
+        n = 1
+        for d in shape:
+            n *= d
+        raw = torch.from_file(str(meta["path"]), shared=False, size=n * torch.empty((), dtype=dtype).element_size(),
+                              dtype=torch.uint8)
+        data = raw.view(dtype).view(shape).clone()
+        if delete:
+            try:
+                os.unlink(meta["path"])
+            except OSError:
+                pass
+        return cls(data, int(meta["length"]), None)
+
 
 class KVCache:
     """Pools ``k[layer]``, ``v[layer]``: ``[num_pages, page_size, kv_heads, head_dim]``."""

@@ -41,7 +41,11 @@ class HashRing:
 
 
 class Router:
-    def __init__(self, urls: list[str], transports: list | None = None, timeout: float = 3600.0):
+    def __init__(self, urls: list[str], transports: list | None = None, timeout: float = 3600.0,
+                 prefill_urls: list[str] | None = None, prefill_transports: list | None = None):
+        """``prefill_urls``: replicas that only run prompts (prefill / decode disaggregation). A generate request
+        then goes to one of them first (``/inference/v1/prefill``); the K / V description and the first token it
+        returns travel with the request to one of the decode replicas (``urls``), which continues from there."""
         import httpx
 
         if not urls:
@@ -50,6 +54,12 @@ class Router:
         self.clients = [httpx.AsyncClient(base_url=u, timeout=timeout,
                                           transport=(transports[i] if transports else None))
                         for i, u in enumerate(self.urls)]
+        self.prefill_urls = [u.rstrip("/") for u in (prefill_urls or [])]
+        self.prefill_clients = [httpx.AsyncClient(base_url=u, timeout=timeout,
+                                                  transport=(prefill_transports[i] if prefill_transports else None))
+                                for i, u in enumerate(self.prefill_urls)]
+        self.prefill_inflight = [0] * len(self.prefill_urls)
+        self.handoffs = 0
         self.inflight = [0] * len(urls)
         self.served = [0] * len(urls)
         self.ring = HashRing(list(range(len(urls))))
@@ -60,7 +70,49 @@ class Router:
             return self.ring.node(str(key))
         return min(range(len(self.urls)), key=lambda i: (self.inflight[i], self.served[i]))
 
+    async def _disaggregated(self, body: dict, headers) -> tuple[int, dict | str]:
+        """One sample per hand-off: prefill replica (least loaded) -> decode replica (the usual choice)."""
+        sp = dict(body.get("sampling_params") or {})
+        n = int(sp.pop("n", 1) or 1)
+
+        async def one():
+            j = min(range(len(self.prefill_clients)), key=lambda i: self.prefill_inflight[i])
+            self.prefill_inflight[j] += 1
+            try:
+                r = await self.prefill_clients[j].post("/inference/v1/prefill", json=dict(body, sampling_params=sp))
+            finally:
+                self.prefill_inflight[j] -= 1
+            first = _payload(r)
+            if r.status_code != 200:
+                return r.status_code, first
+            if not first.get("kv_transfer_params"):        # ended at its first token: nothing left to decode
+                out = first["prefill_output"]
+                return 200, {"id": first["id"], "model": first["model"], "policy_version": first.get("policy_version"),
+                             "usage": first["usage"],
+                             "choices": [{"index": 0, "token_ids": out["token_ids"], "logprobs": out["logprobs"],
+                                          "finish_reason": first["finish_reason"], "prompt_logprobs": None,
+                                          "routed_experts": None, "sampling_mask": None}]}
+            self.handoffs += 1
+            return await self._forward_to_decode("/inference/v1/generate",
+                                                 dict(body, sampling_params=sp, prefill_output=first["prefill_output"],
+                                                      kv_transfer_params=first["kv_transfer_params"]), headers)
+
+        results = await asyncio.gather(*[one() for _ in range(n)])
+        bad = next((r for r in results if r[0] != 200), None)
+        if bad is not None:
+            return bad
+        merged = dict(results[0][1])
+        merged["choices"] = [dict(r[1]["choices"][0], index=i) for i, r in enumerate(results)]
+        merged["usage"] = {"prompt_tokens": results[0][1]["usage"]["prompt_tokens"],
+                           "completion_tokens": sum(r[1]["usage"]["completion_tokens"] for r in results)}
+        return 200, merged
+
     async def forward(self, path: str, body: dict, headers) -> tuple[int, dict | str]:
+        if self.prefill_clients and path == "/inference/v1/generate" and not body.get("kv_transfer_params"):
+            return await self._disaggregated(body, headers)
+        return await self._forward_to_decode(path, body, headers)
+
+    async def _forward_to_decode(self, path: str, body: dict, headers) -> tuple[int, dict | str]:
         i = self.pick(body, headers)
         self.inflight[i] += 1
         try:
@@ -83,10 +135,11 @@ class Router:
                 r = await c.post(path, json=b)
             return r.status_code, _payload(r)
 
-        return list(await asyncio.gather(*[one(i, c) for i, c in enumerate(self.clients)]))
+        # prefill replicas hold weights too: admin commands (pause, weight updates, ...) reach every engine
+        return list(await asyncio.gather(*[one(i, c) for i, c in enumerate(self.clients + self.prefill_clients)]))
 
     async def close(self) -> None:
-        await asyncio.gather(*[c.aclose() for c in self.clients])
+        await asyncio.gather(*[c.aclose() for c in self.clients + self.prefill_clients])
 
 
 def _payload(r):
@@ -179,7 +232,9 @@ def build_app(router: Router):
 
     @app.get("/router/state")
     async def state():
-        return {"replicas": router.urls, "inflight": router.inflight, "served": router.served}
+        return {"replicas": router.urls, "inflight": router.inflight, "served": router.served,
+                "prefill_urls": router.prefill_urls, "prefill_inflight": router.prefill_inflight,
+                "handoffs": router.handoffs}
 
     return app
 
@@ -195,10 +250,14 @@ def main(argv: list[str] | None = None) -> None:
     ap.add_argument("--host", default="0.0.0.0")
     ap.add_argument("--port", type=int, default=8000)
     ap.add_argument("--backends", required=True, help="comma-separated base URLs of the engine servers")
+    ap.add_argument("--prefill-backends", default="", help="comma-separated base URLs of prefill-only engine servers "
+                    "(prefill / decode disaggregation: --backends are then the decode engines)")
     ap.add_argument("--timeout", type=float, default=3600.0)
     args = ap.parse_args(argv)
     urls = [u for u in (x.strip() for x in args.backends.split(",")) if u]
-    uvicorn.run(build_app(Router(urls, timeout=args.timeout)), host=args.host, port=args.port, log_level="warning")
+    pre = [u for u in (x.strip() for x in args.prefill_backends.split(",")) if u]
+    uvicorn.run(build_app(Router(urls, timeout=args.timeout, prefill_urls=pre)), host=args.host, port=args.port,
+                log_level="warning")
 
 
 if __name__ == "__main__":

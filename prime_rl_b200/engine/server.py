@@ -92,7 +92,23 @@ def build_app(engine: Engine, model_name: str, tokenizer=None, liveness_timeout:
         if body.get("return_sampling_mask") or app.state.__dict__.get("return_sampling_mask"):
             params.return_sampling_mask = True
         salt = str(body.get("cache_salt", ""))
-        reqs = await asyncio.gather(*[engine.generate(token_ids, params, salt) for _ in range(n)])
+        kvp = body.get("kv_transfer_params")
+        if kvp:
+            # decode role of a disaggregated deployment: the prompt was run by a prefill engine, whose K / V and first
+            # token come with the request (``/inference/v1/prefill`` of that engine produced them)
+            from .kv_cache import HostKV
+
+            first = body.get("prefill_output") or {}
+            loop = asyncio.get_running_loop()
+            fut = loop.create_future()
+            try:
+                engine.submit_prefilled(token_ids, list(first.get("token_ids") or []), list(first.get("logprobs") or []),
+                                        HostKV.from_file(kvp), params, salt, loop=loop, future=fut)
+            except (ValueError, NotImplementedError, OSError) as e:
+                raise HTTPException(400, f"cannot import the transferred K / V: {e}")
+            reqs = [await fut]
+        else:
+            reqs = await asyncio.gather(*[engine.generate(token_ids, params, salt) for _ in range(n)])
         choices = []
         for i, r in enumerate(reqs):
             choices.append({
@@ -101,6 +117,35 @@ def build_app(engine: Engine, model_name: str, tokenizer=None, liveness_timeout:
                 "sampling_mask": _encode_mask(r.masks)})
         return {"id": reqs[0].request_id, "model": body.get("model", model_name), "choices": choices,
                 "usage": {"prompt_tokens": len(token_ids), "completion_tokens": sum(len(r.output) for r in reqs)},
+                "policy_version": engine.policy_version}
+
+    @app.post("/inference/v1/prefill")
+    async def prefill(body: dict):
+        """Prefill role of a disaggregated deployment: runs the prompt and samples the first token. The K / V of the
+        prompt are written to a file under ``kv_transfer_dir`` (shared memory on one box) and described in
+        ``kv_transfer_params``, which the router passes on to a decode engine together with ``prefill_output``."""
+        import os
+        import tempfile
+        import uuid
+
+        token_ids = body.get("token_ids")
+        if not token_ids:
+            raise HTTPException(400, "token_ids is required")
+        sp = dict(body.get("sampling_params") or {})
+        sp.pop("n", None)
+        params = SamplingParams.from_dict(sp)
+        try:
+            r = await engine.prefill(token_ids, params, str(body.get("cache_salt", "")))
+        except NotImplementedError as e:
+            raise HTTPException(501, str(e))
+        kvp = None
+        if r.finish_reason == "prefill_done" and r.handoff is not None:
+            root = body.get("kv_transfer_dir") or ("/dev/shm" if os.path.isdir("/dev/shm") else tempfile.gettempdir())
+            kvp = r.handoff.to_file(os.path.join(root, f"prb_kv_{uuid.uuid4().hex}.bin"))
+            r.handoff = None
+        return {"id": r.request_id, "model": body.get("model", model_name), "finish_reason": r.finish_reason,
+                "prefill_output": {"token_ids": r.output, "logprobs": r.logprobs}, "kv_transfer_params": kvp,
+                "usage": {"prompt_tokens": len(token_ids), "completion_tokens": len(r.output)},
                 "policy_version": engine.policy_version}
 
     def _need_tokenizer():

@@ -119,11 +119,15 @@ def serve_tensor_parallel(config: InferenceConfig, argv: list[str]) -> int:
     return 0
 
 
-def serve_replicas(config: InferenceConfig, argv: list[str]) -> int:
+def serve_replicas(config: InferenceConfig, argv: list[str], prefill_replicas: int = 0) -> int:
     """Data-parallel serving on one node: ``data_parallel_size`` engine processes, one GPU each, on
     the ports after ``server.port``, and the request router (``engine/router.py``) on ``server.port``
     in this process. The children get the same command line plus their own port and a replica
-    count of one; the first child that dies takes the service down."""
+    count of one; the first child that dies takes the service down.
+
+    ``prefill_replicas`` > 0 (``deployment.type = "disaggregated"`` on one node): that many more engine
+    processes that only run prompts; the router sends every request to one of them first and hands its K / V
+    (a file in shared memory) and first token to one of the ``data_parallel_size`` decode engines."""
     import os
     import subprocess
     import sys
@@ -135,16 +139,20 @@ def serve_replicas(config: InferenceConfig, argv: list[str]) -> int:
     from ..engine.router import Router, build_app
     from ..utils.process import Supervisor
 
-    n, port = config.vllm.data_parallel_size, config.server.port
+    decode_n, port = config.vllm.data_parallel_size, config.server.port
+    n = decode_n + prefill_replicas
     visible = os.environ.get("CUDA_VISIBLE_DEVICES")
-    gpus = [g for g in visible.split(",") if g] if visible else [str(i) for i in range(n)]
+    gpus = [g for g in visible.split(",") if g] if visible is not None else [str(i) for i in range(n)]
     tp = config.vllm.tensor_parallel_size                # every replica may itself span several GPUs
-    if len(gpus) < n * tp:
-        raise ValueError(f"data_parallel_size={n} x tensor_parallel_size={tp} but only {len(gpus)} GPUs are visible")
+    if prefill_replicas and tp > 1:
+        raise ValueError("prefill / decode disaggregation runs single-GPU engines (the K / V hand-off is per process)")
+    if visible != "" and len(gpus) < n * tp:
+        raise ValueError(f"{n} replicas x tensor_parallel_size={tp} but only {len(gpus)} GPUs are visible")
     sup = Supervisor()
     urls = []
     for i in range(n):
         env = dict(os.environ, CUDA_VISIBLE_DEVICES=",".join(gpus[i * tp:(i + 1) * tp]))
+        env["PRIME_RL_ENGINE_CHILD"] = "1"             # the child serves one engine whatever the deployment says
         cmd = [sys.executable, "-m", "prime_rl_b200.entrypoints.inference", *argv, "--vllm.data-parallel-size", "1",
                "--server.port", str(port + 1 + i), "--server.host", "127.0.0.1", "--vllm.data-parallel-rpc-port",
                str(config.vllm.data_parallel_rpc_port + i)]
@@ -162,7 +170,8 @@ def serve_replicas(config: InferenceConfig, argv: list[str]) -> int:
                 sup.shutdown()
                 raise RuntimeError("an engine replica did not come up")
             time.sleep(1.0)
-    server = uvicorn.Server(uvicorn.Config(build_app(Router(urls)), host=config.server.host or "0.0.0.0", port=port,
+    router = Router(urls[:decode_n], prefill_urls=urls[decode_n:])      # the first ``decode_n`` processes decode
+    server = uvicorn.Server(uvicorn.Config(build_app(router), host=config.server.host or "0.0.0.0", port=port,
                                            log_level="warning"))
     import threading
 
@@ -187,6 +196,14 @@ def main(argv: list[str] | None = None) -> None:
         print(config.to_json())
         return
     setup_logger(config.log.level, tag="inference", json_logging=config.log.json_logging)
+    import os
+
+    dep = config.deployment
+    if dep.type == "disaggregated" and config.slurm is None and not os.environ.get("PRIME_RL_ENGINE_CHILD"):
+        # one node: ``num_decode_replicas`` decode engines and ``num_prefill_replicas`` prefill engines behind the router
+        config.vllm.data_parallel_size = dep.num_decode_replicas
+        serve_replicas(config, args, prefill_replicas=dep.num_prefill_replicas)
+        return
     if config.vllm.data_parallel_size > 1:
         serve_replicas(config, args)
         return

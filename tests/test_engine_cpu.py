@@ -442,3 +442,114 @@ def test_weight_broadcast_groups_follow_the_checkpoint_naming_of_every_family(na
     hf = layer_groups(list(convert.model_state(model, "hf")))
     native = layer_groups(list(convert.model_state(model, "native")))
     assert len(hf) == len(native) == arch.num_hidden_layers + 1
+
+
+def test_prefill_decode_disaggregation_through_the_router(tmp_path):
+    """One prefill engine and one decode engine behind the router: the prompt runs on the first, its K / V travel as
+    a file, the second continues without a prefill step; tokens and log-probabilities are those of a single engine.
+    Admin calls reach both roles."""
+    import asyncio
+
+    import httpx
+
+    from prime_rl_b200.engine.router import Router, build_app as build_router
+    from prime_rl_b200.engine.server import build_app
+
+    arch = resolve_arch("tiny-qwen3")
+    mk = lambda: Engine(build_model(arch, device="cpu", dtype=torch.float32, seed=3), num_pages=128)
+    single = mk()
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, arch.vocab_size, (n,), generator=g).tolist() for n in (20, 37, 5)]
+    want = single.generate_sync(prompts, SamplingParams(max_tokens=6, temperature=0.0))
+    pre, dec = mk().start(), mk().start()
+    router = Router(["http://decode"], transports=[httpx.ASGITransport(app=build_app(dec, "tiny-qwen3"))],
+                    prefill_urls=["http://prefill"],
+                    prefill_transports=[httpx.ASGITransport(app=build_app(pre, "tiny-qwen3"))])
+    app = build_router(router)
+
+    async def go():
+        async with httpx.AsyncClient(transport=httpx.ASGITransport(app=app), base_url="http://router") as c:
+            for p, w in zip(prompts, want):
+                body = {"token_ids": p, "sampling_params": {"max_tokens": 6, "temperature": 0.0},
+                        "kv_transfer_dir": str(tmp_path)}
+                r = await c.post("/inference/v1/generate", json=body)
+                assert r.status_code == 200, r.text
+                ch = r.json()["choices"][0]
+                assert ch["token_ids"] == w.output and ch["finish_reason"] == "length"
+                assert max(abs(a - b) for a, b in zip(ch["logprobs"], w.logprobs)) < 1e-4
+            # several samples of one prompt: one hand-off each
+            r = await c.post("/inference/v1/generate", json={"token_ids": prompts[0], "kv_transfer_dir": str(tmp_path),
+                                                            "sampling_params": {"max_tokens": 4, "temperature": 1.0, "n": 3}})
+            assert r.status_code == 200 and [c_["index"] for c_ in r.json()["choices"]] == [0, 1, 2]
+            assert r.json()["usage"]["completion_tokens"] == 12
+            # a request that ends at its first token never reaches the decode engine
+            r = await c.post("/inference/v1/generate", json={"token_ids": prompts[1], "kv_transfer_dir": str(tmp_path),
+                                                            "sampling_params": {"max_tokens": 1, "temperature": 0.0}})
+            assert r.status_code == 200 and r.json()["choices"][0]["token_ids"] == want[1].output[:1]
+            assert (await c.post("/pause")).json()["replicas"] == 2 and pre.paused and dec.paused
+            assert (await c.post("/resume")).status_code == 200
+
+    try:
+        asyncio.run(go())
+    finally:
+        pre.shutdown()
+        dec.shutdown()
+    assert router.handoffs == 6
+    assert dec.stats["prompt_tokens"] == 0 and dec.stats["kv_imports"] == 6          # the decode engine never prefilled
+    assert pre.stats["generation_tokens"] == 7                                       # one token per prompt run
+    assert not list(tmp_path.glob("prb_kv_*"))                                       # every K / V file was consumed
+    assert pre.cache.blocks.num_available == 128 and dec.cache.blocks.num_available == 128
+
+
+@pytest.mark.slow
+def test_disaggregated_deployment_as_processes(tmp_path, free_port):
+    """``deployment.type = "disaggregated"`` on one node: one prefill and one decode engine process and the router in
+    front; greedy tokens equal those of a local engine, and the decode engine reports no prompt tokens."""
+    import os
+    import signal
+    import subprocess
+    import sys
+    import time
+    from pathlib import Path
+
+    import httpx
+
+    root = Path(__file__).resolve().parents[1]
+    port = free_port
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=str(root))
+    log = open(tmp_path / "server.log", "w")
+    proc = subprocess.Popen([sys.executable, "-m", "prime_rl_b200.entrypoints.inference", "@",
+                             str(root / "examples" / "inference.toml"), "--deployment.type", "disaggregated",
+                             "--deployment.num-prefill-replicas", "1", "--deployment.num-decode-replicas", "1",
+                             "--server.port", str(port), "--server.host", "127.0.0.1", "--vllm.num-pages", "256"],
+                            env=env, cwd=str(root), stdout=log, stderr=subprocess.STDOUT, start_new_session=True)
+    try:
+        base = f"http://127.0.0.1:{port}"
+        deadline = time.time() + 240
+        while True:
+            try:
+                if httpx.get(base + "/health", timeout=2).status_code == 200:
+                    break
+            except httpx.HTTPError:
+                pass
+            assert proc.poll() is None and time.time() < deadline, (tmp_path / "server.log").read_text()[-3000:]
+            time.sleep(1.0)
+        prompt = [5, 17, 99, 3, 42, 8, 250, 77, 12, 900, 31]
+        body = {"token_ids": prompt, "sampling_params": {"max_tokens": 6, "temperature": 0.0}}
+        r = httpx.post(base + "/inference/v1/generate", json=body, timeout=120)
+        assert r.status_code == 200, r.text
+        arch = resolve_arch("tiny-qwen3-moe")
+        local = Engine(build_model(arch, device=torch.device("cpu"), dtype=torch.float32, seed=0), num_pages=64)
+        want = local.generate_sync([prompt], SamplingParams(max_tokens=6, temperature=0.0))[0].output
+        assert r.json()["choices"][0]["token_ids"] == want
+        st = httpx.get(base + "/router/state", timeout=10).json()
+        assert st["handoffs"] == 1 and len(st["prefill_urls"]) == 1
+        decode_metrics = httpx.get(f"http://127.0.0.1:{port + 1}/metrics", timeout=10).text
+        assert "vllm:prompt_tokens_total 0" in decode_metrics
+    finally:
+        os.killpg(proc.pid, signal.SIGTERM)
+        try:
+            proc.wait(timeout=30)
+        except subprocess.TimeoutExpired:
+            os.killpg(proc.pid, signal.SIGKILL)
+        log.close()
