@@ -62,7 +62,45 @@ class Mamba2Mixer(nn.Module):
         self.D.fill_(1.0)
         nn.init.uniform_(self.conv1d_weight, -0.5, 0.5)
 
+    def _forward_cp(self, x: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
+        """Context parallelism: the local tokens' projections are exchanged for the whole sequence of ``heads / cp``
+        heads (B / C groups are gathered whole), convolution and scan run on those, the result goes back."""
+        cp = seq.cp
+        if self.nh % cp.cp:
+            raise ValueError(f"{self.nh} Mamba heads cannot be split over cp = {cp.cp}")
+        nh_l = self.nh // cp.cp
+        h0 = cp.rank * nh_l
+        gate, conv_in, dt = self.in_proj(x).split([self.inner, self.conv_dim, self.nh], dim=-1)
+        hs_in, bc_in = conv_in.split([self.inner, 2 * self.ng * self.ns], dim=-1)
+        hs_in = cp.seq_to_heads(hs_in.contiguous())                       # [T, nh_l * hd]
+        bc_in = cp.gather_seq(bc_in)                                      # [T, 2 ng ns]
+        dt = cp.seq_to_heads(dt.contiguous())                             # [T, nh_l]
+        T = hs_in.shape[0]
+        ch = slice(h0 * self.hd, (h0 + nh_l) * self.hd)
+        w = torch.cat([self.conv1d_weight[ch], self.conv1d_weight[self.inner:]], 0)
+        b = None if self.conv1d_bias is None else torch.cat([self.conv1d_bias[ch], self.conv1d_bias[self.inner:]], 0)
+        pos = cp.full_positions(seq)
+        conv = ssm.causal_conv1d(torch.cat([hs_in, bc_in], -1), w, b, pos, "silu")
+        hs, Bm, Cm = conv.split([nh_l * self.hd, self.ng * self.ns, self.ng * self.ns], dim=-1)
+        dtp = F.softplus(dt.float() + self.dt_bias[h0:h0 + nh_l])
+        lo, hi = self.arch.time_step_limit
+        if lo > 0.0 or math.isfinite(hi):
+            dtp = dtp.clamp(lo, hi)
+        # the heads of one group are consecutive: the local heads see the groups they belong to
+        rep = self.nh // self.ng
+        groups = torch.arange(h0, h0 + nh_l, device=x.device) // rep
+        Bh = Bm.reshape(T, self.ng, self.ns)[:, groups]                   # one "group" per local head
+        Ch = Cm.reshape(T, self.ng, self.ns)[:, groups]
+        y = ssm.mamba2_scan(hs.reshape(T, nh_l, self.hd), dtp, -torch.exp(self.A_log.float()[h0:h0 + nh_l]), Bh, Ch,
+                            self.D[h0:h0 + nh_l], pos, chunk=self.arch.ssm_chunk_size)
+        y = cp.heads_to_seq(y.reshape(T, nh_l * self.hd).to(x.dtype))     # [Tl, inner]
+        y = ssm.gated_rms_norm(y, gate, self.norm_weight, self.arch.rms_norm_eps, self.inner // self.ng, "silu",
+                               gate_first=True)
+        return self.out_proj(y)
+
     def forward(self, x: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
+        if seq.cp is not None and seq.engine is None:
+            return self._forward_cp(x, seq)
         T = x.shape[0]
         gate, conv_in, dt = self.in_proj(x).split([self.inner, self.conv_dim, self.nh], dim=-1)
         eng = seq.engine                 # rollout engine: state of the sequences before these tokens (engine/hybrid.py)
@@ -115,7 +153,40 @@ class GatedDeltaNet(nn.Module):
         self.dt_bias.fill_(1.0)
         nn.init.uniform_(self.conv1d_weight, -0.5, 0.5)
 
+    def _forward_cp(self, x: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
+        """Context parallelism: whole sequence of ``heads / cp`` key and value heads per rank (see ``Mamba2Mixer``)."""
+        cp = seq.cp
+        if self.nk % cp.cp or self.nv % cp.cp:
+            raise ValueError(f"{self.nk} key / {self.nv} value heads cannot be split over cp = {cp.cp}")
+        nk_l, nv_l = self.nk // cp.cp, self.nv // cp.cp
+        k0, v0 = cp.rank * nk_l, cp.rank * nv_l
+        q_in, k_in, v_in = self.in_proj_qkv(x).split([self.key_dim, self.key_dim, self.value_dim], dim=-1)
+        q_in, k_in, v_in = (cp.seq_to_heads(t.contiguous()) for t in (q_in, k_in, v_in))
+        T = q_in.shape[0]
+        kq, kv_ = slice(k0 * self.dk, (k0 + nk_l) * self.dk), slice(v0 * self.dv, (v0 + nv_l) * self.dv)
+        w = self.conv1d_weight
+        wl = torch.cat([w[: self.key_dim][kq], w[self.key_dim: 2 * self.key_dim][kq], w[2 * self.key_dim:][kv_]], 0)
+        pos = cp.full_positions(seq)
+        qkv = ssm.causal_conv1d(torch.cat([q_in, k_in, v_in], -1), wl, None, pos, "silu")
+        q, k, v = qkv.split([nk_l * self.dk, nk_l * self.dk, nv_l * self.dv], dim=-1)
+        beta = torch.sigmoid(cp.seq_to_heads(self.in_proj_b(x).contiguous()).float())
+        a = cp.seq_to_heads(self.in_proj_a(x).contiguous()).float()
+        g = -torch.exp(self.A_log.float()[v0:v0 + nv_l]) * F.softplus(a + self.dt_bias[v0:v0 + nv_l])
+        q, k = q.reshape(T, nk_l, self.dk), k.reshape(T, nk_l, self.dk)
+        rep = self.nv // self.nk
+        if rep > 1:
+            q, k = q.repeat_interleave(rep, dim=1), k.repeat_interleave(rep, dim=1)
+        o = delta_rule.gated_delta_rule(q, k, v.reshape(T, nv_l, self.dv), g, beta, pos)
+        o = cp.heads_to_seq(o.reshape(T, nv_l * self.dv).to(x.dtype))      # [Tl, value_dim]
+        Tl = x.shape[0]
+        z = self.in_proj_z(x).reshape(Tl, self.nv, self.dv)
+        o = ssm.gated_rms_norm(o.reshape(Tl, self.nv, self.dv), z, self.norm_weight, self.arch.rms_norm_eps, self.dv,
+                               "silu", gate_first=False)
+        return self.out_proj(o.reshape(Tl, self.value_dim))
+
     def forward(self, x: torch.Tensor, seq: SeqInfo) -> torch.Tensor:
+        if seq.cp is not None and seq.engine is None:
+            return self._forward_cp(x, seq)
         T = x.shape[0]
         eng = seq.engine                 # rollout engine: state of the sequences before these tokens (engine/hybrid.py)
         if eng is not None:
@@ -183,6 +254,8 @@ class GatedAttention(nn.Module):
             k = ops.qknorm_rope(k, self.k_norm.weight, seq.position_ids, self.inv_freq, self.arch.rms_norm_eps)
         if seq.engine is not None:
             o = seq.engine.attend(self.layer_idx, q, k, v, None, None)
+        elif seq.cp is not None:
+            o = seq.cp.attention(q, k, v, seq, backend=self.backend)
         else:
             o = attn_ops.attention(q, k, v, seq.cu_seqlens, seq.max_seqlen, causal=True, backend=self.backend,
                                    cache=seq.attn_cache, cache_key=self.layer_idx)

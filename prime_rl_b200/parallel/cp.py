@@ -236,6 +236,38 @@ class ContextParallel:
             ent = self._to_global_order(_AllGatherSeq.apply(entropy, self.group, False))
         return lp, ent
 
+    # ------------------------------------------------------------------ recurrent mixers
+    # A recurrent state cannot be cut along the sequence, so the state-carrying mixers (Mamba-2, gated delta-net) trade
+    # the sequence split for a head split: every rank gets the WHOLE sequence of its own heads, runs convolution and
+    # scan on them, and goes back (reference: src/prime_rl/trainer/models/nemotron_h/mamba.py:20-48). Contiguous
+    # token layout only (``cp_style = "ulysses"``).
+    def seq_to_heads(self, x: torch.Tensor) -> torch.Tensor:
+        """``[Tl, F]`` (all features of the local tokens) -> ``[T, F / cp]`` (this rank's feature block of all tokens)."""
+        if self.layout != "contiguous":
+            raise ValueError("recurrent mixers under context parallelism need the contiguous token layout "
+                             "(cp_style = 'ulysses')")
+        Tl, F = x.shape
+        x = x.reshape(Tl, self.cp, F // self.cp).permute(1, 0, 2).contiguous()
+        return self._exchange(x).reshape(self.cp * Tl, F // self.cp)
+
+    def heads_to_seq(self, x: torch.Tensor) -> torch.Tensor:
+        """``[T, F / cp]`` -> ``[Tl, F]``: inverse of ``seq_to_heads``."""
+        T, Fl = x.shape
+        x = self._exchange(x.reshape(self.cp, T // self.cp, Fl).contiguous())          # [cp (feature block), Tl, Fl]
+        return x.permute(1, 0, 2).reshape(T // self.cp, self.cp * Fl)
+
+    def gather_seq(self, x: torch.Tensor) -> torch.Tensor:
+        """``[Tl, F]`` -> ``[T, F]`` on every rank (features every rank needs whole: the B / C groups of Mamba-2);
+        gradients are summed over the ranks."""
+        return _AllGatherSeq.apply(x.contiguous(), self.group, True)
+
+    def full_positions(self, seq: SeqInfo) -> torch.Tensor:
+        """Position of every token of the whole packed sequence inside its document."""
+        cu = seq.full_cu_seqlens.to(torch.long)
+        pos = torch.arange(seq.full_len, device=cu.device)
+        doc = torch.searchsorted(cu[1:].contiguous(), pos, right=True)
+        return (pos - cu[doc]).to(torch.int32)
+
     # ------------------------------------------------------------------ attention
     def _doc_ids(self, cu, T, device):
         pos = torch.arange(T, device=device)

@@ -27,7 +27,7 @@ for _ in range(2):
     m = tr.step()
     out.append([m["loss"], m["optim/grad_norm"], m["entropy"]])
 with tr.model.full_parameters():
-    w = tr.model.model.layers[0].self_attn.qkv_proj.weight.detach().double().clone()
+    w = next(p for _, p in tr.model.model.layers[0].named_parameters() if p.dim() == 2).detach().double().clone()
     e = tr.model.model.embed_tokens.weight.detach().double().clone()
 res = dict(rank=tr.world.rank, steps=out, wsum=float(w.sum()), wabs=float(w.abs().sum()), esum=float(e.abs().sum()),
            fsdp=getattr(tr.model.layer_hooks, "stats", None))
@@ -172,3 +172,23 @@ def test_muon_with_the_orthogonalisations_dealt_out_matches_every_rank_doing_all
         for x, y in zip(a["steps"], b["steps"]):
             assert x[0] == pytest.approx(y[0], rel=1e-5, abs=1e-7)
     assert runs[True][0]["wsum"] == pytest.approx(runs[True][1]["wsum"], rel=1e-9)
+
+
+@pytest.mark.slow
+@pytest.mark.parametrize("name", ["tiny-nemotron-h", "tiny-qwen3.5-moe"])
+def test_cp2_of_the_recurrent_state_families_matches_single_process(tmp_path, free_port, name):
+    """Mamba-2 / gated delta-net layers under context parallelism: the sequence split is traded for a head split
+    around the convolution and the scan (every rank runs the whole sequence of half of the heads); attention layers
+    run the Ulysses exchange. CP = 2 must reproduce CP = 1."""
+    base = json.loads(json.dumps(BASE))
+    base["model"]["name"] = name
+    single = _run(tmp_path, free_port, 1, base)[0]
+    cfg = json.loads(json.dumps(base))
+    cfg["model"].update(cp=2, cp_style="ulysses")
+    cp2 = _run(tmp_path, free_port + 1, 2, cfg)
+    assert cp2[0]["wsum"] == pytest.approx(cp2[1]["wsum"], rel=1e-9)
+    assert cp2[0]["esum"] == pytest.approx(single["esum"], rel=1e-5)
+    for a, b in zip(single["steps"], cp2[0]["steps"]):
+        assert a[0] == pytest.approx(b[0], rel=1e-3, abs=1e-6)     # loss
+        assert a[1] == pytest.approx(b[1], rel=2e-3)               # grad norm
+        assert a[2] == pytest.approx(b[2], rel=1e-4)               # entropy
