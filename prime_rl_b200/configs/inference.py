@@ -10,7 +10,7 @@ from typing import Annotated, Any, Literal, TypeAlias
 from pydantic import Field, model_validator
 
 from .base import BaseConfig
-from .shared import EnvVars, LogConfig, SlurmConfig, default_output_dir
+from .shared import VLMConfig, EnvVars, LogConfig, SlurmConfig, default_output_dir
 
 
 class ServerConfig(BaseConfig):
@@ -70,6 +70,8 @@ class EngineConfig(BaseConfig):
     max_loras: int = 1
     max_lora_rank: int | None = None
     lora_target_modules: list[str] | None = None
+    # vision tower for image inputs (same description as ``model.vlm`` of the trainer); None: text only
+    vlm: VLMConfig | None = None
     enable_expert_parallel: bool = False
     all2all_backend: str = "allgather_reducescatter"
     enable_eplb: bool = False

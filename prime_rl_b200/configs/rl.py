@@ -159,6 +159,8 @@ class RLConfig(BaseConfig):
                 v.setdefault("model", m.get("name"))
                 if m.get("arch"):
                     v.setdefault("arch", m["arch"])
+                if m.get("vlm"):
+                    v.setdefault("vlm", m["vlm"])           # the engine runs the same vision tower on image inputs
                 inf["vllm"] = v
         for key in ("max_steps", "resume", "rollout_transport", "weight_broadcast", "tokenizer"):
             if data.get(key) is not None:

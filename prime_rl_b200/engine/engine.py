@@ -48,6 +48,11 @@ class Request:
     # moved to host memory (``handoff``), ready to be imported by another engine (``Engine.submit_prefilled``)
     prefill_only: bool = False
     handoff: object = None
+    # image inputs: {"pixel_values": [patches, patch_dim], "image_grid_thw": [images, 3]}; ``mm_state`` is what the
+    # first prefill step derives from them (features per prompt token, 3-axis positions, position shift of the
+    # generated tokens)
+    mm: dict | None = None
+    mm_state: dict | None = None
 
     @property
     def all_tokens(self) -> list[int]:
@@ -58,7 +63,8 @@ class Engine:
     def __init__(self, model, *, num_pages: int = 4096, page_size: int = 16, max_running: int = 256,
                  max_prefill_tokens: int = 16384, eos_token_id: int | None = None, enable_prefix_cache: bool = True,
                  use_cuda_graphs: bool = False, max_model_len: int = 8192, weight_dtype: str = "bf16", tp=None,
-                 keep_bf16_weights: bool = True, kv_offload_bytes: int = 0, expert_parallel: bool = False):
+                 keep_bf16_weights: bool = True, kv_offload_bytes: int = 0, expert_parallel: bool = False,
+                 vision=None, image_token_id: int | None = None, mrope_section: tuple[int, int, int] = (11, 11, 10)):
         """``expert_parallel`` (with ``tp``): the ranks split the experts by index instead of by width
         (``engine/tp.py``). ``kv_offload_bytes`` > 0: a request that is preempted for lack of pages keeps its K / V in (pinned) host
         memory up to that many bytes in total and resumes without a second prefill (the reference configures this
@@ -107,6 +113,12 @@ class Engine:
                                       tp=tp if self.tp_size > 1 else None, shared_prefix_decode=enable_prefix_cache)
         self.max_running, self.max_prefill_tokens = max_running, max_prefill_tokens
         self.eos, self.enable_prefix_cache = eos_token_id, enable_prefix_cache
+        # image inputs (``models/vision.py: VisionTower``): features replace the embeddings of the placeholder tokens
+        self.vision, self.image_token_id = vision, image_token_id
+        if vision is not None:
+            if not isinstance(self.runner, HybridRunner):
+                raise NotImplementedError("image inputs are served for the families of the recurrent-state runner")
+            self.runner.mrope_section = tuple(mrope_section)
         self.waiting: list[Request] = []
         self.running: list[Request] = []
         self.lock = threading.Lock()
@@ -210,10 +222,13 @@ class Engine:
             if self.waiting or self.running:
                 self._step_local()
 
-    async def generate(self, prompt: list[int], params: SamplingParams, cache_salt: str = "") -> Request:
+    async def generate(self, prompt: list[int], params: SamplingParams, cache_salt: str = "",
+                       mm: dict | None = None) -> Request:
+        """``mm``: image inputs of the prompt (``pixel_values``, ``image_grid_thw``), whose features take the place of
+        the embeddings of the placeholder tokens."""
         loop = asyncio.get_running_loop()
         req = Request(prompt=list(prompt), params=params, cache_salt=cache_salt, loop=loop,
-                      future=loop.create_future())
+                      future=loop.create_future(), mm=mm)
         self.submit(req)
         return await req.future
 
@@ -378,11 +393,14 @@ class Engine:
         for r in reqs:
             toks = r.all_tokens
             self.stats["prefix_queries"] += len(toks)
-            if self.enable_prefix_cache and not r.params.prompt_logprobs:
+            if self.enable_prefix_cache and not r.params.prompt_logprobs and r.mm is None:
                 pages = self.cache.blocks.lookup_prefix(r.cache_salt, toks[:-1])
                 r.kv.pages, r.kv.length = pages, len(pages) * self.cache.page_size
                 self.stats["prefix_hits"] += r.kv.length
-            inputs.append(StepInput(r.kv, toks[r.kv.length:], want_all_logits=r.params.prompt_logprobs))
+            inp = StepInput(r.kv, toks[r.kv.length:], want_all_logits=r.params.prompt_logprobs)
+            if r.mm is not None:
+                self._attach_image_inputs(r, inp, r.kv.length, len(toks))
+            inputs.append(inp)
         try:
             logits, offsets = self.runner.forward(inputs)
         except OutOfPages:
@@ -404,7 +422,7 @@ class Engine:
                 rows.append(off + n - 1)
             else:
                 rows.append(off)
-            if self.enable_prefix_cache:
+            if self.enable_prefix_cache and r.mm is None:
                 self.cache.blocks.register_prefix(r.cache_salt, r.all_tokens, r.kv.pages)
             r.prefilled = True
         self._sample_and_append(reqs, logits[torch.tensor(rows, device=logits.device)], self.runner.last_routed,
@@ -413,8 +431,44 @@ class Engine:
             self.running.extend(r for r in reqs if r.finish_reason is None)
 
     # ------------------------------------------------------------------ decode
+    def _attach_image_inputs(self, r: Request, inp: StepInput, start: int, end: int) -> None:
+        """Image features and 3-axis positions of tokens ``[start, end)`` of ``r`` (prompt + output so far)."""
+        if self.vision is None:
+            raise ValueError("this engine was started without a vision tower")
+        st = r.mm_state
+        if st is None:
+            from ..models.vision import mrope_position_ids
+
+            ids = torch.tensor(r.prompt)
+            is_image = ids == self.image_token_id
+            with torch.no_grad():
+                feats = self.vision(r.mm["pixel_values"].to(self.device), r.mm["image_grid_thw"].to(self.device))
+            if int(is_image.sum()) != feats.shape[0]:
+                raise ValueError(f"{int(is_image.sum())} image tokens but {feats.shape[0]} image features")
+            embeds = torch.zeros(len(r.prompt), feats.shape[1], dtype=feats.dtype, device=feats.device)
+            embeds[is_image.to(feats.device)] = feats
+            pos3 = mrope_position_ids(is_image.long(), [len(r.prompt)], r.mm["image_grid_thw"].tolist(),
+                                      self.vision.config.spatial_merge_size)
+            st = r.mm_state = {"embeds": embeds, "is_image": is_image, "pos3": pos3,
+                               "delta": int(pos3.max()) + 1 - len(r.prompt)}
+        P = len(r.prompt)
+        pos = torch.arange(start, end)
+        pos3 = (pos + st["delta"]).unsqueeze(0).repeat(3, 1)
+        if start < P:
+            hi = min(end, P)
+            pos3[:, : hi - start] = st["pos3"][:, start:hi]
+            rows = torch.zeros(end - start, dtype=torch.bool)
+            rows[: hi - start] = st["is_image"][start:hi]
+            emb = torch.zeros(end - start, st["embeds"].shape[1], dtype=st["embeds"].dtype, device=st["embeds"].device)
+            emb[: hi - start] = st["embeds"][start:hi]
+            inp.embeds, inp.embed_rows = emb, rows
+        inp.pos3 = pos3
+
     def _decode(self, reqs: list[Request]) -> None:
         inputs = [StepInput(r.kv, [r.output[-1]]) for r in reqs]
+        for r, inp in zip(reqs, inputs):
+            if r.mm is not None:
+                self._attach_image_inputs(r, inp, r.kv.length, r.kv.length + 1)
         while True:
             try:
                 logits, _ = self.runner.forward(inputs)

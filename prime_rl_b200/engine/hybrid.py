@@ -199,6 +199,7 @@ class HybridRunner(ModelRunner):
         if model.arch.hc_mult:
             raise NotImplementedError("the rollout engine does not serve hyper-connection models")
         self.pool = StatePool(self.device)
+        self.mrope_section = (11, 11, 10)           # set by the engine when it serves image inputs
 
     def _core(self, ids_t, pos_t, slots_t, rows_t, batch, starts):
         from .. import ops
@@ -209,8 +210,26 @@ class HybridRunner(ModelRunner):
         cu[1:] = torch.tensor(lens, dtype=torch.int32).cumsum(0)
         seq = SeqInfo(cu.to(self.device), max(lens), pos_t)
         seq.engine = RecurrentStep(self, batch, starts, slots_t)
+        embeds = None
+        if any(s.embeds is not None or s.pos3 is not None for s in batch):
+            # image features in place of the placeholder embeddings; positions on three axes (text tokens: the same
+            # value on all of them)
+            from ..models.vision import mrope_angles
+
+            embeds = self.model.model.embed_tokens(ids_t)
+            pos3 = pos_t.to(torch.long).unsqueeze(0).repeat(3, 1)
+            for s, st, n in zip(batch, starts, lens):
+                if s.embeds is not None:
+                    rows = s.embed_rows.to(self.device)
+                    embeds[st:st + n][rows] = s.embeds.to(self.device, embeds.dtype)[rows]
+                if s.pos3 is not None:
+                    pos3[:, st:st + n] = s.pos3.to(self.device)
+            arch = self.model.arch
+            rd = arch.rotary_dim
+            inv_freq = 1.0 / (arch.rope_theta ** (torch.arange(0, rd, 2, dtype=torch.float32, device=self.device) / rd))
+            seq.mrope_angles = mrope_angles(pos3, inv_freq, self.mrope_section)
         with torch.no_grad():
-            h = self.model(ids_t, seq)
+            h = self.model(ids_t, seq, inputs_embeds=embeds)
         routed = None
         if self.capture_routed:
             tops = [l.mlp.last_topk for l in self.model.model.layers

@@ -27,6 +27,12 @@ class StepInput:
     kv: SequenceKV
     tokens: list[int]
     want_all_logits: bool = False     # prompt logprobs
+    # multimodal requests (engine/hybrid.py): rows of ``embeds [n, H]`` replace the token embeddings where
+    # ``embed_rows [n]`` is set (image features at the placeholder tokens); ``pos3 [3, n]`` are the tokens' positions
+    # on the (time, row, column) axes of the rotary embedding
+    embeds: torch.Tensor | None = None
+    embed_rows: torch.Tensor | None = None
+    pos3: torch.Tensor | None = None
 
 
 class ModelRunner:
@@ -114,6 +120,8 @@ class ModelRunner:
         here is device work with static shapes for a given N, so a pure decode step can be captured
         in a CUDA graph (``batch`` / ``starts`` are only used by the non-paged attention paths)."""
         model, cache, tp = self.model, self.cache, self.tp
+        if any(s.embeds is not None or s.pos3 is not None for s in batch):
+            raise NotImplementedError("image inputs are served by the runner of the multimodal families (engine/hybrid.py)")
         seq = SeqInfo(None, 0, pos_t)
         h = model.model.embed_tokens(ids_t)
         N = h.shape[0]

@@ -33,6 +33,24 @@ def _encode_routed(routed: list[torch.Tensor], start: int = 0) -> dict | None:
             "dtype": "int16"}
 
 
+def _decode_images(mm: dict | None) -> dict | None:
+    """``multi_modal_data`` of a generate request: ``pixel_values`` as ``{"dtype", "shape", "data"}`` with base64 bytes (the
+    layout of the trainer's wire tensors) or as nested lists, ``image_grid_thw`` as ``[[t, h, w], ...]``."""
+    if not mm:
+        return None
+    import base64
+
+    pv = mm.get("pixel_values")
+    if pv is None or mm.get("image_grid_thw") is None:
+        raise HTTPException(400, "multi_modal_data needs pixel_values and image_grid_thw")
+    if isinstance(pv, dict):
+        raw = base64.b64decode(pv["data"])
+        pixels = torch.frombuffer(bytearray(raw), dtype=getattr(torch, pv["dtype"])).reshape(pv["shape"]).clone()
+    else:
+        pixels = torch.tensor(pv, dtype=torch.float32)
+    return {"pixel_values": pixels, "image_grid_thw": torch.tensor(mm["image_grid_thw"], dtype=torch.long)}
+
+
 def _encode_mask(masks: list[torch.Tensor]) -> dict | None:
     if not masks:
         return None
@@ -108,7 +126,8 @@ def build_app(engine: Engine, model_name: str, tokenizer=None, liveness_timeout:
                 raise HTTPException(400, f"cannot import the transferred K / V: {e}")
             reqs = [await fut]
         else:
-            reqs = await asyncio.gather(*[engine.generate(token_ids, params, salt) for _ in range(n)])
+            mm = _decode_images(body.get("multi_modal_data"))
+            reqs = await asyncio.gather(*[engine.generate(token_ids, params, salt, mm=mm) for _ in range(n)])
         choices = []
         for i, r in enumerate(reqs):
             choices.append({

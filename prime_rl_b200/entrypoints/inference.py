@@ -44,7 +44,20 @@ def build_engine(config: InferenceConfig, tp=None):
         pages = max(64, int((free - (1.0 - ec.gpu_memory_utilization) * total) // per_page))
     else:
         pages = 2048
-    engine = Engine(model, num_pages=pages, page_size=ec.page_size, max_running=ec.max_num_seqs,
+    vision_kw = {}
+    if ec.vlm is not None:
+        from ..models.vision import VisionConfig, VisionTower
+
+        vc = VisionConfig(**{"out_hidden_size": arch.hidden_size, **ec.vlm.vision})
+        tower = VisionTower(vc, dtype=dtype, device=device).eval()
+        for p in tower.parameters():
+            p.requires_grad_(False)
+        if Path(ec.model).is_dir() and not ec.random_init:
+            from ..trainer.weights import load_vision_tower
+
+            load_vision_tower(tower, Path(ec.model))
+        vision_kw = dict(vision=tower, image_token_id=ec.vlm.image_token_id, mrope_section=tuple(ec.vlm.mrope_section))
+    engine = Engine(model, num_pages=pages, page_size=ec.page_size, max_running=ec.max_num_seqs, **vision_kw,
                     max_prefill_tokens=ec.max_num_batched_tokens,
                     enable_prefix_cache=ec.enable_prefix_caching is not False, tp=tp,
                     kv_offload_bytes=_kv_offload_bytes(config),

@@ -71,6 +71,17 @@ class Algorithm:
         obs = self.observation_weights(rollout, n)
         if obs is not None:
             sample.ce_weights = obs
+        if last.mm is not None:
+            import numpy as np
+
+            from ...transports.batch.types import EncodedTensor
+
+            px = np.ascontiguousarray(np.asarray(last.mm["pixel_values"], dtype=np.float32))
+            grid = np.ascontiguousarray(np.asarray(last.mm["image_grid_thw"], dtype=np.int64))
+            sample.mm_kwargs = {"pixel_values": EncodedTensor("float32", list(px.shape), px.tobytes()),
+                                "image_grid_thw": EncodedTensor("int64", list(grid.shape), grid.tobytes())}
+            img = last.mm.get("image_token_id")
+            sample.mm_token_type_ids = [1 if (img is not None and t == img) else 0 for t in tokens]
         if len(rollout.turns) == 1 and last.routed_experts is not None:
             import numpy as np
 

@@ -60,7 +60,8 @@ class InferenceClient:
                 await asyncio.sleep(min(2.0 ** attempt * 0.2, 5.0))
         raise last  # type: ignore[misc]
 
-    async def generate(self, token_ids: list[int], sampling, cache_salt: str = "", max_tokens: int | None = None) -> dict:
+    async def generate(self, token_ids: list[int], sampling, cache_salt: str = "", max_tokens: int | None = None,
+                       mm: dict | None = None) -> dict:
         sp = {"temperature": sampling.temperature, "top_p": sampling.top_p,
               "max_tokens": max_tokens or sampling.max_completion_tokens or 128, "logprobs": 0}
         if getattr(sampling, "top_k", None):
@@ -70,6 +71,15 @@ class InferenceClient:
             sp["return_routed_experts"] = True
         body = {"model": self.model_name, "token_ids": token_ids, "sampling_params": sp, "cache_salt": cache_salt,
                 "return_sampling_mask": self.return_sampling_mask}
+        if mm is not None:
+            import base64
+
+            import numpy as np
+
+            px = np.ascontiguousarray(np.asarray(mm["pixel_values"], dtype=np.float32))
+            body["multi_modal_data"] = {"pixel_values": {"dtype": "float32", "shape": list(px.shape),
+                                                         "data": base64.b64encode(px.tobytes()).decode()},
+                                        "image_grid_thw": [list(map(int, g)) for g in mm["image_grid_thw"]]}
         out = await self._post(f"{self.root}/inference/v1/generate", body)
         ch = out["choices"][0]
         return {"token_ids": ch["token_ids"], "logprobs": ch["logprobs"], "finish_reason": ch.get("finish_reason"),

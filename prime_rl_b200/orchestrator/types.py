@@ -19,6 +19,10 @@ class Turn:
     sampling_mask: Any | None = None       # (ids int32, counts int32) for the completion
     finish_reason: str | None = None
     role_spans: list[tuple[str, int, int]] = field(default_factory=list)   # (role, start, end) over prompt tokens
+    # image inputs of the prompt: {"pixel_values": float array [patches, patch_dim], "image_grid_thw": [[t, h, w], ...],
+    # "image_token_id": id of the placeholder tokens in prompt_ids}; they go to the engine with the request and to the
+    # trainer with the sample
+    mm: dict | None = None
 
 
 @dataclass

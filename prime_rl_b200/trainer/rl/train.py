@@ -70,6 +70,11 @@ class RLTrainer:
                                    device=self.device)
             for p in self.mm.visual.parameters():
                 p.requires_grad_(False)
+            if not mc.debug.random_init and Path(mc.name).is_dir():
+                from ..weights import load_vision_tower
+
+                n = load_vision_tower(self.mm.visual, Path(mc.name))
+                self.logger.info(f"vision tower: {n} tensors from {mc.name}")
         if mc.debug.force_balanced_routing:
             for m in self.model.moe_layers():
                 m.router.force_balanced = True

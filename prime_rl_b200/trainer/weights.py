@@ -145,3 +145,35 @@ def load_hf_checkpoint(model, path: Path, strict: bool = True) -> None:
     if model.arch.tie_word_embeddings:
         sd.pop("lm_head.weight", None)
     convert.load_model_state(model, sd, "hf", strict=strict)
+
+
+_VISION_PREFIXES = ("model.visual.", "visual.", "model.vision_tower.", "vision_tower.")
+
+
+@torch.no_grad()
+def load_vision_tower(tower, path: Path, strict: bool = True) -> int:
+    """Fills ``models/vision.py: VisionTower`` from the ``visual.*`` tensors of a HF checkpoint directory (the tower's
+    parameter names are the checkpoint's). Returns the number of tensors loaded; 0 when the checkpoint has none
+    (a text-only checkpoint: the tower keeps its initial values)."""
+    path = Path(path)
+    want = tower.state_dict()
+    got: dict[str, torch.Tensor] = {}
+    for f in sorted(path.glob("*.safetensors")):
+        if f.name.startswith("adapter_"):
+            continue
+        with safe_open(str(f), framework="pt", device="cpu") as sf:
+            for k in sf.keys():
+                for pre in _VISION_PREFIXES:
+                    if k.startswith(pre) and k[len(pre):] in want:
+                        got[k[len(pre):]] = sf.get_tensor(k)
+                        break
+    if not got:
+        return 0
+    missing = [k for k in want if k not in got and not k.endswith("inv_freq")]
+    if missing and strict:
+        raise KeyError(f"vision tower tensors missing from {path}: {missing[:5]}{' ...' if len(missing) > 5 else ''}")
+    for k, t in got.items():
+        if tuple(t.shape) != tuple(want[k].shape):
+            raise ValueError(f"vision tower tensor {k}: checkpoint {tuple(t.shape)} vs model {tuple(want[k].shape)}")
+        want[k].copy_(t.to(want[k].dtype))
+    return len(got)

@@ -553,3 +553,109 @@ def test_disaggregated_deployment_as_processes(tmp_path, free_port):
         except subprocess.TimeoutExpired:
             os.killpg(proc.pid, signal.SIGKILL)
         log.close()
+
+
+def test_engine_serves_image_inputs_like_the_multimodal_forward():
+    """A prompt with two images: the engine runs the vision tower once, puts the features in place of the placeholder
+    embeddings, rotates with three-axis positions (generated tokens continue after the largest image position), and
+    must give the tokens and log-probabilities of the multimodal model's own forward over the finished sequence. A
+    text-only request in the same batch is unaffected."""
+    from prime_rl_b200.engine.engine import Request
+    from prime_rl_b200.models import vision
+
+    torch.manual_seed(12)
+    vc = vision.VisionConfig(depth=2, hidden_size=32, intermediate_size=64, num_heads=4, patch_size=4,
+                             temporal_patch_size=2, out_hidden_size=128, num_position_embeddings=64)
+    arch = resolve_arch("tiny-qwen3.5-moe")
+    lm = build_model(arch, device="cpu", dtype=torch.float32, seed=3).eval()
+    image_token = arch.vocab_size - 1
+    mm = vision.MultimodalLM(lm, vc, image_token, mrope_section=(2, 1, 1), dtype=torch.float32).eval()
+    grid = torch.tensor([[1, 4, 6], [1, 2, 2]])
+    pixels = torch.randn(4 * 6 + 2 * 2, 3 * 2 * 4 * 4)
+    prompt = torch.randint(0, arch.vocab_size - 1, (20,))
+    prompt[3:9] = image_token
+    prompt[15:16] = image_token
+    text = torch.randint(0, arch.vocab_size - 1, (11,)).tolist()
+    eng = Engine(lm, num_pages=128, max_model_len=128, max_prefill_tokens=16, vision=mm.visual,
+                 image_token_id=image_token, mrope_section=(2, 1, 1))
+    params = SamplingParams(max_tokens=6, temperature=0.0)
+    reqs = [eng.submit(Request(prompt=prompt.tolist(), params=params,
+                               mm={"pixel_values": pixels, "image_grid_thw": grid})),
+            eng.submit(Request(prompt=text, params=params))]
+    while any(r.finish_reason is None for r in reqs):
+        eng.step()
+    for r, images in zip(reqs, (True, False)):
+        ids = torch.tensor(r.prompt + r.output)
+        seq = SeqInfo.from_lengths([len(ids)], "cpu")
+        with torch.no_grad():
+            h = mm(ids, seq, pixels, grid) if images else lm(ids, seq)
+            lp = torch.log_softmax(h.float() @ lm.output_weight.float().t(), -1)
+        for i, tok in enumerate(r.output):
+            t = len(r.prompt) - 1 + i
+            assert int(lp[t].argmax()) == tok
+            assert abs(float(lp[t, tok]) - r.logprobs[i]) < 1e-3
+
+
+def test_image_inputs_travel_from_the_client_to_the_engine_and_into_the_sample():
+    """Orchestrator client -> HTTP server -> engine with a vision tower, and the same images into the training sample."""
+    import asyncio
+    from types import SimpleNamespace
+
+    import httpx
+    import numpy as np
+
+    from prime_rl_b200.engine.server import build_app
+    from prime_rl_b200.models import vision
+    from prime_rl_b200.orchestrator.algo import Algorithm
+    from prime_rl_b200.orchestrator.clients import InferenceClient
+    from prime_rl_b200.orchestrator.types import Rollout, Turn
+
+    torch.manual_seed(12)
+    vc = vision.VisionConfig(depth=1, hidden_size=32, intermediate_size=64, num_heads=4, patch_size=4,
+                             temporal_patch_size=2, out_hidden_size=128, num_position_embeddings=64)
+    arch = resolve_arch("tiny-qwen3.5-moe")
+    lm = build_model(arch, device="cpu", dtype=torch.float32, seed=3).eval()
+    image_token = arch.vocab_size - 1
+    tower = vision.VisionTower(vc, dtype=torch.float32).eval()
+    grid = [[1, 4, 4]]
+    pixels = torch.randn(16, 3 * 2 * 4 * 4)
+    prompt = torch.randint(0, arch.vocab_size - 1, (12,))
+    prompt[2:6] = image_token
+    mm = {"pixel_values": pixels.numpy(), "image_grid_thw": grid, "image_token_id": image_token}
+    local = Engine(lm, num_pages=64, max_model_len=64, vision=tower, image_token_id=image_token, mrope_section=(2, 1, 1))
+    from prime_rl_b200.engine.engine import Request
+
+    want = local.submit(Request(prompt=prompt.tolist(), params=SamplingParams(max_tokens=5, temperature=0.0),
+                                mm={"pixel_values": pixels, "image_grid_thw": torch.tensor(grid)}))
+    while want.finish_reason is None:
+        local.step()
+    eng = Engine(lm, num_pages=64, max_model_len=64, vision=tower, image_token_id=image_token,
+                 mrope_section=(2, 1, 1)).start()
+    app = build_app(eng, "tiny")
+
+    async def go():
+        cfg = SimpleNamespace(base_url="http://engine/v1", api_key_var="NONE", timeout=60, headers={}, name="tiny")
+        http = httpx.AsyncClient(transport=httpx.ASGITransport(app=app), base_url="http://engine")
+        body = {"token_ids": prompt.tolist(), "sampling_params": {"max_tokens": 5, "temperature": 0.0}}
+        import base64
+
+        px = np.ascontiguousarray(pixels.numpy())
+        body["multi_modal_data"] = {"pixel_values": {"dtype": "float32", "shape": list(px.shape),
+                                                     "data": base64.b64encode(px.tobytes()).decode()},
+                                    "image_grid_thw": grid}
+        r = await http.post("/inference/v1/generate", json=body)
+        assert r.status_code == 200, r.text
+        await http.aclose()
+        return r.json()["choices"][0]
+
+    try:
+        ch = asyncio.run(go())
+    finally:
+        eng.shutdown()
+    assert ch["token_ids"] == want.output
+    turn = Turn(prompt.tolist(), ch["token_ids"], ch["logprobs"], mm=mm)
+    ro = Rollout(env_name="e", task_id=0, group_id="g", turns=[turn], reward=1.0, policy_version=0)
+    ro.advantage = 0.5
+    (sample,) = Algorithm(None).to_samples(ro)
+    assert sample.mm_kwargs["pixel_values"].shape == [16, 96] and sample.mm_kwargs["image_grid_thw"].shape == [1, 3]
+    assert sample.mm_token_type_ids[2:6] == [1, 1, 1, 1] and sum(sample.mm_token_type_ids) == 4

@@ -403,3 +403,24 @@ def test_multimodal_samples_travel_from_packing_to_the_trainer(tmp_path):
     assert m["loss"] == m["loss"] and m["optim/grad_norm"] > 0
     with pytest.raises(ValueError):
         prepare_batch([sample(6, (1, 4, 4))], seq_len=5, num_train_workers=1)
+
+
+def test_vision_tower_loads_from_a_checkpoint_directory(tmp_path):
+    from safetensors.torch import save_file
+
+    from prime_rl_b200.models import vision
+    from prime_rl_b200.trainer.weights import load_vision_tower
+
+    vc = vision.VisionConfig(depth=1, hidden_size=32, intermediate_size=64, num_heads=4, patch_size=4,
+                             temporal_patch_size=2, out_hidden_size=128, num_position_embeddings=64)
+    src, dst = vision.VisionTower(vc), vision.VisionTower(vc)
+    for p in src.parameters():
+        torch.nn.init.normal_(p, std=0.1)
+    sd = {f"model.visual.{k}": v.contiguous() for k, v in src.state_dict().items() if not k.endswith("inv_freq")}
+    sd["model.language_model.embed_tokens.weight"] = torch.zeros(4, 4)
+    save_file(sd, str(tmp_path / "model.safetensors"))
+    assert load_vision_tower(dst, tmp_path) == len(sd) - 1
+    for (k, a), (_, b) in zip(src.state_dict().items(), dst.state_dict().items()):
+        assert torch.equal(a, b), k
+    save_file({"model.embed_tokens.weight": torch.zeros(4, 4)}, str(tmp_path / "model.safetensors"))
+    assert load_vision_tower(vision.VisionTower(vc), tmp_path) == 0
