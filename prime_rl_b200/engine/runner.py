@@ -120,7 +120,7 @@ class ModelRunner:
         here is device work with static shapes for a given N, so a pure decode step can be captured
         in a CUDA graph (``batch`` / ``starts`` are only used by the non-paged attention paths)."""
         model, cache, tp = self.model, self.cache, self.tp
-        if any(s.embeds is not None or s.pos3 is not None for s in batch):
+        if batch is not None and any(s.embeds is not None or s.pos3 is not None for s in batch):
             raise NotImplementedError("image inputs are served by the runner of the multimodal families (engine/hybrid.py)")
         seq = SeqInfo(None, 0, pos_t)
         h = model.model.embed_tokens(ids_t)
