@@ -96,6 +96,43 @@ class RecurrentStep:
         cache.v[layer].view(-1, Hkv, D).index_copy_(0, self.slots, v.to(cache.v.dtype))
         return self.runner._attend(layer, q, k, v, self.batch, self.starts, window, sinks)
 
+    # ---------------------------------------------------------------- latent K / V with a sparse indexer
+    @staticmethod
+    def _append(kv, key, rows: torch.Tensor, length: int) -> torch.Tensor:
+        """Per-sequence growing store (capacity doubles): rows ``[length, length + n)`` are written; returns the
+        filled part."""
+        store = kv.__dict__.setdefault("latent", {})
+        buf = store.get(key)
+        need = length + rows.shape[0]
+        if buf is None or buf.shape[0] < need:
+            new = torch.empty((max(64, 2 * need), rows.shape[1]), dtype=rows.dtype, device=rows.device)
+            if buf is not None and length:
+                new[:length] = buf[:length]
+            store[key] = buf = new
+        buf[length:need] = rows
+        return buf[:need]
+
+    def sparse_mla(self, layer: int, index_source: int, sq, skv, idx_in, topk: int, scale: float, d_v: int):
+        """Multi-head latent attention over the keys the indexer selects: every sequence keeps the latent K / V row
+        and the indexer key of each of its tokens per layer; layers that share a selection read the one their
+        source layer made in this step."""
+        from ..ops import sparse_mla as sm
+
+        outs = []
+        for s, st, n in zip(self.batch, self.starts, self.lens):
+            r = slice(st, st + n)
+            L = s.kv.length
+            kv_all = self._append(s.kv, (layer, "skv"), skv[r], L)
+            picked = s.kv.__dict__.setdefault("dsa_indices", {})
+            if idx_in is not None:
+                q_i, k_i, w_i = idx_in
+                k_all = self._append(s.kv, (layer, "idx_k"), k_i[r], L)
+                ke = torch.arange(L + 1, L + n + 1, dtype=torch.int32, device=sq.device)
+                picked[layer] = sm.dsa_indexer_topk(q_i[r], k_all, w_i[r], torch.zeros_like(ke), ke, topk)
+            indices = picked[index_source]
+            outs.append(sm.sparse_mla_attention(sq[r].contiguous(), kv_all, indices, scale, d_v))
+        return torch.cat(outs, 0)
+
     # ---------------------------------------------------------------- convolution
     def conv(self, layer: int, x, weight, bias, activation="silu"):
         K, C = weight.shape[1], x.shape[1]
@@ -176,7 +213,7 @@ class RecurrentStep:
         return torch.cat(outs, 0)
 
 
-_SUPPORTED = ("Attention", "GatedAttention", "Mamba2Mixer", "GatedDeltaNet")
+_SUPPORTED = ("Attention", "GatedAttention", "Mamba2Mixer", "GatedDeltaNet", "SparseMLAAttention")
 
 
 def needs_hybrid_runner(model) -> bool:

@@ -283,7 +283,8 @@ class DSAIndexer(nn.Module):
             p.requires_grad_(False)
 
     @torch.no_grad()
-    def forward(self, x, q_latent, seq: SeqInfo, inv_freq, topk: int) -> torch.Tensor:
+    def project(self, x, q_latent, seq: SeqInfo, inv_freq):
+        """Indexer queries ``[T, Hi, Di]``, keys ``[T, Di]`` (both rotated) and head weights ``[T, Hi]`` of the tokens."""
         T = x.shape[0]
         q = self.wq_b(q_latent).view(T, self.nh, self.hd)
         k = self.k_norm(self.wk(x)).view(T, 1, self.hd)
@@ -293,8 +294,13 @@ class DSAIndexer(nn.Module):
             pe = ops.qknorm_rope(_deinterleave(t[..., : self.rope]).contiguous(), None, seq.position_ids, inv_freq)
             return torch.cat([pe, t[..., self.rope:]], dim=-1)
 
+        return rope_head(q), rope_head(k)[:, 0], w
+
+    @torch.no_grad()
+    def forward(self, x, q_latent, seq: SeqInfo, inv_freq, topk: int) -> torch.Tensor:
+        q, k, w = self.project(x, q_latent, seq, inv_freq)
         ks, ke = doc_windows(seq)
-        return sparse_mla.dsa_indexer_topk(rope_head(q), rope_head(k)[:, 0], w, ks, ke, topk)
+        return sparse_mla.dsa_indexer_topk(q, k, w, ks, ke, topk)
 
 
 class SparseMLAAttention(nn.Module):
@@ -332,6 +338,8 @@ class SparseMLAAttention(nn.Module):
         q_latent = self.q_a_layernorm(self.q_a_proj(x))
         ckv, k_rope = self.kv_a_proj_with_mqa(x).split([a.kv_lora_rank, a.qk_rope_head_dim], dim=-1)
         ckv = self.kv_a_layernorm(ckv.contiguous())
+        if seq.engine is not None:
+            return self._forward_engine(x, seq, q_latent, ckv, k_rope)
         if self.indexer is not None:
             indices = self.indexer(x, q_latent, seq, self.inv_freq, a.index_topk)
             if seq.shared is None:
@@ -341,6 +349,15 @@ class SparseMLAAttention(nn.Module):
             indices = (seq.shared or {}).get(("dsa", self.index_source))
             if indices is None:
                 raise RuntimeError("a layer that shares sparse indices ran before the layer that computes them")
+        sq, skv, w_v = self._absorbed(q_latent, ckv, k_rope, seq)
+        o = sparse_mla.sparse_mla_attention(sq, skv, indices, self.scaling, a.kv_lora_rank)
+        o = torch.einsum("thk,hdk->thd", o, w_v)                    # value up-projection per head
+        return self.o_proj(o.reshape(T, self.nh * a.v_head_dim))
+
+    def _absorbed(self, q_latent, ckv, k_rope, seq: SeqInfo):
+        """Queries with the key up-projection absorbed ``[T, H, rank + rope]``, the tokens' latent K / V rows
+        ``[T, rank + rope]`` and the value up-projection ``[H, dv, rank]``."""
+        a, T = self.arch, q_latent.shape[0]
         q = self.q_b_proj(q_latent).view(T, self.nh, self.qk_head_dim)
         q_nope, q_rope = q[..., : a.qk_nope_head_dim], q[..., a.qk_nope_head_dim:]
         q_rope = ops.qknorm_rope(_deinterleave(q_rope).contiguous(), None, seq.position_ids, self.inv_freq)
@@ -349,8 +366,15 @@ class SparseMLAAttention(nn.Module):
         w = self.kv_b_proj.weight.view(self.nh, a.qk_nope_head_dim + a.v_head_dim, a.kv_lora_rank)
         w_k, w_v = w[:, : a.qk_nope_head_dim], w[:, a.qk_nope_head_dim:]
         q_abs = torch.einsum("thd,hdk->thk", q_nope, w_k)          # absorb the key up-projection into q
-        sq = torch.cat([q_abs, q_rope], dim=-1)
-        skv = torch.cat([ckv, k_rope], dim=-1)
-        o = sparse_mla.sparse_mla_attention(sq, skv, indices, self.scaling, a.kv_lora_rank)
-        o = torch.einsum("thk,hdk->thd", o, w_v)                    # value up-projection per head
+        return torch.cat([q_abs, q_rope], dim=-1), torch.cat([ckv, k_rope], dim=-1), w_v
+
+    def _forward_engine(self, x, seq: SeqInfo, q_latent, ckv, k_rope) -> torch.Tensor:
+        """Rollout engine: the latent K / V rows and the indexer keys of earlier tokens come from the engine's
+        per-sequence store (``engine/hybrid.py: RecurrentStep.sparse_mla``)."""
+        a, T = self.arch, x.shape[0]
+        sq, skv, w_v = self._absorbed(q_latent, ckv, k_rope, seq)
+        idx_in = self.indexer.project(x, q_latent, seq, self.inv_freq) if self.indexer is not None else None
+        o = seq.engine.sparse_mla(self.layer_idx, self.index_source, sq, skv, idx_in, a.index_topk, self.scaling,
+                                  a.kv_lora_rank)
+        o = torch.einsum("thk,hdk->thd", o, w_v)
         return self.o_proj(o.reshape(T, self.nh * a.v_head_dim))

@@ -46,7 +46,10 @@ def dsa_indexer_topk(q_idx: torch.Tensor, k_idx: torch.Tensor, w: torch.Tensor, 
         logits = (s * w[t0:t1].float().unsqueeze(-1)).sum(1)
         valid = (cols[None, :] >= ks[t0:t1, None]) & (cols[None, :] < ke[t0:t1, None])
         logits = logits.masked_fill(~valid, float("-inf"))
-        idx = logits.topk(kk, dim=-1).indices
+        # The ReLU makes exact ties (several keys at 0) common. A stable sort breaks them towards the earlier key, so
+        # that the selection of a query does not depend on how many keys follow it in the call: the rollout engine
+        # (keys up to the query) and the trainer (the whole packed sequence) then pick the same keys.
+        idx = torch.sort(logits, dim=-1, descending=True, stable=True).indices[:, :kk]
         ok = torch.gather(valid, 1, idx)
         out[t0:t1, :kk] = torch.where(ok, idx, torch.full_like(idx, S)).to(torch.int32)
     return out

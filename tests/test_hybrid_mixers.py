@@ -424,3 +424,24 @@ def test_vision_tower_loads_from_a_checkpoint_directory(tmp_path):
         assert torch.equal(a, b), k
     save_file({"model.embed_tokens.weight": torch.zeros(4, 4)}, str(tmp_path / "model.safetensors"))
     assert load_vision_tower(vision.VisionTower(vc), tmp_path) == 0
+
+
+def test_sparse_indexer_selection_does_not_depend_on_the_keys_that_follow():
+    """Exact ties (ReLU zeros) are broken towards the earlier key: a query picks the same keys whether the call holds
+    the keys up to it (rollout engine) or the whole sequence (trainer)."""
+    from prime_rl_b200.ops import sparse_mla
+
+    torch.manual_seed(0)
+    T, H, D, topk = 40, 2, 8, 6
+    q = torch.randn(T, H, D)
+    k = torch.randn(T, D)
+    k[::3] = 0                     # a third of the keys score exactly 0 with every query
+    w = torch.randn(T, H)
+    me = torch.arange(T, dtype=torch.int32)
+    full = sparse_mla.dsa_indexer_topk(q, k, w, torch.zeros_like(me), me + 1, topk)
+    for t in (7, 19, 33):
+        part = sparse_mla.dsa_indexer_topk(q[t:t + 1], k[:t + 1], w[t:t + 1], torch.zeros(1, dtype=torch.int32),
+                                           torch.tensor([t + 1], dtype=torch.int32), topk)
+        a = full[t][full[t] < T].sort().values
+        b = part[0][part[0] < t + 1].sort().values
+        assert torch.equal(a, b)
