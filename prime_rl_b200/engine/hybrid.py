@@ -96,12 +96,16 @@ class RecurrentStep:
         cache.v[layer].view(-1, Hkv, D).index_copy_(0, self.slots, v.to(cache.v.dtype))
         return self.runner._attend(layer, q, k, v, self.batch, self.starts, window, sinks)
 
-    # ---------------------------------------------------------------- latent K / V with a sparse indexer
+    # ---------------------------------------------------------------- per-sequence stores (model-specific mixers)
+    def sequences(self):
+        """(slice of the new tokens in the packed step, the sequence's store, tokens before them) per sequence."""
+        for s, st, n in zip(self.batch, self.starts, self.lens):
+            yield slice(st, st + n), s.kv.__dict__.setdefault("latent", {}), s.kv.length
+
     @staticmethod
-    def _append(kv, key, rows: torch.Tensor, length: int) -> torch.Tensor:
-        """Per-sequence growing store (capacity doubles): rows ``[length, length + n)`` are written; returns the
+    def append(store: dict, key, rows: torch.Tensor, length: int) -> torch.Tensor:
+        """Growing buffer ``store[key]`` (capacity doubles): rows ``[length, length + n)`` are written; returns the
         filled part."""
-        store = kv.__dict__.setdefault("latent", {})
         buf = store.get(key)
         need = length + rows.shape[0]
         if buf is None or buf.shape[0] < need:
@@ -122,11 +126,12 @@ class RecurrentStep:
         for s, st, n in zip(self.batch, self.starts, self.lens):
             r = slice(st, st + n)
             L = s.kv.length
-            kv_all = self._append(s.kv, (layer, "skv"), skv[r], L)
+            store = s.kv.__dict__.setdefault("latent", {})
+            kv_all = self.append(store, (layer, "skv"), skv[r], L)
             picked = s.kv.__dict__.setdefault("dsa_indices", {})
             if idx_in is not None:
                 q_i, k_i, w_i = idx_in
-                k_all = self._append(s.kv, (layer, "idx_k"), k_i[r], L)
+                k_all = self.append(store, (layer, "idx_k"), k_i[r], L)
                 ke = torch.arange(L + 1, L + n + 1, dtype=torch.int32, device=sq.device)
                 picked[layer] = sm.dsa_indexer_topk(q_i[r], k_all, w_i[r], torch.zeros_like(ke), ke, topk)
             indices = picked[index_source]
@@ -213,7 +218,7 @@ class RecurrentStep:
         return torch.cat(outs, 0)
 
 
-_SUPPORTED = ("Attention", "GatedAttention", "Mamba2Mixer", "GatedDeltaNet", "SparseMLAAttention")
+_SUPPORTED = ("Attention", "GatedAttention", "Mamba2Mixer", "GatedDeltaNet", "SparseMLAAttention", "DSV4Attention")
 
 
 def needs_hybrid_runner(model) -> bool:
@@ -233,8 +238,6 @@ class HybridRunner(ModelRunner):
                 if type(m).__name__ not in _SUPPORTED:
                     raise NotImplementedError(f"the rollout engine has no incremental form of {type(m).__name__} "
                                               f"(model type {model.arch.model_type})")
-        if model.arch.hc_mult:
-            raise NotImplementedError("the rollout engine does not serve hyper-connection models")
         self.pool = StatePool(self.device)
         self.mrope_section = (11, 11, 10)           # set by the engine when it serves image inputs
 

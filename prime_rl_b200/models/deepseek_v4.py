@@ -175,6 +175,57 @@ class Compressor(nn.Module):
         c = self.kv_norm((kv * w).sum(1))
         return rope_interleaved(c.unsqueeze(1), layout.entry_local * self.rate, self.inv_freq).squeeze(1)
 
+    def pool(self, kvp: torch.Tensor, gp: torch.Tensor, first_entry: int, has_prev: bool) -> torch.Tensor:
+        """Entries from the projections of their source tokens (rollout engine: entries are formed as their tokens
+        arrive). ``kvp`` / ``gp``: ``kv_proj(x)`` / ``gate_proj(x)`` of the consecutive tokens of entries
+        ``first_entry - 1`` (only when ``has_prev``: the second series pools from it) ``, first_entry, ...``; returns
+        the entries from ``first_entry`` on, rotated at their first position."""
+        D, R = self.head_dim, self.rate
+        n_all = kvp.shape[0] // R
+        kv = kvp.view(n_all, R, -1)
+        gate = gp.float().view(n_all, R, -1) + self.position_bias
+        if self.n_series == 2:
+            cur_kv, cur_g = kv[1:] if has_prev else kv, gate[1:] if has_prev else gate
+            if has_prev:
+                prev_kv, prev_g = kv[:-1, :, :D], gate[:-1, :, :D]
+            else:                   # the sequence's first entry has no predecessor; later ones of this call do
+                prev_kv = torch.cat([torch.zeros_like(kv[:1, :, :D]), kv[:-1, :, :D]], 0)
+                prev_g = torch.cat([torch.full_like(gate[:1, :, :D], float("-inf")), gate[:-1, :, :D]], 0)
+            kv = torch.cat([prev_kv, cur_kv[..., D:]], dim=1)
+            gate = torch.cat([prev_g, cur_g[..., D:]], dim=1)
+        elif has_prev:
+            kv, gate = kv[1:], gate[1:]
+        n = kv.shape[0]
+        w = gate.softmax(dim=1).to(kv.dtype)
+        c = self.kv_norm((kv * w).sum(1))
+        first = torch.arange(first_entry, first_entry + n, device=kvp.device) * R
+        return rope_interleaved(c.unsqueeze(1), first, self.inv_freq).squeeze(1)
+
+    def engine_entries(self, eng, store: dict, key, x: torch.Tensor, L: int) -> torch.Tensor:
+        """All completed entries of one sequence after its ``x.shape[0]`` new tokens (``L`` tokens before them). The
+        sequence keeps the entries made so far and the projections of the tokens that later entries still need."""
+        R = self.rate
+        st = store.setdefault(key, {"n": 0, "tail_start": 0, "kvp": None, "gp": None})
+        if L == 0:
+            st.update(n=0, tail_start=0, kvp=None, gp=None)
+        kvp, gp = self.kv_proj(x), self.gate_proj(x)
+        if st["kvp"] is not None:
+            kvp, gp = torch.cat([st["kvp"], kvp], 0), torch.cat([st["gp"], gp], 0)
+        total = (L + x.shape[0]) // R
+        done = st["n"]
+        entries = eng.append(store, (key, "entries"), x.new_zeros(0, self.head_dim), done)
+        if total > done:
+            has_prev = self.n_series == 2 and done > 0
+            lo = (done - 1 if has_prev else done) * R - st["tail_start"]
+            hi = total * R - st["tail_start"]
+            new = self.pool(kvp[lo:hi], gp[lo:hi], done, has_prev)
+            entries = eng.append(store, (key, "entries"), new.to(x.dtype), done)
+            st["n"] = total
+        keep_from = (max(total - 1, 0) if self.n_series == 2 else total) * R        # tokens later entries still read
+        cut = keep_from - st["tail_start"]
+        st["kvp"], st["gp"], st["tail_start"] = kvp[cut:], gp[cut:], keep_from
+        return entries
+
     def readable_entries(self, position_ids: torch.Tensor) -> torch.Tensor:
         """How many entries of its own document query ``t`` may read: an entry becomes readable once
         the query has reached its last source token."""
@@ -205,6 +256,19 @@ class LightningIndexer(nn.Module):
             return torch.full((T, self.arch.index_topk), IGNORE_SLOT, dtype=torch.long, device=x.device)
         picks = sparse_mla.dsa_indexer_topk(q, entries, self.weights_proj(x), start, stop, self.arch.index_topk).long()
         return torch.where(picks < layout.n, picks, torch.full_like(picks, IGNORE_SLOT))
+
+    @torch.no_grad()
+    def engine_picks(self, eng, store: dict, layer: int, x, q_residual, pos: torch.Tensor, L: int) -> torch.Tensor:
+        """Rollout engine: the selection for the new tokens of one sequence over its own indexer entries."""
+        entries = self.compressor.engine_entries(eng, store, (layer, "idx"), x, L)
+        n = x.shape[0]
+        if entries.shape[0] == 0:
+            return torch.full((n, self.arch.index_topk), IGNORE_SLOT, dtype=torch.long, device=x.device)
+        q = rope_interleaved(self.q_b_proj(q_residual).view(n, self.nh, self.hd), pos, self.compressor.inv_freq)
+        stop = self.compressor.readable_entries(pos).int()
+        picks = sparse_mla.dsa_indexer_topk(q, entries, self.weights_proj(x), torch.zeros_like(stop), stop,
+                                            self.arch.index_topk).long()
+        return torch.where(picks < entries.shape[0], picks, torch.full_like(picks, IGNORE_SLOT))
 
 
 class GroupedLinear(nn.Module):
@@ -255,6 +319,10 @@ class DSV4Attention(nn.Module):
         q = unweighted_rms_norm(self.q_b_proj(q_res).view(T, self.nh, self.D), a.rms_norm_eps)
         q = rope_interleaved(q, seq.position_ids, self.inv_freq)
         kv = rope_interleaved(self.kv_norm(self.kv_proj(x)).view(T, 1, self.D), seq.position_ids, self.inv_freq)[:, 0]
+        if seq.engine is not None:
+            o = self._engine_attention(x, seq, q, kv, q_res)
+            o = rope_interleaved(o, seq.position_ids, self.inv_freq, conj=True)
+            return self.o_b_proj(self.o_a_proj(o.reshape(T, a.o_groups, -1)).flatten(1))
         indices, kv_buf = ctx["window"], kv
         if self.compressor is not None:
             layout = ctx["layouts"][self.compressor.rate]
@@ -272,6 +340,32 @@ class DSV4Attention(nn.Module):
         o = rope_interleaved(o, seq.position_ids, self.inv_freq, conj=True)      # values carried the keys' rotation
         g = self.o_a_proj(o.reshape(T, a.o_groups, -1)).flatten(1)
         return self.o_b_proj(g)
+
+
+    def _engine_attention(self, x, seq: SeqInfo, q, kv, q_res) -> torch.Tensor:
+        """Rollout engine: every sequence keeps its tokens' shared K / V rows, its completed entries and the
+        projections of the tokens that unfinished entries still need (``engine/hybrid.py: RecurrentStep``)."""
+        a, eng = self.arch, seq.engine
+        outs = []
+        back = torch.arange(a.sliding_window, device=x.device)
+        for r, store, L in eng.sequences():
+            kv_all = eng.append(store, (self.layer_idx, "kv"), kv[r], L)
+            pos = seq.position_ids[r].long()
+            win = pos[:, None] - back[None, :]                               # most recent token first
+            indices = torch.where(win >= 0, win, torch.full_like(win, IGNORE_SLOT))
+            kv_buf = kv_all
+            if self.compressor is not None:
+                entries = self.compressor.engine_entries(eng, store, (self.layer_idx, "cmp"), x[r], L)
+                if self.indexer is not None:
+                    picks = self.indexer.engine_picks(eng, store, self.layer_idx, x[r], q_res[r], pos, L)
+                else:
+                    ready = self.compressor.readable_entries(pos)[:, None]
+                    off = torch.arange(max(entries.shape[0], 1), device=x.device)[None, :]
+                    picks = torch.where(off < ready, off.expand(pos.shape[0], -1), torch.full_like(off, IGNORE_SLOT))
+                kv_buf = torch.cat([kv_all, entries.to(kv_all.dtype)], dim=0)
+                indices = torch.cat([indices, torch.where(picks >= 0, picks + kv_all.shape[0], picks)], dim=1)
+            outs.append(sparse_mla.slot_attention(q[r], kv_buf, indices, self.D ** -0.5, self.sinks))
+        return torch.cat(outs, 0)
 
 
 # ---------------------------------------------------------------------- MoE

@@ -398,10 +398,11 @@ def test_preempted_requests_keep_their_kv_in_host_memory_and_resume_without_a_se
     assert small.stats.get("kv_swap_outs", 0) == 0
 
 
-@pytest.mark.parametrize("name", ["tiny-nemotron-h", "tiny-qwen3.5-moe", "tiny-glm-moe-dsa"])
+@pytest.mark.parametrize("name", ["tiny-nemotron-h", "tiny-qwen3.5-moe", "tiny-glm-moe-dsa", "tiny-deepseek-v4"])
 def test_engine_serves_the_recurrent_state_families(name):
     """(GLM-MoE-DSA: multi-head latent attention over the keys a sparse indexer selects; the engine keeps the latent K / V
-    row and the indexer key of every token per sequence and layer.) Mamba-2 / gated delta-net layers next to attention: the engine keeps a convolution tail and a recurrent state per
+    row and the indexer key of every token per sequence and layer. DeepSeek-V4: shared K / V rows, compressed entries
+    formed as their source tokens arrive, a lightning indexer over the entries, hyper-connection streams.) Mamba-2 / gated delta-net layers next to attention: the engine keeps a convolution tail and a recurrent state per
     sequence and layer, prefills in chunks from the stored state and decodes with one batched recurrence step. Greedy
     tokens and their log-probabilities must be those of the model's own forward over the whole sequence."""
     from prime_rl_b200.engine.engine import Engine
