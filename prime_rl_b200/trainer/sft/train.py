@@ -59,9 +59,16 @@ class SFTTrainer:
         self.model.train()
         multi = dist.is_initialized() and self.world.world_size > 1
         d = self.dims
+        # context parallelism: the ranks of one replica read the same rows and each runs its chunk of every row
+        self.cp_ctx, self.dp_rank, self.dp_size, self.cp_rank = None, self.world.rank, self.world.world_size, 0
         if d.cp_enabled:
-            raise NotImplementedError("context parallelism in the SFT trainer (use the RL trainer's CE loss path: "
-                                      "orchestrator.algo.type = 'sft')")
+            from ...parallel.cp import ContextParallel
+
+            coords = d.coords(self.world.rank)
+            self.dp_rank, self.cp_rank = coords["dp"], coords["cp"]
+            self.dp_size = self.world.world_size // d.cp
+            self.cp_ctx = ContextParallel(d.group("cp"), d.cp, self.cp_rank, style=mc.cp_style,
+                                          fused_kv_gather=mc.cp_kv_exchange == "p2p", kv_exchange=mc.cp_kv_exchange)
         self.dp_group = d.group("dp_cp") if multi else None
         ep_on = d.ep_enabled and multi
         if ep_on:
@@ -107,8 +114,8 @@ class SFTTrainer:
         self.monitor = monitors_mod.setup(cfg.monitors, self.run_dir, "trainer", is_master=self.world.is_master)
         self.ckpt = CheckpointManager(self.run_dir, cfg.ckpt, is_master=self.world.is_master, rank=self.world.rank) \
             if cfg.ckpt is not None or cfg.resume is not None else None
-        self.dataset = setup_dataset(cfg.data, self.arch.vocab_size, self.world.rank, self.world.world_size)
-        self.val_dataset = setup_dataset(cfg.val.data, self.arch.vocab_size, self.world.rank, self.world.world_size) \
+        self.dataset = setup_dataset(cfg.data, self.arch.vocab_size, self.dp_rank, self.dp_size)
+        self.val_dataset = setup_dataset(cfg.val.data, self.arch.vocab_size, self.dp_rank, self.dp_size) \
             if cfg.val is not None else None
         if cfg.resume is not None and self.ckpt is not None:
             step = cfg.resume.step if cfg.resume.step is not None else self.ckpt.latest()
@@ -116,7 +123,7 @@ class SFTTrainer:
                 self.ckpt.load(step, self.model, self.optimizer, self.progress, self.dataset)
                 self.progress.step = step + 1
         self.data_iter = iter(self.dataset)
-        self.micro_steps = max(1, cfg.data.batch_size // (cfg.data.micro_batch_size * self.world.world_size))
+        self.micro_steps = max(1, cfg.data.batch_size // (cfg.data.micro_batch_size * self.dp_size))
         dev_name = torch.cuda.get_device_name(self.device) if self.device.type == "cuda" else "cpu"
         self.perf = PerfCounter(self.arch, cfg.data.seq_len, self.world.world_size, dev_name, lora=mc.lora is not None)
         return self
@@ -131,6 +138,10 @@ class SFTTrainer:
         # the last position of each document predicts the next document's first token: drop it
         ends = torch.tensor(row["sequence_lengths"], device=self.device).cumsum(0) - 1
         lmask[ends] = False
+        if self.cp_ctx is not None:
+            # every rank of the replica runs its chunk(s) of the row and sums the loss of its own tokens
+            ids, labels, lm, seq = self.cp_ctx.shard_inputs(ids, labels, lmask.to(torch.float32), seq)
+            lmask = lm.bool()
         hidden = self.model(ids, seq)
         lp, _ = self.model.logprobs_entropy(hidden, labels)
         return -(lp * lmask).sum(), lmask.sum()
@@ -145,6 +156,8 @@ class SFTTrainer:
             ends = torch.tensor(r["sequence_lengths"]).cumsum(0) - 1
             m[ends] = False
             exact += int(m.sum())
+        if self.cp_rank != 0:
+            exact = 0                                # the replica's rows are counted once
         count = torch.tensor([float(exact)], device=self.device)
         if self.dp_group is not None:
             dist.all_reduce(count, group=self.dp_group)
@@ -159,7 +172,7 @@ class SFTTrainer:
         self.optimizer.zero_grad()
         if self.dp_group is not None:
             dist.all_reduce(total, group=self.dp_group)
-        tokens = len(rows) * self.config.data.seq_len * self.world.world_size
+        tokens = len(rows) * self.config.data.seq_len * self.dp_size
         self.progress.total_tokens += tokens
         dt = time.perf_counter() - t0
         tps = tokens / dt

@@ -192,3 +192,64 @@ def test_cp2_of_the_recurrent_state_families_matches_single_process(tmp_path, fr
         assert a[0] == pytest.approx(b[0], rel=1e-3, abs=1e-6)     # loss
         assert a[1] == pytest.approx(b[1], rel=2e-3)               # grad norm
         assert a[2] == pytest.approx(b[2], rel=1e-4)               # entropy
+
+
+SFT_WORKER = r"""
+import json, os, sys, torch
+sys.path.insert(0, {root!r})
+from prime_rl_b200.configs.sft import SFTConfig
+from prime_rl_b200.trainer.sft.train import SFTTrainer
+from prime_rl_b200.utils.logger import setup_logger
+setup_logger("warning")
+torch.manual_seed(0)
+tr = SFTTrainer(SFTConfig.model_validate(json.loads({cfg!r}))).setup()
+out = []
+for _ in range(2):
+    m = tr.step()
+    out.append([m["loss"], m["optim/grad_norm"], m["loss_tokens"]])
+w = next(p for _, p in tr.model.model.layers[0].named_parameters() if p.dim() == 2).detach().double()
+open(os.path.join({out!r}, f"rank{{tr.world.rank}}.json"), "w").write(json.dumps(dict(steps=out, wsum=float(w.sum()),
+                                                                                      wabs=float(w.abs().sum()))))
+import torch.distributed as dist
+if dist.is_initialized():
+    dist.barrier(); dist.destroy_process_group()
+"""
+
+
+def _run_sft(tmp_path, port, world, cfg, tag):
+    script = tmp_path / f"sft_{tag}.py"
+    out = tmp_path / f"sft_out_{tag}"
+    out.mkdir()
+    cfg = dict(cfg, output_dir=str(out))
+    script.write_text(SFT_WORKER.format(root=str(ROOT), cfg=json.dumps(cfg), out=str(out)))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), CUDA_VISIBLE_DEVICES="")
+    if world == 1:
+        env.update(RANK="0", WORLD_SIZE="1", LOCAL_RANK="0")
+        cmd = [sys.executable, str(script)]
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+               "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    return [json.loads((out / f"rank{i}.json").read_text()) for i in range(world)]
+
+
+@pytest.mark.slow
+@pytest.mark.parametrize("style,exchange", [("ulysses", "nccl"), ("ring", "ring")])
+def test_sft_trainer_with_context_parallelism_matches_single_process(tmp_path, free_port, style, exchange):
+    """SFT under context parallelism: the two ranks of the replica read the same packed rows, each runs its chunks and
+    sums the loss of its own tokens over the global count of loss tokens; losses and weights equal the single process."""
+    base = {"model": {"name": "tiny-qwen3", "ac": None, "debug": {"random_init": True}},
+            "data": {"type": "fake", "batch_size": 4, "seq_len": 128, "micro_batch_size": 1, "length": "variable",
+                     "input_ids": "random"},
+            "optim": {"lr": 1e-3, "max_norm": 1.0}, "monitors": {"file": None}, "max_steps": 2}
+    single = _run_sft(tmp_path, free_port, 1, base, "single")[0]
+    cfg = json.loads(json.dumps(base))
+    cfg["model"].update(cp=2, cp_style=style, cp_kv_exchange=exchange)
+    cp2 = _run_sft(tmp_path, free_port + 1, 2, cfg, f"cp2_{style}")
+    assert cp2[0]["wsum"] == pytest.approx(cp2[1]["wsum"], rel=1e-9)
+    assert cp2[0]["wabs"] == pytest.approx(single["wabs"], rel=1e-5)
+    for a, b in zip(single["steps"], cp2[0]["steps"]):
+        assert a[2] == b[2]                                         # the same loss tokens
+        assert a[0] == pytest.approx(b[0], rel=1e-4, abs=1e-6)      # loss
+        assert a[1] == pytest.approx(b[1], rel=1e-3)                # gradient norm
