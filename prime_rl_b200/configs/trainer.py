@@ -95,6 +95,9 @@ _DEFAULT_FP8_IGNORE = ["lm_head", "router", r"mlp\.gate\.", r"shared_expert\.out
 class FP8Config(BaseConfig):
     type: Literal["fp8"] = "fp8"
     ignore_patterns: list[str] = _DEFAULT_FP8_IGNORE
+    # weight gradient of the dense projections: "bf16" product into the fp32 accumulator (default), or "fp8": dY^T in
+    # 1 x 128 groups along the tokens times X^T in 128 x 128 blocks on the fp8 kernel, then added to the accumulator
+    wgrad: Literal["bf16", "fp8"] = "bf16"
 
 
 class MXFP8Config(BaseConfig):

@@ -221,6 +221,9 @@ def setup_quantization(model: CausalLM, mc, logger=None) -> list[str]:
     if q.type != "fp8":
         raise NotImplementedError(f"model.quantization.type = '{q.type}' is not built (block-scaled 'fp8' is)")
     names = apply_fp8_training(model, q.ignore_patterns, cache_weights=getattr(mc, "zero_stage", 2) != 3)
+    from ..ops import fp8 as fp8_ops
+
+    fp8_ops.FP8_WGRAD = getattr(q, "wgrad", "bf16") == "fp8"
     if logger is not None:
         logger.info(f"fp8 training: forward product and input gradient in block-scaled e4m3 on {len(names)} modules")
     return names

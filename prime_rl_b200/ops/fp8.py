@@ -85,6 +85,7 @@ def fp8_gemm(aq, sa, bq, sb, *, block_expert: torch.Tensor | None = None, out: t
 _WEIGHT_EPOCH = 0
 _WEIGHT_CACHE: dict[int, tuple] = {}
 CACHE_WEIGHTS = True        # False: quantise at every use (parameter sharding: a whole-model fp8 copy would undo it)
+FP8_WGRAD = False           # True: the dense projections' weight gradient is an fp8 product too (quantization.wgrad)
 
 
 def bump_weight_epoch() -> None:
@@ -141,7 +142,16 @@ class _FP8Linear(torch.autograd.Function):
             dx = fp8_gemm(gq, gs, wtq, wts).to(x.dtype).reshape(x.shape)
         if ctx.needs_input_grad[1]:
             x2 = x.reshape(-1, x.shape[-1])
-            if ctx.grad_acc is not None and w.shape[1] % 4 == 0:
+            if FP8_WGRAD and x2.shape[0] % 16 == 0:
+                # dW = dY^T X with the tokens as the contraction: dY^T quantised per 128 tokens, X^T in 128 x 128 blocks
+                gq, gs = quantize_act(dy2.t().contiguous())
+                xq, xs = _quantize_weight(x2.detach().t().contiguous())
+                prod = fp8_gemm(gq, gs, xq, xs)
+                if ctx.grad_acc is not None:
+                    ctx.grad_acc.add_(prod)
+                else:
+                    dw = prod.to(w.dtype)
+            elif ctx.grad_acc is not None and w.shape[1] % 4 == 0:
                 gemm(dy2, x2, a_mn=True, b_mn=True, out=ctx.grad_acc, beta=1.0)
             else:
                 dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype)

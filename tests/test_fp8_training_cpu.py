@@ -96,3 +96,18 @@ def test_trainer_with_fp8_projections_follows_the_unquantised_run(tmp_path):
         assert e1 == pytest.approx(e0, rel=2e-2)
         assert g1 == pytest.approx(g0, rel=0.25)
         assert l1 == pytest.approx(l0, abs=5e-3)
+
+
+def test_fp8_weight_gradient_option():
+    torch.manual_seed(4)
+    x = torch.randn(64, 256, requires_grad=True)
+    w = (torch.randn(384, 256) * 0.05).requires_grad_()
+    dy = torch.randn(64, 384)
+    (rw,) = torch.autograd.grad(x @ w.t(), (w,), dy)
+    F.FP8_WGRAD = True
+    try:
+        (gw,) = torch.autograd.grad(F.fp8_linear(x, w), (w,), dy)
+    finally:
+        F.FP8_WGRAD = False
+    rel = _rel(gw, rw)
+    assert 1e-4 < rel < 0.06            # quantised, and within e4m3 accuracy
