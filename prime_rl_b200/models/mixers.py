@@ -340,6 +340,8 @@ class SparseMLAAttention(nn.Module):
         ckv = self.kv_a_layernorm(ckv.contiguous())
         if seq.engine is not None:
             return self._forward_engine(x, seq, q_latent, ckv, k_rope)
+        if seq.cp is not None:
+            return self._forward_cp(x, seq, q_latent, ckv, k_rope)
         if self.indexer is not None:
             indices = self.indexer(x, q_latent, seq, self.inv_freq, a.index_topk)
             if seq.shared is None:
@@ -367,6 +369,31 @@ class SparseMLAAttention(nn.Module):
         w_k, w_v = w[:, : a.qk_nope_head_dim], w[:, a.qk_nope_head_dim:]
         q_abs = torch.einsum("thd,hdk->thk", q_nope, w_k)          # absorb the key up-projection into q
         return torch.cat([q_abs, q_rope], dim=-1), torch.cat([ckv, k_rope], dim=-1), w_v
+
+    def _forward_cp(self, x, seq: SeqInfo, q_latent, ckv, k_rope) -> torch.Tensor:
+        """Context parallelism: the latent K / V rows (and the indexer keys) are small per token, so they are gathered
+        whole; the local queries select and attend over the global sequence (reference: all-gather of the compressed
+        K / V, src/prime_rl/trainer/models/glm_moe_dsa/sparse_mla_attention.py:208-210)."""
+        a, T, cp = self.arch, x.shape[0], seq.cp
+        sq, skv, w_v = self._absorbed(q_latent, ckv, k_rope, seq)
+        skv_all = cp.gather_rows(skv)
+        rows = cp.global_rows(T, x.device)
+        if self.indexer is not None:
+            q_i, k_i, w_i = self.indexer.project(x, q_latent, seq, self.inv_freq)
+            k_all = cp.gather_rows(k_i, grad=False)
+            ke = (rows + 1).to(torch.int32)
+            ks = (rows - seq.position_ids.to(rows.dtype)).to(torch.int32)          # first token of the row's document
+            indices = sparse_mla.dsa_indexer_topk(q_i, k_all, w_i, ks, ke, a.index_topk)
+            if seq.shared is None:
+                seq.shared = {}
+            seq.shared[("dsa", self.layer_idx)] = indices
+        else:
+            indices = (seq.shared or {}).get(("dsa", self.index_source))
+            if indices is None:
+                raise RuntimeError("a layer that shares sparse indices ran before the layer that computes them")
+        o = sparse_mla.sparse_mla_attention(sq, skv_all, indices, self.scaling, a.kv_lora_rank)
+        o = torch.einsum("thk,hdk->thd", o, w_v)
+        return self.o_proj(o.reshape(T, self.nh * a.v_head_dim))
 
     def _forward_engine(self, x, seq: SeqInfo, q_latent, ckv, k_rope) -> torch.Tensor:
         """Rollout engine: the latent K / V rows and the indexer keys of earlier tokens come from the engine's

@@ -261,6 +261,22 @@ class ContextParallel:
         gradients are summed over the ranks."""
         return _AllGatherSeq.apply(x.contiguous(), self.group, True)
 
+    def global_rows(self, Tl: int, device) -> torch.Tensor:
+        """Global token index of every local row."""
+        if self.layout == "zigzag":
+            c = Tl // 2
+            a, b = self.rank, 2 * self.cp - 1 - self.rank
+            return torch.cat([torch.arange(a * c, (a + 1) * c, device=device), torch.arange(b * c, (b + 1) * c, device=device)])
+        return torch.arange(self.rank * Tl, (self.rank + 1) * Tl, device=device)
+
+    def gather_rows(self, x: torch.Tensor, grad: bool = True) -> torch.Tensor:
+        """``[Tl, ...]`` -> ``[T, ...]`` in global token order on every rank (small per-token features that every query
+        may read: latent K / V rows, indexer keys); with ``grad`` the gradients are summed over the ranks."""
+        if grad:
+            return self._to_global_order(_AllGatherSeq.apply(x.contiguous(), self.group, True))
+        with torch.no_grad():
+            return self._to_global_order(_AllGatherSeq.apply(x.contiguous(), self.group, False))
+
     def full_positions(self, seq: SeqInfo) -> torch.Tensor:
         """Position of every token of the whole packed sequence inside its document."""
         cu = seq.full_cu_seqlens.to(torch.long)
