@@ -124,10 +124,25 @@ class CompressionLayout:
 
 def packed_context(seq: SeqInfo, arch: ModelArch) -> dict:
     """Built once per forward and kept on ``seq.shared``: document id of every token, the sliding
-    window's slot indices, and one ``CompressionLayout`` per compress rate."""
+    window's slot indices, and one ``CompressionLayout`` per compress rate. Under context parallelism the
+    tokens are the local ones, their slot indices and the layouts are those of the whole sequence, and ``gather``
+    maps per-token rows of the local tokens to the rows of all tokens (``parallel/cp.py: gather_rows``)."""
     if seq.shared is None:
         seq.shared = {}
     ctx = seq.shared.get("dsv4")
+    if ctx is None and seq.cp is not None:
+        cp, pos = seq.cp, seq.position_ids.long()
+        me = cp.global_rows(pos.shape[0], pos.device)
+        cu = seq.full_cu_seqlens.to(pos.device)
+        doc = torch.searchsorted(cu[1:].long().contiguous(), me, right=True)
+        back = torch.arange(arch.sliding_window, device=pos.device)
+        win = me[:, None] - back[None, :]
+        win = torch.where(back[None, :] <= pos[:, None], win, torch.full_like(win, IGNORE_SLOT))
+        rates = sorted({r for r in (arch.csa_compress_rate, arch.hca_compress_rate) if r})
+        ctx = {"doc": doc, "window": win, "layouts": {r: CompressionLayout(cu, r) for r in rates},
+               "gather": cp.gather_rows, "gather_nograd": lambda t: cp.gather_rows(t, grad=False),
+               "total": int(seq.full_len)}
+        seq.shared["dsv4"] = ctx
     if ctx is None:
         pos = seq.position_ids.long()
         T = pos.shape[0]
@@ -161,11 +176,16 @@ class Compressor(nn.Module):
         self.register_buffer("inv_freq", inv_freq(arch.qk_rope_head_dim, arch.compress_rope_theta, device=device),
                              persistent=False)
 
-    def compress(self, x: torch.Tensor, layout: CompressionLayout) -> torch.Tensor:
-        """``x [T, hidden]`` -> entries ``[n_entries, head_dim]`` (rotated at their first position)."""
+    def compress(self, x: torch.Tensor, layout: CompressionLayout, gather=None) -> torch.Tensor:
+        """``x [T, hidden]`` -> entries ``[n_entries, head_dim]`` (rotated at their first position). ``gather``
+        (context parallelism): maps the local tokens' projections to those of the whole sequence, which ``layout``
+        then describes; every rank forms all entries."""
         D = self.head_dim
-        kv = self.kv_proj(x)[layout.entry_tok]                          # [n, rate, series * D]
-        gate = self.gate_proj(x)[layout.entry_tok].float() + self.position_bias
+        kvp, gp = self.kv_proj(x), self.gate_proj(x)
+        if gather is not None:
+            kvp, gp = gather(kvp), gather(gp)
+        kv = kvp[layout.entry_tok]                                      # [n, rate, series * D]
+        gate = gp[layout.entry_tok].float() + self.position_bias
         if self.n_series == 2:
             prev = (torch.arange(layout.n, device=x.device) - 1).clamp(min=0)
             first = (layout.entry_local == 0)[:, None, None]
@@ -246,7 +266,7 @@ class LightningIndexer(nn.Module):
     @torch.no_grad()
     def forward(self, x, q_residual, seq: SeqInfo, ctx: dict) -> torch.Tensor:
         layout = ctx["layouts"][self.compressor.rate]
-        entries = self.compressor.compress(x, layout)
+        entries = self.compressor.compress(x, layout, ctx.get("gather_nograd"))
         T = x.shape[0]
         q = rope_interleaved(self.q_b_proj(q_residual).view(T, self.nh, self.hd), seq.position_ids,
                              self.compressor.inv_freq)
@@ -324,9 +344,11 @@ class DSV4Attention(nn.Module):
             o = rope_interleaved(o, seq.position_ids, self.inv_freq, conj=True)
             return self.o_b_proj(self.o_a_proj(o.reshape(T, a.o_groups, -1)).flatten(1))
         indices, kv_buf = ctx["window"], kv
+        if ctx.get("gather") is not None:          # context parallelism: all tokens' rows, slots in global numbering
+            kv_buf = kv = ctx["gather"](kv)
         if self.compressor is not None:
             layout = ctx["layouts"][self.compressor.rate]
-            entries = self.compressor.compress(x, layout)
+            entries = self.compressor.compress(x, layout, ctx.get("gather"))
             if self.indexer is not None:
                 picks = self.indexer(x, q_res, seq, ctx)
             else:                     # every completed entry of the query's own document
@@ -335,7 +357,7 @@ class DSV4Attention(nn.Module):
                 off = torch.arange(max(layout.max_per_doc, 1), device=x.device)[None, :]
                 picks = torch.where(off < ready, base + off, torch.full_like(base + off, IGNORE_SLOT))
             kv_buf = torch.cat([kv, entries], dim=0)        # tokens first, this layer's entries after
-            indices = torch.cat([indices, torch.where(picks >= 0, picks + T, picks)], dim=1)
+            indices = torch.cat([indices, torch.where(picks >= 0, picks + kv.shape[0], picks)], dim=1)
         o = sparse_mla.slot_attention(q, kv_buf, indices, self.D ** -0.5, self.sinks)
         o = rope_interleaved(o, seq.position_ids, self.inv_freq, conj=True)      # values carried the keys' rotation
         g = self.o_a_proj(o.reshape(T, a.o_groups, -1)).flatten(1)

@@ -175,7 +175,7 @@ def test_muon_with_the_orthogonalisations_dealt_out_matches_every_rank_doing_all
 
 
 @pytest.mark.slow
-@pytest.mark.parametrize("name", ["tiny-nemotron-h", "tiny-qwen3.5-moe", "tiny-glm-moe-dsa"])
+@pytest.mark.parametrize("name", ["tiny-nemotron-h", "tiny-qwen3.5-moe", "tiny-glm-moe-dsa", "tiny-deepseek-v4"])
 def test_cp2_of_the_recurrent_state_families_matches_single_process(tmp_path, free_port, name):
     """Mamba-2 / gated delta-net layers under context parallelism: the sequence split is traded for a head split
     around the convolution and the scan (every rank runs the whole sequence of half of the heads); attention layers
