@@ -344,7 +344,8 @@ class FlatOptimizer:
         if self.kind == "muon":
             if fsdp is not None:
                 raise ValueError("Muon needs whole matrices: use model.zero_stage = 2 with it")
-            shard_group = expert_shard_group = None  # Newton-Schulz needs whole matrices
+            if not getattr(config, "distributed", True):
+                shard_group = expert_shard_group = None     # every rank keeps whole state and orthogonalises everything
         if fsdp is not None:
             self.groups = [_FSDPGroup(self.kind, fsdp[0], fsdp[1], reduce_group=replicate_group)]
         else:
@@ -490,11 +491,11 @@ class FlatOptimizer:
         """Muon on >= 2-D matrices that are not embeddings / heads; AdamW on the rest
         (the split the reference makes, trainer/optim/__init__.py:151-249)."""
         c, buf = self.config, grp.buf
+        if grp.sharded:
+            return self._muon_step_sharded(grp, lr, coef, t)
         g_all = buf.grad * coef
         b1, b2 = c.betas1, c.betas2
-
-        def is_matrix(s):
-            return len(s.shape) >= 2 and "embed" not in s.name and "lm_head" not in s.name
+        is_matrix = self._is_muon_matrix
 
         # The gradients are identical on the ranks of the reduction group, so the orthogonalisations can be dealt
         # out: every matrix has one owner (largest first onto the least loaded rank), which writes its scaled update
@@ -543,6 +544,69 @@ class FlatOptimizer:
                 if s.name in owner:
                     sl = slice(s.offset, s.offset + s.numel)
                     buf.master[sl].mul_(1 - lr * c.weight_decay).add_(shared_upd[sl], alpha=-lr)
+
+    @staticmethod
+    def _is_muon_matrix(s) -> bool:
+        return len(s.shape) >= 2 and "embed" not in s.name and "lm_head" not in s.name
+
+    @staticmethod
+    def _muon_scale(c, shape) -> float:
+        rows, cols = shape[-2], shape[-1]
+        if c.adjust_lr == "rms_norm":
+            return 0.2 * math.sqrt(max(rows, cols))
+        return math.sqrt(max(1.0, rows / cols)) if c.adjust_lr == "spectral_norm" else 1.0
+
+    def _muon_step_sharded(self, grp: _Group, lr: float, coef: torch.Tensor, t: int) -> None:
+        """Muon over an optimizer group whose state is partitioned (ZeRO-2): master weights, momentum and the reduced
+        gradient exist as one flat slice per rank, and matrices straddle the slices. Momentum and the Nesterov
+        direction are elementwise on the slice; the directions are all-gathered so that the owner of every matrix
+        (dealt out by cost) can orthogonalise it whole; the scaled updates come back through a reduce-scatter of a buffer
+        that is zero outside the owned matrices. Elements outside the Muon matrices take an AdamW step on the slice.
+        (The reference moves matrix shards to their owners and back with all-to-alls, trainer/optim/__init__.py:151-249;
+        the two collectives here carry the whole flat buffer, transiently 8 bytes per parameter.)"""
+        c, buf = self.config, grp.buf
+        n, lo = grp.shard_len, grp.shard_rank * grp.shard_len
+        world, rank = grp.shard_n, grp.shard_rank
+        dev = grp.master.device
+        mask = getattr(grp, "_muon_mask", None)
+        if mask is None:
+            full = torch.zeros(buf.numel, dtype=torch.bool, device=dev)
+            for s in buf.slots:
+                if self._is_muon_matrix(s):
+                    full[s.offset:s.offset + s.numel] = True
+            mask = grp._muon_mask = full[lo:lo + n].clone()
+        g = grp.grad_shard * coef
+        m, v, p = grp.exp_avg, grp.exp_avg_sq, grp.master
+        b1, b2 = c.betas1, c.betas2
+        # elementwise part on the slice: Muon momentum inside the matrices, AdamW outside
+        m_muon = m * c.mu + g
+        m_adam = m * b1 + g * (1 - b1)
+        m.copy_(torch.where(mask, m_muon, m_adam))
+        v.copy_(torch.where(mask, v, v * b2 + g * g * (1 - b2)))
+        direction = torch.where(mask, g + c.mu * m, torch.zeros_like(g))
+        full_dir = grp.gather_full(direction)
+        upd = torch.zeros_like(full_dir)
+        load = [0.0] * world
+        mats = sorted((s for s in buf.slots if self._is_muon_matrix(s)), key=lambda s: (-s.numel * min(s.shape[-2:]), s.name))
+        owned = 0
+        for s in mats:
+            r = min(range(world), key=lambda i: (load[i], i))
+            load[r] += s.numel * min(s.shape[-2:])
+            if r == rank:
+                sl = slice(s.offset, s.offset + s.numel)
+                upd[sl].view(s.shape).copy_(newton_schulz(full_dir[sl].view(s.shape), c.ns_steps).float()
+                                            * self._muon_scale(c, s.shape))
+                owned += 1
+        self.muon_owned = owned
+        mine = torch.empty(n, dtype=upd.dtype, device=dev)
+        if _backend(grp.shard_group) == "gloo":
+            dist.all_reduce(upd, group=grp.shard_group)
+            mine.copy_(upd[lo:lo + n])
+        else:
+            dist.reduce_scatter_tensor(mine, upd, op=dist.ReduceOp.SUM, group=grp.shard_group)
+        denom = v.sqrt() / math.sqrt(1 - b2 ** t) + 1e-8
+        adam = m / denom / (1 - b1 ** t)
+        p.mul_(1 - lr * c.weight_decay).add_(torch.where(mask, mine, adam), alpha=-lr)
 
     # ------------------------------------------------------------------ state
     def state_dict(self) -> dict:

@@ -30,7 +30,7 @@ with tr.model.full_parameters():
     w = next(p for _, p in tr.model.model.layers[0].named_parameters() if p.dim() == 2).detach().double().clone()
     e = tr.model.model.embed_tokens.weight.detach().double().clone()
 res = dict(rank=tr.world.rank, steps=out, wsum=float(w.sum()), wabs=float(w.abs().sum()), esum=float(e.abs().sum()),
-           fsdp=getattr(tr.model.layer_hooks, "stats", None))
+           fsdp=getattr(tr.model.layer_hooks, "stats", None), sharded=[bool(g.sharded) for g in tr.optimizer.groups])
 open(os.path.join({out!r}, f"rank{{tr.world.rank}}.json"), "w").write(json.dumps(res))
 import torch.distributed as dist
 if dist.is_initialized():
@@ -156,8 +156,9 @@ def test_cpu_optimizer_with_gradients_accumulated_on_the_host_matches_the_device
 
 @pytest.mark.slow
 def test_muon_with_the_orthogonalisations_dealt_out_matches_every_rank_doing_all(tmp_path, free_port):
-    """Two data-parallel ranks: with ``optim.distributed`` every matrix is orthogonalised by one rank and the updates are
-    summed; the weights and the losses must be those of the run where both ranks orthogonalise everything."""
+    """Two data-parallel ranks: with ``optim.distributed`` the optimizer state is partitioned, the update directions are
+    gathered, every matrix is orthogonalised by one rank and the updates return through a reduce-scatter; the weights
+    and the losses must be those of the run where both ranks keep whole state and orthogonalise everything."""
     runs = {}
     for i, distributed in enumerate((False, True)):
         cfg = json.loads(json.dumps(BASE))
@@ -172,6 +173,8 @@ def test_muon_with_the_orthogonalisations_dealt_out_matches_every_rank_doing_all
         for x, y in zip(a["steps"], b["steps"]):
             assert x[0] == pytest.approx(y[0], rel=1e-5, abs=1e-7)
     assert runs[True][0]["wsum"] == pytest.approx(runs[True][1]["wsum"], rel=1e-9)
+    # the distributed run partitions master weights and momentum over the ranks, the other keeps them whole everywhere
+    assert all(runs[True][0]["sharded"]) and not any(runs[False][0]["sharded"])
 
 
 @pytest.mark.slow
