@@ -113,6 +113,7 @@ class Engine:
                                       tp=tp if self.tp_size > 1 else None, shared_prefix_decode=enable_prefix_cache)
         self.max_running, self.max_prefill_tokens = max_running, max_prefill_tokens
         self.eos, self.enable_prefix_cache = eos_token_id, enable_prefix_cache
+        self._hybrid = isinstance(self.runner, HybridRunner)
         # image inputs (``models/vision.py: VisionTower``): features replace the embeddings of the placeholder tokens
         self.vision, self.image_token_id = vision, image_token_id
         if vision is not None:
@@ -389,6 +390,22 @@ class Engine:
 
     # ------------------------------------------------------------------ prefill
     def _prefill(self, reqs: list[Request]) -> None:
+        followers: list[tuple[Request, Request]] = []
+        all_reqs = reqs
+        if self._hybrid and len(reqs) > 1:
+            # samples of one prompt (a group of the RL algorithm arrives together): the families of this runner have
+            # no page-level prefix cache, so the prompt is run once and the other samples fork pages and states
+            first: dict = {}
+            keep = []
+            for r in reqs:
+                key = (r.cache_salt, tuple(r.all_tokens)) if (r.mm is None and not r.params.prompt_logprobs
+                                                              and r.kv.length == 0) else id(r)
+                if key in first:
+                    followers.append((r, first[key]))
+                else:
+                    first[key] = r
+                    keep.append(r)
+            reqs = keep
         inputs = []
         for r in reqs:
             toks = r.all_tokens
@@ -407,7 +424,7 @@ class Engine:
             for r in reqs:
                 self.cache.free(r.kv)
             with self.lock:
-                self.waiting = reqs + self.waiting
+                self.waiting = all_reqs + self.waiting
             if not self._preempt_one():
                 raise
             return
@@ -425,8 +442,19 @@ class Engine:
             if self.enable_prefix_cache and r.mm is None:
                 self.cache.blocks.register_prefix(r.cache_salt, r.all_tokens, r.kv.pages)
             r.prefilled = True
+        routed_rows = [sum(len(i.tokens) for i in inputs[:j + 1]) - 1 for j in range(len(inputs))]
+        if followers:
+            row_of = {id(r): (rows[j], routed_rows[j]) for j, r in enumerate(reqs)}
+            for f, leader in followers:
+                f.kv = self.cache.fork(leader.kv)
+                self.runner.fork_state(leader.kv, f.kv)
+                f.prefilled = True
+                rows.append(row_of[id(leader)][0])
+                routed_rows.append(row_of[id(leader)][1])
+                reqs.append(f)
+            self.stats["prefill_forks"] = self.stats.get("prefill_forks", 0) + len(followers)
         self._sample_and_append(reqs, logits[torch.tensor(rows, device=logits.device)], self.runner.last_routed,
-                                [sum(len(i.tokens) for i in inputs[:j + 1]) - 1 for j in range(len(inputs))])
+                                routed_rows)
         with self.lock:
             self.running.extend(r for r in reqs if r.finish_reason is None)
 

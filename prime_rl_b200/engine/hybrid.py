@@ -69,6 +69,13 @@ class StatePool:
             if slot < t.shape[0]:
                 t[slot].zero_()
 
+    def copy(self, src: int, dst: int) -> None:
+        """State of slot ``src`` into slot ``dst`` in every pool (a sequence forked from another one)."""
+        for key, t in list(self.tensors.items()):
+            if t.shape[0] <= max(src, dst):
+                t = self.get(key, tuple(t.shape[1:]), t.dtype)
+            t[dst].copy_(t[src])
+
 
 class RecurrentStep:
     def __init__(self, runner: "HybridRunner", batch: list[StepInput], starts: list[int], slots_t: torch.Tensor):
@@ -240,6 +247,26 @@ class HybridRunner(ModelRunner):
                                               f"(model type {model.arch.model_type})")
         self.pool = StatePool(self.device)
         self.mrope_section = (11, 11, 10)           # set by the engine when it serves image inputs
+
+    def fork_state(self, src_kv, dst_kv) -> None:
+        """Everything this runner keeps for ``src_kv`` besides the pages (recurrent states, convolution tails, latent
+        rows, pending compressor projections) copied for ``dst_kv``: a second sample of the same prompt continues from
+        the first one's prefill instead of running the prompt again."""
+        import copy
+
+        if getattr(src_kv, "state_slot", None) is not None:
+            self.pool.copy(src_kv.state_slot, self.pool.slot(dst_kv))
+
+        def clone(v):
+            if torch.is_tensor(v):
+                return v.clone()
+            if isinstance(v, dict):
+                return {k: clone(x) for k, x in v.items()}
+            return copy.copy(v)
+
+        latent = src_kv.__dict__.get("latent")
+        if latent is not None:
+            dst_kv.latent = clone(latent)
 
     def _core(self, ids_t, pos_t, slots_t, rows_t, batch, starts):
         from .. import ops

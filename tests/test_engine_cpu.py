@@ -661,3 +661,37 @@ def test_image_inputs_travel_from_the_client_to_the_engine_and_into_the_sample()
     (sample,) = Algorithm(None).to_samples(ro)
     assert sample.mm_kwargs["pixel_values"].shape == [16, 96] and sample.mm_kwargs["image_grid_thw"].shape == [1, 3]
     assert sample.mm_token_type_ids[2:6] == [1, 1, 1, 1] and sum(sample.mm_token_type_ids) == 4
+
+
+@pytest.mark.parametrize("name", ["tiny-nemotron-h", "tiny-deepseek-v4"])
+def test_samples_of_one_prompt_fork_the_prefill_in_the_recurrent_state_runner(name):
+    """A group of samples of one prompt (what the RL orchestrator sends): the prompt runs once, the other samples take
+    copy-on-write pages and copies of the recurrent / latent state; every sample must still be scored as by the
+    model's own forward, and greedy samples must coincide."""
+    from prime_rl_b200.engine.engine import Request
+
+    arch = resolve_arch(name)
+    model = build_model(arch, device="cpu", dtype=torch.float32, seed=0).eval()
+    eng = Engine(model, num_pages=256, page_size=16, max_model_len=256)
+    g = torch.Generator().manual_seed(2)
+    prompt = torch.randint(0, arch.vocab_size, (27,), generator=g).tolist()
+    other = torch.randint(0, arch.vocab_size, (9,), generator=g).tolist()
+    sampled = [eng.submit(Request(prompt=prompt, params=SamplingParams(max_tokens=7, temperature=1.0, seed=10 + i)))
+               for i in range(4)]
+    greedy = [eng.submit(Request(prompt=p, params=SamplingParams(max_tokens=7, temperature=0.0)))
+              for p in (prompt, other, prompt)]
+    reqs = sampled + greedy
+    while any(r.finish_reason is None for r in reqs):
+        eng.step()
+    assert eng.stats["prefill_forks"] == 5                      # six requests share the long prompt: one ran it
+    assert eng.stats["prompt_tokens"] == len(prompt) + len(other)
+    assert greedy[0].output == greedy[2].output
+    assert len({tuple(r.output) for r in sampled}) > 1          # the samples are independent draws
+    for r in reqs:
+        ids = torch.tensor(r.prompt + r.output)
+        with torch.no_grad():
+            h = model(ids, SeqInfo.from_lengths([len(ids)], torch.device("cpu")))
+            lp = torch.log_softmax(h.float() @ model.output_weight.float().t(), -1)
+        for i, tok in enumerate(r.output):
+            assert abs(float(lp[len(r.prompt) - 1 + i, tok]) - r.logprobs[i]) < 1e-3
+    assert eng.cache.blocks.num_available == 256
