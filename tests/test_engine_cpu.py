@@ -695,3 +695,29 @@ def test_samples_of_one_prompt_fork_the_prefill_in_the_recurrent_state_runner(na
         for i, tok in enumerate(r.output):
             assert abs(float(lp[len(r.prompt) - 1 + i, tok]) - r.logprobs[i]) < 1e-3
     assert eng.cache.blocks.num_available == 256
+
+
+def test_preemption_in_the_recurrent_state_runner_restarts_from_the_tokens():
+    """Too few pages for all requests: the preempted ones lose pages and state and later run prompt + output so far
+    again; their final tokens and log-probabilities are still those of the model's own forward."""
+    from prime_rl_b200.engine.engine import Request
+
+    arch = resolve_arch("tiny-nemotron-h")
+    model = build_model(arch, device="cpu", dtype=torch.float32, seed=0).eval()
+    eng = Engine(model, num_pages=9, page_size=16, max_model_len=128)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, arch.vocab_size, (n,), generator=g).tolist() for n in (30, 28, 31)]
+    reqs = [eng.submit(Request(prompt=p, params=SamplingParams(max_tokens=24, temperature=0.0))) for p in prompts]
+    while any(r.finish_reason is None for r in reqs):
+        eng.step()
+    assert eng.stats["preemptions"] > 0
+    for r in reqs:
+        assert len(r.output) == 24
+        ids = torch.tensor(r.prompt + r.output)
+        with torch.no_grad():
+            h = model(ids, SeqInfo.from_lengths([len(ids)], torch.device("cpu")))
+            lp = torch.log_softmax(h.float() @ model.output_weight.float().t(), -1)
+        for i, tok in enumerate(r.output):
+            t = len(r.prompt) - 1 + i
+            assert int(lp[t].argmax()) == tok and abs(float(lp[t, tok]) - r.logprobs[i]) < 1e-3
+    assert eng.cache.blocks.num_available == 9
