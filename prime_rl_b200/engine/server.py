@@ -95,6 +95,11 @@ def build_app(engine: Engine, model_name: str, tokenizer=None, liveness_timeout:
             f"vllm:prefix_cache_queries_total {m['prefix_queries']}", f"vllm:request_success_total {m['requests']}",
             f"prime_rl:policy_version {m['policy_version']}",
         ]
+        # counters that exist once the engine has used the path: K / V swaps of preempted requests, imports from a
+        # prefill engine, prompts shared by forking in the recurrent-state runner
+        for key in ("kv_swap_outs", "kv_swap_ins", "kv_imports", "prefill_forks"):
+            if key in m:
+                lines.append(f"prime_rl:{key}_total {m[key]}")
         return PlainTextResponse("\n".join(lines) + "\n")
 
     @app.post("/inference/v1/generate")
