@@ -317,6 +317,7 @@ class Engine:
     def _admit(self) -> list[Request]:
         """Moves waiting requests to running while pages and the prefill budget allow."""
         admitted, budget = [], self.max_prefill_tokens
+        seen: set = set()
         with self.lock:
             while self.waiting and len(self.running) + len(admitted) < self.max_running:
                 r = self.waiting[0]
@@ -334,13 +335,21 @@ class Engine:
                     continue
                 toks = r.all_tokens
                 need_pages = (len(toks) + self.cache.page_size) // self.cache.page_size + 1
-                if len(toks) > budget and admitted:
+                cost = len(toks)
+                if self._hybrid and r.mm is None and not r.params.prompt_logprobs:
+                    # a further sample of a prompt admitted in this round forks the first one's prefill: it costs no
+                    # prompt tokens and, until it diverges, one page of its own
+                    key = (r.cache_salt, tuple(toks))
+                    if key in seen:
+                        cost, need_pages = 0, 2
+                    seen.add(key)
+                if cost > budget and admitted:
                     break
                 if self.cache.blocks.num_available < need_pages and (self.running or admitted):
                     break
                 self.waiting.pop(0)
                 admitted.append(r)
-                budget -= len(toks)
+                budget -= cost
         return admitted
 
     def _preempt_one(self) -> bool:

@@ -721,3 +721,20 @@ def test_preemption_in_the_recurrent_state_runner_restarts_from_the_tokens():
             t = len(r.prompt) - 1 + i
             assert int(lp[t].argmax()) == tok and abs(float(lp[t, tok]) - r.logprobs[i]) < 1e-3
     assert eng.cache.blocks.num_available == 9
+
+
+def test_a_group_of_samples_is_admitted_as_one_prompt_in_the_recurrent_state_runner():
+    """Eight samples of a prompt longer than an eighth of the prefill budget: they are admitted together (the copies
+    cost no prompt tokens) and the prompt runs once."""
+    from prime_rl_b200.engine.engine import Request
+
+    arch = resolve_arch("tiny-qwen3.5-moe")
+    model = build_model(arch, device="cpu", dtype=torch.float32, seed=0).eval()
+    eng = Engine(model, num_pages=256, page_size=16, max_model_len=256, max_prefill_tokens=64)
+    prompt = torch.randint(0, arch.vocab_size, (40,), generator=torch.Generator().manual_seed(6)).tolist()
+    reqs = [eng.submit(Request(prompt=prompt, params=SamplingParams(max_tokens=3, temperature=1.0, seed=i))) for i in range(8)]
+    eng.step()
+    assert eng.stats["prompt_tokens"] == 40 and eng.stats["prefill_forks"] == 7
+    while any(r.finish_reason is None for r in reqs):
+        eng.step()
+    assert eng.stats["prompt_tokens"] == 40 and all(len(r.output) == 3 for r in reqs)
