@@ -72,6 +72,33 @@ def verify(model, out_dir: Path) -> None:
         raise SystemExit("the reloaded model computes different hidden states")
 
 
+def verify_engine(model, tokens: int = 8) -> float:
+    """The rollout engine on this model against the model's own forward: greedy samples of a few prompts must be the
+    arg-max of the forward over the finished sequences; returns the largest log-probability difference."""
+    from ..engine.engine import Engine
+    from ..engine.sampler import SamplingParams
+
+    arch = model.arch
+    model.eval()
+    eng = Engine(model, num_pages=256, page_size=16, max_model_len=256)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, arch.vocab_size, (n,), generator=g).tolist() for n in (19, 40, 6)]
+    out = eng.generate_sync(prompts, SamplingParams(max_tokens=tokens, temperature=0.0))
+    worst = 0.0
+    dev = next(model.parameters()).device
+    for p, r in zip(prompts, out):
+        ids = torch.tensor(p + r.output, device=dev)
+        with torch.no_grad():
+            h = model(ids, SeqInfo.from_lengths([len(ids)], dev))
+            lp = torch.log_softmax(h.float() @ model.output_weight.float().t(), -1)
+        for i, tok in enumerate(r.output):
+            t = len(p) - 1 + i
+            if int(lp[t].argmax()) != tok and model.output_weight.dtype == torch.float32:
+                raise SystemExit(f"the engine sampled token {tok} where the forward prefers {int(lp[t].argmax())}")
+            worst = max(worst, abs(float(lp[t, tok]) - r.logprobs[i]))
+    return worst
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--arch", required=True, help="a preset name or a local HF directory")
@@ -83,6 +110,8 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", default="float32", choices=["float32", "bfloat16"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--verify", action="store_true")
+    ap.add_argument("--verify-engine", action="store_true",
+                    help="also run the rollout engine on the model and compare its samples with the model's forward")
     args = ap.parse_args(argv)
     arch = shrink(resolve_arch(args.arch), args.layers, args.hidden, args.experts, args.vocab)
     model = build_model(arch, device="cpu", dtype=getattr(torch, args.dtype), seed=args.seed)
@@ -93,6 +122,8 @@ def main(argv=None) -> int:
     if args.verify:
         verify(model, out)
         print("round trip verified")
+    if args.verify_engine:
+        print(f"rollout engine verified: largest log-probability difference {verify_engine(model):.2e}")
     return 0
 
 
