@@ -23,7 +23,10 @@ def test_rl_launcher_runs_three_processes_to_completion(tmp_path, free_port):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:] + "".join(f"\n== {k}\n{v[-1500:]}" for k, v in logs.items())
     assert "trainer and orchestrator finished" in r.stdout
     orch, trainer = logs["orchestrator.log"], logs["trainer.log"]
-    assert all(f"step {s} |" in orch for s in range(8)) and "policy v6" in orch     # the weights of step 5 arrived
+    assert all(f"step {s} |" in orch for s in range(8))
+    import re
+
+    assert max(int(v) for v in re.findall(r"policy v(\d+)", orch)) >= 6            # the weights of step 5 (or later) arrived
     assert all(f"step {s} |" in trainer for s in range(8))
 
 
@@ -43,4 +46,7 @@ def test_rl_launcher_with_a_recurrent_state_family(tmp_path, free_port):
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     logs = {p.name: p.read_text() for p in tmp_path.rglob("*.log")}
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:] + "".join(f"\n== {k}\n{v[-1500:]}" for k, v in logs.items())
-    assert "policy v2" in logs["orchestrator.log"] and "step 3 |" in logs["trainer.log"]
+    import re
+
+    assert max(int(v) for v in re.findall(r"policy v(\d+)", logs["orchestrator.log"])) >= 2
+    assert "step 3 |" in logs["trainer.log"]
