@@ -299,8 +299,8 @@ class _FSDPGroup:
         self.flat_shard = sharded.flat_shard
         self.master = sharded.flat_shard.float().clone()
         self.grad_shard = sharded.grad_shard
-        self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev) if kind in ("adamw", "sgd") else None
-        self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev) if kind == "adamw" else None
+        self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev) if kind in ("adamw", "sgd", "muon") else None
+        self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev) if kind in ("adamw", "muon") else None
 
     sharded = True
 
@@ -342,8 +342,8 @@ class FlatOptimizer:
         self.kind = config.type
         self.step_count = 0
         if self.kind == "muon":
-            if fsdp is not None:
-                raise ValueError("Muon needs whole matrices: use model.zero_stage = 2 with it")
+            if fsdp is not None and not getattr(config, "distributed", True):
+                raise ValueError("Muon over sharded parameters (model.zero_stage = 3) needs optim.distributed = true")
             if not getattr(config, "distributed", True):
                 shard_group = expert_shard_group = None     # every rank keeps whole state and orthogonalises everything
         if fsdp is not None:
@@ -568,13 +568,22 @@ class FlatOptimizer:
         n, lo = grp.shard_len, grp.shard_rank * grp.shard_len
         world, rank = grp.shard_n, grp.shard_rank
         dev = grp.master.device
+        by_unit = isinstance(grp, _FSDPGroup)         # ZeRO-3: the rank's slice is one piece per layer unit
+
+        def my_slice(full: torch.Tensor) -> torch.Tensor:
+            if not by_unit:
+                return full[lo:lo + n].clone()
+            out = torch.empty(n, dtype=full.dtype, device=dev)
+            buf.scatter_full(full, out)
+            return out
+
         mask = getattr(grp, "_muon_mask", None)
         if mask is None:
-            full = torch.zeros(buf.numel, dtype=torch.bool, device=dev)
+            full = torch.zeros(buf.numel, dtype=torch.float32, device=dev)
             for s in buf.slots:
                 if self._is_muon_matrix(s):
-                    full[s.offset:s.offset + s.numel] = True
-            mask = grp._muon_mask = full[lo:lo + n].clone()
+                    full[s.offset:s.offset + s.numel] = 1.0
+            mask = grp._muon_mask = my_slice(full) > 0
         g = grp.grad_shard * coef
         m, v, p = grp.exp_avg, grp.exp_avg_sq, grp.master
         b1, b2 = c.betas1, c.betas2
@@ -598,11 +607,11 @@ class FlatOptimizer:
                                             * self._muon_scale(c, s.shape))
                 owned += 1
         self.muon_owned = owned
-        mine = torch.empty(n, dtype=upd.dtype, device=dev)
-        if _backend(grp.shard_group) == "gloo":
+        if by_unit or _backend(grp.shard_group) == "gloo":
             dist.all_reduce(upd, group=grp.shard_group)
-            mine.copy_(upd[lo:lo + n])
+            mine = my_slice(upd)
         else:
+            mine = torch.empty(n, dtype=upd.dtype, device=dev)
             dist.reduce_scatter_tensor(mine, upd, op=dist.ReduceOp.SUM, group=grp.shard_group)
         denom = v.sqrt() / math.sqrt(1 - b2 ** t) + 1e-8
         adam = m / denom / (1 - b1 ** t)

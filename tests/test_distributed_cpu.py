@@ -160,11 +160,20 @@ def test_muon_with_the_orthogonalisations_dealt_out_matches_every_rank_doing_all
     gathered, every matrix is orthogonalised by one rank and the updates return through a reduce-scatter; the weights
     and the losses must be those of the run where both ranks keep whole state and orthogonalise everything."""
     runs = {}
-    for i, distributed in enumerate((False, True)):
+    for i, distributed in enumerate((False, True, "zero3")):
         cfg = json.loads(json.dumps(BASE))
         cfg["model"]["name"] = "tiny-qwen3-moe"
-        cfg["optim"] = {"type": "muon", "lr": 1e-3, "max_norm": 1.0, "distributed": distributed}
+        cfg["optim"] = {"type": "muon", "lr": 1e-3, "max_norm": 1.0, "distributed": bool(distributed)}
+        if distributed == "zero3":
+            cfg["model"]["zero_stage"] = 3          # parameters sharded per layer as well: the slices are per layer unit
         runs[distributed] = _run(tmp_path, free_port + i, 2, cfg)
+    for r in range(2):
+        for other in (True, "zero3"):
+            a, b = runs[False][r], runs[other][r]
+            assert a["wsum"] == pytest.approx(b["wsum"], rel=1e-6, abs=1e-7)
+            for x, y in zip(a["steps"], b["steps"]):
+                assert x[0] == pytest.approx(y[0], rel=1e-5, abs=1e-7)
+    assert runs["zero3"][0]["fsdp"] is not None
     for r in range(2):
         a, b = runs[False][r], runs[True][r]
         assert a["wsum"] == pytest.approx(b["wsum"], rel=1e-6, abs=1e-7)
