@@ -3,4 +3,4 @@
 from .config import PRESETS, ModelArch, resolve_arch  # noqa: F401
 from .layers import SeqInfo  # noqa: F401
 from .model import (CausalLM, apply_fp8_training, apply_lora, build_model, freeze_router,  # noqa: F401
-                    setup_quantization)
+                    check_context_parallel, setup_quantization)

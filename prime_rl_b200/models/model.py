@@ -211,6 +211,15 @@ def apply_fp8_training(model: CausalLM, ignore_patterns: list[str] | None = None
     return done
 
 
+def check_context_parallel(arch, cp: int, cp_style: str) -> None:
+    """Families with recurrent mixers split heads instead of the sequence around convolution and scan, which needs
+    contiguous chunks per rank: ``cp_style = "ulysses"``."""
+    recurrent = ("mamba" in (arch.block_types or [])) or ("gated_delta_net" in (arch.mixer_types or []))
+    if cp > 1 and recurrent and cp_style != "ulysses":
+        raise ValueError(f"model type '{arch.model_type}' has recurrent mixers: context parallelism needs "
+                         f"model.cp_style = 'ulysses' (got '{cp_style}')")
+
+
 def setup_quantization(model: CausalLM, mc, logger=None) -> list[str]:
     """``model.quantization`` of the trainer config: fp8 = block-scaled e4m3 (1 x 128 activation groups, 128 x 128
     weight blocks) for the forward products and input gradients of the projections outside ``ignore_patterns``. The

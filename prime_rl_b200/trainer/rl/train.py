@@ -179,7 +179,10 @@ class RLTrainer:
         self.dp_rank, self.cp_rank = coords["dp"], coords["cp"]
         self.cp_ctx = None
         if dims.cp_enabled:
+            from ...models import check_context_parallel
             from ...parallel.cp import ContextParallel
+
+            check_context_parallel(self.arch, dims.cp, self.config.model.cp_style)
 
             self.cp_ctx = ContextParallel(dims.group("cp"), dims.cp, self.cp_rank, style=self.config.model.cp_style,
                                           fused_kv_gather=self.config.model.cp_kv_exchange == "p2p",

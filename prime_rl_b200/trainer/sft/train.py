@@ -62,7 +62,10 @@ class SFTTrainer:
         # context parallelism: the ranks of one replica read the same rows and each runs its chunk of every row
         self.cp_ctx, self.dp_rank, self.dp_size, self.cp_rank = None, self.world.rank, self.world.world_size, 0
         if d.cp_enabled:
+            from ...models import check_context_parallel
             from ...parallel.cp import ContextParallel
+
+            check_context_parallel(self.arch, d.cp, mc.cp_style)
 
             coords = d.coords(self.world.rank)
             self.dp_rank, self.cp_rank = coords["dp"], coords["cp"]
