@@ -19,6 +19,7 @@ import torch
 import torch.distributed as dist
 
 from ...models import convert
+from ...utils.logger import get_logger
 from . import WeightSender
 
 
@@ -78,8 +79,15 @@ class NCCLWeightSender(WeightSender):
                     torch.cuda.set_device(device)
                 self.pg, self.store = _new_group(self.config.host, self.config.port, 0,
                                                  self.config.inference_world_size + 1, self.config.timeout, device)
-            except BaseException as e:       # surfaced by the first broadcast
+            except BaseException as e:
+                # The engines are (or will be) waiting in the same rendezvous and the orchestrator behind them, so no
+                # batch would ever reach this trainer: end the main thread now instead of at a first broadcast that
+                # never comes. The launcher sees the exit and takes the run down.
                 self._connect_error = e
+                get_logger().error(f"the weight-broadcast group could not be formed: {type(e).__name__}: {e}")
+                import _thread
+
+                _thread.interrupt_main()
 
         self._connecting = threading.Thread(target=run, name="weight-broadcast-connect", daemon=True)
         self._connecting.start()

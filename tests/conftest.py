@@ -31,3 +31,22 @@ def free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         return s.getsockname()[1]
+
+
+@pytest.fixture
+def free_ports():
+    """``free_ports(n)``: n distinct ports that were free when asked (every one is bound once to find it; a neighbour
+    of a free port is not known to be free)."""
+    import socket
+
+    def take(n: int) -> list[int]:
+        socks = [socket.socket() for _ in range(n)]
+        try:
+            for s in socks:
+                s.bind(("127.0.0.1", 0))
+            return [s.getsockname()[1] for s in socks]
+        finally:
+            for s in socks:
+                s.close()
+
+    return take

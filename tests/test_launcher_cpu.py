@@ -13,11 +13,12 @@ ROOT = Path(__file__).resolve().parents[1]
 
 
 @pytest.mark.slow
-def test_rl_launcher_runs_three_processes_to_completion(tmp_path, free_port):
+def test_rl_launcher_runs_three_processes_to_completion(tmp_path, free_ports):
+    free_port, broadcast_port = free_ports(2)
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=str(ROOT))
     cmd = [sys.executable, "-m", "prime_rl_b200.entrypoints.rl", "@", str(ROOT / "examples" / "rl.toml"),
            "--output-dir", str(tmp_path), "--max-steps", "8", "--inference.server.port", str(free_port),
-           "--weight-broadcast.type", "nccl", "--weight-broadcast.port", str(free_port + 7)]
+           "--weight-broadcast.type", "nccl", "--weight-broadcast.port", str(broadcast_port)]
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     logs = {p.name: p.read_text() for p in tmp_path.rglob("*.log")}
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:] + "".join(f"\n== {k}\n{v[-1500:]}" for k, v in logs.items())
@@ -31,18 +32,16 @@ def test_rl_launcher_runs_three_processes_to_completion(tmp_path, free_port):
 
 
 @pytest.mark.slow
-def test_rl_launcher_with_a_recurrent_state_family(tmp_path, free_port):
+def test_rl_launcher_with_a_recurrent_state_family(tmp_path, free_ports):
     """Nemotron-H (Mamba-2 + attention + MoE blocks) through the same three processes: the engine serves it with the
     recurrent-state runner and takes the in-memory weight updates, whose layer groups follow the family's checkpoint
     naming (``backbone.layers``)."""
-    toml = (ROOT / "examples" / "rl_low_token.toml").read_text().replace(
-        'id = "low-token"', 'id = "low-token"\nargs = { vocab_size = 512 }')
-    cfg = tmp_path / "rl.toml"
-    cfg.write_text(toml)
+    cfg = ROOT / "examples" / "rl_hybrid.toml"
+    free_port, broadcast_port = free_ports(2)
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=str(ROOT))
     cmd = [sys.executable, "-m", "prime_rl_b200.entrypoints.rl", "@", str(cfg), "--output-dir", str(tmp_path / "out"),
-           "--max-steps", "4", "--model.name", "tiny-nemotron-h", "--inference.server.port", str(free_port),
-           "--weight-broadcast.type", "nccl", "--weight-broadcast.port", str(free_port + 7)]
+           "--max-steps", "4", "--inference.server.port", str(free_port),
+           "--weight-broadcast.type", "nccl", "--weight-broadcast.port", str(broadcast_port)]
     r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     logs = {p.name: p.read_text() for p in tmp_path.rglob("*.log")}
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:] + "".join(f"\n== {k}\n{v[-1500:]}" for k, v in logs.items())
