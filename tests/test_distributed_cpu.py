@@ -38,7 +38,18 @@ if dist.is_initialized():
 """
 
 
+
+def _fresh_port() -> int:
+    """A port that is free now (a neighbour of a free port is not known to be free)."""
+    import socket
+
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        return sock.getsockname()[1]
+
+
 def _run(tmp_path, port, world, cfg):
+    port = _fresh_port()
     tag = (f"{world}_{cfg['model'].get('ep', 1)}_{cfg['model'].get('cp', 1)}_{cfg['model'].get('cp_style', 'ring')}"
            f"_z{cfg['model'].get('zero_stage', 2)}_{'ac' if cfg['model'].get('ac') else 'noac'}"
            f"_{cfg.get('optim', {}).get('type', 'adamw')}{int(bool(cfg.get('optim', {}).get('distributed', True)))}")
@@ -233,6 +244,7 @@ if dist.is_initialized():
 
 
 def _run_sft(tmp_path, port, world, cfg, tag):
+    port = _fresh_port()
     script = tmp_path / f"sft_{tag}.py"
     out = tmp_path / f"sft_out_{tag}"
     out.mkdir()
